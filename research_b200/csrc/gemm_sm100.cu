@@ -1,0 +1,613 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   C[M,N] = op(A) * op(B)^T   (fp32 accumulate in TMEM, bf16 or fp32 output)
+//
+// One persistent CTA per SM. Warp roles:
+//   warp 0   : TMA producer (one elected lane) - 128B-swizzled tiles into a multi-stage ring
+//   warp 1   : TMEM allocator + tcgen05.mma issuer (one elected lane)
+//   warps 2-5: epilogue - tcgen05.ld from TMEM, bias / residual / cast, global or peer stores
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main
+// loop of tile i+1.
+//
+// Operand majorness: a "K-major" operand is stored [rows, K] with K contiguous (x @ W^T with
+// torch Linear weights); an "MN-major" operand is stored [K, rows] with rows contiguous.
+// Both are fed by TMA with the 128-byte swizzle and described to the MMA by shared-memory
+// descriptors, so forward, dgrad (B MN-major) and wgrad (A and B MN-major) use one kernel.
+//
+// Peer-partitioned operands: the rows of A (or of B) may be split into `parts` equal slabs,
+// each behind its own tensor map. With the maps pointing at other GPUs' symmetric buffers the
+// producer warp pulls remote tiles over NVLink tile by tile while the tensor cores work on
+// the previous ones: this is the all-gather -> GEMM path (A split: tensor-parallel sequence
+// shards; B split: FSDP parameter shards). Only plain tile loads are used for this; no load
+// that broadcasts to several CTAs exists in this file.
+//
+// Reduce epilogues: in EPI_REDUCE_SCATTER / EPI_ALL_REDUCE mode each finished tile is pushed
+// with peer stores into the owner GPU's staging slab and published with a release flag; the
+// owner's epilogue warps then sum the P partial tiles (their own memory, local reads) and
+// write the result (all-reduce: to every peer). This is the GEMM -> reduce-scatter path.
+#include "common.cuh"
+#include "gemm_sm100.h"
+
+#include <mutex>
+#include <stdio.h>
+
+namespace rb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int NUM_ACC = 2;
+constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 4;
+// MN-major 128B-swizzled tiles: 64-element chunks are BK*128 bytes apart (leading offset),
+// groups of 8 K-rows are 1024 bytes apart (stride offset).
+#ifndef RB_MN_LBO
+#define RB_MN_LBO (BK * 128)
+#define RB_MN_SBO 1024
+#endif
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = (BN >= 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kTmemCols = (NUM_ACC * BN < 32) ? 32 : NUM_ACC * BN;
+};
+
+struct GemmParams {
+  CUtensorMap a_map[RB_MAX_PARTS];
+  CUtensorMap b_map[RB_MAX_PARTS];
+  int M, N, K;            // logical problem (M, N are totals over all parts)
+  int a_parts, b_parts;   // row slabs of A / B, one tensor map each
+  int a_rows_per_part, b_rows_per_part;
+  void* C;                // [M, ldc] bf16 (or fp32 when out_f32)
+  long long ldc;
+  const __nv_bfloat16* bias;      // [N] or null
+  const __nv_bfloat16* residual;  // [M, ldr] or null
+  long long ldr;
+  int out_f32;
+  int epi_mode;           // RB_EPI_*
+  // readiness flags for peer-partitioned operands: flag[p] >= epoch before part p is read
+  const int* a_ready;
+  const int* b_ready;
+  int ready_epoch;
+  // reduce epilogue
+  int rank, world;
+  void* stage_ptrs[RB_MAX_PARTS];   // peer r's staging base: [world][rows_per_rank][N] bf16
+  int* flag_ptrs[RB_MAX_PARTS];     // peer r's flags: [world][tiles_per_rank]
+  void* out_ptrs[RB_MAX_PARTS];     // all-reduce: peer r's output [M, ldc]; RS: out_ptrs[rank]
+  int reduce_epoch;
+  int* status;
+};
+
+__device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
+                                                    long long row, int col, int ncols) {
+  // v holds 32 fp32 values for (row, col..col+31); ncols valid (multiple of 8).
+  if (p.out_f32) {
+    float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (j < ncols) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (j < ncols) {
+        uint4 o;
+        o.x = pack_bf16x2(v[j], v[j + 1]);
+        o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+        o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+        o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+        *reinterpret_cast<uint4*>(dst + j) = o;
+      }
+    }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar[NUM_ACC];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[NUM_ACC];
+  __shared__ __align__(8) uint64_t epi_bar;  // bounded stand-in for a named barrier
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const int m_tiles_per_part = (p.a_rows_per_part + BM - 1) / BM;
+  const int n_tiles_per_part = (p.b_rows_per_part + BN - 1) / BN;
+  const int num_m_tiles = m_tiles_per_part * p.a_parts;
+  const int num_n_tiles = n_tiles_per_part * p.b_parts;
+  const int num_tiles = num_m_tiles * num_n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), EPI_WARPS);
+    }
+    mbar_init(smem_u32(&epi_bar), EPI_WARPS * 32);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  volatile int* abortp = &abort_flag;
+
+  // Tile order. In reduce modes, rank r visits the row slab owned by rank r+1 first and its
+  // own slab last so that every owner finds its partials early.
+  auto tile_coords = [&](int t, int& m_part, int& m_in, int& n_part, int& n_in) {
+    int mt = t % num_m_tiles;
+    int nt = t / num_m_tiles;
+    if (p.epi_mode != RB_EPI_STORE && p.world > 1) {
+      // rotate the slab index
+      int slab = mt / m_tiles_per_part;
+      int within = mt % m_tiles_per_part;
+      slab = (slab + p.rank + 1) % p.a_parts;
+      mt = slab * m_tiles_per_part + within;
+    }
+    m_part = mt / m_tiles_per_part;
+    m_in = (mt % m_tiles_per_part) * BM;
+    n_part = nt / n_tiles_per_part;
+    n_in = (nt % n_tiles_per_part) * BN;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    if (elect_one_sync()) {
+      uint32_t it = 0;
+      bool ok = true;
+      uint32_t a_seen = 0, b_seen = 0;  // bitmask of parts whose readiness was confirmed
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m_part, m_in, n_part, n_in;
+        tile_coords(t, m_part, m_in, n_part, n_in);
+        if (p.a_ready != nullptr && !((a_seen >> m_part) & 1u)) {
+          ok = wait_flag_ge(p.a_ready + m_part, p.ready_epoch, p.status);
+          if (!ok) { *abortp = 1; break; }
+          a_seen |= 1u << m_part;
+        }
+        if (p.b_ready != nullptr && !((b_seen >> n_part) & 1u)) {
+          ok = wait_flag_ge(p.b_ready + n_part, p.ready_epoch, p.status);
+          if (!ok) { *abortp = 1; break; }
+          b_seen |= 1u << n_part;
+        }
+        const CUtensorMap* amap = &p.a_map[m_part];
+        const CUtensorMap* bmap = &p.b_map[n_part];
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abortp, p.status,
+                                 ST_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          const uint32_t sa = smem_base + s * Cfg::kStageBytes;
+          const uint32_t sb = sa + Cfg::kABytes;
+          mbar_expect_tx(fb, Cfg::kStageBytes);
+          if (!A_MN) {
+            tma_load_2d(sa, amap, fb, kb * BK, m_in);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), amap, fb, m_in + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, bmap, fb, kb * BK, n_in);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), bmap, fb, n_in + c * 64, kb * BK);
+          }
+        }
+      }
+      // Drain: never leave the CTA with bulk copies still landing in its shared memory.
+      if (!ok) {
+        const uint32_t issued = it;
+        const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+        for (uint32_t j = first; j < issued; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&full_bar[j % STAGES]), (j / STAGES) & 1u)) {
+            if (globaltimer_ns() - t0 > 50000000ull) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------------------
+    if (elect_one_sync()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+        const int acc = tile_iter % NUM_ACC;
+        const uint32_t acc_ph = (tile_iter / NUM_ACC) & 1u;
+        ok = mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1u, abortp, p.status,
+                               ST_TIMEOUT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status,
+                                 ST_TIMEOUT_SMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * Cfg::kStageBytes;
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(sa + k * 2048, RB_MN_LBO, RB_MN_SBO)
+                                        : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * 2048, RB_MN_LBO, RB_MN_SBO)
+                                        : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps ----------------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    uint32_t epi_phase = 0;
+    // Barrier over the 128 epilogue threads whose wait is bounded: if some thread has left
+    // the loop after a timeout, the others give up too instead of hanging.
+    auto epi_sync = [&]() -> bool {
+      mbar_arrive(smem_u32(&epi_bar));
+      bool r = mbar_wait_bounded(smem_u32(&epi_bar), epi_phase, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      epi_phase ^= 1u;
+      return r;
+    };
+    const int rows_per_rank = p.a_rows_per_part;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      int m_part, m_in, n_part, n_in;
+      tile_coords(t, m_part, m_in, n_part, n_in);
+      const int acc = tile_iter % NUM_ACC;
+      const uint32_t acc_ph = (tile_iter / NUM_ACC) & 1u;
+      ok = mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_ph, abortp, p.status,
+                             ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const int row_in = m_in + q * 32 + lane;                 // row inside the A slab
+      const bool row_ok = row_in < p.a_rows_per_part;
+      const long long row = (long long)m_part * p.a_rows_per_part + row_in;
+      const int n_base = n_part * p.b_rows_per_part + n_in;    // global column
+      const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int ncols = min(32, n_valid - c0);
+        if (row_ok && ncols > 0) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          const int col = n_base + c0;
+          if (p.epi_mode == RB_EPI_STORE) {
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (j < ncols) {
+                  uint4 b = *reinterpret_cast<const uint4*>(p.bias + col + j);
+                  float2 f;
+                  f = unpack_bf16x2(b.x); v[j] += f.x; v[j + 1] += f.y;
+                  f = unpack_bf16x2(b.y); v[j + 2] += f.x; v[j + 3] += f.y;
+                  f = unpack_bf16x2(b.z); v[j + 4] += f.x; v[j + 5] += f.y;
+                  f = unpack_bf16x2(b.w); v[j + 6] += f.x; v[j + 7] += f.y;
+                }
+              }
+            }
+            if (p.residual != nullptr) {
+              const __nv_bfloat16* rp = p.residual + row * p.ldr + col;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (j < ncols) {
+                  uint4 b = *reinterpret_cast<const uint4*>(rp + j);
+                  float2 f;
+                  f = unpack_bf16x2(b.x); v[j] += f.x; v[j + 1] += f.y;
+                  f = unpack_bf16x2(b.y); v[j + 2] += f.x; v[j + 3] += f.y;
+                  f = unpack_bf16x2(b.z); v[j + 4] += f.x; v[j + 5] += f.y;
+                  f = unpack_bf16x2(b.w); v[j + 6] += f.x; v[j + 7] += f.y;
+                }
+              }
+            }
+            epi_store_row_chunk(p, v, row, col, ncols);
+          } else {
+            // push the bf16 partial into the owner's staging slab [src_rank][row_in][N]
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.stage_ptrs[m_part]) +
+                                 ((long long)p.rank * rows_per_rank + row_in) * p.N + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (j < ncols) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = o;
+              }
+            }
+          }
+        }
+      }
+      // accumulator drained: hand the TMEM buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+      if (p.epi_mode != RB_EPI_STORE) {
+        // publish the tile: all 4 epilogue warps must have finished their peer stores
+        __threadfence_system();
+        ok = epi_sync();
+        if (!ok) break;
+        if (warp == 2 && lane == 0) {
+          const int tile_in_part = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
+          int* f = p.flag_ptrs[m_part] + (long long)p.rank * (m_tiles_per_part * num_n_tiles) + tile_in_part;
+          st_release_sys(f, p.reduce_epoch);
+        }
+      }
+    }
+
+    // ---------------- reduce phase: sum the P partials of the tiles this rank owns ----------
+    if (p.epi_mode != RB_EPI_STORE && ok) {
+      const int tiles_owned = m_tiles_per_part * num_n_tiles;
+      const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.stage_ptrs[p.rank]);
+      const int* flags = p.flag_ptrs[p.rank];
+      const int et = (warp - 2) * 32 + lane;  // 0..127
+      for (int ot = blockIdx.x; ot < tiles_owned && ok; ot += gridDim.x) {
+        const int mt = ot / num_n_tiles, nt = ot % num_n_tiles;
+        // wait for every source rank's copy of this tile
+        if (et < p.world) {
+          if (!wait_flag_ge(flags + (long long)et * tiles_owned + ot, p.reduce_epoch, p.status)) *abortp = 1;
+        }
+        ok = epi_sync();
+        if (!ok || *abortp) { ok = false; break; }
+        const int n_part = nt / n_tiles_per_part;
+        const int n0 = n_part * p.b_rows_per_part + (nt % n_tiles_per_part) * BN;
+        const int n_valid = min(BN, p.b_rows_per_part - (nt % n_tiles_per_part) * BN);
+        const int m0 = mt * BM;
+        const int vec_per_row = n_valid / 8;
+        const int rows = min(BM, rows_per_rank - m0);
+        for (int idx = et; idx < rows * vec_per_row; idx += 128) {
+          const int rr = idx / vec_per_row, cc = (idx % vec_per_row) * 8;
+          const int row_in = m0 + rr;
+          const int col = n0 + cc;
+          float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int src = 0; src < p.world; ++src) {
+            uint4 b = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * rows_per_rank + row_in) * p.N + col));
+            float2 f;
+            f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
+            f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
+            f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
+            f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
+          }
+          const long long grow = (long long)p.rank * rows_per_rank + row_in;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+          }
+          if (p.residual != nullptr) {
+            // reduce-scatter: residual is the local row slab; all-reduce: the full matrix
+            const long long rrow = (p.epi_mode == RB_EPI_REDUCE_SCATTER) ? row_in : grow;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.residual[rrow * p.ldr + col + j]);
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc8[0], acc8[1]);
+          o.y = pack_bf16x2(acc8[2], acc8[3]);
+          o.z = pack_bf16x2(acc8[4], acc8[5]);
+          o.w = pack_bf16x2(acc8[6], acc8[7]);
+          if (p.epi_mode == RB_EPI_REDUCE_SCATTER) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[p.rank]);
+            *reinterpret_cast<uint4*>(out + (long long)row_in * p.ldc + col) = o;
+          } else {
+            for (int d = 0; d < p.world; ++d) {
+              __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[d]);
+              *reinterpret_cast<uint4*>(out + grow * p.ldc + col) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown --------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------- host side ------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+    }
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map over `rows` x `cols` (cols contiguous, leading dimension ld elements),
+// box = box_rows x 64 columns, 128-byte swizzle.
+static int make_map_2d(CUtensorMap* out, const void* base, long long rows, long long cols,
+                       long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return -2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  const int m_tiles = ((p.a_rows_per_part + BM - 1) / BM) * p.a_parts;
+  const int n_tiles = ((p.b_rows_per_part + BN - 1) / BN) * p.b_parts;
+  int grid = m_tiles * n_tiles;
+  int cap = num_sms();
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  kern<<<grid, GEMM_THREADS, Cfg::kSmemBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <int BN>
+static int launch_bn(const GemmParams& p, int a_mn, int b_mn, int max_ctas, cudaStream_t s) {
+  if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(p, max_ctas, s);
+  if constexpr (BN >= 64) {
+    if (!a_mn && b_mn) return launch_cfg<BN, false, true>(p, max_ctas, s);
+    if (a_mn && b_mn) return launch_cfg<BN, true, true>(p, max_ctas, s);
+  }
+  if (a_mn && !b_mn) return launch_cfg<BN, true, false>(p, max_ctas, s);
+  return -12;
+}
+
+static int pick_bn(int m_tiles, int n_rows_per_part, int parts, int b_mn) {
+  const int sms = num_sms();
+  const int cands[4] = {256, 128, 64, 32};
+  int best = b_mn ? 64 : 32;
+  for (int i = 0; i < 4; ++i) {
+    int bn = cands[i];
+    if (b_mn && bn < 64) continue;
+    int tiles = m_tiles * ((n_rows_per_part + bn - 1) / bn) * parts;
+    if (tiles >= sms) return bn;
+  }
+  return best;
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
+  if (a == nullptr) return -1;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return -1;
+  if (a->a_parts < 1 || a->a_parts > RB_MAX_PARTS || a->b_parts < 1 || a->b_parts > RB_MAX_PARTS) return -1;
+  if (a->M % a->a_parts != 0 || a->N % a->b_parts != 0) return -1;
+  if (a->N % 8 != 0 || a->K % 8 != 0) return -1;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.a_parts = a->a_parts; p.b_parts = a->b_parts;
+  p.a_rows_per_part = a->M / a->a_parts;
+  p.b_rows_per_part = a->N / a->b_parts;
+  if (p.b_rows_per_part % 8 != 0) return -1;
+  p.C = a->C; p.ldc = a->ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  p.ldr = a->ldr;
+  p.out_f32 = a->out_f32;
+  p.epi_mode = a->epi_mode;
+  p.a_ready = a->a_ready; p.b_ready = a->b_ready; p.ready_epoch = a->ready_epoch;
+  p.rank = a->rank; p.world = a->world < 1 ? 1 : a->world;
+  p.reduce_epoch = a->reduce_epoch;
+  p.status = a->status;
+  if (p.epi_mode != RB_EPI_STORE) {
+    if (a->a_parts != p.world || a->out_f32) return -1;
+    if (p.a_rows_per_part % 8 != 0) return -1;
+    for (int r = 0; r < p.world; ++r) {
+      p.stage_ptrs[r] = a->stage_ptrs[r];
+      p.flag_ptrs[r] = a->flag_ptrs[r];
+      p.out_ptrs[r] = a->out_ptrs[r];
+    }
+  }
+  const int m_tiles = ((p.a_rows_per_part + BM - 1) / BM) * p.a_parts;
+  int bn = a->bn;
+  if (bn == 0) bn = pick_bn(m_tiles, p.b_rows_per_part, p.b_parts, a->b_mn_major);
+  if (a->b_mn_major && bn < 64) bn = 64;
+  // tensor maps: one per slab
+  for (int i = 0; i < p.a_parts; ++i) {
+    int rc = a->a_mn_major
+                 ? make_map_2d(&p.a_map[i], a->A[i], a->K, p.a_rows_per_part, a->lda, BK)
+                 : make_map_2d(&p.a_map[i], a->A[i], p.a_rows_per_part, a->K, a->lda, BM);
+    if (rc != 0) return -20 + rc;
+  }
+  for (int i = 0; i < p.b_parts; ++i) {
+    int rc = a->b_mn_major
+                 ? make_map_2d(&p.b_map[i], a->B[i], a->K, p.b_rows_per_part, a->ldb, BK)
+                 : make_map_2d(&p.b_map[i], a->B[i], p.b_rows_per_part, a->K, a->ldb, bn);
+    if (rc != 0) return -30 + rc;
+  }
+  switch (bn) {
+    case 32: return launch_bn<32>(p, a->a_mn_major, a->b_mn_major, a->max_ctas, stream);
+    case 64: return launch_bn<64>(p, a->a_mn_major, a->b_mn_major, a->max_ctas, stream);
+    case 128: return launch_bn<128>(p, a->a_mn_major, a->b_mn_major, a->max_ctas, stream);
+    case 256: return launch_bn<256>(p, a->a_mn_major, a->b_mn_major, a->max_ctas, stream);
+    default: return -13;
+  }
+}
+
+// Plain single-GPU form: C = A * B^T (+bias) (+residual).
+extern "C" int rb_gemm_bf16(const void* A, const void* B, void* C, const void* bias,
+                            const void* residual, int M, int N, int K, long long lda,
+                            long long ldb, long long ldc, long long ldr, int a_mn_major,
+                            int b_mn_major, int out_f32, int bn, int* status,
+                            cudaStream_t stream) {
+  RbGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.A[0] = A; a.B[0] = B; a.C = C; a.bias = bias; a.residual = residual;
+  a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldb = ldb; a.ldc = ldc; a.ldr = ldr;
+  a.a_parts = 1; a.b_parts = 1;
+  a.a_mn_major = a_mn_major; a.b_mn_major = b_mn_major; a.out_f32 = out_f32; a.bn = bn;
+  a.epi_mode = RB_EPI_STORE; a.world = 1; a.status = status;
+  return rb_gemm_bf16_ex(&a, stream);
+}

@@ -1,0 +1,51 @@
+// C ABI of the sm_100a bf16 GEMM (tcgen05 / TMEM / TMA). Mirrored field by field by the
+// ctypes structure in research_b200/ops/gemm.py.
+#pragma once
+#include <cuda_runtime.h>
+
+#define RB_MAX_PARTS 8
+
+// epilogue modes
+#define RB_EPI_STORE 0            // C = acc (+bias) (+residual), local store
+#define RB_EPI_REDUCE_SCATTER 1   // sum over ranks, rank r keeps row slab r
+#define RB_EPI_ALL_REDUCE 2       // sum over ranks, every rank receives all rows
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct RbGemmArgs {
+  const void* A[RB_MAX_PARTS];   // row slab i of A (may be another GPU's memory)
+  const void* B[RB_MAX_PARTS];   // row slab i of B (may be another GPU's memory)
+  void* C;
+  const void* bias;              // bf16 [N] or NULL
+  const void* residual;          // bf16 [M, ldr] or NULL
+  long long lda, ldb, ldc, ldr;  // leading dimensions in elements
+  int M, N, K;
+  int a_parts, b_parts;
+  int a_mn_major, b_mn_major;
+  int out_f32;
+  int bn;                        // 0 = choose; else 32/64/128/256
+  int max_ctas;                  // 0 = one per SM
+  int epi_mode;
+  int rank, world;
+  const int* a_ready;            // optional [a_parts] flags, waited for >= ready_epoch
+  const int* b_ready;            // optional [b_parts]
+  int ready_epoch;
+  int reduce_epoch;
+  void* stage_ptrs[RB_MAX_PARTS];
+  int* flag_ptrs[RB_MAX_PARTS];
+  void* out_ptrs[RB_MAX_PARTS];
+  int* status;                   // device int, 0 = ok, else rb::StatusCode
+} RbGemmArgs;
+
+int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);
+
+int rb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual,
+                 int M, int N, int K, long long lda, long long ldb, long long ldc, long long ldr,
+                 int a_mn_major, int b_mn_major, int out_f32, int bn, int* status,
+                 cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

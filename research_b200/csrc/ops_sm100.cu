@@ -1,0 +1,446 @@
+// Memory-bound transformer ops for sm_100a: RMSNorm (row and per-head), RoPE fused with the
+// paged KV-cache append, SwiGLU, embedding gather, seeded sampling with log-probabilities.
+// All kernels are single-pass over HBM with 16-byte accesses; rounding points follow the
+// bf16 Hugging Face modules (see the functional oracles in research_b200/models/functional.py)
+// so that greedy decoding matches the fp32/bf16 reference token for token.
+#include "common.cuh"
+
+namespace rb {
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm: y = bf16( bf16(x * rsqrt(mean(x^2)+eps)) * w ). One warp per row.
+// Reference math: rollouts/tools/functional_extractor/qwen_functional.py:46-65.
+// ------------------------------------------------------------------------------------------
+__global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                               __nv_bfloat16* __restrict__ y, long long rows, int d, long long ldx,
+                               long long ldy, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * ldx;
+  __nv_bfloat16* yr = y + row * ldy;
+  const int nvec = d >> 3;
+  float ss = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    uint4 u = *reinterpret_cast<const uint4*>(xr + v * 8);
+    float2 f;
+    f = unpack_bf16x2(u.x); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(u.y); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(u.z); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(u.w); ss += f.x * f.x + f.y * f.y;
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)d + eps);
+  for (int v = lane; v < nvec; v += 32) {
+    uint4 u = *reinterpret_cast<const uint4*>(xr + v * 8);
+    uint4 ww = *reinterpret_cast<const uint4*>(w + v * 8);
+    uint32_t xi[4] = {u.x, u.y, u.z, u.w};
+    uint32_t wi[4] = {ww.x, ww.y, ww.z, ww.w};
+    uint32_t oi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16x2(xi[j]);
+      float2 g = unpack_bf16x2(wi[j]);
+      // round the normalised value to bf16 before the weight multiply, like the HF module
+      float a = __bfloat162float(__float2bfloat16_rn(f.x * rstd));
+      float b = __bfloat162float(__float2bfloat16_rn(f.y * rstd));
+      oi[j] = pack_bf16x2(a * g.x, b * g.y);
+    }
+    *reinterpret_cast<uint4*>(yr + v * 8) = make_uint4(oi[0], oi[1], oi[2], oi[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// RoPE (rotate_half convention) + optional per-head QK RMSNorm + paged KV append.
+//   qkv   : [T, (Hq + 2*Hkv) * D] bf16  (q heads, then k heads, then v heads)
+//   q_out : [T, Hq * D] bf16 (rotated)
+//   k_cache / v_cache : [num_blocks, Hkv, block_size, D] bf16, slot = block*block_size + off
+//   cos_sin : [max_pos, D/2] float2
+// One warp per (token, head). Slots < 0 are skipped (padding rows of a captured graph).
+// Reference math: qwen_functional.py:68-150; cache store: inference/attention/flex_backend.py:116-142.
+// ------------------------------------------------------------------------------------------
+template <int D>
+__global__ void rope_kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                      const int* __restrict__ positions, const int* __restrict__ slots,
+                                      const float2* __restrict__ cos_sin, const __nv_bfloat16* __restrict__ q_norm_w,
+                                      const __nv_bfloat16* __restrict__ k_norm_w, float norm_eps, int T, int Hq,
+                                      int Hkv, int block_size, long long num_slots, int max_pos, int* status) {
+  constexpr int HALF = D / 2;
+  constexpr int PER_LANE = HALF / 32;  // pairs handled per lane: D=64 -> 1, D=128 -> 2
+  const int lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = Hq + 2 * Hkv;
+  if (gw >= (long long)T * heads) return;
+  const int t = (int)(gw / heads);
+  const int h = (int)(gw % heads);
+  const __nv_bfloat16* src = qkv + (long long)t * heads * D + (long long)h * D;
+  int pos = positions[t];
+  const int slot = slots[t];
+  if (pos < 0) pos = 0;
+  if (pos >= max_pos) { set_status(status, ST_BAD_INDEX); pos = max_pos - 1; }
+
+  float lo[PER_LANE], hi[PER_LANE];
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    lo[j] = __bfloat162float(src[lane + 32 * j]);
+    hi[j] = __bfloat162float(src[lane + 32 * j + HALF]);
+  }
+  __nv_bfloat16* dst;
+  bool is_v = h >= Hq + Hkv;
+  if (h < Hq) {
+    dst = q_out + (long long)t * Hq * D + (long long)h * D;
+  } else {
+    if (slot < 0) return;
+    if (slot >= num_slots) { set_status(status, ST_BAD_INDEX); return; }
+    const int kvh = is_v ? h - Hq - Hkv : h - Hq;
+    const long long blk = slot / block_size, off = slot % block_size;
+    __nv_bfloat16* cache = is_v ? v_cache : k_cache;
+    dst = cache + ((blk * Hkv + kvh) * block_size + off) * D;
+  }
+  if (is_v) {
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      dst[lane + 32 * j] = __float2bfloat16_rn(lo[j]);
+      dst[lane + 32 * j + HALF] = __float2bfloat16_rn(hi[j]);
+    }
+    return;
+  }
+  const __nv_bfloat16* nw = (h < Hq) ? q_norm_w : k_norm_w;
+  if (nw != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + norm_eps);
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      float a = __bfloat162float(__float2bfloat16_rn(lo[j] * rstd));
+      float b = __bfloat162float(__float2bfloat16_rn(hi[j] * rstd));
+      lo[j] = __bfloat162float(__float2bfloat16_rn(a * __bfloat162float(nw[lane + 32 * j])));
+      hi[j] = __bfloat162float(__float2bfloat16_rn(b * __bfloat162float(nw[lane + 32 * j + HALF])));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const float2 cs = cos_sin[(long long)pos * HALF + lane + 32 * j];
+    // bf16 rounding of cos/sin and of each product mirrors q*cos + rotate_half(q)*sin in bf16
+    const float c = __bfloat162float(__float2bfloat16_rn(cs.x));
+    const float s = __bfloat162float(__float2bfloat16_rn(cs.y));
+    const float a = __bfloat162float(__float2bfloat16_rn(lo[j] * c));
+    const float b = __bfloat162float(__float2bfloat16_rn(-hi[j] * s));
+    const float e = __bfloat162float(__float2bfloat16_rn(hi[j] * c));
+    const float f = __bfloat162float(__float2bfloat16_rn(lo[j] * s));
+    dst[lane + 32 * j] = __float2bfloat16_rn(a + b);
+    dst[lane + 32 * j + HALF] = __float2bfloat16_rn(e + f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// SwiGLU: out = bf16( bf16(silu(gate)) * up ), gate|up packed as [T, 2F].
+// Reference math: qwen_functional.py:251-274.
+// ------------------------------------------------------------------------------------------
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                              long long T, int F) {
+  const long long nvec = T * (F >> 3);
+  const int fv = F >> 3;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / fv;
+    const int c = (int)(i % fv) * 8;
+    uint4 g = *reinterpret_cast<const uint4*>(gu + t * 2 * F + c);
+    uint4 u = *reinterpret_cast<const uint4*>(gu + t * 2 * F + F + c);
+    uint32_t gi[4] = {g.x, g.y, g.z, g.w}, ui[4] = {u.x, u.y, u.z, u.w}, oi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = unpack_bf16x2(gi[j]);
+      float2 b = unpack_bf16x2(ui[j]);
+      float s0 = __bfloat162float(__float2bfloat16_rn(a.x / (1.f + __expf(-a.x))));
+      float s1 = __bfloat162float(__float2bfloat16_rn(a.y / (1.f + __expf(-a.y))));
+      oi[j] = pack_bf16x2(s0 * b.x, s1 * b.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * F + c) = make_uint4(oi[0], oi[1], oi[2], oi[3]);
+  }
+}
+
+// SwiGLU backward: given gate|up [T,2F] and dout [T,F] writes dgate|dup [T,2F].
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dout,
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int F) {
+  const long long n = T * F;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / F;
+    const int c = (int)(i % F);
+    const float g = __bfloat162float(gu[t * 2 * F + c]);
+    const float u = __bfloat162float(gu[t * 2 * F + F + c]);
+    const float dy = __bfloat162float(dout[i]);
+    const float sig = 1.f / (1.f + __expf(-g));
+    const float silu = g * sig;
+    dgu[t * 2 * F + c] = __float2bfloat16_rn(dy * u * (sig + silu * (1.f - sig)));
+    dgu[t * 2 * F + F + c] = __float2bfloat16_rn(dy * silu);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Embedding gather: out[t, :] = table[ids[t], :]
+// ------------------------------------------------------------------------------------------
+__global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int T, int d, int vocab, int* status) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) { if (threadIdx.x == 0) set_status(status, ST_BAD_INDEX); id = 0; }
+  const uint4* src = reinterpret_cast<const uint4*>(table + (long long)id * d);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * d);
+  for (int v = threadIdx.x; v < (d >> 3); v += blockDim.x) dst[v] = src[v];
+}
+
+// ------------------------------------------------------------------------------------------
+// Sampling with log-probabilities, one CTA per row of fp32 logits [B, V].
+//   token  ~ softmax(logits / T)   via the Gumbel-max trick with a counter-based RNG
+//            (temperature == 0 -> argmax)
+//   logprob = log_softmax(logits)[token]  from the UNSCALED logits (true policy probability)
+// Reference behaviour: rollouts/inference/sampling.py:10-58.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mix32(uint64_t z) {
+  // splitmix64 finaliser, counter-based so every (seed, row, column) gets its own stream
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z = z ^ (z >> 31);
+  return (uint32_t)(z >> 32);
+}
+
+constexpr int SAMPLE_THREADS = 512;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
+                      const float* __restrict__ temperature, const unsigned long long* __restrict__ seeds,
+                      const unsigned long long* __restrict__ step_ptr, unsigned long long step_add,
+                      int* __restrict__ out_tokens, float* __restrict__ out_logprobs) {
+  // The step counter lives in device memory so a captured CUDA graph draws fresh noise on
+  // every replay (the host bumps the counter between replays).
+  const unsigned long long step = step_add + (step_ptr != nullptr ? *step_ptr : 0ull);
+  const int row = blockIdx.x;
+  const float* lr = logits + (long long)row * ld;
+  const float temp = temperature[row];
+  const bool greedy = temp <= 0.f;
+  const float inv_t = greedy ? 1.f : 1.f / temp;
+  const uint64_t key = seeds[row] * 0xD1342543DE82EF95ull + step * 0x9E3779B97F4A7C15ull;
+
+  float m = -INFINITY, ssum = 0.f;     // online log-sum-exp of the unscaled logits
+  float best = -INFINITY;              // best perturbed score
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x * 4; i < V; i += SAMPLE_THREADS * 4) {
+    float v[4];
+    if (i + 3 < V && ((ld & 3) == 0)) {
+      float4 f = *reinterpret_cast<const float4*>(lr + i);
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = (i + j < V) ? lr[i + j] : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (i + j >= V) continue;
+      const float x = v[j];
+      if (x > m) { ssum = ssum * __expf(m - x) + 1.f; m = x; } else { ssum += __expf(x - m); }
+      float score = x * inv_t;
+      if (!greedy) {
+        const uint32_t r = mix32(key ^ ((uint64_t)(uint32_t)(i + j) * 0xA24BAED4963EE407ull));
+        const float u = ((float)(r >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
+        score += -__logf(-__logf(u));
+      }
+      if (score > best || (score == best && i + j < best_i)) { best = score; best_i = i + j; }
+    }
+  }
+  // block reduction
+  __shared__ float sm_m[SAMPLE_THREADS / 32], sm_s[SAMPLE_THREADS / 32], sm_b[SAMPLE_THREADS / 32];
+  __shared__ int sm_i[SAMPLE_THREADS / 32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+    const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+    const float mn = fmaxf(m, m2);
+    ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + s2 * __expf(m2 - mn);
+    m = mn;
+    if (b2 > best || (b2 == best && i2 < best_i)) { best = b2; best_i = i2; }
+  }
+  if (lane == 0) { sm_m[wid] = m; sm_s[wid] = ssum; sm_b[wid] = best; sm_i[wid] = best_i; }
+  __syncthreads();
+  if (wid == 0) {
+    constexpr int NW = SAMPLE_THREADS / 32;
+    m = lane < NW ? sm_m[lane] : -INFINITY;
+    ssum = lane < NW ? sm_s[lane] : 0.f;
+    best = lane < NW ? sm_b[lane] : -INFINITY;
+    best_i = lane < NW ? sm_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+      const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+      const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+      const float mn = fmaxf(m, m2);
+      ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + s2 * __expf(m2 - mn);
+      m = mn;
+      if (b2 > best || (b2 == best && i2 < best_i)) { best = b2; best_i = i2; }
+    }
+    if (lane == 0) {
+      if (best_i >= V) best_i = 0;
+      out_tokens[row] = best_i;
+      out_logprobs[row] = lr[best_i] - (m + __logf(ssum));
+    }
+  }
+}
+
+// Per-token log-probability of given tokens from fp32 logits (teacher forcing / verification).
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+token_logprob_kernel(const float* __restrict__ logits, long long ld, int V, const int* __restrict__ tokens,
+                     float* __restrict__ out_logprobs) {
+  const int row = blockIdx.x;
+  const float* lr = logits + (long long)row * ld;
+  float m = -INFINITY, ssum = 0.f;
+  for (int i = threadIdx.x; i < V; i += SAMPLE_THREADS) {
+    const float x = lr[i];
+    if (x > m) { ssum = ssum * __expf(m - x) + 1.f; m = x; } else { ssum += __expf(x - m); }
+  }
+  __shared__ float sm_m[SAMPLE_THREADS / 32], sm_s[SAMPLE_THREADS / 32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+    const float mn = fmaxf(m, m2);
+    ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + s2 * __expf(m2 - mn);
+    m = mn;
+  }
+  if (lane == 0) { sm_m[wid] = m; sm_s[wid] = ssum; }
+  __syncthreads();
+  if (wid == 0) {
+    constexpr int NW = SAMPLE_THREADS / 32;
+    m = lane < NW ? sm_m[lane] : -INFINITY;
+    ssum = lane < NW ? sm_s[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+      const float s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+      const float mn = fmaxf(m, m2);
+      ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + s2 * __expf(m2 - mn);
+      m = mn;
+    }
+    if (lane == 0) {
+      int tok = tokens[row];
+      if (tok < 0 || tok >= V) tok = 0;
+      out_logprobs[row] = lr[tok] - (m + __logf(ssum));
+    }
+  }
+}
+
+// bf16 2-D transpose (used by the training path when an operand must change majorness).
+__global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                      int rows, int cols) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  int x = blockIdx.x * 32 + threadIdx.x;
+  int y0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int y = y0 + j;
+    if (x < cols && y < rows) tile[j][threadIdx.x] = in[(long long)y * cols + x];
+  }
+  __syncthreads();
+  int ox = blockIdx.y * 32 + threadIdx.x;
+  int oy0 = blockIdx.x * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int oy = oy0 + j;
+    if (ox < rows && oy < cols) out[(long long)oy * rows + ox] = tile[threadIdx.x][j];
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+#define RB_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+
+extern "C" int rb_rmsnorm(const void* x, const void* w, void* y, long long rows, int d, long long ldx,
+                          long long ldy, float eps, cudaStream_t stream) {
+  if (d % 8 != 0 || rows <= 0) return -1;
+  const int warps = 8;
+  const long long grid = (rows + warps - 1) / warps;
+  rmsnorm_kernel<<<(unsigned)grid, warps * 32, 0, stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, d, ldx, ldy, eps);
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_rope_kv_append(const void* qkv, void* q_out, void* k_cache, void* v_cache,
+                                 const int* positions, const int* slots, const void* cos_sin,
+                                 const void* q_norm_w, const void* k_norm_w, float norm_eps, int T, int Hq,
+                                 int Hkv, int D, int block_size, long long num_slots, int max_pos,
+                                 int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long long warps_total = (long long)T * (Hq + 2 * Hkv);
+  const int warps = 8;
+  const unsigned grid = (unsigned)((warps_total + warps - 1) / warps);
+#define LAUNCH_ROPE(DD)                                                                              \
+  rope_kv_append_kernel<DD><<<grid, warps * 32, 0, stream>>>(                                         \
+      (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
+      positions, slots, (const float2*)cos_sin, (const __nv_bfloat16*)q_norm_w,                       \
+      (const __nv_bfloat16*)k_norm_w, norm_eps, T, Hq, Hkv, block_size, num_slots, max_pos, status)
+  if (D == 64) { LAUNCH_ROPE(64); }
+  else if (D == 128) { LAUNCH_ROPE(128); }
+  else return -1;
+#undef LAUNCH_ROPE
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_swiglu(const void* gu, void* out, long long T, int F, cudaStream_t stream) {
+  if (F % 8 != 0 || T <= 0) return -1;
+  const long long nvec = T * (F / 8);
+  long long grid = (nvec + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  swiglu_kernel<<<(unsigned)grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F);
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int F,
+                             cudaStream_t stream) {
+  const long long n = T * F;
+  long long grid = (n + 255) / 256;
+  if (grid > 148 * 32) grid = 148 * 32;
+  swiglu_bwd_kernel<<<(unsigned)grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dout,
+                                                       (__nv_bfloat16*)dgu, T, F);
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_embedding(const int* ids, const void* table, void* out, int T, int d, int vocab,
+                            int* status, cudaStream_t stream) {
+  if (d % 8 != 0 || T <= 0) return -1;
+  embedding_kernel<<<T, 128, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, d, vocab, status);
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_sample_logprob(const float* logits, long long ld, int B, int V, const float* temperature,
+                                 const unsigned long long* seeds, const unsigned long long* step_ptr,
+                                 unsigned long long step_add, int* out_tokens, float* out_logprobs,
+                                 cudaStream_t stream) {
+  if (B <= 0) return 0;
+  sample_logprob_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, seeds, step_ptr, step_add,
+                                                          out_tokens, out_logprobs);
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_token_logprob(const float* logits, long long ld, int B, int V, const int* tokens,
+                                float* out_logprobs, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  token_logprob_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, tokens, out_logprobs);
+  return RB_CHECK_LAUNCH();
+}
+
+extern "C" int rb_transpose_bf16(const void* in, void* out, int rows, int cols, cudaStream_t stream) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+  dim3 block(32, 8);
+  transpose_bf16_kernel<<<grid, block, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, cols);
+  return RB_CHECK_LAUNCH();
+}

@@ -1,0 +1,146 @@
+"""bf16 GEMM on tcgen05 tensor cores (see csrc/gemm_sm100.cu) and its PyTorch reference.
+
+Replaces the cuBLAS ``F.linear`` calls inside the HF modules the reference runs
+(rollouts/inference/engine.py:231, training/backends/pytorch.py:186).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ._util import check_rc, ptr, status_tensor, stream_handle
+
+RB_MAX_PARTS = 8
+EPI_STORE, EPI_REDUCE_SCATTER, EPI_ALL_REDUCE = 0, 1, 2
+
+
+class RbGemmArgs(ctypes.Structure):
+    """Mirror of ``RbGemmArgs`` in csrc/gemm_sm100.h (field order matters)."""
+
+    _fields_ = [
+        ("A", ctypes.c_void_p * RB_MAX_PARTS),
+        ("B", ctypes.c_void_p * RB_MAX_PARTS),
+        ("C", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p),
+        ("residual", ctypes.c_void_p),
+        ("lda", ctypes.c_longlong),
+        ("ldb", ctypes.c_longlong),
+        ("ldc", ctypes.c_longlong),
+        ("ldr", ctypes.c_longlong),
+        ("M", ctypes.c_int),
+        ("N", ctypes.c_int),
+        ("K", ctypes.c_int),
+        ("a_parts", ctypes.c_int),
+        ("b_parts", ctypes.c_int),
+        ("a_mn_major", ctypes.c_int),
+        ("b_mn_major", ctypes.c_int),
+        ("out_f32", ctypes.c_int),
+        ("bn", ctypes.c_int),
+        ("max_ctas", ctypes.c_int),
+        ("epi_mode", ctypes.c_int),
+        ("rank", ctypes.c_int),
+        ("world", ctypes.c_int),
+        ("a_ready", ctypes.c_void_p),
+        ("b_ready", ctypes.c_void_p),
+        ("ready_epoch", ctypes.c_int),
+        ("reduce_epoch", ctypes.c_int),
+        ("stage_ptrs", ctypes.c_void_p * RB_MAX_PARTS),
+        ("flag_ptrs", ctypes.c_void_p * RB_MAX_PARTS),
+        ("out_ptrs", ctypes.c_void_p * RB_MAX_PARTS),
+        ("status", ctypes.c_void_p),
+    ]
+
+
+def _lib() -> ctypes.CDLL:
+    lib = _native.load("rb_gemm")
+    if not getattr(lib, "_rb_typed", False):
+        lib.rb_gemm_bf16_ex.argtypes = [ctypes.POINTER(RbGemmArgs), ctypes.c_void_p]
+        lib.rb_gemm_bf16_ex.restype = ctypes.c_int
+        lib._rb_typed = True
+    return lib
+
+
+def gemm_reference(a, b, bias=None, residual=None, a_mn_major=False, b_mn_major=False, out_dtype=None):
+    """fp32 PyTorch reference: ``op(a) @ op(b).T`` (+bias) (+residual)."""
+    af = a.float().t() if a_mn_major else a.float()
+    bf = b.float().t() if b_mn_major else b.float()
+    c = af @ bf.t()
+    if bias is not None:
+        c = c + bias.float()
+    if residual is not None:
+        c = c + residual.float()
+    return c.to(out_dtype or a.dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    *,
+    a_mn_major: bool = False,
+    b_mn_major: bool = False,
+    out_f32: bool = False,
+    bn: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``C[M,N] = op(A) @ op(B)^T (+bias) (+residual)``.
+
+    K-major operands are ``[rows, K]`` row-major (a torch ``Linear`` weight is a K-major B);
+    MN-major operands are ``[K, rows]`` row-major. On CUDA this launches the tcgen05 kernel;
+    on CPU it evaluates the fp32 reference (used as the oracle in tests).
+    """
+    if not a.is_cuda:
+        return gemm_reference(a, b, bias, residual, a_mn_major, b_mn_major, torch.float32 if out_f32 else None)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1, "operands must be contiguous in their last dim"
+    if a_mn_major:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn_major:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"K mismatch: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    assert out.stride(1) == 1
+    args = RbGemmArgs()
+    args.A[0] = a.data_ptr()
+    args.B[0] = b.data_ptr()
+    args.C = out.data_ptr()
+    args.bias = bias.data_ptr() if bias is not None else None
+    args.residual = residual.data_ptr() if residual is not None else None
+    args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), out.stride(0)
+    args.ldr = residual.stride(0) if residual is not None else 0
+    args.M, args.N, args.K = M, N, K
+    args.a_parts = args.b_parts = 1
+    args.a_mn_major, args.b_mn_major = int(a_mn_major), int(b_mn_major)
+    args.out_f32 = int(out_f32)
+    args.bn = bn
+    args.max_ctas = max_ctas
+    args.epi_mode = EPI_STORE
+    args.rank, args.world = 0, 1
+    args.status = status_tensor(a.device).data_ptr()
+    rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
+    check_rc(rc, "rb_gemm_bf16_ex")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=None, out_f32=False):
+    """``x @ weight.T`` for ``x`` of shape ``[..., K]`` and ``weight`` ``[N, K]``."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    r2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
+    y = gemm(x2, weight, bias, r2, out, out_f32=out_f32)
+    return y.reshape(*lead, weight.shape[0])
+
+
+__all__ = ["gemm", "gemm_reference", "linear", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
+_ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

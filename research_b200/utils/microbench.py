@@ -1,0 +1,115 @@
+"""Kernel micro-benchmarks with roofline fractions: ``python -m research_b200.utils.microbench``.
+
+Prints one JSON object per kernel/shape: device time (CUDA events, L2 flushed between
+iterations), achieved TFLOP/s or GB/s and the fraction of the measured peaks passed with
+``--peak-tflops`` / ``--peak-gbs``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from .. import ops
+from .timing import time_cuda
+
+
+def bench_gemm(M, N, K, peak_tflops, iters=10, **kw):
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    t = time_cuda(lambda: ops.gemm(a, b, out=out, **kw), iters=iters)
+    tl = time_cuda(lambda: torch.matmul(a, b.t(), out=out), iters=iters)
+    flops = 2.0 * M * N * K
+    byts = 2.0 * (M * K + N * K + M * N)
+    ach = flops / (t["median_ms"] * 1e-3) / 1e12
+    return {"kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, **kw, "ms": round(t["median_ms"], 4),
+            "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3),
+            "gbs": round(byts / (t["median_ms"] * 1e-3) / 1e9, 1),
+            "library_matmul_ms": round(tl["median_ms"], 4)}
+
+
+def bench_decode_attention(B, ctx, Hq, Hkv, D, peak_gbs, iters=10):
+    bs = 16
+    nblk = (ctx + bs - 1) // bs
+    total = B * nblk
+    kc = torch.randn(total, Hkv, bs, D, device="cuda").bfloat16()
+    vc = torch.randn(total, Hkv, bs, D, device="cuda").bfloat16()
+    bt = torch.randperm(total, device="cuda").to(torch.int32).reshape(B, nblk).contiguous()
+    sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    splits = ops.decode_num_splits(B, Hkv, ctx)
+    t = time_cuda(lambda: ops.paged_decode(q, kc, vc, bt, sl, num_splits=splits, out=out), iters=iters)
+    byts = 2.0 * B * ctx * Hkv * D * 2
+    ach = byts / (t["median_ms"] * 1e-3) / 1e9
+    return {"kernel": "paged_decode", "B": B, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "D": D, "splits": splits,
+            "ms": round(t["median_ms"], 4), "gbs": round(ach, 1), "frac_of_measured_peak": round(ach / peak_gbs, 3)}
+
+
+def bench_prefill_attention(B, n, Hq, Hkv, D, peak_tflops, iters=5):
+    bs = 16
+    nblk = (n + bs - 1) // bs
+    kc = torch.randn(B * nblk, Hkv, bs, D, device="cuda").bfloat16()
+    vc = torch.randn(B * nblk, Hkv, bs, D, device="cuda").bfloat16()
+    bt = torch.arange(B * nblk, device="cuda", dtype=torch.int32).reshape(B, nblk).contiguous()
+    cu = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
+    sl = torch.full((B,), n, dtype=torch.int32, device="cuda")
+    q = torch.randn(B * n, Hq, D, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    t = time_cuda(lambda: ops.paged_prefill(q, kc, vc, bt, cu, sl, n, out=out), iters=iters)
+    flops = 4.0 * B * Hq * D * n * n / 2
+    ach = flops / (t["median_ms"] * 1e-3) / 1e12
+    return {"kernel": "paged_prefill", "B": B, "n": n, "Hq": Hq, "Hkv": Hkv, "D": D, "ms": round(t["median_ms"], 4),
+            "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3)}
+
+
+def bench_rmsnorm(rows, d, peak_gbs):
+    x = torch.randn(rows, d, device="cuda").bfloat16()
+    w = torch.randn(d, device="cuda").bfloat16()
+    out = torch.empty_like(x)
+    t = time_cuda(lambda: ops.rmsnorm(x, w, 1e-6, out=out))
+    ach = 2.0 * rows * d * 2 / (t["median_ms"] * 1e-3) / 1e9
+    return {"kernel": "rmsnorm", "rows": rows, "d": d, "ms": round(t["median_ms"], 4), "gbs": round(ach, 1),
+            "frac_of_measured_peak": round(ach / peak_gbs, 3)}
+
+
+def bench_sampling(B, V, peak_gbs):
+    logits = torch.randn(B, V, device="cuda")
+    temps = torch.ones(B, device="cuda")
+    t = time_cuda(lambda: ops.sample_with_logprobs(logits, temps))
+    ach = B * V * 4.0 / (t["median_ms"] * 1e-3) / 1e9
+    return {"kernel": "sample_logprob", "B": B, "V": V, "ms": round(t["median_ms"], 4), "gbs": round(ach, 1),
+            "frac_of_measured_peak": round(ach / peak_gbs, 3)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--peak-tflops", type=float, default=1688.4)
+    ap.add_argument("--peak-gbs", type=float, default=6453.4)
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    rows = []
+    shapes = [(8192, 8192, 8192), (4096, 14336, 4096), (8192, 4096, 14336), (256, 1152, 896), (256, 9728, 896),
+              (256, 896, 4864), (256, 151936, 896)]
+    if args.quick:
+        shapes = shapes[:1] + shapes[3:5]
+    for M, N, K in shapes:
+        rows.append(bench_gemm(M, N, K, args.peak_tflops))
+    for bn in (128, 256):
+        rows.append(bench_gemm(8192, 8192, 8192, args.peak_tflops, bn=bn))
+    rows.append(bench_decode_attention(256, 832, 14, 2, 64, args.peak_gbs))
+    rows.append(bench_decode_attention(64, 2304, 32, 8, 128, args.peak_gbs))
+    rows.append(bench_decode_attention(4, 8192, 32, 8, 128, args.peak_gbs))
+    rows.append(bench_prefill_attention(8, 2048, 32, 8, 128, args.peak_tflops))
+    rows.append(bench_prefill_attention(16, 1024, 14, 2, 64, args.peak_tflops))
+    rows.append(bench_rmsnorm(16384, 4096, args.peak_gbs))
+    rows.append(bench_sampling(256, 151936, args.peak_gbs))
+    for r in rows:
+        print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()

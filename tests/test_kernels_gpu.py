@@ -1,0 +1,209 @@
+"""GPU numerics: every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+
+import math
+
+import pytest
+import torch
+
+from research_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, device, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(device)
+
+
+def _assert_close(got, want, atol, rtol, what=""):
+    got, want = got.float(), want.float()
+    err = (got - want).abs()
+    tol = atol + rtol * want.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad} of {err.numel()} off; max err {err.max().item():.4g}"
+
+
+# ------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize(
+    "M,N,K",
+    [(128, 128, 64), (256, 256, 256), (384, 1152, 896), (256, 896, 4864), (1000, 520, 328), (64, 4096, 4096),
+     (2048, 2048, 2048)],
+)
+@pytest.mark.parametrize("bn", [0, 32, 64, 128, 256])
+def test_gemm_tn(cuda_device, M, N, K, bn):
+    a = _rand((M, K), cuda_device, seed=1)
+    b = _rand((N, K), cuda_device, seed=2)
+    out = ops.gemm(a, b, bn=bn)
+    ref = ops.gemm_reference(a, b, out_dtype=torch.float32)
+    _assert_close(out, ref, atol=0.02 * math.sqrt(K), rtol=0.01, what=f"gemm {M}x{N}x{K} bn={bn}")
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (512, 896, 1152), (896, 4864, 512), (136, 264, 200)])
+def test_gemm_majorness(cuda_device, a_mn, b_mn, M, N, K):
+    a = _rand((K, M) if a_mn else (M, K), cuda_device, seed=3)
+    b = _rand((K, N) if b_mn else (N, K), cuda_device, seed=4)
+    out = ops.gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn)
+    ref = ops.gemm_reference(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out_dtype=torch.float32)
+    _assert_close(out, ref, atol=0.02 * math.sqrt(K), rtol=0.01, what=f"gemm mn {a_mn}{b_mn}")
+
+
+def test_gemm_epilogue_bias_residual_f32(cuda_device):
+    M, N, K = 300, 1152, 896
+    a = _rand((M, K), cuda_device, seed=5)
+    b = _rand((N, K), cuda_device, 0.05, seed=6)
+    bias = _rand((N,), cuda_device, seed=7)
+    res = _rand((M, N), cuda_device, seed=8)
+    out = ops.gemm(a, b, bias=bias, residual=res)
+    ref = ops.gemm_reference(a, b, bias, res, out_dtype=torch.float32)
+    _assert_close(out, ref, atol=0.05, rtol=0.01, what="bias+residual")
+    out32 = ops.gemm(a, b, out_f32=True)
+    assert out32.dtype == torch.float32
+    _assert_close(out32, ops.gemm_reference(a, b, out_dtype=torch.float32), atol=2e-3, rtol=1e-3, what="f32 out")
+    # in-place residual (x += proj) as the decoder uses it
+    x = res.clone()
+    ops.gemm(a, b, residual=x, out=x)
+    _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.05, rtol=0.01, what="inplace")
+
+
+def test_gemm_strided_views(cuda_device):
+    big = _rand((256, 2048), cuda_device, seed=9)
+    a = big[:, 512:1024]  # lda = 2048
+    b = _rand((640, 512), cuda_device, seed=10)
+    out = ops.gemm(a, b)
+    _assert_close(out, ops.gemm_reference(a, b, out_dtype=torch.float32), atol=0.5, rtol=0.01, what="strided")
+
+
+# ------------------------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("rows,d", [(7, 64), (300, 896), (33, 4096), (5, 128)])
+def test_rmsnorm(cuda_device, rows, d):
+    x = _rand((rows, d), cuda_device, 3.0, seed=11)
+    w = _rand((d,), cuda_device, seed=12)
+    got = ops.rmsnorm(x, w, 1e-6)
+    want = ops.rmsnorm_reference(x.cpu(), w.cpu(), 1e-6)
+    _assert_close(got.cpu(), want, atol=1e-2, rtol=1e-2, what="rmsnorm")
+    # bit-level agreement with the same rounding points on almost every element
+    exact = (got.cpu() == want).float().mean().item()
+    assert exact > 0.98, exact
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,qknorm", [(64, 14, 2, False), (128, 32, 8, False), (128, 32, 4, True)])
+def test_rope_kv_append(cuda_device, D, Hq, Hkv, qknorm):
+    T, nb, bs = 37, 12, 16
+    qkv = _rand((T, (Hq + 2 * Hkv) * D), cuda_device, seed=13)
+    pos = torch.randint(0, 500, (T,), dtype=torch.int32)
+    slots = torch.randperm(nb * bs)[:T].to(torch.int32)
+    slots[5] = -1
+    table = ops.rope_table(512, D, 1e4)
+    qn = _rand((D,), cuda_device, seed=14) if qknorm else None
+    kn = _rand((D,), cuda_device, seed=15) if qknorm else None
+    kc = torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16, device=cuda_device)
+    vc = torch.zeros_like(kc)
+    q = ops.rope_kv_append(qkv, pos.to(cuda_device), slots.to(cuda_device), table.to(cuda_device), kc, vc, Hq, Hkv, D, qn, kn)
+    kc_ref, vc_ref = torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16), torch.zeros(nb, Hkv, bs, D, dtype=torch.bfloat16)
+    q_ref = ops.rope_kv_append_reference(qkv.cpu(), pos, slots, table, kc_ref, vc_ref, Hq, Hkv, D,
+                                         qn.cpu() if qknorm else None, kn.cpu() if qknorm else None)
+    _assert_close(q.cpu(), q_ref, atol=2e-2, rtol=2e-2, what="rope q")
+    _assert_close(kc.cpu(), kc_ref, atol=2e-2, rtol=2e-2, what="k cache")
+    assert torch.equal(vc.cpu(), vc_ref)
+
+
+def test_swiglu_and_backward(cuda_device):
+    gu = _rand((130, 2 * 4864), cuda_device, 2.0, seed=16)
+    got = ops.swiglu(gu)
+    _assert_close(got.cpu(), ops.swiglu_reference(gu.cpu()), atol=2e-2, rtol=2e-2, what="swiglu")
+    dout = _rand((130, 4864), cuda_device, seed=17)
+    dgu = ops.swiglu_backward(gu, dout)
+    guf = gu.float().cpu().requires_grad_(True)
+    g, u = guf.chunk(2, -1)
+    (torch.nn.functional.silu(g) * u).backward(dout.float().cpu())
+    _assert_close(dgu.cpu(), guf.grad, atol=3e-2, rtol=2e-2, what="swiglu bwd")
+
+
+def test_embedding_transpose(cuda_device):
+    table = _rand((1000, 896), cuda_device, seed=18)
+    ids = torch.randint(0, 1000, (77,), dtype=torch.int32, device=cuda_device)
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    x = _rand((300, 520), cuda_device, seed=19)
+    assert torch.equal(ops.transpose(x), x.t().contiguous())
+
+
+# ------------------------------------------------------------------------------------ sampling
+def test_sampling_greedy_and_logprob(cuda_device):
+    B, V = 9, 151936
+    logits = torch.randn(B, V, device=cuda_device) * 3
+    temps = torch.zeros(B, device=cuda_device)
+    tok, lp = ops.sample_with_logprobs(logits, temps)
+    ref_lp = torch.log_softmax(logits, -1)
+    assert torch.equal(tok.long(), logits.argmax(-1))
+    _assert_close(lp, ref_lp.gather(-1, tok.long()[:, None]).squeeze(-1), atol=1e-4, rtol=1e-4, what="greedy lp")
+    tl = ops.token_logprobs(logits, tok)
+    _assert_close(tl, lp, atol=1e-4, rtol=1e-4, what="token_logprobs")
+
+
+def test_sampling_distribution_and_seeding(cuda_device):
+    V, B = 64, 4096
+    base = torch.randn(V, device=cuda_device) * 2
+    logits = base[None].repeat(B, 1).contiguous()
+    temps = torch.full((B,), 0.7, device=cuda_device)
+    seeds = torch.arange(B, dtype=torch.int64, device=cuda_device)
+    tok, lp = ops.sample_with_logprobs(logits, temps, seeds, step=3)
+    tok2, _ = ops.sample_with_logprobs(logits, temps, seeds, step=3)
+    assert torch.equal(tok, tok2), "same seed and step must reproduce"
+    tok3, _ = ops.sample_with_logprobs(logits, temps, seeds, step=4)
+    assert not torch.equal(tok, tok3)
+    # empirical distribution follows softmax(logits / T)
+    p = torch.softmax(base / 0.7, -1)
+    counts = torch.bincount(tok.long(), minlength=V).float() / B
+    assert (counts - p).abs().max().item() < 0.03
+    # logprob is of the unscaled logits
+    want = torch.log_softmax(base, -1)[tok.long()]
+    _assert_close(lp, want, atol=1e-4, rtol=1e-4, what="unscaled logprob")
+
+
+# ------------------------------------------------------------------------------------ attention
+def _make_paged(B, Hkv, D, lens, device, seed):
+    bs = 16
+    nblk = [(l + bs - 1) // bs for l in lens]
+    total = sum(nblk) + 3
+    perm = torch.randperm(total)
+    kc = _rand((total, Hkv, bs, D), device, seed=seed)
+    vc = _rand((total, Hkv, bs, D), device, seed=seed + 1)
+    max_blocks = max(nblk) + 2
+    bt = torch.zeros(B, max_blocks, dtype=torch.int32)
+    o = 0
+    for b in range(B):
+        bt[b, : nblk[b]] = perm[o : o + nblk[b]].to(torch.int32)
+        o += nblk[b]
+    return kc, vc, bt.to(device)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 14, 2), (128, 32, 8), (128, 32, 4)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_paged_decode(cuda_device, D, Hq, Hkv, splits):
+    lens = [1, 15, 16, 17, 100, 333, 1024, 777]
+    B = len(lens)
+    kc, vc, bt = _make_paged(B, Hkv, D, lens, cuda_device, seed=20)
+    q = _rand((B, Hq, D), cuda_device, seed=22)
+    sl = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    got = ops.paged_decode(q, kc, vc, bt, sl, num_splits=splits)
+    want = ops.paged_decode_reference(q, kc, vc, bt, sl)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.01 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 14, 2), (128, 32, 8)])
+@pytest.mark.parametrize("window", [0, 48])
+def test_paged_prefill(cuda_device, D, Hq, Hkv, window):
+    new = [5, 64, 65, 130, 1, 200]
+    prefix = [0, 16, 3, 100, 40, 0]
+    lens = [n + p for n, p in zip(new, prefix)]
+    B = len(lens)
+    kc, vc, bt = _make_paged(B, Hkv, D, lens, cuda_device, seed=30)
+    cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=cuda_device)
+    q = _rand((sum(new), Hq, D), cuda_device, seed=32)
+    sl = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    got = ops.paged_prefill(q, kc, vc, bt, cu, sl, max(new), window=window)
+    want = ops.paged_prefill_reference(q, kc, vc, bt, cu, sl, window=window)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.01 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
