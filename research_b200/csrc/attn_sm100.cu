@@ -133,7 +133,7 @@ __device__ __forceinline__ void softmax_update(float (&s0)[4], float (&s1)[4], R
 // Decode
 // ------------------------------------------------------------------------------------------
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_STAGES = 4;
+constexpr int DEC_STAGES = 3;  // 50 KB (D=64) / 100 KB (D=128) per CTA -> 4 / 2 CTAs per SM
 
 template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)

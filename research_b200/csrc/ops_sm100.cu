@@ -202,13 +202,20 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat1
 //   logprob = log_softmax(logits)[token]  from the UNSCALED logits (true policy probability)
 // Reference behaviour: rollouts/inference/sampling.py:10-58.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t mix32(uint64_t z) {
-  // splitmix64 finaliser, counter-based so every (seed, row, column) gets its own stream
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  // splitmix64 finaliser: turns (seed, step) into the per-row key once per CTA
   z += 0x9E3779B97F4A7C15ull;
   z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
   z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-  z = z ^ (z >> 31);
-  return (uint32_t)(z >> 32);
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ uint32_t hash32(uint32_t idx, uint32_t k0, uint32_t k1) {
+  // counter-based 32-bit mixer (murmur3 finaliser) - every (row key, column) has its own draw
+  uint32_t h = (idx * 0x9E3779B1u) ^ k0;
+  h ^= h >> 16; h *= 0x85EBCA6Bu;
+  h ^= h >> 13; h *= 0xC2B2AE35u;
+  h ^= h >> 16;
+  return h + k1;
 }
 
 constexpr int SAMPLE_THREADS = 512;
@@ -226,7 +233,8 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
   const float temp = temperature[row];
   const bool greedy = temp <= 0.f;
   const float inv_t = greedy ? 1.f : 1.f / temp;
-  const uint64_t key = seeds[row] * 0xD1342543DE82EF95ull + step * 0x9E3779B97F4A7C15ull;
+  const uint64_t key = mix64(mix64(seeds[row]) ^ (step * 0x9E3779B97F4A7C15ull));
+  const uint32_t k0 = (uint32_t)key, k1 = (uint32_t)(key >> 32);
 
   float m = -INFINITY, ssum = 0.f;     // online log-sum-exp of the unscaled logits
   float best = -INFINITY;              // best perturbed score
@@ -247,9 +255,10 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
       if (x > m) { ssum = ssum * __expf(m - x) + 1.f; m = x; } else { ssum += __expf(x - m); }
       float score = x * inv_t;
       if (!greedy) {
-        const uint32_t r = mix32(key ^ ((uint64_t)(uint32_t)(i + j) * 0xA24BAED4963EE407ull));
+        const uint32_t r = hash32((uint32_t)(i + j), k0, k1);
         const float u = ((float)(r >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
-        score += -__logf(-__logf(u));
+        // Gumbel noise -ln(-ln u) with two fast log2 (ln x = log2 x * ln 2)
+        score -= 0.6931471805599453f * __log2f(-0.6931471805599453f * __log2f(u));
       }
       if (score > best || (score == best && i + j < best_i)) { best = score; best_i = i + j; }
     }

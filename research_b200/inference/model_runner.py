@@ -1,0 +1,384 @@
+"""Kernel-backed execution of a decoder-only model over the paged KV cache.
+
+The runner owns the packed bf16 weights (fused QKV and gate|up matrices, laid out once and
+updated in place so captured CUDA graphs stay valid across weight syncs), the per-layer KV
+cache ``[L, num_blocks, Hkv, 16, D]``, the RoPE table, and the static buffers of the decode
+step. Two entry points:
+
+* ``prefill``: packed varlen batch of new tokens (eager launches);
+* ``decode``: one token per running sequence, replayed from a CUDA graph captured per batch
+  size bucket (the reference has no graph capture and no batching:
+  rollouts/inference/engine.py:218-246 runs ``model(input_ids)`` per sequence per token).
+
+Every GEMM goes through the tcgen05 kernel (csrc/gemm_sm100.cu); attention, RMSNorm, RoPE+KV
+append, SwiGLU and sampling are the kernels in csrc/attn_sm100.cu and csrc/ops_sm100.cu.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..models.config import ModelConfig
+
+BLOCK = 16
+
+
+@dataclass
+class StepBatch:
+    """Host-side description of one packed batch (views into pinned staging memory)."""
+
+    num_rows: int
+    num_tokens: int
+    max_new: int
+    max_blocks: int
+
+
+class LayerWeights:
+    __slots__ = ("ln1", "wqkv", "bqkv", "q_norm", "k_norm", "wo", "ln2", "wgu", "wd", "moe")
+
+
+class ModelRunner:
+    def __init__(self, cfg: ModelConfig, weights: dict[str, torch.Tensor], *, device: torch.device,
+                 num_kv_blocks: int, max_batch: int, max_model_len: int, max_prefill_tokens: int,
+                 use_cuda_graphs: bool = True, graph_batch_sizes: tuple[int, ...] = (), tp=None,
+                 dtype: torch.dtype = torch.bfloat16):
+        # On a CUDA device every op below is an sm_100a kernel. On CPU the same call sequence
+        # runs the PyTorch reference twins of the ops (fp32), which is how the scheduler,
+        # paged cache and radix reuse are exercised without a GPU.
+        self.on_gpu = device.type == "cuda"
+        if self.on_gpu:
+            assert cfg.head_dim in (64, 128), "attention kernels are built for head_dim 64 and 128"
+            assert dtype == torch.bfloat16, "the CUDA kernels are bf16"
+        assert max_batch % 2 == 0 and max_prefill_tokens % 2 == 0
+        use_cuda_graphs = use_cuda_graphs and self.on_gpu
+        self.cfg = cfg
+        self.device = device
+        self.tp = tp
+        self.tp_size = tp.world if tp is not None else 1
+        self.tp_rank = tp.rank if tp is not None else 0
+        assert cfg.num_heads % self.tp_size == 0 and cfg.num_kv_heads % self.tp_size == 0
+        self.Hq = cfg.num_heads // self.tp_size
+        self.Hkv = cfg.num_kv_heads // self.tp_size
+        self.D = cfg.head_dim
+        self.F = (cfg.intermediate_size // self.tp_size) if cfg.intermediate_size else 0
+        self.max_batch = max_batch
+        self.max_model_len = max_model_len
+        self.max_blocks_per_seq = (max_model_len + BLOCK - 1) // BLOCK
+        self.max_prefill_tokens = max_prefill_tokens
+        self.num_kv_blocks = num_kv_blocks
+        self.use_cuda_graphs = use_cuda_graphs
+        self.graph_batch_sizes = tuple(sorted(b for b in graph_batch_sizes if b <= max_batch)) or (max_batch,)
+        if self.graph_batch_sizes[-1] < max_batch:
+            self.graph_batch_sizes += (max_batch,)
+        self.scale = 1.0 / math.sqrt(self.D)
+        self.launches_per_decode_step = 0
+
+        bf = dtype
+        self.dtype = dtype
+        d, L = cfg.hidden_size, cfg.num_layers
+        self.embed = torch.empty(cfg.vocab_size, d, dtype=bf, device=device)
+        self.final_norm = torch.empty(d, dtype=bf, device=device)
+        self.lm_head = self.embed if cfg.tie_word_embeddings else torch.empty(cfg.vocab_size, d, dtype=bf, device=device)
+        self.layers: list[LayerWeights] = []
+        qkv_rows = (self.Hq + 2 * self.Hkv) * self.D
+        for i in range(L):
+            lw = LayerWeights()
+            lw.ln1 = torch.empty(d, dtype=bf, device=device)
+            lw.ln2 = torch.empty(d, dtype=bf, device=device)
+            lw.wqkv = torch.empty(qkv_rows, d, dtype=bf, device=device)
+            lw.bqkv = torch.empty(qkv_rows, dtype=bf, device=device) if cfg.attention_bias else None
+            lw.q_norm = torch.empty(self.D, dtype=bf, device=device) if cfg.qk_norm else None
+            lw.k_norm = torch.empty(self.D, dtype=bf, device=device) if cfg.qk_norm else None
+            lw.wo = torch.empty(d, self.Hq * self.D, dtype=bf, device=device)
+            lw.moe = None
+            if cfg.is_moe and i >= cfg.first_k_dense_replace:
+                from ..parallel.moe import MoELayerWeights
+
+                lw.wgu = lw.wd = None
+                lw.moe = MoELayerWeights(cfg, device, ep=tp if getattr(tp, "expert_parallel", False) else None)
+            else:
+                lw.wgu = torch.empty(2 * self.F, d, dtype=bf, device=device)
+                lw.wd = torch.empty(d, self.F, dtype=bf, device=device)
+            self.layers.append(lw)
+        self.load_weights(weights)
+
+        # KV cache and RoPE table
+        self.k_cache = torch.zeros(L, num_kv_blocks, self.Hkv, BLOCK, self.D, dtype=bf, device=device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.rope = ops.rope_table(max_model_len, self.D, cfg.rope_theta, device=device)
+
+        # ---- static decode buffers (graph inputs/outputs) ----
+        mb = max_batch
+        # one int32 staging vector: tokens | positions | slots | seq_lens | temps | seeds(lo,hi)
+        self.meta_fields = 7
+        self.meta_dev = torch.zeros(self.meta_fields * mb, dtype=torch.int32, device=device)
+        self.meta_host = self._pinned(torch.zeros(self.meta_fields * mb, dtype=torch.int32))
+        self.bt_dev = torch.zeros(mb, self.max_blocks_per_seq, dtype=torch.int32, device=device)
+        self.bt_host = self._pinned(torch.zeros(mb, self.max_blocks_per_seq, dtype=torch.int32))
+        self.out_dev = torch.zeros(2 * mb, dtype=torch.int32, device=device)
+        self.out_host = self._pinned(torch.zeros(2 * mb, dtype=torch.int32))
+        m = self.meta_dev
+        self.d_tokens, self.d_pos, self.d_slots, self.d_lens = m[0:mb], m[mb:2 * mb], m[2 * mb:3 * mb], m[3 * mb:4 * mb]
+        self.d_temps = m[4 * mb:5 * mb].view(torch.float32)
+        self.d_seeds = m[5 * mb:7 * mb].view(torch.int64)
+        self.d_out_tokens = self.out_dev[0:mb]
+        self.d_out_logprobs = self.out_dev[mb:2 * mb].view(torch.float32)
+        # activations for decode
+        self.a_x = torch.empty(mb, d, dtype=bf, device=device)
+        self.a_h = torch.empty(mb, d, dtype=bf, device=device)
+        self.a_qkv = torch.empty(mb, qkv_rows, dtype=bf, device=device)
+        self.a_q = torch.empty(mb, self.Hq * self.D, dtype=bf, device=device)
+        self.a_attn = torch.empty(mb, self.Hq * self.D, dtype=bf, device=device)
+        self.a_gu = torch.empty(mb, 2 * self.F, dtype=bf, device=device) if self.F else None
+        self.a_act = torch.empty(mb, self.F, dtype=bf, device=device) if self.F else None
+        self.a_logits = torch.empty(mb, cfg.vocab_size, dtype=torch.float32, device=device)
+        # split-KV partials for small batches (up to 64 rows x 32 splits)
+        self.dec_ws = torch.empty(min(mb, 64) * self.Hq * 32 * (self.D + 2), dtype=torch.float32, device=device)
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.graph_pool = None
+
+        # prefill staging (pinned): tokens | positions | slots | cu_q | seq_lens | sample_rows | temps | seeds
+        T = max_prefill_tokens
+        self.pf_host = self._pinned(torch.zeros(3 * T + 6 * (mb + 1), dtype=torch.int32))
+        self.pf_dev = torch.zeros_like(self.pf_host, device=device)
+
+    def _pinned(self, t: torch.Tensor) -> torch.Tensor:
+        return t.pin_memory() if self.on_gpu else t
+
+    # ------------------------------------------------------------------ weights
+    def _shard_rows(self, w: torch.Tensor, parts: int, idx: int) -> torch.Tensor:
+        n = w.shape[0] // parts
+        return w[idx * n:(idx + 1) * n]
+
+    def load_weights(self, weights: dict[str, torch.Tensor]) -> None:
+        """Copy HF-named tensors into the packed device buffers (in place)."""
+        cfg, tp, r = self.cfg, self.tp_size, self.tp_rank
+        dev = self.device
+
+        def put(dst: torch.Tensor, src: torch.Tensor) -> None:
+            dst.copy_(src.to(device=dev, dtype=dst.dtype, non_blocking=True))
+
+        put(self.embed, weights["model.embed_tokens.weight"])
+        put(self.final_norm, weights["model.norm.weight"])
+        if not cfg.tie_word_embeddings:
+            put(self.lm_head, weights["lm_head.weight"])
+        qn, kn = self.Hq * self.D, self.Hkv * self.D
+        for i, lw in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            put(lw.ln1, weights[p + "input_layernorm.weight"])
+            put(lw.ln2, weights[p + "post_attention_layernorm.weight"])
+            a = p + "self_attn."
+            put(lw.wqkv[:qn], self._shard_rows(weights[a + "q_proj.weight"], tp, r))
+            put(lw.wqkv[qn:qn + kn], self._shard_rows(weights[a + "k_proj.weight"], tp, r))
+            put(lw.wqkv[qn + kn:], self._shard_rows(weights[a + "v_proj.weight"], tp, r))
+            if lw.bqkv is not None:
+                put(lw.bqkv[:qn], self._shard_rows(weights[a + "q_proj.bias"], tp, r))
+                put(lw.bqkv[qn:qn + kn], self._shard_rows(weights[a + "k_proj.bias"], tp, r))
+                put(lw.bqkv[qn + kn:], self._shard_rows(weights[a + "v_proj.bias"], tp, r))
+            if lw.q_norm is not None:
+                put(lw.q_norm, weights[a + "q_norm.weight"])
+                put(lw.k_norm, weights[a + "k_norm.weight"])
+            wo = weights[a + "o_proj.weight"]
+            cols = wo.shape[1] // tp
+            put(lw.wo, wo[:, r * cols:(r + 1) * cols])
+            m = p + "mlp."
+            if lw.moe is not None:
+                lw.moe.load(weights, m)
+            else:
+                put(lw.wgu[:self.F], self._shard_rows(weights[m + "gate_proj.weight"], tp, r))
+                put(lw.wgu[self.F:], self._shard_rows(weights[m + "up_proj.weight"], tp, r))
+                wd = weights[m + "down_proj.weight"]
+                cols = wd.shape[1] // tp
+                put(lw.wd, wd[:, r * cols:(r + 1) * cols])
+
+    # ------------------------------------------------------------------ layer math
+    def _mlp(self, lw: LayerWeights, h: torch.Tensor, x: torch.Tensor, n: int, static: bool) -> None:
+        """x += MLP(h) for the first n rows."""
+        if lw.moe is not None:
+            lw.moe.forward(h[:n], x[:n])
+            return
+        gu = self.a_gu[:n] if static else None
+        act = self.a_act[:n] if static else None
+        gu = ops.gemm(h[:n], lw.wgu, out=gu)
+        act = ops.swiglu(gu, out=act)
+        self._row_parallel(act, lw.wd, x[:n])
+
+    def _row_parallel(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
+        """x += a @ w.T, summed over tensor-parallel ranks when sharded."""
+        if self.tp is None or self.tp_size == 1:
+            ops.gemm(a, w, residual=x, out=x)
+        else:
+            self.tp.gemm_all_reduce(a, w, x)
+
+    def _forward_layers(self, x, h, n, positions, slots, attn_fn, static: bool):
+        cfg = self.cfg
+        for li, lw in enumerate(self.layers):
+            ops.rmsnorm(x[:n], lw.ln1, cfg.rms_norm_eps, out=h[:n])
+            qkv = ops.gemm(h[:n], lw.wqkv, bias=lw.bqkv, out=self.a_qkv[:n] if static else None)
+            q = ops.rope_kv_append(qkv, positions, slots, self.rope, self.k_cache[li], self.v_cache[li], self.Hq,
+                                   self.Hkv, self.D, lw.q_norm, lw.k_norm, cfg.rms_norm_eps,
+                                   q_out=self.a_q[:n] if static else None)
+            attn = attn_fn(li, q.view(n, self.Hq, self.D))
+            self._row_parallel(attn.view(n, self.Hq * self.D), lw.wo, x[:n])
+            ops.rmsnorm(x[:n], lw.ln2, cfg.rms_norm_eps, out=h[:n])
+            self._mlp(lw, h, x, n, static)
+
+    # ------------------------------------------------------------------ decode
+    def _decode_body(self, bk: int) -> None:
+        cfg = self.cfg
+        x, h = self.a_x, self.a_h
+        ops.embedding(self.d_tokens[:bk], self.embed, out=x[:bk])
+        splits = ops.decode_num_splits(bk, self.Hkv, self.max_model_len)
+        if bk > 64:
+            splits = 1
+        bt = self.bt_dev[:bk]
+        lens = self.d_lens[:bk]
+
+        def attn_fn(li, q):
+            return ops.paged_decode(q, self.k_cache[li], self.v_cache[li], bt, lens, self.scale, splits,
+                                    out=self.a_attn[:bk].view(bk, self.Hq, self.D), workspace=self.dec_ws)
+
+        self._forward_layers(x, h, bk, self.d_pos[:bk], self.d_slots[:bk], attn_fn, static=True)
+        ops.rmsnorm(x[:bk], self.final_norm, cfg.rms_norm_eps, out=h[:bk])
+        logits = ops.gemm(h[:bk], self.lm_head, out=self.a_logits[:bk], out_f32=True)
+        self._sample(logits, self.d_temps[:bk], self.d_seeds[:bk], bk)
+
+    def _sample(self, logits, temps, seeds, n: int) -> None:
+        if self.on_gpu:
+            ops.sample_with_logprobs(logits, temps, seeds, 0, None, self.d_out_tokens[:n], self.d_out_logprobs[:n])
+            return
+        # CPU twin: one seeded generator per row so a request reproduces in any batch slot
+        for r in range(n):
+            g = torch.Generator().manual_seed(int(seeds[r].item()) & 0x7FFFFFFFFFFFFFFF)
+            tok, lp = ops.sample_with_logprobs_reference(logits[r:r + 1].float(), temps[r:r + 1], g)
+            self.d_out_tokens[r] = int(tok[0])
+            self.d_out_logprobs[r] = float(lp[0])
+
+    def bucket(self, n: int) -> int:
+        for b in self.graph_batch_sizes:
+            if b >= n:
+                return b
+        return self.max_batch
+
+    def capture_graphs(self) -> None:
+        """Capture one decode graph per batch-size bucket (largest first, shared memory pool)."""
+        if not self.use_cuda_graphs:
+            return
+        self.d_lens.zero_()
+        self.d_slots.fill_(-1)
+        torch.cuda.synchronize(self.device)
+        stream = torch.cuda.Stream(self.device)
+        with torch.cuda.stream(stream):
+            for bk in sorted(self.graph_batch_sizes, reverse=True):
+                self._decode_body(bk)  # warm-up: sets kernel attributes outside capture
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=self.graph_pool, stream=stream):
+                    self._decode_body(bk)
+                if self.graph_pool is None:
+                    self.graph_pool = g.pool()
+                self.graphs[bk] = g
+        torch.cuda.synchronize(self.device)
+        ops.check_status(self.device)
+
+    def decode(self, n: int, max_blocks: int) -> None:
+        """Run one decode step for the ``n`` rows staged in ``meta_host`` / ``bt_host``.
+
+        Host->device: one copy of the packed metadata vector and one 2-D copy of the used
+        block-table columns. Device->host: one copy of tokens|logprobs into ``out_host``.
+        The caller synchronises before reading ``out_host``.
+        """
+        bk = self.bucket(n) if self.use_cuda_graphs else n
+        self.meta_dev.copy_(self.meta_host, non_blocking=True)
+        self.bt_dev[:n, :max_blocks].copy_(self.bt_host[:n, :max_blocks], non_blocking=True)
+        g = self.graphs.get(bk)
+        if g is not None:
+            g.replay()
+        else:
+            self._decode_body(bk)
+        self.out_host.copy_(self.out_dev, non_blocking=True)
+
+    def stage_decode_padding(self, n: int) -> None:
+        """Mark rows n..bucket as padding (no KV write, empty context)."""
+        bk = self.bucket(n) if self.use_cuda_graphs else n
+        mb = self.max_batch
+        mh = self.meta_host
+        if bk > n:
+            mh[0 * mb + n:0 * mb + bk] = 0
+            mh[1 * mb + n:1 * mb + bk] = 0
+            mh[2 * mb + n:2 * mb + bk] = -1
+            mh[3 * mb + n:3 * mb + bk] = 0
+            mh[4 * mb + n:4 * mb + bk] = 0
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, rows: int, T: int, max_new: int, max_blocks: int, views: dict[str, torch.Tensor]) -> None:
+        """Packed varlen prefill of ``T`` new tokens over ``rows`` sequences.
+
+        ``views`` are slices of ``pf_host`` filled by the engine core. Results land in
+        ``out_host[:rows]`` / ``out_host[max_batch:max_batch+rows]`` after a synchronise.
+        """
+        cfg = self.cfg
+        dev = self.device
+        self.pf_dev.copy_(self.pf_host, non_blocking=True)
+        self.bt_dev[:rows, :max_blocks].copy_(self.bt_host[:rows, :max_blocks], non_blocking=True)
+        o = self._pf_offsets()
+        pd = self.pf_dev
+        tokens = pd[o["tokens"]:o["tokens"] + T]
+        positions = pd[o["positions"]:o["positions"] + T]
+        slots = pd[o["slots"]:o["slots"] + T]
+        cu_q = pd[o["cu_q"]:o["cu_q"] + rows + 1]
+        seq_lens = pd[o["seq_lens"]:o["seq_lens"] + rows]
+        sample_rows = pd[o["sample_rows"]:o["sample_rows"] + rows]
+        temps = pd[o["temps"]:o["temps"] + rows].view(torch.float32)
+        seeds = pd[o["seeds"]:o["seeds"] + 2 * rows].view(torch.int64)
+        x = ops.embedding(tokens, self.embed)
+        h = torch.empty_like(x)
+        bt = self.bt_dev[:rows]
+
+        def attn_fn(li, q):
+            return ops.paged_prefill(q, self.k_cache[li], self.v_cache[li], bt, cu_q, seq_lens, max_new, self.scale,
+                                     cfg.sliding_window)
+
+        self._forward_layers(x, h, T, positions, slots, attn_fn, static=False)
+        last = ops.embedding(sample_rows, x)  # row gather of the last token of every sequence
+        hl = ops.rmsnorm(last, self.final_norm, cfg.rms_norm_eps)
+        logits = ops.gemm(hl, self.lm_head, out=self.a_logits[:rows], out_f32=True)
+        self._sample(logits, temps, seeds, rows)
+        self.out_host.copy_(self.out_dev, non_blocking=True)
+        _ = dev
+
+    def _pf_offsets(self) -> dict[str, int]:
+        T, mb = self.max_prefill_tokens, self.max_batch
+        return {"tokens": 0, "positions": T, "slots": 2 * T, "cu_q": 3 * T, "seq_lens": 3 * T + (mb + 1),
+                "sample_rows": 3 * T + 2 * (mb + 1), "temps": 3 * T + 3 * (mb + 1), "seeds": 3 * T + 4 * (mb + 1)}
+
+    # ------------------------------------------------------------------ teacher forcing
+    def score(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """Full-sequence logits ``[T, V]`` (fp32) for one sequence, without touching live KV blocks.
+
+        Uses the tail of the KV pool as scratch blocks; meant for tests and logprob checks.
+        """
+        T = token_ids.numel()
+        nblk = (T + BLOCK - 1) // BLOCK
+        assert nblk <= self.num_kv_blocks
+        dev = self.device
+        blocks = torch.arange(self.num_kv_blocks - nblk, self.num_kv_blocks, dtype=torch.int32, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        slots = blocks[torch.div(pos, BLOCK, rounding_mode="floor").long()] * BLOCK + pos % BLOCK
+        bt = blocks[None].contiguous()
+        cu_q = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        lens = torch.tensor([T], dtype=torch.int32, device=dev)
+        x = ops.embedding(token_ids.to(device=dev, dtype=torch.int32), self.embed)
+        h = torch.empty_like(x)
+
+        def attn_fn(li, q):
+            return ops.paged_prefill(q, self.k_cache[li], self.v_cache[li], bt, cu_q, lens, T, self.scale,
+                                     self.cfg.sliding_window)
+
+        self._forward_layers(x, h, T, pos, slots.to(torch.int32), attn_fn, static=False)
+        hl = ops.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps)
+        return ops.gemm(hl, self.lm_head, out_f32=True)

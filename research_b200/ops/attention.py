@@ -97,7 +97,11 @@ def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, scale=None, num_sp
                  workspace: torch.Tensor | None = None):
     """One query token per sequence against its paged context. ``q``: ``[B, Hq, D]``."""
     if not q.is_cuda:
-        return paged_decode_reference(q, k_cache, v_cache, block_tables, seq_lens, scale)
+        res = paged_decode_reference(q, k_cache, v_cache, block_tables, seq_lens, scale)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     B, Hq, D = q.shape
     nb, Hkv, bs, _ = k_cache.shape
     scale = scale or 1.0 / math.sqrt(D)
@@ -121,7 +125,11 @@ def paged_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, max_new: in
                   out=None, lse: torch.Tensor | None = None):
     """Causal attention of packed new tokens ``q [T, Hq, D]`` against prefix + themselves."""
     if not q.is_cuda:
-        return paged_prefill_reference(q, k_cache, v_cache, block_tables, cu_q, seq_lens, scale, window)
+        res = paged_prefill_reference(q, k_cache, v_cache, block_tables, cu_q, seq_lens, scale, window)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     T, Hq, D = q.shape
     nb, Hkv, bs, _ = k_cache.shape
     scale = scale or 1.0 / math.sqrt(D)

@@ -43,7 +43,11 @@ def rmsnorm_reference(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Ten
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, out: torch.Tensor | None = None) -> torch.Tensor:
     """Row RMSNorm over the last dim; also used per head (QK-norm) with ``x`` reshaped."""
     if not x.is_cuda:
-        return rmsnorm_reference(x, w, eps)
+        res = rmsnorm_reference(x, w, eps)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     d = x.shape[-1]
     x2 = x.reshape(-1, d)
     assert x2.stride(1) == 1 and x.dtype == torch.bfloat16
@@ -101,7 +105,11 @@ def rope_kv_append(qkv, positions, slots, table, k_cache, v_cache, Hq, Hkv, D, q
     ``k_cache``/``v_cache``: ``[num_blocks, Hkv, block_size, D]``; ``slots`` < 0 rows are skipped.
     """
     if not qkv.is_cuda:
-        return rope_kv_append_reference(qkv, positions, slots, table, k_cache, v_cache, Hq, Hkv, D, q_norm_w, k_norm_w, eps)
+        res = rope_kv_append_reference(qkv, positions, slots, table, k_cache, v_cache, Hq, Hkv, D, q_norm_w, k_norm_w, eps)
+        if q_out is not None:
+            q_out.copy_(res)
+            return q_out
+        return res
     T = qkv.shape[0]
     assert qkv.is_contiguous() and qkv.shape[1] == (Hq + 2 * Hkv) * D
     assert positions.dtype == torch.int32 and slots.dtype == torch.int32
@@ -126,7 +134,11 @@ def swiglu_reference(gu: torch.Tensor) -> torch.Tensor:
 def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """``silu(gate) * up`` for ``gu = [gate | up]`` of shape ``[T, 2F]``."""
     if not gu.is_cuda:
-        return swiglu_reference(gu)
+        res = swiglu_reference(gu)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     T, F2 = gu.reshape(-1, gu.shape[-1]).shape
     F = F2 // 2
     assert gu.is_contiguous()
@@ -154,7 +166,11 @@ def swiglu_backward(gu: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------------------- embedding
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     if not table.is_cuda:
-        return table[ids.long()]
+        res = table[ids.long()]
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     assert ids.dtype == torch.int32 and ids.is_contiguous()
     T = ids.numel()
     d = table.shape[1]

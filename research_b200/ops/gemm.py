@@ -95,7 +95,11 @@ def gemm(
     on CPU it evaluates the fp32 reference (used as the oracle in tests).
     """
     if not a.is_cuda:
-        return gemm_reference(a, b, bias, residual, a_mn_major, b_mn_major, torch.float32 if out_f32 else None)
+        res = gemm_reference(a, b, bias, residual, a_mn_major, b_mn_major, torch.float32 if out_f32 else None)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1, "operands must be contiguous in their last dim"

@@ -206,4 +206,5 @@ def test_paged_prefill(cuda_device, D, Hq, Hkv, window):
     got = ops.paged_prefill(q, kc, vc, bt, cu, sl, max(new), window=window)
     want = ops.paged_prefill_reference(q, kc, vc, bt, cu, sl, window=window)
     diff = (got.float() - want.float()).abs()
-    assert diff.max().item() < 0.01 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+    # rows that attend to one or two keys return |v| ~ 2-4, where one bf16 ulp is 0.0156
+    assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
