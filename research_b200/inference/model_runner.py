@@ -22,6 +22,7 @@ from dataclasses import dataclass
 import torch
 
 from .. import ops
+from ..ops._util import LAUNCH_COUNT
 from ..models.config import ModelConfig
 
 BLOCK = 16
@@ -139,6 +140,7 @@ class ModelRunner:
         # split-KV partials for small batches (up to 64 rows x 32 splits)
         self.dec_ws = torch.empty(min(mb, 64) * self.Hq * 32 * (self.D + 2), dtype=torch.float32, device=device)
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.launches_per_graph: dict[int, int] = {}
         self.graph_pool = None
 
         # prefill staging (pinned): tokens | positions | slots | cu_q | seq_lens | sample_rows | temps | seeds
@@ -277,8 +279,10 @@ class ModelRunner:
                 self._decode_body(bk)  # warm-up: sets kernel attributes outside capture
                 stream.synchronize()
                 g = torch.cuda.CUDAGraph()
+                n0 = LAUNCH_COUNT[0]
                 with torch.cuda.graph(g, pool=self.graph_pool, stream=stream):
                     self._decode_body(bk)
+                self.launches_per_graph[bk] = LAUNCH_COUNT[0] - n0
                 if self.graph_pool is None:
                     self.graph_pool = g.pool()
                 self.graphs[bk] = g

@@ -54,7 +54,13 @@ def check_status(device: torch.device | int | None = None, reset: bool = True) -
         raise KernelStatusError(f"kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
-def check_rc(rc: int, what: str) -> None:
+# Number of kernel launches issued through the wrappers (every wrapper reports exactly one
+# launch per call through check_rc; the split-KV merge adds its own).
+LAUNCH_COUNT = [0]
+
+
+def check_rc(rc: int, what: str, launches: int = 1) -> None:
+    LAUNCH_COUNT[0] += launches
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
 

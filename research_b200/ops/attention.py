@@ -117,7 +117,7 @@ def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, scale=None, num_sp
     rc = _lib().rb_paged_decode(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(seq_lens), ptr(out),
                                 ptr(workspace), B, Hq, Hkv, D, block_tables.shape[1], nb, bs, num_splits, scale,
                                 ptr(status_tensor(q.device)), stream_handle(q.device))
-    check_rc(rc, "rb_paged_decode")
+    check_rc(rc, "rb_paged_decode", 2 if num_splits > 1 else 1)
     return out
 
 

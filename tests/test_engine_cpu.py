@@ -1,0 +1,236 @@
+"""CPU tests of the engine: C++ scheduler / block manager / radix tree and end-to-end generation
+against the functional oracle (greedy exact match, the reference's own correctness criterion)."""
+
+import random
+
+import pytest
+import torch
+
+from research_b200.inference import (EngineConfig, InferenceEngine, SamplingParams, SchedulerConfig, Sequence,
+                                     SequenceStatus, schedule)
+from research_b200.inference.cache import PagedKVCache, RadixKVCache, compute_block_hash
+from research_b200.inference.context import (allocate_and_build_context, build_decode_context,
+                                             build_prefill_context, extend_and_build_context)
+from research_b200.inference.scheduler import can_schedule_any, schedule_native
+from research_b200.models import causal_lm_forward, get_preset, init_random_weights
+
+
+def _seq(i, n, status):
+    return Sequence(i, list(range(n)), [], n, status, 1.0, 8, frozenset())
+
+
+def test_schedule_policy_matches_native():
+    rng = random.Random(0)
+    for _ in range(200):
+        running = [_seq(i, rng.randint(1, 50), SequenceStatus.RUNNING) for i in range(rng.randint(0, 12))]
+        waiting = [_seq(100 + i, rng.randint(1, 300), SequenceStatus.WAITING) for i in range(rng.randint(0, 12))]
+        cfg = SchedulerConfig(rng.randint(1, 10), rng.randint(10, 600), 16)
+        free = rng.randint(0, 40)
+        assert schedule(waiting, running, free, cfg) == schedule_native(waiting, running, free, cfg)
+
+
+def test_schedule_decode_first_and_limits():
+    cfg = SchedulerConfig(max_batch_size=3, max_tokens_per_batch=100, block_size=16)
+    running = [_seq(i, 5, SequenceStatus.RUNNING) for i in range(4)]
+    waiting = [_seq(10, 20, SequenceStatus.WAITING)]
+    out = schedule(waiting, running, 100, cfg)
+    assert out.decode_seqs == (0, 1, 2) and out.preempted_seqs == (3,) and out.prefill_seqs == ()
+    out = schedule([_seq(10, 40, SequenceStatus.WAITING), _seq(11, 70, SequenceStatus.WAITING)], [], 100, cfg)
+    assert out.prefill_seqs == (10,)  # token budget stops the second
+    out = schedule([_seq(10, 40, SequenceStatus.WAITING)], [], 2, cfg)
+    assert out.prefill_seqs == ()  # needs 3 blocks
+    assert can_schedule_any([], running, 0, cfg) and not can_schedule_any([], [], 5, cfg)
+
+
+@pytest.mark.parametrize("cls", [PagedKVCache, RadixKVCache])
+def test_prefix_hit_two_prompts(cls):
+    cache = cls(num_blocks=32, block_size=4)
+    a = list(range(100, 112))
+    b = a[:8] + [7, 8, 9, 10, 11]
+    blocks_a = cache.allocate(0, a)
+    assert len(blocks_a) == 3 and cache.get_cached_tokens(0) == 0
+    blocks_b = cache.allocate(1, b)
+    assert cache.get_cached_tokens(1) == 8
+    assert blocks_b[:2] == blocks_a[:2] and blocks_b[2] != blocks_a[2]
+    assert cache.ref_count(blocks_a[0]) >= 2
+    cache.deallocate(0)
+    cache.deallocate(1)
+    assert cache.check_invariants() == 0
+    # the prefix survives its sequences
+    cache.allocate(2, a[:8] + [1, 2])
+    assert cache.get_cached_tokens(2) == 8
+
+
+def test_fully_cached_prompt_recomputes_last_block():
+    cache = PagedKVCache(16, 4)
+    p = list(range(8))
+    cache.allocate(0, p)
+    cache.allocate(1, p)
+    assert cache.get_cached_tokens(1) == 4  # never the whole prompt: the step needs logits
+
+
+@pytest.mark.parametrize("cls", [PagedKVCache, RadixKVCache])
+def test_append_token_grows_blocks_and_publishes(cls):
+    cache = cls(16, 4)
+    cache.allocate(0, [1, 2, 3])
+    assert cache.append_token(0, 4) is None
+    new = cache.append_token(0, 5)
+    assert new is not None and cache.get_block_ids(0)[-1] == new
+    for t in (6, 7, 8):
+        cache.append_token(0, t)
+    cache.deallocate(0)
+    cache.allocate(1, [1, 2, 3, 4, 5, 6, 7, 8, 9])
+    assert cache.get_cached_tokens(1) == 8  # generated blocks are reusable too
+
+
+def test_radix_eviction_lru_and_pinning():
+    cache = RadixKVCache(num_blocks=8, block_size=4)
+    cache.allocate(0, list(range(0, 16)))      # 4 blocks
+    cache.deallocate(0)
+    cache.allocate(1, list(range(100, 116)))   # 4 blocks
+    assert cache.num_free_blocks() == 4        # seq 0's blocks are cached but evictable
+    cache.allocate(2, list(range(200, 212)))   # forces eviction of seq 0's leaf
+    assert cache.stats()["evictions"] >= 3
+    assert cache.check_invariants() == 0
+    with pytest.raises(RuntimeError):
+        cache.allocate(3, list(range(300, 340)))
+    cache.deallocate(1)
+    cache.deallocate(2)
+    assert cache.check_invariants() == 0
+    cache.flush()
+    assert cache.num_free_blocks() == 8 and cache.stats()["evictable_blocks"] == 0
+
+
+def test_radix_split_keeps_pins_consistent():
+    cache = RadixKVCache(32, 4)
+    long = list(range(24))
+    cache.allocate(0, long)
+    cache.allocate(1, long[:12] + [90, 91, 92, 93, 94])   # splits seq 0's edge while 0 is pinned
+    assert cache.get_cached_tokens(1) == 12
+    cache.deallocate(0)
+    cache.deallocate(1)
+    st = cache.stats()
+    assert st["free_blocks"] + st["evictable_blocks"] == 32, st
+    assert cache.check_invariants() == 0
+
+
+def test_allocator_fuzz_invariants():
+    rng = random.Random(1)
+    for cls in (PagedKVCache, RadixKVCache):
+        cache = cls(64, 4)
+        live = {}
+        for step in range(600):
+            if live and rng.random() < 0.45:
+                sid = rng.choice(list(live))
+                if rng.random() < 0.5:
+                    try:
+                        cache.append_token(sid, rng.randint(0, 5))
+                    except RuntimeError:
+                        pass
+                else:
+                    cache.deallocate(sid)
+                    del live[sid]
+            else:
+                toks = [rng.randint(0, 3) for _ in range(rng.randint(1, 30))]
+                try:
+                    cache.allocate(step, toks)
+                    live[step] = True
+                except RuntimeError:
+                    pass
+            assert cache.check_invariants() == 0
+        for sid in list(live):
+            cache.deallocate(sid)
+        st = cache.stats()
+        assert st["free_blocks"] + st["evictable_blocks"] == 64
+
+
+def test_block_hash_chain():
+    h1 = compute_block_hash([1, 2, 3, 4])
+    assert h1 == compute_block_hash([1, 2, 3, 4]) and h1 != compute_block_hash([1, 2, 3, 5])
+    assert compute_block_hash([5, 6, 7, 8], h1) != compute_block_hash([5, 6, 7, 8])
+
+
+def test_context_builders():
+    cache = PagedKVCache(16, 4)
+    ctx, blocks = allocate_and_build_context(cache, 0, [1, 2, 3, 4, 5, 6])
+    assert ctx.is_prefill and len(ctx.slot_mapping) == 6
+    assert ctx.slot_mapping[0] == blocks[0] * 4 and ctx.slot_mapping[5] == blocks[1] * 4 + 1
+    d = extend_and_build_context(cache, 0, 7, 6)
+    assert not d.is_prefill and d.seq_lens == (7,) and d.slot_mapping == (blocks[1] * 4 + 2,)
+    p = build_prefill_context(cache, [0], [6], [blocks], [4])
+    assert p.query_lens == (2,) and len(p.slot_mapping) == 2
+    assert build_decode_context(cache, [0], [5], [blocks]).slot_mapping == (blocks[1] * 4,)
+
+
+# ------------------------------------------------------------------------------ engine end-to-end
+def _prompts(cfg, n, seed=0, shared_len=24):
+    g = torch.Generator().manual_seed(seed)
+    shared = torch.randint(0, cfg.vocab_size, (shared_len,), generator=g).tolist()
+    out = []
+    for i in range(n):
+        k = int(torch.randint(16, 64, (1,), generator=g))
+        p = torch.randint(0, cfg.vocab_size, (k,), generator=g).tolist()
+        out.append(shared + p if i % 2 == 0 else p)
+    return out
+
+
+def _oracle_greedy(w, cfg, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        ids.append(int(causal_lm_forward(torch.tensor([ids]), w, cfg)[0, -1].argmax()))
+    return tuple(ids[len(prompt):])
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen2", "tiny-qwen3", "tiny-llama"])
+@pytest.mark.parametrize("cache_type", ["radix", "paged", "none"])
+def test_engine_greedy_matches_oracle(preset, cache_type):
+    cfg = get_preset(preset, num_layers=2)
+    w = init_random_weights(cfg, seed=0)
+    eng = InferenceEngine(EngineConfig(cache_type=cache_type, max_batch_size=4, max_model_len=256, num_kv_blocks=96,
+                                       ignore_eos=True), cfg, w, device="cpu")
+    prompts = _prompts(cfg, 6)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6))
+    for p, s in zip(prompts, outs):
+        assert s.prompt_tokens == tuple(p)
+        assert s.completion_tokens == _oracle_greedy(w, cfg, p, 6)
+        assert len(s.logprobs) == 6 and all(lp <= 0 for lp in s.logprobs) and s.finish_reason == "length"
+    if cache_type != "none":
+        assert eng.cache_stats()["hit_tokens"] > 0
+    assert eng.check_invariants() == 0 and not eng.has_pending()
+
+
+def test_engine_preemption_recomputes_and_finishes():
+    cfg = get_preset("tiny-qwen2", num_layers=1)
+    w = init_random_weights(cfg, seed=0)
+    # pool so small that running sequences must be preempted while they grow
+    eng = InferenceEngine(EngineConfig(cache_type="none", max_batch_size=4, max_model_len=128, num_kv_blocks=10,
+                                       ignore_eos=True), cfg, w, device="cpu")
+    prompts = [p[:30] for p in _prompts(cfg, 4, seed=3)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40))
+    for p, s in zip(prompts, outs):
+        assert s.completion_tokens == _oracle_greedy(w, cfg, p, 40)
+    assert eng.check_invariants() == 0
+
+
+def test_engine_sampling_seeded_stop_tokens_and_weight_update():
+    cfg = get_preset("tiny-qwen2", num_layers=1)
+    w = init_random_weights(cfg, seed=0)
+    eng = InferenceEngine(EngineConfig(max_batch_size=4, max_model_len=128, num_kv_blocks=64, ignore_eos=True), cfg, w,
+                          device="cpu")
+    p = _prompts(cfg, 2)
+    a = eng.generate(p, SamplingParams(temperature=1.0, max_tokens=5, seed=7))
+    b = eng.generate(p, SamplingParams(temperature=1.0, max_tokens=5, seed=7))
+    assert [s.completion_tokens for s in a] == [s.completion_tokens for s in b]
+    first = a[0].completion_tokens[0]
+    c = eng.generate(p[:1], SamplingParams(temperature=1.0, max_tokens=5, seed=7, stop_token_ids=frozenset({first})))
+    assert c[0].completion_tokens == (first,) and c[0].finish_reason == "stop"
+    # weight update bumps the version and invalidates cached prefixes
+    assert eng.cache_stats()["hit_tokens"] > 0
+    w2 = init_random_weights(cfg, seed=1)
+    eng.update_weights(w2)
+    assert eng.get_weight_version() == 1
+    d = eng.generate(p[:1], SamplingParams(temperature=0.0, max_tokens=4))
+    assert d[0].weight_version == 1 and d[0].cached_tokens == 0
+    assert d[0].completion_tokens == _oracle_greedy(w2, cfg, p[0], 4)
+    with pytest.raises(ValueError):
+        eng.add_request([1] * 100, SamplingParams(max_tokens=100))
