@@ -182,7 +182,8 @@ def run_native(args) -> dict:
     check_status(dev)
     launches = r.launches_per_graph.get(MAX_BATCH, 0) * K
 
-    value = world * MAX_BATCH * K / (dev_ms * 1e-3)
+    rows_replayed = int((r.meta_host[3 * MAX_BATCH:4 * MAX_BATCH] > 0).sum())  # live rows in the replayed batch
+    value = sum_over_ranks(float(rows_replayed * K), world) / (dev_ms * 1e-3)
     e2e = toks_e2e_total / (e2e_ms * 1e-3)
     out = {
         "metric": "rollout_decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,

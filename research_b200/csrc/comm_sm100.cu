@@ -1,0 +1,281 @@
+// Collectives written as kernels over peer (symmetric) memory on NVLink 5 / NVSwitch.
+//
+// Every rank maps every peer's communication buffers into its own address space; the kernels
+// below move data with plain 16-byte peer loads / stores and synchronise with release/acquire
+// flags at system scope. Every wait is bounded and reports through the status word.
+//
+//   symm_barrier        all ranks signal all peers and wait for all peers (epoch based)
+//   symm_signal         one-way "my data is ready" flag to every peer
+//   rs_reduce           gradient reduce-scatter: each rank PULLS its shard of every peer's bf16
+//                       gradient bucket, sums in fp32, applies the 1/N scale, writes its fp32
+//                       shard and per-CTA partial sums of squares (global grad norm), one pass
+//   clip_coef           exchanges the per-rank sums of squares through peer memory and turns
+//                       them into the clip coefficient, on the device (no host round trip)
+//   adamw_allgather     sharded AdamW (fp32 master + moments) fused with the parameter
+//                       all-gather: the updated bf16 values are PUSHED into every peer's full
+//                       parameter buffer from inside the optimizer kernel
+//   reshard_copy        trainer -> engine weight sync: one launch copies a table of 2-D
+//                       segments from (peer) trainer shards into the engine's packed tensor-
+//                       parallel layout (fused QKV / gate|up packing, row or column slices)
+//
+// Replaces: FSDP2 NCCL reduce-scatter + clip_grad_norm_ + torch AdamW + all-gather
+// (rollouts/training/backends/fsdp.py:289-322, 398-452) and the per-tensor dist.broadcast /
+// disk round trip of the weight sync (rollouts/training/weight_sync.py:233-282).
+#include "common.cuh"
+
+#define RB_MAX_RANKS 8
+
+namespace rb {
+
+struct PeerPtrs { void* p[RB_MAX_RANKS]; };
+
+// flags: each rank owns int flags[slots][world] in symmetric memory; peer r writes [slot][r].
+__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch, int* status) {
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < world) {
+    st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, epoch);
+    wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, epoch, status);
+  }
+}
+__global__ void symm_signal_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch) {
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < world) st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, epoch);
+}
+__global__ void symm_wait_kernel(const int* my_flags, int world, int slot, int epoch, int* status) {
+  const int r = threadIdx.x;
+  if (r < world) wait_flag_ge(my_flags + slot * world + r, epoch, status);
+}
+
+__device__ __forceinline__ uint4 ld_peer_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer_16(void* p, uint4 v) {
+  asm volatile("st.global.relaxed.sys.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// ---- reduce-scatter of a bf16 gradient bucket into this rank's fp32 shard -----------------
+// grads.p[r] : rank r's full bucket [n_total] bf16; this rank reduces [rank*n_shard, +n_shard)
+// ready flags (slot) must be >= epoch for every peer before its bucket is read.
+__global__ void rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, int epoch, int rank, int world,
+                                 long long n_shard, float scale, float* __restrict__ shard_f32, int accumulate,
+                                 float* __restrict__ sumsq_partial, int* status) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (my_flags != nullptr && threadIdx.x < world) {
+    if (!wait_flag_ge(my_flags + slot * world + threadIdx.x, epoch, status)) failed = 1;
+  }
+  __syncthreads();
+  float acc_sq = 0.f;
+  if (!failed) {
+    const long long nvec = n_shard >> 3;
+    const long long base = (long long)rank * n_shard;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+      float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int rr = 0; rr < world; ++rr) {
+        const int src = (rank + rr) % world;  // stagger the peers so links are used evenly
+        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + base + i * 8;
+        const uint4 v = ld_peer_16(g);
+        float2 f;
+        f = unpack_bf16x2(v.x); s[0] += f.x; s[1] += f.y;
+        f = unpack_bf16x2(v.y); s[2] += f.x; s[3] += f.y;
+        f = unpack_bf16x2(v.z); s[4] += f.x; s[5] += f.y;
+        f = unpack_bf16x2(v.w); s[6] += f.x; s[7] += f.y;
+      }
+      float* o = shard_f32 + i * 8;
+      float4 a = make_float4(s[0] * scale, s[1] * scale, s[2] * scale, s[3] * scale);
+      float4 b = make_float4(s[4] * scale, s[5] * scale, s[6] * scale, s[7] * scale);
+      if (accumulate) {
+        const float4 pa = *reinterpret_cast<float4*>(o), pb = *reinterpret_cast<float4*>(o + 4);
+        a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
+        b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+      }
+      *reinterpret_cast<float4*>(o) = a;
+      *reinterpret_cast<float4*>(o + 4) = b;
+      acc_sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+    }
+  }
+  // block reduce of the squares
+  __shared__ float sm[32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  acc_sq = warp_sum(acc_sq);
+  if (lane == 0) sm[wid] = acc_sq;
+  __syncthreads();
+  if (wid == 0) {
+    float r = lane < (blockDim.x >> 5) ? sm[lane] : 0.f;
+    r = warp_sum(r);
+    if (lane == 0 && sumsq_partial != nullptr) sumsq_partial[blockIdx.x] += r;
+  }
+}
+
+// ---- global grad norm -> clip coefficient, exchanged through peer memory ---------------------
+// partial: [n_partial] this rank's sums of squares. norm_slots.p[r]: rank r's float slots[world].
+__global__ void clip_coef_kernel(const float* __restrict__ partial, int n_partial, PeerPtrs norm_slots, PeerPtrs flags,
+                                 int slot, int epoch, int rank, int world, float max_norm, float* __restrict__ out_coef,
+                                 float* __restrict__ out_norm, int* status) {
+  __shared__ float sm[32];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < n_partial; i += blockDim.x) acc += partial[i];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  acc = warp_sum(acc);
+  if (lane == 0) sm[wid] = acc;
+  __syncthreads();
+  if (wid == 0) {
+    float r = lane < (blockDim.x >> 5) ? sm[lane] : 0.f;
+    r = warp_sum(r);
+    if (lane == 0) sm[0] = r;
+  }
+  __syncthreads();
+  const float mine = sm[0];
+  const int r = threadIdx.x;
+  if (r < world) {
+    reinterpret_cast<float*>(norm_slots.p[r])[rank] = mine;
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, epoch);
+  }
+  __syncthreads();
+  bool ok = true;
+  if (r < world) ok = wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, epoch, status);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    const volatile float* slots = reinterpret_cast<const volatile float*>(norm_slots.p[rank]);
+    for (int i = 0; i < world; ++i) total += slots[i];
+    const float norm = sqrtf(total);
+    *out_norm = norm;
+    *out_coef = (max_norm > 0.f) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  }
+  (void)ok;
+}
+
+// ---- sharded AdamW fused with the parameter all-gather ------------------------------------------
+// params.p[r]: rank r's full bf16 parameter bucket [n_total]; this rank owns [rank*n_shard, +n_shard).
+__global__ void adamw_allgather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                                       const float* __restrict__ grad, PeerPtrs params, int rank, int world,
+                                       long long n_shard, float lr, float beta1, float beta2, float eps,
+                                       float weight_decay, float bc1, float bc2, const float* __restrict__ clip_coef) {
+  const float clip = clip_coef != nullptr ? *clip_coef : 1.f;
+  const long long nvec = n_shard >> 3;
+  const long long base = (long long)rank * n_shard;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long k = i * 8 + j;
+      const float g = grad[k] * clip;
+      const float mi = beta1 * m[k] + (1.f - beta1) * g;
+      const float vi = beta2 * v[k] + (1.f - beta2) * g * g;
+      m[k] = mi;
+      v[k] = vi;
+      p[j] = master[k] * (1.f - lr * weight_decay) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+      master[k] = p[j];
+    }
+    uint4 o;
+    o.x = pack_bf16x2(p[0], p[1]);
+    o.y = pack_bf16x2(p[2], p[3]);
+    o.z = pack_bf16x2(p[4], p[5]);
+    o.w = pack_bf16x2(p[6], p[7]);
+    for (int rr = 0; rr < world; ++rr) {
+      const int dst = (rank + rr) % world;
+      st_peer_16(reinterpret_cast<__nv_bfloat16*>(params.p[dst]) + base + i * 8, o);
+    }
+  }
+}
+
+// ---- weight reshard copy ---------------------------------------------------------------------------
+struct Segment {
+  const void* src;     // bf16, may be peer memory
+  void* dst;           // bf16, local
+  long long src_ld, dst_ld;   // elements
+  int rows, cols;      // cols multiple of 8
+  long long vec_begin; // prefix sum of rows * cols / 8
+};
+
+__global__ void reshard_copy_kernel(const Segment* __restrict__ segs, int n_segs, long long total_vecs) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
+       i += (long long)gridDim.x * blockDim.x) {
+    int lo = 0, hi = n_segs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (segs[mid].vec_begin <= i) lo = mid; else hi = mid - 1;
+    }
+    const Segment s = segs[lo];
+    const long long k = i - s.vec_begin;
+    const int vpr = s.cols >> 3;
+    const long long r = k / vpr;
+    const int c = (int)(k % vpr) * 8;
+    const uint4 v = ld_peer_16(reinterpret_cast<const __nv_bfloat16*>(s.src) + r * s.src_ld + c);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(s.dst) + r * s.dst_ld + c) = v;
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+#define RB_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+
+static PeerPtrs make_ptrs(void* const* p, int world) {
+  PeerPtrs o;
+  for (int i = 0; i < RB_MAX_RANKS; ++i) o.p[i] = i < world ? p[i] : nullptr;
+  return o;
+}
+
+extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int slot, int epoch, int* status,
+                               cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS) return -1;
+  symm_barrier_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch, status);
+  return RB_OK();
+}
+extern "C" int rb_symm_signal(void* const* flag_ptrs, int rank, int world, int slot, int epoch, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS) return -1;
+  symm_signal_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch);
+  return RB_OK();
+}
+extern "C" int rb_symm_wait(const int* my_flags, int world, int slot, int epoch, int* status, cudaStream_t s) {
+  symm_wait_kernel<<<1, 32, 0, s>>>(my_flags, world, slot, epoch, status);
+  return RB_OK();
+}
+extern "C" int rb_rs_num_partials() { return 148 * 4; }
+extern "C" int rb_rs_reduce(void* const* grad_ptrs, const int* my_flags, int slot, int epoch, int rank, int world,
+                            long long n_shard, float scale, float* shard_f32, int accumulate, float* sumsq_partial,
+                            int* status, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
+  rs_reduce_kernel<<<rb_rs_num_partials(), 256, 0, s>>>(make_ptrs(grad_ptrs, world), my_flags, slot, epoch, rank, world,
+                                                        n_shard, scale, shard_f32, accumulate, sumsq_partial, status);
+  return RB_OK();
+}
+extern "C" int rb_clip_coef(const float* partial, int n_partial, void* const* norm_slot_ptrs, void* const* flag_ptrs,
+                            int slot, int epoch, int rank, int world, float max_norm, float* out_coef, float* out_norm,
+                            int* status, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS) return -1;
+  clip_coef_kernel<<<1, 256, 0, s>>>(partial, n_partial, make_ptrs(norm_slot_ptrs, world), make_ptrs(flag_ptrs, world),
+                                     slot, epoch, rank, world, max_norm, out_coef, out_norm, status);
+  return RB_OK();
+}
+extern "C" int rb_adamw_allgather(float* master, float* m, float* v, const float* grad, void* const* param_ptrs,
+                                  int rank, int world, long long n_shard, float lr, float beta1, float beta2, float eps,
+                                  float weight_decay, int step, const float* clip_coef, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
+  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  adamw_allgather_kernel<<<148 * 4, 256, 0, s>>>(master, m, v, grad, make_ptrs(param_ptrs, world), rank, world, n_shard,
+                                                 lr, beta1, beta2, eps, weight_decay, bc1, bc2, clip_coef);
+  return RB_OK();
+}
+// segs: device array of Segment (layout mirrored by research_b200/parallel/weight_sync.py)
+extern "C" int rb_reshard_copy(const void* segs, int n_segs, long long total_vecs, cudaStream_t s) {
+  if (n_segs <= 0 || total_vecs <= 0) return 0;
+  long long grid = (total_vecs + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  reshard_copy_kernel<<<(unsigned)grid, 256, 0, s>>>((const Segment*)segs, n_segs, total_vecs);
+  return RB_OK();
+}

@@ -521,15 +521,25 @@ static int launch_bn(const GemmParams& p, int a_mn, int b_mn, int max_ctas, cuda
   return -12;
 }
 
-static int pick_bn(int m_tiles, int n_rows_per_part, int parts, int b_mn) {
+// Tile-width choice. A persistent CTA streams its tiles one after another, so the launch
+// costs waves x (fixed + k-blocks x stage bytes / per-SM streaming rate); e.g. 152 tiles on 148
+// SMs cost two full waves, which a wider tile avoids.
+static int pick_bn(int m_tiles, int n_rows_per_part, int parts, int b_mn, int K) {
   const int sms = num_sms();
   const int cands[4] = {256, 128, 64, 32};
+  const double num_kb = (K + BK - 1) / BK;
   int best = b_mn ? 64 : 32;
+  double best_cost = 1e30;
   for (int i = 0; i < 4; ++i) {
-    int bn = cands[i];
+    const int bn = cands[i];
     if (b_mn && bn < 64) continue;
-    int tiles = m_tiles * ((n_rows_per_part + bn - 1) / bn) * parts;
-    if (tiles >= sms) return bn;
+    const int tiles = m_tiles * ((n_rows_per_part + bn - 1) / bn) * parts;
+    const double waves = (tiles + sms - 1) / sms;
+    const double stage_us = (double)(BM + bn) * BK * 2 / 100e3;   // ~100 GB/s per SM
+    const double mma_us = (double)BM * bn * BK * 2 / 8.0e6;        // ~8 TFLOP/s per SM
+    const double per_tile = 2.5 + num_kb * (stage_us > mma_us ? stage_us : mma_us);
+    const double cost = waves * per_tile;
+    if (cost < best_cost * 0.98) { best_cost = cost; best = bn; }
   }
   return best;
 }
@@ -572,7 +582,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   }
   const int m_tiles = ((p.a_rows_per_part + BM - 1) / BM) * p.a_parts;
   int bn = a->bn;
-  if (bn == 0) bn = pick_bn(m_tiles, p.b_rows_per_part, p.b_parts, a->b_mn_major);
+  if (bn == 0) bn = pick_bn(m_tiles, p.b_rows_per_part, p.b_parts, a->b_mn_major, p.K);
   if (a->b_mn_major && bn < 64) bn = 64;
   // tensor maps: one per slab
   for (int i = 0; i < p.a_parts; ++i) {

@@ -239,20 +239,23 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
   float m = -INFINITY, ssum = 0.f;     // online log-sum-exp of the unscaled logits
   float best = -INFINITY;              // best perturbed score
   int best_i = 0x7fffffff;
+  const bool vec_ok = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15) == 0);
   for (int i = threadIdx.x * 4; i < V; i += SAMPLE_THREADS * 4) {
     float v[4];
-    if (i + 3 < V && ((ld & 3) == 0)) {
-      float4 f = *reinterpret_cast<const float4*>(lr + i);
+    if (i + 3 < V && vec_ok) {
+      float4 f = __ldcs(reinterpret_cast<const float4*>(lr + i));
       v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) v[j] = (i + j < V) ? lr[i + j] : -INFINITY;
     }
+    // one rescale of the running sum per 4 elements instead of a branch per element
+    const float m4 = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+    if (m4 > m) { ssum *= __expf(m - m4); m = m4; }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (i + j >= V) continue;
-      const float x = v[j];
-      if (x > m) { ssum = ssum * __expf(m - x) + 1.f; m = x; } else { ssum += __expf(x - m); }
+      const float x = v[j];          // -inf past the end: contributes exp(-inf) = 0
+      ssum += __expf(x - m);
       float score = x * inv_t;
       if (!greedy) {
         const uint32_t r = hash32((uint32_t)(i + j), k0, k1);
@@ -260,7 +263,7 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
         // Gumbel noise -ln(-ln u) with two fast log2 (ln x = log2 x * ln 2)
         score -= 0.6931471805599453f * __log2f(-0.6931471805599453f * __log2f(u));
       }
-      if (score > best || (score == best && i + j < best_i)) { best = score; best_i = i + j; }
+      if (score > best) { best = score; best_i = i + j; }
     }
   }
   // block reduction

@@ -1,0 +1,303 @@
+// Training-side kernels for sm_100a (all HBM-bound, single pass, 16-byte accesses):
+//
+//   logprob_entropy_fwd / _bwd : per-token log-probability of a target and (optionally) the
+//       entropy straight from a chunk of fp32 logits, and the matching gradient written as
+//       bf16 dlogits. Together with the chunked lm_head GEMM this replaces the reference's
+//       log_softmax over [B,T,V] (rollouts/training/losses.py:98-124, 171-175, 216-226).
+//   rmsnorm_bwd                : dx and per-CTA partial dw of RMSNorm.
+//   rope_fwd / rope_bwd        : rotate_half RoPE on [T,H,D] (backward = rotation by -angle).
+//   adamw                      : fp32 master weights + moments, bf16 or fp32 grads, optional
+//                                clip coefficient read from device memory, bf16 param write-back.
+//   sumsq_partial              : per-CTA partial sums of squares for the global grad norm
+//                                (replaces one .norm().item() per parameter,
+//                                rollouts/training/backends/fsdp.py:398-419).
+#include "common.cuh"
+
+namespace rb {
+
+constexpr int ROW_THREADS = 512;
+
+struct Lse { float m, s; };
+__device__ __forceinline__ Lse lse_merge(Lse a, Lse b) {
+  const float m = fmaxf(a.m, b.m);
+  if (m == -INFINITY) return {m, 0.f};
+  return {m, a.s * __expf(a.m - m) + b.s * __expf(b.m - m)};
+}
+__device__ __forceinline__ Lse block_lse(Lse v) {
+  __shared__ float sm_m[ROW_THREADS / 32], sm_s[ROW_THREADS / 32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Lse other = {__shfl_xor_sync(0xffffffffu, v.m, o), __shfl_xor_sync(0xffffffffu, v.s, o)};
+    v = lse_merge(v, other);
+  }
+  if (lane == 0) { sm_m[wid] = v.m; sm_s[wid] = v.s; }
+  __syncthreads();
+  Lse r = {lane < ROW_THREADS / 32 ? sm_m[lane] : -INFINITY, lane < ROW_THREADS / 32 ? sm_s[lane] : 0.f};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Lse other = {__shfl_xor_sync(0xffffffffu, r.m, o), __shfl_xor_sync(0xffffffffu, r.s, o)};
+    r = lse_merge(r, other);
+  }
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_sum(float v) {
+  __shared__ float sm[ROW_THREADS / 32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  v = warp_sum(v);
+  if (lane == 0) sm[wid] = v;
+  __syncthreads();
+  float r = lane < (blockDim.x >> 5) ? sm[lane] : 0.f;
+  r = warp_sum(r);
+  __syncthreads();
+  return r;
+}
+
+// One CTA per row. entropy may be null. Targets < 0 (ignored positions) give logprob 0.
+__global__ void __launch_bounds__(ROW_THREADS)
+logprob_entropy_fwd_kernel(const float* __restrict__ logits, long long ld, int V, const int* __restrict__ targets,
+                           float* __restrict__ logprob, float* __restrict__ lse_out, float* __restrict__ entropy) {
+  const long long row = blockIdx.x;
+  const float* x = logits + row * ld;
+  Lse v = {-INFINITY, 0.f};
+  for (int i = threadIdx.x; i < V; i += ROW_THREADS) v = lse_merge(v, {x[i], 1.f});
+  v = block_lse(v);
+  const float lse = v.m + __logf(v.s);
+  float ent = 0.f;
+  if (entropy != nullptr) {
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < V; i += ROW_THREADS) {
+      const float lp = x[i] - lse;
+      acc -= __expf(lp) * lp;
+    }
+    ent = block_sum(acc);
+  }
+  if (threadIdx.x == 0) {
+    const int t = targets[row];
+    logprob[row] = (t >= 0 && t < V) ? x[t] - lse : 0.f;
+    lse_out[row] = lse;
+    if (entropy != nullptr) entropy[row] = ent;
+  }
+}
+
+// dlogits[j] = g_lp * (1[j == t] - p_j) - g_ent * p_j * (log p_j + H)
+__global__ void __launch_bounds__(ROW_THREADS)
+logprob_entropy_bwd_kernel(const float* __restrict__ logits, long long ld, int V, const int* __restrict__ targets,
+                           const float* __restrict__ lse, const float* __restrict__ entropy,
+                           const float* __restrict__ g_logprob, const float* __restrict__ g_entropy,
+                           __nv_bfloat16* __restrict__ dlogits, long long ldd) {
+  const long long row = blockIdx.x;
+  const float* x = logits + row * ld;
+  __nv_bfloat16* d = dlogits + row * ldd;
+  const int t = targets[row];
+  const float glp = (t >= 0 && t < V) ? g_logprob[row] : 0.f;
+  const float gent = g_entropy != nullptr ? g_entropy[row] : 0.f;
+  const float H = entropy != nullptr ? entropy[row] : 0.f;
+  const float l = lse[row];
+  for (int i = threadIdx.x * 2; i < V; i += ROW_THREADS * 2) {
+    float o[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int c = i + j;
+      if (c < V) {
+        const float lp = x[c] - l;
+        const float p = __expf(lp);
+        o[j] = glp * ((c == t ? 1.f : 0.f) - p) - gent * p * (lp + H);
+      } else {
+        o[j] = 0.f;
+      }
+    }
+    if (i + 1 < V && ((ldd & 1) == 0)) {
+      *reinterpret_cast<uint32_t*>(d + i) = pack_bf16x2(o[0], o[1]);
+    } else {
+      d[i] = __float2bfloat16_rn(o[0]);
+      if (i + 1 < V) d[i + 1] = __float2bfloat16_rn(o[1]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm backward. y = w * xhat, xhat = x * rstd.  dx = rstd * (g - xhat * mean(g * xhat)),
+// g = dy * w. dw partials: one row of [gridDim.x, d] fp32 per CTA (summed by the caller).
+// ------------------------------------------------------------------------------------------
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
+                                   float* __restrict__ dw_partial, long long rows, int d, float eps) {
+  extern __shared__ float dw_acc[];  // [d]
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (long long row = (long long)blockIdx.x * nw + wid; row < rows; row += (long long)gridDim.x * nw) {
+    const __nv_bfloat16* xr = x + row * d;
+    const __nv_bfloat16* gr = dy + row * d;
+    float ss = 0.f, dot = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float xv = __bfloat162float(xr[i]);
+      ss += xv * xv;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    for (int i = lane; i < d; i += 32) {
+      const float xh = __bfloat162float(xr[i]) * rstd;
+      const float g = __bfloat162float(gr[i]) * __bfloat162float(w[i]);
+      dot += g * xh;
+    }
+    dot = warp_sum(dot) / (float)d;
+    for (int i = lane; i < d; i += 32) {
+      const float xh = __bfloat162float(xr[i]) * rstd;
+      const float dyv = __bfloat162float(gr[i]);
+      const float g = dyv * __bfloat162float(w[i]);
+      dx[row * d + i] = __float2bfloat16_rn(rstd * (g - xh * dot));
+      atomicAdd(&dw_acc[i], dyv * xh);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_partial[(long long)blockIdx.x * d + i] = dw_acc[i];
+}
+
+// ------------------------------------------------------------------------------------------
+// RoPE on [T, H, D] (training: no cache). sign = +1 forward, -1 backward (inverse rotation).
+// fp32 math, one rounding at the end.
+// ------------------------------------------------------------------------------------------
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                            const int* __restrict__ positions, const float2* __restrict__ cos_sin, long long T, int H,
+                            int D, long long ldx, long long ldy, int max_pos, float sign) {
+  const int half = D >> 1;
+  const long long n = T * H * half;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % half);
+    const long long th = i / half;
+    const int h = (int)(th % H);
+    const long long t = th / H;
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float2 cs = cos_sin[(long long)pos * half + j];
+    const float s = cs.y * sign;
+    const __nv_bfloat16* xr = x + t * ldx + (long long)h * D;
+    __nv_bfloat16* yr = y + t * ldy + (long long)h * D;
+    const float lo = __bfloat162float(xr[j]), hi = __bfloat162float(xr[j + half]);
+    yr[j] = __float2bfloat16_rn(lo * cs.x - hi * s);
+    yr[j + half] = __float2bfloat16_rn(hi * cs.x + lo * s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Sum of squares partials and AdamW
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename G>
+__global__ void sumsq_partial_kernel(const G* __restrict__ g, long long n, float scale, float* __restrict__ partial) {
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = to_f<G>(g[i]) * scale;
+    acc += v * v;
+  }
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) partial[blockIdx.x] = acc;
+}
+
+// clip_coef: device pointer to min(1, max_norm / (norm + 1e-6)) or null.
+template <typename G>
+__global__ void adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                             const G* __restrict__ grad, __nv_bfloat16* __restrict__ param_bf16, long long n, float lr,
+                             float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                             float grad_scale, const float* __restrict__ clip_coef) {
+  const float clip = clip_coef != nullptr ? *clip_coef : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float g = to_f<G>(grad[i]) * grad_scale * clip;
+    float p = master[i];
+    const float mi = beta1 * m[i] + (1.f - beta1) * g;
+    const float vi = beta2 * v[i] + (1.f - beta2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    p = p * (1.f - lr * weight_decay) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+    master[i] = p;
+    if (param_bf16 != nullptr) param_bf16[i] = __float2bfloat16_rn(p);
+  }
+}
+
+// out (bf16 or fp32) += in (bf16), used for gradient accumulation buffers.
+__global__ void accumulate_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ in, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    acc[i] += __bfloat162float(in[i]);
+}
+
+}  // namespace rb
+
+using namespace rb;
+#define RB_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+static inline unsigned grid_for(long long n, int threads, int cap = 148 * 16) {
+  long long g = (n + threads - 1) / threads;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (unsigned)g;
+}
+
+extern "C" int rb_logprob_entropy_fwd(const float* logits, long long ld, int rows, int V, const int* targets,
+                                      float* logprob, float* lse, float* entropy, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  logprob_entropy_fwd_kernel<<<rows, ROW_THREADS, 0, s>>>(logits, ld, V, targets, logprob, lse, entropy);
+  return RB_OK();
+}
+extern "C" int rb_logprob_entropy_bwd(const float* logits, long long ld, int rows, int V, const int* targets,
+                                      const float* lse, const float* entropy, const float* g_logprob,
+                                      const float* g_entropy, void* dlogits, long long ldd, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  logprob_entropy_bwd_kernel<<<rows, ROW_THREADS, 0, s>>>(logits, ld, V, targets, lse, entropy, g_logprob, g_entropy,
+                                                         (__nv_bfloat16*)dlogits, ldd);
+  return RB_OK();
+}
+extern "C" int rb_rmsnorm_bwd_num_partials() { return 148 * 2; }
+extern "C" int rb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw_partial,
+                              long long rows, int d, float eps, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  const int grid = rb_rmsnorm_bwd_num_partials();
+  rmsnorm_bwd_kernel<<<grid, 256, d * sizeof(float), s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                          (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, dw_partial,
+                                                          rows, d, eps);
+  return RB_OK();
+}
+extern "C" int rb_rope(const void* x, void* y, const int* positions, const void* cos_sin, long long T, int H, int D,
+                       long long ldx, long long ldy, int max_pos, int backward, cudaStream_t s) {
+  if (T <= 0) return 0;
+  const long long n = T * H * (D / 2);
+  rope_kernel<<<grid_for(n, 256), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, positions,
+                                               (const float2*)cos_sin, T, H, D, ldx, ldy, max_pos,
+                                               backward ? -1.f : 1.f);
+  return RB_OK();
+}
+extern "C" int rb_sumsq_num_partials() { return 148 * 4; }
+extern "C" int rb_sumsq_partial(const void* g, long long n, int grad_is_f32, float scale, float* partial,
+                                cudaStream_t s) {
+  const int grid = rb_sumsq_num_partials();
+  if (grad_is_f32) sumsq_partial_kernel<float><<<grid, ROW_THREADS, 0, s>>>((const float*)g, n, scale, partial);
+  else sumsq_partial_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, s>>>((const __nv_bfloat16*)g, n, scale, partial);
+  return RB_OK();
+}
+extern "C" int rb_adamw(float* master, float* m, float* v, const void* grad, int grad_is_f32, void* param_bf16,
+                        long long n, float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                        float grad_scale, const float* clip_coef, cudaStream_t s) {
+  if (n <= 0) return 0;
+  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  const unsigned grid = grid_for(n, 256, 148 * 8);
+  if (grad_is_f32)
+    adamw_kernel<float><<<grid, 256, 0, s>>>(master, m, v, (const float*)grad, (__nv_bfloat16*)param_bf16, n, lr, beta1,
+                                             beta2, eps, weight_decay, bc1, bc2, grad_scale, clip_coef);
+  else
+    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(master, m, v, (const __nv_bfloat16*)grad,
+                                                     (__nv_bfloat16*)param_bf16, n, lr, beta1, beta2, eps, weight_decay,
+                                                     bc1, bc2, grad_scale, clip_coef);
+  return RB_OK();
+}
+extern "C" int rb_accumulate_f32_bf16(float* acc, const void* in, long long n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  accumulate_kernel<<<grid_for(n, 256), 256, 0, s>>>(acc, (const __nv_bfloat16*)in, n);
+  return RB_OK();
+}
