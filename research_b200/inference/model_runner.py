@@ -77,6 +77,12 @@ class ModelRunner:
             self.graph_batch_sizes += (max_batch,)
         self.scale = 1.0 / math.sqrt(self.D)
         self.launches_per_decode_step = 0
+        # fused GEMM+all-reduce works on row counts that split evenly into 8-row vectors per rank
+        self.row_align = tp.row_align if tp is not None else 1
+        if self.row_align > 1:
+            ra = self.row_align
+            assert max_batch % ra == 0, f"max_batch must be a multiple of {ra} with tensor parallelism"
+            self.graph_batch_sizes = tuple(sorted({-(-b // ra) * ra for b in self.graph_batch_sizes}))
 
         bf = dtype
         self.dtype = dtype
@@ -129,7 +135,7 @@ class ModelRunner:
         self.d_out_tokens = self.out_dev[0:mb]
         self.d_out_logprobs = self.out_dev[mb:2 * mb].view(torch.float32)
         # activations for decode
-        self.a_x = torch.empty(mb, d, dtype=bf, device=device)
+        self.a_x = tp.alloc((mb, d), bf) if (tp is not None and self.on_gpu) else torch.empty(mb, d, dtype=bf, device=device)
         self.a_h = torch.empty(mb, d, dtype=bf, device=device)
         self.a_qkv = torch.empty(mb, qkv_rows, dtype=bf, device=device)
         self.a_q = torch.empty(mb, self.Hq * self.D, dtype=bf, device=device)
@@ -147,6 +153,8 @@ class ModelRunner:
         T = max_prefill_tokens
         self.pf_host = self._pinned(torch.zeros(3 * T + 6 * (mb + 1), dtype=torch.int32))
         self.pf_dev = torch.zeros_like(self.pf_host, device=device)
+        # residual stream of the prefill pass; symmetric when ranks all-reduce into it
+        self.pf_x = tp.alloc((T + self.row_align, d), bf) if (tp is not None and self.on_gpu) else None
 
     def _pinned(self, t: torch.Tensor) -> torch.Tensor:
         return t.pin_memory() if self.on_gpu else t
@@ -296,7 +304,7 @@ class ModelRunner:
         block-table columns. Device->host: one copy of tokens|logprobs into ``out_host``.
         The caller synchronises before reading ``out_host``.
         """
-        bk = self.bucket(n) if self.use_cuda_graphs else n
+        bk = self.bucket(n) if (self.use_cuda_graphs or self.row_align > 1) else n
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
         self.bt_dev[:n, :max_blocks].copy_(self.bt_host[:n, :max_blocks], non_blocking=True)
         g = self.graphs.get(bk)
@@ -308,7 +316,7 @@ class ModelRunner:
 
     def stage_decode_padding(self, n: int) -> None:
         """Mark rows n..bucket as padding (no KV write, empty context)."""
-        bk = self.bucket(n) if self.use_cuda_graphs else n
+        bk = self.bucket(n) if (self.use_cuda_graphs or self.row_align > 1) else n
         mb = self.max_batch
         mh = self.meta_host
         if bk > n:
@@ -327,27 +335,34 @@ class ModelRunner:
         """
         cfg = self.cfg
         dev = self.device
+        o = self._pf_offsets()
+        Tp = -(-T // self.row_align) * self.row_align  # padded row count (tensor parallel only)
+        if Tp > T:
+            ph = self.pf_host
+            ph[o["tokens"] + T:o["tokens"] + Tp] = 0
+            ph[o["positions"] + T:o["positions"] + Tp] = 0
+            ph[o["slots"] + T:o["slots"] + Tp] = -1   # padding rows never touch the KV cache
         self.pf_dev.copy_(self.pf_host, non_blocking=True)
         self.bt_dev[:rows, :max_blocks].copy_(self.bt_host[:rows, :max_blocks], non_blocking=True)
-        o = self._pf_offsets()
         pd = self.pf_dev
-        tokens = pd[o["tokens"]:o["tokens"] + T]
-        positions = pd[o["positions"]:o["positions"] + T]
-        slots = pd[o["slots"]:o["slots"] + T]
+        tokens = pd[o["tokens"]:o["tokens"] + Tp]
+        positions = pd[o["positions"]:o["positions"] + Tp]
+        slots = pd[o["slots"]:o["slots"] + Tp]
         cu_q = pd[o["cu_q"]:o["cu_q"] + rows + 1]
         seq_lens = pd[o["seq_lens"]:o["seq_lens"] + rows]
         sample_rows = pd[o["sample_rows"]:o["sample_rows"] + rows]
         temps = pd[o["temps"]:o["temps"] + rows].view(torch.float32)
         seeds = pd[o["seeds"]:o["seeds"] + 2 * rows].view(torch.int64)
-        x = ops.embedding(tokens, self.embed)
+        x = ops.embedding(tokens, self.embed, out=self.pf_x[:Tp] if self.pf_x is not None else None)
         h = torch.empty_like(x)
         bt = self.bt_dev[:rows]
+        attn_out = torch.zeros(Tp, self.Hq, self.D, dtype=x.dtype, device=dev) if Tp > T else None
 
         def attn_fn(li, q):
             return ops.paged_prefill(q, self.k_cache[li], self.v_cache[li], bt, cu_q, seq_lens, max_new, self.scale,
-                                     cfg.sliding_window)
+                                     cfg.sliding_window, out=attn_out)
 
-        self._forward_layers(x, h, T, positions, slots, attn_fn, static=False)
+        self._forward_layers(x, h, Tp, positions, slots, attn_fn, static=False)
         last = ops.embedding(sample_rows, x)  # row gather of the last token of every sequence
         hl = ops.rmsnorm(last, self.final_norm, cfg.rms_norm_eps)
         logits = ops.gemm(hl, self.lm_head, out=self.a_logits[:rows], out_f32=True)

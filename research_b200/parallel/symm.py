@@ -1,0 +1,158 @@
+"""Symmetric peer memory and flag-based synchronisation between the GPUs of one node.
+
+``PeerComm`` is the transport layer under every fused compute+collective kernel: it allocates
+buffers that every rank maps into its own address space (``torch.distributed._symmetric_memory``
+does the CUDA VMM allocation and the handle exchange; NVLS multicast binding is switched off so
+kernels only use plain peer loads/stores), and it owns the flag words used for barriers and
+ready signals. Flag values are monotonically increasing epochs, so nothing is ever reset.
+
+On CPU (gloo ranks, used by the tests) the same object degrades to ordinary collectives so the
+host-side logic of the training backend and weight sync runs without a GPU.
+
+The reference has no equivalent: its communication is ``torch.distributed`` NCCL calls only
+(rollouts/training/distributed_utils.py:37-360).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops._util import check_rc, status_tensor, stream_handle
+
+MAX_RANKS = 8
+_VP, _I, _LL, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def _lib():
+    lib = _native.load("rb_comm")
+    if not getattr(lib, "_rb_typed", False):
+        PP = ctypes.POINTER(_VP)
+        lib.rb_symm_barrier.argtypes = [PP, _I, _I, _I, _I, _VP, _VP]
+        lib.rb_symm_signal.argtypes = [PP, _I, _I, _I, _I, _VP]
+        lib.rb_symm_wait.argtypes = [_VP, _I, _I, _I, _VP, _VP]
+        lib.rb_rs_reduce.argtypes = [PP, _VP, _I, _I, _I, _I, _LL, _F, _VP, _I, _VP, _VP, _VP]
+        lib.rb_clip_coef.argtypes = [_VP, _I, PP, PP, _I, _I, _I, _I, _F, _VP, _VP, _VP, _VP]
+        lib.rb_adamw_allgather.argtypes = [_VP, _VP, _VP, _VP, PP, _I, _I, _LL, _F, _F, _F, _F, _F, _I, _VP, _VP]
+        lib.rb_reshard_copy.argtypes = [_VP, _I, _LL, _VP]
+        lib.rb_rs_num_partials.restype = _I
+        for f in ("rb_symm_barrier", "rb_symm_signal", "rb_symm_wait", "rb_rs_reduce", "rb_clip_coef",
+                  "rb_adamw_allgather", "rb_reshard_copy"):
+            getattr(lib, f).restype = _I
+        lib._rb_typed = True
+    return lib
+
+
+def ptr_array(ptrs: list[int]):
+    arr = (_VP * MAX_RANKS)()
+    for i, p in enumerate(ptrs):
+        arr[i] = p
+    return arr
+
+
+class SymmBuffer:
+    """A tensor allocated at the same offset on every rank, with every peer's address known."""
+
+    def __init__(self, local: torch.Tensor, peer_ptrs: list[int], handle=None):
+        self.local = local
+        self.peer_ptrs = peer_ptrs
+        self.handle = handle
+
+    def ptrs(self, byte_offset: int = 0):
+        return ptr_array([p + byte_offset for p in self.peer_ptrs])
+
+    def peer_tensor(self, rank: int) -> torch.Tensor:
+        """View of rank ``rank``'s buffer in this process (CUDA only)."""
+        assert self.handle is not None
+        return self.handle.get_buffer(rank, self.local.shape, self.local.dtype)
+
+
+class PeerComm:
+    """Peer-memory context of one process group (one rank per GPU, single node)."""
+
+    NUM_SLOTS = 64
+
+    def __init__(self, group: dist.ProcessGroup | None = None, device: torch.device | None = None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        assert self.world <= MAX_RANKS
+        self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                                 else torch.device("cpu"))
+        self.on_gpu = self.device.type == "cuda"
+        self._epochs = [0] * self.NUM_SLOTS
+        self._next_slot = 1  # slot 0 is the generic barrier
+        if self.on_gpu:
+            # plain peer loads/stores only: never bind these buffers to an NVLink multicast object
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            self.flags = self.alloc((self.NUM_SLOTS, self.world), torch.int32, zero=True)
+            self.norm_slots = self.alloc((self.world,), torch.float32, zero=True)
+            self.barrier_host()
+        else:
+            self.flags = None
+            self.norm_slots = None
+
+    # ---------------------------------------------------------------- allocation
+    def alloc(self, shape, dtype=torch.bfloat16, zero: bool = False) -> SymmBuffer:
+        if not self.on_gpu:
+            t = torch.zeros(shape, dtype=dtype)
+            return SymmBuffer(t, [t.data_ptr()] * self.world)
+        import torch.distributed._symmetric_memory as symm_mem
+
+        t = symm_mem.empty(*shape, dtype=dtype, device=self.device)
+        hdl = symm_mem.rendezvous(t, self.group)
+        if zero:
+            t.zero_()
+        return SymmBuffer(t, [int(p) for p in hdl.buffer_ptrs], hdl)
+
+    def new_slot(self) -> int:
+        s = self._next_slot
+        assert s < self.NUM_SLOTS, "out of flag slots"
+        self._next_slot += 1
+        return s
+
+    def next_epoch(self, slot: int) -> int:
+        self._epochs[slot] += 1
+        return self._epochs[slot]
+
+    # ---------------------------------------------------------------- synchronisation
+    def barrier_host(self) -> None:
+        """Host-level barrier (process group) plus device synchronise; used at set-up only."""
+        if self.on_gpu:
+            torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def barrier(self, slot: int = 0) -> None:
+        """Device-side barrier on the current stream: every rank signals every peer, then waits."""
+        if not self.on_gpu:
+            dist.barrier(self.group)
+            return
+        ep = self.next_epoch(slot)
+        rc = _lib().rb_symm_barrier(self.flags.ptrs(), self.rank, self.world, slot, ep,
+                                    status_tensor(self.device).data_ptr(), stream_handle(self.device))
+        check_rc(rc, "rb_symm_barrier")
+
+    def signal(self, slot: int) -> int:
+        """Publish "my data for this slot is ready" to every peer; returns the epoch signalled."""
+        ep = self.next_epoch(slot)
+        if self.on_gpu:
+            rc = _lib().rb_symm_signal(self.flags.ptrs(), self.rank, self.world, slot, ep, stream_handle(self.device))
+            check_rc(rc, "rb_symm_signal")
+        else:
+            dist.barrier(self.group)
+        return ep
+
+    def wait(self, slot: int, epoch: int) -> None:
+        """Wait (bounded, on the stream) until every peer signalled ``epoch`` on ``slot``."""
+        if self.on_gpu:
+            rc = _lib().rb_symm_wait(self.flags.local.data_ptr(), self.world, slot, epoch,
+                                     status_tensor(self.device).data_ptr(), stream_handle(self.device))
+            check_rc(rc, "rb_symm_wait")
+
+    def flag_ptr(self, slot: int) -> int:
+        """Address of this rank's flag row ``[world]`` for ``slot``."""
+        return self.flags.local.data_ptr() + slot * self.world * 4

@@ -1,0 +1,200 @@
+"""Tensor-parallel linear layers whose collective runs inside the tcgen05 GEMM kernel.
+
+* ``all_gather_gemm``  (column-parallel; activations sharded by rows across ranks): the GEMM's
+  TMA producer pulls the A tiles of remote row slabs straight from the peers' symmetric
+  buffers, tile by tile, while the tensor cores work on the previous tiles.
+* ``fsdp_gemm`` (FSDP parameter shards): same mechanism on the B operand - the weight rows a
+  rank does not own are read from the owning peer inside the first GEMM that consumes them.
+* ``gemm_reduce_scatter`` / ``gemm_all_reduce`` (row-parallel): finished tiles are pushed with
+  peer stores into the owner's staging slab and published with a flag; the owner's epilogue
+  warps sum the partials and write the result (all-reduce: to every peer).
+
+Staging slabs are double buffered: a rank can only enter call i+2 after every peer finished
+call i (its reduce phase waits for all peers' call-(i+1) tiles, which they push only after
+finishing call i), so no barrier is needed between reduce-scatters. After an all-reduce the
+outputs live in peer memory written by other GPUs, so a device-side barrier follows.
+
+The reference has no tensor parallelism in-tree (``EngineConfig.tensor_parallel_size`` is
+unused, rollouts/inference/types.py:25; only ``--tp`` forwarded to an external SGLang).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops._util import check_rc, status_tensor, stream_handle
+from ..ops.gemm import EPI_ALL_REDUCE, EPI_REDUCE_SCATTER, EPI_STORE, RbGemmArgs, _lib as _gemm_lib
+from .symm import PeerComm, SymmBuffer
+
+
+class TensorParallel:
+    def __init__(self, comm: PeerComm, max_rows: int, max_cols: int, expert_parallel: bool = False):
+        self.comm = comm
+        self.rank, self.world = comm.rank, comm.world
+        self.expert_parallel = expert_parallel
+        self.row_align = 8 * self.world
+        self.max_rows = -(-max_rows // self.row_align) * self.row_align
+        self.max_cols = max_cols
+        self._registry: dict[int, SymmBuffer] = {}
+        self._call = 0
+        self._ready_slot = comm.new_slot()
+        if comm.on_gpu:
+            rpr = self.max_rows // self.world
+            self.stage = comm.alloc((2, self.world, rpr, max_cols), torch.bfloat16)
+            self.max_tiles = (-(-rpr // 128)) * (-(-max_cols // 32))
+            self.tile_flags = comm.alloc((2, self.world, self.max_tiles), torch.int32, zero=True)
+            comm.barrier_host()
+
+    # ---------------------------------------------------------------- buffers
+    def alloc(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """Symmetric tensor (same address layout on every rank); remembered by base pointer."""
+        buf = self.comm.alloc(tuple(shape), dtype, zero=True)
+        self._registry[buf.local.data_ptr()] = buf
+        return buf.local
+
+    def symm_of(self, t: torch.Tensor) -> SymmBuffer:
+        buf = self._registry.get(t.data_ptr())
+        assert buf is not None, "tensor was not allocated with TensorParallel.alloc (or is not a row-0 view)"
+        return buf
+
+    # ---------------------------------------------------------------- helpers
+    def _base_args(self, M, N, K, a, w, bn) -> RbGemmArgs:
+        args = RbGemmArgs()
+        args.M, args.N, args.K = M, N, K
+        args.lda, args.ldb = a.stride(0), w.stride(0)
+        args.a_parts = args.b_parts = 1
+        args.bn = bn
+        args.rank, args.world = self.rank, self.world
+        args.status = status_tensor(a.device).data_ptr()
+        return args
+
+    def _launch(self, args: RbGemmArgs, device) -> None:
+        rc = _gemm_lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(device))
+        check_rc(rc, "rb_gemm_bf16_ex(tp)")
+
+    @staticmethod
+    def _pick_bn(rows_per_rank: int, N: int) -> int:
+        return 128 if N >= 2048 and rows_per_rank >= 128 else (64 if N >= 512 else 32)
+
+    # ---------------------------------------------------------------- row-parallel
+    def _reduce(self, a: torch.Tensor, w: torch.Tensor, mode: int, out_ptrs, ldc: int, residual, ldr: int) -> None:
+        M, K = a.shape
+        N = w.shape[0]
+        assert M % self.row_align == 0, f"rows ({M}) must be a multiple of {self.row_align}"
+        assert M <= self.max_rows and N <= self.max_cols
+        rpr = M // self.world
+        bn = self._pick_bn(rpr, N)
+        par = self._call % 2
+        self._call += 1
+        args = self._base_args(M, N, K, a, w, bn)
+        args.a_parts = self.world
+        for i in range(self.world):
+            args.A[i] = a.data_ptr() + i * rpr * a.stride(0) * 2
+        args.B[0] = w.data_ptr()
+        args.epi_mode = mode
+        args.ldc, args.ldr = ldc, ldr
+        args.residual = residual
+        args.reduce_epoch = self._call
+        stage_bytes = self.world * (self.max_rows // self.world) * self.max_cols * 2
+        flag_bytes = self.world * self.max_tiles * 4
+        # staging is addressed as [src_rank][rows_per_rank][N] inside one parity slab
+        for r in range(self.world):
+            args.stage_ptrs[r] = self.stage.peer_ptrs[r] + par * stage_bytes
+            args.flag_ptrs[r] = self.tile_flags.peer_ptrs[r] + par * flag_bytes
+            args.out_ptrs[r] = out_ptrs[r]
+        args.C = out_ptrs[self.rank]
+        self._launch(args, a.device)
+
+    def gemm_all_reduce(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
+        """``x += sum_ranks(a_r @ w_r.T)`` in place on every rank; ``x`` is a symmetric tensor."""
+        if not self.comm.on_gpu:
+            part = a.float() @ w.float().t()
+            dist.all_reduce(part, group=self.comm.group)
+            x.add_(part.to(x.dtype))
+            return
+        buf = self.symm_of(x)
+        self._reduce(a, w, EPI_ALL_REDUCE, buf.peer_ptrs, x.stride(0), x.data_ptr(), x.stride(0))
+        self.comm.barrier()
+
+    def gemm_reduce_scatter(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                            residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``out[M/P, N] = (sum_ranks a_r @ w_r.T)[rank's row slab] (+ residual)``; ``out`` is local."""
+        if not self.comm.on_gpu:
+            part = a.float() @ w.float().t()
+            dist.all_reduce(part, group=self.comm.group)
+            rpr = a.shape[0] // self.world
+            res = part[self.rank * rpr:(self.rank + 1) * rpr]
+            if residual is not None:
+                res = res + residual.float()
+            out.copy_(res.to(out.dtype))
+            return out
+        ptrs = [0] * self.world
+        ptrs[self.rank] = out.data_ptr()
+        self._reduce(a, w, EPI_REDUCE_SCATTER, ptrs, out.stride(0), residual.data_ptr() if residual is not None else None,
+                     residual.stride(0) if residual is not None else 0)
+        return out
+
+    # ---------------------------------------------------------------- column-parallel / FSDP
+    def publish(self) -> int:
+        """Signal that this rank's symmetric operand (activation or weight shard) is complete."""
+        return self.comm.signal(self._ready_slot)
+
+    def all_gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None,
+                        ready_epoch: int | None = None) -> torch.Tensor:
+        """``out[M, N] = concat_ranks(x_shard_r) @ w.T``; ``x_shard`` is a symmetric ``[M/P, K]`` tensor.
+
+        ``ready_epoch`` is the value returned by ``publish()`` on every rank after the shard was
+        written; the kernel's producer warp waits for each peer's flag before its first load
+        from that peer.
+        """
+        rows, K = x_shard.shape
+        N = w.shape[0]
+        if not self.comm.on_gpu:
+            parts = [torch.empty_like(x_shard) for _ in range(self.world)]
+            dist.all_gather(parts, x_shard.contiguous(), group=self.comm.group)
+            res = torch.cat(parts).float() @ w.float().t()
+            if bias is not None:
+                res = res + bias.float()
+            out.copy_(res.to(out.dtype))
+            return out
+        buf = self.symm_of(x_shard)
+        args = self._base_args(rows * self.world, N, K, x_shard, w, 0)
+        args.a_parts = self.world
+        for r in range(self.world):
+            args.A[r] = buf.peer_ptrs[r]
+        args.B[0] = w.data_ptr()
+        args.C, args.ldc = out.data_ptr(), out.stride(0)
+        args.bias = bias.data_ptr() if bias is not None else None
+        args.epi_mode = EPI_STORE
+        if ready_epoch is not None:
+            args.a_ready = self.comm.flag_ptr(self._ready_slot)
+            args.ready_epoch = ready_epoch
+        self._launch(args, x_shard.device)
+        return out
+
+    def fsdp_gemm(self, x: torch.Tensor, w_shard: torch.Tensor, out: torch.Tensor,
+                  ready_epoch: int | None = None) -> torch.Tensor:
+        """``out[M, N] = x @ concat_ranks(w_shard_r).T``; ``w_shard`` is a symmetric ``[N/P, K]`` tensor."""
+        M, K = x.shape
+        rows = w_shard.shape[0]
+        if not self.comm.on_gpu:
+            parts = [torch.empty_like(w_shard) for _ in range(self.world)]
+            dist.all_gather(parts, w_shard.contiguous(), group=self.comm.group)
+            out.copy_((x.float() @ torch.cat(parts).float().t()).to(out.dtype))
+            return out
+        buf = self.symm_of(w_shard)
+        args = self._base_args(M, rows * self.world, K, x, w_shard, 0)
+        args.b_parts = self.world
+        args.A[0] = x.data_ptr()
+        for r in range(self.world):
+            args.B[r] = buf.peer_ptrs[r]
+        args.C, args.ldc = out.data_ptr(), out.stride(0)
+        args.epi_mode = EPI_STORE
+        if ready_epoch is not None:
+            args.b_ready = self.comm.flag_ptr(self._ready_slot)
+            args.ready_epoch = ready_epoch
+        self._launch(args, x.device)
+        return out

@@ -1,0 +1,201 @@
+"""Worker run by the multi-rank tests: ``torchrun --nproc-per-node N multi_rank_worker.py <device> <cases>``.
+
+Each case checks a fused compute+collective path against a plain PyTorch fp32 reference built
+from all ranks' data (every rank regenerates every rank's inputs from seeds). With ``cpu`` the
+ranks are gloo processes and the host-side logic runs on the collective fallbacks.
+"""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from research_b200.parallel.fsdp import FlatBuckets, ShardedAdamW  # noqa: E402
+from research_b200.parallel.symm import PeerComm  # noqa: E402
+from research_b200.parallel.tp import TensorParallel  # noqa: E402
+
+
+def rnd(shape, seed, dev, dtype, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev)
+
+
+def close(got, want, atol, rtol, what):
+    err = (got.float().cpu() - want.float().cpu()).abs()
+    tol = atol + rtol * want.float().cpu().abs()
+    assert (err <= tol).all(), f"{what}: max err {err.max().item():.4g}"
+
+
+def case_barrier(comm, dev, dt):
+    for _ in range(5):
+        comm.barrier()
+    ep = comm.signal(comm.new_slot())
+    assert ep == 1
+
+
+def case_tp_gemms(comm, dev, dt):
+    W = comm.world
+    tp = TensorParallel(comm, max_rows=512, max_cols=1024)
+    for (M, N, K) in [(64 * W, 256, 128), (128 * W, 896, 512), (256, 1024, 320)]:
+        if M % (8 * W):
+            continue
+        a_all = [rnd((M, K), 100 + r, dev, dt) for r in range(W)]
+        w_all = [rnd((N, K), 200 + r, dev, dt, 0.1) for r in range(W)]
+        full = sum(a.float() @ w.float().t() for a, w in zip(a_all, w_all))
+        # all-reduce into a symmetric residual stream
+        x = tp.alloc((512, N), dt)
+        x0 = rnd((M, N), 7, dev, dt)
+        x[:M].copy_(x0)
+        comm.barrier()
+        tp.gemm_all_reduce(a_all[comm.rank], w_all[comm.rank], x[:M])
+        close(x[:M], full + x0.float(), 0.08 * K ** 0.5 / 4 + 0.05, 0.02, f"gemm_all_reduce {M}x{N}x{K}")
+        # twice in a row exercises the double-buffered staging
+        tp.gemm_all_reduce(a_all[comm.rank], w_all[comm.rank], x[:M])
+        close(x[:M], 2 * full + x0.float(), 0.15 * K ** 0.5 / 4 + 0.1, 0.02, "gemm_all_reduce x2")
+        # reduce-scatter
+        rpr = M // W
+        out = torch.zeros(rpr, N, dtype=dt, device=dev)
+        res = rnd((rpr, N), 9 + comm.rank, dev, dt)
+        tp.gemm_reduce_scatter(a_all[comm.rank], w_all[comm.rank], out, residual=res)
+        close(out, full[comm.rank * rpr:(comm.rank + 1) * rpr] + res.float(), 0.08 * K ** 0.5 / 4 + 0.05, 0.02,
+              f"gemm_reduce_scatter {M}x{N}x{K}")
+        comm.barrier()
+    # all-gather -> GEMM (activation shards) and FSDP weight shards read from peers in the GEMM
+    rows, K, N = 128, 256, 384
+    xs = tp.alloc((rows, K), dt)
+    shards = [rnd((rows, K), 300 + r, dev, dt) for r in range(W)]
+    xs.copy_(shards[comm.rank])
+    w = rnd((N, K), 5, dev, dt, 0.1)
+    ep = tp.publish()
+    out = torch.empty(rows * W, N, dtype=dt, device=dev)
+    tp.all_gather_gemm(xs, w, out, ready_epoch=ep)
+    close(out, torch.cat(shards).float() @ w.float().t(), 0.1, 0.02, "all_gather_gemm")
+    ws = tp.alloc((N // W if N % W == 0 else N, K), dt)
+    wsh = [rnd((ws.shape[0], K), 400 + r, dev, dt, 0.1) for r in range(W)]
+    ws.copy_(wsh[comm.rank])
+    xin = rnd((192, K), 6, dev, dt)
+    ep = tp.publish()
+    out2 = torch.empty(192, ws.shape[0] * W, dtype=dt, device=dev)
+    tp.fsdp_gemm(xin, ws, out2, ready_epoch=ep)
+    close(out2, xin.float() @ torch.cat(wsh).float().t(), 0.1, 0.02, "fsdp_gemm")
+    comm.barrier()
+
+
+def case_sharded_adamw(comm, dev, dt):
+    W = comm.world
+    shapes = [("layers.0.a", (64, 48)), ("layers.0.b", (48,)), ("layers.1.a", (40, 64)), ("head", (128, 64))]
+    chunk_of = lambda n: 0 if n.startswith("layers.0") else (1 if n.startswith("layers.1") else 2)  # noqa: E731
+    b = FlatBuckets(comm, shapes, chunk_of, dtype=dt)
+    init = {n: rnd(s, 10 + i, dev, dt) for i, (n, s) in enumerate(shapes)}
+    for n, _ in shapes:
+        b.param_view(n).copy_(init[n])
+    comm.barrier()
+    opt = ShardedAdamW(b, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0)
+    # reference: torch AdamW on fp32 copies with the rank-averaged gradient and the same clipping
+    ref = {n: init[n].float().cpu().clone().requires_grad_(True) for n, _ in shapes}
+    ropt = torch.optim.AdamW(ref.values(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(3):
+        grads_all = [{n: rnd(s, 1000 * step + 50 * r + i, dev, dt, 0.5) for i, (n, s) in enumerate(shapes)} for r in range(W)]
+        for n, _ in shapes:
+            b.grad_view(n).copy_(grads_all[comm.rank][n])
+        opt.reduce_chunk(2)  # chunks may be reduced early, in any order (overlap with backward)
+        norm = opt.step()
+        for n, _ in shapes:
+            ref[n].grad = sum(g[n].float().cpu() for g in grads_all) / W
+        ref_norm = torch.nn.utils.clip_grad_norm_(ref.values(), 1.0)
+        ropt.step()
+        assert abs(float(norm) - float(ref_norm)) < 2e-2 * float(ref_norm) + 1e-3, (float(norm), float(ref_norm))
+        for n, _ in shapes:
+            close(b.param_view(n), ref[n].detach(), 2e-2, 2e-2, f"adamw step {step} {n}")
+        assert float(b.grads.abs().sum()) == 0.0
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
+
+
+def case_weight_sync_and_tp_engine(comm, dev, dt):
+    from research_b200.inference import EngineConfig, InferenceEngine, SamplingParams
+    from research_b200.models import get_preset, init_random_weights
+    from research_b200.models.weights import param_shapes
+    from research_b200.parallel.weight_sync import sync_engine_from_buckets
+
+    W = comm.world
+    cfg = get_preset("tiny-qwen2", num_layers=2, init_std=0.05)
+    w0 = {k: v.to(dt) for k, v in init_random_weights(cfg, seed=0).items()}
+    w1 = {k: v.to(dt) for k, v in init_random_weights(cfg, seed=1).items()}
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (33, 50, 18, 64)]
+    ecfg = EngineConfig(max_batch_size=8, max_model_len=256, num_kv_blocks=128, ignore_eos=True, graph_batch_sizes=(8,))
+    # single-rank engine as the oracle for the TP engine
+    solo = InferenceEngine(ecfg, cfg, w0, device=dev)
+    want = solo.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    # ---- weight sync: rank 0's flat bucket is the trainer; every rank's engine pulls from it ----
+    b = FlatBuckets(comm, list(param_shapes(cfg).items()), dtype=dt)
+    if comm.rank == 0:
+        for n in b.specs:
+            b.param_view(n).copy_(w1[n])
+    comm.barrier()
+    if dev.type == "cuda":
+        sync_engine_from_buckets(solo, b, src_rank=0, comm=comm)  # every rank pulls rank 0's bucket over NVLink
+    else:
+        sync_engine_from_buckets(solo, _bcast_buckets(b, comm))
+    assert solo.get_weight_version() == 1
+    oracle1 = InferenceEngine(ecfg, cfg, w1, device=dev)
+    a = solo.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    c = oracle1.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    assert [s.completion_tokens for s in a] == [s.completion_tokens for s in c], "synced engine differs from fresh engine"
+    assert all(s.weight_version == 1 and s.cached_tokens == 0 for s in a)
+    solo.shutdown()
+    oracle1.shutdown()
+    # ---- tensor-parallel engine over the fused GEMM + all-reduce kernel ----
+    tp = TensorParallel(comm, max_rows=2048, max_cols=max(cfg.hidden_size, 1024))
+    tcfg = EngineConfig(max_batch_size=16, max_model_len=256, num_kv_blocks=128, ignore_eos=True, graph_batch_sizes=(16,))
+    eng = InferenceEngine(tcfg, cfg, w0, device=dev, tp=tp)
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    same = sum(x.completion_tokens == y.completion_tokens for x, y in zip(got, want))
+    assert same >= len(prompts) - 1, f"TP engine diverges from single-GPU engine ({same}/{len(prompts)})"
+    for x, y in zip(got, want):
+        if x.completion_tokens == y.completion_tokens:
+            assert max(abs(p - q) for p, q in zip(x.logprobs, y.logprobs)) < 0.05
+    eng.shutdown()
+    _ = W
+
+
+def _bcast_buckets(b, comm):
+    dist.broadcast(b.params, src=0, group=comm.group)
+    return b
+
+
+CASES = {"barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
+         "weight_sync_tp_engine": case_weight_sync_and_tp_engine}
+
+
+def main():
+    device = sys.argv[1]
+    cases = sys.argv[2].split(",") if len(sys.argv) > 2 else list(CASES)
+    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", "0"))
+    if device == "cuda":
+        torch.cuda.set_device(local)
+        dev, dt = torch.device("cuda", local), torch.bfloat16
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        dev, dt = torch.device("cpu"), torch.float32
+        dist.init_process_group("gloo")
+    comm = PeerComm(device=dev)
+    for name in cases:
+        CASES[name](comm, dev, dt)
+        if device == "cuda":
+            from research_b200.ops import check_status
+
+            torch.cuda.synchronize()
+            check_status(dev)
+        dist.barrier()
+        if rank == 0:
+            print(f"CASE_OK {name}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
