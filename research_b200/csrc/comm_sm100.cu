@@ -30,13 +30,21 @@ namespace rb {
 struct PeerPtrs { void* p[RB_MAX_RANKS]; };
 
 // flags: each rank owns int flags[slots][world] in symmetric memory; peer r writes [slot][r].
-__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch, int* status) {
+// The epoch lives in device memory (counter) so that a barrier captured in a CUDA graph uses a
+// fresh epoch on every replay: epoch = *counter + 1, stored back once every peer arrived.
+__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch, int* counter,
+                                    int* status) {
+  __shared__ int ep;
+  if (threadIdx.x == 0) ep = counter != nullptr ? *counter + 1 : epoch;
+  __syncthreads();
   __threadfence_system();
   const int r = threadIdx.x;
   if (r < world) {
-    st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, epoch);
-    wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, epoch, status);
+    st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, ep);
+    wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, ep, status);
   }
+  __syncthreads();
+  if (threadIdx.x == 0 && counter != nullptr) *counter = ep;
 }
 __global__ void symm_signal_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch) {
   __threadfence_system();
@@ -230,10 +238,10 @@ static PeerPtrs make_ptrs(void* const* p, int world) {
   return o;
 }
 
-extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int slot, int epoch, int* status,
-                               cudaStream_t s) {
+extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int slot, int epoch, int* counter,
+                               int* status, cudaStream_t s) {
   if (world < 1 || world > RB_MAX_RANKS) return -1;
-  symm_barrier_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch, status);
+  symm_barrier_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch, counter, status);
   return RB_OK();
 }
 extern "C" int rb_symm_signal(void* const* flag_ptrs, int rank, int world, int slot, int epoch, cudaStream_t s) {

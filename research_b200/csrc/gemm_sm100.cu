@@ -79,6 +79,9 @@ struct GemmParams {
   void* out_ptrs[RB_MAX_PARTS];     // all-reduce: peer r's output [M, ldc]; RS: out_ptrs[rank]
   int reduce_epoch;
   int* status;
+  int* epoch_counter;
+  int* cta_ticket;
+  long long stage_parity_bytes, flag_parity_bytes;
 };
 
 __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
@@ -153,6 +156,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
   volatile int* abortp = &abort_flag;
+  // epoch of this reduce call: a host constant, or (graph replay) one past the device counter
+  int reduce_epoch = p.reduce_epoch;
+  long long stage_off = 0, flag_off = 0;
+  if (p.epoch_counter != nullptr) {
+    reduce_epoch = ld_relaxed_sys(p.epoch_counter) + 1;
+    stage_off = (reduce_epoch & 1) * p.stage_parity_bytes;
+    flag_off = (reduce_epoch & 1) * p.flag_parity_bytes;
+  }
 
   // Tile order. In reduce modes, rank r visits the row slab owned by rank r+1 first and its
   // own slab last so that every owner finds its partials early.
@@ -337,7 +348,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
             epi_store_row_chunk(p, v, row, col, ncols);
           } else {
             // push the bf16 partial into the owner's staging slab [src_rank][row_in][N]
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.stage_ptrs[m_part]) +
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[m_part]) + stage_off) +
                                  ((long long)p.rank * rows_per_rank + row_in) * p.N + col;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -364,8 +375,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (!ok) break;
         if (warp == 2 && lane == 0) {
           const int tile_in_part = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
-          int* f = p.flag_ptrs[m_part] + (long long)p.rank * (m_tiles_per_part * num_n_tiles) + tile_in_part;
-          st_release_sys(f, p.reduce_epoch);
+          int* f = reinterpret_cast<int*>(reinterpret_cast<char*>(p.flag_ptrs[m_part]) + flag_off) +
+                   (long long)p.rank * (m_tiles_per_part * num_n_tiles) + tile_in_part;
+          st_release_sys(f, reduce_epoch);
         }
       }
     }
@@ -373,14 +385,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     // ---------------- reduce phase: sum the P partials of the tiles this rank owns ----------
     if (p.epi_mode != RB_EPI_STORE && ok) {
       const int tiles_owned = m_tiles_per_part * num_n_tiles;
-      const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.stage_ptrs[p.rank]);
-      const int* flags = p.flag_ptrs[p.rank];
+      const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(p.stage_ptrs[p.rank]) + stage_off);
+      const int* flags = reinterpret_cast<const int*>(reinterpret_cast<const char*>(p.flag_ptrs[p.rank]) + flag_off);
       const int et = (warp - 2) * 32 + lane;  // 0..127
       for (int ot = blockIdx.x; ot < tiles_owned && ok; ot += gridDim.x) {
         const int mt = ot / num_n_tiles, nt = ot % num_n_tiles;
         // wait for every source rank's copy of this tile
         if (et < p.world) {
-          if (!wait_flag_ge(flags + (long long)et * tiles_owned + ot, p.reduce_epoch, p.status)) *abortp = 1;
+          if (!wait_flag_ge(flags + (long long)et * tiles_owned + ot, reduce_epoch, p.status)) *abortp = 1;
         }
         ok = epi_sync();
         if (!ok || *abortp) { ok = false; break; }
@@ -439,6 +451,15 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (p.epoch_counter != nullptr && threadIdx.x == 0) {
+    // every CTA read the counter before arriving here, so the last one may advance it
+    __threadfence();
+    if (atomicAdd(p.cta_ticket, 1) == (int)gridDim.x - 1) {
+      *p.cta_ticket = 0;
+      *p.epoch_counter = reduce_epoch;
+      __threadfence();
+    }
   }
 }
 
@@ -571,6 +592,11 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.rank = a->rank; p.world = a->world < 1 ? 1 : a->world;
   p.reduce_epoch = a->reduce_epoch;
   p.status = a->status;
+  p.epoch_counter = a->epoch_counter;
+  p.cta_ticket = a->cta_ticket;
+  p.stage_parity_bytes = a->stage_parity_bytes;
+  p.flag_parity_bytes = a->flag_parity_bytes;
+  if (p.epoch_counter != nullptr && p.cta_ticket == nullptr) return -1;
   if (p.epi_mode != RB_EPI_STORE) {
     if (a->a_parts != p.world || a->out_f32) return -1;
     if (p.a_rows_per_part % 8 != 0) return -1;

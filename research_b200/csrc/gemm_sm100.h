@@ -37,6 +37,13 @@ typedef struct RbGemmArgs {
   int* flag_ptrs[RB_MAX_PARTS];
   void* out_ptrs[RB_MAX_PARTS];
   int* status;                   // device int, 0 = ok, else rb::StatusCode
+  // Reduce modes under CUDA-graph replay: when epoch_counter is set the kernel uses
+  // epoch = *epoch_counter + 1 (the last CTA to finish stores it back), and picks the staging /
+  // flag slab by epoch parity, so a captured launch stays correct on every replay.
+  int* epoch_counter;
+  int* cta_ticket;
+  long long stage_parity_bytes;
+  long long flag_parity_bytes;
 } RbGemmArgs;
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);

@@ -51,6 +51,10 @@ class RbGemmArgs(ctypes.Structure):
         ("flag_ptrs", ctypes.c_void_p * RB_MAX_PARTS),
         ("out_ptrs", ctypes.c_void_p * RB_MAX_PARTS),
         ("status", ctypes.c_void_p),
+        ("epoch_counter", ctypes.c_void_p),
+        ("cta_ticket", ctypes.c_void_p),
+        ("stage_parity_bytes", ctypes.c_longlong),
+        ("flag_parity_bytes", ctypes.c_longlong),
     ]
 
 

@@ -1,0 +1,149 @@
+"""Training-side kernel wrappers (csrc/train_sm100.cu) with PyTorch reference twins."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native
+from ._util import check_rc, ptr, stream_handle
+
+c_int, c_ll, c_float, c_vp = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def _lib() -> ctypes.CDLL:
+    lib = _native.load("rb_train")
+    if not getattr(lib, "_rb_typed", False):
+        lib.rb_logprob_entropy_fwd.argtypes = [c_vp, c_ll, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp]
+        lib.rb_logprob_entropy_bwd.argtypes = [c_vp, c_ll, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_vp]
+        lib.rb_rmsnorm_bwd.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_float, c_vp]
+        lib.rb_rope.argtypes = [c_vp, c_vp, c_vp, c_vp, c_ll, c_int, c_int, c_ll, c_ll, c_int, c_int, c_vp]
+        lib.rb_sumsq_partial.argtypes = [c_vp, c_ll, c_int, c_float, c_vp, c_vp]
+        lib.rb_adamw.argtypes = [c_vp, c_vp, c_vp, c_vp, c_int, c_vp, c_ll, c_float, c_float, c_float, c_float, c_float,
+                                 c_int, c_float, c_vp, c_vp]
+        lib.rb_accumulate_f32_bf16.argtypes = [c_vp, c_vp, c_ll, c_vp]
+        for f in ("rb_logprob_entropy_fwd", "rb_logprob_entropy_bwd", "rb_rmsnorm_bwd", "rb_rope", "rb_sumsq_partial",
+                  "rb_adamw", "rb_accumulate_f32_bf16", "rb_rmsnorm_bwd_num_partials", "rb_sumsq_num_partials"):
+            getattr(lib, f).restype = c_int
+        lib._rb_typed = True
+    return lib
+
+
+# ---------------------------------------------------------------- log-prob / entropy from logits
+def logprob_entropy_reference(logits: torch.Tensor, targets: torch.Tensor, need_entropy: bool = True):
+    lp_all = torch.log_softmax(logits.float(), -1)
+    lse = torch.logsumexp(logits.float(), -1)
+    safe = targets.long().clamp(min=0)
+    lp = lp_all.gather(-1, safe[:, None]).squeeze(-1)
+    lp = torch.where(targets >= 0, lp, torch.zeros_like(lp))
+    ent = -(lp_all.exp() * lp_all).sum(-1) if need_entropy else None
+    return lp, lse, ent
+
+
+def logprob_entropy_fwd(logits: torch.Tensor, targets: torch.Tensor, need_entropy: bool = True):
+    """Per-row ``log p(target)``, log-sum-exp and entropy from fp32 logits ``[R, V]``."""
+    if not logits.is_cuda:
+        return logprob_entropy_reference(logits, targets, need_entropy)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and targets.dtype == torch.int32
+    R, V = logits.shape
+    lp = torch.empty(R, dtype=torch.float32, device=logits.device)
+    lse = torch.empty_like(lp)
+    ent = torch.empty_like(lp) if need_entropy else None
+    rc = _lib().rb_logprob_entropy_fwd(ptr(logits), logits.stride(0), R, V, ptr(targets), ptr(lp), ptr(lse), ptr(ent),
+                                       stream_handle(logits.device))
+    check_rc(rc, "rb_logprob_entropy_fwd")
+    return lp, lse, ent
+
+
+def logprob_entropy_bwd(logits, targets, lse, entropy, g_logprob, g_entropy, out: torch.Tensor | None = None):
+    """``dlogits`` (bf16) for upstream gradients of the per-row log-prob and entropy."""
+    if not logits.is_cuda:
+        lp_all = logits.float() - lse[:, None]
+        p = lp_all.exp()
+        onehot = torch.zeros_like(p)
+        valid = targets >= 0
+        onehot[valid, targets[valid].long()] = 1.0
+        d = (g_logprob * valid)[:, None] * (onehot - p)
+        if g_entropy is not None:
+            d = d - g_entropy[:, None] * p * (lp_all + entropy[:, None])
+        return d
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty(R, V, dtype=torch.bfloat16, device=logits.device)
+    rc = _lib().rb_logprob_entropy_bwd(ptr(logits), logits.stride(0), R, V, ptr(targets), ptr(lse), ptr(entropy),
+                                       ptr(g_logprob), ptr(g_entropy), ptr(out), out.stride(0), stream_handle(logits.device))
+    check_rc(rc, "rb_logprob_entropy_bwd")
+    return out
+
+
+# ---------------------------------------------------------------- RMSNorm backward
+def rmsnorm_bwd(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, eps: float):
+    """Returns ``(dx, dw)`` with dw in fp32."""
+    if not x.is_cuda:
+        xf = x.float().detach().requires_grad_(True)
+        wf = w.float().detach().requires_grad_(True)
+        y = wf * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps))
+        y.backward(dy.float())
+        return xf.grad.to(x.dtype), wf.grad
+    d = x.shape[-1]
+    x2, dy2 = x.reshape(-1, d), dy.reshape(-1, d)
+    assert x2.is_contiguous() and dy2.is_contiguous() and d * 4 <= 48 * 1024
+    dx = torch.empty_like(x2)
+    nparts = _lib().rb_rmsnorm_bwd_num_partials()
+    part = torch.empty(nparts, d, dtype=torch.float32, device=x.device)
+    rc = _lib().rb_rmsnorm_bwd(ptr(x2), ptr(w), ptr(dy2), ptr(dx), ptr(part), x2.shape[0], d, eps, stream_handle(x.device))
+    check_rc(rc, "rb_rmsnorm_bwd")
+    return dx.reshape(x.shape), part.sum(0)
+
+
+# ---------------------------------------------------------------- RoPE (training, no cache)
+def rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, backward: bool = False) -> torch.Tensor:
+    """Rotate ``x [T, H, D]`` (last dim contiguous) by +angle (forward) or -angle (backward)."""
+    T, H, D = x.shape
+    if not x.is_cuda:
+        cs = table[positions.long()]
+        c, s = cs[..., 0][:, None, :], cs[..., 1][:, None, :]
+        if backward:
+            s = -s
+        lo, hi = x[..., : D // 2].float(), x[..., D // 2:].float()
+        return torch.cat([lo * c - hi * s, hi * c + lo * s], -1).to(x.dtype)
+    assert x.stride(2) == 1 and x.stride(1) == D and positions.dtype == torch.int32
+    y = torch.empty(T, H, D, dtype=x.dtype, device=x.device)
+    rc = _lib().rb_rope(ptr(x), ptr(y), ptr(positions), ptr(table), T, H, D, x.stride(0), y.stride(0), table.shape[0],
+                        int(backward), stream_handle(x.device))
+    check_rc(rc, "rb_rope")
+    return y
+
+
+# ---------------------------------------------------------------- optimizer pieces
+def sumsq(g: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Sum of squares of ``g * scale`` as a device scalar (fp32)."""
+    if not g.is_cuda:
+        return (g.float() * scale).pow(2).sum()
+    n = _lib().rb_sumsq_num_partials()
+    part = torch.empty(n, dtype=torch.float32, device=g.device)
+    rc = _lib().rb_sumsq_partial(ptr(g), g.numel(), int(g.dtype == torch.float32), scale, ptr(part), stream_handle(g.device))
+    check_rc(rc, "rb_sumsq_partial")
+    return part.sum()
+
+
+def adamw_step(master, exp_avg, exp_avg_sq, grad, param_bf16, lr, beta1, beta2, eps, weight_decay, step,
+               grad_scale: float = 1.0, clip_coef: torch.Tensor | None = None) -> None:
+    """Fused AdamW on flat tensors: fp32 master + moments, bf16/fp32 grads, bf16 write-back."""
+    if not master.is_cuda:
+        g = grad.float() * grad_scale
+        if clip_coef is not None:
+            g = g * float(clip_coef)
+        exp_avg.mul_(beta1).add_(g, alpha=1 - beta1)
+        exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
+        master.mul_(1 - lr * weight_decay)
+        master.addcdiv_(exp_avg / bc1, (exp_avg_sq / bc2).sqrt() + eps, value=-lr)
+        if param_bf16 is not None:
+            param_bf16.copy_(master.to(param_bf16.dtype))
+        return
+    rc = _lib().rb_adamw(ptr(master), ptr(exp_avg), ptr(exp_avg_sq), ptr(grad), int(grad.dtype == torch.float32),
+                         ptr(param_bf16), master.numel(), lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                         ptr(clip_coef), stream_handle(master.device))
+    check_rc(rc, "rb_adamw")

@@ -137,7 +137,8 @@ class ShardedAdamW:
         scale = grad_scale / comm.world
         if not self.on_gpu:
             g = b.grads[off:off + length].float()
-            dist.all_reduce(g, group=comm.group)
+            if comm.world > 1:
+                dist.all_reduce(g, group=comm.group)
             mine = g[comm.rank * n:(comm.rank + 1) * n] * scale
             self.red[chunk].copy_(mine)
             self._sumsq_cpu += float((mine * mine).sum())
@@ -163,7 +164,8 @@ class ShardedAdamW:
         b1, b2 = self.betas
         if not self.on_gpu:
             t = torch.tensor([self._sumsq_cpu], dtype=torch.float64)
-            dist.all_reduce(t, group=comm.group)
+            if comm.world > 1:
+                dist.all_reduce(t, group=comm.group)
             norm = float(t.sqrt())
             coef = min(1.0, self.max_grad_norm / (norm + 1e-6)) if self.max_grad_norm > 0 else 1.0
             bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
@@ -175,9 +177,12 @@ class ShardedAdamW:
                 p.mul_(1 - self.lr * self.weight_decay)
                 p.addcdiv_(self.exp_avg[c] / bc1, (self.exp_avg_sq[c] / bc2).sqrt() + self.eps, value=-self.lr)
                 off, length = b.chunks[c]
-                parts = [torch.empty_like(p) for _ in range(comm.world)]
-                dist.all_gather(parts, p, group=comm.group)
-                b.params[off:off + length].copy_(torch.cat(parts).to(b.dtype))
+                if comm.world > 1:
+                    parts = [torch.empty_like(p) for _ in range(comm.world)]
+                    dist.all_gather(parts, p, group=comm.group)
+                    b.params[off:off + length].copy_(torch.cat(parts).to(b.dtype))
+                else:
+                    b.params[off:off + length].copy_(p.to(b.dtype))
             b.grads.zero_()
             self._reduced.clear()
             self._sumsq_cpu = 0.0

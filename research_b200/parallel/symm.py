@@ -32,7 +32,7 @@ def _lib():
     lib = _native.load("rb_comm")
     if not getattr(lib, "_rb_typed", False):
         PP = ctypes.POINTER(_VP)
-        lib.rb_symm_barrier.argtypes = [PP, _I, _I, _I, _I, _VP, _VP]
+        lib.rb_symm_barrier.argtypes = [PP, _I, _I, _I, _I, _VP, _VP, _VP]
         lib.rb_symm_signal.argtypes = [PP, _I, _I, _I, _I, _VP]
         lib.rb_symm_wait.argtypes = [_VP, _I, _I, _I, _VP, _VP]
         lib.rb_rs_reduce.argtypes = [PP, _VP, _I, _I, _I, _I, _LL, _F, _VP, _I, _VP, _VP, _VP]
@@ -91,6 +91,8 @@ class PeerComm:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             self.flags = self.alloc((self.NUM_SLOTS, self.world), torch.int32, zero=True)
             self.norm_slots = self.alloc((self.world,), torch.float32, zero=True)
+            # barrier epochs are counted on the device so captured barriers replay correctly
+            self.barrier_counters = torch.zeros(self.NUM_SLOTS, dtype=torch.int32, device=self.device)
             self.barrier_host()
         else:
             self.flags = None
@@ -131,8 +133,8 @@ class PeerComm:
         if not self.on_gpu:
             dist.barrier(self.group)
             return
-        ep = self.next_epoch(slot)
-        rc = _lib().rb_symm_barrier(self.flags.ptrs(), self.rank, self.world, slot, ep,
+        rc = _lib().rb_symm_barrier(self.flags.ptrs(), self.rank, self.world, slot, 0,
+                                    self.barrier_counters.data_ptr() + 4 * slot,
                                     status_tensor(self.device).data_ptr(), stream_handle(self.device))
         check_rc(rc, "rb_symm_barrier")
 
@@ -156,3 +158,41 @@ class PeerComm:
     def flag_ptr(self, slot: int) -> int:
         """Address of this rank's flag row ``[world]`` for ``slot``."""
         return self.flags.local.data_ptr() + slot * self.world * 4
+
+
+class LocalComm(PeerComm):
+    """Single-process, single-rank stand-in: the same kernels run with this GPU as its only peer."""
+
+    def __init__(self, device: torch.device | None = None):  # noqa: D107 - no process group involved
+        self.group = None
+        self.rank, self.world = 0, 1
+        self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                                 else torch.device("cpu"))
+        self.on_gpu = self.device.type == "cuda"
+        self._epochs = [0] * self.NUM_SLOTS
+        self._next_slot = 1
+        if self.on_gpu:
+            self.flags = self.alloc((self.NUM_SLOTS, 1), torch.int32, zero=True)
+            self.norm_slots = self.alloc((1,), torch.float32, zero=True)
+            self.barrier_counters = torch.zeros(self.NUM_SLOTS, dtype=torch.int32, device=self.device)
+        else:
+            self.flags = self.norm_slots = None
+
+    def alloc(self, shape, dtype=torch.bfloat16, zero: bool = False) -> SymmBuffer:
+        t = torch.zeros(shape, dtype=dtype, device=self.device)
+        return SymmBuffer(t, [t.data_ptr()])
+
+    def barrier_host(self) -> None:
+        if self.on_gpu:
+            torch.cuda.synchronize(self.device)
+
+    def barrier(self, slot: int = 0) -> None:
+        if self.on_gpu:
+            super().barrier(slot)
+
+    def signal(self, slot: int) -> int:
+        ep = self.next_epoch(slot)
+        if self.on_gpu:
+            rc = _lib().rb_symm_signal(self.flags.ptrs(), 0, 1, slot, ep, stream_handle(self.device))
+            check_rc(rc, "rb_symm_signal")
+        return ep

@@ -46,6 +46,9 @@ class TensorParallel:
             self.stage = comm.alloc((2, self.world, rpr, max_cols), torch.bfloat16)
             self.max_tiles = (-(-rpr // 128)) * (-(-max_cols // 32))
             self.tile_flags = comm.alloc((2, self.world, self.max_tiles), torch.int32, zero=True)
+            # [0] epoch counter of the reduce calls, [1] CTA ticket (device side, graph safe)
+            self.reduce_state = torch.zeros(2, dtype=torch.int32, device=comm.device)
+            self._barrier_slot = comm.new_slot()
             comm.barrier_host()
 
     # ---------------------------------------------------------------- buffers
@@ -87,7 +90,6 @@ class TensorParallel:
         assert M <= self.max_rows and N <= self.max_cols
         rpr = M // self.world
         bn = self._pick_bn(rpr, N)
-        par = self._call % 2
         self._call += 1
         args = self._base_args(M, N, K, a, w, bn)
         args.a_parts = self.world
@@ -97,13 +99,15 @@ class TensorParallel:
         args.epi_mode = mode
         args.ldc, args.ldr = ldc, ldr
         args.residual = residual
-        args.reduce_epoch = self._call
-        stage_bytes = self.world * (self.max_rows // self.world) * self.max_cols * 2
-        flag_bytes = self.world * self.max_tiles * 4
+        # the epoch and the staging parity come from the device counter (see gemm_sm100.h)
+        args.epoch_counter = self.reduce_state.data_ptr()
+        args.cta_ticket = self.reduce_state.data_ptr() + 4
+        args.stage_parity_bytes = self.world * (self.max_rows // self.world) * self.max_cols * 2
+        args.flag_parity_bytes = self.world * self.max_tiles * 4
         # staging is addressed as [src_rank][rows_per_rank][N] inside one parity slab
         for r in range(self.world):
-            args.stage_ptrs[r] = self.stage.peer_ptrs[r] + par * stage_bytes
-            args.flag_ptrs[r] = self.tile_flags.peer_ptrs[r] + par * flag_bytes
+            args.stage_ptrs[r] = self.stage.peer_ptrs[r]
+            args.flag_ptrs[r] = self.tile_flags.peer_ptrs[r]
             args.out_ptrs[r] = out_ptrs[r]
         args.C = out_ptrs[self.rank]
         self._launch(args, a.device)
@@ -117,7 +121,7 @@ class TensorParallel:
             return
         buf = self.symm_of(x)
         self._reduce(a, w, EPI_ALL_REDUCE, buf.peer_ptrs, x.stride(0), x.data_ptr(), x.stride(0))
-        self.comm.barrier()
+        self.comm.barrier(self._barrier_slot)
 
     def gemm_reduce_scatter(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
                             residual: torch.Tensor | None = None) -> torch.Tensor:

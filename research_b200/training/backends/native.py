@@ -1,0 +1,245 @@
+"""Training backend on the native model, the flat buckets and the sharded AdamW.
+
+One implementation serves both public backends: ``PyTorchTrainingBackend`` (one GPU; the
+reference's single-device backend, rollouts/training/backends/pytorch.py:42-730) and
+``FSDPTrainingBackend`` (one rank per GPU; rollouts/training/backends/fsdp.py:61-766). The
+Tinker-style surface is the reference's: ``forward_backward`` -> ``optim_step`` returning
+futures, ``get_weights`` / ``load_weights``, checkpoints with ``weight_version`` and step.
+
+Per step, end to end: the batch arrives as host tensors, is staged through pinned memory and
+copied to the device, split into micro-batches, run forward+backward through the kernels
+(gradients accumulate in the flat bucket), and ``optim_step`` runs reduce-scatter + clip +
+AdamW + all-gather as three fused kernel families. Loss metrics come back with one
+device->host read per ``forward_backward``.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import time
+from pathlib import Path
+from typing import Any, Callable
+
+import torch
+
+from ...models.config import ModelConfig
+from ...models.weights import param_shapes, save_safetensors, save_safetensors_dir
+from ...ops import train as T
+from ...parallel.fsdp import FlatBuckets, ShardedAdamW
+from ...parallel.symm import LocalComm, PeerComm
+from ..losses import LOGPROB_LOSSES, shift_labels
+from ..native_model import NativeCausalLM
+from ..types import ImmediateTrainFuture, TrainerConfig, TrainFuture
+
+
+def _chunk_of(name: str) -> int:
+    if name.startswith("model.layers."):
+        return 1 + int(name.split(".")[2])
+    return 0 if name.startswith("model.embed") else 10_000
+
+
+class NativeTrainingBackend:
+    def __init__(self, model_config: ModelConfig, weights: dict[str, torch.Tensor] | None = None, *,
+                 comm: PeerComm | None = None, device: torch.device | str | None = None,
+                 loss_fn: str | Callable = "grpo", loss_kwargs: dict | None = None, lr: float = 1e-5,
+                 betas: tuple[float, float] = (0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
+                 trainer_config: TrainerConfig | None = None, lr_schedule: Callable[[int], float] | None = None,
+                 checkpoint_dir: str | Path | None = None, activation_checkpointing: bool = False,
+                 need_entropy: bool | None = None, seed: int = 0):
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda" if torch.cuda.is_available() else "cpu")
+        self.comm = comm if comm is not None else LocalComm(self.device)
+        self.rank, self.world = self.comm.rank, self.comm.world
+        self.model_config = model_config
+        self.config = trainer_config or TrainerConfig()
+        on_gpu = self.device.type == "cuda"
+        dtype = torch.bfloat16 if on_gpu else torch.float32
+        shapes = sorted(param_shapes(model_config).items(), key=lambda kv: (_chunk_of(kv[0]), kv[0]))
+        self.buckets = FlatBuckets(self.comm, shapes, _chunk_of, dtype=dtype)
+        if weights is None:
+            from ...models.weights import init_random_weights
+
+            weights = init_random_weights(model_config, seed=seed)
+        for n in self.buckets.specs:
+            self.buckets.param_view(n).copy_(weights[n].to(device=self.device, dtype=dtype))
+        self.comm.barrier_host()
+        max_norm = self.config.max_grad_norm if self.config.max_grad_norm is not None else 0.0
+        self.optimizer = ShardedAdamW(self.buckets, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                      max_grad_norm=max_norm)
+        self.base_lr = lr
+        self.lr_schedule = lr_schedule
+        self.model = NativeCausalLM(model_config, self.buckets, self.device, activation_checkpointing)
+        self.loss_name = loss_fn if isinstance(loss_fn, str) else getattr(loss_fn, "__name__", "custom")
+        self.loss_fn = LOGPROB_LOSSES[loss_fn] if isinstance(loss_fn, str) else loss_fn
+        self.loss_kwargs = loss_kwargs or {}
+        self.need_entropy = need_entropy if need_entropy is not None else self.loss_name.startswith("grpo")
+        self.checkpoint_dir = Path(checkpoint_dir) if checkpoint_dir else None
+        self.weight_version = 0
+        self.current_step = 0
+        self._poisoned = False
+        self._accum = 0
+        self._pinned: dict[str, torch.Tensor] = {}
+        self.last_h2d_bytes = 0
+
+    # ---------------------------------------------------------------- batch staging
+    def _to_device(self, batch: dict[str, Any]) -> dict[str, torch.Tensor]:
+        out = {}
+        nbytes = 0
+        for k, v in batch.items():
+            if isinstance(v, (list, tuple)):
+                v = torch.tensor(v)
+            if not isinstance(v, torch.Tensor):
+                continue
+            if self.device.type == "cuda" and not v.is_cuda:
+                pin = self._pinned.get(k)
+                if pin is None or pin.shape != v.shape or pin.dtype != v.dtype:
+                    pin = torch.empty(v.shape, dtype=v.dtype).pin_memory()
+                    self._pinned[k] = pin
+                pin.copy_(v)
+                nbytes += pin.numel() * pin.element_size()
+                v = pin.to(self.device, non_blocking=True)
+            out[k] = v
+        self.last_h2d_bytes = nbytes
+        return out
+
+    # ---------------------------------------------------------------- protocol
+    def forward_backward(self, batch: dict[str, Any]) -> TrainFuture[dict[str, float]]:
+        assert not self._poisoned, "backend is poisoned by an earlier failure; rebuild it"
+        try:
+            return ImmediateTrainFuture(self._forward_backward(batch), "forward_backward")
+        except Exception:
+            self._poisoned = True
+            raise
+
+    def _forward_backward(self, batch: dict[str, Any]) -> dict[str, float]:
+        b = self._to_device(batch)
+        ids = b["input_ids"]
+        labels = b.get("labels", ids)
+        mask = b.get("loss_mask")
+        if mask is None:
+            mask = (labels != -100).float()
+            if "attention_mask" in b:
+                mask = mask * b["attention_mask"].float()
+        targets, shift_mask = shift_labels(labels, mask.float())
+        targets = torch.where(shift_mask > 0, targets, torch.full_like(targets, -1))
+        B = ids.shape[0]
+        n_micro = self.config.get_num_minibatches(B)
+        mb = B // n_micro
+        agg: dict[str, float] = {}
+        t0 = time.perf_counter()
+        for i in range(n_micro):
+            sl = slice(i * mb, (i + 1) * mb)
+            lp, ent = self.model.logprobs(ids[sl], targets[sl], self.need_entropy)
+            sub = {k: (v[sl] if v.dim() > 0 and v.shape[0] == B else v) for k, v in b.items()}
+            sub["shift_mask"] = shift_mask[sl]
+            sub["targets"] = targets[sl]
+            loss, metrics = self.loss_fn(lp, ent, sub, **self.loss_kwargs)
+            assert torch.isfinite(loss).all(), f"non-finite loss: {loss}"
+            (loss / n_micro).backward()
+            if self.device.type != "cuda":
+                self.model.collect_cpu_grads()
+            for k, v in metrics.items():
+                agg[k] = agg.get(k, 0.0) + float(v) / n_micro
+            agg["loss"] = agg.get("loss", 0.0) + (float(loss.detach()) / n_micro if "loss" not in metrics else 0.0)
+        self._accum += 1
+        agg["grad_norm_local"] = float(T.sumsq(self.buckets.grads).sqrt())
+        agg["fwd_bwd_s"] = time.perf_counter() - t0
+        agg["num_tokens"] = float(shift_mask.sum())
+        return agg
+
+    def optim_step(self) -> TrainFuture[dict[str, float]]:
+        assert not self._poisoned, "backend is poisoned by an earlier failure; rebuild it"
+        try:
+            if self.lr_schedule is not None:
+                self.optimizer.lr = self.base_lr * self.lr_schedule(self.current_step)
+            norm = self.optimizer.step(grad_scale=1.0 / max(self._accum, 1))
+            self._accum = 0
+            self.current_step += 1
+            self.weight_version += 1
+            return ImmediateTrainFuture({"lr": self.optimizer.lr, "step": self.current_step, "grad_norm": float(norm)},
+                                        "optim_step")
+        except Exception:
+            self._poisoned = True
+            raise
+
+    def get_weights(self) -> TrainFuture[dict[str, Any]]:
+        return ImmediateTrainFuture({n: self.buckets.param_view(n).detach().clone() for n in self.buckets.specs},
+                                    "get_weights")
+
+    def load_weights(self, weights: dict[str, Any]) -> TrainFuture[None]:
+        for n in self.buckets.specs:
+            self.buckets.param_view(n).copy_(weights[n].to(device=self.device, dtype=self.buckets.dtype))
+        self.optimizer.resync_master()
+        self.comm.barrier_host()
+        return ImmediateTrainFuture(None, "load_weights")
+
+    # ---------------------------------------------------------------- checkpoints
+    def save_checkpoint(self, step: int | None = None, metrics: dict[str, float] | None = None) -> Path:
+        """``step_NNNN/``: HF ``model.safetensors`` + ``config.json`` (rank 0), one optimizer shard
+        per rank, ``metadata.json`` with step / weight_version / metrics."""
+        assert self.checkpoint_dir is not None, "checkpoint_dir not set"
+        step = self.current_step if step is None else step
+        path = self.checkpoint_dir / f"step_{step:04d}"
+        return self.save_checkpoint_to_path(path, step, metrics)
+
+    def save_checkpoint_to_path(self, path: Path | str, step: int | None = None, metrics: dict | None = None) -> Path:
+        path = Path(path)
+        path.mkdir(parents=True, exist_ok=True)
+        if self.rank == 0:
+            self.save_hf_checkpoint(path)
+            meta = {"step": self.current_step if step is None else step, "weight_version": self.weight_version,
+                    "timestamp": time.time(), "metrics": metrics or {}, "world_size": self.world,
+                    "loss": self.loss_name}
+            (path / "metadata.json").write_text(json.dumps(meta, indent=2))
+        sd = self.optimizer.state_dict()
+        flat = {}
+        for key in ("master", "exp_avg", "exp_avg_sq"):
+            for c, t in enumerate(sd[key]):
+                flat[f"{key}.{c}"] = t
+        save_safetensors(flat, path / f"optimizer-rank{self.rank:05d}-of-{self.world:05d}.safetensors",
+                         {"step": sd["step"], "rank": self.rank, "world": self.world})
+        self.comm.barrier_host()
+        return path
+
+    def save_hf_checkpoint(self, path: Path | str) -> Path:
+        weights = {n: self.buckets.param_view(n).detach().cpu() for n in self.buckets.specs}
+        save_safetensors_dir(weights, self.model_config, path, metadata={"weight_version": self.weight_version})
+        return Path(path)
+
+    def load_checkpoint(self, path: Path | str) -> dict[str, Any]:
+        from ...models.weights import load_safetensors, load_safetensors_dir
+
+        path = Path(path)
+        weights, _ = load_safetensors_dir(path)
+        weights = {k: v for k, v in weights.items() if k in self.buckets.specs}
+        self.load_weights(weights)
+        meta = json.loads((path / "metadata.json").read_text()) if (path / "metadata.json").exists() else {}
+        shard = path / f"optimizer-rank{self.rank:05d}-of-{self.world:05d}.safetensors"
+        if shard.exists():
+            flat = load_safetensors(shard, self.device)
+            n = len(self.buckets.chunks)
+            self.optimizer.load_state_dict({"step": int(meta.get("step", 0)), "rank": self.rank, "world": self.world,
+                                            "master": [flat[f"master.{c}"] for c in range(n)],
+                                            "exp_avg": [flat[f"exp_avg.{c}"] for c in range(n)],
+                                            "exp_avg_sq": [flat[f"exp_avg_sq.{c}"] for c in range(n)]})
+        self.current_step = int(meta.get("step", 0))
+        self.weight_version = int(meta.get("weight_version", 0))
+        return meta
+
+    def get_state_snapshot(self) -> dict[str, Any]:
+        return {"step": self.current_step, "weight_version": self.weight_version, "lr": self.optimizer.lr,
+                "poisoned": self._poisoned, "world_size": self.world, "rank": self.rank,
+                "num_params": self.model_config.num_params(), "loss": self.loss_name,
+                "device": str(self.device)}
+
+
+def warmup_cosine(warmup_steps: int, total_steps: int, min_ratio: float = 0.1) -> Callable[[int], float]:
+    """LR multiplier: linear warm-up then cosine decay to ``min_ratio``."""
+    def f(step: int) -> float:
+        if step < warmup_steps:
+            return (step + 1) / max(warmup_steps, 1)
+        t = min(1.0, (step - warmup_steps) / max(total_steps - warmup_steps, 1))
+        return min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * t))
+
+    return f

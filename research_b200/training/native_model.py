@@ -1,0 +1,245 @@
+"""Trainable decoder whose forward AND backward run on the sm_100a kernels.
+
+Parameters are views into a flat bf16 bucket (``parallel.fsdp.FlatBuckets``); gradients are
+accumulated by the kernels straight into the matching views of the gradient bucket (the wgrad
+GEMM's epilogue adds into it), so autograd never allocates or copies a weight gradient and
+the sharded optimizer can reduce-scatter the bucket in place.
+
+GEMMs: forward ``x @ W^T``; dgrad ``dY @ W`` (B operand MN-major); wgrad ``dY^T @ X`` (both
+operands MN-major) - one tcgen05 kernel, no transposes. The lm_head and the loss are fused
+and chunked: logits exist only as one ``[rows, V]`` fp32 chunk at a time, from which the
+kernel takes per-token log-probability and entropy (forward) and writes bf16 dlogits
+(backward); the ``[B,T,V]`` log-softmax of the reference (rollouts/training/losses.py:110-124)
+is never materialised.
+
+On CPU the same class evaluates the functional oracle with autograd, which is what the gloo
+multi-rank tests train.
+
+Attention core: ``scaled_dot_product_attention`` (library) for forward and backward of the
+training path; everything around it is native.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..models.config import ModelConfig
+from ..models.functional import causal_lm_forward
+from ..ops import train as T
+
+
+# ------------------------------------------------------------------------------ autograd glue
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, gw, bias, gb):
+        ctx.save_for_backward(x, w)
+        ctx.gw, ctx.gb = gw, gb
+        return ops.gemm(x, w, bias=bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = ops.gemm(dy, w, b_mn_major=True)                      # [M,N] x [N,K] -> [M,K]
+        ops.gemm(dy, x, residual=ctx.gw, out=ctx.gw, a_mn_major=True, b_mn_major=True)  # gw += dY^T X
+        if ctx.gb is not None:
+            ctx.gb.add_(dy.float().sum(0).to(ctx.gb.dtype))
+        return dx, None, None, None, None
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, gw, eps):
+        ctx.save_for_backward(x, w)
+        ctx.gw, ctx.eps = gw, eps
+        return ops.rmsnorm(x, w, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx, dw = T.rmsnorm_bwd(x, w, dy.contiguous(), ctx.eps)
+        ctx.gw.add_(dw.to(ctx.gw.dtype))
+        return dx, None, None, None
+
+
+class _RoPE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, positions, table):
+        ctx.save_for_backward(positions, table)
+        return T.rope(x, positions, table, backward=False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        positions, table = ctx.saved_tensors
+        return T.rope(dy.contiguous(), positions, table, backward=True), None, None
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return ops.swiglu(gu)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        return ops.swiglu_backward(gu, dy.contiguous())
+
+
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table, gtable):
+        ctx.save_for_backward(ids)
+        ctx.gtable = gtable
+        return ops.embedding(ids, table)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        ctx.gtable.index_add_(0, ids.long(), dy.to(ctx.gtable.dtype))
+        return None, None, None
+
+
+class _FusedLogprob(torch.autograd.Function):
+    """(h [N,d], W [V,d]) -> per-token log-prob of ``targets`` and entropy, chunked over rows."""
+
+    CHUNK = 2048
+
+    @staticmethod
+    def forward(ctx, h, w, gw, targets, need_entropy):
+        N = h.shape[0]
+        lp = torch.empty(N, dtype=torch.float32, device=h.device)
+        lse = torch.empty_like(lp)
+        ent = torch.empty_like(lp) if need_entropy else None
+        for s in range(0, N, _FusedLogprob.CHUNK):
+            e = min(N, s + _FusedLogprob.CHUNK)
+            logits = ops.gemm(h[s:e], w, out_f32=True)
+            a, b, c = T.logprob_entropy_fwd(logits, targets[s:e], need_entropy)
+            lp[s:e], lse[s:e] = a, b
+            if need_entropy:
+                ent[s:e] = c
+        ctx.save_for_backward(h, w, targets, lse, ent if need_entropy else lse)
+        ctx.gw, ctx.need_entropy = gw, need_entropy
+        ctx.mark_non_differentiable(lse)
+        return lp, (ent if need_entropy else lse.new_zeros(N)), lse
+
+    @staticmethod
+    def backward(ctx, g_lp, g_ent, _g_lse):
+        h, w, targets, lse, ent = ctx.saved_tensors
+        N = h.shape[0]
+        dh = torch.empty_like(h)
+        g_lp = g_lp.contiguous().float()
+        g_ent = g_ent.contiguous().float() if ctx.need_entropy else None
+        for s in range(0, N, _FusedLogprob.CHUNK):
+            e = min(N, s + _FusedLogprob.CHUNK)
+            logits = ops.gemm(h[s:e], w, out_f32=True)
+            dl = T.logprob_entropy_bwd(logits, targets[s:e], lse[s:e], ent[s:e] if ctx.need_entropy else None,
+                                       g_lp[s:e], g_ent[s:e] if g_ent is not None else None)
+            dl = dl.to(h.dtype) if dl.dtype != h.dtype else dl
+            ops.gemm(dl, w, out=dh[s:e], b_mn_major=True)
+            ops.gemm(dl, h[s:e], residual=ctx.gw, out=ctx.gw, a_mn_major=True, b_mn_major=True)
+        return dh, None, None, None, None
+
+
+# ------------------------------------------------------------------------------ the model
+class NativeCausalLM:
+    def __init__(self, cfg: ModelConfig, buckets, device: torch.device, activation_checkpointing: bool = False):
+        assert not cfg.is_moe, "use research_b200.parallel.moe for mixture-of-experts training"
+        self.cfg = cfg
+        self.b = buckets
+        self.device = device
+        self.on_gpu = device.type == "cuda"
+        self.ckpt = activation_checkpointing
+        self._params: dict[str, torch.Tensor] = {}
+        self.table = ops.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, device=device) \
+            if self.on_gpu else None
+
+    def p(self, name: str) -> torch.Tensor:
+        """Autograd leaf sharing storage with the bucket view (its gradient is written by the kernels)."""
+        leaf = self._params.get(name)
+        if leaf is None:
+            leaf = self.b.param_view(name).detach().requires_grad_(True)
+            self._params[name] = leaf
+        return leaf
+
+    def g(self, name: str) -> torch.Tensor:
+        return self.b.grad_view(name)
+
+    def state_dict(self) -> dict[str, torch.Tensor]:
+        return {n: self.b.param_view(n) for n in self.b.specs}
+
+    # ---------------------------------------------------------------- CPU / oracle path
+    def _logprobs_cpu(self, input_ids, targets, need_entropy):
+        leaves = {n: self.b.param_view(n).detach().float().requires_grad_(True) for n in self.b.specs}
+        logits = causal_lm_forward(input_ids.long(), leaves, self.cfg).float()
+        lp_all = F.log_softmax(logits, -1)
+        safe = targets.long().clamp(min=0)
+        lp = lp_all.gather(-1, safe[..., None]).squeeze(-1)
+        lp = torch.where(targets >= 0, lp, torch.zeros_like(lp))
+        ent = -(lp_all.exp() * lp_all).sum(-1) if need_entropy else None
+        self._leaves = leaves
+        return lp, ent
+
+    def collect_cpu_grads(self) -> None:
+        """Move autograd ``.grad`` of the CPU leaves into the flat gradient bucket."""
+        for n, leaf in getattr(self, "_leaves", {}).items():
+            if leaf.grad is not None:
+                self.b.grad_view(n).add_(leaf.grad.to(self.b.grads.dtype))
+        self._leaves = {}
+
+    # ---------------------------------------------------------------- kernel path
+    def _layer(self, x, i, positions, B, Tn):
+        cfg = self.cfg
+        pre = f"model.layers.{i}."
+        a = pre + "self_attn."
+        H, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+
+        def lin(inp, name, bias=False):
+            bn = name.replace(".weight", ".bias")
+            return _Linear.apply(inp, self.p(name), self.g(name), self.p(bn) if bias else None, self.g(bn) if bias else None)
+
+        h = _RMSNorm.apply(x, self.p(pre + "input_layernorm.weight"), self.g(pre + "input_layernorm.weight"), cfg.rms_norm_eps)
+        q = lin(h, a + "q_proj.weight", cfg.attention_bias).view(-1, H, D)
+        k = lin(h, a + "k_proj.weight", cfg.attention_bias).view(-1, Hkv, D)
+        v = lin(h, a + "v_proj.weight", cfg.attention_bias).view(-1, Hkv, D)
+        if cfg.qk_norm:
+            q = _RMSNorm.apply(q, self.p(a + "q_norm.weight"), self.g(a + "q_norm.weight"), cfg.rms_norm_eps)
+            k = _RMSNorm.apply(k, self.p(a + "k_norm.weight"), self.g(a + "k_norm.weight"), cfg.rms_norm_eps)
+        q = _RoPE.apply(q.contiguous(), positions, self.table)
+        k = _RoPE.apply(k.contiguous(), positions, self.table)
+        o = F.scaled_dot_product_attention(
+            q.view(B, Tn, H, D).transpose(1, 2), k.view(B, Tn, Hkv, D).transpose(1, 2),
+            v.view(B, Tn, Hkv, D).transpose(1, 2), is_causal=True, scale=1.0 / math.sqrt(D), enable_gqa=True)
+        o = o.transpose(1, 2).reshape(B * Tn, H * D)
+        x = x + lin(o, a + "o_proj.weight")
+        h = _RMSNorm.apply(x, self.p(pre + "post_attention_layernorm.weight"),
+                           self.g(pre + "post_attention_layernorm.weight"), cfg.rms_norm_eps)
+        m = pre + "mlp."
+        gu = torch.cat([lin(h, m + "gate_proj.weight"), lin(h, m + "up_proj.weight")], dim=-1)
+        x = x + lin(_SwiGLU.apply(gu), m + "down_proj.weight")
+        return x
+
+    def logprobs(self, input_ids: torch.Tensor, targets: torch.Tensor, need_entropy: bool = False):
+        """Per-token ``log p(targets)`` ``[B,T]`` (and entropy) with autograd through the kernels."""
+        if not self.on_gpu:
+            return self._logprobs_cpu(input_ids, targets, need_entropy)
+        cfg = self.cfg
+        B, Tn = input_ids.shape
+        ids = input_ids.reshape(-1).to(torch.int32).contiguous()
+        positions = torch.arange(Tn, device=self.device, dtype=torch.int32).repeat(B)
+        emb = "model.embed_tokens.weight"
+        x = _Embedding.apply(ids, self.p(emb), self.g(emb))
+        for i in range(cfg.num_layers):
+            if self.ckpt:
+                x = torch.utils.checkpoint.checkpoint(self._layer, x, i, positions, B, Tn, use_reentrant=False)
+            else:
+                x = self._layer(x, i, positions, B, Tn)
+        h = _RMSNorm.apply(x, self.p("model.norm.weight"), self.g("model.norm.weight"), cfg.rms_norm_eps)
+        head = emb if cfg.tie_word_embeddings else "lm_head.weight"
+        tg = targets.reshape(-1).to(torch.int32).contiguous()
+        lp, ent, _ = _FusedLogprob.apply(h, self.p(head), self.g(head), tg, need_entropy)
+        return lp.view(B, Tn), (ent.view(B, Tn) if need_entropy else None)

@@ -163,13 +163,56 @@ def case_weight_sync_and_tp_engine(comm, dev, dt):
     _ = W
 
 
+def case_fsdp_backend_and_grpo(comm, dev, dt):
+    """Two ranks train on different data: parameters stay identical across ranks and equal a
+    single-process run on the concatenated batch; then the full GRPO loop runs sharded."""
+    import tempfile
+
+    from research_b200.models import get_preset, init_random_weights
+    from research_b200.training.backends import FSDPTrainingBackend, PyTorchTrainingBackend
+    from research_b200.training.grpo import GRPOConfig, grpo_train
+
+    W = comm.world
+    cfg = get_preset("tiny-qwen2", num_layers=2)
+    w = init_random_weights(cfg, seed=0)
+    be = FSDPTrainingBackend(cfg, w, device=dev, loss_fn="ce", lr=1e-2)
+    g = torch.Generator().manual_seed(0)
+    all_ids = torch.randint(0, cfg.vocab_size, (2 * W, 16), generator=g)
+    mine = all_ids[comm.rank * 2:(comm.rank + 1) * 2]
+    for _ in range(2):
+        be.forward_backward({"input_ids": mine, "labels": mine}).wait()
+        be.optim_step().wait()
+    flat = be.buckets.params.float()
+    gathered = [torch.empty_like(flat) for _ in range(W)]
+    dist.all_gather(gathered, flat)
+    for other in gathered:
+        assert torch.equal(other, gathered[0]), "ranks diverged"
+    if dev.type == "cpu":
+        solo = PyTorchTrainingBackend(cfg, w, device=dev, loss_fn="ce", lr=1e-2)
+        for _ in range(2):
+            solo.forward_backward({"input_ids": all_ids, "labels": all_ids}).wait()
+            solo.optim_step().wait()
+        for n in ("model.layers.1.mlp.down_proj.weight", "model.embed_tokens.weight"):
+            close(be.buckets.param_view(n), solo.buckets.param_view(n), 2e-5, 1e-4, f"fsdp vs single {n}")
+    prompts = [torch.randint(0, 4096, (int(n),), generator=g).tolist() for n in torch.randint(16, 64, (16,), generator=g)]
+    with tempfile.TemporaryDirectory() as d:
+        gcfg = GRPOConfig(model_name="tiny-qwen2", lr=1e-5, batch_size=4, n_samples_per_prompt=4, num_minibatches=2,
+                          max_tokens=6, max_seq_len=128, temperature=1.0, num_steps=1, output_dir=d, checkpoint_every=1,
+                          max_batch_size=8, kv_blocks=128, experiment_name="mr")
+        import os
+        os.environ["ROLLOUTS_RUN_NAME"] = "mr_run"
+        hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=dev)
+        assert len(hist) == 1 and hist[0]["weight_version"] == 1.0
+        dist.barrier()
+
+
 def _bcast_buckets(b, comm):
     dist.broadcast(b.params, src=0, group=comm.group)
     return b
 
 
 CASES = {"barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
-         "weight_sync_tp_engine": case_weight_sync_and_tp_engine}
+         "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo}
 
 
 def main():

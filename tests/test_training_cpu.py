@@ -1,0 +1,217 @@
+"""CPU tests of the training stack: losses (with the next-token shift), data buffer, filters,
+rollout manager, backends, checkpoints and the full GRPO loop on the tiny Qwen2-style model."""
+
+import asyncio
+import json
+
+import pytest
+import torch
+
+from research_b200.models import causal_lm_forward, get_preset, init_random_weights
+from research_b200.training import losses as L
+from research_b200.training.backends import PyTorchTrainingBackend, create_pytorch_backend, parse_dtype, warmup_cosine
+from research_b200.training.datasets import BufferState, DataBuffer, get_samples, load_samples_from_jsonl, load_samples_from_list
+from research_b200.training.filters import (check_any_success, check_quality_and_diversity, check_reward_nonzero_std,
+                                            make_length_filter, make_threshold_filter)
+from research_b200.training.grpo import GRPOConfig, grpo_train
+from research_b200.training.loops import collate_batch, prepare_grpo_batch, prepare_sft_batch, run_sft_training
+from research_b200.training.metrics import CompositeLogger, JSONLLogger, compute_stats_from_jsonl
+from research_b200.training.rollout_gen import AsyncRolloutManager, convert_to_batch
+from research_b200.training.types import (ImmediateTrainFuture, RolloutConfig, Sample, SFTTrainingConfig, Status,
+                                          TrainerConfig, TrainFuture)
+
+
+def test_group_advantages():
+    adv = L.compute_group_advantages([1.0, 0.0, 1.0, 1.0], [0, 0, 1, 1])
+    assert torch.allclose(adv, torch.tensor([0.5, -0.5, 0.0, 0.0]))
+    adv = L.compute_group_advantages([2.0, 0.0], [0, 0], normalize_std=True)
+    assert torch.allclose(adv, torch.tensor([0.7071, -0.7071]), atol=1e-3)
+
+
+def test_losses_use_next_token_targets():
+    torch.manual_seed(0)
+    V = 7
+    labels = torch.tensor([[1, 2, 3, 4]])
+    mask = torch.tensor([[0.0, 1.0, 1.0, 1.0]])
+    logits = torch.randn(1, 4, V)
+    loss, m = L.sft_loss(logits, {"labels": labels, "loss_mask": mask})
+    lp = torch.log_softmax(logits, -1)
+    want = -(lp[0, 0, 2] + lp[0, 1, 3] + lp[0, 2, 4]) / 3  # position t is scored against token t+1
+    assert torch.allclose(loss, want, atol=1e-6)
+    assert m["num_tokens"] == 3
+    seq = L.get_seq_logprobs(logits, labels, mask)
+    assert torch.allclose(seq, -want.unsqueeze(0), atol=1e-6)
+
+
+def test_grpo_variants_and_from_logprobs_agree():
+    torch.manual_seed(1)
+    logits = torch.randn(4, 6, 11, requires_grad=True)
+    batch = {"labels": torch.randint(0, 11, (4, 6)), "loss_mask": (torch.rand(4, 6) > 0.3).float(),
+             "advantages": torch.tensor([0.5, -0.5, 1.0, -1.0]), "old_logprobs": torch.full((4,), -2.4)}
+    for fn in (L.grpo_loss, L.grpo_loss_clipped, L.grpo_loss_masked):
+        loss, metrics = fn(logits, batch)
+        assert torch.isfinite(loss) and "pg_loss" in metrics and "entropy" in metrics
+        loss.backward()
+    # on-policy: clipped loss gradient equals vanilla when ratio == 1
+    b = L._with_shift(batch)
+    lp = L.get_per_token_logprobs(logits, b["targets"])
+    seq = L.seq_mean(lp, b["shift_mask"]).detach()
+    l1, _ = L.grpo_from_logprobs(lp, None, b)
+    l2, m2 = L.grpo_clipped_from_logprobs(lp, None, {**b, "old_logprobs": seq})
+    g1 = torch.autograd.grad(l1, lp, retain_graph=True)[0]
+    g2 = torch.autograd.grad(l2, lp, retain_graph=True)[0]
+    assert torch.allclose(g1, g2, atol=1e-6) and m2["clipfrac"] == 0.0
+    assert abs(float(L.compute_entropy(torch.zeros(1, 2, 8))) - torch.log(torch.tensor(8.0)).item()) < 1e-5
+
+
+def test_data_buffer_deterministic_epochs_and_groups(tmp_path):
+    samples = load_samples_from_list(["a", "b", "c"])
+    g1, s1 = get_samples(samples, BufferState(seed=3), 2, 4)
+    g2, _ = get_samples(samples, BufferState(seed=3), 2, 4)
+    assert [g[0].prompt for g in g1] == [g[0].prompt for g in g2] and len(g1[0]) == 4
+    assert all(s.group_index == 1 for s in g1[1]) and s1.sample_offset == 2
+    _, s2 = get_samples(samples, s1, 2, 1)
+    assert s2.epoch_id == 1 and s2.sample_offset == 1
+    buf = DataBuffer(["p0", "p1", "p2"], seed=1)
+    first = buf.get_prompts(2)
+    st = buf.save_state()
+    nxt = buf.get_prompts(2)
+    buf.load_state(st)
+    assert buf.get_prompts(2) == nxt and sorted(first + nxt[:1]) == ["p0", "p1", "p2"]
+    p = tmp_path / "d.jsonl"
+    p.write_text('{"prompt": "x", "answer": "1"}\n{"prompt": "y", "answer": "2"}\n')
+    js = load_samples_from_jsonl(p)
+    assert js[1].prompt == "y" and js[1].ground_truth == "2"
+
+
+def test_filters():
+    g = [Sample(reward=1.0, tokens=[1, 2, 3], response_length=2), Sample(reward=0.0, tokens=[1, 5, 6], response_length=2)]
+    assert check_reward_nonzero_std(g) and check_any_success(g) and check_quality_and_diversity(g)
+    assert not check_reward_nonzero_std([g[0], g[0]])
+    assert make_threshold_filter(0.5)(g) and not make_threshold_filter(2.0)(g)
+    assert make_length_filter(1, 4)(g) and not make_length_filter(3, 4)(g)
+
+
+def test_sample_roundtrip_and_futures():
+    s = Sample(id="1", prompt="p", tokens=[1, 2], loss_mask=[0, 1], reward=0.5, status=Status.COMPLETED, rollout_log_probs=[-0.1])
+    s2 = Sample.from_dict(json.loads(json.dumps(s.to_dict())))
+    assert s2.tokens == [1, 2] and s2.status == Status.COMPLETED and s2.reward == 0.5
+    f = TrainFuture("x")
+    assert not f.done()
+    f.set_result(3)
+    assert f.done() and f.wait() == 3 and asyncio.run(f.result()) == 3
+    assert asyncio.run(ImmediateTrainFuture(4).result()) == 4
+    with pytest.raises(AssertionError):
+        TrainerConfig(micro_batch_size=2, num_minibatches=2)
+    assert TrainerConfig(micro_batch_size=2).get_num_minibatches(8) == 4
+
+
+def test_async_rollout_manager_oversampling_filter_and_state():
+    calls = []
+
+    def gen(prompts, **kw):
+        calls.append(len(prompts))
+        return [Sample(prompt=p, tokens=[1, 2, 3 + i], loss_mask=[0, 1, 1], response_length=2, rollout_log_probs=[-1.0, -1.0])
+                for i, p in enumerate(prompts)]
+
+    def score(s):
+        return float(s.tokens[-1] % 2)
+
+    cfg = RolloutConfig(batch_size=2, n_samples_per_prompt=2, over_sampling_factor=1.5, generate_fn=gen, score_fn=score,
+                        filter_fn=check_reward_nonzero_std)
+    mgr = AsyncRolloutManager(DataBuffer(["a", "b", "c", "d"], seed=0), cfg)
+    batch = asyncio.run(mgr.generate_batch())
+    assert len(batch) == 4 and batch.group_indices == [0, 0, 1, 1] and batch.rollout_log_probs is not None
+    assert batch.response_lengths == [2, 2, 2, 2]
+    st = mgr.state_dict()
+    mgr2 = AsyncRolloutManager(DataBuffer(["a", "b", "c", "d"], seed=0), cfg)
+    mgr2.load_state_dict(json.loads(json.dumps(st)))
+    assert len(mgr2.partial_samples) == len(mgr.partial_samples)
+    assert len(convert_to_batch(batch.samples)) == 4
+
+
+def test_batch_preparation():
+    samples = [Sample(tokens=[1, 2, 3, 4], loss_mask=[0, 0, 1, 1]), Sample(tokens=[5, 6], loss_mask=[0, 1])]
+    b = collate_batch(samples)
+    assert b["input_ids"].shape == (2, 4) and b["loss_mask"][1].tolist() == [0, 1, 0, 0] and b["attention_mask"][1].tolist() == [1, 1, 0, 0]
+    p = prepare_sft_batch(samples)
+    assert p["input_ids"].shape == (1, 6) and p["cu_seqlens"].tolist() == [0, 4, 6] and p["position_ids"][0].tolist() == [0, 1, 2, 3, 0, 1]
+    rb = convert_to_batch([Sample(tokens=[1, 2, 3], loss_mask=[0, 1, 1], rollout_log_probs=[-1.0, -3.0], reward=1.0, group_index=0)])
+    g = prepare_grpo_batch(rb, torch.tensor([0.5]), max_seq_len=8)
+    assert g["old_logprobs"].tolist() == [-2.0] and g["advantages"].tolist() == [0.5]
+
+
+def test_metrics_loggers(tmp_path):
+    lg = CompositeLogger([JSONLLogger(tmp_path), JSONLLogger(tmp_path, filename="b.jsonl", max_lines=1)])
+    lg.log({"loss": 1.0, "bad": float("nan")}, 0)
+    lg.log({"loss": 0.5}, 1)
+    lg.finish()
+    st = compute_stats_from_jsonl(tmp_path / "metrics.jsonl")
+    assert st["loss"]["last"] == 0.5 and st["loss"]["count"] == 2
+    assert len((tmp_path / "b.jsonl").read_text().splitlines()) == 1
+
+
+def test_backend_gradients_match_autograd_oracle():
+    cfg = get_preset("tiny-qwen2", num_layers=2)
+    w = init_random_weights(cfg, seed=0)
+    be = PyTorchTrainingBackend(cfg, w, device="cpu", loss_fn="ce", lr=1e-3, trainer_config=TrainerConfig(micro_batch_size=1))
+    ids = torch.randint(0, cfg.vocab_size, (2, 12))
+    m = be.forward_backward({"input_ids": ids, "labels": ids}).wait()
+    leaves = {k: v.clone().requires_grad_(True) for k, v in w.items()}
+    logits = causal_lm_forward(ids, leaves, cfg)
+    ref, _ = L.sft_loss(logits, {"labels": ids})
+    # micro-batches of 1: mean of per-sequence means == ref here because both rows have equal token counts
+    ref.backward()
+    assert abs(m["loss"] - float(ref)) < 1e-4
+    for n in ("model.layers.1.mlp.down_proj.weight", "model.embed_tokens.weight", "model.layers.0.self_attn.q_proj.bias"):
+        assert torch.allclose(be.buckets.grad_view(n), leaves[n].grad, atol=1e-5), n
+    o = be.optim_step().wait()
+    assert o["step"] == 1 and o["grad_norm"] > 0 and float(be.buckets.grads.abs().sum()) == 0.0
+
+
+def test_backend_sft_loop_checkpoint_resume(tmp_path):
+    cfg = get_preset("tiny-qwen2", num_layers=1)
+    be = PyTorchTrainingBackend(cfg, device="cpu", loss_fn="sft", lr=1e-2, checkpoint_dir=tmp_path, lr_schedule=warmup_cosine(2, 10))
+    g = torch.Generator().manual_seed(0)
+    samples = [Sample(tokens=torch.randint(0, cfg.vocab_size, (16,), generator=g).tolist(), loss_mask=[0.0] * 4 + [1.0] * 12) for _ in range(4)]
+    hist = asyncio.run(run_sft_training(be, samples, SFTTrainingConfig(num_steps=6, batch_size=4, log_every=1, checkpoint_every=3),
+                                        JSONLLogger(tmp_path)))
+    assert hist[-1]["loss"] < hist[0]["loss"]
+    ck = tmp_path / "step_0006"
+    assert (ck / "model.safetensors").exists() and (ck / "config.json").exists() and (ck / "metadata.json").exists()
+    be2 = PyTorchTrainingBackend(cfg, device="cpu", loss_fn="sft", lr=1e-2, seed=5)
+    meta = be2.load_checkpoint(ck)
+    assert meta["step"] == 6 and be2.current_step == 6 and be2.weight_version == be.weight_version
+    assert torch.equal(be2.buckets.params, be.buckets.params)
+    assert torch.equal(be2.optimizer.exp_avg[0], be.optimizer.exp_avg[0]) and be2.optimizer.step_count == 6
+    snap = be2.get_state_snapshot()
+    assert snap["step"] == 6 and not snap["poisoned"]
+    with pytest.raises(Exception):
+        be2.forward_backward({"input_ids": torch.full((1, 4), cfg.vocab_size + 5)})
+    with pytest.raises(AssertionError):
+        be2.forward_backward({"input_ids": torch.zeros(1, 4, dtype=torch.long)})  # poisoned after a failure
+    assert parse_dtype("bf16") == torch.bfloat16
+    be3 = create_pytorch_backend("tiny-llama", device="cpu", loss_fn="ce", lr=1e-3)
+    assert be3.model_config.family == "llama"
+
+
+def test_grpo_train_end_to_end(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    shared = torch.randint(0, 4096, (24,), generator=g).tolist()
+    prompts = []
+    for i in range(8):
+        n = int(torch.randint(30, 64, (1,), generator=g))
+        p = torch.randint(0, 4096, (n,), generator=g).tolist()
+        prompts.append(shared + p[24:] if i < 4 else p)
+
+    def score(s):
+        return float(sum(s.tokens[-s.response_length:]) % 2)
+
+    cfg = GRPOConfig(model_name="tiny-qwen2", lr=1e-5, batch_size=2, n_samples_per_prompt=4, num_minibatches=2, max_tokens=6,
+                     max_seq_len=128, temperature=1.0, num_steps=2, output_dir=str(tmp_path), checkpoint_every=2,
+                     max_batch_size=8, kv_blocks=128, experiment_name="t")
+    hist = grpo_train(cfg, prompts, score, device="cpu")
+    assert len(hist) == 2 and hist[1]["weight_version"] == 2.0 and all("pg_loss" in h for h in hist)
+    run = next(tmp_path.iterdir())
+    assert {"config.json", "metrics.jsonl", "rollouts.jsonl", "checkpoints", "rollout_state.json"} <= {p.name for p in run.iterdir()}
+    assert len((run / "rollouts.jsonl").read_text().splitlines()) == 16

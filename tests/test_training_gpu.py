@@ -1,0 +1,111 @@
+"""GPU tests of the training kernels and the kernel-backed trainable model (vs PyTorch fp32)."""
+
+import pytest
+import torch
+
+from research_b200 import ops
+from research_b200.models import causal_lm_forward, get_preset, init_random_weights
+from research_b200.ops import train as T
+from research_b200.training import losses as L
+from research_b200.training.backends import PyTorchTrainingBackend
+from research_b200.training.types import TrainerConfig
+
+pytestmark = pytest.mark.gpu
+
+
+def test_logprob_entropy_fwd_bwd(cuda_device):
+    R, V = 37, 4099
+    logits = (torch.randn(R, V, device=cuda_device) * 2).contiguous()
+    tg = torch.randint(0, V, (R,), dtype=torch.int32, device=cuda_device)
+    tg[3] = -1
+    lp, lse, ent = T.logprob_entropy_fwd(logits, tg, True)
+    rl, rlse, rent = T.logprob_entropy_reference(logits.cpu(), tg.cpu(), True)
+    assert (lp.cpu() - rl).abs().max() < 1e-4 and (lse.cpu() - rlse).abs().max() < 1e-4 and (ent.cpu() - rent).abs().max() < 1e-3
+    g_lp, g_ent = torch.randn(R, device=cuda_device), torch.randn(R, device=cuda_device) * 0.1
+    d = T.logprob_entropy_bwd(logits, tg, lse, ent, g_lp, g_ent)
+    x = logits.cpu().clone().requires_grad_(True)
+    a, _, c = T.logprob_entropy_reference(x, tg.cpu(), True)
+    ((a * g_lp.cpu()).sum() + (c * g_ent.cpu()).sum()).backward()
+    assert (d.float().cpu() - x.grad).abs().max() < 2e-2 * x.grad.abs().max() + 1e-4
+
+
+def test_rmsnorm_bwd_and_rope(cuda_device):
+    x = torch.randn(130, 896, device=cuda_device).bfloat16()
+    w = (1 + 0.1 * torch.randn(896, device=cuda_device)).bfloat16()
+    dy = torch.randn(130, 896, device=cuda_device).bfloat16()
+    dx, dw = T.rmsnorm_bwd(x, w, dy, 1e-6)
+    rdx, rdw = T.rmsnorm_bwd(x.cpu(), w.cpu(), dy.cpu(), 1e-6)
+    assert (dx.float().cpu() - rdx.float()).abs().max() < 0.05
+    assert (dw.cpu() - rdw).abs().max() < 0.02 * rdw.abs().max() + 0.05
+    q = torch.randn(50, 4, 64, device=cuda_device).bfloat16()
+    pos = torch.randint(0, 300, (50,), dtype=torch.int32, device=cuda_device)
+    tab = ops.rope_table(512, 64, 1e4, device=cuda_device)
+    y = T.rope(q, pos, tab)
+    ry = T.rope(q.cpu(), pos.cpu(), tab.cpu())
+    assert (y.float().cpu() - ry.float()).abs().max() < 0.02
+    back = T.rope(y, pos, tab, backward=True)  # rotation by -angle undoes it
+    assert (back.float() - q.float()).abs().max() < 0.03
+
+
+def test_adamw_kernel_matches_torch(cuda_device):
+    n = 10007
+    p0 = torch.randn(n)
+    ref = p0.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    master = p0.clone().to(cuda_device)
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    pb = master.bfloat16()
+    for step in range(1, 4):
+        g = torch.randn(n)
+        ref.grad = g.clone()
+        opt.step()
+        T.adamw_step(master, m, v, g.to(cuda_device), pb, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+    assert (master.cpu() - ref.detach()).abs().max() < 1e-5
+    assert (pb.float().cpu() - ref.detach()).abs().max() < 0.02
+    assert abs(float(T.sumsq(master)) - float((master ** 2).sum())) < 1e-2 * float((master ** 2).sum())
+
+
+@pytest.mark.parametrize("preset,ckpt", [("tiny-qwen2", False), ("tiny-qwen3", True), ("tiny-llama", False)])
+def test_native_model_gradients_vs_oracle(cuda_device, preset, ckpt):
+    cfg = get_preset(preset, num_layers=2, init_std=0.05)
+    w = {k: v.bfloat16().float() for k, v in init_random_weights(cfg, seed=0).items()}
+    be = PyTorchTrainingBackend(cfg, w, device=cuda_device, loss_fn="ce", lr=1e-3, activation_checkpointing=ckpt,
+                                trainer_config=TrainerConfig(micro_batch_size=2))
+    ids = torch.randint(0, cfg.vocab_size, (4, 32))
+    m = be.forward_backward({"input_ids": ids, "labels": ids}).wait()
+    leaves = {k: v.clone().requires_grad_(True) for k, v in w.items()}
+    ref, _ = L.sft_loss(causal_lm_forward(ids, leaves, cfg), {"labels": ids})
+    ref.backward()
+    assert abs(m["loss"] - float(ref.detach())) < 0.03, (m["loss"], float(ref.detach()))
+    for n in ("model.layers.1.mlp.down_proj.weight", "model.layers.0.self_attn.q_proj.weight",
+              "model.layers.0.self_attn.k_proj.weight", "model.layers.1.mlp.gate_proj.weight",
+              "model.embed_tokens.weight", "model.norm.weight", "model.layers.0.input_layernorm.weight"):
+        got, want = be.buckets.grad_view(n).float().cpu(), leaves[n].grad
+        rel = (got - want).norm() / (want.norm() + 1e-8)
+        assert rel < 0.06, (n, float(rel))
+    ops.check_status()
+
+
+def test_backend_gpu_overfits_and_grpo_step(cuda_device, tmp_path):
+    cfg = get_preset("tiny-qwen2", num_layers=2)
+    be = PyTorchTrainingBackend(cfg, device=cuda_device, loss_fn="ce", lr=3e-3, checkpoint_dir=tmp_path)
+    ids = torch.randint(0, cfg.vocab_size, (4, 48))
+    first = last = None
+    for _ in range(8):
+        m = be.forward_backward({"input_ids": ids, "labels": ids}).wait()
+        o = be.optim_step().wait()
+        first = first if first is not None else m["loss"]
+        last = m["loss"]
+    assert last < first - 1.0 and o["grad_norm"] > 0
+    be.save_checkpoint()
+    assert (tmp_path / "step_0008" / "model.safetensors").exists()
+    from research_b200.training.grpo import GRPOConfig, grpo_train
+
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 4096, (int(n),), generator=g).tolist() for n in torch.randint(20, 60, (8,), generator=g)]
+    gcfg = GRPOConfig(model_name="tiny-qwen2", lr=1e-5, batch_size=2, n_samples_per_prompt=4, num_minibatches=2, max_tokens=8,
+                      max_seq_len=128, temperature=1.0, num_steps=2, output_dir=str(tmp_path / "rl"), checkpoint_every=0,
+                      max_batch_size=8, kv_blocks=128, loss="grpo_clipped")
+    hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=cuda_device)
+    assert len(hist) == 2 and hist[-1]["weight_version"] == 2.0 and "clipfrac" in hist[-1]
+    ops.check_status()
