@@ -82,6 +82,9 @@ struct GemmParams {
   int* epoch_counter;
   int* cta_ticket;
   long long stage_parity_bytes, flag_parity_bytes;
+  const int4* tile_table;
+  const int* num_tiles_ptr;
+  const unsigned long long* row_dst;
 };
 
 __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
@@ -131,7 +134,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   const int n_tiles_per_part = (p.b_rows_per_part + BN - 1) / BN;
   const int num_m_tiles = m_tiles_per_part * p.a_parts;
   const int num_n_tiles = n_tiles_per_part * p.b_parts;
-  const int num_tiles = num_m_tiles * num_n_tiles;
+  const bool grouped = p.tile_table != nullptr;
+  const int num_tiles = grouped ? *p.num_tiles_ptr : num_m_tiles * num_n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -167,7 +171,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
 
   // Tile order. In reduce modes, rank r visits the row slab owned by rank r+1 first and its
   // own slab last so that every owner finds its partials early.
+  // grouped tiles: m_in = first A row, n_part = first B row, n_in = first output column,
+  // m_part carries the number of valid rows
   auto tile_coords = [&](int t, int& m_part, int& m_in, int& n_part, int& n_in) {
+    if (grouped) {
+      const int4 e = p.tile_table[t];
+      m_in = e.x; m_part = e.y; n_part = e.z; n_in = e.w;
+      return;
+    }
     int mt = t % num_m_tiles;
     int nt = t / num_m_tiles;
     if (p.epi_mode != RB_EPI_STORE && p.world > 1) {
@@ -192,18 +203,19 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_part, m_in, n_part, n_in;
         tile_coords(t, m_part, m_in, n_part, n_in);
-        if (p.a_ready != nullptr && !((a_seen >> m_part) & 1u)) {
+        if (!grouped && p.a_ready != nullptr && !((a_seen >> m_part) & 1u)) {
           ok = wait_flag_ge(p.a_ready + m_part, p.ready_epoch, p.status);
           if (!ok) { *abortp = 1; break; }
           a_seen |= 1u << m_part;
         }
-        if (p.b_ready != nullptr && !((b_seen >> n_part) & 1u)) {
+        if (!grouped && p.b_ready != nullptr && !((b_seen >> n_part) & 1u)) {
           ok = wait_flag_ge(p.b_ready + n_part, p.ready_epoch, p.status);
           if (!ok) { *abortp = 1; break; }
           b_seen |= 1u << n_part;
         }
-        const CUtensorMap* amap = &p.a_map[m_part];
-        const CUtensorMap* bmap = &p.b_map[n_part];
+        const CUtensorMap* amap = &p.a_map[grouped ? 0 : m_part];
+        const CUtensorMap* bmap = &p.b_map[grouped ? 0 : n_part];
+        const int b_row = grouped ? n_part : n_in;   // first B row of the tile
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -221,10 +233,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), amap, fb, m_in + c * 64, kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d(sb, bmap, fb, kb * BK, n_in);
+            tma_load_2d(sb, bmap, fb, kb * BK, b_row);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), bmap, fb, n_in + c * 64, kb * BK);
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), bmap, fb, b_row + c * 64, kb * BK);
           }
         }
       }
@@ -302,9 +314,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       if (!ok) break;
       tc_fence_after();
       const int row_in = m_in + q * 32 + lane;                 // row inside the A slab
-      const bool row_ok = row_in < p.a_rows_per_part;
-      const long long row = (long long)m_part * p.a_rows_per_part + row_in;
-      const int n_base = n_part * p.b_rows_per_part + n_in;    // global column
+      const bool row_ok = grouped ? (q * 32 + lane < m_part) : (row_in < p.a_rows_per_part);
+      const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
+      const int n_base = grouped ? n_in : n_part * p.b_rows_per_part + n_in;    // global column
       const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -345,7 +357,23 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                 }
               }
             }
-            epi_store_row_chunk(p, v, row, col, ncols);
+            if (p.row_dst != nullptr) {
+              // fused combine: this row's home is an arbitrary (possibly remote) address
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.row_dst[row]) + col;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (j < ncols) {
+                  uint4 o;
+                  o.x = pack_bf16x2(v[j], v[j + 1]);
+                  o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                  o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                  o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                  *reinterpret_cast<uint4*>(dst + j) = o;
+                }
+              }
+            } else {
+              epi_store_row_chunk(p, v, row, col, ncols);
+            }
           } else {
             // push the bf16 partial into the owner's staging slab [src_rank][row_in][N]
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[m_part]) + stage_off) +
@@ -523,6 +551,7 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   const int m_tiles = ((p.a_rows_per_part + BM - 1) / BM) * p.a_parts;
   const int n_tiles = ((p.b_rows_per_part + BN - 1) / BN) * p.b_parts;
   int grid = m_tiles * n_tiles;
+  if (p.tile_table != nullptr) grid = max_ctas > 0 ? max_ctas : num_sms();  // tile count is only known on the device
   int cap = num_sms();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
@@ -574,7 +603,9 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0) return -1;
   if (a->a_parts < 1 || a->a_parts > RB_MAX_PARTS || a->b_parts < 1 || a->b_parts > RB_MAX_PARTS) return -1;
   if (a->M % a->a_parts != 0 || a->N % a->b_parts != 0) return -1;
-  if (a->N % 8 != 0 || a->K % 8 != 0) return -1;
+  if (a->N % 8 != 0) return -1;
+  // K is a row stride only for K-major operands; MN-major operands may have any K (TMA zero-fills)
+  if ((!a->a_mn_major || !a->b_mn_major) && a->K % 8 != 0) return -1;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = a->M; p.N = a->N; p.K = a->K;
@@ -597,6 +628,14 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.stage_parity_bytes = a->stage_parity_bytes;
   p.flag_parity_bytes = a->flag_parity_bytes;
   if (p.epoch_counter != nullptr && p.cta_ticket == nullptr) return -1;
+  p.tile_table = reinterpret_cast<const int4*>(a->tile_table);
+  p.num_tiles_ptr = a->num_tiles_ptr;
+  p.row_dst = a->row_dst;
+  if (p.tile_table != nullptr) {
+    if (p.num_tiles_ptr == nullptr || a->group_n <= 0 || a->group_n % 8 != 0 || a->a_parts != 1 || a->b_parts != 1 ||
+        a->a_mn_major || a->b_mn_major || a->bn == 0 || p.epi_mode != RB_EPI_STORE)
+      return -1;
+  }
   if (p.epi_mode != RB_EPI_STORE) {
     if (a->a_parts != p.world || a->out_f32) return -1;
     if (p.a_rows_per_part % 8 != 0) return -1;
@@ -607,6 +646,8 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
     }
   }
   const int m_tiles = ((p.a_rows_per_part + BM - 1) / BM) * p.a_parts;
+  const int total_b_rows = p.b_rows_per_part;   // rows of the (stacked) B matrix for its tensor map
+  if (p.tile_table != nullptr) p.b_rows_per_part = a->group_n;  // columns valid per group
   int bn = a->bn;
   if (bn == 0) bn = pick_bn(m_tiles, p.b_rows_per_part, p.b_parts, a->b_mn_major, p.K);
   if (a->b_mn_major && bn < 64) bn = 64;
@@ -619,8 +660,8 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   }
   for (int i = 0; i < p.b_parts; ++i) {
     int rc = a->b_mn_major
-                 ? make_map_2d(&p.b_map[i], a->B[i], a->K, p.b_rows_per_part, a->ldb, BK)
-                 : make_map_2d(&p.b_map[i], a->B[i], p.b_rows_per_part, a->K, a->ldb, bn);
+                 ? make_map_2d(&p.b_map[i], a->B[i], a->K, total_b_rows, a->ldb, BK)
+                 : make_map_2d(&p.b_map[i], a->B[i], total_b_rows, a->K, a->ldb, bn);
     if (rc != 0) return -30 + rc;
   }
   switch (bn) {

@@ -44,6 +44,16 @@ typedef struct RbGemmArgs {
   int* cta_ticket;
   long long stage_parity_bytes;
   long long flag_parity_bytes;
+  // Grouped mode (mixture of experts): tiles come from a device table of int4
+  // {a_row0, valid_rows, b_row0, n0}; *num_tiles_ptr entries. A is [rows, K], B is
+  // [groups * group_n, K] (group_n output columns per group), C row = A row. When row_dst is
+  // set, output row r is written to the address row_dst[r] (possibly another GPU's memory)
+  // instead of C: the combine of expert-parallel MoE fused into the epilogue.
+  const int* tile_table;
+  const int* num_tiles_ptr;
+  int group_n;
+  int max_tiles;
+  const unsigned long long* row_dst;
 } RbGemmArgs;
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);

@@ -1,0 +1,304 @@
+// Mixture-of-experts routing and token movement for sm_100a.
+//
+//   moe_route      softmax-top-k (Qwen3-MoE: softmax over all experts, top-k, renormalise) or
+//                  sigmoid + correction-bias top-k (GLM-4-MoE), one warp per token
+//   moe_plan       per-expert counts -> offsets, and the tile table of the grouped GEMM
+//                  (entries {a_row0, valid_rows, b_row0, n0}) built on the device so the
+//                  whole layer stays inside one CUDA graph
+//   moe_permute    scatter token rows into expert-contiguous order; the destination may be the
+//                  receive buffer of the expert's owner GPU (dispatch over peer memory), and
+//                  each row records where its result has to be written back
+//   moe_combine    out[t] += sum_j w[t,j] * y[t*k + j]
+//
+// The expert GEMMs themselves are the grouped mode of csrc/gemm_sm100.cu; with row_dst set, the
+// down-projection epilogue stores every result row straight into the token's home buffer
+// (local or on the source GPU), which is the combine half of the all-to-all.
+//
+// Math oracles: rollouts/tools/functional_extractor/qwen3_next_functional.py:409-490 (softmax
+// top-k) and glm4_moe_functional.py:230-369 (sigmoid router, per-expert loop with index_add_).
+#include "common.cuh"
+
+#define RB_MAX_RANKS 8
+
+namespace rb {
+
+constexpr int MAX_E_PER_LANE = 8;  // up to 256 experts
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E,
+                                 int k, int sigmoid_router, int norm_topk, float scaling, int* __restrict__ topk_idx,
+                                 float* __restrict__ topk_w) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  float score[MAX_E_PER_LANE], choice[MAX_E_PER_LANE];
+  const int per = (E + 31) / 32;
+  float mx = -INFINITY;
+  for (int i = 0; i < per; ++i) {
+    const int e = lane + 32 * i;
+    const float x = e < E ? logits[(long long)t * E + e] : -INFINITY;
+    score[i] = x;
+    mx = fmaxf(mx, x);
+  }
+  if (sigmoid_router) {
+    for (int i = 0; i < per; ++i) {
+      const int e = lane + 32 * i;
+      score[i] = e < E ? 1.f / (1.f + __expf(-score[i])) : -INFINITY;
+      choice[i] = e < E ? score[i] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
+    }
+  } else {
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = 0; i < per; ++i) {
+      const int e = lane + 32 * i;
+      score[i] = e < E ? __expf(score[i] - mx) : 0.f;
+      sum += score[i];
+    }
+    sum = warp_sum(sum);
+    for (int i = 0; i < per; ++i) {
+      score[i] /= sum;
+      choice[i] = (lane + 32 * i) < E ? score[i] : -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_e = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int i = 0; i < per; ++i) {
+      const int e = lane + 32 * i;
+      if (choice[i] > best || (choice[i] == best && e < best_e)) { best = choice[i]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+      const int e2 = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (b2 > best || (b2 == best && e2 < best_e)) { best = b2; best_e = e2; }
+    }
+    // the owner lane reports the (un-biased) score and retires the expert
+    float w = 0.f;
+    if ((best_e & 31) == lane) {
+      const int i = best_e >> 5;
+      w = score[i];
+      choice[i] = -INFINITY;
+    }
+    w = __shfl_sync(0xffffffffu, w, best_e & 31);
+    wsum += w;
+    if (lane == j) { my_w = w; my_e = best_e; }
+  }
+  if (lane < k) {
+    float w = my_w;
+    if (norm_topk) w = w / (wsum + 1e-20f);
+    topk_idx[(long long)t * k + lane] = my_e;
+    topk_w[(long long)t * k + lane] = w * scaling;
+  }
+}
+
+// counts_all: [world][E] rows routed from each source rank to each expert (world = 1 locally).
+// Experts [e_lo, e_hi) are owned by this rank. Outputs (for the owned experts): offsets of each
+// expert's row block in the local expert-ordered buffer and the grouped-GEMM tile tables for
+// two GEMMs with different N (gate|up and down), all built by one CTA.
+__global__ void moe_plan_kernel(const int* __restrict__ counts_all, int world, int E, int e_lo, int e_hi,
+                                int* __restrict__ expert_offset /*[E_local+1]*/, int n_gu, int bn_gu,
+                                int4* __restrict__ tiles_gu, int* __restrict__ ntiles_gu, int n_dn, int bn_dn,
+                                int4* __restrict__ tiles_dn, int* __restrict__ ntiles_dn, int max_tiles,
+                                int* status) {
+  __shared__ int cnt[256], off[257], tb_gu[257], tb_dn[257];
+  const int EL = e_hi - e_lo;
+  for (int i = threadIdx.x; i < EL; i += blockDim.x) {
+    int c = 0;
+    for (int r = 0; r < world; ++r) c += counts_all[r * E + e_lo + i];
+    cnt[i] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, tg = 0, td = 0;
+    const int ngu = (n_gu + bn_gu - 1) / bn_gu, ndn = (n_dn + bn_dn - 1) / bn_dn;
+    for (int i = 0; i < EL; ++i) {
+      off[i] = o; tb_gu[i] = tg; tb_dn[i] = td;
+      const int mt = (cnt[i] + 127) / 128;
+      o += cnt[i]; tg += mt * ngu; td += mt * ndn;
+    }
+    off[EL] = o; tb_gu[EL] = tg; tb_dn[EL] = td;
+    if (tg > max_tiles || td > max_tiles) { set_status(status, ST_BAD_INDEX); tg = min(tg, max_tiles); td = min(td, max_tiles); }
+    *ntiles_gu = tg; *ntiles_dn = td;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= EL; i += blockDim.x) expert_offset[i] = off[i];
+  const int ngu = (n_gu + bn_gu - 1) / bn_gu, ndn = (n_dn + bn_dn - 1) / bn_dn;
+  for (int i = threadIdx.x; i < EL; i += blockDim.x) {
+    const int mt = (cnt[i] + 127) / 128;
+    for (int m = 0; m < mt; ++m) {
+      const int rows = min(128, cnt[i] - m * 128);
+      for (int n = 0; n < ngu; ++n) {
+        const int idx = tb_gu[i] + m * ngu + n;
+        if (idx < max_tiles) tiles_gu[idx] = make_int4(off[i] + m * 128, rows, i * n_gu + n * bn_gu, n * bn_gu);
+      }
+      for (int n = 0; n < ndn; ++n) {
+        const int idx = tb_dn[i] + m * ndn + n;
+        if (idx < max_tiles) tiles_dn[idx] = make_int4(off[i] + m * 128, rows, i * n_dn + n * bn_dn, n * bn_dn);
+      }
+    }
+  }
+}
+
+// Per-expert histogram of this rank's routing decisions.
+__global__ void moe_count_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict__ counts) {
+  __shared__ int h[256];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) h[i] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int e = topk_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&h[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += blockDim.x)
+    if (h[i]) atomicAdd(&counts[i], h[i]);
+}
+
+struct PeerPtrs { void* p[RB_MAX_RANKS]; };
+
+// Dispatch: row (t, j) goes to the owner of its expert. Position inside the owner's
+// expert-ordered buffer = expert block offset on the owner + rows from lower source ranks +
+// a running cursor for this (source, expert). ret_addr records where the result row must be
+// written (this rank's y buffer, slot t*k+j), as seen from the owner.
+__global__ void moe_permute_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx, int T, int k,
+                                   int d, int E, int world, int rank, const int* __restrict__ counts_all,
+                                   int* __restrict__ cursor /*[E]*/, PeerPtrs xp /*[cap, d] per rank*/,
+                                   PeerPtrs ret_code /*u64[cap] per rank*/, int cap, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)T * k) return;
+  const int t = (int)(gw / k);
+  const int e = topk_idx[gw];
+  if (e < 0 || e >= E) { set_status(status, ST_BAD_INDEX); return; }
+  const int epr = E / world;
+  const int owner = e / epr;
+  int pos = 0;
+  if (lane == 0) {
+    // block offset of expert e on its owner
+    int off = 0;
+    for (int ee = owner * epr; ee < e; ++ee)
+      for (int r = 0; r < world; ++r) off += counts_all[r * E + ee];
+    for (int r = 0; r < rank; ++r) off += counts_all[r * E + e];
+    pos = off + atomicAdd(&cursor[e], 1);
+  }
+  pos = __shfl_sync(0xffffffffu, pos, 0);
+  if (pos >= cap) { set_status(status, ST_BAD_INDEX); return; }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * d);
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(xp.p[owner]) + (long long)pos * d);
+  for (int v = lane; v < (d >> 3); v += 32) dst[v] = src[v];
+  if (lane == 0) {
+    // home of the result: (source rank, slot t*k+j); the owner turns it into an address in ITS
+    // mapping of the source's y buffer (peer mappings differ between processes)
+    reinterpret_cast<unsigned long long*>(ret_code.p[owner])[pos] =
+        ((unsigned long long)rank << 40) | (unsigned long long)gw;
+  }
+}
+
+// Owner side: (source rank, slot) -> address of y[slot] in the source's buffer as mapped here.
+__global__ void moe_translate_kernel(unsigned long long* __restrict__ ret, int n, PeerPtrs y_ptrs, int world, int d) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const unsigned long long code = ret[i];
+    int src = (int)(code >> 40);
+    if (src < 0 || src >= world) src = 0;
+    const unsigned long long slot = code & ((1ull << 40) - 1);
+    ret[i] = reinterpret_cast<unsigned long long>(y_ptrs.p[src]) + slot * (unsigned long long)d * 2ull;
+  }
+}
+
+// out[t] (+)= sum_j w[t,j] * y[t*k+j]
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w, int T, int k, int d,
+                                   __nv_bfloat16* __restrict__ out, int accumulate) {
+  const long long nvec = (long long)T * (d >> 3);
+  const int vpr = d >> 3;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (accumulate) {
+      const uint4 o = *reinterpret_cast<const uint4*>(out + t * d + c);
+      float2 f;
+      f = unpack_bf16x2(o.x); acc[0] = f.x; acc[1] = f.y;
+      f = unpack_bf16x2(o.y); acc[2] = f.x; acc[3] = f.y;
+      f = unpack_bf16x2(o.z); acc[4] = f.x; acc[5] = f.y;
+      f = unpack_bf16x2(o.w); acc[6] = f.x; acc[7] = f.y;
+    }
+    for (int j = 0; j < k; ++j) {
+      const float wj = w[t * k + j];
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(y + (t * k + j) * d + c));
+      float2 f;
+      f = unpack_bf16x2(v.x); acc[0] += wj * f.x; acc[1] += wj * f.y;
+      f = unpack_bf16x2(v.y); acc[2] += wj * f.x; acc[3] += wj * f.y;
+      f = unpack_bf16x2(v.z); acc[4] += wj * f.x; acc[5] += wj * f.y;
+      f = unpack_bf16x2(v.w); acc[6] += wj * f.x; acc[7] += wj * f.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * d + c) = o;
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+#define RB_OK() (cudaGetLastError() == cudaSuccess ? 0 : -11)
+static PeerPtrs mk(void* const* p, int world) {
+  PeerPtrs o;
+  for (int i = 0; i < RB_MAX_RANKS; ++i) o.p[i] = i < world ? p[i] : nullptr;
+  return o;
+}
+
+extern "C" int rb_moe_route(const float* logits, const float* bias, int T, int E, int k, int sigmoid_router,
+                            int norm_topk, float scaling, int* topk_idx, float* topk_w, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (E > 32 * MAX_E_PER_LANE || k > 32 || k > E) return -1;
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w);
+  return RB_OK();
+}
+extern "C" int rb_moe_count(const int* topk_idx, int n, int E, int* counts, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (E > 256) return -1;
+  int grid = (n + 255) / 256;
+  if (grid > 148) grid = 148;
+  moe_count_kernel<<<grid, 256, 0, s>>>(topk_idx, n, E, counts);
+  return RB_OK();
+}
+extern "C" int rb_moe_plan(const int* counts_all, int world, int E, int e_lo, int e_hi, int* expert_offset, int n_gu,
+                           int bn_gu, void* tiles_gu, int* ntiles_gu, int n_dn, int bn_dn, void* tiles_dn,
+                           int* ntiles_dn, int max_tiles, int* status, cudaStream_t s) {
+  if (e_hi - e_lo > 256 || e_hi <= e_lo) return -1;
+  moe_plan_kernel<<<1, 256, 0, s>>>(counts_all, world, E, e_lo, e_hi, expert_offset, n_gu, bn_gu, (int4*)tiles_gu,
+                                    ntiles_gu, n_dn, bn_dn, (int4*)tiles_dn, ntiles_dn, max_tiles, status);
+  return RB_OK();
+}
+extern "C" int rb_moe_permute(const void* x, const int* topk_idx, int T, int k, int d, int E, int world, int rank,
+                              const int* counts_all, int* cursor, void* const* xp_ptrs, void* const* ret_ptrs,
+                              int cap, int* status, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (d % 8 != 0 || E % world != 0) return -1;
+  const long long warps = (long long)T * k;
+  moe_permute_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)x, topk_idx, T, k, d, E, world, rank,
+                                                                counts_all, cursor, mk(xp_ptrs, world), mk(ret_ptrs, world),
+                                                                cap, status);
+  return RB_OK();
+}
+extern "C" int rb_moe_translate(void* ret, int n, void* const* y_ptrs, int world, int d, cudaStream_t s) {
+  if (n <= 0) return 0;
+  int grid = (n + 255) / 256;
+  if (grid > 148 * 4) grid = 148 * 4;
+  moe_translate_kernel<<<grid, 256, 0, s>>>((unsigned long long*)ret, n, mk(y_ptrs, world), world, d);
+  return RB_OK();
+}
+extern "C" int rb_moe_combine(const void* y, const float* w, int T, int k, int d, void* out, int accumulate,
+                              cudaStream_t s) {
+  if (T <= 0) return 0;
+  const long long nvec = (long long)T * (d / 8);
+  long long grid = (nvec + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_combine_kernel<<<(unsigned)grid, 256, 0, s>>>((const __nv_bfloat16*)y, w, T, k, d, (__nv_bfloat16*)out, accumulate);
+  return RB_OK();
+}

@@ -55,6 +55,11 @@ class RbGemmArgs(ctypes.Structure):
         ("cta_ticket", ctypes.c_void_p),
         ("stage_parity_bytes", ctypes.c_longlong),
         ("flag_parity_bytes", ctypes.c_longlong),
+        ("tile_table", ctypes.c_void_p),
+        ("num_tiles_ptr", ctypes.c_void_p),
+        ("group_n", ctypes.c_int),
+        ("max_tiles", ctypes.c_int),
+        ("row_dst", ctypes.c_void_p),
     ]
 
 

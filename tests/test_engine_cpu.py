@@ -181,7 +181,7 @@ def _oracle_greedy(w, cfg, prompt, n):
     return tuple(ids[len(prompt):])
 
 
-@pytest.mark.parametrize("preset", ["tiny-qwen2", "tiny-qwen3", "tiny-llama"])
+@pytest.mark.parametrize("preset", ["tiny-qwen2", "tiny-qwen3", "tiny-llama", "tiny-moe", "tiny-glm4-moe"])
 @pytest.mark.parametrize("cache_type", ["radix", "paged", "none"])
 def test_engine_greedy_matches_oracle(preset, cache_type):
     cfg = get_preset(preset, num_layers=2)

@@ -29,7 +29,7 @@ def _run(device: str, nproc: int, cases: str, timeout: int = 600) -> str:
     return proc.stdout
 
 
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "moe_ep"])
 def test_gloo_two_ranks(cases):
     out = _run("cpu", 2, cases)
     for c in cases.split(","):
@@ -37,7 +37,7 @@ def test_gloo_two_ranks(cases):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "moe_ep"])
 def test_gpu_ranks(cases):
     import torch
 
