@@ -1,0 +1,105 @@
+"""Session persistence: ``session.json`` + append-only ``messages.jsonl`` per session, atomic
+metadata writes (tmp + rename), branching, crash logs (rollouts/store.py:39-446)."""
+
+from __future__ import annotations
+
+import json
+import os
+import time
+import traceback
+import uuid
+from dataclasses import asdict
+from pathlib import Path
+from typing import Any, Protocol, runtime_checkable
+
+from .dtypes import AgentSession, Message
+
+
+@runtime_checkable
+class SessionStore(Protocol):
+    async def create(self, endpoint: dict[str, Any], environment: dict[str, Any] | None = None, parent_id: str | None = None,
+                     branch_point: int | None = None, tags: dict[str, Any] | None = None) -> str: ...
+    async def get(self, session_id: str) -> tuple[AgentSession, list[Message]]: ...
+    async def append_message(self, session_id: str, message: Message) -> None: ...
+    async def update(self, session_id: str, **fields: Any) -> None: ...
+    async def list(self) -> list[AgentSession]: ...
+
+
+class FileSessionStore:
+    def __init__(self, root: str | Path):
+        self.root = Path(root)
+        self.root.mkdir(parents=True, exist_ok=True)
+
+    def _dir(self, sid: str) -> Path:
+        return self.root / sid
+
+    def _write_meta(self, s: AgentSession) -> None:
+        d = self._dir(s.session_id)
+        d.mkdir(parents=True, exist_ok=True)
+        tmp = d / f".session.json.{os.getpid()}.tmp"
+        tmp.write_text(json.dumps(asdict(s), indent=2, default=str))
+        os.replace(tmp, d / "session.json")
+
+    def _read_meta(self, sid: str) -> AgentSession:
+        return AgentSession(**json.loads((self._dir(sid) / "session.json").read_text()))
+
+    async def create(self, endpoint, environment=None, parent_id=None, branch_point=None, tags=None) -> str:
+        sid = f"{time.strftime('%Y%m%d-%H%M%S')}-{uuid.uuid4().hex[:8]}"
+        self._write_meta(AgentSession(sid, endpoint=endpoint, environment=environment, parent_id=parent_id,
+                                      branch_point=branch_point, tags=tags or {}))
+        (self._dir(sid) / "messages.jsonl").touch()
+        return sid
+
+    async def get(self, session_id: str) -> tuple[AgentSession, list[Message]]:
+        msgs = []
+        p = self._dir(session_id) / "messages.jsonl"
+        if p.exists():
+            for line in p.read_text().splitlines():
+                if line.strip():
+                    try:
+                        msgs.append(Message.from_dict(json.loads(line)))
+                    except json.JSONDecodeError:
+                        break  # a torn last line from a crash: everything before it is intact
+        return self._read_meta(session_id), msgs
+
+    async def append_message(self, session_id: str, message: Message) -> None:
+        with open(self._dir(session_id) / "messages.jsonl", "a") as f:
+            f.write(json.dumps(message.to_dict()) + "\n")
+            f.flush()
+            os.fsync(f.fileno())
+        s = self._read_meta(session_id)
+        s.num_messages += 1
+        s.updated_at = time.time()
+        self._write_meta(s)
+
+    async def update(self, session_id: str, **fields: Any) -> None:
+        s = self._read_meta(session_id)
+        for k, v in fields.items():
+            setattr(s, k, v)
+        s.updated_at = time.time()
+        self._write_meta(s)
+
+    async def list(self) -> list[AgentSession]:
+        out = []
+        for d in sorted(self.root.iterdir()):
+            if (d / "session.json").exists():
+                out.append(self._read_meta(d.name))
+        return out
+
+    async def branch(self, session_id: str, at_message: int) -> str:
+        """New session that shares the first ``at_message`` messages of ``session_id``."""
+        parent, msgs = await self.get(session_id)
+        sid = await self.create(parent.endpoint, parent.environment, parent_id=session_id, branch_point=at_message)
+        for m in msgs[:at_message]:
+            await self.append_message(sid, m)
+        return sid
+
+
+def log_crash(root: str | Path, error: BaseException, context: dict[str, Any] | None = None) -> Path:
+    d = Path(root) / "crashes"
+    d.mkdir(parents=True, exist_ok=True)
+    p = d / f"crash-{time.strftime('%Y%m%d-%H%M%S')}-{uuid.uuid4().hex[:6]}.json"
+    p.write_text(json.dumps({"error": f"{type(error).__name__}: {error}",
+                             "traceback": "".join(traceback.format_exception(type(error), error, error.__traceback__)),
+                             "context": context or {}, "time": time.time()}, indent=2, default=str))
+    return p
