@@ -150,6 +150,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,         // [B, Hq, D]
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = KV_BLOCK * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = Hq / Hkv;
@@ -268,6 +270,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,         // [B, Hq, D]
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int num_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
   if (d >= D) return;
@@ -441,6 +445,8 @@ constexpr int prefill_smem_bytes() {
 
 using namespace rb;
 
+extern "C" void rb_attn_set_pdl(int on) { rb::pdl_enabled() = on != 0; }
+
 // Scratch needed by rb_paged_decode when num_splits > 1, in floats.
 extern "C" long long rb_paged_decode_workspace_floats(int B, int Hq, int D, int num_splits) {
   if (num_splits <= 1) return 0;
@@ -465,12 +471,13 @@ extern "C" int rb_paged_decode(const void* q, const void* k_cache, const void* v
                                decode_smem_bytes<DD>()) != cudaSuccess) return -10;                           \
       attr = true;                                                                                            \
     }                                                                                                         \
-    paged_decode_kernel<DD><<<grid, DEC_WARPS * 32, decode_smem_bytes<DD>(), stream>>>(                        \
+    launch_kernel(paged_decode_kernel<DD>, grid, dim3(DEC_WARPS * 32), decode_smem_bytes<DD>(), stream,        \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,  \
         seq_lens, (__nv_bfloat16*)out, part_o, part_ml, Hq, Hkv, max_blocks, num_blocks, num_splits, scale,   \
         status);                                                                                              \
     if (num_splits > 1)                                                                                       \
-      decode_merge_kernel<DD><<<B * Hq, DD, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, num_splits);   \
+      launch_kernel(decode_merge_kernel<DD>, dim3(B * Hq), dim3(DD), 0, stream, (const float*)part_o,         \
+                    (const float*)part_ml, (__nv_bfloat16*)out, num_splits);                                  \
   } while (0)
   if (D == 64) LAUNCH_DEC(64);
   else if (D == 128) LAUNCH_DEC(128);

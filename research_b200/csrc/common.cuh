@@ -231,6 +231,13 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its
+// predecessor on the stream is still running; it must execute pdl_wait() before it touches any
+// global memory the predecessor may write or read. Without the attribute both calls are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- cross-GPU flags (release/acquire at system scope, bounded) -----------------------------
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -261,3 +268,29 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status
 }
 
 }  // namespace rb
+
+// ---- host: launch helper with the optional programmatic-dependent-launch attribute -------------
+#ifdef __CUDACC__
+#include <utility>
+namespace rb {
+inline bool& pdl_enabled() {
+  static bool on = false;
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(std::forward<Args>(args))...);
+}
+}  // namespace rb
+#endif

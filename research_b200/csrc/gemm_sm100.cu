@@ -85,6 +85,7 @@ struct GemmParams {
   const int4* tile_table;
   const int* num_tiles_ptr;
   const unsigned long long* row_dst;
+  int swiglu;
 };
 
 __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
@@ -129,12 +130,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  pdl_launch_dependents();  // the next kernel may begin its own prologue now
 
   const int m_tiles_per_part = (p.a_rows_per_part + BM - 1) / BM;
   const int n_tiles_per_part = (p.b_rows_per_part + BN - 1) / BN;
   const int num_m_tiles = m_tiles_per_part * p.a_parts;
   const int num_n_tiles = n_tiles_per_part * p.b_parts;
   const bool grouped = p.tile_table != nullptr;
+  if (grouped) pdl_wait();  // the tile count itself is produced by the previous kernel
   const int num_tiles = grouped ? *p.num_tiles_ptr : num_m_tiles * num_n_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
 
@@ -158,6 +161,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // barriers and TMEM are set up; from here on we read what the previous kernel wrote
   const uint32_t tmem_base = tmem_base_smem;
   volatile int* abortp = &abort_flag;
   // epoch of this reduce call: a host constant, or (graph replay) one past the device counter
@@ -318,6 +322,38 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
       const int n_base = grouped ? n_in : n_part * p.b_rows_per_part + n_in;    // global column
       const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
+      if (p.swiglu) {
+        if constexpr (BN >= 64) {
+          // gate columns [0, BN/2), up columns [BN/2, BN) of the same output channels
+          const int out_col0 = (n_base / BN) * (BN / 2);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), g);
+            tmem_ld_32x32(tmem_base + acc * BN + BN / 2 + c0 + ((uint32_t)(q * 32) << 16), u);
+            tmem_ld_wait();
+            if (row_ok) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + out_col0 + c0;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  // same rounding points as the unfused path: bf16(gate), bf16(silu), bf16(up), bf16(product)
+                  const float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * e])));
+                  const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * e + 1])));
+                  const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * e])));
+                  const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * e + 1])));
+                  const float s0 = __bfloat162float(__float2bfloat16_rn(g0 / (1.f + __expf(-g0))));
+                  const float s1 = __bfloat162float(__float2bfloat16_rn(g1 / (1.f + __expf(-g1))));
+                  o[e] = pack_bf16x2(s0 * u0, s1 * u1);
+                }
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -556,8 +592,7 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  kern<<<grid, GEMM_THREADS, Cfg::kSmemBytes, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::kSmemBytes, stream, p) == cudaSuccess ? 0 : -11;
 }
 
 template <int BN>
@@ -631,6 +666,12 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.tile_table = reinterpret_cast<const int4*>(a->tile_table);
   p.num_tiles_ptr = a->num_tiles_ptr;
   p.row_dst = a->row_dst;
+  p.swiglu = a->swiglu;
+  if (p.swiglu) {
+    if (a->bn < 64 || a->N % a->bn != 0 || a->b_parts != 1 || a->out_f32 || p.epi_mode != RB_EPI_STORE || a->bias ||
+        a->residual || a->tile_table)
+      return -1;
+  }
   if (p.tile_table != nullptr) {
     if (p.num_tiles_ptr == nullptr || a->group_n <= 0 || a->group_n % 8 != 0 || a->a_parts != 1 || a->b_parts != 1 ||
         a->a_mn_major || a->b_mn_major || a->bn == 0 || p.epi_mode != RB_EPI_STORE)
@@ -672,6 +713,8 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
     default: return -13;
   }
 }
+
+extern "C" void rb_gemm_set_pdl(int on) { rb::pdl_enabled() = on != 0; }
 
 // Plain single-GPU form: C = A * B^T (+bias) (+residual).
 extern "C" int rb_gemm_bf16(const void* A, const void* B, void* C, const void* bias,

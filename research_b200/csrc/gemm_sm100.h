@@ -54,6 +54,10 @@ typedef struct RbGemmArgs {
   int group_n;
   int max_tiles;
   const unsigned long long* row_dst;
+  // Fused SwiGLU epilogue: B holds gate and up rows interleaved in blocks of bn/2 (block j =
+  // gate rows [j*bn/2, (j+1)*bn/2) followed by the matching up rows); the kernel writes
+  // silu(gate) * up to C, which has N/2 columns. Requires an explicit bn and N % bn == 0.
+  int swiglu;
 } RbGemmArgs;
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);

@@ -14,6 +14,8 @@ namespace rb {
 __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                __nv_bfloat16* __restrict__ y, long long rows, int d, long long ldx,
                                long long ldy, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -68,6 +70,8 @@ __global__ void rope_kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __n
                                       int Hkv, int block_size, long long num_slots, int max_pos, int* status) {
   constexpr int HALF = D / 2;
   constexpr int PER_LANE = HALF / 32;  // pairs handled per lane: D=64 -> 1, D=128 -> 2
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int heads = Hq + 2 * Hkv;
@@ -142,6 +146,8 @@ __global__ void rope_kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __n
 // ------------------------------------------------------------------------------------------
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                               long long T, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long nvec = T * (F >> 3);
   const int fv = F >> 3;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
@@ -186,6 +192,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 // ------------------------------------------------------------------------------------------
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int T, int d, int vocab, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= T) return;
   int id = ids[t];
@@ -225,6 +233,8 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
                       const float* __restrict__ temperature, const unsigned long long* __restrict__ seeds,
                       const unsigned long long* __restrict__ step_ptr, unsigned long long step_add,
                       int* __restrict__ out_tokens, float* __restrict__ out_logprobs) {
+  pdl_launch_dependents();
+  pdl_wait();
   // The step counter lives in device memory so a captured CUDA graph draws fresh noise on
   // every replay (the host bumps the counter between replays).
   const unsigned long long step = step_add + (step_ptr != nullptr ? *step_ptr : 0ull);
@@ -376,14 +386,15 @@ using namespace rb;
 
 #define RB_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? 0 : -11)
 
+extern "C" void rb_ops_set_pdl(int on) { rb::pdl_enabled() = on != 0; }
+
 extern "C" int rb_rmsnorm(const void* x, const void* w, void* y, long long rows, int d, long long ldx,
                           long long ldy, float eps, cudaStream_t stream) {
   if (d % 8 != 0 || rows <= 0) return -1;
   const int warps = 8;
   const long long grid = (rows + warps - 1) / warps;
-  rmsnorm_kernel<<<(unsigned)grid, warps * 32, 0, stream>>>(
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, d, ldx, ldy, eps);
-  return RB_CHECK_LAUNCH();
+  return launch_kernel(rmsnorm_kernel, dim3((unsigned)grid), dim3(warps * 32), 0, stream, (const __nv_bfloat16*)x,
+                       (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, d, ldx, ldy, eps) == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int rb_rope_kv_append(const void* qkv, void* q_out, void* k_cache, void* v_cache,
@@ -396,15 +407,16 @@ extern "C" int rb_rope_kv_append(const void* qkv, void* q_out, void* k_cache, vo
   const int warps = 8;
   const unsigned grid = (unsigned)((warps_total + warps - 1) / warps);
 #define LAUNCH_ROPE(DD)                                                                              \
-  rope_kv_append_kernel<DD><<<grid, warps * 32, 0, stream>>>(                                         \
+  launch_kernel(rope_kv_append_kernel<DD>, dim3(grid), dim3(warps * 32), 0, stream,                   \
       (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
       positions, slots, (const float2*)cos_sin, (const __nv_bfloat16*)q_norm_w,                       \
       (const __nv_bfloat16*)k_norm_w, norm_eps, T, Hq, Hkv, block_size, num_slots, max_pos, status)
-  if (D == 64) { LAUNCH_ROPE(64); }
-  else if (D == 128) { LAUNCH_ROPE(128); }
+  cudaError_t e;
+  if (D == 64) { e = LAUNCH_ROPE(64); }
+  else if (D == 128) { e = LAUNCH_ROPE(128); }
   else return -1;
 #undef LAUNCH_ROPE
-  return RB_CHECK_LAUNCH();
+  return e == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int rb_swiglu(const void* gu, void* out, long long T, int F, cudaStream_t stream) {
@@ -412,8 +424,8 @@ extern "C" int rb_swiglu(const void* gu, void* out, long long T, int F, cudaStre
   const long long nvec = T * (F / 8);
   long long grid = (nvec + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;
-  swiglu_kernel<<<(unsigned)grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F);
-  return RB_CHECK_LAUNCH();
+  return launch_kernel(swiglu_kernel, dim3((unsigned)grid), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                       (__nv_bfloat16*)out, T, F) == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int rb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int F,
@@ -429,8 +441,8 @@ extern "C" int rb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long l
 extern "C" int rb_embedding(const int* ids, const void* table, void* out, int T, int d, int vocab,
                             int* status, cudaStream_t stream) {
   if (d % 8 != 0 || T <= 0) return -1;
-  embedding_kernel<<<T, 128, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, d, vocab, status);
-  return RB_CHECK_LAUNCH();
+  return launch_kernel(embedding_kernel, dim3(T), dim3(128), 0, stream, ids, (const __nv_bfloat16*)table,
+                       (__nv_bfloat16*)out, T, d, vocab, status) == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int rb_sample_logprob(const float* logits, long long ld, int B, int V, const float* temperature,
@@ -438,9 +450,8 @@ extern "C" int rb_sample_logprob(const float* logits, long long ld, int B, int V
                                  unsigned long long step_add, int* out_tokens, float* out_logprobs,
                                  cudaStream_t stream) {
   if (B <= 0) return 0;
-  sample_logprob_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, temperature, seeds, step_ptr, step_add,
-                                                          out_tokens, out_logprobs);
-  return RB_CHECK_LAUNCH();
+  return launch_kernel(sample_logprob_kernel, dim3(B), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
+                       seeds, step_ptr, step_add, out_tokens, out_logprobs) == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int rb_token_logprob(const float* logits, long long ld, int B, int V, const int* tokens,

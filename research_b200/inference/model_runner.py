@@ -77,6 +77,10 @@ class ModelRunner:
             self.graph_batch_sizes += (max_batch,)
         self.scale = 1.0 / math.sqrt(self.D)
         self.launches_per_decode_step = 0
+        # gate|up projection with SwiGLU fused into the GEMM epilogue: weights are stored
+        # interleaved in blocks of 128 gate rows + 128 up rows (tile width 256)
+        self.swiglu_bn = 256
+        self.fuse_swiglu = self.on_gpu and self.F > 0 and self.F % (self.swiglu_bn // 2) == 0
         # fused GEMM+all-reduce works on row counts that split evenly into 8-row vectors per rank
         self.row_align = tp.row_align if tp is not None else 1
         if self.row_align > 1:
@@ -199,8 +203,13 @@ class ModelRunner:
             if lw.moe is not None:
                 lw.moe.load(weights, m)
             else:
-                put(lw.wgu[:self.F], self._shard_rows(weights[m + "gate_proj.weight"], tp, r))
-                put(lw.wgu[self.F:], self._shard_rows(weights[m + "up_proj.weight"], tp, r))
+                g_ = self._shard_rows(weights[m + "gate_proj.weight"], tp, r)
+                u_ = self._shard_rows(weights[m + "up_proj.weight"], tp, r)
+                if self.fuse_swiglu:
+                    put(lw.wgu, ops.gemm_mod.interleave_gate_up(g_.to(dev), u_.to(dev), self.swiglu_bn))
+                else:
+                    put(lw.wgu[:self.F], g_)
+                    put(lw.wgu[self.F:], u_)
                 wd = weights[m + "down_proj.weight"]
                 cols = wd.shape[1] // tp
                 put(lw.wd, wd[:, r * cols:(r + 1) * cols])
@@ -213,8 +222,11 @@ class ModelRunner:
             return
         gu = self.a_gu[:n] if static else None
         act = self.a_act[:n] if static else None
-        gu = ops.gemm(h[:n], lw.wgu, out=gu)
-        act = ops.swiglu(gu, out=act)
+        if self.fuse_swiglu:
+            act = ops.gemm(h[:n], lw.wgu, out=act, bn=self.swiglu_bn, swiglu=True)
+        else:
+            gu = ops.gemm(h[:n], lw.wgu, out=gu)
+            act = ops.swiglu(gu, out=act)
         self._row_parallel(act, lw.wd, x[:n])
 
     def _row_parallel(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
@@ -282,6 +294,7 @@ class ModelRunner:
         self.d_slots.fill_(-1)
         torch.cuda.synchronize(self.device)
         stream = torch.cuda.Stream(self.device)
+        ops.set_pdl(True)  # decode kernels overlap their prologue with the previous kernel's tail
         with torch.cuda.stream(stream):
             for bk in sorted(self.graph_batch_sizes, reverse=True):
                 self._decode_body(bk)  # warm-up: sets kernel attributes outside capture
@@ -294,6 +307,7 @@ class ModelRunner:
                 if self.graph_pool is None:
                     self.graph_pool = g.pool()
                 self.graphs[bk] = g
+        ops.set_pdl(False)
         torch.cuda.synchronize(self.device)
         ops.check_status(self.device)
 

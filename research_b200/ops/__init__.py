@@ -22,13 +22,23 @@ from .elementwise import (
     swiglu_reference,
     transpose,
 )
-from .gemm import gemm, gemm_reference, linear
+from . import gemm as gemm_mod
+from .gemm import gemm, gemm_reference, interleave_gate_up, linear
 from .sampling import sample_with_logprobs, sample_with_logprobs_reference, token_logprobs
+
+def set_pdl(on: bool) -> None:
+    """Enable programmatic dependent launch for the decode-path kernels (GEMM, norms, RoPE,
+    attention, SwiGLU, embedding, sampling): consecutive kernels overlap prologue and tail."""
+    from .. import _native
+
+    for lib, fn in (("rb_gemm", "rb_gemm_set_pdl"), ("rb_ops", "rb_ops_set_pdl"), ("rb_attn", "rb_attn_set_pdl")):
+        getattr(_native.load(lib), fn)(int(on))
+
 
 __all__ = [
     "KernelStatusError", "check_status", "status_tensor", "decode_num_splits", "gather_kv", "paged_decode",
     "paged_decode_reference", "paged_prefill", "paged_prefill_reference", "embedding", "rmsnorm",
     "rmsnorm_reference", "rope_kv_append", "rope_kv_append_reference", "rope_table", "swiglu", "swiglu_backward",
     "swiglu_reference", "transpose", "gemm", "gemm_reference", "linear", "sample_with_logprobs",
-    "sample_with_logprobs_reference", "token_logprobs",
+    "sample_with_logprobs_reference", "token_logprobs", "set_pdl", "interleave_gate_up", "gemm_mod",
 ]

@@ -60,6 +60,7 @@ class RbGemmArgs(ctypes.Structure):
         ("group_n", ctypes.c_int),
         ("max_tiles", ctypes.c_int),
         ("row_dst", ctypes.c_void_p),
+        ("swiglu", ctypes.c_int),
     ]
 
 
@@ -96,6 +97,7 @@ def gemm(
     out_f32: bool = False,
     bn: int = 0,
     max_ctas: int = 0,
+    swiglu: bool = False,
 ) -> torch.Tensor:
     """``C[M,N] = op(A) @ op(B)^T (+bias) (+residual)``.
 
@@ -103,8 +105,12 @@ def gemm(
     MN-major operands are ``[K, rows]`` row-major. On CUDA this launches the tcgen05 kernel;
     on CPU it evaluates the fp32 reference (used as the oracle in tests).
     """
+    if swiglu:
+        assert bn >= 64 and not (a_mn_major or b_mn_major), "fused SwiGLU needs an explicit bn and K-major operands"
     if not a.is_cuda:
         res = gemm_reference(a, b, bias, residual, a_mn_major, b_mn_major, torch.float32 if out_f32 else None)
+        if swiglu:
+            res = swiglu_interleaved_reference(res, bn)
         if out is not None:
             out.copy_(res)
             return out
@@ -122,7 +128,7 @@ def gemm(
         N, Kb = b.shape
     assert K == Kb, f"K mismatch: {K} vs {Kb}"
     if out is None:
-        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+        out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
     assert out.stride(1) == 1
     args = RbGemmArgs()
     args.A[0] = a.data_ptr()
@@ -140,10 +146,28 @@ def gemm(
     args.max_ctas = max_ctas
     args.epi_mode = EPI_STORE
     args.rank, args.world = 0, 1
+    args.swiglu = int(swiglu)
     args.status = status_tensor(a.device).data_ptr()
     rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
     check_rc(rc, "rb_gemm_bf16_ex")
     return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, bn: int) -> torch.Tensor:
+    """Pack ``gate`` and ``up`` ``[F, K]`` for the fused SwiGLU epilogue: blocks of ``bn/2`` gate rows
+    followed by the matching ``bn/2`` up rows."""
+    F, K = gate.shape
+    h = bn // 2
+    assert F % h == 0, f"F={F} must be a multiple of {h}"
+    return torch.stack([gate.view(F // h, h, K), up.view(F // h, h, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def swiglu_interleaved_reference(y: torch.Tensor, bn: int) -> torch.Tensor:
+    """``silu(gate) * up`` for GEMM output whose columns are interleaved as ``interleave_gate_up`` packs them."""
+    M, N2 = y.shape
+    h = bn // 2
+    yv = y.view(M, N2 // bn, 2, h)
+    return (torch.nn.functional.silu(yv[:, :, 0]) * yv[:, :, 1]).reshape(M, N2 // 2)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=None, out_f32=False):
@@ -155,5 +179,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=
     return y.reshape(*lead, weight.shape[0])
 
 
-__all__ = ["gemm", "gemm_reference", "linear", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
+__all__ = ["gemm", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
 _ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

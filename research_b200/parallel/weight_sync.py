@@ -76,8 +76,14 @@ class WeightSyncPlan:
                     add(name, dst, rows, cols, row0, col0)
             else:
                 F = runner.F
-                add(m + "gate_proj.weight", lw.wgu[:F], F, d, row0=r * F)
-                add(m + "up_proj.weight", lw.wgu[F:], F, d, row0=r * F)
+                if runner.fuse_swiglu:
+                    hb = runner.swiglu_bn // 2   # interleaved blocks: hb gate rows then hb up rows
+                    for j in range(F // hb):
+                        add(m + "gate_proj.weight", lw.wgu[2 * j * hb:(2 * j + 1) * hb], hb, d, row0=r * F + j * hb)
+                        add(m + "up_proj.weight", lw.wgu[(2 * j + 1) * hb:(2 * j + 2) * hb], hb, d, row0=r * F + j * hb)
+                else:
+                    add(m + "gate_proj.weight", lw.wgu[:F], F, d, row0=r * F)
+                    add(m + "up_proj.weight", lw.wgu[F:], F, d, row0=r * F)
                 add(m + "down_proj.weight", lw.wd, d, F, col0=r * F)
         _ = tp
         arr = np.zeros(len(segs), dtype=SEG_DTYPE)

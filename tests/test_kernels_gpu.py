@@ -66,6 +66,25 @@ def test_gemm_epilogue_bias_residual_f32(cuda_device):
     _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.05, rtol=0.01, what="inplace")
 
 
+@pytest.mark.parametrize("M,F,K,bn", [(256, 4864, 896, 256), (70, 512, 256, 128), (300, 256, 320, 64)])
+def test_gemm_fused_swiglu(cuda_device, M, F, K, bn):
+    from research_b200.ops.gemm import interleave_gate_up
+
+    x = _rand((M, K), cuda_device, seed=40)
+    g = _rand((F, K), cuda_device, 0.05, seed=41)
+    u = _rand((F, K), cuda_device, 0.05, seed=42)
+    got = ops.gemm(x, interleave_gate_up(g, u, bn), bn=bn, swiglu=True)
+    want = ops.swiglu_reference(torch.cat([x.float() @ g.float().t(), x.float() @ u.float().t()], -1).bfloat16())
+    assert got.shape == (M, F)
+    _assert_close(got, want, atol=0.02, rtol=0.03, what="fused swiglu")
+    # programmatic dependent launch must not change results
+    ops.set_pdl(True)
+    again = ops.gemm(x, interleave_gate_up(g, u, bn), bn=bn, swiglu=True)
+    y = ops.rmsnorm(again, _rand((F,), cuda_device, seed=43) * 0 + 1)
+    ops.set_pdl(False)
+    assert torch.equal(again, got) and torch.isfinite(y.float()).all()
+
+
 def test_gemm_strided_views(cuda_device):
     big = _rand((256, 2048), cuda_device, seed=9)
     a = big[:, 512:1024]  # lda = 2048
