@@ -511,3 +511,56 @@ extern "C" int rb_paged_prefill(const void* q, const void* k_cache, const void* 
 #undef LAUNCH_PF
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant (see attn_noalloc.h for the contract and for who needs it).
+// ------------------------------------------------------------------------------------------
+#include "attn_noalloc.h"
+
+#include <mutex>
+
+// Per-split partial outputs and (max, sum) pairs. In host code this name is only a handle for
+// the runtime, not a device address: the address is fetched with cudaGetSymbolAddress below.
+static __device__ __align__(256) float rb_decode_noalloc_scratch[RB_DECODE_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device, looked up once per device.
+int noalloc_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return RB_NOALLOC_SYMBOL_LOOKUP_FAILED;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), rb_decode_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) return RB_NOALLOC_SYMBOL_LOOKUP_FAILED;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" long long rb_paged_decode_noalloc_required_floats(int B, int Hq, int D, int num_splits) {
+  if (B <= 0 || Hq <= 0 || D <= 0 || num_splits <= 0) return 0;
+  return (long long)B * Hq * num_splits * (D + 2);
+}
+
+extern "C" int rb_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                       const int* block_tables, const int* seq_lens, void* out, int B, int Hq,
+                                       int Hkv, int D, int max_blocks, int num_blocks, int block_size, int num_splits,
+                                       float scale, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (num_splits < 1) return -1;
+  if (rb_paged_decode_noalloc_required_floats(B, Hq, D, num_splits) > (long long)RB_DECODE_NOALLOC_MAX_FLOATS)
+    return RB_NOALLOC_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // Same kernels and launch logic as the regular entry point, with the library's own workspace.
+  return rb_paged_decode(q, k_cache, v_cache, block_tables, seq_lens, out, scratch, B, Hq, Hkv, D, max_blocks,
+                         num_blocks, block_size, num_splits, scale, status, stream);
+}
