@@ -47,10 +47,13 @@ constexpr int EPI_WARPS = 4;
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int kStages = (BN >= 256) ? 4 : 6;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  // As many stages as fit in 224 KB: small-M GEMMs are bound by TMA round-trip latency divided
+  // by the number of loads in flight, so narrow tiles get deep rings (BN=32: 11 stages).
+  static constexpr int kStagesFit = (224 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 12 ? 12 : kStagesFit;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
   static constexpr int kTmemCols = (NUM_ACC * BN < 32) ? 32 : NUM_ACC * BN;
 };
@@ -86,6 +89,9 @@ struct GemmParams {
   const int* num_tiles_ptr;
   const unsigned long long* row_dst;
   int swiglu;
+  int split_k, kb_per_split;
+  float* splitk_ws;
+  int* splitk_tickets;
 };
 
 __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
@@ -126,6 +132,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   __shared__ __align__(8) uint64_t epi_bar;  // bounded stand-in for a named barrier
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
+  __shared__ int splitk_last;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -138,7 +145,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   const int num_n_tiles = n_tiles_per_part * p.b_parts;
   const bool grouped = p.tile_table != nullptr;
   if (grouped) pdl_wait();  // the tile count itself is produced by the previous kernel
-  const int num_tiles = grouped ? *p.num_tiles_ptr : num_m_tiles * num_n_tiles;
+  const int split_k = p.split_k;
+  const int num_tiles = (grouped ? *p.num_tiles_ptr : num_m_tiles * num_n_tiles) * split_k;  // work units
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -178,6 +186,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   // grouped tiles: m_in = first A row, n_part = first B row, n_in = first output column,
   // m_part carries the number of valid rows
   auto tile_coords = [&](int t, int& m_part, int& m_in, int& n_part, int& n_in) {
+    t /= split_k;
     if (grouped) {
       const int4 e = p.tile_table[t];
       m_in = e.x; m_part = e.y; n_part = e.z; n_in = e.w;
@@ -220,7 +229,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         const CUtensorMap* amap = &p.a_map[grouped ? 0 : m_part];
         const CUtensorMap* bmap = &p.b_map[grouped ? 0 : n_part];
         const int b_row = grouped ? n_part : n_in;   // first B row of the tile
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (t % split_k) * p.kb_per_split;
+        const int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abortp, p.status,
@@ -271,7 +282,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = (t % split_k) * p.kb_per_split;
+        const int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status,
@@ -286,7 +299,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                                         : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * 2048, RB_MN_LBO, RB_MN_SBO)
                                         : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_bf16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
         }
@@ -322,6 +335,68 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
       const int n_base = grouped ? n_in : n_part * p.b_rows_per_part + n_in;    // global column
       const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
+      if (split_k > 1) {
+        // ---- split-K: fp32 partial tile -> workspace; the last slice to arrive finishes the tile ----
+        const int ks = t % split_k;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), r);
+          tmem_ld_wait();
+          const int ncols = min(32, n_valid - c0);
+          if (row_ok && ncols > 0) {
+            float* dst = p.splitk_ws + ((long long)ks * p.M + row) * p.N + n_base + c0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (j < ncols)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        __threadfence();
+        ok = epi_sync();
+        if (!ok) break;
+        if (warp == 2 && lane == 0) {
+          const int tk = atomicAdd(&p.splitk_tickets[t / split_k], 1);
+          splitk_last = (tk == split_k - 1) ? 1 : 0;
+          if (tk == split_k - 1) p.splitk_tickets[t / split_k] = 0;  // ready for the next launch
+        }
+        ok = epi_sync();
+        if (!ok) break;
+        if (splitk_last) {
+          __threadfence();
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            const int ncols = min(32, n_valid - c0);
+            if (row_ok && ncols > 0) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              for (int s2 = 0; s2 < split_k; ++s2) {
+                const float* src = p.splitk_ws + ((long long)s2 * p.M + row) * p.N + n_base + c0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  if (j < ncols) {
+                    const float4 f = __ldcg(reinterpret_cast<const float4*>(src + j));
+                    v[j] += f.x; v[j + 1] += f.y; v[j + 2] += f.z; v[j + 3] += f.w;
+                  }
+              }
+              const int col = n_base + c0;
+              if (p.bias != nullptr)
+                for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(p.bias[col + j]);
+              if (p.residual != nullptr)
+                for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(p.residual[row * p.ldr + col + j]);
+              epi_store_row_chunk(p, v, row, col, ncols);
+            }
+          }
+        }
+        ok = epi_sync();   // splitk_last is reused by the next unit
+        if (!ok) break;
+        continue;
+      }
       if (p.swiglu) {
         if constexpr (BN >= 64) {
           // gate columns [0, BN/2), up columns [BN/2, BN) of the same output channels
@@ -586,7 +661,7 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   }
   const int m_tiles = ((p.a_rows_per_part + BM - 1) / BM) * p.a_parts;
   const int n_tiles = ((p.b_rows_per_part + BN - 1) / BN) * p.b_parts;
-  int grid = m_tiles * n_tiles;
+  int grid = m_tiles * n_tiles * (p.split_k > 1 ? p.split_k : 1);
   if (p.tile_table != nullptr) grid = max_ctas > 0 ? max_ctas : num_sms();  // tile count is only known on the device
   int cap = num_sms();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
@@ -667,6 +742,19 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.num_tiles_ptr = a->num_tiles_ptr;
   p.row_dst = a->row_dst;
   p.swiglu = a->swiglu;
+  p.split_k = a->split_k > 1 ? a->split_k : 1;
+  p.splitk_ws = a->splitk_ws;
+  p.splitk_tickets = a->splitk_tickets;
+  p.kb_per_split = 0;
+  if (p.split_k > 1) {
+    if (p.splitk_ws == nullptr || p.splitk_tickets == nullptr || a->swiglu || a->tile_table || p.epi_mode != RB_EPI_STORE ||
+        a->a_parts != 1 || a->b_parts != 1 || a->N % 4 != 0)
+      return -1;
+    const int num_kb = (a->K + BK - 1) / BK;
+    p.kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
+    p.split_k = (num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty slices
+    if (p.split_k <= 1) { p.split_k = 1; p.kb_per_split = 0; }
+  }
   if (p.swiglu) {
     if (a->bn < 64 || a->N % a->bn != 0 || a->b_parts != 1 || a->out_f32 || p.epi_mode != RB_EPI_STORE || a->bias ||
         a->residual || a->tile_table)

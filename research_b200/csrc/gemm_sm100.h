@@ -58,6 +58,13 @@ typedef struct RbGemmArgs {
   // gate rows [j*bn/2, (j+1)*bn/2) followed by the matching up rows); the kernel writes
   // silu(gate) * up to C, which has N/2 columns. Requires an explicit bn and N % bn == 0.
   int swiglu;
+  // Split-K for skinny problems (few output tiles, long K): the K loop of every tile is cut
+  // into split_k slices computed by different CTAs; each writes an fp32 partial tile to
+  // splitk_ws [split_k][M][N] and the last CTA to finish a tile (ticket counter, self-resetting)
+  // sums the slices in fixed order and applies the epilogue. Deterministic.
+  int split_k;
+  float* splitk_ws;
+  int* splitk_tickets;           // [tiles], zero before first use
 } RbGemmArgs;
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);

@@ -61,6 +61,9 @@ class RbGemmArgs(ctypes.Structure):
         ("max_tiles", ctypes.c_int),
         ("row_dst", ctypes.c_void_p),
         ("swiglu", ctypes.c_int),
+        ("split_k", ctypes.c_int),
+        ("splitk_ws", ctypes.c_void_p),
+        ("splitk_tickets", ctypes.c_void_p),
     ]
 
 
@@ -98,6 +101,7 @@ def gemm(
     bn: int = 0,
     max_ctas: int = 0,
     swiglu: bool = False,
+    split_k: int = 0,
 ) -> torch.Tensor:
     """``C[M,N] = op(A) @ op(B)^T (+bias) (+residual)``.
 
@@ -147,10 +151,45 @@ def gemm(
     args.epi_mode = EPI_STORE
     args.rank, args.world = 0, 1
     args.swiglu = int(swiglu)
+    if split_k == 0:
+        split_k, auto_bn = _auto_split_k(M, N, K, a_mn_major or b_mn_major or swiglu or out_f32)
+        if split_k > 1 and bn == 0:
+            args.bn = auto_bn
+    if split_k > 1:
+        ws, tickets = _splitk_scratch(a.device, split_k * M * N, (-(-M // 128)) * (-(-N // 32)))
+        args.split_k, args.splitk_ws, args.splitk_tickets = split_k, ws.data_ptr(), tickets.data_ptr()
     args.status = status_tensor(a.device).data_ptr()
     rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
     check_rc(rc, "rb_gemm_bf16_ex")
     return out
+
+
+_SPLITK: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _auto_split_k(M: int, N: int, K: int, excluded: bool) -> tuple[int, int]:
+    """Skinny problems (decode-time down projection: few output tiles, long K) are bound by the
+    length of each CTA's serial K loop; cut K so that about two waves of CTAs stream weights."""
+    if excluded or M > 512 or K < 2048:
+        return 1, 0
+    bn = 64
+    tiles = (-(-M // 128)) * (-(-N // bn))
+    if tiles >= 148:
+        return 1, 0
+    num_kb = -(-K // 64)
+    return max(1, min(296 // tiles, num_kb // 4, 16)), bn
+
+
+def _splitk_scratch(device: torch.device, floats: int, tiles: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 partial-tile workspace and per-tile ticket counters, one growing pair per device.
+    Kernels on one stream run in order, so the pair is shared by all split-K launches of that stream."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    cur = _SPLITK.get(idx)
+    if cur is None or cur[0].numel() < floats or cur[1].numel() < tiles:
+        ws = torch.empty(max(floats, cur[0].numel() if cur else 0, 1 << 22), dtype=torch.float32, device=device)
+        tk = torch.zeros(max(tiles, cur[1].numel() if cur else 0, 4096), dtype=torch.int32, device=device)
+        _SPLITK[idx] = (ws, tk)
+    return _SPLITK[idx]
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, bn: int) -> torch.Tensor:

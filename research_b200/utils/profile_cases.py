@@ -1,0 +1,74 @@
+"""Small, fixed workloads for Nsight Compute captures: ``python -m research_b200.utils.profile_cases <case>``.
+
+Each case holds well under a few GB on the device, uses inputs larger than the 126 MB L2 where
+DRAM figures matter, and launches the kernel of interest a handful of times so a
+``--set full`` capture of 1-3 launches ends by itself in a minute or two.
+"""
+
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from .. import ops
+
+
+def case_decode_attn() -> None:
+    """paged_decode at the flagship decode shape: 256 sequences x 832 tokens, 14q/2kv heads, D=64."""
+    from .microbench import bench_decode_attention
+
+    print(bench_decode_attention(256, 832, 14, 2, 64, 6453.4, iters=3))
+
+
+def case_decode_attn_d128() -> None:
+    from .microbench import bench_decode_attention
+
+    print(bench_decode_attention(64, 2304, 32, 8, 128, 6453.4, iters=3))
+
+
+def case_gemm_down() -> None:
+    """Decode-time down projection of the 0.5B shape: M=256, N=896, K=4864."""
+    from .microbench import bench_gemm
+
+    print(bench_gemm(256, 896, 4864, 1688.4, iters=3))
+
+
+def case_gemm_large() -> None:
+    from .microbench import bench_gemm
+
+    print(bench_gemm(4096, 14336, 4096, 1688.4, iters=3))
+
+
+def case_decode_step() -> None:
+    """Two eager decode steps of the 0.5B-shaped model at batch 256 (for a per-launch time list)."""
+    from ..inference import EngineConfig, InferenceEngine, SamplingParams
+    from ..models import get_preset, init_random_weights
+
+    cfg = get_preset("qwen2.5-0.5b")
+    dev = torch.device("cuda:0")
+    w = init_random_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
+    eng = InferenceEngine(EngineConfig(max_batch_size=256, max_model_len=2048, num_kv_blocks=20000, ignore_eos=True,
+                                       use_cuda_graphs=False, max_tokens_per_batch=16384), cfg, w, device=dev)
+    g = torch.Generator().manual_seed(0)
+    for i in range(256):
+        n = int(torch.randint(600, 1000, (1,), generator=g))
+        eng.add_request(torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), SamplingParams(1.0, 64, seed=i))
+    while eng.last_step_rows != (0, 256):
+        eng.step()
+    torch.cuda.synchronize()
+    ops.set_pdl(False)
+    # with `ncu --profile-from-start off` only the launches between start() and stop() are captured
+    torch.cuda.profiler.start()
+    for _ in range(2):
+        eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print("ok")
+
+
+CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else "decode_attn"
+    CASES[name]()

@@ -85,6 +85,22 @@ def test_gemm_fused_swiglu(cuda_device, M, F, K, bn):
     assert torch.equal(again, got) and torch.isfinite(y.float()).all()
 
 
+@pytest.mark.parametrize("M,N,K,split", [(256, 896, 4864, 0), (256, 896, 4864, 5), (64, 4096, 14336, 0), (130, 520, 2056, 3)])
+def test_gemm_split_k(cuda_device, M, N, K, split):
+    a = _rand((M, K), cuda_device, seed=50)
+    b = _rand((N, K), cuda_device, 0.05, seed=51)
+    bias = _rand((N,), cuda_device, seed=52)
+    res = _rand((M, N), cuda_device, seed=53)
+    want = ops.gemm_reference(a, b, bias, res, out_dtype=torch.float32)
+    got = ops.gemm(a, b, bias=bias, residual=res, split_k=split)
+    _assert_close(got, want, atol=0.06, rtol=0.01, what=f"split-k {split}")
+    again = ops.gemm(a, b, bias=bias, residual=res, split_k=split)   # tickets reset themselves; sums are deterministic
+    assert torch.equal(got, again)
+    x = res.clone()
+    ops.gemm(a, b, residual=x, out=x, split_k=split)                  # in-place residual as the decoder uses it
+    _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.06, rtol=0.01, what="split-k inplace")
+
+
 def test_gemm_strided_views(cuda_device):
     big = _rand((256, 2048), cuda_device, seed=9)
     a = big[:, 512:1024]  # lda = 2048
