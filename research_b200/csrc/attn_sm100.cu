@@ -16,6 +16,9 @@
 // Behaviour replaced: rollouts/inference/attention/flex_backend.py:144-279 (SDPA prefill and
 // the host-loop gather decode). Numerics oracle: qwen_functional.py:173-248.
 #include "common.cuh"
+#include "tma_host.h"
+
+#include <stdlib.h>
 
 namespace rb {
 
@@ -267,6 +270,178 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,         // [B, Hq, D]
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Decode, TMA variant (default): every 16-token block of one KV head is a contiguous [16, D]
+// tile, fetched with ONE tile copy per 128 bytes of row (1 for D=64, 2 for D=128) instead of 128
+// sixteen-byte requests. The 128-byte swizzle of the copy is exactly the XOR layout ldmatrix
+// needs. Each warp owns a ring of 3-4 (K,V) tiles with one mbarrier per stage; an
+// out-of-range block id lands on an out-of-bounds coordinate, which TMA fills with zeros.
+// ------------------------------------------------------------------------------------------
+template <int D>
+constexpr int dec_tma_stages() { return D <= 64 ? 4 : 3; }   // 3 CTAs/SM at D=64, 2 at D=128
+
+// 16-byte chunk c of row r inside a [16, D] tile loaded as D/64 swizzled [16][128 B] half tiles
+template <int D>
+__device__ __forceinline__ uint32_t swz_tma(int r, int c) {
+  return (uint32_t)((c >> 3) * (KV_BLOCK * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+paged_decode_tma_kernel(const __nv_bfloat16* __restrict__ q, const __grid_constant__ CUtensorMap k_map,
+                        const __grid_constant__ CUtensorMap v_map, const int* __restrict__ block_tables,
+                        const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int Hq, int Hkv, int max_blocks,
+                        int num_blocks, int num_splits, float scale, int* status) {
+  constexpr int CH = D / 8;
+  constexpr int TILE_BYTES = KV_BLOCK * D * 2;
+  constexpr int ST = dec_tma_stages<D>();
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ __align__(8) uint64_t bars[DEC_WARPS][ST];
+  __shared__ int abort_flag;
+  pdl_launch_dependents();
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = Hq / Hkv;
+  // layout: [ring: DEC_WARPS x ST x (K tile, V tile)] (1024-byte aligned) then the Q tile
+  const uint32_t ring0 = (smem_u32(smem) + 1023u) & ~1023u;
+  uint8_t* ring_ptr = smem + (ring0 - smem_u32(smem));
+  const uint32_t kv_smem = ring0 + warp * (ST * 2 * TILE_BYTES);
+  uint8_t* q_ptr = ring_ptr + DEC_WARPS * ST * 2 * TILE_BYTES;
+  const uint32_t q_smem = smem_u32(q_ptr);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int w = 0; w < DEC_WARPS; ++w)
+      for (int s2 = 0; s2 < ST; ++s2) mbar_init(smem_u32(&bars[w][s2]), 1);
+    fence_mbar_init();
+  }
+  pdl_wait();
+  const int L = seq_lens[b];
+  const int n_chunks = (L + KV_BLOCK - 1) / KV_BLOCK;
+  const int per = (n_chunks + num_splits - 1) / num_splits;
+  const int c_begin = split * per;
+  const int c_end = min(n_chunks, c_begin + per);
+  for (int i = threadIdx.x; i < 16 * CH; i += blockDim.x) {
+    const int r = i / CH, c = i % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)b * Hq + kvh * G + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_ptr + swz<D>(r, c)) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+  {
+    const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+      ldsm_x4(q_smem + swz<D>((mat & 1) * 8 + r, 2 * ks + (mat >> 1)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  RowState st = {-INFINITY, -INFINITY, 0.f, 0.f};
+  const float scale_log2 = scale * 1.4426950408889634f;
+  volatile int* abortp = &abort_flag;
+
+  const int first = c_begin + warp;
+  const int n_my = first < c_end ? (c_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
+  auto issue = [&](int i) {   // lane 0 only
+    const int chunk = first + i * DEC_WARPS;
+    const int stage = i % ST;
+    int blk = block_tables[(long long)b * max_blocks + chunk];
+    if (blk < 0 || blk >= num_blocks) { set_status(status, ST_BAD_INDEX); blk = num_blocks; }  // OOB -> zeros
+    const int y = (blk * Hkv + kvh) * KV_BLOCK;
+    const uint32_t bar = smem_u32(&bars[warp][stage]);
+    const uint32_t ks = kv_smem + stage * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+    mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+    for (int hx = 0; hx < D / 64; ++hx) {
+      tma_load_2d(ks + hx * (KV_BLOCK * 128), &k_map, bar, hx * 64, y);
+      tma_load_2d(vs + hx * (KV_BLOCK * 128), &v_map, bar, hx * 64, y);
+    }
+  };
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < ST - 1 && issued < n_my; ++issued) issue(issued);
+  issued = __shfl_sync(0xffffffffu, issued, 0);
+  bool ok = true;
+  const int mat = lane >> 3, rr = lane & 7;
+  for (int i = 0; i < n_my; ++i) {
+    if (lane == 0 && issued < n_my) issue(issued);
+    if (issued < n_my) ++issued;
+    const int stage = i % ST;
+    ok = mbar_wait_bounded(smem_u32(&bars[warp][stage]), (uint32_t)((i / ST) & 1), abortp, status, ST_TIMEOUT_SMEM_FULL);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const uint32_t ks = kv_smem + stage * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+    float s0[4] = {0, 0, 0, 0}, s1[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(ks + swz_tma<D>((mat >> 1) * 8 + rr, 2 * kk + (mat & 1)), b0, b1, b2, b3);
+      mma_16816(s0, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
+      mma_16816(s1, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
+    }
+    const int tok0 = (first + i * DEC_WARPS) * KV_BLOCK + 2 * (lane & 3);
+    if (tok0 >= L) { s0[0] = s0[2] = -INFINITY; }
+    if (tok0 + 1 >= L) { s0[1] = s0[3] = -INFINITY; }
+    if (tok0 + 8 >= L) { s1[0] = s1[2] = -INFINITY; }
+    if (tok0 + 9 >= L) { s1[1] = s1[3] = -INFINITY; }
+    uint32_t p0, p1, p2, p3;
+    softmax_update<D>(s0, s1, st, o, scale_log2, p0, p1, p2, p3);
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(vs + swz_tma<D>((mat & 1) * 8 + rr, 2 * dp + (mat >> 1)), b0, b1, b2, b3);
+      mma_16816(o[2 * dp], p0, p1, p2, p3, b0, b1);
+      mma_16816(o[2 * dp + 1], p0, p1, p2, p3, b2, b3);
+    }
+    __syncwarp();   // every lane is done with this stage before lane 0 refills it
+  }
+  if (!ok && lane == 0) {
+    // drain: wait (bounded) for copies already issued so none lands after the CTA has exited
+    for (int j = max(0, issued - ST); j < issued; ++j) {   // the latest phase of every stage
+      const uint64_t t0 = globaltimer_ns();
+      while (!mbar_try_wait(smem_u32(&bars[warp][j % ST]), (uint32_t)((j / ST) & 1)))
+        if (globaltimer_ns() - t0 > 50000000ull) break;
+    }
+  }
+  __syncthreads();
+
+  float* mo = reinterpret_cast<float*>(ring_ptr);                   // [DEC_WARPS][8][D]
+  float* mml = mo + DEC_WARPS * 8 * D;                              // [DEC_WARPS][8][2]
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    mo[(warp * 8 + g) * D + n * 8 + 2 * t] = o[n][0];
+    mo[(warp * 8 + g) * D + n * 8 + 2 * t + 1] = o[n][1];
+  }
+  if (t == 0) { mml[(warp * 8 + g) * 2] = st.m0; mml[(warp * 8 + g) * 2 + 1] = st.l0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int r = i / D, d = i % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mml[(w * 8 + r) * 2]);
+    float acc = 0.f, l = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; ++w) {
+        const float e = exp2f(mml[(w * 8 + r) * 2] - M);
+        acc += e * mo[(w * 8 + r) * D + d];
+        l += e * mml[(w * 8 + r) * 2 + 1];
+      }
+    }
+    const int h = kvh * G + r;
+    if (num_splits == 1) {
+      out[((long long)b * Hq + h) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      const long long pi = ((long long)b * Hq + h) * num_splits + split;
+      part_o[pi * D + d] = acc;
+      if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = l; }
+    }
+  }
+}
+
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int num_splits) {
@@ -437,6 +612,10 @@ constexpr int decode_smem_bytes() {
   return 16 * D * 2 + DEC_WARPS * DEC_STAGES * 2 * KV_BLOCK * D * 2;
 }
 template <int D>
+constexpr int decode_tma_smem_bytes() {
+  return 1024 + DEC_WARPS * dec_tma_stages<D>() * 2 * KV_BLOCK * D * 2 + 16 * D * 2;
+}
+template <int D>
 constexpr int prefill_smem_bytes() {
   return PF_BM * D * 2 + 4 * PF_BN * D * 2;
 }
@@ -463,6 +642,33 @@ extern "C" int rb_paged_decode(const void* q, const void* k_cache, const void* v
   float* part_o = workspace;
   float* part_ml = workspace ? workspace + (long long)B * Hq * num_splits * D : nullptr;
   dim3 grid(num_splits, Hkv, B);
+  static const bool use_cpasync = getenv("RB_DECODE_CPASYNC") != nullptr;
+  if (!use_cpasync) {
+    CUtensorMap kmap, vmap;
+    const unsigned long long rows = (unsigned long long)num_blocks * Hkv * KV_BLOCK;
+    if (tma_map_2d_bf16(&kmap, k_cache, rows, D, D, KV_BLOCK) != 0) return -20;
+    if (tma_map_2d_bf16(&vmap, v_cache, rows, D, D, KV_BLOCK) != 0) return -21;
+#define LAUNCH_DEC_TMA(DD)                                                                                    \
+  do {                                                                                                        \
+    static bool attr = false;                                                                                 \
+    if (!attr) {                                                                                              \
+      if (cudaFuncSetAttribute(paged_decode_tma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                               decode_tma_smem_bytes<DD>()) != cudaSuccess) return -10;                       \
+      attr = true;                                                                                            \
+    }                                                                                                         \
+    launch_kernel(paged_decode_tma_kernel<DD>, grid, dim3(DEC_WARPS * 32), decode_tma_smem_bytes<DD>(), stream, \
+        (const __nv_bfloat16*)q, kmap, vmap, block_tables, seq_lens, (__nv_bfloat16*)out, part_o, part_ml, Hq, \
+        Hkv, max_blocks, num_blocks, num_splits, scale, status);                                              \
+    if (num_splits > 1)                                                                                       \
+      launch_kernel(decode_merge_kernel<DD>, dim3(B * Hq), dim3(DD), 0, stream, (const float*)part_o,         \
+                    (const float*)part_ml, (__nv_bfloat16*)out, num_splits);                                  \
+  } while (0)
+    if (D == 64) LAUNCH_DEC_TMA(64);
+    else if (D == 128) LAUNCH_DEC_TMA(128);
+    else return -1;
+#undef LAUNCH_DEC_TMA
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
 #define LAUNCH_DEC(DD)                                                                                        \
   do {                                                                                                        \
     static bool attr = false;                                                                                 \

@@ -11,30 +11,50 @@ namespace rb {
 // RMSNorm: y = bf16( bf16(x * rsqrt(mean(x^2)+eps)) * w ). One warp per row.
 // Reference math: rollouts/tools/functional_extractor/qwen_functional.py:46-65.
 // ------------------------------------------------------------------------------------------
+// The row is read from global memory once: up to 8 vectors of 8 bf16 per lane stay in
+// registers (d <= 2048); longer rows fall back to a second read that hits L1/L2.
 __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                __nv_bfloat16* __restrict__ y, long long rows, int d, long long ldx,
                                long long ldy, float eps) {
   pdl_launch_dependents();
   pdl_wait();
+  constexpr int MAXV = 8;
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const __nv_bfloat16* xr = x + row * ldx;
   __nv_bfloat16* yr = y + row * ldy;
   const int nvec = d >> 3;
+  const bool in_regs = nvec <= MAXV * 32;
+  uint4 keep[MAXV];
   float ss = 0.f;
-  for (int v = lane; v < nvec; v += 32) {
-    uint4 u = *reinterpret_cast<const uint4*>(xr + v * 8);
-    float2 f;
-    f = unpack_bf16x2(u.x); ss += f.x * f.x + f.y * f.y;
-    f = unpack_bf16x2(u.y); ss += f.x * f.x + f.y * f.y;
-    f = unpack_bf16x2(u.z); ss += f.x * f.x + f.y * f.y;
-    f = unpack_bf16x2(u.w); ss += f.x * f.x + f.y * f.y;
+  if (in_regs) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      keep[i] = v < nvec ? *reinterpret_cast<const uint4*>(xr + v * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      float2 f;
+      f = unpack_bf16x2(keep[i].x); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(keep[i].y); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(keep[i].z); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(keep[i].w); ss += f.x * f.x + f.y * f.y;
+    }
+  } else {
+    for (int v = lane; v < nvec; v += 32) {
+      uint4 u = *reinterpret_cast<const uint4*>(xr + v * 8);
+      float2 f;
+      f = unpack_bf16x2(u.x); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(u.y); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(u.z); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(u.w); ss += f.x * f.x + f.y * f.y;
+    }
   }
   ss = warp_sum(ss);
   const float rstd = rsqrtf(ss / (float)d + eps);
-  for (int v = lane; v < nvec; v += 32) {
-    uint4 u = *reinterpret_cast<const uint4*>(xr + v * 8);
+  auto emit = [&](int v, uint4 u) {
     uint4 ww = *reinterpret_cast<const uint4*>(w + v * 8);
     uint32_t xi[4] = {u.x, u.y, u.z, u.w};
     uint32_t wi[4] = {ww.x, ww.y, ww.z, ww.w};
@@ -49,6 +69,15 @@ __global__ void rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
       oi[j] = pack_bf16x2(a * g.x, b * g.y);
     }
     *reinterpret_cast<uint4*>(yr + v * 8) = make_uint4(oi[0], oi[1], oi[2], oi[3]);
+  };
+  if (in_regs) {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) emit(v, keep[i]);
+    }
+  } else {
+    for (int v = lane; v < nvec; v += 32) emit(v, *reinterpret_cast<const uint4*>(xr + v * 8));
   }
 }
 
@@ -391,7 +420,7 @@ extern "C" void rb_ops_set_pdl(int on) { rb::pdl_enabled() = on != 0; }
 extern "C" int rb_rmsnorm(const void* x, const void* w, void* y, long long rows, int d, long long ldx,
                           long long ldy, float eps, cudaStream_t stream) {
   if (d % 8 != 0 || rows <= 0) return -1;
-  const int warps = 8;
+  const int warps = rows >= 148 * 8 * 4 ? 8 : 2;   // few rows: spread them over more SMs
   const long long grid = (rows + warps - 1) / warps;
   return launch_kernel(rmsnorm_kernel, dim3((unsigned)grid), dim3(warps * 32), 0, stream, (const __nv_bfloat16*)x,
                        (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rows, d, ldx, ldy, eps) == cudaSuccess ? 0 : -11;
