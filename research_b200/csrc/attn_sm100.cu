@@ -278,7 +278,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,         // [B, Hq, D]
 // out-of-range block id lands on an out-of-bounds coordinate, which TMA fills with zeros.
 // ------------------------------------------------------------------------------------------
 template <int D>
-constexpr int dec_tma_stages() { return D <= 64 ? 4 : 3; }   // 3 CTAs/SM at D=64, 2 at D=128
+__host__ __device__ constexpr int dec_tma_stages() { return D <= 64 ? 4 : 3; }   // 3 CTAs/SM at D=64, 2 at D=128
 
 // 16-byte chunk c of row r inside a [16, D] tile loaded as D/64 swizzled [16][128 B] half tiles
 template <int D>
@@ -296,7 +296,7 @@ paged_decode_tma_kernel(const __nv_bfloat16* __restrict__ q, const __grid_consta
   constexpr int CH = D / 8;
   constexpr int TILE_BYTES = KV_BLOCK * D * 2;
   constexpr int ST = dec_tma_stages<D>();
-  extern __shared__ __align__(1024) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];   // the ring is aligned to 1024 bytes by hand below
   __shared__ __align__(8) uint64_t bars[DEC_WARPS][ST];
   __shared__ int abort_flag;
   pdl_launch_dependents();
