@@ -278,7 +278,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q,         // [B, Hq, D]
 // out-of-range block id lands on an out-of-bounds coordinate, which TMA fills with zeros.
 // ------------------------------------------------------------------------------------------
 template <int D>
-__host__ __device__ constexpr int dec_tma_stages() { return D <= 64 ? 4 : 3; }   // 3 CTAs/SM at D=64, 2 at D=128
+__host__ __device__ constexpr int dec_tma_stages() { return 3; }   // 52 KB (D=64: 4 CTAs/SM) or 103 KB (D=128: 2 CTAs/SM)
 
 // 16-byte chunk c of row r inside a [16, D] tile loaded as D/64 swizzled [16][128 B] half tiles
 template <int D>
@@ -344,10 +344,20 @@ paged_decode_tma_kernel(const __nv_bfloat16* __restrict__ q, const __grid_consta
 
   const int first = c_begin + warp;
   const int n_my = first < c_end ? (c_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
-  auto issue = [&](int i) {   // lane 0 only
-    const int chunk = first + i * DEC_WARPS;
+  // Block ids of this warp's chunks are fetched 32 at a time (lane j holds chunk round*32+j) so the
+  // table lookup is off the critical path of every copy.
+  const int* bt_row = block_tables + (long long)b * max_blocks;
+  auto load_ids = [&](int round) {
+    const int j = round * 32 + lane;
+    return j < n_my ? __ldg(bt_row + first + j * DEC_WARPS) : 0;
+  };
+  int ids_round = 0, ids = load_ids(0), ids_next = load_ids(1);
+  auto blk_of = [&](int i) {   // all lanes, i uniform and non-decreasing
+    if ((i >> 5) > ids_round) { ids = ids_next; ids_round = i >> 5; ids_next = load_ids(ids_round + 1); }
+    return __shfl_sync(0xffffffffu, ids, i & 31);
+  };
+  auto issue = [&](int i, int blk) {   // lane 0 only
     const int stage = i % ST;
-    int blk = block_tables[(long long)b * max_blocks + chunk];
     if (blk < 0 || blk >= num_blocks) { set_status(status, ST_BAD_INDEX); blk = num_blocks; }  // OOB -> zeros
     const int y = (blk * Hkv + kvh) * KV_BLOCK;
     const uint32_t bar = smem_u32(&bars[warp][stage]);
@@ -360,14 +370,18 @@ paged_decode_tma_kernel(const __nv_bfloat16* __restrict__ q, const __grid_consta
     }
   };
   int issued = 0;
-  if (lane == 0)
-    for (; issued < ST - 1 && issued < n_my; ++issued) issue(issued);
-  issued = __shfl_sync(0xffffffffu, issued, 0);
+  for (; issued < ST - 1 && issued < n_my; ++issued) {
+    const int blk = blk_of(issued);
+    if (lane == 0) issue(issued, blk);
+  }
   bool ok = true;
   const int mat = lane >> 3, rr = lane & 7;
   for (int i = 0; i < n_my; ++i) {
-    if (lane == 0 && issued < n_my) issue(issued);
-    if (issued < n_my) ++issued;
+    if (issued < n_my) {
+      const int blk = blk_of(issued);
+      if (lane == 0) issue(issued, blk);
+      ++issued;
+    }
     const int stage = i % ST;
     ok = mbar_wait_bounded(smem_u32(&bars[warp][stage]), (uint32_t)((i / ST) & 1), abortp, status, ST_TIMEOUT_SMEM_FULL);
     ok = __all_sync(0xffffffffu, ok);

@@ -90,6 +90,7 @@ struct GemmParams {
   const unsigned long long* row_dst;
   int swiglu;
   int split_k, kb_per_split;
+  int stages;
   float* splitk_ws;
   int* splitk_tickets;
 };
@@ -123,10 +124,11 @@ template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
-  constexpr int STAGES = Cfg::kStages;
+  constexpr int MAX_STAGES = Cfg::kStages;
+  const int STAGES = p.stages;   // ring depth of this launch (<= MAX_STAGES); short-K launches use a shallow ring
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES];
   __shared__ __align__(8) uint64_t tmem_full_bar[NUM_ACC];
   __shared__ __align__(8) uint64_t tmem_empty_bar[NUM_ACC];
   __shared__ __align__(8) uint64_t epi_bar;  // bounded stand-in for a named barrier
@@ -337,21 +339,21 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
       if (split_k > 1) {
         // ---- split-K: fp32 partial tile -> workspace; the last slice to arrive finishes the tile ----
+        // Workspace layout per work unit: [BN/4 column quads][BM rows] of float4, so that the 32
+        // lanes of a warp (32 consecutive rows) store and load 512 contiguous bytes.
+        constexpr int UNIT_F4 = BM * BN / 4;
         const int ks = t % split_k;
+        const int trow = q * 32 + lane;
+        float4* wsu = reinterpret_cast<float4*>(p.splitk_ws) + (long long)t * UNIT_F4;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), r);
           tmem_ld_wait();
-          const int ncols = min(32, n_valid - c0);
-          if (row_ok && ncols > 0) {
-            float* dst = p.splitk_ws + ((long long)ks * p.M + row) * p.N + n_base + c0;
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (j < ncols)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-          }
+          for (int j = 0; j < 32; j += 4)
+            wsu[((c0 + j) >> 2) * BM + trow] = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
         }
         tc_fence_before();
         __syncwarp();
@@ -368,27 +370,35 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (!ok) break;
         if (splitk_last) {
           __threadfence();
+          const float4* base = reinterpret_cast<const float4*>(p.splitk_ws) + (long long)(t - ks) * UNIT_F4;
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 32) {
             const int ncols = min(32, n_valid - c0);
-            if (row_ok && ncols > 0) {
-              float v[32];
+            if (ncols <= 0) break;
+            float v[32];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = 0.f;
-              for (int s2 = 0; s2 < split_k; ++s2) {
-                const float* src = p.splitk_ws + ((long long)s2 * p.M + row) * p.N + n_base + c0;
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+#pragma unroll 4
+            for (int s2 = 0; s2 < split_k; ++s2) {   // fixed order: the sum does not depend on arrival order
+              const float4* src = base + (long long)s2 * UNIT_F4 + (c0 >> 2) * BM + trow;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                  if (j < ncols) {
-                    const float4 f = __ldcg(reinterpret_cast<const float4*>(src + j));
-                    v[j] += f.x; v[j + 1] += f.y; v[j + 2] += f.z; v[j + 3] += f.w;
-                  }
+              for (int j = 0; j < 32; j += 4) {
+                const float4 f = __ldcg(src + (j >> 2) * BM);
+                v[j] += f.x; v[j + 1] += f.y; v[j + 2] += f.z; v[j + 3] += f.w;
               }
+            }
+            if (row_ok) {
               const int col = n_base + c0;
-              if (p.bias != nullptr)
-                for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(p.bias[col + j]);
-              if (p.residual != nullptr)
-                for (int j = 0; j < ncols; ++j) v[j] += __bfloat162float(p.residual[row * p.ldr + col + j]);
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < ncols) v[j] += __bfloat162float(p.bias[col + j]);
+              }
+              if (p.residual != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < ncols) v[j] += __bfloat162float(p.residual[row * p.ldr + col + j]);
+              }
               epi_store_row_chunk(p, v, row, col, ncols);
             }
           }
@@ -667,7 +677,26 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::kSmemBytes, stream, p) == cudaSuccess ? 0 : -11;
+  // Ring depth. A CTA that runs a single short work unit is latency-bound and gains nothing from a
+  // deep ring, while a small footprint lets it become resident (programmatic dependent launch)
+  // beside the CTAs of the kernel before it; long persistent launches take the full ring.
+  GemmParams q = p;
+  int stages = Cfg::kStages;
+  if (p.tile_table == nullptr) {
+    const long long units = (long long)m_tiles * n_tiles * (p.split_k > 1 ? p.split_k : 1);
+    const long long units_per_cta = (units + grid - 1) / grid;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const long long kb_cta = units_per_cta * (p.split_k > 1 ? p.kb_per_split : num_kb);
+    if (kb_cta < stages) stages = kb_cta < 2 ? 2 : (int)kb_cta;
+    if (units_per_cta == 1) {
+      const int fit = (112 * 1024) / Cfg::kStageBytes;
+      const int lim = fit > 4 ? fit : 4;
+      if (stages > lim) stages = lim;
+    }
+  }
+  q.stages = stages;
+  const int smem = stages * Cfg::kStageBytes + 1024;
+  return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
 }
 
 template <int BN>

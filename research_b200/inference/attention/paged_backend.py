@@ -55,5 +55,5 @@ class PagedAttentionBackend:
             cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=dev)
             return ops.paged_prefill(q.contiguous(), self.k_cache[layer_idx], self.v_cache[layer_idx], bt, cu, lens,
                                      max(qlens), self.scale, ctx.sliding_window or self.config.sliding_window)
-        splits = ops.decode_num_splits(B, self.config.num_kv_heads, max(ctx.seq_lens))
+        splits = ops.decode_num_splits(B, self.config.num_kv_heads, max(ctx.seq_lens), head_dim=self.config.head_dim)
         return ops.paged_decode(q.contiguous(), self.k_cache[layer_idx], self.v_cache[layer_idx], bt, lens, self.scale, splits)

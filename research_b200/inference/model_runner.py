@@ -254,7 +254,7 @@ class ModelRunner:
         cfg = self.cfg
         x, h = self.a_x, self.a_h
         ops.embedding(self.d_tokens[:bk], self.embed, out=x[:bk])
-        splits = ops.decode_num_splits(bk, self.Hkv, self.max_model_len)
+        splits = ops.decode_num_splits(bk, self.Hkv, self.max_model_len, head_dim=self.D)
         if bk > 64:
             splits = 1
         bt = self.bt_dev[:bk]

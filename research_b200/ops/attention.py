@@ -83,14 +83,22 @@ def paged_prefill_reference(q, k_cache, v_cache, block_tables, cu_q, seq_lens, s
     return out.to(q.dtype)
 
 
-def decode_num_splits(batch: int, hkv: int, max_len: int, sms: int = 148) -> int:
-    """Split long contexts when (batch x kv heads) alone cannot fill the GPU."""
-    ctas = batch * hkv
-    if ctas >= 2 * sms or max_len <= 512:
+def decode_num_splits(batch: int, hkv: int, max_len: int, sms: int = 148, head_dim: int = 64) -> int:
+    """Number of KV splits per (sequence, kv head). One CTA handles one split; the GPU holds
+    ``sms x (4 CTAs at head_dim 64, 2 at 128)`` CTAs at once, so the cost of a choice is the number
+    of CTA waves divided by the split count, plus a small charge per split for the merge pass."""
+    if max_len <= 512:
         return 1
-    want = max(1, (2 * sms) // max(ctas, 1))
-    chunks = max(1, max_len // 256)
-    return int(min(want, chunks, 32))
+    slots = sms * (4 if head_dim <= 64 else 2)
+    ctas = max(batch * hkv, 1)
+    max_splits = int(min(32, max(1, max_len // 256)))
+    best, best_cost = 1, None
+    for s in range(1, max_splits + 1):
+        waves = -(-ctas * s // slots)
+        cost = waves / s + 0.02 * (s - 1)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def paged_decode(q, k_cache, v_cache, block_tables, seq_lens, scale=None, num_splits: int = 1, out=None,

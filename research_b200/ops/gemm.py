@@ -7,6 +7,7 @@ Replaces the cuBLAS ``F.linear`` calls inside the HF modules the reference runs
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -156,7 +157,8 @@ def gemm(
         if split_k > 1 and bn == 0:
             args.bn = auto_bn
     if split_k > 1:
-        ws, tickets = _splitk_scratch(a.device, split_k * M * N, (-(-M // 128)) * (-(-N // 32)))
+        # one [128 x bn] fp32 tile per (output tile, K slice); padded for the widest tile the kernel may pick
+        ws, tickets = _splitk_scratch(a.device, split_k * (-(-M // 128) * 128) * (-(-N // 256) * 256), (-(-M // 128)) * (-(-N // 32)))
         args.split_k, args.splitk_ws, args.splitk_tickets = split_k, ws.data_ptr(), tickets.data_ptr()
     args.status = status_tensor(a.device).data_ptr()
     rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
@@ -168,16 +170,18 @@ _SPLITK: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def _auto_split_k(M: int, N: int, K: int, excluded: bool) -> tuple[int, int]:
-    """Skinny problems (decode-time down projection: few output tiles, long K) are bound by the
-    length of each CTA's serial K loop; cut K so that about two waves of CTAs stream weights."""
-    if excluded or M > 512 or K < 2048:
+    """Split K only for very skinny, very long problems. Measured on the flagship decode step
+    (M=256, N=896, K=4864) a 5-way split that fills one wave of CTAs is slower than 56 unsplit CTAs:
+    the partial-tile round trip through L2 (store, fence, ticket, reload) costs more than the
+    shorter K loop saves, so the automatic choice starts at K >= 8192 with fewer than 37 tiles."""
+    if excluded or M > 512 or K < 8192 or os.environ.get("RB_NO_SPLITK"):
         return 1, 0
     bn = 64
     tiles = (-(-M // 128)) * (-(-N // bn))
-    if tiles >= 148:
+    if tiles > 37:
         return 1, 0
     num_kb = -(-K // 64)
-    return max(1, min(296 // tiles, num_kb // 4, 16)), bn
+    return max(1, min(148 // tiles, num_kb // 8, 16)), bn
 
 
 def _splitk_scratch(device: torch.device, floats: int, tiles: int) -> tuple[torch.Tensor, torch.Tensor]:

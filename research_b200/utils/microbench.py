@@ -41,7 +41,7 @@ def bench_decode_attention(B, ctx, Hq, Hkv, D, peak_gbs, iters=10):
     sl = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
     q = torch.randn(B, Hq, D, device="cuda").bfloat16()
     out = torch.empty_like(q)
-    splits = ops.decode_num_splits(B, Hkv, ctx)
+    splits = ops.decode_num_splits(B, Hkv, ctx, head_dim=D)
     t = time_cuda(lambda: ops.paged_decode(q, kc, vc, bt, sl, num_splits=splits, out=out), iters=iters)
     byts = 2.0 * B * ctx * Hkv * D * 2
     ach = byts / (t["median_ms"] * 1e-3) / 1e9
