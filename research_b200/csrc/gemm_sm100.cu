@@ -28,6 +28,8 @@
 #include "common.cuh"
 #include "gemm_sm100.h"
 
+#include <stdlib.h>
+
 #include <mutex>
 #include <stdio.h>
 
@@ -688,7 +690,8 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
     const int num_kb = (p.K + BK - 1) / BK;
     const long long kb_cta = units_per_cta * (p.split_k > 1 ? p.kb_per_split : num_kb);
     if (kb_cta < stages) stages = kb_cta < 2 ? 2 : (int)kb_cta;
-    if (units_per_cta == 1) {
+    static const bool deep = getenv("RB_GEMM_DEEP_RING") != nullptr;
+    if (units_per_cta == 1 && !deep) {
       const int fit = (112 * 1024) / Cfg::kStageBytes;
       const int lim = fit > 4 ? fit : 4;
       if (stages > lim) stages = lim;
