@@ -1,0 +1,424 @@
+// Flash attention for sm_100a on the 5th-generation tensor cores.
+//
+// Forward: one CTA owns 128 query rows of one head. S = Q K^T and O += P V are tcgen05.mma
+// instructions issued by one thread; S (two buffers) and O live in tensor memory, Q/K/V tiles are
+// brought into 128-byte-swizzled shared memory by TMA, P goes back to shared memory as the A operand
+// of the second product. Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5
+// softmax (one query row per thread, read from TMEM with tcgen05.ld). The running maximum is only
+// refreshed when it grew by more than 2^8, so the O accumulator is rescaled rarely.
+//
+// Inputs are packed variable-length batches (`cu_seqlens`), grouped-query heads, causal and
+// sliding-window masks; K/V come either from dense [T, Hkv, D] tensors (training) or from the paged
+// cache [num_blocks, Hkv, 16, D] through a block table (prefill with a cached prefix).
+//
+// Replaces F.scaled_dot_product_attention / FlexAttention in the reference
+// (rollouts/inference/attention/flex_backend.py:144-185) and the Hopper-only varlen flash kernel of
+// dev/speedrun/single-file.py:932-943.
+//
+// Every wait is bounded; on a timeout the kernel records a status code, drains its copies, frees
+// tensor memory and returns.
+#include "common.cuh"
+#include "tma_host.h"
+
+#include <math.h>
+
+namespace rb {
+
+constexpr int FA_BM = 128;        // query rows per CTA
+constexpr int FA_BN = 128;        // keys per iteration
+constexpr int FA_THREADS = 192;   // 6 warps
+constexpr int FA_KV_SLOTS = 4;    // ring of K/V tiles: K0 V0 K1 V1 ...
+constexpr int FA_TMEM_COLS = 512;
+constexpr float FA_RESCALE_THRESHOLD = 8.f;   // log2 units
+
+struct FlashFwdParams {
+  CUtensorMap q_map;   // [Tq, Hq*D], box 64 x 128
+  CUtensorMap k_map;   // dense: [Tk, Hkv*D], box 64 x 128; paged: [num_blocks*Hkv*16, D], box 64 x 16
+  CUtensorMap v_map;
+  __nv_bfloat16* out;  // [Tq, Hq, D]
+  float* lse;          // [Hq, Tq] natural-log sum-exp of the scaled scores
+  const int* cu_q;     // [B+1]
+  const int* cu_k;     // [B+1] (dense)
+  const int* seq_lens; // [B] total keys per sequence (paged)
+  const int* block_tables;  // [B, max_blocks] (paged)
+  int max_blocks, num_blocks;
+  int Hq, Hkv, Tq;
+  int causal, window, paged;
+  float scale_log2;
+  int* status;
+};
+
+template <int D>
+struct FlashCfg {
+  static constexpr int kTileBytes = FA_BN * D * 2;          // one K or V tile (and the Q tile)
+  static constexpr int kPBytes = FA_BM * FA_BN * 2;
+  static constexpr int kSmemBytes = 1024 + kTileBytes + FA_KV_SLOTS * kTileBytes + 2 * kPBytes;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_constant__ FlashFwdParams p) {
+  using Cfg = FlashCfg<D>;
+  constexpr int DCH = D / 64;                    // 64-column chunks of the head dimension
+  constexpr int CHUNK_BYTES = FA_BN * 128;       // 128 rows x 128 B
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t q_full, kv_full[FA_KV_SLOTS], kv_empty[FA_KV_SLOTS];
+  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_done;
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;           // long (late) tiles first
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int q0 = q_tile * FA_BM;
+  if (q0 >= q_len) return;                                  // uniform per CTA, before any set-up
+  const int kv_len = p.paged ? p.seq_lens[b] : (p.cu_k[b + 1] - p.cu_k[b]);
+  const int k_begin = p.paged ? 0 : p.cu_k[b];
+  const int off = kv_len - q_len;                           // key position of query 0
+  const int kvh = h / (p.Hq / p.Hkv);
+  // keys this tile can see
+  int hi = p.causal ? min(kv_len, off + q0 + FA_BM) : kv_len;
+  int lo = 0;
+  if (p.window > 0) lo = max(0, off + q0 - p.window + 1);
+  const int t_begin = lo / FA_BN;
+  const int t_end = (hi + FA_BN - 1) / FA_BN;
+  const int n_tiles = max(t_end - t_begin, 0);
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t q_s = smem_base;
+  const uint32_t kv_s = q_s + Cfg::kTileBytes;
+  const uint32_t p_s = kv_s + FA_KV_SLOTS * Cfg::kTileBytes;
+  uint8_t* p_ptr = smem_al + Cfg::kTileBytes + FA_KV_SLOTS * Cfg::kTileBytes;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&q_full), 1);
+    for (int i = 0; i < FA_KV_SLOTS; ++i) {
+      mbar_init(smem_u32(&kv_full[i]), 1);
+      mbar_init(smem_u32(&kv_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&s_empty[i]), 4);
+      mbar_init(smem_u32(&p_full[i]), 4);
+      mbar_init(smem_u32(&p_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&o_done), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), FA_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  const uint32_t tmem_o = tmem_base + 2 * FA_BN;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one_sync()) {
+      bool ok = true;
+      mbar_expect_tx(smem_u32(&q_full), Cfg::kTileBytes);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c)
+        tma_load_2d(q_s + c * CHUNK_BYTES, &p.q_map, smem_u32(&q_full), h * D + c * 64, q_begin + q0);
+      uint32_t it = 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int k0 = (t_begin + j) * FA_BN;
+#pragma unroll 1
+        for (int which = 0; which < 2 && ok; ++which, ++it) {   // 0: K tile, 1: V tile
+          const int slot = it % FA_KV_SLOTS;
+          ok = mbar_wait_bounded(smem_u32(&kv_empty[slot]), ((it / FA_KV_SLOTS) & 1u) ^ 1u, abortp, p.status,
+                                 ST_TIMEOUT_SMEM_EMPTY);
+          if (!ok) break;
+          const uint32_t fb = smem_u32(&kv_full[slot]);
+          const uint32_t dst = kv_s + slot * Cfg::kTileBytes;
+          const CUtensorMap* map = which == 0 ? &p.k_map : &p.v_map;
+          mbar_expect_tx(fb, Cfg::kTileBytes);
+          if (!p.paged) {
+#pragma unroll
+            for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, fb, kvh * D + c * 64, k_begin + k0);
+          } else {
+            const int* bt = p.block_tables + (long long)b * p.max_blocks;
+            const int n_blk = (kv_len + 15) >> 4;
+#pragma unroll 1
+            for (int i = 0; i < FA_BN / 16; ++i) {
+              const int bi = (k0 >> 4) + i;
+              int blk = p.num_blocks;                         // out of range: the copy fills zeros
+              if (bi < n_blk) {
+                blk = bt[bi];
+                if (blk < 0 || blk >= p.num_blocks) { set_status(p.status, ST_BAD_INDEX); blk = p.num_blocks; }
+              }
+              const int y = (blk * p.Hkv + kvh) * 16;
+#pragma unroll
+              for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES + i * 2048, map, fb, c * 64, y);
+            }
+          }
+        }
+      }
+      if (!ok) {   // drain: no bulk copy may land after the CTA has gone
+        const uint32_t first = it > (uint32_t)FA_KV_SLOTS ? it - FA_KV_SLOTS : 0;
+        for (uint32_t j = first; j < it; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&kv_full[j % FA_KV_SLOTS]), (j / FA_KV_SLOTS) & 1u))
+            if (globaltimer_ns() - t0 > 50000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one_sync()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, FA_BN, 0, 0);   // Q, K both K-major
+      constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, D, 0, 1);       // P K-major, V MN-major
+      bool ok = mbar_wait_bounded(smem_u32(&q_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      auto issue_s = [&](int j) -> bool {
+        const uint32_t it = 2 * j;
+        const int slot = it % FA_KV_SLOTS;
+        if (!mbar_wait_bounded(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL))
+          return false;
+        if (!mbar_wait_bounded(smem_u32(&s_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY))
+          return false;
+        tc_fence_after();
+        const uint32_t ks = kv_s + slot * Cfg::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(q_s + (k >> 2) * CHUNK_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(ks + (k >> 2) * CHUNK_BYTES + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + (j & 1) * FA_BN, adesc, bdesc, idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&kv_empty[slot]));
+        umma_commit(smem_u32(&s_full[j & 1]));
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
+        const uint32_t it = 2 * j + 1;
+        const int slot = it % FA_KV_SLOTS;
+        ok = mbar_wait_bounded(smem_u32(&p_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        ok = mbar_wait_bounded(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t vs = kv_s + slot * Cfg::kTileBytes;
+        const uint32_t ps = p_s + (j & 1) * Cfg::kPBytes;
+#pragma unroll
+        for (int k = 0; k < FA_BN / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(ps + (k >> 2) * CHUNK_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(vs + k * 2048, CHUNK_BYTES, 1024);
+          umma_bf16(tmem_o, adesc, bdesc, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&kv_empty[slot]));
+        umma_commit(smem_u32(&p_empty[j & 1]));
+        umma_commit(smem_u32(&o_done));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int qd = warp & 3;                     // TMEM lane quarter of this warp
+    const int r = qd * 32 + lane;                // query row inside the tile
+    const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
+    const int qpos = off + q0 + r;               // key position of this query
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int k0 = (t_begin + j) * FA_BN;
+      const uint32_t s_addr = tmem_base + (j & 1) * FA_BN + lane_addr;
+      ok = mbar_wait_bounded(smem_u32(&s_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const bool need_mask = (k0 + FA_BN > kv_len) || (p.causal && k0 + FA_BN - 1 > off + q0) ||
+                             (p.window > 0 && k0 <= off + q0 + FA_BM - 1 - p.window);
+      auto masked = [&](int kj) -> bool {
+        return kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window);
+      };
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < FA_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!masked(k0 + c * 32 + i)) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      const bool need = m_new > m_used + FA_RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
+      if (__any_sync(0xffffffffu, need)) {
+        if (j > 0) {
+          // O holds the products of tiles 0..j-1 once the previous P V has completed
+          ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = need ? exp2f((m_used == -INFINITY ? m_new : m_used) - m_new) : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(tmem_o + lane_addr + c * 32, v);
+          }
+          tmem_st_wait();
+          l *= alpha;
+        }
+        if (need) m_used = m_new;
+      }
+      const float mref = m_used == -INFINITY ? 0.f : m_used;
+      // pass 2: P = exp2(S * scale - m), row sums, bf16 P into shared memory (A operand of P V)
+      ok = mbar_wait_bounded(smem_u32(&p_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      uint8_t* prow = p_ptr + (j & 1) * Cfg::kPBytes + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < FA_BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_addr + c * 32, v);
+        tmem_ld_wait();
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -mref));
+          if (need_mask && masked(k0 + c * 32 + i)) x = 0.f;
+          e[i] = x;
+          l += x;
+        }
+        uint8_t* pc = prow + (c >> 1) * CHUNK_BYTES;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint4 w;
+          w.x = pack_bf16x2(e[u * 8 + 0], e[u * 8 + 1]);
+          w.y = pack_bf16x2(e[u * 8 + 2], e[u * 8 + 3]);
+          w.z = pack_bf16x2(e[u * 8 + 4], e[u * 8 + 5]);
+          w.w = pack_bf16x2(e[u * 8 + 6], e[u * 8 + 7]);
+          const int unit = (c & 1) * 4 + u;
+          *reinterpret_cast<uint4*>(pc + ((unit ^ (r & 7)) << 4)) = w;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();   // P was written with ordinary stores and is read by the tensor core
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&s_empty[j & 1]));
+        mbar_arrive(smem_u32(&p_full[j & 1]));
+      }
+    }
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((n_tiles - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = q0 + r < q_len;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.out + ((long long)(q_begin + q0 + r) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+          }
+        }
+      }
+      if (row_ok && p.lse != nullptr)
+        p.lse[(long long)h * p.Tq + q_begin + q0 + r] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, FA_TMEM_COLS);
+  }
+}
+
+
+template <int D>
+static int launch_flash_fwd(const FlashFwdParams& p, dim3 grid, cudaStream_t stream) {
+  using Cfg = FlashCfg<D>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
+        cudaSuccess)
+      return -10;
+    attr = true;
+  }
+  return launch_kernel(flash_fwd_kernel<D>, grid, dim3(FA_THREADS), Cfg::kSmemBytes, stream, p) == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace rb
+
+extern "C" {
+
+// Packed varlen attention forward. Dense mode: k, v are [Tk, Hkv, D] views with row strides
+// ldk, ldv (elements) and cu_k gives the key ranges. Paged mode: k, v are the cache
+// [num_blocks, Hkv, 16, D] (kv_rows = num_blocks), keys of sequence b are the first seq_lens[b]
+// slots of its block table and its queries are the LAST (cu_q[b+1]-cu_q[b]) positions.
+int rb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q,
+                 const int* cu_k, const int* seq_lens, const int* block_tables, int B, int Tq, int kv_rows,
+                 int Hq, int Hkv, int D, int ldq, int ldk, int ldv, int max_seqlen_q, int max_blocks, int causal,
+                 int window, int paged, float scale, int* status, cudaStream_t stream) {
+  using namespace rb;
+  if (B <= 0 || Tq <= 0 || max_seqlen_q <= 0) return 0;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0) return -1;
+  FlashFwdParams p;
+  if (tma_map_2d_bf16(&p.q_map, q, Tq, (unsigned long long)Hq * D, ldq, FA_BM) != 0) return -20;
+  if (!paged) {
+    if (tma_map_2d_bf16(&p.k_map, k, kv_rows, (unsigned long long)Hkv * D, ldk, FA_BN) != 0) return -21;
+    if (tma_map_2d_bf16(&p.v_map, v, kv_rows, (unsigned long long)Hkv * D, ldv, FA_BN) != 0) return -22;
+  } else {
+    const unsigned long long rows = (unsigned long long)kv_rows * Hkv * 16;
+    if (tma_map_2d_bf16(&p.k_map, k, rows, D, D, 16) != 0) return -21;
+    if (tma_map_2d_bf16(&p.v_map, v, rows, D, D, 16) != 0) return -22;
+  }
+  p.out = (__nv_bfloat16*)out;
+  p.lse = lse;
+  p.cu_q = cu_q;
+  p.cu_k = cu_k;
+  p.seq_lens = seq_lens;
+  p.block_tables = block_tables;
+  p.max_blocks = max_blocks;
+  p.num_blocks = paged ? kv_rows : 0;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.Tq = Tq;
+  p.causal = causal;
+  p.window = window;
+  p.paged = paged;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((max_seqlen_q + FA_BM - 1) / FA_BM, Hq, B);
+  int rc = D == 64 ? launch_flash_fwd<64>(p, grid, stream) : launch_flash_fwd<128>(p, grid, stream);
+  if (rc != 0) return rc;
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+}  // extern "C"

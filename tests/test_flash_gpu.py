@@ -1,0 +1,94 @@
+"""tcgen05 flash attention (forward and backward) against fp32 PyTorch references."""
+
+import math
+
+import pytest
+import torch
+
+from research_b200 import ops
+from research_b200.ops import flash
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, device, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).to(device)
+
+
+def _cu(lens, device):
+    return torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=device)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 14, 2), (128, 8, 2), (128, 4, 4)])
+@pytest.mark.parametrize("causal,window", [(True, 0), (True, 100), (False, 0)])
+def test_flash_varlen_forward(cuda_device, D, Hq, Hkv, causal, window):
+    lens = [1, 127, 128, 129, 300, 517]
+    T = sum(lens)
+    # q, k, v as views of one fused projection output (row stride > H*D)
+    qkv = _rand((T, (Hq + 2 * Hkv) * D), cuda_device, seed=1)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D :].view(T, Hkv, D)
+    cu = _cu(lens, cuda_device)
+    got, lse = flash.flash_attn_varlen(q, k, v, cu, cu, max(lens), causal=causal, window=window, return_lse=True)
+    want, lse_ref = flash.flash_attn_varlen_reference(q, k, v, cu, cu, causal=causal, window=window)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+    assert torch.allclose(lse, lse_ref, atol=2e-3, rtol=1e-4), (lse - lse_ref).abs().max().item()
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 14, 2), (128, 8, 2)])
+def test_flash_cross_lengths(cuda_device, D, Hq, Hkv):
+    """More keys than queries: the queries are the last positions (chunked prefill)."""
+    q_lens, k_lens = [5, 64, 130, 1], [5, 200, 400, 77]
+    q = _rand((sum(q_lens), Hq, D), cuda_device, seed=2)
+    k = _rand((sum(k_lens), Hkv, D), cuda_device, seed=3)
+    v = _rand((sum(k_lens), Hkv, D), cuda_device, seed=4)
+    cu_q, cu_k = _cu(q_lens, cuda_device), _cu(k_lens, cuda_device)
+    got = flash.flash_attn_varlen(q, k, v, cu_q, cu_k, max(q_lens))
+    want, _ = flash.flash_attn_varlen_reference(q, k, v, cu_q, cu_k)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 14, 2), (128, 32, 8)])
+@pytest.mark.parametrize("window", [0, 48])
+def test_flash_paged_prefill(cuda_device, D, Hq, Hkv, window):
+    new = [5, 64, 65, 130, 1, 200]
+    prefix = [0, 16, 3, 100, 40, 0]
+    lens = [n + p for n, p in zip(new, prefix)]
+    B, bs = len(lens), 16
+    nblk = [(l + bs - 1) // bs for l in lens]
+    total = sum(nblk) + 3
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(5))
+    kc = _rand((total, Hkv, bs, D), cuda_device, seed=30)
+    vc = _rand((total, Hkv, bs, D), cuda_device, seed=31)
+    bt = torch.zeros(B, max(nblk) + 2, dtype=torch.int32)
+    o = 0
+    for b in range(B):
+        bt[b, : nblk[b]] = perm[o : o + nblk[b]].to(torch.int32)
+        o += nblk[b]
+    bt = bt.to(cuda_device)
+    cu = _cu(new, cuda_device)
+    q = _rand((sum(new), Hq, D), cuda_device, seed=32)
+    sl = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    got = flash.flash_paged_prefill(q, kc, vc, bt, cu, sl, max(new), window=window)
+    want = ops.paged_prefill_reference(q, kc, vc, bt, cu, sl, window=window)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+
+
+def test_flash_large_scores(cuda_device):
+    """Scores that grow along the sequence exercise the lazy rescale of the O accumulator."""
+    D, H, T = 128, 2, 1024
+    q = _rand((T, H, D), cuda_device, seed=7, scale=3.0)
+    k = _rand((T, H, D), cuda_device, seed=8, scale=3.0)
+    k = (k.float() * torch.linspace(0.2, 3.0, T, device=cuda_device)[:, None, None]).to(torch.bfloat16)
+    v = _rand((T, H, D), cuda_device, seed=9)
+    cu = _cu([T], cuda_device)
+    got, lse = flash.flash_attn_varlen(q, k, v, cu, cu, T, return_lse=True)
+    want, lse_ref = flash.flash_attn_varlen_reference(q, k, v, cu, cu)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.03 and diff.mean().item() < 0.002, (diff.max().item(), diff.mean().item())
+    assert torch.allclose(lse, lse_ref, atol=5e-3, rtol=1e-4)
