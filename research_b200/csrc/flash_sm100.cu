@@ -31,6 +31,33 @@ constexpr int FA_KV_SLOTS = 4;    // ring of K/V tiles: K0 V0 K1 V1 ...
 constexpr int FA_TMEM_COLS = 512;
 constexpr float FA_RESCALE_THRESHOLD = 8.f;   // log2 units
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Polling wait for the single-thread producer / MMA roles: sleeps between polls so the spinning
+// thread does not take issue slots from the softmax warps on the same scheduler.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(64);
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0) return false;
+      if (globaltimer_ns() - t0 > RB_WAIT_BUDGET_NS) {
+        *abort_flag = 1;
+        set_status(status, code);
+        return false;
+      }
+    }
+  }
+}
+
 struct FlashFwdParams {
   CUtensorMap q_map;   // [Tq, Hq*D], box 64 x 128
   CUtensorMap k_map;   // dense: [Tk, Hkv*D], box 64 x 128; paged: [num_blocks*Hkv*16, D], box 64 x 16
@@ -133,7 +160,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
 #pragma unroll 1
         for (int which = 0; which < 2 && ok; ++which, ++it) {   // 0: K tile, 1: V tile
           const int slot = it % FA_KV_SLOTS;
-          ok = mbar_wait_bounded(smem_u32(&kv_empty[slot]), ((it / FA_KV_SLOTS) & 1u) ^ 1u, abortp, p.status,
+          ok = mbar_wait_backoff(smem_u32(&kv_empty[slot]), ((it / FA_KV_SLOTS) & 1u) ^ 1u, abortp, p.status,
                                  ST_TIMEOUT_SMEM_EMPTY);
           if (!ok) break;
           const uint32_t fb = smem_u32(&kv_full[slot]);
@@ -175,13 +202,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
     if (elect_one_sync()) {
       constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, FA_BN, 0, 0);   // Q, K both K-major
       constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, D, 0, 1);       // P K-major, V MN-major
-      bool ok = mbar_wait_bounded(smem_u32(&q_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      bool ok = mbar_wait_backoff(smem_u32(&q_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
       auto issue_s = [&](int j) -> bool {
         const uint32_t it = 2 * j;
         const int slot = it % FA_KV_SLOTS;
-        if (!mbar_wait_bounded(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL))
+        if (!mbar_wait_backoff(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL))
           return false;
-        if (!mbar_wait_bounded(smem_u32(&s_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY))
+        if (!mbar_wait_backoff(smem_u32(&s_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY))
           return false;
         tc_fence_after();
         const uint32_t ks = kv_s + slot * Cfg::kTileBytes;
@@ -200,9 +227,9 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
         if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
         const uint32_t it = 2 * j + 1;
         const int slot = it % FA_KV_SLOTS;
-        ok = mbar_wait_bounded(smem_u32(&p_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        ok = mbar_wait_backoff(smem_u32(&p_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
         if (!ok) break;
-        ok = mbar_wait_bounded(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+        ok = mbar_wait_backoff(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
         if (!ok) break;
         tc_fence_after();
         const uint32_t vs = kv_s + slot * Cfg::kTileBytes;
@@ -234,26 +261,32 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       tc_fence_after();
       const bool need_mask = (k0 + FA_BN > kv_len) || (p.causal && k0 + FA_BN - 1 > off + q0) ||
                              (p.window > 0 && k0 <= off + q0 + FA_BM - 1 - p.window);
-      auto masked = [&](int kj) -> bool {
-        return kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window);
-      };
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      // the whole score row (128 columns) goes to registers with one wait; the S buffer is free again
+      uint32_t v[FA_BN];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (!masked(k0 + c * 32 + i)) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
+      for (int c = 0; c < FA_BN / 32; ++c)
+        tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_empty[j & 1]));
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        for (int i = 0; i < FA_BN; ++i) {
+          const int kj = k0 + i;
+          const bool dead = kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window);
+          if (dead) v[i] = 0xff800000u;   // -inf
         }
       }
-      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 4) {
+        mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
+        mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
+        mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
+        mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
+      }
+      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
       const bool need = m_new > m_used + FA_RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
       if (__any_sync(0xffffffffu, need)) {
         if (j > 0) {
@@ -262,15 +295,15 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
-          const float alpha = need ? exp2f((m_used == -INFINITY ? m_new : m_used) - m_new) : 1.f;
+          const float alpha = need ? fast_exp2((m_used == -INFINITY ? m_new : m_used) - m_new) : 1.f;
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_addr + c * 32, v);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_o + lane_addr + c * 32, o);
           }
           tmem_st_wait();
           l *= alpha;
@@ -278,43 +311,35 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
         if (need) m_used = m_new;
       }
       const float mref = m_used == -INFINITY ? 0.f : m_used;
-      // pass 2: P = exp2(S * scale - m), row sums, bf16 P into shared memory (A operand of P V)
+      // P = exp2(S * scale - m): a masked score is -inf and gives exactly 0
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 4) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float x = fast_exp2(fmaf(__uint_as_float(v[i + t]), p.scale_log2, -mref));
+          ls[t] += x;
+          v[i + t] = __float_as_uint(x);
+        }
+      }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      // bf16 P into shared memory (A operand of P V) once the P V of two tiles ago has read the buffer
       ok = mbar_wait_bounded(smem_u32(&p_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* prow = p_ptr + (j & 1) * Cfg::kPBytes + r * 128;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(s_addr + c * 32, v);
-        tmem_ld_wait();
-        float e[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = exp2f(fmaf(__uint_as_float(v[i]), p.scale_log2, -mref));
-          if (need_mask && masked(k0 + c * 32 + i)) x = 0.f;
-          e[i] = x;
-          l += x;
-        }
-        uint8_t* pc = prow + (c >> 1) * CHUNK_BYTES;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 w;
-          w.x = pack_bf16x2(e[u * 8 + 0], e[u * 8 + 1]);
-          w.y = pack_bf16x2(e[u * 8 + 2], e[u * 8 + 3]);
-          w.z = pack_bf16x2(e[u * 8 + 4], e[u * 8 + 5]);
-          w.w = pack_bf16x2(e[u * 8 + 6], e[u * 8 + 7]);
-          const int unit = (c & 1) * 4 + u;
-          *reinterpret_cast<uint4*>(pc + ((unit ^ (r & 7)) << 4)) = w;
-        }
+      for (int unit = 0; unit < FA_BN / 8; ++unit) {
+        uint4 w;
+        w.x = pack_bf16x2(__uint_as_float(v[unit * 8 + 0]), __uint_as_float(v[unit * 8 + 1]));
+        w.y = pack_bf16x2(__uint_as_float(v[unit * 8 + 2]), __uint_as_float(v[unit * 8 + 3]));
+        w.z = pack_bf16x2(__uint_as_float(v[unit * 8 + 4]), __uint_as_float(v[unit * 8 + 5]));
+        w.w = pack_bf16x2(__uint_as_float(v[unit * 8 + 6]), __uint_as_float(v[unit * 8 + 7]));
+        *reinterpret_cast<uint4*>(prow + (unit >> 3) * CHUNK_BYTES + (((unit & 7) ^ (r & 7)) << 4)) = w;
       }
-      tc_fence_before();
       fence_proxy_async_smem();   // P was written with ordinary stores and is read by the tensor core
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(&s_empty[j & 1]));
-        mbar_arrive(smem_u32(&p_full[j & 1]));
-      }
+      if (lane == 0) mbar_arrive(smem_u32(&p_full[j & 1]));
     }
     if (ok && n_tiles > 0) {
       ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((n_tiles - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);

@@ -66,6 +66,32 @@ def bench_prefill_attention(B, n, Hq, Hkv, D, peak_tflops, iters=5):
             "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3)}
 
 
+def bench_flash_forward(B, n, Hq, Hkv, D, peak_tflops, iters=5, paged=False):
+    """tcgen05 flash attention forward, causal, B sequences of n tokens (dense or paged K/V)."""
+    from ..ops import flash
+
+    q = torch.randn(B * n, Hq, D, device="cuda").bfloat16()
+    cu = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
+    out = torch.empty_like(q)
+    if paged:
+        bs = 16
+        nblk = (n + bs - 1) // bs
+        kc = torch.randn(B * nblk, Hkv, bs, D, device="cuda").bfloat16()
+        vc = torch.randn(B * nblk, Hkv, bs, D, device="cuda").bfloat16()
+        bt = torch.arange(B * nblk, device="cuda", dtype=torch.int32).reshape(B, nblk).contiguous()
+        sl = torch.full((B,), n, dtype=torch.int32, device="cuda")
+        fn = lambda: flash.flash_paged_prefill(q, kc, vc, bt, cu, sl, n, out=out)  # noqa: E731
+    else:
+        k = torch.randn(B * n, Hkv, D, device="cuda").bfloat16()
+        v = torch.randn(B * n, Hkv, D, device="cuda").bfloat16()
+        fn = lambda: flash.flash_attn_varlen(q, k, v, cu, cu, n, out=out)  # noqa: E731
+    t = time_cuda(fn, iters=iters)
+    flops = 4.0 * B * Hq * D * n * n / 2
+    ach = flops / (t["median_ms"] * 1e-3) / 1e12
+    return {"kernel": "flash_fwd_paged" if paged else "flash_fwd", "B": B, "n": n, "Hq": Hq, "Hkv": Hkv, "D": D,
+            "ms": round(t["median_ms"], 4), "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3)}
+
+
 def bench_rmsnorm(rows, d, peak_gbs):
     x = torch.randn(rows, d, device="cuda").bfloat16()
     w = torch.randn(d, device="cuda").bfloat16()
@@ -105,6 +131,10 @@ def main() -> None:
     rows.append(bench_decode_attention(4, 8192, 32, 8, 128, args.peak_gbs))
     rows.append(bench_prefill_attention(8, 2048, 32, 8, 128, args.peak_tflops))
     rows.append(bench_prefill_attention(16, 1024, 14, 2, 64, args.peak_tflops))
+    rows.append(bench_flash_forward(8, 2048, 32, 8, 128, args.peak_tflops))
+    rows.append(bench_flash_forward(8, 2048, 32, 8, 128, args.peak_tflops, paged=True))
+    rows.append(bench_flash_forward(4, 8192, 32, 8, 128, args.peak_tflops))
+    rows.append(bench_flash_forward(16, 1024, 14, 2, 64, args.peak_tflops))
     rows.append(bench_rmsnorm(16384, 4096, args.peak_gbs))
     rows.append(bench_sampling(256, 151936, args.peak_gbs))
     for r in rows:
