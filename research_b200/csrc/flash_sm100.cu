@@ -386,6 +386,565 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
 }
 
 
+// ==========================================================================================
+// Backward. Three kernels, no atomics, deterministic:
+//   prep : delta[h,t] = sum_d dO*O and lse in log2 units
+//   dkdv : one CTA per (128-key tile, kv head); loops over the query heads of the group and their
+//          64-query tiles. S^T = K Q^T and dP^T = V dO^T land in TMEM (keys on the 128 lanes, so a
+//          thread owns a key row), P^T and dS^T go to shared memory as K-major A operands of
+//          dV += P^T dO and dK += dS^T Q, which accumulate in TMEM over the whole loop.
+//   dq   : one CTA per (128-query tile, head); loops over 64-key tiles. S = Q K^T, dP = dO V^T in
+//          TMEM, dS to shared memory, dQ += dS K accumulates in TMEM.
+// The same Q / dO / K / V shared-memory tile serves as a K-major operand of the score products and
+// as an MN-major operand of the gradient products: only the descriptor differs.
+// ==========================================================================================
+struct FlashBwdParams {
+  CUtensorMap q64, do64, k128, v128;     // dkdv kernel boxes
+  CUtensorMap q128, do128, k64, v64;     // dq kernel boxes
+  const float* lse2;                     // [Hq, Tq]
+  const float* delta;                    // [Hq, Tq]
+  __nv_bfloat16 *dq, *dk, *dv;           // [Tq,Hq,D], [Tk,Hkv,D], [Tk,Hkv,D]
+  const int* cu_q;
+  const int* cu_k;
+  int Hq, Hkv, Tq, Tk;
+  int causal, window;
+  float scale_log2, scale;
+  int* status;
+};
+
+__global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                      const float* __restrict__ lse, float* __restrict__ delta,
+                                      float* __restrict__ lse2, int Tq, int Hq, int D) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= Tq * Hq) return;
+  const int t = warp / Hq, h = warp % Hq;
+  const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(dout + ((long long)t * Hq + h) * D);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(out + ((long long)t * Hq + h) * D);
+  float acc = 0.f;
+  for (int i = lane; i < D / 2; i += 32) {
+    const float2 x = __bfloat1622float2(a[i]), y = __bfloat1622float2(b[i]);
+    acc += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    delta[(long long)h * Tq + t] = acc;
+    lse2[(long long)h * Tq + t] = lse[(long long)h * Tq + t] * 1.4426950408889634f;
+  }
+}
+
+template <int D>
+struct FlashBwdCfg {
+  static constexpr int kQdoStages = D == 128 ? 2 : 4;       // dkdv: (Q, dO) 64-row tiles in flight
+  static constexpr int kKvStages = 3;                       // dq: (K, V) 64-row tiles in flight
+  static constexpr int kBig = 128 * D * 2;                  // a 128-row tile
+  static constexpr int kSmall = 64 * D * 2;                 // a 64-row tile
+  static constexpr int kPd = 128 * 64 * 2;                  // P^T / dS^T / dS tile
+  static constexpr int kSmemDkdv = 1024 + 2 * kBig + kQdoStages * 2 * kSmall + 4 * kPd;
+  static constexpr int kSmemDq = 1024 + 2 * kBig + kKvStages * 2 * kSmall + 2 * kPd;
+};
+
+// 64 packed bf16 values of one row into a 128-byte swizzled row of a K-major tile
+__device__ __forceinline__ void store_row64_sw128(uint8_t* row_ptr, int r, const float (&x)[64]) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    uint4 w;
+    w.x = pack_bf16x2(x[u * 8 + 0], x[u * 8 + 1]);
+    w.y = pack_bf16x2(x[u * 8 + 2], x[u * 8 + 3]);
+    w.z = pack_bf16x2(x[u * 8 + 4], x[u * 8 + 5]);
+    w.w = pack_bf16x2(x[u * 8 + 6], x[u * 8 + 7]);
+    *reinterpret_cast<uint4*>(row_ptr + ((u ^ (r & 7)) << 4)) = w;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __grid_constant__ FlashBwdParams p) {
+  using Cfg = FlashBwdCfg<D>;
+  constexpr int DCH = D / 64;
+  constexpr int ST = Cfg::kQdoStages;
+  constexpr int CH128 = 128 * 128, CH64 = 64 * 128;   // bytes of one 64-column chunk of a 128- / 64-row tile
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t kv_full, qdo_full[ST], qdo_empty[ST];
+  __shared__ __align__(8) uint64_t st_full[2], st_empty[2], pds_full[2], pds_empty[2], acc_done, stat_bar;
+  __shared__ float stat[2][2][64];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int k_begin = p.cu_k[b], kv_len = p.cu_k[b + 1] - k_begin;
+  const int k0 = blockIdx.x * 128;
+  if (k0 >= kv_len) return;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int off = kv_len - q_len;
+  const int G = p.Hq / p.Hkv;
+  // queries that see at least one key of this tile
+  const int kmax = min(k0 + 127, kv_len - 1);
+  int qi_lo = 0, qi_hi = q_len;
+  if (p.causal) qi_lo = max(0, k0 - off);
+  if (p.window > 0) qi_hi = min(q_len, kmax + p.window - off);
+  const int i_begin = qi_lo / 64;
+  const int n_qt = qi_hi > qi_lo ? (qi_hi + 63) / 64 - i_begin : 0;
+  const int n_iter = n_qt * G;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t k_s = smem_base, v_s = k_s + Cfg::kBig;
+  const uint32_t qdo_s = v_s + Cfg::kBig;                       // stage: Q tile then dO tile
+  const uint32_t pds_off = 2 * Cfg::kBig + ST * 2 * Cfg::kSmall;   // buffer: P^T then dS^T
+  const uint32_t pds_s = smem_base + pds_off;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&kv_full), 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(smem_u32(&qdo_full[i]), 1); mbar_init(smem_u32(&qdo_empty[i]), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&st_full[i]), 1);
+      mbar_init(smem_u32(&st_empty[i]), 4);
+      mbar_init(smem_u32(&pds_full[i]), 4);
+      mbar_init(smem_u32(&pds_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&acc_done), 1);
+    mbar_init(smem_u32(&stat_bar), 128);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), FA_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  const uint32_t tm_dv = tmem_base + 256, tm_dk = tmem_base + 256 + D;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      bool ok = true;
+      mbar_expect_tx(smem_u32(&kv_full), 2 * Cfg::kBig);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_2d(k_s + c * CH128, &p.k128, smem_u32(&kv_full), kvh * D + c * 64, k_begin + k0);
+        tma_load_2d(v_s + c * CH128, &p.v128, smem_u32(&kv_full), kvh * D + c * 64, k_begin + k0);
+      }
+      int it = 0;
+      for (; it < n_iter; ++it) {
+        const int h = kvh * G + it / n_qt, i = i_begin + it % n_qt;
+        const int stage = it % ST;
+        ok = mbar_wait_backoff(smem_u32(&qdo_empty[stage]), ((it / ST) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&qdo_full[stage]);
+        const uint32_t dst = qdo_s + stage * 2 * Cfg::kSmall;
+        mbar_expect_tx(fb, 2 * Cfg::kSmall);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_2d(dst + c * CH64, &p.q64, fb, h * D + c * 64, q_begin + i * 64);
+          tma_load_2d(dst + Cfg::kSmall + c * CH64, &p.do64, fb, h * D + c * 64, q_begin + i * 64);
+        }
+      }
+      if (!ok) {
+        for (int j = max(0, it - ST); j < it; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&qdo_full[j % ST]), (j / ST) & 1u))
+            if (globaltimer_ns() - t0 > 50000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+      bool ok = mbar_wait_backoff(smem_u32(&kv_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      auto issue_st = [&](int it) -> bool {
+        const int stage = it % ST;
+        if (!mbar_wait_backoff(smem_u32(&qdo_full[stage]), (it / ST) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
+        if (!mbar_wait_backoff(smem_u32(&st_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t q_s = qdo_s + stage * 2 * Cfg::kSmall, do_s = q_s + Cfg::kSmall;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a = make_smem_desc_sw128(k_s + (k >> 2) * CH128 + (k & 3) * 32, 16, 1024);
+          const uint64_t bq = make_smem_desc_sw128(q_s + (k >> 2) * CH64 + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + (it & 1) * 64, a, bq, idesc_st, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a = make_smem_desc_sw128(v_s + (k >> 2) * CH128 + (k & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(do_s + (k >> 2) * CH64 + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + 128 + (it & 1) * 64, a, bd, idesc_st, k > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&st_full[it & 1]));
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_st(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (it + 1 < n_iter) { ok = issue_st(it + 1); if (!ok) break; }
+        ok = mbar_wait_backoff(smem_u32(&pds_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const int stage = it % ST;
+        const uint32_t q_s = qdo_s + stage * 2 * Cfg::kSmall, do_s = q_s + Cfg::kSmall;
+        const uint32_t pt_s = pds_s + (it & 1) * 2 * Cfg::kPd, dst_s = pt_s + Cfg::kPd;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // 64 queries = 4 k-steps
+          const uint64_t a = make_smem_desc_sw128(pt_s + k * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(do_s + k * 2048, CH64, 1024);
+          umma_bf16(tm_dv, a, bd, idesc_acc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t a = make_smem_desc_sw128(dst_s + k * 32, 16, 1024);
+          const uint64_t bq = make_smem_desc_sw128(q_s + k * 2048, CH64, 1024);
+          umma_bf16(tm_dk, a, bq, idesc_acc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&qdo_empty[stage]));
+        umma_commit(smem_u32(&pds_empty[it & 1]));
+      }
+      if (ok) umma_commit(smem_u32(&acc_done));
+    }
+  } else {
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;                  // key row of the tile
+    const int kj = k0 + r;
+    const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
+    const int tid = threadIdx.x - 64;              // 0..127
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int h = kvh * G + it / n_qt, qi0 = (i_begin + it % n_qt) * 64;
+      {   // row statistics of the 64 queries: thread t<64 -> lse2, t>=64 -> delta
+        const int idx = tid & 63, which = tid >> 6;
+        const int qi = qi0 + idx;
+        float val = which == 0 ? INFINITY : 0.f;    // lse2 = +inf makes P exactly 0 for rows past the end
+        if (qi < q_len) val = (which == 0 ? p.lse2 : p.delta)[(long long)h * p.Tq + q_begin + qi];
+        stat[it & 1][which][idx] = val;
+        mbar_arrive(smem_u32(&stat_bar));
+        ok = mbar_wait_bounded(smem_u32(&stat_bar), (uint32_t)(it & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      ok = mbar_wait_bounded(smem_u32(&st_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
+      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&st_empty[it & 1]));
+      const bool need_mask = (k0 + 127 >= kv_len) || (p.causal && k0 + 127 > off + qi0) ||
+                             (p.window > 0 && k0 <= off + qi0 + 63 - p.window);
+      const float* l2 = stat[it & 1][0];
+      const float* dl = stat[it & 1][1];
+      float pr[64], ds[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float pv = fast_exp2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -l2[c]));
+        if (need_mask) {
+          const int qpos = off + qi0 + c;
+          if (kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window)) pv = 0.f;
+        }
+        pr[c] = pv;
+        ds[c] = pv * (__uint_as_float(dv[c]) - dl[c]) * p.scale;
+      }
+      ok = mbar_wait_bounded(smem_u32(&pds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      uint8_t* pt_row = smem_al + pds_off + (it & 1) * 2 * Cfg::kPd + r * 128;
+      store_row64_sw128(pt_row, r, pr);
+      store_row64_sw128(pt_row + Cfg::kPd, r, ds);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&pds_full[it & 1]));
+    }
+    if (ok && n_iter > 0) {
+      ok = mbar_wait_bounded(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = kj < kv_len;
+      __nv_bfloat16* dv_row = p.dv + ((long long)(k_begin + kj) * p.Hkv + kvh) * D;
+      __nv_bfloat16* dk_row = p.dk + ((long long)(k_begin + kj) * p.Hkv + kvh) * D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          if (n_iter > 0) {
+            tmem_ld_32x32((which == 0 ? tm_dv : tm_dk) + lane_addr + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (row_ok) {
+            __nv_bfloat16* dst = (which == 0 ? dv_row : dk_row) + c * 32;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[u * 8 + 0]), __uint_as_float(v[u * 8 + 1]));
+              w.y = pack_bf16x2(__uint_as_float(v[u * 8 + 2]), __uint_as_float(v[u * 8 + 3]));
+              w.z = pack_bf16x2(__uint_as_float(v[u * 8 + 4]), __uint_as_float(v[u * 8 + 5]));
+              w.w = pack_bf16x2(__uint_as_float(v[u * 8 + 6]), __uint_as_float(v[u * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + u * 8) = w;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, FA_TMEM_COLS);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __grid_constant__ FlashBwdParams p) {
+  using Cfg = FlashBwdCfg<D>;
+  constexpr int DCH = D / 64;
+  constexpr int ST = Cfg::kKvStages;
+  constexpr int CH128 = 128 * 128, CH64 = 64 * 128;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t qdo_full, kv_full[ST], kv_empty[ST];
+  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], ds_full[2], ds_empty[2], acc_done;
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int q0 = q_tile * 128;
+  if (q0 >= q_len) return;
+  const int k_begin = p.cu_k[b], kv_len = p.cu_k[b + 1] - k_begin;
+  const int off = kv_len - q_len;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int hi = p.causal ? min(kv_len, off + q0 + 128) : kv_len;
+  const int lo = p.window > 0 ? max(0, off + q0 - p.window + 1) : 0;
+  const int t_begin = lo / 64;
+  const int n_iter = max((hi + 63) / 64 - t_begin, 0);
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t q_s = smem_base, do_s = q_s + Cfg::kBig;
+  const uint32_t kv_s = do_s + Cfg::kBig;                        // stage: K tile then V tile (64 rows each)
+  const uint32_t ds_off = 2 * Cfg::kBig + ST * 2 * Cfg::kSmall;
+  const uint32_t ds_s = smem_base + ds_off;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&qdo_full), 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(smem_u32(&kv_full[i]), 1); mbar_init(smem_u32(&kv_empty[i]), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&s_empty[i]), 4);
+      mbar_init(smem_u32(&ds_full[i]), 4);
+      mbar_init(smem_u32(&ds_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&acc_done), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), FA_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  const uint32_t tm_dq = tmem_base + 256;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (elect_one_sync()) {
+      bool ok = true;
+      mbar_expect_tx(smem_u32(&qdo_full), 2 * Cfg::kBig);
+#pragma unroll
+      for (int c = 0; c < DCH; ++c) {
+        tma_load_2d(q_s + c * CH128, &p.q128, smem_u32(&qdo_full), h * D + c * 64, q_begin + q0);
+        tma_load_2d(do_s + c * CH128, &p.do128, smem_u32(&qdo_full), h * D + c * 64, q_begin + q0);
+      }
+      int it = 0;
+      for (; it < n_iter; ++it) {
+        const int stage = it % ST;
+        ok = mbar_wait_backoff(smem_u32(&kv_empty[stage]), ((it / ST) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&kv_full[stage]);
+        const uint32_t dst = kv_s + stage * 2 * Cfg::kSmall;
+        const int y = k_begin + (t_begin + it) * 64;
+        mbar_expect_tx(fb, 2 * Cfg::kSmall);
+#pragma unroll
+        for (int c = 0; c < DCH; ++c) {
+          tma_load_2d(dst + c * CH64, &p.k64, fb, kvh * D + c * 64, y);
+          tma_load_2d(dst + Cfg::kSmall + c * CH64, &p.v64, fb, kvh * D + c * 64, y);
+        }
+      }
+      if (!ok) {
+        for (int j = max(0, it - ST); j < it; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&kv_full[j % ST]), (j / ST) & 1u))
+            if (globaltimer_ns() - t0 > 50000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one_sync()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, 0, 1);
+      bool ok = mbar_wait_backoff(smem_u32(&qdo_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      auto issue_s = [&](int it) -> bool {
+        const int stage = it % ST;
+        if (!mbar_wait_backoff(smem_u32(&kv_full[stage]), (it / ST) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL)) return false;
+        if (!mbar_wait_backoff(smem_u32(&s_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t k_s = kv_s + stage * 2 * Cfg::kSmall, v_s = k_s + Cfg::kSmall;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a = make_smem_desc_sw128(q_s + (k >> 2) * CH128 + (k & 3) * 32, 16, 1024);
+          const uint64_t bk = make_smem_desc_sw128(k_s + (k >> 2) * CH64 + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + (it & 1) * 64, a, bk, idesc_s, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a = make_smem_desc_sw128(do_s + (k >> 2) * CH128 + (k & 3) * 32, 16, 1024);
+          const uint64_t bv = make_smem_desc_sw128(v_s + (k >> 2) * CH64 + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + 128 + (it & 1) * 64, a, bv, idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_full[it & 1]));
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_s(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (it + 1 < n_iter) { ok = issue_s(it + 1); if (!ok) break; }
+        ok = mbar_wait_backoff(smem_u32(&ds_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const int stage = it % ST;
+        const uint32_t k_s = kv_s + stage * 2 * Cfg::kSmall;
+        const uint32_t dsb = ds_s + (it & 1) * Cfg::kPd;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // 64 keys = 4 k-steps
+          const uint64_t a = make_smem_desc_sw128(dsb + k * 32, 16, 1024);
+          const uint64_t bk = make_smem_desc_sw128(k_s + k * 2048, CH64, 1024);
+          umma_bf16(tm_dq, a, bk, idesc_acc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&kv_empty[stage]));
+        umma_commit(smem_u32(&ds_empty[it & 1]));
+      }
+      if (ok) umma_commit(smem_u32(&acc_done));
+    }
+  } else {
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;                  // query row of the tile
+    const int qi = q0 + r, qpos = off + qi;
+    const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
+    float l2 = INFINITY, dl = 0.f;                 // a row past the end gets P = 0 everywhere
+    if (qi < q_len) {
+      l2 = p.lse2[(long long)h * p.Tq + q_begin + qi];
+      dl = p.delta[(long long)h * p.Tq + q_begin + qi];
+    }
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int k0 = (t_begin + it) * 64;
+      ok = mbar_wait_bounded(smem_u32(&s_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[64], dv[64];
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
+      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_empty[it & 1]));
+      const bool need_mask = (k0 + 63 >= kv_len) || (p.causal && k0 + 63 > off + q0) ||
+                             (p.window > 0 && k0 <= off + q0 + 127 - p.window);
+      float ds[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float pv = fast_exp2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -l2));
+        if (need_mask) {
+          const int kj = k0 + c;
+          if (kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window)) pv = 0.f;
+        }
+        ds[c] = pv * (__uint_as_float(dv[c]) - dl) * p.scale;
+      }
+      ok = mbar_wait_bounded(smem_u32(&ds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      store_row64_sw128(smem_al + ds_off + (it & 1) * Cfg::kPd + r * 128, r, ds);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ds_full[it & 1]));
+    }
+    if (ok && n_iter > 0) {
+      ok = mbar_wait_bounded(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = qi < q_len;
+      __nv_bfloat16* dq_row = p.dq + ((long long)(q_begin + qi) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        if (n_iter > 0) {
+          tmem_ld_32x32(tm_dq + lane_addr + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(v[u * 8 + 0]), __uint_as_float(v[u * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(v[u * 8 + 2]), __uint_as_float(v[u * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(v[u * 8 + 4]), __uint_as_float(v[u * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(v[u * 8 + 6]), __uint_as_float(v[u * 8 + 7]));
+            *reinterpret_cast<uint4*>(dq_row + c * 32 + u * 8) = w;
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, FA_TMEM_COLS);
+  }
+}
+
+template <int D>
+static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, cudaStream_t stream) {
+  using Cfg = FlashBwdCfg<D>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemDkdv) !=
+        cudaSuccess)
+      return -10;
+    if (cudaFuncSetAttribute(flash_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemDq) !=
+        cudaSuccess)
+      return -10;
+    attr = true;
+  }
+  if (launch_kernel(flash_bwd_dkdv_kernel<D>, grid_kv, dim3(FA_THREADS), Cfg::kSmemDkdv, stream, p) != cudaSuccess) return -11;
+  if (launch_kernel(flash_bwd_dq_kernel<D>, grid_q, dim3(FA_THREADS), Cfg::kSmemDq, stream, p) != cudaSuccess) return -11;
+  return 0;
+}
+
 template <int D>
 static int launch_flash_fwd(const FlashFwdParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = FlashCfg<D>;
@@ -442,6 +1001,44 @@ int rb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* 
   p.status = status;
   dim3 grid((max_seqlen_q + FA_BM - 1) / FA_BM, Hq, B);
   int rc = D == 64 ? launch_flash_fwd<64>(p, grid, stream) : launch_flash_fwd<128>(p, grid, stream);
+  if (rc != 0) return rc;
+  return cudaGetLastError() == cudaSuccess ? 0 : -12;
+}
+
+// Backward of rb_flash_fwd in dense mode. out, dout, dq are contiguous [Tq,Hq,D]; dk, dv contiguous
+// [Tk,Hkv,D]; workspace holds 2*Hq*Tq floats (delta, lse in log2 units).
+int rb_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                 void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, float* workspace, int B, int Tq,
+                 int Tk, int Hq, int Hkv, int D, int ldq, int ldk, int ldv, int max_seqlen_q, int max_seqlen_k,
+                 int causal, int window, float scale, int* status, cudaStream_t stream) {
+  using namespace rb;
+  if (B <= 0 || Tq <= 0 || Tk <= 0) return 0;
+  if ((D != 64 && D != 128) || Hq % Hkv != 0) return -1;
+  FlashBwdParams p;
+  const unsigned long long qc = (unsigned long long)Hq * D, kc = (unsigned long long)Hkv * D;
+  if (tma_map_2d_bf16(&p.q64, q, Tq, qc, ldq, 64) != 0 || tma_map_2d_bf16(&p.q128, q, Tq, qc, ldq, 128) != 0) return -20;
+  if (tma_map_2d_bf16(&p.do64, dout, Tq, qc, qc, 64) != 0 || tma_map_2d_bf16(&p.do128, dout, Tq, qc, qc, 128) != 0) return -21;
+  if (tma_map_2d_bf16(&p.k64, k, Tk, kc, ldk, 64) != 0 || tma_map_2d_bf16(&p.k128, k, Tk, kc, ldk, 128) != 0) return -22;
+  if (tma_map_2d_bf16(&p.v64, v, Tk, kc, ldv, 64) != 0 || tma_map_2d_bf16(&p.v128, v, Tk, kc, ldv, 128) != 0) return -23;
+  float* delta = workspace;
+  float* lse2 = workspace + (long long)Hq * Tq;
+  p.lse2 = lse2;
+  p.delta = delta;
+  p.dq = (__nv_bfloat16*)dq;
+  p.dk = (__nv_bfloat16*)dk;
+  p.dv = (__nv_bfloat16*)dv;
+  p.cu_q = cu_q;
+  p.cu_k = cu_k;
+  p.Hq = Hq; p.Hkv = Hkv; p.Tq = Tq; p.Tk = Tk;
+  p.causal = causal; p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  const long long warps = (long long)Tq * Hq;
+  launch_kernel(flash_bwd_prep_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, stream,
+                (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, lse, delta, lse2, Tq, Hq, D);
+  dim3 grid_kv((max_seqlen_k + 127) / 128, Hkv, B), grid_q((max_seqlen_q + 127) / 128, Hq, B);
+  int rc = D == 64 ? launch_flash_bwd<64>(p, grid_kv, grid_q, stream) : launch_flash_bwd<128>(p, grid_kv, grid_q, stream);
   if (rc != 0) return rc;
   return cudaGetLastError() == cudaSuccess ? 0 : -12;
 }

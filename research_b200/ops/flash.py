@@ -27,9 +27,8 @@ def _lib() -> ctypes.CDLL:
     if not getattr(lib, "_rb_typed", False):
         lib.rb_flash_fwd.argtypes = [c_vp] * 9 + [c_int] * 14 + [c_float, c_vp, c_vp]
         lib.rb_flash_fwd.restype = c_int
-        if hasattr(lib, "rb_flash_bwd"):
-            lib.rb_flash_bwd.argtypes = [c_vp] * 12 + [c_int] * 13 + [c_float, c_vp, c_vp]
-            lib.rb_flash_bwd.restype = c_int
+        lib.rb_flash_bwd.argtypes = [c_vp] * 12 + [c_int] * 13 + [c_float, c_vp, c_vp]
+        lib.rb_flash_bwd.restype = c_int
         lib._rb_typed = True
     return lib
 
@@ -113,3 +112,55 @@ def flash_paged_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, max_n
                              stream_handle(q.device))
     check_rc(rc, "rb_flash_fwd(paged)")
     return out
+
+
+def flash_attn_varlen_backward(q, k, v, out, dout, lse, cu_q, cu_k, max_seqlen_q: int, max_seqlen_k: int,
+                               causal: bool = True, window: int = 0, scale=None):
+    """Gradients ``(dq, dk, dv)`` of ``flash_attn_varlen`` (bf16, contiguous ``[T, H, D]``)."""
+    Tq, Hq, D = q.shape
+    Tk, Hkv, _ = k.shape
+    scale = scale or 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        with torch.enable_grad():
+            qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+            o, _ = flash_attn_varlen_reference(qf, kf, vf, cu_q, cu_k, causal, window, scale)
+            dq, dk, dv = torch.autograd.grad(o, (qf, kf, vf), dout.float())
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+    dout = dout.contiguous()
+    assert out.is_contiguous() and lse.is_contiguous() and dout.dtype == torch.bfloat16
+    dq = torch.empty(Tq, Hq, D, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(Tk, Hkv, D, dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty(Tk, Hkv, D, dtype=torch.bfloat16, device=q.device)
+    ws = torch.empty(2 * Hq * Tq, dtype=torch.float32, device=q.device)
+    B = cu_q.shape[0] - 1
+    rc = _lib().rb_flash_bwd(ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(lse), ptr(dq), ptr(dk), ptr(dv), ptr(cu_q),
+                             ptr(cu_k), ptr(ws), B, Tq, Tk, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
+                             max_seqlen_q, max_seqlen_k, int(causal), int(window), scale,
+                             ptr(status_tensor(q.device)), stream_handle(q.device))
+    check_rc(rc, "rb_flash_bwd")
+    return dq, dk, dv
+
+
+class FlashAttnVarlen(torch.autograd.Function):
+    """Differentiable packed attention: tcgen05 kernels on CUDA, the fp32 reference on CPU."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, max_q, max_k, causal, window, scale):
+        out, lse = flash_attn_varlen(q, k, v, cu_q, cu_k, max_q, causal=causal, window=window, scale=scale,
+                                     return_lse=True)
+        ctx.save_for_backward(q, k, v, out, lse, cu_q, cu_k)
+        ctx.cfg = (max_q, max_k, causal, window, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        max_q, max_k, causal, window, scale = ctx.cfg
+        dq, dk, dv = flash_attn_varlen_backward(q, k, v, out, dout, lse, cu_q, cu_k, max_q, max_k, causal, window, scale)
+        return dq, dk, dv, None, None, None, None, None, None, None
+
+
+def flash_attention(q, k, v, cu_q, cu_k, max_seqlen_q: int, max_seqlen_k: int, causal: bool = True, window: int = 0,
+                    scale=None):
+    """Autograd entry point used by the training model."""
+    return FlashAttnVarlen.apply(q, k, v, cu_q, cu_k, max_seqlen_q, max_seqlen_k, causal, window, scale)

@@ -92,3 +92,48 @@ def test_flash_large_scores(cuda_device):
     diff = (got.float() - want.float()).abs()
     assert diff.max().item() < 0.03 and diff.mean().item() < 0.002, (diff.max().item(), diff.mean().item())
     assert torch.allclose(lse, lse_ref, atol=5e-3, rtol=1e-4)
+
+
+def _grad_check(got, want, what, tol_max=0.06, tol_rel=0.02):
+    diff = (got.float() - want.float()).abs()
+    rel = diff.sum().item() / max(want.float().abs().sum().item(), 1e-9)
+    assert diff.max().item() < tol_max and rel < tol_rel, (what, diff.max().item(), rel)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(64, 14, 2), (128, 8, 2), (128, 4, 4)])
+@pytest.mark.parametrize("causal,window", [(True, 0), (True, 100), (False, 0)])
+def test_flash_varlen_backward(cuda_device, D, Hq, Hkv, causal, window):
+    lens = [1, 63, 64, 129, 300, 517]
+    T = sum(lens)
+    qkv = _rand((T, (Hq + 2 * Hkv) * D), cuda_device, seed=11)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D :].view(T, Hkv, D)
+    dout = _rand((T, Hq, D), cuda_device, seed=12)
+    cu = _cu(lens, cuda_device)
+    out, lse = flash.flash_attn_varlen(q, k, v, cu, cu, max(lens), causal=causal, window=window, return_lse=True)
+    dq, dk, dv = flash.flash_attn_varlen_backward(q, k, v, out, dout, lse, cu, cu, max(lens), max(lens), causal, window)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o_ref, _ = flash.flash_attn_varlen_reference(qf, kf, vf, cu, cu, causal=causal, window=window)
+    rq, rk, rv = torch.autograd.grad(o_ref, (qf, kf, vf), dout.float())
+    _grad_check(dv, rv, "dv")
+    _grad_check(dk, rk, "dk")
+    _grad_check(dq, rq, "dq")
+
+
+def test_flash_autograd_cross_lengths(cuda_device):
+    D, Hq, Hkv = 128, 8, 2
+    q_lens, k_lens = [5, 64, 130], [5, 200, 400]
+    q = _rand((sum(q_lens), Hq, D), cuda_device, seed=13).requires_grad_(True)
+    k = _rand((sum(k_lens), Hkv, D), cuda_device, seed=14).requires_grad_(True)
+    v = _rand((sum(k_lens), Hkv, D), cuda_device, seed=15).requires_grad_(True)
+    cu_q, cu_k = _cu(q_lens, cuda_device), _cu(k_lens, cuda_device)
+    out = flash.flash_attention(q, k, v, cu_q, cu_k, max(q_lens), max(k_lens))
+    w = _rand(out.shape, cuda_device, seed=16)
+    (out.float() * w.float()).sum().backward()
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o_ref, _ = flash.flash_attn_varlen_reference(qf, kf, vf, cu_q, cu_k)
+    rq, rk, rv = torch.autograd.grad(o_ref, (qf, kf, vf), w.float())
+    _grad_check(v.grad, rv, "dv")
+    _grad_check(k.grad, rk, "dk")
+    _grad_check(q.grad, rq, "dq")
