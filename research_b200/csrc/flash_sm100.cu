@@ -457,8 +457,25 @@ __device__ __forceinline__ void store_row64_sw128(uint8_t* row_ptr, int r, const
   }
 }
 
+// 32 values (columns half*32 .. half*32+31) of one row into its 128-byte swizzled row
+__device__ __forceinline__ void store_row32_sw128(uint8_t* row_ptr, int r, int half, const float (&x)[32]) {
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    uint4 w;
+    w.x = pack_bf16x2(x[u * 8 + 0], x[u * 8 + 1]);
+    w.y = pack_bf16x2(x[u * 8 + 2], x[u * 8 + 3]);
+    w.z = pack_bf16x2(x[u * 8 + 4], x[u * 8 + 5]);
+    w.w = pack_bf16x2(x[u * 8 + 6], x[u * 8 + 7]);
+    *reinterpret_cast<uint4*>(row_ptr + (((half * 4 + u) ^ (r & 7)) << 4)) = w;
+  }
+}
+
+// The backward kernels run two softmax warpgroups (warps 2-5 and 6-9): both see the same 128 TMEM
+// lanes and split the 64 columns of a tile, which puts two such warps on every scheduler.
+constexpr int FA_BWD_THREADS = 320;
+
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __grid_constant__ FlashBwdParams p) {
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const __grid_constant__ FlashBwdParams p) {
   using Cfg = FlashBwdCfg<D>;
   constexpr int DCH = D / 64;
   constexpr int ST = Cfg::kQdoStages;
@@ -466,7 +483,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t kv_full, qdo_full[ST], qdo_empty[ST];
   __shared__ __align__(8) uint64_t st_full[2], st_empty[2], pds_full[2], pds_empty[2], acc_done, stat_bar;
-  __shared__ float stat[2][2][64];
+  __shared__ __align__(16) float stat[2][2][64];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -500,12 +517,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
     for (int i = 0; i < ST; ++i) { mbar_init(smem_u32(&qdo_full[i]), 1); mbar_init(smem_u32(&qdo_empty[i]), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&st_full[i]), 1);
-      mbar_init(smem_u32(&st_empty[i]), 4);
-      mbar_init(smem_u32(&pds_full[i]), 4);
+      mbar_init(smem_u32(&st_empty[i]), 8);
+      mbar_init(smem_u32(&pds_full[i]), 8);
       mbar_init(smem_u32(&pds_empty[i]), 1);
     }
     mbar_init(smem_u32(&acc_done), 1);
-    mbar_init(smem_u32(&stat_bar), 128);
+    mbar_init(smem_u32(&stat_bar), 256);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -608,16 +625,19 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
     const int r = qd * 32 + lane;                  // key row of the tile
     const int kj = k0 + r;
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
-    const int tid = threadIdx.x - 64;              // 0..127
+    const int half = (warp - 2) >> 2;              // which 32 of the 64 query columns
+    const int tid = threadIdx.x - 64;              // 0..255
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int h = kvh * G + it / n_qt, qi0 = (i_begin + it % n_qt) * 64;
       {   // row statistics of the 64 queries: thread t<64 -> lse2, t>=64 -> delta
-        const int idx = tid & 63, which = tid >> 6;
-        const int qi = qi0 + idx;
-        float val = which == 0 ? INFINITY : 0.f;    // lse2 = +inf makes P exactly 0 for rows past the end
-        if (qi < q_len) val = (which == 0 ? p.lse2 : p.delta)[(long long)h * p.Tq + q_begin + qi];
-        stat[it & 1][which][idx] = val;
+        if (tid < 128) {
+          const int idx = tid & 63, which = tid >> 6;
+          const int qi = qi0 + idx;
+          float val = which == 0 ? INFINITY : 0.f;    // lse2 = +inf makes P exactly 0 for rows past the end
+          if (qi < q_len) val = (which == 0 ? p.lse2 : p.delta)[(long long)h * p.Tq + q_begin + qi];
+          stat[it & 1][which][idx] = val;
+        }
         mbar_arrive(smem_u32(&stat_bar));
         ok = mbar_wait_bounded(smem_u32(&stat_bar), (uint32_t)(it & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
         ok = __all_sync(0xffffffffu, ok);
@@ -627,25 +647,23 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[64], dv[64];
-      tmem_ld_32x32(tmem_base + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld_32x32(tmem_base + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
-      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + half * 32 + lane_addr, sv);
+      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + half * 32 + lane_addr, dv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&st_empty[it & 1]));
       const bool need_mask = (k0 + 127 >= kv_len) || (p.causal && k0 + 127 > off + qi0) ||
                              (p.window > 0 && k0 <= off + qi0 + 63 - p.window);
-      const float* l2 = stat[it & 1][0];
-      const float* dl = stat[it & 1][1];
-      float pr[64], ds[64];
+      const float* l2 = stat[it & 1][0] + half * 32;
+      const float* dl = stat[it & 1][1] + half * 32;
+      float pr[32], ds[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         float pv = fast_exp2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -l2[c]));
         if (need_mask) {
-          const int qpos = off + qi0 + c;
+          const int qpos = off + qi0 + half * 32 + c;
           if (kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window)) pv = 0.f;
         }
         pr[c] = pv;
@@ -655,8 +673,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* pt_row = smem_al + pds_off + (it & 1) * 2 * Cfg::kPd + r * 128;
-      store_row64_sw128(pt_row, r, pr);
-      store_row64_sw128(pt_row + Cfg::kPd, r, ds);
+      store_row32_sw128(pt_row, r, half, pr);
+      store_row32_sw128(pt_row + Cfg::kPd, r, half, ds);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&pds_full[it & 1]));
@@ -673,7 +691,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {   // each warpgroup stores half the columns
           uint32_t v[32];
           if (n_iter > 0) {
             tmem_ld_32x32((which == 0 ? tm_dv : tm_dk) + lane_addr + c * 32, v);
@@ -707,7 +725,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dkdv_kernel(const __g
 }
 
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __grid_constant__ FlashBwdParams p) {
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dq_kernel(const __grid_constant__ FlashBwdParams p) {
   using Cfg = FlashBwdCfg<D>;
   constexpr int DCH = D / 64;
   constexpr int ST = Cfg::kKvStages;
@@ -745,8 +763,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __gri
     for (int i = 0; i < ST; ++i) { mbar_init(smem_u32(&kv_full[i]), 1); mbar_init(smem_u32(&kv_empty[i]), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_full[i]), 1);
-      mbar_init(smem_u32(&s_empty[i]), 4);
-      mbar_init(smem_u32(&ds_full[i]), 4);
+      mbar_init(smem_u32(&s_empty[i]), 8);
+      mbar_init(smem_u32(&ds_full[i]), 8);
       mbar_init(smem_u32(&ds_empty[i]), 1);
     }
     mbar_init(smem_u32(&acc_done), 1);
@@ -844,6 +862,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __gri
   } else {
     const int qd = warp & 3;
     const int r = qd * 32 + lane;                  // query row of the tile
+    const int half = (warp - 2) >> 2;              // which 32 of the 64 key columns
     const int qi = q0 + r, qpos = off + qi;
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
     float l2 = INFINITY, dl = 0.f;                 // a row past the end gets P = 0 everywhere
@@ -858,23 +877,21 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __gri
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[64], dv[64];
-      tmem_ld_32x32(tmem_base + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld_32x32(tmem_base + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
-      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + half * 32 + lane_addr, sv);
+      tmem_ld_32x32(tmem_base + 128 + (it & 1) * 64 + half * 32 + lane_addr, dv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_empty[it & 1]));
       const bool need_mask = (k0 + 63 >= kv_len) || (p.causal && k0 + 63 > off + q0) ||
                              (p.window > 0 && k0 <= off + q0 + 127 - p.window);
-      float ds[64];
+      float ds[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         float pv = fast_exp2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -l2));
         if (need_mask) {
-          const int kj = k0 + c;
+          const int kj = k0 + half * 32 + c;
           if (kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window)) pv = 0.f;
         }
         ds[c] = pv * (__uint_as_float(dv[c]) - dl) * p.scale;
@@ -882,7 +899,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __gri
       ok = mbar_wait_bounded(smem_u32(&ds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      store_row64_sw128(smem_al + ds_off + (it & 1) * Cfg::kPd + r * 128, r, ds);
+      store_row32_sw128(smem_al + ds_off + (it & 1) * Cfg::kPd + r * 128, r, half, ds);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ds_full[it & 1]));
@@ -896,7 +913,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_bwd_dq_kernel(const __gri
       const bool row_ok = qi < q_len;
       __nv_bfloat16* dq_row = p.dq + ((long long)(q_begin + qi) * p.Hq + h) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {   // each warpgroup stores half the columns
         uint32_t v[32];
         if (n_iter > 0) {
           tmem_ld_32x32(tm_dq + lane_addr + c * 32, v);
@@ -940,8 +957,8 @@ static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, 
       return -10;
     attr = true;
   }
-  if (launch_kernel(flash_bwd_dkdv_kernel<D>, grid_kv, dim3(FA_THREADS), Cfg::kSmemDkdv, stream, p) != cudaSuccess) return -11;
-  if (launch_kernel(flash_bwd_dq_kernel<D>, grid_q, dim3(FA_THREADS), Cfg::kSmemDq, stream, p) != cudaSuccess) return -11;
+  if (launch_kernel(flash_bwd_dkdv_kernel<D>, grid_kv, dim3(FA_BWD_THREADS), Cfg::kSmemDkdv, stream, p) != cudaSuccess) return -11;
+  if (launch_kernel(flash_bwd_dq_kernel<D>, grid_q, dim3(FA_BWD_THREADS), Cfg::kSmemDq, stream, p) != cudaSuccess) return -11;
   return 0;
 }
 

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -145,6 +146,10 @@ def paged_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, max_new: in
     if out is None:
         out = torch.empty_like(q)
     B = seq_lens.shape[0]
+    if D in (64, 128) and bs == 16 and not os.environ.get("RB_PREFILL_MMA_SYNC"):
+        from .flash import flash_paged_prefill   # tcgen05 kernel; the mma.sync kernel below is the fallback
+
+        return flash_paged_prefill(q, k_cache, v_cache, block_tables, cu_q, seq_lens, max_new, scale, window, out, lse)
     rc = _lib().rb_paged_prefill(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_tables), ptr(cu_q), ptr(seq_lens),
                                  ptr(out), ptr(lse), B, max_new, Hq, Hkv, D, block_tables.shape[1], nb, bs, scale,
                                  window, ptr(status_tensor(q.device)), stream_handle(q.device))

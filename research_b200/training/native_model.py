@@ -15,8 +15,8 @@ is never materialised.
 On CPU the same class evaluates the functional oracle with autograd, which is what the gloo
 multi-rank tests train.
 
-Attention core: ``scaled_dot_product_attention`` (library) for forward and backward of the
-training path; everything around it is native.
+Attention core: the tcgen05 flash attention kernels (forward and backward) for head sizes 64 and
+128; other head sizes (tiny test models) fall back to ``scaled_dot_product_attention``.
 """
 
 from __future__ import annotations
@@ -30,6 +30,7 @@ from .. import ops
 from ..models.config import ModelConfig
 from ..models.functional import causal_lm_forward
 from ..ops import train as T
+from ..ops.flash import flash_attention
 
 
 # ------------------------------------------------------------------------------ autograd glue
@@ -155,6 +156,7 @@ class NativeCausalLM:
         self.on_gpu = device.type == "cuda"
         self.ckpt = activation_checkpointing
         self._params: dict[str, torch.Tensor] = {}
+        self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.table = ops.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, device=device) \
             if self.on_gpu else None
 
@@ -192,6 +194,14 @@ class NativeCausalLM:
         self._leaves = {}
 
     # ---------------------------------------------------------------- kernel path
+    def _cu_seqlens(self, B: int, Tn: int) -> torch.Tensor:
+        key = (B, Tn)
+        cu = self._cu_cache.get(key)
+        if cu is None:
+            cu = (torch.arange(B + 1, device=self.device) * Tn).to(torch.int32)
+            self._cu_cache[key] = cu
+        return cu
+
     def _layer(self, x, i, positions, B, Tn):
         cfg = self.cfg
         pre = f"model.layers.{i}."
@@ -211,10 +221,17 @@ class NativeCausalLM:
             k = _RMSNorm.apply(k, self.p(a + "k_norm.weight"), self.g(a + "k_norm.weight"), cfg.rms_norm_eps)
         q = _RoPE.apply(q.contiguous(), positions, self.table)
         k = _RoPE.apply(k.contiguous(), positions, self.table)
-        o = F.scaled_dot_product_attention(
-            q.view(B, Tn, H, D).transpose(1, 2), k.view(B, Tn, Hkv, D).transpose(1, 2),
-            v.view(B, Tn, Hkv, D).transpose(1, 2), is_causal=True, scale=1.0 / math.sqrt(D), enable_gqa=True)
-        o = o.transpose(1, 2).reshape(B * Tn, H * D)
+        if D in (64, 128):
+            # tcgen05 flash attention, forward and backward (csrc/flash_sm100.cu); rows are the B padded sequences
+            cu = self._cu_seqlens(B, Tn)
+            o = flash_attention(q, k, v.contiguous(), cu, cu, Tn, Tn, causal=True, scale=1.0 / math.sqrt(D))
+            o = o.reshape(B * Tn, H * D)
+        else:
+            # head sizes the flash kernel does not cover (tiny test models): library attention
+            o = F.scaled_dot_product_attention(
+                q.view(B, Tn, H, D).transpose(1, 2), k.view(B, Tn, Hkv, D).transpose(1, 2),
+                v.view(B, Tn, Hkv, D).transpose(1, 2), is_causal=True, scale=1.0 / math.sqrt(D), enable_gqa=True)
+            o = o.transpose(1, 2).reshape(B * Tn, H * D)
         x = x + lin(o, a + "o_proj.weight")
         h = _RMSNorm.apply(x, self.p(pre + "post_attention_layernorm.weight"),
                            self.g(pre + "post_attention_layernorm.weight"), cfg.rms_norm_eps)

@@ -92,6 +92,23 @@ def bench_flash_forward(B, n, Hq, Hkv, D, peak_tflops, iters=5, paged=False):
             "ms": round(t["median_ms"], 4), "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3)}
 
 
+def bench_flash_backward(B, n, Hq, Hkv, D, peak_tflops, iters=5):
+    """tcgen05 flash attention backward (prep + dK/dV + dQ kernels), causal. FLOPs counted as 2.5x forward."""
+    from ..ops import flash
+
+    q = torch.randn(B * n, Hq, D, device="cuda").bfloat16()
+    k = torch.randn(B * n, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(B * n, Hkv, D, device="cuda").bfloat16()
+    do = torch.randn(B * n, Hq, D, device="cuda").bfloat16()
+    cu = (torch.arange(B + 1, device="cuda") * n).to(torch.int32)
+    out, lse = flash.flash_attn_varlen(q, k, v, cu, cu, n, return_lse=True)
+    t = time_cuda(lambda: flash.flash_attn_varlen_backward(q, k, v, out, do, lse, cu, cu, n, n), iters=iters)
+    flops = 2.5 * 4.0 * B * Hq * D * n * n / 2
+    ach = flops / (t["median_ms"] * 1e-3) / 1e12
+    return {"kernel": "flash_bwd", "B": B, "n": n, "Hq": Hq, "Hkv": Hkv, "D": D, "ms": round(t["median_ms"], 4),
+            "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3)}
+
+
 def bench_rmsnorm(rows, d, peak_gbs):
     x = torch.randn(rows, d, device="cuda").bfloat16()
     w = torch.randn(d, device="cuda").bfloat16()
@@ -135,6 +152,8 @@ def main() -> None:
     rows.append(bench_flash_forward(8, 2048, 32, 8, 128, args.peak_tflops, paged=True))
     rows.append(bench_flash_forward(4, 8192, 32, 8, 128, args.peak_tflops))
     rows.append(bench_flash_forward(16, 1024, 14, 2, 64, args.peak_tflops))
+    rows.append(bench_flash_backward(8, 2048, 32, 8, 128, args.peak_tflops))
+    rows.append(bench_flash_backward(4, 8192, 32, 8, 128, args.peak_tflops))
     rows.append(bench_rmsnorm(16384, 4096, args.peak_gbs))
     rows.append(bench_sampling(256, 151936, args.peak_gbs))
     for r in rows:

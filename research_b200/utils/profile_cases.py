@@ -47,6 +47,13 @@ def case_flash_fwd() -> None:
     print(bench_flash_forward(8, 2048, 32, 8, 128, 1688.4, iters=3))
 
 
+def case_flash_bwd() -> None:
+    """tcgen05 flash attention backward: 8 x 2048 tokens, 32q/8kv heads, D=128, causal."""
+    from .microbench import bench_flash_backward
+
+    print(bench_flash_backward(8, 2048, 32, 8, 128, 1688.4, iters=3))
+
+
 def case_decode_step() -> None:
     """Two eager decode steps of the 0.5B-shaped model at batch 256 (for a per-launch time list)."""
     from ..inference import EngineConfig, InferenceEngine, SamplingParams
