@@ -3,8 +3,8 @@
 // Forward: one CTA owns 128 query rows of one head. S = Q K^T and O += P V are tcgen05.mma
 // instructions issued by one thread; S (two buffers) and O live in tensor memory, Q/K/V tiles are
 // brought into 128-byte-swizzled shared memory by TMA, P goes back to shared memory as the A operand
-// of the second product. Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5
-// softmax (one query row per thread, read from TMEM with tcgen05.ld). The running maximum is only
+// of the second product. Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-9
+// softmax (two threads per query row, each reading half of it from TMEM with tcgen05.ld). The running maximum is only
 // refreshed when it grew by more than 2^8, so the O accumulator is rescaled rarely.
 //
 // Inputs are packed variable-length batches (`cu_seqlens`), grouped-query heads, causal and
@@ -26,8 +26,8 @@ namespace rb {
 
 constexpr int FA_BM = 128;        // query rows per CTA
 constexpr int FA_BN = 128;        // keys per iteration
-constexpr int FA_THREADS = 192;   // 6 warps
-constexpr int FA_KV_SLOTS = 4;    // ring of K/V tiles: K0 V0 K1 V1 ...
+constexpr int FA_THREADS = 320;   // 10 warps: TMA, MMA, two softmax warpgroups
+constexpr int FA_KV_SLOTS = 3;    // ring of K/V tiles in consumption order: K0 K1 V0 K2 V1 K3 V2 ...
 constexpr int FA_TMEM_COLS = 512;
 constexpr float FA_RESCALE_THRESHOLD = 8.f;   // log2 units
 
@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
   constexpr int CHUNK_BYTES = FA_BN * 128;       // 128 rows x 128 B
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, kv_full[FA_KV_SLOTS], kv_empty[FA_KV_SLOTS];
-  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_done;
+  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_done, xch_bar[4];
+  __shared__ float xch[2][2][FA_BM];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -128,10 +129,11 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&s_full[i]), 1);
-      mbar_init(smem_u32(&s_empty[i]), 4);
-      mbar_init(smem_u32(&p_full[i]), 4);
+      mbar_init(smem_u32(&s_empty[i]), 8);
+      mbar_init(smem_u32(&p_full[i]), 8);
       mbar_init(smem_u32(&p_empty[i]), 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&xch_bar[i]), 64);
     mbar_init(smem_u32(&o_done), 1);
     fence_mbar_init();
   }
@@ -155,38 +157,43 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       for (int c = 0; c < DCH; ++c)
         tma_load_2d(q_s + c * CHUNK_BYTES, &p.q_map, smem_u32(&q_full), h * D + c * 64, q_begin + q0);
       uint32_t it = 0;
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      // tiles are loaded in the order the MMA warp consumes them: K0, then (K_{j+1}, V_j) for every j
+      auto load_tile = [&](int j, int which) -> bool {   // which 0: K tile, 1: V tile
         const int k0 = (t_begin + j) * FA_BN;
-#pragma unroll 1
-        for (int which = 0; which < 2 && ok; ++which, ++it) {   // 0: K tile, 1: V tile
-          const int slot = it % FA_KV_SLOTS;
-          ok = mbar_wait_backoff(smem_u32(&kv_empty[slot]), ((it / FA_KV_SLOTS) & 1u) ^ 1u, abortp, p.status,
-                                 ST_TIMEOUT_SMEM_EMPTY);
-          if (!ok) break;
-          const uint32_t fb = smem_u32(&kv_full[slot]);
-          const uint32_t dst = kv_s + slot * Cfg::kTileBytes;
-          const CUtensorMap* map = which == 0 ? &p.k_map : &p.v_map;
-          mbar_expect_tx(fb, Cfg::kTileBytes);
-          if (!p.paged) {
+        const int slot = it % FA_KV_SLOTS;
+        if (!mbar_wait_backoff(smem_u32(&kv_empty[slot]), ((it / FA_KV_SLOTS) & 1u) ^ 1u, abortp, p.status,
+                               ST_TIMEOUT_SMEM_EMPTY))
+          return false;
+        const uint32_t fb = smem_u32(&kv_full[slot]);
+        const uint32_t dst = kv_s + slot * Cfg::kTileBytes;
+        const CUtensorMap* map = which == 0 ? &p.k_map : &p.v_map;
+        mbar_expect_tx(fb, Cfg::kTileBytes);
+        if (!p.paged) {
 #pragma unroll
-            for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, fb, kvh * D + c * 64, k_begin + k0);
-          } else {
-            const int* bt = p.block_tables + (long long)b * p.max_blocks;
-            const int n_blk = (kv_len + 15) >> 4;
+          for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, fb, kvh * D + c * 64, k_begin + k0);
+        } else {
+          const int* bt = p.block_tables + (long long)b * p.max_blocks;
+          const int n_blk = (kv_len + 15) >> 4;
 #pragma unroll 1
-            for (int i = 0; i < FA_BN / 16; ++i) {
-              const int bi = (k0 >> 4) + i;
-              int blk = p.num_blocks;                         // out of range: the copy fills zeros
-              if (bi < n_blk) {
-                blk = bt[bi];
-                if (blk < 0 || blk >= p.num_blocks) { set_status(p.status, ST_BAD_INDEX); blk = p.num_blocks; }
-              }
-              const int y = (blk * p.Hkv + kvh) * 16;
-#pragma unroll
-              for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES + i * 2048, map, fb, c * 64, y);
+          for (int i = 0; i < FA_BN / 16; ++i) {
+            const int bi = (k0 >> 4) + i;
+            int blk = p.num_blocks;                         // out of range: the copy fills zeros
+            if (bi < n_blk) {
+              blk = bt[bi];
+              if (blk < 0 || blk >= p.num_blocks) { set_status(p.status, ST_BAD_INDEX); blk = p.num_blocks; }
             }
+            const int y = (blk * p.Hkv + kvh) * 16;
+#pragma unroll
+            for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES + i * 2048, map, fb, c * 64, y);
           }
         }
+        ++it;
+        return true;
+      };
+      if (n_tiles > 0) ok = load_tile(0, 0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) { ok = load_tile(j + 1, 0); if (!ok) break; }
+        ok = load_tile(j, 1);
       }
       if (!ok) {   // drain: no bulk copy may land after the CTA has gone
         const uint32_t first = it > (uint32_t)FA_KV_SLOTS ? it - FA_KV_SLOTS : 0;
@@ -203,8 +210,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, FA_BN, 0, 0);   // Q, K both K-major
       constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, D, 0, 1);       // P K-major, V MN-major
       bool ok = mbar_wait_backoff(smem_u32(&q_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      uint32_t it = 0;   // tiles consumed so far, in the producer's order
       auto issue_s = [&](int j) -> bool {
-        const uint32_t it = 2 * j;
         const int slot = it % FA_KV_SLOTS;
         if (!mbar_wait_backoff(smem_u32(&kv_full[slot]), (it / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL))
           return false;
@@ -220,12 +227,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
         }
         umma_commit(smem_u32(&kv_empty[slot]));
         umma_commit(smem_u32(&s_full[j & 1]));
+        ++it;
         return true;
       };
       if (ok && n_tiles > 0) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) { ok = issue_s(j + 1); if (!ok) break; }
-        const uint32_t it = 2 * j + 1;
         const int slot = it % FA_KV_SLOTS;
         ok = mbar_wait_backoff(smem_u32(&p_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
         if (!ok) break;
@@ -243,28 +250,44 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
         umma_commit(smem_u32(&kv_empty[slot]));
         umma_commit(smem_u32(&p_empty[j & 1]));
         umma_commit(smem_u32(&o_done));
+        ++it;
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
+    // Two warpgroups (warps 2-5 and 6-9) share the 128 rows: `half` owns 64 of the 128 score columns
+    // of a row, half of the O columns and one 64-column chunk of P. The two threads of a row swap
+    // their partial row maximum (and, at the end, their partial row sum) through shared memory.
+    constexpr int HC = FA_BN / 2;                // score columns per thread
     const int qd = warp & 3;                     // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;
     const int r = qd * 32 + lane;                // query row inside the tile
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
     const int qpos = off + q0 + r;               // key position of this query
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    uint32_t xph = 0;                            // phase of the pair barrier
+    auto swap_with_partner = [&](float mine, float& other) -> bool {
+      xch[xph & 1][half][r] = mine;
+      mbar_arrive(smem_u32(&xch_bar[qd]));
+      bool good = mbar_wait_bounded(smem_u32(&xch_bar[qd]), xph & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      other = xch[xph & 1][half ^ 1][r];
+      ++xph;
+      return __all_sync(0xffffffffu, good);
+    };
     for (int j = 0; j < n_tiles; ++j) {
       const int k0 = (t_begin + j) * FA_BN;
-      const uint32_t s_addr = tmem_base + (j & 1) * FA_BN + lane_addr;
+      const uint32_t s_addr = tmem_base + (j & 1) * FA_BN + half * HC + lane_addr;
       ok = mbar_wait_bounded(smem_u32(&s_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = (k0 + FA_BN > kv_len) || (p.causal && k0 + FA_BN - 1 > off + q0) ||
                              (p.window > 0 && k0 <= off + q0 + FA_BM - 1 - p.window);
-      // the whole score row (128 columns) goes to registers with one wait; the S buffer is free again
-      uint32_t v[FA_BN];
+      // this thread's 64 score columns go to registers with one wait; then the S buffer is free again
+      uint32_t v[HC];
 #pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c)
+      for (int c = 0; c < HC / 32; ++c)
         tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
       tmem_ld_wait();
       tc_fence_before();
@@ -272,23 +295,27 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       if (lane == 0) mbar_arrive(smem_u32(&s_empty[j & 1]));
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < FA_BN; ++i) {
-          const int kj = k0 + i;
+        for (int i = 0; i < HC; ++i) {
+          const int kj = k0 + half * HC + i;
           const bool dead = kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window);
           if (dead) v[i] = 0xff800000u;   // -inf
         }
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < FA_BN; i += 4) {
+      for (int i = 0; i < HC; i += 4) {
         mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
         mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
         mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
         mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
       }
-      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+      const float mine = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      float other;
+      ok = swap_with_partner(mine, other);
+      if (!ok) break;
+      const float m_new = fmaxf(m_used, fmaxf(mine, other) * p.scale_log2);
       const bool need = m_new > m_used + FA_RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
-      if (__any_sync(0xffffffffu, need)) {
+      if (__any_sync(0xffffffffu, need)) {   // same rows, same inputs: both warps of a quarter agree
         if (j > 0) {
           // O holds the products of tiles 0..j-1 once the previous P V has completed
           ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -297,7 +324,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
           tc_fence_after();
           const float alpha = need ? fast_exp2((m_used == -INFINITY ? m_new : m_used) - m_new) : 1.f;
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
             uint32_t o[32];
             tmem_ld_32x32(tmem_o + lane_addr + c * 32, o);
             tmem_ld_wait();
@@ -314,7 +341,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       // P = exp2(S * scale - m): a masked score is -inf and gives exactly 0
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < FA_BN; i += 4) {
+      for (int i = 0; i < HC; i += 4) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           const float x = fast_exp2(fmaf(__uint_as_float(v[i + t]), p.scale_log2, -mref));
@@ -327,19 +354,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       ok = mbar_wait_bounded(smem_u32(&p_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      uint8_t* prow = p_ptr + (j & 1) * Cfg::kPBytes + r * 128;
+      uint8_t* prow = p_ptr + (j & 1) * Cfg::kPBytes + half * CHUNK_BYTES + r * 128;
 #pragma unroll
-      for (int unit = 0; unit < FA_BN / 8; ++unit) {
+      for (int unit = 0; unit < HC / 8; ++unit) {
         uint4 w;
         w.x = pack_bf16x2(__uint_as_float(v[unit * 8 + 0]), __uint_as_float(v[unit * 8 + 1]));
         w.y = pack_bf16x2(__uint_as_float(v[unit * 8 + 2]), __uint_as_float(v[unit * 8 + 3]));
         w.z = pack_bf16x2(__uint_as_float(v[unit * 8 + 4]), __uint_as_float(v[unit * 8 + 5]));
         w.w = pack_bf16x2(__uint_as_float(v[unit * 8 + 6]), __uint_as_float(v[unit * 8 + 7]));
-        *reinterpret_cast<uint4*>(prow + (unit >> 3) * CHUNK_BYTES + (((unit & 7) ^ (r & 7)) << 4)) = w;
+        *reinterpret_cast<uint4*>(prow + ((unit ^ (r & 7)) << 4)) = w;
       }
       fence_proxy_async_smem();   // P was written with ordinary stores and is read by the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&p_full[j & 1]));
+    }
+    if (ok && n_tiles > 0) {
+      float l_other;
+      ok = swap_with_partner(l, l_other);   // both halves used the same m_used, so the sums simply add
+      l += l_other;
     }
     if (ok && n_tiles > 0) {
       ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((n_tiles - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -351,7 +383,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.out + ((long long)(q_begin + q0 + r) * p.Hq + h) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {   // each warpgroup stores half the columns
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
@@ -372,7 +404,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
           }
         }
       }
-      if (row_ok && p.lse != nullptr)
+      if (row_ok && half == 0 && p.lse != nullptr)
         p.lse[(long long)h * p.Tq + q_begin + q0 + r] =
             l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       tc_fence_before();
