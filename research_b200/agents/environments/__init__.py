@@ -1,5 +1,10 @@
 from .basic import BasicEnvironment, BinarySearchEnvironment, CalculatorEnvironment, ComposedEnvironment, safe_eval
+from .chess_puzzle import Board, ChessPuzzleEnvironment
 from .coding import LocalFilesystemEnvironment, MessageParsingREPLEnvironment, REPLEnvironment
+from .git_worktree import GitWorktreeEnvironment
+from .interactive import AskUserQuestionEnvironment, BrowsingEnvironment, ScreenSpotEnvironment
 
 __all__ = ["BasicEnvironment", "BinarySearchEnvironment", "CalculatorEnvironment", "ComposedEnvironment", "safe_eval",
-           "LocalFilesystemEnvironment", "MessageParsingREPLEnvironment", "REPLEnvironment"]
+           "LocalFilesystemEnvironment", "MessageParsingREPLEnvironment", "REPLEnvironment", "Board",
+           "ChessPuzzleEnvironment", "GitWorktreeEnvironment", "AskUserQuestionEnvironment", "BrowsingEnvironment",
+           "ScreenSpotEnvironment"]
