@@ -10,6 +10,9 @@ from .base import (ContextTooLongError, NonRetryableError, ProviderError, RateLi
                    classify_http_status, retry)
 from .chat import ScriptedLLM, messages_to_openai, rollout_openai_compatible
 from .models import MODELS, ModelInfo, estimate_cost, get_model
+from .streaming import (aggregate_anthropic_stream, aggregate_google_stream, aggregate_openai_responses_stream,
+                        aggregate_openai_stream, messages_to_anthropic, messages_to_google, messages_to_openai_responses,
+                        rollout_anthropic, rollout_google, rollout_openai_responses, rollout_openai_streaming, sse_events)
 from .token_level import (build_input_ids_from_trajectory, generate_sglang, generate_vllm, rollout_native_token_level,
                           rollout_sglang_token_level, rollout_vllm_token_level)
 from .tool_parsers import parse_hermes_tool_calls, parse_json_tool_calls, parse_tool_calls, render_tools_system_prompt
@@ -17,7 +20,9 @@ from .tool_parsers import parse_hermes_tool_calls, parse_json_tool_calls, parse_
 RolloutFn = Callable[[Actor, RunConfig], Awaitable[Actor]]
 
 _TEXT: dict[str, RolloutFn] = {"openai": rollout_openai_compatible, "sglang": rollout_openai_compatible,
-                               "vllm": rollout_openai_compatible, "native": rollout_native_token_level}
+                               "vllm": rollout_openai_compatible, "native": rollout_native_token_level,
+                               "openai-stream": rollout_openai_streaming, "openai-responses": rollout_openai_responses,
+                               "anthropic": rollout_anthropic, "google": rollout_google}
 _TOKEN: dict[str, RolloutFn] = {"native": rollout_native_token_level, "sglang": rollout_sglang_token_level,
                                 "vllm": rollout_vllm_token_level}
 
@@ -40,4 +45,7 @@ __all__ = ["ContextTooLongError", "NonRetryableError", "ProviderError", "RateLim
            "ModelInfo", "estimate_cost", "get_model", "build_input_ids_from_trajectory", "generate_sglang",
            "generate_vllm", "rollout_native_token_level", "rollout_sglang_token_level", "rollout_vllm_token_level",
            "parse_hermes_tool_calls", "parse_json_tool_calls", "parse_tool_calls", "render_tools_system_prompt",
-           "register_provider", "get_provider"]
+           "register_provider", "get_provider", "aggregate_anthropic_stream", "aggregate_google_stream",
+           "aggregate_openai_responses_stream", "aggregate_openai_stream", "messages_to_anthropic", "messages_to_google",
+           "messages_to_openai_responses", "rollout_anthropic", "rollout_google", "rollout_openai_responses",
+           "rollout_openai_streaming", "sse_events"]

@@ -1,0 +1,133 @@
+"""Stream aggregators and message transforms against recorded event sequences (no network)."""
+
+import asyncio
+
+from research_b200.agents.dtypes import (Message, TextContent, ThinkingContent, ToolCall, ToolCallContent)
+from research_b200.agents.providers import (aggregate_anthropic_stream, aggregate_google_stream,
+                                            aggregate_openai_responses_stream, aggregate_openai_stream, get_provider,
+                                            messages_to_anthropic, messages_to_google, messages_to_openai_responses, sse_events)
+from research_b200.agents.transform_messages import transform_messages
+
+
+async def _aiter(items):
+    for x in items:
+        yield x
+
+
+def _run(coro):
+    return asyncio.run(coro)
+
+
+def test_sse_parser():
+    async def go():
+        lines = ["event: a", 'data: {"x": 1}', "", ": comment", 'data: {"y":', "data: 2}", "", "data: [DONE]", "", 'data: {"z": 3}', ""]
+        return [e async for e in sse_events(_aiter(lines))]
+
+    assert _run(go()) == [{"x": 1}, {"y": 2}]
+
+
+def test_anthropic_stream():
+    events = [
+        {"type": "message_start", "message": {"id": "msg_1", "usage": {"input_tokens": 12, "cache_read_input_tokens": 4}}},
+        {"type": "content_block_start", "index": 0, "content_block": {"type": "thinking", "thinking": ""}},
+        {"type": "content_block_delta", "index": 0, "delta": {"type": "thinking_delta", "thinking": "hmm"}},
+        {"type": "content_block_delta", "index": 0, "delta": {"type": "signature_delta", "signature": "sig"}},
+        {"type": "content_block_stop", "index": 0},
+        {"type": "content_block_start", "index": 1, "content_block": {"type": "text", "text": ""}},
+        {"type": "content_block_delta", "index": 1, "delta": {"type": "text_delta", "text": "Let me "}},
+        {"type": "content_block_delta", "index": 1, "delta": {"type": "text_delta", "text": "compute."}},
+        {"type": "content_block_stop", "index": 1},
+        {"type": "content_block_start", "index": 2, "content_block": {"type": "tool_use", "id": "tu_1", "name": "calc"}},
+        {"type": "content_block_delta", "index": 2, "delta": {"type": "input_json_delta", "partial_json": '{"expr": "1'}},
+        {"type": "content_block_delta", "index": 2, "delta": {"type": "input_json_delta", "partial_json": '+1"}'}},
+        {"type": "content_block_stop", "index": 2},
+        {"type": "message_delta", "delta": {"stop_reason": "tool_use"}, "usage": {"output_tokens": 30}},
+        {"type": "message_stop"},
+    ]
+    seen = []
+
+    async def on_chunk(ev):
+        seen.append(ev.type)
+
+    comp = _run(aggregate_anthropic_stream(_aiter(events), "claude-x", on_chunk))
+    msg = comp.choices[0].message
+    assert comp.id == "msg_1" and comp.choices[0].finish_reason == "tool_calls"
+    assert msg.text() == "Let me compute." and msg.get_tool_calls() == [ToolCall("tu_1", "calc", {"expr": "1+1"})]
+    assert isinstance(msg.content[0], ThinkingContent) and msg.content[0].signature == "sig"
+    assert comp.usage.input_tokens == 12 and comp.usage.output_tokens == 30 and comp.usage.cache_read_tokens == 4
+    assert seen == ["thinking_delta", "text_delta", "text_delta", "tool_call_start", "tool_call_end"]
+
+
+def test_openai_chat_stream():
+    events = [
+        {"id": "c1", "choices": [{"delta": {"role": "assistant", "content": "Hi"}}]},
+        {"id": "c1", "choices": [{"delta": {"tool_calls": [{"index": 0, "id": "call_a", "function": {"name": "f", "arguments": '{"a"'}}]}}]},
+        {"id": "c1", "choices": [{"delta": {"tool_calls": [{"index": 0, "function": {"arguments": ": 1}"}}]}}]},
+        {"id": "c1", "choices": [{"delta": {}, "finish_reason": "tool_calls"}]},
+        {"id": "c1", "choices": [], "usage": {"prompt_tokens": 5, "completion_tokens": 7}},
+    ]
+    comp = _run(aggregate_openai_stream(_aiter(events), "gpt-x"))
+    assert comp.choices[0].message.text() == "Hi" and comp.choices[0].finish_reason == "tool_calls"
+    assert comp.choices[0].message.get_tool_calls() == [ToolCall("call_a", "f", {"a": 1})]
+    assert comp.usage.total_tokens == 12
+
+
+def test_openai_responses_stream():
+    events = [
+        {"type": "response.created", "response": {"id": "resp_1"}},
+        {"type": "response.reasoning_summary_text.delta", "delta": "thinking"},
+        {"type": "response.output_text.delta", "delta": "Answer"},
+        {"type": "response.output_item.added", "item": {"type": "function_call", "id": "fc_1", "call_id": "call_1", "name": "g", "arguments": ""}},
+        {"type": "response.function_call_arguments.delta", "item_id": "fc_1", "delta": '{"q": "x"}'},
+        {"type": "response.output_item.done", "item": {"type": "function_call", "id": "fc_1", "call_id": "call_1", "name": "g", "arguments": '{"q": "x"}'}},
+        {"type": "response.completed", "response": {"usage": {"input_tokens": 3, "output_tokens": 9, "output_tokens_details": {"reasoning_tokens": 4}}}},
+    ]
+    comp = _run(aggregate_openai_responses_stream(_aiter(events), "o-x"))
+    m = comp.choices[0].message
+    assert comp.id == "resp_1" and m.text() == "Answer" and m.get_tool_calls() == [ToolCall("call_1", "g", {"q": "x"})]
+    assert comp.usage.reasoning_tokens == 4 and comp.choices[0].finish_reason == "tool_calls"
+
+
+def test_google_stream():
+    events = [
+        {"candidates": [{"content": {"parts": [{"text": "plan", "thought": True}]}}]},
+        {"candidates": [{"content": {"parts": [{"text": "Hello "}, {"text": "world"}]}}]},
+        {"candidates": [{"content": {"parts": [{"functionCall": {"name": "lookup", "args": {"k": 2}}}]}, "finishReason": "STOP"}],
+         "usageMetadata": {"promptTokenCount": 8, "candidatesTokenCount": 6, "thoughtsTokenCount": 2}},
+    ]
+    comp = _run(aggregate_google_stream(_aiter(events), "gemini-x"))
+    m = comp.choices[0].message
+    assert m.text() == "Hello world" and m.get_tool_calls()[0].name == "lookup" and m.get_tool_calls()[0].args == {"k": 2}
+    assert comp.usage.input_tokens == 8 and comp.usage.reasoning_tokens == 2
+
+
+def test_wire_formats():
+    msgs = (Message("system", "be brief"), Message("user", "2+2?"),
+            Message("assistant", [TextContent("calling"), ToolCallContent("t1", "calc", {"e": "2+2"})]),
+            Message("tool", "4", tool_call_id="t1", name="calc"), Message("user", "thanks"))
+    system, a = messages_to_anthropic(msgs)
+    assert system == "be brief" and [m["role"] for m in a] == ["user", "assistant", "user"]
+    assert a[2]["content"][0]["type"] == "tool_result" and a[2]["content"][1] == {"type": "text", "text": "thanks"}
+    system, g = messages_to_google(msgs)
+    assert [m["role"] for m in g] == ["user", "model", "user"] and g[2]["parts"][0]["functionResponse"]["name"] == "calc"
+    items = messages_to_openai_responses(msgs)
+    assert [i["type"] for i in items] == ["message", "message", "message", "function_call", "function_call_output", "message"]
+    assert items[0]["role"] == "developer"
+    assert get_provider("anthropic").__name__ == "rollout_anthropic"
+
+
+def test_transform_messages():
+    msgs = [Message("user", "q"),
+            Message("assistant", [ThinkingContent("secret", "sig"), TextContent("a"), ToolCallContent("t1", "f", {})]),
+            Message("tool", "orphan", tool_call_id="zzz"),
+            Message("user", "next"), Message("user", "again")]
+    out = transform_messages(msgs, source=("anthropic", "m1"), target=("openai", "m2"), require_alternation=True)
+    roles = [m.role for m in out]
+    assert roles == ["user", "assistant", "tool", "user"]
+    assert not any(isinstance(b, ThinkingContent) for b in out[1].content)
+    assert out[2].tool_call_id == "t1" and "interrupted" in out[2].text()
+    assert out[3].text() == "next\n\nagain"
+    same = transform_messages(msgs, source=("anthropic", "m1"), target=("anthropic", "m1"))
+    assert isinstance(same[1].content[0], ThinkingContent)
+    inl = transform_messages(msgs, source=("a", "1"), target=("b", "2"), inline_thinking="<think>{thinking}</think>")
+    assert inl[1].content[0].text == "<think>secret</think>"
