@@ -39,6 +39,7 @@ LIBRARIES: dict[str, tuple[str, list[str]]] = {
     "rb_ops": ("nvcc", ["ops_sm100.cu"]),
     "rb_attn": ("nvcc", ["attn_sm100.cu"]),
     "rb_flash": ("nvcc", ["flash_sm100.cu"]),
+    "rb_quant": ("nvcc", ["quant_sm100.cu"]),
     "rb_train": ("nvcc", ["train_sm100.cu"]),
     "rb_comm": ("nvcc", ["comm_sm100.cu"]),
     "rb_moe": ("nvcc", ["moe_sm100.cu"]),

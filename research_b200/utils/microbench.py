@@ -109,6 +109,30 @@ def bench_flash_backward(B, n, Hq, Hkv, D, peak_tflops, iters=5):
             "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3)}
 
 
+def bench_nvfp4_gemv(M, K, L, peak_gbs, launches=50):
+    """NVFP4 block-scaled GEMV; timed as one CUDA graph of `launches` back-to-back launches so that the
+    figure is device time per launch, not host launch overhead."""
+    from ..ops import nvfp4
+
+    a = torch.randint(0, 256, (L, M, K // 2), dtype=torch.uint8, device="cuda")
+    b = torch.randint(0, 256, (L, K // 2), dtype=torch.uint8, device="cuda")
+    sfa = torch.randint(40, 72, (L, M, K // 16), dtype=torch.uint8, device="cuda")
+    sfb = torch.randint(40, 72, (L, K // 16), dtype=torch.uint8, device="cuda")
+    out = torch.empty(L, M, dtype=torch.float16, device="cuda")
+    nvfp4.nvfp4_gemv(a, b, sfa, sfb, out=out)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(launches):
+            nvfp4.nvfp4_gemv(a, b, sfa, sfb, out=out)
+    t = time_cuda(g.replay, iters=10)
+    us = t["median_ms"] * 1e3 / launches
+    byts = L * (M * K / 2 + M * K / 16 + K / 2 + K / 16 + 2 * M)
+    ach = byts / (us * 1e-6) / 1e9
+    return {"kernel": "nvfp4_gemv", "M": M, "K": K, "L": L, "us_per_launch": round(us, 2), "gbs": round(ach, 1),
+            "frac_of_measured_peak": round(ach / peak_gbs, 3)}
+
+
 def bench_rmsnorm(rows, d, peak_gbs):
     x = torch.randn(rows, d, device="cuda").bfloat16()
     w = torch.randn(d, device="cuda").bfloat16()
@@ -152,6 +176,8 @@ def main() -> None:
     rows.append(bench_flash_forward(8, 2048, 32, 8, 128, args.peak_tflops, paged=True))
     rows.append(bench_flash_forward(4, 8192, 32, 8, 128, args.peak_tflops))
     rows.append(bench_flash_forward(16, 1024, 14, 2, 64, args.peak_tflops))
+    for M, K, L in ((256, 512, 2), (128, 256, 1), (7168, 16384, 1), (4096, 7168, 8), (7168, 2048, 4)):
+        rows.append(bench_nvfp4_gemv(M, K, L, args.peak_gbs))
     rows.append(bench_flash_backward(8, 2048, 32, 8, 128, args.peak_tflops))
     rows.append(bench_flash_backward(4, 8192, 32, 8, 128, args.peak_tflops))
     rows.append(bench_rmsnorm(16384, 4096, args.peak_gbs))

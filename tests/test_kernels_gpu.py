@@ -243,3 +243,17 @@ def test_paged_prefill(cuda_device, D, Hq, Hkv, window):
     diff = (got.float() - want.float()).abs()
     # rows that attend to one or two keys return |v| ~ 2-4, where one bf16 ulp is 0.0156
     assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+
+
+# ------------------------------------------------------------------------------------ NVFP4 GEMV
+@pytest.mark.parametrize("L,M,K", [(2, 256, 512), (1, 128, 256), (3, 77, 2048), (1, 1024, 7168)])
+def test_nvfp4_gemv(cuda_device, L, M, K):
+    from research_b200.ops import nvfp4
+
+    g = torch.Generator().manual_seed(5)
+    a, sfa = nvfp4.quantize_nvfp4(torch.randn(L, M, K, generator=g))
+    b, sfb = nvfp4.quantize_nvfp4(torch.randn(L, K, generator=g))
+    want = nvfp4.nvfp4_gemv_reference(a, b, sfa, sfb).float()
+    got = nvfp4.nvfp4_gemv(a.to(cuda_device), b.to(cuda_device), sfa.to(cuda_device), sfb.to(cuda_device)).float().cpu()
+    # fp16 output: one ulp of the result magnitude
+    assert torch.allclose(got, want, rtol=2e-3, atol=2e-3 * want.abs().max().item()), (got - want).abs().max().item()
