@@ -93,6 +93,8 @@ struct GemmParams {
   int swiglu;
   int split_k, kb_per_split;
   int stages;
+  int scaled_epilogue, mirror;
+  float alpha, beta;
   float* splitk_ws;
   int* splitk_tickets;
 };
@@ -452,6 +454,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           const int col = n_base + c0;
+          if (p.scaled_epilogue) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+          }
           if (p.epi_mode == RB_EPI_STORE) {
             if (p.bias != nullptr) {
 #pragma unroll
@@ -472,11 +478,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
               for (int j = 0; j < 32; j += 8) {
                 if (j < ncols) {
                   uint4 b = *reinterpret_cast<const uint4*>(rp + j);
+                  const float rs = p.scaled_epilogue ? p.beta : 1.f;
                   float2 f;
-                  f = unpack_bf16x2(b.x); v[j] += f.x; v[j + 1] += f.y;
-                  f = unpack_bf16x2(b.y); v[j + 2] += f.x; v[j + 3] += f.y;
-                  f = unpack_bf16x2(b.z); v[j + 4] += f.x; v[j + 5] += f.y;
-                  f = unpack_bf16x2(b.w); v[j + 6] += f.x; v[j + 7] += f.y;
+                  f = unpack_bf16x2(b.x); v[j] = fmaf(rs, f.x, v[j]); v[j + 1] = fmaf(rs, f.y, v[j + 1]);
+                  f = unpack_bf16x2(b.y); v[j + 2] = fmaf(rs, f.x, v[j + 2]); v[j + 3] = fmaf(rs, f.y, v[j + 3]);
+                  f = unpack_bf16x2(b.z); v[j + 4] = fmaf(rs, f.x, v[j + 4]); v[j + 5] = fmaf(rs, f.y, v[j + 5]);
+                  f = unpack_bf16x2(b.w); v[j + 6] = fmaf(rs, f.x, v[j + 6]); v[j + 7] = fmaf(rs, f.y, v[j + 7]);
                 }
               }
             }
@@ -496,6 +503,17 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
               }
             } else {
               epi_store_row_chunk(p, v, row, col, ncols);
+              if (p.mirror) {
+                // transposed copy of the part below the diagonal: for a fixed j the lanes of a warp
+                // (consecutive rows) write consecutive addresses
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < ncols && col + j < row) {
+                    if (p.out_f32) reinterpret_cast<float*>(p.C)[(long long)(col + j) * p.ldc + row] = v[j];
+                    else reinterpret_cast<__nv_bfloat16*>(p.C)[(long long)(col + j) * p.ldc + row] = __float2bfloat16_rn(v[j]);
+                  }
+                }
+              }
             }
           } else {
             // push the bf16 partial into the owner's staging slab [src_rank][row_in][N]
@@ -774,6 +792,10 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.num_tiles_ptr = a->num_tiles_ptr;
   p.row_dst = a->row_dst;
   p.swiglu = a->swiglu;
+  p.scaled_epilogue = a->scaled_epilogue;
+  p.alpha = a->alpha;
+  p.beta = a->beta;
+  p.mirror = a->mirror;
   p.split_k = a->split_k > 1 ? a->split_k : 1;
   p.splitk_ws = a->splitk_ws;
   p.splitk_tickets = a->splitk_tickets;

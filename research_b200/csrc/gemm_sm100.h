@@ -65,6 +65,13 @@ typedef struct RbGemmArgs {
   int split_k;
   float* splitk_ws;
   int* splitk_tickets;           // [tiles], zero before first use
+  // Scaled epilogue C = alpha * (A B^T) + bias + beta * residual (used when scaled_epilogue != 0).
+  int scaled_epilogue;
+  float alpha, beta;
+  // Symmetric output (C = A A^T and friends): after the normal store every element below the
+  // diagonal is also written to its transposed position, so a tile table that lists only the tiles
+  // touching the lower triangle produces the full matrix.
+  int mirror;
 } RbGemmArgs;
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);

@@ -65,6 +65,10 @@ class RbGemmArgs(ctypes.Structure):
         ("split_k", ctypes.c_int),
         ("splitk_ws", ctypes.c_void_p),
         ("splitk_tickets", ctypes.c_void_p),
+        ("scaled_epilogue", ctypes.c_int),
+        ("alpha", ctypes.c_float),
+        ("beta", ctypes.c_float),
+        ("mirror", ctypes.c_int),
     ]
 
 
@@ -103,8 +107,10 @@ def gemm(
     max_ctas: int = 0,
     swiglu: bool = False,
     split_k: int = 0,
+    alpha: float = 1.0,
+    beta: float = 1.0,
 ) -> torch.Tensor:
-    """``C[M,N] = op(A) @ op(B)^T (+bias) (+residual)``.
+    """``C[M,N] = alpha * op(A) @ op(B)^T (+bias) (+ beta * residual)``.
 
     K-major operands are ``[rows, K]`` row-major (a torch ``Linear`` weight is a K-major B);
     MN-major operands are ``[K, rows]`` row-major. On CUDA this launches the tcgen05 kernel;
@@ -113,7 +119,15 @@ def gemm(
     if swiglu:
         assert bn >= 64 and not (a_mn_major or b_mn_major), "fused SwiGLU needs an explicit bn and K-major operands"
     if not a.is_cuda:
-        res = gemm_reference(a, b, bias, residual, a_mn_major, b_mn_major, torch.float32 if out_f32 else None)
+        if alpha != 1.0 or beta != 1.0:
+            res = alpha * gemm_reference(a, b, None, None, a_mn_major, b_mn_major, torch.float32)
+            if bias is not None:
+                res = res + bias.float()
+            if residual is not None:
+                res = res + beta * residual.float()
+            res = res.to(torch.float32 if out_f32 else a.dtype)
+        else:
+            res = gemm_reference(a, b, bias, residual, a_mn_major, b_mn_major, torch.float32 if out_f32 else None)
         if swiglu:
             res = swiglu_interleaved_reference(res, bn)
         if out is not None:
@@ -152,6 +166,10 @@ def gemm(
     args.epi_mode = EPI_STORE
     args.rank, args.world = 0, 1
     args.swiglu = int(swiglu)
+    if alpha != 1.0 or beta != 1.0:
+        assert not swiglu, "the scaled epilogue is not combined with the fused SwiGLU"
+        args.scaled_epilogue, args.alpha, args.beta = 1, alpha, beta
+        split_k = 1
     if split_k == 0:
         split_k, auto_bn = _auto_split_k(M, N, K, a_mn_major or b_mn_major or swiglu or out_f32)
         if split_k > 1 and bn == 0:
@@ -196,6 +214,67 @@ def _splitk_scratch(device: torch.device, floats: int, tiles: int) -> tuple[torc
     return _SPLITK[idx]
 
 
+_SYM_TABLES: dict[tuple, tuple[torch.Tensor, torch.Tensor, int]] = {}
+
+
+def _symmetric_tiles(M: int, bn: int, device: torch.device) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """Tile table (first A row, valid rows, first B row, first output column) of the tiles that touch
+    the lower triangle of an M x M output."""
+    key = (M, bn, device.index)
+    if key not in _SYM_TABLES:
+        rows = [(mt * 128, min(128, M - mt * 128), nt * bn, nt * bn)
+                for mt in range(-(-M // 128)) for nt in range(-(-M // bn)) if nt * bn < min((mt + 1) * 128, M)]
+        # longest rows of tiles first: the persistent CTAs then finish together
+        table = torch.tensor(rows, dtype=torch.int32, device=device)
+        count = torch.tensor([len(rows)], dtype=torch.int32, device=device)
+        _SYM_TABLES[key] = (table, count, len(rows))
+    return _SYM_TABLES[key]
+
+
+def gemm_symmetric(a: torch.Tensor, alpha: float = 1.0, beta: float = 0.0, residual: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None, bn: int = 128) -> torch.Tensor:
+    """``C = alpha * A @ A^T + beta * residual`` for ``A [M, K]``; ``residual`` must be symmetric.
+
+    Only the output tiles that touch the lower triangle are computed (a device tile table drives the
+    grouped mode of the GEMM kernel); the epilogue writes every element below the diagonal to its
+    transposed position as well. Covers the ``A A^T`` and ``b A + c A A`` products of the Muon /
+    Polar Express orthogonalisation (dev/speedrun/single-file.py:172-383)."""
+    M, K = a.shape
+    if not a.is_cuda:
+        res = alpha * (a.float() @ a.float().T)
+        if residual is not None:
+            res = res + beta * residual.float()
+        res = res.to(a.dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    assert a.dtype == torch.bfloat16 and a.stride(1) == 1 and M % 8 == 0 and K % 8 == 0
+    if out is None:
+        out = torch.empty(M, M, dtype=torch.bfloat16, device=a.device)
+    table, count, n_tiles = _symmetric_tiles(M, bn, a.device)
+    args = RbGemmArgs()
+    args.A[0] = args.B[0] = a.data_ptr()
+    args.C = out.data_ptr()
+    args.residual = residual.data_ptr() if residual is not None else None
+    args.lda = args.ldb = a.stride(0)
+    args.ldc = out.stride(0)
+    args.ldr = residual.stride(0) if residual is not None else 0
+    args.M, args.N, args.K = M, M, K
+    args.a_parts = args.b_parts = 1
+    args.bn = bn
+    args.epi_mode = EPI_STORE
+    args.rank, args.world = 0, 1
+    args.tile_table, args.num_tiles_ptr = table.data_ptr(), count.data_ptr()
+    args.group_n, args.max_tiles = M, n_tiles
+    args.scaled_epilogue, args.alpha, args.beta = 1, alpha, beta
+    args.mirror = 1
+    args.status = status_tensor(a.device).data_ptr()
+    rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
+    check_rc(rc, "rb_gemm_bf16_ex(symmetric)")
+    return out
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, bn: int) -> torch.Tensor:
     """Pack ``gate`` and ``up`` ``[F, K]`` for the fused SwiGLU epilogue: blocks of ``bn/2`` gate rows
     followed by the matching ``bn/2`` up rows."""
@@ -222,5 +301,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=
     return y.reshape(*lead, weight.shape[0])
 
 
-__all__ = ["gemm", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
+__all__ = ["gemm", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
 _ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

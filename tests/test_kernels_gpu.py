@@ -257,3 +257,31 @@ def test_nvfp4_gemv(cuda_device, L, M, K):
     got = nvfp4.nvfp4_gemv(a.to(cuda_device), b.to(cuda_device), sfa.to(cuda_device), sfb.to(cuda_device)).float().cpu()
     # fp16 output: one ulp of the result magnitude
     assert torch.allclose(got, want, rtol=2e-3, atol=2e-3 * want.abs().max().item()), (got - want).abs().max().item()
+
+
+# ------------------------------------------------------------------------------------ symmetric GEMM / Muon
+@pytest.mark.parametrize("M,K", [(256, 512), (136, 72), (1024, 256)])
+def test_gemm_symmetric_and_scaled_epilogue(cuda_device, M, K):
+    a = _rand((M, K), cuda_device, seed=41) * 0.2
+    got = ops.gemm_symmetric(a).float()
+    want = a.float() @ a.float().T
+    _assert_close(got, want, atol=0.06, rtol=0.02, what="A A^T")
+    assert torch.equal(got, got.T), "mirrored store must give an exactly symmetric matrix"
+    sym = (want * 0.1).to(torch.bfloat16)
+    got2 = ops.gemm_symmetric(sym, alpha=0.5, beta=-1.5, residual=sym).float()
+    want2 = 0.5 * sym.float() @ sym.float().T - 1.5 * sym.float()
+    _assert_close(got2, want2, atol=0.08, rtol=0.03, what="b A + c A A")
+    x = _rand((M, 192), cuda_device, seed=42)
+    got3 = ops.gemm(sym, x, residual=x, b_mn_major=True, alpha=1.0, beta=2.5).float()
+    _assert_close(got3, sym.float() @ x.float() + 2.5 * x.float(), atol=0.08, rtol=0.03, what="a X + B X")
+
+
+def test_polar_express_gpu(cuda_device):
+    from research_b200.training.muon import polar_express, polar_express_reference
+
+    G = torch.randn(256, 640, generator=torch.Generator().manual_seed(3)).to(cuda_device)
+    X = polar_express(G).float()
+    ref = polar_express_reference(G)
+    assert (X - ref).abs().max().item() < 0.05
+    s = torch.linalg.svdvals(X)
+    assert s.min().item() > 0.6 and s.max().item() < 1.25

@@ -215,3 +215,28 @@ def test_grpo_train_end_to_end(tmp_path):
     run = next(tmp_path.iterdir())
     assert {"config.json", "metrics.jsonl", "rollouts.jsonl", "checkpoints", "rollout_state.json"} <= {p.name for p in run.iterdir()}
     assert len((run / "rollouts.jsonl").read_text().splitlines()) == 16
+
+
+def test_polar_express_and_muon_cpu():
+    from research_b200.training.muon import Muon, polar_express, polar_express_reference
+
+    g = torch.Generator().manual_seed(0)
+    G = torch.randn(24, 40, generator=g)
+    X = polar_express(G).float()
+    ref = polar_express_reference(G)
+    assert (X - ref).abs().max() < 0.08                                   # bf16 iteration vs fp32
+    s = torch.linalg.svdvals(ref)
+    assert s.min() > 0.6 and s.max() < 1.25                               # singular values pushed towards 1
+    tall = polar_express(torch.randn(40, 24, generator=g))
+    assert tall.shape == (40, 24)
+    w = torch.nn.Parameter(torch.randn(16, 32, generator=g))
+    opt = Muon([w], lr=0.1, momentum=0.9, weight_decay=0.01)
+    target = torch.randn(16, 32, generator=g)
+    losses = []
+    for _ in range(30):
+        opt.zero_grad()
+        loss = ((w - target) ** 2).mean()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.5 * losses[0]
