@@ -95,6 +95,7 @@ struct GemmParams {
   int stages;
   int scaled_epilogue, mirror;
   float alpha, beta;
+  int fp8;
   float* splitk_ws;
   int* splitk_tickets;
 };
@@ -277,6 +278,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------ MMA issuer --------------------------------------------
     if (elect_one_sync()) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t idesc8 = make_idesc_f8(BM, BN, (p.fp8 >> 1) & 1, (p.fp8 >> 2) & 1);
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
@@ -305,7 +307,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                                         : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc_sw128(sb + k * 2048, RB_MN_LBO, RB_MN_SBO)
                                         : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_bf16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (p.fp8) umma_f8(tmem_d, adesc, bdesc, idesc8, (kb > kb0 || k > 0) ? 1u : 0u);
+            else umma_bf16(tmem_d, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
         }
@@ -796,6 +799,8 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.alpha = a->alpha;
   p.beta = a->beta;
   p.mirror = a->mirror;
+  p.fp8 = a->fp8;
+  if (p.fp8 && (a->a_mn_major || a->b_mn_major)) return -1;   // 8-bit operands are K-major only
   p.split_k = a->split_k > 1 ? a->split_k : 1;
   p.splitk_ws = a->splitk_ws;
   p.splitk_tickets = a->splitk_tickets;

@@ -72,6 +72,11 @@ typedef struct RbGemmArgs {
   // diagonal is also written to its transposed position, so a tile table that lists only the tiles
   // touching the lower triangle produces the full matrix.
   int mirror;
+  // 8-bit floating point operands (both K-major): bit 0 enables, bit 1 = A is e5m2, bit 2 = B is
+  // e5m2 (otherwise e4m3). The caller describes the operands as if they were bf16 matrices with half
+  // as many columns (K, lda, ldb in units of two bytes): the tiles are moved as bytes and only the
+  // tensor-core instruction differs. Per-tensor scales go into alpha.
+  int fp8;
 } RbGemmArgs;
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);

@@ -69,6 +69,7 @@ class RbGemmArgs(ctypes.Structure):
         ("alpha", ctypes.c_float),
         ("beta", ctypes.c_float),
         ("mirror", ctypes.c_int),
+        ("fp8", ctypes.c_int),
     ]
 
 
@@ -214,6 +215,54 @@ def _splitk_scratch(device: torch.device, floats: int, tiles: int) -> tuple[torc
     return _SPLITK[idx]
 
 
+def gemm_fp8(a: torch.Tensor, b: torch.Tensor, scale: float = 1.0, bias=None, out: torch.Tensor | None = None,
+             out_f32: bool = False, bn: int = 0) -> torch.Tensor:
+    """``C = scale * A @ B^T`` for ``float8_e4m3fn`` / ``float8_e5m2`` operands ``A [M,K]``, ``B [N,K]``
+    (fp32 accumulation on the tcgen05 ``kind::f8f6f4`` path, bf16 or fp32 output). ``scale`` is the
+    product of the per-tensor scales, as with ``torch._scaled_mm`` (dev/speedrun/single-file.py:35-96)."""
+    f8 = (torch.float8_e4m3fn, torch.float8_e5m2)
+    assert a.dtype in f8 and b.dtype in f8 and a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
+    M, K = a.shape
+    N = b.shape[0]
+    if not a.is_cuda:
+        res = scale * (a.float() @ b.float().T)
+        if bias is not None:
+            res = res + bias.float()
+        res = res.to(torch.float32 if out_f32 else torch.bfloat16)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    assert K % 16 == 0 and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) % 16 == 0 and b.stride(0) % 16 == 0
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    args = RbGemmArgs()
+    args.A[0], args.B[0], args.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.bias = bias.data_ptr() if bias is not None else None
+    # described as bf16 matrices with half as many columns: same bytes, see RbGemmArgs.fp8
+    args.lda, args.ldb, args.ldc = a.stride(0) // 2, b.stride(0) // 2, out.stride(0)
+    args.M, args.N, args.K = M, N, K // 2
+    args.a_parts = args.b_parts = 1
+    args.out_f32 = int(out_f32)
+    args.bn = bn
+    args.epi_mode = EPI_STORE
+    args.rank, args.world = 0, 1
+    args.fp8 = 1 | (2 if a.dtype == torch.float8_e5m2 else 0) | (4 if b.dtype == torch.float8_e5m2 else 0)
+    if scale != 1.0:
+        args.scaled_epilogue, args.alpha, args.beta = 1, scale, 1.0
+    args.status = status_tensor(a.device).data_ptr()
+    rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
+    check_rc(rc, "rb_gemm_bf16_ex(fp8)")
+    return out
+
+
+def quantize_fp8(x: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn) -> tuple[torch.Tensor, float]:
+    """Per-tensor scaled cast: returns ``(x / s as fp8, s)`` with ``s = amax / fp8_max``."""
+    fmax = torch.finfo(dtype).max
+    s = max(x.abs().max().item() / fmax, 1e-12)
+    return (x.float() / s).clamp(-fmax, fmax).to(dtype), s
+
+
 _SYM_TABLES: dict[tuple, tuple[torch.Tensor, torch.Tensor, int]] = {}
 
 
@@ -301,5 +350,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=
     return y.reshape(*lead, weight.shape[0])
 
 
-__all__ = ["gemm", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
+__all__ = ["gemm", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
 _ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

@@ -285,3 +285,19 @@ def test_polar_express_gpu(cuda_device):
     assert (X - ref).abs().max().item() < 0.05
     s = torch.linalg.svdvals(X)
     assert s.min().item() > 0.6 and s.max().item() < 1.25
+
+
+# ------------------------------------------------------------------------------------ FP8 GEMM
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (130, 264, 80), (4096, 1024, 768)])
+@pytest.mark.parametrize("a_dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_gemm_fp8(cuda_device, M, N, K, a_dtype):
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(M, K, generator=g).to(cuda_device)
+    w = torch.randn(N, K, generator=g).to(cuda_device)
+    xq, sx = ops.quantize_fp8(x, a_dtype)
+    wq, sw = ops.quantize_fp8(w)
+    got = ops.gemm_fp8(xq, wq, scale=sx * sw, out_f32=True)
+    want = (xq.float() @ wq.float().T) * (sx * sw)          # exact product of the quantised operands
+    _assert_close(got, want, atol=2e-3 * want.abs().max().item(), rtol=1e-3, what="fp8 gemm")
+    got16 = ops.gemm_fp8(xq, wq, scale=sx * sw)
+    assert got16.dtype == torch.bfloat16 and (got16.float() - want).abs().max().item() < 0.02 * want.abs().max().item()
