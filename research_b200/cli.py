@@ -1,0 +1,237 @@
+"""Command line: ``python -m research_b200.cli <command>`` (rollouts/cli.py:117-1457, run_eval.py).
+
+    serve     start the native engine behind the HTTP front end
+    chat      talk to a model (any provider) with an agent preset; sessions are stored and resumable
+    sessions  list / show / export / slice / import stored sessions
+    eval      run a JSONL dataset through an agent and score it with a dotted-path score function
+    bench     the flagship benchmark (same as the repository's bench.py)
+    build     compile the native libraries
+"""
+
+from __future__ import annotations
+
+import argparse
+import asyncio
+import importlib
+import json
+import os
+import sys
+from pathlib import Path
+
+
+def _store(args):
+    from .agents.store import FileSessionStore
+
+    return FileSessionStore(args.store or os.path.join(os.path.expanduser("~"), ".research_b200", "sessions"))
+
+
+def _endpoint(args):
+    from .agents.dtypes import Endpoint
+
+    return Endpoint(provider=args.provider, model=args.model or "", api_base=args.api_base or "",
+                    api_key=os.environ.get(args.api_key_env or "", "") if args.api_key_env else "",
+                    max_tokens=args.max_tokens, temperature=args.temperature)
+
+
+def _add_endpoint_args(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--provider", default="openai", help="native | sglang | vllm | openai | openai-stream | openai-responses | anthropic | google")
+    p.add_argument("--model", default="")
+    p.add_argument("--api-base", default="")
+    p.add_argument("--api-key-env", default="", help="name of the environment variable that holds the API key")
+    p.add_argument("--max-tokens", type=int, default=1024)
+    p.add_argument("--temperature", type=float, default=1.0)
+
+
+def load_object(path: str):
+    """``package.module:attr`` or ``path/to/file.py:attr``."""
+    mod_name, _, attr = path.partition(":")
+    assert attr, "expected module:attribute"
+    if mod_name.endswith(".py"):
+        spec = importlib.util.spec_from_file_location(Path(mod_name).stem, mod_name)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    else:
+        mod = importlib.import_module(mod_name)
+    return getattr(mod, attr)
+
+
+# ------------------------------------------------------------------------------------------ commands
+def cmd_build(args) -> int:
+    from . import _native
+
+    for name, path in _native.build_all(force=args.force).items():
+        print(f"{name}: {path}")
+    return 0
+
+
+def cmd_serve(args) -> int:
+    import torch
+
+    from .inference import EngineConfig, InferenceEngine
+    from .inference.server import serve
+    from .models import get_preset, init_random_weights
+    from .models.weights import load_safetensors_dir
+
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    if os.path.isdir(args.model):
+        from .models.config import ModelConfig
+
+        cfg = ModelConfig.from_hf_config(json.loads((Path(args.model) / "config.json").read_text()))
+        weights = load_safetensors_dir(args.model)
+        tokenizer = None
+        try:
+            from transformers import AutoTokenizer
+
+            tokenizer = AutoTokenizer.from_pretrained(args.model)
+        except Exception:  # noqa: BLE001 - token-id requests work without a tokenizer
+            pass
+    else:
+        cfg = get_preset(args.model)
+        weights = init_random_weights(cfg, seed=0, dtype=torch.bfloat16 if device == "cuda" else torch.float32, device=device)
+        tokenizer = None
+    ecfg = EngineConfig(cache_type=args.cache, max_batch_size=args.max_batch_size, max_model_len=args.max_model_len,
+                        gpu_memory_utilization=args.gpu_memory_utilization, tensor_parallel_size=args.tp)
+    engine = InferenceEngine(ecfg, cfg, weights, device=device)
+    print(f"serving {args.model} on http://{args.host}:{args.port} ({device})", flush=True)
+    serve(engine, args.host, args.port, args.model, tokenizer)
+    return 0
+
+
+async def _chat(args) -> int:
+    from .agents.agents import resume_session, run_agent
+    from .agents.dtypes import Actor, AgentState, Message, RunConfig, TextDelta, Trajectory
+    from .agents.presets import get_preset
+
+    preset, store, ep = get_preset(args.preset), _store(args), _endpoint(args)
+
+    async def on_chunk(ev):
+        if isinstance(ev, TextDelta):
+            print(ev.delta, end="", flush=True)
+
+    async def confirm(call, state, rc):
+        return args.yes or input(f"\nrun {call.name}({json.dumps(call.args)[:200]})? [y/N] ").strip().lower() == "y"
+
+    rc = RunConfig(on_chunk=on_chunk, confirm_tool=confirm, session_store=store)
+    if args.session:
+        state = await resume_session(args.session, store, ep, type(preset.environment(args.cwd)), preset.max_turns)
+    else:
+        env = preset.environment(args.cwd)
+        if hasattr(env, "on_session_start"):
+            await env.on_session_start(f"cli-{os.getpid()}")
+        state = AgentState(Actor(Trajectory((Message("system", preset.system_prompt),)), ep), env, max_turns=preset.max_turns)
+    prompt = args.prompt
+    while True:
+        if prompt is None:
+            try:
+                prompt = input("\n> ").strip()
+            except EOFError:
+                break
+        if not prompt or prompt in ("/exit", "/quit"):
+            break
+        traj = state.actor.trajectory.append(Message("user", prompt))
+        state = AgentState(Actor(traj, ep), state.environment, max_turns=state.turn_idx + preset.max_turns,
+                           turn_idx=state.turn_idx, session_id=state.session_id)
+        state = (await run_agent(state, rc))[-1]
+        print()
+        if args.prompt is not None:
+            break
+        prompt = None
+    if state.session_id:
+        print(f"session: {state.session_id}", file=sys.stderr)
+    return 0
+
+
+def cmd_chat(args) -> int:
+    return asyncio.run(_chat(args))
+
+
+async def _sessions(args) -> int:
+    from .agents.export import export_session
+    from .agents.import_cc import import_transcript
+    from .agents.slice import slice_session
+
+    store = _store(args)
+    if args.action == "list":
+        for s in sorted(await store.list(), key=lambda s: s.updated_at, reverse=True)[: args.limit]:
+            print(f"{s.session_id}  {s.status:<10} {s.num_messages:>4} msgs  {s.endpoint.get('provider', '?')}/{s.endpoint.get('model', '?')}")
+    elif args.action in ("show", "export"):
+        text = await export_session(store, args.id, args.format, args.output)
+        if not args.output:
+            print(text)
+    elif args.action == "slice":
+        print(await slice_session(store, args.id, args.spec))
+    elif args.action == "import":
+        print(await import_transcript(store, Path(args.id)))
+    return 0
+
+
+def cmd_sessions(args) -> int:
+    return asyncio.run(_sessions(args))
+
+
+async def _eval(args) -> int:
+    from .agents.dtypes import EvalConfig
+    from .agents.evaluation import evaluate
+    from .agents.presets import get_preset
+
+    rows = [json.loads(line) for line in Path(args.dataset).read_text().splitlines() if line.strip()]
+    preset = get_preset(args.preset)
+    cfg = EvalConfig(endpoint=_endpoint(args), score_fn=load_object(args.score_fn),
+                     environment_factory=(lambda row: preset.environment(args.cwd)) if preset.name != "chat" else None,
+                     max_turns=preset.max_turns, max_samples=args.max_samples, max_concurrent=args.max_concurrent,
+                     output_dir=args.output_dir, eval_name=args.name)
+    report = await evaluate(rows, cfg)
+    print(json.dumps(report.summary, indent=2))
+    return 0
+
+
+def cmd_eval(args) -> int:
+    return asyncio.run(_eval(args))
+
+
+def cmd_bench(args) -> int:
+    root = Path(__file__).resolve().parent.parent
+    os.execv(sys.executable, [sys.executable, str(root / "bench.py")] + args.rest)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="research_b200")
+    sub = ap.add_subparsers(dest="command", required=True)
+    p = sub.add_parser("build"); p.add_argument("--force", action="store_true"); p.set_defaults(fn=cmd_build)
+    p = sub.add_parser("serve")
+    p.add_argument("--model", default="qwen2.5-0.5b", help="preset name (random weights) or a checkpoint directory")
+    p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=30000)
+    p.add_argument("--cache", default="radix", choices=["paged", "radix", "none"])
+    p.add_argument("--max-batch-size", type=int, default=256); p.add_argument("--max-model-len", type=int, default=8192)
+    p.add_argument("--gpu-memory-utilization", type=float, default=0.9); p.add_argument("--tp", type=int, default=1)
+    p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("chat")
+    _add_endpoint_args(p)
+    p.add_argument("--preset", default="chat"); p.add_argument("--cwd", default="."); p.add_argument("--store", default="")
+    p.add_argument("--session", default="", help="resume this session"); p.add_argument("-p", "--prompt", default=None)
+    p.add_argument("-y", "--yes", action="store_true", help="run tools without asking")
+    p.set_defaults(fn=cmd_chat)
+    p = sub.add_parser("sessions")
+    p.add_argument("action", choices=["list", "show", "export", "slice", "import"]); p.add_argument("id", nargs="?")
+    p.add_argument("--spec", default=""); p.add_argument("--format", default="md", choices=["md", "html"])
+    p.add_argument("--output", default=""); p.add_argument("--store", default=""); p.add_argument("--limit", type=int, default=20)
+    p.set_defaults(fn=cmd_sessions)
+    p = sub.add_parser("eval")
+    _add_endpoint_args(p)
+    p.add_argument("--dataset", required=True, help="JSONL file, one row per sample")
+    p.add_argument("--score-fn", required=True, help="module:function(trajectory, row) -> float | Score")
+    p.add_argument("--preset", default="chat"); p.add_argument("--cwd", default=".")
+    p.add_argument("--max-samples", type=int, default=None); p.add_argument("--max-concurrent", type=int, default=8)
+    p.add_argument("--output-dir", default=None); p.add_argument("--name", default="eval")
+    p.set_defaults(fn=cmd_eval)
+    p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
+    return ap
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = build_parser().parse_args(argv)
+    return int(args.fn(args) or 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,72 @@
+"""CLI plumbing and deploy helpers, offline."""
+
+import asyncio
+import json
+
+import pytest
+
+from research_b200 import cli
+from research_b200.agents.dtypes import Message
+from research_b200.agents.presets import PRESETS, get_preset
+from research_b200.agents.providers import ScriptedLLM, register_provider
+from research_b200.agents.store import FileSessionStore
+from research_b200.deploy import (ServerConfig, build_command, build_native_command, build_sglang_command, preflight,
+                                  wait_until_healthy)
+
+
+def test_server_commands():
+    with pytest.raises(ValueError):
+        ServerConfig(tensor_parallel_size=2)
+    c = ServerConfig(model="Qwen/Qwen2.5-0.5B", engine="sglang", gpu_ranks=[2, 3], tensor_parallel_size=2, max_model_len=4096,
+                     attention_backend="triton")
+    cmd = build_sglang_command(c)
+    assert "--tp 2" in cmd and "--context-length 4096" in cmd and "--enable-radix-cache" in cmd and "--attention-backend triton" in cmd
+    assert build_command(c).startswith("CUDA_VISIBLE_DEVICES=2,3 ")
+    n = build_native_command(ServerConfig(model="llama-3-8b", gpu_ranks=[0, 1], tensor_parallel_size=2, port=31000))
+    assert "torch.distributed.run" in n and "--nproc-per-node 2" in n and "--master-addr 127.0.0.1" in n and "--tp 2" in n
+    assert "research_b200.cli serve" in build_native_command(ServerConfig())
+
+
+def test_preflight_and_health_with_fakes():
+    def run(cmd):
+        if cmd.startswith("nvidia-smi"):
+            return 0, "0, 12\n1, 90000\n"
+        if "ss -ltn" in cmd:
+            return 0, "taken"
+        return 1, "no module"
+
+    problems = preflight(ServerConfig(engine="sglang", gpu_ranks=[1, 2], tensor_parallel_size=2), run)
+    assert any("GPU 1 is busy" in p for p in problems) and any("GPU 2 does not exist" in p for p in problems)
+    assert any("port" in p for p in problems) and any("sglang" in p for p in problems)
+    assert preflight(ServerConfig(), lambda c: (0, "0, 3\n") if c.startswith("nvidia-smi") else (0, "free")) == []
+    calls = []
+    assert wait_until_healthy("http://x", timeout=5, poll=0.01, probe=lambda u: calls.append(u) or len(calls) >= 3)
+    assert not wait_until_healthy("http://x", timeout=5, poll=0.01, probe=lambda u: False, alive=lambda: False)
+
+
+def test_presets_build_environments(tmp_path):
+    for name in PRESETS:
+        env = get_preset(name).environment(str(tmp_path))
+        assert hasattr(env, "get_tools") and hasattr(env, "exec_tool")
+    with pytest.raises(KeyError):
+        get_preset("nope")
+
+
+def test_cli_chat_sessions_eval(tmp_path, capsys):
+    register_provider("cli-mock", ScriptedLLM(["hello from the model"]))
+    store_dir = str(tmp_path / "sessions")
+    assert cli.main(["chat", "--provider", "cli-mock", "--store", store_dir, "-p", "hi"]) == 0
+    assert "hello from the model" in capsys.readouterr().out
+    sid = asyncio.run(FileSessionStore(store_dir).list())[0].session_id
+    assert cli.main(["sessions", "list", "--store", store_dir]) == 0 and sid in capsys.readouterr().out
+    assert cli.main(["sessions", "show", sid, "--store", store_dir]) == 0 and "hello from the model" in capsys.readouterr().out
+    assert cli.main(["sessions", "slice", sid, "--spec", "0:2", "--store", store_dir]) == 0
+    ds = tmp_path / "d.jsonl"
+    ds.write_text("\n".join(json.dumps({"prompt": f"q{i}", "answer": "hello"}) for i in range(3)))
+    score = tmp_path / "score.py"
+    score.write_text("def score(traj, row):\n    return 1.0 if row['answer'] in traj.messages[-1].text() else 0.0\n")
+    assert cli.main(["eval", "--provider", "cli-mock", "--dataset", str(ds), "--score-fn", f"{score}:score",
+                     "--output-dir", str(tmp_path / "out")]) == 0
+    out = capsys.readouterr().out
+    assert json.loads(out[out.index("{"):])["mean_reward"] == 1.0
+    assert isinstance(cli.load_object("research_b200.agents.dtypes:Message")("user", "x"), Message)
