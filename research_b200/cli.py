@@ -59,8 +59,8 @@ def load_object(path: str):
 def cmd_build(args) -> int:
     from . import _native
 
-    for name, path in _native.build_all(force=args.force).items():
-        print(f"{name}: {path}")
+    for path in _native.build_all(force=args.force):
+        print(path)
     return 0
 
 
@@ -76,7 +76,7 @@ def cmd_serve(args) -> int:
     if os.path.isdir(args.model):
         from .models.config import ModelConfig
 
-        cfg = ModelConfig.from_hf_config(json.loads((Path(args.model) / "config.json").read_text()))
+        cfg = ModelConfig.from_hf_dict(json.loads((Path(args.model) / "config.json").read_text()))
         weights = load_safetensors_dir(args.model)
         tokenizer = None
         try:
