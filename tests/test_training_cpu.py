@@ -240,3 +240,42 @@ def test_polar_express_and_muon_cpu():
         opt.step()
         losses.append(loss.item())
     assert losses[-1] < 0.5 * losses[0]
+
+
+class _ToyChatTokenizer:
+    """Character-level tokenizer with a prefix-stable chat template: <role>text\\n per message."""
+
+    def encode(self, text, add_special_tokens=False):
+        return [ord(c) for c in text]
+
+    def apply_chat_template(self, messages, tokenize=True, add_generation_prompt=False):
+        text = "".join(f"<{m['role']}>{m['content']}\n" for m in messages) + ("<assistant>" if add_generation_prompt else "")
+        return self.encode(text) if tokenize else text
+
+
+def test_sft_dataset_preparation(tmp_path):
+    import json
+
+    from research_b200.training.datasets.sft import (export_samples_to_jsonl, load_rl_prompts, load_samples_from_export,
+                                                     load_sft_dataset, tokenize_conversation)
+
+    tok = _ToyChatTokenizer()
+    conv = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"},
+            {"role": "user", "content": "bye"}, {"role": "assistant", "content": "ciao"}]
+    ids, spans = tokenize_conversation(tok, conv)
+    assert [r for _, _, r in spans] == ["system", "user", "assistant", "user", "assistant"] and spans[-1][1] == len(ids)
+    rows = [{"messages": conv}, {"conversations": [{"from": "human", "value": "q"}, {"from": "gpt", "value": "a"}]},
+            {"prompt": "2+2?", "response": "4"}, {"messages": [{"role": "user", "content": "no answer"}]}]
+    p = tmp_path / "sft.jsonl"
+    p.write_text("\n".join(json.dumps(r) for r in rows))
+    samples = load_sft_dataset(p, tok, max_length=200)
+    assert len(samples) == 3
+    s = samples[0]
+    text = "".join(chr(t) for t, m in zip(s.tokens, s.loss_mask) if m)
+    assert text == "<assistant>hello\n<assistant>ciao\n" and s.response_length == len(text)
+    assert len(load_sft_dataset(rows, tok, max_length=30, skip_too_long=True)) == 2
+    export_samples_to_jsonl(samples, tmp_path / "out.jsonl")
+    back = load_samples_from_export(tmp_path / "out.jsonl")
+    assert back[0].tokens == s.tokens and back[0].loss_mask == s.loss_mask
+    prompts = load_rl_prompts([{"question": "1+1?", "answer": 2}, {"messages": conv}, {"nothing": 1}])
+    assert [x.prompt for x in prompts] == ["1+1?", "hi"] and prompts[0].ground_truth == "2"
