@@ -115,13 +115,23 @@ def run_native(args) -> dict:
 
     rank, world, local = dist_setup(args.gpus)
     dev = torch.device(f"cuda:{local}")
-    cfg = get_preset("qwen2.5-0.5b")
+    cfg = get_preset(args.model)
     weights = init_random_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
+    tp = None
+    if args.tp and world > 1:
+        # one engine over all ranks: fused GEMM + all-reduce kernels over NVLink peer memory; every rank
+        # runs the same schedule on the same requests, so the workload seed is shared
+        from research_b200.parallel.symm import PeerComm
+        from research_b200.parallel.tp import TensorParallel
+
+        tp = TensorParallel(PeerComm(device=dev), max_rows=16384 + 64, max_cols=max(cfg.hidden_size, 1024))
+    wl_rank = 0 if tp is not None else rank
     eng = InferenceEngine(
         EngineConfig(cache_type="radix", max_batch_size=MAX_BATCH, max_model_len=2048, ignore_eos=True,
-                     max_tokens_per_batch=16384, num_kv_blocks=40000, seed=rank),
-        cfg, weights, device=dev)
+                     max_tokens_per_batch=16384, num_kv_blocks=40000, seed=wl_rank),
+        cfg, weights, device=dev, tp=tp)
     del weights
+    rank_for_seeds, rank = rank, wl_rank
     prompts = make_workload(rank, cfg.vocab_size)
     params = SamplingParams(temperature=1.0, max_tokens=NEW_TOKENS)
     for i, p in enumerate(prompts):
@@ -183,18 +193,23 @@ def run_native(args) -> dict:
     launches = r.launches_per_graph.get(MAX_BATCH, 0) * K
 
     rows_replayed = int((r.meta_host[3 * MAX_BATCH:4 * MAX_BATCH] > 0).sum())  # live rows in the replayed batch
-    value = sum_over_ranks(float(rows_replayed * K), world) / (dev_ms * 1e-3)
-    e2e = toks_e2e_total / (e2e_ms * 1e-3)
+    replicas = 1 if tp is not None else world
+    value = sum_over_ranks(float(rows_replayed * K), world) / max(world // replicas, 1) / (dev_ms * 1e-3)
+    e2e = toks_e2e_total / max(world // replicas, 1) / (e2e_ms * 1e-3)
+    rank = rank_for_seeds
     out = {
-        "metric": "rollout_decode_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
-        "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "weak",
+        "metric": "rollout_decode_tokens_per_s" if tp is None else "tp_serving_decode_tokens_per_s",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True,
+        "scaling": "weak" if tp is None else "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
         "impl": "native",
-        "config": {"model": "qwen2.5-0.5b-shaped (24L d896 14q/2kv hd64 ffn4864 vocab151936)",
-                   "global_batch": MAX_BATCH * world, "seq_len": "prompt U[128,1024] (50% share a 512-token prefix) + 512 new",
-                   "parallelism": f"dp{world}", "requests_per_replica": N_REQUESTS, "temperature": 1.0,
+        "config": {"model": (f"{args.model}-shaped ({cfg.num_layers}L d{cfg.hidden_size} {cfg.num_heads}q/{cfg.num_kv_heads}kv "
+                             f"hd{cfg.head_dim} ffn{cfg.intermediate_size} vocab{cfg.vocab_size})"),
+                   "global_batch": MAX_BATCH * replicas, "seq_len": "prompt U[128,1024] (50% share a 512-token prefix) + 512 new",
+                   "parallelism": f"dp{world}" if tp is None else f"tp{world}", "requests_per_replica": N_REQUESTS, "temperature": 1.0,
                    "cuda_graph_decode": True, "kv_cache": "paged, radix prefix reuse",
-                   "l2": "inputs larger than L2 (0.99 GB weights + ~2.5 GB KV read per step)"},
+                   "l2": "inputs larger than L2 (weights + KV read per step exceed 126 MB)"},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
                 "wall_ms_per_step": round(wall_ms / K, 4), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
@@ -275,7 +290,7 @@ def run_reference(args) -> dict:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
         "impl": "reference",
         "config": {"model": "qwen2.5-0.5b-shaped via HF transformers", "global_batch": MAX_BATCH * world,
-                   "parallelism": f"dp{world}", "requests_per_replica": N_REQUESTS,
+                   "parallelism": f"dp{world}" if tp is None else f"tp{world}", "requests_per_replica": N_REQUESTS,
                    "engine": "rollouts.inference.InferenceEngine (unmodified; no KV cache, one sequence per forward)"},
         "e2e": {"value": round(value, 2), "unit": "tokens/s",
                 "note": "the reference's step() is already end to end: it builds inputs on the host and reads .item() per token"},
@@ -289,6 +304,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
+    ap.add_argument("--model", default="qwen2.5-0.5b", help="model preset of the native arm (the flagship is the default)")
+    ap.add_argument("--tp", action="store_true", help="native arm: one tensor-parallel engine over all GPUs instead of replicas")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 200 if args.impl == "native" else 3

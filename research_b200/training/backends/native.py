@@ -57,12 +57,24 @@ class NativeTrainingBackend:
         dtype = torch.bfloat16 if on_gpu else torch.float32
         shapes = sorted(param_shapes(model_config).items(), key=lambda kv: (_chunk_of(kv[0]), kv[0]))
         self.buckets = FlatBuckets(self.comm, shapes, _chunk_of, dtype=dtype)
-        if weights is None:
-            from ...models.weights import init_random_weights
+        if weights is None and on_gpu:
+            # random init written straight into the bucket (an 8B model never exists twice in memory)
+            g = torch.Generator(device=self.device).manual_seed(seed)
+            for n in self.buckets.specs:
+                v = self.buckets.param_view(n)
+                if n.endswith("norm.weight") or n.endswith("layernorm.weight"):
+                    v.fill_(1.0)
+                elif n.endswith(".bias"):
+                    v.zero_()
+                else:
+                    v.normal_(0.0, model_config.init_std, generator=g)
+        else:
+            if weights is None:
+                from ...models.weights import init_random_weights
 
-            weights = init_random_weights(model_config, seed=seed)
-        for n in self.buckets.specs:
-            self.buckets.param_view(n).copy_(weights[n].to(device=self.device, dtype=dtype))
+                weights = init_random_weights(model_config, seed=seed)
+            for n in self.buckets.specs:
+                self.buckets.param_view(n).copy_(weights[n].to(device=self.device, dtype=dtype))
         self.comm.barrier_host()
         max_norm = self.config.max_grad_norm if self.config.max_grad_norm is not None else 0.0
         self.optimizer = ShardedAdamW(self.buckets, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,

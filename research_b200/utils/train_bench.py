@@ -1,0 +1,98 @@
+"""Training throughput of the native backend: tokens/s and model FLOP utilisation for one model shape.
+
+    python -m research_b200.utils.train_bench --model llama-3-8b --seq 4096 --batch 1 --steps 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \\
+        -m research_b200.utils.train_bench --model llama-3-8b --seq 4096 --batch 1
+
+A step is ``forward_backward`` (host batch -> pinned -> device, forward, backward) plus ``optim_step``
+(reduce-scatter, clip, AdamW, parameter all-gather). Timed with CUDA events between barriers, maximum
+over ranks; weak scaling (``--batch`` is per rank). Random-init weights, uniform random tokens.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def model_flops_per_token(cfg, seq: int) -> float:
+    """6 * matmul parameters + causal attention (12 * L * d_head * Hq * seq / 2 per token)."""
+    d, L, F = cfg.hidden_size, cfg.num_layers, cfg.intermediate_size
+    qkv = d * (cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_dim
+    per_layer = qkv + cfg.num_heads * cfg.head_dim * d + 3 * d * F
+    matmul_params = L * per_layer + cfg.vocab_size * d
+    return 6.0 * matmul_params + 12.0 * L * cfg.num_heads * cfg.head_dim * seq / 2
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen2.5-0.5b")
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--batch", type=int, default=2, help="sequences per rank per step")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--loss", default="sft")
+    ap.add_argument("--no-checkpointing", action="store_true")
+    ap.add_argument("--peak-tflops", type=float, default=1426.3, help="sustained cuBLAS bf16 TFLOP/s per GPU for the MFU line")
+    args = ap.parse_args()
+
+    import torch.distributed as dist
+
+    from ..models import get_preset
+    from ..training.backends.fsdp import FSDPTrainingBackend
+    from ..training.backends.native import NativeTrainingBackend
+    from ..training.types import TrainerConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = get_preset(args.model)
+    kw = dict(loss_fn=args.loss, lr=1e-5, trainer_config=TrainerConfig(micro_batch_size=1), activation_checkpointing=not args.no_checkpointing,
+              need_entropy=False)
+    backend = FSDPTrainingBackend(cfg, None, **kw) if world > 1 else NativeTrainingBackend(cfg, None, device=dev, **kw)
+    g = torch.Generator().manual_seed(1234 + local)
+
+    def batch():
+        ids = torch.randint(0, cfg.vocab_size, (args.batch, args.seq), generator=g)
+        return {"input_ids": ids, "labels": ids.clone(), "loss_mask": torch.ones(args.batch, args.seq)}
+
+    def step():
+        m = backend.forward_backward(batch()).wait()
+        backend.optim_step().wait()
+        return m
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        m = step()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    tokens = args.batch * args.seq * world
+    tok_s = tokens / (ms.item() * 1e-3)
+    mfu = tok_s / world * model_flops_per_token(cfg, args.seq) / (args.peak_tflops * 1e12)
+    if local == 0 and int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"metric": "train_tokens_per_s", "model": args.model, "n_gpus": world, "seq_len": args.seq,
+                          "batch_per_gpu": args.batch, "ms_per_step": round(ms.item(), 2), "value": round(tok_s, 1),
+                          "mfu_of_sustained_cublas": round(mfu, 3), "loss": round(float(m.get("loss", 0.0)), 4),
+                          "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
+                          "activation_checkpointing": not args.no_checkpointing, "dtype": "bf16", "data": "synthetic"}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
