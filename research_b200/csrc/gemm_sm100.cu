@@ -518,6 +518,23 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                 }
               }
             }
+          } else if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT) {
+            // push the bf16 partial into every rank's staging slab [src_rank][M][N]
+            uint4 o[4];
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              o[j / 8].x = pack_bf16x2(v[j], v[j + 1]);
+              o[j / 8].y = pack_bf16x2(v[j + 2], v[j + 3]);
+              o[j / 8].z = pack_bf16x2(v[j + 4], v[j + 5]);
+              o[j / 8].w = pack_bf16x2(v[j + 6], v[j + 7]);
+            }
+            for (int d = 0; d < p.world; ++d) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[d]) + stage_off) +
+                                   ((long long)p.rank * p.M + row) * p.N + col;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                if (j < ncols) *reinterpret_cast<uint4*>(dst + j) = o[j / 8];
+            }
           } else {
             // push the bf16 partial into the owner's staging slab [src_rank][row_in][N]
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[m_part]) + stage_off) +
@@ -545,8 +562,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         __threadfence_system();
         ok = epi_sync();
         if (!ok) break;
-        if (warp == 2 && lane == 0) {
-          const int tile_in_part = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
+        const int tile_in_part = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
+        if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT) {
+          if (warp == 2 && lane < p.world) {   // one flag per destination rank
+            int* f = reinterpret_cast<int*>(reinterpret_cast<char*>(p.flag_ptrs[lane]) + flag_off) +
+                     (long long)p.rank * (m_tiles_per_part * num_n_tiles) + tile_in_part;
+            st_release_sys(f, reduce_epoch);
+          }
+        } else if (warp == 2 && lane == 0) {
           int* f = reinterpret_cast<int*>(reinterpret_cast<char*>(p.flag_ptrs[m_part]) + flag_off) +
                    (long long)p.rank * (m_tiles_per_part * num_n_tiles) + tile_in_part;
           st_release_sys(f, reduce_epoch);
@@ -560,6 +583,53 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(p.stage_ptrs[p.rank]) + stage_off);
       const int* flags = reinterpret_cast<const int*>(reinterpret_cast<const char*>(p.flag_ptrs[p.rank]) + flag_off);
       const int et = (warp - 2) * 32 + lane;  // 0..127
+      if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT) {
+        // every rank holds all partials of every tile: sum the tiles this CTA computed, store locally
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+          int m_part, m_in, n_part, n_in;
+          tile_coords(t, m_part, m_in, n_part, n_in);
+          const int tile_idx = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
+          if (et < p.world) {
+            if (!wait_flag_ge(flags + (long long)et * tiles_owned + tile_idx, reduce_epoch, p.status)) *abortp = 1;
+          }
+          ok = epi_sync();
+          if (!ok || *abortp) { ok = false; break; }
+          const int n0 = n_part * p.b_rows_per_part + n_in;
+          const int vec_per_row = min(BN, p.b_rows_per_part - n_in) / 8;
+          const int rows = min(BM, p.M - m_in);
+          for (int idx = et; idx < rows * vec_per_row; idx += 128) {
+            const long long row = m_in + idx / vec_per_row;
+            const int col = n0 + (idx % vec_per_row) * 8;
+            float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int src = 0; src < p.world; ++src) {
+              const uint4 b = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * p.M + row) * p.N + col));
+              float2 f;
+              f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
+              f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
+              f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
+              f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
+            }
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+            }
+            if (p.residual != nullptr) {
+              const uint4 b = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
+              float2 f;
+              f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
+              f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
+              f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
+              f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc8[0], acc8[1]);
+            o.y = pack_bf16x2(acc8[2], acc8[3]);
+            o.z = pack_bf16x2(acc8[4], acc8[5]);
+            o.w = pack_bf16x2(acc8[6], acc8[7]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col) = o;
+          }
+        }
+      } else
       for (int ot = blockIdx.x; ot < tiles_owned && ok; ot += gridDim.x) {
         const int mt = ot / num_n_tiles, nt = ot % num_n_tiles;
         // wait for every source rank's copy of this tile
@@ -825,7 +895,8 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
       return -1;
   }
   if (p.epi_mode != RB_EPI_STORE) {
-    if (a->a_parts != p.world || a->out_f32) return -1;
+    if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? (a->a_parts != 1 || a->b_parts != 1) : (a->a_parts != p.world)) return -1;
+    if (a->out_f32 || p.world > 32) return -1;
     if (p.a_rows_per_part % 8 != 0) return -1;
     for (int r = 0; r < p.world; ++r) {
       p.stage_ptrs[r] = a->stage_ptrs[r];

@@ -9,6 +9,10 @@
 #define RB_EPI_STORE 0            // C = acc (+bias) (+residual), local store
 #define RB_EPI_REDUCE_SCATTER 1   // sum over ranks, rank r keeps row slab r
 #define RB_EPI_ALL_REDUCE 2       // sum over ranks, every rank receives all rows
+// One-shot all-reduce for small outputs (decode): every rank pushes its partial tile to EVERY rank's
+// staging slab [src][M][N] and then sums all sources for the tiles it computed, writing only its own
+// output. One cross-GPU hop, no ownership, no trailing barrier; traffic grows with the rank count.
+#define RB_EPI_ALL_REDUCE_ONESHOT 3
 
 #ifdef __cplusplus
 extern "C" {

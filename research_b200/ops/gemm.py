@@ -15,7 +15,7 @@ from .. import _native
 from ._util import check_rc, ptr, status_tensor, stream_handle
 
 RB_MAX_PARTS = 8
-EPI_STORE, EPI_REDUCE_SCATTER, EPI_ALL_REDUCE = 0, 1, 2
+EPI_STORE, EPI_REDUCE_SCATTER, EPI_ALL_REDUCE, EPI_ALL_REDUCE_ONESHOT = 0, 1, 2, 3
 
 
 class RbGemmArgs(ctypes.Structure):
@@ -350,5 +350,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=
     return y.reshape(*lead, weight.shape[0])
 
 
-__all__ = ["gemm", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE"]
+__all__ = ["gemm", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE", "EPI_ALL_REDUCE_ONESHOT"]
 _ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

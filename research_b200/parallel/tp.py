@@ -11,8 +11,10 @@
 
 Staging slabs are double buffered: a rank can only enter call i+2 after every peer finished
 call i (its reduce phase waits for all peers' call-(i+1) tiles, which they push only after
-finishing call i), so no barrier is needed between reduce-scatters. After an all-reduce the
-outputs live in peer memory written by other GPUs, so a device-side barrier follows.
+finishing call i), so no barrier is needed between reduce-scatters. After a two-hop all-reduce the
+outputs live in peer memory written by other GPUs, so a device-side barrier follows. Decode-sized
+all-reduces take the one-shot form instead (every rank pushes its partial to every rank and sums
+locally): one hop, one kernel, no barrier.
 
 The reference has no tensor parallelism in-tree (``EngineConfig.tensor_parallel_size`` is
 unused, rollouts/inference/types.py:25; only ``--tp`` forwarded to an external SGLang).
@@ -26,7 +28,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops._util import check_rc, status_tensor, stream_handle
-from ..ops.gemm import EPI_ALL_REDUCE, EPI_REDUCE_SCATTER, EPI_STORE, RbGemmArgs, _lib as _gemm_lib
+from ..ops.gemm import EPI_ALL_REDUCE, EPI_ALL_REDUCE_ONESHOT, EPI_REDUCE_SCATTER, EPI_STORE, RbGemmArgs, _lib as _gemm_lib
 from .symm import PeerComm, SymmBuffer
 
 
@@ -119,9 +121,38 @@ class TensorParallel:
             dist.all_reduce(part, group=self.comm.group)
             x.add_(part.to(x.dtype))
             return
+        M, N = a.shape[0], w.shape[0]
+        if M <= self.max_rows // self.world and M * N * 2 * self.world <= self.ONESHOT_MAX_BYTES:
+            # decode-sized output: push the partial to every rank, each rank sums locally. One hop, one kernel,
+            # and no barrier afterwards: staging alternates between two parity slabs and a rank cannot run two
+            # calls ahead of a peer, because finishing a call needs the peer's partial of that call.
+            self._reduce_oneshot(a, w, x)
+            return
         buf = self.symm_of(x)
         self._reduce(a, w, EPI_ALL_REDUCE, buf.peer_ptrs, x.stride(0), x.data_ptr(), x.stride(0))
         self.comm.barrier(self._barrier_slot)
+
+    ONESHOT_MAX_BYTES = 32 << 20     # total bytes a rank pushes per call (output bytes x ranks)
+
+    def _reduce_oneshot(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
+        M, K = a.shape
+        N = w.shape[0]
+        assert M % 8 == 0 and N <= self.max_cols
+        bn = self._pick_bn(M, N)
+        self._call += 1
+        args = self._base_args(M, N, K, a, w, bn)
+        args.A[0], args.B[0] = a.data_ptr(), w.data_ptr()
+        args.epi_mode = EPI_ALL_REDUCE_ONESHOT
+        args.C, args.ldc = x.data_ptr(), x.stride(0)
+        args.residual, args.ldr = x.data_ptr(), x.stride(0)
+        args.epoch_counter = self.reduce_state.data_ptr()
+        args.cta_ticket = self.reduce_state.data_ptr() + 4
+        args.stage_parity_bytes = self.world * (self.max_rows // self.world) * self.max_cols * 2
+        args.flag_parity_bytes = self.world * self.max_tiles * 4
+        for r in range(self.world):
+            args.stage_ptrs[r] = self.stage.peer_ptrs[r]
+            args.flag_ptrs[r] = self.tile_flags.peer_ptrs[r]
+        self._launch(args, a.device)
 
     def gemm_reduce_scatter(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
                             residual: torch.Tensor | None = None) -> torch.Tensor:
