@@ -318,6 +318,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   } else {
     // ------------------------------ epilogue warps ----------------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    // reduce modes: a [32 rows][BN columns] bf16 slab per epilogue warp behind the TMA ring (row pitch
+    // padded by 16 bytes so that the row-per-lane writes spread over the banks)
+    constexpr int EPI_ROWB = BN * 2 + 16;
+    uint8_t* epi_stage = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)STAGES * Cfg::kStageBytes +
+                         (size_t)(warp - 2) * 32 * EPI_ROWB;
     uint32_t tile_iter = 0;
     bool ok = true;
     uint32_t epi_phase = 0;
@@ -518,37 +523,19 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                 }
               }
             }
-          } else if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT) {
-            // push the bf16 partial into every rank's staging slab [src_rank][M][N]
-            uint4 o[4];
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              o[j / 8].x = pack_bf16x2(v[j], v[j + 1]);
-              o[j / 8].y = pack_bf16x2(v[j + 2], v[j + 3]);
-              o[j / 8].z = pack_bf16x2(v[j + 4], v[j + 5]);
-              o[j / 8].w = pack_bf16x2(v[j + 6], v[j + 7]);
-            }
-            for (int d = 0; d < p.world; ++d) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[d]) + stage_off) +
-                                   ((long long)p.rank * p.M + row) * p.N + col;
-#pragma unroll
-              for (int j = 0; j < 32; j += 8)
-                if (j < ncols) *reinterpret_cast<uint4*>(dst + j) = o[j / 8];
-            }
           } else {
-            // push the bf16 partial into the owner's staging slab [src_rank][row_in][N]
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[m_part]) + stage_off) +
-                                 ((long long)p.rank * rows_per_rank + row_in) * p.N + col;
+            // reduce modes: park the bf16 partial in this warp's shared-memory slab; the rows are sent to
+            // the peers below with lane-contiguous stores (a thread-per-row store would cross NVLink as
+            // 16-byte packets)
+            uint8_t* srow = epi_stage + (size_t)lane * EPI_ROWB + c0 * 2;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              if (j < ncols) {
-                uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(dst + j) = o;
-              }
+              uint4 o;
+              o.x = pack_bf16x2(v[j], v[j + 1]);
+              o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+              o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+              o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(srow + j * 2) = o;
             }
           }
         }
@@ -558,6 +545,27 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
       if (p.epi_mode != RB_EPI_STORE) {
+        // rows of this warp: q*32 .. q*32+31 of the tile; each row holds n_valid columns
+        const int units_per_row = n_valid >> 3;                      // 16-byte units
+        const int rows_here = min(32, (grouped ? m_part : p.a_rows_per_part - m_in) - q * 32);
+        const int n_dst = p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? p.world : 1;
+        for (int u = lane; u < rows_here * units_per_row; u += 32) {
+          const int rr = u / units_per_row, cu = u - rr * units_per_row;
+          const uint4 o = *reinterpret_cast<const uint4*>(epi_stage + (size_t)rr * EPI_ROWB + cu * 16);
+          const int r_in = m_in + q * 32 + rr;                         // row inside the A slab
+          const int ccol = n_base + cu * 8;
+          for (int di = 0; di < n_dst; ++di) {
+            __nv_bfloat16* dst;
+            if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT)
+              dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[di]) + stage_off) +
+                    ((long long)p.rank * p.M + (long long)m_part * p.a_rows_per_part + r_in) * p.N + ccol;
+            else
+              dst = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(p.stage_ptrs[m_part]) + stage_off) +
+                    ((long long)p.rank * rows_per_rank + r_in) * p.N + ccol;
+            *reinterpret_cast<uint4*>(dst) = o;
+          }
+        }
+        __syncwarp();   // the slab is rewritten by the next tile
         // publish the tile: all 4 epilogue warps must have finished their peer stores
         __threadfence_system();
         ok = epi_sync();
@@ -752,13 +760,15 @@ static int num_sms() {
   return n;
 }
 
+constexpr int kMaxDynSmem = 227 * 1024 - 1024;   // 227 KB per CTA minus the kernel's static shared memory
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
     if (e != cudaSuccess) return -10;
     attr_set = true;
   }
@@ -770,9 +780,7 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  // Ring depth. A CTA that runs a single short work unit is latency-bound and gains nothing from a
-  // deep ring, while a small footprint lets it become resident (programmatic dependent launch)
-  // beside the CTAs of the kernel before it; long persistent launches take the full ring.
+  // Ring depth: never deeper than the k-blocks a CTA will load in total.
   GemmParams q = p;
   int stages = Cfg::kStages;
   if (p.tile_table == nullptr) {
@@ -781,15 +789,14 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
     const int num_kb = (p.K + BK - 1) / BK;
     const long long kb_cta = units_per_cta * (p.split_k > 1 ? p.kb_per_split : num_kb);
     if (kb_cta < stages) stages = kb_cta < 2 ? 2 : (int)kb_cta;
-    static const bool deep = getenv("RB_GEMM_DEEP_RING") != nullptr;
-    if (units_per_cta == 1 && !deep) {
-      const int fit = (112 * 1024) / Cfg::kStageBytes;
-      const int lim = fit > 4 ? fit : 4;
-      if (stages > lim) stages = lim;
-    }
   }
+  // reduce modes stage the outgoing partial tile in shared memory behind the ring
+  const int extra = p.epi_mode != RB_EPI_STORE ? 128 * (BN * 2 + 16) : 0;
+  const int fit = (kMaxDynSmem - 1024 - extra) / Cfg::kStageBytes;
+  if (stages > fit) stages = fit;
+  if (stages < 2) return -14;
   q.stages = stages;
-  const int smem = stages * Cfg::kStageBytes + 1024;
+  const int smem = stages * Cfg::kStageBytes + 1024 + extra;
   return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
 }
 
@@ -908,7 +915,11 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   const int total_b_rows = p.b_rows_per_part;   // rows of the (stacked) B matrix for its tensor map
   if (p.tile_table != nullptr) p.b_rows_per_part = a->group_n;  // columns valid per group
   int bn = a->bn;
-  if (bn == 0) bn = pick_bn(m_tiles, p.b_rows_per_part, p.b_parts, a->b_mn_major, p.K);
+  if (bn == 0) {
+    bn = pick_bn(m_tiles, p.b_rows_per_part, p.b_parts, a->b_mn_major, p.K);
+    // partial tiles cross NVLink row by row: at least 128 contiguous bytes per row
+    if (p.epi_mode != RB_EPI_STORE && bn < 64) bn = 64;
+  }
   if (a->b_mn_major && bn < 64) bn = 64;
   // tensor maps: one per slab
   for (int i = 0; i < p.a_parts; ++i) {

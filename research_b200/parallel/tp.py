@@ -82,7 +82,10 @@ class TensorParallel:
 
     @staticmethod
     def _pick_bn(rows_per_rank: int, N: int) -> int:
-        return 128 if N >= 2048 and rows_per_rank >= 128 else (64 if N >= 512 else 32)
+        """0 = let the kernel's cost model choose (it weighs tile count against the 148 SMs: decode-sized
+        problems get narrow tiles so that every SM streams weights). The flag arrays are sized for the
+        narrowest tile (32 columns), so any choice fits."""
+        return 0
 
     # ---------------------------------------------------------------- row-parallel
     def _reduce(self, a: torch.Tensor, w: torch.Tensor, mode: int, out_ptrs, ldc: int, residual, ldr: int) -> None:

@@ -34,6 +34,13 @@ def case_gemm_down() -> None:
     print(bench_gemm(256, 896, 4864, 1688.4, iters=3))
 
 
+def case_gemm_gateup_8b() -> None:
+    """Decode-time gate|up projection of the 8B shape: M=256, N=28672, K=4096 (weights 235 MB, streamed from HBM)."""
+    from .microbench import bench_gemm
+
+    print(bench_gemm(256, 28672, 4096, 1688.4, iters=3, bn=256))
+
+
 def case_gemm_large() -> None:
     from .microbench import bench_gemm
 
@@ -55,11 +62,14 @@ def case_flash_bwd() -> None:
 
 
 def case_decode_step() -> None:
-    """Two eager decode steps of the 0.5B-shaped model at batch 256 (for a per-launch time list)."""
+    """Two eager decode steps at batch 256 (for a per-launch time list); the model preset comes from
+    RB_PROFILE_MODEL (default: the 0.5B flagship shape)."""
     from ..inference import EngineConfig, InferenceEngine, SamplingParams
     from ..models import get_preset, init_random_weights
 
-    cfg = get_preset("qwen2.5-0.5b")
+    import os
+
+    cfg = get_preset(os.environ.get("RB_PROFILE_MODEL", "qwen2.5-0.5b"))
     dev = torch.device("cuda:0")
     w = init_random_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
     eng = InferenceEngine(EngineConfig(max_batch_size=256, max_model_len=2048, num_kv_blocks=20000, ignore_eos=True,
