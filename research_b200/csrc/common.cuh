@@ -283,6 +283,11 @@ __device__ __forceinline__ int ld_relaxed_sys(const int* p) {
   asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Plain system-scope store: for a flag written after every producing thread has executed a
+// system-scope fence and a CTA barrier (the fences already ordered the data before it).
+__device__ __forceinline__ void st_relaxed_sys(int* p, int v) {
+  asm volatile("st.relaxed.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 // Wait until *p >= want. Returns false (and records ST_TIMEOUT_PEER_FLAG) after budget_ns.
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status,
                                              uint64_t budget_ns = RB_WAIT_BUDGET_NS) {

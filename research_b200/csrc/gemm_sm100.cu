@@ -125,6 +125,14 @@ __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const f
   }
 }
 
+#ifdef RB_GEMM_TIMESTAMPS
+// diagnostic build only: per-CTA time stamps of the reduce path, [cta][8]
+__device__ unsigned long long g_ts[148 * 8];
+#define RB_TS(i) do { if (p.epi_mode != RB_EPI_STORE && threadIdx.x == 64) g_ts[blockIdx.x * 8 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define RB_TS(i) do { } while (0)
+#endif
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
@@ -177,6 +185,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   __syncthreads();
   tc_fence_after();
   pdl_wait();  // barriers and TMEM are set up; from here on we read what the previous kernel wrote
+  RB_TS(0);
   const uint32_t tmem_base = tmem_base_smem;
   volatile int* abortp = &abort_flag;
   // epoch of this reduce call: a host constant, or (graph replay) one past the device counter
@@ -344,6 +353,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                              ST_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
+      RB_TS(1);
       const int row_in = m_in + q * 32 + lane;                 // row inside the A slab
       const bool row_ok = grouped ? (q * 32 + lane < m_part) : (row_in < p.a_rows_per_part);
       const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
@@ -567,7 +577,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         }
         __syncwarp();   // the slab is rewritten by the next tile
         // publish the tile: all 4 epilogue warps must have finished their peer stores
+        RB_TS(2);
         __threadfence_system();
+        RB_TS(3);
         ok = epi_sync();
         if (!ok) break;
         const int tile_in_part = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
@@ -575,7 +587,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
           if (warp == 2 && lane < p.world) {   // one flag per destination rank
             int* f = reinterpret_cast<int*>(reinterpret_cast<char*>(p.flag_ptrs[lane]) + flag_off) +
                      (long long)p.rank * (m_tiles_per_part * num_n_tiles) + tile_in_part;
-            st_release_sys(f, reduce_epoch);
+            // every writer fenced at system scope before the barrier above: a relaxed store is enough and
+            // saves the second fence round trip a release store would pay
+            st_relaxed_sys(f, reduce_epoch);
           }
         } else if (warp == 2 && lane == 0) {
           int* f = reinterpret_cast<int*>(reinterpret_cast<char*>(p.flag_ptrs[m_part]) + flag_off) +
@@ -591,6 +605,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const char*>(p.stage_ptrs[p.rank]) + stage_off);
       const int* flags = reinterpret_cast<const int*>(reinterpret_cast<const char*>(p.flag_ptrs[p.rank]) + flag_off);
       const int et = (warp - 2) * 32 + lane;  // 0..127
+      RB_TS(4);
       if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT) {
         // every rank holds all partials of every tile: sum the tiles this CTA computed, store locally
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -601,40 +616,55 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
             if (!wait_flag_ge(flags + (long long)et * tiles_owned + tile_idx, reduce_epoch, p.status)) *abortp = 1;
           }
           ok = epi_sync();
+          RB_TS(5);
           if (!ok || *abortp) { ok = false; break; }
           const int n0 = n_part * p.b_rows_per_part + n_in;
           const int vec_per_row = min(BN, p.b_rows_per_part - n_in) / 8;
           const int rows = min(BM, p.M - m_in);
-          for (int idx = et; idx < rows * vec_per_row; idx += 128) {
-            const long long row = m_in + idx / vec_per_row;
-            const int col = n0 + (idx % vec_per_row) * 8;
-            float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int src = 0; src < p.world; ++src) {
-              const uint4 b = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * p.M + row) * p.N + col));
-              float2 f;
-              f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
-              f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
-              f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
-              f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
-            }
-            if (p.bias != nullptr) {
+          // all loads of a batch are issued before the first add: the loop is a chain of L2 round trips otherwise
+          constexpr int UNR = 4;
+          const int total = rows * vec_per_row;
+          for (int base = et; base < total; base += 128 * UNR) {
+            uint4 part[UNR][8];
+            uint4 res[UNR];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+            for (int u = 0; u < UNR; ++u) {
+              const int idx = base + u * 128;
+              if (idx < total) {
+                const long long row = m_in + idx / vec_per_row;
+                const int col = n0 + (idx % vec_per_row) * 8;
+                for (int src = 0; src < p.world && src < 8; ++src)
+                  part[u][src] = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * p.M + row) * p.N + col));
+                if (p.residual != nullptr) res[u] = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
+              }
             }
-            if (p.residual != nullptr) {
-              const uint4 b = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
-              float2 f;
-              f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
-              f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
-              f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
-              f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+              const int idx = base + u * 128;
+              if (idx >= total) break;
+              const long long row = m_in + idx / vec_per_row;
+              const int col = n0 + (idx % vec_per_row) * 8;
+              float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+              auto add = [&](const uint4& b) {
+                float2 f;
+                f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
+                f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
+                f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
+                f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
+              };
+              for (int src = 0; src < p.world && src < 8; ++src) add(part[u][src]);
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+              }
+              if (p.residual != nullptr) add(res[u]);
+              uint4 o;
+              o.x = pack_bf16x2(acc8[0], acc8[1]);
+              o.y = pack_bf16x2(acc8[2], acc8[3]);
+              o.z = pack_bf16x2(acc8[4], acc8[5]);
+              o.w = pack_bf16x2(acc8[6], acc8[7]);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col) = o;
             }
-            uint4 o;
-            o.x = pack_bf16x2(acc8[0], acc8[1]);
-            o.y = pack_bf16x2(acc8[2], acc8[3]);
-            o.z = pack_bf16x2(acc8[4], acc8[5]);
-            o.w = pack_bf16x2(acc8[6], acc8[7]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col) = o;
           }
         }
       } else
@@ -695,6 +725,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     }
   }
 
+  RB_TS(6);
   // ------------------------------ teardown --------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -759,6 +790,14 @@ static int num_sms() {
   }
   return n;
 }
+
+#ifdef RB_GEMM_TIMESTAMPS
+}  // namespace rb
+extern "C" int rb_gemm_read_timestamps(unsigned long long* out, int n) {
+  return cudaMemcpyFromSymbol(out, rb::g_ts, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+namespace rb {
+#endif
 
 constexpr int kMaxDynSmem = 227 * 1024 - 1024;   // 227 KB per CTA minus the kernel's static shared memory
 
@@ -903,7 +942,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   }
   if (p.epi_mode != RB_EPI_STORE) {
     if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? (a->a_parts != 1 || a->b_parts != 1) : (a->a_parts != p.world)) return -1;
-    if (a->out_f32 || p.world > 32) return -1;
+    if (a->out_f32 || p.world > (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? 8 : 32)) return -1;
     if (p.a_rows_per_part % 8 != 0) return -1;
     for (int r = 0; r < p.world; ++r) {
       p.stage_ptrs[r] = a->stage_ptrs[r];
