@@ -123,19 +123,30 @@ def decoder_layer_forward(x, w, layer: int, cfg: ModelConfig, positions, attn_ma
 
 
 def causal_lm_forward(input_ids: torch.Tensor, w: dict, cfg: ModelConfig, positions: torch.Tensor | None = None,
-                      attn_mask: torch.Tensor | None = None, return_hidden: bool = False) -> torch.Tensor:
-    """``input_ids [B,T]`` -> logits ``[B,T,V]`` (or final hidden states)."""
+                      attn_mask: torch.Tensor | None = None, return_hidden: bool = False,
+                      trace: dict | None = None) -> torch.Tensor:
+    """``input_ids [B,T]`` -> logits ``[B,T,V]`` (or final hidden states). ``trace``, when given, receives the
+    residual stream after the embedding and after every layer, the final norm and the logits."""
     B, T = input_ids.shape
     if positions is None:
         positions = torch.arange(T, device=input_ids.device)[None].expand(B, T)
     x = F.embedding(input_ids, w["model.embed_tokens.weight"])
+    if trace is not None:
+        trace["embed"] = x.detach()
     for layer in range(cfg.num_layers):
         x = decoder_layer_forward(x, w, layer, cfg, positions, attn_mask)
+        if trace is not None:
+            trace[f"layer.{layer}"] = x.detach()
     x = rms_norm(x, w["model.norm.weight"], cfg.rms_norm_eps)
+    if trace is not None:
+        trace["final_norm"] = x.detach()
     if return_hidden:
         return x
     head = w["model.embed_tokens.weight"] if cfg.tie_word_embeddings else w["lm_head.weight"]
-    return F.linear(x, head)
+    logits = F.linear(x, head)
+    if trace is not None:
+        trace["logits"] = logits.detach()
+    return logits
 
 
 def packed_document_mask(cu_seqlens: torch.Tensor, total: int, device=None) -> torch.Tensor:

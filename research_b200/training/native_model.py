@@ -157,6 +157,7 @@ class NativeCausalLM:
         self.ckpt = activation_checkpointing
         self._params: dict[str, torch.Tensor] = {}
         self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
+        self.trace: dict | None = None
         self.table = ops.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, device=device) \
             if self.on_gpu else None
 
@@ -250,12 +251,19 @@ class NativeCausalLM:
         positions = torch.arange(Tn, device=self.device, dtype=torch.int32).repeat(B)
         emb = "model.embed_tokens.weight"
         x = _Embedding.apply(ids, self.p(emb), self.g(emb))
+        trace = self.trace            # set to a dict to record the residual stream (layer-by-layer debugging)
+        if trace is not None:
+            trace["embed"] = x.detach().view(B, Tn, -1)
         for i in range(cfg.num_layers):
             if self.ckpt:
                 x = torch.utils.checkpoint.checkpoint(self._layer, x, i, positions, B, Tn, use_reentrant=False)
             else:
                 x = self._layer(x, i, positions, B, Tn)
+            if trace is not None:
+                trace[f"layer.{i}"] = x.detach().view(B, Tn, -1)
         h = _RMSNorm.apply(x, self.p("model.norm.weight"), self.g("model.norm.weight"), cfg.rms_norm_eps)
+        if trace is not None:
+            trace["final_norm"] = h.detach().view(B, Tn, -1)
         head = emb if cfg.tie_word_embeddings else "lm_head.weight"
         tg = targets.reshape(-1).to(torch.int32).contiguous()
         lp, ent, _ = _FusedLogprob.apply(h, self.p(head), self.g(head), tg, need_entropy)

@@ -332,3 +332,20 @@ def test_hybrid_oracle_blocks():
         wm.update({f"{pe}.gate_proj.weight": r(F_, hidden) * 0.2, f"{pe}.up_proj.weight": r(F_, hidden) * 0.2, f"{pe}.down_proj.weight": r(hidden, F_) * 0.2})
     ym = qwen3_next_moe(xh, wm, "m", top_k=2)
     assert ym.shape == xh.shape and torch.isfinite(ym).all() and not math.isnan(float(ym.sum()))
+
+
+def test_layerwise_debug_report():
+    from research_b200.models import get_preset, init_random_weights
+    from research_b200.models.debug import compare_traces, oracle_trace
+
+    cfg = get_preset("tiny-qwen2", num_layers=3)
+    w = init_random_weights(cfg, seed=0)
+    ids = torch.randint(0, cfg.vocab_size, (2, 9), generator=torch.Generator().manual_seed(0))
+    ref = oracle_trace(ids, w, cfg)
+    assert list(ref)[:2] == ["embed", "layer.0"] and "logits" in ref
+    rep = compare_traces(oracle_trace(ids, w, cfg, torch.bfloat16), ref, rel_tol=5e-2)
+    assert rep.ok and "within tolerance" in rep.format()
+    broken = dict(w)
+    broken["model.layers.1.mlp.down_proj.weight"] = w["model.layers.1.mlp.down_proj.weight"] * 1.5
+    rep = compare_traces(oracle_trace(ids, broken, cfg), ref, rel_tol=1e-3)
+    assert rep.first_divergence.name == "layer.1" and "first divergence at layer.1" in rep.format()

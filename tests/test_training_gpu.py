@@ -109,3 +109,16 @@ def test_backend_gpu_overfits_and_grpo_step(cuda_device, tmp_path):
     hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=cuda_device)
     assert len(hist) == 2 and hist[-1]["weight_version"] == 2.0 and "clipfrac" in hist[-1]
     ops.check_status()
+
+
+def test_native_model_matches_oracle_layer_by_layer(cuda_device):
+    """The kernel path (tcgen05 GEMMs, flash attention at head size 64) against the fp32 oracle, per layer."""
+    from research_b200.models import get_preset
+    from research_b200.models.debug import verify_against_oracle
+    from research_b200.training.backends.native import NativeTrainingBackend
+
+    cfg = get_preset("tiny-qwen2", num_layers=3, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=512)
+    backend = NativeTrainingBackend(cfg, None, device=cuda_device, loss_fn="sft")
+    ids = torch.randint(0, cfg.vocab_size, (2, 160), generator=torch.Generator().manual_seed(0))
+    rep = verify_against_oracle(backend.model, ids, rel_tol=3e-2)
+    assert rep.ok, rep.format()
