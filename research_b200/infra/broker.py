@@ -1,0 +1,154 @@
+"""GPU inventory queries and provisioning behind one interface (broker/broker/client.py:38-326,
+query.py:10-136, api.py:32-638).
+
+Providers implement ``search() -> list[GPUOffer]``, ``create(offer, **kw) -> GPUInstance`` and
+``terminate(id)``. ``GPUClient`` merges offers from all providers, filters them with a small
+composable query language (``(q.gpu_type == "B200") & (q.price_per_hour < 4)``) and sorts them.
+A ``StaticProvider`` (a fixed inventory, e.g. the machines a lab owns) ships here; cloud back ends plug
+in through the same three methods.
+"""
+
+from __future__ import annotations
+
+import itertools
+import operator
+from dataclasses import dataclass, field
+from typing import Any, Callable, Protocol
+
+
+@dataclass(frozen=True)
+class GPUOffer:
+    provider: str
+    offer_id: str
+    gpu_type: str
+    gpu_count: int = 1
+    vram_gb: int = 0
+    price_per_hour: float = 0.0
+    region: str = ""
+    interconnect: str = ""        # e.g. "nvlink5"
+    spot: bool = False
+    extra: dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass
+class GPUInstance:
+    provider: str
+    instance_id: str
+    offer: GPUOffer
+    status: str = "running"
+    ssh_connection: str | None = None
+
+
+class Condition:
+    def __init__(self, fn: Callable[[GPUOffer], bool], text: str):
+        self.fn, self.text = fn, text
+
+    def __call__(self, o: GPUOffer) -> bool:
+        return self.fn(o)
+
+    def __and__(self, other: "Condition") -> "Condition":
+        return Condition(lambda o: self(o) and other(o), f"({self.text} & {other.text})")
+
+    def __or__(self, other: "Condition") -> "Condition":
+        return Condition(lambda o: self(o) or other(o), f"({self.text} | {other.text})")
+
+    def __invert__(self) -> "Condition":
+        return Condition(lambda o: not self(o), f"~{self.text}")
+
+    def __repr__(self) -> str:
+        return self.text
+
+
+class Field:
+    def __init__(self, name: str):
+        self.name = name
+
+    def _cmp(self, op, sym, value) -> Condition:
+        return Condition(lambda o: op(getattr(o, self.name), value), f"{self.name} {sym} {value!r}")
+
+    def __eq__(self, v): return self._cmp(operator.eq, "==", v)      # noqa: E704
+    def __ne__(self, v): return self._cmp(operator.ne, "!=", v)      # noqa: E704
+    def __lt__(self, v): return self._cmp(operator.lt, "<", v)       # noqa: E704
+    def __le__(self, v): return self._cmp(operator.le, "<=", v)      # noqa: E704
+    def __gt__(self, v): return self._cmp(operator.gt, ">", v)       # noqa: E704
+    def __ge__(self, v): return self._cmp(operator.ge, ">=", v)      # noqa: E704
+
+    def isin(self, values) -> Condition:
+        vs = set(values)
+        return Condition(lambda o: getattr(o, self.name) in vs, f"{self.name} in {sorted(vs)!r}")
+
+    def contains(self, text: str) -> Condition:
+        return Condition(lambda o: text.lower() in str(getattr(o, self.name)).lower(), f"{text!r} in {self.name}")
+
+    __hash__ = None  # type: ignore[assignment]
+
+
+class _Query:
+    def __getattr__(self, name: str) -> Field:
+        if name not in GPUOffer.__dataclass_fields__:
+            raise AttributeError(f"GPUOffer has no field {name!r}")
+        return Field(name)
+
+
+q = _Query()
+
+
+class Provider(Protocol):
+    name: str
+
+    def search(self) -> list[GPUOffer]: ...
+    def create(self, offer: GPUOffer, **kw: Any) -> GPUInstance: ...
+    def terminate(self, instance_id: str) -> bool: ...
+
+
+class StaticProvider:
+    """A fixed list of machines; ``create`` hands one out, ``terminate`` returns it."""
+
+    def __init__(self, name: str, offers: list[GPUOffer], connections: dict[str, str] | None = None):
+        self.name, self._offers, self._conn = name, list(offers), connections or {}
+        self._busy: dict[str, str] = {}
+        self._ids = itertools.count(1)
+
+    def search(self) -> list[GPUOffer]:
+        return [o for o in self._offers if o.offer_id not in self._busy.values()]
+
+    def create(self, offer: GPUOffer, **kw: Any) -> GPUInstance:
+        if offer.offer_id in self._busy.values():
+            raise RuntimeError(f"{offer.offer_id} is already in use")
+        iid = f"{self.name}-{next(self._ids)}"
+        self._busy[iid] = offer.offer_id
+        return GPUInstance(self.name, iid, offer, "running", self._conn.get(offer.offer_id))
+
+    def terminate(self, instance_id: str) -> bool:
+        return self._busy.pop(instance_id, None) is not None
+
+
+class GPUClient:
+    def __init__(self, providers: list[Provider]):
+        self.providers = {p.name: p for p in providers}
+        self.instances: dict[str, GPUInstance] = {}
+
+    def search(self, where: Condition | None = None, sort_by: str = "price_per_hour", reverse: bool = False) -> list[GPUOffer]:
+        offers = [o for p in self.providers.values() for o in p.search()]
+        if where is not None:
+            offers = [o for o in offers if where(o)]
+        return sorted(offers, key=lambda o: getattr(o, sort_by), reverse=reverse)
+
+    def create(self, where: Condition | None = None, **kw: Any) -> GPUInstance:
+        """Take the cheapest matching offer; fall through to the next one if a provider refuses."""
+        errors = []
+        for o in self.search(where):
+            try:
+                inst = self.providers[o.provider].create(o, **kw)
+                self.instances[inst.instance_id] = inst
+                return inst
+            except Exception as e:  # noqa: BLE001 - try the next offer
+                errors.append(f"{o.provider}/{o.offer_id}: {e}")
+        raise RuntimeError("no offer could be provisioned" + (": " + "; ".join(errors) if errors else " (nothing matched)"))
+
+    def terminate(self, instance_id: str) -> bool:
+        inst = self.instances.pop(instance_id, None)
+        return bool(inst) and self.providers[inst.provider].terminate(instance_id)
+
+    def terminate_all(self) -> int:
+        return sum(self.terminate(i) for i in list(self.instances))
