@@ -70,3 +70,30 @@ def test_cli_chat_sessions_eval(tmp_path, capsys):
     out = capsys.readouterr().out
     assert json.loads(out[out.index("{"):])["mean_reward"] == 1.0
     assert isinstance(cli.load_object("research_b200.agents.dtypes:Message")("user", "x"), Message)
+
+
+def test_session_frontend(tmp_path):
+    from fastapi.testclient import TestClient
+
+    from research_b200.frontend.server import create_app
+
+    store = FileSessionStore(tmp_path)
+
+    async def seed():
+        sid = await store.create({"provider": "front-mock", "model": "m"})
+        await store.append_message(sid, Message("user", "first <question>"))
+        await store.append_message(sid, Message("assistant", "first answer"))
+        return sid
+
+    sid = asyncio.run(seed())
+    client = TestClient(create_app(store, rollout_override=ScriptedLLM(["second answer"])))
+    assert sid in client.get("/").text
+    page = client.get(f"/session/{sid}").text
+    assert "first answer" in page and "&lt;question&gt;" in page
+    assert client.get("/session/nope").status_code == 404
+    assert client.get("/api/sessions").json()[0]["id"] == sid
+    r = client.post(f"/api/session/{sid}/message", json={"content": "and then?"}).json()
+    assert r["content"] == "second answer"
+    msgs = client.get(f"/api/session/{sid}").json()["messages"]
+    assert [m["role"] for m in msgs] == ["user", "assistant", "user", "assistant"]
+    assert client.post(f"/api/session/{sid}/message", json={"content": " "}).status_code == 400
