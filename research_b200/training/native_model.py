@@ -149,7 +149,6 @@ class _FusedLogprob(torch.autograd.Function):
 # ------------------------------------------------------------------------------ the model
 class NativeCausalLM:
     def __init__(self, cfg: ModelConfig, buckets, device: torch.device, activation_checkpointing: bool = False):
-        assert not cfg.is_moe, "use research_b200.parallel.moe for mixture-of-experts training"
         self.cfg = cfg
         self.b = buckets
         self.device = device
@@ -237,9 +236,53 @@ class NativeCausalLM:
         h = _RMSNorm.apply(x, self.p(pre + "post_attention_layernorm.weight"),
                            self.g(pre + "post_attention_layernorm.weight"), cfg.rms_norm_eps)
         m = pre + "mlp."
+        if cfg.is_moe and i >= cfg.first_k_dense_replace:
+            return x + self._moe(h, m, lin)
         gu = torch.cat([lin(h, m + "gate_proj.weight"), lin(h, m + "up_proj.weight")], dim=-1)
         x = x + lin(_SwiGLU.apply(gu), m + "down_proj.weight")
         return x
+
+    def _moe(self, h, m: str, lin):
+        """Mixture-of-experts MLP for training: router and expert projections are tcgen05 GEMMs (forward, dgrad
+        and wgrad through ``_Linear``), tokens are grouped by expert with one sort, and every expert with work
+        runs its three GEMMs on its slice (math of models/functional.py::moe_mlp). One host sync per layer
+        (the per-expert token counts); the serving path uses the grouped GEMM with a device tile table instead."""
+        cfg = self.cfg
+        k, E = cfg.num_experts_per_tok, cfg.num_experts
+        logits = lin(h, m + "gate.weight").float()
+        if cfg.router_type == "sigmoid":
+            scores = logits.sigmoid()
+            idx = (scores + self.p(m + "gate.e_score_correction_bias").float()).topk(k, dim=-1).indices
+            wt = scores.gather(-1, idx)
+            if cfg.norm_topk_prob:
+                wt = wt / (wt.sum(-1, keepdim=True) + 1e-20)
+            wt = wt * cfg.routed_scaling_factor
+        else:
+            wt, idx = logits.softmax(-1).topk(k, dim=-1)
+            if cfg.norm_topk_prob:
+                wt = wt / wt.sum(-1, keepdim=True)
+        flat = idx.reshape(-1)
+        order = flat.argsort(stable=True)                       # (token, slot) pairs grouped by expert
+        counts = torch.bincount(flat, minlength=E).tolist()     # the one host sync
+        tok = order // k
+        xs = h.index_select(0, tok)                              # [T*k, d] rows in expert order
+        ws = wt.reshape(-1).index_select(0, order).to(h.dtype)
+        outs, off = [], 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            xe = xs[off:off + n]
+            p = f"{m}experts.{e}."
+            gu = torch.cat([lin(xe, p + "gate_proj.weight"), lin(xe, p + "up_proj.weight")], dim=-1)
+            outs.append(lin(_SwiGLU.apply(gu), p + "down_proj.weight"))
+            off += n
+        y = torch.cat(outs, 0) * ws[:, None]
+        out = torch.zeros_like(h).index_add(0, tok, y)
+        if cfg.n_shared_experts > 0:
+            p = m + "shared_experts."
+            gu = torch.cat([lin(h, p + "gate_proj.weight"), lin(h, p + "up_proj.weight")], dim=-1)
+            out = out + lin(_SwiGLU.apply(gu), p + "down_proj.weight")
+        return out
 
     def logprobs(self, input_ids: torch.Tensor, targets: torch.Tensor, need_entropy: bool = False):
         """Per-token ``log p(targets)`` ``[B,T]`` (and entropy) with autograd through the kernels."""

@@ -349,3 +349,17 @@ def test_layerwise_debug_report():
     broken["model.layers.1.mlp.down_proj.weight"] = w["model.layers.1.mlp.down_proj.weight"] * 1.5
     rep = compare_traces(oracle_trace(ids, broken, cfg), ref, rel_tol=1e-3)
     assert rep.first_divergence.name == "layer.1" and "first divergence at layer.1" in rep.format()
+
+
+def test_moe_training_backend_cpu():
+    from research_b200.models import get_preset
+    from research_b200.training.backends import PyTorchTrainingBackend
+
+    cfg = get_preset("tiny-moe", num_layers=2)
+    be = PyTorchTrainingBackend(cfg, device="cpu", loss_fn="ce", lr=3e-3)
+    ids = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(0))
+    losses = []
+    for _ in range(4):
+        losses.append(be.forward_backward({"input_ids": ids, "labels": ids}).wait()["loss"])
+        be.optim_step().wait()
+    assert losses[-1] < losses[0]

@@ -122,3 +122,34 @@ def test_native_model_matches_oracle_layer_by_layer(cuda_device):
     ids = torch.randint(0, cfg.vocab_size, (2, 160), generator=torch.Generator().manual_seed(0))
     rep = verify_against_oracle(backend.model, ids, rel_tol=3e-2)
     assert rep.ok, rep.format()
+
+
+@pytest.mark.parametrize("preset", ["tiny-moe", "tiny-glm4-moe"])
+def test_native_moe_gradients_vs_oracle(cuda_device, preset):
+    """Mixture-of-experts training on the kernel path: loss and expert / router gradients against the oracle."""
+    cfg = get_preset(preset, num_layers=2, init_std=0.05)
+    w = {k: v.bfloat16().float() for k, v in init_random_weights(cfg, seed=0).items()}
+    be = PyTorchTrainingBackend(cfg, w, device=cuda_device, loss_fn="ce", lr=1e-3)
+    ids = torch.randint(0, cfg.vocab_size, (4, 32), generator=torch.Generator().manual_seed(1))
+    m = be.forward_backward({"input_ids": ids, "labels": ids}).wait()
+    leaves = {k: v.clone().requires_grad_(True) for k, v in w.items()}
+    ref, _ = L.sft_loss(causal_lm_forward(ids, leaves, cfg), {"labels": ids})
+    ref.backward()
+    assert abs(m["loss"] - float(ref.detach())) < 0.05, (m["loss"], float(ref.detach()))
+    moe_layer = max(cfg.first_k_dense_replace, 1)
+    used = [e for e in range(cfg.num_experts) if leaves[f"model.layers.{moe_layer}.mlp.experts.{e}.down_proj.weight"].grad.abs().sum() > 0]
+    names = [f"model.layers.{moe_layer}.mlp.experts.{used[0]}.down_proj.weight", f"model.layers.{moe_layer}.mlp.experts.{used[-1]}.gate_proj.weight",
+             f"model.layers.{moe_layer}.mlp.gate.weight", "model.layers.0.self_attn.q_proj.weight", "model.embed_tokens.weight"]
+    if cfg.n_shared_experts > 0:
+        names.append(f"model.layers.{moe_layer}.mlp.shared_experts.up_proj.weight")
+    for n in names:
+        got, want = be.buckets.grad_view(n).float().cpu(), leaves[n].grad
+        rel = (got - want).norm() / (want.norm() + 1e-8)
+        cos = torch.nn.functional.cosine_similarity(got.reshape(-1), want.reshape(-1), dim=0)
+        if ".experts." in n or ".gate.weight" in n:
+            # the kernel path routes on bf16 activations: a few near-tie tokens pick another expert than the
+            # fp32 oracle, which moves whole rows of an expert's gradient; direction and scale must still agree
+            assert cos > 0.93 and rel < 0.4, (n, float(rel), float(cos))
+        else:
+            assert rel < 0.1, (n, float(rel), float(cos))
+    ops.check_status()
