@@ -96,6 +96,11 @@ struct GemmParams {
   int scaled_epilogue, mirror;
   float alpha, beta;
   int fp8;
+  float* sample_ws;
+  const float* sample_temperature;
+  const unsigned long long* sample_seeds;
+  const unsigned long long* sample_step_ptr;
+  unsigned long long sample_step_add;
   float* splitk_ws;
   int* splitk_tickets;
 };
@@ -123,6 +128,22 @@ __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const f
       }
     }
   }
+}
+
+// Counter-based random stream of the sampler (identical to rb_sample_logprob: splitmix64 row key,
+// murmur3-style 32-bit mixer per column).
+__device__ __forceinline__ uint64_t sample_mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ uint32_t sample_hash32(uint32_t idx, uint32_t k0, uint32_t k1) {
+  uint32_t h = (idx * 0x9E3779B1u) ^ k0;
+  h ^= h >> 16; h *= 0x85EBCA6Bu;
+  h ^= h >> 13; h *= 0xC2B2AE35u;
+  h ^= h >> 16;
+  return h + k1;
 }
 
 #ifdef RB_GEMM_TIMESTAMPS
@@ -429,7 +450,53 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (!ok) break;
         continue;
       }
-      if (p.swiglu) {
+      if (p.sample_ws != nullptr) {
+        // ---- fused sampling: reduce this tile's logits per row, store one record per (row, n tile) ----
+        float temp = 1.f;
+        uint32_t k0 = 0, k1 = 0;
+        if (row_ok) {
+          temp = p.sample_temperature[row];
+          const unsigned long long step = p.sample_step_add + (p.sample_step_ptr != nullptr ? *p.sample_step_ptr : 0ull);
+          const uint64_t key = sample_mix64(sample_mix64(p.sample_seeds[row]) ^ (step * 0x9E3779B97F4A7C15ull));
+          k0 = (uint32_t)key; k1 = (uint32_t)(key >> 32);
+        }
+        const bool greedy = temp <= 0.f;
+        const float inv_t = greedy ? 1.f : 1.f / temp;
+        float m = -INFINITY, ssum = 0.f, best = -INFINITY, best_logit = 0.f;
+        int best_i = 0x7fffffff;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), r);
+          tmem_ld_wait();
+          const int ncols = min(32, n_valid - c0);
+          if (ncols <= 0) break;
+          float m4 = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < ncols) m4 = fmaxf(m4, __uint_as_float(r[j]));
+          if (m4 > m) { ssum *= __expf(m - m4); m = m4; }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < ncols) {
+              const float x = __uint_as_float(r[j]);
+              ssum += __expf(x - m);
+              float score = x * inv_t;
+              if (!greedy) {
+                const uint32_t h = sample_hash32((uint32_t)(n_base + c0 + j), k0, k1);
+                const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+                score -= 0.6931471805599453f * __log2f(-0.6931471805599453f * __log2f(u));
+              }
+              if (score > best) { best = score; best_i = n_base + c0 + j; best_logit = x; }
+            }
+          }
+        }
+        if (row_ok) {
+          float4* rec = reinterpret_cast<float4*>(p.sample_ws) + ((long long)row * num_n_tiles + n_in / BN) * 2;
+          rec[0] = make_float4(m, ssum, best, best_logit);
+          rec[1] = make_float4(__int_as_float(best_i), 0.f, 0.f, 0.f);
+        }
+      } else if (p.swiglu) {
         if constexpr (BN >= 64) {
           // gate columns [0, BN/2), up columns [BN/2, BN) of the same output channels
           const int out_col0 = (n_base / BN) * (BN / 2);
@@ -916,6 +983,14 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.beta = a->beta;
   p.mirror = a->mirror;
   p.fp8 = a->fp8;
+  p.sample_ws = a->sample_ws;
+  p.sample_temperature = a->sample_temperature;
+  p.sample_seeds = a->sample_seeds;
+  p.sample_step_ptr = a->sample_step_ptr;
+  p.sample_step_add = a->sample_step_add;
+  if (p.sample_ws != nullptr && (a->tile_table || a->swiglu || a->split_k > 1 || a->epi_mode != RB_EPI_STORE || a->a_parts != 1 ||
+                                a->b_parts != 1 || !a->sample_temperature || !a->sample_seeds))
+    return -1;
   if (p.fp8 && (a->a_mn_major || a->b_mn_major)) return -1;   // 8-bit operands are K-major only
   p.split_k = a->split_k > 1 ? a->split_k : 1;
   p.splitk_ws = a->splitk_ws;
@@ -980,6 +1055,47 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
     case 256: return launch_bn<256>(p, a->a_mn_major, a->b_mn_major, a->max_ctas, stream);
     default: return -13;
   }
+}
+
+namespace rb {
+__global__ void sample_merge_kernel(const float4* __restrict__ ws, int M, int n_tiles, int* __restrict__ out_tokens,
+                                    float* __restrict__ out_logprobs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float m = -INFINITY, ssum = 0.f, best = -INFINITY, best_logit = 0.f;
+  int best_i = 0x7fffffff;
+  for (int t = lane; t < n_tiles; t += 32) {
+    const float4 a = ws[((long long)row * n_tiles + t) * 2], b = ws[((long long)row * n_tiles + t) * 2 + 1];
+    const float mn = fmaxf(m, a.x);
+    ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + a.y * __expf(a.x - mn);
+    m = mn;
+    const int bi = __float_as_int(b.x);
+    if (a.z > best || (a.z == best && bi < best_i)) { best = a.z; best_i = bi; best_logit = a.w; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+    const float b2 = __shfl_xor_sync(0xffffffffu, best, o), l2 = __shfl_xor_sync(0xffffffffu, best_logit, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+    const float mn = fmaxf(m, m2);
+    ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + s2 * __expf(m2 - mn);
+    m = mn;
+    if (b2 > best || (b2 == best && i2 < best_i)) { best = b2; best_i = i2; best_logit = l2; }
+  }
+  if (lane == 0) {
+    out_tokens[row] = best_i;
+    out_logprobs[row] = best_logit - (m + __logf(ssum));
+  }
+}
+}  // namespace rb
+
+extern "C" int rb_sample_merge(const float* sample_ws, int M, int n_tiles, int* out_tokens, float* out_logprobs,
+                               cudaStream_t stream) {
+  if (M <= 0) return 0;
+  return rb::launch_kernel(rb::sample_merge_kernel, dim3((M + 3) / 4), dim3(128), 0, stream,
+                           reinterpret_cast<const float4*>(sample_ws), M, n_tiles, out_tokens, out_logprobs) == cudaSuccess ? 0 : -11;
 }
 
 extern "C" void rb_gemm_set_pdl(int on) { rb::pdl_enabled() = on != 0; }

@@ -81,7 +81,20 @@ typedef struct RbGemmArgs {
   // as many columns (K, lda, ldb in units of two bytes): the tiles are moved as bytes and only the
   // tensor-core instruction differs. Per-tensor scales go into alpha.
   int fp8;
+  // Fused sampling epilogue (lm_head): instead of storing the fp32 logits, every tile reduces its
+  // columns per row to (running max, sum of exponentials, best Gumbel-perturbed score, the logit and
+  // column of that score) and writes the 8-float record sample_ws[row][n_tile]; rb_sample_merge
+  // finishes token and log-probability. Same random stream as rb_sample_logprob.
+  float* sample_ws;
+  const float* sample_temperature;              // [M]
+  const unsigned long long* sample_seeds;       // [M]
+  const unsigned long long* sample_step_ptr;    // device step counter (may be null)
+  unsigned long long sample_step_add;
 } RbGemmArgs;
+
+// Token and log-probability from the per-tile records written by the sampling epilogue.
+int rb_sample_merge(const float* sample_ws, int M, int n_tiles, int* out_tokens, float* out_logprobs,
+                    cudaStream_t stream);
 
 int rb_gemm_bf16_ex(const RbGemmArgs* args, cudaStream_t stream);
 

@@ -16,6 +16,8 @@ append, SwiGLU and sampling are the kernels in csrc/attn_sm100.cu and csrc/ops_s
 
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass
 
@@ -147,6 +149,8 @@ class ModelRunner:
         self.a_gu = torch.empty(mb, 2 * self.F, dtype=bf, device=device) if self.F else None
         self.a_act = torch.empty(mb, self.F, dtype=bf, device=device) if self.F else None
         self.a_logits = torch.empty(mb, cfg.vocab_size, dtype=torch.float32, device=device)
+        self.fused_sample = self.on_gpu and not os.environ.get("RB_NO_FUSED_SAMPLE")
+        self.sample_ws = ops.lm_head_sample_workspace(mb, cfg.vocab_size, device) if self.fused_sample else None
         # split-KV partials for small batches (up to 64 rows x 32 splits)
         self.dec_ws = torch.empty(min(mb, 64) * self.Hq * 32 * (self.D + 2), dtype=torch.float32, device=device)
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
@@ -266,8 +270,18 @@ class ModelRunner:
 
         self._forward_layers(x, h, bk, self.d_pos[:bk], self.d_slots[:bk], attn_fn, static=True)
         ops.rmsnorm(x[:bk], self.final_norm, cfg.rms_norm_eps, out=h[:bk])
-        logits = ops.gemm(h[:bk], self.lm_head, out=self.a_logits[:bk], out_f32=True)
-        self._sample(logits, self.d_temps[:bk], self.d_seeds[:bk], bk)
+        self._lm_head_sample(h[:bk], self.d_temps[:bk], self.d_seeds[:bk], bk)
+
+    def _lm_head_sample(self, h, temps, seeds, n: int) -> None:
+        """Final projection + sampling. On the GPU one GEMM whose epilogue reduces each tile to a sampling record
+        (no [n, vocab] fp32 logits are written), then a merge kernel; the two-kernel form is kept for CPU and
+        behind RB_NO_FUSED_SAMPLE."""
+        if self.on_gpu and self.fused_sample:
+            ops.lm_head_sample(h, self.lm_head, temps, seeds, 0, None, self.d_out_tokens[:n], self.d_out_logprobs[:n],
+                               workspace=self.sample_ws)
+            return
+        logits = ops.gemm(h, self.lm_head, out=self.a_logits[:n], out_f32=True)
+        self._sample(logits, temps, seeds, n)
 
     def _sample(self, logits, temps, seeds, n: int) -> None:
         if self.on_gpu:
@@ -379,8 +393,7 @@ class ModelRunner:
         self._forward_layers(x, h, Tp, positions, slots, attn_fn, static=False)
         last = ops.embedding(sample_rows, x)  # row gather of the last token of every sequence
         hl = ops.rmsnorm(last, self.final_norm, cfg.rms_norm_eps)
-        logits = ops.gemm(hl, self.lm_head, out=self.a_logits[:rows], out_f32=True)
-        self._sample(logits, temps, seeds, rows)
+        self._lm_head_sample(hl, temps, seeds, rows)
         self.out_host.copy_(self.out_dev, non_blocking=True)
         _ = dev
 

@@ -30,7 +30,7 @@ from .flash import (
     flash_paged_prefill,
 )
 from . import gemm as gemm_mod
-from .gemm import gemm, gemm_fp8, gemm_reference, gemm_symmetric, quantize_fp8, interleave_gate_up, linear
+from .gemm import gemm, gemm_fp8, lm_head_sample, lm_head_sample_workspace, gemm_reference, gemm_symmetric, quantize_fp8, interleave_gate_up, linear
 from .sampling import sample_with_logprobs, sample_with_logprobs_reference, token_logprobs
 
 def set_pdl(on: bool) -> None:
@@ -47,6 +47,6 @@ __all__ = [
     "paged_decode_reference", "paged_prefill", "paged_prefill_reference", "embedding", "rmsnorm",
     "rmsnorm_reference", "rope_kv_append", "rope_kv_append_reference", "rope_table", "swiglu", "swiglu_backward",
     "swiglu_reference", "transpose", "gemm", "gemm_reference", "linear", "sample_with_logprobs",
-    "sample_with_logprobs_reference", "token_logprobs", "set_pdl", "interleave_gate_up", "gemm_mod", "gemm_symmetric", "gemm_fp8", "quantize_fp8", "flash_attention", "flash_attn_varlen",
+    "sample_with_logprobs_reference", "token_logprobs", "set_pdl", "interleave_gate_up", "gemm_mod", "gemm_symmetric", "gemm_fp8", "quantize_fp8", "lm_head_sample", "lm_head_sample_workspace", "flash_attention", "flash_attn_varlen",
     "flash_attn_varlen_backward", "flash_attn_varlen_reference", "flash_paged_prefill",
 ]

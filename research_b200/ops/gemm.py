@@ -70,6 +70,11 @@ class RbGemmArgs(ctypes.Structure):
         ("beta", ctypes.c_float),
         ("mirror", ctypes.c_int),
         ("fp8", ctypes.c_int),
+        ("sample_ws", ctypes.c_void_p),
+        ("sample_temperature", ctypes.c_void_p),
+        ("sample_seeds", ctypes.c_void_p),
+        ("sample_step_ptr", ctypes.c_void_p),
+        ("sample_step_add", ctypes.c_ulonglong),
     ]
 
 
@@ -78,6 +83,8 @@ def _lib() -> ctypes.CDLL:
     if not getattr(lib, "_rb_typed", False):
         lib.rb_gemm_bf16_ex.argtypes = [ctypes.POINTER(RbGemmArgs), ctypes.c_void_p]
         lib.rb_gemm_bf16_ex.restype = ctypes.c_int
+        lib.rb_sample_merge.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        lib.rb_sample_merge.restype = ctypes.c_int
         lib._rb_typed = True
     return lib
 
@@ -277,6 +284,55 @@ def quantize_fp8(x: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn) -> t
     return (x.float() / s).clamp(-fmax, fmax).to(dtype), s
 
 
+SAMPLE_BN = 256     # tile width of the fused lm_head + sampling launch
+
+
+def lm_head_sample_workspace(M: int, V: int, device) -> torch.Tensor:
+    return torch.empty(M * (-(-V // SAMPLE_BN)) * 8, dtype=torch.float32, device=device)
+
+
+def lm_head_sample(h: torch.Tensor, w: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor, step: int = 0,
+                   step_tensor: torch.Tensor | None = None, out_tokens=None, out_logprobs=None, workspace=None):
+    """Sample one token per row of ``h [M, K]`` from ``softmax(h @ w.T / T)`` and return its log-probability
+    under the unscaled logits, without materialising the ``[M, V]`` logits: the GEMM epilogue reduces every
+    tile to a small record and a merge kernel finishes. Same random stream as ``sample_with_logprobs``."""
+    M, K = h.shape
+    V = w.shape[0]
+    if not h.is_cuda:
+        from .sampling import sample_with_logprobs
+
+        return sample_with_logprobs(gemm_reference(h, w, None, None, False, False, torch.float32), temperatures, seeds, step)
+    assert h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and temperatures.dtype == torch.float32
+    if out_tokens is None:
+        out_tokens = torch.empty(M, dtype=torch.int32, device=h.device)
+    if out_logprobs is None:
+        out_logprobs = torch.empty(M, dtype=torch.float32, device=h.device)
+    if workspace is None:
+        workspace = lm_head_sample_workspace(M, V, h.device)
+    n_tiles = -(-V // SAMPLE_BN)
+    assert workspace.numel() >= M * n_tiles * 8
+    args = RbGemmArgs()
+    args.A[0], args.B[0] = h.data_ptr(), w.data_ptr()
+    args.C = workspace.data_ptr()          # unused by the sampling epilogue, must be a valid pointer
+    args.lda, args.ldb, args.ldc = h.stride(0), w.stride(0), V
+    args.M, args.N, args.K = M, V, K
+    args.a_parts = args.b_parts = 1
+    args.out_f32 = 1
+    args.bn = SAMPLE_BN
+    args.epi_mode = EPI_STORE
+    args.rank, args.world = 0, 1
+    args.sample_ws = workspace.data_ptr()
+    args.sample_temperature = temperatures.data_ptr()
+    args.sample_seeds = seeds.data_ptr()
+    args.sample_step_ptr = step_tensor.data_ptr() if step_tensor is not None else None
+    args.sample_step_add = step
+    args.status = status_tensor(h.device).data_ptr()
+    check_rc(_lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(h.device)), "rb_gemm_bf16_ex(sample)")
+    check_rc(_lib().rb_sample_merge(workspace.data_ptr(), M, n_tiles, out_tokens.data_ptr(), out_logprobs.data_ptr(),
+                                    stream_handle(h.device)), "rb_sample_merge")
+    return out_tokens, out_logprobs
+
+
 _SYM_TABLES: dict[tuple, tuple[torch.Tensor, torch.Tensor, int]] = {}
 
 
@@ -364,5 +420,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=
     return y.reshape(*lead, weight.shape[0])
 
 
-__all__ = ["gemm", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE", "EPI_ALL_REDUCE_ONESHOT"]
+__all__ = ["gemm", "lm_head_sample", "lm_head_sample_workspace", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE", "EPI_ALL_REDUCE_ONESHOT"]
 _ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

@@ -201,7 +201,7 @@ def _make_paged(B, Hkv, D, lens, device, seed):
     bs = 16
     nblk = [(l + bs - 1) // bs for l in lens]
     total = sum(nblk) + 3
-    perm = torch.randperm(total)
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(seed + 7))   # block placement is part of the case
     kc = _rand((total, Hkv, bs, D), device, seed=seed)
     vc = _rand((total, Hkv, bs, D), device, seed=seed + 1)
     max_blocks = max(nblk) + 2
@@ -301,3 +301,24 @@ def test_gemm_fp8(cuda_device, M, N, K, a_dtype):
     _assert_close(got, want, atol=2e-3 * want.abs().max().item(), rtol=1e-3, what="fp8 gemm")
     got16 = ops.gemm_fp8(xq, wq, scale=sx * sw)
     assert got16.dtype == torch.bfloat16 and (got16.float() - want).abs().max().item() < 0.02 * want.abs().max().item()
+
+
+# ------------------------------------------------------------------------------------ fused lm_head + sampling
+@pytest.mark.parametrize("M,V,K", [(256, 151936, 896), (7, 1000, 64), (130, 32000, 256)])
+def test_lm_head_sample_matches_two_step(cuda_device, M, V, K):
+    h = _rand((M, K), cuda_device, seed=51)
+    w = _rand((V, K), cuda_device, seed=52) * 0.2
+    temps = torch.ones(M, device=cuda_device)
+    temps[::3] = 0.0                                     # greedy rows
+    temps[1::3] = 0.7
+    seeds = torch.arange(M, device=cuda_device, dtype=torch.int64) * 7919 + 1
+    step_t = torch.tensor([5], dtype=torch.int64, device=cuda_device)
+    logits = ops.gemm(h, w, out_f32=True)
+    tok_ref, lp_ref = ops.sample_with_logprobs(logits, temps, seeds, step=3, step_tensor=step_t)
+    tok, lp = ops.lm_head_sample(h, w, temps, seeds, step=3, step_tensor=step_t)
+    assert torch.equal(tok, tok_ref), (tok != tok_ref).sum().item()
+    assert torch.allclose(lp, lp_ref, atol=2e-4, rtol=1e-4), (lp - lp_ref).abs().max().item()
+    greedy = logits.argmax(-1).to(torch.int32)
+    assert torch.equal(tok[::3], greedy[::3])
+    tok2, _ = ops.lm_head_sample(h, w, temps, seeds, step=4, step_tensor=step_t)
+    assert (tok2[1::3] != tok[1::3]).any(), "another step must draw other noise"
