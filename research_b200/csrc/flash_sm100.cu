@@ -21,6 +21,7 @@
 #include "tma_host.h"
 
 #include <math.h>
+#include <stdlib.h>
 
 namespace rb {
 
@@ -407,6 +408,352 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       if (row_ok && half == 0 && p.lse != nullptr)
         p.lse[(long long)h * p.Tq + q_begin + q0 + r] =
             l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, FA_TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------
+// Forward, two query tiles per CTA ("ping-pong"): 256 query rows of one head, handled as tiles a and b
+// with one softmax warpgroup each (warps 2-5 and 6-9, a full score row per thread). Both tiles share the
+// K/V tiles in shared memory (loaded once for 256 rows), and while one warpgroup is in its softmax the
+// tensor core works for the other tile, so neither the TMEM read, the P store nor the polling of the MMA
+// thread sits on a critical path. TMEM: S_a, S_b (128 columns each), O_a, O_b (D columns each).
+// ------------------------------------------------------------------------------------------
+template <int D>
+struct Flash2Cfg {
+  static constexpr int kTileBytes = FA_BN * D * 2;
+  static constexpr int kPBytes = FA_BM * FA_BN * 2;
+  static constexpr int kSmemBytes = 1024 + 2 * kTileBytes + FA_KV_SLOTS * kTileBytes + 2 * kPBytes;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_constant__ FlashFwdParams p) {
+  using Cfg = Flash2Cfg<D>;
+  constexpr int DCH = D / 64;
+  constexpr int CHUNK_BYTES = FA_BN * 128;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t q_full, kv_full[FA_KV_SLOTS], kv_empty[FA_KV_SLOTS];
+  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_done[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;
+  const int q_begin = p.cu_q[b];
+  const int q_len = p.cu_q[b + 1] - q_begin;
+  const int q0 = q_tile * 2 * FA_BM;
+  if (q0 >= q_len) return;
+  const int kv_len = p.paged ? p.seq_lens[b] : (p.cu_k[b + 1] - p.cu_k[b]);
+  const int k_begin = p.paged ? 0 : p.cu_k[b];
+  const int off = kv_len - q_len;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const bool has_b = q0 + FA_BM < q_len;
+  // key tiles: both query tiles start at tile a's first visible tile; each stops at its own last one
+  const int lo = p.window > 0 ? max(0, off + q0 - p.window + 1) : 0;
+  const int t_begin = lo / FA_BN;
+  const int hi_a = p.causal ? min(kv_len, off + q0 + FA_BM) : kv_len;
+  const int hi_b = p.causal ? min(kv_len, off + q0 + 2 * FA_BM) : kv_len;
+  const int n_a = max((hi_a + FA_BN - 1) / FA_BN - t_begin, 0);
+  const int n_b = has_b ? max((hi_b + FA_BN - 1) / FA_BN - t_begin, 0) : 0;
+  const int n_tiles = max(n_a, n_b);
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t q_s = smem_base;                                   // Q_a then Q_b
+  const uint32_t kv_s = q_s + 2 * Cfg::kTileBytes;
+  const uint32_t p_off = 2 * Cfg::kTileBytes + FA_KV_SLOTS * Cfg::kTileBytes;   // P_a then P_b
+  const uint32_t p_s = smem_base + p_off;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&q_full), 1);
+    for (int i = 0; i < FA_KV_SLOTS; ++i) {
+      mbar_init(smem_u32(&kv_full[i]), 1);
+      mbar_init(smem_u32(&kv_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&s_full[i]), 1);
+      mbar_init(smem_u32(&s_empty[i]), 4);
+      mbar_init(smem_u32(&p_full[i]), 4);
+      mbar_init(smem_u32(&p_empty[i]), 1);
+      mbar_init(smem_u32(&o_done[i]), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), FA_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one_sync()) {
+      bool ok = true;
+      mbar_expect_tx(smem_u32(&q_full), (has_b ? 2 : 1) * Cfg::kTileBytes);
+      for (int x = 0; x < (has_b ? 2 : 1); ++x)
+#pragma unroll
+        for (int c = 0; c < DCH; ++c)
+          tma_load_2d(q_s + x * Cfg::kTileBytes + c * CHUNK_BYTES, &p.q_map, smem_u32(&q_full), h * D + c * 64,
+                      q_begin + q0 + x * FA_BM);
+      uint32_t it = 0;
+      auto load_tile = [&](int j, int which) -> bool {
+        const int k0 = (t_begin + j) * FA_BN;
+        const int slot = it % FA_KV_SLOTS;
+        if (!mbar_wait_backoff(smem_u32(&kv_empty[slot]), ((it / FA_KV_SLOTS) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY))
+          return false;
+        const uint32_t fb = smem_u32(&kv_full[slot]);
+        const uint32_t dst = kv_s + slot * Cfg::kTileBytes;
+        const CUtensorMap* map = which == 0 ? &p.k_map : &p.v_map;
+        mbar_expect_tx(fb, Cfg::kTileBytes);
+        if (!p.paged) {
+#pragma unroll
+          for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, fb, kvh * D + c * 64, k_begin + k0);
+        } else {
+          const int* bt = p.block_tables + (long long)b * p.max_blocks;
+          const int n_blk = (kv_len + 15) >> 4;
+#pragma unroll 1
+          for (int i = 0; i < FA_BN / 16; ++i) {
+            const int bi = (k0 >> 4) + i;
+            int blk = p.num_blocks;
+            if (bi < n_blk) {
+              blk = bt[bi];
+              if (blk < 0 || blk >= p.num_blocks) { set_status(p.status, ST_BAD_INDEX); blk = p.num_blocks; }
+            }
+            const int y = (blk * p.Hkv + kvh) * 16;
+#pragma unroll
+            for (int c = 0; c < DCH; ++c) tma_load_2d(dst + c * CHUNK_BYTES + i * 2048, map, fb, c * 64, y);
+          }
+        }
+        ++it;
+        return true;
+      };
+      if (n_tiles > 0) ok = load_tile(0, 0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) { ok = load_tile(j + 1, 0); if (!ok) break; }
+        ok = load_tile(j, 1);
+      }
+      if (!ok) {
+        const uint32_t first = it > (uint32_t)FA_KV_SLOTS ? it - FA_KV_SLOTS : 0;
+        for (uint32_t j = first; j < it; ++j) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(smem_u32(&kv_full[j % FA_KV_SLOTS]), (j / FA_KV_SLOTS) & 1u))
+            if (globaltimer_ns() - t0 > 50000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one_sync()) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(FA_BM, FA_BN, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc_bf16(FA_BM, D, 0, 1);
+      bool ok = mbar_wait_backoff(smem_u32(&q_full), 0, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      uint32_t it = 0;                       // K/V tiles consumed, in the producer's order
+      const int n_x[2] = {n_a, n_b};
+      // S_x(j) = Q_x K_j^T into TMEM columns x*128; the K tile sits in ring slot `slot`
+      auto issue_s = [&](int x, int j, int slot) -> bool {
+        if (!mbar_wait_backoff(smem_u32(&s_empty[x]), (uint32_t)((j & 1) ^ 1), abortp, p.status, ST_TIMEOUT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t ks = kv_s + slot * Cfg::kTileBytes, qs = q_s + x * Cfg::kTileBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(qs + (k >> 2) * CHUNK_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(ks + (k >> 2) * CHUNK_BYTES + (k & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + x * FA_BN, adesc, bdesc, idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_full[x]));
+        return true;
+      };
+      auto issue_pv = [&](int x, int j, int slot) -> bool {
+        if (!mbar_wait_backoff(smem_u32(&p_full[x]), (uint32_t)(j & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL)) return false;
+        tc_fence_after();
+        const uint32_t vs = kv_s + slot * Cfg::kTileBytes, ps = p_s + x * Cfg::kPBytes;
+#pragma unroll
+        for (int k = 0; k < FA_BN / 16; ++k) {
+          const uint64_t adesc = make_smem_desc_sw128(ps + (k >> 2) * CHUNK_BYTES + (k & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(vs + k * 2048, CHUNK_BYTES, 1024);
+          umma_bf16(tmem_base + 2 * FA_BN + x * D, adesc, bdesc, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&p_empty[x]));
+        umma_commit(smem_u32(&o_done[x]));
+        return true;
+      };
+      auto wait_kv = [&](int slot, uint32_t idx) -> bool {
+        return mbar_wait_backoff(smem_u32(&kv_full[slot]), (idx / FA_KV_SLOTS) & 1u, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+      };
+      if (ok && n_tiles > 0) {
+        const int slot = it % FA_KV_SLOTS;
+        ok = wait_kv(slot, it);
+        if (ok && n_x[0] > 0) ok = issue_s(0, 0, slot);
+        if (ok && n_x[1] > 0) ok = issue_s(1, 0, slot);
+        if (ok) umma_commit(smem_u32(&kv_empty[slot]));
+        ++it;
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        int kslot = -1;
+        if (j + 1 < n_tiles) {
+          kslot = it % FA_KV_SLOTS;
+          ok = wait_kv(kslot, it);
+          ++it;
+          if (ok && j + 1 < n_x[0]) ok = issue_s(0, j + 1, kslot);
+          if (!ok) break;
+        }
+        const int vslot = it % FA_KV_SLOTS;
+        ok = wait_kv(vslot, it);
+        ++it;
+        if (!ok) break;
+        if (j < n_x[0]) { ok = issue_pv(0, j, vslot); if (!ok) break; }
+        if (kslot >= 0) {
+          if (j + 1 < n_x[1]) { ok = issue_s(1, j + 1, kslot); if (!ok) break; }
+          umma_commit(smem_u32(&kv_empty[kslot]));     // K_{j+1} is free once both score products have run
+        }
+        if (j < n_x[1]) { ok = issue_pv(1, j, vslot); if (!ok) break; }
+        umma_commit(smem_u32(&kv_empty[vslot]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue, one warpgroup per query tile
+    const int x = (warp - 2) >> 2;               // 0: tile a, 1: tile b
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
+    const int q0x = q0 + x * FA_BM;
+    const int qpos = off + q0x + r;
+    const int n_mine = x == 0 ? n_a : n_b;
+    const uint32_t tmem_s = tmem_base + x * FA_BN + lane_addr;
+    const uint32_t tmem_o = tmem_base + 2 * FA_BN + x * D + lane_addr;
+    uint8_t* prow = smem_al + p_off + x * Cfg::kPBytes + r * 128;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_mine; ++j) {
+      const int k0 = (t_begin + j) * FA_BN;
+      ok = mbar_wait_bounded(smem_u32(&s_full[x]), (uint32_t)(j & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool need_mask = (k0 + FA_BN > kv_len) || (p.causal && k0 + FA_BN - 1 > off + q0x) ||
+                             (p.window > 0 && k0 <= off + q0x + FA_BM - 1 - p.window);
+      uint32_t v[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c)
+        tmem_ld_32x32(tmem_s + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_empty[x]));       // the next score product may overwrite S now
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < FA_BN; ++i) {
+          const int kj = k0 + i;
+          const bool dead = kj >= kv_len || (p.causal && kj > qpos) || (p.window > 0 && kj <= qpos - p.window);
+          if (dead) v[i] = 0xff800000u;
+        }
+      }
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 4) {
+        mx[0] = fmaxf(mx[0], __uint_as_float(v[i]));
+        mx[1] = fmaxf(mx[1], __uint_as_float(v[i + 1]));
+        mx[2] = fmaxf(mx[2], __uint_as_float(v[i + 2]));
+        mx[3] = fmaxf(mx[3], __uint_as_float(v[i + 3]));
+      }
+      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+      const bool need = m_new > m_used + FA_RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
+      if (__any_sync(0xffffffffu, need)) {
+        if (j > 0) {
+          ok = mbar_wait_bounded(smem_u32(&o_done[x]), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = need ? fast_exp2((m_used == -INFINITY ? m_new : m_used) - m_new) : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_o + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_o + c * 32, o);
+          }
+          tmem_st_wait();
+          l *= alpha;
+        }
+        if (need) m_used = m_new;
+      }
+      const float mref = m_used == -INFINITY ? 0.f : m_used;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 4) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float e = fast_exp2(fmaf(__uint_as_float(v[i + t]), p.scale_log2, -mref));
+          ls[t] += e;
+          v[i + t] = __float_as_uint(e);
+        }
+      }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      // P buffer is free once the previous P V of this tile has read it
+      ok = mbar_wait_bounded(smem_u32(&p_empty[x]), (uint32_t)((j & 1) ^ 1), abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+#pragma unroll
+      for (int unit = 0; unit < FA_BN / 8; ++unit) {
+        uint4 w;
+        w.x = pack_bf16x2(__uint_as_float(v[unit * 8 + 0]), __uint_as_float(v[unit * 8 + 1]));
+        w.y = pack_bf16x2(__uint_as_float(v[unit * 8 + 2]), __uint_as_float(v[unit * 8 + 3]));
+        w.z = pack_bf16x2(__uint_as_float(v[unit * 8 + 4]), __uint_as_float(v[unit * 8 + 5]));
+        w.w = pack_bf16x2(__uint_as_float(v[unit * 8 + 6]), __uint_as_float(v[unit * 8 + 7]));
+        *reinterpret_cast<uint4*>(prow + (unit >> 3) * CHUNK_BYTES + (((unit & 7) ^ (r & 7)) << 4)) = w;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&p_full[x]));
+    }
+    if (ok && n_mine > 0) {
+      ok = mbar_wait_bounded(smem_u32(&o_done[x]), (uint32_t)((n_mine - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && (x == 0 || has_b)) {
+      tc_fence_after();
+      const bool row_ok = q0x + r < q_len;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.out + ((long long)(q_begin + q0x + r) * p.Hq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_mine > 0) {
+          tmem_ld_32x32(tmem_o + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[u * 8 + 0]) * inv, __uint_as_float(o[u * 8 + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[u * 8 + 2]) * inv, __uint_as_float(o[u * 8 + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[u * 8 + 4]) * inv, __uint_as_float(o[u * 8 + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[u * 8 + 6]) * inv, __uint_as_float(o[u * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + u * 8) = w;
+          }
+        }
+      }
+      if (row_ok && p.lse != nullptr)
+        p.lse[(long long)h * p.Tq + q_begin + q0x + r] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       tc_fence_before();
     }
   }
@@ -995,16 +1342,21 @@ static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, 
 }
 
 template <int D>
-static int launch_flash_fwd(const FlashFwdParams& p, dim3 grid, cudaStream_t stream) {
-  using Cfg = FlashCfg<D>;
+static int launch_flash_fwd(const FlashFwdParams& p, int max_seqlen_q, int B, cudaStream_t stream) {
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Flash2Cfg<D>::kSmemBytes) != cudaSuccess)
       return -10;
     attr = true;
   }
-  return launch_kernel(flash_fwd_kernel<D>, grid, dim3(FA_THREADS), Cfg::kSmemBytes, stream, p) == cudaSuccess ? 0 : -11;
+  static const bool one_tile = getenv("RB_FLASH_ONE_TILE") != nullptr;
+  if (max_seqlen_q > FA_BM && !one_tile) {   // two query tiles per CTA share every K/V tile
+    dim3 grid((max_seqlen_q + 2 * FA_BM - 1) / (2 * FA_BM), p.Hq, B);
+    return launch_kernel(flash_fwd2_kernel<D>, grid, dim3(FA_THREADS), Flash2Cfg<D>::kSmemBytes, stream, p) == cudaSuccess ? 0 : -11;
+  }
+  dim3 grid((max_seqlen_q + FA_BM - 1) / FA_BM, p.Hq, B);
+  return launch_kernel(flash_fwd_kernel<D>, grid, dim3(FA_THREADS), FlashCfg<D>::kSmemBytes, stream, p) == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace rb
@@ -1048,8 +1400,7 @@ int rb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* 
   p.paged = paged;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  dim3 grid((max_seqlen_q + FA_BM - 1) / FA_BM, Hq, B);
-  int rc = D == 64 ? launch_flash_fwd<64>(p, grid, stream) : launch_flash_fwd<128>(p, grid, stream);
+  int rc = D == 64 ? launch_flash_fwd<64>(p, max_seqlen_q, B, stream) : launch_flash_fwd<128>(p, max_seqlen_q, B, stream);
   if (rc != 0) return rc;
   return cudaGetLastError() == cudaSuccess ? 0 : -12;
 }
