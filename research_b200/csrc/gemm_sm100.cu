@@ -700,8 +700,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
               if (idx < total) {
                 const long long row = m_in + idx / vec_per_row;
                 const int col = n0 + (idx % vec_per_row) * 8;
-                for (int src = 0; src < p.world && src < 8; ++src)
-                  part[u][src] = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * p.M + row) * p.N + col));
+#pragma unroll
+                for (int src = 0; src < 8; ++src)
+                  if (src < p.world)
+                    part[u][src] = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * p.M + row) * p.N + col));
                 if (p.residual != nullptr) res[u] = *reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col);
               }
             }
@@ -719,7 +721,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
                 f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
                 f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
               };
-              for (int src = 0; src < p.world && src < 8; ++src) add(part[u][src]);
+#pragma unroll
+              for (int src = 0; src < 8; ++src)
+                if (src < p.world) add(part[u][src]);
               if (p.bias != nullptr) {
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
@@ -749,42 +753,63 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         const int m0 = mt * BM;
         const int vec_per_row = n_valid / 8;
         const int rows = min(BM, rows_per_rank - m0);
-        for (int idx = et; idx < rows * vec_per_row; idx += 128) {
-          const int rr = idx / vec_per_row, cc = (idx % vec_per_row) * 8;
-          const int row_in = m0 + rr;
-          const int col = n0 + cc;
-          float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          for (int src = 0; src < p.world; ++src) {
-            uint4 b = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * rows_per_rank + row_in) * p.N + col));
-            float2 f;
-            f = unpack_bf16x2(b.x); acc8[0] += f.x; acc8[1] += f.y;
-            f = unpack_bf16x2(b.y); acc8[2] += f.x; acc8[3] += f.y;
-            f = unpack_bf16x2(b.z); acc8[4] += f.x; acc8[5] += f.y;
-            f = unpack_bf16x2(b.w); acc8[6] += f.x; acc8[7] += f.y;
-          }
-          const long long grow = (long long)p.rank * rows_per_rank + row_in;
-          if (p.bias != nullptr) {
+        // loads of two steps are in flight before the first add (each step reads `world` partial rows)
+        constexpr int UNR2 = 2;
+        const int total = rows * vec_per_row;
+        for (int base = et; base < total; base += 128 * UNR2) {
+          uint4 part[UNR2][8];   // up to 8 ranks (one NVLink domain); registers, not local memory
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
-          }
-          if (p.residual != nullptr) {
-            // reduce-scatter: residual is the local row slab; all-reduce: the full matrix
-            const long long rrow = (p.epi_mode == RB_EPI_REDUCE_SCATTER) ? row_in : grow;
+          for (int u = 0; u < UNR2; ++u) {
+            const int idx = base + u * 128;
+            if (idx < total) {
+              const int row_in = m0 + idx / vec_per_row, col = n0 + (idx % vec_per_row) * 8;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.residual[rrow * p.ldr + col + j]);
+              for (int src = 0; src < 8; ++src)
+                if (src < p.world)
+                  part[u][src] = __ldcg(reinterpret_cast<const uint4*>(stage + ((long long)src * rows_per_rank + row_in) * p.N + col));
+            }
           }
-          uint4 o;
-          o.x = pack_bf16x2(acc8[0], acc8[1]);
-          o.y = pack_bf16x2(acc8[2], acc8[3]);
-          o.z = pack_bf16x2(acc8[4], acc8[5]);
-          o.w = pack_bf16x2(acc8[6], acc8[7]);
-          if (p.epi_mode == RB_EPI_REDUCE_SCATTER) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[p.rank]);
-            *reinterpret_cast<uint4*>(out + (long long)row_in * p.ldc + col) = o;
-          } else {
-            for (int d = 0; d < p.world; ++d) {
-              __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[d]);
-              *reinterpret_cast<uint4*>(out + grow * p.ldc + col) = o;
+#pragma unroll
+          for (int u = 0; u < UNR2; ++u) {
+            const int idx = base + u * 128;
+            if (idx >= total) break;
+            const int row_in = m0 + idx / vec_per_row, col = n0 + (idx % vec_per_row) * 8;
+            float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int src = 0; src < 8; ++src) {
+              if (src < p.world) {
+                const uint4 bq = part[u][src];
+                float2 f;
+                f = unpack_bf16x2(bq.x); acc8[0] += f.x; acc8[1] += f.y;
+                f = unpack_bf16x2(bq.y); acc8[2] += f.x; acc8[3] += f.y;
+                f = unpack_bf16x2(bq.z); acc8[4] += f.x; acc8[5] += f.y;
+                f = unpack_bf16x2(bq.w); acc8[6] += f.x; acc8[7] += f.y;
+              }
+            }
+            const long long grow = (long long)p.rank * rows_per_rank + row_in;
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.bias[col + j]);
+            }
+            if (p.residual != nullptr) {
+              // reduce-scatter: residual is the local row slab; all-reduce: the full matrix
+              const long long rrow = (p.epi_mode == RB_EPI_REDUCE_SCATTER) ? row_in : grow;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc8[j] += __bfloat162float(p.residual[rrow * p.ldr + col + j]);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc8[0], acc8[1]);
+            o.y = pack_bf16x2(acc8[2], acc8[3]);
+            o.z = pack_bf16x2(acc8[4], acc8[5]);
+            o.w = pack_bf16x2(acc8[6], acc8[7]);
+            if (p.epi_mode == RB_EPI_REDUCE_SCATTER) {
+              __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[p.rank]);
+              *reinterpret_cast<uint4*>(out + (long long)row_in * p.ldc + col) = o;
+            } else {
+              for (int d = 0; d < p.world; ++d) {
+                __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out_ptrs[d]);
+                *reinterpret_cast<uint4*>(out + grow * p.ldc + col) = o;
+              }
             }
           }
         }
@@ -1017,7 +1042,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   }
   if (p.epi_mode != RB_EPI_STORE) {
     if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? (a->a_parts != 1 || a->b_parts != 1) : (a->a_parts != p.world)) return -1;
-    if (a->out_f32 || p.world > (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? 8 : 32)) return -1;
+    if (a->out_f32 || p.world > 8) return -1;   // the reduce keeps one partial per rank in registers
     if (p.a_rows_per_part % 8 != 0) return -1;
     for (int r = 0; r < p.world; ++r) {
       p.stage_ptrs[r] = a->stage_ptrs[r];

@@ -137,3 +137,19 @@ def test_flash_autograd_cross_lengths(cuda_device):
     _grad_check(v.grad, rv, "dv")
     _grad_check(k.grad, rk, "dk")
     _grad_check(q.grad, rq, "dq")
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 4, 2), (64, 4, 1)])
+@pytest.mark.parametrize("causal,window", [(True, 0), (True, 300), (False, 0)])
+def test_flash_long_sequences_two_tile_kernel(cuda_device, D, Hq, Hkv, causal, window):
+    """Lengths around multiples of 256 exercise the two-query-tile kernel: tile b missing, tile b with more key
+    tiles than tile a, window starting inside tile a's range."""
+    lens = [255, 256, 257, 1000, 1281]
+    T = sum(lens)
+    q, k, v = _rand((T, Hq, D), cuda_device, seed=21), _rand((T, Hkv, D), cuda_device, seed=22), _rand((T, Hkv, D), cuda_device, seed=23)
+    cu = _cu(lens, cuda_device)
+    got, lse = flash.flash_attn_varlen(q, k, v, cu, cu, max(lens), causal=causal, window=window, return_lse=True)
+    want, lse_ref = flash.flash_attn_varlen_reference(q, k, v, cu, cu, causal=causal, window=window)
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
+    assert torch.allclose(lse, lse_ref, atol=2e-3, rtol=1e-4), (lse - lse_ref).abs().max().item()
