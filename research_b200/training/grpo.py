@@ -160,12 +160,16 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
     manager = AsyncRolloutManager(buffer, rollout_cfg)
     plan = None
     history: list[dict[str, float]] = []
+    from ..utils.timing import PhaseTimer
+
+    timer = PhaseTimer(device)     # wall + device time + NVTX range per phase
     rollouts_file = open(out_dir / f"rollouts{'' if world == 1 else f'.rank{rank}'}.jsonl", "a")
     try:
         for step in range(config.num_steps):
             t0 = time.perf_counter()
-            batch = await manager.generate_batch()
-            t_roll = time.perf_counter() - t0
+            timer.reset()
+            with timer.phase("rollout"):
+                batch = await manager.generate_batch()
             for s in batch.samples:
                 rollouts_file.write(json.dumps({"step": step, "reward": s.reward, "tokens": len(s.tokens),
                                                 "response_length": s.response_length, "group": s.group_index,
@@ -176,17 +180,15 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
             if n % config.num_minibatches != 0:  # keep whole micro-batches
                 keep = max(config.num_minibatches, n - n % config.num_minibatches)
                 tb = {k: (v[:keep] if isinstance(v, torch.Tensor) and v.shape[0] == n else v) for k, v in tb.items()}
-            t1 = time.perf_counter()
-            fb = await backend.forward_backward(tb).result()
-            opt = await backend.optim_step().result()
-            t_train = time.perf_counter() - t1
-            t2 = time.perf_counter()
-            if (step + 1) % config.sync_weights_every == 0:
-                plan = sync_engine_from_buckets(engine, backend.buckets, plan)
-                engine.weight_version = backend.weight_version
-            t_sync = time.perf_counter() - t2
+            with timer.phase("train"):
+                fb = await backend.forward_backward(tb).result()
+                opt = await backend.optim_step().result()
+            with timer.phase("sync"):
+                if (step + 1) % config.sync_weights_every == 0:
+                    plan = sync_engine_from_buckets(engine, backend.buckets, plan)
+                    engine.weight_version = backend.weight_version
             m = {**fb, **opt, "mean_reward": sum(batch.rewards) / max(len(batch.rewards), 1),
-                 "rollout_s": t_roll, "train_s": t_train, "sync_s": t_sync, "step_s": time.perf_counter() - t0,
+                 **timer.summary(), "step_s": time.perf_counter() - t0,
                  "num_samples": float(len(batch)), "weight_version": float(backend.weight_version),
                  "cache_hit_tokens": float(engine.cache_stats()["hit_tokens"])}
             history.append(m)

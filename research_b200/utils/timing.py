@@ -119,3 +119,62 @@ class ClockSampler:
             "reasons": sorted(reasons),
             "samples": len(sm),
         }
+
+
+class PhaseTimer:
+    """Per-phase timing of a training step (rollout / fwd-bwd / optim / sync): wall clock always, plus the device
+    time between CUDA events when a GPU is in use, plus an NVTX range per phase so the phases show up in a
+    timeline profile. ``with timer.phase("rollout"): ...``; ``timer.summary()`` -> ``{"rollout_s": .., "rollout_dev_ms": ..}``."""
+
+    def __init__(self, device=None, nvtx: bool = True):
+        import torch
+
+        self.cuda = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
+        self.nvtx = nvtx and self.cuda
+        self.wall: dict[str, float] = {}
+        self._events: dict[str, list] = {}
+
+    def phase(self, name: str):
+        return _Phase(self, name)
+
+    def summary(self) -> dict[str, float]:
+        import torch
+
+        out = {f"{k}_s": v for k, v in self.wall.items()}
+        if self.cuda:
+            torch.cuda.synchronize()
+            for k, pairs in self._events.items():
+                out[f"{k}_dev_ms"] = float(sum(a.elapsed_time(b) for a, b in pairs))
+        return out
+
+    def reset(self) -> None:
+        self.wall.clear()
+        self._events.clear()
+
+
+class _Phase:
+    def __init__(self, timer: PhaseTimer, name: str):
+        self.t, self.name = timer, name
+
+    def __enter__(self):
+        import torch
+
+        if self.t.nvtx:
+            torch.cuda.nvtx.range_push(self.name)
+        if self.t.cuda:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        self.w0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc):
+        import torch
+
+        self.t.wall[self.name] = self.t.wall.get(self.name, 0.0) + time.perf_counter() - self.w0
+        if self.t.cuda:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.t._events.setdefault(self.name, []).append((self.e0, e1))
+        if self.t.nvtx:
+            torch.cuda.nvtx.range_pop()
+        return False
