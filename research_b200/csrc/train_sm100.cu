@@ -301,3 +301,100 @@ extern "C" int rb_accumulate_f32_bf16(float* acc, const void* in, long long n, c
   accumulate_kernel<<<grid_for(n, 256), 256, 0, s>>>(acc, (const __nv_bfloat16*)in, n);
   return RB_OK();
 }
+
+// ------------------------------------------------------------------------------------------
+// Small activation / normalisation kernels of the dev experiments (dev/speedrun/single-file.py:786-787,
+// 973-975, 1140: relu^2 MLP, logit soft-capping; dev/integration-evaluation: row log-softmax forward and
+// backward). Elementwise ones stream bf16 with 16-byte accesses; log-softmax keeps one row per warp.
+// ------------------------------------------------------------------------------------------
+namespace rb {
+
+// mode 0: y = relu(x)^2          backward: dx = 2 relu(x) dy
+// mode 1: y = cap * tanh(x/cap)  backward: dx = (1 - tanh(x/cap)^2) dy
+template <bool BWD>
+__global__ void unary_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                             __nv_bfloat16* __restrict__ out, long long n, int mode, float cap) {
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 xv = reinterpret_cast<const uint4*>(x)[i];
+    uint4 gv = make_uint4(0, 0, 0, 0);
+    if (BWD) gv = reinterpret_cast<const uint4*>(dy)[i];
+    const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, gs[4] = {gv.x, gv.y, gv.z, gv.w};
+    uint32_t os[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = unpack_bf16x2(xs[j]), g = unpack_bf16x2(gs[j]);
+      float r[2];
+      const float in[2] = {a.x, a.y}, gg[2] = {g.x, g.y};
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (mode == 0) {
+          const float p = fmaxf(in[t], 0.f);
+          r[t] = BWD ? 2.f * p * gg[t] : p * p;
+        } else {
+          const float th = tanhf(in[t] / cap);
+          r[t] = BWD ? (1.f - th * th) * gg[t] : cap * th;
+        }
+      }
+      os[j] = pack_bf16x2(r[0], r[1]);
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(os[0], os[1], os[2], os[3]);
+  }
+}
+
+// y[r, :] = x[r, :] - logsumexp(x[r, :])   (fp32 in / out), one warp per row
+__global__ void log_softmax_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int rows, int cols) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float* xr = x + (long long)row * cols;
+  float m = -INFINITY, s = 0.f;
+  for (int c = lane; c < cols; c += 32) {
+    const float v = xr[c];
+    if (v > m) { s *= __expf(m - v); m = v; }
+    s += __expf(v - m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, m2);
+    s = (mn == -INFINITY) ? 0.f : s * __expf(m - mn) + s2 * __expf(m2 - mn);
+    m = mn;
+  }
+  const float lse = m + __logf(s);
+  for (int c = lane; c < cols; c += 32) y[(long long)row * cols + c] = xr[c] - lse;
+}
+
+// dx = dy - exp(y) * sum(dy)
+__global__ void log_softmax_bwd_kernel(const float* __restrict__ y, const float* __restrict__ dy, float* __restrict__ dx,
+                                       int rows, int cols) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const long long base = (long long)row * cols;
+  float s = 0.f;
+  for (int c = lane; c < cols; c += 32) s += dy[base + c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  for (int c = lane; c < cols; c += 32) dx[base + c] = dy[base + c] - __expf(y[base + c]) * s;
+}
+
+}  // namespace rb
+
+extern "C" int rb_unary(const void* x, const void* dy, void* out, long long n, int mode, float cap, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0 || mode < 0 || mode > 1 || (mode == 1 && cap <= 0.f)) return -1;
+  long long grid = ((n >> 3) + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  if (dy == nullptr)
+    rb::unary_kernel<false><<<(unsigned)grid, 256, 0, s>>>((const __nv_bfloat16*)x, nullptr, (__nv_bfloat16*)out, n, mode, cap);
+  else
+    rb::unary_kernel<true><<<(unsigned)grid, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)out, n, mode, cap);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int rb_log_softmax(const float* x, const float* dy, float* out, int rows, int cols, cudaStream_t s) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const unsigned grid = (rows + 7) / 8;
+  if (dy == nullptr) rb::log_softmax_fwd_kernel<<<grid, 256, 0, s>>>(x, out, rows, cols);
+  else rb::log_softmax_bwd_kernel<<<grid, 256, 0, s>>>(x, dy, out, rows, cols);     // x is y (the forward output) here
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

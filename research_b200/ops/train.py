@@ -147,3 +147,55 @@ def adamw_step(master, exp_avg, exp_avg_sq, grad, param_bf16, lr, beta1, beta2, 
                          ptr(param_bf16), master.numel(), lr, beta1, beta2, eps, weight_decay, step, grad_scale,
                          ptr(clip_coef), stream_handle(master.device))
     check_rc(rc, "rb_adamw")
+
+
+# ------------------------------------------------------------------------------ small activation kernels
+def _unary(x: torch.Tensor, dy: torch.Tensor | None, mode: int, cap: float) -> torch.Tensor:
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 8 == 0
+    out = torch.empty_like(x)
+    lib = _lib()
+    lib.rb_unary.argtypes = [c_vp, c_vp, c_vp, c_ll, c_int, c_float, c_vp]
+    rc = lib.rb_unary(ptr(x), ptr(dy.contiguous()) if dy is not None else None, ptr(out), x.numel(), mode, cap, stream_handle(x.device))
+    check_rc(rc, "rb_unary")
+    return out
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    """``relu(x)**2`` (the MLP activation of dev/speedrun/single-file.py:973-975)."""
+    return _unary(x, None, 0, 1.0) if x.is_cuda else torch.relu(x.float()).square().to(x.dtype)
+
+
+def relu2_backward(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    return _unary(x, dy, 0, 1.0) if x.is_cuda else (2 * torch.relu(x.float()) * dy.float()).to(x.dtype)
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(x / cap)`` (logit soft-capping, dev/speedrun/single-file.py:1140)."""
+    return _unary(x, None, 1, cap) if x.is_cuda else (cap * torch.tanh(x.float() / cap)).to(x.dtype)
+
+
+def softcap_backward(x: torch.Tensor, dy: torch.Tensor, cap: float) -> torch.Tensor:
+    return _unary(x, dy, 1, cap) if x.is_cuda else ((1 - torch.tanh(x.float() / cap) ** 2) * dy.float()).to(x.dtype)
+
+
+def log_softmax(x: torch.Tensor) -> torch.Tensor:
+    """Row log-softmax of fp32 ``[rows, cols]``."""
+    if not x.is_cuda:
+        return torch.log_softmax(x.float(), -1)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    out = torch.empty_like(x)
+    lib = _lib()
+    lib.rb_log_softmax.argtypes = [c_vp, c_vp, c_vp, c_int, c_int, c_vp]
+    check_rc(lib.rb_log_softmax(ptr(x), None, ptr(out), x.shape[0], x.shape[1], stream_handle(x.device)), "rb_log_softmax")
+    return out
+
+
+def log_softmax_backward(y: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """Gradient w.r.t. the input given the forward output ``y`` and ``dy``."""
+    if not y.is_cuda:
+        return dy.float() - torch.exp(y.float()) * dy.float().sum(-1, keepdim=True)
+    out = torch.empty_like(y)
+    lib = _lib()
+    lib.rb_log_softmax.argtypes = [c_vp, c_vp, c_vp, c_int, c_int, c_vp]
+    check_rc(lib.rb_log_softmax(ptr(y), ptr(dy.contiguous()), ptr(out), y.shape[0], y.shape[1], stream_handle(y.device)), "rb_log_softmax(bwd)")
+    return out

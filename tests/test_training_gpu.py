@@ -153,3 +153,20 @@ def test_native_moe_gradients_vs_oracle(cuda_device, preset):
         else:
             assert rel < 0.1, (n, float(rel), float(cos))
     ops.check_status()
+
+
+def test_small_activation_kernels(cuda_device):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 1024, generator=g).bfloat16().to(cuda_device)
+    dy = torch.randn(64, 1024, generator=g).bfloat16().to(cuda_device)
+    xf, df = x.float(), dy.float()
+    assert torch.allclose(T.relu2(x).float(), torch.relu(xf) ** 2, atol=2e-2, rtol=1e-2)
+    assert torch.allclose(T.relu2_backward(x, dy).float(), 2 * torch.relu(xf) * df, atol=3e-2, rtol=1e-2)
+    assert torch.allclose(T.softcap(x, 15.0).float(), 15 * torch.tanh(xf / 15), atol=2e-2, rtol=1e-2)
+    assert torch.allclose(T.softcap_backward(x, dy, 15.0).float(), (1 - torch.tanh(xf / 15) ** 2) * df, atol=2e-2, rtol=1e-2)
+    z = torch.randn(33, 5001, generator=g).to(cuda_device)
+    y = T.log_softmax(z)
+    assert torch.allclose(y, torch.log_softmax(z, -1), atol=1e-4)
+    w = torch.randn(33, 5001, generator=g).to(cuda_device)
+    ref = torch.autograd.functional.vjp(lambda t: torch.log_softmax(t, -1), z, w)[1]
+    assert torch.allclose(T.log_softmax_backward(y, w), ref, atol=1e-3)
