@@ -91,9 +91,25 @@ def cmd_serve(args) -> int:
         tokenizer = None
     ecfg = EngineConfig(cache_type=args.cache, max_batch_size=args.max_batch_size, max_model_len=args.max_model_len,
                         gpu_memory_utilization=args.gpu_memory_utilization, tensor_parallel_size=args.tp)
-    engine = InferenceEngine(ecfg, cfg, weights, device=device)
-    print(f"serving {args.model} on http://{args.host}:{args.port} ({device})", flush=True)
-    serve(engine, args.host, args.port, args.model, tokenizer)
+    tp = group = None
+    if args.tp > 1:       # launched with torch.distributed.run: one rank per GPU, rank 0 serves HTTP
+        import torch.distributed as dist
+
+        from .parallel.symm import PeerComm
+        from .parallel.tp import TensorParallel
+
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        if device == "cuda":
+            torch.cuda.set_device(local)
+            device = f"cuda:{local}"
+        if not dist.is_initialized():
+            dist.init_process_group("nccl" if device != "cpu" else "gloo")
+        group = dist.new_group(backend="gloo")       # request broadcast travels on a CPU-side group
+        tp = TensorParallel(PeerComm(device=torch.device(device)), max_rows=ecfg.max_batch_size * 64 + 64, max_cols=max(cfg.hidden_size, 1024))
+    engine = InferenceEngine(ecfg, cfg, weights, device=device, tp=tp)
+    if tp is None or tp.rank == 0:
+        print(f"serving {args.model} on http://{args.host}:{args.port} ({device}, tp={args.tp})", flush=True)
+    serve(engine, args.host, args.port, args.model, tokenizer, group=group)
     return 0
 
 

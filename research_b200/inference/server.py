@@ -112,6 +112,78 @@ class EngineService:
         self.thread.join(timeout=5)
 
 
+class LockstepEngineService(EngineService):
+    """Engine service for a tensor-parallel engine: every rank must see the same requests in the same order
+    and step the same number of times. Rank 0 owns the HTTP side; before every step it broadcasts the requests
+    admitted since the last one (an object broadcast on a CPU-side group) together with a stop flag, and all
+    ranks add them and step together. Ranks other than 0 never resolve futures; they call ``follow()``."""
+
+    def __init__(self, engine, group=None, idle_sleep: float = 0.001):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        super().__init__(engine, idle_sleep)
+
+    def _exchange(self, batch, stop: bool):
+        payload = [(([t for t, _, _ in batch], [p for _, p, _ in batch]), stop)] if self.rank == 0 else [None]
+        self.dist.broadcast_object_list(payload, src=0, group=self.group)
+        return payload[0]
+
+    def _run(self) -> None:
+        if self.rank != 0:
+            return                      # followers run the loop in the caller's thread (see follow)
+        while True:
+            if self._paused.is_set():
+                self._idle.set()
+                time.sleep(self.idle_sleep)
+                continue
+            with self._lock:
+                batch, self._pending = self._pending, []
+            stop = self._stop.is_set()
+            if not batch and not self.engine.has_pending() and not stop:
+                self._idle.set()
+                time.sleep(self.idle_sleep)
+                continue
+            self._idle.clear()
+            self._exchange(batch, stop)
+            if stop:
+                return
+            for toks, params, fut in batch:
+                try:
+                    self._futures[self.engine.add_request(toks, params)] = fut
+                except Exception as e:  # noqa: BLE001 - the followers fail the same way and skip it too
+                    fut.set_exception(e)
+            if self.engine.has_pending():
+                for sid, sample in self.engine._step_with_ids():
+                    fut = self._futures.pop(sid, None)
+                    if fut is not None and not fut.done():
+                        fut.set_result(sample)
+                self.steps += 1
+
+    def follow(self) -> None:
+        """Body of every rank other than 0: mirror rank 0's admissions and steps until it says stop."""
+        assert self.rank != 0
+        while True:
+            (toks, params), stop = self._exchange([], False)
+            if stop:
+                return
+            for t, p in zip(toks, params):
+                try:
+                    self.engine.add_request(t, p)
+                except Exception:  # noqa: BLE001 - rank 0 reports it to the caller
+                    pass
+            if self.engine.has_pending():
+                self.engine._step_with_ids()
+                self.steps += 1
+
+    def shutdown(self) -> None:
+        self._stop.set()
+        if self.rank == 0:
+            self.thread.join(timeout=30)
+
+
 def _params_from_sglang(sp: dict[str, Any]) -> SamplingParams:
     return SamplingParams(temperature=float(sp.get("temperature", 1.0)), max_tokens=int(sp.get("max_new_tokens", 128)),
                           stop_token_ids=frozenset(sp.get("stop_token_ids") or ()), seed=sp.get("seed"))
@@ -230,10 +302,19 @@ def default_weight_loader(path: str) -> dict:
     return torch.load(path, map_location="cpu", weights_only=True)
 
 
-def serve(engine, host: str = "127.0.0.1", port: int = 30000, model_name: str = "native", tokenizer=None) -> None:
+def serve(engine, host: str = "127.0.0.1", port: int = 30000, model_name: str = "native", tokenizer=None, group=None) -> None:
+    """Blocks. With an initialised process group of more than one rank (tensor-parallel engine) rank 0 serves HTTP
+    and the other ranks follow its schedule."""
+    import torch.distributed as dist
     import uvicorn
 
-    service = EngineService(engine)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        service = LockstepEngineService(engine, group)
+        if service.rank != 0:
+            service.follow()
+            return
+    else:
+        service = EngineService(engine)
     try:
         uvicorn.run(create_app(service, model_name, tokenizer), host=host, port=port, log_level="warning")
     finally:

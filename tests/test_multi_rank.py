@@ -47,3 +47,12 @@ def test_gpu_ranks(cases):
     out = _run("cuda", 2 if n < 4 else 4 if cases != "weight_sync_tp_engine" else 2, cases)
     for c in cases.split(","):
         assert f"CASE_OK {c}" in out
+
+
+def test_lockstep_tp_serving_two_ranks():
+    """Rank 0 takes requests, rank 1 mirrors its admissions and steps (gloo, CPU)."""
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "lockstep_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode == 0 and "LOCKSTEP_OK" in proc.stdout, proc.stdout[-1500:] + proc.stderr[-3000:]
