@@ -125,11 +125,20 @@ def run_native(args) -> dict:
         from research_b200.parallel.tp import TensorParallel
 
         tp = TensorParallel(PeerComm(device=dev), max_rows=16384 + 64, max_cols=max(cfg.hidden_size, 1024))
+    ep = None
+    if args.ep and world > 1:
+        # one engine per rank on its own requests (data-parallel attention), experts split over the ranks;
+        # dispatch and combine are peer stores from inside the MoE kernels, the engines step in lock step
+        from research_b200.parallel import ExpertParallel
+        from research_b200.parallel.symm import PeerComm
+
+        assert cfg.is_moe and tp is None, "--ep needs a mixture-of-experts model and excludes --tp"
+        ep = ExpertParallel(PeerComm(device=dev))
     wl_rank = 0 if tp is not None else rank
     eng = InferenceEngine(
         EngineConfig(cache_type="radix", max_batch_size=MAX_BATCH, max_model_len=2048, ignore_eos=True,
                      max_tokens_per_batch=16384, num_kv_blocks=40000, seed=wl_rank),
-        cfg, weights, device=dev, tp=tp)
+        cfg, weights, device=dev, tp=tp, ep=ep)
     del weights
     rank_for_seeds, rank = rank, wl_rank
     prompts = make_workload(rank, cfg.vocab_size)
@@ -143,7 +152,10 @@ def run_native(args) -> dict:
         eng.step()
         ramp_steps += 1
         n_prefill, n_decode = eng.last_step_rows
-        if n_prefill == 0 and n_decode == MAX_BATCH:
+        full = n_prefill == 0 and n_decode == MAX_BATCH
+        if ep is not None:       # lock step: every rank leaves the ramp in the same iteration
+            full = not ep.agree(int(not full))[0]
+        if full:
             break
         assert ramp_steps < 64, "engine did not reach a full running batch"
     K, W = args.steps, max(args.warmup, 3)
@@ -198,7 +210,8 @@ def run_native(args) -> dict:
     e2e = toks_e2e_total / max(world // replicas, 1) / (e2e_ms * 1e-3)
     rank = rank_for_seeds
     out = {
-        "metric": "rollout_decode_tokens_per_s" if tp is None else "tp_serving_decode_tokens_per_s",
+        "metric": ("ep_rollout_decode_tokens_per_s" if ep is not None else
+                   "rollout_decode_tokens_per_s" if tp is None else "tp_serving_decode_tokens_per_s"),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
         "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True,
         "scaling": "weak" if tp is None else "strong",
@@ -207,7 +220,8 @@ def run_native(args) -> dict:
         "config": {"model": (f"{args.model}-shaped ({cfg.num_layers}L d{cfg.hidden_size} {cfg.num_heads}q/{cfg.num_kv_heads}kv "
                              f"hd{cfg.head_dim} ffn{cfg.intermediate_size} vocab{cfg.vocab_size})"),
                    "global_batch": MAX_BATCH * replicas, "seq_len": "prompt U[128,1024] (50% share a 512-token prefix) + 512 new",
-                   "parallelism": f"dp{world}" if tp is None else f"tp{world}", "requests_per_replica": N_REQUESTS, "temperature": 1.0,
+                   "parallelism": f"dp{world}+ep{world}" if ep is not None else f"dp{world}" if tp is None else f"tp{world}",
+                   "requests_per_replica": N_REQUESTS, "temperature": 1.0,
                    "cuda_graph_decode": True, "kv_cache": "paged, radix prefix reuse",
                    "l2": "inputs larger than L2 (weights + KV read per step exceed 126 MB)"},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
@@ -290,7 +304,7 @@ def run_reference(args) -> dict:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random-init weights)",
         "impl": "reference",
         "config": {"model": "qwen2.5-0.5b-shaped via HF transformers", "global_batch": MAX_BATCH * world,
-                   "parallelism": f"dp{world}" if tp is None else f"tp{world}", "requests_per_replica": N_REQUESTS,
+                   "parallelism": f"dp{world}", "requests_per_replica": N_REQUESTS,
                    "engine": "rollouts.inference.InferenceEngine (unmodified; no KV cache, one sequence per forward)"},
         "e2e": {"value": round(value, 2), "unit": "tokens/s",
                 "note": "the reference's step() is already end to end: it builds inputs on the host and reads .item() per token"},
@@ -305,6 +319,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--model", default="qwen2.5-0.5b", help="model preset of the native arm (the flagship is the default)")
+    ap.add_argument("--ep", action="store_true", help="native arm, MoE models: data-parallel engines with the experts split over all GPUs")
     ap.add_argument("--tp", action="store_true", help="native arm: one tensor-parallel engine over all GPUs instead of replicas")
     args = ap.parse_args()
     if args.steps is None:

@@ -158,6 +158,14 @@ __global__ void moe_count_kernel(const int* __restrict__ topk_idx, int n, int E,
 
 struct PeerPtrs { void* p[RB_MAX_RANKS]; };
 
+// Publish this rank's histogram as row `rank` of the [world, E] count matrix on every rank (peer stores).
+__global__ void moe_publish_counts_kernel(const int* __restrict__ counts, PeerPtrs counts_all, int rank, int world, int E) {
+  const int r = blockIdx.x;
+  if (r >= world) return;
+  int* dst = reinterpret_cast<int*>(counts_all.p[r]) + (long long)rank * E;
+  for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = counts[i];
+}
+
 // Dispatch: row (t, j) goes to the owner of its expert. Position inside the owner's
 // expert-ordered buffer = expert block offset on the owner + rows from lower source ranks +
 // a running cursor for this (source, expert). ret_addr records where the result row must be
@@ -265,6 +273,11 @@ extern "C" int rb_moe_count(const int* topk_idx, int n, int E, int* counts, cuda
   int grid = (n + 255) / 256;
   if (grid > 148) grid = 148;
   moe_count_kernel<<<grid, 256, 0, s>>>(topk_idx, n, E, counts);
+  return RB_OK();
+}
+extern "C" int rb_moe_publish_counts(const int* counts, void* const* counts_all, int rank, int world, int E, cudaStream_t s) {
+  if (world <= 0 || world > RB_MAX_RANKS) return -1;
+  moe_publish_counts_kernel<<<world, 128, 0, s>>>(counts, mk(counts_all, world), rank, world, E);
   return RB_OK();
 }
 extern "C" int rb_moe_plan(const int* counts_all, int world, int E, int e_lo, int e_hi, int* expert_offset, int n_gu,

@@ -173,10 +173,16 @@ __global__ void rope_kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, __n
 // SwiGLU: out = bf16( bf16(silu(gate)) * up ), gate|up packed as [T, 2F].
 // Reference math: qwen_functional.py:251-274.
 // ------------------------------------------------------------------------------------------
+// `rows_dev` (optional) bounds the row count from device memory: the expert-parallel MoE layer only knows on the
+// device how many routed rows it received.
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                              long long T, int F) {
+                              long long T, int F, const int* __restrict__ rows_dev) {
   pdl_launch_dependents();
   pdl_wait();
+  if (rows_dev != nullptr) {
+    const long long r = *rows_dev;
+    T = r < T ? (r < 0 ? 0 : r) : T;
+  }
   const long long nvec = T * (F >> 3);
   const int fv = F >> 3;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
@@ -448,13 +454,20 @@ extern "C" int rb_rope_kv_append(const void* qkv, void* q_out, void* k_cache, vo
   return e == cudaSuccess ? 0 : -11;
 }
 
-extern "C" int rb_swiglu(const void* gu, void* out, long long T, int F, cudaStream_t stream) {
+static int swiglu_launch(const void* gu, void* out, long long T, int F, const int* rows_dev, cudaStream_t stream) {
   if (F % 8 != 0 || T <= 0) return -1;
   const long long nvec = T * (F / 8);
   long long grid = (nvec + 255) / 256;
   if (grid > 148 * 16) grid = 148 * 16;
   return launch_kernel(swiglu_kernel, dim3((unsigned)grid), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
-                       (__nv_bfloat16*)out, T, F) == cudaSuccess ? 0 : -11;
+                       (__nv_bfloat16*)out, T, F, rows_dev) == cudaSuccess ? 0 : -11;
+}
+extern "C" int rb_swiglu(const void* gu, void* out, long long T, int F, cudaStream_t stream) {
+  return swiglu_launch(gu, out, T, F, nullptr, stream);
+}
+// At most T rows, and no more than *rows_dev (read on the device when the kernel runs).
+extern "C" int rb_swiglu_bounded(const void* gu, void* out, long long T, int F, const int* rows_dev, cudaStream_t stream) {
+  return swiglu_launch(gu, out, T, F, rows_dev, stream);
 }
 
 extern "C" int rb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int F,

@@ -56,7 +56,7 @@ def _core_lib():
 class InferenceEngine:
     def __init__(self, config: EngineConfig, model_config: ModelConfig | None = None,
                  weights: dict[str, torch.Tensor] | None = None, tokenizer=None,
-                 device: torch.device | str | None = None, tp=None) -> None:
+                 device: torch.device | str | None = None, tp=None, ep=None) -> None:
         assert config.block_size == BLOCK, "the KV kernels use 16-token blocks"
         assert config.max_batch_size > 0
         self.config = config
@@ -83,7 +83,12 @@ class InferenceEngine:
         self.runner = ModelRunner(
             model_config, weights, device=self.device, num_kv_blocks=num_blocks, max_batch=config.max_batch_size,
             max_model_len=config.max_model_len, max_prefill_tokens=self.max_tokens_per_batch + 2 * BLOCK,
-            use_cuda_graphs=config.use_cuda_graphs, graph_batch_sizes=config.graph_batch_sizes, tp=tp, dtype=dtype)
+            use_cuda_graphs=config.use_cuda_graphs, graph_batch_sizes=config.graph_batch_sizes, tp=tp, ep=ep, dtype=dtype)
+        # expert parallel: the engines of all ranks step together (see parallel/ep.py); every rank must then call
+        # step() / generate() the same way, and a rank without work of its own runs idle passes
+        self.ep = ep if (ep is not None and ep.world > 1) else None
+        self.peers_pending = False
+        self.idle_passes = 0
         self._lib = _core_lib()
         self._core = self._lib.rbe_create(num_blocks, BLOCK, _CACHE_MODES[config.cache_type], config.max_batch_size,
                                           self.max_tokens_per_batch, config.max_model_len)
@@ -122,15 +127,17 @@ class InferenceEngine:
     def generate(self, prompts: list[list[int]], sampling_params: SamplingParams,
                  num_samples_per_prompt: int = 1) -> list[TrainingSample]:
         """Generate ``num_samples_per_prompt`` completions per prompt; results in request order."""
-        assert len(prompts) > 0 and num_samples_per_prompt > 0
+        assert (len(prompts) > 0 or self.ep is not None) and num_samples_per_prompt > 0
         ids = []
         for prompt in prompts:
             for _ in range(num_samples_per_prompt):
                 ids.append(self.add_request(list(prompt), sampling_params))
         done: dict[int, TrainingSample] = {}
-        while self.has_pending():
+        while True:                      # under expert parallelism all ranks leave the loop in the same iteration
             for sid, sample in self._step_with_ids():
                 done[sid] = sample
+            if not (self.peers_pending if self.ep is not None else self.has_pending()):
+                break
         assert len(done) == len(ids)
         return [done[i] for i in ids]
 
@@ -172,15 +179,26 @@ class InferenceEngine:
         return [s for _, s in self._step_with_ids()]
 
     def _step_with_ids(self) -> list[tuple[int, TrainingSample]]:
-        if not self.has_pending():
-            return []
         lib, core, r = self._lib, self._core, self.runner
-        lib.rbe_schedule(core, self._counts)
-        n_prefill, n_decode = self._counts[0], self._counts[1]
+        mine = self.has_pending()
+        if not mine and self.ep is None:
+            return []
+        n_prefill = n_decode = 0
+        if mine:
+            lib.rbe_schedule(core, self._counts)
+            n_prefill, n_decode = self._counts[0], self._counts[1]
         self.last_step_rows = (n_prefill, n_decode)
+        any_decode, any_prefill = n_decode > 0, n_prefill > 0
+        if self.ep is not None:
+            any_decode, any_prefill, pend = self.ep.agree(n_decode > 0, n_prefill > 0, mine)
+            self.peers_pending = bool(pend)
+        if mine and n_prefill + n_decode == 0 and self._counts[2] == 0:
+            raise RuntimeError("scheduler made no progress: a request does not fit the KV cache")
+        if any_decode and n_decode == 0:
+            self._idle_pass()
+        if any_prefill and n_prefill == 0:
+            self._idle_pass()
         if n_prefill + n_decode == 0:
-            if self._counts[2] == 0:
-                raise RuntimeError("scheduler made no progress: a request does not fit the KV cache")
             return []
         mb = r.max_batch
         if n_decode > 0:
@@ -218,6 +236,19 @@ class InferenceEngine:
         if self.device.type == "cuda" and self.steps % 256 == 0:
             check_status(self.device)
         return self._collect_finished()
+
+    def _idle_pass(self) -> None:
+        """A decode pass over padding rows only: it feeds every MoE layer one (tiny) batch, which is what the peers'
+        dispatch / combine barriers of this phase wait for. Nothing is read back."""
+        r = self.runner
+        r.stage_decode_padding(0)
+        r.decode(0, 1)
+        self._sync()
+        self.idle_passes += 1
+
+    def global_pending(self) -> bool:
+        """True while this rank, or under expert parallelism any rank (as of the last step), still has work."""
+        return self.has_pending() or (self.ep is not None and self.peers_pending)
 
     @staticmethod
     def _max_blocks_in(seq_lens: torch.Tensor) -> int:

@@ -47,7 +47,7 @@ class LayerWeights:
 class ModelRunner:
     def __init__(self, cfg: ModelConfig, weights: dict[str, torch.Tensor], *, device: torch.device,
                  num_kv_blocks: int, max_batch: int, max_model_len: int, max_prefill_tokens: int,
-                 use_cuda_graphs: bool = True, graph_batch_sizes: tuple[int, ...] = (), tp=None,
+                 use_cuda_graphs: bool = True, graph_batch_sizes: tuple[int, ...] = (), tp=None, ep=None,
                  dtype: torch.dtype = torch.bfloat16):
         # On a CUDA device every op below is an sm_100a kernel. On CPU the same call sequence
         # runs the PyTorch reference twins of the ops (fp32), which is how the scheduler,
@@ -61,6 +61,9 @@ class ModelRunner:
         self.cfg = cfg
         self.device = device
         self.tp = tp
+        # expert parallelism: attention and dense layers stay whole on every rank (each rank serves its own
+        # requests), only the experts of the MoE layers are split; ``ep`` carries the peer-memory context
+        self.ep = ep if ep is not None else (tp if getattr(tp, "expert_parallel", False) else None)
         self.tp_size = tp.world if tp is not None else 1
         self.tp_rank = tp.rank if tp is not None else 0
         assert cfg.num_heads % self.tp_size == 0 and cfg.num_kv_heads % self.tp_size == 0
@@ -98,6 +101,7 @@ class ModelRunner:
         self.lm_head = self.embed if cfg.tie_word_embeddings else torch.empty(cfg.vocab_size, d, dtype=bf, device=device)
         self.layers: list[LayerWeights] = []
         qkv_rows = (self.Hq + 2 * self.Hkv) * self.D
+        self.moe_scratch = None
         for i in range(L):
             lw = LayerWeights()
             lw.ln1 = torch.empty(d, dtype=bf, device=device)
@@ -109,10 +113,13 @@ class ModelRunner:
             lw.wo = torch.empty(d, self.Hq * self.D, dtype=bf, device=device)
             lw.moe = None
             if cfg.is_moe and i >= cfg.first_k_dense_replace:
-                from ..parallel.moe import MoELayerWeights
+                from ..parallel.moe import MoELayerWeights, MoEScratch
 
                 lw.wgu = lw.wd = None
-                lw.moe = MoELayerWeights(cfg, device, ep=tp if getattr(tp, "expert_parallel", False) else None)
+                if self.moe_scratch is None and self.on_gpu:
+                    # one fixed-size scratch for all layers: captured graphs keep its addresses
+                    self.moe_scratch = MoEScratch(cfg, device, self.ep, capacity=max(max_prefill_tokens, max_batch))
+                lw.moe = MoELayerWeights(cfg, device, ep=self.ep, scratch=self.moe_scratch)
             else:
                 lw.wgu = torch.empty(2 * self.F, d, dtype=bf, device=device)
                 lw.wd = torch.empty(d, self.F, dtype=bf, device=device)
@@ -334,7 +341,7 @@ class ModelRunner:
         block-table columns. Device->host: one copy of tokens|logprobs into ``out_host``.
         The caller synchronises before reading ``out_host``.
         """
-        bk = self.bucket(n) if (self.use_cuda_graphs or self.row_align > 1) else n
+        bk = self.bucket(n) if (self.use_cuda_graphs or self.row_align > 1) else max(n, 1)
         self.meta_dev.copy_(self.meta_host, non_blocking=True)
         self.bt_dev[:n, :max_blocks].copy_(self.bt_host[:n, :max_blocks], non_blocking=True)
         g = self.graphs.get(bk)
@@ -346,7 +353,7 @@ class ModelRunner:
 
     def stage_decode_padding(self, n: int) -> None:
         """Mark rows n..bucket as padding (no KV write, empty context)."""
-        bk = self.bucket(n) if (self.use_cuda_graphs or self.row_align > 1) else n
+        bk = self.bucket(n) if (self.use_cuda_graphs or self.row_align > 1) else max(n, 1)
         mb = self.max_batch
         mh = self.meta_host
         if bk > n:

@@ -24,6 +24,8 @@ def _lib() -> ctypes.CDLL:
         lib.rb_rope_kv_append.argtypes = [c_vp] * 9 + [c_float, c_int, c_int, c_int, c_int, c_int, c_ll, c_int, c_vp, c_vp]
         lib.rb_swiglu.argtypes = [c_vp, c_vp, c_ll, c_int, c_vp]
         lib.rb_swiglu_bwd.argtypes = [c_vp, c_vp, c_vp, c_ll, c_int, c_vp]
+        lib.rb_swiglu_bounded.argtypes = [c_vp, c_vp, c_ll, c_int, c_vp, c_vp]
+        lib.rb_swiglu_bounded.restype = c_int
         lib.rb_embedding.argtypes = [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp]
         lib.rb_transpose_bf16.argtypes = [c_vp, c_vp, c_int, c_int, c_vp]
         for f in ("rb_rmsnorm", "rb_rope_kv_append", "rb_swiglu", "rb_swiglu_bwd", "rb_embedding", "rb_transpose_bf16"):
@@ -131,8 +133,9 @@ def swiglu_reference(gu: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.silu(g) * u
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``silu(gate) * up`` for ``gu = [gate | up]`` of shape ``[T, 2F]``."""
+def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None, rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gu = [gate | up]`` of shape ``[T, 2F]``. ``rows_dev`` (an int32 element on the
+    device) caps the number of rows processed at run time; rows beyond it are left untouched."""
     if not gu.is_cuda:
         res = swiglu_reference(gu)
         if out is not None:
@@ -144,7 +147,11 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     assert gu.is_contiguous()
     if out is None:
         out = torch.empty(*gu.shape[:-1], F, dtype=gu.dtype, device=gu.device)
-    rc = _lib().rb_swiglu(ptr(gu), ptr(out), T, F, stream_handle(gu.device))
+    if rows_dev is not None:
+        assert rows_dev.dtype == torch.int32 and rows_dev.is_cuda
+        rc = _lib().rb_swiglu_bounded(ptr(gu), ptr(out), T, F, rows_dev.data_ptr(), stream_handle(gu.device))
+    else:
+        rc = _lib().rb_swiglu(ptr(gu), ptr(out), T, F, stream_handle(gu.device))
     check_rc(rc, "rb_swiglu")
     return out
 

@@ -1,0 +1,43 @@
+"""Expert-parallel serving context: data-parallel attention, expert-parallel MoE, engines in lock step.
+
+Every rank runs a whole engine of its own (scheduler, KV cache, attention and dense weights) on its own
+requests; only the experts are split over the ranks. The MoE layers' dispatch and combine are collectives
+(peer stores plus device barriers, ``parallel/moe.py``), so every rank has to run the same number of MoE
+forwards in the same order. ``agree`` is the control plane for that: before each step the ranks exchange what
+they are about to run (a MAX all-reduce of a few flags on a CPU-side group) and a rank with nothing of its own
+runs an idle pass, which feeds the MoE layers a padding batch.
+
+The reference serves MoE models through external engines only (rollouts/inference/backends.py:1-60 starts
+SGLang / vLLM servers); this is the in-tree equivalent of their ``--dp --enable-dp-attention --ep`` mode.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .symm import PeerComm
+
+
+class ExpertParallel:
+    def __init__(self, comm: PeerComm, cpu_group=None):
+        self.comm = comm
+        self.rank, self.world = comm.rank, comm.world
+        if cpu_group is None and self.world > 1:
+            # agreement travels over a host-side group so that it never queues behind device work
+            cpu_group = dist.new_group(backend="gloo") if comm.on_gpu else comm.group
+        self.cpu_group = cpu_group
+        self._buf = torch.zeros(4, dtype=torch.int32)
+        self.agreements = 0
+
+    def agree(self, *flags: int) -> tuple[int, ...]:
+        """Element-wise maximum of up to four small integers over the ranks."""
+        assert len(flags) <= 4
+        if self.world == 1:
+            return tuple(int(f) for f in flags)
+        self._buf.zero_()
+        for i, f in enumerate(flags):
+            self._buf[i] = int(f)
+        dist.all_reduce(self._buf, op=dist.ReduceOp.MAX, group=self.cpu_group)
+        self.agreements += 1
+        return tuple(int(v) for v in self._buf[:len(flags)])

@@ -42,7 +42,8 @@ def _lib():
         lib.rb_moe_permute.argtypes = [_VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _VP, PP, PP, _I, _VP, _VP]
         lib.rb_moe_translate.argtypes = [_VP, _I, PP, _I, _I, _VP]
         lib.rb_moe_combine.argtypes = [_VP, _VP, _I, _I, _I, _VP, _I, _VP]
-        for f in ("rb_moe_route", "rb_moe_count", "rb_moe_plan", "rb_moe_permute", "rb_moe_translate", "rb_moe_combine"):
+        lib.rb_moe_publish_counts.argtypes = [_VP, PP, _I, _I, _I, _VP]
+        for f in ("rb_moe_publish_counts", "rb_moe_route", "rb_moe_count", "rb_moe_plan", "rb_moe_permute", "rb_moe_translate", "rb_moe_combine"):
             getattr(lib, f).restype = _I
         lib._rb_typed = True
     return lib
@@ -65,12 +66,74 @@ def route_reference(logits: torch.Tensor, k: int, sigmoid: bool, bias, norm_topk
     return idx.to(torch.int32), (w * scaling).float()
 
 
+class MoEScratch:
+    """Routing tables, dispatch / receive buffers and tile tables of the MoE forward. One object can serve every MoE
+    layer of a model (the three device barriers of a layer order its reuse by the next one). With ``fixed=True`` it is
+    sized once for ``capacity`` tokens and never reallocated, which CUDA graphs (captured pointers) and expert
+    parallelism (allocation is a collective) both need."""
+
+    BN_GU, BN_DN = 128, 128
+
+    def __init__(self, cfg: ModelConfig, device: torch.device, ep=None, capacity: int = 0, fixed: bool = True):
+        self.cfg, self.device, self.ep = cfg, device, ep
+        self.world = ep.world if ep is not None else 1
+        self.fixed = fixed
+        self._scratch_for = 0
+        if fixed:
+            self._alloc(max(capacity, 256))
+
+    def ensure(self, T: int) -> None:
+        if T <= self._scratch_for:
+            return
+        assert not self.fixed, f"MoE scratch sized for {self._scratch_for} tokens, got {T}"
+        self._alloc(max(T, 256))
+
+    def _alloc(self, Tcap: int) -> None:
+        cfg = self.cfg
+        dev, k, d, F, E = self.device, cfg.num_experts_per_tok, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
+        EL = E // self.world
+        cap = Tcap * k * (1 if self.world == 1 else min(self.world, 4))
+        self.cap = cap
+        self.logits = torch.empty(Tcap, E, dtype=torch.float32, device=dev)
+        self.idx = torch.empty(Tcap, k, dtype=torch.int32, device=dev)
+        self.w = torch.empty(Tcap, k, dtype=torch.float32, device=dev)
+        self.cursor = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.local_counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        alloc = (lambda shape, dt: self.ep.comm.alloc(shape, dt, zero=True)) if self.ep is not None else None
+        if alloc is None:
+            self.counts_all = torch.zeros(1, E, dtype=torch.int32, device=dev)
+            self.xp = torch.empty(cap, d, dtype=torch.bfloat16, device=dev)
+            self.ret = torch.zeros(cap, dtype=torch.int64, device=dev)
+            self.y = torch.empty(Tcap * k, d, dtype=torch.bfloat16, device=dev)
+            self.xp_ptrs, self.ret_ptrs, self.y_ptrs = [self.xp.data_ptr()], [self.ret.data_ptr()], [self.y.data_ptr()]
+            self.counts_ptrs = None
+        else:
+            c = alloc((self.world, E), torch.int32)
+            xp, ret, y = alloc((cap, d), torch.bfloat16), alloc((cap,), torch.int64), alloc((Tcap * k, d), torch.bfloat16)
+            self.counts_all, self.xp, self.ret, self.y = c.local, xp.local, ret.local, y.local
+            self.xp_ptrs, self.ret_ptrs, self.y_ptrs = xp.peer_ptrs, ret.peer_ptrs, y.peer_ptrs
+            self.counts_ptrs = c.peer_ptrs
+            self._symm = (c, xp, ret, y)         # keeps the rendezvous handles alive
+            if not hasattr(self, "_barrier_slot"):
+                self._barrier_slot = self.ep.comm.new_slot()
+            self.ep.comm.barrier_host()
+        self.gu = torch.empty(cap, 2 * F, dtype=torch.bfloat16, device=dev)
+        self.act = torch.empty(cap, F, dtype=torch.bfloat16, device=dev)
+        self.max_tiles = (cap // 128 + EL + 1) * max(-(-2 * F // self.BN_GU), -(-d // self.BN_DN))
+        self.tiles_gu = torch.zeros(self.max_tiles, 4, dtype=torch.int32, device=dev)
+        self.tiles_dn = torch.zeros(self.max_tiles, 4, dtype=torch.int32, device=dev)
+        self.ntiles = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.expert_offset = torch.zeros(EL + 1, dtype=torch.int32, device=dev)
+        self._scratch_for = Tcap
+
+
 class MoELayerWeights:
     """Weights and scratch of one MoE layer; ``forward(h, x)`` does ``x += MoE(h)`` in place."""
 
     BN_GU, BN_DN = 128, 128
 
-    def __init__(self, cfg: ModelConfig, device: torch.device, ep=None, max_tokens: int = 16384):
+    def __init__(self, cfg: ModelConfig, device: torch.device, ep=None, scratch: "MoEScratch | None" = None):
+        self.scratch = scratch if device.type == "cuda" else None
         self.cfg = cfg
         self.device = device
         self.ep = ep                      # TensorParallel context used as the expert-parallel group, or None
@@ -90,8 +153,6 @@ class MoELayerWeights:
         if cfg.n_shared_experts > 0:
             Fs = F * cfg.n_shared_experts
             self.shared = (torch.empty(2 * Fs, d, dtype=dt, device=device), torch.empty(d, Fs, dtype=dt, device=device))
-        self.max_tokens = max_tokens
-        self._scratch_for = 0
         self._on_gpu = on_gpu
 
     # ---------------------------------------------------------------- weights
@@ -133,41 +194,16 @@ class MoELayerWeights:
 
     # ---------------------------------------------------------------- scratch
     def _ensure_scratch(self, T: int) -> None:
-        if T <= self._scratch_for:
-            return
-        Tcap = max(T, 256)
-        dev, k, d, F, E = self.device, self.k, self.d, self.F, self.E
-        cap = Tcap * k * (1 if self.world == 1 else min(self.world, 4))
-        self.cap = cap
-        self.logits = torch.empty(Tcap, E, dtype=torch.float32, device=dev)
-        self.idx = torch.empty(Tcap, k, dtype=torch.int32, device=dev)
-        self.w = torch.empty(Tcap, k, dtype=torch.float32, device=dev)
-        self.cursor = torch.zeros(E, dtype=torch.int32, device=dev)
-        self.local_counts = torch.zeros(E, dtype=torch.int32, device=dev)
-        alloc = (lambda shape, dt: self.ep.comm.alloc(shape, dt, zero=True)) if self.ep is not None else None
-        if alloc is None:
-            self.counts_all = torch.zeros(1, E, dtype=torch.int32, device=dev)
-            self.xp = torch.empty(cap, d, dtype=torch.bfloat16, device=dev)
-            self.ret = torch.zeros(cap, dtype=torch.int64, device=dev)
-            self.y = torch.empty(Tcap * k, d, dtype=torch.bfloat16, device=dev)
-            self.xp_ptrs, self.ret_ptrs, self.y_ptrs = [self.xp.data_ptr()], [self.ret.data_ptr()], [self.y.data_ptr()]
-            self.counts_peers = None
-        else:
-            c = alloc((self.world, E), torch.int32)
-            xp, ret, y = alloc((cap, d), torch.bfloat16), alloc((cap,), torch.int64), alloc((Tcap * k, d), torch.bfloat16)
-            self.counts_all, self.xp, self.ret, self.y = c.local, xp.local, ret.local, y.local
-            self.xp_ptrs, self.ret_ptrs, self.y_ptrs = xp.peer_ptrs, ret.peer_ptrs, y.peer_ptrs
-            self.counts_peers = [c.peer_tensor(r) for r in range(self.world)]
-            self._barrier_slot = self.ep.comm.new_slot()
-            self.ep.comm.barrier_host()
-        self.gu = torch.empty(cap, 2 * F, dtype=torch.bfloat16, device=dev)
-        self.act = torch.empty(cap, F, dtype=torch.bfloat16, device=dev)
-        self.max_tiles = (cap // 128 + self.EL + 1) * max(-(-2 * F // self.BN_GU), -(-d // self.BN_DN))
-        self.tiles_gu = torch.zeros(self.max_tiles, 4, dtype=torch.int32, device=dev)
-        self.tiles_dn = torch.zeros(self.max_tiles, 4, dtype=torch.int32, device=dev)
-        self.ntiles = torch.zeros(2, dtype=torch.int32, device=dev)
-        self.expert_offset = torch.zeros(self.EL + 1, dtype=torch.int32, device=dev)
-        self._scratch_for = Tcap
+        if self.scratch is None:
+            self.scratch = MoEScratch(self.cfg, self.device, self.ep, fixed=False)
+        self.scratch.ensure(T)
+
+    def __getattr__(self, name):
+        # routing tables, receive buffers and tile tables live in the (possibly shared) scratch object
+        sc = self.__dict__.get("scratch")
+        if sc is not None and name in sc.__dict__:
+            return sc.__dict__[name]
+        raise AttributeError(name)
 
     # ---------------------------------------------------------------- forward
     def forward(self, h: torch.Tensor, x: torch.Tensor) -> None:
@@ -189,11 +225,11 @@ class MoELayerWeights:
         self.local_counts.zero_()
         self.cursor.zero_()
         check_rc(lib.rb_moe_count(self.idx.data_ptr(), T * k, E, self.local_counts.data_ptr(), s), "rb_moe_count")
-        if self.counts_peers is None:
+        if self.counts_ptrs is None:
             self.counts_all[0].copy_(self.local_counts)
-        else:
-            for r in range(self.world):           # publish my counts row on every rank
-                self.counts_peers[r][self.rank].copy_(self.local_counts)
+        else:                                     # one kernel stores my counts row on every rank
+            check_rc(lib.rb_moe_publish_counts(self.local_counts.data_ptr(), ptr_array(self.counts_ptrs), self.rank,
+                                               self.world, E, s), "rb_moe_publish_counts")
             self.ep.comm.barrier(self._barrier_slot)
         check_rc(lib.rb_moe_plan(self.counts_all.data_ptr(), self.world, E, self.e_lo, self.e_lo + self.EL,
                                  self.expert_offset.data_ptr(), 2 * F, self.BN_GU, self.tiles_gu.data_ptr(),
@@ -202,14 +238,16 @@ class MoELayerWeights:
         check_rc(lib.rb_moe_permute(h.data_ptr(), self.idx.data_ptr(), T, k, d, E, self.world, self.rank,
                                     self.counts_all.data_ptr(), self.cursor.data_ptr(), ptr_array(self.xp_ptrs),
                                     ptr_array(self.ret_ptrs), self.cap, st, s), "rb_moe_permute")
-        if self.counts_peers is not None:
+        if self.counts_ptrs is not None:
             self.ep.comm.barrier(self._barrier_slot)   # every routed row has landed on its owner
         check_rc(lib.rb_moe_translate(self.ret.data_ptr(), self.cap, ptr_array(self.y_ptrs), self.world, d, s), "rb_moe_translate")
         self._grouped(self.xp, self.wgu, self.gu, 2 * F, d, self.BN_GU, self.tiles_gu, self.ntiles.data_ptr(), None)
-        rows = self.cap if self.world > 1 else T * k
-        ops.swiglu(self.gu[:rows], out=self.act[:rows])
+        if self.world > 1:   # only the device knows how many rows arrived: expert_offset[EL] bounds the pass
+            ops.swiglu(self.gu, out=self.act, rows_dev=self.expert_offset[self.EL:])
+        else:
+            ops.swiglu(self.gu[:T * k], out=self.act[:T * k])
         self._grouped(self.act, self.wd, None, d, F, self.BN_DN, self.tiles_dn, self.ntiles.data_ptr() + 4, self.ret)
-        if self.counts_peers is not None:
+        if self.counts_ptrs is not None:
             self.ep.comm.barrier(self._barrier_slot)   # every result row is home
         check_rc(lib.rb_moe_combine(self.y.data_ptr(), self.w.data_ptr(), T, k, d, x.data_ptr(), 1, s), "rb_moe_combine")
         if self.shared is not None:
@@ -242,16 +280,27 @@ class MoELayerWeights:
                                  cfg.norm_topk_prob, cfg.routed_scaling_factor)
         if self.world > 1:
             # every rank evaluates its own experts for everyone's tokens, then the sums are exchanged
-            hs = [torch.empty_like(hf) for _ in range(self.world)]
-            ids = [torch.empty_like(idx) for _ in range(self.world)]
-            ws = [torch.empty_like(w) for _ in range(self.world)]
-            dist.all_gather(hs, hf, group=self.ep.comm.group)
-            dist.all_gather(ids, idx, group=self.ep.comm.group)
-            dist.all_gather(ws, w, group=self.ep.comm.group)
+            g = self.ep.comm.group
+            n_all = [torch.zeros(1, dtype=torch.int64) for _ in range(self.world)]
+            dist.all_gather(n_all, torch.tensor([hf.shape[0]]), group=g)
+            Tm = int(max(int(n) for n in n_all))            # ranks may hold different token counts: pad to the largest
+
+            def padded(t, fill):
+                out = torch.full((Tm,) + tuple(t.shape[1:]), fill, dtype=t.dtype)
+                out[:t.shape[0]] = t
+                return out
+
+            hp, ip, wp = padded(hf, 0.0), padded(idx, -1), padded(w, 0.0)
+            hs = [torch.empty_like(hp) for _ in range(self.world)]
+            ids = [torch.empty_like(ip) for _ in range(self.world)]
+            ws = [torch.empty_like(wp) for _ in range(self.world)]
+            dist.all_gather(hs, hp, group=g)
+            dist.all_gather(ids, ip, group=g)
+            dist.all_gather(ws, wp, group=g)
             outs = [self._experts_reference(a, b, c) for a, b, c in zip(hs, ids, ws)]
             tot = torch.stack(outs)
-            dist.all_reduce(tot, group=self.ep.comm.group)
-            out = tot[self.rank]
+            dist.all_reduce(tot, group=g)
+            out = tot[self.rank][:hf.shape[0]]
         else:
             out = self._experts_reference(hf, idx, w)
         if self.shared is not None:

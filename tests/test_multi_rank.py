@@ -56,3 +56,27 @@ def test_lockstep_tp_serving_two_ranks():
            "--master-port", str(_free_port()), os.path.join(HERE, "lockstep_worker.py")]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert proc.returncode == 0 and "LOCKSTEP_OK" in proc.stdout, proc.stdout[-1500:] + proc.stderr[-3000:]
+
+
+def test_expert_parallel_engines_lockstep_two_ranks():
+    """Two engines with split experts serve different request mixes and stay paired (gloo, CPU)."""
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "ep_engine_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode == 0 and proc.stdout.count("EP_ENGINE_OK") == 2, proc.stdout[-1500:] + proc.stderr[-3000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("flags", [["--cuda"], ["--cuda", "--graphs"]])
+def test_expert_parallel_engines_gpu(flags):
+    """The same lock-step check with the peer-memory dispatch / combine kernels, eager and inside CUDA graphs."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "ep_engine_worker.py"), *flags]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode == 0 and proc.stdout.count("EP_ENGINE_OK") == 2, proc.stdout[-1500:] + proc.stderr[-3000:]
