@@ -166,13 +166,27 @@ __global__ void moe_publish_counts_kernel(const int* __restrict__ counts, PeerPt
   for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = counts[i];
 }
 
+// Where this rank's rows for expert e start in the owner's expert-ordered receive buffer: the rows of the owner's
+// lower experts (from all ranks) plus the rows of lower source ranks for e. Written to cursor[E + e].
+__global__ void moe_send_base_kernel(const int* __restrict__ counts_all, int world, int E, int rank, int* __restrict__ cursor) {
+  const int epr = E / world;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int owner = e / epr;
+    int off = 0;
+    for (int ee = owner * epr; ee < e; ++ee)
+      for (int r = 0; r < world; ++r) off += counts_all[r * E + ee];
+    for (int r = 0; r < rank; ++r) off += counts_all[r * E + e];
+    cursor[E + e] = off;
+  }
+}
+
 // Dispatch: row (t, j) goes to the owner of its expert. Position inside the owner's
 // expert-ordered buffer = expert block offset on the owner + rows from lower source ranks +
 // a running cursor for this (source, expert). ret_addr records where the result row must be
 // written (this rank's y buffer, slot t*k+j), as seen from the owner.
 __global__ void moe_permute_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx, int T, int k,
                                    int d, int E, int world, int rank, const int* __restrict__ counts_all,
-                                   int* __restrict__ cursor /*[E]*/, PeerPtrs xp /*[cap, d] per rank*/,
+                                   int* __restrict__ cursor /*[2E]: running index | send base*/, PeerPtrs xp /*[cap, d] per rank*/,
                                    PeerPtrs ret_code /*u64[cap] per rank*/, int cap, int* status) {
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -183,14 +197,7 @@ __global__ void moe_permute_kernel(const __nv_bfloat16* __restrict__ x, const in
   const int epr = E / world;
   const int owner = e / epr;
   int pos = 0;
-  if (lane == 0) {
-    // block offset of expert e on its owner
-    int off = 0;
-    for (int ee = owner * epr; ee < e; ++ee)
-      for (int r = 0; r < world; ++r) off += counts_all[r * E + ee];
-    for (int r = 0; r < rank; ++r) off += counts_all[r * E + e];
-    pos = off + atomicAdd(&cursor[e], 1);
-  }
+  if (lane == 0) pos = cursor[E + e] + atomicAdd(&cursor[e], 1);   // base of (this rank, e) on the owner + running index
   pos = __shfl_sync(0xffffffffu, pos, 0);
   if (pos >= cap) { set_status(status, ST_BAD_INDEX); return; }
   const uint4* src = reinterpret_cast<const uint4*>(x + (long long)t * d);
@@ -294,6 +301,7 @@ extern "C" int rb_moe_permute(const void* x, const int* topk_idx, int T, int k, 
   if (T <= 0) return 0;
   if (d % 8 != 0 || E % world != 0) return -1;
   const long long warps = (long long)T * k;
+  moe_send_base_kernel<<<1, 256, 0, s>>>(counts_all, world, E, rank, cursor);
   moe_permute_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)x, topk_idx, T, k, d, E, world, rank,
                                                                 counts_all, cursor, mk(xp_ptrs, world), mk(ret_ptrs, world),
                                                                 cap, status);

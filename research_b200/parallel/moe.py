@@ -97,7 +97,7 @@ class MoEScratch:
         self.logits = torch.empty(Tcap, E, dtype=torch.float32, device=dev)
         self.idx = torch.empty(Tcap, k, dtype=torch.int32, device=dev)
         self.w = torch.empty(Tcap, k, dtype=torch.float32, device=dev)
-        self.cursor = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.cursor = torch.zeros(2 * E, dtype=torch.int32, device=dev)   # running index | dispatch base per expert
         self.local_counts = torch.zeros(E, dtype=torch.int32, device=dev)
         alloc = (lambda shape, dt: self.ep.comm.alloc(shape, dt, zero=True)) if self.ep is not None else None
         if alloc is None:
