@@ -9,7 +9,8 @@ import uuid
 from dataclasses import replace
 from typing import Any
 
-from ..dtypes import (Actor, ChatCompletion, Choice, Cost, Message, RunConfig, TextDelta, ToolCall, Usage)
+from ..dtypes import (Actor, ChatCompletion, Choice, Cost, Message, RunConfig, TextDelta, ToolCall, ToolCallEnd, ToolCallStart,
+                      Usage)
 from .base import NonRetryableError, async_retry, classify_http_status
 from .models import estimate_cost
 from .tool_parsers import parse_tool_calls
@@ -87,5 +88,9 @@ class ScriptedLLM:
             msg = Message("assistant", text, tool_calls=tuple(calls))
         if run_config.on_chunk is not None and msg.text():
             await run_config.on_chunk(TextDelta(delta=msg.text()))
+        if run_config.on_chunk is not None:
+            for c in msg.get_tool_calls():      # the same events a streaming provider emits per call
+                await run_config.on_chunk(ToolCallStart(tool_call_id=c.id, name=c.name))
+                await run_config.on_chunk(ToolCallEnd(tool_call_id=c.id, name=c.name, args=dict(c.args)))
         comp = ChatCompletion(f"mock_{self.calls}", "scripted", (Choice(0, msg),), Usage(1, 1, cost=Cost()))
         return replace(actor, trajectory=actor.trajectory.append(msg).with_completion(comp))

@@ -114,44 +114,24 @@ def cmd_serve(args) -> int:
 
 
 async def _chat(args) -> int:
-    from .agents.agents import resume_session, run_agent
-    from .agents.dtypes import Actor, AgentState, Message, RunConfig, TextDelta, Trajectory
+    from .agents.agents import resume_session
     from .agents.presets import get_preset
+    from .frontend.terminal import InteractiveRunner, make_frontend
 
     preset, store, ep = get_preset(args.preset), _store(args), _endpoint(args)
-
-    async def on_chunk(ev):
-        if isinstance(ev, TextDelta):
-            print(ev.delta, end="", flush=True)
-
-    async def confirm(call, state, rc):
-        return args.yes or input(f"\nrun {call.name}({json.dumps(call.args)[:200]})? [y/N] ").strip().lower() == "y"
-
-    rc = RunConfig(on_chunk=on_chunk, confirm_tool=confirm, session_store=store)
+    frontend = make_frontend(args.frontend, auto_confirm=args.yes)
+    trajectory = session_id = None
     if args.session:
         state = await resume_session(args.session, store, ep, type(preset.environment(args.cwd)), preset.max_turns)
+        env, trajectory, session_id = state.environment, state.actor.trajectory, state.session_id
     else:
         env = preset.environment(args.cwd)
         if hasattr(env, "on_session_start"):
             await env.on_session_start(f"cli-{os.getpid()}")
-        state = AgentState(Actor(Trajectory((Message("system", preset.system_prompt),)), ep), env, max_turns=preset.max_turns)
-    prompt = args.prompt
-    while True:
-        if prompt is None:
-            try:
-                prompt = input("\n> ").strip()
-            except EOFError:
-                break
-        if not prompt or prompt in ("/exit", "/quit"):
-            break
-        traj = state.actor.trajectory.append(Message("user", prompt))
-        state = AgentState(Actor(traj, ep), state.environment, max_turns=state.turn_idx + preset.max_turns,
-                           turn_idx=state.turn_idx, session_id=state.session_id)
-        state = (await run_agent(state, rc))[-1]
-        print()
-        if args.prompt is not None:
-            break
-        prompt = None
+    runner = InteractiveRunner(ep, frontend, environment=env, system_prompt=preset.system_prompt, session_store=store,
+                               session_id=session_id, max_turns=preset.max_turns, initial_prompt=args.prompt,
+                               single_turn=args.prompt is not None, trajectory=trajectory)
+    state = await runner.run()
     if state.session_id:
         print(f"session: {state.session_id}", file=sys.stderr)
     return 0
@@ -226,6 +206,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--preset", default="chat"); p.add_argument("--cwd", default="."); p.add_argument("--store", default="")
     p.add_argument("--session", default="", help="resume this session"); p.add_argument("-p", "--prompt", default=None)
     p.add_argument("-y", "--yes", action="store_true", help="run tools without asking")
+    p.add_argument("--frontend", default="auto", choices=["auto", "plain", "json", "ansi"], help="terminal front end")
     p.set_defaults(fn=cmd_chat)
     p = sub.add_parser("sessions")
     p.add_argument("action", choices=["list", "show", "export", "slice", "import"]); p.add_argument("id", nargs="?")

@@ -1,0 +1,499 @@
+"""Terminal front ends for the interactive agent and the loop that drives them.
+
+The agent loop emits ``StreamEvent`` objects; a front end renders them and supplies user input and
+tool confirmations (rollouts/frontends/protocol.py:19-158). Three implementations:
+
+* ``PlainFrontend`` - line-oriented stdout/stdin, no escape codes (pipes, logs);
+* ``JsonFrontend`` - one JSON object per event on stdout, input lines from stdin, for driving the agent
+  from another process (rollouts/frontends/json_frontend.py, headless_json.py);
+* ``AnsiFrontend`` - a terminal UI drawn with ANSI escape codes only (no curses, no external toolkit):
+  coloured roles, dimmed reasoning, boxed tool calls with truncated results, fenced-code highlighting,
+  a spinner while the model is thinking and a status line with model / turn / token counts
+  (the roles of rollouts/frontends/tui_frontend.py and tui/agent_renderer.py).
+
+``InteractiveRunner`` is the front-end-agnostic chat loop (rollouts/frontends/runner.py:117): read a line,
+handle slash commands, run the agent until it stops, persist to the session store, repeat.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import itertools
+import json
+import shutil
+import sys
+import time
+from dataclasses import asdict, replace
+from typing import Any, Callable, Protocol, TextIO, runtime_checkable
+
+from ..agents.agents import run_agent
+from ..agents.dtypes import (Actor, AgentState, Endpoint, Message, RunConfig, StopReason, StreamDone, StreamError,
+                             StreamEvent, TextDelta, ThinkingDelta, ToolCall, ToolCallEnd, ToolCallStart,
+                             ToolResultReceived, Trajectory)
+
+
+@runtime_checkable
+class Frontend(Protocol):
+    async def start(self) -> None: ...
+    async def stop(self) -> None: ...
+    async def handle_event(self, event: StreamEvent) -> None: ...
+    async def get_input(self, prompt: str = "") -> str: ...
+    async def confirm_tool(self, tool_call: ToolCall) -> bool: ...
+    def show_loader(self, text: str) -> None: ...
+    def hide_loader(self) -> None: ...
+    def set_status(self, **fields: Any) -> None: ...
+
+
+async def _readline(stream: TextIO) -> str:
+    line = await asyncio.get_running_loop().run_in_executor(None, stream.readline)
+    if line == "":
+        raise EOFError
+    return line.rstrip("\n")
+
+
+class PlainFrontend:
+    """Unadorned text on ``out``; input lines from ``inp``."""
+
+    def __init__(self, out: TextIO | None = None, inp: TextIO | None = None, show_thinking: bool = False,
+                 auto_confirm: bool = True):
+        self.out, self.inp = out or sys.stdout, inp or sys.stdin
+        self.show_thinking, self.auto_confirm = show_thinking, auto_confirm
+        self._mid_line = False
+        self.status: dict[str, Any] = {}
+
+    def _w(self, s: str) -> None:
+        self.out.write(s)
+        self.out.flush()
+        if s:
+            self._mid_line = not s.endswith("\n")
+
+    def _fresh_line(self) -> None:
+        if self._mid_line:
+            self._w("\n")
+
+    async def start(self) -> None: ...
+
+    async def stop(self) -> None:
+        self._fresh_line()
+
+    async def handle_event(self, event: StreamEvent) -> None:
+        if isinstance(event, TextDelta):
+            self._w(event.delta)
+        elif isinstance(event, ThinkingDelta):
+            if self.show_thinking:
+                self._w(event.delta)
+        elif isinstance(event, ToolCallEnd):
+            self._fresh_line()
+            self._w(f"[tool] {event.name}({json.dumps(event.args, ensure_ascii=False)})\n")
+        elif isinstance(event, ToolResultReceived):
+            self._fresh_line()
+            tag = "error" if event.is_error else "result"
+            self._w(f"[{tag}] {_truncate(event.content, 2000)}\n")
+        elif isinstance(event, StreamError):
+            self._fresh_line()
+            self._w(f"[error] {event.error}\n")
+        elif isinstance(event, StreamDone):
+            self._fresh_line()
+
+    async def get_input(self, prompt: str = "") -> str:
+        self._fresh_line()
+        self._w(prompt)
+        return await _readline(self.inp)
+
+    async def confirm_tool(self, tool_call: ToolCall) -> bool:
+        if self.auto_confirm:
+            return True
+        ans = await self.get_input(f"run {tool_call.name}({json.dumps(tool_call.args, ensure_ascii=False)})? [y/N] ")
+        return ans.strip().lower() in ("y", "yes")
+
+    def show_loader(self, text: str) -> None: ...
+
+    def hide_loader(self) -> None: ...
+
+    def set_status(self, **fields: Any) -> None:
+        self.status.update(fields)
+
+
+class JsonFrontend(PlainFrontend):
+    """Newline-delimited JSON: every event is ``{"type": ..., ...}``; requests for input are events too
+    (``input_request`` / ``confirm_request``) and are answered by one line on ``inp``."""
+
+    def _emit(self, obj: dict[str, Any]) -> None:
+        self.out.write(json.dumps(obj, ensure_ascii=False, default=str) + "\n")
+        self.out.flush()
+
+    async def start(self) -> None:
+        self._emit({"type": "start", "timestamp": time.time()})
+
+    async def stop(self) -> None:
+        self._emit({"type": "stop", "timestamp": time.time(), **{k: v for k, v in self.status.items()}})
+
+    async def handle_event(self, event: StreamEvent) -> None:
+        self._emit(asdict(event))
+
+    async def get_input(self, prompt: str = "") -> str:
+        self._emit({"type": "input_request", "prompt": prompt})
+        line = await _readline(self.inp)
+        try:                      # either a bare line or {"text": "..."}
+            obj = json.loads(line)
+            if isinstance(obj, dict) and "text" in obj:
+                return str(obj["text"])
+        except ValueError:
+            pass
+        return line
+
+    async def confirm_tool(self, tool_call: ToolCall) -> bool:
+        if self.auto_confirm:
+            return True
+        self._emit({"type": "confirm_request", "tool": tool_call.name, "args": tool_call.args, "id": tool_call.id})
+        return (await _readline(self.inp)).strip().lower() in ("y", "yes", "true", '{"ok": true}')
+
+    def show_loader(self, text: str) -> None:
+        self._emit({"type": "loader", "text": text})
+
+
+# ------------------------------------------------------------------------------------------ ANSI rendering
+class Theme:
+    RESET, BOLD, DIM, ITALIC = "\x1b[0m", "\x1b[1m", "\x1b[2m", "\x1b[3m"
+    USER, ASSISTANT, TOOL, ERROR, CODE, STATUS = "\x1b[36m", "\x1b[0m", "\x1b[33m", "\x1b[31m", "\x1b[32m", "\x1b[7m"
+    CLEAR_LINE, HIDE_CURSOR, SHOW_CURSOR = "\r\x1b[2K", "\x1b[?25l", "\x1b[?25h"
+
+
+def _truncate(text: str, limit: int) -> str:
+    return text if len(text) <= limit else text[:limit] + f"... (+{len(text) - limit} chars)"
+
+
+def truncate_lines(text: str, max_lines: int, width: int) -> list[str]:
+    """First ``max_lines`` display lines of ``text`` (long lines cut to ``width``) and a count of what was dropped."""
+    lines = text.splitlines() or [""]
+    shown = [ln if len(ln) <= width else ln[:max(width - 1, 1)] + "…" for ln in lines[:max_lines]]
+    if len(lines) > max_lines:
+        shown.append(f"… {len(lines) - max_lines} more lines")
+    return shown
+
+
+def box(title: str, body_lines: list[str], width: int, color: str = "") -> str:
+    """A one-line-border box around ``body_lines``; ``width`` is the total width in columns."""
+    inner = max(width - 4, 8)
+    top = f"┌─ {title[:inner - 2]} " + "─" * max(inner - len(title[:inner - 2]) - 1, 0) + "┐"
+    rows = [f"│ {ln[:inner].ljust(inner)} │" for ln in body_lines]
+    bottom = "└" + "─" * (inner + 2) + "┘"
+    reset = Theme.RESET if color else ""
+    return "\n".join(f"{color}{r}{reset}" for r in [top, *rows, bottom])
+
+
+class FenceHighlighter:
+    """Streaming colouriser for Markdown code fences: text arrives in arbitrary pieces, lines inside a
+    ``` fence are coloured, everything else passes through. Partial lines are emitted at once (the colour
+    state only changes at line starts), so streaming stays character-granular."""
+
+    def __init__(self, code_color: str = Theme.CODE, reset: str = Theme.RESET):
+        self.code_color, self.reset = code_color, reset
+        self.in_code = False
+        self._line = ""          # the current (unfinished) line as seen so far
+
+    def feed(self, piece: str) -> str:
+        out = []
+        for ch in piece:
+            at_start = self._line == ""
+            self._line += ch
+            if ch == "\n":
+                if self._line.lstrip().startswith("```"):
+                    self.in_code = not self.in_code
+                    out.append(self.reset if not self.in_code else "")
+                self._line = ""
+                out.append(ch)
+                continue
+            if at_start and self.in_code:
+                out.append(self.code_color)
+            out.append(ch)
+        return "".join(out)
+
+
+class AnsiFrontend(PlainFrontend):
+    """Escape-code terminal UI. All drawing goes through ``_w`` so tests can capture it from ``out``."""
+
+    SPIN = "⠋⠙⠹⠸⠼⠴⠦⠧⠇⠏"
+
+    def __init__(self, out: TextIO | None = None, inp: TextIO | None = None, show_thinking: bool = True,
+                 auto_confirm: bool = False, width: int | None = None, max_result_lines: int = 12):
+        super().__init__(out, inp, show_thinking, auto_confirm)
+        self.width = width or shutil.get_terminal_size((100, 24)).columns
+        self.max_result_lines = max_result_lines
+        self._fence = FenceHighlighter()
+        self._loader_task: asyncio.Task | None = None
+        self._loader_text = ""
+        self._mode = ""           # "", "text", "thinking"
+        self._t_stream = 0.0
+        self._chars = 0
+
+    async def start(self) -> None:
+        self._w(f"{Theme.BOLD}research_b200 chat{Theme.RESET}  {Theme.DIM}/help for commands, ctrl-d to quit{Theme.RESET}\n")
+
+    async def stop(self) -> None:
+        self.hide_loader()
+        self._fresh_line()
+        self._w(Theme.SHOW_CURSOR + Theme.RESET)
+
+    # ---- loader / status
+    def show_loader(self, text: str) -> None:
+        self.hide_loader()
+        self._loader_text = text
+        try:
+            loop = asyncio.get_running_loop()
+        except RuntimeError:
+            return
+        self._loader_task = loop.create_task(self._spin())
+
+    async def _spin(self) -> None:
+        t0 = time.monotonic()
+        try:
+            for frame in itertools.cycle(self.SPIN):
+                self.out.write(f"{Theme.CLEAR_LINE}{Theme.DIM}{frame} {self._loader_text} {time.monotonic() - t0:4.1f}s{Theme.RESET}")
+                self.out.flush()
+                await asyncio.sleep(0.08)
+        except asyncio.CancelledError:
+            self.out.write(Theme.CLEAR_LINE)
+            self.out.flush()
+
+    def hide_loader(self) -> None:
+        if self._loader_task is not None:
+            self._loader_task.cancel()
+            self._loader_task = None
+            self.out.write(Theme.CLEAR_LINE)
+            self.out.flush()
+
+    def status_line(self) -> str:
+        s = self.status
+        parts = [str(s.get("model", "")), f"turn {s.get('turn', 0)}", f"{s.get('input_tokens', 0)}→{s.get('output_tokens', 0)} tok"]
+        if s.get("cost"):
+            parts.append(f"${s['cost']:.4f}")
+        if s.get("session_id"):
+            parts.append(str(s["session_id"])[:12])
+        text = "  ".join(p for p in parts if p)
+        return f"{Theme.STATUS} {text[:self.width - 2].ljust(self.width - 2)} {Theme.RESET}"
+
+    # ---- events
+    def _enter(self, mode: str) -> None:
+        if mode == self._mode:
+            return
+        self.hide_loader()
+        if self._mode == "thinking":
+            self._w(Theme.RESET)
+        self._fresh_line()
+        if mode == "thinking":
+            self._w(f"{Theme.DIM}{Theme.ITALIC}")
+        elif mode == "text":
+            self._t_stream, self._chars = time.monotonic(), 0
+        self._mode = mode
+
+    async def handle_event(self, event: StreamEvent) -> None:
+        if isinstance(event, TextDelta):
+            self._enter("text")
+            self._chars += len(event.delta)
+            self._w(self._fence.feed(event.delta))
+        elif isinstance(event, ThinkingDelta):
+            if self.show_thinking:
+                self._enter("thinking")
+                self._w(event.delta)
+        elif isinstance(event, ToolCallStart):
+            self._enter("")
+            self.show_loader(f"{event.name}: receiving arguments")
+        elif isinstance(event, ToolCallEnd):
+            self._enter("")
+            args = json.dumps(event.args, ensure_ascii=False, indent=2)
+            self._w(box(f"tool: {event.name}", truncate_lines(args, 10, self.width - 4), self.width, Theme.TOOL) + "\n")
+            self.show_loader(f"running {event.name}")
+        elif isinstance(event, ToolResultReceived):
+            self._enter("")
+            color = Theme.ERROR if event.is_error else Theme.DIM
+            title = "error" if event.is_error else "result"
+            self._w(box(title, truncate_lines(event.content, self.max_result_lines, self.width - 4), self.width, color) + "\n")
+        elif isinstance(event, StreamError):
+            self._enter("")
+            self._w(f"{Theme.ERROR}error: {event.error}{Theme.RESET}\n")
+        elif isinstance(event, StreamDone):
+            self._enter("")
+            self._w(Theme.RESET)
+
+    async def get_input(self, prompt: str = "") -> str:
+        self._enter("")
+        self._w(self.status_line() + "\n")
+        self._w(f"{Theme.USER}{Theme.BOLD}{prompt or '> '}{Theme.RESET}")
+        return await _readline(self.inp)
+
+    async def confirm_tool(self, tool_call: ToolCall) -> bool:
+        if self.auto_confirm:
+            return True
+        self.hide_loader()
+        self._fresh_line()
+        self._w(f"{Theme.TOOL}allow {tool_call.name}? [y/N/a(lways)] {Theme.RESET}")
+        ans = (await _readline(self.inp)).strip().lower()
+        if ans in ("a", "always"):
+            self.auto_confirm = True
+            return True
+        return ans in ("y", "yes")
+
+
+# ------------------------------------------------------------------------------------------ the chat loop
+HELP = """/help               this text
+/quit               leave (ctrl-d works too)
+/clear              start a new conversation (keeps the system prompt)
+/model NAME         switch the model of the endpoint
+/temperature X      sampling temperature
+/thinking on|off    show or hide reasoning text
+/status             session, turns, token counts
+/save PATH          write the conversation as JSON lines
+/retry              drop the last assistant turn and ask again"""
+
+
+class InteractiveRunner:
+    """Chat loop over any ``Frontend``: prompts, slash commands, tool confirmation, session persistence."""
+
+    def __init__(self, endpoint: Endpoint, frontend: Frontend, environment: Any = None, system_prompt: str | None = None,
+                 session_store: Any = None, session_id: str | None = None, max_turns: int = 20,
+                 initial_prompt: str | None = None, single_turn: bool = False, trajectory: Trajectory | None = None):
+        self.endpoint, self.frontend, self.environment = endpoint, frontend, environment
+        self.system_prompt = system_prompt
+        self.store, self.session_id = session_store, session_id
+        self.max_turns, self.initial_prompt, self.single_turn = max_turns, initial_prompt, single_turn
+        base = trajectory or Trajectory(tuple([Message("system", system_prompt)] if system_prompt else []))
+        self.state = AgentState(actor=Actor(base, endpoint), environment=environment, max_turns=max_turns, session_id=session_id)
+        self.turns = 0
+        self.commands: dict[str, Callable[[str], Any]] = {
+            "help": self._cmd_help, "clear": self._cmd_clear, "model": self._cmd_model, "temperature": self._cmd_temperature,
+            "thinking": self._cmd_thinking, "status": self._cmd_status, "save": self._cmd_save, "retry": self._cmd_retry}
+
+    # ---- slash commands: return text to print; "retry" returns a prompt to resend
+    def _cmd_help(self, arg: str) -> str:
+        return HELP
+
+    def _cmd_clear(self, arg: str) -> str:
+        msgs = tuple(m for m in self.state.actor.trajectory.messages if m.role == "system")
+        self.state = replace(self.state, actor=Actor(Trajectory(msgs), self.endpoint), turn_idx=0, stop=None, session_id=None,
+                             pending_tool_calls=())
+        return "conversation cleared"
+
+    def _cmd_model(self, arg: str) -> str:
+        if not arg:
+            return f"model: {self.endpoint.model}"
+        self.endpoint = replace(self.endpoint, model=arg)
+        self.state = replace(self.state, actor=replace(self.state.actor, endpoint=self.endpoint))
+        return f"model set to {arg}"
+
+    def _cmd_temperature(self, arg: str) -> str:
+        try:
+            t = float(arg)
+        except ValueError:
+            return "usage: /temperature 0.7"
+        self.endpoint = replace(self.endpoint, temperature=t)
+        self.state = replace(self.state, actor=replace(self.state.actor, endpoint=self.endpoint))
+        return f"temperature set to {t}"
+
+    def _cmd_thinking(self, arg: str) -> str:
+        on = arg.strip().lower() in ("on", "1", "true", "yes", "")
+        if hasattr(self.frontend, "show_thinking"):
+            self.frontend.show_thinking = on
+        return f"thinking {'shown' if on else 'hidden'}"
+
+    def _cmd_status(self, arg: str) -> str:
+        u = self.state.usage
+        return (f"session {self.state.session_id or '-'}  turns {self.turns}  messages {len(self.state.actor.trajectory.messages)}  "
+                f"tokens in/out {u.input_tokens}/{u.output_tokens}")
+
+    def _cmd_save(self, arg: str) -> str:
+        if not arg:
+            return "usage: /save conversation.jsonl"
+        with open(arg, "w") as f:
+            for m in self.state.actor.trajectory.messages:
+                f.write(json.dumps(m.to_dict(), ensure_ascii=False) + "\n")
+        return f"saved {len(self.state.actor.trajectory.messages)} messages to {arg}"
+
+    def _cmd_retry(self, arg: str):
+        msgs = list(self.state.actor.trajectory.messages)
+        while msgs and msgs[-1].role != "user":
+            msgs.pop()
+        if not msgs:
+            return "nothing to retry"
+        last_user = msgs.pop()
+        self.state = replace(self.state, actor=Actor(Trajectory(tuple(msgs)), self.endpoint), stop=None, pending_tool_calls=())
+        return ("retry", last_user.text())
+
+    # ---- loop
+    def _run_config(self) -> RunConfig:
+        fe = self.frontend
+
+        async def on_chunk(ev: StreamEvent) -> None:
+            await fe.handle_event(ev)
+
+        async def confirm(call: ToolCall, state: AgentState, rc: RunConfig) -> bool:
+            return await fe.confirm_tool(call)
+
+        async def on_input(prompt: str) -> str:
+            return await fe.get_input(prompt)
+
+        return RunConfig(on_chunk=on_chunk, confirm_tool=confirm, on_input=on_input, session_store=self.store)
+
+    def _publish_status(self) -> None:
+        u = self.state.usage
+        self.frontend.set_status(model=self.endpoint.model or self.endpoint.provider, turn=self.turns, input_tokens=u.input_tokens,
+                                 output_tokens=u.output_tokens, cost=u.cost.input + u.cost.output + u.cost.cache_read + u.cost.cache_write,
+                                 session_id=self.state.session_id)
+
+    async def _one_exchange(self, text: str) -> None:
+        traj = self.state.actor.trajectory.append(Message("user", text))
+        self.state = replace(self.state, actor=replace(self.state.actor, trajectory=traj, endpoint=self.endpoint), stop=None, turn_idx=0)
+        if self.store is not None and self.state.session_id:
+            await self.store.append_message(self.state.session_id, traj.messages[-1])
+        self.frontend.show_loader("thinking")
+        try:
+            states = await run_agent(self.state, self._run_config())
+            self.state = states[-1]
+        except Exception as e:  # noqa: BLE001 - a provider failure ends the exchange, not the chat
+            await self.frontend.handle_event(StreamError(error=f"{type(e).__name__}: {e}"))
+            self.state = replace(self.state, stop=StopReason.ERROR)
+        finally:
+            self.frontend.hide_loader()
+        self.turns += 1
+        self._publish_status()
+
+    async def run(self) -> AgentState:
+        fe = self.frontend
+        await fe.start()
+        self._publish_status()
+        pending = self.initial_prompt
+        try:
+            while True:
+                if pending is None:
+                    try:
+                        pending = await fe.get_input("> ")
+                    except (EOFError, KeyboardInterrupt):
+                        break
+                text, pending = pending.strip(), None
+                if not text:
+                    continue
+                if text.startswith("/"):
+                    name, _, arg = text[1:].partition(" ")
+                    if name in ("quit", "exit", "q"):
+                        break
+                    fn = self.commands.get(name)
+                    res = fn(arg.strip()) if fn else f"unknown command /{name} (try /help)"
+                    if isinstance(res, tuple) and res[0] == "retry":
+                        pending = res[1]
+                    else:
+                        await fe.handle_event(TextDelta(delta=str(res) + "\n"))
+                        await fe.handle_event(StreamDone())
+                    continue
+                await self._one_exchange(text)
+                if self.single_turn:
+                    break
+        finally:
+            await fe.stop()
+        return self.state
+
+
+def make_frontend(kind: str, **kw: Any) -> Frontend:
+    """``plain`` | ``json`` | ``ansi`` (``auto`` = ansi on a terminal, plain otherwise)."""
+    if kind == "auto":
+        kind = "ansi" if sys.stdout.isatty() else "plain"
+    return {"plain": PlainFrontend, "none": PlainFrontend, "json": JsonFrontend, "ansi": AnsiFrontend, "tui": AnsiFrontend}[kind](**kw)

@@ -1,0 +1,82 @@
+"""Terminal front ends and the interactive chat loop, driven by scripted input and a scripted model."""
+
+import asyncio
+import io
+import json
+
+from research_b200.agents.dtypes import (Endpoint, StreamDone, TextDelta, ThinkingDelta, ToolCallEnd, ToolResultReceived)
+from research_b200.agents.environments import CalculatorEnvironment
+from research_b200.agents.providers import ScriptedLLM, register_provider
+from research_b200.frontend.terminal import (AnsiFrontend, FenceHighlighter, InteractiveRunner, JsonFrontend, PlainFrontend,
+                                             Theme, box, truncate_lines)
+
+
+def test_box_and_truncate():
+    lines = truncate_lines("a\n" * 30 + "x" * 500, 5, 20)
+    assert len(lines) == 6 and lines[-1].startswith("…") and all(len(ln) <= 20 for ln in lines[:5])
+    b = box("tool: calc", ["1+1", "=2"], 30)
+    rows = b.split("\n")
+    assert len(rows) == 4 and len({len(r) for r in rows}) == 1 and rows[0].startswith("┌─ tool: calc")
+
+
+def test_fence_highlighter_streams_in_pieces():
+    text = "see:\n```python\nx = 1\ny = 2\n```\nafter\n"
+    whole = FenceHighlighter().feed(text)
+    h = FenceHighlighter()
+    pieces = "".join(h.feed(text[i:i + 3]) for i in range(0, len(text), 3))
+    assert whole == pieces
+    assert Theme.CODE + "x = 1" in whole and Theme.CODE + "after" not in whole and not h.in_code
+
+
+def test_ansi_frontend_renders_events():
+    out = io.StringIO()
+    fe = AnsiFrontend(out=out, inp=io.StringIO("y\n"), width=60, auto_confirm=False)
+
+    async def go():
+        await fe.start()
+        await fe.handle_event(ThinkingDelta(delta="hmm"))
+        await fe.handle_event(TextDelta(delta="The answer"))
+        await fe.handle_event(ToolCallEnd(tool_call_id="1", name="evaluate", args={"expression": "2+2"}))
+        await fe.handle_event(ToolResultReceived(tool_call_id="1", content="4\n" * 40))
+        await fe.handle_event(StreamDone())
+        fe.set_status(model="m", turn=2, input_tokens=10, output_tokens=5)
+        line = await fe.get_input("> ")
+        await fe.stop()
+        return line
+
+    assert asyncio.run(go()) == "y"
+    s = out.getvalue()
+    assert "tool: evaluate" in s and "more lines" in s and "hmm" in s and "turn 2" in s and "10→5 tok" in s
+    assert fe._loader_task is None
+
+
+def test_interactive_runner_with_tools_and_commands(tmp_path):
+    register_provider("scripted-chat", ScriptedLLM([
+        '<tool_call>{"name": "evaluate", "arguments": {"expression": "6*7"}}</tool_call>', "It is 42.", "Again 42."]))
+    out = io.StringIO()
+    save = tmp_path / "c.jsonl"
+    inp = io.StringIO(f"what is 6*7?\n/status\n/bogus\n/temperature 0.3\n/retry\n/save {save}\n/quit\n")
+    fe = PlainFrontend(out=out, inp=inp)
+    runner = InteractiveRunner(Endpoint(provider="scripted-chat", model="s"), fe, environment=CalculatorEnvironment(),
+                               system_prompt="be brief")
+    state = asyncio.run(runner.run())
+    s = out.getvalue()
+    assert "[tool] evaluate" in s and "[result] current value: 42" in s and "It is 42." in s and "Again 42." in s
+    assert "unknown command /bogus" in s and "temperature set to 0.3" in s and runner.endpoint.temperature == 0.3
+    roles = [m.role for m in state.actor.trajectory.messages]
+    assert roles[0] == "system" and roles.count("user") == 1 and roles[-1] == "assistant"
+    saved = [json.loads(ln) for ln in save.read_text().splitlines()]
+    assert saved[0]["role"] == "system" and saved[-1]["role"] == "assistant"
+    assert fe.status["turn"] == 2
+
+
+def test_json_frontend_protocol():
+    register_provider("scripted-json", ScriptedLLM(["hello there"]))
+    out = io.StringIO()
+    fe = JsonFrontend(out=out, inp=io.StringIO('{"text": "hi"}\n'))
+    runner = InteractiveRunner(Endpoint(provider="scripted-json"), fe, single_turn=True)
+    asyncio.run(runner.run())
+    events = [json.loads(ln) for ln in out.getvalue().splitlines()]
+    kinds = [e["type"] for e in events]
+    assert kinds[0] == "start" and kinds[-1] == "stop" and "input_request" in kinds and "text_delta" in kinds and "done" in kinds
+    assert next(e for e in events if e["type"] == "text_delta")["delta"] == "hello there"
