@@ -92,6 +92,8 @@ struct GemmParams {
   const unsigned long long* row_dst;
   int swiglu;
   int split_k, kb_per_split;
+  int cluster_k;   // split-K slices are the CTAs of one thread-block cluster; partial tiles meet in distributed shared memory
+  int red_alias;   // cluster split-K, one work unit per CTA: the partial tile reuses the (drained) TMA ring
   int stages;
   int scaled_epilogue, mirror;
   float alpha, beta;
@@ -169,6 +171,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
   __shared__ int splitk_last;
+  __shared__ __align__(8) uint64_t red_full_bar;    // cluster split-K: every slice's partial tile is in shared memory
+  __shared__ __align__(8) uint64_t red_empty_bar;   // cluster split-K: every peer has finished reading this CTA's partial
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -196,6 +200,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(smem_u32(&tmem_empty_bar[a]), EPI_WARPS);
     }
     mbar_init(smem_u32(&epi_bar), EPI_WARPS * 32);
+    if (p.cluster_k) {
+      mbar_init(smem_u32(&red_full_bar), split_k * EPI_WARPS);
+      mbar_init(smem_u32(&red_empty_bar), split_k * EPI_WARPS);
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -205,6 +213,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (p.cluster_k) cluster_sync_all();   // no peer may signal a barrier that is not initialised yet
   pdl_wait();  // barriers and TMEM are set up; from here on we read what the previous kernel wrote
   RB_TS(0);
   const uint32_t tmem_base = tmem_base_smem;
@@ -380,6 +389,82 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
       const int n_base = grouped ? n_in : n_part * p.b_rows_per_part + n_in;    // global column
       const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
+      if (p.cluster_k) {
+        // ---- cluster split-K: the split_k CTAs of a cluster each hold the fp32 partial tile of one K slice.
+        // Every CTA parks its partial in its own shared memory, then reduces and stores one column slice of
+        // the tile, reading the peers' partials through distributed shared memory (fixed slice order, so the
+        // sum is deterministic). No global workspace, no tickets.
+        const int S = split_k;
+        const int ks = t % S;   // == rank of this CTA in its cluster (the grid is a multiple of S)
+        const int trow = q * 32 + lane;
+        // behind the ring, or (one unit per CTA: every load has landed and every MMA has retired once the
+        // accumulator is complete) on top of it
+        const uint32_t red_off = p.red_alias ? 0u : (uint32_t)STAGES * Cfg::kStageBytes;
+        const uint32_t red_u32 = smem_base + red_off;
+        float4* red = reinterpret_cast<float4*>(smem_raw + (smem_base - smem_u32(smem_raw)) + red_off);
+        if (tile_iter > 0) {   // the peers must have finished reading the previous partial
+          ok = mbar_wait_bounded_cluster(smem_u32(&red_empty_bar), (tile_iter - 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY);
+          if (!ok) break;
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            red[((c0 + j) >> 2) * BM + trow] = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        fence_acq_rel_cluster();
+        __syncwarp();
+        if (lane < S) mbar_arrive_cluster(mapa_cluster(smem_u32(&red_full_bar), (uint32_t)lane));
+        ok = mbar_wait_bounded_cluster(smem_u32(&red_full_bar), tile_iter & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        const int W = BN / S;   // columns this CTA finishes (a multiple of 8)
+#pragma unroll 1
+        for (int w0 = 0; w0 < W; w0 += 32) {
+          const int wn = min(32, W - w0);
+          const int cbase = ks * W + w0;            // first column inside the tile
+          const int ncols = min(wn, n_valid - cbase);
+          if (ncols <= 0) break;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+#pragma unroll 1
+          for (int s2 = 0; s2 < S; ++s2) {
+            const uint32_t peer = mapa_cluster(red_u32, (uint32_t)s2);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (j < wn) {
+                const float4 f = ld_dsmem_f4(peer + (uint32_t)((((cbase + j) >> 2) * BM + trow) * 16));
+                v[j] += f.x; v[j + 1] += f.y; v[j + 2] += f.z; v[j + 3] += f.w;
+              }
+            }
+          }
+          if (row_ok) {
+            const int col = n_base + cbase;
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) v[j] += __bfloat162float(p.bias[col + j]);
+            }
+            if (p.residual != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols) v[j] += __bfloat162float(p.residual[row * p.ldr + col + j]);
+            }
+            epi_store_row_chunk(p, v, row, col, ncols);
+          }
+        }
+        fence_acq_rel_cluster();
+        __syncwarp();
+        if (lane < S) mbar_arrive_cluster(mapa_cluster(smem_u32(&red_empty_bar), (uint32_t)lane));
+        continue;
+      }
       if (split_k > 1) {
         // ---- split-K: fp32 partial tile -> workspace; the last slice to arrive finishes the tile ----
         // Workspace layout per work unit: [BN/4 column quads][BM rows] of float4, so that the 32
@@ -815,6 +900,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
+    if (p.cluster_k && tile_iter > 0) {
+      // peers may still be reading this CTA's last partial tile through distributed shared memory: stay
+      // resident until they signalled, whatever else went wrong (only the time budget ends this wait)
+      mbar_wait_bounded_cluster(smem_u32(&red_empty_bar), (tile_iter - 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY, false);
+    }
   }
 
   RB_TS(6);
@@ -911,6 +1001,10 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
+  if (p.cluster_k) {
+    grid -= grid % p.split_k;                       // whole clusters only
+    if (grid < p.split_k || BN / p.split_k < 8) return -15;
+  }
   // Ring depth: never deeper than the k-blocks a CTA will load in total.
   GemmParams q = p;
   int stages = Cfg::kStages;
@@ -922,12 +1016,21 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
     if (kb_cta < stages) stages = kb_cta < 2 ? 2 : (int)kb_cta;
   }
   // reduce modes stage the outgoing partial tile in shared memory behind the ring
-  const int extra = p.epi_mode != RB_EPI_STORE ? 128 * (BN * 2 + 16) : 0;
-  const int fit = (kMaxDynSmem - 1024 - extra) / Cfg::kStageBytes;
+  // cluster split-K parks the fp32 partial tile ([BN/4 column quads][BM rows] float4) there instead; with one
+  // unit per CTA the partial reuses the ring itself
+  int extra = p.cluster_k ? BM * BN * 4 : p.epi_mode != RB_EPI_STORE ? 128 * (BN * 2 + 16) : 0;
+  if (p.cluster_k) {
+    const long long units = (long long)m_tiles * n_tiles * p.split_k;
+    q.red_alias = units <= grid ? 1 : 0;
+  }
+  int fit = (kMaxDynSmem - 1024 - (q.red_alias ? 0 : extra)) / Cfg::kStageBytes;
   if (stages > fit) stages = fit;
   if (stages < 2) return -14;
   q.stages = stages;
-  const int smem = stages * Cfg::kStageBytes + 1024 + extra;
+  int smem = stages * Cfg::kStageBytes + 1024 + extra;
+  if (q.red_alias) smem = (stages * Cfg::kStageBytes > extra ? stages * Cfg::kStageBytes : extra) + 1024;
+  if (p.cluster_k)
+    return launch_kernel_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, (unsigned)p.split_k, q) == cudaSuccess ? 0 : -11;
   return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
 }
 
@@ -1021,7 +1124,16 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.splitk_ws = a->splitk_ws;
   p.splitk_tickets = a->splitk_tickets;
   p.kb_per_split = 0;
-  if (p.split_k > 1) {
+  p.cluster_k = (a->cluster_split && p.split_k > 1) ? 1 : 0;
+  if (p.cluster_k) {
+    // slices = CTAs of one cluster; needs a power-of-two slice count up to 8 and a non-empty K range for each
+    const int S = p.split_k, num_kb = (a->K + BK - 1) / BK;
+    if ((S != 2 && S != 4 && S != 8) || a->swiglu || a->tile_table || p.epi_mode != RB_EPI_STORE || a->a_parts != 1 ||
+        a->b_parts != 1 || p.sample_ws != nullptr || p.scaled_epilogue || p.mirror)
+      return -1;
+    p.kb_per_split = (num_kb + S - 1) / S;
+    if ((S - 1) * p.kb_per_split >= num_kb) return -1;
+  } else if (p.split_k > 1) {
     if (p.splitk_ws == nullptr || p.splitk_tickets == nullptr || a->swiglu || a->tile_table || p.epi_mode != RB_EPI_STORE ||
         a->a_parts != 1 || a->b_parts != 1 || a->N % 4 != 0)
       return -1;

@@ -90,6 +90,10 @@ typedef struct RbGemmArgs {
   const unsigned long long* sample_seeds;       // [M]
   const unsigned long long* sample_step_ptr;    // device step counter (may be null)
   unsigned long long sample_step_add;
+  // Split-K inside a thread-block cluster (split_k = 2, 4 or 8 CTAs per cluster): the slices exchange their fp32
+  // partial tiles through distributed shared memory and each CTA finishes one column slice of the tile. Needs no
+  // workspace or tickets; bn / split_k must be at least 8 columns. Deterministic.
+  int cluster_split;
 } RbGemmArgs;
 
 // Token and log-probability from the per-tile records written by the sampling epilogue.

@@ -7,6 +7,7 @@ Replaces the cuBLAS ``F.linear`` calls inside the HF modules the reference runs
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 
 import torch
@@ -75,6 +76,7 @@ class RbGemmArgs(ctypes.Structure):
         ("sample_seeds", ctypes.c_void_p),
         ("sample_step_ptr", ctypes.c_void_p),
         ("sample_step_add", ctypes.c_ulonglong),
+        ("cluster_split", ctypes.c_int),
     ]
 
 
@@ -117,6 +119,7 @@ def gemm(
     split_k: int = 0,
     alpha: float = 1.0,
     beta: float = 1.0,
+    cluster_split: bool | None = None,
 ) -> torch.Tensor:
     """``C[M,N] = alpha * op(A) @ op(B)^T (+bias) (+ beta * residual)``.
 
@@ -182,7 +185,13 @@ def gemm(
         split_k, auto_bn = _auto_split_k(M, N, K, a_mn_major or b_mn_major or swiglu or out_f32 or bn != 0)
         if auto_bn:
             args.bn = auto_bn
-    if split_k > 1:
+    if cluster_split is None:
+        # slices as one thread-block cluster (partials meet in distributed shared memory) whenever the shape allows
+        cluster_split = (split_k in (2, 4, 8) and args.bn in (32, 64, 128, 256) and args.bn // split_k >= 8 and not swiglu
+                         and (-(-K // 64)) > (split_k - 1) * (-(-(-(-K // 64)) // split_k)) and _SPLITK_MODE != "l2")
+    if split_k > 1 and cluster_split:
+        args.split_k, args.cluster_split = split_k, 1
+    elif split_k > 1:
         # one [128 x bn] fp32 tile per (output tile, K slice); padded for the widest tile the kernel may pick
         ws, tickets = _splitk_scratch(a.device, split_k * (-(-M // 128) * 128) * (-(-N // 256) * 256), (-(-M // 128)) * (-(-N // 32)))
         args.split_k, args.splitk_ws, args.splitk_tickets = split_k, ws.data_ptr(), tickets.data_ptr()
@@ -193,20 +202,66 @@ def gemm(
 
 
 _SPLITK: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+_SPLITK_MODE = os.environ.get("RB_SPLITK_MODE", "cluster")   # "l2" keeps the workspace + ticket reduction
 
 
 def _auto_split_k(M: int, N: int, K: int, excluded: bool) -> tuple[int, int]:
-    """Tile width and K split for decode-sized problems (M <= 256, K >= 3072).
+    """Tile width and K split for decode-sized problems (M <= 256): returns ``(split, bn)``, ``(1, 0)`` = leave it
+    to the kernel.
 
-    With narrow tiles every CTA re-reads the whole activation slab from L2 (N/32 times in total), which
-    is what bounds these launches; wide tiles cut that traffic but leave too few CTAs, so K is split to
-    bring the CTA count back towards one wave of 148. Chosen: the (bn, split) with the most CTAs that
-    still fits one wave, at least 1024 of K per slice, ties to the wider tile. Measured on B200 with
-    weights streamed from HBM (M=256): N=896,K=4864 25.5 -> 14.8 us (bn 64, 4 slices), 5 % on the 0.5B
-    decode step. Wide outputs (N >= 2048) are left unsplit: isolated launches gain (N=4096,K=14336
-    73.6 -> 44.7 us) but inside the 8B decode graph the step got 3 % slower."""
-    if excluded or M > 256 or K < 3072 or N % 8 or N >= 2048 or os.environ.get("RB_NO_SPLITK"):
-        return 1, 0     # N >= 2048: enough tiles without a split (8B decode step: 11.09 ms with, 10.78 ms without)
+    These launches are bound by what one SM can pull from L2 (about 80 GB/s measured): a CTA streams
+    ``(128 + bn) * 128`` bytes per k-block, and with narrow tiles or few tiles most of the 148 SMs idle. Splitting
+    K inside a thread-block cluster (the slices exchange partial tiles through distributed shared memory) fills
+    the machine without a workspace round trip. The choice minimises a small cost model fitted to B200
+    timings with weights streamed from HBM (M=256): N=896,K=4864 29.1 us unsplit -> 18.7 (bn 64, 4 slices);
+    N=4096,K=14336 74.6 -> 54.5 (bn 128, 2 slices); K <= 896 is never split (12.2 us either way)."""
+    if excluded or M > 256 or N % 8 or os.environ.get("RB_NO_SPLITK"):
+        return 1, 0
+    if _SPLITK_MODE == "l2":
+        return _auto_split_k_workspace(M, N, K)
+    return _cluster_split_choice(M, N, K)
+
+
+_STREAM_GBS = {32: 80e3, 64: 85e3, 128: 98e3, 256: 114e3}     # bytes per microsecond one SM pulls from L2, by tile width
+
+
+@functools.lru_cache(maxsize=4096)
+def _cluster_split_choice(M: int, N: int, K: int) -> tuple[int, int]:
+    """Cheapest (split, bn) under a model fitted to 100 timed B200 launches (mean error 10 %): per k-block a CTA
+    streams ``(128 + bn) * 128`` bytes at the per-SM rate above; a cluster reduction costs 1 + 0.045 bn (2 slices),
+    1.5 + 0.025 bn (4) or 3 + 0.03 bn microseconds (8); split launches must fit one wave."""
+    m_tiles = -(-M // 128)
+    num_kb = -(-K // 64)
+    best = None
+    for bn in (256, 128, 64, 32):
+        if bn > 32 and N < bn:
+            continue
+        n_tiles = -(-N // bn)
+        stage_us = (128 + bn) * 128 / _STREAM_GBS[bn]
+        mma_us = 128 * bn * 64 * 2 / 8.0e6
+        for s in (1, 2, 4, 8):
+            per = -(-num_kb // s)
+            if s > 1 and (bn // s < 8 or per < 4 or (s - 1) * per >= num_kb):
+                continue
+            units = m_tiles * n_tiles * s
+            grid = min(units, 148 - 148 % s)
+            if s > 1 and units > grid:
+                continue
+            waves = -(-units // grid)
+            red = {1: 0.0, 2: 1 + 0.045 * bn, 4: 1.5 + 0.025 * bn, 8: 3 + 0.03 * bn}[s]
+            cost = waves * (per * max(stage_us, mma_us) + 1.0 + red)
+            if best is None or cost < best[0] - 0.5:
+                best = (cost, s, bn)
+    if best is None or best[1] == 1:
+        return 1, 0
+    return best[1], best[2]
+
+
+def _auto_split_k_workspace(M: int, N: int, K: int) -> tuple[int, int]:
+    """Choice for the workspace + ticket reduction (RB_SPLITK_MODE=l2): most CTAs within one wave, at least 1024 of
+    K per slice, N < 2048 only (wider outputs measured slower inside the decode graph)."""
+    if K < 3072 or N >= 2048:
+        return 1, 0
     m_tiles = -(-M // 128)
     best = None
     for bn in (256, 128, 64, 32):

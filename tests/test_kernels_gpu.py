@@ -101,6 +101,29 @@ def test_gemm_split_k(cuda_device, M, N, K, split):
     _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.06, rtol=0.01, what="split-k inplace")
 
 
+@pytest.mark.parametrize("M,N,K,bn,split,max_ctas", [
+    (256, 896, 4864, 64, 4, 0), (256, 896, 4864, 32, 4, 0), (256, 896, 4864, 32, 2, 0), (256, 4096, 14336, 128, 2, 0),
+    (130, 520, 2056, 64, 2, 0), (256, 4096, 4096, 128, 8, 0), (384, 1024, 2048, 64, 4, 16), (8, 1152, 896, 32, 2, 0),
+    (256, 4096, 14336, 256, 4, 0), (64, 4096, 4096, 256, 8, 0), (256, 6144, 4096, 256, 2, 0), (256, 1024, 2048, 256, 2, 4)])
+def test_gemm_cluster_split_k(cuda_device, M, N, K, bn, split, max_ctas):
+    """K slices are the CTAs of one thread-block cluster; partial tiles meet in distributed shared memory."""
+    a = _rand((M, K), cuda_device, seed=60)
+    b = _rand((N, K), cuda_device, 0.05, seed=61)
+    bias = _rand((N,), cuda_device, seed=62)
+    res = _rand((M, N), cuda_device, seed=63)
+    want = ops.gemm_reference(a, b, bias, res, out_dtype=torch.float32)
+    got = ops.gemm(a, b, bias=bias, residual=res, bn=bn, split_k=split, cluster_split=True, max_ctas=max_ctas)
+    _assert_close(got, want, atol=0.06, rtol=0.01, what=f"cluster split-k bn={bn} s={split}")
+    again = ops.gemm(a, b, bias=bias, residual=res, bn=bn, split_k=split, cluster_split=True, max_ctas=max_ctas)
+    assert torch.equal(got, again)                                      # fixed slice order: bitwise repeatable
+    f32 = ops.gemm(a, b, bn=bn, split_k=split, cluster_split=True, out_f32=True)
+    _assert_close(f32, ops.gemm_reference(a, b, out_dtype=torch.float32), atol=0.02, rtol=0.005, what="cluster split-k fp32")
+    x = res.clone()
+    ops.gemm(a, b, residual=x, out=x, bn=bn, split_k=split, cluster_split=True)   # in-place residual
+    _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.06, rtol=0.01, what="cluster inplace")
+    ops.check_status()
+
+
 def test_gemm_strided_views(cuda_device):
     big = _rand((256, 2048), cuda_device, seed=9)
     a = big[:, 512:1024]  # lda = 2048
