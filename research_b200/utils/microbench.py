@@ -152,12 +152,68 @@ def bench_sampling(B, V, peak_gbs):
             "frac_of_measured_peak": round(ach / peak_gbs, 3)}
 
 
+def sweep_decode_gemm(shapes=((256, 896, 4864), (256, 896, 896), (256, 4096, 14336), (256, 4096, 4096), (256, 6144, 4096),
+                              (64, 4096, 14336)), launches: int = 60) -> list[dict]:
+    """Decode-sized GEMMs (x += a @ W^T) over tile widths and K splits: unsplit, split inside a thread-block cluster
+    (``c<S>``) and split through the global workspace (``l2_<S>``). Weights rotate through a ring larger than L2, so
+    every launch streams them from HBM. Times are microseconds per launch, back to back on one stream."""
+    import itertools
+
+    from research_b200.ops.gemm import _auto_split_k
+
+    dev = torch.device("cuda")
+    rows = []
+    for M, N, K in shapes:
+        nw = max(2, int(400e6 // (N * K * 2)) + 1)
+        ws = [torch.randn(N, K, device=dev).bfloat16() * 0.05 for _ in range(nw)]
+        a = torch.randn(M, K, device=dev).bfloat16()
+        x = torch.zeros(M, N, device=dev).bfloat16()
+        it = itertools.cycle(range(nw))
+
+        def run(**kw):
+            def once():
+                ops.gemm(a, ws[next(it)], residual=x, out=x, **kw)
+
+            for _ in range(10):
+                once()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(launches):
+                once()
+            e1.record()
+            torch.cuda.synchronize()
+            return round(e0.elapsed_time(e1) / launches * 1e3, 1)
+
+        res = {"kernel": "decode_gemm_sweep", "M": M, "N": N, "K": K, "chosen": _auto_split_k(M, N, K, False),
+               "auto_us": run(), "unsplit_us": run(split_k=1)}
+        for bn in (32, 64, 128, 256):
+            if bn > N:
+                continue
+            res[f"bn{bn}"] = run(split_k=1, bn=bn)
+            for s in (2, 4, 8):
+                units = -(-M // 128) * -(-N // bn) * s
+                if bn // s < 8 or K // 64 < 4 * s or units > 148 - 148 % s:
+                    continue
+                res[f"bn{bn}_c{s}"] = run(split_k=s, bn=bn, cluster_split=True)
+                if bn < 256:
+                    res[f"bn{bn}_l2_{s}"] = run(split_k=s, bn=bn, cluster_split=False)
+        ops.check_status()
+        rows.append(res)
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--decode-gemm-sweep", action="store_true", help="only the tile-width / split-K sweep of decode GEMMs")
     ap.add_argument("--peak-tflops", type=float, default=1688.4)
     ap.add_argument("--peak-gbs", type=float, default=6453.4)
     ap.add_argument("--quick", action="store_true")
     args = ap.parse_args()
+    if args.decode_gemm_sweep:
+        for r in sweep_decode_gemm():
+            print(json.dumps(r))
+        return
     rows = []
     shapes = [(8192, 8192, 8192), (4096, 14336, 4096), (8192, 4096, 14336), (256, 1152, 896), (256, 9728, 896),
               (256, 896, 4864), (256, 151936, 896)]
