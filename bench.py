@@ -109,14 +109,17 @@ def run_native(args) -> dict:
     import torch
 
     from research_b200.inference import EngineConfig, InferenceEngine, SamplingParams
-    from research_b200.models import get_preset, init_random_weights
+    from research_b200.models import LazyRandomWeights, get_preset, init_random_weights
     from research_b200.ops import check_status
     from research_b200.utils.timing import ClockSampler
 
     rank, world, local = dist_setup(args.gpus)
     dev = torch.device(f"cuda:{local}")
     cfg = get_preset(args.model)
-    weights = init_random_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
+    if cfg.num_params() > 12e9:   # tens of GB: build each tensor when the engine asks for it instead of a second full copy
+        weights = LazyRandomWeights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
+    else:
+        weights = init_random_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
     tp = None
     if args.tp and world > 1:
         # one engine over all ranks: fused GEMM + all-reduce kernels over NVLink peer memory; every rank
@@ -135,9 +138,12 @@ def run_native(args) -> dict:
         assert cfg.is_moe and tp is None, "--ep needs a mixture-of-experts model and excludes --tp"
         ep = ExpertParallel(PeerComm(device=dev))
     wl_rank = 0 if tp is not None else rank
+    # KV pool: 640k tokens, or what 80 GB hold (large models)
+    per_block = cfg.num_layers * 2 * (cfg.num_kv_heads // (world if tp is not None else 1)) * 16 * cfg.head_dim * 2
+    KV_BLOCKS = int(min(40000, 80e9 // per_block))
     eng = InferenceEngine(
         EngineConfig(cache_type="radix", max_batch_size=MAX_BATCH, max_model_len=2048, ignore_eos=True,
-                     max_tokens_per_batch=16384, num_kv_blocks=40000, seed=wl_rank),
+                     max_tokens_per_batch=16384, num_kv_blocks=KV_BLOCKS, seed=wl_rank),
         cfg, weights, device=dev, tp=tp, ep=ep)
     del weights
     rank_for_seeds, rank = rank, wl_rank

@@ -26,10 +26,15 @@ constexpr int MAX_E_PER_LANE = 8;  // up to 256 experts
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E,
                                  int k, int sigmoid_router, int norm_topk, float scaling, int* __restrict__ topk_idx,
-                                 float* __restrict__ topk_w) {
+                                 float* __restrict__ topk_w, int* __restrict__ counts /*[E] histogram, may be null*/) {
+  __shared__ int hist[256];
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
+  if (counts != nullptr) {
+    for (int i = threadIdx.x; i < E; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+  }
+  if (t < T) {
   float score[MAX_E_PER_LANE], choice[MAX_E_PER_LANE];
   const int per = (E + 31) / 32;
   float mx = -INFINITY;
@@ -91,6 +96,13 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
     if (norm_topk) w = w / (wsum + 1e-20f);
     topk_idx[(long long)t * k + lane] = my_e;
     topk_w[(long long)t * k + lane] = w * scaling;
+    if (counts != nullptr) atomicAdd(&hist[my_e], 1);
+  }
+  }
+  if (counts != nullptr) {   // integer adds: the histogram does not depend on their order
+    __syncthreads();
+    for (int i = threadIdx.x; i < E; i += blockDim.x)
+      if (hist[i]) atomicAdd(&counts[i], hist[i]);
   }
 }
 
@@ -102,9 +114,22 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int world, i
                                 int* __restrict__ expert_offset /*[E_local+1]*/, int n_gu, int bn_gu,
                                 int4* __restrict__ tiles_gu, int* __restrict__ ntiles_gu, int n_dn, int bn_dn,
                                 int4* __restrict__ tiles_dn, int* __restrict__ ntiles_dn, int max_tiles,
-                                int* status) {
+                                int* status, int rank, int* __restrict__ cursor /*[2E] or null: [E..2E) = send bases*/) {
   __shared__ int cnt[256], off[257], tb_gu[257], tb_dn[257];
   const int EL = e_hi - e_lo;
+  if (cursor != nullptr) {
+    // where this rank's rows for expert e start in the owner's expert-ordered receive buffer: the rows of the
+    // owner's lower experts (from all ranks) plus the rows of lower source ranks for e
+    const int epr = E / world;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int owner = e / epr;
+      int o = 0;
+      for (int ee = owner * epr; ee < e; ++ee)
+        for (int r = 0; r < world; ++r) o += counts_all[r * E + ee];
+      for (int r = 0; r < rank; ++r) o += counts_all[r * E + e];
+      cursor[E + e] = o;
+    }
+  }
   for (int i = threadIdx.x; i < EL; i += blockDim.x) {
     int c = 0;
     for (int r = 0; r < world; ++r) c += counts_all[r * E + e_lo + i];
@@ -271,7 +296,15 @@ extern "C" int rb_moe_route(const float* logits, const float* bias, int T, int E
                             int norm_topk, float scaling, int* topk_idx, float* topk_w, cudaStream_t s) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_E_PER_LANE || k > 32 || k > E) return -1;
-  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w);
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w, nullptr);
+  return RB_OK();
+}
+// Routing plus the per-expert histogram of the choices (added into counts[E], which the caller zeroes).
+extern "C" int rb_moe_route_count(const float* logits, const float* bias, int T, int E, int k, int sigmoid_router,
+                                  int norm_topk, float scaling, int* topk_idx, float* topk_w, int* counts, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (E > 32 * MAX_E_PER_LANE || k > 32 || k > E || counts == nullptr) return -1;
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w, counts);
   return RB_OK();
 }
 extern "C" int rb_moe_count(const int* topk_idx, int n, int E, int* counts, cudaStream_t s) {
@@ -292,7 +325,16 @@ extern "C" int rb_moe_plan(const int* counts_all, int world, int E, int e_lo, in
                            int* ntiles_dn, int max_tiles, int* status, cudaStream_t s) {
   if (e_hi - e_lo > 256 || e_hi <= e_lo) return -1;
   moe_plan_kernel<<<1, 256, 0, s>>>(counts_all, world, E, e_lo, e_hi, expert_offset, n_gu, bn_gu, (int4*)tiles_gu,
-                                    ntiles_gu, n_dn, bn_dn, (int4*)tiles_dn, ntiles_dn, max_tiles, status);
+                                    ntiles_gu, n_dn, bn_dn, (int4*)tiles_dn, ntiles_dn, max_tiles, status, 0, nullptr);
+  return RB_OK();
+}
+// The same plus the dispatch bases of rb_moe_permute_planned (cursor[E..2E)).
+extern "C" int rb_moe_plan_dispatch(const int* counts_all, int world, int E, int e_lo, int e_hi, int* expert_offset, int n_gu,
+                                    int bn_gu, void* tiles_gu, int* ntiles_gu, int n_dn, int bn_dn, void* tiles_dn,
+                                    int* ntiles_dn, int max_tiles, int* status, int rank, int* cursor, cudaStream_t s) {
+  if (e_hi - e_lo > 256 || e_hi <= e_lo || E % world != 0 || cursor == nullptr) return -1;
+  moe_plan_kernel<<<1, 256, 0, s>>>(counts_all, world, E, e_lo, e_hi, expert_offset, n_gu, bn_gu, (int4*)tiles_gu,
+                                    ntiles_gu, n_dn, bn_dn, (int4*)tiles_dn, ntiles_dn, max_tiles, status, rank, cursor);
   return RB_OK();
 }
 extern "C" int rb_moe_permute(const void* x, const int* topk_idx, int T, int k, int d, int E, int world, int rank,
@@ -302,6 +344,18 @@ extern "C" int rb_moe_permute(const void* x, const int* topk_idx, int T, int k, 
   if (d % 8 != 0 || E % world != 0) return -1;
   const long long warps = (long long)T * k;
   moe_send_base_kernel<<<1, 256, 0, s>>>(counts_all, world, E, rank, cursor);
+  moe_permute_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)x, topk_idx, T, k, d, E, world, rank,
+                                                                counts_all, cursor, mk(xp_ptrs, world), mk(ret_ptrs, world),
+                                                                cap, status);
+  return RB_OK();
+}
+// Dispatch when cursor[E..2E) already holds the send bases (rb_moe_plan_dispatch ran on the same counts).
+extern "C" int rb_moe_permute_planned(const void* x, const int* topk_idx, int T, int k, int d, int E, int world, int rank,
+                                      const int* counts_all, int* cursor, void* const* xp_ptrs, void* const* ret_ptrs,
+                                      int cap, int* status, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (d % 8 != 0 || E % world != 0) return -1;
+  const long long warps = (long long)T * k;
   moe_permute_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)x, topk_idx, T, k, d, E, world, rank,
                                                                 counts_all, cursor, mk(xp_ptrs, world), mk(ret_ptrs, world),
                                                                 cap, status);

@@ -2,9 +2,9 @@
 
 from .config import ModelConfig, PRESETS, get_preset
 from .functional import causal_lm_forward, decoder_layer_forward
-from .weights import init_random_weights, load_safetensors_dir, save_safetensors_dir
+from .weights import LazyRandomWeights, init_random_weights, load_safetensors_dir, save_safetensors_dir
 
 __all__ = [
     "ModelConfig", "PRESETS", "get_preset", "causal_lm_forward", "decoder_layer_forward",
-    "init_random_weights", "load_safetensors_dir", "save_safetensors_dir",
+    "LazyRandomWeights", "init_random_weights", "load_safetensors_dir", "save_safetensors_dir",
 ]

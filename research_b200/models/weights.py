@@ -12,6 +12,8 @@ from __future__ import annotations
 
 import json
 import struct
+import zlib
+from collections.abc import Mapping
 from pathlib import Path
 
 import numpy as np
@@ -84,6 +86,31 @@ def init_random_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32, de
             t = torch.empty(shape, dtype=torch.float32, device=dev).normal_(0.0, cfg.init_std, generator=g).to(dtype)
         out[name] = t
     return out
+
+
+class LazyRandomWeights(Mapping):
+    """Random-init weights materialised one tensor at a time: ``weights[name]`` builds the tensor (deterministic in
+    ``(seed, name)``) and keeps no reference, so loading a 30B-parameter model into an engine needs the engine's own
+    buffers plus one tensor, not a second full copy. Values differ from ``init_random_weights`` (per-name streams)."""
+
+    def __init__(self, cfg: ModelConfig, seed: int = 0, dtype=torch.float32, device="cpu"):
+        self.cfg, self.seed, self.dtype, self.device = cfg, seed, dtype, torch.device(device)
+        self.shapes = param_shapes(cfg)
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        shape = self.shapes[name]
+        if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+            return torch.ones(shape, dtype=self.dtype, device=self.device)
+        if name.endswith(".bias"):
+            return torch.zeros(shape, dtype=self.dtype, device=self.device)
+        g = torch.Generator(device=self.device).manual_seed((self.seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFF)
+        return torch.empty(shape, dtype=torch.float32, device=self.device).normal_(0.0, self.cfg.init_std, generator=g).to(self.dtype)
+
+    def __iter__(self):
+        return iter(self.shapes)
+
+    def __len__(self) -> int:
+        return len(self.shapes)
 
 
 # ---------------------------------------------------------------------------- safetensors

@@ -43,7 +43,10 @@ def _lib():
         lib.rb_moe_translate.argtypes = [_VP, _I, PP, _I, _I, _VP]
         lib.rb_moe_combine.argtypes = [_VP, _VP, _I, _I, _I, _VP, _I, _VP]
         lib.rb_moe_publish_counts.argtypes = [_VP, PP, _I, _I, _I, _VP]
-        for f in ("rb_moe_publish_counts", "rb_moe_route", "rb_moe_count", "rb_moe_plan", "rb_moe_permute", "rb_moe_translate", "rb_moe_combine"):
+        lib.rb_moe_route_count.argtypes = [_VP, _VP, _I, _I, _I, _I, _I, _F, _VP, _VP, _VP, _VP]
+        lib.rb_moe_plan_dispatch.argtypes = [_VP, _I, _I, _I, _I, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _VP, _I, _VP, _I, _VP, _VP]
+        lib.rb_moe_permute_planned.argtypes = lib.rb_moe_permute.argtypes
+        for f in ("rb_moe_publish_counts", "rb_moe_route_count", "rb_moe_plan_dispatch", "rb_moe_permute_planned", "rb_moe_route", "rb_moe_count", "rb_moe_plan", "rb_moe_permute", "rb_moe_translate", "rb_moe_combine"):
             getattr(lib, f).restype = _I
         lib._rb_typed = True
     return lib
@@ -97,8 +100,9 @@ class MoEScratch:
         self.logits = torch.empty(Tcap, E, dtype=torch.float32, device=dev)
         self.idx = torch.empty(Tcap, k, dtype=torch.int32, device=dev)
         self.w = torch.empty(Tcap, k, dtype=torch.float32, device=dev)
-        self.cursor = torch.zeros(2 * E, dtype=torch.int32, device=dev)   # running index | dispatch base per expert
-        self.local_counts = torch.zeros(E, dtype=torch.int32, device=dev)
+        # one buffer, one memset per forward: histogram of this rank's choices | running index | dispatch base
+        self.zbuf = torch.zeros(3 * E, dtype=torch.int32, device=dev)
+        self.local_counts, self.cursor = self.zbuf[:E], self.zbuf[E:]
         alloc = (lambda shape, dt: self.ep.comm.alloc(shape, dt, zero=True)) if self.ep is not None else None
         if alloc is None:
             self.counts_all = torch.zeros(1, E, dtype=torch.int32, device=dev)
@@ -219,25 +223,25 @@ class MoELayerWeights:
         s = stream_handle(dev)
         lib = _lib()
         logits = ops.gemm(h, self.gate, out=self.logits[:T], out_f32=True)
-        check_rc(lib.rb_moe_route(logits.data_ptr(), self.gate_bias.data_ptr() if self.gate_bias is not None else None,
-                                  T, E, k, int(cfg.router_type == "sigmoid"), int(cfg.norm_topk_prob),
-                                  float(cfg.routed_scaling_factor), self.idx.data_ptr(), self.w.data_ptr(), s), "rb_moe_route")
-        self.local_counts.zero_()
-        self.cursor.zero_()
-        check_rc(lib.rb_moe_count(self.idx.data_ptr(), T * k, E, self.local_counts.data_ptr(), s), "rb_moe_count")
+        self.zbuf.zero_()
+        check_rc(lib.rb_moe_route_count(logits.data_ptr(), self.gate_bias.data_ptr() if self.gate_bias is not None else None,
+                                        T, E, k, int(cfg.router_type == "sigmoid"), int(cfg.norm_topk_prob),
+                                        float(cfg.routed_scaling_factor), self.idx.data_ptr(), self.w.data_ptr(),
+                                        self.local_counts.data_ptr(), s), "rb_moe_route_count")
         if self.counts_ptrs is None:
             self.counts_all[0].copy_(self.local_counts)
         else:                                     # one kernel stores my counts row on every rank
             check_rc(lib.rb_moe_publish_counts(self.local_counts.data_ptr(), ptr_array(self.counts_ptrs), self.rank,
                                                self.world, E, s), "rb_moe_publish_counts")
             self.ep.comm.barrier(self._barrier_slot)
-        check_rc(lib.rb_moe_plan(self.counts_all.data_ptr(), self.world, E, self.e_lo, self.e_lo + self.EL,
-                                 self.expert_offset.data_ptr(), 2 * F, self.BN_GU, self.tiles_gu.data_ptr(),
-                                 self.ntiles.data_ptr(), d, self.BN_DN, self.tiles_dn.data_ptr(),
-                                 self.ntiles.data_ptr() + 4, self.max_tiles, st, s), "rb_moe_plan")
-        check_rc(lib.rb_moe_permute(h.data_ptr(), self.idx.data_ptr(), T, k, d, E, self.world, self.rank,
+        check_rc(lib.rb_moe_plan_dispatch(self.counts_all.data_ptr(), self.world, E, self.e_lo, self.e_lo + self.EL,
+                                          self.expert_offset.data_ptr(), 2 * F, self.BN_GU, self.tiles_gu.data_ptr(),
+                                          self.ntiles.data_ptr(), d, self.BN_DN, self.tiles_dn.data_ptr(),
+                                          self.ntiles.data_ptr() + 4, self.max_tiles, st, self.rank, self.cursor.data_ptr(), s),
+                 "rb_moe_plan_dispatch")
+        check_rc(lib.rb_moe_permute_planned(h.data_ptr(), self.idx.data_ptr(), T, k, d, E, self.world, self.rank,
                                     self.counts_all.data_ptr(), self.cursor.data_ptr(), ptr_array(self.xp_ptrs),
-                                    ptr_array(self.ret_ptrs), self.cap, st, s), "rb_moe_permute")
+                                    ptr_array(self.ret_ptrs), self.cap, st, s), "rb_moe_permute_planned")
         if self.counts_ptrs is not None:
             self.ep.comm.barrier(self._barrier_slot)   # every routed row has landed on its owner
         check_rc(lib.rb_moe_translate(self.ret.data_ptr(), self.cap, ptr_array(self.y_ptrs), self.world, d, s), "rb_moe_translate")
