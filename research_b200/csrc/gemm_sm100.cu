@@ -40,6 +40,8 @@ constexpr int BK = 64;
 constexpr int NUM_ACC = 2;
 constexpr int GEMM_THREADS = 192;
 constexpr int EPI_WARPS = 4;
+constexpr int NORM_WARPS = 4;                                   // extra warps of a launch with a folded RMSNorm
+constexpr int GEMM_THREADS_NORM = GEMM_THREADS + NORM_WARPS * 32;
 // MN-major 128B-swizzled tiles: 64-element chunks are BK*128 bytes apart (leading offset),
 // groups of 8 K-rows are 1024 bytes apart (stride offset).
 #ifndef RB_MN_LBO
@@ -94,6 +96,11 @@ struct GemmParams {
   int split_k, kb_per_split;
   int cluster_k;   // split-K slices are the CTAs of one thread-block cluster; partial tiles meet in distributed shared memory
   int red_alias;   // cluster split-K, one work unit per CTA: the partial tile reuses the (drained) TMA ring
+  // Folded RMSNorm: C = rstd(row of A) * (A B^T) (+bias), rstd = rsqrt(mean(A[row,:]^2) + eps). Four extra warps
+  // read every A tile from the TMA ring as it lands and accumulate the row sums of squares; the caller has
+  // multiplied the norm weight into B's columns.
+  int norm_fold;
+  float norm_eps, norm_inv_k;
   int stages;
   int scaled_epilogue, mirror;
   float alpha, beta;
@@ -157,7 +164,7 @@ __device__ unsigned long long g_ts[148 * 8];
 #endif
 
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_NORM, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int MAX_STAGES = Cfg::kStages;
@@ -173,6 +180,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   __shared__ int splitk_last;
   __shared__ __align__(8) uint64_t red_full_bar;    // cluster split-K: every slice's partial tile is in shared memory
   __shared__ __align__(8) uint64_t red_empty_bar;   // cluster split-K: every peer has finished reading this CTA's partial
+  __shared__ __align__(8) uint64_t rs_full_bar[NUM_ACC];   // folded RMSNorm: the row scales of this accumulator are in rs_smem
+  __shared__ float rs_smem[NUM_ACC][BM];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -193,11 +202,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), p.norm_fold ? 1 + NORM_WARPS : 1);   // MMA commit (+ the norm warps' reads)
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[a]), EPI_WARPS);
+      mbar_init(smem_u32(&rs_full_bar[a]), NORM_WARPS);
     }
     mbar_init(smem_u32(&epi_bar), EPI_WARPS * 32);
     if (p.cluster_k) {
@@ -354,6 +364,43 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
       }
     }
+  } else if (warp >= 2 + EPI_WARPS) {
+    // ------------------------------ norm warps (folded RMSNorm only) -----------------------
+    // One thread per tile row: as each A tile lands in the ring, add the squares of its 64 values of that row
+    // (a row is 128 contiguous bytes whose 16-byte chunks are permuted by the swizzle, which a sum ignores).
+    const int nrow = (warp - 2 - EPI_WARPS) * 32 + lane;
+    uint32_t it = 0, tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const int acc = tile_iter % NUM_ACC;
+      const uint32_t acc_ph = (tile_iter / NUM_ACC) & 1u;
+      // rs_smem[acc] was read by the epilogue of the tile that last used this accumulator
+      ok = mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY);
+      if (!ok) break;
+      float ss = 0.f;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+        if (!ok) break;
+        const uint8_t* arow = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * Cfg::kStageBytes + (size_t)nrow * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 c = *reinterpret_cast<const uint4*>(arow + ((j ^ (lane & 7)) << 4));
+          float2 f;
+          f = unpack_bf16x2(c.x); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+          f = unpack_bf16x2(c.y); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+          f = unpack_bf16x2(c.z); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+          f = unpack_bf16x2(c.w); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));   // this warp no longer needs the stage
+      }
+      if (!ok) break;
+      rs_smem[acc][nrow] = rsqrtf(ss * p.norm_inv_k + p.norm_eps);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&rs_full_bar[acc]));
+    }
   } else {
     // ------------------------------ epilogue warps ----------------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -384,6 +431,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       if (!ok) break;
       tc_fence_after();
       RB_TS(1);
+      float rscale = 1.f;
+      if (p.norm_fold) {
+        ok = mbar_wait_bounded(smem_u32(&rs_full_bar[acc]), acc_ph, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
+        if (!ok) break;
+        rscale = rs_smem[acc][q * 32 + lane];
+      }
       const int row_in = m_in + q * 32 + lane;                 // row inside the A slab
       const bool row_ok = grouped ? (q * 32 + lane < m_part) : (row_in < p.a_rows_per_part);
       const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
@@ -599,10 +652,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   // same rounding points as the unfused path: bf16(gate), bf16(silu), bf16(up), bf16(product)
-                  const float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * e])));
-                  const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * e + 1])));
-                  const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * e])));
-                  const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * e + 1])));
+                  const float g0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * e]) * rscale));
+                  const float g1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[j + 2 * e + 1]) * rscale));
+                  const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * e]) * rscale));
+                  const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * e + 1]) * rscale));
                   const float s0 = __bfloat162float(__float2bfloat16_rn(g0 / (1.f + __expf(-g0))));
                   const float s1 = __bfloat162float(__float2bfloat16_rn(g1 / (1.f + __expf(-g1))));
                   o[e] = pack_bf16x2(s0 * u0, s1 * u1);
@@ -622,7 +675,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (row_ok && ncols > 0) {
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rscale;
           const int col = n_base + c0;
           if (p.scaled_epilogue) {
 #pragma unroll
@@ -981,7 +1034,7 @@ extern "C" int rb_gemm_read_timestamps(unsigned long long* out, int n) {
 namespace rb {
 #endif
 
-constexpr int kMaxDynSmem = 227 * 1024 - 1024;   // 227 KB per CTA minus the kernel's static shared memory
+constexpr int kMaxDynSmem = 227 * 1024 - 2048;   // 227 KB per CTA minus the kernel's static shared memory (about 1.3 KB)
 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
@@ -1031,7 +1084,7 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (q.red_alias) smem = (stages * Cfg::kStageBytes > extra ? stages * Cfg::kStageBytes : extra) + 1024;
   if (p.cluster_k)
     return launch_kernel_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, (unsigned)p.split_k, q) == cudaSuccess ? 0 : -11;
-  return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
+  return launch_kernel(kern, dim3(grid), dim3(p.norm_fold ? GEMM_THREADS_NORM : GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
 }
 
 template <int BN>
@@ -1124,6 +1177,12 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.splitk_ws = a->splitk_ws;
   p.splitk_tickets = a->splitk_tickets;
   p.kb_per_split = 0;
+  p.norm_fold = a->norm_fold ? 1 : 0;
+  p.norm_eps = a->norm_eps;
+  p.norm_inv_k = 1.f / (float)a->K;
+  if (p.norm_fold && (a->a_mn_major || a->split_k > 1 || a->epi_mode != RB_EPI_STORE || a->tile_table || p.sample_ws != nullptr ||
+                      a->a_parts != 1 || p.fp8 || p.mirror || a->row_dst))
+    return -1;
   p.cluster_k = (a->cluster_split && p.split_k > 1) ? 1 : 0;
   if (p.cluster_k) {
     // slices = CTAs of one cluster; needs a power-of-two slice count up to 8 and a non-empty K range for each

@@ -94,6 +94,11 @@ typedef struct RbGemmArgs {
   // partial tiles through distributed shared memory and each CTA finishes one column slice of the tile. Needs no
   // workspace or tickets; bn / split_k must be at least 8 columns. Deterministic.
   int cluster_split;
+  // Folded RMSNorm: C = rstd(row) * (A B^T) (+bias, SwiGLU), rstd = rsqrt(mean(A[row,:]^2) + norm_eps), computed
+  // inside the kernel from the A tiles as they stream through shared memory. The caller multiplies the norm weight
+  // into B's columns beforehand. K-major A, plain store or SwiGLU epilogue, no split.
+  int norm_fold;
+  float norm_eps;
 } RbGemmArgs;
 
 // Token and log-probability from the per-tile records written by the sampling epilogue.

@@ -77,6 +77,8 @@ class RbGemmArgs(ctypes.Structure):
         ("sample_step_ptr", ctypes.c_void_p),
         ("sample_step_add", ctypes.c_ulonglong),
         ("cluster_split", ctypes.c_int),
+        ("norm_fold", ctypes.c_int),
+        ("norm_eps", ctypes.c_float),
     ]
 
 
@@ -120,8 +122,13 @@ def gemm(
     alpha: float = 1.0,
     beta: float = 1.0,
     cluster_split: bool | None = None,
+    norm_eps: float | None = None,
 ) -> torch.Tensor:
     """``C[M,N] = alpha * op(A) @ op(B)^T (+bias) (+ beta * residual)``.
+
+    ``norm_eps`` folds an RMSNorm of A's rows into the launch: ``C = rstd(row) * (A @ B^T) (+bias)`` with
+    ``rstd = rsqrt(mean(A[row]^2) + norm_eps)``; together with the norm weight multiplied into B's columns
+    beforehand this equals ``rmsnorm(A) @ B^T`` without a separate normalisation pass.
 
     K-major operands are ``[rows, K]`` row-major (a torch ``Linear`` weight is a K-major B);
     MN-major operands are ``[K, rows]`` row-major. On CUDA this launches the tcgen05 kernel;
@@ -129,7 +136,13 @@ def gemm(
     """
     if swiglu:
         assert bn >= 64 and not (a_mn_major or b_mn_major), "fused SwiGLU needs an explicit bn and K-major operands"
+    if norm_eps is not None:
+        assert not a_mn_major and split_k in (0, 1) and alpha == 1.0 and beta == 1.0, "folded RMSNorm: K-major A, no split"
+        split_k = 1
     if not a.is_cuda:
+        if norm_eps is not None:
+            af = a.float()
+            a = (af * torch.rsqrt(af.pow(2).mean(-1, keepdim=True) + norm_eps)).to(a.dtype)
         if alpha != 1.0 or beta != 1.0:
             res = alpha * gemm_reference(a, b, None, None, a_mn_major, b_mn_major, torch.float32)
             if bias is not None:
@@ -177,6 +190,8 @@ def gemm(
     args.epi_mode = EPI_STORE
     args.rank, args.world = 0, 1
     args.swiglu = int(swiglu)
+    if norm_eps is not None:
+        args.norm_fold, args.norm_eps = 1, float(norm_eps)
     if alpha != 1.0 or beta != 1.0:
         assert not swiglu, "the scaled epilogue is not combined with the fused SwiGLU"
         args.scaled_epilogue, args.alpha, args.beta = 1, alpha, beta

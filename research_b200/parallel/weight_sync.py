@@ -124,6 +124,7 @@ def sync_engine_from_buckets(engine, buckets, plan: WeightSyncPlan | None = None
         if comm is not None:
             comm.barrier()  # trainer finished writing the parameters
         plan.run()
+        runner.fold_norm_weights()   # raw projections were just rewritten: fold the norm weights in again
         if comm is not None:
             comm.barrier()  # engines finished reading: the trainer may update again
     engine.weight_version += 1

@@ -124,6 +124,42 @@ def test_gemm_cluster_split_k(cuda_device, M, N, K, bn, split, max_ctas):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,N,K,bn,max_ctas", [(256, 1152, 896, 0, 0), (8, 1152, 896, 32, 0), (300, 512, 904, 64, 0), (1000, 1024, 2048, 128, 5),
+                                               (256, 6144, 4096, 0, 0)])
+def test_gemm_folded_rmsnorm(cuda_device, M, N, K, bn, max_ctas):
+    """rstd(row) * (A W'^T) + bias with W' = W * norm weight equals rmsnorm(A) W^T + bias; the row statistics come
+    from the A tiles as they pass through shared memory."""
+    a = _rand((M, K), cuda_device, 3.0, seed=70)
+    w = _rand((N, K), cuda_device, 0.05, seed=71)
+    ln = (1 + 0.2 * _rand((K,), cuda_device, seed=72).float()).bfloat16()
+    bias = _rand((N,), cuda_device, seed=73)
+    af = a.float()
+    h = af * torch.rsqrt(af.pow(2).mean(-1, keepdim=True) + 1e-6) * ln.float()
+    want = h @ w.float().T + bias.float()
+    wf = (w.float() * ln.float()[None, :]).bfloat16()
+    got = ops.gemm(a, wf, bias=bias, bn=bn, max_ctas=max_ctas, norm_eps=1e-6)
+    _assert_close(got, want, atol=0.08, rtol=0.02, what="folded rmsnorm")
+    assert torch.equal(got, ops.gemm(a, wf, bias=bias, bn=bn, max_ctas=max_ctas, norm_eps=1e-6))
+    ops.check_status()
+
+
+def test_gemm_folded_rmsnorm_swiglu(cuda_device):
+    from research_b200.ops.gemm import interleave_gate_up
+
+    M, F, K, bn = 256, 1024, 896, 256
+    x = _rand((M, K), cuda_device, 2.0, seed=80)
+    g = _rand((F, K), cuda_device, 0.05, seed=81)
+    u = _rand((F, K), cuda_device, 0.05, seed=82)
+    ln = (1 + 0.2 * _rand((K,), cuda_device, seed=83).float()).bfloat16()
+    xf = x.float()
+    h = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * ln.float())
+    want = torch.nn.functional.silu(h @ g.float().T) * (h @ u.float().T)
+    fold = lambda t: (t.float() * ln.float()[None, :]).bfloat16()
+    got = ops.gemm(x, interleave_gate_up(fold(g), fold(u), bn), bn=bn, swiglu=True, norm_eps=1e-6)
+    _assert_close(got, want, atol=0.05, rtol=0.03, what="folded rmsnorm + swiglu")
+    ops.check_status()
+
+
 def test_gemm_strided_views(cuda_device):
     big = _rand((256, 2048), cuda_device, seed=9)
     a = big[:, 512:1024]  # lda = 2048
