@@ -119,14 +119,23 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int world, i
   const int EL = e_hi - e_lo;
   if (cursor != nullptr) {
     // where this rank's rows for expert e start in the owner's expert-ordered receive buffer: the rows of the
-    // owner's lower experts (from all ranks) plus the rows of lower source ranks for e
+    // owner's lower experts (from all ranks) plus the rows of lower source ranks for e. Column sums go through
+    // shared memory first so that no thread walks the count matrix serially.
+    __shared__ int tot[256], below[256];
     const int epr = E / world;
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
-      const int owner = e / epr;
-      int o = 0;
-      for (int ee = owner * epr; ee < e; ++ee)
-        for (int r = 0; r < world; ++r) o += counts_all[r * E + ee];
-      for (int r = 0; r < rank; ++r) o += counts_all[r * E + e];
+      int a = 0, b = 0;
+      for (int r = 0; r < world; ++r) {
+        const int c = counts_all[r * E + e];
+        a += c;
+        if (r < rank) b += c;
+      }
+      tot[e] = a; below[e] = b;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      int o = below[e];
+      for (int ee = (e / epr) * epr; ee < e; ++ee) o += tot[ee];
       cursor[E + e] = o;
     }
   }

@@ -197,7 +197,7 @@ def gemm(
         args.scaled_epilogue, args.alpha, args.beta = 1, alpha, beta
         split_k = 1
     if split_k == 0:
-        split_k, auto_bn = _auto_split_k(M, N, K, a_mn_major or b_mn_major or swiglu or out_f32 or bn != 0)
+        split_k, auto_bn = _auto_split_k(M, N, K, a_mn_major or b_mn_major or swiglu or bn != 0)
         if auto_bn:
             args.bn = auto_bn
     if cluster_split is None:

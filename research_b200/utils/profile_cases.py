@@ -63,13 +63,14 @@ def case_flash_bwd() -> None:
 
 def case_decode_step() -> None:
     """Two eager decode steps at batch 256 (for a per-launch time list); the model preset comes from
-    RB_PROFILE_MODEL (default: the 0.5B flagship shape)."""
+    RB_PROFILE_MODEL (default: the 0.5B flagship shape), optionally cut to RB_PROFILE_LAYERS layers."""
     from ..inference import EngineConfig, InferenceEngine, SamplingParams
     from ..models import get_preset, init_random_weights
 
     import os
 
-    cfg = get_preset(os.environ.get("RB_PROFILE_MODEL", "qwen2.5-0.5b"))
+    over = {"num_layers": int(os.environ["RB_PROFILE_LAYERS"])} if os.environ.get("RB_PROFILE_LAYERS") else {}
+    cfg = get_preset(os.environ.get("RB_PROFILE_MODEL", "qwen2.5-0.5b"), **over)   # fewer layers keep big models small
     dev = torch.device("cuda:0")
     w = init_random_weights(cfg, seed=0, dtype=torch.bfloat16, device=dev)
     eng = InferenceEngine(EngineConfig(max_batch_size=256, max_model_len=2048, num_kv_blocks=20000, ignore_eos=True,
