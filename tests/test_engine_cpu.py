@@ -234,3 +234,60 @@ def test_engine_sampling_seeded_stop_tokens_and_weight_update():
     assert d[0].completion_tokens == _oracle_greedy(w2, cfg, p[0], 4)
     with pytest.raises(ValueError):
         eng.add_request([1] * 100, SamplingParams(max_tokens=100))
+
+
+def test_folded_rmsnorm_matches_separate_norm(monkeypatch):
+    """Norm weights folded into the projections + row statistics inside the GEMM give the same tokens and
+    log-probabilities as separate RMSNorm calls (CPU twins of both paths)."""
+    import torch
+
+    from research_b200.inference import EngineConfig, InferenceEngine, SamplingParams
+    from research_b200.models import get_preset, init_random_weights
+
+    cfg = get_preset("tiny-qwen3", num_layers=2)
+    w = init_random_weights(cfg, seed=3)
+    for k in list(w):
+        if k.endswith("layernorm.weight"):
+            w[k] = 1 + 0.3 * torch.randn(w[k].shape, generator=torch.Generator().manual_seed(len(k)))
+    ecfg = EngineConfig(max_batch_size=4, max_model_len=64, num_kv_blocks=32, use_cuda_graphs=False, ignore_eos=True)
+    prompts = [[5, 6, 7, 8, 9], [11, 12, 13]]
+    sp = SamplingParams(temperature=0.0, max_tokens=6)
+    folded = InferenceEngine(ecfg, cfg, w, device="cpu")
+    assert folded.runner.fold_norm
+    a = folded.generate(prompts, sp)
+    monkeypatch.setenv("RB_NO_NORM_FOLD", "1")
+    plain = InferenceEngine(ecfg, cfg, w, device="cpu")
+    assert not plain.runner.fold_norm
+    b = plain.generate(prompts, sp)
+    for x, y in zip(a, b):
+        assert x.completion_tokens == y.completion_tokens
+        assert max(abs(p - q) for p, q in zip(x.logprobs, y.logprobs)) < 1e-4
+    # a second load must not fold twice
+    folded.update_weights(w)
+    assert folded.generate(prompts, sp)[0].completion_tokens == a[0].completion_tokens
+
+
+def test_lazy_random_weights_and_split_chooser():
+    import torch
+
+    from research_b200.models import LazyRandomWeights, get_preset
+    from research_b200.models.weights import param_shapes
+    from research_b200.ops.gemm import _cluster_split_choice
+
+    cfg = get_preset("tiny-moe", num_layers=2)
+    lw = LazyRandomWeights(cfg, seed=1)
+    assert set(lw) == set(param_shapes(cfg)) and len(lw) == len(param_shapes(cfg))
+    n = "model.layers.1.mlp.experts.3.up_proj.weight"
+    assert torch.equal(lw[n], lw[n]) and not torch.equal(lw[n], LazyRandomWeights(cfg, seed=2)[n])
+    assert float(lw["model.norm.weight"].min()) == 1.0
+    for M in (1, 64, 256):
+        for N in (128, 896, 1152, 4096, 6144, 28672):
+            for K in (768, 896, 2048, 4096, 14336):
+                s, bn = _cluster_split_choice(M, N, K)
+                if s > 1:
+                    units = -(-M // 128) * -(-N // bn) * s
+                    per = -(-(-(-K // 64)) // s)
+                    assert s in (2, 4, 8) and bn // s >= 8 and units <= 148 - 148 % s and (s - 1) * per < -(-K // 64)
+                else:
+                    assert bn == 0
+    assert _cluster_split_choice(256, 896, 896) == (1, 0) and _cluster_split_choice(256, 896, 4864)[0] > 1
