@@ -60,3 +60,18 @@ def test_phase_timer_cpu():
     assert set(s) == {"a_s", "b_s"} and s["a_s"] >= 0
     t.reset()
     assert t.summary() == {}
+
+
+def test_grpo_bench_cpu_smoke():
+    """The end-to-end GRPO step benchmark runs on the CPU twins and reports every phase."""
+    import json
+    import subprocess
+    import sys
+
+    proc = subprocess.run([sys.executable, "-m", "research_b200.utils.grpo_bench", "--model", "tiny-qwen2", "--prompts", "4",
+                           "--samples", "4", "--prompt-len", "16", "--max-tokens", "8", "--steps", "1", "--minibatches", "2",
+                           "--device", "cpu"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    row = json.loads([ln for ln in proc.stdout.splitlines() if ln.startswith("{")][-1])
+    assert row["bench"] == "grpo_step" and row["samples_per_step"] == 16 and row["rollout_s"] > 0 and row["train_s"] > 0
+    assert row["rollout_tokens_per_s"] > 0 and row["sync_s"] >= 0
