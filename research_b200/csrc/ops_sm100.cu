@@ -267,13 +267,21 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
                       const float* __restrict__ temperature, const unsigned long long* __restrict__ seeds,
                       const unsigned long long* __restrict__ step_ptr, unsigned long long step_add,
-                      int* __restrict__ out_tokens, float* __restrict__ out_logprobs) {
+                      int* __restrict__ out_tokens, float* __restrict__ out_logprobs,
+                      float4* __restrict__ partials /*[rows][splits], splits > 1 only*/, int* __restrict__ tickets /*[rows]*/) {
   pdl_launch_dependents();
   pdl_wait();
+  // grid (splits, rows): with few rows the vocabulary of a row is cut into `splits` contiguous chunks so that all
+  // SMs share the transcendental work (three per element); the last CTA of a row merges the chunk records in
+  // chunk order
+  const int splits = gridDim.x;
+  const int chunk = (((V + splits - 1) / splits) + 3) & ~3;
+  const int v_lo = blockIdx.x * chunk;
+  const int v_hi = min(V, v_lo + chunk);
   // The step counter lives in device memory so a captured CUDA graph draws fresh noise on
   // every replay (the host bumps the counter between replays).
   const unsigned long long step = step_add + (step_ptr != nullptr ? *step_ptr : 0ull);
-  const int row = blockIdx.x;
+  const int row = blockIdx.y;
   const float* lr = logits + (long long)row * ld;
   const float temp = temperature[row];
   const bool greedy = temp <= 0.f;
@@ -285,14 +293,14 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
   float best = -INFINITY;              // best perturbed score
   int best_i = 0x7fffffff;
   const bool vec_ok = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15) == 0);
-  for (int i = threadIdx.x * 4; i < V; i += SAMPLE_THREADS * 4) {
+  for (int i = v_lo + threadIdx.x * 4; i < v_hi; i += SAMPLE_THREADS * 4) {
     float v[4];
-    if (i + 3 < V && vec_ok) {
+    if (i + 3 < v_hi && vec_ok) {
       float4 f = __ldcs(reinterpret_cast<const float4*>(lr + i));
       v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = (i + j < V) ? lr[i + j] : -INFINITY;
+      for (int j = 0; j < 4; ++j) v[j] = (i + j < v_hi) ? lr[i + j] : -INFINITY;
     }
     // one rescale of the running sum per 4 elements instead of a branch per element
     const float m4 = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
@@ -346,6 +354,23 @@ sample_logprob_kernel(const float* __restrict__ logits, long long ld, int V,
       if (b2 > best || (b2 == best && i2 < best_i)) { best = b2; best_i = i2; }
     }
     if (lane == 0) {
+      if (splits > 1) {
+        partials[(long long)row * splits + blockIdx.x] = make_float4(m, ssum, best, __int_as_float(best_i));
+        __threadfence();
+        const int tk = atomicAdd(&tickets[row], 1);
+        if (tk != splits - 1) return;
+        tickets[row] = 0;           // ready for the next launch
+        __threadfence();
+        m = -INFINITY; ssum = 0.f; best = -INFINITY; best_i = 0x7fffffff;
+        for (int c = 0; c < splits; ++c) {   // chunk order: the sums do not depend on which CTA finished last
+          const float4 r = __ldcg(&partials[(long long)row * splits + c]);
+          const int i2 = __float_as_int(r.w);
+          const float mn = fmaxf(m, r.x);
+          ssum = (mn == -INFINITY) ? 0.f : ssum * __expf(m - mn) + r.y * __expf(r.x - mn);
+          m = mn;
+          if (r.z > best || (r.z == best && i2 < best_i)) { best = r.z; best_i = i2; }
+        }
+      }
       if (best_i >= V) best_i = 0;
       out_tokens[row] = best_i;
       out_logprobs[row] = lr[best_i] - (m + __logf(ssum));
@@ -492,8 +517,22 @@ extern "C" int rb_sample_logprob(const float* logits, long long ld, int B, int V
                                  unsigned long long step_add, int* out_tokens, float* out_logprobs,
                                  cudaStream_t stream) {
   if (B <= 0) return 0;
-  return launch_kernel(sample_logprob_kernel, dim3(B), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
-                       seeds, step_ptr, step_add, out_tokens, out_logprobs) == cudaSuccess ? 0 : -11;
+  return launch_kernel(sample_logprob_kernel, dim3(1, B), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
+                       seeds, step_ptr, step_add, out_tokens, out_logprobs, (float4*)nullptr, (int*)nullptr) == cudaSuccess ? 0 : -11;
+}
+// Same with every row's vocabulary cut into `splits` chunks (grid splits x B). `partials` holds B * splits float4
+// records, `tickets` B zero-initialised counters (they reset themselves). splits <= 0 picks about four CTAs per SM.
+extern "C" int rb_sample_logprob_split(const float* logits, long long ld, int B, int V, const float* temperature,
+                                       const unsigned long long* seeds, const unsigned long long* step_ptr,
+                                       unsigned long long step_add, int* out_tokens, float* out_logprobs, void* partials,
+                                       int* tickets, int splits, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (splits <= 0) splits = (4 * 148 + B - 1) / B;
+  if (splits > 8) splits = 8;
+  while (splits > 1 && V / splits < 4096) --splits;
+  if (splits > 1 && (partials == nullptr || tickets == nullptr)) return -1;
+  return launch_kernel(sample_logprob_kernel, dim3(splits, B), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, temperature,
+                       seeds, step_ptr, step_add, out_tokens, out_logprobs, (float4*)partials, tickets) == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int rb_token_logprob(const float* logits, long long ld, int B, int V, const int* tokens,

@@ -22,6 +22,8 @@ def _lib() -> ctypes.CDLL:
     if not getattr(lib, "_rb_typed_s", False):
         lib.rb_sample_logprob.argtypes = [c_vp, c_ll, c_int, c_int, c_vp, c_vp, c_vp, c_ull, c_vp, c_vp, c_vp]
         lib.rb_sample_logprob.restype = c_int
+        lib.rb_sample_logprob_split.argtypes = [c_vp, c_ll, c_int, c_int, c_vp, c_vp, c_vp, c_ull, c_vp, c_vp, c_vp, c_vp, c_int, c_vp]
+        lib.rb_sample_logprob_split.restype = c_int
         lib.rb_token_logprob.argtypes = [c_vp, c_ll, c_int, c_int, c_vp, c_vp, c_vp]
         lib.rb_token_logprob.restype = c_int
         lib._rb_typed_s = True
@@ -60,10 +62,30 @@ def sample_with_logprobs(logits, temperatures, seeds=None, step: int = 0, step_t
         out_tokens = torch.empty(B, dtype=torch.int32, device=logits.device)
     if out_logprobs is None:
         out_logprobs = torch.empty(B, dtype=torch.float32, device=logits.device)
-    rc = _lib().rb_sample_logprob(ptr(logits), logits.stride(0), B, V, ptr(temperatures), ptr(seeds), ptr(step_tensor),
-                                  step, ptr(out_tokens), ptr(out_logprobs), stream_handle(logits.device))
-    check_rc(rc, "rb_sample_logprob")
+    part, tickets = _split_scratch(logits.device, B)
+    rc = _lib().rb_sample_logprob_split(ptr(logits), logits.stride(0), B, V, ptr(temperatures), ptr(seeds), ptr(step_tensor),
+                                        step, ptr(out_tokens), ptr(out_logprobs), ptr(part), ptr(tickets), 0,
+                                        stream_handle(logits.device))
+    check_rc(rc, "rb_sample_logprob_split")
     return out_tokens, out_logprobs
+
+
+_SPLIT_SCRATCH: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+_SPLIT_KEEP: list = []
+
+
+def _split_scratch(device: torch.device, rows: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-device chunk records ([rows, 8 chunks, 4] fp32) and row tickets of the split sampler; launches on one
+    stream run in order, so one pair serves them all. Never shrinks (captured graphs keep the address)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    cur = _SPLIT_SCRATCH.get(idx)
+    if cur is None or cur[1].numel() < rows:
+        n = max(rows, 1024)
+        if cur is not None:
+            _SPLIT_KEEP.append(cur)       # a captured graph may still point at the old pair
+        _SPLIT_SCRATCH[idx] = (torch.empty(n * 8 * 4, dtype=torch.float32, device=device),
+                               torch.zeros(n, dtype=torch.int32, device=device))
+    return _SPLIT_SCRATCH[idx]
 
 
 def token_logprobs(logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
