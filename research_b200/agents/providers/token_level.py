@@ -69,7 +69,10 @@ async def rollout_native_token_level(actor: Actor, run_config: RunConfig) -> Act
     if tok is None:
         raise NonRetryableError("token-level rollouts need a tokenizer", provider="native")
     prompt_ids = build_input_ids_from_trajectory(actor, tok, run_config.suffix_ids)
-    out = engine.generate([prompt_ids], SamplingParams(temperature=ep.temperature, max_tokens=ep.max_tokens))[0]
+    # concurrent agent loops share the engine's batches through its asyncio front
+    from ...inference.async_engine import batcher_for
+
+    out = await batcher_for(engine).generate(prompt_ids, SamplingParams(temperature=ep.temperature, max_tokens=ep.max_tokens))
     return _completion_from_tokens(actor, prompt_ids, list(out.completion_tokens), list(out.logprobs), out.finish_reason,
                                    tok, ep.model or "native", out.weight_version)
 

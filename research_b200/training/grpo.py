@@ -108,6 +108,7 @@ def _create_tito_generate_fn(engine: InferenceEngine, config: GRPOConfig, tokeni
                                   metadata=meta, weight_version=o.weight_version))
         return samples
 
+    generate.batched = True     # the rollout manager may pass the prompts of all groups in one call
     return generate
 
 

@@ -31,11 +31,8 @@ class AsyncRolloutManager:
             out = await out
         return list(out)
 
-    async def _generate_group(self, group: list[Sample], sem: asyncio.Semaphore, **kw) -> list[Sample]:
-        async with sem:
-            if self._abort:
-                return []
-            out = await self._call_generate([s.prompt for s in group], **kw)
+    @staticmethod
+    def _adopt(group: list[Sample], out: list[Sample]) -> list[Sample]:
         for src, dst in zip(group, out):
             dst.group_index, dst.index = src.group_index, src.index
             if dst.ground_truth is None:
@@ -44,7 +41,25 @@ class AsyncRolloutManager:
                 dst.status = Status.COMPLETED
         return out
 
+    async def _generate_group(self, group: list[Sample], sem: asyncio.Semaphore, **kw) -> list[Sample]:
+        async with sem:
+            if self._abort:
+                return []
+            out = await self._call_generate([s.prompt for s in group], **kw)
+        return self._adopt(group, out)
+
     async def _generate_samples_parallel(self, groups: list[list[Sample]], **kw) -> list[list[Sample]]:
+        if getattr(self.config.generate_fn, "batched", False):
+            # an in-process engine batches continuously on its own: hand it every prompt of every group in ONE call
+            # (one call per group would run the engine at a batch of n_samples_per_prompt, group after group)
+            if self._abort:
+                return [[] for _ in groups]
+            flat = await self._call_generate([s.prompt for g in groups for s in g], **kw)
+            out, at = [], 0
+            for g in groups:
+                out.append(self._adopt(g, flat[at:at + len(g)]))
+                at += len(g)
+            return out
         sem = asyncio.Semaphore(self.max_concurrency)
         return list(await asyncio.gather(*[self._generate_group(g, sem, **kw) for g in groups]))
 

@@ -291,3 +291,32 @@ def test_lazy_random_weights_and_split_chooser():
                 else:
                     assert bn == 0
     assert _cluster_split_choice(256, 896, 896) == (1, 0) and _cluster_split_choice(256, 896, 4864)[0] > 1
+
+
+def test_async_batcher_shares_batches():
+    """Eight coroutines generating concurrently run in shared engine steps, not one after another."""
+    import asyncio
+
+    from research_b200.inference import EngineConfig, InferenceEngine, SamplingParams
+    from research_b200.inference.async_engine import batcher_for
+    from research_b200.models import get_preset, init_random_weights
+
+    cfg = get_preset("tiny-qwen2", num_layers=2)
+    eng = InferenceEngine(EngineConfig(max_batch_size=8, max_model_len=64, num_kv_blocks=64, use_cuda_graphs=False, ignore_eos=True),
+                          cfg, init_random_weights(cfg, seed=0), device="cpu")
+    sp = SamplingParams(temperature=0.0, max_tokens=6)
+    prompts = [[3 + i, 4, 5, 6 + i] for i in range(8)]
+
+    async def go():
+        b = batcher_for(eng)
+        outs = await asyncio.gather(*[b.generate(p, sp) for p in prompts])
+        # a second wave from coroutines that continue after their first result (multi-turn agents)
+        more = await asyncio.gather(*[b.generate(p + list(o.completion_tokens), SamplingParams(temperature=0.0, max_tokens=2))
+                                      for p, o in zip(prompts[:3], outs[:3])])
+        return b, outs, more
+
+    b, outs, more = asyncio.run(go())
+    ref = eng.generate(prompts, sp)
+    assert [o.completion_tokens for o in outs] == [r.completion_tokens for r in ref]
+    assert b.max_rows == 8 and b.steps <= 6 + 2 + 4, (b.max_rows, b.steps)   # ~one step per token, not per request
+    assert all(len(m.completion_tokens) == 2 for m in more) and batcher_for(eng) is b
