@@ -207,18 +207,28 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
 // SwiGLU backward: given gate|up [T,2F] and dout [T,F] writes dgate|dup [T,2F].
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dout,
                                   __nv_bfloat16* __restrict__ dgu, long long T, int F) {
-  const long long n = T * F;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+  // 8 columns (16 bytes) per thread and step; F % 8 == 0 is checked by the launcher
+  const int fv = F >> 3;
+  const long long nvec = T * fv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / F;
-    const int c = (int)(i % F);
-    const float g = __bfloat162float(gu[t * 2 * F + c]);
-    const float u = __bfloat162float(gu[t * 2 * F + F + c]);
-    const float dy = __bfloat162float(dout[i]);
-    const float sig = 1.f / (1.f + __expf(-g));
-    const float silu = g * sig;
-    dgu[t * 2 * F + c] = __float2bfloat16_rn(dy * u * (sig + silu * (1.f - sig)));
-    dgu[t * 2 * F + F + c] = __float2bfloat16_rn(dy * silu);
+    const long long t = i / fv;
+    const int c = (int)(i % fv) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * F + c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * F + F + c);
+    const uint4 d4 = *reinterpret_cast<const uint4*>(dout + t * F + c);
+    const uint32_t gi[4] = {g4.x, g4.y, g4.z, g4.w}, ui[4] = {u4.x, u4.y, u4.z, u4.w}, di[4] = {d4.x, d4.y, d4.z, d4.w};
+    uint32_t og[4], ou[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = unpack_bf16x2(gi[j]), u = unpack_bf16x2(ui[j]), dy = unpack_bf16x2(di[j]);
+      const float s0 = 1.f / (1.f + __expf(-g.x)), s1 = 1.f / (1.f + __expf(-g.y));
+      const float l0 = g.x * s0, l1 = g.y * s1;
+      og[j] = pack_bf16x2(dy.x * u.x * (s0 + l0 * (1.f - s0)), dy.y * u.y * (s1 + l1 * (1.f - s1)));
+      ou[j] = pack_bf16x2(dy.x * l0, dy.y * l1);
+    }
+    *reinterpret_cast<uint4*>(dgu + t * 2 * F + c) = make_uint4(og[0], og[1], og[2], og[3]);
+    *reinterpret_cast<uint4*>(dgu + t * 2 * F + F + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
   }
 }
 
@@ -497,7 +507,8 @@ extern "C" int rb_swiglu_bounded(const void* gu, void* out, long long T, int F, 
 
 extern "C" int rb_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int F,
                              cudaStream_t stream) {
-  const long long n = T * F;
+  if (F % 8 != 0 || T <= 0) return -1;
+  const long long n = T * (F / 8);
   long long grid = (n + 255) / 256;
   if (grid > 148 * 32) grid = 148 * 32;
   swiglu_bwd_kernel<<<(unsigned)grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dout,

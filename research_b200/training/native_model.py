@@ -34,22 +34,31 @@ from ..ops.flash import flash_attention
 
 
 # ------------------------------------------------------------------------------ autograd glue
+def _rows_ok(t: torch.Tensor) -> torch.Tensor:
+    """The GEMM takes any row stride (16-byte aligned rows, unit column stride): only other layouts are copied."""
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
 class _Linear(torch.autograd.Function):
+    """``y = x W^T (+ bias) (+ residual)``; the residual add rides in the GEMM epilogue and its gradient is ``dy``."""
+
     @staticmethod
-    def forward(ctx, x, w, gw, bias, gb):
+    def forward(ctx, x, w, gw, bias, gb, residual=None):
         ctx.save_for_backward(x, w)
-        ctx.gw, ctx.gb = gw, gb
-        return ops.gemm(x, w, bias=bias)
+        ctx.gw, ctx.gb, ctx.has_res = gw, gb, residual is not None
+        return ops.gemm(x, w, bias=bias, residual=residual)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dy = dy.contiguous()
+        dy = _rows_ok(dy)
         dx = ops.gemm(dy, w, b_mn_major=True)                      # [M,N] x [N,K] -> [M,K]
         ops.gemm(dy, x, residual=ctx.gw, out=ctx.gw, a_mn_major=True, b_mn_major=True)  # gw += dY^T X
         if ctx.gb is not None:
             ctx.gb.add_(dy.float().sum(0).to(ctx.gb.dtype))
-        return dx, None, None, None, None
+        return dx, None, None, None, None, (dy if ctx.has_res else None)
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -88,7 +97,7 @@ class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         (gu,) = ctx.saved_tensors
-        return ops.swiglu_backward(gu, dy.contiguous())
+        return ops.swiglu_backward(gu, dy.contiguous())   # (the kernel indexes dy densely)
 
 
 class _Embedding(torch.autograd.Function):
@@ -155,6 +164,7 @@ class NativeCausalLM:
         self.on_gpu = device.type == "cuda"
         self.ckpt = activation_checkpointing
         self._params: dict[str, torch.Tensor] = {}
+        self._stacked: dict[str, tuple] = {}
         self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.trace: dict | None = None
         self.table = ops.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, device=device) \
@@ -170,6 +180,24 @@ class NativeCausalLM:
 
     def g(self, name: str) -> torch.Tensor:
         return self.b.grad_view(name)
+
+    def stacked(self, names: tuple[str, ...]):
+        """(parameter leaf, gradient view) of several matrices that lie back to back in the flat bucket, seen as one
+        ``[sum(rows), cols]`` matrix, so that e.g. gate and up projections run as one GEMM; ``(None, None)`` when
+        they are not adjacent."""
+        key = "+".join(names)
+        if key not in self._stacked:
+            specs = [self.b.specs[n] for n in names]
+            ok = all(a.offset + a.numel == b.offset and a.shape[1:] == b.shape[1:] and len(a.shape) == 2
+                     for a, b in zip(specs, specs[1:]))
+            if ok:
+                rows, cols = sum(sp.shape[0] for sp in specs), specs[0].shape[1]
+                o = specs[0].offset
+                leaf = self.b.params[o:o + rows * cols].view(rows, cols).detach().requires_grad_(True)
+                self._stacked[key] = (leaf, self.b.grads[o:o + rows * cols].view(rows, cols))
+            else:
+                self._stacked[key] = (None, None)
+        return self._stacked[key]
 
     def state_dict(self) -> dict[str, torch.Tensor]:
         return {n: self.b.param_view(n) for n in self.b.specs}
@@ -208,9 +236,10 @@ class NativeCausalLM:
         a = pre + "self_attn."
         H, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
 
-        def lin(inp, name, bias=False):
+        def lin(inp, name, bias=False, residual=None):
             bn = name.replace(".weight", ".bias")
-            return _Linear.apply(inp, self.p(name), self.g(name), self.p(bn) if bias else None, self.g(bn) if bias else None)
+            return _Linear.apply(inp, self.p(name), self.g(name), self.p(bn) if bias else None, self.g(bn) if bias else None,
+                                 residual)
 
         h = _RMSNorm.apply(x, self.p(pre + "input_layernorm.weight"), self.g(pre + "input_layernorm.weight"), cfg.rms_norm_eps)
         q = lin(h, a + "q_proj.weight", cfg.attention_bias).view(-1, H, D)
@@ -232,15 +261,18 @@ class NativeCausalLM:
                 q.view(B, Tn, H, D).transpose(1, 2), k.view(B, Tn, Hkv, D).transpose(1, 2),
                 v.view(B, Tn, Hkv, D).transpose(1, 2), is_causal=True, scale=1.0 / math.sqrt(D), enable_gqa=True)
             o = o.transpose(1, 2).reshape(B * Tn, H * D)
-        x = x + lin(o, a + "o_proj.weight")
+        x = lin(o, a + "o_proj.weight", residual=x)
         h = _RMSNorm.apply(x, self.p(pre + "post_attention_layernorm.weight"),
                            self.g(pre + "post_attention_layernorm.weight"), cfg.rms_norm_eps)
         m = pre + "mlp."
         if cfg.is_moe and i >= cfg.first_k_dense_replace:
             return x + self._moe(h, m, lin)
-        gu = torch.cat([lin(h, m + "gate_proj.weight"), lin(h, m + "up_proj.weight")], dim=-1)
-        x = x + lin(_SwiGLU.apply(gu), m + "down_proj.weight")
-        return x
+        wgu, ggu = self.stacked((m + "gate_proj.weight", m + "up_proj.weight"))
+        if wgu is not None:       # gate and up are neighbours in the bucket: one GEMM forward, dgrad and wgrad
+            gu = _Linear.apply(h, wgu, ggu, None, None, None)
+        else:
+            gu = torch.cat([lin(h, m + "gate_proj.weight"), lin(h, m + "up_proj.weight")], dim=-1)
+        return lin(_SwiGLU.apply(gu), m + "down_proj.weight", residual=x)
 
     def _moe(self, h, m: str, lin):
         """Mixture-of-experts MLP for training: router and expert projections are tcgen05 GEMMs (forward, dgrad

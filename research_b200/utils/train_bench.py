@@ -36,6 +36,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--loss", default="sft")
     ap.add_argument("--no-checkpointing", action="store_true")
+    ap.add_argument("--micro-batch", type=int, default=1, help="sequences per forward/backward pass")
+    ap.add_argument("--kernel-table", default="", help="write a table of device time per kernel (one extra step under the "
+                                                       "PyTorch profiler, after the timed steps) to this file")
     ap.add_argument("--peak-tflops", type=float, default=1426.3, help="sustained cuBLAS bf16 TFLOP/s per GPU for the MFU line")
     args = ap.parse_args()
 
@@ -53,7 +56,7 @@ def main() -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     cfg = get_preset(args.model)
-    kw = dict(loss_fn=args.loss, lr=1e-5, trainer_config=TrainerConfig(micro_batch_size=1), activation_checkpointing=not args.no_checkpointing,
+    kw = dict(loss_fn=args.loss, lr=1e-5, trainer_config=TrainerConfig(micro_batch_size=args.micro_batch), activation_checkpointing=not args.no_checkpointing,
               need_entropy=False)
     backend = FSDPTrainingBackend(cfg, None, **kw) if world > 1 else NativeTrainingBackend(cfg, None, device=dev, **kw)
     g = torch.Generator().manual_seed(1234 + local)
@@ -90,6 +93,19 @@ def main() -> None:
                           "mfu_of_sustained_cublas": round(mfu, 3), "loss": round(float(m.get("loss", 0.0)), 4),
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
                           "activation_checkpointing": not args.no_checkpointing, "dtype": "bf16", "data": "synthetic"}))
+    if args.kernel_table and local == 0:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            step()
+            torch.cuda.synchronize()
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows) or 1.0
+        with open(args.kernel_table, "w") as f:
+            f.write(f"# device time per kernel, one training step ({args.model}, batch {args.batch} x seq {args.seq}, "
+                    f"micro-batch {args.micro_batch}); total {total / 1e3:.1f} ms under the profiler\n")
+            for e in rows[:40]:
+                f.write(f"{e.device_time_total / total * 100:5.1f}%  n={e.count:5d}  avg={e.device_time_total / max(e.count, 1):9.1f}us  {e.key[:110]}\n")
     if world > 1:
         dist.destroy_process_group()
 
