@@ -197,7 +197,7 @@ def gemm(
         args.scaled_epilogue, args.alpha, args.beta = 1, alpha, beta
         split_k = 1
     if split_k == 0:
-        split_k, auto_bn = _auto_split_k(M, N, K, a_mn_major or b_mn_major or swiglu or bn != 0)
+        split_k, auto_bn = _auto_split_k(M, N, K, swiglu or bn != 0, 64 if b_mn_major else 32)
         if auto_bn:
             args.bn = auto_bn
     if cluster_split is None:
@@ -220,9 +220,9 @@ _SPLITK: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
 _SPLITK_MODE = os.environ.get("RB_SPLITK_MODE", "cluster")   # "l2" keeps the workspace + ticket reduction
 
 
-def _auto_split_k(M: int, N: int, K: int, excluded: bool) -> tuple[int, int]:
-    """Tile width and K split for decode-sized problems (M <= 256): returns ``(split, bn)``, ``(1, 0)`` = leave it
-    to the kernel.
+def _auto_split_k(M: int, N: int, K: int, excluded: bool, min_bn: int = 32) -> tuple[int, int]:
+    """Tile width and K split for problems with few output tiles and a long K (decode-sized GEMMs, weight gradients
+    of narrow projections): returns ``(split, bn)``, ``(1, 0)`` = leave it to the kernel.
 
     These launches are bound by what one SM can pull from L2 (about 80 GB/s measured): a CTA streams
     ``(128 + bn) * 128`` bytes per k-block, and with narrow tiles or few tiles most of the 148 SMs idle. Splitting
@@ -230,18 +230,18 @@ def _auto_split_k(M: int, N: int, K: int, excluded: bool) -> tuple[int, int]:
     the machine without a workspace round trip. The choice minimises a small cost model fitted to B200
     timings with weights streamed from HBM (M=256): N=896,K=4864 29.1 us unsplit -> 18.7 (bn 64, 4 slices);
     N=4096,K=14336 74.6 -> 54.5 (bn 128, 2 slices); K <= 896 is never split (12.2 us either way)."""
-    if excluded or M > 256 or N % 8 or os.environ.get("RB_NO_SPLITK"):
-        return 1, 0
+    if excluded or N % 8 or os.environ.get("RB_NO_SPLITK") or -(-M // 128) * -(-N // 256) > 74:
+        return 1, 0       # more than half a wave of the widest tiles: nothing to gain from a split
     if _SPLITK_MODE == "l2":
-        return _auto_split_k_workspace(M, N, K)
-    return _cluster_split_choice(M, N, K)
+        return _auto_split_k_workspace(M, N, K) if M <= 256 and min_bn == 32 else (1, 0)
+    return _cluster_split_choice(M, N, K, min_bn)
 
 
 _STREAM_GBS = {32: 80e3, 64: 85e3, 128: 98e3, 256: 114e3}     # bytes per microsecond one SM pulls from L2, by tile width
 
 
 @functools.lru_cache(maxsize=4096)
-def _cluster_split_choice(M: int, N: int, K: int) -> tuple[int, int]:
+def _cluster_split_choice(M: int, N: int, K: int, min_bn: int = 32) -> tuple[int, int]:
     """Cheapest (split, bn) under a model fitted to 100 timed B200 launches (mean error 10 %): per k-block a CTA
     streams ``(128 + bn) * 128`` bytes at the per-SM rate above; a cluster reduction costs 1 + 0.045 bn (2 slices),
     1.5 + 0.025 bn (4) or 3 + 0.03 bn microseconds (8); split launches must fit one wave."""
@@ -249,7 +249,7 @@ def _cluster_split_choice(M: int, N: int, K: int) -> tuple[int, int]:
     num_kb = -(-K // 64)
     best = None
     for bn in (256, 128, 64, 32):
-        if bn > 32 and N < bn:
+        if (bn > 32 and N < bn) or bn < min_bn:
             continue
         n_tiles = -(-N // bn)
         stage_us = (128 + bn) * 128 / _STREAM_GBS[bn]

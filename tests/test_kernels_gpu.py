@@ -160,6 +160,28 @@ def test_gemm_folded_rmsnorm_swiglu(cuda_device):
     ops.check_status()
 
 
+@pytest.mark.parametrize("K,M,N", [(16384, 128, 896), (16384, 896, 896), (4096, 1152, 896), (8192, 256, 520)])
+def test_gemm_weight_gradient_shapes_split(cuda_device, K, M, N):
+    """Weight-gradient GEMMs of narrow projections (both operands MN-major, few output tiles, K = tokens): the
+    chooser cuts K over a cluster; accumulation into the gradient buffer happens in the epilogue."""
+    from research_b200.ops.gemm import _auto_split_k
+
+    dy = _rand((K, M), cuda_device, 0.3, seed=90)
+    x = _rand((K, N), cuda_device, 0.3, seed=91)
+    acc = _rand((M, N), cuda_device, seed=92)
+    want = dy.float().T @ x.float() + acc.float()
+    got = acc.clone()
+    ops.gemm(dy, x, residual=got, out=got, a_mn_major=True, b_mn_major=True)
+    rel = (got.float() - want).norm() / want.norm()
+    assert rel < 5e-3, float(rel)
+    again = acc.clone()
+    ops.gemm(dy, x, residual=again, out=again, a_mn_major=True, b_mn_major=True)
+    assert torch.equal(got, again)
+    if K >= 16384:
+        assert _auto_split_k(M, N, K, False, 64)[0] > 1     # these shapes are meant to take the split path
+    ops.check_status()
+
+
 def test_gemm_strided_views(cuda_device):
     big = _rand((256, 2048), cuda_device, seed=9)
     a = big[:, 512:1024]  # lda = 2048
