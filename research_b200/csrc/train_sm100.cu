@@ -156,6 +156,89 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   for (int i = threadIdx.x; i < d; i += blockDim.x) dw_partial[(long long)blockIdx.x * d + i] = dw_acc[i];
 }
 
+// Same result for d <= 1024, d % 8 == 0 (wider rows would spill): one warp per row, the row of x and dy read once with 16-byte loads and
+// kept in registers (VPL vectors of 8 values per lane), the weight-gradient contribution of all rows a warp
+// handles accumulated in registers and merged into shared memory once at the end.
+template <int VPL>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, long long rows, int d, float eps) {
+  extern __shared__ float dw_acc[];  // [d]
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int nvec = d >> 3;
+  float wv[VPL][8], dwv[VPL][8];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (v < nvec) q = *reinterpret_cast<const uint4*>(w + v * 8);
+    const uint32_t qi[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(qi[e]);
+      wv[j][2 * e] = f.x; wv[j][2 * e + 1] = f.y;
+      dwv[j][2 * e] = 0.f; dwv[j][2 * e + 1] = 0.f;
+    }
+  }
+  for (long long row = (long long)blockIdx.x * nw + wid; row < rows; row += (long long)gridDim.x * nw) {
+    float xs[VPL][8], gs[VPL][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int v = lane + 32 * j;
+      uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+      if (v < nvec) {
+        a = *reinterpret_cast<const uint4*>(x + row * d + v * 8);
+        b = *reinterpret_cast<const uint4*>(dy + row * d + v * 8);
+      }
+      const uint32_t ai[4] = {a.x, a.y, a.z, a.w}, bi[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = unpack_bf16x2(ai[e]), fb = unpack_bf16x2(bi[e]);
+        xs[j][2 * e] = fa.x; xs[j][2 * e + 1] = fa.y;
+        gs[j][2 * e] = fb.x; gs[j][2 * e + 1] = fb.y;
+        ss = fmaf(fa.x, fa.x, ss); ss = fmaf(fa.y, fa.y, ss);
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        xs[j][e] *= rstd;                                   // xhat
+        dot = fmaf(gs[j][e] * wv[j][e], xs[j][e], dot);
+      }
+    dot = warp_sum(dot) / (float)d;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int v = lane + 32 * j;
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float g0 = gs[j][2 * e] * wv[j][2 * e], g1 = gs[j][2 * e + 1] * wv[j][2 * e + 1];
+        o[e] = pack_bf16x2(rstd * (g0 - xs[j][2 * e] * dot), rstd * (g1 - xs[j][2 * e + 1] * dot));
+        dwv[j][2 * e] = fmaf(gs[j][2 * e], xs[j][2 * e], dwv[j][2 * e]);
+        dwv[j][2 * e + 1] = fmaf(gs[j][2 * e + 1], xs[j][2 * e + 1], dwv[j][2 * e + 1]);
+      }
+      if (v < nvec) *reinterpret_cast<uint4*>(dx + row * d + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+    if (v < nvec)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) atomicAdd(&dw_acc[v * 8 + e], dwv[j][e]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_partial[(long long)blockIdx.x * d + i] = dw_acc[i];
+}
+
 // ------------------------------------------------------------------------------------------
 // RoPE on [T, H, D] (training: no cache). sign = +1 forward, -1 backward (inverse rotation).
 // fp32 math, one rounding at the end.
@@ -259,9 +342,14 @@ extern "C" int rb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void
                               long long rows, int d, float eps, cudaStream_t s) {
   if (rows <= 0) return 0;
   const int grid = rb_rmsnorm_bwd_num_partials();
-  rmsnorm_bwd_kernel<<<grid, 256, d * sizeof(float), s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                          (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, dw_partial,
-                                                          rows, d, eps);
+  const __nv_bfloat16 *xb = (const __nv_bfloat16*)x, *wb = (const __nv_bfloat16*)w, *gb = (const __nv_bfloat16*)dy;
+  const bool vec = d % 8 == 0 && d <= 1024 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                                                reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  const size_t sm = d * sizeof(float);
+  if (!vec) rmsnorm_bwd_kernel<<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
+  else if (d <= 256) rmsnorm_bwd_vec_kernel<1><<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
+  else if (d <= 512) rmsnorm_bwd_vec_kernel<2><<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
+  else rmsnorm_bwd_vec_kernel<4><<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
   return RB_OK();
 }
 extern "C" int rb_rope(const void* x, void* y, const int* positions, const void* cos_sin, long long T, int H, int D,

@@ -47,6 +47,20 @@ def test_rmsnorm_bwd_and_rope(cuda_device):
     assert (back.float() - q.float()).abs().max() < 0.03
 
 
+@pytest.mark.parametrize("rows,d", [(1000, 64), (77, 256), (300, 512), (2049, 896), (65, 1024), (33, 4096)])
+def test_rmsnorm_bwd_widths(cuda_device, rows, d):
+    """Register-resident path (d <= 1024) and the generic one against the PyTorch twin."""
+    g = torch.Generator().manual_seed(d)
+    x = torch.randn(rows, d, generator=g).bfloat16().to(cuda_device)
+    w = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16().to(cuda_device)
+    dy = torch.randn(rows, d, generator=g).bfloat16().to(cuda_device)
+    dx, dw = T.rmsnorm_bwd(x, w, dy, 1e-6)
+    rdx, rdw = T.rmsnorm_bwd(x.cpu(), w.cpu(), dy.cpu(), 1e-6)
+    assert (dx.float().cpu() - rdx.float()).abs().max() < 0.06
+    assert (dw.cpu() - rdw).abs().max() < 0.02 * rdw.abs().max() + 0.05
+    ops.check_status()
+
+
 def test_adamw_kernel_matches_torch(cuda_device):
     n = 10007
     p0 = torch.randn(n)
