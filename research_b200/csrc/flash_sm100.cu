@@ -38,16 +38,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Polling wait for the single-thread producer / MMA roles: sleeps between polls so the spinning
-// thread does not take issue slots from the softmax warps on the same scheduler.
+// Wait for the single-thread producer / MMA roles. `mbarrier.try_wait` with a suspend-time hint parks the thread in
+// hardware until the phase completes or the hint runs out: the waiter takes no issue slots from the softmax warps
+// on its scheduler (what a plain poll loop did) and wakes as soon as the barrier flips (what a poll + nanosleep
+// loop did not: at short sequences every hand-off on the critical path paid a sleep quantum).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                                   int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(64);
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > RB_WAIT_BUDGET_NS) {
@@ -271,7 +283,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
     auto swap_with_partner = [&](float mine, float& other) -> bool {
       xch[xph & 1][half][r] = mine;
       mbar_arrive(smem_u32(&xch_bar[qd]));
-      bool good = mbar_wait_bounded(smem_u32(&xch_bar[qd]), xph & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      bool good = mbar_wait_backoff(smem_u32(&xch_bar[qd]), xph & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       other = xch[xph & 1][half ^ 1][r];
       ++xph;
       return __all_sync(0xffffffffu, good);
@@ -279,7 +291,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
     for (int j = 0; j < n_tiles; ++j) {
       const int k0 = (t_begin + j) * FA_BN;
       const uint32_t s_addr = tmem_base + (j & 1) * FA_BN + half * HC + lane_addr;
-      ok = mbar_wait_bounded(smem_u32(&s_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&s_full[j & 1]), (j >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -319,7 +331,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       if (__any_sync(0xffffffffu, need)) {   // same rows, same inputs: both warps of a quarter agree
         if (j > 0) {
           // O holds the products of tiles 0..j-1 once the previous P V has completed
-          ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+          ok = mbar_wait_backoff(smem_u32(&o_done), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -352,7 +364,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // bf16 P into shared memory (A operand of P V) once the P V of two tiles ago has read the buffer
-      ok = mbar_wait_bounded(smem_u32(&p_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = mbar_wait_backoff(smem_u32(&p_empty[j & 1]), ((j >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* prow = p_ptr + (j & 1) * Cfg::kPBytes + half * CHUNK_BYTES + r * 128;
@@ -375,7 +387,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd_kernel(const __grid_c
       l += l_other;
     }
     if (ok && n_tiles > 0) {
-      ok = mbar_wait_bounded(smem_u32(&o_done), (uint32_t)((n_tiles - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&o_done), (uint32_t)((n_tiles - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -639,7 +651,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
     bool ok = true;
     for (int j = 0; j < n_mine; ++j) {
       const int k0 = (t_begin + j) * FA_BN;
-      ok = mbar_wait_bounded(smem_u32(&s_full[x]), (uint32_t)(j & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&s_full[x]), (uint32_t)(j & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -673,7 +685,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
       const bool need = m_new > m_used + FA_RESCALE_THRESHOLD || (m_used == -INFINITY && m_new != -INFINITY);
       if (__any_sync(0xffffffffu, need)) {
         if (j > 0) {
-          ok = mbar_wait_bounded(smem_u32(&o_done[x]), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+          ok = mbar_wait_backoff(smem_u32(&o_done[x]), (uint32_t)((j - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -705,7 +717,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // P buffer is free once the previous P V of this tile has read it
-      ok = mbar_wait_bounded(smem_u32(&p_empty[x]), (uint32_t)((j & 1) ^ 1), abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = mbar_wait_backoff(smem_u32(&p_empty[x]), (uint32_t)((j & 1) ^ 1), abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
 #pragma unroll
@@ -722,7 +734,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) flash_fwd2_kernel(const __grid_
       if (lane == 0) mbar_arrive(smem_u32(&p_full[x]));
     }
     if (ok && n_mine > 0) {
-      ok = mbar_wait_bounded(smem_u32(&o_done[x]), (uint32_t)((n_mine - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&o_done[x]), (uint32_t)((n_mine - 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok && (x == 0 || has_b)) {
@@ -1018,11 +1030,11 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
           stat[it & 1][which][idx] = val;
         }
         mbar_arrive(smem_u32(&stat_bar));
-        ok = mbar_wait_bounded(smem_u32(&stat_bar), (uint32_t)(it & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        ok = mbar_wait_backoff(smem_u32(&stat_bar), (uint32_t)(it & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
-      ok = mbar_wait_bounded(smem_u32(&st_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&st_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -1048,7 +1060,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
         pr[c] = pv;
         ds[c] = pv * (__uint_as_float(dv[c]) - dl[c]) * p.scale;
       }
-      ok = mbar_wait_bounded(smem_u32(&pds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = mbar_wait_backoff(smem_u32(&pds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* pt_row = smem_al + pds_off + (it & 1) * 2 * Cfg::kPd + r * 128;
@@ -1059,7 +1071,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
       if (lane == 0) mbar_arrive(smem_u32(&pds_full[it & 1]));
     }
     if (ok && n_iter > 0) {
-      ok = mbar_wait_bounded(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -1252,7 +1264,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dq_kernel(const _
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int k0 = (t_begin + it) * 64;
-      ok = mbar_wait_bounded(smem_u32(&s_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&s_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -1275,7 +1287,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dq_kernel(const _
         }
         ds[c] = pv * (__uint_as_float(dv[c]) - dl) * p.scale;
       }
-      ok = mbar_wait_bounded(smem_u32(&ds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
+      ok = mbar_wait_backoff(smem_u32(&ds_empty[it & 1]), ((it >> 1) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       store_row32_sw128(smem_al + ds_off + (it & 1) * Cfg::kPd + r * 128, r, half, ds);
@@ -1284,7 +1296,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dq_kernel(const _
       if (lane == 0) mbar_arrive(smem_u32(&ds_full[it & 1]));
     }
     if (ok && n_iter > 0) {
-      ok = mbar_wait_bounded(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_backoff(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {

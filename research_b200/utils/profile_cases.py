@@ -54,6 +54,13 @@ def case_flash_fwd() -> None:
     print(bench_flash_forward(8, 2048, 32, 8, 128, 1688.4, iters=3))
 
 
+def case_flash_fwd_short() -> None:
+    """Flash attention forward at training-rollout lengths: 32 x 512 tokens, 14q/2kv heads, D=64, causal."""
+    from .microbench import bench_flash_forward
+
+    print(bench_flash_forward(32, 512, 14, 2, 64, 1688.4, iters=3))
+
+
 def case_flash_bwd() -> None:
     """tcgen05 flash attention backward: 8 x 2048 tokens, 32q/8kv heads, D=128, causal."""
     from .microbench import bench_flash_backward
