@@ -13,19 +13,29 @@ SGLang / vLLM servers); this is the in-tree equivalent of their ``--dp --enable-
 
 from __future__ import annotations
 
+from datetime import timedelta
+
 import torch
 import torch.distributed as dist
 
 from .symm import PeerComm
 
 
+class PeerFailure(RuntimeError):
+    """A rank of the expert-parallel group did not answer the per-step agreement in time (it exited, hung or lost
+    its connection). Raised on the host before anything is launched for the step, so no kernel is left waiting on
+    the missing rank's barriers."""
+
+
 class ExpertParallel:
-    def __init__(self, comm: PeerComm, cpu_group=None):
+    def __init__(self, comm: PeerComm, cpu_group=None, timeout_s: float = 120.0):
         self.comm = comm
         self.rank, self.world = comm.rank, comm.world
+        self.timeout_s = timeout_s
         if cpu_group is None and self.world > 1:
-            # agreement travels over a host-side group so that it never queues behind device work
-            cpu_group = dist.new_group(backend="gloo") if comm.on_gpu else comm.group
+            # agreement travels over a host-side group of its own: it never queues behind device work, and its
+            # timeout doubles as the failure detector of the lock-step loop
+            cpu_group = dist.new_group(backend="gloo", timeout=timedelta(seconds=timeout_s))
         self.cpu_group = cpu_group
         self._buf = torch.zeros(4, dtype=torch.int32)
         self.agreements = 0
@@ -38,6 +48,9 @@ class ExpertParallel:
         self._buf.zero_()
         for i, f in enumerate(flags):
             self._buf[i] = int(f)
-        dist.all_reduce(self._buf, op=dist.ReduceOp.MAX, group=self.cpu_group)
+        try:
+            dist.all_reduce(self._buf, op=dist.ReduceOp.MAX, group=self.cpu_group)
+        except Exception as e:  # noqa: BLE001 - gloo reports a lost or silent peer as a RuntimeError / timeout
+            raise PeerFailure(f"rank {self.rank}: expert-parallel agreement failed after {self.agreements} steps: {e}") from e
         self.agreements += 1
         return tuple(int(v) for v in self._buf[:len(flags)])

@@ -80,3 +80,12 @@ def test_expert_parallel_engines_gpu(flags):
            "--master-port", str(_free_port()), os.path.join(HERE, "ep_engine_worker.py"), *flags]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert proc.returncode == 0 and proc.stdout.count("EP_ENGINE_OK") == 2, proc.stdout[-1500:] + proc.stderr[-3000:]
+
+
+def test_expert_parallel_peer_failure_is_detected_on_the_host():
+    """A rank that leaves between steps makes the survivor's next agreement raise PeerFailure (gloo, CPU)."""
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "ep_failure_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert "RANK1_LEAVING" in proc.stdout and "PEER_FAILURE_DETECTED" in proc.stdout, proc.stdout[-1500:] + proc.stderr[-2000:]
