@@ -104,7 +104,11 @@ def cmd_serve(args) -> int:
             device = f"cuda:{local}"
         if not dist.is_initialized():
             dist.init_process_group("nccl" if device != "cpu" else "gloo")
-        group = dist.new_group(backend="gloo")       # request broadcast travels on a CPU-side group
+        from datetime import timedelta
+
+        # request broadcast travels on a CPU-side group; rank 0 heartbeats every few seconds when idle, so this
+        # timeout only fires when a rank is gone
+        group = dist.new_group(backend="gloo", timeout=timedelta(seconds=120))
         tp = TensorParallel(PeerComm(device=torch.device(device)), max_rows=ecfg.max_batch_size * 64 + 64, max_cols=max(cfg.hidden_size, 1024))
     engine = InferenceEngine(ecfg, cfg, weights, device=device, tp=tp)
     if tp is None or tp.rank == 0:

@@ -118,17 +118,22 @@ class LockstepEngineService(EngineService):
     admitted since the last one (an object broadcast on a CPU-side group) together with a stop flag, and all
     ranks add them and step together. Ranks other than 0 never resolve futures; they call ``follow()``."""
 
-    def __init__(self, engine, group=None, idle_sleep: float = 0.001):
+    def __init__(self, engine, group=None, idle_sleep: float = 0.001, heartbeat_s: float = 5.0):
         import torch.distributed as dist
 
         self.dist = dist
         self.group = group
         self.rank = dist.get_rank(group)
+        # an idle rank 0 still exchanges an empty batch this often, so that followers blocked in the broadcast
+        # never run into the group's timeout (which is what detects a dead rank 0)
+        self.heartbeat_s = heartbeat_s
+        self._last_exchange = time.monotonic()
         super().__init__(engine, idle_sleep)
 
     def _exchange(self, batch, stop: bool):
         payload = [(([t for t, _, _ in batch], [p for _, p, _ in batch]), stop)] if self.rank == 0 else [None]
         self.dist.broadcast_object_list(payload, src=0, group=self.group)
+        self._last_exchange = time.monotonic()
         return payload[0]
 
     def _run(self) -> None:
@@ -144,6 +149,8 @@ class LockstepEngineService(EngineService):
             stop = self._stop.is_set()
             if not batch and not self.engine.has_pending() and not stop:
                 self._idle.set()
+                if time.monotonic() - self._last_exchange > self.heartbeat_s:
+                    self._exchange([], False)          # heartbeat: followers see an empty step and wait again
                 time.sleep(self.idle_sleep)
                 continue
             self._idle.clear()
