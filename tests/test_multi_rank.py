@@ -36,6 +36,14 @@ def test_gloo_two_ranks(cases):
         assert f"CASE_OK {c}" in out
 
 
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "moe_ep"])
+def test_gloo_four_ranks(cases):
+    """The host-side logic (slab rotation, shard ranges, count matrices, dispatch offsets) at world size 4."""
+    out = _run("cpu", 4, cases)
+    for c in cases.split(","):
+        assert f"CASE_OK {c}" in out
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "moe_ep"])
 def test_gpu_ranks(cases):
@@ -58,13 +66,14 @@ def test_lockstep_tp_serving_two_ranks():
     assert proc.returncode == 0 and "LOCKSTEP_OK" in proc.stdout, proc.stdout[-1500:] + proc.stderr[-3000:]
 
 
-def test_expert_parallel_engines_lockstep_two_ranks():
-    """Two engines with split experts serve different request mixes and stay paired (gloo, CPU)."""
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_expert_parallel_engines_lockstep_two_ranks(ranks):
+    """Engines with split experts serve different request mixes and stay paired (gloo, CPU)."""
     env = dict(os.environ, OMP_NUM_THREADS="2")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "ep_engine_worker.py")]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert proc.returncode == 0 and proc.stdout.count("EP_ENGINE_OK") == 2, proc.stdout[-1500:] + proc.stderr[-3000:]
+    assert proc.returncode == 0 and proc.stdout.count("EP_ENGINE_OK") == ranks, proc.stdout[-1500:] + proc.stderr[-3000:]
 
 
 @pytest.mark.gpu
