@@ -486,3 +486,80 @@ extern "C" int rb_log_softmax(const float* x, const float* dy, float* out, int r
   else rb::log_softmax_bwd_kernel<<<grid, 256, 0, s>>>(x, dy, out, rows, cols);     // x is y (the forward output) here
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
+
+// ------------------------------------------------------------------------------------------
+// Adaptive average pooling over [N, C, H, W] fp32 (dev/integration-evaluation/_adaptive_avg_pool2d*.py) and a
+// 16-byte vector add (dev/kernel-learning/leetgpu/vector-addition). Pooling window of output o along an axis of
+// length L pooled to O cells: [floor(o L / O), ceil((o + 1) L / O)). The backward gathers: every input element
+// sums dy / window size over the output cells whose window contains it, so no atomics are needed.
+// ------------------------------------------------------------------------------------------
+namespace rb {
+__device__ __forceinline__ int pool_lo(int o, int L, int O) { return (int)(((long long)o * L) / O); }
+__device__ __forceinline__ int pool_hi(int o, int L, int O) { return (int)((((long long)(o + 1)) * L + O - 1) / O); }
+
+__global__ void adaptive_avg_pool2d_kernel(const float* __restrict__ x, float* __restrict__ y, long long planes, int H, int W,
+                                           int OH, int OW) {
+  const long long n = planes * OH * OW;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int ow = (int)(i % OW), oh = (int)((i / OW) % OH);
+    const long long pl = i / ((long long)OW * OH);
+    const int h0 = pool_lo(oh, H, OH), h1 = pool_hi(oh, H, OH), w0 = pool_lo(ow, W, OW), w1 = pool_hi(ow, W, OW);
+    float acc = 0.f;
+    for (int h = h0; h < h1; ++h)
+      for (int w = w0; w < w1; ++w) acc += x[(pl * H + h) * W + w];
+    y[i] = acc / (float)((h1 - h0) * (w1 - w0));
+  }
+}
+__global__ void adaptive_avg_pool2d_bwd_kernel(const float* __restrict__ dy, float* __restrict__ dx, long long planes, int H,
+                                               int W, int OH, int OW) {
+  const long long n = planes * H * W;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int w = (int)(i % W), h = (int)((i / W) % H);
+    const long long pl = i / ((long long)W * H);
+    // output cells whose window can contain h lie in (h OH / H - 1, (h + 1) OH / H); one spare cell on each side,
+    // the containment test below decides
+    const int oh_a = max((int)(((long long)h * OH) / H) - 1, 0), oh_b = min((int)((((long long)h + 1) * OH + H - 1) / H) + 1, OH);
+    const int ow_a = max((int)(((long long)w * OW) / W) - 1, 0), ow_b = min((int)((((long long)w + 1) * OW + W - 1) / W) + 1, OW);
+    float acc = 0.f;
+    for (int oh = oh_a; oh < oh_b; ++oh) {
+      const int h0 = pool_lo(oh, H, OH), h1 = pool_hi(oh, H, OH);
+      if (h < h0 || h >= h1) continue;
+      for (int ow = ow_a; ow < ow_b; ++ow) {
+        const int w0 = pool_lo(ow, W, OW), w1 = pool_hi(ow, W, OW);
+        if (w < w0 || w >= w1) continue;
+        acc += dy[(pl * OH + oh) * OW + ow] / (float)((h1 - h0) * (w1 - w0));
+      }
+    }
+    dx[i] = acc;
+  }
+}
+__global__ void vec_add_bf16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ c, long long nvec) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 x = a[i], y = b[i];
+    const uint32_t xi[4] = {x.x, x.y, x.z, x.w}, yi[4] = {y.x, y.y, y.z, y.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(xi[j]), g = unpack_bf16x2(yi[j]);
+      o[j] = pack_bf16x2(f.x + g.x, f.y + g.y);
+    }
+    c[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+}  // namespace rb
+
+extern "C" int rb_adaptive_avg_pool2d(const float* x, const float* dy, float* out, long long planes, int H, int W, int OH, int OW,
+                                      cudaStream_t s) {
+  if (planes <= 0 || H <= 0 || W <= 0 || OH <= 0 || OW <= 0) return -1;
+  if (dy == nullptr) {
+    rb::adaptive_avg_pool2d_kernel<<<grid_for(planes * OH * OW, 256), 256, 0, s>>>(x, out, planes, H, W, OH, OW);
+  } else {
+    rb::adaptive_avg_pool2d_bwd_kernel<<<grid_for(planes * H * W, 256), 256, 0, s>>>(dy, out, planes, H, W, OH, OW);
+  }
+  return RB_OK();
+}
+extern "C" int rb_vec_add_bf16(const void* a, const void* b, void* c, long long n, cudaStream_t s) {
+  if (n <= 0 || n % 8 != 0) return -1;
+  rb::vec_add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)a, (const uint4*)b, (uint4*)c, n / 8);
+  return RB_OK();
+}

@@ -199,3 +199,50 @@ def log_softmax_backward(y: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     lib.rb_log_softmax.argtypes = [c_vp, c_vp, c_vp, c_int, c_int, c_vp]
     check_rc(lib.rb_log_softmax(ptr(y), ptr(dy.contiguous()), ptr(out), y.shape[0], y.shape[1], stream_handle(y.device)), "rb_log_softmax(bwd)")
     return out
+
+
+# ---------------------------------------------------------------- pooling / vector add (small kernels of the dev tree)
+def adaptive_avg_pool2d(x: torch.Tensor, output_size: tuple[int, int]) -> torch.Tensor:
+    """``[N, C, H, W]`` fp32 -> ``[N, C, OH, OW]`` (windows as in ``torch.nn.functional.adaptive_avg_pool2d``)."""
+    if not x.is_cuda:
+        return torch.nn.functional.adaptive_avg_pool2d(x, output_size)
+    assert x.dtype == torch.float32 and x.dim() == 4
+    x = x.contiguous()
+    N, C, H, W = x.shape
+    OH, OW = output_size
+    out = torch.empty(N, C, OH, OW, dtype=torch.float32, device=x.device)
+    lib = _lib()
+    lib.rb_adaptive_avg_pool2d.argtypes = [c_vp, c_vp, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp]
+    check_rc(lib.rb_adaptive_avg_pool2d(ptr(x), None, ptr(out), N * C, H, W, OH, OW, stream_handle(x.device)), "rb_adaptive_avg_pool2d")
+    return out
+
+
+def adaptive_avg_pool2d_backward(dy: torch.Tensor, input_size: tuple[int, int]) -> torch.Tensor:
+    """Gradient w.r.t. the ``[N, C, H, W]`` input given ``dy [N, C, OH, OW]`` (gather form, no atomics)."""
+    H, W = input_size
+    if not dy.is_cuda:
+        x = torch.zeros(dy.shape[0], dy.shape[1], H, W, dtype=torch.float32, requires_grad=True)
+        torch.nn.functional.adaptive_avg_pool2d(x, dy.shape[-2:]).backward(dy.float())
+        return x.grad
+    assert dy.dtype == torch.float32 and dy.dim() == 4
+    dy = dy.contiguous()
+    N, C, OH, OW = dy.shape
+    out = torch.empty(N, C, H, W, dtype=torch.float32, device=dy.device)
+    lib = _lib()
+    lib.rb_adaptive_avg_pool2d.argtypes = [c_vp, c_vp, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp]
+    check_rc(lib.rb_adaptive_avg_pool2d(None, ptr(dy), ptr(out), N * C, H, W, OH, OW, stream_handle(dy.device)),
+             "rb_adaptive_avg_pool2d(bwd)")
+    return out
+
+
+def vec_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Element-wise bf16 sum with 16-byte accesses (element count a multiple of 8)."""
+    if not a.is_cuda:
+        return a + b
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape == b.shape and a.numel() % 8 == 0
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty_like(a)
+    lib = _lib()
+    lib.rb_vec_add_bf16.argtypes = [c_vp, c_vp, c_vp, c_ll, c_vp]
+    check_rc(lib.rb_vec_add_bf16(ptr(a), ptr(b), ptr(out), a.numel(), stream_handle(a.device)), "rb_vec_add_bf16")
+    return out

@@ -184,3 +184,20 @@ def test_small_activation_kernels(cuda_device):
     w = torch.randn(33, 5001, generator=g).to(cuda_device)
     ref = torch.autograd.functional.vjp(lambda t: torch.log_softmax(t, -1), z, w)[1]
     assert torch.allclose(T.log_softmax_backward(y, w), ref, atol=1e-3)
+
+
+@pytest.mark.parametrize("shape,out", [((2, 3, 17, 23), (5, 7)), ((1, 4, 8, 8), (1, 1)), ((3, 2, 10, 6), (10, 6)), ((2, 2, 5, 9), (7, 4)), ((1, 2, 3, 4), (13, 9))])
+def test_adaptive_avg_pool2d_and_vec_add(cuda_device, shape, out):
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g).to(cuda_device)
+    y = T.adaptive_avg_pool2d(x, out)
+    ref = torch.nn.functional.adaptive_avg_pool2d(x, out)
+    assert torch.allclose(y, ref, atol=1e-5)
+    dy = torch.randn(ref.shape, generator=g).to(cuda_device)
+    xr = x.clone().requires_grad_(True)
+    torch.nn.functional.adaptive_avg_pool2d(xr, out).backward(dy)
+    assert torch.allclose(T.adaptive_avg_pool2d_backward(dy, shape[-2:]), xr.grad, atol=1e-5)
+    a = torch.randn(1000, 8, generator=g).bfloat16().to(cuda_device)
+    b = torch.randn(1000, 8, generator=g).bfloat16().to(cuda_device)
+    assert torch.equal(T.vec_add(a, b), a + b)
+    ops.check_status()
