@@ -75,3 +75,52 @@ def test_grpo_bench_cpu_smoke():
     row = json.loads([ln for ln in proc.stdout.splitlines() if ln.startswith("{")][-1])
     assert row["bench"] == "grpo_step" and row["samples_per_step"] == 16 and row["rollout_s"] > 0 and row["train_s"] > 0
     assert row["rollout_tokens_per_s"] > 0 and row["sync_s"] >= 0
+
+
+def test_print_capture_and_validation(tmp_path):
+    import logging
+
+    import pytest
+
+    from research_b200.utils.print_capture import intercept_prints
+    from research_b200.utils.validation import (parse_ssh_target, validate_hostname, validate_port, validate_ssh_key_path,
+                                                validate_timeout, validate_username)
+
+    records = []
+
+    class H(logging.Handler):
+        def emit(self, r):
+            records.append((r.levelno, r.getMessage()))
+
+    log = logging.getLogger("capture-test")
+    log.setLevel(logging.DEBUG)
+    log.addHandler(H())
+    import sys
+    before = sys.stdout
+    with intercept_prints(log, intercept_stderr=True):
+        print("hello", end="")
+        print(" world")
+        print("second line")
+        print("oops", file=sys.stderr)
+        print("tail without newline", end="")
+    assert sys.stdout is before
+    assert (logging.INFO, "hello world") in records and (logging.INFO, "second line") in records
+    assert (logging.ERROR, "oops") in records and (logging.INFO, "tail without newline") in records
+    with pytest.raises(RuntimeError):
+        with intercept_prints(log):
+            raise RuntimeError("x")
+    assert sys.stdout is before
+
+    assert validate_port(22) == 22 and validate_timeout(2.5) == 2.5 and validate_hostname("gpu-1.example.org") == "gpu-1.example.org"
+    assert parse_ssh_target("root@10.0.0.5:2222") == ("root", "10.0.0.5", 2222) and parse_ssh_target("me@host")[2] == 22
+    for bad in (lambda: validate_port(0), lambda: validate_port(True), lambda: validate_timeout(0), lambda: validate_hostname("a b"),
+                lambda: validate_username("1abc"), lambda: parse_ssh_target("nohost"), lambda: validate_ssh_key_path(str(tmp_path / "none"))):
+        with pytest.raises(ValueError):
+            bad()
+    key = tmp_path / "id"
+    key.write_text("k")
+    key.chmod(0o644)
+    with pytest.raises(ValueError):
+        validate_ssh_key_path(str(key))
+    key.chmod(0o600)
+    assert validate_ssh_key_path(str(key)) == str(key)
