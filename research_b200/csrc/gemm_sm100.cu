@@ -377,26 +377,29 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       // rs_smem[acc] was read by the epilogue of the tile that last used this accumulator
       ok = mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY);
       if (!ok) break;
-      float ss = 0.f;
+      float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;   // four chains: the sums must not serialise the loop
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
         if (!ok) break;
         const uint8_t* arow = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * Cfg::kStageBytes + (size_t)nrow * 128;
+        uint4 c[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) c[j] = *reinterpret_cast<const uint4*>(arow + ((j ^ (lane & 7)) << 4));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));   // the tile is in registers: release the stage first
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint4 c = *reinterpret_cast<const uint4*>(arow + ((j ^ (lane & 7)) << 4));
           float2 f;
-          f = unpack_bf16x2(c.x); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
-          f = unpack_bf16x2(c.y); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
-          f = unpack_bf16x2(c.z); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
-          f = unpack_bf16x2(c.w); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+          f = unpack_bf16x2(c[j].x); ss0 = fmaf(f.x, f.x, ss0); ss1 = fmaf(f.y, f.y, ss1);
+          f = unpack_bf16x2(c[j].y); ss2 = fmaf(f.x, f.x, ss2); ss3 = fmaf(f.y, f.y, ss3);
+          f = unpack_bf16x2(c[j].z); ss0 = fmaf(f.x, f.x, ss0); ss1 = fmaf(f.y, f.y, ss1);
+          f = unpack_bf16x2(c[j].w); ss2 = fmaf(f.x, f.x, ss2); ss3 = fmaf(f.y, f.y, ss3);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));   // this warp no longer needs the stage
       }
       if (!ok) break;
+      const float ss = (ss0 + ss1) + (ss2 + ss3);
       rs_smem[acc][nrow] = rsqrtf(ss * p.norm_inv_k + p.norm_eps);
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&rs_full_bar[acc]));

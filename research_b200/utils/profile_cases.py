@@ -41,6 +41,34 @@ def case_gemm_gateup_8b() -> None:
     print(bench_gemm(256, 28672, 4096, 1688.4, iters=3, bn=256))
 
 
+def case_gemm_down_8b_cluster() -> None:
+    """Decode-time down projection of the 8B shape with split-K over a thread-block cluster: M=256, N=4096, K=14336
+    (weights 117 MB per launch, four copies rotated so that every launch streams them from HBM)."""
+    import itertools
+
+    ws = [torch.randn(4096, 14336, device="cuda").bfloat16() * 0.05 for _ in range(4)]
+    a = torch.randn(256, 14336, device="cuda").bfloat16()
+    x = torch.zeros(256, 4096, device="cuda").bfloat16()
+    it = itertools.cycle(range(4))
+    for _ in range(6):
+        ops.gemm(a, ws[next(it)], residual=x, out=x)       # the chooser takes bn 256, 4 slices
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
+def case_gemm_qkv_folded_norm() -> None:
+    """qkv projection of the 0.5B shape with the RMSNorm folded in: M=256, N=1152, K=896."""
+    a = torch.randn(256, 896, device="cuda").bfloat16()
+    w = torch.randn(1152, 896, device="cuda").bfloat16() * 0.05
+    b = torch.zeros(1152, device="cuda").bfloat16()
+    for _ in range(6):
+        ops.gemm(a, w, bias=b, norm_eps=1e-6)
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
 def case_gemm_large() -> None:
     from .microbench import bench_gemm
 
