@@ -40,7 +40,14 @@ constexpr int BK = 64;
 constexpr int NUM_ACC = 2;
 constexpr int GEMM_THREADS = 192;
 constexpr int EPI_WARPS = 4;
-constexpr int NORM_WARPS = 4;                                   // extra warps of a launch with a folded RMSNorm
+// Four norm warps (one tile row per lane) measured 2 % faster per 0.5B decode step than two warps with two rows per
+// lane, although 320 threads cap that variant at 168 registers (a few spills in its epilogue): 2.40 vs 2.47 ms,
+// 2.45 ms without the fold.
+#ifndef RB_NORM_WARPS
+#define RB_NORM_WARPS 4
+#endif
+constexpr int NORM_WARPS = RB_NORM_WARPS;                       // extra warps of a launch with a folded RMSNorm
+constexpr int NORM_ROWS = 128 / (NORM_WARPS * 32);  // tile rows per lane of a norm warp
 constexpr int GEMM_THREADS_NORM = GEMM_THREADS + NORM_WARPS * 32;
 // MN-major 128B-swizzled tiles: 64-element chunks are BK*128 bytes apart (leading offset),
 // groups of 8 K-rows are 1024 bytes apart (stride offset).
@@ -163,8 +170,12 @@ __device__ unsigned long long g_ts[148 * 8];
 #define RB_TS(i) do { } while (0)
 #endif
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS_NORM, 1)
+// NORM = the launch carries the four extra warps of a folded RMSNorm. It is a template parameter because the launch
+// bound decides the register budget: 320 threads cap the kernel at 168 registers (with spills in the epilogue),
+// 192 threads leave it its 221. Compiling every launch for 320 threads cost the plain GEMMs 4 % (8192^3) and the
+// 0.5B decode step 0.1 ms.
+template <int BN, bool A_MN, bool B_MN, bool NORM = false>
+__global__ void __launch_bounds__(NORM ? GEMM_THREADS_NORM : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int MAX_STAGES = Cfg::kStages;
@@ -202,7 +213,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
-      mbar_init(smem_u32(&empty_bar[s]), p.norm_fold ? 1 + NORM_WARPS : 1);   // MMA commit (+ the norm warps' reads)
+      mbar_init(smem_u32(&empty_bar[s]), NORM ? 1 + NORM_WARPS : 1);   // MMA commit (+ the norm warps' reads)
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
@@ -366,9 +377,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     }
   } else if (warp >= 2 + EPI_WARPS) {
     // ------------------------------ norm warps (folded RMSNorm only) -----------------------
-    // One thread per tile row: as each A tile lands in the ring, add the squares of its 64 values of that row
-    // (a row is 128 contiguous bytes whose 16-byte chunks are permuted by the swizzle, which a sum ignores).
-    const int nrow = (warp - 2 - EPI_WARPS) * 32 + lane;
+    // NORM_ROWS tile rows per lane: as each A tile lands in the ring, add the squares of its 64 values of those
+    // rows (a row is 128 contiguous bytes whose 16-byte chunks are permuted by the swizzle, which a sum ignores).
+    const int nrow = (warp - 2 - EPI_WARPS) * (NORM_ROWS * 32) + lane;
     uint32_t it = 0, tile_iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
@@ -377,30 +388,37 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       // rs_smem[acc] was read by the epilogue of the tile that last used this accumulator
       ok = mbar_wait_bounded(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1u, abortp, p.status, ST_TIMEOUT_TMEM_EMPTY);
       if (!ok) break;
-      float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;   // four chains: the sums must not serialise the loop
+      float ss[NORM_ROWS][4];   // four chains per row: the sums must not serialise
+#pragma unroll
+      for (int r = 0; r < NORM_ROWS; ++r) ss[r][0] = ss[r][1] = ss[r][2] = ss[r][3] = 0.f;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
         if (!ok) break;
         const uint8_t* arow = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * Cfg::kStageBytes + (size_t)nrow * 128;
-        uint4 c[8];
+        uint4 c[NORM_ROWS][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) c[j] = *reinterpret_cast<const uint4*>(arow + ((j ^ (lane & 7)) << 4));
+        for (int r = 0; r < NORM_ROWS; ++r)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) c[r][j] = *reinterpret_cast<const uint4*>(arow + r * 32 * 128 + ((j ^ (lane & 7)) << 4));
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));   // the tile is in registers: release the stage first
+        if (lane == 0) mbar_arrive(smem_u32(&empty_bar[s]));   // the rows are in registers: release the stage first
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float2 f;
-          f = unpack_bf16x2(c[j].x); ss0 = fmaf(f.x, f.x, ss0); ss1 = fmaf(f.y, f.y, ss1);
-          f = unpack_bf16x2(c[j].y); ss2 = fmaf(f.x, f.x, ss2); ss3 = fmaf(f.y, f.y, ss3);
-          f = unpack_bf16x2(c[j].z); ss0 = fmaf(f.x, f.x, ss0); ss1 = fmaf(f.y, f.y, ss1);
-          f = unpack_bf16x2(c[j].w); ss2 = fmaf(f.x, f.x, ss2); ss3 = fmaf(f.y, f.y, ss3);
-        }
+        for (int r = 0; r < NORM_ROWS; ++r)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float2 f;
+            f = unpack_bf16x2(c[r][j].x); ss[r][0] = fmaf(f.x, f.x, ss[r][0]); ss[r][1] = fmaf(f.y, f.y, ss[r][1]);
+            f = unpack_bf16x2(c[r][j].y); ss[r][2] = fmaf(f.x, f.x, ss[r][2]); ss[r][3] = fmaf(f.y, f.y, ss[r][3]);
+            f = unpack_bf16x2(c[r][j].z); ss[r][0] = fmaf(f.x, f.x, ss[r][0]); ss[r][1] = fmaf(f.y, f.y, ss[r][1]);
+            f = unpack_bf16x2(c[r][j].w); ss[r][2] = fmaf(f.x, f.x, ss[r][2]); ss[r][3] = fmaf(f.y, f.y, ss[r][3]);
+          }
       }
       if (!ok) break;
-      const float ss = (ss0 + ss1) + (ss2 + ss3);
-      rs_smem[acc][nrow] = rsqrtf(ss * p.norm_inv_k + p.norm_eps);
+#pragma unroll
+      for (int r = 0; r < NORM_ROWS; ++r)
+        rs_smem[acc][nrow + r * 32] = rsqrtf(((ss[r][0] + ss[r][1]) + (ss[r][2] + ss[r][3])) * p.norm_inv_k + p.norm_eps);
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&rs_full_bar[acc]));
     }
@@ -435,7 +453,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       tc_fence_after();
       RB_TS(1);
       float rscale = 1.f;
-      if (p.norm_fold) {
+      if constexpr (NORM) {
         ok = mbar_wait_bounded(smem_u32(&rs_full_bar[acc]), acc_ph, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
         if (!ok) break;
         rscale = rs_smem[acc][q * 32 + lane];
@@ -1039,10 +1057,10 @@ namespace rb {
 
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;   // 227 KB per CTA minus the kernel's static shared memory (about 1.3 KB)
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool NORM = false>
 static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, NORM>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
@@ -1087,12 +1105,13 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (q.red_alias) smem = (stages * Cfg::kStageBytes > extra ? stages * Cfg::kStageBytes : extra) + 1024;
   if (p.cluster_k)
     return launch_kernel_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, (unsigned)p.split_k, q) == cudaSuccess ? 0 : -11;
-  return launch_kernel(kern, dim3(grid), dim3(p.norm_fold ? GEMM_THREADS_NORM : GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
+  return launch_kernel(kern, dim3(grid), dim3(NORM ? GEMM_THREADS_NORM : GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
 }
 
 template <int BN>
 static int launch_bn(const GemmParams& p, int a_mn, int b_mn, int max_ctas, cudaStream_t s) {
-  if (!a_mn && !b_mn) return launch_cfg<BN, false, false>(p, max_ctas, s);
+  if (!a_mn && !b_mn) return p.norm_fold ? launch_cfg<BN, false, false, true>(p, max_ctas, s) : launch_cfg<BN, false, false>(p, max_ctas, s);
+  if (p.norm_fold) return -12;   // the folded norm exists for K-major operands only
   if constexpr (BN >= 64) {
     if (!a_mn && b_mn) return launch_cfg<BN, false, true>(p, max_ctas, s);
     if (a_mn && b_mn) return launch_cfg<BN, true, true>(p, max_ctas, s);

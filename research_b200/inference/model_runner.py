@@ -90,7 +90,7 @@ class ModelRunner:
         # when weights are loaded, the row statistic is computed inside the GEMM from its own A tiles and applied
         # in the epilogue, so the two normalisation launches of a layer disappear (input norm -> qkv, post-attention
         # norm -> gate|up of dense layers; MoE layers keep their norm kernel). The extra reads of the A tiles load
-        # the shared-memory pipe that bounds long-K launches: measured per decode step 2.59 -> 2.45 ms at hidden
+        # the shared-memory pipe that bounds long-K launches: measured per decode step 2.45 -> 2.40 ms at hidden
         # size 896 but 9.82 -> 9.91 ms at 4096, so only narrow models fold
         self.fold_norm = cfg.hidden_size <= 2048 and not os.environ.get("RB_NO_NORM_FOLD")
         # fused GEMM+all-reduce works on row counts that split evenly into 8-row vectors per rank
