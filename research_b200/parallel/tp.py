@@ -23,6 +23,7 @@ unused, rollouts/inference/types.py:25; only ``--tp`` forwarded to an external S
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -135,7 +136,9 @@ class TensorParallel:
         self._reduce(a, w, EPI_ALL_REDUCE, buf.peer_ptrs, x.stride(0), x.data_ptr(), x.stride(0))
         self.comm.barrier(self._barrier_slot)
 
-    ONESHOT_MAX_BYTES = 32 << 20     # total bytes a rank pushes per call (output bytes x ranks)
+    # total bytes a rank pushes per one-shot call (output bytes x ranks); RB_TP_ONESHOT_MAX_BYTES overrides (0 = always
+    # take the two-hop reduce-scatter + all-gather path)
+    ONESHOT_MAX_BYTES = int(os.environ.get("RB_TP_ONESHOT_MAX_BYTES", 32 << 20))
 
     def _reduce_oneshot(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
         M, K = a.shape
