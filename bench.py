@@ -38,13 +38,26 @@ MODEL = dict(vocab=151936, layers=24, d=896, heads=14, kv_heads=2, head_dim=64, 
 N_REQUESTS, PROMPT_LO, PROMPT_HI, SHARED_PREFIX, NEW_TOKENS, MAX_BATCH = 1024, 128, 1024, 512, 512, 256
 
 
+MAX_MODEL_LEN = 2048
+SEQ_DESC = "prompt U[128,1024] (50% share a 512-token prefix) + 512 new"
+
+
+def set_workload(name: str) -> None:
+    """``rollout``: the flagship workload above. ``serving``: the tensor-parallel serving case (batch 64, random-token
+    prompts of 2048 tokens, 256 decoded tokens each, no shared prefix)."""
+    global N_REQUESTS, PROMPT_LO, PROMPT_HI, SHARED_PREFIX, NEW_TOKENS, MAX_BATCH, MAX_MODEL_LEN, SEQ_DESC
+    if name == "serving":
+        N_REQUESTS, PROMPT_LO, PROMPT_HI, SHARED_PREFIX, NEW_TOKENS, MAX_BATCH = 256, 2048, 2048, 0, 256, 64
+        MAX_MODEL_LEN, SEQ_DESC = 2560, "prompt 2048 random tokens + 256 new"
+
+
 def make_workload(seed: int, vocab: int):
     import torch
 
     g = torch.Generator().manual_seed(seed)
     shared = torch.randint(0, vocab, (SHARED_PREFIX,), generator=g).tolist()
     lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (N_REQUESTS,), generator=g).tolist()
-    share = (torch.rand(N_REQUESTS, generator=g) < 0.5).tolist()
+    share = (torch.rand(N_REQUESTS, generator=g) < (0.5 if SHARED_PREFIX > 0 else -1.0)).tolist()
     prompts = []
     for n, s in zip(lens, share):
         if s:
@@ -142,7 +155,7 @@ def run_native(args) -> dict:
     per_block = cfg.num_layers * 2 * (cfg.num_kv_heads // (world if tp is not None else 1)) * 16 * cfg.head_dim * 2
     KV_BLOCKS = int(min(40000, 80e9 // per_block))
     eng = InferenceEngine(
-        EngineConfig(cache_type="radix", max_batch_size=MAX_BATCH, max_model_len=2048, ignore_eos=True,
+        EngineConfig(cache_type="radix", max_batch_size=MAX_BATCH, max_model_len=MAX_MODEL_LEN, ignore_eos=True,
                      max_tokens_per_batch=16384, num_kv_blocks=KV_BLOCKS, seed=wl_rank),
         cfg, weights, device=dev, tp=tp, ep=ep)
     del weights
@@ -225,7 +238,7 @@ def run_native(args) -> dict:
         "impl": "native",
         "config": {"model": (f"{args.model}-shaped ({cfg.num_layers}L d{cfg.hidden_size} {cfg.num_heads}q/{cfg.num_kv_heads}kv "
                              f"hd{cfg.head_dim} ffn{cfg.intermediate_size} vocab{cfg.vocab_size})"),
-                   "global_batch": MAX_BATCH * replicas, "seq_len": "prompt U[128,1024] (50% share a 512-token prefix) + 512 new",
+                   "global_batch": MAX_BATCH * replicas, "seq_len": SEQ_DESC, "workload": args.workload,
                    "parallelism": f"dp{world}+ep{world}" if ep is not None else f"dp{world}" if tp is None else f"tp{world}",
                    "requests_per_replica": N_REQUESTS, "temperature": 1.0,
                    "cuda_graph_decode": True, "kv_cache": "paged, radix prefix reuse",
@@ -326,8 +339,13 @@ def main() -> None:
     ap.add_argument("--impl", choices=["native", "reference"], default="native")
     ap.add_argument("--model", default="qwen2.5-0.5b", help="model preset of the native arm (the flagship is the default)")
     ap.add_argument("--ep", action="store_true", help="native arm, MoE models: data-parallel engines with the experts split over all GPUs")
+    ap.add_argument("--workload", choices=["rollout", "serving"], default="rollout",
+                    help="native arm: rollout = 1024 requests, prompts U[128,1024], 512 new tokens, batch 256 (the flagship); "
+                         "serving = batch 64, prompts of 2048 tokens, 256 new tokens (the tensor-parallel serving case)")
     ap.add_argument("--tp", action="store_true", help="native arm: one tensor-parallel engine over all GPUs instead of replicas")
     args = ap.parse_args()
+    if args.impl == "native":
+        set_workload(args.workload)
     if args.steps is None:
         args.steps = 200 if args.impl == "native" else 3
     if args.warmup is None:

@@ -126,7 +126,7 @@ class TensorParallel:
             x.add_(part.to(x.dtype))
             return
         M, N = a.shape[0], w.shape[0]
-        if M <= self.max_rows // self.world and M * N * 2 * self.world <= self.ONESHOT_MAX_BYTES:
+        if M <= self.max_rows // self.world and M * N * 2 * (self.world - 1) <= self.ONESHOT_MAX_BYTES:
             # decode-sized output: push the partial to every rank, each rank sums locally. One hop, one kernel,
             # and no barrier afterwards: staging alternates between two parity slabs and a rank cannot run two
             # calls ahead of a peer, because finishing a call needs the peer's partial of that call.
@@ -136,9 +136,11 @@ class TensorParallel:
         self._reduce(a, w, EPI_ALL_REDUCE, buf.peer_ptrs, x.stride(0), x.data_ptr(), x.stride(0))
         self.comm.barrier(self._barrier_slot)
 
-    # total bytes a rank pushes per one-shot call (output bytes x ranks); RB_TP_ONESHOT_MAX_BYTES overrides (0 = always
-    # take the two-hop reduce-scatter + all-gather path)
-    ONESHOT_MAX_BYTES = int(os.environ.get("RB_TP_ONESHOT_MAX_BYTES", 32 << 20))
+    # Bytes a rank may push to its peers in a one-shot call (output bytes x (ranks - 1)). One shot saves a hop and a
+    # barrier but moves (W - 1) copies of the output per rank where the two-hop path moves 2 (W - 1) / W: measured on
+    # the 8B decode step (M = 256, N = 4096) one shot wins at 2 ranks (2 MB pushed) and loses at 8 (14 MB pushed:
+    # 7.20 vs 6.59 ms per step). RB_TP_ONESHOT_MAX_BYTES overrides (0 = always two hops).
+    ONESHOT_MAX_BYTES = int(os.environ.get("RB_TP_ONESHOT_MAX_BYTES", 4 << 20))
 
     def _reduce_oneshot(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
         M, K = a.shape
