@@ -278,6 +278,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------ TMA producer ------------------------------------------
     if (elect_one_sync()) {
       uint32_t it = 0;
+      int ring_s = 0;
+      uint32_t ring_ph = 0;
       bool ok = true;
       uint32_t a_seen = 0, b_seen = 0;  // bitmask of parts whose readiness was confirmed
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -299,8 +301,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         const int kb0 = (t % split_k) * p.kb_per_split;
         const int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+          // ring slot and phase advance incrementally: the depth is a run-time value, and a division per k-block sat
+          // on the single-thread critical path of this role
+          const int s = ring_s;
+          const uint32_t ph = ring_ph;
+          if (++ring_s == STAGES) { ring_s = 0; ring_ph ^= 1u; }
           ok = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abortp, p.status,
                                  ST_TIMEOUT_SMEM_EMPTY);
           if (!ok) break;
@@ -340,6 +345,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       const uint32_t idesc8 = make_idesc_f8(BM, BN, (p.fp8 >> 1) & 1, (p.fp8 >> 2) & 1);
       uint32_t it = 0;
+      int ring_s = 0;
+      uint32_t ring_ph = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
@@ -353,8 +360,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         const int kb0 = (t % split_k) * p.kb_per_split;
         const int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+          // ring slot and phase advance incrementally: the depth is a run-time value, and a division per k-block sat
+          // on the single-thread critical path of this role
+          const int s = ring_s;
+          const uint32_t ph = ring_ph;
+          if (++ring_s == STAGES) { ring_s = 0; ring_ph ^= 1u; }
           ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status,
                                  ST_TIMEOUT_SMEM_FULL);
           if (!ok) break;
@@ -381,6 +391,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     // rows (a row is 128 contiguous bytes whose 16-byte chunks are permuted by the swizzle, which a sum ignores).
     const int nrow = (warp - 2 - EPI_WARPS) * (NORM_ROWS * 32) + lane;
     uint32_t it = 0, tile_iter = 0;
+    int ring_s = 0;
+    uint32_t ring_ph = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
       const int acc = tile_iter % NUM_ACC;
@@ -392,8 +404,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
       for (int r = 0; r < NORM_ROWS; ++r) ss[r][0] = ss[r][1] = ss[r][2] = ss[r][3] = 0.f;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
+        const int s = ring_s;
+        const uint32_t ph = ring_ph;
+        if (++ring_s == STAGES) { ring_s = 0; ring_ph ^= 1u; }
         ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abortp, p.status, ST_TIMEOUT_SMEM_FULL);
         if (!ok) break;
         const uint8_t* arow = smem_raw + (smem_base - smem_u32(smem_raw)) + (size_t)s * Cfg::kStageBytes + (size_t)nrow * 128;
