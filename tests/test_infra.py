@@ -76,3 +76,78 @@ def test_code_search(tmp_path):
     ix.save(tmp_path / "ix.json")
     ix2 = CodeIndex.load(tmp_path / "ix.json")
     assert ix2.search("Engine")[0].line == 4 and ix2.stale_files() == []
+
+
+def test_cloud_provider_adapters_with_fake_transport(monkeypatch):
+    """Request shapes and reply mapping of the four cloud adapters, against a scripted transport (no network)."""
+    import pytest
+
+    from research_b200.infra.broker import GPUClient, q as Q
+    from research_b200.infra.broker_providers import (LambdaProvider, PrimeIntellectProvider, ProviderError, RunPodProvider,
+                                                      VastProvider, providers_from_env)
+
+    calls = []
+
+    def transport(method, url, headers, body):
+        calls.append((method, url, body))
+        assert headers["Authorization"] == "Bearer k"
+        if url.endswith("/instance-types"):
+            return 200, {"data": {"gpu_8x_b200": {"instance_type": {"description": "8x B200 (180 GB)", "price_cents_per_hour": 3992,
+                                                                    "specs": {"gpus": 8}},
+                                                  "regions_with_capacity_available": [{"name": "us-east-1"}]}}}
+        if url.endswith("/instance-operations/launch"):
+            return 200, {"data": {"instance_ids": ["i-1"]}}
+        if url.endswith("/instances/i-1"):
+            return 200, {"data": {"status": "active", "ip": "1.2.3.4"}}
+        if url.endswith("/instance-operations/terminate"):
+            return 200, {"data": {}}
+        if "runpod" in url:
+            q = body["query"]
+            if "gpuTypes" in q:
+                return 200, {"data": {"gpuTypes": [{"id": "NVIDIA B200", "displayName": "B200", "memoryInGb": 180, "secureCloud": True,
+                                                    "lowestPrice": {"minimumBidPrice": 3.1, "uninterruptablePrice": 5.9}}]}}
+            if "podFindAndDeployOnDemand" in q:
+                assert body["variables"]["input"]["gpuTypeId"] == "NVIDIA B200" and body["variables"]["input"]["cloudType"] == "SECURE"
+                return 200, {"data": {"podFindAndDeployOnDemand": {"id": "pod-9", "desiredStatus": "RUNNING"}}}
+            if "podTerminate" in q:
+                return 200, {"data": {"podTerminate": None}}
+            return 200, {"errors": [{"message": "bad query"}]}
+        if url.endswith("/bundles/"):
+            return 200, {"offers": [{"id": 77, "gpu_name": "H100 SXM", "num_gpus": 4, "gpu_ram": 81920, "dph_total": 9.5, "geolocation": "DE"}]}
+        if "/asks/77/" in url:
+            return 200, {"success": True, "new_contract": 555}
+        if "/instances/555/" in url and method == "DELETE":
+            return 200, {"success": True}
+        if url.endswith("/availability/"):
+            return 200, {"B200_180GB": [{"cloudId": "c-1", "gpuCount": 8, "gpuMemory": 180, "prices": {"onDemand": 30.0},
+                                         "dataCenter": "dc-7", "interconnectType": "nvlink5", "provider": "px", "socket": "SXM6"}]}
+        if url.endswith("/pods/") and method == "POST":
+            assert body["pod"]["cloudId"] == "c-1" and body["provider"]["type"] == "px"
+            return 200, {"id": "p-3", "status": "PROVISIONING"}
+        if "/pods/p-3" in url and method == "DELETE":
+            return 200, None
+        return 404, {"error": "not found"}
+
+    lam, rp, va, pi = (cls("k", transport) for cls in (LambdaProvider, RunPodProvider, VastProvider, PrimeIntellectProvider))
+    client = GPUClient([lam, rp, va, pi])
+    offers = client.search(Q.gpu_type.contains("B200"))
+    assert {o.provider for o in offers} == {"lambda", "runpod", "primeintellect"} and offers[0].price_per_hour <= offers[-1].price_per_hour
+    lo = lam.search()[0]
+    assert lo.gpu_count == 8 and lo.vram_gb == 180 and abs(lo.price_per_hour - 39.92) < 1e-9 and lo.region == "us-east-1"
+    inst = lam.create(lo, ssh_key_names=["me"])
+    assert inst.instance_id == "i-1" and lam.refresh("i-1").ssh_connection == "ubuntu@1.2.3.4:22" and lam.terminate("i-1")
+    on_demand = [o for o in rp.search() if not o.spot][0]
+    pod = rp.create(on_demand)
+    assert pod.instance_id == "pod-9" and pod.status == "running" and rp.terminate("pod-9")
+    vo = va.search()[0]
+    assert vo.vram_gb == 80 and va.create(vo).instance_id == "555" and va.terminate("555")
+    po = pi.search()[0]
+    assert po.interconnect == "nvlink5" and pi.create(po).instance_id == "p-3" and pi.terminate("p-3")
+    with pytest.raises(ProviderError):
+        lam._call("GET", "/nope")
+    with pytest.raises(ProviderError):
+        rp._gql("query { nonsense }")
+    monkeypatch.setenv("VAST_API_KEY", "k")
+    for var in ("LAMBDA_API_KEY", "RUNPOD_API_KEY", "PRIME_API_KEY"):
+        monkeypatch.delenv(var, raising=False)
+    assert [p.name for p in providers_from_env(transport)] == ["vast"]
