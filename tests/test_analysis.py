@@ -47,3 +47,26 @@ def test_corpus_proximity():
     tree = cluster_recursively(pts, max_depth=1, branching=4, min_size=8)
     sizes = sorted(len(c["ids"]) for c in tree["children"])
     assert sum(sizes) == 120 and len(tree["ids"]) == 120 and max(sizes) <= 60
+
+
+def test_optimizer_paths():
+    from research_b200.analysis.optimizer_paths import distance_to_minimum, render, trajectory
+
+    adam = trajectory("quadratic", "adam", steps=400, lr=0.05)
+    sgd = trajectory("quadratic", "sgd", steps=400, lr=0.05)
+    mom = trajectory("quadratic", "momentum", steps=400, lr=0.01)
+    assert adam.shape == (401, 2) and distance_to_minimum("quadratic", adam) < 0.05
+    assert distance_to_minimum("quadratic", sgd) < 1e-3 and distance_to_minimum("quadratic", mom) < 1e-2
+    ref = torch.tensor([2.0, 2.0], dtype=torch.float64, requires_grad=True)      # hand-written Adam against torch's
+    opt = torch.optim.Adam([ref], lr=0.05)
+    for _ in range(10):
+        opt.zero_grad()
+        (0.5 * (10 * ref[0] ** 2 + ref[1] ** 2)).backward()
+        opt.step()
+    assert torch.allclose(adam[10], ref.detach(), atol=1e-9)
+    blew_up = trajectory("rosenbrock", "sgd", steps=50, lr=0.1)                     # diverges: the path stops early
+    assert blew_up.shape[0] < 51
+    rose = trajectory("rosenbrock", "adam", steps=3000, lr=0.02)
+    assert distance_to_minimum("rosenbrock", rose) < 0.2
+    pic = render("rosenbrock", {"adam": rose[::50]}, width=40, height=16)
+    assert len(pic.split("\n")) == 16 and "*" in pic and "A" in pic
