@@ -1,0 +1,56 @@
+"""The speedrun GPT oracle: shapes, causality, sliding windows, document boundaries, gradients."""
+
+import torch
+
+from research_b200.models.speedrun import SpeedrunConfig, forward, init_weights, loss, rotary, rotary_tables
+
+CFG = SpeedrunConfig(vocab_size=97, num_heads=2, head_dim=16, max_seq_len=64, block_size=4)
+
+
+def test_shapes_softcap_and_zero_init():
+    w0 = init_weights(CFG, seed=0)
+    toks = torch.randint(0, CFG.vocab_size, (32,), generator=torch.Generator().manual_seed(1))
+    out0 = forward(w0, toks, CFG)
+    assert out0.shape == (32, CFG.vocab_size) and torch.allclose(out0, torch.full_like(out0, 15.0))   # zero head: sigmoid(0) * 30
+    w = init_weights(CFG, seed=0, zero_init_projections=False)
+    out = forward(w, toks, CFG)
+    assert float(out.min()) > 0 and float(out.max()) < 30 and out.std() > 1e-3
+    cos, sin = rotary_tables(CFG)
+    assert cos.shape == (64, 8) and torch.all(cos[:, 4:] == 1) and torch.all(sin[:, 4:] == 0)    # half of the pairs carry no position
+    x = torch.randn(5, 2, 16)
+    assert torch.allclose(rotary(x, cos, sin).norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+
+
+def test_causality_windows_and_documents():
+    w = init_weights(CFG, seed=2, zero_init_projections=False)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, CFG.vocab_size, (48,), generator=g)
+    base = forward(w, toks, CFG, ws_short=2, ws_long=3)
+    fut = toks.clone()
+    fut[30] = (fut[30] + 1) % CFG.vocab_size
+    changed = forward(w, fut, CFG, ws_short=2, ws_long=3)
+    assert torch.allclose(base[:30], changed[:30], atol=1e-6) and not torch.allclose(base[30:], changed[30:])
+    # a packed second document does not see the first one
+    cu = torch.tensor([0, 20, 48])
+    two = forward(w, toks, CFG, cu_seqlens=cu, ws_short=2, ws_long=3)
+    alone = forward(w, toks[20:], CFG, ws_short=2, ws_long=3)
+    # the smear gate starts at zero, so the packed document equals the same document run on its own
+    assert torch.allclose(two[20:], alone, atol=1e-4)
+    first_changed = toks.clone()
+    first_changed[5] = (first_changed[5] + 1) % CFG.vocab_size
+    two_b = forward(w, first_changed, CFG, cu_seqlens=cu, ws_short=2, ws_long=3)
+    assert torch.allclose(two[21:], two_b[21:], atol=1e-6)            # document 2 is blind to document 1
+    one_b = forward(w, first_changed, CFG, ws_short=2, ws_long=3)
+    assert not torch.allclose(base[6:12], one_b[6:12])                 # inside one document the change is seen nearby
+
+
+def test_loss_and_gradients_reach_every_parameter():
+    raw = init_weights(CFG, seed=4, zero_init_projections=False)
+    raw["scalars"][-2] = 0.3            # the smear scalar starts at zero, which would hide its gate from the gradient
+    w = {k: v.clone().requires_grad_(True) for k, v in raw.items()}
+    toks = torch.randint(0, CFG.vocab_size, (24,), generator=torch.Generator().manual_seed(5))
+    val = loss(w, toks[:-1], toks[1:], CFG, ws_short=1, ws_long=2)
+    assert torch.isfinite(val) and abs(float(val.detach()) - torch.log(torch.tensor(float(CFG.vocab_size)))) < 1.5
+    val.backward()
+    silent = [k for k, v in w.items() if v.grad is None or float(v.grad.abs().sum()) == 0.0]
+    assert silent == [], silent
