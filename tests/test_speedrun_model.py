@@ -54,3 +54,18 @@ def test_loss_and_gradients_reach_every_parameter():
     val.backward()
     silent = [k for k, v in w.items() if v.grad is None or float(v.grad.abs().sum()) == 0.0]
     assert silent == [], silent
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_flash_attention_path_matches_the_masked_oracle(cuda_device):
+    """Sliding windows over packed documents through the tcgen05 flash kernel against the explicit-mask oracle."""
+    cfg = SpeedrunConfig(vocab_size=211, num_heads=2, head_dim=64, max_seq_len=512, block_size=16)
+    w = {k: v.to(cuda_device) for k, v in init_weights(cfg, seed=6, zero_init_projections=False).items()}
+    toks = torch.randint(0, cfg.vocab_size, (384,), generator=torch.Generator().manual_seed(7)).to(cuda_device)
+    cu = torch.tensor([0, 100, 257, 384], device=cuda_device)
+    want = forward(w, toks, cfg, cu_seqlens=cu, ws_short=2, ws_long=5)
+    got = forward(w, toks, cfg, cu_seqlens=cu, ws_short=2, ws_long=5, use_flash=True)
+    assert (got - want).abs().max() < 0.15 and (got - want).abs().mean() < 0.01, ((got - want).abs().max(), (got - want).abs().mean())
