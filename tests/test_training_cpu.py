@@ -363,3 +363,32 @@ def test_moe_training_backend_cpu():
         losses.append(be.forward_backward({"input_ids": ids, "labels": ids}).wait()["loss"])
         be.optim_step().wait()
     assert losses[-1] < losses[0]
+
+
+def test_packed_shards_bos_aligned_batches(tmp_path):
+    import numpy as np
+    import pytest
+
+    from research_b200.training.datasets.packed_shards import (document_starts, load_shard, pack_documents, packed_batches,
+                                                               write_shard)
+
+    BOS = 1
+    rng = np.random.default_rng(0)
+    docs = [[BOS] + list(rng.integers(2, 500, size=int(n))) for n in rng.integers(5, 40, size=60)]
+    flat = [t for d in docs for t in d]
+    write_shard(tmp_path / "a.bin", flat)
+    toks = load_shard(tmp_path / "a.bin")
+    assert toks.tolist() == flat and len(document_starts(toks, BOS)) == 60
+    (tmp_path / "bad.bin").write_bytes(b"\0" * 2048)
+    with pytest.raises(ValueError):
+        load_shard(tmp_path / "bad.bin")
+    x, y, cu, nxt = pack_documents(toks, document_starts(toks, BOS), 0, 64, 16)
+    assert x.numel() == y.numel() == 64 and int(cu[-1]) == 64 and nxt > 0
+    lens = (cu[1:] - cu[:-1]).tolist()
+    assert max(lens) <= 16 and all(int(x[int(s)]) == BOS for s in cu[:-1])          # every sequence starts a document
+    assert torch.equal(y[:lens[0] - 1], x[1:lens[0]])                                # targets are the inputs shifted by one
+    b0 = list(packed_batches([tmp_path / "a.bin"], 64, 16, BOS, rank=0, world=2))
+    b1 = list(packed_batches([tmp_path / "a.bin"], 64, 16, BOS, rank=1, world=2))
+    assert len(b0) == len(b1) >= 2 and not torch.equal(b0[0][0], b1[0][0])
+    single = list(packed_batches([tmp_path / "a.bin"], 64, 16, BOS))
+    assert torch.equal(single[0][0], b0[0][0]) and torch.equal(single[1][0], b1[0][0])    # ranks split the same stream
