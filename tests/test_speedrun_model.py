@@ -69,3 +69,19 @@ def test_flash_attention_path_matches_the_masked_oracle(cuda_device):
     want = forward(w, toks, cfg, cu_seqlens=cu, ws_short=2, ws_long=5)
     got = forward(w, toks, cfg, cu_seqlens=cu, ws_short=2, ws_long=5, use_flash=True)
     assert (got - want).abs().max() < 0.15 and (got - want).abs().mean() < 0.01, ((got - want).abs().max(), (got - want).abs().mean())
+
+
+def test_speedrun_training_driver_learns_a_repeating_stream(tmp_path):
+    from research_b200.training.datasets.packed_shards import packed_batches, write_shard
+    from research_b200.training.speedrun import SpeedrunHyper, get_lr, get_muon_momentum, get_windows, train
+
+    h = SpeedrunHyper(num_iterations=40, adam_lr=0.02, muon_lr=0.02, ws_short_final=2, ws_long_final=4, muon_momentum_warmup=10)
+    assert get_lr(0, h) == 1.0 and abs(get_lr(40, h) - 0.1) < 1e-9 and 0.1 < get_lr(35, h) < 1.0
+    assert get_windows(0, h) == (1, 1) and get_windows(39, h) == (2, 4)
+    assert get_muon_momentum(0, h) == 0.85 and get_muon_momentum(100, h) == 0.95
+    BOS = 1
+    doc = [BOS] + [2 + (i * 7) % 11 for i in range(15)]                    # every document is the same 16 tokens
+    write_shard(tmp_path / "s.bin", doc * 400)
+    cfg = SpeedrunConfig(vocab_size=32, num_heads=2, head_dim=16, max_seq_len=64, block_size=8)
+    _, losses = train(cfg, packed_batches([tmp_path / "s.bin"], 64, 16, BOS, loop=True), h)
+    assert len(losses) == 40 and losses[0] > 3.0 and losses[-1] < 0.6 * losses[0], (losses[0], losses[-1])
