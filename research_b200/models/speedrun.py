@@ -97,12 +97,12 @@ def _attention_mask(T: int, cu_seqlens: torch.Tensor, window: int, device) -> to
 def _attend(q, k, v, cu_seqlens, window: int, scale: float, use_flash: bool) -> torch.Tensor:
     T, H, D = q.shape
     if use_flash and q.is_cuda and D in (64, 128):
-        from ..ops.flash import flash_attn_varlen
+        from ..ops.flash import flash_attention      # autograd entry: forward and backward kernels
 
         cu = cu_seqlens.to(device=q.device, dtype=torch.int32)
         max_len = int((cu[1:] - cu[:-1]).max())
-        return flash_attn_varlen(q.bfloat16().contiguous(), k.bfloat16().contiguous(), v.bfloat16().contiguous(), cu, cu, max_len,
-                                 causal=True, window=window + 1, scale=scale).to(q.dtype)
+        return flash_attention(q.bfloat16().contiguous(), k.bfloat16().contiguous(), v.bfloat16().contiguous(), cu, cu, max_len,
+                               max_len, causal=True, window=window + 1, scale=scale).to(q.dtype)
     mask = _attention_mask(T, cu_seqlens, window, q.device)
     s = torch.einsum("ihd,jhd->hij", q.float(), k.float()) * scale
     p = s.masked_fill(~mask[None], float("-inf")).softmax(-1)

@@ -69,6 +69,16 @@ def test_flash_attention_path_matches_the_masked_oracle(cuda_device):
     want = forward(w, toks, cfg, cu_seqlens=cu, ws_short=2, ws_long=5)
     got = forward(w, toks, cfg, cu_seqlens=cu, ws_short=2, ws_long=5, use_flash=True)
     assert (got - want).abs().max() < 0.15 and (got - want).abs().mean() < 0.01, ((got - want).abs().max(), (got - want).abs().mean())
+    # gradients through the flash backward kernels against autograd through the masked oracle
+    grads = {}
+    for flash in (False, True):
+        leaves = {k: v.clone().requires_grad_(True) for k, v in w.items()}
+        loss(leaves, toks[:-1], toks[1:], cfg, cu_seqlens=torch.tensor([0, 100, 257, 383], device=cuda_device), ws_short=2, ws_long=5,
+             use_flash=flash).backward()
+        grads[flash] = leaves
+    for name in ("blocks.3.qkv", "blocks.10.qkv", "embed", "value_embed.1"):
+        a, b = grads[True][name].grad.float(), grads[False][name].grad.float()
+        assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.98, name
 
 
 def test_speedrun_training_driver_learns_a_repeating_stream(tmp_path):
