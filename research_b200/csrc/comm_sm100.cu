@@ -238,6 +238,55 @@ static PeerPtrs make_ptrs(void* const* p, int world) {
   return o;
 }
 
+namespace rb {
+// Pull-based sum of one bf16 tile held by every rank: out = residual + sum_r src[r], fp32 accumulation in rank order
+// (the same order on every rank, so all ranks end with identical bits). src[r] are peer mappings of the ranks' slabs;
+// the caller's device barrier has made them complete. 16-byte vectors.
+__global__ void pull_sum_kernel(PeerPtrs src, const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
+                                long long nvec, int world) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+    {
+      const uint4 r = reinterpret_cast<const uint4*>(residual)[i];
+      const uint32_t ri[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(ri[j]);
+        acc[2 * j] = f.x; acc[2 * j + 1] = f.y;
+      }
+    }
+    uint4 part[RB_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < RB_MAX_RANKS; ++r)
+      if (r < world) part[r] = reinterpret_cast<const uint4*>(src.p[r])[i];     // all loads in flight before the adds
+#pragma unroll
+    for (int r = 0; r < RB_MAX_RANKS; ++r) {
+      if (r < world) {
+        const uint32_t pi[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(pi[j]);
+          acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+        }
+      }
+    }
+    reinterpret_cast<uint4*>(out)[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                  pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+}  // namespace rb
+using namespace rb;
+
+extern "C" int rb_pull_sum(void* const* src_ptrs, const void* residual, void* out, long long n, int world, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || n <= 0 || n % 8 != 0) return -1;
+  const long long nvec = n / 8;
+  long long grid = (nvec + 255) / 256;
+  if (grid > 148 * 4) grid = 148 * 4;
+  pull_sum_kernel<<<(unsigned)grid, 256, 0, s>>>(make_ptrs(src_ptrs, world), (const __nv_bfloat16*)residual, (__nv_bfloat16*)out,
+                                                 nvec, world);
+  return RB_OK();
+}
+
 extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int slot, int epoch, int* counter,
                                int* status, cudaStream_t s) {
   if (world < 1 || world > RB_MAX_RANKS) return -1;

@@ -39,6 +39,8 @@ def _lib():
         lib.rb_clip_coef.argtypes = [_VP, _I, PP, PP, _I, _I, _I, _I, _F, _VP, _VP, _VP, _VP]
         lib.rb_adamw_allgather.argtypes = [_VP, _VP, _VP, _VP, PP, _I, _I, _LL, _F, _F, _F, _F, _F, _I, _VP, _VP]
         lib.rb_reshard_copy.argtypes = [_VP, _I, _LL, _VP]
+        lib.rb_pull_sum.argtypes = [PP, _VP, _VP, _LL, _I, _VP]
+        lib.rb_pull_sum.restype = _I
         lib.rb_rs_num_partials.restype = _I
         for f in ("rb_symm_barrier", "rb_symm_signal", "rb_symm_wait", "rb_rs_reduce", "rb_clip_coef",
                   "rb_adamw_allgather", "rb_reshard_copy"):

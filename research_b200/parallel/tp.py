@@ -52,6 +52,10 @@ class TensorParallel:
             # [0] epoch counter of the reduce calls, [1] CTA ticket (device side, graph safe)
             self.reduce_state = torch.zeros(2, dtype=torch.int32, device=comm.device)
             self._barrier_slot = comm.new_slot()
+            # decode-sized row-parallel GEMMs with a long K: partial tile of this rank for the split path below
+            self.SPLIT_AR_ROWS = 256
+            self.ar_slab = comm.alloc((self.SPLIT_AR_ROWS * max_cols,), torch.bfloat16, zero=True)
+            self._ar_slot = comm.new_slot()
             comm.barrier_host()
 
     # ---------------------------------------------------------------- buffers
@@ -126,6 +130,10 @@ class TensorParallel:
             x.add_(part.to(x.dtype))
             return
         M, N = a.shape[0], w.shape[0]
+        if (self.SPLIT_AR and M <= self.SPLIT_AR_ROWS and a.shape[1] >= 2048 and N <= self.max_cols and x.stride(0) == N
+                and (M * N) % 8 == 0):
+            self._reduce_split(a, w, x)
+            return
         if M <= self.max_rows // self.world and M * N * 2 * (self.world - 1) <= self.ONESHOT_MAX_BYTES:
             # decode-sized output: push the partial to every rank, each rank sums locally. One hop, one kernel,
             # and no barrier afterwards: staging alternates between two parity slabs and a rank cannot run two
@@ -141,6 +149,26 @@ class TensorParallel:
     # the 8B decode step (M = 256, N = 4096) one shot wins at 2 ranks (2 MB pushed) and loses at 8 (14 MB pushed:
     # 7.20 vs 6.59 ms per step). RB_TP_ONESHOT_MAX_BYTES overrides (0 = always two hops).
     ONESHOT_MAX_BYTES = int(os.environ.get("RB_TP_ONESHOT_MAX_BYTES", 4 << 20))
+
+    # The fused reduce epilogues cannot split K (their epilogue is the reduction), so with few rows and a long K the
+    # per-rank GEMM runs on few CTAs at the rate one SM streams operands and does not shrink with the rank count.
+    # This path spends three small launches instead: the plain GEMM (which splits K over thread-block clusters) into
+    # this rank's slab, a device barrier, a pull-sum over all ranks' slabs (peer loads, rank order, so every rank gets
+    # the same bits), and a second barrier before anyone may overwrite a slab. RB_TP_SPLIT_AR=0 switches it off.
+    SPLIT_AR = os.environ.get("RB_TP_SPLIT_AR", "1") != "0"
+
+    def _reduce_split(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
+        from .symm import _lib as _comm_lib, ptr_array
+        from .. import ops
+
+        M, N = a.shape[0], w.shape[0]
+        part = self.ar_slab.local[: M * N].view(M, N)
+        ops.gemm(a, w, out=part)
+        self.comm.barrier(self._ar_slot)                  # every rank's partial is complete
+        rc = _comm_lib().rb_pull_sum(ptr_array(self.ar_slab.peer_ptrs), x.data_ptr(), x.data_ptr(), M * N, self.world,
+                                     stream_handle(a.device))
+        check_rc(rc, "rb_pull_sum")
+        self.comm.barrier(self._ar_slot)                  # every rank has read every slab: the next call may write
 
     def _reduce_oneshot(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
         M, K = a.shape

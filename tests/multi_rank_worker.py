@@ -39,7 +39,8 @@ def case_barrier(comm, dev, dt):
 def case_tp_gemms(comm, dev, dt):
     W = comm.world
     tp = TensorParallel(comm, max_rows=512, max_cols=1024)
-    for (M, N, K) in [(64 * W, 256, 128), (128 * W, 896, 512), (256, 1024, 320)]:
+    # the last two shapes (few rows, K >= 2048) take the split-K GEMM + pull-sum path on a GPU
+    for (M, N, K) in [(64 * W, 256, 128), (128 * W, 896, 512), (256, 1024, 320), (64, 1024, 4096), (256, 896, 2048)]:
         if M % (8 * W):
             continue
         a_all = [rnd((M, K), 100 + r, dev, dt) for r in range(W)]
