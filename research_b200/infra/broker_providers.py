@@ -3,8 +3,8 @@ protocol of ``infra/broker.py`` (broker/broker/providers/{lambdalabs,runpod,vast
 
 Every adapter only builds requests and maps replies; the HTTP exchange itself is a ``Transport`` callable
 ``(method, url, headers, body) -> (status, parsed JSON)``. The default transport uses ``urllib``; tests (and any
-offline use) pass a fake. Nothing here has been exercised against the real services: the build machine has no
-network, so the request shapes follow the providers' public API documentation as the reference's adapters do.
+offline use) pass a fake. The adapters have only been exercised against scripted transports; the request shapes
+follow the providers' public API documentation, as the reference's adapters do.
 """
 
 from __future__ import annotations
