@@ -1,6 +1,8 @@
 """ncu report parsing, the metrics monitor and the phase timer."""
 
 import json
+import pytest
+import torch
 
 from research_b200.utils.monitor import MetricsTail, sparkline
 from research_b200.utils.ncu_report import aggregate_launch_list, compare, read_raw, summarise_launch
@@ -124,3 +126,55 @@ def test_print_capture_and_validation(tmp_path):
         validate_ssh_key_path(str(key))
     key.chmod(0o600)
     assert validate_ssh_key_path(str(key)) == str(key)
+
+
+def test_kernel_harness_checks_times_and_round_trips(tmp_path):
+    from research_b200.utils import kernel_harness as kh
+
+    reg = kh.nvfp4_backends()
+    assert "reference" in reg and "native" in reg and len(reg) == 2
+    with pytest.raises(ValueError):
+        reg.register("reference", lambda x: x[0])
+    with pytest.raises(ValueError):
+        reg.register("odd", lambda x: x[0], language="fortran")
+
+    from research_b200.ops import nvfp4
+
+    def fp32_dot(x):                      # a second honest implementation: fp32 accumulation
+        a, b, sfa, sfb = x
+        av = nvfp4.decode_e2m1(a) * nvfp4.decode_e4m3(sfa).repeat_interleave(16, dim=-1)
+        bv = nvfp4.decode_e2m1(b) * nvfp4.decode_e4m3(sfb).repeat_interleave(16, dim=-1)
+        return torch.einsum("lmk,lk->lm", av, bv).to(torch.float16)
+
+    def off_by_a_bit(x):
+        return fp32_dot(x) + 0.5
+
+    def broken(x):
+        raise RuntimeError("no kernel image")
+
+    reg.register("fp32", fp32_dot, "fp32 accumulate", "pytorch")
+    reg.register("biased", off_by_a_bit, "wrong on purpose", "pytorch")
+    reg.register("broken", broken, "raises", "other")
+    lines = []
+    res = kh.run_suite(reg, correctness_cases=kh.SMOKE, performance_cases=[kh.GemvCase(128, 256, 1, 7, "p")], iters=3, log=lines.append)
+    assert res.get("reference").all_correct and res.get("fp32").all_correct
+    assert res.get("native").skipped and not res.get("native").correctness
+    assert res.get("biased").correctness_score == 0.0 and "elements differ" in res.get("biased").correctness[0].detail
+    assert "RuntimeError" in res.get("broken").correctness[0].detail and not res.get("broken").performance
+    assert res.get("reference").performance[0].speedup == pytest.approx(1.0)
+    assert res.get("fp32").geomean_speedup > 0 and res.get("fp32").performance[0].gbs > 0
+    table = res.table()
+    assert "skipped" in table and "2/2" in table and "0/2" in table
+    p = tmp_path / "r.json"
+    res.to_json(p)
+    back = kh.SuiteResults.from_json(p)
+    assert back.to_dict() == res.to_dict() and back.get("fp32").avg_speedup == pytest.approx(res.get("fp32").avg_speedup)
+    # same seed, same bytes; different seed, different bytes
+    a1, a2, a3 = kh.SMOKE[0].generate()[0], kh.SMOKE[0].generate()[0], kh.SMOKE[1].generate()[0]
+    assert torch.equal(a1, a2) and a1.shape != a3.shape
+    ok, rep = kh.closeness(torch.ones(2, 3), torch.ones(3, 2))
+    assert not ok and "shape" in rep
+    ok, rep = kh.closeness(torch.tensor([1.0, float("inf")]), torch.tensor([1.0, 2.0]))
+    assert not ok and "non-finite" in rep
+    assert kh.main(["--tier", "smoke", "--backends", "reference", "--device", "cpu"]) == 0
+    assert kh.main(["--list"]) == 0
