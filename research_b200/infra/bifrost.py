@@ -33,9 +33,9 @@ class ProcessSpec:
     name: str = "job"
 
     def shell_line(self) -> str:
-        env = " ".join(f"{k}={shlex.quote(v)}" for k, v in self.env.items())
+        env = "".join(f"export {k}={shlex.quote(v)}; " for k, v in self.env.items())   # exported first, so the command line may expand them
         cd = f"cd {shlex.quote(self.cwd)} && " if self.cwd else ""
-        return f"{cd}{env + ' ' if env else ''}{self.command}"
+        return f"{cd}{env}{self.command}"
 
 
 @dataclass(frozen=True)
@@ -124,3 +124,194 @@ class RemoteClient:
     def stop_job(self, name: str) -> None:
         """Terminate exactly the recorded pid of this job (never a pattern match)."""
         self.exec(f"kill $(cat {self._jd(name)}/pid) 2>/dev/null; true")
+
+    # ------------------------------------------------------------------ streaming, paths, files
+    def exec_stream(self, command: str):
+        """Yield the command's output (stdout and stderr merged) line by line as it appears; the generator's return
+        value (``StopIteration.value``) is the exit code (bifrost/bifrost/client.py:383). Streams through a local
+        ``ssh`` / ``sh`` child whatever the configured transport is."""
+        argv = self._argv(command)
+        p = subprocess.Popen(argv, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, bufsize=1)
+        drained = False
+        try:
+            for line in p.stdout:
+                yield line.rstrip("\n")
+            drained = True
+        finally:
+            p.stdout.close()
+            if not drained and p.poll() is None:      # the consumer stopped early: end exactly this child
+                p.terminate()
+        return p.wait()
+
+    def expand_path(self, path: str) -> str:
+        """``~`` and variables expanded by the target's shell."""
+        return self.exec(f"echo {path}", check=True)[1].strip()
+
+    def upload(self, local: str | Path, remote: str) -> int:
+        """Copy a file or a directory tree to ``remote`` (created as needed); returns the bytes sent. The payload is a
+        tar stream on the command's standard input, so one connection carries any number of files."""
+        import io
+        import tarfile
+
+        local = Path(local)
+        if not local.exists():
+            raise FileNotFoundError(local)
+        buf = io.BytesIO()
+        with tarfile.open(fileobj=buf, mode="w") as tf:
+            if local.is_dir():
+                for p in sorted(local.rglob("*")):
+                    tf.add(p, arcname=str(p.relative_to(local)), recursive=False)
+            else:
+                tf.add(local, arcname=Path(remote).name if not remote.endswith("/") else local.name)
+        dest = remote if local.is_dir() or remote.endswith("/") else str(Path(remote).parent)
+        q = shlex.quote(dest) if not dest.startswith("~") else dest
+        self.exec(f"mkdir -p {q} && tar -xf - -C {q}", check=True, data=buf.getvalue())
+        return buf.getbuffer().nbytes
+
+    def download(self, remote: str, local: str | Path) -> int:
+        """Copy a remote file or directory tree to ``local``; returns the number of files written. Content travels
+        base64-encoded because the transport returns text."""
+        import base64
+        import io
+        import tarfile
+
+        q = shlex.quote(remote) if not remote.startswith("~") else remote
+        _, out, _ = self.exec(f"if [ -d {q} ]; then tar -cf - -C {q} . | base64; elif [ -f {q} ]; then "
+                              f"tar -cf - -C $(dirname {q}) $(basename {q}) | base64; else exit 44; fi", check=True)
+        local = Path(local)
+        is_dir = self.exec(f"[ -d {q} ]")[0] == 0
+        n = 0
+        with tarfile.open(fileobj=io.BytesIO(base64.b64decode(out)), mode="r") as tf:
+            for m in tf.getmembers():
+                if not m.isfile() or m.name.startswith("/") or ".." in Path(m.name).parts:
+                    continue
+                target = (local / m.name) if is_dir else local
+                target.parent.mkdir(parents=True, exist_ok=True)
+                target.write_bytes(tf.extractfile(m).read())
+                n += 1
+        return n
+
+    # ------------------------------------------------------------------ servers
+    def serve(self, spec: ProcessSpec, port: int, health_path: str = "/health", timeout: float = 600.0, poll: float = 1.0) -> "ServerInfo":
+        """Start ``spec`` as a detached job and wait until ``http://127.0.0.1:<port><health_path>`` answers on the target
+        (probed there, so no tunnel is needed); raises with the log tail if the job exits first
+        (bifrost/bifrost/client.py:638, server.py)."""
+        job = self.start_job(spec)
+        probe = (f"python3 -c \"import urllib.request,sys; sys.exit(0 if urllib.request.urlopen('http://127.0.0.1:{int(port)}{health_path}',"
+                 f" timeout=2).status < 500 else 1)\" 2>/dev/null || curl -sf -o /dev/null http://127.0.0.1:{int(port)}{health_path}")
+        deadline = time.monotonic() + timeout
+        while True:
+            if self.exec(probe)[0] == 0:
+                host = "127.0.0.1" if self.connection == "local" else self.connection.partition(":")[0].rpartition("@")[2]
+                return ServerInfo(spec.name, job.pid, port, f"http://{host}:{port}", job.log_path)
+            info = self.job_status(spec.name)
+            if info.status != "running":
+                raise RemoteError(f"server {spec.name!r} ended ({info.status}, exit {info.exit_code}) before it answered:\n"
+                                  + self.job_logs(spec.name, 30))
+            if time.monotonic() > deadline:
+                raise TimeoutError(f"server {spec.name!r} did not answer on port {port} within {timeout}s")
+            time.sleep(poll)
+
+    def tunnel_argv(self, local_port: int, remote_port: int) -> list[str]:
+        """Command line of an ssh port forward to a served port (run it with ``subprocess.Popen``)."""
+        if self.connection == "local":
+            raise RemoteError("a local target needs no tunnel")
+        host, _, port = self.connection.partition(":")
+        argv = ["ssh", "-N", "-L", f"{int(local_port)}:127.0.0.1:{int(remote_port)}", "-o", "BatchMode=yes", "-o", "ExitOnForwardFailure=yes"]
+        return argv + (["-p", port] if port else []) + (["-i", self.key] if self.key else []) + [host]
+
+
+@dataclass(frozen=True)
+class ServerInfo:
+    name: str
+    pid: int | None
+    port: int
+    url: str
+    log_path: str
+
+
+class AsyncRemoteClient:
+    """The same operations as coroutines (bifrost/bifrost/async_client.py): each call runs the blocking client in a
+    worker thread, so many targets can be driven from one event loop."""
+
+    def __init__(self, *a, **kw):
+        self.sync = RemoteClient(*a, **kw)
+
+    def __getattr__(self, name: str):
+        import asyncio
+        import functools
+
+        fn = getattr(self.sync, name)
+        if not callable(fn) or name in ("exec_stream", "tunnel_argv"):
+            return fn
+
+        @functools.wraps(fn)
+        async def call(*a, **kw):
+            return await asyncio.to_thread(fn, *a, **kw)
+        return call
+
+    async def exec_stream(self, command: str):
+        import asyncio
+
+        proc = await asyncio.create_subprocess_exec(*self.sync._argv(command), stdout=asyncio.subprocess.PIPE,
+                                                    stderr=asyncio.subprocess.STDOUT)
+        async for raw in proc.stdout:
+            yield raw.decode(errors="replace").rstrip("\n")
+        await proc.wait()
+
+
+@dataclass(frozen=True)
+class GPUQuery:
+    """What to provision when no machine is given (bifrost/bifrost/provision.py:30)."""
+    type: str = "B200"
+    count: int = 1
+    max_price: float | None = None
+    min_vram_gb: int | None = None
+    spot: bool | None = None
+
+    def condition(self):
+        from .broker import q
+
+        cond = q.gpu_type.contains(self.type) & (q.gpu_count >= self.count)
+        if self.max_price is not None:
+            cond = cond & (q.price_per_hour <= self.max_price)
+        if self.min_vram_gb is not None:
+            cond = cond & (q.vram_gb >= self.min_vram_gb)
+        if self.spot is not None:
+            cond = cond & (q.spot == self.spot)
+        return cond
+
+
+def acquire_node(ssh: str | None = None, node_id: str | None = None, provision: GPUQuery | None = None, gpu_client=None,
+                 key: str | None = None, ssh_timeout: float = 600.0, poll: float = 5.0, transport: Transport = subprocess_transport,
+                 **create_kw):
+    """Exactly one of: ``ssh`` (a ``user@host[:port]`` string), ``node_id`` (an instance the broker already tracks) or
+    ``provision`` (a query; the cheapest match is created). Returns ``(RemoteClient, instance | None)`` once the target
+    answers ``echo ok`` (bifrost/bifrost/provision.py:50). ``gpu_client`` is a ``broker.GPUClient``."""
+    if sum(x is not None for x in (ssh, node_id, provision)) != 1:
+        raise ValueError("give exactly one of ssh, node_id, provision")
+    inst = None
+    if ssh is None:
+        if gpu_client is None:
+            raise ValueError("node_id / provision need a gpu_client")
+        if node_id is not None:
+            inst = gpu_client.instances.get(node_id.partition(":")[2] or node_id)
+            if inst is None:
+                raise RemoteError(f"the broker tracks no instance {node_id!r}")
+        else:
+            inst = gpu_client.create(provision.condition(), **create_kw)
+    deadline = time.monotonic() + ssh_timeout
+    while True:
+        conn = ssh or inst.ssh_connection
+        if not conn and inst is not None:
+            refresh = getattr(gpu_client.providers[inst.provider], "refresh", None)
+            if refresh:
+                inst = refresh(inst.instance_id)
+                conn = inst.ssh_connection
+        if conn:
+            client = RemoteClient(conn, key=key, transport=transport)
+            if client.exec("echo ok")[1].strip() == "ok":
+                return client, inst
+        if time.monotonic() > deadline:
+            raise TimeoutError(f"no ssh answer from {conn or (inst and inst.instance_id)!r} within {ssh_timeout}s")
+        time.sleep(poll)

@@ -125,7 +125,7 @@ class CodeIndex:
             text = (self.root / rel).read_text(errors="ignore")
             for m in _DEF.finditer(text):
                 if name is None or m.group(1) == name:
-                    out.append(Hit(rel, text.count("\n", 0, m.start()) + 1, m.group(0).strip()))
+                    out.append(Hit(rel, text.count("\n", 0, m.start(1)) + 1, m.group(0).strip()))   # the match may begin on blank lines above
         return out
 
     def stale_files(self) -> list[str]:

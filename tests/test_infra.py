@@ -151,3 +151,149 @@ def test_cloud_provider_adapters_with_fake_transport(monkeypatch):
     for var in ("LAMBDA_API_KEY", "RUNPOD_API_KEY", "PRIME_API_KEY"):
         monkeypatch.delenv(var, raising=False)
     assert [p.name for p in providers_from_env(transport)] == ["vast"]
+
+
+def test_remote_stream_files_server_and_async(tmp_path):
+    import asyncio
+    import socket
+
+    from research_b200.infra.bifrost import AsyncRemoteClient, ServerInfo
+
+    c = RemoteClient("local", job_dir=str(tmp_path / "jobs"))
+    gen = c.exec_stream("echo one; echo two >&2; exit 5")
+    lines = []
+    try:
+        while True:
+            lines.append(next(gen))
+    except StopIteration as stop:
+        assert stop.value == 5
+    assert sorted(lines) == ["one", "two"]
+    assert c.expand_path("$HOME") and "$" not in c.expand_path("$HOME")
+
+    src = tmp_path / "src"
+    (src / "sub").mkdir(parents=True)
+    (src / "a.txt").write_text("A")
+    (src / "sub" / "b.bin").write_bytes(bytes(range(256)))
+    assert c.upload(src, str(tmp_path / "up")) > 0
+    assert (tmp_path / "up" / "sub" / "b.bin").read_bytes() == bytes(range(256))
+    c.upload(src / "a.txt", str(tmp_path / "single" / "renamed.txt"))
+    assert (tmp_path / "single" / "renamed.txt").read_text() == "A"
+    assert c.download(str(tmp_path / "up"), tmp_path / "down") == 2 and (tmp_path / "down" / "a.txt").read_text() == "A"
+    assert c.download(str(tmp_path / "up" / "sub" / "b.bin"), tmp_path / "one.bin") == 1
+    assert (tmp_path / "one.bin").read_bytes() == bytes(range(256))
+    with pytest.raises(RemoteError):
+        c.download(str(tmp_path / "missing"), tmp_path / "x")
+    with pytest.raises(FileNotFoundError):
+        c.upload(tmp_path / "nope", "/tmp/x")
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    server = ProcessSpec(f"python3 -m http.server {port} --bind 127.0.0.1", cwd=str(src), name="web")
+    info = c.serve(server, port, health_path="/a.txt", timeout=30, poll=0.2)
+    try:
+        assert isinstance(info, ServerInfo) and info.url == f"http://127.0.0.1:{port}" and c.job_status("web").status == "running"
+    finally:
+        c.stop_job("web")
+    with pytest.raises(RemoteError, match="ended"):
+        c.serve(ProcessSpec("echo boom; exit 2", name="dies"), port, timeout=10, poll=0.1)
+    r = RemoteClient("u@gpu.example:2200", key="/k")
+    argv = r.tunnel_argv(8000, 30000)
+    assert argv[0] == "ssh" and "8000:127.0.0.1:30000" in argv and argv[-1] == "u@gpu.example" and "2200" in argv
+
+    async def go():
+        ac = AsyncRemoteClient("local", job_dir=str(tmp_path / "jobs"))
+        outs = await asyncio.gather(*(ac.exec(f"echo {i}") for i in range(4)))
+        streamed = [line async for line in ac.exec_stream("echo x; echo y")]
+        return [o[1].strip() for o in outs], streamed
+
+    outs, streamed = asyncio.run(go())
+    assert outs == ["0", "1", "2", "3"] and streamed == ["x", "y"]
+
+
+def test_acquire_node_three_modes():
+    from research_b200.infra.bifrost import GPUQuery, acquire_node
+
+    ok = lambda argv, data=None: (0, "ok\n", "")                                   # noqa: E731
+    client, inst = acquire_node(ssh="root@h:22", transport=ok)
+    assert client.connection == "root@h:22" and inst is None
+    offers = [GPUOffer("lab", "m1", "B200", 8, 180, 30.0), GPUOffer("lab", "m2", "B200", 1, 180, 4.0), GPUOffer("lab", "m3", "H100", 8, 80, 16.0)]
+    gc = GPUClient([StaticProvider("lab", offers, {"m1": "root@m1", "m2": "root@m2"})])
+    client, inst = acquire_node(provision=GPUQuery("B200", count=8, max_price=40.0), gpu_client=gc, transport=ok)
+    assert inst.offer.offer_id == "m1" and client.connection == "root@m1"
+    again, same = acquire_node(node_id=f"lab:{inst.instance_id}", gpu_client=gc, transport=ok)
+    assert same is inst and again.connection == "root@m1"
+    with pytest.raises(ValueError):
+        acquire_node(ssh="a@b", provision=GPUQuery())
+    with pytest.raises(RemoteError):
+        acquire_node(node_id="lab:ghost", gpu_client=gc, transport=ok)
+    with pytest.raises(RuntimeError):                                                # nothing that large
+        acquire_node(provision=GPUQuery("B200", count=16), gpu_client=gc, transport=ok)
+    with pytest.raises(TimeoutError):                                                # a machine that never answers
+        acquire_node(ssh="root@dead", transport=lambda argv, data=None: (255, "", "refused"), ssh_timeout=0.2, poll=0.05)
+
+
+def test_infra_cli_gpus_remote_and_code(tmp_path):
+    import json
+
+    from research_b200.infra.cli import main, parse_where
+
+    offers = [GPUOffer("lab", "m1", "B200", 8, 180, 30.0, "us"), GPUOffer("lab", "m2", "B200", 1, 180, 4.0, "eu", spot=True),
+              GPUOffer("lab", "m3", "H100", 8, 80, 16.0, "us")]
+    gc = GPUClient([StaticProvider("lab", offers, {"m1": "root@m1"})])
+    cond = parse_where("gpu_type~B200 gpu_count>=8 price_per_hour<40")
+    assert [o.offer_id for o in offers if cond(o)] == ["m1"] and parse_where("") is None
+    assert [o.offer_id for o in offers if parse_where("spot==true")(o)] == ["m2"]
+    with pytest.raises(ValueError):
+        parse_where("gpu_count=>8")
+    with pytest.raises(AttributeError):
+        parse_where("flops>3")
+    lines = []
+    assert main(["gpus", "search", "--where", "gpu_count>=8"], lines.append, gc) == 0
+    assert "m3" in lines[0] and lines[0].index("m3") < lines[0].index("m1") and "m2" not in lines[0]      # cheapest first
+    lines.clear()
+    assert main(["gpus", "search", "--json", "--limit", "1"], lines.append, gc) == 0 and json.loads(lines[0])[0]["offer_id"] == "m2"
+    lines.clear()
+    assert main(["gpus", "create", "--where", "gpu_type~B200 gpu_count>=8", "--provider", "lab"], lines.append, gc) == 0
+    made = json.loads(lines[0])
+    assert made["ssh"] == "root@m1" and made["offer"]["offer_id"] == "m1"
+    assert main(["gpus", "terminate", "--provider", "lab", "--id", made["id"]], lines.append, gc) == 0
+    assert main(["gpus", "terminate", "--provider", "lab", "--id", made["id"]], lines.append, gc) == 1
+
+    lines.clear()
+    assert main(["remote", "exec", "local", "echo hi; exit 4"], lines.append) == 4 and lines == ["hi"]
+    lines.clear()
+    assert main(["remote", "exec", "local", "--stream", "echo a; echo b"], lines.append) == 0 and lines == ["a", "b"]
+    home = tmp_path / "home"
+    home.mkdir()
+    import os
+    old = os.environ.get("HOME")
+    os.environ["HOME"] = str(home)                  # jobs are kept under ~/.bifrost/jobs of the target
+    try:
+        lines.clear()
+        assert main(["remote", "run", "local", "--name", "t1", "--env", "X=5", "--wait", "--timeout", "20", "echo val=$X; exit 3"], lines.append) == 3
+        assert any("val=5" in x for x in lines)
+        lines.clear()
+        assert main(["remote", "status", "local", "--name", "t1"], lines.append) == 0 and "exited" in lines[0] and "exit 3" in lines[0]
+        assert main(["remote", "logs", "local", "--name", "t1", "--tail", "5"], lines.append) == 0 and "val=5" in lines[-1]
+    finally:
+        if old is None:
+            del os.environ["HOME"]
+        else:
+            os.environ["HOME"] = old
+
+    proj = tmp_path / "proj"
+    proj.mkdir()
+    (proj / "mod.py").write_text("def rollout_step(x):\n    return x + 1\n\nclass Sampler:\n    pass\n")
+    lines.clear()
+    assert main(["code", "index", "--root", str(proj)], lines.append) == 0 and "indexed 1 files" in lines[0]
+    lines.clear()
+    assert main(["code", "search", "rollout_step", "--root", str(proj)], lines.append) == 0 and lines[0].startswith("mod.py:1:")
+    lines.clear()
+    assert main(["code", "symbols", "Sampler", "--root", str(proj)], lines.append) == 0 and "mod.py:4" in lines[0]
+    assert main(["code", "search", "nothing_like_this", "--root", str(proj)], lines.append) == 1
+    (proj / "new.py").write_text("def later():\n    pass\n")                         # an index on disk that predates a file
+    lines.clear()
+    main(["code", "index", "--root", str(proj)], lines.append)
+    assert main(["code", "search", "later", "--root", str(proj)], lines.append) == 0
