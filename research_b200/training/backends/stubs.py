@@ -1,6 +1,7 @@
-"""Placeholders the reference also ships as stubs: torch.func, JAX and torchax backends
-(rollouts/training/backends/torch_func.py:27, jax_backend.py:29, torchax_backend.py:27).
-Every method raises ``NotImplementedError``; they exist so configuration code can name them."""
+"""Placeholders the reference also ships as stubs: JAX and torchax backends
+(rollouts/training/backends/jax_backend.py:29, torchax_backend.py:27). Every method raises
+``NotImplementedError``; they exist so configuration code can name them. The third stub of the reference,
+the torch.func backend, is a working backend here (``backends/torch_func.py``)."""
 
 from __future__ import annotations
 
@@ -22,10 +23,6 @@ class _Unavailable:
 
     def load_weights(self, weights):
         raise NotImplementedError
-
-
-class TorchFuncTrainingBackend(_Unavailable):
-    _why = "functional-transform backend is a stub in the reference as well; use PyTorchTrainingBackend"
 
 
 class JAXTrainingBackend(_Unavailable):
