@@ -1,0 +1,132 @@
+"""Verifiers-style environment adapters: dataset rows, rubric -> Score, environment replies in the agent loop."""
+
+import asyncio
+from dataclasses import replace
+
+import pytest
+
+from research_b200.agents.dtypes import Endpoint, Message, Score, ToolCall, Trajectory
+from research_b200.agents.integrations import (dataset_rows, evaluate_env, prepare_messages, prime_reward_fn,
+                                               split_prompt_completion, to_chat)
+from research_b200.agents.providers import ScriptedLLM, register_provider
+
+
+class _Result:
+    def __init__(self, reward, metrics):
+        self.reward, self.metrics = reward, metrics
+
+
+class _Rubric:
+    async def score_rollout(self, prompt, completion, answer, state, **_):
+        last = next((m["content"] for m in reversed(completion) if m["role"] == "assistant"), "")
+        return _Result(1.0 if last.strip() == answer else 0.0, {"turns": state["turn"], "prompt_len": len(prompt)})
+
+
+class _SingleTurnEnv:
+    max_turns = 1
+    parser = None
+    rubric = _Rubric()
+    dataset = [{"question": "2+2?", "answer": "4"}, {"question": "3+3?", "answer": "6"}, {"question": "1+1?", "answer": "2"}]
+
+
+class _GuessEnv:
+    """Higher / lower game: the environment answers every guess until the number is hit."""
+    max_turns = 6
+    rubric = _Rubric()
+    eval_dataset = [{"prompt": [{"role": "system", "content": "guess"}, {"role": "user", "content": "start"}], "answer": "7", "id": "g0"}]
+
+    def is_completed(self, messages, state):
+        return messages[-1]["content"].strip() == state["answer"]
+
+    async def env_response(self, messages, state):
+        guess = int(messages[-1]["content"])
+        return [{"role": "user", "content": "higher" if guess < int(state["answer"]) else "lower"}], {"guesses": state.get("guesses", 0) + 1}
+
+
+def test_rows_messages_and_chat_conversion():
+    assert len(dataset_rows(_SingleTurnEnv())) == 3 and len(dataset_rows(_SingleTurnEnv(), 2)) == 2
+    assert dataset_rows(_GuessEnv())[0]["id"] == "g0"
+    with pytest.raises(ValueError):
+        dataset_rows(object())
+    m = prepare_messages({"question": "q"}, "be brief")
+    assert [x.role for x in m] == ["system", "user"] and m[1].text() == "q"
+    assert [x.role for x in prepare_messages(_GuessEnv.eval_dataset[0])] == ["system", "user"]
+    chat = to_chat([Message("assistant", "hi", tool_calls=(ToolCall("c1", "add", {"v": 1}),)), Message("tool", "3", tool_call_id="c1")])
+    assert chat[0]["tool_calls"][0]["function"] == {"name": "add", "arguments": {"v": 1}} and chat[1]["tool_call_id"] == "c1"
+    traj = Trajectory((Message("system", "be brief"), Message("user", "q"), Message("assistant", "a")))
+    prompt, completion = split_prompt_completion(traj, {"question": "q"})
+    assert [p["role"] for p in prompt] == ["system", "user"] and completion == [{"role": "assistant", "content": "a"}]
+
+
+def test_rubric_forms():
+    traj = Trajectory((Message("user", "2+2?"), Message("assistant", "4")))
+    row = {"question": "2+2?", "answer": "4"}
+    s = asyncio.run(prime_reward_fn(_SingleTurnEnv())(traj, row))
+    assert isinstance(s, Score) and s.reward == 1.0 and {m.name for m in s.metrics} == {"reward", "turns", "prompt_len"}
+
+    def exact(completion, answer):
+        return float(completion[-1]["content"] == answer)
+
+    async def brevity(completion, **kw):
+        return 1.0 / len(completion[-1]["content"])
+
+    class FuncRubric:
+        reward_funcs = [exact, brevity]
+        reward_weights = [1.0, 0.5]
+
+    class E:
+        rubric = FuncRubric()
+
+    s = asyncio.run(prime_reward_fn(E())(traj, row))
+    assert s.reward == pytest.approx(1.5) and [m.name for m in s.metrics] == ["reward", "exact", "brevity"]
+
+    class NumberRubric:
+        def score_rollout(self, completion):
+            return 0.25
+
+    class DictRubric:
+        def score_rollout(self, **kw):
+            return {"reward": 0.5, "metrics": {"x": 2}}
+
+    for rub, want in ((NumberRubric(), 0.25), (DictRubric(), 0.5)):
+        env = type("Env", (), {"rubric": rub})()
+        assert asyncio.run(prime_reward_fn(env)(traj, row)).reward == want
+    with pytest.raises(ValueError):
+        prime_reward_fn(object())
+    with pytest.raises(ValueError):
+        asyncio.run(prime_reward_fn(type("Env", (), {"rubric": object()})())(traj, row))
+
+
+def test_single_and_multi_turn_evaluation(tmp_path):
+    answers = {"2+2?": "4", "3+3?": "6", "1+1?": "3"}                     # the model gets the last one wrong
+
+    async def model(actor, run_config):
+        q = next(m.text() for m in actor.trajectory.messages if m.role == "user")
+        return await ScriptedLLM([answers[q]])(actor, run_config)
+
+    register_provider("mock", model)
+    rep = asyncio.run(evaluate_env(_SingleTurnEnv(), Endpoint(provider="mock"), output_dir=str(tmp_path)))
+    assert [s.score.reward for s in rep.samples] == [1.0, 1.0, 0.0] and rep.summary["mean_reward"] == pytest.approx(2 / 3)
+    assert any(tmp_path.iterdir())
+
+    class Bisect:                                                           # a model that really plays the game
+        async def __call__(self, actor, run_config):
+            lo, hi, last = 0, 16, None
+            for m in actor.trajectory.messages:
+                if m.role == "assistant":
+                    last = int(m.text())
+                elif last is not None and m.text() == "higher":
+                    lo = last + 1
+                elif last is not None and m.text() == "lower":
+                    hi = last - 1
+            return await ScriptedLLM([str((lo + hi) // 2)])(actor, run_config)
+
+    register_provider("mock", Bisect())
+    rep = asyncio.run(evaluate_env(_GuessEnv(), Endpoint(provider="mock")))
+    s = rep.samples[0]
+    assert s.sample_id == "g0" and s.score.reward == 1.0 and s.stop_reason == "task_completed"
+    roles = [m.role for m in s.trajectory.messages]
+    assert roles[:2] == ["system", "user"] and roles[-1] == "assistant" and roles.count("user") >= 2
+    assert s.trajectory.metadata["env_state"]["guesses"] >= 1
+    turns = next(m.value for m in s.score.metrics if m.name == "turns")
+    assert turns == roles.count("assistant")
