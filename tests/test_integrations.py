@@ -130,3 +130,37 @@ def test_single_and_multi_turn_evaluation(tmp_path):
     assert s.trajectory.metadata["env_state"]["guesses"] >= 1
     turns = next(m.value for m in s.score.metrics if m.name == "turns")
     assert turns == roles.count("assistant")
+
+
+def test_rate_limit_stress_run():
+    from research_b200.agents.providers import NonRetryableError
+    from research_b200.agents.providers.stress import main, simulated_provider, stress
+
+    async def no_sleep(_):
+        await asyncio.sleep(0)
+
+    # a tight server quota with an unthrottled client: many calls get a 429 first, all succeed after retries
+    rep = asyncio.run(stress(simulated_provider(quota=5, window_s=0.05, latency_s=0.001), requests=40, max_concurrent=16,
+                             max_attempts=50, backoff_base=0.01, max_delay=0.05))
+    assert rep.succeeded == 40 and rep.failed == 0 and rep.rate_limited_calls > 0 and rep.retries >= rep.rate_limited_calls
+    assert rep.peak_in_flight <= 16 and rep.achieved_rps > 0 and rep.percentile(0.95) >= rep.percentile(0.5) > 0
+    d = rep.to_dict()
+    assert "latencies" not in d and d["p99_s"] >= d["p50_s"] and "40/40 ok" in rep.summary()
+    # a client-side rate below the quota never trips it
+    calm = asyncio.run(stress(simulated_provider(quota=50, window_s=0.2, latency_s=0.0), requests=20, max_concurrent=4, requests_per_second=200))
+    assert calm.succeeded == 20 and calm.rate_limited_calls == 0 and calm.retries == 0 and calm.peak_in_flight <= 4
+    # attempts exhausted -> failed; a non-retryable error is not retried
+
+    async def always_429():
+        from research_b200.agents.providers import ProviderError
+        raise ProviderError("HTTP 429", 429)
+
+    gone = asyncio.run(stress(always_429, requests=3, max_attempts=3, sleep=no_sleep))
+    assert gone.failed == 3 and gone.retries == 6 and gone.succeeded == 0
+
+    async def bad_key():
+        raise NonRetryableError("HTTP 401", 401)
+
+    auth = asyncio.run(stress(bad_key, requests=4, sleep=no_sleep))
+    assert auth.failed == 4 and auth.non_retryable == 4 and auth.retries == 0
+    assert main(["--requests", "20", "--concurrency", "4", "--quota", "100", "--latency", "0"]) == 0
