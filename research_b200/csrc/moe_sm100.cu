@@ -24,9 +24,13 @@ namespace rb {
 
 constexpr int MAX_E_PER_LANE = 8;  // up to 256 experts
 
+// n_group > 1 (sigmoid router only): group-limited routing. Experts form n_group contiguous groups, a group scores
+// the sum of its two best choice values, the topk_group best groups stay eligible and the choice values of the
+// other experts become 0 (glm4_moe_functional.py:278-301).
 __global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E,
                                  int k, int sigmoid_router, int norm_topk, float scaling, int* __restrict__ topk_idx,
-                                 float* __restrict__ topk_w, int* __restrict__ counts /*[E] histogram, may be null*/) {
+                                 float* __restrict__ topk_w, int* __restrict__ counts /*[E] histogram, may be null*/,
+                                 int n_group, int topk_group) {
   __shared__ int hist[256];
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -49,6 +53,45 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
       const int e = lane + 32 * i;
       score[i] = e < E ? 1.f / (1.f + __expf(-score[i])) : -INFINITY;
       choice[i] = e < E ? score[i] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
+    }
+    if (n_group > 1 && topk_group < n_group) {
+      const int gsz = E / n_group;
+      float my_g = -INFINITY;                       // lane g keeps the score of group g (n_group <= 32)
+      for (int g = 0; g < n_group; ++g) {
+        float m1 = -INFINITY, m2 = -INFINITY;       // the two best choice values of this lane's experts in group g
+        for (int i = 0; i < per; ++i) {
+          const int e = lane + 32 * i;
+          if (e < E && e / gsz == g) {
+            const float c = choice[i];
+            if (c > m1) { m2 = m1; m1 = c; } else if (c > m2) { m2 = c; }
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {          // merge top-2 pairs of disjoint lane sets
+          const float a1 = __shfl_xor_sync(0xffffffffu, m1, o);
+          const float a2 = __shfl_xor_sync(0xffffffffu, m2, o);
+          m2 = fmaxf(fminf(m1, a1), fmaxf(m2, a2));
+          m1 = fmaxf(m1, a1);
+        }
+        if (lane == g) my_g = m1 + m2;
+      }
+      unsigned keep = 0u;
+      for (int j = 0; j < topk_group; ++j) {
+        float best = my_g;
+        int best_g = lane;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+          const int g2 = __shfl_xor_sync(0xffffffffu, best_g, o);
+          if (b2 > best || (b2 == best && g2 < best_g)) { best = b2; best_g = g2; }
+        }
+        keep |= 1u << best_g;
+        if (lane == best_g) my_g = -INFINITY;
+      }
+      for (int i = 0; i < per; ++i) {
+        const int e = lane + 32 * i;
+        if (e < E && !((keep >> (e / gsz)) & 1u)) choice[i] = 0.f;
+      }
     }
   } else {
     mx = warp_max(mx);
@@ -305,7 +348,7 @@ extern "C" int rb_moe_route(const float* logits, const float* bias, int T, int E
                             int norm_topk, float scaling, int* topk_idx, float* topk_w, cudaStream_t s) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_E_PER_LANE || k > 32 || k > E) return -1;
-  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w, nullptr);
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w, nullptr, 1, 1);
   return RB_OK();
 }
 // Routing plus the per-expert histogram of the choices (added into counts[E], which the caller zeroes).
@@ -313,7 +356,19 @@ extern "C" int rb_moe_route_count(const float* logits, const float* bias, int T,
                                   int norm_topk, float scaling, int* topk_idx, float* topk_w, int* counts, cudaStream_t s) {
   if (T <= 0) return 0;
   if (E > 32 * MAX_E_PER_LANE || k > 32 || k > E || counts == nullptr) return -1;
-  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w, counts);
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, sigmoid_router, norm_topk, scaling, topk_idx, topk_w, counts, 1, 1);
+  return RB_OK();
+}
+// The same with group-limited routing (n_group groups of E / n_group >= 2 experts, topk_group of them eligible).
+// counts may be null (no histogram).
+extern "C" int rb_moe_route_groups(const float* logits, const float* bias, int T, int E, int k, int norm_topk, float scaling,
+                                   int n_group, int topk_group, int* topk_idx, float* topk_w, int* counts, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (E > 32 * MAX_E_PER_LANE || k > 32 || k > E) return -1;
+  if (n_group < 1 || n_group > 32 || topk_group < 1 || topk_group > n_group || E % n_group != 0) return -1;
+  if (n_group > 1 && E / n_group < 2) return -1;
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, s>>>(logits, bias, T, E, k, 1, norm_topk, scaling, topk_idx, topk_w, counts, n_group,
+                                               topk_group);
   return RB_OK();
 }
 extern "C" int rb_moe_count(const int* topk_idx, int n, int E, int* counts, cudaStream_t s) {

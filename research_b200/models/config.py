@@ -40,6 +40,8 @@ class ModelConfig:
     n_shared_experts: int = 0
     first_k_dense_replace: int = 0
     routed_scaling_factor: float = 1.0
+    n_group: int = 1                   # group-limited routing (sigmoid router): expert groups ...
+    topk_group: int = 1                # ... of which this many stay eligible per token
     eos_token_id: int = -1
     init_std: float = 0.02
 
@@ -89,7 +91,8 @@ class ModelConfig:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
                      n_shared_experts=self.n_shared_experts, first_k_dense_replace=self.first_k_dense_replace,
-                     routed_scaling_factor=self.routed_scaling_factor, n_routed_experts=self.num_experts)
+                     routed_scaling_factor=self.routed_scaling_factor, n_routed_experts=self.num_experts,
+                     n_group=self.n_group, topk_group=self.topk_group)
         return d
 
     @staticmethod
@@ -116,6 +119,7 @@ class ModelConfig:
             n_shared_experts=d.get("n_shared_experts", 0) or 0,
             first_k_dense_replace=d.get("first_k_dense_replace", 0) or 0,
             routed_scaling_factor=d.get("routed_scaling_factor", 1.0) or 1.0,
+            n_group=d.get("n_group", 1) or 1, topk_group=d.get("topk_group", 1) or 1,
             eos_token_id=d.get("eos_token_id", -1) if isinstance(d.get("eos_token_id", -1), int) else -1,
             init_std=d.get("initializer_range", 0.02),
         )

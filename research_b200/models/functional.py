@@ -73,6 +73,19 @@ def dense_mlp(x, w, prefix):
     return F.linear(F.silu(g) * u, w[prefix + "down_proj.weight"])
 
 
+def group_limited_choice(choice: torch.Tensor, n_group: int, topk_group: int) -> torch.Tensor:
+    """DeepSeek-V3 / GLM-4.5 group-limited routing (glm4_moe_functional.py:278-301): experts form ``n_group``
+    contiguous groups, a group scores the sum of its two best choice values, only the ``topk_group`` best groups stay
+    eligible and the choice values of all other experts become 0 (not -inf, as in the reference)."""
+    if n_group <= 1 or topk_group >= n_group:
+        return choice
+    N, E = choice.shape
+    assert E % n_group == 0 and E // n_group >= 2, "group-limited routing needs equal groups of at least two experts"
+    group_scores = choice.view(N, n_group, E // n_group).topk(2, dim=-1).values.sum(-1)
+    keep = torch.zeros_like(group_scores, dtype=torch.bool).scatter_(1, group_scores.topk(topk_group, dim=-1).indices, True)
+    return choice.masked_fill(~keep.repeat_interleave(E // n_group, dim=1), 0.0)
+
+
 def route(x2: torch.Tensor, w, prefix: str, cfg: ModelConfig):
     """Router: returns (topk_idx [N,k] int64, topk_weight [N,k] in x dtype)."""
     logits = F.linear(x2.float(), w[prefix + "gate.weight"].float())
@@ -80,6 +93,7 @@ def route(x2: torch.Tensor, w, prefix: str, cfg: ModelConfig):
     if cfg.router_type == "sigmoid":
         scores = logits.sigmoid()
         choice = scores + w[prefix + "gate.e_score_correction_bias"].float()
+        choice = group_limited_choice(choice, cfg.n_group, cfg.topk_group)
         idx = choice.topk(k, dim=-1).indices
         wt = scores.gather(-1, idx)
         if cfg.norm_topk_prob:

@@ -44,19 +44,23 @@ def _lib():
         lib.rb_moe_combine.argtypes = [_VP, _VP, _I, _I, _I, _VP, _I, _VP]
         lib.rb_moe_publish_counts.argtypes = [_VP, PP, _I, _I, _I, _VP]
         lib.rb_moe_route_count.argtypes = [_VP, _VP, _I, _I, _I, _I, _I, _F, _VP, _VP, _VP, _VP]
+        lib.rb_moe_route_groups.argtypes = [_VP, _VP, _I, _I, _I, _I, _F, _I, _I, _VP, _VP, _VP, _VP]
         lib.rb_moe_plan_dispatch.argtypes = [_VP, _I, _I, _I, _I, _VP, _I, _I, _VP, _VP, _I, _I, _VP, _VP, _I, _VP, _I, _VP, _VP]
         lib.rb_moe_permute_planned.argtypes = lib.rb_moe_permute.argtypes
-        for f in ("rb_moe_publish_counts", "rb_moe_route_count", "rb_moe_plan_dispatch", "rb_moe_permute_planned", "rb_moe_route", "rb_moe_count", "rb_moe_plan", "rb_moe_permute", "rb_moe_translate", "rb_moe_combine"):
+        for f in ("rb_moe_publish_counts", "rb_moe_route_groups", "rb_moe_route_count", "rb_moe_plan_dispatch", "rb_moe_permute_planned", "rb_moe_route", "rb_moe_count", "rb_moe_plan", "rb_moe_permute", "rb_moe_translate", "rb_moe_combine"):
             getattr(lib, f).restype = _I
         lib._rb_typed = True
     return lib
 
 
-def route_reference(logits: torch.Tensor, k: int, sigmoid: bool, bias, norm_topk: bool, scaling: float):
+def route_reference(logits: torch.Tensor, k: int, sigmoid: bool, bias, norm_topk: bool, scaling: float, n_group: int = 1,
+                    topk_group: int = 1):
     lg = logits.float()
     if sigmoid:
+        from ..models.functional import group_limited_choice
+
         scores = lg.sigmoid()
-        choice = scores + (bias.float() if bias is not None else 0)
+        choice = group_limited_choice(scores + (bias.float() if bias is not None else 0), n_group, topk_group)
         idx = choice.topk(k, -1).indices
         w = scores.gather(-1, idx)
         if norm_topk:
@@ -224,10 +228,15 @@ class MoELayerWeights:
         lib = _lib()
         logits = ops.gemm(h, self.gate, out=self.logits[:T], out_f32=True)
         self.zbuf.zero_()
-        check_rc(lib.rb_moe_route_count(logits.data_ptr(), self.gate_bias.data_ptr() if self.gate_bias is not None else None,
-                                        T, E, k, int(cfg.router_type == "sigmoid"), int(cfg.norm_topk_prob),
-                                        float(cfg.routed_scaling_factor), self.idx.data_ptr(), self.w.data_ptr(),
-                                        self.local_counts.data_ptr(), s), "rb_moe_route_count")
+        bias = self.gate_bias.data_ptr() if self.gate_bias is not None else None
+        if cfg.router_type == "sigmoid" and cfg.n_group > 1 and cfg.topk_group < cfg.n_group:
+            check_rc(lib.rb_moe_route_groups(logits.data_ptr(), bias, T, E, k, int(cfg.norm_topk_prob), float(cfg.routed_scaling_factor),
+                                             cfg.n_group, cfg.topk_group, self.idx.data_ptr(), self.w.data_ptr(),
+                                             self.local_counts.data_ptr(), s), "rb_moe_route_groups")
+        else:
+            check_rc(lib.rb_moe_route_count(logits.data_ptr(), bias, T, E, k, int(cfg.router_type == "sigmoid"), int(cfg.norm_topk_prob),
+                                            float(cfg.routed_scaling_factor), self.idx.data_ptr(), self.w.data_ptr(),
+                                            self.local_counts.data_ptr(), s), "rb_moe_route_count")
         if self.counts_ptrs is None:
             self.counts_all[0].copy_(self.local_counts)
         else:                                     # one kernel stores my counts row on every rank
@@ -281,7 +290,7 @@ class MoELayerWeights:
         cfg, F, d = self.cfg, self.F, self.d
         hf = h.float()
         idx, w = route_reference(hf @ self.gate.float().t(), self.k, cfg.router_type == "sigmoid", self.gate_bias,
-                                 cfg.norm_topk_prob, cfg.routed_scaling_factor)
+                                 cfg.norm_topk_prob, cfg.routed_scaling_factor, cfg.n_group, cfg.topk_group)
         if self.world > 1:
             # every rank evaluates its own experts for everyone's tokens, then the sums are exchanged
             g = self.ep.comm.group

@@ -284,7 +284,10 @@ class NativeCausalLM:
         logits = lin(h, m + "gate.weight").float()
         if cfg.router_type == "sigmoid":
             scores = logits.sigmoid()
-            idx = (scores + self.p(m + "gate.e_score_correction_bias").float()).topk(k, dim=-1).indices
+            from ..models.functional import group_limited_choice
+
+            choice = group_limited_choice(scores + self.p(m + "gate.e_score_correction_bias").float(), cfg.n_group, cfg.topk_group)
+            idx = choice.topk(k, dim=-1).indices
             wt = scores.gather(-1, idx)
             if cfg.norm_topk_prob:
                 wt = wt / (wt.sum(-1, keepdim=True) + 1e-20)

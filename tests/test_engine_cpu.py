@@ -320,3 +320,39 @@ def test_async_batcher_shares_batches():
     assert [o.completion_tokens for o in outs] == [r.completion_tokens for r in ref]
     assert b.max_rows == 8 and b.steps <= 6 + 2 + 4, (b.max_rows, b.steps)   # ~one step per token, not per request
     assert all(len(m.completion_tokens) == 2 for m in more) and batcher_for(eng) is b
+
+
+def test_group_limited_routing_oracle_and_config():
+    import torch
+
+    from research_b200.models import ModelConfig, get_preset, init_random_weights
+    from research_b200.models.functional import causal_lm_forward, group_limited_choice, route
+    from research_b200.parallel.moe import route_reference
+
+    g = torch.Generator().manual_seed(0)
+    E, ng, tg = 24, 4, 2
+    choice = torch.rand(50, E, generator=g)
+    got = group_limited_choice(choice, ng, tg)
+    for r in range(50):                                                  # an independent restatement, row by row
+        gs = [sum(sorted(choice[r, a * 6:(a + 1) * 6].tolist())[-2:]) for a in range(ng)]
+        keep = sorted(range(ng), key=lambda a: -gs[a])[:tg]
+        for e in range(E):
+            assert float(got[r, e]) == (float(choice[r, e]) if e // 6 in keep else 0.0)
+    assert group_limited_choice(choice, 1, 1) is choice and group_limited_choice(choice, 4, 4) is choice
+    with pytest.raises(AssertionError):
+        group_limited_choice(choice, 24, 2)                              # groups of one expert
+    cfg = get_preset("tiny-glm4-moe", num_layers=2, num_experts=16, num_experts_per_tok=4, n_group=4, topk_group=2)
+    back = ModelConfig.from_hf_dict(cfg.to_hf_dict())
+    assert back.n_group == 4 and back.topk_group == 2
+    w = init_random_weights(cfg, seed=0)
+    x = torch.randn(40, cfg.hidden_size, generator=g)
+    idx, wt = route(x, w, "model.layers.1.mlp.", cfg)
+    assert max(len(set((row // 4).tolist())) for row in idx) <= 2        # at most two groups per token
+    plain = route(x, w, "model.layers.1.mlp.", get_preset("tiny-glm4-moe", num_layers=2, num_experts=16, num_experts_per_tok=4))[0]
+    assert not torch.equal(plain.sort(-1).values, idx.sort(-1).values)    # the limit changes some choices
+    logits = x @ w["model.layers.1.mlp.gate.weight"].float().t()
+    ridx, rw = route_reference(logits, 4, True, w["model.layers.1.mlp.gate.e_score_correction_bias"], cfg.norm_topk_prob,
+                               cfg.routed_scaling_factor, 4, 2)
+    assert torch.equal(ridx.long().sort(-1).values, idx.sort(-1).values) and torch.allclose(rw.sum(-1), wt.float().sum(-1), atol=1e-5)
+    out = causal_lm_forward(torch.randint(0, cfg.vocab_size, (1, 12), generator=g), w, cfg)
+    assert torch.isfinite(out).all()

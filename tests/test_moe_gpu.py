@@ -50,3 +50,47 @@ def test_moe_engine_vs_oracle(cuda_device, preset):
             row = lps[len(p) + j - 1]
             assert row[tok].item() >= row.max().item() - 0.3 and abs(row[tok].item() - lp) < 0.08
     eng.shutdown()
+
+
+@pytest.mark.parametrize("E,n_group,topk_group,k", [(64, 4, 2, 6), (256, 8, 4, 8), (16, 8, 3, 2), (96, 3, 1, 4), (64, 4, 4, 6)])
+def test_group_limited_router_kernel(cuda_device, E, n_group, topk_group, k):
+    import ctypes
+
+    from research_b200.ops._util import check_rc, stream_handle
+    from research_b200.parallel.moe import _lib, route_reference
+
+    g = torch.Generator().manual_seed(E + n_group)
+    T = 333
+    logits = torch.randn(T, E, generator=g) * 2.0
+    bias = torch.randn(E, generator=g) * 0.05
+    want_idx, want_w = route_reference(logits, k, True, bias, True, 2.5, n_group, topk_group)
+    lg, bs = logits.to(cuda_device), bias.to(cuda_device)
+    idx = torch.empty(T, k, dtype=torch.int32, device=cuda_device)
+    w = torch.empty(T, k, dtype=torch.float32, device=cuda_device)
+    counts = torch.zeros(E, dtype=torch.int32, device=cuda_device)
+    check_rc(_lib().rb_moe_route_groups(lg.data_ptr(), bs.data_ptr(), T, E, k, 1, ctypes.c_float(2.5), n_group, topk_group,
+                                        idx.data_ptr(), w.data_ptr(), counts.data_ptr(), stream_handle(cuda_device)), "rb_moe_route_groups")
+    got_idx, got_w = idx.cpu().long(), w.cpu()
+    order_g, order_w = got_idx.argsort(-1), want_idx.long().argsort(-1)
+    assert torch.equal(got_idx.gather(-1, order_g), want_idx.long().gather(-1, order_w))
+    assert torch.allclose(got_w.gather(-1, order_g), want_w.gather(-1, order_w), rtol=1e-4, atol=1e-6)
+    assert torch.equal(counts.cpu().long(), torch.bincount(want_idx.long().reshape(-1), minlength=E))
+    if topk_group < n_group:                                     # every chosen expert lies in one of topk_group groups
+        groups = got_idx // (E // n_group)
+        assert max(len(set(r.tolist())) for r in groups) <= topk_group
+
+
+def test_moe_layer_with_group_limited_routing(cuda_device):
+    cfg = get_preset("tiny-glm4-moe", num_layers=2, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, hidden_size=256,
+                     init_std=0.05, n_group=4, topk_group=2)
+    w = {n: v.bfloat16().float() for n, v in init_random_weights(cfg, seed=0).items() if n.startswith("model.layers.1.mlp.")}
+    layer = MoELayerWeights(cfg, cuda_device)
+    layer.load(w, "model.layers.1.mlp.")
+    T = 200
+    h = (torch.randn(T, 256) * 0.5).bfloat16()
+    x0 = torch.randn(T, 256).bfloat16()
+    x = x0.clone().to(cuda_device)
+    layer.forward(h.to(cuda_device), x)
+    want = x0.float() + moe_mlp(h.float()[None], w, "model.layers.1.mlp.", cfg)[0]
+    err = (x.float().cpu() - want).abs()
+    assert err.max().item() < 0.06 + 0.02 * want.abs().max().item(), err.max().item()
