@@ -167,6 +167,9 @@ __global__ void clip_coef_kernel(const float* __restrict__ partial, int n_partia
 
 // ---- sharded AdamW fused with the parameter all-gather ------------------------------------------
 // params.p[r]: rank r's full bf16 parameter bucket [n_total]; this rank owns [rank*n_shard, +n_shard).
+// VEC: the four fp32 streams are read and written as float4 (needs 16-byte aligned base pointers); otherwise each
+// thread walks its eight elements with scalar accesses.
+template <bool VEC>
 __global__ void adamw_allgather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                                        const float* __restrict__ grad, PeerPtrs params, int rank, int world,
                                        long long n_shard, float lr, float beta1, float beta2, float eps,
@@ -174,25 +177,64 @@ __global__ void adamw_allgather_kernel(float* __restrict__ master, float* __rest
   const float clip = clip_coef != nullptr ? *clip_coef : 1.f;
   const long long nvec = n_shard >> 3;
   const long long base = (long long)rank * n_shard;
+  const float decay = 1.f - lr * weight_decay, ibc1 = 1.f / bc1, ibc2 = 1.f / bc2;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
-    float p[8];
+    float g8[8], m8[8], v8[8], p8[8];
+    if constexpr (VEC) {
+      const float4* g4 = reinterpret_cast<const float4*>(grad) + 2 * i;
+      const float4* m4 = reinterpret_cast<const float4*>(m) + 2 * i;
+      const float4* v4 = reinterpret_cast<const float4*>(v) + 2 * i;
+      const float4* p4 = reinterpret_cast<const float4*>(master) + 2 * i;
+      *reinterpret_cast<float4*>(g8) = g4[0];
+      *reinterpret_cast<float4*>(g8 + 4) = g4[1];
+      *reinterpret_cast<float4*>(m8) = m4[0];
+      *reinterpret_cast<float4*>(m8 + 4) = m4[1];
+      *reinterpret_cast<float4*>(v8) = v4[0];
+      *reinterpret_cast<float4*>(v8 + 4) = v4[1];
+      *reinterpret_cast<float4*>(p8) = p4[0];
+      *reinterpret_cast<float4*>(p8 + 4) = p4[1];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const long long k = i * 8 + j;
+        g8[j] = grad[k];
+        m8[j] = m[k];
+        v8[j] = v[k];
+        p8[j] = master[k];
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const long long k = i * 8 + j;
-      const float g = grad[k] * clip;
-      const float mi = beta1 * m[k] + (1.f - beta1) * g;
-      const float vi = beta2 * v[k] + (1.f - beta2) * g * g;
-      m[k] = mi;
-      v[k] = vi;
-      p[j] = master[k] * (1.f - lr * weight_decay) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-      master[k] = p[j];
+      const float g = g8[j] * clip;
+      m8[j] = beta1 * m8[j] + (1.f - beta1) * g;
+      v8[j] = beta2 * v8[j] + (1.f - beta2) * g * g;
+      p8[j] = p8[j] * decay - lr * (m8[j] * ibc1) / (sqrtf(v8[j] * ibc2) + eps);
+    }
+    if constexpr (VEC) {
+      float4* m4 = reinterpret_cast<float4*>(m) + 2 * i;
+      float4* v4 = reinterpret_cast<float4*>(v) + 2 * i;
+      float4* p4 = reinterpret_cast<float4*>(master) + 2 * i;
+      m4[0] = *reinterpret_cast<float4*>(m8);
+      m4[1] = *reinterpret_cast<float4*>(m8 + 4);
+      v4[0] = *reinterpret_cast<float4*>(v8);
+      v4[1] = *reinterpret_cast<float4*>(v8 + 4);
+      p4[0] = *reinterpret_cast<float4*>(p8);
+      p4[1] = *reinterpret_cast<float4*>(p8 + 4);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const long long k = i * 8 + j;
+        m[k] = m8[j];
+        v[k] = v8[j];
+        master[k] = p8[j];
+      }
     }
     uint4 o;
-    o.x = pack_bf16x2(p[0], p[1]);
-    o.y = pack_bf16x2(p[2], p[3]);
-    o.z = pack_bf16x2(p[4], p[5]);
-    o.w = pack_bf16x2(p[6], p[7]);
+    o.x = pack_bf16x2(p8[0], p8[1]);
+    o.y = pack_bf16x2(p8[2], p8[3]);
+    o.z = pack_bf16x2(p8[4], p8[5]);
+    o.w = pack_bf16x2(p8[6], p8[7]);
     for (int rr = 0; rr < world; ++rr) {
       const int dst = (rank + rr) % world;
       st_peer_16(reinterpret_cast<__nv_bfloat16*>(params.p[dst]) + base + i * 8, o);
@@ -324,8 +366,14 @@ extern "C" int rb_adamw_allgather(float* master, float* m, float* v, const float
                                   float weight_decay, int step, const float* clip_coef, cudaStream_t s) {
   if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
   const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
-  adamw_allgather_kernel<<<148 * 4, 256, 0, s>>>(master, m, v, grad, make_ptrs(param_ptrs, world), rank, world, n_shard,
-                                                 lr, beta1, beta2, eps, weight_decay, bc1, bc2, clip_coef);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         reinterpret_cast<uintptr_t>(grad)) & 15) == 0;
+  if (aligned)
+    adamw_allgather_kernel<true><<<148 * 8, 256, 0, s>>>(master, m, v, grad, make_ptrs(param_ptrs, world), rank, world, n_shard,
+                                                         lr, beta1, beta2, eps, weight_decay, bc1, bc2, clip_coef);
+  else
+    adamw_allgather_kernel<false><<<148 * 4, 256, 0, s>>>(master, m, v, grad, make_ptrs(param_ptrs, world), rank, world, n_shard,
+                                                          lr, beta1, beta2, eps, weight_decay, bc1, bc2, clip_coef);
   return RB_OK();
 }
 // segs: device array of Segment (layout mirrored by research_b200/parallel/weight_sync.py)

@@ -143,8 +143,11 @@ def find_shards(path: str) -> list[Path]:
 
 
 def pretrain(cfg: PretrainConfig, steps: int | None = None, device: str | None = None, synthetic: bool | None = None,
-             backend_factory: Callable[..., Any] | None = None, log: Callable[[str], None] | None = print) -> list[dict[str, float]]:
-    """Run the loop; returns one metrics dict per step (``loss``, ``lr``, ``grad_norm``, ``tokens_per_s``, ``step_s``)."""
+             backend_factory: Callable[..., Any] | None = None, log: Callable[[str], None] | None = print,
+             kernel_table: str | Path | None = None) -> list[dict[str, float]]:
+    """Run the loop; returns one metrics dict per step (``loss``, ``lr``, ``grad_norm``, ``tokens_per_s``, ``step_s``).
+    ``kernel_table`` (CUDA only): after the loop, one more step runs under the PyTorch profiler and the device time
+    per kernel is written to that file."""
     from .backends.native import NativeTrainingBackend, warmup_cosine
     from .types import TrainerConfig
 
@@ -183,6 +186,20 @@ def pretrain(cfg: PretrainConfig, steps: int | None = None, device: str | None =
             log(f"step {rec['step']:5d}  loss {rec['loss']:.4f}  lr {rec['lr']:.2e}  |g| {rec['grad_norm']:.3f}  {rec['tokens_per_s']:,.0f} tok/s")
         if t.checkpoint_every and t.checkpoint_dir and (step + 1) % t.checkpoint_every == 0:
             backend.save_checkpoint(step + 1, {"loss": rec["loss"]})
+    if kernel_table and str(backend.device).startswith("cuda"):
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            backend.forward_backward(next(data)).wait()
+            backend.optim_step().wait()
+            torch.cuda.synchronize(backend.device)
+        rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in rows) or 1.0
+        with open(kernel_table, "w") as f:
+            f.write(f"# device time per kernel, one pretraining step ({mc.family}, {mc.num_params() / 1e6:.0f}M params, batch "
+                    f"{t.batch_size} x {t.seq_len}); total {total / 1e3:.1f} ms under the profiler\n")
+            for e in rows[:40]:
+                f.write(f"{e.device_time_total / total * 100:5.1f}%  n={e.count:5d}  avg={e.device_time_total / max(e.count, 1):9.1f}us  {e.key[:110]}\n")
     return history
 
 
@@ -194,11 +211,12 @@ def main(argv: Sequence[str] | None = None) -> int:
     ap.add_argument("--synthetic", action="store_true")
     ap.add_argument("--seq-len", type=int, default=None, help="override [training].seq_len")
     ap.add_argument("--json", default="", help="write the per-step metrics here")
+    ap.add_argument("--kernel-table", default="", help="write device time per kernel of one extra, profiled step here (CUDA)")
     a = ap.parse_args(argv)
     cfg = PretrainConfig.from_toml(a.config)
     if a.seq_len:
         cfg = replace(cfg, training=replace(cfg.training, seq_len=a.seq_len))
-    hist = pretrain(cfg, a.steps, a.device, True if a.synthetic else None)
+    hist = pretrain(cfg, a.steps, a.device, True if a.synthetic else None, kernel_table=a.kernel_table or None)
     if a.json:
         Path(a.json).write_text(json.dumps(hist))
     return 0
