@@ -104,9 +104,10 @@ def grpo_clipped_from_logprobs(logprobs, entropy, batch, clip_range: float = 0.2
     loss = pg - entropy_coef * ent
     with torch.no_grad():
         clipped = (ratio < 1 - clip_range) | (ratio > 1 + clip_range)
-    return loss, {"pg_loss": pg.item(), "entropy": float(ent), "clipfrac": clipped.float().mean().item(),
-                  "approx_kl": ((ratio - 1) - log_ratio).mean().item(), "avg_ratio": ratio.mean().item(),
-                  "avg_logprob": seq_lp.mean().item(), "avg_advantage": adv.mean().item()}
+        metrics = {"pg_loss": pg.item(), "entropy": float(ent), "clipfrac": clipped.float().mean().item(),
+                   "approx_kl": ((ratio - 1) - log_ratio).mean().item(), "avg_ratio": ratio.mean().item(),
+                   "avg_logprob": seq_lp.mean().item(), "avg_advantage": adv.mean().item()}
+    return loss, metrics
 
 
 def grpo_masked_from_logprobs(logprobs, entropy, batch, ratio_low: float = 0.1, ratio_high: float = 10.0,
