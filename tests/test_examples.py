@@ -110,3 +110,30 @@ def test_run_remote_against_this_machine(tmp_path, monkeypatch):
     assert code == 0 and any("hello from job" in x for x in lines)
     fetched = list((repo / "results").rglob("out.txt"))
     assert fetched and fetched[0].read_text() == "42"
+
+
+def test_integration_training_single_device_and_two_cpu_ranks(tmp_path):
+    import json
+    import subprocess
+
+    from examples.integration_training.base_config import Config, OutputSection, RLSection, SFTSection, TargetConfig
+    from examples.integration_training.train import launch_command, main
+
+    one = tmp_path / "one.py"
+    one.write_text("from examples.integration_training.base_config import *\n"
+                   f"config = Config(target=TargetConfig(device='cpu'), sft=SFTSection(num_steps=4, batch_size=4, num_rows=16), "
+                   f"rl=RLSection(num_steps=1, batch_size=2, n_samples_per_prompt=2, max_tokens=6, num_prompts=4), "
+                   f"output=OutputSection(mode='sft_then_rl', save_dir={str(tmp_path)!r}, experiment_name='one'))\n")
+    assert main([str(one)]) == 0
+    s = json.loads((tmp_path / "one" / "summary.json").read_text())
+    assert s["sft"]["last_loss"] < s["sft"]["first_loss"] and s["rl"]["steps"] == 1 and (tmp_path / "one" / "sft_hf" / "model.safetensors").exists()
+    two = tmp_path / "two.py"
+    two.write_text("from examples.integration_training.base_config import *\n"
+                   f"config = Config(target=TargetConfig(gpu_ranks=(0, 1), train_backend='fsdp', device='cpu', master_port=29533), "
+                   f"sft=SFTSection(num_steps=4, batch_size=4, num_rows=16), output=OutputSection(mode='sft', save_dir={str(tmp_path)!r}, experiment_name='two'))\n")
+    cmd = launch_command(Config(target=TargetConfig(gpu_ranks=(0, 1))), "train.py", "c.py")
+    assert "--nproc-per-node=2" in cmd and "--master-addr=127.0.0.1" in cmd and cmd[-2:] == ["train.py", "c.py"]
+    r = subprocess.run([sys.executable, str(ROOT / "examples" / "integration_training" / "train.py"), str(two)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    s2 = json.loads((tmp_path / "two" / "summary.json").read_text())
+    assert s2["sft"]["steps"] == 4 and s2["sft"]["last_loss"] < s2["sft"]["first_loss"]
