@@ -137,3 +137,14 @@ def test_integration_training_single_device_and_two_cpu_ranks(tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     s2 = json.loads((tmp_path / "two" / "summary.json").read_text())
     assert s2["sft"]["steps"] == 4 and s2["sft"]["last_loss"] < s2["sft"]["first_loss"]
+
+
+def test_chess_examples():
+    from examples.eval.chess_puzzles.beam_search_demo import run as beam
+    from examples.eval.chess_puzzles.run import PUZZLES, mate_in_one, run
+
+    assert all(mate_in_one(p["fen"]) in p["solution"] for p in PUZZLES)
+    rep = run()
+    assert rep.summary["mean_reward"] == 1.0 and all(s.stop_reason == "task_completed" for s in rep.samples)
+    node = beam()
+    assert node.score == 1.0 and node.depth == 3 and node.state.is_checkmate()
