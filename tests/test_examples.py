@@ -148,3 +148,13 @@ def test_chess_examples():
     assert rep.summary["mean_reward"] == 1.0 and all(s.stop_reason == "task_completed" for s in rep.samples)
     node = beam()
     assert node.score == 1.0 and node.depth == 3 and node.state.is_checkmate()
+
+
+def test_rlm_needle_in_haystack():
+    from examples.eval.rlm.needle_haystack import make_rows, run
+
+    rows = make_rows(n=2, lines=300)
+    rep = run(rows)
+    assert rep.summary["mean_reward"] == 1.0
+    chars = [m.value for s in rep.samples for m in s.score.metrics if m.name == "prompt_chars"]
+    assert max(chars) < 400 < len(rows[0]["context"])                    # the document never entered the prompt
