@@ -71,8 +71,8 @@ def run_remote(script_path: str, ssh: str | None = None, node_id: str | None = N
     rel = Path(script_path).resolve().relative_to(REPO_ROOT)
     try:
         workspace = client.expand_path("~/.bifrost/workspaces/research_b200")
-        out(f"deploying {client.push(REPO_ROOT, workspace)[:12]} to {client.connection}:{workspace}")
-        client.exec(f"cd {workspace} && python -m research_b200._native", check=True)
+        commit = client.push(REPO_ROOT, workspace, bootstrap="python -m research_b200._native")     # build the kernels there
+        out(f"deployed {commit[:12]} to {client.connection}:{workspace}")
         spec = ProcessSpec(f"python {rel}", cwd=workspace, env={"PYTHONUNBUFFERED": "1", "ROLLOUTS_RUN_NAME": run_name}, name=run_name)
         job = client.start_job(spec)
         out(f"started {run_name} (pid {job.pid}, log {job.log_path})")

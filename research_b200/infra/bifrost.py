@@ -76,8 +76,9 @@ class RemoteClient:
         return code, out, err
 
     # ------------------------------------------------------------------ code push
-    def push(self, repo: str | Path, dest: str, ref: str = "HEAD") -> str:
-        """Ship ``ref`` of a local git repository to ``dest`` on the target; returns the commit id deployed."""
+    def push(self, repo: str | Path, dest: str, ref: str = "HEAD", bootstrap: str | list[str] | None = None) -> str:
+        """Ship ``ref`` of a local git repository to ``dest`` on the target; returns the commit id deployed.
+        ``bootstrap``: command(s) run in ``dest`` afterwards (environment set-up, builds); a failure raises."""
         repo = Path(repo)
         commit = subprocess.run(["git", "-C", str(repo), "rev-parse", ref], capture_output=True, text=True, check=True).stdout.strip()
         bundle = subprocess.run(["git", "-C", str(repo), "bundle", "create", "-", ref], capture_output=True, check=True).stdout
@@ -85,6 +86,8 @@ class RemoteClient:
         script = (f"set -e; mkdir -p {q}; cat > {q}/.incoming.bundle; cd {q}; [ -d .git ] || git init -q; "
                   f"git fetch -q .incoming.bundle {shlex.quote(ref)}; git checkout -q -f {commit}; rm -f .incoming.bundle")
         self.exec(script, check=True, data=bundle)
+        for cmd in ([bootstrap] if isinstance(bootstrap, str) else list(bootstrap or [])):
+            self.exec(f"cd {q} && {cmd}", check=True)
         return commit
 
     # ------------------------------------------------------------------ detached jobs

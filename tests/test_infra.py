@@ -38,6 +38,10 @@ def test_remote_client_local_jobs_and_push(tmp_path):
     (repo / "f.txt").write_text("v2")
     git("commit", "-qam", "two")
     c.push(repo, str(tmp_path / "deploy"), ref="main")
+    c.push(repo, str(tmp_path / "deploy"), ref="main", bootstrap=["cp f.txt copy.txt", "echo built > stamp"])
+    assert (tmp_path / "deploy" / "copy.txt").read_text() == "v2" and (tmp_path / "deploy" / "stamp").exists()
+    with pytest.raises(RemoteError):
+        c.push(repo, str(tmp_path / "deploy"), ref="main", bootstrap="exit 9")
     assert (tmp_path / "deploy" / "f.txt").read_text() == "v2"
 
 
