@@ -172,9 +172,16 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
             with timer.phase("rollout"):
                 batch = await manager.generate_batch()
             for s in batch.samples:
-                rollouts_file.write(json.dumps({"step": step, "reward": s.reward, "tokens": len(s.tokens),
-                                                "response_length": s.response_length, "group": s.group_index,
-                                                "weight_version": s.weight_version}) + "\n")
+                rec = {"step": step, "reward": s.reward, "tokens": len(s.tokens), "response_length": s.response_length,
+                       "group": s.group_index, "weight_version": s.weight_version}
+                text = (s.metadata or {}).get("response_text")
+                if text is not None:                       # with a tokenizer the record is readable (trace viewer)
+                    p = s.prompt
+                    rec["prompt"] = (p[-1].get("content", "") if isinstance(p, list) and p and isinstance(p[-1], dict) else str(p))[:2000]
+                    rec["response"] = str(text)[:4000]
+                    if s.ground_truth is not None:
+                        rec["ground_truth"] = str(s.ground_truth)[:500]
+                rollouts_file.write(json.dumps(rec) + "\n")
             adv = compute_group_advantages(batch.rewards, batch.group_indices, config.normalize_advantage_std)
             tb = _prepare_training_batch(batch, adv, config.max_seq_len)
             n = tb["input_ids"].shape[0]

@@ -61,3 +61,37 @@ def test_replay_directory_and_cli(tmp_path, capsys):
     mon = TrainingMonitor()
     mon.run(io.StringIO(_log("training", "from a stream", step=7) + "\n"))          # not a tty: feeds, prints once, returns
     assert "from a stream" in capsys.readouterr().out and mon.last_step == 7
+
+
+def test_trace_viewer_on_a_real_run(tmp_path, capsys):
+    import sys
+    from dataclasses import replace
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    if str(root) not in sys.path:
+        sys.path.insert(0, str(root))
+    from examples.rl.reverse_text.base_config import DEFAULT, train
+    from research_b200.frontend.traces import TraceData, main as traces_main
+
+    train(replace(DEFAULT, num_steps=2, output_dir=str(tmp_path), batch_size=2, n_samples_per_prompt=2, max_tokens=6, num_minibatches=1),
+          num_samples=4, device="cpu")
+    run = next(p for p in tmp_path.iterdir() if p.is_dir())
+    data = TraceData.load(run)
+    assert data.steps() == [0, 1] and len(data.traces) == 8
+    t = data.by_step[0][0]
+    assert t.prompt and t.ground_truth == t.prompt[::-1] and t.response_length == 6 and "weight_version" in t.extra
+    s = data.step_summary(1)
+    assert s["samples"] == 4 and s["groups"] == 2 and s["min_reward"] <= s["mean_reward"] <= s["max_reward"]
+    assert traces_main([str(run)]) == 0 and "mean reward per step" in capsys.readouterr().out
+    assert traces_main([str(run), "--step", "1"]) == 0 and "group" in capsys.readouterr().out
+    assert traces_main([str(run), "--step", "1", "--sample", "0"]) == 0
+    out = capsys.readouterr().out
+    assert "--- prompt" in out and "--- ground truth" in out
+    assert traces_main([str(run), "--step", "9"]) == 1 and traces_main([str(tmp_path / "none")]) == 1
+    # the monitor's replay skips rollout records but shows the run's metrics
+    from research_b200.frontend.training_monitor import TrainingMonitor, replay_lines
+
+    mon = TrainingMonitor()
+    mon.feed(replay_lines(run))
+    assert "mean_reward" in mon.series and mon.last_step is not None
