@@ -158,3 +158,17 @@ def test_rlm_needle_in_haystack():
     assert rep.summary["mean_reward"] == 1.0
     chars = [m.value for s in rep.samples for m in s.score.metrics if m.name == "prompt_chars"]
     assert max(chars) < 400 < len(rows[0]["context"])                    # the document never entered the prompt
+
+
+def test_browsing_eval_on_the_offline_web():
+    from examples.eval.browsecomp.base_config import BrowseConfig, extract_answer, run_eval
+    from examples.eval.browsecomp.eval_scripted_01_01 import searcher_reader
+    from research_b200.agents.dtypes import Endpoint
+    from research_b200.agents.providers import register_provider
+
+    assert extract_answer("x\nExact Answer: Askvik.") == "Askvik" and extract_answer("no answer") is None
+    register_provider("mock", searcher_reader)
+    rep = run_eval(BrowseConfig(endpoint=Endpoint(provider="mock")))
+    assert rep.summary["mean_reward"] == 1.0
+    by = {s.sample_id: {m.name: m.value for m in s.score.metrics} for s in rep.samples}
+    assert all(1 <= m["pages_read"] <= 3 and m["searches"] == 1 and m["answered"] == 1.0 for m in by.values())
