@@ -194,6 +194,20 @@ def cmd_bench(args) -> int:
     os.execv(sys.executable, [sys.executable, str(root / "bench.py")] + args.rest)
 
 
+_DELEGATES = {   # sub-command -> module whose ``main(argv)`` takes the remaining arguments
+    "monitor": "research_b200.frontend.training_monitor", "traces": "research_b200.frontend.traces",
+    "pretrain": "research_b200.training.pretrain", "infra": "research_b200.infra.cli",
+    "kernel-harness": "research_b200.utils.kernel_harness",
+}
+
+
+def cmd_delegate(args) -> int:
+    import importlib
+
+    rest = args.rest[1:] if args.rest[:1] == ["--"] else args.rest
+    return int(importlib.import_module(_DELEGATES[args.command]).main(rest) or 0)
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="research_b200")
     sub = ap.add_subparsers(dest="command", required=True)
@@ -226,10 +240,17 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--output-dir", default=None); p.add_argument("--name", default="eval")
     p.set_defaults(fn=cmd_eval)
     p = sub.add_parser("bench"); p.add_argument("rest", nargs=argparse.REMAINDER); p.set_defaults(fn=cmd_bench)
+    for name, module in _DELEGATES.items():
+        p = sub.add_parser(name, help=f"python -m {module}", add_help=False)
+        p.add_argument("rest", nargs=argparse.REMAINDER)
+        p.set_defaults(fn=cmd_delegate)
     return ap
 
 
 def main(argv: list[str] | None = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in _DELEGATES:           # handed over whole: argparse would trip over the tool's own options
+        return cmd_delegate(argparse.Namespace(command=argv[0], rest=argv[1:]))
     args = build_parser().parse_args(argv)
     return int(args.fn(args) or 0)
 

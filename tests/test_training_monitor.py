@@ -95,3 +95,14 @@ def test_trace_viewer_on_a_real_run(tmp_path, capsys):
     mon = TrainingMonitor()
     mon.feed(replay_lines(run))
     assert "mean_reward" in mon.series and mon.last_step is not None
+
+
+def test_cli_delegates_to_the_tools(tmp_path, capsys):
+    from research_b200.cli import main as cli
+
+    (tmp_path / "rollouts.jsonl").write_text(json.dumps({"step": 0, "reward": 1.0, "group": 0, "tokens": 5, "response_length": 2}) + "\n")
+    assert cli(["traces", str(tmp_path)]) == 0 and "mean reward per step" in capsys.readouterr().out
+    (tmp_path / "training.log").write_text(_log("training", "hello monitor") + "\n")
+    assert cli(["monitor", "--replay", str(tmp_path), "--once"]) == 0 and "hello monitor" in capsys.readouterr().out
+    assert cli(["infra", "remote", "exec", "local", "echo via-cli"]) == 0 and "via-cli" in capsys.readouterr().out
+    assert cli(["kernel-harness", "--list"]) == 0 and "reference" in capsys.readouterr().out
