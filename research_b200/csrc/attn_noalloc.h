@@ -12,8 +12,9 @@
 // Contract
 //   * The partial results live in one file-scope device array of RB_DECODE_NOALLOC_MAX_FLOATS
 //     floats (16 MiB). Every GPU that loads the library holds that array until the process
-//     exits. A call needs B * Hq * num_splits * (D + 2) floats; a call that needs more is
-//     rejected with RB_NOALLOC_TOO_LARGE and nothing is launched.
+//     exits. A call with num_splits > 1 needs B * Hq * num_splits * (D + 2) floats; a call that
+//     needs more is rejected with RB_NOALLOC_TOO_LARGE and nothing is launched. A call with
+//     num_splits == 1 writes its output directly, uses none of the array and has no size limit.
 //   * The first call on each device looks up the array's device address (with that device
 //     current) and remembers it. Make that first call before starting any stream capture.
 //   * The function calls no cudaMalloc / cudaFree and no allocating library routine. Inputs

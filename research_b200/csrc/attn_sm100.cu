@@ -640,6 +640,15 @@ using namespace rb;
 
 extern "C" void rb_attn_set_pdl(int on) { rb::pdl_enabled() = on != 0; }
 
+// Function attributes (the dynamic shared-memory opt-in) belong to a device, so the "already set" flags of the
+// launchers below are kept per device: a process that drives several GPUs sets them on each.
+#define RB_MAX_DEVICES 64
+static int current_device_index() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= RB_MAX_DEVICES) return -1;
+  return dev;
+}
+
 // Scratch needed by rb_paged_decode when num_splits > 1, in floats.
 extern "C" long long rb_paged_decode_workspace_floats(int B, int Hq, int D, int num_splits) {
   if (num_splits <= 1) return 0;
@@ -664,11 +673,13 @@ extern "C" int rb_paged_decode(const void* q, const void* k_cache, const void* v
     if (tma_map_2d_bf16(&vmap, v_cache, rows, D, D, KV_BLOCK) != 0) return -21;
 #define LAUNCH_DEC_TMA(DD)                                                                                    \
   do {                                                                                                        \
-    static bool attr = false;                                                                                 \
-    if (!attr) {                                                                                              \
+    static bool attr[RB_MAX_DEVICES] = {};   /* the opt-in above 48 KB is a per-device function attribute */  \
+    const int dev_ = current_device_index();                                                                  \
+    if (dev_ < 0) return -10;                                                                                 \
+    if (!attr[dev_]) {                                                                                        \
       if (cudaFuncSetAttribute(paged_decode_tma_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
                                decode_tma_smem_bytes<DD>()) != cudaSuccess) return -10;                       \
-      attr = true;                                                                                            \
+      attr[dev_] = true;                                                                                      \
     }                                                                                                         \
     launch_kernel(paged_decode_tma_kernel<DD>, grid, dim3(DEC_WARPS * 32), decode_tma_smem_bytes<DD>(), stream, \
         (const __nv_bfloat16*)q, kmap, vmap, block_tables, seq_lens, (__nv_bfloat16*)out, part_o, part_ml, Hq, \
@@ -685,11 +696,13 @@ extern "C" int rb_paged_decode(const void* q, const void* k_cache, const void* v
   }
 #define LAUNCH_DEC(DD)                                                                                        \
   do {                                                                                                        \
-    static bool attr = false;                                                                                 \
-    if (!attr) {                                                                                              \
+    static bool attr[RB_MAX_DEVICES] = {};                                                                    \
+    const int dev_ = current_device_index();                                                                  \
+    if (dev_ < 0) return -10;                                                                                 \
+    if (!attr[dev_]) {                                                                                        \
       if (cudaFuncSetAttribute(paged_decode_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                                decode_smem_bytes<DD>()) != cudaSuccess) return -10;                           \
-      attr = true;                                                                                            \
+      attr[dev_] = true;                                                                                      \
     }                                                                                                         \
     launch_kernel(paged_decode_kernel<DD>, grid, dim3(DEC_WARPS * 32), decode_smem_bytes<DD>(), stream,        \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,  \
@@ -715,11 +728,13 @@ extern "C" int rb_paged_prefill(const void* q, const void* k_cache, const void* 
   dim3 grid((max_new + PF_BM - 1) / PF_BM, Hq, B);
 #define LAUNCH_PF(DD)                                                                                         \
   do {                                                                                                        \
-    static bool attr = false;                                                                                 \
-    if (!attr) {                                                                                              \
+    static bool attr[RB_MAX_DEVICES] = {};                                                                    \
+    const int dev_ = current_device_index();                                                                  \
+    if (dev_ < 0) return -10;                                                                                 \
+    if (!attr[dev_]) {                                                                                        \
       if (cudaFuncSetAttribute(paged_prefill_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                                prefill_smem_bytes<DD>()) != cudaSuccess) return -10;                          \
-      attr = true;                                                                                            \
+      attr[dev_] = true;                                                                                      \
     }                                                                                                         \
     paged_prefill_kernel<DD><<<grid, PF_WARPS * 32, prefill_smem_bytes<DD>(), stream>>>(                       \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,  \
@@ -744,7 +759,7 @@ extern "C" int rb_paged_prefill(const void* q, const void* k_cache, const void* 
 static __device__ __align__(256) float rb_decode_noalloc_scratch[RB_DECODE_NOALLOC_MAX_FLOATS];
 
 namespace {
-constexpr int kMaxDevices = 64;
+constexpr int kMaxDevices = RB_MAX_DEVICES;
 float* g_noalloc_ptr[kMaxDevices] = {};
 std::mutex g_noalloc_mutex;
 
@@ -765,7 +780,8 @@ int noalloc_scratch_for_current_device(float** out) {
 }  // namespace
 
 extern "C" long long rb_paged_decode_noalloc_required_floats(int B, int Hq, int D, int num_splits) {
-  if (B <= 0 || Hq <= 0 || D <= 0 || num_splits <= 0) return 0;
+  // one split writes the output directly: nothing of the array is touched, whatever the batch
+  if (B <= 0 || Hq <= 0 || D <= 0 || num_splits <= 1) return 0;
   return (long long)B * Hq * num_splits * (D + 2);
 }
 
@@ -778,8 +794,10 @@ extern "C" int rb_paged_decode_noalloc(const void* q, const void* k_cache, const
   if (rb_paged_decode_noalloc_required_floats(B, Hq, D, num_splits) > (long long)RB_DECODE_NOALLOC_MAX_FLOATS)
     return RB_NOALLOC_TOO_LARGE;
   float* scratch = nullptr;
-  const int rc = noalloc_scratch_for_current_device(&scratch);
-  if (rc != 0) return rc;
+  if (num_splits > 1) {   // a single split needs no workspace, so no lookup either
+    const int rc = noalloc_scratch_for_current_device(&scratch);
+    if (rc != 0) return rc;
+  }
   // Same kernels and launch logic as the regular entry point, with the library's own workspace.
   return rb_paged_decode(q, k_cache, v_cache, block_tables, seq_lens, out, scratch, B, Hq, Hkv, D, max_blocks,
                          num_blocks, block_size, num_splits, scale, status, stream);

@@ -33,7 +33,7 @@ struct PeerPtrs { void* p[RB_MAX_RANKS]; };
 // The epoch lives in device memory (counter) so that a barrier captured in a CUDA graph uses a
 // fresh epoch on every replay: epoch = *counter + 1, stored back once every peer arrived.
 __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch, int* counter,
-                                    int* status) {
+                                    int* status, unsigned long long budget_ns) {
   __shared__ int ep;
   if (threadIdx.x == 0) ep = counter != nullptr ? *counter + 1 : epoch;
   __syncthreads();
@@ -41,7 +41,7 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slo
   const int r = threadIdx.x;
   if (r < world) {
     st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, ep);
-    wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, ep, status);
+    wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, ep, status, budget_ns);
   }
   __syncthreads();
   if (threadIdx.x == 0 && counter != nullptr) *counter = ep;
@@ -51,9 +51,10 @@ __global__ void symm_signal_kernel(PeerPtrs flags, int rank, int world, int slot
   const int r = threadIdx.x;
   if (r < world) st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, epoch);
 }
-__global__ void symm_wait_kernel(const int* my_flags, int world, int slot, int epoch, int* status) {
+__global__ void symm_wait_kernel(const int* my_flags, int world, int slot, int epoch, int* status,
+                                 unsigned long long budget_ns) {
   const int r = threadIdx.x;
-  if (r < world) wait_flag_ge(my_flags + slot * world + r, epoch, status);
+  if (r < world) wait_flag_ge(my_flags + slot * world + r, epoch, status, budget_ns);
 }
 
 __device__ __forceinline__ uint4 ld_peer_16(const void* p) {
@@ -71,45 +72,75 @@ __device__ __forceinline__ void st_peer_16(void* p, uint4 v) {
 
 // ---- reduce-scatter of a bf16 gradient bucket into this rank's fp32 shard -----------------
 // grads.p[r] : rank r's full bucket [n_total] bf16; this rank reduces [rank*n_shard, +n_shard)
-// ready flags (slot) must be >= epoch for every peer before its bucket is read.
+// ready flags (slot) must be >= epoch for every peer before its bucket is read (my_flags == nullptr: the caller
+// has already waited, e.g. with symm_wait on the same stream). shard_f32 == nullptr: only the sum of squares is
+// wanted (one rank, whose AdamW reads the bf16 gradients directly). The peers' loads of one vector are all in
+// flight before the first add, two vectors per thread per trip.
 __global__ void rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, int epoch, int rank, int world,
                                  long long n_shard, float scale, float* __restrict__ shard_f32, int accumulate,
-                                 float* __restrict__ sumsq_partial, int* status) {
+                                 float* __restrict__ sumsq_partial, int* status, unsigned long long budget_ns) {
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
   if (my_flags != nullptr && threadIdx.x < world) {
-    if (!wait_flag_ge(my_flags + slot * world + threadIdx.x, epoch, status)) failed = 1;
+    if (!wait_flag_ge(my_flags + slot * world + threadIdx.x, epoch, status, budget_ns)) failed = 1;
   }
   __syncthreads();
   float acc_sq = 0.f;
   if (!failed) {
     const long long nvec = n_shard >> 3;
     const long long base = (long long)rank * n_shard;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
-         i += (long long)gridDim.x * blockDim.x) {
-      float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int rr = 0; rr < world; ++rr) {
-        const int src = (rank + rr) % world;  // stagger the peers so links are used evenly
-        const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + base + i * 8;
-        const uint4 v = ld_peer_16(g);
-        float2 f;
-        f = unpack_bf16x2(v.x); s[0] += f.x; s[1] += f.y;
-        f = unpack_bf16x2(v.y); s[2] += f.x; s[3] += f.y;
-        f = unpack_bf16x2(v.z); s[4] += f.x; s[5] += f.y;
-        f = unpack_bf16x2(v.w); s[6] += f.x; s[7] += f.y;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    constexpr int UNR = 4;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * UNR) {
+      uint4 part[UNR][RB_MAX_RANKS];
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) {
+#pragma unroll
+          for (int rr = 0; rr < RB_MAX_RANKS; ++rr) {
+            if (rr < world) {
+              int src = rank + rr;  // stagger the peers so links are used evenly
+              if (src >= world) src -= world;
+              const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + base + i * 8;
+              // this rank's own bucket was written by kernels earlier on this GPU: an ordinary (cacheable, streaming)
+              // load; a peer's bucket is read at system scope
+              part[u][rr] = rr == 0 ? __ldcs(reinterpret_cast<const uint4*>(g)) : ld_peer_16(g);
+            }
+          }
+        }
       }
-      float* o = shard_f32 + i * 8;
-      float4 a = make_float4(s[0] * scale, s[1] * scale, s[2] * scale, s[3] * scale);
-      float4 b = make_float4(s[4] * scale, s[5] * scale, s[6] * scale, s[7] * scale);
-      if (accumulate) {
-        const float4 pa = *reinterpret_cast<float4*>(o), pb = *reinterpret_cast<float4*>(o + 4);
-        a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
-        b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) break;
+        float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int rr = 0; rr < RB_MAX_RANKS; ++rr) {
+          if (rr < world) {
+            const uint4 v = part[u][rr];
+            float2 f;
+            f = unpack_bf16x2(v.x); s[0] += f.x; s[1] += f.y;
+            f = unpack_bf16x2(v.y); s[2] += f.x; s[3] += f.y;
+            f = unpack_bf16x2(v.z); s[4] += f.x; s[5] += f.y;
+            f = unpack_bf16x2(v.w); s[6] += f.x; s[7] += f.y;
+          }
+        }
+        float4 a = make_float4(s[0] * scale, s[1] * scale, s[2] * scale, s[3] * scale);
+        float4 b = make_float4(s[4] * scale, s[5] * scale, s[6] * scale, s[7] * scale);
+        if (shard_f32 != nullptr) {
+          float* o = shard_f32 + i * 8;
+          if (accumulate) {
+            const float4 pa = *reinterpret_cast<float4*>(o), pb = *reinterpret_cast<float4*>(o + 4);
+            a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
+            b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+          }
+          *reinterpret_cast<float4*>(o) = a;
+          *reinterpret_cast<float4*>(o + 4) = b;
+        }
+        acc_sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
       }
-      *reinterpret_cast<float4*>(o) = a;
-      *reinterpret_cast<float4*>(o + 4) = b;
-      acc_sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
     }
   }
   // block reduce of the squares
@@ -127,9 +158,11 @@ __global__ void rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, 
 
 // ---- global grad norm -> clip coefficient, exchanged through peer memory ---------------------
 // partial: [n_partial] this rank's sums of squares. norm_slots.p[r]: rank r's float slots[world].
+// out_coef = pre_scale * min(1, max_norm / (pre_scale * norm + 1e-6)): what AdamW multiplies the stored gradients by.
 __global__ void clip_coef_kernel(const float* __restrict__ partial, int n_partial, PeerPtrs norm_slots, PeerPtrs flags,
-                                 int slot, int epoch, int rank, int world, float max_norm, float* __restrict__ out_coef,
-                                 float* __restrict__ out_norm, int* status) {
+                                 int slot, int epoch, int rank, int world, float max_norm, float pre_scale,
+                                 float* __restrict__ out_coef, float* __restrict__ out_norm, int* status,
+                                 unsigned long long budget_ns) {
   __shared__ float sm[32];
   float acc = 0.f;
   for (int i = threadIdx.x; i < n_partial; i += blockDim.x) acc += partial[i];
@@ -152,15 +185,17 @@ __global__ void clip_coef_kernel(const float* __restrict__ partial, int n_partia
   }
   __syncthreads();
   bool ok = true;
-  if (r < world) ok = wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, epoch, status);
+  if (r < world) ok = wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, epoch, status, budget_ns);
   __syncthreads();
   if (threadIdx.x == 0) {
     float total = 0.f;
     const volatile float* slots = reinterpret_cast<const volatile float*>(norm_slots.p[rank]);
     for (int i = 0; i < world; ++i) total += slots[i];
-    const float norm = sqrtf(total);
+    // pre_scale: the sums were taken over gradients that still carry a common factor (1 / accumulated passes);
+    // the norm is reported for the scaled gradients and the factor rides in the coefficient
+    const float norm = sqrtf(total) * pre_scale;
     *out_norm = norm;
-    *out_coef = (max_norm > 0.f) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+    *out_coef = pre_scale * ((max_norm > 0.f) ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f);
   }
   (void)ok;
 }
@@ -169,9 +204,11 @@ __global__ void clip_coef_kernel(const float* __restrict__ partial, int n_partia
 // params.p[r]: rank r's full bf16 parameter bucket [n_total]; this rank owns [rank*n_shard, +n_shard).
 // VEC: the four fp32 streams are read and written as float4 (needs 16-byte aligned base pointers); otherwise each
 // thread walks its eight elements with scalar accesses.
-template <bool VEC>
+// GBF16: `grad` is this rank's slice of the bf16 gradient bucket itself (one rank: nothing was reduced, so no fp32
+// copy of the gradients exists); the common scale rides in *clip_coef.
+template <bool VEC, bool GBF16>
 __global__ void adamw_allgather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
-                                       const float* __restrict__ grad, PeerPtrs params, int rank, int world,
+                                       const void* __restrict__ grad_any, PeerPtrs params, int rank, int world,
                                        long long n_shard, float lr, float beta1, float beta2, float eps,
                                        float weight_decay, float bc1, float bc2, const float* __restrict__ clip_coef) {
   const float clip = clip_coef != nullptr ? *clip_coef : 1.f;
@@ -181,13 +218,24 @@ __global__ void adamw_allgather_kernel(float* __restrict__ master, float* __rest
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     float g8[8], m8[8], v8[8], p8[8];
+    const float* grad = reinterpret_cast<const float*>(grad_any);
+    if constexpr (GBF16) {
+      const uint4 gv = *(reinterpret_cast<const uint4*>(grad_any) + i);
+      float2 f;
+      f = unpack_bf16x2(gv.x); g8[0] = f.x; g8[1] = f.y;
+      f = unpack_bf16x2(gv.y); g8[2] = f.x; g8[3] = f.y;
+      f = unpack_bf16x2(gv.z); g8[4] = f.x; g8[5] = f.y;
+      f = unpack_bf16x2(gv.w); g8[6] = f.x; g8[7] = f.y;
+    }
     if constexpr (VEC) {
       const float4* g4 = reinterpret_cast<const float4*>(grad) + 2 * i;
       const float4* m4 = reinterpret_cast<const float4*>(m) + 2 * i;
       const float4* v4 = reinterpret_cast<const float4*>(v) + 2 * i;
       const float4* p4 = reinterpret_cast<const float4*>(master) + 2 * i;
-      *reinterpret_cast<float4*>(g8) = g4[0];
-      *reinterpret_cast<float4*>(g8 + 4) = g4[1];
+      if constexpr (!GBF16) {
+        *reinterpret_cast<float4*>(g8) = g4[0];
+        *reinterpret_cast<float4*>(g8 + 4) = g4[1];
+      }
       *reinterpret_cast<float4*>(m8) = m4[0];
       *reinterpret_cast<float4*>(m8 + 4) = m4[1];
       *reinterpret_cast<float4*>(v8) = v4[0];
@@ -198,7 +246,7 @@ __global__ void adamw_allgather_kernel(float* __restrict__ master, float* __rest
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const long long k = i * 8 + j;
-        g8[j] = grad[k];
+        if constexpr (!GBF16) g8[j] = grad[k];
         m8[j] = m[k];
         v8[j] = v[k];
         p8[j] = master[k];
@@ -329,10 +377,16 @@ extern "C" int rb_pull_sum(void* const* src_ptrs, const void* residual, void* ou
   return RB_OK();
 }
 
+static unsigned long long g_wait_budget_ns = RB_WAIT_BUDGET_NS;
+// Budget of every cross-GPU flag wait launched through this library from now on (nanoseconds; 0 restores the
+// default). A wait that runs out records ST_TIMEOUT_PEER_FLAG in the status word and the kernel returns.
+extern "C" void rb_comm_set_wait_budget_ns(unsigned long long ns) { g_wait_budget_ns = ns ? ns : RB_WAIT_BUDGET_NS; }
+extern "C" unsigned long long rb_comm_get_wait_budget_ns() { return g_wait_budget_ns; }
+
 extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int slot, int epoch, int* counter,
                                int* status, cudaStream_t s) {
   if (world < 1 || world > RB_MAX_RANKS) return -1;
-  symm_barrier_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch, counter, status);
+  symm_barrier_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch, counter, status, g_wait_budget_ns);
   return RB_OK();
 }
 extern "C" int rb_symm_signal(void* const* flag_ptrs, int rank, int world, int slot, int epoch, cudaStream_t s) {
@@ -341,40 +395,80 @@ extern "C" int rb_symm_signal(void* const* flag_ptrs, int rank, int world, int s
   return RB_OK();
 }
 extern "C" int rb_symm_wait(const int* my_flags, int world, int slot, int epoch, int* status, cudaStream_t s) {
-  symm_wait_kernel<<<1, 32, 0, s>>>(my_flags, world, slot, epoch, status);
+  symm_wait_kernel<<<1, 32, 0, s>>>(my_flags, world, slot, epoch, status, g_wait_budget_ns);
+  return RB_OK();
+}
+// Same wait with its own budget (the failure branch of the bounded wait is tested with a millisecond).
+extern "C" int rb_symm_wait_budget(const int* my_flags, int world, int slot, int epoch, int* status,
+                                   unsigned long long budget_ns, cudaStream_t s) {
+  if (world < 1 || world > 32) return -1;
+  symm_wait_kernel<<<1, 32, 0, s>>>(my_flags, world, slot, epoch, status, budget_ns);
   return RB_OK();
 }
 extern "C" int rb_rs_num_partials() { return 148 * 4; }
+// grid_ctas: 0 = one CTA per partial slot (a launch that has the GPU to itself); a launch that shares the SMs with
+// the backward pass asks for fewer. my_flags may be null when the caller has waited already; shard_f32 may be null
+// when only the sum of squares is wanted.
+extern "C" int rb_rs_reduce_ex(void* const* grad_ptrs, const int* my_flags, int slot, int epoch, int rank, int world,
+                               long long n_shard, float scale, float* shard_f32, int accumulate, float* sumsq_partial,
+                               int* status, int grid_ctas, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
+  if (shard_f32 == nullptr && accumulate) return -1;
+  int grid = grid_ctas > 0 ? grid_ctas : rb_rs_num_partials();
+  if (grid > rb_rs_num_partials()) grid = rb_rs_num_partials();
+  rs_reduce_kernel<<<grid, 256, 0, s>>>(make_ptrs(grad_ptrs, world), my_flags, slot, epoch, rank, world, n_shard, scale,
+                                        shard_f32, accumulate, sumsq_partial, status, g_wait_budget_ns);
+  return RB_OK();
+}
 extern "C" int rb_rs_reduce(void* const* grad_ptrs, const int* my_flags, int slot, int epoch, int rank, int world,
                             long long n_shard, float scale, float* shard_f32, int accumulate, float* sumsq_partial,
                             int* status, cudaStream_t s) {
-  if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
-  rs_reduce_kernel<<<rb_rs_num_partials(), 256, 0, s>>>(make_ptrs(grad_ptrs, world), my_flags, slot, epoch, rank, world,
-                                                        n_shard, scale, shard_f32, accumulate, sumsq_partial, status);
+  return rb_rs_reduce_ex(grad_ptrs, my_flags, slot, epoch, rank, world, n_shard, scale, shard_f32, accumulate, sumsq_partial,
+                         status, 0, s);
+}
+extern "C" int rb_clip_coef_ex(const float* partial, int n_partial, void* const* norm_slot_ptrs, void* const* flag_ptrs,
+                               int slot, int epoch, int rank, int world, float max_norm, float pre_scale, float* out_coef,
+                               float* out_norm, int* status, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS) return -1;
+  clip_coef_kernel<<<1, 256, 0, s>>>(partial, n_partial, make_ptrs(norm_slot_ptrs, world), make_ptrs(flag_ptrs, world),
+                                     slot, epoch, rank, world, max_norm, pre_scale, out_coef, out_norm, status, g_wait_budget_ns);
   return RB_OK();
 }
 extern "C" int rb_clip_coef(const float* partial, int n_partial, void* const* norm_slot_ptrs, void* const* flag_ptrs,
                             int slot, int epoch, int rank, int world, float max_norm, float* out_coef, float* out_norm,
                             int* status, cudaStream_t s) {
-  if (world < 1 || world > RB_MAX_RANKS) return -1;
-  clip_coef_kernel<<<1, 256, 0, s>>>(partial, n_partial, make_ptrs(norm_slot_ptrs, world), make_ptrs(flag_ptrs, world),
-                                     slot, epoch, rank, world, max_norm, out_coef, out_norm, status);
+  return rb_clip_coef_ex(partial, n_partial, norm_slot_ptrs, flag_ptrs, slot, epoch, rank, world, max_norm, 1.f, out_coef,
+                         out_norm, status, s);
+}
+// grad_is_bf16: `grad` points at this rank's slice of the bf16 gradient bucket instead of an fp32 reduced copy.
+extern "C" int rb_adamw_allgather_ex(float* master, float* m, float* v, const void* grad, int grad_is_bf16,
+                                     void* const* param_ptrs, int rank, int world, long long n_shard, float lr, float beta1,
+                                     float beta2, float eps, float weight_decay, int step, const float* clip_coef,
+                                     cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
+  if (n_shard == 0) return 0;
+  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                         reinterpret_cast<uintptr_t>(grad)) & 15) == 0;
+  const PeerPtrs pp = make_ptrs(param_ptrs, world);
+  if (grad_is_bf16) {
+    if (!aligned) return -2;
+    adamw_allgather_kernel<true, true><<<148 * 8, 256, 0, s>>>(master, m, v, grad, pp, rank, world, n_shard, lr, beta1, beta2,
+                                                               eps, weight_decay, bc1, bc2, clip_coef);
+  } else if (aligned) {
+    adamw_allgather_kernel<true, false><<<148 * 8, 256, 0, s>>>(master, m, v, grad, pp, rank, world, n_shard, lr, beta1, beta2,
+                                                                eps, weight_decay, bc1, bc2, clip_coef);
+  } else {
+    adamw_allgather_kernel<false, false><<<148 * 4, 256, 0, s>>>(master, m, v, grad, pp, rank, world, n_shard, lr, beta1, beta2,
+                                                                 eps, weight_decay, bc1, bc2, clip_coef);
+  }
   return RB_OK();
 }
 extern "C" int rb_adamw_allgather(float* master, float* m, float* v, const float* grad, void* const* param_ptrs,
                                   int rank, int world, long long n_shard, float lr, float beta1, float beta2, float eps,
                                   float weight_decay, int step, const float* clip_coef, cudaStream_t s) {
-  if (world < 1 || world > RB_MAX_RANKS || n_shard % 8 != 0) return -1;
-  const float bc1 = 1.f - powf(beta1, (float)step), bc2 = 1.f - powf(beta2, (float)step);
-  const bool aligned = ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
-                         reinterpret_cast<uintptr_t>(grad)) & 15) == 0;
-  if (aligned)
-    adamw_allgather_kernel<true><<<148 * 8, 256, 0, s>>>(master, m, v, grad, make_ptrs(param_ptrs, world), rank, world, n_shard,
-                                                         lr, beta1, beta2, eps, weight_decay, bc1, bc2, clip_coef);
-  else
-    adamw_allgather_kernel<false><<<148 * 4, 256, 0, s>>>(master, m, v, grad, make_ptrs(param_ptrs, world), rank, world, n_shard,
-                                                          lr, beta1, beta2, eps, weight_decay, bc1, bc2, clip_coef);
-  return RB_OK();
+  return rb_adamw_allgather_ex(master, m, v, grad, 0, param_ptrs, rank, world, n_shard, lr, beta1, beta2, eps, weight_decay,
+                               step, clip_coef, s);
 }
 // segs: device array of Segment (layout mirrored by research_b200/parallel/weight_sync.py)
 extern "C" int rb_reshard_copy(const void* segs, int n_segs, long long total_vecs, cudaStream_t s) {

@@ -239,6 +239,89 @@ rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   for (int i = threadIdx.x; i < d; i += blockDim.x) dw_partial[(long long)blockIdx.x * d + i] = dw_acc[i];
 }
 
+// Wide rows (1024 < d <= 8192, d % 8 == 0): one CTA of 256 threads per row at a time. Thread t owns the 16-byte
+// vectors t, t + 256, ... of every row it sees, so x and dy are read once into registers, the two row sums
+// (sum x^2 and sum dy*w*x) share one block reduction, and the weight-gradient contribution of all rows of the CTA
+// accumulates in registers (the columns of a thread never change): no shared-memory atomics.
+template <int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_wide_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw_partial, long long rows, int d, float eps) {
+  __shared__ float red[2][8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nvec = d >> 3;
+  float wv[VPT][8], dwv[VPT][8];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int v = threadIdx.x + 256 * j;
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (v < nvec) q = *reinterpret_cast<const uint4*>(w + v * 8);
+    const uint32_t qi[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(qi[e]);
+      wv[j][2 * e] = f.x; wv[j][2 * e + 1] = f.y;
+      dwv[j][2 * e] = 0.f; dwv[j][2 * e + 1] = 0.f;
+    }
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    float xs[VPT][8], gs[VPT][8];
+    float ss = 0.f, gwx = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = threadIdx.x + 256 * j;
+      uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+      if (v < nvec) {
+        a = *reinterpret_cast<const uint4*>(x + row * d + v * 8);
+        b = *reinterpret_cast<const uint4*>(dy + row * d + v * 8);
+      }
+      const uint32_t ai[4] = {a.x, a.y, a.z, a.w}, bi[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = unpack_bf16x2(ai[e]), fb = unpack_bf16x2(bi[e]);
+        xs[j][2 * e] = fa.x; xs[j][2 * e + 1] = fa.y;
+        gs[j][2 * e] = fb.x; gs[j][2 * e + 1] = fb.y;
+        ss = fmaf(fa.x, fa.x, ss); ss = fmaf(fa.y, fa.y, ss);
+        gwx = fmaf(fb.x * wv[j][2 * e], fa.x, gwx); gwx = fmaf(fb.y * wv[j][2 * e + 1], fa.y, gwx);
+      }
+    }
+    ss = warp_sum(ss);
+    gwx = warp_sum(gwx);
+    __syncthreads();   // the previous row's sums have been read by every warp
+    if (lane == 0) { red[0][wid] = ss; red[1][wid] = gwx; }
+    __syncthreads();
+    float tss = 0.f, tg = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { tss += red[0][k]; tg += red[1][k]; }
+    const float rstd = rsqrtf(tss / (float)d + eps);
+    const float dot = tg * rstd / (float)d;     // mean over the row of (dy * w) * xhat
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = threadIdx.x + 256 * j;
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float xh0 = xs[j][2 * e] * rstd, xh1 = xs[j][2 * e + 1] * rstd;
+        const float g0 = gs[j][2 * e] * wv[j][2 * e], g1 = gs[j][2 * e + 1] * wv[j][2 * e + 1];
+        o[e] = pack_bf16x2(rstd * (g0 - xh0 * dot), rstd * (g1 - xh1 * dot));
+        dwv[j][2 * e] = fmaf(gs[j][2 * e], xh0, dwv[j][2 * e]);
+        dwv[j][2 * e + 1] = fmaf(gs[j][2 * e + 1], xh1, dwv[j][2 * e + 1]);
+      }
+      if (v < nvec) *reinterpret_cast<uint4*>(dx + row * d + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int v = threadIdx.x + 256 * j;
+    if (v < nvec) {
+      float* dst = dw_partial + (long long)blockIdx.x * d + v * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(dwv[j][0], dwv[j][1], dwv[j][2], dwv[j][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwv[j][4], dwv[j][5], dwv[j][6], dwv[j][7]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // RoPE on [T, H, D] (training: no cache). sign = +1 forward, -1 backward (inverse rotation).
 // fp32 math, one rounding at the end.
@@ -262,6 +345,39 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
     const float lo = __bfloat162float(xr[j]), hi = __bfloat162float(xr[j + half]);
     yr[j] = __float2bfloat16_rn(lo * cs.x - hi * s);
     yr[j + half] = __float2bfloat16_rn(hi * cs.x + lo * s);
+  }
+}
+
+// Same rotation with 16-byte accesses: one thread rotates eight (lo, hi) pairs of one head. Needs D / 2 to be a
+// multiple of 8 and 16-byte aligned rows (x, y, row strides, the table).
+__global__ void rope_vec8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                 const int* __restrict__ positions, const float2* __restrict__ cos_sin, long long T, int H,
+                                 int D, long long ldx, long long ldy, int max_pos, float sign) {
+  const int half = D >> 1, groups = half >> 3;
+  const long long n = T * H * groups;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % groups) * 8;
+    const long long th = i / groups;
+    const int h = (int)(th % H);
+    const long long t = th / H;
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (long long)pos * half + j);
+    const __nv_bfloat16* xr = x + t * ldx + (long long)h * D + j;
+    __nv_bfloat16* yr = y + t * ldy + (long long)h * D + j;
+    const uint4 lo4 = *reinterpret_cast<const uint4*>(xr), hi4 = *reinterpret_cast<const uint4*>(xr + half);
+    const uint32_t lo_w[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hi_w[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+    uint32_t olo[4], ohi[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float4 cs = cs4[e];   // (cos, sin) of two consecutive rotation pairs
+      const float2 lo = unpack_bf16x2(lo_w[e]), hi = unpack_bf16x2(hi_w[e]);
+      const float s0 = cs.y * sign, s1 = cs.w * sign;
+      olo[e] = pack_bf16x2(lo.x * cs.x - hi.x * s0, lo.y * cs.z - hi.y * s1);
+      ohi[e] = pack_bf16x2(hi.x * cs.x + lo.x * s0, hi.y * cs.z + lo.y * s1);
+    }
+    *reinterpret_cast<uint4*>(yr) = make_uint4(olo[0], olo[1], olo[2], olo[3]);
+    *reinterpret_cast<uint4*>(yr + half) = make_uint4(ohi[0], ohi[1], ohi[2], ohi[3]);
   }
 }
 
@@ -346,6 +462,14 @@ extern "C" int rb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void
   const bool vec = d % 8 == 0 && d <= 1024 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
                                                 reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   const size_t sm = d * sizeof(float);
+  const bool wide = d % 8 == 0 && d > 1024 && d <= 8192 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                    reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(dw_partial)) & 15) == 0;
+  if (wide) {
+    if (d <= 2048) rmsnorm_bwd_wide_kernel<1><<<grid, 256, 0, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
+    else if (d <= 4096) rmsnorm_bwd_wide_kernel<2><<<grid, 256, 0, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
+    else rmsnorm_bwd_wide_kernel<4><<<grid, 256, 0, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
+    return RB_OK();
+  }
   if (!vec) rmsnorm_bwd_kernel<<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
   else if (d <= 256) rmsnorm_bwd_vec_kernel<1><<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
   else if (d <= 512) rmsnorm_bwd_vec_kernel<2><<<grid, 256, sm, s>>>(xb, wb, gb, (__nv_bfloat16*)dx, dw_partial, rows, d, eps);
@@ -356,9 +480,16 @@ extern "C" int rb_rope(const void* x, void* y, const int* positions, const void*
                        long long ldx, long long ldy, int max_pos, int backward, cudaStream_t s) {
   if (T <= 0) return 0;
   const long long n = T * H * (D / 2);
-  rope_kernel<<<grid_for(n, 256), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, positions,
-                                               (const float2*)cos_sin, T, H, D, ldx, ldy, max_pos,
-                                               backward ? -1.f : 1.f);
+  const bool vec = (D % 16 == 0) && ldx % 8 == 0 && ldy % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(cos_sin)) & 15) == 0;
+  if (vec)
+    rope_vec8_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, positions,
+                                                          (const float2*)cos_sin, T, H, D, ldx, ldy, max_pos,
+                                                          backward ? -1.f : 1.f);
+  else
+    rope_kernel<<<grid_for(n, 256), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, positions,
+                                                 (const float2*)cos_sin, T, H, D, ldx, ldy, max_pos,
+                                                 backward ? -1.f : 1.f);
   return RB_OK();
 }
 extern "C" int rb_sumsq_num_partials() { return 148 * 4; }

@@ -107,6 +107,18 @@ class EngineService:
             self.resume()
         return self.engine.get_weight_version()
 
+    def flush_cache(self) -> None:
+        """Drop the prefix cache once nothing is running."""
+        self.quiesce()
+        try:
+            self.engine.flush_cache()
+        finally:
+            self.resume()
+
+    def update_weights_from_path(self, path: str, loader=None) -> int:
+        """Load a checkpoint (safetensors directory or ``torch.save`` file) and swap it in."""
+        return self.update_weights((loader or default_weight_loader)(path))
+
     def shutdown(self) -> None:
         self._stop.set()
         self.thread.join(timeout=5)
@@ -128,25 +140,90 @@ class LockstepEngineService(EngineService):
         # never run into the group's timeout (which is what detects a dead rank 0)
         self.heartbeat_s = heartbeat_s
         self._last_exchange = time.monotonic()
+        self._control: list = []        # (operation, future) queued on rank 0
+        self._loader = None
         super().__init__(engine, idle_sleep)
 
-    def _exchange(self, batch, stop: bool):
-        payload = [(([t for t, _, _ in batch], [p for _, p, _ in batch]), stop)] if self.rank == 0 else [None]
+    def _exchange(self, batch, stop: bool, control=None):
+        """One broadcast from rank 0: the requests admitted since the last one, the stop flag and at most one
+        control operation (``("flush", None)``, ``("load", path)`` or ``("weights", state_dict)``) that every rank
+        applies at this point of the common step sequence."""
+        payload = [(([t for t, _, _ in batch], [p for _, p, _ in batch]), stop, control)] if self.rank == 0 else [None]
         self.dist.broadcast_object_list(payload, src=0, group=self.group)
         self._last_exchange = time.monotonic()
         return payload[0]
+
+    def _apply_control(self, control) -> None:
+        kind, arg = control
+        if kind == "flush":
+            self.engine.flush_cache()
+        elif kind == "load":
+            self.engine.update_weights((self._loader or default_weight_loader)(arg))
+            self.engine.flush_cache()
+        elif kind == "weights":
+            self.engine.update_weights(arg)
+            self.engine.flush_cache()
+        else:
+            raise ValueError(f"unknown control operation {kind!r}")
+
+    def _control_op(self, control, timeout: float = 600.0):
+        """Queue a control operation on rank 0 and wait until every rank has applied it (between two steps, with
+        nothing running)."""
+        assert self.rank == 0, "control operations enter through rank 0"
+        fut: Future = Future()
+        with self._lock:
+            self._control.append((control, fut))
+        return fut.result(timeout=timeout)
+
+    def flush_cache(self) -> None:
+        self._control_op(("flush", None))
+
+    def update_weights(self, state_dict: dict) -> int:
+        """Broadcasts the tensors themselves to the followers (pickled); for large models hand every rank a path with
+        ``update_weights_from_path`` instead."""
+        self._control_op(("weights", state_dict))
+        return self.engine.get_weight_version()
+
+    def update_weights_from_path(self, path: str, loader=None) -> int:
+        if loader is not None:
+            self._loader = loader
+        self._control_op(("load", path))
+        return self.engine.get_weight_version()
+
+    def _fail_all(self, e: Exception) -> None:
+        for fut in self._futures.values():
+            if not fut.done():
+                fut.set_exception(e)
+        self._futures.clear()
 
     def _run(self) -> None:
         if self.rank != 0:
             return                      # followers run the loop in the caller's thread (see follow)
         while True:
-            if self._paused.is_set():
+            stop = self._stop.is_set()
+            if self._paused.is_set() and not stop:
+                # paused (a caller holds the engine): keep the followers' broadcast alive
                 self._idle.set()
+                if time.monotonic() - self._last_exchange > self.heartbeat_s:
+                    self._exchange([], False)
                 time.sleep(self.idle_sleep)
                 continue
             with self._lock:
-                batch, self._pending = self._pending, []
-            stop = self._stop.is_set()
+                draining = bool(self._control)
+                if draining:
+                    batch = []          # admissions wait until the control operation has run
+                else:
+                    batch, self._pending = self._pending, []
+            if draining and not self.engine.has_pending() and not stop:
+                with self._lock:
+                    control, cfut = self._control.pop(0)
+                self._exchange([], False, control)
+                try:
+                    self._apply_control(control)
+                    cfut.set_result(True)
+                except Exception as e:  # noqa: BLE001 - reported to the caller of the control operation
+                    cfut.set_exception(e)
+                continue
             if not batch and not self.engine.has_pending() and not stop:
                 self._idle.set()
                 if time.monotonic() - self._last_exchange > self.heartbeat_s:
@@ -156,6 +233,11 @@ class LockstepEngineService(EngineService):
             self._idle.clear()
             self._exchange(batch, stop)
             if stop:
+                self._fail_all(RuntimeError("engine service stopped"))
+                with self._lock:
+                    for _, cfut in self._control:
+                        cfut.set_exception(RuntimeError("engine service stopped"))
+                    self._control.clear()
                 return
             for toks, params, fut in batch:
                 try:
@@ -163,26 +245,40 @@ class LockstepEngineService(EngineService):
                 except Exception as e:  # noqa: BLE001 - the followers fail the same way and skip it too
                     fut.set_exception(e)
             if self.engine.has_pending():
-                for sid, sample in self.engine._step_with_ids():
+                try:
+                    finished = self.engine._step_with_ids()
+                except Exception as e:  # noqa: BLE001 - a failed step fails every in-flight request
+                    self._fail_all(e)
+                    continue
+                for sid, sample in finished:
                     fut = self._futures.pop(sid, None)
                     if fut is not None and not fut.done():
                         fut.set_result(sample)
                 self.steps += 1
 
     def follow(self) -> None:
-        """Body of every rank other than 0: mirror rank 0's admissions and steps until it says stop."""
+        """Body of every rank other than 0: mirror rank 0's admissions, steps and control operations until it says stop."""
         assert self.rank != 0
         while True:
-            (toks, params), stop = self._exchange([], False)
+            (toks, params), stop, control = self._exchange([], False)
             if stop:
                 return
+            if control is not None:
+                try:
+                    self._apply_control(control)
+                except Exception:  # noqa: BLE001 - rank 0 fails the same way and reports it
+                    pass
+                continue
             for t, p in zip(toks, params):
                 try:
                     self.engine.add_request(t, p)
                 except Exception:  # noqa: BLE001 - rank 0 reports it to the caller
                     pass
             if self.engine.has_pending():
-                self.engine._step_with_ids()
+                try:
+                    self.engine._step_with_ids()
+                except Exception:  # noqa: BLE001 - rank 0 fails the same step and reports it
+                    continue
                 self.steps += 1
 
     def shutdown(self) -> None:
@@ -271,11 +367,7 @@ def create_app(service: EngineService, model_name: str = "native", tokenizer=Non
 
     @app.post("/flush_cache")
     async def flush():
-        service.quiesce()
-        try:
-            service.engine.flush_cache()
-        finally:
-            service.resume()
+        await asyncio.get_running_loop().run_in_executor(None, service.flush_cache)
         return {"success": True}
 
     @app.post("/update_weights_from_disk")
@@ -284,8 +376,7 @@ def create_app(service: EngineService, model_name: str = "native", tokenizer=Non
         if not path:
             raise HTTPException(400, "model_path is required")
         try:
-            sd = (weight_loader or default_weight_loader)(path)
-            version = await asyncio.get_running_loop().run_in_executor(None, service.update_weights, sd)
+            version = await asyncio.get_running_loop().run_in_executor(None, service.update_weights_from_path, path, weight_loader)
         except FileNotFoundError as e:
             raise HTTPException(404, str(e)) from e
         return {"success": True, "message": f"weights loaded from {path}", "weight_version": version}
@@ -302,7 +393,7 @@ def default_weight_loader(path: str) -> dict:
 
     if os.path.isdir(path):
         if any(f.endswith(".safetensors") for f in os.listdir(path)):
-            return load_safetensors_dir(path)
+            return load_safetensors_dir(path)[0]       # (weights, config): the engine keeps its own config
         path = os.path.join(path, "pytorch_model.bin")
     if not os.path.exists(path):
         raise FileNotFoundError(path)

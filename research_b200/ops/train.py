@@ -98,8 +98,10 @@ def rmsnorm_bwd(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, eps: float):
 
 
 # ---------------------------------------------------------------- RoPE (training, no cache)
-def rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, backward: bool = False) -> torch.Tensor:
-    """Rotate ``x [T, H, D]`` (last dim contiguous) by +angle (forward) or -angle (backward)."""
+def rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, backward: bool = False,
+         out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate ``x [T, H, D]`` (heads packed, any row stride) by +angle (forward) or -angle (backward); ``out`` may be
+    a ``[T, H, D]`` view with its own row stride (e.g. the q columns of a fused QKV gradient)."""
     T, H, D = x.shape
     if not x.is_cuda:
         cs = table[positions.long()]
@@ -107,9 +109,14 @@ def rope(x: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, backward
         if backward:
             s = -s
         lo, hi = x[..., : D // 2].float(), x[..., D // 2:].float()
-        return torch.cat([lo * c - hi * s, hi * c + lo * s], -1).to(x.dtype)
+        res = torch.cat([lo * c - hi * s, hi * c + lo * s], -1).to(x.dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     assert x.stride(2) == 1 and x.stride(1) == D and positions.dtype == torch.int32
-    y = torch.empty(T, H, D, dtype=x.dtype, device=x.device)
+    y = torch.empty(T, H, D, dtype=x.dtype, device=x.device) if out is None else out
+    assert y.shape == x.shape and y.stride(2) == 1 and y.stride(1) == D
     rc = _lib().rb_rope(ptr(x), ptr(y), ptr(positions), ptr(table), T, H, D, x.stride(0), y.stride(0), table.shape[0],
                         int(backward), stream_handle(x.device))
     check_rc(rc, "rb_rope")

@@ -78,6 +78,13 @@ class FlatBuckets:
         self.params_buf = comm.alloc((self.numel,), dtype, zero=True)
         self.grads_buf = comm.alloc((self.numel,), dtype, zero=True)
         self.params, self.grads = self.params_buf.local, self.grads_buf.local
+        # Gradient windows: the kernels write a gradient view either over what is there (its first write of a
+        # window) or on top of it (later micro-batches, tied weights), so the bucket is never zeroed as a whole.
+        self.track_writes = False
+        self._written: dict[int, int] = {}     # element offset -> end offset of views written in this window
+        self._chunk_specs: list[list[ParamSpec]] = [[] for _ in self.chunks]
+        for sp in self.specs.values():
+            self._chunk_specs[sp.chunk].append(sp)
 
     def param_view(self, name: str) -> torch.Tensor:
         s = self.specs[name]
@@ -86,6 +93,36 @@ class FlatBuckets:
     def grad_view(self, name: str) -> torch.Tensor:
         s = self.specs[name]
         return self.grads[s.offset:s.offset + s.numel].view(s.shape)
+
+    # ---------------------------------------------------------------- gradient windows
+    def begin_window(self) -> None:
+        """Forget which gradient views were written: the next write of each view overwrites."""
+        self._written.clear()
+
+    def accumulate_into(self, gview: torch.Tensor) -> bool:
+        """True when ``gview`` (a view of the gradient bucket) already holds this window's gradients, i.e. the
+        caller must add to it; False on its first write of the window, which must overwrite. Without write
+        tracking (CPU, or a caller that zeroes the bucket itself) every write accumulates."""
+        if not self.track_writes:
+            return True
+        off = (gview.data_ptr() - self.grads.data_ptr()) // self.grads.element_size()
+        end = off + gview.numel()
+        prev = self._written.get(off)
+        if prev is not None and prev >= end:
+            return True
+        self._written[off] = end
+        return False
+
+    def zero_unwritten(self, chunk: int) -> None:
+        """Zero the gradient views of ``chunk`` that nothing wrote in this window (unused parameters, experts
+        without tokens): what they hold is the previous step's gradient."""
+        if not self.track_writes:
+            return
+        spans = sorted(self._written.items())
+        for sp in self._chunk_specs[chunk]:
+            covered = any(a <= sp.offset and sp.offset + sp.numel <= b for a, b in spans)
+            if not covered:
+                self.grads[sp.offset:sp.offset + sp.numel].zero_()
 
     def shard_range(self, chunk: int) -> tuple[int, int]:
         """(element offset, length) of this rank's slice of ``chunk``."""
@@ -103,23 +140,28 @@ class ShardedAdamW:
         self.max_grad_norm = max_grad_norm
         self.step_count = 0
         dev = buckets.params.device
+        self.on_gpu = self.comm.on_gpu
+        # One rank on a GPU reduces nothing: AdamW reads the bf16 gradient bucket itself and no fp32 copy of the
+        # gradients exists (4 bytes per parameter that an 8B model on one 180 GB GPU cannot spare).
+        self.direct_grads = self.on_gpu and self.comm.world == 1
         self.master, self.exp_avg, self.exp_avg_sq, self.red = [], [], [], []
         for c in range(len(buckets.chunks)):
             off, n = buckets.shard_range(c)
             self.master.append(buckets.params[off:off + n].float().clone())
             self.exp_avg.append(torch.zeros(n, dtype=torch.float32, device=dev))
             self.exp_avg_sq.append(torch.zeros(n, dtype=torch.float32, device=dev))
-            self.red.append(torch.zeros(n, dtype=torch.float32, device=dev))
-        self.on_gpu = self.comm.on_gpu
+            self.red.append(None if self.direct_grads else torch.zeros(n, dtype=torch.float32, device=dev))
+        self.zero_grads_after_step = True
+        self.overlap_grid = 0          # CTAs of a reduce launch that shares the GPU with backward (0 = full grid)
         if self.on_gpu:
             self.n_partial = _lib().rb_rs_num_partials()
             self.partial = torch.zeros(self.n_partial, dtype=torch.float32, device=dev)
             self.coef = torch.ones(1, dtype=torch.float32, device=dev)
             self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
-            self.grad_slots = [self.comm.new_slot() for _ in buckets.chunks] if len(buckets.chunks) <= 40 else None
+            self.grad_slots = [self.comm.new_slot() for _ in buckets.chunks]    # one ready flag row per chunk
             self.norm_slot = self.comm.new_slot()
-            self._shared_slot = self.comm.new_slot()
         self._reduced: set[int] = set()
+        self._passes: dict[int, int] = {}     # reduce launches per chunk since the last step
         self._sumsq_cpu = 0.0
 
     def resync_master(self) -> None:
@@ -129,41 +171,70 @@ class ShardedAdamW:
             self.master[c].copy_(self.b.params[off:off + n].float())
 
     # ---------------------------------------------------------------- phase 1
-    def reduce_chunk(self, chunk: int, grad_scale: float = 1.0) -> None:
-        """Reduce-scatter one gradient chunk into this rank's fp32 slice (call once its backward is done)."""
+    def reduce_chunk(self, chunk: int, grad_scale: float = 1.0, accumulate: bool = False, overlapped: bool = False) -> None:
+        """Reduce-scatter one gradient chunk into this rank's fp32 slice (call once its backward is done).
+
+        ``accumulate`` adds to what earlier passes of the same step reduced (several ``forward_backward`` calls per
+        optimizer step); ``overlapped`` marks a launch that runs beside the backward pass on another stream: the wait
+        for the peers' flags is then a one-CTA kernel of its own and the reduction uses ``overlap_grid`` CTAs."""
         b, comm = self.b, self.comm
         off, length = b.chunks[chunk]
         n = length // comm.world
         scale = grad_scale / comm.world
+        b.zero_unwritten(chunk)
+        self._passes[chunk] = self._passes.get(chunk, 0) + 1
         if not self.on_gpu:
             g = b.grads[off:off + length].float()
             if comm.world > 1:
                 dist.all_reduce(g, group=comm.group)
             mine = g[comm.rank * n:(comm.rank + 1) * n] * scale
-            self.red[chunk].copy_(mine)
-            self._sumsq_cpu += float((mine * mine).sum())
+            if accumulate:
+                self.red[chunk].add_(mine)
+            else:
+                self.red[chunk].copy_(mine)
             self._reduced.add(chunk)
             return
-        slot = self.grad_slots[chunk] if self.grad_slots is not None else self._shared_slot
-        epoch = comm.signal(slot)  # my gradients for this chunk are final
+        dev = b.params.device
+        st = status_tensor(dev).data_ptr()
         ptrs = b.grads_buf.ptrs(off * 2)
-        rc = _lib().rb_rs_reduce(ptrs, comm.flags.local.data_ptr(), slot, epoch, comm.rank, comm.world, n, scale,
-                                 self.red[chunk].data_ptr(), 0, self.partial.data_ptr(),
-                                 status_tensor(b.params.device).data_ptr(), stream_handle(b.params.device))
-        check_rc(rc, "rb_rs_reduce")
+        if self.direct_grads:
+            # nothing to reduce: only this chunk's share of the gradient norm (the scale rides in the clip coefficient)
+            rc = _lib().rb_rs_reduce_ex(ptrs, None, 0, 0, 0, 1, n, 1.0, None, 0, self.partial.data_ptr(), st, 0,
+                                        stream_handle(dev))
+            check_rc(rc, "rb_rs_reduce_ex")
+            self._reduced.add(chunk)
+            return
+        slot = self.grad_slots[chunk]
+        epoch = comm.signal(slot)  # my gradients for this chunk are final
+        flags = comm.flags.local.data_ptr()
+        if overlapped:
+            comm.wait(slot, epoch)
+            flags = None
+        rc = _lib().rb_rs_reduce_ex(ptrs, flags, slot, epoch, comm.rank, comm.world, n, scale,
+                                    self.red[chunk].data_ptr(), int(accumulate), self.partial.data_ptr(), st,
+                                    self.overlap_grid if overlapped else 0, stream_handle(dev))
+        check_rc(rc, "rb_rs_reduce_ex")
         self._reduced.add(chunk)
 
     # ---------------------------------------------------------------- phases 2-4
     def step(self, grad_scale: float = 1.0) -> torch.Tensor:
-        """Finish the optimizer step; returns the global gradient norm (a device scalar on GPU)."""
+        """Finish the optimizer step; returns the global gradient norm (a device scalar on GPU).
+
+        ``grad_scale`` multiplies every gradient (1 / accumulated passes). Chunks that were reduced early carry the
+        unscaled sums, so on the GPU the factor is applied with the clip coefficient."""
         b, comm = self.b, self.comm
+        early = set(self._reduced)
         for c in range(len(b.chunks)):
             if c not in self._reduced:
-                self.reduce_chunk(c, grad_scale)
+                self.reduce_chunk(c, 1.0 if self.on_gpu else grad_scale)
         self.step_count += 1
         b1, b2 = self.betas
         if not self.on_gpu:
-            t = torch.tensor([self._sumsq_cpu], dtype=torch.float64)
+            if early and grad_scale != 1.0:
+                for c in early:
+                    self.red[c].mul_(grad_scale)
+            sq = sum(float((self.red[c] * self.red[c]).sum()) for c in range(len(b.chunks)))
+            t = torch.tensor([sq], dtype=torch.float64)
             if comm.world > 1:
                 dist.all_reduce(t, group=comm.group)
             norm = float(t.sqrt())
@@ -185,27 +256,37 @@ class ShardedAdamW:
                     b.params[off:off + length].copy_(p.to(b.dtype))
             b.grads.zero_()
             self._reduced.clear()
+            self._passes.clear()
             self._sumsq_cpu = 0.0
             return torch.tensor(norm)
         dev = b.params.device
         st = status_tensor(dev).data_ptr()
+        if not self.direct_grads and any(v > 1 for v in self._passes.values()):
+            # several reduce passes were summed into the fp32 slices: the partial sums of squares of the kernels
+            # cover intermediate values, so take the norm from the slices themselves (rare path, plain tensor ops)
+            self.partial.zero_()
+            self.partial[0] = torch.stack([(r * r).sum() for r in self.red]).sum()
         ep = comm.next_epoch(self.norm_slot)
-        rc = _lib().rb_clip_coef(self.partial.data_ptr(), self.n_partial, comm.norm_slots.ptrs(), comm.flags.ptrs(),
-                                 self.norm_slot, ep, comm.rank, comm.world, float(self.max_grad_norm),
-                                 self.coef.data_ptr(), self.norm.data_ptr(), st, stream_handle(dev))
-        check_rc(rc, "rb_clip_coef")
+        rc = _lib().rb_clip_coef_ex(self.partial.data_ptr(), self.n_partial, comm.norm_slots.ptrs(), comm.flags.ptrs(),
+                                    self.norm_slot, ep, comm.rank, comm.world, float(self.max_grad_norm), float(grad_scale),
+                                    self.coef.data_ptr(), self.norm.data_ptr(), st, stream_handle(dev))
+        check_rc(rc, "rb_clip_coef_ex")
         for c in range(len(b.chunks)):
             off, length = b.chunks[c]
             n = length // comm.world
-            rc = _lib().rb_adamw_allgather(
+            grad_ptr = b.grads.data_ptr() + off * 2 if self.direct_grads else self.red[c].data_ptr()
+            rc = _lib().rb_adamw_allgather_ex(
                 self.master[c].data_ptr(), self.exp_avg[c].data_ptr(), self.exp_avg_sq[c].data_ptr(),
-                self.red[c].data_ptr(), b.params_buf.ptrs(off * 2), comm.rank, comm.world, n, self.lr, b1, b2, self.eps,
-                self.weight_decay, self.step_count, self.coef.data_ptr(), stream_handle(dev))
-            check_rc(rc, "rb_adamw_allgather")
+                grad_ptr, int(self.direct_grads), b.params_buf.ptrs(off * 2), comm.rank, comm.world, n, self.lr, b1, b2,
+                self.eps, self.weight_decay, self.step_count, self.coef.data_ptr(), stream_handle(dev))
+            check_rc(rc, "rb_adamw_allgather_ex")
         comm.barrier()  # every rank's pushes landed; peers are done reading my gradients
-        b.grads.zero_()
+        if self.zero_grads_after_step:
+            b.grads.zero_()
+        b.begin_window()
         self.partial.zero_()
         self._reduced.clear()
+        self._passes.clear()
         return self.norm
 
     # ---------------------------------------------------------------- state

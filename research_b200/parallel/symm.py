@@ -40,10 +40,18 @@ def _lib():
         lib.rb_adamw_allgather.argtypes = [_VP, _VP, _VP, _VP, PP, _I, _I, _LL, _F, _F, _F, _F, _F, _I, _VP, _VP]
         lib.rb_reshard_copy.argtypes = [_VP, _I, _LL, _VP]
         lib.rb_pull_sum.argtypes = [PP, _VP, _VP, _LL, _I, _VP]
+        lib.rb_symm_wait_budget.argtypes = [_VP, _I, _I, _I, _VP, ctypes.c_ulonglong, _VP]
+        lib.rb_rs_reduce_ex.argtypes = [PP, _VP, _I, _I, _I, _I, _LL, _F, _VP, _I, _VP, _VP, _I, _VP]
+        lib.rb_clip_coef_ex.argtypes = [_VP, _I, PP, PP, _I, _I, _I, _I, _F, _F, _VP, _VP, _VP, _VP]
+        lib.rb_adamw_allgather_ex.argtypes = [_VP, _VP, _VP, _VP, _I, PP, _I, _I, _LL, _F, _F, _F, _F, _F, _I, _VP, _VP]
+        lib.rb_comm_set_wait_budget_ns.argtypes = [ctypes.c_ulonglong]
+        lib.rb_comm_set_wait_budget_ns.restype = None
+        lib.rb_comm_get_wait_budget_ns.restype = ctypes.c_ulonglong
         lib.rb_pull_sum.restype = _I
         lib.rb_rs_num_partials.restype = _I
         for f in ("rb_symm_barrier", "rb_symm_signal", "rb_symm_wait", "rb_rs_reduce", "rb_clip_coef",
-                  "rb_adamw_allgather", "rb_reshard_copy"):
+                  "rb_adamw_allgather", "rb_reshard_copy", "rb_symm_wait_budget", "rb_rs_reduce_ex", "rb_clip_coef_ex",
+                  "rb_adamw_allgather_ex"):
             getattr(lib, f).restype = _I
         lib._rb_typed = True
     return lib
@@ -76,7 +84,7 @@ class SymmBuffer:
 class PeerComm:
     """Peer-memory context of one process group (one rank per GPU, single node)."""
 
-    NUM_SLOTS = 64
+    NUM_SLOTS = 512     # one ready-flag row per gradient chunk (a layer) plus barriers and the norm exchange
 
     def __init__(self, group: dist.ProcessGroup | None = None, device: torch.device | None = None):
         self.group = group if group is not None else dist.group.WORLD

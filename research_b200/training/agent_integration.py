@@ -40,7 +40,7 @@ def _extract_tokens_from_trajectory(traj: Trajectory) -> tuple[list[int], list[f
         if len(prompt) >= len(tokens) and prompt[:len(tokens)] == tokens:
             new = prompt[len(tokens):]
         else:  # the engine saw a different prefix (e.g. truncated history): restart from its prompt
-            tokens, mask, new = [], [], prompt
+            tokens, mask, lps, new = [], [], [], prompt   # the discarded turns' log-probs go with their tokens
         tokens += new
         mask += [0.0] * len(new)
         tokens += list(ch.token_ids)
@@ -123,7 +123,16 @@ async def generate_rollout_batch(prompts: list[Any], endpoint: Endpoint, environ
             return await agent_rollout_to_sample(p, endpoint, environment_factory, run_config, max_turns, **kw)
 
     groups = await asyncio.gather(*[one(p) for p in prompts])
-    return [s for g in groups for s in g[:1]]
+    if kw.get("strategy", "interleaved") != "branching":
+        return [s for g in groups for s in g[:1]]
+    # branching: one sample per assistant turn, all trained on; each remembers which prompt it came from so that the
+    # rollout manager gives the whole branch set its prompt's group
+    out = []
+    for i, g in enumerate(groups):
+        for s in g:
+            s.metadata["source_prompt"] = i
+            out.append(s)
+    return out
 
 
 def make_agent_generate_fn(engine, environment_cls, config, tokenizer):

@@ -21,7 +21,10 @@ from .native import NativeTrainingBackend
 class FSDPConfig:
     """Knobs kept from the reference; the ones it declares but never applies are honoured or rejected here."""
 
-    sharding_strategy: str = "shard_optimizer_and_grads"   # parameters stay replicated in bf16
+    # "shard_optimizer_and_grads": bf16 parameters replicated, gradients / fp32 master / moments sharded;
+    # "full_shard": the decoder layers' weight matrices are sharded too and gathered from the peers inside the
+    # consuming GEMM launch (the reference's FULL_SHARD, rollouts/training/backends/fsdp.py:47-58)
+    sharding_strategy: str = "shard_optimizer_and_grads"
     mixed_precision: bool = True                           # bf16 params/grads, fp32 master + moments
     cpu_offload: bool = False
     gradient_checkpointing: bool = False
@@ -29,6 +32,9 @@ class FSDPConfig:
 
     def __post_init__(self) -> None:
         assert not self.cpu_offload, "cpu_offload is not supported: 180 GB of HBM per GPU holds the state"
+        alias = {"FULL_SHARD": "full_shard", "SHARD_GRAD_OP": "shard_optimizer_and_grads"}
+        object.__setattr__(self, "sharding_strategy", alias.get(self.sharding_strategy, self.sharding_strategy))
+        assert self.sharding_strategy in ("shard_optimizer_and_grads", "full_shard"), self.sharding_strategy
 
 
 class FSDPTrainingBackend(NativeTrainingBackend):

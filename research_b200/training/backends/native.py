@@ -39,6 +39,20 @@ def _chunk_of(name: str) -> int:
     return 0 if name.startswith("model.embed") else 10_000
 
 
+# Order of a layer's parameters inside its chunk: projections that share their input lie back to back (q|k|v,
+# gate|up, and their biases), so each group runs as one stacked GEMM in forward, dgrad and wgrad.
+_GROUPED = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+            "self_attn.q_proj.bias", "self_attn.k_proj.bias", "self_attn.v_proj.bias",
+            "mlp.gate_proj.weight", "mlp.up_proj.weight")
+
+
+def _order_key(name: str) -> tuple:
+    for i, suffix in enumerate(_GROUPED):
+        if name.endswith(suffix):
+            return (_chunk_of(name), name[:-len(suffix)], i, name)
+    return (_chunk_of(name), name, len(_GROUPED), name)
+
+
 class NativeTrainingBackend:
     def __init__(self, model_config: ModelConfig, weights: dict[str, torch.Tensor] | None = None, *,
                  comm: PeerComm | None = None, device: torch.device | str | None = None,
@@ -46,7 +60,7 @@ class NativeTrainingBackend:
                  betas: tuple[float, float] = (0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
                  trainer_config: TrainerConfig | None = None, lr_schedule: Callable[[int], float] | None = None,
                  checkpoint_dir: str | Path | None = None, activation_checkpointing: bool = False,
-                 need_entropy: bool | None = None, seed: int = 0):
+                 need_entropy: bool | None = None, seed: int = 0, overlap_comm: bool = True):
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda" if torch.cuda.is_available() else "cpu")
         self.comm = comm if comm is not None else LocalComm(self.device)
@@ -55,7 +69,7 @@ class NativeTrainingBackend:
         self.config = trainer_config or TrainerConfig()
         on_gpu = self.device.type == "cuda"
         dtype = torch.bfloat16 if on_gpu else torch.float32
-        shapes = sorted(param_shapes(model_config).items(), key=lambda kv: (_chunk_of(kv[0]), kv[0]))
+        shapes = sorted(param_shapes(model_config).items(), key=lambda kv: _order_key(kv[0]))
         self.buckets = FlatBuckets(self.comm, shapes, _chunk_of, dtype=dtype)
         if weights is None and on_gpu:
             # random init written straight into the bucket (an 8B model never exists twice in memory)
@@ -81,6 +95,17 @@ class NativeTrainingBackend:
                                       max_grad_norm=max_norm)
         self.base_lr = lr
         self.lr_schedule = lr_schedule
+        # On the GPU the kernels write each gradient view in place of the old one on its first write of a window, so
+        # the 2 bytes per parameter of the bucket are neither zeroed nor re-read per step.
+        self.buckets.track_writes = on_gpu
+        self.optimizer.zero_grads_after_step = not on_gpu
+        # Reduce-scatter of a layer's gradients as soon as backward has left the layer, on a second stream
+        # (what FSDP2's backward hooks do in the reference, rollouts/training/backends/fsdp.py:289-322).
+        self.overlap_comm = bool(overlap_comm) and on_gpu and self.world > 1
+        self._side = torch.cuda.Stream(self.device) if self.overlap_comm else None
+        self._pass_reduced: set[int] = set()
+        if self.overlap_comm:
+            self.optimizer.overlap_grid = 64
         self.model = NativeCausalLM(model_config, self.buckets, self.device, activation_checkpointing)
         self.loss_name = loss_fn if isinstance(loss_fn, str) else getattr(loss_fn, "__name__", "custom")
         self.loss_fn = LOGPROB_LOSSES[loss_fn] if isinstance(loss_fn, str) else loss_fn
@@ -124,6 +149,17 @@ class NativeTrainingBackend:
             self._poisoned = True
             raise
 
+    def _chunk_grads_final(self, chunk: int) -> None:
+        """Autograd hook of the last micro-batch: backward has finished ``chunk``; reduce it beside the rest of backward."""
+        if chunk in self._pass_reduced:
+            return
+        self._pass_reduced.add(chunk)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._side.wait_event(ev)
+        with torch.cuda.stream(self._side):
+            self.optimizer.reduce_chunk(chunk, 1.0, accumulate=self._accum > 0, overlapped=True)
+
     def _forward_backward(self, batch: dict[str, Any]) -> dict[str, float]:
         b = self._to_device(batch)
         ids = b["input_ids"]
@@ -140,8 +176,13 @@ class NativeTrainingBackend:
         mb = B // n_micro
         agg: dict[str, float] = {}
         t0 = time.perf_counter()
+        if self.overlap_comm:
+            # every pass reduces its own gradients (summed into the fp32 slices), so each pass is a window of its own
+            self.buckets.begin_window()
+            self._pass_reduced.clear()
         for i in range(n_micro):
             sl = slice(i * mb, (i + 1) * mb)
+            self.model.on_chunk_grads_final = self._chunk_grads_final if (self.overlap_comm and i == n_micro - 1) else None
             lp, ent = self.model.logprobs(ids[sl], targets[sl], self.need_entropy)
             sub = {k: (v[sl] if v.dim() > 0 and v.shape[0] == B else v) for k, v in b.items()}
             sub["shift_mask"] = shift_mask[sl]
@@ -154,13 +195,28 @@ class NativeTrainingBackend:
             for k, v in metrics.items():
                 agg[k] = agg.get(k, 0.0) + float(v) / n_micro
             agg["loss"] = agg.get("loss", 0.0) + (float(loss.detach()) / n_micro if "loss" not in metrics else 0.0)
+        self.model.on_chunk_grads_final = None
+        if self.overlap_comm:
+            # what no hook covered (the embedding, reached last), then the main stream joins the reductions
+            ev = torch.cuda.Event()
+            ev.record()
+            self._side.wait_event(ev)
+            with torch.cuda.stream(self._side):
+                for c in range(len(self.buckets.chunks)):
+                    if c not in self._pass_reduced:
+                        self._pass_reduced.add(c)
+                        self.optimizer.reduce_chunk(c, 1.0, accumulate=self._accum > 0, overlapped=True)
+                done = torch.cuda.Event()
+                done.record()
+            torch.cuda.current_stream(self.device).wait_event(done)
         self._accum += 1
-        agg["grad_norm_local"] = float(T.sumsq(self.buckets.grads).sqrt())
         agg["fwd_bwd_s"] = time.perf_counter() - t0
         agg["num_tokens"] = float(shift_mask.sum())
         return agg
 
-    def optim_step(self) -> TrainFuture[dict[str, float]]:
+    def optim_step(self, read_back: bool = True) -> TrainFuture[dict[str, float]]:
+        """Clip, AdamW and parameter all-gather. ``read_back=False`` leaves the gradient norm on the device (no
+        device-to-host read, so the host runs on into the next step's launches)."""
         assert not self._poisoned, "backend is poisoned by an earlier failure; rebuild it"
         try:
             if self.lr_schedule is not None:
@@ -169,8 +225,10 @@ class NativeTrainingBackend:
             self._accum = 0
             self.current_step += 1
             self.weight_version += 1
-            return ImmediateTrainFuture({"lr": self.optimizer.lr, "step": self.current_step, "grad_norm": float(norm)},
-                                        "optim_step")
+            out = {"lr": self.optimizer.lr, "step": self.current_step}
+            if read_back:
+                out["grad_norm"] = float(norm)
+            return ImmediateTrainFuture(out, "optim_step")
         except Exception:
             self._poisoned = True
             raise

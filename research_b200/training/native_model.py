@@ -42,38 +42,50 @@ def _rows_ok(t: torch.Tensor) -> torch.Tensor:
 
 
 class _Linear(torch.autograd.Function):
-    """``y = x W^T (+ bias) (+ residual)``; the residual add rides in the GEMM epilogue and its gradient is ``dy``."""
+    """``y = x W^T (+ bias) (+ residual)``; the residual add rides in the GEMM epilogue and its gradient is ``dy``.
+
+    ``sink`` is the gradient bucket: it knows whether a gradient view already holds this window's gradient (the
+    wgrad GEMM then adds to it through its residual input) or is written for the first time (plain store, so the
+    bucket is never zeroed or re-read as a whole)."""
 
     @staticmethod
-    def forward(ctx, x, w, gw, bias, gb, residual=None):
+    def forward(ctx, x, w, gw, bias, gb, residual, sink):
         ctx.save_for_backward(x, w)
-        ctx.gw, ctx.gb, ctx.has_res = gw, gb, residual is not None
+        ctx.gw, ctx.gb, ctx.has_res, ctx.sink = gw, gb, residual is not None, sink
         return ops.gemm(x, w, bias=bias, residual=residual)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = _rows_ok(dy)
-        dx = ops.gemm(dy, w, b_mn_major=True)                      # [M,N] x [N,K] -> [M,K]
-        ops.gemm(dy, x, residual=ctx.gw, out=ctx.gw, a_mn_major=True, b_mn_major=True)  # gw += dY^T X
+        dx = ops.gemm(dy, w, b_mn_major=True) if ctx.needs_input_grad[0] else None   # [M,N] x [N,K] -> [M,K]
+        acc = ctx.sink.accumulate_into(ctx.gw)
+        ops.gemm(dy, x, residual=ctx.gw if acc else None, out=ctx.gw, a_mn_major=True, b_mn_major=True)  # gw (+)= dY^T X
         if ctx.gb is not None:
-            ctx.gb.add_(dy.float().sum(0).to(ctx.gb.dtype))
-        return dx, None, None, None, None, (dy if ctx.has_res else None)
+            db = dy.float().sum(0).to(ctx.gb.dtype)
+            if ctx.sink.accumulate_into(ctx.gb):
+                ctx.gb.add_(db)
+            else:
+                ctx.gb.copy_(db)
+        return dx, None, None, None, None, (dy if ctx.has_res else None), None
 
 
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, gw, eps):
+    def forward(ctx, x, w, gw, eps, sink):
         ctx.save_for_backward(x, w)
-        ctx.gw, ctx.eps = gw, eps
+        ctx.gw, ctx.eps, ctx.sink = gw, eps, sink
         return ops.rmsnorm(x, w, eps)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dx, dw = T.rmsnorm_bwd(x, w, dy.contiguous(), ctx.eps)
-        ctx.gw.add_(dw.to(ctx.gw.dtype))
-        return dx, None, None, None
+        if ctx.sink.accumulate_into(ctx.gw):
+            ctx.gw.add_(dw.to(ctx.gw.dtype))
+        else:
+            ctx.gw.copy_(dw)
+        return dx, None, None, None, None
 
 
 class _RoPE(torch.autograd.Function):
@@ -86,6 +98,33 @@ class _RoPE(torch.autograd.Function):
     def backward(ctx, dy):
         positions, table = ctx.saved_tensors
         return T.rope(dy.contiguous(), positions, table, backward=True), None, None
+
+
+class _SplitQKVRope(torch.autograd.Function):
+    """One fused ``[T, (H + 2 Hkv) D]`` projection -> rotated ``q [T,H,D]``, rotated ``k [T,Hkv,D]`` and ``v`` (a view of
+    the input). The rotation kernel reads the strided slices in place; backward rotates ``dq`` / ``dk`` back straight
+    into the matching columns of one ``d_qkv`` buffer, so the split costs no copy in either direction."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, table, H, Hkv, D):
+        ctx.save_for_backward(positions, table)
+        ctx.dims = (H, Hkv, D)
+        Tn = qkv.shape[0]
+        q = T.rope(qkv[:, :H * D].view(Tn, H, D), positions, table, backward=False)
+        k = T.rope(qkv[:, H * D:(H + Hkv) * D].view(Tn, Hkv, D), positions, table, backward=False)
+        v = qkv[:, (H + Hkv) * D:].view(Tn, Hkv, D)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        positions, table = ctx.saved_tensors
+        H, Hkv, D = ctx.dims
+        Tn = dq.shape[0]
+        d_qkv = torch.empty(Tn, (H + 2 * Hkv) * D, dtype=dq.dtype, device=dq.device)
+        T.rope(dq.contiguous(), positions, table, backward=True, out=d_qkv[:, :H * D].view(Tn, H, D))
+        T.rope(dk.contiguous(), positions, table, backward=True, out=d_qkv[:, H * D:(H + Hkv) * D].view(Tn, Hkv, D))
+        d_qkv[:, (H + Hkv) * D:].view(Tn, Hkv, D).copy_(dv)
+        return d_qkv, None, None, None, None, None
 
 
 class _SwiGLU(torch.autograd.Function):
@@ -102,16 +141,18 @@ class _SwiGLU(torch.autograd.Function):
 
 class _Embedding(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ids, table, gtable):
+    def forward(ctx, ids, table, gtable, sink):
         ctx.save_for_backward(ids)
-        ctx.gtable = gtable
+        ctx.gtable, ctx.sink = gtable, sink
         return ops.embedding(ids, table)
 
     @staticmethod
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
+        if not ctx.sink.accumulate_into(ctx.gtable):
+            ctx.gtable.zero_()          # rows no token selected carry no gradient
         ctx.gtable.index_add_(0, ids.long(), dy.to(ctx.gtable.dtype))
-        return None, None, None
+        return None, None, None, None
 
 
 class _FusedLogprob(torch.autograd.Function):
@@ -120,7 +161,7 @@ class _FusedLogprob(torch.autograd.Function):
     CHUNK = 2048
 
     @staticmethod
-    def forward(ctx, h, w, gw, targets, need_entropy):
+    def forward(ctx, h, w, gw, targets, need_entropy, sink):
         N = h.shape[0]
         lp = torch.empty(N, dtype=torch.float32, device=h.device)
         lse = torch.empty_like(lp)
@@ -133,7 +174,7 @@ class _FusedLogprob(torch.autograd.Function):
             if need_entropy:
                 ent[s:e] = c
         ctx.save_for_backward(h, w, targets, lse, ent if need_entropy else lse)
-        ctx.gw, ctx.need_entropy = gw, need_entropy
+        ctx.gw, ctx.need_entropy, ctx.sink = gw, need_entropy, sink
         ctx.mark_non_differentiable(lse)
         return lp, (ent if need_entropy else lse.new_zeros(N)), lse
 
@@ -151,8 +192,9 @@ class _FusedLogprob(torch.autograd.Function):
                                        g_lp[s:e], g_ent[s:e] if g_ent is not None else None)
             dl = dl.to(h.dtype) if dl.dtype != h.dtype else dl
             ops.gemm(dl, w, out=dh[s:e], b_mn_major=True)
-            ops.gemm(dl, h[s:e], residual=ctx.gw, out=ctx.gw, a_mn_major=True, b_mn_major=True)
-        return dh, None, None, None, None
+            acc = ctx.sink.accumulate_into(ctx.gw)
+            ops.gemm(dl, h[s:e], residual=ctx.gw if acc else None, out=ctx.gw, a_mn_major=True, b_mn_major=True)
+        return dh, None, None, None, None, None
 
 
 # ------------------------------------------------------------------------------ the model
@@ -167,6 +209,9 @@ class NativeCausalLM:
         self._stacked: dict[str, tuple] = {}
         self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.trace: dict | None = None
+        # called with the index of a gradient chunk once backward has finished every gradient of that chunk
+        # (chunk 0 = embedding, 1 + i = layer i, last = final norm / untied lm_head); set per backward pass
+        self.on_chunk_grads_final = None
         self.table = ops.rope_table(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, device=device) \
             if self.on_gpu else None
 
@@ -187,14 +232,17 @@ class NativeCausalLM:
         they are not adjacent."""
         key = "+".join(names)
         if key not in self._stacked:
-            specs = [self.b.specs[n] for n in names]
-            ok = all(a.offset + a.numel == b.offset and a.shape[1:] == b.shape[1:] and len(a.shape) == 2
-                     for a, b in zip(specs, specs[1:]))
+            specs = [self.b.specs.get(n) for n in names]
+            ok = all(sp is not None for sp in specs) and all(
+                a.offset + a.numel == b.offset and a.shape[1:] == b.shape[1:] and len(a.shape) in (1, 2)
+                for a, b in zip(specs, specs[1:]))
             if ok:
-                rows, cols = sum(sp.shape[0] for sp in specs), specs[0].shape[1]
+                rows = sum(sp.shape[0] for sp in specs)
+                shape = (rows,) + tuple(specs[0].shape[1:])
+                n = sum(sp.numel for sp in specs)
                 o = specs[0].offset
-                leaf = self.b.params[o:o + rows * cols].view(rows, cols).detach().requires_grad_(True)
-                self._stacked[key] = (leaf, self.b.grads[o:o + rows * cols].view(rows, cols))
+                leaf = self.b.params[o:o + n].view(shape).detach().requires_grad_(True)
+                self._stacked[key] = (leaf, self.b.grads[o:o + n].view(shape))
             else:
                 self._stacked[key] = (None, None)
         return self._stacked[key]
@@ -235,41 +283,59 @@ class NativeCausalLM:
         pre = f"model.layers.{i}."
         a = pre + "self_attn."
         H, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        sink = self.b
 
         def lin(inp, name, bias=False, residual=None):
             bn = name.replace(".weight", ".bias")
             return _Linear.apply(inp, self.p(name), self.g(name), self.p(bn) if bias else None, self.g(bn) if bias else None,
-                                 residual)
+                                 residual, sink)
 
-        h = _RMSNorm.apply(x, self.p(pre + "input_layernorm.weight"), self.g(pre + "input_layernorm.weight"), cfg.rms_norm_eps)
-        q = lin(h, a + "q_proj.weight", cfg.attention_bias).view(-1, H, D)
-        k = lin(h, a + "k_proj.weight", cfg.attention_bias).view(-1, Hkv, D)
-        v = lin(h, a + "v_proj.weight", cfg.attention_bias).view(-1, Hkv, D)
-        if cfg.qk_norm:
-            q = _RMSNorm.apply(q, self.p(a + "q_norm.weight"), self.g(a + "q_norm.weight"), cfg.rms_norm_eps)
-            k = _RMSNorm.apply(k, self.p(a + "k_norm.weight"), self.g(a + "k_norm.weight"), cfg.rms_norm_eps)
-        q = _RoPE.apply(q.contiguous(), positions, self.table)
-        k = _RoPE.apply(k.contiguous(), positions, self.table)
+        def norm(inp, name, eps=cfg.rms_norm_eps):
+            return _RMSNorm.apply(inp, self.p(name), self.g(name), eps, sink)
+
+        h = norm(x, pre + "input_layernorm.weight")
+        qkv_names = tuple(a + n + "_proj.weight" for n in "qkv")
+        wqkv, gqkv = self.stacked(qkv_names)
+        bqkv, gbqkv = self.stacked(tuple(n.replace(".weight", ".bias") for n in qkv_names)) if cfg.attention_bias else (None, None)
+        fused = wqkv is not None and (not cfg.attention_bias or bqkv is not None)
+        if fused:       # q, k and v are neighbours in the bucket: one GEMM forward, dgrad and wgrad
+            qkv = _Linear.apply(h, wqkv, gqkv, bqkv, gbqkv, None, sink)
+        if fused and not cfg.qk_norm:
+            q, k, v = _SplitQKVRope.apply(qkv, positions, self.table, H, Hkv, D)
+        else:
+            if fused:
+                q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], dim=-1)
+                q, k, v = q.reshape(-1, H, D), k.reshape(-1, Hkv, D), v.reshape(-1, Hkv, D)
+            else:
+                q = lin(h, a + "q_proj.weight", cfg.attention_bias).view(-1, H, D)
+                k = lin(h, a + "k_proj.weight", cfg.attention_bias).view(-1, Hkv, D)
+                v = lin(h, a + "v_proj.weight", cfg.attention_bias).view(-1, Hkv, D)
+            if cfg.qk_norm:
+                q = norm(q.contiguous(), a + "q_norm.weight")
+                k = norm(k.contiguous(), a + "k_norm.weight")
+            q = _RoPE.apply(q.contiguous(), positions, self.table)
+            k = _RoPE.apply(k.contiguous(), positions, self.table)
         if D in (64, 128):
             # tcgen05 flash attention, forward and backward (csrc/flash_sm100.cu); rows are the B padded sequences
             cu = self._cu_seqlens(B, Tn)
-            o = flash_attention(q, k, v.contiguous(), cu, cu, Tn, Tn, causal=True, scale=1.0 / math.sqrt(D))
+            if v.stride(1) != D or v.stride(2) != 1:
+                v = v.contiguous()
+            o = flash_attention(q, k, v, cu, cu, Tn, Tn, causal=True, scale=1.0 / math.sqrt(D))
             o = o.reshape(B * Tn, H * D)
         else:
             # head sizes the flash kernel does not cover (tiny test models): library attention
             o = F.scaled_dot_product_attention(
                 q.view(B, Tn, H, D).transpose(1, 2), k.view(B, Tn, Hkv, D).transpose(1, 2),
-                v.view(B, Tn, Hkv, D).transpose(1, 2), is_causal=True, scale=1.0 / math.sqrt(D), enable_gqa=True)
+                v.reshape(B, Tn, Hkv, D).transpose(1, 2), is_causal=True, scale=1.0 / math.sqrt(D), enable_gqa=True)
             o = o.transpose(1, 2).reshape(B * Tn, H * D)
         x = lin(o, a + "o_proj.weight", residual=x)
-        h = _RMSNorm.apply(x, self.p(pre + "post_attention_layernorm.weight"),
-                           self.g(pre + "post_attention_layernorm.weight"), cfg.rms_norm_eps)
+        h = norm(x, pre + "post_attention_layernorm.weight")
         m = pre + "mlp."
         if cfg.is_moe and i >= cfg.first_k_dense_replace:
             return x + self._moe(h, m, lin)
         wgu, ggu = self.stacked((m + "gate_proj.weight", m + "up_proj.weight"))
         if wgu is not None:       # gate and up are neighbours in the bucket: one GEMM forward, dgrad and wgrad
-            gu = _Linear.apply(h, wgu, ggu, None, None, None)
+            gu = _Linear.apply(h, wgu, ggu, None, None, None, sink)
         else:
             gu = torch.cat([lin(h, m + "gate_proj.weight"), lin(h, m + "up_proj.weight")], dim=-1)
         return lin(_SwiGLU.apply(gu), m + "down_proj.weight", residual=x)
@@ -328,21 +394,32 @@ class NativeCausalLM:
         ids = input_ids.reshape(-1).to(torch.int32).contiguous()
         positions = torch.arange(Tn, device=self.device, dtype=torch.int32).repeat(B)
         emb = "model.embed_tokens.weight"
-        x = _Embedding.apply(ids, self.p(emb), self.g(emb))
+        sink = self.b
+        x = _Embedding.apply(ids, self.p(emb), self.g(emb), sink)
         trace = self.trace            # set to a dict to record the residual stream (layer-by-layer debugging)
         if trace is not None:
             trace["embed"] = x.detach().view(B, Tn, -1)
+        cb = self.on_chunk_grads_final
+
+        def watch(t, chunk):
+            # the gradient of a layer's input is complete only after every gradient inside that layer is
+            if cb is not None and t.requires_grad:
+                t.register_hook(lambda g, c=chunk: cb(c))
+
         for i in range(cfg.num_layers):
+            watch(x, 1 + i)
             if self.ckpt:
                 x = torch.utils.checkpoint.checkpoint(self._layer, x, i, positions, B, Tn, use_reentrant=False)
             else:
                 x = self._layer(x, i, positions, B, Tn)
             if trace is not None:
                 trace[f"layer.{i}"] = x.detach().view(B, Tn, -1)
-        h = _RMSNorm.apply(x, self.p("model.norm.weight"), self.g("model.norm.weight"), cfg.rms_norm_eps)
+        head = emb if cfg.tie_word_embeddings else "lm_head.weight"
+        if len(self.b.chunks) > 1 + cfg.num_layers:
+            watch(x, 1 + cfg.num_layers)          # final norm (and the untied lm_head)
+        h = _RMSNorm.apply(x, self.p("model.norm.weight"), self.g("model.norm.weight"), cfg.rms_norm_eps, sink)
         if trace is not None:
             trace["final_norm"] = h.detach().view(B, Tn, -1)
-        head = emb if cfg.tie_word_embeddings else "lm_head.weight"
         tg = targets.reshape(-1).to(torch.int32).contiguous()
-        lp, ent, _ = _FusedLogprob.apply(h, self.p(head), self.g(head), tg, need_entropy)
+        lp, ent, _ = _FusedLogprob.apply(h, self.p(head), self.g(head), tg, need_entropy, sink)
         return lp.view(B, Tn), (ent.view(B, Tn) if need_entropy else None)

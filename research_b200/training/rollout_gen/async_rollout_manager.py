@@ -33,7 +33,14 @@ class AsyncRolloutManager:
 
     @staticmethod
     def _adopt(group: list[Sample], out: list[Sample]) -> list[Sample]:
-        for src, dst in zip(group, out):
+        """Give every generated sample the group / index / ground truth of the prompt it answers: one per prompt in
+        order, or (a generate function that returns several samples per prompt, e.g. one per branch) the prompt named
+        by ``metadata["source_prompt"]``."""
+        for j, dst in enumerate(out):
+            k = dst.metadata.get("source_prompt", j) if isinstance(dst.metadata, dict) else j
+            if not 0 <= k < len(group):
+                continue
+            src = group[k]
             dst.group_index, dst.index = src.group_index, src.index
             if dst.ground_truth is None:
                 dst.ground_truth = src.ground_truth

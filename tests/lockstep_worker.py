@@ -32,6 +32,22 @@ if rank == 0:
     ref = solo.generate([[3, 4, 5, 6]], SamplingParams(temperature=0.0, max_tokens=5))[0]
     assert outs[0].completion_tokens == ref.completion_tokens, (outs[0].completion_tokens, ref.completion_tokens)
     assert len(late.completion_tokens) == 3 and svc.steps > 0
+    # a weight update and a cache flush go through the same broadcast: every rank swaps its shards at the same step
+    import tempfile
+
+    from research_b200.models.weights import save_safetensors_dir
+
+    w2 = init_random_weights(cfg, seed=1)
+    with tempfile.TemporaryDirectory() as d:
+        save_safetensors_dir(w2, cfg, d)
+        assert svc.update_weights_from_path(d) == 1
+    svc.flush_cache()
+    after = svc.submit([3, 4, 5, 6], SamplingParams(temperature=0.0, max_tokens=5)).result(timeout=180)
+    solo.update_weights(w2)
+    solo.flush_cache()
+    ref2 = solo.generate([[3, 4, 5, 6]], SamplingParams(temperature=0.0, max_tokens=5))[0]
+    assert after.completion_tokens == ref2.completion_tokens, (after.completion_tokens, ref2.completion_tokens)
+    assert after.weight_version == 1
     svc.shutdown()
     print("LOCKSTEP_OK", flush=True)
 else:

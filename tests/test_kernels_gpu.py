@@ -403,3 +403,49 @@ def test_lm_head_sample_matches_two_step(cuda_device, M, V, K):
     assert torch.equal(tok[::3], greedy[::3])
     tok2, _ = ops.lm_head_sample(h, w, temps, seeds, step=4, step_tensor=step_t)
     assert (tok2[1::3] != tok[1::3]).any(), "another step must draw other noise"
+
+
+# ------------------------------------------------------------------------------------ bounded waits
+def test_bounded_flag_wait_runs_out_and_the_device_stays_usable(cuda_device):
+    """The failure branch of the cross-GPU flag wait: a wait on a flag that nothing sets, with a budget of one
+    millisecond, returns on its own, records its status code for the host, and the next kernel runs normally."""
+    import time
+
+    from research_b200.ops._util import KernelStatusError, check_status, status_tensor, stream_handle
+    from research_b200.parallel.symm import LocalComm, _lib
+
+    comm = LocalComm(cuda_device)
+    slot = comm.new_slot()
+    st = status_tensor(cuda_device)
+    torch.cuda.synchronize()
+    check_status(cuda_device)
+    t0 = time.perf_counter()
+    rc = _lib().rb_symm_wait_budget(comm.flags.local.data_ptr(), 1, slot, 1, st.data_ptr(), 1_000_000,
+                                    stream_handle(cuda_device))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 2.0, "the wait did not honour its budget"
+    with pytest.raises(KernelStatusError, match="flag written by another GPU"):
+        check_status(cuda_device)
+    # the status word was reset by the failed check; the context is intact
+    a, b = _rand((256, 128), cuda_device, seed=1), _rand((192, 128), cuda_device, 0.1, seed=2)
+    _assert_close(ops.gemm(a, b), a.float() @ b.float().t(), 0.05, 0.02, "gemm after a timed-out wait")
+    # a flag that IS set lets the same wait through
+    comm.signal(slot)
+    rc = _lib().rb_symm_wait_budget(comm.flags.local.data_ptr(), 1, slot, 1, st.data_ptr(), 1_000_000,
+                                    stream_handle(cuda_device))
+    assert rc == 0
+    torch.cuda.synchronize()
+    check_status(cuda_device)
+
+
+def test_wait_budget_is_a_launch_setting(cuda_device):
+    """The library-wide budget of the flag waits can be set and restored from the host."""
+    from research_b200.parallel.symm import _lib
+
+    lib = _lib()
+    default = lib.rb_comm_get_wait_budget_ns()
+    lib.rb_comm_set_wait_budget_ns(5_000_000)
+    assert lib.rb_comm_get_wait_budget_ns() == 5_000_000
+    lib.rb_comm_set_wait_budget_ns(0)
+    assert lib.rb_comm_get_wait_budget_ns() == default

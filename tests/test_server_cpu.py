@@ -54,8 +54,17 @@ def test_http_endpoints(tmp_path):
         r2 = client.post("/generate", json={"input_ids": [5, 6, 7], "sampling_params": {"temperature": 0.0, "max_new_tokens": 4}}).json()
         assert r2["meta_info"]["weight_version"] == 1 and r2["output_ids"] != r["output_ids"]
         assert client.post("/update_weights_from_disk", json={"model_path": str(tmp_path / "nope")}).status_code == 404
+        # the layout the training backend writes: a safetensors directory with config.json
+        from research_b200.models.weights import save_safetensors_dir
+
+        st_dir = tmp_path / "st_ckpt"
+        save_safetensors_dir(init_random_weights(cfg, seed=2), cfg, st_dir)
+        u3 = client.post("/update_weights_from_disk", json={"model_path": str(st_dir)})
+        assert u3.status_code == 200 and u3.json()["weight_version"] == 2, u3.text
+        r3 = client.post("/generate", json={"input_ids": [5, 6, 7], "sampling_params": {"temperature": 0.0, "max_new_tokens": 4}}).json()
+        assert r3["meta_info"]["weight_version"] == 2 and r3["output_ids"] != r2["output_ids"]
         assert client.post("/flush_cache").json()["success"]
         info = client.get("/get_server_info").json()
-        assert info["weight_version"] == 1 and info["running"] == 0
+        assert info["weight_version"] == 2 and info["running"] == 0
     finally:
         svc.shutdown()

@@ -91,3 +91,20 @@ def test_noalloc_decode_rejects_oversize(cuda_device):
     assert rc == TOO_LARGE
     torch.cuda.synchronize()
     ops.check_status()
+
+
+def test_noalloc_decode_single_split_uses_no_scratch_and_has_no_size_limit(cuda_device):
+    """One split writes the output directly: the entry point asks for none of the internal array, so a shape whose
+    split form would not fit is still accepted, and the result equals the regular entry point's."""
+    lib = _lib()
+    assert lib.rb_paged_decode_noalloc_required_floats(4096, 32, 128, 1) == 0
+    assert lib.rb_paged_decode_noalloc_required_floats(4096, 32, 128, 2) > MAX_FLOATS
+    q, kc, vc, bt, sl = _case(cuda_device, 5, 14, 2, 64, [300, 17, 512, 1, 96], 11)
+    want = ops.paged_decode(q, kc, vc, bt, sl, num_splits=1)
+    for _ in range(2):
+        rc, got = _call(lib, q, kc, vc, bt, sl, 1)
+        assert rc == 0
+        torch.cuda.synchronize()
+        diff = (got.float() - want.float()).abs()
+        assert diff.max().item() < 0.01 and diff.mean().item() < 0.001
+    ops.check_status()
