@@ -36,6 +36,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
 # library name -> (compiler, [sources])
 LIBRARIES: dict[str, tuple[str, list[str]]] = {
     "rb_gemm": ("nvcc", ["gemm_sm100.cu"]),
+    "rb_gemm2": ("nvcc", ["gemm2_sm100.cu"]),
     "rb_ops": ("nvcc", ["ops_sm100.cu"]),
     "rb_attn": ("nvcc", ["attn_sm100.cu"]),
     "rb_flash": ("nvcc", ["flash_sm100.cu"]),

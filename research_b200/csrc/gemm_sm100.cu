@@ -49,6 +49,10 @@ constexpr int EPI_WARPS = 4;
 constexpr int NORM_WARPS = RB_NORM_WARPS;                       // extra warps of a launch with a folded RMSNorm
 constexpr int NORM_ROWS = 128 / (NORM_WARPS * 32);  // tile rows per lane of a norm warp
 constexpr int GEMM_THREADS_NORM = GEMM_THREADS + NORM_WARPS * 32;
+// Launches that carry an all-gather (see GemmParams::gather_*): two extra warps per CTA copy the peers' shards into
+// local memory while the tensor cores work. 256 threads keep the full register budget of the plain kernel.
+constexpr int GATHER_WARPS = 2;
+constexpr int GEMM_THREADS_GATHER = GEMM_THREADS + GATHER_WARPS * 32;
 // MN-major 128B-swizzled tiles: 64-element chunks are BK*128 bytes apart (leading offset),
 // groups of 8 K-rows are 1024 bytes apart (stride offset).
 #ifndef RB_MN_LBO
@@ -119,6 +123,19 @@ struct GemmParams {
   unsigned long long sample_step_add;
   float* splitk_ws;
   int* splitk_tickets;
+  // Fused all-gather of a row-sharded matrix (sharded-parameter training): part r is a contiguous block of
+  // gather_part_bytes at gather_src[r] (rank r's shard, peer memory); the two gather warps of every CTA copy an
+  // interleaved share of each part to gather_dst + r * gather_part_bytes (local), own part first, and the last CTA
+  // to finish a part publishes gather_ready[r] = gather_epoch. When the gathered matrix is this launch's own B
+  // operand (b_parts = parts, b_ready = gather_ready), tiles of part r start as soon as part r has landed, and the
+  // tile order starts at b_part_rot (the local part). Each remote byte crosses NVLink once.
+  const void* gather_src[RB_MAX_PARTS];
+  void* gather_dst;
+  long long gather_part_bytes;
+  int* gather_count;      // [parts] arrival counters, zero between launches
+  int* gather_ready;      // [parts]
+  int gather_epoch, gather_parts;
+  int b_part_rot;
 };
 
 __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
@@ -174,9 +191,10 @@ __device__ unsigned long long g_ts[148 * 8];
 // bound decides the register budget: 320 threads cap the kernel at 168 registers (with spills in the epilogue),
 // 192 threads leave it its 221. Compiling every launch for 320 threads cost the plain GEMMs 4 % (8192^3) and the
 // 0.5B decode step 0.1 ms.
-template <int BN, bool A_MN, bool B_MN, bool NORM = false>
-__global__ void __launch_bounds__(NORM ? GEMM_THREADS_NORM : GEMM_THREADS, 1)
+template <int BN, bool A_MN, bool B_MN, bool NORM = false, bool GATHER = false>
+__global__ void __launch_bounds__(NORM ? GEMM_THREADS_NORM : (GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS), 1)
 gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
+  static_assert(!(NORM && GATHER), "the extra warps are either norm warps or gather warps");
   using Cfg = GemmCfg<BN>;
   constexpr int MAX_STAGES = Cfg::kStages;
   const int STAGES = p.stages;   // ring depth of this launch (<= MAX_STAGES); short-K launches use a shallow ring
@@ -271,6 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     m_part = mt / m_tiles_per_part;
     m_in = (mt % m_tiles_per_part) * BM;
     n_part = nt / n_tiles_per_part;
+    if (p.b_part_rot) { n_part += p.b_part_rot; if (n_part >= p.b_parts) n_part -= p.b_parts; }   // local shard first
     n_in = (nt % n_tiles_per_part) * BN;
   };
 
@@ -293,6 +312,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (!grouped && p.b_ready != nullptr && !((b_seen >> n_part) & 1u)) {
           ok = wait_flag_ge(p.b_ready + n_part, p.ready_epoch, p.status);
           if (!ok) { *abortp = 1; break; }
+          // the part may have been written by ordinary stores of this launch's gather warps: order them before
+          // the tile loads of the async proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
           b_seen |= 1u << n_part;
         }
         const CUtensorMap* amap = &p.a_map[grouped ? 0 : m_part];
@@ -383,6 +405,45 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
           umma_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
         }
         if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else if (GATHER && warp >= 2 + EPI_WARPS) {
+    // ------------------------------ gather warps (fused all-gather only) ---------------------
+    constexpr int GT = GATHER_WARPS * 32;
+    const int gt = (warp - 2 - EPI_WARPS) * 32 + lane;
+    const long long nvec = p.gather_part_bytes >> 4;
+    const long long stride = (long long)gridDim.x * GT;
+    for (int pp = 0; pp < p.gather_parts; ++pp) {
+      int part = p.rank + pp;
+      if (part >= p.gather_parts) part -= p.gather_parts;
+      const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[part]);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.gather_dst) + (long long)part * p.gather_part_bytes);
+      constexpr int U = 8;     // eight 16-byte loads in flight per thread: the copy is bound by NVLink latency otherwise
+      for (long long i0 = (long long)blockIdx.x * GT + gt; i0 < nvec; i0 += stride * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < nvec)
+            asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i) : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < nvec) dst[i] = v[u];
+        }
+      }
+      __threadfence();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");    // the gather warps of this CTA only
+      if (gt == 0) {
+        const int old = atomicAdd(p.gather_count + part, 1);
+        if (old == (int)gridDim.x - 1) {     // every CTA's share of this part is in place
+          p.gather_count[part] = 0;
+          __threadfence();
+          st_release_sys(p.gather_ready + part, p.gather_epoch);
+        }
       }
     }
   } else if (warp >= 2 + EPI_WARPS) {
@@ -1070,10 +1131,10 @@ namespace rb {
 
 constexpr int kMaxDynSmem = 227 * 1024 - 2048;   // 227 KB per CTA minus the kernel's static shared memory (about 1.3 KB)
 
-template <int BN, bool A_MN, bool B_MN, bool NORM = false>
+template <int BN, bool A_MN, bool B_MN, bool NORM = false, bool GATHER = false>
 static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, NORM>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, NORM, GATHER>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
@@ -1118,11 +1179,20 @@ static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   if (q.red_alias) smem = (stages * Cfg::kStageBytes > extra ? stages * Cfg::kStageBytes : extra) + 1024;
   if (p.cluster_k)
     return launch_kernel_cluster(kern, dim3(grid), dim3(GEMM_THREADS), smem, stream, (unsigned)p.split_k, q) == cudaSuccess ? 0 : -11;
-  return launch_kernel(kern, dim3(grid), dim3(NORM ? GEMM_THREADS_NORM : GEMM_THREADS), smem, stream, q) == cudaSuccess ? 0 : -11;
+  return launch_kernel(kern, dim3(grid), dim3(NORM ? GEMM_THREADS_NORM : (GATHER ? GEMM_THREADS_GATHER : GEMM_THREADS)), smem,
+                       stream, q) == cudaSuccess ? 0 : -11;
 }
 
 template <int BN>
 static int launch_bn(const GemmParams& p, int a_mn, int b_mn, int max_ctas, cudaStream_t s) {
+  if (p.gather_parts > 0) {
+    // launches that carry an all-gather: forward (K-major operands) and weight gradient (both MN-major), wide tiles
+    if constexpr (BN >= 128) {
+      if (!a_mn && !b_mn) return launch_cfg<BN, false, false, false, true>(p, max_ctas, s);
+      if (a_mn && b_mn) return launch_cfg<BN, true, true, false, true>(p, max_ctas, s);
+    }
+    return -12;
+  }
   if (!a_mn && !b_mn) return p.norm_fold ? launch_cfg<BN, false, false, true>(p, max_ctas, s) : launch_cfg<BN, false, false>(p, max_ctas, s);
   if (p.norm_fold) return -12;   // the folded norm exists for K-major operands only
   if constexpr (BN >= 64) {
@@ -1218,6 +1288,20 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   if (p.norm_fold && (a->a_mn_major || a->split_k > 1 || a->epi_mode != RB_EPI_STORE || a->tile_table || p.sample_ws != nullptr ||
                       a->a_parts != 1 || p.fp8 || p.mirror || a->row_dst))
     return -1;
+  if (a->gather_parts > 0) {
+    if (a->gather_parts > RB_MAX_PARTS || a->gather_dst == nullptr || a->gather_count == nullptr || a->gather_ready == nullptr ||
+        a->gather_part_bytes <= 0 || a->gather_part_bytes % 16 != 0 || p.norm_fold || a->split_k > 1 || a->tile_table ||
+        a->swiglu || p.epi_mode != RB_EPI_STORE || p.sample_ws != nullptr || a->rank < 0 || a->rank >= a->gather_parts)
+      return -1;
+    p.gather_parts = a->gather_parts;
+    for (int r = 0; r < a->gather_parts; ++r) p.gather_src[r] = a->gather_src[r];
+    p.gather_dst = a->gather_dst;
+    p.gather_part_bytes = a->gather_part_bytes;
+    p.gather_count = a->gather_count;
+    p.gather_ready = a->gather_ready;
+    p.gather_epoch = a->gather_epoch;
+  }
+  p.b_part_rot = (a->b_part_rot > 0 && a->b_part_rot < a->b_parts) ? a->b_part_rot : 0;
   p.cluster_k = (a->cluster_split && p.split_k > 1) ? 1 : 0;
   if (p.cluster_k) {
     // slices = CTAs of one cluster; needs a power-of-two slice count up to 8 and a non-empty K range for each
@@ -1266,6 +1350,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
     if (p.epi_mode != RB_EPI_STORE && bn < 64) bn = 64;
   }
   if (a->b_mn_major && bn < 64) bn = 64;
+  if (p.gather_parts > 0 && bn < 128) bn = 128;
   // tensor maps: one per slab
   for (int i = 0; i < p.a_parts; ++i) {
     int rc = a->a_mn_major

@@ -99,6 +99,21 @@ typedef struct RbGemmArgs {
   // into B's columns beforehand. K-major A, plain store or SwiGLU epilogue, no split.
   int norm_fold;
   float norm_eps;
+  // Fused all-gather (sharded parameters): the launch also copies `gather_parts` equal, contiguous blocks of
+  // gather_part_bytes from gather_src[r] (rank r's shard; peer memory, plain loads) to gather_dst + r * bytes in local
+  // memory, this rank's own part first, and publishes gather_ready[r] = gather_epoch when part r is complete
+  // (gather_count: [parts] counters, zero between launches). To consume the gathered matrix in the SAME launch
+  // describe it as the B operand with b_parts = gather_parts, B[r] = gather_dst + r * bytes, b_ready = gather_ready,
+  // ready_epoch = gather_epoch and b_part_rot = rank: tiles of a part start when that part has landed. A launch
+  // whose operands are unrelated (a weight-gradient GEMM) can carry the gather for the launch that follows it.
+  const void* gather_src[RB_MAX_PARTS];
+  void* gather_dst;
+  long long gather_part_bytes;
+  int* gather_count;
+  int* gather_ready;
+  int gather_epoch;
+  int gather_parts;
+  int b_part_rot;                // visit B's parts starting at this one
 } RbGemmArgs;
 
 // Token and log-probability from the per-tile records written by the sampling epilogue.

@@ -79,6 +79,14 @@ class RbGemmArgs(ctypes.Structure):
         ("cluster_split", ctypes.c_int),
         ("norm_fold", ctypes.c_int),
         ("norm_eps", ctypes.c_float),
+        ("gather_src", ctypes.c_void_p * RB_MAX_PARTS),
+        ("gather_dst", ctypes.c_void_p),
+        ("gather_part_bytes", ctypes.c_longlong),
+        ("gather_count", ctypes.c_void_p),
+        ("gather_ready", ctypes.c_void_p),
+        ("gather_epoch", ctypes.c_int),
+        ("gather_parts", ctypes.c_int),
+        ("b_part_rot", ctypes.c_int),
     ]
 
 
@@ -91,6 +99,52 @@ def _lib() -> ctypes.CDLL:
         lib.rb_sample_merge.restype = ctypes.c_int
         lib._rb_typed = True
     return lib
+
+
+def _lib2() -> ctypes.CDLL:
+    lib = _native.load("rb_gemm2")
+    if not getattr(lib, "_rb_typed", False):
+        vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        lib.rb_gemm2_bf16.argtypes = [vp] * 5 + [i, i, i, ll, ll, ll, ll, i, i, i, i, vp, vp]
+        lib.rb_gemm2_bf16.restype = i
+        lib.rb_gemm2_pairs.restype = i
+        lib._rb_typed = True
+    return lib
+
+
+_GEMM2 = os.environ.get("RB_GEMM2", "1") != "0"
+_GEMM2_PAIRS = 74      # CTA pairs resident on a B200 (148 SMs)
+
+
+def _use_pair_kernel(M: int, N: int, K: int, a_mn_major: bool, b_mn_major: bool) -> bool:
+    """Large problems go to the two-CTA kernel (csrc/gemm2_sm100.cu): at least one full wave of 256-row tiles and a
+    K loop long enough to amortise a tile's prologue. Small or skinny problems stay on the one-CTA kernel, which has
+    the narrow tiles and the split-K forms they need."""
+    if not _GEMM2 or (a_mn_major and not b_mn_major) or N % 8 or K < 256 or M < 512:
+        return False
+    if not (a_mn_major and b_mn_major) and K % 8:
+        return False
+    return -(-M // 256) * -(-N // 128) >= _GEMM2_PAIRS
+
+
+def gemm2(a: torch.Tensor, b: torch.Tensor, bias=None, residual=None, out=None, *, a_mn_major=False, b_mn_major=False,
+          out_f32=False, bn: int = 0) -> torch.Tensor:
+    """``C = op(A) @ op(B)^T (+bias) (+residual)`` on the two-CTA (``cta_group::2``) kernel; same operand conventions
+    as ``gemm``. ``bn``: 256 or 128 output columns per tile (0 = fewest waves)."""
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    K, M = a.shape if a_mn_major else a.shape[::-1]
+    Kb, N = b.shape if b_mn_major else b.shape[::-1]
+    assert K == Kb, f"K mismatch: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    assert out.stride(1) == 1 and (residual is None or residual.stride(1) == 1)
+    rc = _lib2().rb_gemm2_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+                               residual.data_ptr() if residual is not None else None, M, N, K, a.stride(0), b.stride(0),
+                               out.stride(0), residual.stride(0) if residual is not None else 0, int(a_mn_major),
+                               int(b_mn_major), int(out_f32), bn, status_tensor(a.device).data_ptr(), stream_handle(a.device))
+    check_rc(rc, "rb_gemm2_bf16")
+    return out
 
 
 def gemm_reference(a, b, bias=None, residual=None, a_mn_major=False, b_mn_major=False, out_dtype=None):
@@ -123,8 +177,16 @@ def gemm(
     beta: float = 1.0,
     cluster_split: bool | None = None,
     norm_eps: float | None = None,
+    b_gather=None,
+    carry_gather=None,
 ) -> torch.Tensor:
     """``C[M,N] = alpha * op(A) @ op(B)^T (+bias) (+ beta * residual)``.
+
+    Sharded parameters (``parallel.fsdp.ShardedWeight`` handles): with ``b_gather=w`` (pass ``b=None``) the K-major B
+    operand is the row-sharded matrix ``w``; the launch itself gathers the peers' slabs into the local staging matrix
+    and its tiles start part by part as the slabs land (all-gather fused into the consuming GEMM). With
+    ``carry_gather=w`` the launch computes its own, unrelated product and fetches ``w`` on the side for the launch
+    that follows (the weight-gradient GEMM carries the gather for the data-gradient GEMM).
 
     ``norm_eps`` folds an RMSNorm of A's rows into the launch: ``C = rstd(row) * (A @ B^T) (+bias)`` with
     ``rstd = rsqrt(mean(A[row]^2) + norm_eps)``; together with the norm weight multiplied into B's columns
@@ -139,7 +201,13 @@ def gemm(
     if norm_eps is not None:
         assert not a_mn_major and split_k in (0, 1) and alpha == 1.0 and beta == 1.0, "folded RMSNorm: K-major A, no split"
         split_k = 1
+    if b_gather is not None:
+        assert b is None and not b_mn_major and not a_mn_major, "the gathered operand is a K-major B"
+        if not a.is_cuda:
+            b = b_gather.b.full_param(b_gather.spec.name)
+            b_gather = None
     if not a.is_cuda:
+        carry_gather = None
         if norm_eps is not None:
             af = a.float()
             a = (af * torch.rsqrt(af.pow(2).mean(-1, keepdim=True) + norm_eps)).to(a.dtype)
@@ -158,6 +226,8 @@ def gemm(
             out.copy_(res)
             return out
         return res
+    if b_gather is not None:
+        b = b_gather.staged          # [rows, cols] view of the staging matrix this launch fills
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1, "operands must be contiguous in their last dim"
@@ -170,6 +240,10 @@ def gemm(
     else:
         N, Kb = b.shape
     assert K == Kb, f"K mismatch: {K} vs {Kb}"
+    gather = b_gather if b_gather is not None else carry_gather
+    if (gather is None and not swiglu and norm_eps is None and alpha == 1.0 and beta == 1.0 and bn == 0 and max_ctas == 0 and split_k in (0, 1)
+            and not cluster_split and _use_pair_kernel(M, N, K, a_mn_major, b_mn_major)):
+        return gemm2(a, b, bias, residual, out, a_mn_major=a_mn_major, b_mn_major=b_mn_major, out_f32=out_f32)
     if out is None:
         out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
     assert out.stride(1) == 1
@@ -192,6 +266,26 @@ def gemm(
     args.swiglu = int(swiglu)
     if norm_eps is not None:
         args.norm_fold, args.norm_eps = 1, float(norm_eps)
+    if gather is not None:
+        assert not swiglu and norm_eps is None and alpha == 1.0 and beta == 1.0 and split_k in (0, 1), "gather launches are plain GEMMs"
+        split_k = 1
+        W = gather.world
+        for r in range(W):
+            args.gather_src[r] = gather.peer_ptrs[r]
+        args.gather_dst = gather.b.stage.data_ptr()
+        args.gather_part_bytes = gather.part_bytes
+        args.gather_count = gather.b.gather_count.data_ptr()
+        args.gather_ready = gather.b.gather_ready.data_ptr()
+        args.gather_epoch = gather.next_epoch()
+        args.gather_parts = W
+        args.rank = gather.rank
+        if b_gather is not None:          # consumed by this launch: B is the staging matrix, part by part
+            args.b_parts = W
+            for r in range(W):
+                args.B[r] = args.gather_dst + r * gather.part_bytes
+            args.b_ready = args.gather_ready
+            args.ready_epoch = args.gather_epoch
+            args.b_part_rot = gather.rank
     if alpha != 1.0 or beta != 1.0:
         assert not swiglu, "the scaled epilogue is not combined with the fused SwiGLU"
         args.scaled_epilogue, args.alpha, args.beta = 1, alpha, beta
@@ -490,5 +584,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias=None, residual=None, out=
     return y.reshape(*lead, weight.shape[0])
 
 
-__all__ = ["gemm", "lm_head_sample", "lm_head_sample_workspace", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE", "EPI_ALL_REDUCE_ONESHOT"]
+__all__ = ["gemm", "gemm2", "lm_head_sample", "lm_head_sample_workspace", "gemm_fp8", "quantize_fp8", "gemm_symmetric", "gemm_reference", "linear", "interleave_gate_up", "swiglu_interleaved_reference", "RbGemmArgs", "EPI_STORE", "EPI_REDUCE_SCATTER", "EPI_ALL_REDUCE", "EPI_ALL_REDUCE_ONESHOT"]
 _ = ptr  # re-exported helper kept for wrappers that build RbGemmArgs themselves

@@ -41,41 +41,69 @@ from .symm import PeerComm, _lib
 class ParamSpec:
     name: str
     shape: tuple[int, ...]
-    offset: int        # element offset inside the flat buckets
+    offset: int        # element offset inside the flat gradient bucket (always the full parameter)
     numel: int
     chunk: int
+    p_offset: int = 0  # element offset inside this rank's parameter storage
+    sharded: bool = False   # the parameter storage holds rows [rank * rows / world, (rank + 1) * rows / world) only
 
 
 class FlatBuckets:
-    """Flat bf16 parameter and gradient storage with per-parameter views."""
+    """Flat bf16 parameter and gradient storage with per-parameter views.
+
+    ``shard_rule(name, shape) -> bool`` marks matrices whose ROWS are split over the ranks (sharded-parameter
+    training): the parameter storage of a rank then holds its row slab only, the gradient bucket still holds the
+    full matrix (backward writes all of it, the reduce-scatter keeps this rank's slab). A chunk holds either sharded
+    or unsharded parameters, never both; sharded chunks reduce and update slab by slab and push nothing to the
+    peers, whose GEMM launches fetch the slabs when they need the matrix (``ShardedWeight``)."""
 
     def __init__(self, comm: PeerComm, named_shapes: list[tuple[str, tuple[int, ...]]], chunk_of=None,
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, shard_rule=None):
         self.comm = comm
-        align = 8 * comm.world
+        W = comm.world
+        align = 8 * W
         self.specs: dict[str, ParamSpec] = {}
-        self.chunks: list[tuple[int, int]] = []  # (offset, length) per chunk, length % align == 0
-        off = 0
-        cur_chunk, chunk_start = None, 0
+        self.chunks: list[tuple[int, int]] = []  # (offset, length) per chunk in the gradient bucket, length % align == 0
+        self.p_chunks: list[tuple[int, int]] = []  # the same chunks in this rank's parameter storage
+        self.chunk_sharded: list[bool] = []
+        off = p_off = 0
+        cur_chunk, chunk_start, p_chunk_start, cur_sharded = None, 0, 0, False
+
+        def close_chunk():
+            nonlocal off, p_off
+            off = -(-off // align) * align
+            self.chunks.append((chunk_start, off - chunk_start))
+            if not cur_sharded:
+                p_off = p_chunk_start + (off - chunk_start)      # same layout as the gradient chunk
+            self.p_chunks.append((p_chunk_start, p_off - p_chunk_start))
+            self.chunk_sharded.append(cur_sharded)
+
         for name, shape in named_shapes:
             c = chunk_of(name) if chunk_of else 0
-            if cur_chunk is None:
-                cur_chunk = c
-            if c != cur_chunk:
-                off = -(-off // align) * align
-                self.chunks.append((chunk_start, off - chunk_start))
-                chunk_start, cur_chunk = off, c
             n = 1
             for s in shape:
                 n *= s
+            sharded = bool(shard_rule(name, tuple(shape))) if (shard_rule is not None and W > 1) else False
+            if sharded:
+                assert len(shape) == 2 and shape[0] % W == 0 and (n // W) % 8 == 0, f"{name} {shape} cannot be row-sharded over {W}"
+            if cur_chunk is None:
+                cur_chunk, cur_sharded = c, sharded
+            if c != cur_chunk:
+                close_chunk()
+                chunk_start, p_chunk_start, cur_chunk, cur_sharded = off, p_off, c, sharded
+            assert sharded == cur_sharded, f"chunk {c} mixes sharded and unsharded parameters ({name})"
             n_pad = -(-n // 8) * 8  # keep every parameter 16-byte aligned for TMA
-            self.specs[name] = ParamSpec(name, tuple(shape), off, n, len(self.chunks))
+            self.specs[name] = ParamSpec(name, tuple(shape), off, n, len(self.chunks),
+                                         p_off if sharded else p_chunk_start + (off - chunk_start), sharded)
             off += n_pad
-        off = -(-off // align) * align
-        self.chunks.append((chunk_start, off - chunk_start))
+            if sharded:
+                p_off += n // W
+        close_chunk()
         self.numel = off
+        self.p_numel = p_off
+        self.any_sharded = any(self.chunk_sharded)
         self.dtype = dtype
-        self.params_buf = comm.alloc((self.numel,), dtype, zero=True)
+        self.params_buf = comm.alloc((self.p_numel,), dtype, zero=True)
         self.grads_buf = comm.alloc((self.numel,), dtype, zero=True)
         self.params, self.grads = self.params_buf.local, self.grads_buf.local
         # Gradient windows: the kernels write a gradient view either over what is there (its first write of a
@@ -85,10 +113,82 @@ class FlatBuckets:
         self._chunk_specs: list[list[ParamSpec]] = [[] for _ in self.chunks]
         for sp in self.specs.values():
             self._chunk_specs[sp.chunk].append(sp)
+        # Parameter chunks whose update of the last optimizer step may still be running on another stream / arriving
+        # from the peers: chunk -> (event recorded after this rank's update, flag slot, epoch every rank signals)
+        self._pending: dict[int, tuple] = {}
+        # sharded parameters are gathered into one staging matrix per GEMM launch (the largest sharded matrix)
+        self.stage = None
+        self._gather_epoch = 0
+        if self.any_sharded:
+            biggest = max(sp.numel for sp in self.specs.values() if sp.sharded)
+            self.stage = torch.empty(biggest, dtype=dtype, device=self.params.device)
+            if comm.on_gpu:
+                self.gather_count = torch.zeros(8, dtype=torch.int32, device=self.params.device)
+                self.gather_ready = torch.zeros(8, dtype=torch.int32, device=self.params.device)
+
+    # ---------------------------------------------------------------- deferred parameter updates
+    def ensure_chunk(self, chunk: int) -> None:
+        """Make the current stream wait until ``chunk``'s parameters of the last optimizer step are in place on this
+        rank: its own update has run and every peer has pushed its slice (or, sharded chunks, updated its slabs)."""
+        t = self._pending.pop(chunk, None)
+        if t is not None:
+            ev, slot, epoch = t
+            torch.cuda.current_stream(self.params.device).wait_event(ev)
+            self.comm.wait(slot, epoch)
+
+    def finish_pending(self) -> None:
+        for c in list(self._pending):
+            self.ensure_chunk(c)
 
     def param_view(self, name: str) -> torch.Tensor:
+        """The parameter as this rank stores it: the whole tensor, or (row-sharded) this rank's ``[rows / world, cols]`` slab."""
+        if self._pending:
+            self.finish_pending()
         s = self.specs[name]
-        return self.params[s.offset:s.offset + s.numel].view(s.shape)
+        if s.sharded:
+            n = s.numel // self.comm.world
+            return self.params[s.p_offset:s.p_offset + n].view(s.shape[0] // self.comm.world, s.shape[1])
+        return self.params[s.p_offset:s.p_offset + s.numel].view(s.shape)
+
+    def full_param(self, name: str) -> torch.Tensor:
+        """The whole parameter; for a row-sharded one a fresh tensor gathered from every rank (a collective on CPU
+        groups: every rank must call it; peer reads on the GPU)."""
+        if self._pending:
+            self.finish_pending()
+        s = self.specs[name]
+        if not s.sharded:
+            return self.param_view(name)
+        W = self.comm.world
+        mine = self.param_view(name)
+        if not self.comm.on_gpu:
+            parts = [torch.empty_like(mine) for _ in range(W)]
+            dist.all_gather(parts, mine.contiguous(), group=self.comm.group)
+            return torch.cat(parts, 0)
+        n = s.numel // W
+        parts = [self.params_buf.peer_tensor(r)[s.p_offset:s.p_offset + n].view(mine.shape) for r in range(W)]
+        return torch.cat(parts, 0)
+
+    def set_param(self, name: str, value: torch.Tensor) -> None:
+        """Store ``value`` (the whole parameter) as this rank keeps it."""
+        s = self.specs[name]
+        v = value.to(device=self.params.device, dtype=self.dtype)
+        if s.sharded:
+            rows = s.shape[0] // self.comm.world
+            v = v[self.comm.rank * rows:(self.comm.rank + 1) * rows]
+        self.param_view(name).copy_(v)
+
+    def sharded_weight(self, name: str) -> "ShardedWeight":
+        return ShardedWeight(self, self.specs[name])
+
+    def segments(self, chunk: int) -> list[tuple[int, int, int]]:
+        """This rank's pieces of a sharded chunk: (offset in the gradient bucket, length, offset inside the rank's shard of the chunk)."""
+        W, r = self.comm.world, self.comm.rank
+        out, at = [], 0
+        for sp in self._chunk_specs[chunk]:
+            n = sp.numel // W
+            out.append((sp.offset + r * n, n, at))
+            at += n
+        return out
 
     def grad_view(self, name: str) -> torch.Tensor:
         s = self.specs[name]
@@ -146,28 +246,44 @@ class ShardedAdamW:
         self.direct_grads = self.on_gpu and self.comm.world == 1
         self.master, self.exp_avg, self.exp_avg_sq, self.red = [], [], [], []
         for c in range(len(buckets.chunks)):
-            off, n = buckets.shard_range(c)
+            off, n = self._param_shard_range(c)
             self.master.append(buckets.params[off:off + n].float().clone())
             self.exp_avg.append(torch.zeros(n, dtype=torch.float32, device=dev))
             self.exp_avg_sq.append(torch.zeros(n, dtype=torch.float32, device=dev))
             self.red.append(None if self.direct_grads else torch.zeros(n, dtype=torch.float32, device=dev))
         self.zero_grads_after_step = True
         self.overlap_grid = 0          # CTAs of a reduce launch that shares the GPU with backward (0 = full grid)
+        # With a stream here, AdamW and the parameter all-gather of a step run on it chunk by chunk, in the order the
+        # next forward pass uses the chunks, and the forward waits chunk by chunk (FlatBuckets.ensure_chunk) instead
+        # of after one barrier: the NVLink-bound pushes hide under the next step's first layers.
+        self.update_stream = None
+        self.update_order: list[int] | None = None
         if self.on_gpu:
             self.n_partial = _lib().rb_rs_num_partials()
             self.partial = torch.zeros(self.n_partial, dtype=torch.float32, device=dev)
             self.coef = torch.ones(1, dtype=torch.float32, device=dev)
             self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
             self.grad_slots = [self.comm.new_slot() for _ in buckets.chunks]    # one ready flag row per chunk
+            self.param_slots = [self.comm.new_slot() for _ in buckets.chunks]
             self.norm_slot = self.comm.new_slot()
         self._reduced: set[int] = set()
         self._passes: dict[int, int] = {}     # reduce launches per chunk since the last step
         self._sumsq_cpu = 0.0
 
+    def _param_shard_range(self, chunk: int) -> tuple[int, int]:
+        """(offset, length) inside this rank's parameter storage of the elements whose optimizer state it owns: its
+        even slice of an unsharded chunk, or everything it stores of a sharded one (its row slabs)."""
+        b = self.b
+        p_off, p_len = b.p_chunks[chunk]
+        if b.chunk_sharded[chunk]:
+            return p_off, p_len
+        n = p_len // self.comm.world
+        return p_off + self.comm.rank * n, n
+
     def resync_master(self) -> None:
         """Re-read the fp32 master slices from the bf16 parameters (after loading weights)."""
         for c in range(len(self.b.chunks)):
-            off, n = self.b.shard_range(c)
+            off, n = self._param_shard_range(c)
             self.master[c].copy_(self.b.params[off:off + n].float())
 
     # ---------------------------------------------------------------- phase 1
@@ -183,11 +299,15 @@ class ShardedAdamW:
         scale = grad_scale / comm.world
         b.zero_unwritten(chunk)
         self._passes[chunk] = self._passes.get(chunk, 0) + 1
+        sharded = b.chunk_sharded[chunk]
         if not self.on_gpu:
             g = b.grads[off:off + length].float()
             if comm.world > 1:
                 dist.all_reduce(g, group=comm.group)
-            mine = g[comm.rank * n:(comm.rank + 1) * n] * scale
+            if sharded:
+                mine = torch.cat([g[o - off:o - off + m] for o, m, _ in b.segments(chunk)]) * scale
+            else:
+                mine = g[comm.rank * n:(comm.rank + 1) * n] * scale
             if accumulate:
                 self.red[chunk].add_(mine)
             else:
@@ -207,9 +327,19 @@ class ShardedAdamW:
         slot = self.grad_slots[chunk]
         epoch = comm.signal(slot)  # my gradients for this chunk are final
         flags = comm.flags.local.data_ptr()
-        if overlapped:
+        if overlapped or sharded:
             comm.wait(slot, epoch)
             flags = None
+        if sharded:
+            # one launch per matrix: this rank's row slab of every peer's full gradient
+            for g_off, m, at in b.segments(chunk):
+                sp_base = g_off - comm.rank * m                    # start of the matrix in the gradient bucket
+                rc = _lib().rb_rs_reduce_ex(b.grads_buf.ptrs(sp_base * 2), None, slot, epoch, comm.rank, comm.world, m, scale,
+                                            self.red[chunk].data_ptr() + at * 4, int(accumulate), self.partial.data_ptr(), st,
+                                            self.overlap_grid if overlapped else 0, stream_handle(dev))
+                check_rc(rc, "rb_rs_reduce_ex")
+            self._reduced.add(chunk)
+            return
         rc = _lib().rb_rs_reduce_ex(ptrs, flags, slot, epoch, comm.rank, comm.world, n, scale,
                                     self.red[chunk].data_ptr(), int(accumulate), self.partial.data_ptr(), st,
                                     self.overlap_grid if overlapped else 0, stream_handle(dev))
@@ -247,8 +377,10 @@ class ShardedAdamW:
                 p = self.master[c]
                 p.mul_(1 - self.lr * self.weight_decay)
                 p.addcdiv_(self.exp_avg[c] / bc1, (self.exp_avg_sq[c] / bc2).sqrt() + self.eps, value=-self.lr)
-                off, length = b.chunks[c]
-                if comm.world > 1:
+                off, length = b.p_chunks[c]
+                if b.chunk_sharded[c]:
+                    b.params[off:off + length].copy_(p.to(b.dtype))        # this rank's slabs; nothing is pushed
+                elif comm.world > 1:
                     parts = [torch.empty_like(p) for _ in range(comm.world)]
                     dist.all_gather(parts, p, group=comm.group)
                     b.params[off:off + length].copy_(torch.cat(parts).to(b.dtype))
@@ -271,23 +403,56 @@ class ShardedAdamW:
                                     self.norm_slot, ep, comm.rank, comm.world, float(self.max_grad_norm), float(grad_scale),
                                     self.coef.data_ptr(), self.norm.data_ptr(), st, stream_handle(dev))
         check_rc(rc, "rb_clip_coef_ex")
-        for c in range(len(b.chunks)):
-            off, length = b.chunks[c]
-            n = length // comm.world
-            grad_ptr = b.grads.data_ptr() + off * 2 if self.direct_grads else self.red[c].data_ptr()
-            rc = _lib().rb_adamw_allgather_ex(
-                self.master[c].data_ptr(), self.exp_avg[c].data_ptr(), self.exp_avg_sq[c].data_ptr(),
-                grad_ptr, int(self.direct_grads), b.params_buf.ptrs(off * 2), comm.rank, comm.world, n, self.lr, b1, b2,
-                self.eps, self.weight_decay, self.step_count, self.coef.data_ptr(), stream_handle(dev))
-            check_rc(rc, "rb_adamw_allgather_ex")
-        comm.barrier()  # every rank's pushes landed; peers are done reading my gradients
+        deferred = self.update_stream is not None and comm.world > 1
+        order = self.update_order if self.update_order is not None else list(range(len(b.chunks)))
+        if deferred:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.update_stream.wait_event(ev)
+            with torch.cuda.stream(self.update_stream):
+                for c in order:
+                    self._update_chunk(c, b1, b2)
+                    epoch = comm.signal(self.param_slots[c])     # my slice of chunk c is everywhere / my slabs are final
+                    done = torch.cuda.Event()
+                    done.record()
+                    b._pending[c] = (done, self.param_slots[c], epoch)
+                self.partial.zero_()
+        else:
+            for c in order:
+                self._update_chunk(c, b1, b2)
+            comm.barrier()  # every rank's pushes landed; peers are done reading my gradients
+            self.partial.zero_()
         if self.zero_grads_after_step:
             b.grads.zero_()
         b.begin_window()
-        self.partial.zero_()
         self._reduced.clear()
         self._passes.clear()
         return self.norm
+
+    def _update_chunk(self, c: int, b1: float, b2: float) -> None:
+        """AdamW on this rank's share of chunk ``c`` (current stream), new bf16 values written where they live."""
+        b, comm = self.b, self.comm
+        dev = b.params.device
+        p_off, p_len = b.p_chunks[c]
+        if b.chunk_sharded[c]:
+            # the rank owns everything it stores of this chunk: update in place, nothing is pushed (the peers'
+            # GEMM launches fetch the slabs when they need the matrix)
+            from .symm import ptr_array
+
+            rc = _lib().rb_adamw_allgather_ex(
+                self.master[c].data_ptr(), self.exp_avg[c].data_ptr(), self.exp_avg_sq[c].data_ptr(),
+                self.red[c].data_ptr(), 0, ptr_array([b.params.data_ptr() + p_off * 2]), 0, 1, p_len, self.lr, b1, b2,
+                self.eps, self.weight_decay, self.step_count, self.coef.data_ptr(), stream_handle(dev))
+            check_rc(rc, "rb_adamw_allgather_ex")
+            return
+        off = b.chunks[c][0]
+        n = p_len // comm.world
+        grad_ptr = b.grads.data_ptr() + off * 2 if self.direct_grads else self.red[c].data_ptr()
+        rc = _lib().rb_adamw_allgather_ex(
+            self.master[c].data_ptr(), self.exp_avg[c].data_ptr(), self.exp_avg_sq[c].data_ptr(),
+            grad_ptr, int(self.direct_grads), b.params_buf.ptrs(p_off * 2), comm.rank, comm.world, n, self.lr, b1, b2,
+            self.eps, self.weight_decay, self.step_count, self.coef.data_ptr(), stream_handle(dev))
+        check_rc(rc, "rb_adamw_allgather_ex")
 
     # ---------------------------------------------------------------- state
     def state_dict(self) -> dict:
@@ -301,6 +466,33 @@ class ShardedAdamW:
         for dst, src in ((self.master, sd["master"]), (self.exp_avg, sd["exp_avg"]), (self.exp_avg_sq, sd["exp_avg_sq"])):
             for d, s in zip(dst, src):
                 d.copy_(s)
+
+
+class ShardedWeight:
+    """Handle of one row-sharded matrix ``[rows, cols]``: where every rank keeps its slab, and the staging matrix a
+    GEMM launch gathers it into (``ops.gemm`` with ``b_gather=`` for the launch that consumes it, ``carry_gather=`` for a
+    launch that fetches it for the next one)."""
+
+    def __init__(self, buckets: FlatBuckets, spec: ParamSpec):
+        self.b, self.spec = buckets, spec
+        W = buckets.comm.world
+        self.rows, self.cols = spec.shape
+        self.part_rows = self.rows // W
+        self.part_bytes = (spec.numel // W) * 2
+        self.peer_ptrs = [p + spec.p_offset * 2 for p in buckets.params_buf.peer_ptrs]
+        self.rank, self.world = buckets.comm.rank, W
+
+    @property
+    def staged(self) -> torch.Tensor:
+        """``[rows, cols]`` view of the staging buffer (valid after a launch that gathered THIS matrix, until the next gather)."""
+        return self.b.stage[:self.spec.numel].view(self.rows, self.cols)
+
+    def next_epoch(self) -> int:
+        self.b._gather_epoch += 1
+        return self.b._gather_epoch
+
+    def local(self) -> torch.Tensor:
+        return self.b.param_view(self.spec.name)
 
 
 _ = ctypes

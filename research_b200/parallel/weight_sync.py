@@ -26,9 +26,13 @@ SEG_DTYPE = np.dtype([("src", "<u8"), ("dst", "<u8"), ("src_ld", "<i8"), ("dst_l
 
 
 class WeightSyncPlan:
-    def __init__(self, runner, src_specs: dict, src_base_ptr: int, src_elem_size: int = 2):
+    def __init__(self, runner, src_specs: dict, src_base_ptr: int, src_elem_size: int = 2,
+                 shard_bases: list[int] | None = None):
         """``runner``: the engine's ModelRunner; ``src_specs``: name -> ParamSpec of the trainer's flat
-        bucket; ``src_base_ptr``: address of that bucket as seen from the engine's GPU."""
+        bucket; ``src_base_ptr``: address of that bucket as seen from the engine's GPU. ``shard_bases``: for a
+        trainer with row-sharded parameters, the addresses of EVERY trainer rank's parameter storage as seen from
+        the engine's GPU (rank q keeps rows ``[q R / W, (q + 1) R / W)`` of a sharded matrix); a segment that spans
+        several slabs is cut at the slab boundaries, each piece read from its owner."""
         assert src_elem_size == 2, "weights travel as bf16"
         self.runner = runner
         self.device = runner.device
@@ -37,17 +41,24 @@ class WeightSyncPlan:
         tp, r = runner.tp_size, runner.tp_rank
         d = cfg.hidden_size
 
-        def src(name: str, row0: int = 0, col0: int = 0, ld: int | None = None) -> int:
-            s = src_specs[name]
-            ld = ld if ld is not None else (s.shape[-1] if len(s.shape) > 1 else s.numel)
-            return src_base_ptr + (s.offset + row0 * ld + col0) * 2
-
         def add(name, dst: torch.Tensor, rows, cols, row0=0, col0=0):
             s = src_specs[name]
             src_ld = s.shape[-1] if len(s.shape) > 1 else s.numel
+            dst_ld = dst.stride(0) if dst.dim() > 1 else cols
+            p_off = getattr(s, "p_offset", s.offset)
             assert cols % 8 == 0 and col0 % 8 == 0, f"{name}: columns must be multiples of 8 ({cols}, {col0})"
-            segs.append((src(name, row0, col0, src_ld), dst.data_ptr(), src_ld, dst.stride(0) if dst.dim() > 1 else cols,
-                         rows, cols))
+            if not getattr(s, "sharded", False):
+                segs.append((src_base_ptr + (p_off + row0 * src_ld + col0) * 2, dst.data_ptr(), src_ld, dst_ld, rows, cols))
+                return
+            assert shard_bases is not None, f"{name} is row-sharded: the plan needs every trainer rank's address"
+            part = s.shape[0] // len(shard_bases)            # rows per trainer rank
+            row, end = row0, row0 + rows
+            while row < end:
+                q = row // part
+                take = min(end, (q + 1) * part) - row
+                segs.append((shard_bases[q] + (p_off + (row - q * part) * src_ld + col0) * 2,
+                             dst.data_ptr() + (row - row0) * dst_ld * 2, src_ld, dst_ld, take, cols))
+                row += take
 
         add("model.embed_tokens.weight", runner.embed, cfg.vocab_size, d)
         add("model.norm.weight", runner.final_norm, 1, d)
@@ -114,13 +125,15 @@ def sync_engine_from_buckets(engine, buckets, plan: WeightSyncPlan | None = None
     copy is read over NVLink. On CPU the engine falls back to ``load_weights`` on the views.
     """
     assert not engine.has_pending(), "weight sync while requests are in flight"
+    buckets.finish_pending()      # a deferred optimizer step: every parameter chunk must be in place before it is read
     runner = engine.runner
     if runner.device.type != "cuda":
         runner.load_weights({name: buckets.param_view(name) for name in buckets.specs})
     else:
         if plan is None:
             base = buckets.params.data_ptr() if src_rank is None else buckets.params_buf.peer_ptrs[src_rank]
-            plan = WeightSyncPlan(runner, buckets.specs, base)
+            plan = WeightSyncPlan(runner, buckets.specs, base,
+                                  shard_bases=list(buckets.params_buf.peer_ptrs) if buckets.any_sharded else None)
         if comm is not None:
             comm.barrier()  # trainer finished writing the parameters
         plan.run()

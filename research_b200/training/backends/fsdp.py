@@ -46,6 +46,7 @@ class FSDPTrainingBackend(NativeTrainingBackend):
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         comm = kw.pop("comm", None) or PeerComm(group, torch.device(device))
         kw.setdefault("activation_checkpointing", cfg.gradient_checkpointing)
+        kw.setdefault("shard_params", cfg.sharding_strategy == "full_shard")
         super().__init__(model_config, weights, comm=comm, device=device, **kw)
         self.fsdp_config = cfg
 

@@ -46,11 +46,22 @@ _GROUPED = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_p
             "mlp.gate_proj.weight", "mlp.up_proj.weight")
 
 
-def _order_key(name: str) -> tuple:
+def _order_key(name: str, chunk_of=_chunk_of) -> tuple:
     for i, suffix in enumerate(_GROUPED):
         if name.endswith(suffix):
-            return (_chunk_of(name), name[:-len(suffix)], i, name)
-    return (_chunk_of(name), name, len(_GROUPED), name)
+            return (chunk_of(name), name[:-len(suffix)], i, name)
+    return (chunk_of(name), name, len(_GROUPED), name)
+
+
+def _shardable(name: str, shape: tuple, world: int) -> bool:
+    """Sharded-parameter mode splits the rows of every weight matrix of the decoder layers (87 % of an 8B model);
+    embeddings, the lm_head and all vectors stay whole on every rank (sharded gradients and optimizer state only)."""
+    if not name.startswith("model.layers.") or len(shape) != 2 or ".experts." in name or name.endswith("gate.weight"):
+        return False
+    return shape[0] % world == 0 and (shape[0] // world * shape[1]) % 8 == 0 and shape[0] // world >= 64
+
+
+_VECTOR_CHUNK = 9_000     # sharded mode: the layers' vectors (norm weights, biases) live in one chunk of their own
 
 
 class NativeTrainingBackend:
@@ -60,7 +71,7 @@ class NativeTrainingBackend:
                  betas: tuple[float, float] = (0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
                  trainer_config: TrainerConfig | None = None, lr_schedule: Callable[[int], float] | None = None,
                  checkpoint_dir: str | Path | None = None, activation_checkpointing: bool = False,
-                 need_entropy: bool | None = None, seed: int = 0, overlap_comm: bool = True):
+                 need_entropy: bool | None = None, seed: int = 0, overlap_comm: bool = True, shard_params: bool = False):
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda" if torch.cuda.is_available() else "cpu")
         self.comm = comm if comm is not None else LocalComm(self.device)
@@ -69,26 +80,40 @@ class NativeTrainingBackend:
         self.config = trainer_config or TrainerConfig()
         on_gpu = self.device.type == "cuda"
         dtype = torch.bfloat16 if on_gpu else torch.float32
-        shapes = sorted(param_shapes(model_config).items(), key=lambda kv: _order_key(kv[0]))
-        self.buckets = FlatBuckets(self.comm, shapes, _chunk_of, dtype=dtype)
+        all_shapes = param_shapes(model_config)
+        self.shard_params = bool(shard_params) and self.world > 1
+        chunk_of, rule = _chunk_of, None
+        if self.shard_params:
+            W = self.world
+
+            def rule(name, shape):
+                return _shardable(name, shape, W)
+
+            def chunk_of(name):      # a layer's chunk keeps its sharded matrices only
+                return _chunk_of(name) if (not name.startswith("model.layers.") or rule(name, tuple(all_shapes[name]))) else _VECTOR_CHUNK
+
+        shapes = sorted(all_shapes.items(), key=lambda kv: _order_key(kv[0], chunk_of))
+        self.buckets = FlatBuckets(self.comm, shapes, chunk_of, dtype=dtype, shard_rule=rule)
         if weights is None and on_gpu:
             # random init written straight into the bucket (an 8B model never exists twice in memory)
+            # whole tensors: the same seed on every rank gives every rank the same values; row slabs: seeded per rank
             g = torch.Generator(device=self.device).manual_seed(seed)
-            for n in self.buckets.specs:
-                v = self.buckets.param_view(n)
+            g_slab = torch.Generator(device=self.device).manual_seed(seed * 1009 + 1 + self.rank)
+            for n, sp in self.buckets.specs.items():
+                v = self.buckets.param_view(n)       # the whole tensor, or this rank's row slab
                 if n.endswith("norm.weight") or n.endswith("layernorm.weight"):
                     v.fill_(1.0)
                 elif n.endswith(".bias"):
                     v.zero_()
                 else:
-                    v.normal_(0.0, model_config.init_std, generator=g)
+                    v.normal_(0.0, model_config.init_std, generator=g_slab if sp.sharded else g)
         else:
             if weights is None:
                 from ...models.weights import init_random_weights
 
                 weights = init_random_weights(model_config, seed=seed)
             for n in self.buckets.specs:
-                self.buckets.param_view(n).copy_(weights[n].to(device=self.device, dtype=dtype))
+                self.buckets.set_param(n, weights[n])
         self.comm.barrier_host()
         max_norm = self.config.max_grad_norm if self.config.max_grad_norm is not None else 0.0
         self.optimizer = ShardedAdamW(self.buckets, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
@@ -106,6 +131,13 @@ class NativeTrainingBackend:
         self._pass_reduced: set[int] = set()
         if self.overlap_comm:
             self.optimizer.overlap_grid = 64
+            # AdamW + parameter all-gather of a step run on the second stream too, chunk by chunk in the order the next
+            # forward pass needs them (embedding, the layers' vectors, the layers, the head)
+            self.optimizer.update_stream = self._side
+            ids = {n: sp.chunk for n, sp in self.buckets.specs.items()}
+            first = [ids[n] for n in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight") if n in ids]
+            rest = [c for c in range(len(self.buckets.chunks)) if c not in first]
+            self.optimizer.update_order = list(dict.fromkeys(first)) + rest
         self.model = NativeCausalLM(model_config, self.buckets, self.device, activation_checkpointing)
         self.loss_name = loss_fn if isinstance(loss_fn, str) else getattr(loss_fn, "__name__", "custom")
         self.loss_fn = LOGPROB_LOSSES[loss_fn] if isinstance(loss_fn, str) else loss_fn
@@ -234,12 +266,12 @@ class NativeTrainingBackend:
             raise
 
     def get_weights(self) -> TrainFuture[dict[str, Any]]:
-        return ImmediateTrainFuture({n: self.buckets.param_view(n).detach().clone() for n in self.buckets.specs},
+        return ImmediateTrainFuture({n: self.buckets.full_param(n).detach().clone() for n in self.buckets.specs},
                                     "get_weights")
 
     def load_weights(self, weights: dict[str, Any]) -> TrainFuture[None]:
         for n in self.buckets.specs:
-            self.buckets.param_view(n).copy_(weights[n].to(device=self.device, dtype=self.buckets.dtype))
+            self.buckets.set_param(n, weights[n])
         self.optimizer.resync_master()
         self.comm.barrier_host()
         return ImmediateTrainFuture(None, "load_weights")
@@ -256,8 +288,12 @@ class NativeTrainingBackend:
     def save_checkpoint_to_path(self, path: Path | str, step: int | None = None, metrics: dict | None = None) -> Path:
         path = Path(path)
         path.mkdir(parents=True, exist_ok=True)
+        if self.buckets.any_sharded and self.device.type != "cuda":
+            gathered = {n: self.buckets.full_param(n).detach().cpu() for n in self.buckets.specs}   # a collective on CPU groups
+        else:
+            gathered = None
         if self.rank == 0:
-            self.save_hf_checkpoint(path)
+            self.save_hf_checkpoint(path, gathered)
             meta = {"step": self.current_step if step is None else step, "weight_version": self.weight_version,
                     "timestamp": time.time(), "metrics": metrics or {}, "world_size": self.world,
                     "loss": self.loss_name}
@@ -272,8 +308,9 @@ class NativeTrainingBackend:
         self.comm.barrier_host()
         return path
 
-    def save_hf_checkpoint(self, path: Path | str) -> Path:
-        weights = {n: self.buckets.param_view(n).detach().cpu() for n in self.buckets.specs}
+    def save_hf_checkpoint(self, path: Path | str, weights: dict | None = None) -> Path:
+        if weights is None:
+            weights = {n: self.buckets.full_param(n).detach().cpu() for n in self.buckets.specs}
         save_safetensors_dir(weights, self.model_config, path, metadata={"weight_version": self.weight_version})
         return Path(path)
 

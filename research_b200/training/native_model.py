@@ -70,6 +70,38 @@ class _Linear(torch.autograd.Function):
         return dx, None, None, None, None, (dy if ctx.has_res else None), None
 
 
+class _ShardedLinear(torch.autograd.Function):
+    """``y = x W^T (+ bias) (+ residual)`` for a row-sharded ``W`` (``parallel.fsdp.ShardedWeight``).
+
+    Forward: ONE launch gathers the peers' row slabs of ``W`` into the local staging matrix and multiplies, its tiles
+    starting part by part as the slabs land (what FSDP2's pre-forward all-gather + ``F.linear`` do in the reference,
+    rollouts/training/backends/fsdp.py:289-322). Backward: the weight-gradient launch (which does not need ``W``)
+    carries the gather for the data-gradient launch right behind it. ``W`` is never saved for backward."""
+
+    @staticmethod
+    def forward(ctx, x, w, gw, bias, gb, residual, sink):
+        ctx.save_for_backward(x)
+        ctx.w, ctx.gw, ctx.gb, ctx.has_res, ctx.sink = w, gw, gb, residual is not None, sink
+        return ops.gemm(x, None, bias=bias, residual=residual, b_gather=w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dy = _rows_ok(dy)
+        acc = ctx.sink.accumulate_into(ctx.gw)
+        need_dx = ctx.needs_input_grad[0]
+        ops.gemm(dy, x, residual=ctx.gw if acc else None, out=ctx.gw, a_mn_major=True, b_mn_major=True,
+                 carry_gather=ctx.w if need_dx else None)                       # gw (+)= dY^T X, and W arrives
+        dx = ops.gemm(dy, ctx.w.staged, b_mn_major=True) if need_dx else None   # [M,N] x [N,K] -> [M,K]
+        if ctx.gb is not None:
+            db = dy.float().sum(0).to(ctx.gb.dtype)
+            if ctx.sink.accumulate_into(ctx.gb):
+                ctx.gb.add_(db)
+            else:
+                ctx.gb.copy_(db)
+        return dx, None, None, None, None, (dy if ctx.has_res else None), None
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, gw, eps, sink):
@@ -207,6 +239,7 @@ class NativeCausalLM:
         self.ckpt = activation_checkpointing
         self._params: dict[str, torch.Tensor] = {}
         self._stacked: dict[str, tuple] = {}
+        self._sharded: dict[str, object] = {}
         self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.trace: dict | None = None
         # called with the index of a gradient chunk once backward has finished every gradient of that chunk
@@ -217,6 +250,8 @@ class NativeCausalLM:
 
     def p(self, name: str) -> torch.Tensor:
         """Autograd leaf sharing storage with the bucket view (its gradient is written by the kernels)."""
+        if self.b._pending:
+            self.b.ensure_chunk(self.b.specs[name].chunk)     # its update of the last step may still be on its way
         leaf = self._params.get(name)
         if leaf is None:
             leaf = self.b.param_view(name).detach().requires_grad_(True)
@@ -226,14 +261,24 @@ class NativeCausalLM:
     def g(self, name: str) -> torch.Tensor:
         return self.b.grad_view(name)
 
+    def sharded(self, name: str):
+        if self.b._pending:
+            self.b.ensure_chunk(self.b.specs[name].chunk)
+        h = self._sharded.get(name)
+        if h is None:
+            h = self._sharded[name] = self.b.sharded_weight(name)
+        return h
+
     def stacked(self, names: tuple[str, ...]):
         """(parameter leaf, gradient view) of several matrices that lie back to back in the flat bucket, seen as one
         ``[sum(rows), cols]`` matrix, so that e.g. gate and up projections run as one GEMM; ``(None, None)`` when
         they are not adjacent."""
         key = "+".join(names)
+        if self.b._pending and names[0] in self.b.specs:
+            self.b.ensure_chunk(self.b.specs[names[0]].chunk)
         if key not in self._stacked:
             specs = [self.b.specs.get(n) for n in names]
-            ok = all(sp is not None for sp in specs) and all(
+            ok = all(sp is not None and not sp.sharded for sp in specs) and all(
                 a.offset + a.numel == b.offset and a.shape[1:] == b.shape[1:] and len(a.shape) in (1, 2)
                 for a, b in zip(specs, specs[1:]))
             if ok:
@@ -241,18 +286,19 @@ class NativeCausalLM:
                 shape = (rows,) + tuple(specs[0].shape[1:])
                 n = sum(sp.numel for sp in specs)
                 o = specs[0].offset
-                leaf = self.b.params[o:o + n].view(shape).detach().requires_grad_(True)
+                po = specs[0].p_offset
+                leaf = self.b.params[po:po + n].view(shape).detach().requires_grad_(True)
                 self._stacked[key] = (leaf, self.b.grads[o:o + n].view(shape))
             else:
                 self._stacked[key] = (None, None)
         return self._stacked[key]
 
     def state_dict(self) -> dict[str, torch.Tensor]:
-        return {n: self.b.param_view(n) for n in self.b.specs}
+        return {n: self.b.full_param(n) for n in self.b.specs}
 
     # ---------------------------------------------------------------- CPU / oracle path
     def _logprobs_cpu(self, input_ids, targets, need_entropy):
-        leaves = {n: self.b.param_view(n).detach().float().requires_grad_(True) for n in self.b.specs}
+        leaves = {n: self.b.full_param(n).detach().float().requires_grad_(True) for n in self.b.specs}
         logits = causal_lm_forward(input_ids.long(), leaves, self.cfg).float()
         lp_all = F.log_softmax(logits, -1)
         safe = targets.long().clamp(min=0)
@@ -287,8 +333,10 @@ class NativeCausalLM:
 
         def lin(inp, name, bias=False, residual=None):
             bn = name.replace(".weight", ".bias")
-            return _Linear.apply(inp, self.p(name), self.g(name), self.p(bn) if bias else None, self.g(bn) if bias else None,
-                                 residual, sink)
+            bp, bg = (self.p(bn), self.g(bn)) if bias else (None, None)
+            if self.b.specs[name].sharded:      # row-sharded weight: gathered inside the consuming GEMM launch
+                return _ShardedLinear.apply(inp, self.sharded(name), self.g(name), bp, bg, residual, sink)
+            return _Linear.apply(inp, self.p(name), self.g(name), bp, bg, residual, sink)
 
         def norm(inp, name, eps=cfg.rms_norm_eps):
             return _RMSNorm.apply(inp, self.p(name), self.g(name), eps, sink)
@@ -407,7 +455,7 @@ class NativeCausalLM:
                 t.register_hook(lambda g, c=chunk: cb(c))
 
         for i in range(cfg.num_layers):
-            watch(x, 1 + i)
+            watch(x, self.b.specs[f"model.layers.{i}.self_attn.o_proj.weight"].chunk)
             if self.ckpt:
                 x = torch.utils.checkpoint.checkpoint(self._layer, x, i, positions, B, Tn, use_reentrant=False)
             else:
@@ -415,8 +463,7 @@ class NativeCausalLM:
             if trace is not None:
                 trace[f"layer.{i}"] = x.detach().view(B, Tn, -1)
         head = emb if cfg.tie_word_embeddings else "lm_head.weight"
-        if len(self.b.chunks) > 1 + cfg.num_layers:
-            watch(x, 1 + cfg.num_layers)          # final norm (and the untied lm_head)
+        watch(x, self.b.specs["model.norm.weight"].chunk)          # final norm (and the untied lm_head)
         h = _RMSNorm.apply(x, self.p("model.norm.weight"), self.g("model.norm.weight"), cfg.rms_norm_eps, sink)
         if trace is not None:
             trace["final_norm"] = h.detach().view(B, Tn, -1)

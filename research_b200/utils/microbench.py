@@ -203,15 +203,64 @@ def sweep_decode_gemm(shapes=((256, 896, 4864), (256, 896, 896), (256, 4096, 143
     return rows
 
 
+# GEMMs of one training step on the Llama-3-8B shape with 4096 tokens: (role, M, N, K, A MN-major, B MN-major)
+TRAIN_GEMMS_8B = (
+    ("qkv forward", 4096, 6144, 4096, False, False), ("o forward", 4096, 4096, 4096, False, False),
+    ("gate|up forward", 4096, 28672, 4096, False, False), ("down forward", 4096, 4096, 14336, False, False),
+    ("lm_head forward chunk", 2048, 128256, 4096, False, False),
+    ("qkv dgrad", 4096, 4096, 6144, False, True), ("gate|up dgrad", 4096, 4096, 28672, False, True),
+    ("down dgrad", 4096, 14336, 4096, False, True), ("lm_head dgrad chunk", 2048, 4096, 128256, False, True),
+    ("qkv wgrad", 6144, 4096, 4096, True, True), ("o wgrad", 4096, 4096, 4096, True, True),
+    ("gate|up wgrad", 28672, 4096, 4096, True, True), ("down wgrad", 4096, 14336, 4096, True, True),
+)
+
+
+def sweep_train_gemm(peak_tflops: float, iters: int = 10, shapes=TRAIN_GEMMS_8B):
+    """Every GEMM of a training step three ways on identical operands: the one-CTA kernel, the two-CTA
+    (``cta_group::2``) kernel at both tile widths, and the library (``torch.matmul``). L2 is flushed between launches."""
+    from ..ops import gemm_mod as G
+
+    rows = []
+    for role, M, N, K, a_mn, b_mn in shapes:
+        a = torch.randn((K, M) if a_mn else (M, K), device="cuda").bfloat16()
+        b = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.05).bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        la, lb = (a.t() if a_mn else a), (b if b_mn else b.t())
+        flops = 2.0 * M * N * K
+
+        def tf(fn):
+            return round(flops / (time_cuda(fn, iters=iters)["median_ms"] * 1e-3) / 1e12, 1)
+
+        saved = G._GEMM2
+        G._GEMM2 = False
+        one = tf(lambda: ops.gemm(a, b, out=out, a_mn_major=a_mn, b_mn_major=b_mn))
+        G._GEMM2 = saved
+        p256 = tf(lambda: G.gemm2(a, b, out=out, a_mn_major=a_mn, b_mn_major=b_mn, bn=256))
+        p128 = tf(lambda: G.gemm2(a, b, out=out, a_mn_major=a_mn, b_mn_major=b_mn, bn=128))
+        auto = tf(lambda: G.gemm2(a, b, out=out, a_mn_major=a_mn, b_mn_major=b_mn))
+        lib = tf(lambda: torch.matmul(la, lb, out=out))
+        ops.check_status()
+        rows.append({"gemm": role, "M": M, "N": N, "K": K, "one_cta_tflops": one, "pair_bn256_tflops": p256,
+                     "pair_bn128_tflops": p128, "pair_auto_tflops": auto, "library_tflops": lib,
+                     "pair_vs_library": round(auto / lib, 3), "pair_frac_of_measured_peak": round(auto / peak_tflops, 3)})
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--decode-gemm-sweep", action="store_true", help="only the tile-width / split-K sweep of decode GEMMs")
+    ap.add_argument("--train-gemm-sweep", action="store_true",
+                    help="only the GEMMs of a Llama-3-8B training step: one-CTA kernel, two-CTA kernel, library")
     ap.add_argument("--peak-tflops", type=float, default=1688.4)
     ap.add_argument("--peak-gbs", type=float, default=6453.4)
     ap.add_argument("--quick", action="store_true")
     args = ap.parse_args()
     if args.decode_gemm_sweep:
         for r in sweep_decode_gemm():
+            print(json.dumps(r))
+        return
+    if args.train_gemm_sweep:
+        for r in sweep_train_gemm(args.peak_tflops):
             print(json.dumps(r))
         return
     rows = []

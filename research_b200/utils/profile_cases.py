@@ -127,6 +127,65 @@ def case_decode_step() -> None:
     print("ok")
 
 
+def case_gemm_pair() -> None:
+    """Two-CTA (``cta_group::2``) GEMM at a training shape: the o projection forward, 4096 x 4096 x 4096, and the gate|up
+    projection forward, 4096 x 28672 x 4096 (weights 235 MB: streamed from HBM)."""
+    from ..ops.gemm import gemm2
+
+    a = torch.randn(4096, 4096, device="cuda").bfloat16()
+    wo = torch.randn(4096, 4096, device="cuda").bfloat16() * 0.05
+    wgu = torch.randn(28672, 4096, device="cuda").bfloat16() * 0.05
+    out_o = torch.empty(4096, 4096, device="cuda", dtype=torch.bfloat16)
+    out_gu = torch.empty(4096, 28672, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        gemm2(a, wo, out=out_o)
+        gemm2(a, wgu, out=out_gu)
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
+def _optimizer_case(n_params: int):
+    """One rank's sharded-optimizer state over ``n_params`` parameters in three chunks (this GPU is its only peer)."""
+    from ..parallel.fsdp import FlatBuckets, ShardedAdamW
+    from ..parallel.symm import LocalComm
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    comm = LocalComm(dev)
+    rows = n_params // 3 // 4096
+    shapes = [(f"w{i}", (rows, 4096)) for i in range(3)]
+    fb = FlatBuckets(comm, shapes, lambda n: int(n[1:]))
+    fb.params.normal_(0, 0.02)
+    fb.grads.normal_(0, 0.01)
+    return fb, ShardedAdamW(fb, lr=1e-5, max_grad_norm=1.0)
+
+
+def case_rs_reduce() -> None:
+    """Gradient reduce kernel on one GPU: 96 Mi bf16 gradients (192 MB, larger than L2) in three chunks; with one rank
+    the launch reads the bucket once and produces the sum of squares (the norm pass of a single-GPU step)."""
+    fb, opt = _optimizer_case(96 * 1024 * 1024)
+    for _ in range(3):
+        for c in range(3):
+            opt.reduce_chunk(c)
+        opt._reduced.clear()
+        opt._passes.clear()
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
+def case_adamw_allgather() -> None:
+    """Sharded AdamW + parameter write-back on one GPU: 96 Mi parameters (fp32 master and both moments 1.1 GB, bf16
+    gradients and parameters 192 MB each), three steps of three chunk launches."""
+    fb, opt = _optimizer_case(96 * 1024 * 1024)
+    for _ in range(3):
+        opt.step()
+        fb.grads.normal_(0, 0.01)
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 if __name__ == "__main__":

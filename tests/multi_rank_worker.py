@@ -217,6 +217,52 @@ def case_fsdp_backend_and_grpo(comm, dev, dt):
         dist.barrier()
 
 
+def case_fsdp_full_shard(comm, dev, dt):
+    """Sharded parameters (layer matrices split by rows, gathered inside the consuming GEMM launches) against the
+    replicated-parameter mode: same data, same steps, same weights afterwards."""
+    from research_b200.models import get_preset, init_random_weights
+    from research_b200.training.backends import FSDPTrainingBackend
+    from research_b200.training.backends.fsdp import FSDPConfig
+
+    W = comm.world
+    # head size 64: the flash kernels run on a GPU; 512 tokens per rank: the GEMMs have several tiles per part
+    cfg = get_preset("tiny-qwen2", num_layers=2, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64,
+                     intermediate_size=512 * W if dev.type == "cuda" else 256 * W, vocab_size=1024)
+    w = init_random_weights(cfg, seed=3)
+    g = torch.Generator().manual_seed(1)
+    T = 256 if dev.type == "cuda" else 24
+    all_ids = torch.randint(0, cfg.vocab_size, (2 * W, T), generator=g)
+    mine = all_ids[comm.rank * 2:(comm.rank + 1) * 2]
+    results = {}
+    for mode in ("shard_optimizer_and_grads", "full_shard"):
+        # a small learning rate: AdamW moves every weight by about lr per step whatever the gradient's size, so where
+        # the two modes' bf16 GEMMs round a tiny gradient to opposite signs the weights part by 2 lr per step
+        be = FSDPTrainingBackend(cfg, w, device=dev, loss_fn="ce", lr=2e-3, comm=comm, config=FSDPConfig(sharding_strategy=mode))
+        assert be.buckets.any_sharded == (mode == "full_shard")
+        losses = []
+        for _ in range(3):
+            losses.append(be.forward_backward({"input_ids": mine, "labels": mine}).wait()["loss"])
+            be.optim_step().wait()
+        results[mode] = (losses, {n: be.buckets.full_param(n).float().cpu() for n in
+                                  ("model.layers.1.mlp.down_proj.weight", "model.layers.0.self_attn.q_proj.weight",
+                                   "model.layers.0.self_attn.k_proj.weight", "model.layers.1.mlp.gate_proj.weight",
+                                   "model.embed_tokens.weight", "model.layers.0.input_layernorm.weight")})
+        if mode == "full_shard":
+            sp = be.buckets.specs["model.layers.0.mlp.up_proj.weight"]
+            assert sp.sharded and be.buckets.param_view(sp.name).shape[0] == sp.shape[0] // W
+            assert be.buckets.p_numel < be.buckets.numel
+            sd = be.get_weights().wait()
+            assert sd["model.layers.0.mlp.up_proj.weight"].shape == sp.shape
+        comm.barrier_host()
+    (la, pa), (lb, pb) = results["shard_optimizer_and_grads"], results["full_shard"]
+    tol = 1.5e-2 if dev.type == "cuda" else 2e-4
+    for x, y in zip(la, lb):
+        assert abs(x - y) < tol * max(1.0, abs(x)), (la, lb)
+    assert lb[-1] < lb[0], lb
+    for n in pa:
+        close(pb[n], pa[n], tol, tol, f"full_shard vs replicated {n}")
+
+
 def case_moe_expert_parallel(comm, dev, dt):
     """Each rank routes its own tokens; experts are split over the ranks; dispatch and combine
     travel through peer memory. Checked against the single-process functional MoE."""
@@ -247,6 +293,7 @@ def _bcast_buckets(b, comm):
 
 CASES = {"barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
          "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo,
+         "fsdp_full_shard": case_fsdp_full_shard,
          "moe_ep": case_moe_expert_parallel}
 
 

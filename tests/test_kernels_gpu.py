@@ -66,6 +66,49 @@ def test_gemm_epilogue_bias_residual_f32(cuda_device):
     _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.05, rtol=0.01, what="inplace")
 
 
+# two-CTA kernel (tcgen05.mma.cta_group::2, csrc/gemm2_sm100.cu): forward, dgrad and wgrad operand layouts, ragged M / N / K
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (1024, 768, 320), (600, 1000, 512), (256, 2048, 4096), (4096, 1024, 1088)])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_gemm_pair_kernel(cuda_device, a_mn, b_mn, M, N, K, bn):
+    from research_b200.ops.gemm import gemm2
+
+    a = _rand((K, M) if a_mn else (M, K), cuda_device, seed=11)
+    b = _rand((K, N) if b_mn else (N, K), cuda_device, seed=12)
+    out = gemm2(a, b, a_mn_major=a_mn, b_mn_major=b_mn, bn=bn)
+    ref = ops.gemm_reference(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out_dtype=torch.float32)
+    _assert_close(out, ref, atol=0.02 * math.sqrt(K), rtol=0.01, what=f"gemm2 {M}x{N}x{K} mn {a_mn}{b_mn} bn={bn}")
+
+
+def test_gemm_pair_kernel_epilogues_and_dispatch(cuda_device):
+    from research_b200.ops.gemm import _use_pair_kernel, gemm2
+
+    M, N, K = 1024, 1152, 896
+    a = _rand((M, K), cuda_device, seed=5)
+    b = _rand((N, K), cuda_device, 0.05, seed=6)
+    bias = _rand((N,), cuda_device, seed=7)
+    res = _rand((M, N), cuda_device, seed=8)
+    ref = ops.gemm_reference(a, b, bias, res, out_dtype=torch.float32)
+    _assert_close(gemm2(a, b, bias=bias, residual=res), ref, atol=0.05, rtol=0.01, what="gemm2 bias+residual")
+    out32 = gemm2(a, b, out_f32=True)
+    assert out32.dtype == torch.float32
+    _assert_close(out32, ops.gemm_reference(a, b, out_dtype=torch.float32), atol=2e-3, rtol=1e-3, what="gemm2 f32 out")
+    x = res.clone()                                     # accumulate in place, as the weight-gradient GEMM does
+    gemm2(a, b, residual=x, out=x)
+    _assert_close(x, ops.gemm_reference(a, b, None, res, out_dtype=torch.float32), atol=0.05, rtol=0.01, what="gemm2 inplace")
+    # strided output rows and operand rows (views of wider matrices)
+    wide = torch.zeros(M, N + 64, dtype=torch.bfloat16, device=cuda_device)
+    gemm2(a, b, out=wide[:, :N])
+    _assert_close(wide[:, :N], ops.gemm_reference(a, b, out_dtype=torch.float32), atol=0.02 * math.sqrt(K), rtol=0.01, what="gemm2 ldc")
+    assert float(wide[:, N:].abs().sum()) == 0.0
+    # the public entry point sends training-sized problems here and keeps decode-sized ones on the one-CTA kernel
+    assert _use_pair_kernel(4096, 6144, 4096, False, False) and _use_pair_kernel(28672, 4096, 4096, True, True)
+    assert not _use_pair_kernel(256, 28672, 4096, False, False) and not _use_pair_kernel(4096, 4096, 4096, True, False)
+    big_a, big_b = _rand((2048, 1024), cuda_device, seed=13), _rand((4736, 1024), cuda_device, 0.05, seed=14)
+    _assert_close(ops.gemm(big_a, big_b), ops.gemm_reference(big_a, big_b, out_dtype=torch.float32), atol=0.1, rtol=0.01,
+                  what="gemm dispatch to the pair kernel")
+
+
 @pytest.mark.parametrize("M,F,K,bn", [(256, 4864, 896, 256), (70, 512, 256, 128), (300, 256, 320, 64)])
 def test_gemm_fused_swiglu(cuda_device, M, F, K, bn):
     from research_b200.ops.gemm import interleave_gate_up
