@@ -8,6 +8,7 @@
     python -m research_b200.infra.cli remote run    user@host:22 --name train "python train.py"
     python -m research_b200.infra.cli remote status|logs|stop user@host:22 --name train
     python -m research_b200.infra.cli code index|search|symbols --root . [query]
+    python -m research_b200.infra.cli code defs|refs|outline --root . [--backend auto|tree-sitter|ast|scan|ctags] [--snippet] [name]
 
 ``gpus`` talks to every provider whose API key is in the environment. The ``--where`` mini-language is a list of
 ``field OP value`` terms joined by blanks (all must hold); OP is one of ``== != >= <= > <`` or ``~`` (substring).
@@ -132,6 +133,14 @@ def cmd_remote(a, out: Callable[[str], None]) -> int:
 
 def cmd_code(a, out: Callable[[str], None]) -> int:
     root = Path(a.root).resolve()
+    if a.action in ("defs", "refs", "outline"):
+        from .csearch_symbols import SearchOptions, list_symbols, search_definitions, search_references
+
+        o = SearchOptions(path=root, backend=a.backend, include_snippet=a.snippet, limit=a.limit, exact=not a.fuzzy)
+        res = list_symbols(o) if a.action == "outline" else (search_definitions if a.action == "defs" else search_references)(a.query, o)
+        for r in res:
+            out(r.format_with_snippet() if a.snippet else r.format_compact())
+        return 0 if res else 1
     cache = Path(a.index) if a.index else root / ".csearch_index.json"
     if a.action == "index" or not cache.exists():
         ix = CodeIndex(root).build()
@@ -185,6 +194,11 @@ def build_parser() -> argparse.ArgumentParser:
         p.add_argument("query", nargs="?" if name != "search" else None, default="")
         p.add_argument("--root", default="."); p.add_argument("--index", default=""); p.add_argument("--regex", action="store_true")
         p.add_argument("--limit", type=int, default=200)
+    for name in ("defs", "refs", "outline"):
+        p = c.add_parser(name)
+        p.add_argument("query", nargs="?" if name == "outline" else None, default="")
+        p.add_argument("--root", default="."); p.add_argument("--backend", default="auto", choices=["auto", "tree-sitter", "ast", "scan", "ctags"])
+        p.add_argument("--snippet", action="store_true"); p.add_argument("--fuzzy", action="store_true"); p.add_argument("--limit", type=int, default=200)
     return ap
 
 
