@@ -51,6 +51,18 @@ __global__ void symm_signal_kernel(PeerPtrs flags, int rank, int world, int slot
   const int r = threadIdx.x;
   if (r < world) st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, epoch);
 }
+// Same signal with the epoch kept on the device (*counter + 1, stored back): a launch captured in a CUDA graph
+// publishes a fresh epoch on every replay. Every rank replays the same launches, so the counters stay equal.
+__global__ void symm_signal_counter_kernel(PeerPtrs flags, int rank, int world, int slot, int* counter) {
+  __shared__ int ep;
+  if (threadIdx.x == 0) ep = *counter + 1;
+  __syncthreads();
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < world) st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, ep);
+  __syncthreads();
+  if (threadIdx.x == 0) *counter = ep;
+}
 __global__ void symm_wait_kernel(const int* my_flags, int world, int slot, int epoch, int* status,
                                  unsigned long long budget_ns) {
   const int r = threadIdx.x;
@@ -392,6 +404,11 @@ extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int 
 extern "C" int rb_symm_signal(void* const* flag_ptrs, int rank, int world, int slot, int epoch, cudaStream_t s) {
   if (world < 1 || world > RB_MAX_RANKS) return -1;
   symm_signal_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch);
+  return RB_OK();
+}
+extern "C" int rb_symm_signal_counter(void* const* flag_ptrs, int rank, int world, int slot, int* counter, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || counter == nullptr) return -1;
+  symm_signal_counter_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, counter);
   return RB_OK();
 }
 extern "C" int rb_symm_wait(const int* my_flags, int world, int slot, int epoch, int* status, cudaStream_t s) {

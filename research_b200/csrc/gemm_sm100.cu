@@ -90,6 +90,7 @@ struct GemmParams {
   const int* a_ready;
   const int* b_ready;
   int ready_epoch;
+  const int* ready_epoch_ptr;   // when set, the epoch to wait for is read from here (graph replay: a device counter)
   // reduce epilogue
   int rank, world;
   void* stage_ptrs[RB_MAX_PARTS];   // peer r's staging base: [world][rows_per_rank][N] bf16
@@ -301,16 +302,17 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       uint32_t ring_ph = 0;
       bool ok = true;
       uint32_t a_seen = 0, b_seen = 0;  // bitmask of parts whose readiness was confirmed
+      const int ready_epoch = p.ready_epoch_ptr != nullptr ? *p.ready_epoch_ptr : p.ready_epoch;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_part, m_in, n_part, n_in;
         tile_coords(t, m_part, m_in, n_part, n_in);
         if (!grouped && p.a_ready != nullptr && !((a_seen >> m_part) & 1u)) {
-          ok = wait_flag_ge(p.a_ready + m_part, p.ready_epoch, p.status);
+          ok = wait_flag_ge(p.a_ready + m_part, ready_epoch, p.status);
           if (!ok) { *abortp = 1; break; }
           a_seen |= 1u << m_part;
         }
         if (!grouped && p.b_ready != nullptr && !((b_seen >> n_part) & 1u)) {
-          ok = wait_flag_ge(p.b_ready + n_part, p.ready_epoch, p.status);
+          ok = wait_flag_ge(p.b_ready + n_part, ready_epoch, p.status);
           if (!ok) { *abortp = 1; break; }
           // the part may have been written by ordinary stores of this launch's gather warps: order them before
           // the tile loads of the async proxy
@@ -1252,6 +1254,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   p.out_f32 = a->out_f32;
   p.epi_mode = a->epi_mode;
   p.a_ready = a->a_ready; p.b_ready = a->b_ready; p.ready_epoch = a->ready_epoch;
+  p.ready_epoch_ptr = a->ready_epoch_ptr;
   p.rank = a->rank; p.world = a->world < 1 ? 1 : a->world;
   p.reduce_epoch = a->reduce_epoch;
   p.status = a->status;

@@ -114,6 +114,9 @@ typedef struct RbGemmArgs {
   int gather_epoch;
   int gather_parts;
   int b_part_rot;                // visit B's parts starting at this one
+  // Ready epoch of a_ready / b_ready read from device memory at kernel start instead of ready_epoch: a launch
+  // captured in a CUDA graph then waits for the epoch its own replay's signal kernel published.
+  const int* ready_epoch_ptr;
 } RbGemmArgs;
 
 // Token and log-probability from the per-tile records written by the sampling epilogue.

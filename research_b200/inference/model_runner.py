@@ -93,6 +93,17 @@ class ModelRunner:
         # the shared-memory pipe that bounds long-K launches: measured per decode step 2.45 -> 2.40 ms at hidden
         # size 896 but 9.82 -> 9.91 ms at 4096, so only narrow models fold
         self.fold_norm = cfg.hidden_size <= 2048 and not os.environ.get("RB_NO_NORM_FOLD")
+        # Tensor-parallel decode with the residual stream sharded by ROWS over the ranks ("sequence parallel"): the
+        # column-parallel projections (q|k|v, gate|up, lm_head) gather the peers' normalised rows inside the GEMM
+        # (all_gather_gemm: the A tiles of remote slabs are loaded from the peers' memory by the TMA producer) and the
+        # row-parallel projections (o, down) end in a reduce-scatter epilogue that leaves every rank with its rows
+        # of the new residual (gemm_reduce_scatter). No all-reduce, no replicated activations, no barrier between
+        # layers. RB_TP_MODE=allreduce keeps replicated activations and the fused GEMM + all-reduce launches.
+        self.sp = (tp is not None and self.tp_size > 1 and not cfg.is_moe and not getattr(tp, "expert_parallel", False)
+                   and os.environ.get("RB_TP_MODE", "sequence") == "sequence")
+        if self.sp:
+            self.fuse_swiglu = False     # plain gate|up rows: the gathered GEMM has the ordinary epilogue
+            self.fold_norm = False       # each rank normalises only its own rows, before they are gathered
         # fused GEMM+all-reduce works on row counts that split evenly into 8-row vectors per rank
         self.row_align = tp.row_align if tp is not None else 1
         if self.row_align > 1:
@@ -157,6 +168,11 @@ class ModelRunner:
         # activations for decode
         self.a_x = tp.alloc((mb, d), bf) if (tp is not None and self.on_gpu) else torch.empty(mb, d, dtype=bf, device=device)
         self.a_h = torch.empty(mb, d, dtype=bf, device=device)
+        if self.sp:
+            rows = mb // self.tp_size
+            self.a_xs = torch.empty(rows, d, dtype=bf, device=device)                       # this rank's rows of the residual
+            self.a_hs = tp.alloc((rows, d), bf) if self.on_gpu else torch.empty(rows, d, dtype=bf, device=device)  # read by the peers
+            self._sp_slot = tp.comm.new_slot() if self.on_gpu else 0
         self.a_qkv = torch.empty(mb, qkv_rows, dtype=bf, device=device)
         self.a_q = torch.empty(mb, self.Hq * self.D, dtype=bf, device=device)
         self.a_attn = torch.empty(mb, self.Hq * self.D, dtype=bf, device=device)
@@ -290,7 +306,46 @@ class ModelRunner:
             self._mlp(lw, h, x, n, static)
 
     # ------------------------------------------------------------------ decode
+    def _decode_body_sp(self, bk: int) -> None:
+        """One decode step with the residual stream sharded by rows (see ``self.sp``)."""
+        cfg, tp = self.cfg, self.tp
+        P, r = self.tp_size, self.tp_rank
+        rpr = bk // P
+        xs, hs = self.a_xs[:rpr], self.a_hs[:rpr]
+        eps = cfg.rms_norm_eps
+        ops.embedding(self.d_tokens[r * rpr:(r + 1) * rpr], self.embed, out=xs)
+        splits = ops.decode_num_splits(bk, self.Hkv, self.max_model_len, head_dim=self.D)
+        if bk > 64:
+            splits = 1
+        bt, lens = self.bt_dev[:bk], self.d_lens[:bk]
+
+        def gathered(w, out, bias=None, out_f32=False):
+            tp.publish_device()            # hs holds this rank's rows: tell the peers (epoch counted on the device)
+            return tp.all_gather_gemm(hs, w, out, bias=bias, ready_epoch="device", out_f32=out_f32)
+
+        for li, lw in enumerate(self.layers):
+            ops.rmsnorm(xs, lw.ln1, eps, out=hs)
+            qkv = gathered(lw.wqkv, self.a_qkv[:bk], lw.bqkv)
+            q = ops.rope_kv_append(qkv, self.d_pos[:bk], self.d_slots[:bk], self.rope, self.k_cache[li], self.v_cache[li],
+                                   self.Hq, self.Hkv, self.D, lw.q_norm, lw.k_norm, eps, q_out=self.a_q[:bk])
+            attn = ops.paged_decode(q.view(bk, self.Hq, self.D), self.k_cache[li], self.v_cache[li], bt, lens, self.scale,
+                                    splits, out=self.a_attn[:bk].view(bk, self.Hq, self.D), workspace=self.dec_ws)
+            # a rank gets the last partial of its rows only after every peer has finished the GEMM above, so hs may
+            # be rewritten once this returns
+            tp.gemm_reduce_scatter(attn.view(bk, self.Hq * self.D), lw.wo, xs, residual=xs)
+            ops.rmsnorm(xs, lw.ln2, eps, out=hs)
+            gu = gathered(lw.wgu, self.a_gu[:bk])
+            act = ops.swiglu(gu, out=self.a_act[:bk])
+            tp.gemm_reduce_scatter(act, lw.wd, xs, residual=xs)
+        ops.rmsnorm(xs, self.final_norm, eps, out=hs)
+        logits = gathered(self.lm_head, self.a_logits[:bk], out_f32=True)
+        self._sample(logits, self.d_temps[:bk], self.d_seeds[:bk], bk)
+        tp.comm.barrier(self._sp_slot)     # every peer has read hs: the next step may overwrite it
+
     def _decode_body(self, bk: int) -> None:
+        if self.sp:
+            self._decode_body_sp(bk)
+            return
         cfg = self.cfg
         x, h = self.a_x, self.a_h
         ops.embedding(self.d_tokens[:bk], self.embed, out=x[:bk])

@@ -87,6 +87,7 @@ class RbGemmArgs(ctypes.Structure):
         ("gather_epoch", ctypes.c_int),
         ("gather_parts", ctypes.c_int),
         ("b_part_rot", ctypes.c_int),
+        ("ready_epoch_ptr", ctypes.c_void_p),
     ]
 
 

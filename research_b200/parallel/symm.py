@@ -41,6 +41,8 @@ def _lib():
         lib.rb_reshard_copy.argtypes = [_VP, _I, _LL, _VP]
         lib.rb_pull_sum.argtypes = [PP, _VP, _VP, _LL, _I, _VP]
         lib.rb_symm_wait_budget.argtypes = [_VP, _I, _I, _I, _VP, ctypes.c_ulonglong, _VP]
+        lib.rb_symm_signal_counter.argtypes = [PP, _I, _I, _I, _VP, _VP]
+        lib.rb_symm_signal_counter.restype = _I
         lib.rb_rs_reduce_ex.argtypes = [PP, _VP, _I, _I, _I, _I, _LL, _F, _VP, _I, _VP, _VP, _I, _VP]
         lib.rb_clip_coef_ex.argtypes = [_VP, _I, PP, PP, _I, _I, _I, _I, _F, _F, _VP, _VP, _VP, _VP]
         lib.rb_adamw_allgather_ex.argtypes = [_VP, _VP, _VP, _VP, _I, PP, _I, _I, _LL, _F, _F, _F, _F, _F, _I, _VP, _VP]

@@ -51,6 +51,8 @@ class TensorParallel:
             self.tile_flags = comm.alloc((2, self.world, self.max_tiles), torch.int32, zero=True)
             # [0] epoch counter of the reduce calls, [1] CTA ticket (device side, graph safe)
             self.reduce_state = torch.zeros(2, dtype=torch.int32, device=comm.device)
+            # epoch of the "my shard is ready" signal, counted on the device (see publish_device)
+            self.ready_counter = torch.zeros(1, dtype=torch.int32, device=comm.device)
             self._barrier_slot = comm.new_slot()
             # decode-sized row-parallel GEMMs with a long K: partial tile of this rank for the split path below
             self.SPLIT_AR_ROWS = 256
@@ -213,13 +215,24 @@ class TensorParallel:
         """Signal that this rank's symmetric operand (activation or weight shard) is complete."""
         return self.comm.signal(self._ready_slot)
 
+    def publish_device(self) -> None:
+        """``publish`` with the epoch counted on the device: safe inside a captured CUDA graph. Pair it with
+        ``all_gather_gemm(..., ready_epoch="device")``."""
+        if not self.comm.on_gpu:
+            return
+        from .symm import _lib as _comm_lib
+
+        rc = _comm_lib().rb_symm_signal_counter(self.comm.flags.ptrs(), self.rank, self.world, self._ready_slot,
+                                                self.ready_counter.data_ptr(), stream_handle(self.comm.device))
+        check_rc(rc, "rb_symm_signal_counter")
+
     def all_gather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None,
-                        ready_epoch: int | None = None) -> torch.Tensor:
+                        ready_epoch: int | str | None = None, out_f32: bool = False) -> torch.Tensor:
         """``out[M, N] = concat_ranks(x_shard_r) @ w.T``; ``x_shard`` is a symmetric ``[M/P, K]`` tensor.
 
         ``ready_epoch`` is the value returned by ``publish()`` on every rank after the shard was
-        written; the kernel's producer warp waits for each peer's flag before its first load
-        from that peer.
+        written (or ``"device"`` after ``publish_device()``); the kernel's producer warp waits for each peer's
+        flag before its first load from that peer.
         """
         rows, K = x_shard.shape
         N = w.shape[0]
@@ -231,8 +244,10 @@ class TensorParallel:
                 res = res + bias.float()
             out.copy_(res.to(out.dtype))
             return out
+        assert out.dtype == (torch.float32 if out_f32 else torch.bfloat16)
         buf = self.symm_of(x_shard)
         args = self._base_args(rows * self.world, N, K, x_shard, w, 0)
+        args.out_f32 = int(out_f32)
         args.a_parts = self.world
         for r in range(self.world):
             args.A[r] = buf.peer_ptrs[r]
@@ -240,7 +255,10 @@ class TensorParallel:
         args.C, args.ldc = out.data_ptr(), out.stride(0)
         args.bias = bias.data_ptr() if bias is not None else None
         args.epi_mode = EPI_STORE
-        if ready_epoch is not None:
+        if ready_epoch == "device":
+            args.a_ready = self.comm.flag_ptr(self._ready_slot)
+            args.ready_epoch_ptr = self.ready_counter.data_ptr()
+        elif ready_epoch is not None:
             args.a_ready = self.comm.flag_ptr(self._ready_slot)
             args.ready_epoch = ready_epoch
         self._launch(args, x_shard.device)
