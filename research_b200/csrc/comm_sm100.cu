@@ -87,10 +87,18 @@ __device__ __forceinline__ void st_peer_16(void* p, uint4 v) {
 // ready flags (slot) must be >= epoch for every peer before its bucket is read (my_flags == nullptr: the caller
 // has already waited, e.g. with symm_wait on the same stream). shard_f32 == nullptr: only the sum of squares is
 // wanted (one rank, whose AdamW reads the bf16 gradients directly). The peers' loads of one vector are all in
-// flight before the first add, two vectors per thread per trip.
-__global__ void rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, int epoch, int rank, int world,
-                                 long long n_shard, float scale, float* __restrict__ shard_f32, int accumulate,
-                                 float* __restrict__ sumsq_partial, int* status, unsigned long long budget_ns) {
+// flight before the first add.
+// WT: the rank count when it is 1, 2, 4 or 8 (the loads of a vector then sit in exactly WT registers and the trip
+// count per thread is chosen so that eight 16-byte loads are in flight), 0 = any rank count up to RB_MAX_RANKS.
+// Register use decides this kernel: with the loads of 4 x 8 vectors held at once it needed 190 registers, one CTA
+// per SM, and read at 0.9 TB/s; at 85 registers or fewer three CTAs per SM keep the memory system busy.
+template <int WT>
+__global__ void __launch_bounds__(256, 3)
+rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, int epoch, int rank, int world, long long n_shard, float scale,
+                 float* __restrict__ shard_f32, int accumulate, float* __restrict__ sumsq_partial, int* status,
+                 unsigned long long budget_ns) {
+  constexpr int WMAX = WT ? WT : RB_MAX_RANKS;
+  constexpr int UNR = WT == 1 ? 4 : WT == 2 ? 2 : WT == 4 ? 2 : 1;
   __shared__ int failed;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
@@ -103,22 +111,26 @@ __global__ void rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, 
     const long long nvec = n_shard >> 3;
     const long long base = (long long)rank * n_shard;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    constexpr int UNR = 4;
+    // source pointers of this rank's slice, own bucket first, then the peers in ring order (links are used evenly)
+    const __nv_bfloat16* src[WMAX];
+#pragma unroll
+    for (int rr = 0; rr < WMAX; ++rr) {
+      int q = rank + rr;
+      if (q >= world) q -= world;
+      src[rr] = reinterpret_cast<const __nv_bfloat16*>(grads.p[rr < world ? q : rank]) + base;
+    }
     for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * UNR) {
-      uint4 part[UNR][RB_MAX_RANKS];
+      uint4 part[UNR][WMAX];
 #pragma unroll
       for (int u = 0; u < UNR; ++u) {
         const long long i = i0 + u * stride;
         if (i < nvec) {
 #pragma unroll
-          for (int rr = 0; rr < RB_MAX_RANKS; ++rr) {
+          for (int rr = 0; rr < WMAX; ++rr) {
             if (rr < world) {
-              int src = rank + rr;  // stagger the peers so links are used evenly
-              if (src >= world) src -= world;
-              const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(grads.p[src]) + base + i * 8;
-              // this rank's own bucket was written by kernels earlier on this GPU: an ordinary (cacheable, streaming)
-              // load; a peer's bucket is read at system scope
-              part[u][rr] = rr == 0 ? __ldcs(reinterpret_cast<const uint4*>(g)) : ld_peer_16(g);
+              // this rank's own bucket was written by kernels earlier on this GPU: an ordinary streaming load; a
+              // peer's bucket is read at system scope
+              part[u][rr] = rr == 0 ? __ldcs(reinterpret_cast<const uint4*>(src[0] + i * 8)) : ld_peer_16(src[rr] + i * 8);
             }
           }
         }
@@ -129,7 +141,7 @@ __global__ void rs_reduce_kernel(PeerPtrs grads, const int* my_flags, int slot, 
         if (i >= nvec) break;
         float s[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
-        for (int rr = 0; rr < RB_MAX_RANKS; ++rr) {
+        for (int rr = 0; rr < WMAX; ++rr) {
           if (rr < world) {
             const uint4 v = part[u][rr];
             float2 f;
@@ -433,8 +445,17 @@ extern "C" int rb_rs_reduce_ex(void* const* grad_ptrs, const int* my_flags, int 
   if (shard_f32 == nullptr && accumulate) return -1;
   int grid = grid_ctas > 0 ? grid_ctas : rb_rs_num_partials();
   if (grid > rb_rs_num_partials()) grid = rb_rs_num_partials();
-  rs_reduce_kernel<<<grid, 256, 0, s>>>(make_ptrs(grad_ptrs, world), my_flags, slot, epoch, rank, world, n_shard, scale,
-                                        shard_f32, accumulate, sumsq_partial, status, g_wait_budget_ns);
+  const PeerPtrs pp = make_ptrs(grad_ptrs, world);
+#define RB_RS_LAUNCH(WT) rs_reduce_kernel<WT><<<grid, 256, 0, s>>>(pp, my_flags, slot, epoch, rank, world, n_shard, scale, shard_f32, \
+                                                                  accumulate, sumsq_partial, status, g_wait_budget_ns)
+  switch (world) {
+    case 1: RB_RS_LAUNCH(1); break;
+    case 2: RB_RS_LAUNCH(2); break;
+    case 4: RB_RS_LAUNCH(4); break;
+    case 8: RB_RS_LAUNCH(8); break;
+    default: RB_RS_LAUNCH(0); break;
+  }
+#undef RB_RS_LAUNCH
   return RB_OK();
 }
 extern "C" int rb_rs_reduce(void* const* grad_ptrs, const int* my_flags, int slot, int epoch, int rank, int world,

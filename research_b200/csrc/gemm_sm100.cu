@@ -137,6 +137,11 @@ struct GemmParams {
   int* gather_ready;      // [parts]
   int gather_epoch, gather_parts;
   int b_part_rot;
+  // The shards may themselves be produced by the peers just before (activations of a tensor-parallel step): a gather
+  // warp then waits for gather_src_ready[r] >= the ready epoch before it copies part r. gather_wait_all: the gathered
+  // matrix is this launch's A operand as ONE matrix (tiles span the parts), so the producer waits for every part.
+  const int* gather_src_ready;
+  int gather_wait_all;
 };
 
 __device__ __forceinline__ void epi_store_row_chunk(const GemmParams& p, const float* v,
@@ -303,6 +308,13 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       bool ok = true;
       uint32_t a_seen = 0, b_seen = 0;  // bitmask of parts whose readiness was confirmed
       const int ready_epoch = p.ready_epoch_ptr != nullptr ? *p.ready_epoch_ptr : p.ready_epoch;
+      if (GATHER && p.gather_wait_all) {
+        // the A operand is the staging matrix as a whole: every part must have landed (decode-sized copies)
+        const int gep = p.ready_epoch_ptr != nullptr ? ready_epoch : p.gather_epoch;
+        for (int r = 0; r < p.gather_parts && ok; ++r) ok = wait_flag_ge(p.gather_ready + r, gep, p.status);
+        if (!ok) *abortp = 1;
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_part, m_in, n_part, n_in;
         tile_coords(t, m_part, m_in, n_part, n_in);
@@ -415,9 +427,20 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     const int gt = (warp - 2 - EPI_WARPS) * 32 + lane;
     const long long nvec = p.gather_part_bytes >> 4;
     const long long stride = (long long)gridDim.x * GT;
+    const int src_epoch = p.ready_epoch_ptr != nullptr ? *p.ready_epoch_ptr : p.ready_epoch;
+    const int gather_epoch = p.ready_epoch_ptr != nullptr ? src_epoch : p.gather_epoch;
+    __shared__ int gather_failed;
+    if (gt == 0) gather_failed = 0;
+    asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");
     for (int pp = 0; pp < p.gather_parts; ++pp) {
       int part = p.rank + pp;
       if (part >= p.gather_parts) part -= p.gather_parts;
+      if (p.gather_src_ready != nullptr && part != p.rank) {
+        // the owner of this part publishes it with a flag: wait (bounded) before the first byte is read
+        if (gt == 0 && !wait_flag_ge(p.gather_src_ready + part, src_epoch, p.status)) gather_failed = 1;
+        asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");
+        if (gather_failed) break;
+      }
       const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[part]);
       uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.gather_dst) + (long long)part * p.gather_part_bytes);
       constexpr int U = 8;     // eight 16-byte loads in flight per thread: the copy is bound by NVLink latency otherwise
@@ -444,7 +467,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (old == (int)gridDim.x - 1) {     // every CTA's share of this part is in place
           p.gather_count[part] = 0;
           __threadfence();
-          st_release_sys(p.gather_ready + part, p.gather_epoch);
+          st_release_sys(p.gather_ready + part, gather_epoch);
         }
       }
     }
@@ -1189,8 +1212,8 @@ template <int BN>
 static int launch_bn(const GemmParams& p, int a_mn, int b_mn, int max_ctas, cudaStream_t s) {
   if (p.gather_parts > 0) {
     // launches that carry an all-gather: forward (K-major operands) and weight gradient (both MN-major), wide tiles
+    if (!a_mn && !b_mn) return launch_cfg<BN, false, false, false, true>(p, max_ctas, s);
     if constexpr (BN >= 128) {
-      if (!a_mn && !b_mn) return launch_cfg<BN, false, false, false, true>(p, max_ctas, s);
       if (a_mn && b_mn) return launch_cfg<BN, true, true, false, true>(p, max_ctas, s);
     }
     return -12;
@@ -1303,6 +1326,8 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
     p.gather_count = a->gather_count;
     p.gather_ready = a->gather_ready;
     p.gather_epoch = a->gather_epoch;
+    p.gather_src_ready = a->gather_src_ready;
+    p.gather_wait_all = a->gather_wait_all ? 1 : 0;
   }
   p.b_part_rot = (a->b_part_rot > 0 && a->b_part_rot < a->b_parts) ? a->b_part_rot : 0;
   p.cluster_k = (a->cluster_split && p.split_k > 1) ? 1 : 0;
@@ -1353,7 +1378,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
     if (p.epi_mode != RB_EPI_STORE && bn < 64) bn = 64;
   }
   if (a->b_mn_major && bn < 64) bn = 64;
-  if (p.gather_parts > 0 && bn < 128) bn = 128;
+  if (p.gather_parts > 0 && bn < 128 && !p.gather_wait_all) bn = 128;   // weight gathers ride on wide-tile launches
   // tensor maps: one per slab
   for (int i = 0; i < p.a_parts; ++i) {
     int rc = a->a_mn_major

@@ -117,6 +117,13 @@ typedef struct RbGemmArgs {
   // Ready epoch of a_ready / b_ready read from device memory at kernel start instead of ready_epoch: a launch
   // captured in a CUDA graph then waits for the epoch its own replay's signal kernel published.
   const int* ready_epoch_ptr;
+  // Gather of shards that the peers produce just before the launch (tensor-parallel activations): a gather warp
+  // waits for gather_src_ready[r] >= the ready epoch before copying part r (the own part needs no wait). With
+  // gather_wait_all the gathered matrix is the launch's A operand as one matrix (A[0] = gather_dst, a_parts = 1)
+  // and the tile producer waits for every part; the gather epoch is then the ready epoch too, so a launch captured
+  // in a CUDA graph (ready_epoch_ptr) publishes a fresh value on every replay.
+  const int* gather_src_ready;
+  int gather_wait_all;
 } RbGemmArgs;
 
 // Token and log-probability from the per-tile records written by the sampling epilogue.

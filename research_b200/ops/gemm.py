@@ -88,6 +88,8 @@ class RbGemmArgs(ctypes.Structure):
         ("gather_parts", ctypes.c_int),
         ("b_part_rot", ctypes.c_int),
         ("ready_epoch_ptr", ctypes.c_void_p),
+        ("gather_src_ready", ctypes.c_void_p),
+        ("gather_wait_all", ctypes.c_int),
     ]
 
 

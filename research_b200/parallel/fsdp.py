@@ -58,7 +58,12 @@ class FlatBuckets:
     peers, whose GEMM launches fetch the slabs when they need the matrix (``ShardedWeight``)."""
 
     def __init__(self, comm: PeerComm, named_shapes: list[tuple[str, tuple[int, ...]]], chunk_of=None,
-                 dtype: torch.dtype = torch.bfloat16, shard_rule=None):
+                 dtype: torch.dtype = torch.bfloat16, shard_rule=None, param_comm: PeerComm | None = None,
+                 with_grads: bool = True):
+        """``param_comm``: allocate the parameter storage in the symmetric memory of ANOTHER (larger) group, so that
+        ranks outside ``comm`` (inference engines on their own GPUs) can read it over NVLink; the members of ``comm``
+        must be that group's first ranks, in order. ``with_grads=False``: a layout-only instance on such an outside
+        rank (it takes part in the collective allocation and knows every offset, but holds no gradients)."""
         self.comm = comm
         W = comm.world
         align = 8 * W
@@ -103,9 +108,13 @@ class FlatBuckets:
         self.p_numel = p_off
         self.any_sharded = any(self.chunk_sharded)
         self.dtype = dtype
-        self.params_buf = comm.alloc((self.p_numel,), dtype, zero=True)
-        self.grads_buf = comm.alloc((self.numel,), dtype, zero=True)
-        self.params, self.grads = self.params_buf.local, self.grads_buf.local
+        self.params_buf = (param_comm or comm).alloc((self.p_numel,), dtype, zero=True)
+        self.params = self.params_buf.local
+        if with_grads:
+            self.grads_buf = comm.alloc((self.numel,), dtype, zero=True)
+            self.grads = self.grads_buf.local
+        else:
+            self.grads_buf = self.grads = None
         # Gradient windows: the kernels write a gradient view either over what is there (its first write of a
         # window) or on top of it (later micro-batches, tied weights), so the bucket is never zeroed as a whole.
         self.track_writes = False
@@ -134,7 +143,8 @@ class FlatBuckets:
         if t is not None:
             ev, slot, epoch = t
             torch.cuda.current_stream(self.params.device).wait_event(ev)
-            self.comm.wait(slot, epoch)
+            if slot >= 0:
+                self.comm.wait(slot, epoch)
 
     def finish_pending(self) -> None:
         for c in list(self._pending):
@@ -403,8 +413,11 @@ class ShardedAdamW:
                                     self.norm_slot, ep, comm.rank, comm.world, float(self.max_grad_norm), float(grad_scale),
                                     self.coef.data_ptr(), self.norm.data_ptr(), st, stream_handle(dev))
         check_rc(rc, "rb_clip_coef_ex")
-        deferred = self.update_stream is not None and comm.world > 1
+        deferred = self.update_stream is not None
         order = self.update_order if self.update_order is not None else list(range(len(b.chunks)))
+        # the clip kernel has consumed the partial sums: clear them on THIS stream, before anything of the next step
+        # (its reductions run on this stream or, ordered behind the event below, on the update stream) adds to them
+        self.partial.zero_()
         if deferred:
             ev = torch.cuda.Event()
             ev.record()
@@ -412,16 +425,15 @@ class ShardedAdamW:
             with torch.cuda.stream(self.update_stream):
                 for c in order:
                     self._update_chunk(c, b1, b2)
-                    epoch = comm.signal(self.param_slots[c])     # my slice of chunk c is everywhere / my slabs are final
+                    # several ranks: tell the peers that my slice of chunk c is everywhere / my slabs are final
+                    epoch = comm.signal(self.param_slots[c]) if comm.world > 1 else 0
                     done = torch.cuda.Event()
                     done.record()
-                    b._pending[c] = (done, self.param_slots[c], epoch)
-                self.partial.zero_()
+                    b._pending[c] = (done, self.param_slots[c] if comm.world > 1 else -1, epoch)
         else:
             for c in order:
                 self._update_chunk(c, b1, b2)
             comm.barrier()  # every rank's pushes landed; peers are done reading my gradients
-            self.partial.zero_()
         if self.zero_grads_after_step:
             b.grads.zero_()
         b.begin_window()

@@ -172,6 +172,19 @@ class PeerComm:
         return self.flags.local.data_ptr() + slot * self.world * 4
 
 
+class LayoutComm:
+    """Stand-in for a training group's ``PeerComm`` on a rank that is NOT in that group (an inference engine on its own
+    GPU): it only says how many training ranks there are, which is all a parameter layout depends on. Nothing can be
+    allocated or synchronised through it."""
+
+    def __init__(self, world: int, device: torch.device):
+        self.rank, self.world, self.device, self.group = 0, world, device, None
+        self.on_gpu = device.type == "cuda"
+
+    def alloc(self, *a, **kw):
+        raise RuntimeError("a layout-only communicator allocates nothing")
+
+
 class LocalComm(PeerComm):
     """Single-process, single-rank stand-in: the same kernels run with this GPU as its only peer."""
 

@@ -1,8 +1,9 @@
 """Tensor-parallel linear layers whose collective runs inside the tcgen05 GEMM kernel.
 
-* ``all_gather_gemm``  (column-parallel; activations sharded by rows across ranks): the GEMM's
-  TMA producer pulls the A tiles of remote row slabs straight from the peers' symmetric
-  buffers, tile by tile, while the tensor cores work on the previous tiles.
+* ``all_gather_gemm``  (column-parallel; activations sharded by rows across ranks): two gather
+  warps in every CTA of the GEMM launch copy the peers' row slabs from their symmetric buffers
+  into a local staging matrix (each remote row crosses NVLink once), the tile producers wait
+  for the parts and the tiles run over the staged matrix.
 * ``fsdp_gemm`` (FSDP parameter shards): same mechanism on the B operand - the weight rows a
   rank does not own are read from the owning peer inside the first GEMM that consumes them.
 * ``gemm_reduce_scatter`` / ``gemm_all_reduce`` (row-parallel): finished tiles are pushed with
@@ -43,6 +44,8 @@ class TensorParallel:
         self.max_cols = max_cols
         self._registry: dict[int, SymmBuffer] = {}
         self._call = 0
+        self._ag_epoch = 0
+        self.ag_stage = self.ag_flags = None
         self._ready_slot = comm.new_slot()
         if comm.on_gpu:
             rpr = self.max_rows // self.world
@@ -245,22 +248,41 @@ class TensorParallel:
             out.copy_(res.to(out.dtype))
             return out
         assert out.dtype == (torch.float32 if out_f32 else torch.bfloat16)
+        assert x_shard.is_contiguous() and rows * self.world <= self.max_rows and K <= self.max_cols
         buf = self.symm_of(x_shard)
+        # Every CTA of the launch copies a share of the peers' slabs into the local staging matrix with its two gather
+        # warps (each remote row crosses NVLink once, whatever the number of column tiles), the tile producers wait for
+        # the parts, and the tiles then run over the staged [M, K] matrix as one A operand.
+        if self.ag_stage is None:
+            self.ag_stage = torch.empty(self.max_rows * self.max_cols, dtype=torch.bfloat16, device=x_shard.device)
+            self.ag_flags = torch.zeros(4, 8, dtype=torch.int32, device=x_shard.device)   # count / ready: host epochs, device epochs
         args = self._base_args(rows * self.world, N, K, x_shard, w, 0)
         args.out_f32 = int(out_f32)
-        args.a_parts = self.world
-        for r in range(self.world):
-            args.A[r] = buf.peer_ptrs[r]
+        args.A[0] = self.ag_stage.data_ptr()
+        args.lda = K
         args.B[0] = w.data_ptr()
         args.C, args.ldc = out.data_ptr(), out.stride(0)
         args.bias = bias.data_ptr() if bias is not None else None
         args.epi_mode = EPI_STORE
-        if ready_epoch == "device":
-            args.a_ready = self.comm.flag_ptr(self._ready_slot)
+        args.world = 1                      # plain store epilogue; `rank` names this rank's part of the gather
+        for r in range(self.world):
+            args.gather_src[r] = buf.peer_ptrs[r]
+        args.gather_dst = self.ag_stage.data_ptr()
+        args.gather_part_bytes = rows * K * 2
+        args.gather_parts = self.world
+        args.gather_wait_all = 1
+        device_epoch = ready_epoch == "device"
+        flags = self.ag_flags[2:] if device_epoch else self.ag_flags[:2]
+        args.gather_count, args.gather_ready = flags[0].data_ptr(), flags[1].data_ptr()
+        if device_epoch:
+            args.gather_src_ready = self.comm.flag_ptr(self._ready_slot)
             args.ready_epoch_ptr = self.ready_counter.data_ptr()
-        elif ready_epoch is not None:
-            args.a_ready = self.comm.flag_ptr(self._ready_slot)
-            args.ready_epoch = ready_epoch
+        else:
+            self._ag_epoch += 1
+            args.gather_epoch = self._ag_epoch
+            if ready_epoch is not None:
+                args.gather_src_ready = self.comm.flag_ptr(self._ready_slot)
+                args.ready_epoch = ready_epoch
         self._launch(args, x_shard.device)
         return out
 

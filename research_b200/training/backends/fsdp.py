@@ -45,6 +45,7 @@ class FSDPTrainingBackend(NativeTrainingBackend):
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         comm = kw.pop("comm", None) or PeerComm(group, torch.device(device))
+        assert group is None or comm.group is group or comm.world == dist.get_world_size(group)
         kw.setdefault("activation_checkpointing", cfg.gradient_checkpointing)
         kw.setdefault("shard_params", cfg.sharding_strategy == "full_shard")
         super().__init__(model_config, weights, comm=comm, device=device, **kw)

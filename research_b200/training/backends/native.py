@@ -64,6 +64,27 @@ def _shardable(name: str, shape: tuple, world: int) -> bool:
 _VECTOR_CHUNK = 9_000     # sharded mode: the layers' vectors (norm weights, biases) live in one chunk of their own
 
 
+def build_buckets(model_config: ModelConfig, comm, dtype: torch.dtype, shard_params: bool = False, param_comm=None,
+                  with_grads: bool = True) -> FlatBuckets:
+    """The flat parameter / gradient layout of a model for ``comm.world`` training ranks. A rank outside the training
+    group (an inference engine on its own GPU) builds the SAME layout with a stand-in ``comm`` of the trainers' size and
+    ``with_grads=False``: it then knows where every parameter lies in the trainers' storage (``param_comm``: the
+    symmetric memory both sides share)."""
+    all_shapes = param_shapes(model_config)
+    chunk_of, rule = _chunk_of, None
+    if shard_params and comm.world > 1:
+        W = comm.world
+
+        def rule(name, shape):
+            return _shardable(name, shape, W)
+
+        def chunk_of(name):      # a layer's chunk keeps its sharded matrices only
+            return _chunk_of(name) if (not name.startswith("model.layers.") or rule(name, tuple(all_shapes[name]))) else _VECTOR_CHUNK
+
+    shapes = sorted(all_shapes.items(), key=lambda kv: _order_key(kv[0], chunk_of))
+    return FlatBuckets(comm, shapes, chunk_of, dtype=dtype, shard_rule=rule, param_comm=param_comm, with_grads=with_grads)
+
+
 class NativeTrainingBackend:
     def __init__(self, model_config: ModelConfig, weights: dict[str, torch.Tensor] | None = None, *,
                  comm: PeerComm | None = None, device: torch.device | str | None = None,
@@ -71,7 +92,8 @@ class NativeTrainingBackend:
                  betas: tuple[float, float] = (0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.0,
                  trainer_config: TrainerConfig | None = None, lr_schedule: Callable[[int], float] | None = None,
                  checkpoint_dir: str | Path | None = None, activation_checkpointing: bool = False,
-                 need_entropy: bool | None = None, seed: int = 0, overlap_comm: bool = True, shard_params: bool = False):
+                 need_entropy: bool | None = None, seed: int = 0, overlap_comm: bool = True, shard_params: bool = False,
+                 param_comm: PeerComm | None = None):
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda" if torch.cuda.is_available() else "cpu")
         self.comm = comm if comm is not None else LocalComm(self.device)
@@ -80,20 +102,8 @@ class NativeTrainingBackend:
         self.config = trainer_config or TrainerConfig()
         on_gpu = self.device.type == "cuda"
         dtype = torch.bfloat16 if on_gpu else torch.float32
-        all_shapes = param_shapes(model_config)
         self.shard_params = bool(shard_params) and self.world > 1
-        chunk_of, rule = _chunk_of, None
-        if self.shard_params:
-            W = self.world
-
-            def rule(name, shape):
-                return _shardable(name, shape, W)
-
-            def chunk_of(name):      # a layer's chunk keeps its sharded matrices only
-                return _chunk_of(name) if (not name.startswith("model.layers.") or rule(name, tuple(all_shapes[name]))) else _VECTOR_CHUNK
-
-        shapes = sorted(all_shapes.items(), key=lambda kv: _order_key(kv[0], chunk_of))
-        self.buckets = FlatBuckets(self.comm, shapes, chunk_of, dtype=dtype, shard_rule=rule)
+        self.buckets = build_buckets(model_config, self.comm, dtype, self.shard_params, param_comm)
         if weights is None and on_gpu:
             # random init written straight into the bucket (an 8B model never exists twice in memory)
             # whole tensors: the same seed on every rank gives every rank the same values; row slabs: seeded per rank
@@ -127,12 +137,15 @@ class NativeTrainingBackend:
         # Reduce-scatter of a layer's gradients as soon as backward has left the layer, on a second stream
         # (what FSDP2's backward hooks do in the reference, rollouts/training/backends/fsdp.py:289-322).
         self.overlap_comm = bool(overlap_comm) and on_gpu and self.world > 1
-        self._side = torch.cuda.Stream(self.device) if self.overlap_comm else None
+        self._side = torch.cuda.Stream(self.device) if (bool(overlap_comm) and on_gpu) else None
         self._pass_reduced: set[int] = set()
         if self.overlap_comm:
             self.optimizer.overlap_grid = 64
-            # AdamW + parameter all-gather of a step run on the second stream too, chunk by chunk in the order the next
-            # forward pass needs them (embedding, the layers' vectors, the layers, the head)
+        if self._side is not None:
+            # AdamW (+ the parameter all-gather) of a step runs on the second stream, chunk by chunk in the order the
+            # next forward pass needs the chunks (embedding, the layers' vectors, the layers, the head); the forward
+            # waits chunk by chunk. On one GPU this hides the memory-bound update (30 bytes per parameter) under the
+            # compute-bound first layers of the next step; on several it also hides the NVLink-bound pushes.
             self.optimizer.update_stream = self._side
             ids = {n: sp.chunk for n, sp in self.buckets.specs.items()}
             first = [ids[n] for n in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight") if n in ids]

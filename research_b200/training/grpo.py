@@ -125,11 +125,26 @@ def grpo_train(config: GRPOConfig, prompts: list[Any], score_fn: Callable[[Sampl
                                          ground_truths, filter_fn))
 
 
+def device_roles(config: GRPOConfig, world: int) -> tuple[list[int], list[int]] | None:
+    """Ranks that train and ranks that serve when ``trainer_cuda_device_ids`` and ``inference_cuda_device_ids`` name
+    DISJOINT device sets that together make up the job (rollouts/training/grpo.py:55,59,172-199 places the SGLang
+    engine and the trainer on different device tuples): the first ``len(trainer ids)`` ranks train, the rest serve,
+    and rank ``r`` runs on device ``(trainer ids + inference ids)[r]``. None = every rank does both (same devices)."""
+    t, e = tuple(config.trainer_cuda_device_ids), tuple(config.inference_cuda_device_ids)
+    if set(t) & set(e) or len(t) + len(e) != world or not t or not e:
+        return None
+    return list(range(len(t))), list(range(len(t), len(t) + len(e)))
+
+
 async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_logger, device, tokenizer,
                             ground_truths, filter_fn) -> list[dict[str, float]]:
     distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
     rank = dist.get_rank() if distributed else 0
     world = dist.get_world_size() if distributed else 1
+    roles = device_roles(config, world) if distributed else None
+    if roles is not None:
+        return await _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls, metrics_logger, device, tokenizer,
+                                          ground_truths, filter_fn)
     dev = torch.device(device) if device is not None else torch.device(
         f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu")
     out_dir = _setup_output_dir(config)
@@ -210,4 +225,144 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
         if logger is not None:
             logger.finish()
         engine.shutdown()
+    return history
+
+
+async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls, metrics_logger, device, tokenizer,
+                               ground_truths, filter_fn) -> list[dict[str, float]]:
+    """GRPO with the trainers and the engines on different GPUs of one node.
+
+    Per step: the engine ranks generate and score their share of the prompt groups; the samples travel to the
+    trainer ranks (one object all-gather); the trainers split the GROUPS among themselves, run the sharded
+    forward/backward + optimizer step; then every engine pulls the new parameters out of a trainer's flat bucket
+    over NVLink with one ``reshard_copy`` launch that writes its own packed layout (the bucket lives in symmetric
+    memory allocated over ALL ranks, so the engines hold a mapping of it; host barriers fence the copy on both
+    sides). On CPU groups the parameters travel with a broadcast instead."""
+    from ..parallel.symm import LayoutComm, PeerComm
+    from .backends.native import build_buckets
+    from .rollout_gen.rollout_generation import convert_to_batch
+
+    trainer_ranks, engine_ranks = roles
+    rank, world = dist.get_rank(), dist.get_world_size()
+    T, E = len(trainer_ranks), len(engine_ranks)
+    is_trainer = rank in trainer_ranks
+    ids = tuple(config.trainer_cuda_device_ids) + tuple(config.inference_cuda_device_ids)
+    if device is not None:
+        dev = torch.device(device)
+    elif torch.cuda.is_available():
+        dev = torch.device("cuda", ids[rank])
+        torch.cuda.set_device(dev)
+    else:
+        dev = torch.device("cpu")
+    out_dir = _setup_output_dir(config)
+    if rank == 0:
+        config.save(out_dir / "config.json")
+    logger = metrics_logger or (JSONLLogger(out_dir) if rank == 0 else None)
+    tgroup = dist.new_group(trainer_ranks)         # every rank creates both groups, in the same order
+    egroup = dist.new_group(engine_ranks)
+    _ = egroup
+    world_comm = PeerComm(dist.group.WORLD, dev)
+    weights, model_cfg = load_model_weights(config.checkpoint_path or config.model_name, config.seed)
+    on_gpu = dev.type == "cuda"
+    dtype = torch.bfloat16 if on_gpu else torch.float32
+    backend = engine = manager = None
+    if is_trainer:
+        tcfg = TrainerConfig(num_minibatches=config.num_minibatches, max_grad_norm=config.max_grad_norm)
+        backend = FSDPTrainingBackend(model_cfg, weights, comm=PeerComm(tgroup, dev), device=dev, param_comm=world_comm,
+                                      loss_fn=config.loss, lr=config.lr, weight_decay=config.weight_decay, trainer_config=tcfg,
+                                      checkpoint_dir=out_dir / "checkpoints")
+        buckets = backend.buckets
+    else:
+        buckets = build_buckets(model_cfg, LayoutComm(T, dev), dtype, False, param_comm=world_comm, with_grads=False)
+        ei = engine_ranks.index(rank)
+        ecfg = EngineConfig(cache_type=config.cache_type, max_batch_size=config.max_batch_size,
+                            max_model_len=max(config.max_seq_len + config.max_tokens, 64), num_kv_blocks=config.kv_blocks,
+                            seed=config.seed * 1009 + ei, ignore_eos=tokenizer is None)
+        engine = InferenceEngine(ecfg, model_cfg, weights, tokenizer=tokenizer, device=dev)
+        mine = prompts[ei::E]
+        truths = ground_truths[ei::E] if ground_truths else None
+        gen_fn = _create_tito_generate_fn(engine, config, tokenizer)
+        if environment_cls is not None and not config.use_tito:
+            from .agent_integration import make_agent_generate_fn
+
+            gen_fn = make_agent_generate_fn(engine, environment_cls, config, tokenizer)
+        manager = AsyncRolloutManager(DataBuffer(mine, seed=config.seed, ground_truths=truths),
+                                      RolloutConfig(batch_size=max(config.batch_size // E, 1), n_samples_per_prompt=config.n_samples_per_prompt,
+                                                    generate_fn=gen_fn, score_fn=score_fn, filter_fn=filter_fn))
+    del weights
+    dist.barrier()
+    plan = None
+    history: list[dict[str, float]] = []
+    rollouts_file = open(out_dir / f"rollouts.rank{rank}.jsonl", "a") if not is_trainer else None
+    try:
+        for step in range(config.num_steps):
+            t0 = time.perf_counter()
+            mine_out: list[dict] = []
+            if not is_trainer:
+                batch = await manager.generate_batch()
+                ei = engine_ranks.index(rank)
+                for s in batch.samples:
+                    s.group_index = (s.group_index or 0) * E + ei          # group ids stay distinct across engines
+                    rollouts_file.write(json.dumps({"step": step, "reward": s.reward, "tokens": len(s.tokens),
+                                                    "response_length": s.response_length, "group": s.group_index,
+                                                    "weight_version": s.weight_version}) + "\n")
+                    mine_out.append(s.to_dict())
+            t_roll = time.perf_counter() - t0
+            gathered: list = [None] * world
+            dist.all_gather_object(gathered, mine_out)
+            samples = [Sample.from_dict(d) for part in gathered for d in (part or [])]
+            m: dict[str, float] = {"rollout_s": t_roll, "num_samples": float(len(samples)),
+                                   "mean_reward": sum(s.reward for s in samples) / max(len(samples), 1)}
+            t1 = time.perf_counter()
+            if is_trainer:
+                ti = trainer_ranks.index(rank)
+                groups = sorted({s.group_index for s in samples})
+                my_groups = set(groups[ti::T])                                # whole groups per trainer
+                part = [s for s in samples if s.group_index in my_groups]
+                tb_batch = convert_to_batch(part)
+                adv = compute_group_advantages(tb_batch.rewards, tb_batch.group_indices, config.normalize_advantage_std)
+                tb = _prepare_training_batch(tb_batch, adv, config.max_seq_len)
+                n = tb["input_ids"].shape[0]
+                if n % config.num_minibatches != 0:
+                    keep = max(config.num_minibatches, n - n % config.num_minibatches)
+                    tb = {k: (v[:keep] if isinstance(v, torch.Tensor) and v.shape[0] == n else v) for k, v in tb.items()}
+                fb = await backend.forward_backward(tb).result()
+                opt = await backend.optim_step().result()
+                m.update(fb)
+                m.update(opt)
+                backend.buckets.finish_pending()
+                if on_gpu:
+                    torch.cuda.synchronize(dev)
+            m["train_s"] = time.perf_counter() - t1
+            t2 = time.perf_counter()
+            if (step + 1) % config.sync_weights_every == 0:
+                dist.barrier()                                                  # the trainers' parameters are final
+                if on_gpu:
+                    if not is_trainer:
+                        src = trainer_ranks[engine_ranks.index(rank) % T]
+                        plan = sync_engine_from_buckets(engine, buckets, plan, src_rank=src)
+                        torch.cuda.synchronize(dev)
+                else:
+                    flat = buckets.params
+                    dist.broadcast(flat, src=trainer_ranks[0])
+                    if not is_trainer:
+                        sync_engine_from_buckets(engine, buckets)
+                dist.barrier()                                                  # the engines have read them
+                if not is_trainer:
+                    engine.weight_version = step + 1
+            m["sync_s"] = time.perf_counter() - t2
+            m["step_s"] = time.perf_counter() - t0
+            m["weight_version"] = float(step + 1)
+            history.append(m)
+            if logger is not None and step % config.log_every == 0:
+                logger.log({k: v for k, v in m.items() if isinstance(v, (int, float))}, step)
+            if is_trainer and config.checkpoint_every and (step + 1) % config.checkpoint_every == 0:
+                backend.save_checkpoint(step + 1, {k: v for k, v in m.items() if isinstance(v, float)})
+    finally:
+        if rollouts_file is not None:
+            rollouts_file.close()
+        if logger is not None:
+            logger.finish()
+        if engine is not None:
+            engine.shutdown()
     return history

@@ -155,21 +155,25 @@ def case_weight_sync_and_tp_engine(comm, dev, dt):
     tcfg = EngineConfig(max_batch_size=16, max_model_len=256, num_kv_blocks=128, ignore_eos=True, graph_batch_sizes=(16,))
     eng = InferenceEngine(tcfg, cfg, w0, device=dev, tp=tp)
     got = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
-    # criterion of the reference's correctness harness: exact greedy match, else every chosen token
-    # must be a near-top token of the fp32 oracle and the reported log-prob must agree with it
+    # Criterion of the reference's correctness harness: exact greedy match, else every chosen token must be a near-top
+    # token of the fp32 oracle and the reported log-prob must agree with it. Expected bf16 error: activations carry 8
+    # mantissa bits (relative rounding 2^-9), logits of magnitude 5-10 come out of two layers and a 256-wide product with
+    # an absolute error of 0.01-0.04, and the tensor-parallel engine sums its partial products in a different order than
+    # one GPU does. So two tokens closer than about 0.1 nats may swap (margin 0.15 = three times the typical error) and a
+    # reported log-prob may be off by the same amount (0.05); a wrong shard, mask or position shows as errors of 0.5 and up.
     from research_b200.models import causal_lm_forward
 
     w32 = {k: v.float().cpu() for k, v in w0.items()}
     for p_, x, y in zip(prompts, got, want):
         if x.completion_tokens == y.completion_tokens:
-            assert max(abs(a_ - b_) for a_, b_ in zip(x.logprobs, y.logprobs)) < 0.06
+            assert max(abs(a_ - b_) for a_, b_ in zip(x.logprobs, y.logprobs)) < 0.05
             continue
         ids = list(p_) + list(x.completion_tokens)
         lps = torch.log_softmax(causal_lm_forward(torch.tensor([ids]), w32, cfg)[0].float(), -1)
         for j, (tok, lp) in enumerate(zip(x.completion_tokens, x.logprobs)):
             row = lps[len(p_) + j - 1]
-            assert row[tok].item() >= row.max().item() - 0.3, ("not a near-top token", j)
-            assert abs(row[tok].item() - lp) < 0.08, ("log-prob mismatch", j, row[tok].item(), lp)
+            assert row[tok].item() >= row.max().item() - 0.15, ("not a near-top token", j, row[tok].item(), row.max().item())
+            assert abs(row[tok].item() - lp) < 0.05, ("log-prob mismatch", j, row[tok].item(), lp)
     eng.shutdown()
     _ = W
 
@@ -263,6 +267,35 @@ def case_fsdp_full_shard(comm, dev, dt):
         close(pb[n], pa[n], tol, tol, f"full_shard vs replicated {n}")
 
 
+def case_grpo_disjoint(comm, dev, dt):
+    """Trainers and engine on different ranks: the last rank only serves, the others only train; samples travel to the
+    trainers, the new parameters travel back into the engine's packed layout."""
+    import tempfile
+
+    from research_b200.training.grpo import GRPOConfig, device_roles, grpo_train
+
+    W = comm.world
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 4096, (int(n),), generator=g).tolist() for n in torch.randint(16, 48, (12,), generator=g)]
+    with tempfile.TemporaryDirectory() as d:
+        os.environ["ROLLOUTS_RUN_NAME"] = "disjoint_run"
+        gcfg = GRPOConfig(model_name="tiny-qwen2", lr=1e-4, batch_size=4, n_samples_per_prompt=4, num_minibatches=2, max_tokens=6,
+                          max_seq_len=96, temperature=1.0, num_steps=2, output_dir=d, checkpoint_every=0, max_batch_size=16,
+                          kv_blocks=128, trainer_cuda_device_ids=tuple(range(W - 1)), inference_cuda_device_ids=(W - 1,))
+        assert device_roles(gcfg, W) == (list(range(W - 1)), [W - 1])
+        assert device_roles(GRPOConfig(), W) is None
+        hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=dev)
+        assert len(hist) == 2 and hist[-1]["weight_version"] == 2.0 and hist[0]["num_samples"] == 16.0
+        if comm.rank < W - 1:
+            assert "loss" in hist[-1] or "pg_loss" in hist[-1], hist[-1]
+        # every rank saw the same samples and the same reward statistics
+        t = torch.tensor([hist[-1]["mean_reward"]], dtype=torch.float64, device=dev)
+        ref = t.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(t, ref)
+        dist.barrier()
+
+
 def case_moe_expert_parallel(comm, dev, dt):
     """Each rank routes its own tokens; experts are split over the ranks; dispatch and combine
     travel through peer memory. Checked against the single-process functional MoE."""
@@ -293,7 +326,7 @@ def _bcast_buckets(b, comm):
 
 CASES = {"barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
          "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo,
-         "fsdp_full_shard": case_fsdp_full_shard,
+         "fsdp_full_shard": case_fsdp_full_shard, "grpo_disjoint": case_grpo_disjoint,
          "moe_ep": case_moe_expert_parallel}
 
 

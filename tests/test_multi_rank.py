@@ -25,18 +25,24 @@ def _run(device: str, nproc: int, cases: str, timeout: int = 600) -> str:
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(HERE, "multi_rank_worker.py"), device, cases]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    for _ in range(2):
+        # the port picked above was free when probed; another process may have taken it since: pick again
+        if proc.returncode == 0 or "EADDRINUSE" not in proc.stderr:
+            break
+        cmd[cmd.index("--master-port") + 1] = str(_free_port())
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-4000:]
     return proc.stdout
 
 
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "moe_ep"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "grpo_disjoint", "moe_ep"])
 def test_gloo_two_ranks(cases):
     out = _run("cpu", 2, cases)
     for c in cases.split(","):
         assert f"CASE_OK {c}" in out
 
 
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "fsdp_full_shard", "moe_ep"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "fsdp_full_shard", "grpo_disjoint", "moe_ep"])
 def test_gloo_four_ranks(cases):
     """The host-side logic (slab rotation, shard ranges, count matrices, dispatch offsets) at world size 4."""
     out = _run("cpu", 4, cases)
@@ -45,7 +51,7 @@ def test_gloo_four_ranks(cases):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "moe_ep"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "grpo_disjoint", "moe_ep"])
 def test_gpu_ranks(cases):
     import torch
 
