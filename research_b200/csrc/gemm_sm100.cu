@@ -103,6 +103,7 @@ struct GemmParams {
   long long stage_parity_bytes, flag_parity_bytes;
   const int4* tile_table;
   const int* num_tiles_ptr;
+  int group_k;            // grouped weight gradient: tiles carry their own K range and output group (see RbGemmArgs::group_mode)
   const unsigned long long* row_dst;
   int swiglu;
   int split_k, kb_per_split;
@@ -228,6 +229,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   const int num_m_tiles = m_tiles_per_part * p.a_parts;
   const int num_n_tiles = n_tiles_per_part * p.b_parts;
   const bool grouped = p.tile_table != nullptr;
+  const bool grp = grouped && !p.group_k;   // tiles address rows of A directly (forward and data-gradient forms)
   if (grouped) pdl_wait();  // the tile count itself is produced by the previous kernel
   const int split_k = p.split_k;
   const int num_tiles = (grouped ? *p.num_tiles_ptr : num_m_tiles * num_n_tiles) * split_k;  // work units
@@ -276,10 +278,18 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
   // own slab last so that every owner finds its partials early.
   // grouped tiles: m_in = first A row, n_part = first B row, n_in = first output column,
   // m_part carries the number of valid rows
-  auto tile_coords = [&](int t, int& m_part, int& m_in, int& n_part, int& n_in) {
+  // kb_lo / kb_hi: the k-blocks of the work unit (a split-K slice, or a group's row range in the grouped weight gradient)
+  auto tile_coords = [&](int t, int& m_part, int& m_in, int& n_part, int& n_in, int& kb_lo, int& kb_hi) {
+    kb_lo = (t % split_k) * p.kb_per_split;
+    kb_hi = split_k > 1 ? min(num_kb, kb_lo + p.kb_per_split) : num_kb;
     t /= split_k;
     if (grouped) {
       const int4 e = p.tile_table[t];
+      if (p.group_k) {
+        kb_lo = e.x / BK; kb_hi = kb_lo + e.y / BK;
+        m_part = e.z; m_in = (e.w >> 16) * BM; n_part = 0; n_in = (e.w & 0xffff) * BN;
+        return;
+      }
       m_in = e.x; m_part = e.y; n_part = e.z; n_in = e.w;
       return;
     }
@@ -316,8 +326,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         asm volatile("fence.proxy.async.global;" ::: "memory");
       }
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m_part, m_in, n_part, n_in;
-        tile_coords(t, m_part, m_in, n_part, n_in);
+        int m_part, m_in, n_part, n_in, kb0, kb1;
+        tile_coords(t, m_part, m_in, n_part, n_in, kb0, kb1);
         if (!grouped && p.a_ready != nullptr && !((a_seen >> m_part) & 1u)) {
           ok = wait_flag_ge(p.a_ready + m_part, ready_epoch, p.status);
           if (!ok) { *abortp = 1; break; }
@@ -333,9 +343,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         }
         const CUtensorMap* amap = &p.a_map[grouped ? 0 : m_part];
         const CUtensorMap* bmap = &p.b_map[grouped ? 0 : n_part];
-        const int b_row = grouped ? n_part : n_in;   // first B row of the tile
-        const int kb0 = (t % split_k) * p.kb_per_split;
-        const int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
+        const int b_row = (grp && !B_MN) ? n_part : n_in;   // first B row (K-major) or column (MN-major) of the tile
+        const int b_k0 = (grp && B_MN) ? n_part : 0;        // grouped data gradient: the group's first row of the stacked B
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           // ring slot and phase advance incrementally: the depth is a run-time value, and a division per k-block sat
           // on the single-thread critical path of this role
@@ -359,7 +368,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
             tma_load_2d(sb, bmap, fb, kb * BK, b_row);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), bmap, fb, b_row + c * 64, kb * BK);
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (BK * 128), bmap, fb, b_row + c * 64, b_k0 + kb * BK);
           }
         }
       }
@@ -393,8 +402,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        const int kb0 = (t % split_k) * p.kb_per_split;
-        const int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
+        int kb0 = (t % split_k) * p.kb_per_split;
+        int kb1 = split_k > 1 ? min(num_kb, kb0 + p.kb_per_split) : num_kb;
+        if (p.group_k) {
+          const int4 e = p.tile_table[t];
+          kb0 = e.x / BK; kb1 = kb0 + e.y / BK;
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           // ring slot and phase advance incrementally: the depth is a run-time value, and a division per k-block sat
           // on the single-thread critical path of this role
@@ -542,8 +555,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
     };
     const int rows_per_rank = p.a_rows_per_part;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_iter) {
-      int m_part, m_in, n_part, n_in;
-      tile_coords(t, m_part, m_in, n_part, n_in);
+      int m_part, m_in, n_part, n_in, kb_lo_, kb_hi_;
+      tile_coords(t, m_part, m_in, n_part, n_in, kb_lo_, kb_hi_);
       const int acc = tile_iter % NUM_ACC;
       const uint32_t acc_ph = (tile_iter / NUM_ACC) & 1u;
       ok = mbar_wait_bounded(smem_u32(&tmem_full_bar[acc]), acc_ph, abortp, p.status,
@@ -558,9 +571,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
         rscale = rs_smem[acc][q * 32 + lane];
       }
       const int row_in = m_in + q * 32 + lane;                 // row inside the A slab
-      const bool row_ok = grouped ? (q * 32 + lane < m_part) : (row_in < p.a_rows_per_part);
-      const long long row = grouped ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
-      const int n_base = grouped ? n_in : n_part * p.b_rows_per_part + n_in;    // global column
+      const bool row_ok = grp ? (q * 32 + lane < m_part) : (row_in < p.a_rows_per_part);
+      const long long row = grp ? (long long)row_in : (long long)m_part * p.a_rows_per_part + row_in;
+      const int n_base = grp ? n_in : n_part * p.b_rows_per_part + n_in;    // global column
       const int n_valid = min(BN, p.b_rows_per_part - n_in);   // columns valid in this tile
       if (p.cluster_k) {
         // ---- cluster split-K: the split_k CTAs of a cluster each hold the fp32 partial tile of one K slice.
@@ -882,7 +895,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       if (p.epi_mode != RB_EPI_STORE) {
         // rows of this warp: q*32 .. q*32+31 of the tile; each row holds n_valid columns
         const int units_per_row = n_valid >> 3;                      // 16-byte units
-        const int rows_here = min(32, (grouped ? m_part : p.a_rows_per_part - m_in) - q * 32);
+        const int rows_here = min(32, (grp ? m_part : p.a_rows_per_part - m_in) - q * 32);
         const int n_dst = p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? p.world : 1;
         for (int u = lane; u < rows_here * units_per_row; u += 32) {
           const int rr = u / units_per_row, cu = u - rr * units_per_row;
@@ -934,8 +947,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmParams p) {
       if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT) {
         // every rank holds all partials of every tile: sum the tiles this CTA computed, store locally
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-          int m_part, m_in, n_part, n_in;
-          tile_coords(t, m_part, m_in, n_part, n_in);
+          int m_part, m_in, n_part, n_in, kb_lo_, kb_hi_;
+          tile_coords(t, m_part, m_in, n_part, n_in, kb_lo_, kb_hi_);
           const int tile_idx = (m_in / BM) * num_n_tiles + (n_part * n_tiles_per_part + n_in / BN);
           if (et < p.world) {
             if (!wait_flag_ge(flags + (long long)et * tiles_owned + tile_idx, reduce_epoch, p.status)) *abortp = 1;
@@ -1355,8 +1368,17 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   }
   if (p.tile_table != nullptr) {
     if (p.num_tiles_ptr == nullptr || a->group_n <= 0 || a->group_n % 8 != 0 || a->a_parts != 1 || a->b_parts != 1 ||
-        a->a_mn_major || a->b_mn_major || a->bn == 0 || p.epi_mode != RB_EPI_STORE)
+        a->bn == 0 || p.epi_mode != RB_EPI_STORE)
       return -1;
+    const int gm = a->group_mode;
+    if (gm == 0 ? (a->a_mn_major || a->b_mn_major)
+        : gm == 1 ? (a->a_mn_major || !a->b_mn_major || a->group_b_rows <= 0 || a->K % BK != 0 || a->row_dst || a->swiglu)
+        : gm == 2 ? (!a->a_mn_major || !a->b_mn_major || a->K % BK != 0 || a->row_dst || a->swiglu || a->bn < 64)
+                  : true)
+      return -1;
+    p.group_k = gm == 2;
+  } else if (a->group_mode != 0) {
+    return -1;
   }
   if (p.epi_mode != RB_EPI_STORE) {
     if (p.epi_mode == RB_EPI_ALL_REDUCE_ONESHOT ? (a->a_parts != 1 || a->b_parts != 1) : (a->a_parts != p.world)) return -1;
@@ -1388,7 +1410,7 @@ extern "C" int rb_gemm_bf16_ex(const RbGemmArgs* a, cudaStream_t stream) {
   }
   for (int i = 0; i < p.b_parts; ++i) {
     int rc = a->b_mn_major
-                 ? make_map_2d(&p.b_map[i], a->B[i], a->K, total_b_rows, a->ldb, BK)
+                 ? make_map_2d(&p.b_map[i], a->B[i], a->group_mode == 1 ? a->group_b_rows : a->K, total_b_rows, a->ldb, BK)
                  : make_map_2d(&p.b_map[i], a->B[i], total_b_rows, a->K, a->ldb, bn);
     if (rc != 0) return -30 + rc;
   }

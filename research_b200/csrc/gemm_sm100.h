@@ -124,6 +124,14 @@ typedef struct RbGemmArgs {
   // in a CUDA graph (ready_epoch_ptr) publishes a fresh value on every replay.
   const int* gather_src_ready;
   int gather_wait_all;
+  // Grouped mode for the backward pass of a mixture of experts (tile_table set). 0: the forward form above.
+  // 1 (data gradient): B is MN-major, the groups' [group K, N] matrices stacked along its rows (group_b_rows rows in
+  // all); table entries are {a_row0, valid_rows, first B row of the group, n0} and K is the K extent of one group.
+  // 2 (weight gradient): A [rows, M] and B [rows, N] are both MN-major and the contraction runs over a group's row
+  // range; table entries are {first row, row count (a multiple of 64), group, (m tile << 16) | n tile}, the output of
+  // group g is C rows [g * M, (g + 1) * M), and K is the total row count of A and B.
+  int group_mode;
+  int group_b_rows;
 } RbGemmArgs;
 
 // Token and log-probability from the per-tile records written by the sampling epilogue.

@@ -334,6 +334,193 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const fl
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// Training: expert-grouped rows with every group padded to a multiple of 64 rows (zero rows), so that the weight
+// gradient dW_e = dY_e^T X_e can run as one grouped launch whose K range is the group's row range: a 64-row k-block
+// never straddles two experts. Everything is derived from the per-expert counts on the device (no host sync), and
+// the row order inside an expert is the token order, so results do not depend on scheduling.
+
+struct TrainTableDesc {
+  int mode;        // 0 forward {a_row0, valid_rows, e * b_stride + n0, n0}; 1 data gradient {a_row0, valid_rows, e * b_stride, n0};
+                   // 2 weight gradient {row0, rows, e, (m tile << 16) | n tile}
+  int n_total;     // output columns per expert
+  int bn;          // tile width
+  int b_stride;    // rows of the stacked B matrix per expert (modes 0, 1); output rows per expert M (mode 2)
+  int4* tiles;
+  int* ntiles;
+};
+constexpr int MAX_TRAIN_TABLES = 6;
+struct TrainTables { TrainTableDesc t[MAX_TRAIN_TABLES]; int n; };
+
+// One CTA. offsets[e] = first row of expert e, offsets[E] = rows in use (all multiples of 64; an expert without tokens
+// still gets 64 zero rows, which keeps its weight gradient an ordinary tile whose product is zero).
+__global__ void moe_train_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, TrainTables tabs,
+                                      int max_tiles, int cap_rows, int* __restrict__ status) {
+  __shared__ int off_s[257];
+  __shared__ int base_s[257];
+  if (threadIdx.x == 0) {
+    int o = 0;
+    for (int e = 0; e < E; ++e) {
+      off_s[e] = o;
+      const int c = counts[e];
+      o += c > 0 ? ((c + 63) / 64) * 64 : 64;
+    }
+    off_s[E] = o;
+    if (o > cap_rows && status != nullptr) set_status(status, ST_BAD_INDEX);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off_s[e];
+  for (int ti = 0; ti < tabs.n; ++ti) {
+    const TrainTableDesc d = tabs.t[ti];
+    const int nt = (d.n_total + d.bn - 1) / d.bn;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int b = 0;
+      for (int e = 0; e < E; ++e) {
+        base_s[e] = b;
+        const int rows = off_s[e + 1] - off_s[e];
+        b += (d.mode == 2 ? (d.b_stride + 127) / 128 : (rows + 127) / 128) * nt;
+      }
+      base_s[E] = b;
+      if (b > max_tiles) {
+        if (status != nullptr) set_status(status, ST_BAD_INDEX);
+        base_s[E] = 0;
+      }
+      *d.ntiles = base_s[E];
+    }
+    __syncthreads();
+    if (base_s[E] == 0) continue;
+    for (int e = 0; e < E; ++e) {
+      const int rows = off_s[e + 1] - off_s[e];
+      const int mt = d.mode == 2 ? (d.b_stride + 127) / 128 : (rows + 127) / 128;
+      const int n = mt * nt;
+      for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        // consecutive tiles share the B tile (modes 0, 1) or the A tile's k range (mode 2)
+        const int in = j / mt, im = j % mt;
+        int4 v;
+        if (d.mode == 2) {
+          v = make_int4(off_s[e], rows, e, (im << 16) | in);
+        } else {
+          const int r0 = off_s[e] + im * 128;
+          v = make_int4(r0, min(128, off_s[e + 1] - r0), d.mode == 0 ? e * d.b_stride + in * d.bn : e * d.b_stride, in * d.bn);
+        }
+        d.tiles[base_s[e] + j] = v;
+      }
+    }
+  }
+}
+
+// One CTA per expert: walk the (token, slot) pairs in order and hand out the expert's rows in that order.
+// row_of[i] = row of pair i; src_of[row] = pair of a row, -1 for the padding rows.
+__global__ void moe_train_rows_kernel(const int* __restrict__ topk_idx, int n_pairs, const int* __restrict__ offsets,
+                                      int* __restrict__ row_of, int* __restrict__ src_of) {
+  const int e = blockIdx.x;
+  const int row0 = offsets[e], row_end = offsets[e + 1];
+  __shared__ int warp_sum[32];
+  __shared__ int running;
+  if (threadIdx.x == 0) running = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int i0 = 0; i0 < n_pairs; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    const bool hit = i < n_pairs && topk_idx[i] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_sum[warp] = __popc(m);
+    __syncthreads();
+    int before = running;
+    for (int w = 0; w < warp; ++w) before += warp_sum[w];
+    if (hit) {
+      const int row = row0 + before + __popc(m & ((1u << lane) - 1u));
+      row_of[i] = row;
+      src_of[row] = i;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < nwarp; ++w) tot += warp_sum[w];
+      running += tot;
+    }
+    __syncthreads();
+  }
+  for (int r = row0 + running + threadIdx.x; r < row_end; r += blockDim.x) src_of[r] = -1;
+}
+
+// out[row] = scale(row) * src[src_of[row] / k] for the rows in use (zeros for padding rows); scale = w[src_of[row]] or 1.
+__global__ void moe_train_gather_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ w,
+                                        const int* __restrict__ src_of, const int* __restrict__ total_rows, int k, int d,
+                                        __nv_bfloat16* __restrict__ out) {
+  const int vpr = d >> 3;
+  const long long nvec = (long long)(*total_rows) * vpr;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    const int s = src_of[row];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (s >= 0) {
+      v = *reinterpret_cast<const uint4*>(src + (long long)(s / k) * d + c);
+      if (w != nullptr) {
+        const float ws = w[s];
+        float2 f;
+        f = unpack_bf16x2(v.x); v.x = pack_bf16x2(ws * f.x, ws * f.y);
+        f = unpack_bf16x2(v.y); v.y = pack_bf16x2(ws * f.x, ws * f.y);
+        f = unpack_bf16x2(v.z); v.z = pack_bf16x2(ws * f.x, ws * f.y);
+        f = unpack_bf16x2(v.w); v.w = pack_bf16x2(ws * f.x, ws * f.y);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + row * d + c) = v;
+  }
+}
+
+// out[t] = sum_j (w ? w[t,j] : 1) * y[row_of[t*k+j]] (fp32 accumulation in slot order)
+__global__ void moe_train_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
+                                         const int* __restrict__ row_of, int T, int k, int d, __nv_bfloat16* __restrict__ out) {
+  const int vpr = d >> 3;
+  const long long nvec = (long long)T * vpr;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vpr;
+    const int c = (int)(i % vpr) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < k; ++j) {
+      const float wj = w != nullptr ? w[t * k + j] : 1.f;
+      const uint4 v = *reinterpret_cast<const uint4*>(y + (long long)row_of[t * k + j] * d + c);
+      float2 f;
+      f = unpack_bf16x2(v.x); acc[0] += wj * f.x; acc[1] += wj * f.y;
+      f = unpack_bf16x2(v.y); acc[2] += wj * f.x; acc[3] += wj * f.y;
+      f = unpack_bf16x2(v.z); acc[4] += wj * f.x; acc[5] += wj * f.y;
+      f = unpack_bf16x2(v.w); acc[6] += wj * f.x; acc[7] += wj * f.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * d + c) = o;
+  }
+}
+
+// dw[t,j] = <g[t,:], y[row_of[t*k+j],:]> : gradient of the combine weights. One warp per (token, slot).
+__global__ void moe_train_dot_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ y,
+                                     const int* __restrict__ row_of, int n_pairs, int k, int d, float* __restrict__ dw) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= n_pairs) return;
+  const __nv_bfloat16* a = g + (long long)(i / k) * d;
+  const __nv_bfloat16* b = y + (long long)row_of[i] * d;
+  float acc = 0.f;
+  for (int c = lane * 8; c < d; c += 256) {
+    const uint4 va = *reinterpret_cast<const uint4*>(a + c), vb = *reinterpret_cast<const uint4*>(b + c);
+    float2 fa, fb;
+    fa = unpack_bf16x2(va.x); fb = unpack_bf16x2(vb.x); acc += fa.x * fb.x + fa.y * fb.y;
+    fa = unpack_bf16x2(va.y); fb = unpack_bf16x2(vb.y); acc += fa.x * fb.x + fa.y * fb.y;
+    fa = unpack_bf16x2(va.z); fb = unpack_bf16x2(vb.z); acc += fa.x * fb.x + fa.y * fb.y;
+    fa = unpack_bf16x2(va.w); fb = unpack_bf16x2(vb.w); acc += fa.x * fb.x + fa.y * fb.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) dw[i] = acc;
+}
+
 }  // namespace rb
 
 using namespace rb;
@@ -439,5 +626,56 @@ extern "C" int rb_moe_combine(const void* y, const float* w, int T, int k, int d
   long long grid = (nvec + 255) / 256;
   if (grid > 148 * 8) grid = 148 * 8;
   moe_combine_kernel<<<(unsigned)grid, 256, 0, s>>>((const __nv_bfloat16*)y, w, T, k, d, (__nv_bfloat16*)out, accumulate);
+  return RB_OK();
+}
+
+// ---------------------------------------------------------------- training (expert-grouped rows, padded to 64)
+// tables: n_tables entries of {mode, n_total, bn, b_stride} in `desc` (4 ints each), output pointers in tiles / ntiles.
+extern "C" int rb_moe_train_plan(const int* counts, int E, int* offsets, const int* desc, void* const* tiles, int* const* ntiles,
+                                 int n_tables, int max_tiles, int cap_rows, int* status, cudaStream_t s) {
+  if (E <= 0 || E > 256 || n_tables < 0 || n_tables > MAX_TRAIN_TABLES) return -1;
+  TrainTables tabs;
+  tabs.n = n_tables;
+  for (int i = 0; i < n_tables; ++i) {
+    tabs.t[i].mode = desc[4 * i]; tabs.t[i].n_total = desc[4 * i + 1]; tabs.t[i].bn = desc[4 * i + 2]; tabs.t[i].b_stride = desc[4 * i + 3];
+    tabs.t[i].tiles = reinterpret_cast<int4*>(tiles[i]); tabs.t[i].ntiles = ntiles[i];
+    if (tabs.t[i].mode < 0 || tabs.t[i].mode > 2 || tabs.t[i].bn <= 0 || tabs.t[i].n_total <= 0 || tabs.t[i].tiles == nullptr ||
+        tabs.t[i].ntiles == nullptr)
+      return -1;
+    if (tabs.t[i].mode == 2 && ((tabs.t[i].b_stride + 127) / 128 > 0xffff || (tabs.t[i].n_total + tabs.t[i].bn - 1) / tabs.t[i].bn > 0xffff)) return -1;
+  }
+  moe_train_plan_kernel<<<1, 256, 0, s>>>(counts, E, offsets, tabs, max_tiles, cap_rows, status);
+  return RB_OK();
+}
+
+extern "C" int rb_moe_train_rows(const int* topk_idx, int n_pairs, int E, const int* offsets, int* row_of, int* src_of, cudaStream_t s) {
+  if (n_pairs <= 0) return 0;
+  moe_train_rows_kernel<<<E, 1024, 0, s>>>(topk_idx, n_pairs, offsets, row_of, src_of);
+  return RB_OK();
+}
+
+extern "C" int rb_moe_train_gather(const void* src, const float* w, const int* src_of, const int* total_rows, int cap_rows, int k, int d,
+                                   void* out, cudaStream_t s) {
+  if (cap_rows <= 0) return 0;
+  if (d % 8 != 0) return -1;
+  long long grid = ((long long)cap_rows * (d / 8) + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_train_gather_kernel<<<(unsigned)grid, 256, 0, s>>>((const __nv_bfloat16*)src, w, src_of, total_rows, k, d, (__nv_bfloat16*)out);
+  return RB_OK();
+}
+
+extern "C" int rb_moe_train_combine(const void* y, const float* w, const int* row_of, int T, int k, int d, void* out, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (d % 8 != 0) return -1;
+  long long grid = ((long long)T * (d / 8) + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_train_combine_kernel<<<(unsigned)grid, 256, 0, s>>>((const __nv_bfloat16*)y, w, row_of, T, k, d, (__nv_bfloat16*)out);
+  return RB_OK();
+}
+
+extern "C" int rb_moe_train_dot(const void* g, const void* y, const int* row_of, int n_pairs, int k, int d, float* dw, cudaStream_t s) {
+  if (n_pairs <= 0) return 0;
+  if (d % 8 != 0) return -1;
+  moe_train_dot_kernel<<<(n_pairs + 7) / 8, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)y, row_of, n_pairs, k, d, dw);
   return RB_OK();
 }

@@ -90,6 +90,8 @@ class RbGemmArgs(ctypes.Structure):
         ("ready_epoch_ptr", ctypes.c_void_p),
         ("gather_src_ready", ctypes.c_void_p),
         ("gather_wait_all", ctypes.c_int),
+        ("group_mode", ctypes.c_int),
+        ("group_b_rows", ctypes.c_int),
     ]
 
 

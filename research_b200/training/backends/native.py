@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import json
 import math
+import re
 import time
 from pathlib import Path
 from typing import Any, Callable
@@ -46,7 +47,16 @@ _GROUPED = ("self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_p
             "mlp.gate_proj.weight", "mlp.up_proj.weight")
 
 
+_EXPERT = re.compile(r"(.*\.mlp\.experts)\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+
+
 def _order_key(name: str, chunk_of=_chunk_of) -> tuple:
+    m = _EXPERT.match(name)
+    if m:
+        # a layer's experts: every expert's gate then up rows back to back ([E * 2F, d] as one stacked matrix), then
+        # all down projections ([E * d, F]): the grouped expert GEMMs of training address them as two matrices
+        proj = m.group(3)
+        return (chunk_of(name), m.group(1), 1 if proj == "down_proj" else 0, int(m.group(2)), 0 if proj == "gate_proj" else 1, name)
     for i, suffix in enumerate(_GROUPED):
         if name.endswith(suffix):
             return (chunk_of(name), name[:-len(suffix)], i, name)

@@ -228,6 +228,31 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
     return history
 
 
+class _SizeProbe:
+    """Stands in for a communicator to learn how much parameter storage a bucket layout asks for."""
+
+    def __init__(self, world: int):
+        self.world, self.shape = world, None
+
+    def alloc(self, shape, dtype=torch.bfloat16, zero: bool = False):
+        from ..parallel.symm import SymmBuffer
+
+        self.shape = tuple(shape)
+        return SymmBuffer(torch.empty(0, dtype=dtype), [0] * self.world)
+
+
+class _Prealloc:
+    """Hands a buffer that was allocated earlier to the one ``alloc`` call of a bucket layout."""
+
+    def __init__(self, buf):
+        self.buf = buf
+
+    def alloc(self, shape, dtype=torch.bfloat16, zero: bool = False):
+        assert tuple(shape) == tuple(self.buf.local.shape) and dtype == self.buf.local.dtype and self.buf is not None
+        buf, self.buf = self.buf, None
+        return buf
+
+
 async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls, metrics_logger, device, tokenizer,
                                ground_truths, filter_fn) -> list[dict[str, float]]:
     """GRPO with the trainers and the engines on different GPUs of one node.
@@ -265,15 +290,22 @@ async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls
     weights, model_cfg = load_model_weights(config.checkpoint_path or config.model_name, config.seed)
     on_gpu = dev.type == "cuda"
     dtype = torch.bfloat16 if on_gpu else torch.float32
+    # The parameter storage is allocated in the world-wide symmetric memory BEFORE any rank allocates in a sub-group:
+    # with torch 2.11 a world-wide symmetric-memory rendezvous that follows a sub-group one on only some of the ranks
+    # never completes (its exchanges appear to be numbered per process, not per group), so once the trainers have
+    # rendezvoused among themselves (flags, gradients) they and the engines can no longer meet.
+    probe = _SizeProbe(T)
+    build_buckets(model_cfg, LayoutComm(T, torch.device("cpu")), dtype, False, param_comm=probe, with_grads=False)
+    shared_params = _Prealloc(world_comm.alloc(probe.shape, dtype, zero=True))
     backend = engine = manager = None
     if is_trainer:
         tcfg = TrainerConfig(num_minibatches=config.num_minibatches, max_grad_norm=config.max_grad_norm)
-        backend = FSDPTrainingBackend(model_cfg, weights, comm=PeerComm(tgroup, dev), device=dev, param_comm=world_comm,
+        backend = FSDPTrainingBackend(model_cfg, weights, comm=PeerComm(tgroup, dev), device=dev, param_comm=shared_params,
                                       loss_fn=config.loss, lr=config.lr, weight_decay=config.weight_decay, trainer_config=tcfg,
                                       checkpoint_dir=out_dir / "checkpoints")
         buckets = backend.buckets
     else:
-        buckets = build_buckets(model_cfg, LayoutComm(T, dev), dtype, False, param_comm=world_comm, with_grads=False)
+        buckets = build_buckets(model_cfg, LayoutComm(T, dev), dtype, False, param_comm=shared_params, with_grads=False)
         ei = engine_ranks.index(rank)
         ecfg = EngineConfig(cache_type=config.cache_type, max_batch_size=config.max_batch_size,
                             max_model_len=max(config.max_seq_len + config.max_tokens, 64), num_kv_blocks=config.kv_blocks,

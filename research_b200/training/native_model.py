@@ -22,6 +22,7 @@ Attention core: the tcgen05 flash attention kernels (forward and backward) for h
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.nn.functional as F
@@ -239,6 +240,7 @@ class NativeCausalLM:
         self.ckpt = activation_checkpointing
         self._params: dict[str, torch.Tensor] = {}
         self._stacked: dict[str, tuple] = {}
+        self._experts: dict[str, tuple | None] = {}
         self._sharded: dict[str, object] = {}
         self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.trace: dict | None = None
@@ -389,10 +391,9 @@ class NativeCausalLM:
         return lin(_SwiGLU.apply(gu), m + "down_proj.weight", residual=x)
 
     def _moe(self, h, m: str, lin):
-        """Mixture-of-experts MLP for training: router and expert projections are tcgen05 GEMMs (forward, dgrad
-        and wgrad through ``_Linear``), tokens are grouped by expert with one sort, and every expert with work
-        runs its three GEMMs on its slice (math of models/functional.py::moe_mlp). One host sync per layer
-        (the per-expert token counts); the serving path uses the grouped GEMM with a device tile table instead."""
+        """Mixture-of-experts MLP for training (math of models/functional.py::moe_mlp): the router is a tcgen05 GEMM
+        through ``_Linear``; the experts run as grouped tcgen05 GEMMs over expert-sorted rows, forward, data gradient
+        and weight gradient alike, with no host synchronisation (``ops.moe_train.GroupedExperts``)."""
         cfg = self.cfg
         k, E = cfg.num_experts_per_tok, cfg.num_experts
         logits = lin(h, m + "gate.weight").float()
@@ -410,6 +411,26 @@ class NativeCausalLM:
             wt, idx = logits.softmax(-1).topk(k, dim=-1)
             if cfg.norm_topk_prob:
                 wt = wt / wt.sum(-1, keepdim=True)
+        experts = self.stacked_experts(m)
+        if experts is not None:
+            from ..ops.moe_train import GroupedExperts, GroupedPlan
+
+            wgu, ggu, wd, gd = experts
+            plan = GroupedPlan(idx.to(torch.int32).contiguous(), E, cfg.hidden_size, cfg.moe_intermediate_size)
+            out = GroupedExperts.apply(h, wt.float(), wgu, ggu, wd, gd, plan, self.b)
+        else:
+            out = self._moe_loop(h, m, lin, idx, wt)
+        if cfg.n_shared_experts > 0:
+            p = m + "shared_experts."
+            gu = torch.cat([lin(h, p + "gate_proj.weight"), lin(h, p + "up_proj.weight")], dim=-1)
+            out = out + lin(_SwiGLU.apply(gu), p + "down_proj.weight")
+        return out
+
+    def _moe_loop(self, h, m: str, lin, idx, wt):
+        """Per-expert loop (one host sync for the counts): layers whose experts do not lie back to back in the bucket,
+        more than 256 experts, or ``RB_MOE_GROUPED=0``."""
+        cfg = self.cfg
+        k, E = cfg.num_experts_per_tok, cfg.num_experts
         flat = idx.reshape(-1)
         order = flat.argsort(stable=True)                       # (token, slot) pairs grouped by expert
         counts = torch.bincount(flat, minlength=E).tolist()     # the one host sync
@@ -426,12 +447,25 @@ class NativeCausalLM:
             outs.append(lin(_SwiGLU.apply(gu), p + "down_proj.weight"))
             off += n
         y = torch.cat(outs, 0) * ws[:, None]
-        out = torch.zeros_like(h).index_add(0, tok, y)
-        if cfg.n_shared_experts > 0:
-            p = m + "shared_experts."
-            gu = torch.cat([lin(h, p + "gate_proj.weight"), lin(h, p + "up_proj.weight")], dim=-1)
-            out = out + lin(_SwiGLU.apply(gu), p + "down_proj.weight")
-        return out
+        return torch.zeros_like(h).index_add(0, tok, y)
+
+    def stacked_experts(self, m: str):
+        """``(wgu [E*2F, d], its gradient view, wd [E*d, F], its gradient view)`` of the layer whose MLP prefix is ``m``
+        when its experts lie back to back in the bucket (gate|up of every expert, then every down projection), else
+        None."""
+        cfg = self.cfg
+        E = cfg.num_experts
+        first = f"{m}experts.0.gate_proj.weight"
+        if self.b._pending and first in self.b.specs:
+            self.b.ensure_chunk(self.b.specs[first].chunk)
+        if m not in self._experts:
+            self._experts[m] = None
+            if os.environ.get("RB_MOE_GROUPED", "1") != "0" and E <= 256 and cfg.hidden_size % 64 == 0 and cfg.moe_intermediate_size % 32 == 0:
+                wgu, ggu = self.stacked(tuple(f"{m}experts.{e}.{p}.weight" for e in range(E) for p in ("gate_proj", "up_proj")))
+                wd, gd = self.stacked(tuple(f"{m}experts.{e}.down_proj.weight" for e in range(E)))
+                if wgu is not None and wd is not None:
+                    self._experts[m] = (wgu, ggu, wd, gd)
+        return self._experts[m]
 
     def logprobs(self, input_ids: torch.Tensor, targets: torch.Tensor, need_entropy: bool = False):
         """Per-token ``log p(targets)`` ``[B,T]`` (and entropy) with autograd through the kernels."""

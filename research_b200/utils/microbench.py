@@ -246,8 +246,64 @@ def sweep_train_gemm(peak_tflops: float, iters: int = 10, shapes=TRAIN_GEMMS_8B)
     return rows
 
 
+def bench_moe_train(T, k, E, d, F, peak_tflops, iters=5):
+    """Forward + backward of one layer's routed experts in training: the grouped launches against a loop over the
+    experts with one library GEMM triple each (what a module-per-expert model runs)."""
+    from ..ops.moe_train import GroupedExperts, GroupedPlan
+
+    class Sink:
+        def accumulate_into(self, view):
+            return False
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    h = (torch.randn(T, d, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+    wgu = (torch.randn(E * 2 * F, d, device="cuda", generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(E * d, F, device="cuda", generator=g) * 0.02).bfloat16()
+    ggu, gd = torch.empty_like(wgu), torch.empty_like(wd)
+    wt, idx = torch.randn(T, E, device="cuda", generator=g).softmax(-1).topk(k, dim=-1)
+    wt = wt.contiguous().requires_grad_(True)
+    idx32 = idx.to(torch.int32).contiguous()
+    dout = (torch.randn(T, d, device="cuda", generator=g) * 0.1).bfloat16()
+    sink = Sink()
+
+    def grouped():
+        plan = GroupedPlan(idx32, E, d, F)
+        GroupedExperts.apply(h, wt, wgu, ggu, wd, gd, plan, sink).backward(dout)
+        h.grad = wt.grad = None
+
+    wl = [(wgu[e * 2 * F:(e + 1) * 2 * F].clone().requires_grad_(True), wd[e * d:(e + 1) * d].clone().requires_grad_(True)) for e in range(E)]
+
+    def loop():
+        flat = idx.reshape(-1)
+        order = flat.argsort(stable=True)
+        counts = torch.bincount(flat, minlength=E).tolist()
+        tok = order // k
+        xs = h.index_select(0, tok)
+        ws = wt.reshape(-1).index_select(0, order).to(h.dtype)
+        outs, off = [], 0
+        for e, n in enumerate(counts):
+            if n:
+                gu = xs[off:off + n] @ wl[e][0].t()
+                outs.append((torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ wl[e][1].t())
+                off += n
+        out = torch.zeros_like(h).index_add(0, tok, torch.cat(outs) * ws[:, None])
+        out.backward(dout)
+        h.grad = wt.grad = None
+        for a, b in wl:
+            a.grad = b.grad = None
+
+    tg = time_cuda(grouped, iters=iters)
+    tl = time_cuda(loop, iters=iters)
+    flops = 18.0 * T * k * F * d
+    ach = flops / (tg["median_ms"] * 1e-3) / 1e12
+    return {"kernel": "moe_grouped_experts_fwd_bwd", "T": T, "k": k, "E": E, "d": d, "F": F, "ms": round(tg["median_ms"], 3),
+            "tflops": round(ach, 1), "frac_of_measured_peak": round(ach / peak_tflops, 3),
+            "per_expert_library_loop_ms": round(tl["median_ms"], 3), "speedup": round(tl["median_ms"] / tg["median_ms"], 2)}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--moe-train", action="store_true", help="only the grouped expert MLP of training (Qwen3-30B-A3B and a small shape)")
     ap.add_argument("--decode-gemm-sweep", action="store_true", help="only the tile-width / split-K sweep of decode GEMMs")
     ap.add_argument("--train-gemm-sweep", action="store_true",
                     help="only the GEMMs of a Llama-3-8B training step: one-CTA kernel, two-CTA kernel, library")
@@ -262,6 +318,10 @@ def main() -> None:
     if args.train_gemm_sweep:
         for r in sweep_train_gemm(args.peak_tflops):
             print(json.dumps(r))
+        return
+    if args.moe_train:
+        for shape in ((4096, 8, 128, 2048, 768), (8192, 8, 128, 2048, 768), (4096, 2, 8, 4096, 14336 // 4)):
+            print(json.dumps(bench_moe_train(*shape, args.peak_tflops)), flush=True)
         return
     rows = []
     shapes = [(8192, 8192, 8192), (4096, 14336, 4096), (8192, 4096, 14336), (256, 1152, 896), (256, 9728, 896),

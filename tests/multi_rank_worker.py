@@ -334,6 +334,10 @@ def main():
     device = sys.argv[1]
     cases = sys.argv[2].split(",") if len(sys.argv) > 2 else list(CASES)
     rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", "0"))
+    if os.environ.get("RB_TEST_DUMP_AFTER"):
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["RB_TEST_DUMP_AFTER"]), exit=True)
     if device == "cuda":
         torch.cuda.set_device(local)
         dev, dt = torch.device("cuda", local), torch.bfloat16

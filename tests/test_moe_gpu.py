@@ -3,6 +3,7 @@
 import pytest
 import torch
 
+from research_b200 import ops
 from research_b200.inference import EngineConfig, InferenceEngine, SamplingParams
 from research_b200.models import causal_lm_forward, get_preset, init_random_weights
 from research_b200.models.functional import moe_mlp
@@ -94,3 +95,63 @@ def test_moe_layer_with_group_limited_routing(cuda_device):
     want = x0.float() + moe_mlp(h.float()[None], w, "model.layers.1.mlp.", cfg)[0]
     err = (x.float().cpu() - want).abs()
     assert err.max().item() < 0.06 + 0.02 * want.abs().max().item(), err.max().item()
+
+
+class _Sink:
+    """Stand-in for the gradient bucket: the first write of a view stores, later writes add."""
+
+    def __init__(self):
+        self.seen = set()
+
+    def accumulate_into(self, view) -> bool:
+        key = view.data_ptr()
+        hit = key in self.seen
+        self.seen.add(key)
+        return hit
+
+
+@pytest.mark.parametrize("T,k,E,d,F", [(200, 2, 8, 256, 128), (1024, 4, 16, 512, 192), (96, 8, 64, 128, 64)])
+def test_grouped_experts_training_vs_reference(cuda_device, T, k, E, d, F):
+    """Forward, data gradient, weight gradients and combine-weight gradient of the grouped expert MLP against the fp32
+    per-expert loop; a second backward pass must ADD to the weight gradients; experts without tokens get zeros."""
+    from research_b200.ops.moe_train import GroupedExperts, GroupedPlan, grouped_experts_reference
+
+    g = torch.Generator().manual_seed(T + E)
+    h = (torch.randn(T, d, generator=g) * 0.5).bfloat16().to(cuda_device)
+    wgu = (torch.randn(E * 2 * F, d, generator=g) * 0.05).bfloat16().to(cuda_device)
+    wd = (torch.randn(E * d, F, generator=g) * 0.05).bfloat16().to(cuda_device)
+    logits = torch.randn(T, E, generator=g)
+    logits[:, E - 1] = -1e9                       # the last expert never gets a token
+    wt, idx = logits.softmax(-1).topk(k, dim=-1)
+    wt, idx = wt.to(cuda_device), idx.to(cuda_device)
+    dout = (torch.randn(T, d, generator=g) * 0.1).bfloat16().to(cuda_device)
+
+    hr, wtr = h.float().requires_grad_(True), wt.clone().requires_grad_(True)
+    wgur, wdr = wgu.float().requires_grad_(True), wd.float().requires_grad_(True)
+    ref = grouped_experts_reference(hr, idx, wtr, wgur, wdr)
+    ref.backward(dout.float())
+
+    plan = GroupedPlan(idx.to(torch.int32).contiguous(), E, d, F)
+    offs = plan.offsets.cpu()
+    counts = torch.bincount(idx.reshape(-1).cpu(), minlength=E)
+    assert all(int(offs[e + 1] - offs[e]) == max(64, -(-int(counts[e]) // 64) * 64) for e in range(E))
+    ggu, gd = torch.full_like(wgu, 7.0), torch.full_like(wd, 7.0)    # must be overwritten, not added to
+    sink = _Sink()
+    hk, wtk = h.clone().requires_grad_(True), wt.clone().requires_grad_(True)
+    out = GroupedExperts.apply(hk, wtk, wgu, ggu, wd, gd, plan, sink)
+    out.backward(dout)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+    assert rel(out, ref) < 2e-2, rel(out, ref)
+    assert rel(hk.grad, hr.grad) < 3e-2, rel(hk.grad, hr.grad)
+    assert rel(wtk.grad, wtr.grad) < 3e-2, rel(wtk.grad, wtr.grad)
+    assert rel(ggu, wgur.grad) < 3e-2, rel(ggu, wgur.grad)
+    assert rel(gd, wdr.grad) < 3e-2, rel(gd, wdr.grad)
+    assert float(ggu[(E - 1) * 2 * F:].abs().max()) == 0.0 and float(gd[(E - 1) * d:].abs().max()) == 0.0
+    # second pass of the same window: gradients add up
+    out2 = GroupedExperts.apply(hk, wtk, wgu, ggu, wd, gd, plan, sink)
+    out2.backward(dout)
+    assert rel(ggu, 2 * wgur.grad) < 3e-2 and rel(gd, 2 * wdr.grad) < 3e-2
+    ops.check_status()

@@ -392,3 +392,32 @@ def test_packed_shards_bos_aligned_batches(tmp_path):
     assert len(b0) == len(b1) >= 2 and not torch.equal(b0[0][0], b1[0][0])
     single = list(packed_batches([tmp_path / "a.bin"], 64, 16, BOS))
     assert torch.equal(single[0][0], b0[0][0]) and torch.equal(single[1][0], b1[0][0])    # ranks split the same stream
+
+
+def test_grouped_experts_layout_and_reference():
+    """The experts of a layer lie back to back in the flat bucket (gate|up of every expert, then every down projection),
+    and the grouped-experts oracle equals the functional MoE layer."""
+    from research_b200.models.functional import moe_mlp
+    from research_b200.ops.moe_train import grouped_experts_reference
+    from research_b200.parallel.symm import LocalComm
+    from research_b200.training.backends.native import build_buckets
+
+    cfg = get_preset("tiny-moe", num_layers=2, init_std=0.05)
+    b = build_buckets(cfg, LocalComm(torch.device("cpu")), torch.float32)
+    E, F, d = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    m = "model.layers.1.mlp."
+    names = [f"{m}experts.{e}.{p}.weight" for e in range(E) for p in ("gate_proj", "up_proj")] + [f"{m}experts.{e}.down_proj.weight" for e in range(E)]
+    specs = [b.specs[n] for n in names]
+    assert all(x.offset + x.numel == y.offset for x, y in zip(specs, specs[1:]))
+    w = init_random_weights(cfg, seed=0)
+    wgu = torch.cat([w[n] for n in names[:2 * E]])
+    wd = torch.cat([w[n] for n in names[2 * E:]])
+    assert wgu.shape == (E * 2 * F, d) and wd.shape == (E * d, F)
+    h = torch.randn(37, d) * 0.5
+    logits = h @ w[m + "gate.weight"].t()
+    wt, idx = logits.softmax(-1).topk(cfg.num_experts_per_tok, dim=-1)
+    if cfg.norm_topk_prob:
+        wt = wt / wt.sum(-1, keepdim=True)
+    got = grouped_experts_reference(h, idx, wt, wgu, wd)
+    want = moe_mlp(h[None], w, m, cfg)[0]
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
