@@ -647,6 +647,53 @@ def run_library_train(args) -> dict:
                                        "parameters, gradients and moments (no fp32 master copy)"})
 
 
+def _install_trio_standin() -> bool:
+    """The reference's training package imports ``trio`` at module level (``training/types.py``: a ``trio.Event`` inside
+    its futures; type annotations elsewhere). The image has no trio. This registers a stand-in module with a working
+    ``Event`` and placeholder classes for every other name, so that the UNMODIFIED package imports; the backend calls
+    this arm times return already-completed futures and never touch it. Returns True if the stand-in was installed."""
+    import asyncio
+    import threading
+    import types
+
+    try:
+        import trio  # noqa: F401
+
+        return False
+    except ImportError:
+        pass
+
+    class Event:
+        def __init__(self):
+            self._e = threading.Event()
+
+        def set(self):
+            self._e.set()
+
+        def is_set(self):
+            return self._e.is_set()
+
+        async def wait(self):
+            while not self._e.is_set():
+                await asyncio.sleep(0)
+
+    class _Missing:
+        def __init__(self, *a, **k):
+            raise RuntimeError("trio is not installed; this is an import-time stand-in")
+
+    mod = types.ModuleType("trio")
+    mod.Event = Event
+
+    def _getattr(name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return type(name, (_Missing,), {})
+
+    mod.__getattr__ = _getattr
+    sys.modules["trio"] = mod
+    return True
+
+
 def run_reference_train(args) -> dict:
     """The reference's own ``FSDPTrainingBackend`` (unmodified, from ``baseline/_ref``) on a random-init HF Llama of
     the benchmark shape, driven through ``forward_backward`` / ``optim_step``."""
@@ -654,13 +701,13 @@ def run_reference_train(args) -> dict:
     if not os.path.isdir(os.path.join(ref_dir, "rollouts")):
         return {"impl": "reference", "unavailable": "baseline/_ref/rollouts is absent (reference not installed on this box)"}
     sys.path.insert(0, ref_dir)
+    standin = _install_trio_standin()
     try:
         from rollouts.training.backends.fsdp import FSDPConfig as RefFSDPConfig
         from rollouts.training.backends.fsdp import FSDPTrainingBackend as RefBackend
-    except Exception as e:   # e.g. the reference's training package imports trio, which this image does not ship
-        return {"impl": "reference", "unavailable":
-                (f"reference training backend cannot be imported: {type(e).__name__}: {e} "
-                 "(rollouts/training/types.py imports trio; not in this image nor its wheelhouse)")[:300]}
+        from rollouts.training.losses import sft_loss as ref_sft_loss
+    except Exception as e:
+        return {"impl": "reference", "unavailable": f"reference training backend cannot be imported: {type(e).__name__}: {e}"[:300]}
     import tempfile
 
     import torch
@@ -674,7 +721,8 @@ def run_reference_train(args) -> dict:
     cfg, model = _hf_llama(args, dev)
 
     def loss_fn(logits, batch):
-        return _ce_full_logits(logits, batch)
+        # the reference's own SFT loss (it returns (loss, metrics); its FSDP backend wants the tensor)
+        return ref_sft_loss(logits, batch)[0]
 
     backend = RefBackend(model=model, optimizer_fn=lambda m: torch.optim.AdamW(m.parameters(), lr=1e-5, betas=(0.9, 0.95)),
                          loss_fn=loss_fn, checkpoint_dir=__import__("pathlib").Path(tempfile.mkdtemp(prefix="ref_ckpt_")),
@@ -687,12 +735,22 @@ def run_reference_train(args) -> dict:
         return getattr(fut, "_result", None)
 
     def step(b):
-        m = resolve(backend.forward_backward(b))
+        # the reference's losses take labels already shifted to the next token (-100 = ignore)
+        ids = b["input_ids"]
+        labels = torch.full_like(ids, -100)
+        labels[:, :-1] = ids[:, 1:]
+        mask = torch.zeros_like(b["loss_mask"])
+        mask[:, :-1] = b["loss_mask"][:, 1:]
+        m = resolve(backend.forward_backward({"input_ids": ids, "labels": labels, "loss_mask": mask}))
         resolve(backend.optim_step())
         return (m or {}).get("loss", 0.0)
 
-    return _time_train_arm(args, step, world, rank, local, "reference",
-                           {"engine": "rollouts.training.backends.fsdp.FSDPTrainingBackend (unmodified)"})
+    extra = {"engine": "rollouts.training.backends.fsdp.FSDPTrainingBackend (unmodified) on a random-init HF LlamaForCausalLM, "
+                       "the reference's sft_loss, torch AdamW"}
+    if standin:
+        extra["import_note"] = ("trio is not in this image: a stand-in module provides trio.Event (used by the reference's futures) so that "
+                                "the unmodified training package imports; the timed path never awaits it")
+    return _time_train_arm(args, step, world, rank, local, "reference", extra)
 
 
 def main() -> None:

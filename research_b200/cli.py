@@ -28,7 +28,16 @@ def _store(args):
 def _endpoint(args):
     from .agents.dtypes import Endpoint
 
-    return Endpoint(provider=args.provider, model=args.model or "", api_base=args.api_base or "",
+    provider, model = args.provider, args.model or ""
+    if "/" in model:      # --model anthropic/claude-... names the provider too, when the part before the slash is one
+        from .agents.providers import NonRetryableError, get_provider
+
+        try:
+            get_provider(model.split("/", 1)[0])
+            provider, model = parse_model_string(model)
+        except NonRetryableError:
+            pass          # an organisation prefix of a model name (meta-llama/...), not a provider
+    return Endpoint(provider=provider, model=model, api_base=args.api_base or "",
                     api_key=os.environ.get(args.api_key_env or "", "") if args.api_key_env else "",
                     max_tokens=args.max_tokens, temperature=args.temperature)
 
@@ -122,23 +131,47 @@ async def _chat(args) -> int:
     from .agents.presets import get_preset
     from .frontend.terminal import InteractiveRunner, make_frontend
 
-    preset, store, ep = get_preset(args.preset), _store(args), _endpoint(args)
-    frontend = make_frontend(args.frontend, auto_confirm=args.yes)
+    if args.list_presets:
+        from .agents.presets import PRESETS
+
+        for p in PRESETS.values():
+            print(f"{p.name:<20} {p.description}  (max {p.max_turns} turns)")
+        return 0
+    preset, ep = get_preset(args.preset), _endpoint(args)
+    store = None if args.no_session else _store(args)
+    frontend = make_frontend("json" if args.stream_json else ("plain" if args.quiet and args.frontend == "auto" else args.frontend),
+                             auto_confirm=args.yes)
+    system_prompt = preset.system_prompt
+    if args.system_prompt:
+        system_prompt = Path(args.system_prompt).read_text() if os.path.isfile(args.system_prompt) else args.system_prompt
+    context = [c for c in (args.context or [])] + [f"# {f}\n{Path(f).read_text()}" for f in (args.context_file or [])]
+    if context:
+        system_prompt = system_prompt + "\n\n" + "\n\n".join(context)
     trajectory = session_id = None
-    if args.session:
+    if getattr(args, "continue_session", False) and not args.session and store is not None:
+        args.session = await _latest(store) or ""
+    if args.session and store is not None:
         state = await resume_session(args.session, store, ep, type(preset.environment(args.cwd)), preset.max_turns)
         env, trajectory, session_id = state.environment, state.actor.trajectory, state.session_id
     else:
         env = preset.environment(args.cwd)
         if hasattr(env, "on_session_start"):
             await env.on_session_start(f"cli-{os.getpid()}")
-    runner = InteractiveRunner(ep, frontend, environment=env, system_prompt=preset.system_prompt, session_store=store,
+    runner = InteractiveRunner(ep, frontend, environment=env, system_prompt=system_prompt, session_store=store,
                                session_id=session_id, max_turns=preset.max_turns, initial_prompt=args.prompt,
                                single_turn=args.prompt is not None, trajectory=trajectory)
     state = await runner.run()
-    if state.session_id:
+    if state.session_id and not args.quiet:
         print(f"session: {state.session_id}", file=sys.stderr)
     return 0
+
+
+def parse_model_string(model: str) -> tuple[str, str]:
+    """``provider/model`` -> ``(provider, model)`` (rollouts/cli.py:493-508); a bare model name has no provider part."""
+    if "/" not in model:
+        raise ValueError(f'expected "provider/model" (e.g. "anthropic/claude-sonnet-4-5"), got {model!r}')
+    provider, name = model.split("/", 1)
+    return provider, name
 
 
 def cmd_chat(args) -> int:
@@ -152,8 +185,11 @@ async def _sessions(args) -> int:
 
     store = _store(args)
     if args.action == "list":
+        from .agents.doctor import format_time_ago
+
         for s in sorted(await store.list(), key=lambda s: s.updated_at, reverse=True)[: args.limit]:
-            print(f"{s.session_id}  {s.status:<10} {s.num_messages:>4} msgs  {s.endpoint.get('provider', '?')}/{s.endpoint.get('model', '?')}")
+            print(f"{s.session_id}  {s.status:<10} {s.num_messages:>4} msgs  {format_time_ago(s.updated_at):>9}  "
+                  f"{s.endpoint.get('provider', '?')}/{s.endpoint.get('model', '?')}")
     elif args.action in ("show", "export"):
         text = await export_session(store, args.id, args.format, args.output)
         if not args.output:
@@ -162,7 +198,42 @@ async def _sessions(args) -> int:
         print(await slice_session(store, args.id, args.spec))
     elif args.action == "import":
         print(await import_transcript(store, Path(args.id)))
+    elif args.action == "handoff":
+        from .agents.export import handoff_summary
+
+        text = await handoff_summary(store, args.id or await _latest(store), args.goal or None)
+        if args.output:
+            Path(args.output).write_text(text)
+        else:
+            print(text)
+    elif args.action == "doctor":
+        from .agents import doctor
+
+        sid = args.id or await _latest(store)
+        if not sid:
+            print("no session found", file=sys.stderr)
+            return 1
+        session, messages = await store.get(sid)
+        issues = doctor.diagnose(messages)
+        print(doctor.report(doctor.session_stats(session, messages), issues, messages))
+        if args.fix:
+            new, dropped = await doctor.fix_session(store, sid)
+            print(f"\ncreated fixed session {new} (dropped messages {dropped}); resume with: chat --session {new}" if new
+                  else "\nnothing auto-fixable; use --trim N for oversized or unanswered messages")
+        if args.trim:
+            try:
+                new = await doctor.trim_session(store, sid, args.trim)
+            except ValueError as e:
+                print(f"\n{e}", file=sys.stderr)
+                return 1
+            print(f"\ncreated trimmed session {new} (dropped the last {args.trim} messages); resume with: chat --session {new}")
     return 0
+
+
+async def _latest(store) -> str | None:
+    from .agents.doctor import latest_session_id
+
+    return await latest_session_id(store)
 
 
 def cmd_sessions(args) -> int:
@@ -225,9 +296,20 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--session", default="", help="resume this session"); p.add_argument("-p", "--prompt", default=None)
     p.add_argument("-y", "--yes", action="store_true", help="run tools without asking")
     p.add_argument("--frontend", default="auto", choices=["auto", "plain", "json", "ansi"], help="terminal front end")
+    p.add_argument("-c", "--continue", dest="continue_session", action="store_true", help="resume the most recent session")
+    p.add_argument("--no-session", action="store_true", help="do not store this conversation")
+    p.add_argument("--system-prompt", default="", help="text, or a file holding it, that replaces the preset's system prompt")
+    p.add_argument("--context", action="append", help="extra text appended to the system prompt (repeatable)")
+    p.add_argument("--context-file", action="append", help="file whose content is appended to the system prompt (repeatable)")
+    p.add_argument("--stream-json", action="store_true", help="print every event as one JSON line (for programs)")
+    p.add_argument("-q", "--quiet", action="store_true", help="only the model's text")
+    p.add_argument("--list-presets", action="store_true")
     p.set_defaults(fn=cmd_chat)
     p = sub.add_parser("sessions")
-    p.add_argument("action", choices=["list", "show", "export", "slice", "import"]); p.add_argument("id", nargs="?")
+    p.add_argument("action", choices=["list", "show", "export", "slice", "import", "doctor", "handoff"]); p.add_argument("id", nargs="?")
+    p.add_argument("--fix", action="store_true", help="doctor: write a child session without duplicate / orphaned tool results")
+    p.add_argument("--trim", type=int, default=0, help="doctor: write a child session without the last N messages")
+    p.add_argument("--goal", default="", help="handoff: what the next session should do")
     p.add_argument("--spec", default=""); p.add_argument("--format", default="md", choices=["md", "html"])
     p.add_argument("--output", default=""); p.add_argument("--store", default=""); p.add_argument("--limit", type=int, default=20)
     p.set_defaults(fn=cmd_sessions)

@@ -353,61 +353,61 @@ struct TrainTableDesc {
 constexpr int MAX_TRAIN_TABLES = 6;
 struct TrainTables { TrainTableDesc t[MAX_TRAIN_TABLES]; int n; };
 
-// One CTA. offsets[e] = first row of expert e, offsets[E] = rows in use (all multiples of 64; an expert without tokens
-// still gets 64 zero rows, which keeps its weight gradient an ordinary tile whose product is zero).
+// One CTA per table (blockIdx.x) plus every CTA's own copy of the offsets. offsets[e] = first row of expert e,
+// offsets[E] = rows in use (all multiples of 64; an expert without tokens still gets 64 zero rows, which keeps its weight
+// gradient an ordinary tile whose product is zero).
 __global__ void moe_train_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, TrainTables tabs,
                                       int max_tiles, int cap_rows, int* __restrict__ status) {
   __shared__ int off_s[257];
   __shared__ int base_s[257];
-  if (threadIdx.x == 0) {
-    int o = 0;
-    for (int e = 0; e < E; ++e) {
-      off_s[e] = o;
-      const int c = counts[e];
-      o += c > 0 ? ((c + 63) / 64) * 64 : 64;
-    }
-    off_s[E] = o;
-    if (o > cap_rows && status != nullptr) set_status(status, ST_BAD_INDEX);
+  const TrainTableDesc d = tabs.t[blockIdx.x];
+  const int nt = (d.n_total + d.bn - 1) / d.bn;
+  // padded row counts and tile counts per expert, then two serial prefix sums over at most 256 entries
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int c = counts[e];
+    off_s[e + 1] = c > 0 ? ((c + 63) / 64) * 64 : 64;
   }
   __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off_s[e];
-  for (int ti = 0; ti < tabs.n; ++ti) {
-    const TrainTableDesc d = tabs.t[ti];
-    const int nt = (d.n_total + d.bn - 1) / d.bn;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int b = 0;
-      for (int e = 0; e < E; ++e) {
-        base_s[e] = b;
-        const int rows = off_s[e + 1] - off_s[e];
-        b += (d.mode == 2 ? (d.b_stride + 127) / 128 : (rows + 127) / 128) * nt;
-      }
-      base_s[E] = b;
-      if (b > max_tiles) {
-        if (status != nullptr) set_status(status, ST_BAD_INDEX);
-        base_s[E] = 0;
-      }
-      *d.ntiles = base_s[E];
-    }
-    __syncthreads();
-    if (base_s[E] == 0) continue;
+  if (threadIdx.x == 0) {
+    int o = 0, b = 0;
+    off_s[0] = 0;
     for (int e = 0; e < E; ++e) {
-      const int rows = off_s[e + 1] - off_s[e];
-      const int mt = d.mode == 2 ? (d.b_stride + 127) / 128 : (rows + 127) / 128;
-      const int n = mt * nt;
-      for (int j = threadIdx.x; j < n; j += blockDim.x) {
-        // consecutive tiles share the B tile (modes 0, 1) or the A tile's k range (mode 2)
-        const int in = j / mt, im = j % mt;
-        int4 v;
-        if (d.mode == 2) {
-          v = make_int4(off_s[e], rows, e, (im << 16) | in);
-        } else {
-          const int r0 = off_s[e] + im * 128;
-          v = make_int4(r0, min(128, off_s[e + 1] - r0), d.mode == 0 ? e * d.b_stride + in * d.bn : e * d.b_stride, in * d.bn);
-        }
-        d.tiles[base_s[e] + j] = v;
-      }
+      const int rows = off_s[e + 1];
+      base_s[e] = b;
+      b += (d.mode == 2 ? (d.b_stride + 127) / 128 : (rows + 127) / 128) * nt;
+      o += rows;
+      off_s[e + 1] = o;
     }
+    base_s[E] = b;
+    if (o > cap_rows || b > max_tiles) {
+      set_status(status, ST_BAD_INDEX);
+      base_s[E] = 0;
+    }
+    *d.ntiles = base_s[E];
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off_s[e];
+  const int total = base_s[E];
+  for (int t = threadIdx.x; t < total; t += blockDim.x) {
+    int lo = 0, hi = E - 1;                       // the expert whose tile range holds t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (base_s[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    const int e = lo, j = t - base_s[e];
+    const int rows = off_s[e + 1] - off_s[e];
+    const int mt = d.mode == 2 ? (d.b_stride + 127) / 128 : (rows + 127) / 128;
+    // consecutive tiles share the B tile (modes 0, 1) or the A tile's k range (mode 2)
+    const int in = j / mt, im = j % mt;
+    int4 v;
+    if (d.mode == 2) {
+      v = make_int4(off_s[e], rows, e, (im << 16) | in);
+    } else {
+      const int r0 = off_s[e] + im * 128;
+      v = make_int4(r0, min(128, off_s[e + 1] - r0), d.mode == 0 ? e * d.b_stride + in * d.bn : e * d.b_stride, in * d.bn);
+    }
+    d.tiles[t] = v;
   }
 }
 
@@ -644,7 +644,8 @@ extern "C" int rb_moe_train_plan(const int* counts, int E, int* offsets, const i
       return -1;
     if (tabs.t[i].mode == 2 && ((tabs.t[i].b_stride + 127) / 128 > 0xffff || (tabs.t[i].n_total + tabs.t[i].bn - 1) / tabs.t[i].bn > 0xffff)) return -1;
   }
-  moe_train_plan_kernel<<<1, 256, 0, s>>>(counts, E, offsets, tabs, max_tiles, cap_rows, status);
+  if (n_tables == 0) return -1;
+  moe_train_plan_kernel<<<n_tables, 256, 0, s>>>(counts, E, offsets, tabs, max_tiles, cap_rows, status);
   return RB_OK();
 }
 

@@ -369,6 +369,7 @@ async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls
             t2 = time.perf_counter()
             if (step + 1) % config.sync_weights_every == 0:
                 dist.barrier()                                                  # the trainers' parameters are final
+                t2 = time.perf_counter()                                        # (an engine waited for the trainers here)
                 if on_gpu:
                     if not is_trainer:
                         src = trainer_ranks[engine_ranks.index(rank) % T]

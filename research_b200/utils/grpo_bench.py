@@ -31,6 +31,8 @@ def main() -> None:
     ap.add_argument("--minibatches", type=int, default=8)
     ap.add_argument("--loss", default="grpo_clipped")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--trainers", type=int, default=0,
+                    help="several ranks: the first N ranks only train, the others only serve (disjoint device sets); 0 = every rank does both")
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -56,15 +58,29 @@ def main() -> None:
     gcfg = GRPOConfig(model_name=args.model, lr=1e-6, batch_size=args.prompts, n_samples_per_prompt=args.samples,
                       num_minibatches=args.minibatches, max_tokens=args.max_tokens, max_seq_len=args.prompt_len + args.max_tokens,
                       temperature=1.0, num_steps=args.steps + 1, output_dir=out, checkpoint_every=0, loss=args.loss,
-                      max_batch_size=min(256, args.prompts * args.samples // world))
+                      max_batch_size=min(256, args.prompts * args.samples // max(world - args.trainers, 1)))
+    disjoint = world > 1 and 0 < args.trainers < world
+    if disjoint:
+        import dataclasses
+
+        gcfg = dataclasses.replace(gcfg, trainer_cuda_device_ids=tuple(range(args.trainers)),
+                                   inference_cuda_device_ids=tuple(range(args.trainers, world)))
     hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=args.device)
     steps = hist[1:]                      # the first step pays one-time set-up (graph capture, allocator growth)
     n = len(steps)
-    mean = lambda k: sum(h.get(k, 0.0) for h in steps) / n  # noqa: E731
-    samples = mean("num_samples") * world
+    phase = {k: sum(h.get(k, 0.0) for h in steps) / n for k in ("step_s", "rollout_s", "train_s", "sync_s", "num_samples")}
+    if disjoint:
+        # every rank reports its own phases (an engine does not train, a trainer does not generate): the slowest rank counts
+        t = torch.tensor([phase[k] for k in sorted(phase)], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        phase = dict(zip(sorted(phase), t.tolist()))
+    mean = phase.__getitem__
+    samples = mean("num_samples") * (1 if disjoint else world)      # disjoint ranks all see the gathered samples
     gen_tokens = samples * args.max_tokens
     trained_tokens = samples * (args.prompt_len * 0.75 + args.max_tokens)     # prompts are U[len/2, len]
-    row = {"bench": "grpo_step", "model": args.model, "world": world, "samples_per_step": samples,
+    row = {"bench": "grpo_step", "model": args.model, "world": world,
+           "placement": f"{args.trainers} trainer + {world - args.trainers} engine ranks" if disjoint else "every rank trains and serves",
+           "samples_per_step": samples,
            "max_tokens": args.max_tokens, "prompt_len": f"U[{args.prompt_len // 2},{args.prompt_len}]", "loss": args.loss,
            "step_s": round(mean("step_s"), 4),
            "rollout_s": round(mean("rollout_s"), 4), "train_s": round(mean("train_s"), 4), "sync_s": round(mean("sync_s"), 5),

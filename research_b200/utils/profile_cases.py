@@ -186,6 +186,34 @@ def case_adamw_allgather() -> None:
     print("ok")
 
 
+def case_moe_train() -> None:
+    """Grouped expert MLP of training, forward + backward, at the Qwen3-30B-A3B layer shape: 4096 tokens, top-8 of 128
+    experts, d = 2048, F = 768 (two warm-up passes, then one pass for the launch list)."""
+    from ..ops.moe_train import GroupedExperts, GroupedPlan
+
+    class Sink:
+        def accumulate_into(self, view):
+            return False
+
+    T, k, E, d, F = 4096, 8, 128, 2048, 768
+    g = torch.Generator(device="cuda").manual_seed(0)
+    h = (torch.randn(T, d, device="cuda", generator=g) * 0.5).bfloat16().requires_grad_(True)
+    wgu = (torch.randn(E * 2 * F, d, device="cuda", generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(E * d, F, device="cuda", generator=g) * 0.02).bfloat16()
+    ggu, gd = torch.empty_like(wgu), torch.empty_like(wd)
+    wt, idx = torch.randn(T, E, device="cuda", generator=g).softmax(-1).topk(k, dim=-1)
+    wt = wt.contiguous().requires_grad_(True)
+    idx32 = idx.to(torch.int32).contiguous()
+    dout = (torch.randn(T, d, device="cuda", generator=g) * 0.1).bfloat16()
+    for _ in range(3):
+        plan = GroupedPlan(idx32, E, d, F)
+        GroupedExperts.apply(h, wt, wgu, ggu, wd, gd, plan, Sink()).backward(dout)
+        h.grad = wt.grad = None
+    torch.cuda.synchronize()
+    ops.check_status()
+    print("ok")
+
+
 CASES = {k[5:]: v for k, v in globals().items() if k.startswith("case_")}
 
 if __name__ == "__main__":

@@ -22,8 +22,15 @@ def model_flops_per_token(cfg, seq: int) -> float:
     """6 * matmul parameters + causal attention (12 * L * d_head * Hq * seq / 2 per token)."""
     d, L, F = cfg.hidden_size, cfg.num_layers, cfg.intermediate_size
     qkv = d * (cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_dim
-    per_layer = qkv + cfg.num_heads * cfg.head_dim * d + 3 * d * F
-    matmul_params = L * per_layer + cfg.vocab_size * d
+    attn = qkv + cfg.num_heads * cfg.head_dim * d
+    dense_layers = L
+    matmul_params = 0.0
+    if getattr(cfg, "is_moe", False):
+        # a token multiplies with the router, its top-k experts and the shared experts (the ACTIVE parameters)
+        dense_layers = min(cfg.first_k_dense_replace, L)
+        Fm = cfg.moe_intermediate_size
+        matmul_params += (L - dense_layers) * (attn + d * cfg.num_experts + 3 * d * Fm * (cfg.num_experts_per_tok + cfg.n_shared_experts))
+    matmul_params += dense_layers * (attn + 3 * d * F) + cfg.vocab_size * d
     return 6.0 * matmul_params + 12.0 * L * cfg.num_heads * cfg.head_dim * seq / 2
 
 
@@ -40,6 +47,8 @@ def main() -> None:
     ap.add_argument("--kernel-table", default="", help="write a table of device time per kernel (one extra step under the "
                                                        "PyTorch profiler, after the timed steps) to this file")
     ap.add_argument("--peak-tflops", type=float, default=1426.3, help="sustained cuBLAS bf16 TFLOP/s per GPU for the MFU line")
+    ap.add_argument("--layers", type=int, default=0, help="keep only the first N layers of the preset (a model that does not "
+                                                          "fit otherwise; the output says so)")
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -55,7 +64,7 @@ def main() -> None:
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    cfg = get_preset(args.model)
+    cfg = get_preset(args.model, num_layers=args.layers) if args.layers else get_preset(args.model)
     kw = dict(loss_fn=args.loss, lr=1e-5, trainer_config=TrainerConfig(micro_batch_size=args.micro_batch), activation_checkpointing=not args.no_checkpointing,
               need_entropy=False)
     backend = FSDPTrainingBackend(cfg, None, **kw) if world > 1 else NativeTrainingBackend(cfg, None, device=dev, **kw)
@@ -88,7 +97,8 @@ def main() -> None:
     tok_s = tokens / (ms.item() * 1e-3)
     mfu = tok_s / world * model_flops_per_token(cfg, args.seq) / (args.peak_tflops * 1e12)
     if local == 0 and int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"metric": "train_tokens_per_s", "model": args.model, "n_gpus": world, "seq_len": args.seq,
+        print(json.dumps({"metric": "train_tokens_per_s", "model": args.model + (f" (first {args.layers} of its layers)" if args.layers else ""),
+                          "n_gpus": world, "seq_len": args.seq,
                           "batch_per_gpu": args.batch, "ms_per_step": round(ms.item(), 2), "value": round(tok_s, 1),
                           "mfu_of_sustained_cublas": round(mfu, 3), "loss": round(float(m.get("loss", 0.0)), 4),
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),

@@ -183,3 +183,72 @@ def test_trajectory_to_samples_uses_engine_token_ids():
     assert len(br) == 2 and br[1].tokens == [1, 2, 3, 4, 5, 9, 9, 6] and br[1].response_length == 1
     t2 = Trajectory.from_dict(json.loads(traj.to_jsonl()))
     assert t2.completions[1].choices[0].token_ids == (6,) and t2.hash() == traj.hash()
+
+
+def test_evaluate_outcomes_resume_and_files(tmp_path):
+    """Three outcomes (success / failed / provider_error), success_rate without the provider errors in its denominator,
+    per-sample files with credentials redacted, resume that re-runs only what is missing or hit a provider error."""
+    from research_b200.agents.evaluation import (EvalReport, compute_summary_metrics, group_by, load_csv, load_jsonl,
+                                                 sanitize_api_keys, simple_evaluate, summarize)
+
+    class Flaky:
+        """Answers the prompt with its digits; rows whose prompt says 'down' always raise a provider error."""
+
+        def __init__(self):
+            self.calls = []
+
+        async def __call__(self, actor, run_config):
+            prompt = actor.trajectory.messages[-1].text()
+            self.calls.append(prompt)
+            if "down" in prompt:
+                raise ProviderError("rate limited", 429)
+            return await ScriptedLLM(["".join(c for c in prompt if c.isdigit())])(actor, run_config)
+
+    llm = Flaky()
+    register_provider("mock", llm)
+
+    def score(traj, row):
+        if row.get("explode"):
+            raise ValueError("scorer cannot read this row")
+        return Score((Metric("correct", float(traj.messages[-1].text() == row["answer"]), 1.0),))
+
+    rows = [{"id": "a", "prompt": "say 12", "answer": "12", "kind": "easy"}, {"id": "b", "prompt": "say 7", "answer": "8", "kind": "easy"},
+            {"id": "c", "prompt": "down 1", "answer": "1", "kind": "hard"}, {"id": "d", "prompt": "say 3", "answer": "3", "explode": True, "kind": "hard"}]
+    cfg = EvalConfig(endpoint=Endpoint(provider="mock", api_key="sk-abcdefghijklmnop"), max_turns=1, output_dir=str(tmp_path), eval_name="mix",
+                     score_fn=score, n_retries=1, retry_delays=(0.0,))
+    seen = []
+    rep = asyncio.run(evaluate(rows, cfg, on_sample_done=lambda s, done, total: seen.append((s.sample_id, done, total))))
+    by_id = {s.sample_id: s for s in rep.samples}
+    assert [by_id[i].status for i in "abcd"] == ["success", "success", "provider_error", "failed"]
+    assert by_id["c"].attempts == 2 and by_id["d"].error.startswith("ValueError")
+    sm = rep.summary
+    assert sm["successful_samples"] == 2 and sm["provider_errors"] == 1 and sm["failed_samples"] == 1
+    assert sm["success_rate"] == pytest.approx(2 / 3) and sm["completion_rate"] == 0.5
+    assert sm["error_breakdown"] == {"ValueError": 1} and sm["provider_error_breakdown"] == {"mock": 1}
+    assert sm["min_correct"] == 0.0 and sm["max_correct"] == 1.0 and sm["std_correct"] == pytest.approx(0.5)
+    assert sorted(x[0] for x in seen) == list("abcd") and seen[-1][1:] == (4, 4)
+    run = tmp_path / "mix"
+    assert sorted(p.name for p in (run / "samples").iterdir()) == ["a.json", "b.json", "c.json", "d.json"]
+    assert "sk-abcdefghijklmnop" not in (run / "report.json").read_text()
+    assert sanitize_api_keys({"x": [{"api_key": "sk-1"}, "sk-abcdefghijklmnop"], "n": 1}) == {"x": [{"api_key": "***REDACTED***"}, "***REDACTED***"], "n": 1}
+    back = EvalReport.load(run)
+    assert [s.sample_id for s in back.samples] == list("abcd") and back.samples[0].score.reward == 1.0
+    assert back.samples[0].trajectory.messages[-1].text() == "12"
+    # resume: only the provider-error sample runs again
+    llm.calls.clear()
+    rep2 = asyncio.run(evaluate(rows, cfg, resume=True))
+    assert llm.calls == ["down 1", "down 1"] and rep2.config["resumed_samples"] == 3
+    groups = group_by(rep.samples, key=lambda s: s.input["kind"])
+    assert summarize(groups)["easy"]["mean_reward"] == 0.5 and summarize(rep.samples)["n"] == 4
+    assert compute_summary_metrics([]) == {"num_samples": 0.0}
+    # dataset files
+    import json as _json
+
+    (tmp_path / "d.jsonl").write_text("\n".join(_json.dumps(r) for r in rows[:2]) + "\n\n")
+    (tmp_path / "d.csv").write_text("id,prompt,answer\nq,say 5,5\n")
+    assert [r["id"] for r in load_jsonl(tmp_path / "d.jsonl")] == ["a", "b"] and next(load_csv(tmp_path / "d.csv"))["answer"] == "5"
+    cfg2 = EvalConfig(endpoint=Endpoint(provider="mock"), max_turns=1, score_fn=score, eval_name="files")
+    assert asyncio.run(simple_evaluate(tmp_path / "d.csv", cfg2)).summary["mean_reward"] == 1.0
+    assert asyncio.run(simple_evaluate(tmp_path / "d.jsonl", cfg2)).dataset_path.endswith("d.jsonl")
+    with pytest.raises(ValueError):
+        asyncio.run(simple_evaluate(tmp_path / "d.txt", cfg2))

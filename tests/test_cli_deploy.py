@@ -97,3 +97,73 @@ def test_session_frontend(tmp_path):
     msgs = client.get(f"/api/session/{sid}").json()["messages"]
     assert [m["role"] for m in msgs] == ["user", "assistant", "user", "assistant"]
     assert client.post(f"/api/session/{sid}/message", json={"content": " "}).status_code == 400
+
+
+def test_session_doctor_and_chat_flags(tmp_path, capsys):
+    """Duplicate / orphaned tool results are found and dropped into a child session, trimming writes another child,
+    `chat --continue` resumes the latest session, `--no-session` stores nothing, `--context` reaches the system prompt."""
+    from research_b200.agents import ToolCall
+    from research_b200.agents import doctor
+
+    store_dir = str(tmp_path / "sessions")
+    store = FileSessionStore(store_dir)
+
+    async def build():
+        sid = await store.create({"provider": "cli-mock", "model": "m"})
+        call = ToolCall("call_1", "add", {"value": 2})
+        msgs = [Message("user", "add two"), Message("assistant", "", tool_calls=(call,)),
+                Message("tool", "2", tool_call_id="call_1"), Message("tool", "2", tool_call_id="call_1"),
+                Message("tool", "lost", tool_call_id="call_gone"), Message("assistant", "done"), Message("user", "x" * 120_000)]
+        for m in msgs:
+            await store.append_message(sid, m)
+        return sid
+
+    sid = asyncio.run(build())
+    _, msgs = asyncio.run(store.get(sid))
+    kinds = sorted(i.kind for i in doctor.diagnose(msgs))
+    assert kinds == ["duplicate_tool_result", "orphaned_tool_result", "oversized_message"]
+    assert cli.main(["sessions", "doctor", sid, "--store", store_dir, "--fix"]) == 0
+    out = capsys.readouterr().out
+    assert "duplicate_tool_result" in out and "created fixed session" in out
+    children = [s for s in asyncio.run(store.list()) if s.parent_id == sid]
+    assert len(children) == 1 and children[0].tags["doctor"] == "fixed" and children[0].num_messages == 5
+    assert [i.kind for i in doctor.diagnose(asyncio.run(store.get(children[0].session_id))[1])] == ["oversized_message"]
+    assert cli.main(["sessions", "doctor", sid, "--store", store_dir, "--trim", "1"]) == 0
+    trimmed = [s for s in asyncio.run(store.list()) if s.tags.get("doctor") == "trimmed"]
+    assert len(trimmed) == 1 and trimmed[0].num_messages == 6
+    assert cli.main(["sessions", "doctor", sid, "--store", store_dir, "--trim", "99"]) == 1
+    capsys.readouterr()
+    assert cli.main(["sessions", "handoff", sid, "--store", store_dir, "--goal", "finish the sum"]) == 0
+    assert "finish the sum" in capsys.readouterr().out
+    # an unanswered tool call followed by more conversation is reported but not auto-fixed
+    broken = [Message("user", "q"), Message("assistant", "", tool_calls=(ToolCall("c9", "add", {}),)), Message("user", "still there?")]
+    (issue,) = doctor.diagnose(broken)
+    assert issue.kind == "unanswered_tool_call" and not issue.fixable
+    assert doctor.format_time_ago(0, now=30) == "just now" and doctor.format_time_ago(0, now=7200) == "2h ago" and doctor.format_time_ago(0, now=3 * 86400) == "3d ago"
+    assert cli.parse_model_string("anthropic/claude-x") == ("anthropic", "claude-x")
+    with pytest.raises(ValueError):
+        cli.parse_model_string("claude-x")
+
+    # chat flags
+    class Echo:
+        """Replies with the system prompt it was given, so the test can see what reached the model."""
+
+        async def __call__(self, actor, run_config):
+            sys_text = " | ".join(m.text() for m in actor.trajectory.messages if m.role == "system")
+            return await ScriptedLLM([f"system was: {sys_text}"])(actor, run_config)
+
+    register_provider("cli-mock", Echo())
+    ctx = tmp_path / "notes.txt"
+    ctx.write_text("the deadline is friday")
+    store2 = str(tmp_path / "s2")
+    assert cli.main(["chat", "--model", "cli-mock/any", "--store", store2, "-p", "hi", "--system-prompt", "be terse",
+                     "--context", "user likes tables", "--context-file", str(ctx), "-q"]) == 0
+    out = capsys.readouterr().out
+    assert "be terse" in out and "user likes tables" in out and "the deadline is friday" in out
+    first = asyncio.run(FileSessionStore(store2).list())
+    assert len(first) == 1
+    assert cli.main(["chat", "--provider", "cli-mock", "--store", store2, "-p", "again", "--continue"]) == 0
+    after = asyncio.run(FileSessionStore(store2).list())
+    assert len(after) == 1 and after[0].num_messages > first[0].num_messages
+    assert cli.main(["chat", "--provider", "cli-mock", "--store", str(tmp_path / "s3"), "-p", "hi", "--no-session"]) == 0
+    assert not (tmp_path / "s3").exists() or not list((tmp_path / "s3").iterdir())
