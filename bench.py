@@ -701,13 +701,18 @@ def run_reference_train(args) -> dict:
     if not os.path.isdir(os.path.join(ref_dir, "rollouts")):
         return {"impl": "reference", "unavailable": "baseline/_ref/rollouts is absent (reference not installed on this box)"}
     sys.path.insert(0, ref_dir)
-    standin = _install_trio_standin()
+    # --impl reference imports the reference as the image allows it: its training package imports trio at module level
+    # and trio is not installed, so that arm reports itself unavailable. --impl reference-standin is a separate,
+    # labelled context measurement: the same unmodified package imported with a stand-in for trio.Event.
+    standin = _install_trio_standin() if args.impl == "reference-standin" else False
     try:
         from rollouts.training.backends.fsdp import FSDPConfig as RefFSDPConfig
         from rollouts.training.backends.fsdp import FSDPTrainingBackend as RefBackend
         from rollouts.training.losses import sft_loss as ref_sft_loss
     except Exception as e:
-        return {"impl": "reference", "unavailable": f"reference training backend cannot be imported: {type(e).__name__}: {e}"[:300]}
+        return {"impl": args.impl, "unavailable":
+                (f"reference training backend cannot be imported: {type(e).__name__}: {e} (rollouts/training/types.py imports trio, "
+                 "which is neither in this image nor in its wheelhouse; same-box context: --impl library, --impl reference-standin)")[:400]}
     import tempfile
 
     import torch
@@ -750,7 +755,7 @@ def run_reference_train(args) -> dict:
     if standin:
         extra["import_note"] = ("trio is not in this image: a stand-in module provides trio.Event (used by the reference's futures) so that "
                                 "the unmodified training package imports; the timed path never awaits it")
-    return _time_train_arm(args, step, world, rank, local, "reference", extra)
+    return _time_train_arm(args, step, world, rank, local, args.impl, extra)
 
 
 def main() -> None:
@@ -758,7 +763,10 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--impl", choices=["native", "reference", "library"], default="native")
+    ap.add_argument("--impl", choices=["native", "reference", "library", "reference-standin"], default="native",
+                    help="reference = the unmodified reference through its own API (unavailable for training where its imports "
+                         "cannot be met); library = HF Llama + FSDP2 + torch AdamW driven by this script; reference-standin = the "
+                         "reference's FSDP backend class imported with a stand-in for the missing trio module (context only)")
     ap.add_argument("--workload", choices=["train", "rollout", "serving"], default="train",
                     help="train = sharded training step on the Llama-3-8B shape, seq 4096, one sequence per GPU (the flagship); "
                          "rollout = engine decode, 1024 requests, prompts U[128,1024], 512 new tokens, batch 256; "
@@ -780,10 +788,11 @@ def main() -> None:
     if args.workload == "train":
         args.steps = 10 if args.steps is None else args.steps
         args.warmup = 3 if args.warmup is None else args.warmup
-        out = {"native": run_train, "reference": run_reference_train, "library": run_library_train}[args.impl](args)
+        out = {"native": run_train, "reference": run_reference_train, "library": run_library_train,
+               "reference-standin": run_reference_train}[args.impl](args)
     else:
-        if args.impl == "library":
-            out = {"impl": "library", "unavailable": "the library baseline exists for the train workload only"}
+        if args.impl in ("library", "reference-standin"):
+            out = {"impl": args.impl, "unavailable": "this arm exists for the train workload only"}
         else:
             if args.impl == "native":
                 set_workload(args.workload)
