@@ -542,7 +542,34 @@ def run_train(args) -> dict:
     if checks is not None:
         out["selfcheck"] = checks
     _ = dist
+    if world == 1 and args.extras and args.model == "llama-3-8b":
+        # the same shape's rollout decode rate, outside the timed region, in a child process (a failure there cannot
+        # take this line with it): the trainer's memory goes back to the driver first
+        del backend, batches, dev_batches, m, o
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        out["extras"] = _rollout_decode_extra(args.model)
     return out if rank == 0 else {}
+
+
+def _rollout_decode_extra(model: str) -> dict:
+    """``bench.py --workload rollout --model <model>`` on this GPU as a child process; its headline numbers, or why not."""
+    import subprocess
+
+    cmd = [sys.executable, os.path.abspath(__file__), "--workload", "rollout", "--model", model, "--steps", "100", "--warmup", "5"]
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        line = next((ln for ln in reversed(proc.stdout.splitlines()) if ln.startswith("{")), None)
+        if proc.returncode != 0 or line is None:
+            return {"rollout_decode": {"error": f"child exited {proc.returncode}: {(proc.stderr or proc.stdout)[-300:]}"}}
+        d = json.loads(line)
+        return {"rollout_decode": {"metric": d["metric"], "model": model, "tokens_per_s": d["value"], "ms_per_step": d["ms_per_step"],
+                                   "e2e_tokens_per_s": d["e2e"]["value"], "batch": d["config"].get("global_batch"),
+                                   "note": "measured after the timed region by `bench.py --workload rollout` in a child process"}}
+    except Exception as e:   # noqa: BLE001 - an extra must never cost the headline
+        return {"rollout_decode": {"error": f"{type(e).__name__}: {e}"[:300]}}
 
 
 def _hf_llama(args, dev):
@@ -779,6 +806,8 @@ def main() -> None:
                     choices=["shard_optimizer_and_grads", "full_shard"],
                     help="train, N > 1: replicated bf16 parameters with sharded gradients / optimizer state, or parameters "
                          "sharded too (layer weights gathered from the peers inside the consuming GEMM launch)")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="train, 1 GPU: skip the rollout-decode measurement of the same model that follows the timed region")
     ap.add_argument("--peak-tflops", type=float, default=1426.3, help="sustained cuBLAS bf16 TFLOP/s per GPU for the MFU figure")
     ap.add_argument("--ep", action="store_true", help="engine workloads, MoE models: data-parallel engines with the experts split over all GPUs")
     ap.add_argument("--tp", action="store_true", help="engine workloads: one tensor-parallel engine over all GPUs instead of replicas")

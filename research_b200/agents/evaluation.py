@@ -201,6 +201,7 @@ async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfi
     last_err: str | None = None
     status = "provider_error"
     attempts = 0
+    failing_provider = ""
     for attempt in range(config.n_retries + 1):
         attempts = attempt + 1
         try:
@@ -228,12 +229,13 @@ async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfi
             break
         except (ProviderError, asyncio.TimeoutError, ConnectionError) as e:
             last_err = f"{type(e).__name__}: {e}"
+            failing_provider = getattr(e, "provider", "") or failing_provider
             if attempt < config.n_retries:
                 await asyncio.sleep(config.retry_delays[min(attempt, len(config.retry_delays) - 1)])
         except Exception as e:   # noqa: BLE001 - a broken environment or scorer fails this sample, not the run
             last_err, status = f"{type(e).__name__}: {e}", "failed"
             break
-    provider = getattr(config.endpoint, "provider", None)
+    provider = failing_provider or getattr(config.endpoint, "provider", None)
     return EvalSample(sample_id, row, Trajectory(), Score(), None, last_err, attempts, time.time() - t0,
                       {"status": status, "provider": provider, "turns_used": 0, "total_tokens": 0})
 

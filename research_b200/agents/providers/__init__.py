@@ -6,10 +6,11 @@ from __future__ import annotations
 from typing import Awaitable, Callable
 
 from ..dtypes import Actor, RunConfig
-from .base import (ContextTooLongError, NonRetryableError, ProviderError, RateLimiter, async_retry, backoff_delay,
-                   classify_http_status, retry)
+from .base import (ContextTooLongError, NonRetryableError, ProviderError, RateLimiter, add_cache_control_to_last_content,
+                   async_retry, backoff_delay, calculate_cost_from_usage, classify_http_status, classify_server_error,
+                   explain_server_error, parse_context_overflow, prepare_messages_for_llm, retry, sanitize_request_for_logging)
 from .chat import ScriptedLLM, messages_to_openai, rollout_openai_compatible
-from .models import MODELS, ModelInfo, estimate_cost, get_model
+from .models import MODELS, ModelInfo, estimate_cost, get_model, get_models, get_providers, register_model
 from .streaming import (aggregate_anthropic_stream, aggregate_google_stream, aggregate_openai_responses_stream,
                         aggregate_openai_stream, messages_to_anthropic, messages_to_google, messages_to_openai_responses,
                         rollout_anthropic, rollout_google, rollout_openai_responses, rollout_openai_streaming, sse_events)
@@ -40,7 +41,9 @@ def get_provider(name: str, token_level: bool = False) -> RolloutFn:
     return table[name]
 
 
-__all__ = ["ContextTooLongError", "NonRetryableError", "ProviderError", "RateLimiter", "async_retry", "backoff_delay",
+__all__ = ["add_cache_control_to_last_content", "calculate_cost_from_usage", "classify_server_error", "explain_server_error",
+           "parse_context_overflow", "prepare_messages_for_llm", "sanitize_request_for_logging", "get_models", "get_providers",
+           "register_model", "ContextTooLongError", "NonRetryableError", "ProviderError", "RateLimiter", "async_retry", "backoff_delay",
            "classify_http_status", "retry", "ScriptedLLM", "messages_to_openai", "rollout_openai_compatible", "MODELS",
            "ModelInfo", "estimate_cost", "get_model", "build_input_ids_from_trajectory", "generate_sglang",
            "generate_vllm", "rollout_native_token_level", "rollout_sglang_token_level", "rollout_vllm_token_level",

@@ -5,20 +5,22 @@ OpenAI and friends) and a scripted mock used by tests
 from __future__ import annotations
 
 import json
+import logging
 import uuid
 from dataclasses import replace
 from typing import Any
 
 from ..dtypes import (Actor, ChatCompletion, Choice, Cost, Message, RunConfig, TextDelta, ToolCall, ToolCallEnd, ToolCallStart,
                       Usage)
-from .base import NonRetryableError, async_retry, classify_http_status
+from .base import (NonRetryableError, async_retry, classify_http_status, classify_server_error, explain_server_error,
+                   prepare_messages_for_llm, sanitize_request_for_logging)
 from .models import estimate_cost
 from .tool_parsers import parse_tool_calls
 
 
 def messages_to_openai(actor: Actor) -> list[dict[str, Any]]:
     out = []
-    for m in actor.trajectory.messages:
+    for m in prepare_messages_for_llm(list(actor.trajectory.messages)):
         d: dict[str, Any] = {"role": m.role, "content": m.text()}
         calls = m.get_tool_calls()
         if m.role == "assistant" and calls:
@@ -40,6 +42,10 @@ async def _chat_completion(ep, payload: dict) -> dict:
     async with httpx.AsyncClient(timeout=ep.timeout) as client:
         r = await client.post(f"{ep.api_base.rstrip('/')}/v1/chat/completions", json=payload, headers=headers)
     if r.status_code != 200:
+        kind = classify_server_error(r.status_code, r.text)
+        if kind in ("context_length", "invalid_param"):     # retrying cannot help: say what will, once
+            logging.getLogger(__name__).error("%s\nrequest: %s", explain_server_error(kind, max_tokens=payload.get("max_tokens"), param_keys=list(payload)),
+                                              sanitize_request_for_logging(payload))
         raise classify_http_status(r.status_code, r.text, ep.provider)
     return r.json()
 

@@ -340,9 +340,14 @@ def _append(actor: Actor, comp: ChatCompletion) -> Actor:
 
 async def rollout_anthropic(actor: Actor, run_config: RunConfig) -> Actor:
     ep = actor.endpoint
-    system, msgs = messages_to_anthropic(actor.trajectory.messages)
+    from .base import add_cache_control_to_last_content, prepare_messages_for_llm
+
+    system, msgs = messages_to_anthropic(prepare_messages_for_llm(list(actor.trajectory.messages)))
+    extra = dict(ep.extra_params)
+    if extra.pop("prompt_caching", True):      # a cache break point at the end of the conversation so far (at most four per request)
+        msgs = add_cache_control_to_last_content(msgs)
     payload: dict[str, Any] = {"model": ep.model, "max_tokens": ep.max_tokens, "messages": msgs, "stream": True,
-                               "temperature": ep.temperature, **ep.extra_params}
+                               "temperature": ep.temperature, **extra}
     if system:
         payload["system"] = system
     if actor.tools:

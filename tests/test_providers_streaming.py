@@ -131,3 +131,71 @@ def test_transform_messages():
     assert isinstance(same[1].content[0], ThinkingContent)
     inl = transform_messages(msgs, source=("a", "1"), target=("b", "2"), inline_thinking="<think>{thinking}</think>")
     assert inl[1].content[0].text == "<think>secret</think>"
+
+
+def test_provider_request_hygiene_and_errors():
+    """Context-overflow parsing in the three providers' wordings, error kinds and advice, log sanitising of inline images,
+    prompt-cache markers capped at four, UI-only tool details stripped, cache-aware cost, retry exhaustion wrapped."""
+    import asyncio
+
+    import pytest
+
+    from research_b200.agents.dtypes import Message, Usage
+    from research_b200.agents.providers import (ContextTooLongError, NonRetryableError, ProviderError, add_cache_control_to_last_content,
+                                                 async_retry, calculate_cost_from_usage, classify_http_status, classify_server_error,
+                                                 explain_server_error, get_model, get_models, get_providers, parse_context_overflow,
+                                                 prepare_messages_for_llm, sanitize_request_for_logging)
+
+    openai_msg = "This model's maximum context length is 8192 tokens. However, you requested 9000 tokens (8000 in the messages, 1000 in the completion)."
+    assert parse_context_overflow(openai_msg) == (9000, 8192)
+    assert parse_context_overflow("prompt is too long: 210000 tokens > 200000 maximum") == (210000, 200000)
+    assert parse_context_overflow("The input token count (1200000) exceeds the maximum number of tokens allowed (1048576).") == (1200000, 1048576)
+    assert parse_context_overflow("context window exceeded") == (None, None) and parse_context_overflow("bad json") is None
+    err = classify_http_status(400, openai_msg, "vllm")
+    assert isinstance(err, ContextTooLongError) and (err.current_tokens, err.max_tokens, err.provider) == (9000, 8192, "vllm")
+    assert classify_server_error(200, "") == "success" and classify_server_error(400, "logprobs is not a valid parameter") == "invalid_param"
+    assert classify_server_error(429, "slow down") == "rate_limit" and classify_server_error(401, "") == "auth"
+    assert classify_server_error(503, "") == "server" and classify_server_error(404, "") == "http_error"
+    assert "try 2048" in explain_server_error("context_length", max_tokens=4096) and "echo" in explain_server_error("invalid_param", param_keys=["echo"])
+    assert isinstance(classify_http_status(401, ""), NonRetryableError)
+
+    req = {"model": "m", "api_key": "sk-secret", "messages": [
+        {"role": "user", "content": [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + "A" * 200_000}},
+                                     {"type": "image", "source": {"type": "base64", "data": "B" * 50_000}},
+                                     {"type": "text", "text": "x" * 2000}]}]}
+    clean = sanitize_request_for_logging(req)
+    blob = str(clean)
+    assert len(blob) < 1500 and "<image: 200022 bytes>" in blob and "<image: 50000 bytes>" in blob and "(2000 chars total)" in blob
+    assert clean["api_key"] == "***" and len(req["messages"][0]["content"][2]["text"]) == 2000      # the original is untouched
+
+    msgs = [{"role": "user", "content": "hello"}]
+    marked = add_cache_control_to_last_content(msgs)
+    assert marked[0]["content"] == [{"type": "text", "text": "hello", "cache_control": {"type": "ephemeral"}}] and msgs[0]["content"] == "hello"
+    four = [{"role": "user", "content": [{"type": "text", "text": str(i), "cache_control": {"type": "ephemeral"}}]} for i in range(4)]
+    capped = add_cache_control_to_last_content(four + [{"role": "user", "content": [{"type": "text", "text": "new"}]}])
+    assert "cache_control" not in capped[-1]["content"][0]
+
+    tool = Message("tool", "ok", tool_call_id="c1", metadata={"details": {"diff": "x" * 1000}, "kept": 1})
+    sent = prepare_messages_for_llm([Message("user", "q"), tool])
+    assert len(sent) == 2 and sent[1].metadata == {"kept": 1} and tool.metadata["details"]
+
+    sonnet = get_model("claude-sonnet-4-5")
+    cost = calculate_cost_from_usage(Usage(1_000_000, 100_000, cache_read_tokens=2_000_000, cache_write_tokens=500_000), sonnet)
+    assert (cost.input, cost.output, cost.cache_read, cost.cache_write) == (3.0, 1.5, pytest.approx(0.6), pytest.approx(1.875))
+    assert calculate_cost_from_usage(Usage(10, 10), None).total == 0.0
+    assert get_model("gpt-4o-2024-08-06").name == "gpt-4o" and get_model("gpt-4o", provider="anthropic") is None
+    assert "anthropic" in get_providers() and all(m.provider == "google" for m in get_models("google"))
+
+    calls = {"n": 0}
+
+    async def nosleep(_):
+        return None
+
+    @async_retry(max_attempts=2, sleep=nosleep, wrap_as_provider_error="anthropic")
+    async def always_down():
+        calls["n"] += 1
+        raise ConnectionError("reset")
+
+    with pytest.raises(ProviderError) as ei:
+        asyncio.run(always_down())
+    assert ei.value.provider == "anthropic" and ei.value.attempts == 2 and isinstance(ei.value.original_error, ConnectionError) and calls["n"] == 2
