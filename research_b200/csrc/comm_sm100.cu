@@ -21,6 +21,8 @@
 // Replaces: FSDP2 NCCL reduce-scatter + clip_grad_norm_ + torch AdamW + all-gather
 // (rollouts/training/backends/fsdp.py:289-322, 398-452) and the per-tensor dist.broadcast /
 // disk round trip of the weight sync (rollouts/training/weight_sync.py:233-282).
+#include <climits>
+
 #include "common.cuh"
 
 #define RB_MAX_RANKS 8
@@ -45,6 +47,41 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int slo
   }
   __syncthreads();
   if (threadIdx.x == 0 && counter != nullptr) *counter = ep;
+}
+// Element-wise maximum of four integers over the ranks without leaving the device: every rank stores its values into
+// every peer's exchange buffer (slot [epoch parity][source rank][4]), raises its flag there, waits (bounded) for all
+// flags and reduces its own copy. out[0..3] = maxima, out[4] = 1 if every peer answered in time, else 0 (then the
+// epoch is not advanced and nothing in the shared status word is touched: the caller decides what a silent peer means).
+// Two parities suffice: a rank can start epoch e + 2 only after every peer has raised its flag of e + 1, which a peer
+// does after reading the values of e.
+__global__ void symm_agree_max_kernel(PeerPtrs xchg, PeerPtrs flags, int rank, int world, int slot, int* counter,
+                                      int v0, int v1, int v2, int v3, int* out, unsigned long long budget_ns) {
+  __shared__ int ep;
+  __shared__ int ok_all;
+  if (threadIdx.x == 0) { ep = *counter + 1; ok_all = 1; }
+  __syncthreads();
+  const int parity = ep & 1;
+  const int r = threadIdx.x;
+  int private_status = 0;
+  if (r < world) {
+    int* dst = reinterpret_cast<int*>(xchg.p[r]) + (parity * world + rank) * 4;
+    st_relaxed_sys(dst + 0, v0); st_relaxed_sys(dst + 1, v1); st_relaxed_sys(dst + 2, v2); st_relaxed_sys(dst + 3, v3);
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, ep);
+    if (!wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, ep, &private_status, budget_ns)) ok_all = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int* mine = reinterpret_cast<const int*>(xchg.p[rank]) + parity * world * 4;
+    int m[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+    if (ok_all) {
+      for (int q = 0; q < world; ++q)
+        for (int i = 0; i < 4; ++i) m[i] = max(m[i], ld_relaxed_sys(mine + q * 4 + i));
+      *counter = ep;
+    }
+    for (int i = 0; i < 4; ++i) out[i] = m[i];
+    out[4] = ok_all;
+  }
 }
 __global__ void symm_signal_kernel(PeerPtrs flags, int rank, int world, int slot, int epoch) {
   __threadfence_system();
@@ -388,6 +425,76 @@ __global__ void pull_sum_kernel(PeerPtrs src, const __nv_bfloat16* __restrict__ 
                                                   pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
   }
 }
+
+// The same sum with its synchronisation inside the launch (tensor-parallel all-reduce of decode-sized outputs as
+// GEMM + this kernel, nothing else): block 0 tells every peer that this rank's slab is complete (the GEMM before this
+// launch on the stream wrote it), every block waits (bounded) for all peers' flags, sums, and the last block to
+// finish tells every peer that their slabs have been read (one increment of the peer's acknowledgement counter per
+// call) and raises the count this rank's NEXT slab write has to wait for (`need`, consumed by the GEMM's producer).
+// Epochs and tickets live on the device, so a captured launch replays correctly. sync: [0] epoch, [1] ticket.
+__global__ void pull_sum_sync_kernel(PeerPtrs src, const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
+                                     long long nvec, int world, int rank, PeerPtrs flags, int slot, int* sync, PeerPtrs ack,
+                                     int* need, int* status, unsigned long long budget_ns) {
+  __shared__ int ep_s;
+  __shared__ int failed;
+  if (threadIdx.x == 0) { ep_s = ld_relaxed_sys(sync) + 1; failed = 0; }
+  __syncthreads();
+  const int ep = ep_s;
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + slot * world + rank, ep);
+  }
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    if (!wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + threadIdx.x, ep, status, budget_ns)) failed = 1;
+  }
+  __syncthreads();
+  if (!failed) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+      float acc[8];
+      {
+        const uint4 r = reinterpret_cast<const uint4*>(residual)[i];
+        const uint32_t ri[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(ri[j]);
+          acc[2 * j] = f.x; acc[2 * j + 1] = f.y;
+        }
+      }
+      uint4 part[RB_MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < RB_MAX_RANKS; ++r)
+        if (r < world) part[r] = ld_peer_16(reinterpret_cast<const uint4*>(src.p[r]) + i);   // rank order: same bits on every rank
+#pragma unroll
+      for (int r = 0; r < RB_MAX_RANKS; ++r) {
+        if (r < world) {
+          const uint32_t pi[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(pi[j]);
+            acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+          }
+        }
+      }
+      reinterpret_cast<uint4*>(out)[i] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                    pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int old = atomicAdd(sync + 1, 1);
+    if (old == (int)gridDim.x - 1) {          // every block of this launch is done reading the peers' slabs
+      sync[1] = 0;
+      if (!failed) {
+        sync[0] = ep;
+        *need += world - 1;
+        __threadfence_system();
+        for (int r = 0; r < world; ++r)
+          if (r != rank) asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(reinterpret_cast<int*>(ack.p[r])) : "memory");
+      }
+    }
+  }
+}
 }  // namespace rb
 using namespace rb;
 
@@ -411,6 +518,25 @@ extern "C" int rb_symm_barrier(void* const* flag_ptrs, int rank, int world, int 
                                int* status, cudaStream_t s) {
   if (world < 1 || world > RB_MAX_RANKS) return -1;
   symm_barrier_kernel<<<1, 32, 0, s>>>(make_ptrs(flag_ptrs, world), rank, world, slot, epoch, counter, status, g_wait_budget_ns);
+  return RB_OK();
+}
+extern "C" int rb_pull_sum_sync(void* const* src_ptrs, const void* residual, void* out, long long n, int world, int rank,
+                                void* const* flag_ptrs, int slot, int* sync, void* const* ack_ptrs, int* need, int* status,
+                                cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || n <= 0 || n % 8 != 0 || sync == nullptr || need == nullptr) return -1;
+  const long long nvec = n / 8;
+  long long grid = (nvec + 255) / 256;
+  if (grid > 148 * 2) grid = 148 * 2;      // every block must be resident: they all wait for the peers
+  pull_sum_sync_kernel<<<(unsigned)grid, 256, 0, s>>>(make_ptrs(src_ptrs, world), (const __nv_bfloat16*)residual, (__nv_bfloat16*)out,
+                                                      nvec, world, rank, make_ptrs(flag_ptrs, world), slot, sync,
+                                                      make_ptrs(ack_ptrs, world), need, status, g_wait_budget_ns);
+  return RB_OK();
+}
+extern "C" int rb_symm_agree_max(void* const* xchg_ptrs, void* const* flag_ptrs, int rank, int world, int slot, int* counter,
+                                 int v0, int v1, int v2, int v3, int* out, unsigned long long budget_ns, cudaStream_t s) {
+  if (world < 1 || world > RB_MAX_RANKS || counter == nullptr || out == nullptr) return -1;
+  symm_agree_max_kernel<<<1, 32, 0, s>>>(make_ptrs(xchg_ptrs, world), make_ptrs(flag_ptrs, world), rank, world, slot, counter,
+                                         v0, v1, v2, v3, out, budget_ns ? budget_ns : g_wait_budget_ns);
   return RB_OK();
 }
 extern "C" int rb_symm_signal(void* const* flag_ptrs, int rank, int world, int slot, int epoch, cudaStream_t s) {

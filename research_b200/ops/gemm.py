@@ -184,6 +184,7 @@ def gemm(
     norm_eps: float | None = None,
     b_gather=None,
     carry_gather=None,
+    wait_flag: tuple[int, int] | None = None,
 ) -> torch.Tensor:
     """``C[M,N] = alpha * op(A) @ op(B)^T (+bias) (+ beta * residual)``.
 
@@ -192,6 +193,10 @@ def gemm(
     and its tiles start part by part as the slabs land (all-gather fused into the consuming GEMM). With
     ``carry_gather=w`` the launch computes its own, unrelated product and fetches ``w`` on the side for the launch
     that follows (the weight-gradient GEMM carries the gather for the data-gradient GEMM).
+
+    ``wait_flag=(flag_address, value_address)``: the launch's tile producers wait (bounded) until the int at
+    ``flag_address`` has reached the int at ``value_address`` before their first load, and so before anything is stored:
+    a launch that overwrites a buffer other GPUs read waits for their acknowledgements this way, inside the launch.
 
     ``norm_eps`` folds an RMSNorm of A's rows into the launch: ``C = rstd(row) * (A @ B^T) (+bias)`` with
     ``rstd = rsqrt(mean(A[row]^2) + norm_eps)``; together with the norm weight multiplied into B's columns
@@ -246,7 +251,7 @@ def gemm(
         N, Kb = b.shape
     assert K == Kb, f"K mismatch: {K} vs {Kb}"
     gather = b_gather if b_gather is not None else carry_gather
-    if (gather is None and not swiglu and norm_eps is None and alpha == 1.0 and beta == 1.0 and bn == 0 and max_ctas == 0 and split_k in (0, 1)
+    if (gather is None and wait_flag is None and not swiglu and norm_eps is None and alpha == 1.0 and beta == 1.0 and bn == 0 and max_ctas == 0 and split_k in (0, 1)
             and not cluster_split and _use_pair_kernel(M, N, K, a_mn_major, b_mn_major)):
         return gemm2(a, b, bias, residual, out, a_mn_major=a_mn_major, b_mn_major=b_mn_major, out_f32=out_f32)
     if out is None:
@@ -309,6 +314,9 @@ def gemm(
         # one [128 x bn] fp32 tile per (output tile, K slice); padded for the widest tile the kernel may pick
         ws, tickets = _splitk_scratch(a.device, split_k * (-(-M // 128) * 128) * (-(-N // 256) * 256), (-(-M // 128)) * (-(-N // 32)))
         args.split_k, args.splitk_ws, args.splitk_tickets = split_k, ws.data_ptr(), tickets.data_ptr()
+    if wait_flag is not None:
+        assert gather is None, "a launch waits either for a gather's parts or for a flag"
+        args.a_ready, args.ready_epoch_ptr = wait_flag
     args.status = status_tensor(a.device).data_ptr()
     rc = _lib().rb_gemm_bf16_ex(ctypes.byref(args), stream_handle(a.device))
     check_rc(rc, "rb_gemm_bf16_ex")

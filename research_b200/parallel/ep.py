@@ -4,8 +4,9 @@ Every rank runs a whole engine of its own (scheduler, KV cache, attention and de
 requests; only the experts are split over the ranks. The MoE layers' dispatch and combine are collectives
 (peer stores plus device barriers, ``parallel/moe.py``), so every rank has to run the same number of MoE
 forwards in the same order. ``agree`` is the control plane for that: before each step the ranks exchange what
-they are about to run (a MAX all-reduce of a few flags on a CPU-side group) and a rank with nothing of its own
-runs an idle pass, which feeds the MoE layers a padding batch.
+they are about to run (the maximum of a few flags: on GPUs one small kernel that stores the values into every peer's
+memory, waits for the peers' flags and reduces, `PeerComm.agree_max`; on CPU groups a gloo all-reduce) and a rank with
+nothing of its own runs an idle pass, which feeds the MoE layers a padding batch.
 
 The reference serves MoE models through external engines only (rollouts/inference/backends.py:1-60 starts
 SGLang / vLLM servers); this is the in-tree equivalent of their ``--dp --enable-dp-attention --ep`` mode.
@@ -32,7 +33,9 @@ class ExpertParallel:
         self.comm = comm
         self.rank, self.world = comm.rank, comm.world
         self.timeout_s = timeout_s
-        if cpu_group is None and self.world > 1:
+        # GPUs exchange the flags through peer memory; the host-side group is only for ranks without one
+        self.device_agree = bool(comm.on_gpu) and self.world > 1
+        if cpu_group is None and self.world > 1 and not self.device_agree:
             # agreement travels over a host-side group of its own: it never queues behind device work, and its
             # timeout doubles as the failure detector of the lock-step loop
             cpu_group = dist.new_group(backend="gloo", timeout=timedelta(seconds=timeout_s))
@@ -45,6 +48,15 @@ class ExpertParallel:
         assert len(flags) <= 4
         if self.world == 1:
             return tuple(int(f) for f in flags)
+        if self.device_agree:
+            # the wait inside the kernel is bounded by the same timeout the host-side group would use; a peer that
+            # stays silent that long is reported before anything else is launched for the step
+            got = self.comm.agree_max(flags, budget_s=self.timeout_s)
+            if got is None:
+                raise PeerFailure(f"rank {self.rank}: expert-parallel agreement failed after {self.agreements} steps: "
+                                  f"a peer did not answer within {self.timeout_s:.0f} s")
+            self.agreements += 1
+            return got
         self._buf.zero_()
         for i, f in enumerate(flags):
             self._buf[i] = int(f)

@@ -46,6 +46,10 @@ def _lib():
         lib.rb_rs_reduce_ex.argtypes = [PP, _VP, _I, _I, _I, _I, _LL, _F, _VP, _I, _VP, _VP, _I, _VP]
         lib.rb_clip_coef_ex.argtypes = [_VP, _I, PP, PP, _I, _I, _I, _I, _F, _F, _VP, _VP, _VP, _VP]
         lib.rb_adamw_allgather_ex.argtypes = [_VP, _VP, _VP, _VP, _I, PP, _I, _I, _LL, _F, _F, _F, _F, _F, _I, _VP, _VP]
+        lib.rb_pull_sum_sync.argtypes = [PP, _VP, _VP, _LL, _I, _I, PP, _I, _VP, PP, _VP, _VP, _VP]
+        lib.rb_pull_sum_sync.restype = _I
+        lib.rb_symm_agree_max.argtypes = [PP, PP, _I, _I, _I, _VP, _I, _I, _I, _I, _VP, ctypes.c_ulonglong, _VP]
+        lib.rb_symm_agree_max.restype = _I
         lib.rb_comm_set_wait_budget_ns.argtypes = [ctypes.c_ulonglong]
         lib.rb_comm_set_wait_budget_ns.restype = None
         lib.rb_comm_get_wait_budget_ns.restype = ctypes.c_ulonglong
@@ -170,6 +174,27 @@ class PeerComm:
     def flag_ptr(self, slot: int) -> int:
         """Address of this rank's flag row ``[world]`` for ``slot``."""
         return self.flags.local.data_ptr() + slot * self.world * 4
+
+    def agree_max(self, values, budget_s: float = 0.0) -> tuple[int, ...] | None:
+        """Element-wise maximum of up to four small integers over the ranks, exchanged through peer memory by one
+        small kernel (values stored into every peer's buffer, flags, bounded wait) and read back by the host. Returns
+        None when a peer did not answer within ``budget_s`` (0 = the library's wait budget): nothing else was
+        launched, the GPU and the context stay usable."""
+        vals = [int(v) for v in values] + [0] * (4 - len(values))
+        assert len(vals) == 4 and self.on_gpu
+        if getattr(self, "_agree", None) is None:
+            xchg = self.alloc((2, self.world, 4), torch.int32, zero=True)
+            self._agree = (xchg, self.new_slot(), torch.zeros(1, dtype=torch.int32, device=self.device),
+                           torch.zeros(5, dtype=torch.int32, device=self.device))
+            self.barrier_host()
+        xchg, slot, counter, out = self._agree
+        rc = _lib().rb_symm_agree_max(xchg.ptrs(), self.flags.ptrs(), self.rank, self.world, slot, counter.data_ptr(),
+                                      vals[0], vals[1], vals[2], vals[3], out.data_ptr(), int(budget_s * 1e9), stream_handle(self.device))
+        check_rc(rc, "rb_symm_agree_max")
+        host = out.tolist()            # the one synchronisation of the exchange
+        if not host[4]:
+            return None
+        return tuple(host[:len(values)])
 
 
 class LayoutComm:

@@ -45,6 +45,7 @@ class TensorParallel:
         self._registry: dict[int, SymmBuffer] = {}
         self._call = 0
         self._ag_epoch = 0
+        self._ar_sync = self._ar_ack = None
         self.ag_stage = self.ag_flags = None
         self._ready_slot = comm.new_slot()
         if comm.on_gpu:
@@ -61,6 +62,11 @@ class TensorParallel:
             self.SPLIT_AR_ROWS = 256
             self.ar_slab = comm.alloc((self.SPLIT_AR_ROWS * max_cols,), torch.bfloat16, zero=True)
             self._ar_slot = comm.new_slot()
+            # two-launch form of that path: [0] epoch, [1] block ticket, [2] acknowledgements this rank's next slab
+            # write waits for; the peers count their reads of this rank's slab in _ar_ack
+            self._ar_sync = torch.zeros(3, dtype=torch.int32, device=comm.device)
+            self._ar_ack = comm.alloc((1,), torch.int32, zero=True)
+            self._ar_flag_slot = comm.new_slot()
             comm.barrier_host()
 
     # ---------------------------------------------------------------- buffers
@@ -157,10 +163,14 @@ class TensorParallel:
 
     # The fused reduce epilogues cannot split K (their epilogue is the reduction), so with few rows and a long K the
     # per-rank GEMM runs on few CTAs at the rate one SM streams operands and does not shrink with the rank count.
-    # This path spends three small launches instead: the plain GEMM (which splits K over thread-block clusters) into
-    # this rank's slab, a device barrier, a pull-sum over all ranks' slabs (peer loads, rank order, so every rank gets
-    # the same bits), and a second barrier before anyone may overwrite a slab. RB_TP_SPLIT_AR=0 switches it off.
+    # This path is two launches instead: the plain GEMM (which splits K over thread-block clusters) into this rank's
+    # slab, and a pull-sum over all ranks' slabs (peer loads, rank order, so every rank gets the same bits) that
+    # carries its own synchronisation: it publishes "my slab is complete", waits for the peers' flags, sums, and
+    # acknowledges the peers' slabs; the NEXT call's GEMM waits inside its launch for the acknowledgements of this
+    # call before it overwrites the slab. No barrier launches; epochs live on the device (graph replay).
+    # RB_TP_SPLIT_AR=0 switches the path off, RB_TP_SPLIT_AR=barriers keeps the earlier four-launch form.
     SPLIT_AR = os.environ.get("RB_TP_SPLIT_AR", "1") != "0"
+    SPLIT_AR_BARRIERS = os.environ.get("RB_TP_SPLIT_AR", "1") == "barriers"
 
     def _reduce_split(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
         from .symm import _lib as _comm_lib, ptr_array
@@ -168,12 +178,21 @@ class TensorParallel:
 
         M, N = a.shape[0], w.shape[0]
         part = self.ar_slab.local[: M * N].view(M, N)
-        ops.gemm(a, w, out=part)
-        self.comm.barrier(self._ar_slot)                  # every rank's partial is complete
-        rc = _comm_lib().rb_pull_sum(ptr_array(self.ar_slab.peer_ptrs), x.data_ptr(), x.data_ptr(), M * N, self.world,
-                                     stream_handle(a.device))
-        check_rc(rc, "rb_pull_sum")
-        self.comm.barrier(self._ar_slot)                  # every rank has read every slab: the next call may write
+        dev = a.device
+        if self.SPLIT_AR_BARRIERS:
+            ops.gemm(a, w, out=part)
+            self.comm.barrier(self._ar_slot)                  # every rank's partial is complete
+            rc = _comm_lib().rb_pull_sum(ptr_array(self.ar_slab.peer_ptrs), x.data_ptr(), x.data_ptr(), M * N, self.world,
+                                         stream_handle(dev))
+            check_rc(rc, "rb_pull_sum")
+            self.comm.barrier(self._ar_slot)                  # every rank has read every slab: the next call may write
+            return
+        sync = self._ar_sync.data_ptr()
+        ops.gemm(a, w, out=part, wait_flag=(self._ar_ack.local.data_ptr(), sync + 8))
+        rc = _comm_lib().rb_pull_sum_sync(ptr_array(self.ar_slab.peer_ptrs), x.data_ptr(), x.data_ptr(), M * N, self.world, self.rank,
+                                          self.comm.flags.ptrs(), self._ar_flag_slot, sync, self._ar_ack.ptrs(), sync + 8,
+                                          status_tensor(dev).data_ptr(), stream_handle(dev))
+        check_rc(rc, "rb_pull_sum_sync")
 
     def _reduce_oneshot(self, a: torch.Tensor, w: torch.Tensor, x: torch.Tensor) -> None:
         M, K = a.shape

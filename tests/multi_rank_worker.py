@@ -64,6 +64,26 @@ def case_tp_gemms(comm, dev, dt):
         close(out, full[comm.rank * rpr:(comm.rank + 1) * rpr] + res.float(), 0.08 * K ** 0.5 / 4 + 0.05, 0.02,
               f"gemm_reduce_scatter {M}x{N}x{K}")
         comm.barrier()
+    if comm.on_gpu:
+        # the split path from a CUDA graph: three calls per replay, two replays; the epochs, the block ticket and the
+        # acknowledgement counts of the slab all live on the device, so the replays must keep adding correctly
+        M, N, K = 64, 1024, 4096
+        a_all = [rnd((M, K), 100 + r, dev, dt) for r in range(W)]
+        w_all = [rnd((N, K), 200 + r, dev, dt, 0.1) for r in range(W)]
+        full = sum(a.float() @ w.float().t() for a, w in zip(a_all, w_all))
+        x = tp.alloc((M, N), dt)
+        tp.gemm_all_reduce(a_all[comm.rank], w_all[comm.rank], x)          # eager once: work buffers exist before the capture
+        comm.barrier_host()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(3):
+                tp.gemm_all_reduce(a_all[comm.rank], w_all[comm.rank], x)
+        x.zero_()
+        g.replay()
+        g.replay()
+        torch.cuda.synchronize()
+        close(x, 6 * full, 0.5 * K ** 0.5 / 4 + 0.3, 0.03, "gemm_all_reduce split path, graph replays")
+        comm.barrier_host()
     # all-gather -> GEMM (activation shards) and FSDP weight shards read from peers in the GEMM
     rows, K, N = 128, 256, 384
     xs = tp.alloc((rows, K), dt)
@@ -324,7 +344,40 @@ def _bcast_buckets(b, comm):
     return b
 
 
-CASES = {"barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
+def case_ep_agree(comm, dev, dt):
+    """Per-step agreement of the expert-parallel engines: element-wise maximum over the ranks. On GPUs it travels through
+    peer memory with a bounded wait: one rank arrives late ON THE HOST (nothing of it is in flight), its peers' wait
+    runs out after a second and reports the failure, the context stays usable and the retry succeeds."""
+    import time
+
+    from research_b200.parallel.ep import ExpertParallel, PeerFailure
+
+    W, r = comm.world, comm.rank
+    ep = ExpertParallel(comm, timeout_s=1.0 if comm.on_gpu else 30.0)
+    assert ep.agree(r, 5 - r, 0) == (W - 1, 5, 0)
+    assert ep.agree(0) == (0,) and ep.agree(int(r == 0)) == (1,)
+    if comm.on_gpu:
+        assert ep.device_agree
+        dist.barrier()
+        late = r == W - 1
+        if late:
+            time.sleep(2.5)
+        try:
+            got, failed = ep.agree(1), False
+        except PeerFailure:
+            got, failed = None, True
+        assert failed == (not late), (r, failed)
+        if late:
+            assert got == (1,)        # the peers' values of this epoch were already in its buffer
+        dist.barrier()
+        if failed:                    # the ranks that gave up did not advance their epoch: they ask again
+            assert ep.agree(1) == (1,)
+        x = torch.ones(4, device=dev)                 # the device still runs ordinary work
+        assert float((x * 2).sum()) == 8.0
+        assert ep.agree(r) == (W - 1,)
+
+
+CASES = {"ep_agree": case_ep_agree, "barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
          "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo,
          "fsdp_full_shard": case_fsdp_full_shard, "grpo_disjoint": case_grpo_disjoint,
          "moe_ep": case_moe_expert_parallel}

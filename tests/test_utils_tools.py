@@ -132,7 +132,7 @@ def test_kernel_harness_checks_times_and_round_trips(tmp_path):
     from research_b200.utils import kernel_harness as kh
 
     reg = kh.nvfp4_backends()
-    assert "reference" in reg and "native" in reg and len(reg) == 2
+    assert "reference" in reg and "native" in reg and "library_scaled_mm" in reg and len(reg) == 3
     with pytest.raises(ValueError):
         reg.register("reference", lambda x: x[0])
     with pytest.raises(ValueError):
