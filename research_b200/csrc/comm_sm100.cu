@@ -62,13 +62,12 @@ __global__ void symm_agree_max_kernel(PeerPtrs xchg, PeerPtrs flags, int rank, i
   __syncthreads();
   const int parity = ep & 1;
   const int r = threadIdx.x;
-  int private_status = 0;
   if (r < world) {
     int* dst = reinterpret_cast<int*>(xchg.p[r]) + (parity * world + rank) * 4;
     st_relaxed_sys(dst + 0, v0); st_relaxed_sys(dst + 1, v1); st_relaxed_sys(dst + 2, v2); st_relaxed_sys(dst + 3, v3);
     __threadfence_system();
     st_release_sys(reinterpret_cast<int*>(flags.p[r]) + slot * world + rank, ep);
-    if (!wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, ep, &private_status, budget_ns)) ok_all = 0;
+    if (!wait_flag_ge(reinterpret_cast<const int*>(flags.p[rank]) + slot * world + r, ep, nullptr, budget_ns)) ok_all = 0;   // no status word: out[4] reports
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -801,6 +801,11 @@ struct FlashBwdParams {
   int causal, window;
   float scale_log2, scale;
   int* status;
+  // dK/dV with one CTA per (key tile, QUERY head) instead of per (key tile, key/value head): the CTAs of a group write
+  // fp32 partials [2 (dV, dK)][G][Tk][Hkv][D] here and flash_bwd_reduce_kernel sums them in a fixed order. With few
+  // long sequences the per-kv-head form leaves most SMs idle behind its longest CTA (G x the query tiles of the
+  // first key tile); null = off.
+  float* dkv_part;
 };
 
 __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
@@ -879,13 +884,18 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, kvh = blockIdx.y;
+  // Under a causal mask the first key tiles have the longest loops: hand them out first, across all heads (blocks
+  // are scheduled in the order of their linear index)
+  const int lin = blockIdx.x + gridDim.x * blockIdx.y;
+  const int b = blockIdx.z, hy = lin % gridDim.y;
+  const int G = p.Hq / p.Hkv;
+  const bool head_split = p.dkv_part != nullptr;
+  const int kvh = head_split ? hy / G : hy, g_base = head_split ? hy % G : 0;
   const int k_begin = p.cu_k[b], kv_len = p.cu_k[b + 1] - k_begin;
-  const int k0 = blockIdx.x * 128;
+  const int k0 = (lin / gridDim.y) * 128;
   if (k0 >= kv_len) return;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int off = kv_len - q_len;
-  const int G = p.Hq / p.Hkv;
   // queries that see at least one key of this tile
   const int kmax = min(k0 + 127, kv_len - 1);
   int qi_lo = 0, qi_hi = q_len;
@@ -893,7 +903,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
   if (p.window > 0) qi_hi = min(q_len, kmax + p.window - off);
   const int i_begin = qi_lo / 64;
   const int n_qt = qi_hi > qi_lo ? (qi_hi + 63) / 64 - i_begin : 0;
-  const int n_iter = n_qt * G;
+  const int n_iter = n_qt * (head_split ? 1 : G);
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -938,7 +948,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
       }
       int it = 0;
       for (; it < n_iter; ++it) {
-        const int h = kvh * G + it / n_qt, i = i_begin + it % n_qt;
+        const int h = kvh * G + g_base + it / n_qt, i = i_begin + it % n_qt;
         const int stage = it % ST;
         ok = mbar_wait_backoff(smem_u32(&qdo_empty[stage]), ((it / ST) & 1u) ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
         if (!ok) break;
@@ -1020,7 +1030,7 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
     const int tid = threadIdx.x - 64;              // 0..255
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
-      const int h = kvh * G + it / n_qt, qi0 = (i_begin + it % n_qt) * 64;
+      const int h = kvh * G + g_base + it / n_qt, qi0 = (i_begin + it % n_qt) * 64;
       {   // row statistics of the 64 queries: thread t<64 -> lse2, t>=64 -> delta
         if (tid < 128) {
           const int idx = tid & 63, which = tid >> 6;
@@ -1091,7 +1101,13 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          if (row_ok) {
+          if (row_ok && head_split) {
+            float* dst = p.dkv_part + (((long long)(which * G + g_base) * p.Tk + k_begin + kj) * p.Hkv + kvh) * D + c * 32;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              *reinterpret_cast<float4*>(dst + u * 4) = make_float4(__uint_as_float(v[u * 4]), __uint_as_float(v[u * 4 + 1]),
+                                                                    __uint_as_float(v[u * 4 + 2]), __uint_as_float(v[u * 4 + 3]));
+          } else if (row_ok) {
             __nv_bfloat16* dst = (which == 0 ? dv_row : dk_row) + c * 32;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
@@ -1335,6 +1351,25 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dq_kernel(const _
   }
 }
 
+// dv / dk = sum over the G query heads of a group of their fp32 partials (fixed order), rounded to bf16.
+__global__ void flash_bwd_reduce_kernel(const float* __restrict__ part, int G, long long n, __nv_bfloat16* __restrict__ dv,
+                                        __nv_bfloat16* __restrict__ dk) {
+  const long long nvec = n >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < 2 * nvec; i += (long long)gridDim.x * blockDim.x) {
+    const int which = i >= nvec;
+    const long long j = which ? i - nvec : i;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int g = 0; g < G; ++g) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(part + ((long long)which * G + g) * n) + j);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc.x, acc.y);
+    o.y = pack_bf16x2(acc.z, acc.w);
+    reinterpret_cast<uint2*>(which ? dk : dv)[j] = o;
+  }
+}
+
 template <int D>
 static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, cudaStream_t stream) {
   using Cfg = FlashBwdCfg<D>;
@@ -1350,6 +1385,12 @@ static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, 
   }
   if (launch_kernel(flash_bwd_dkdv_kernel<D>, grid_kv, dim3(FA_BWD_THREADS), Cfg::kSmemDkdv, stream, p) != cudaSuccess) return -11;
   if (launch_kernel(flash_bwd_dq_kernel<D>, grid_q, dim3(FA_BWD_THREADS), Cfg::kSmemDq, stream, p) != cudaSuccess) return -11;
+  if (p.dkv_part != nullptr) {
+    const long long n = (long long)p.Tk * p.Hkv * D;
+    long long blocks = (2 * (n >> 2) + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    flash_bwd_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.dkv_part, p.Hq / p.Hkv, n, p.dv, p.dk);
+  }
   return 0;
 }
 
@@ -1418,9 +1459,11 @@ int rb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* 
 }
 
 // Backward of rb_flash_fwd in dense mode. out, dout, dq are contiguous [Tq,Hq,D]; dk, dv contiguous
-// [Tk,Hkv,D]; workspace holds 2*Hq*Tq floats (delta, lse in log2 units).
+// [Tk,Hkv,D]; workspace holds 2*Hq*Tq floats (delta, lse in log2 units). dkv_part (may be null): 2*(Hq/Hkv)*Tk*Hkv*D
+// floats; when given, dK/dV run with one CTA per (key tile, query head) and are reduced over each group afterwards
+// (few long sequences: the per-kv-head grid is too coarse to fill the SMs).
 int rb_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
-                 void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, float* workspace, int B, int Tq,
+                 void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, float* workspace, float* dkv_part, int B, int Tq,
                  int Tk, int Hq, int Hkv, int D, int ldq, int ldk, int ldv, int max_seqlen_q, int max_seqlen_k,
                  int causal, int window, float scale, int* status, cudaStream_t stream) {
   using namespace rb;
@@ -1436,6 +1479,7 @@ int rb_flash_bwd(const void* q, const void* k, const void* v, const void* out, c
   float* lse2 = workspace + (long long)Hq * Tq;
   p.lse2 = lse2;
   p.delta = delta;
+  p.dkv_part = (Hq > Hkv) ? dkv_part : nullptr;
   p.dq = (__nv_bfloat16*)dq;
   p.dk = (__nv_bfloat16*)dk;
   p.dv = (__nv_bfloat16*)dv;
@@ -1449,7 +1493,7 @@ int rb_flash_bwd(const void* q, const void* k, const void* v, const void* out, c
   const long long warps = (long long)Tq * Hq;
   launch_kernel(flash_bwd_prep_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, stream,
                 (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, lse, delta, lse2, Tq, Hq, D);
-  dim3 grid_kv((max_seqlen_k + 127) / 128, Hkv, B), grid_q((max_seqlen_q + 127) / 128, Hq, B);
+  dim3 grid_kv((max_seqlen_k + 127) / 128, p.dkv_part != nullptr ? Hq : Hkv, B), grid_q((max_seqlen_q + 127) / 128, Hq, B);
   int rc = D == 64 ? launch_flash_bwd<64>(p, grid_kv, grid_q, stream) : launch_flash_bwd<128>(p, grid_kv, grid_q, stream);
   if (rc != 0) return rc;
   return cudaGetLastError() == cudaSuccess ? 0 : -12;

@@ -53,7 +53,24 @@ struct G2Params {
   const __nv_bfloat16* bias;
   int out_f32;
   int* status;
+  // Fused all-gather of a row-sharded matrix (GATHER instantiations; same contract as the one-CTA kernel): part r is
+  // gather_part_bytes at gather_src[r] (rank r's shard, peer memory); the two gather warps of every CTA copy an
+  // interleaved share of each part to gather_dst + r * bytes, own part first, and the last CTA to finish a part
+  // publishes gather_ready[r] = gather_epoch. With `consume` the gathered matrix is this launch's K-major B operand:
+  // tiles visit the parts starting at the local one and their producers wait for the part they read.
+  const void* gather_src[8];
+  void* gather_dst;
+  long long gather_part_bytes;
+  int* gather_count;
+  int* gather_ready;
+  int gather_epoch, gather_parts, rank, consume, n_tiles_per_part;
+  // A part is copied and published in `gather_chunks` pieces of gather_chunk_tiles column tiles (256 rows of the
+  // gathered matrix) each, so the tiles of a remote part start while the rest of it is still crossing NVLink:
+  // flag / counter index = part * gather_chunks + chunk.
+  int gather_chunks, gather_chunk_tiles;
+  long long gather_chunk_bytes;
 };
+constexpr int G2_THREADS_GATHER = G2_THREADS + 64;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -82,8 +99,8 @@ __device__ __forceinline__ void umma2_commit(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(G2_THREADS, 1) gemm2cta_kernel(const __grid_constant__ G2Params p) {
+template <int BN, bool A_MN, bool B_MN, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? G2_THREADS_GATHER : G2_THREADS, 1) gemm2cta_kernel(const __grid_constant__ G2Params p) {
   using Cfg = G2Cfg<BN>;
   constexpr int STAGES = Cfg::kStages;
   constexpr int HALF_N = BN / 2;
@@ -103,6 +120,13 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm2cta_kernel(const __grid_co
   const int m_tiles = (p.M + 255) / 256, n_tiles = (p.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  // tile t -> (row tile, column tile); a launch that consumes its own gather starts at the local part's columns
+  const int nt_rot = (GATHER && p.consume) ? p.rank * p.n_tiles_per_part : 0;
+  auto tile_mn = [&](int t, int& mt, int& nt) {
+    mt = t % m_tiles;
+    nt = t / m_tiles + nt_rot;
+    if (nt >= n_tiles) nt -= n_tiles;
+  };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -133,10 +157,23 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm2cta_kernel(const __grid_co
       int s = 0;
       uint32_t ph = 0, issued = 0;
       bool ok = true;
+      unsigned long long chunks_seen = 0;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const int mt = t % m_tiles, nt = t / m_tiles;
+        int mt, nt;
+        tile_mn(t, mt, nt);
         const int m0 = mt * 256 + (int)cta * G2_BM;        // this CTA's rows of A
         const int n0 = nt * BN + (int)cta * HALF_N;        // this CTA's rows of B
+        if (GATHER && p.consume) {
+          const int part = nt / p.n_tiles_per_part;
+          const int idx = part * p.gather_chunks + (nt - part * p.n_tiles_per_part) / p.gather_chunk_tiles;
+          if (!((chunks_seen >> idx) & 1ull)) {
+            ok = wait_flag_ge(p.gather_ready + idx, p.gather_epoch, p.status);
+            if (!ok) { *abortp = 1; break; }
+            // the rows were written by ordinary stores of the gather warps: order them before the async-proxy tile loads
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            chunks_seen |= 1ull << idx;
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++issued) {
           ok = mbar_wait_bounded_cluster(smem_u32(&empty_bar[s]), ph ^ 1u, abortp, p.status, ST_TIMEOUT_SMEM_EMPTY);
           if (!ok) break;
@@ -205,6 +242,50 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm2cta_kernel(const __grid_co
         }
       }
     }
+  } else if (GATHER && warp >= 2 + G2_EPI_WARPS) {
+    // ------------------------------ gather warps (both CTAs) ------------------------------------
+    constexpr int GT = 64;
+    const int gt = (warp - 2 - G2_EPI_WARPS) * 32 + lane;
+    const long long stride = (long long)gridDim.x * GT;
+    for (int pp = 0; pp < p.gather_parts; ++pp) {
+      int part = p.rank + pp;
+      if (part >= p.gather_parts) part -= p.gather_parts;
+      for (int ch = 0; ch < p.gather_chunks; ++ch) {
+        const long long b0 = (long long)ch * p.gather_chunk_bytes;
+        const long long b1 = min(b0 + p.gather_chunk_bytes, p.gather_part_bytes);
+        const long long nvec = (b1 - b0) >> 4;
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.gather_src[part]) + b0);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.gather_dst) + (long long)part * p.gather_part_bytes + b0);
+        constexpr int U = 8;     // eight 16-byte loads in flight per thread: the copy is bound by NVLink latency otherwise
+        for (long long i0 = (long long)blockIdx.x * GT + gt; i0 < nvec; i0 += stride * U) {
+          uint4 v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < nvec)
+              asm volatile("ld.global.relaxed.sys.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i) : "memory");
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long i = i0 + u * stride;
+            if (i < nvec) dst[i] = v[u];
+          }
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(GT) : "memory");    // the gather warps of this CTA only
+        if (gt == 0) {
+          const int idx = part * p.gather_chunks + ch;
+          const int old = atomicAdd(p.gather_count + idx, 1);
+          if (old == (int)gridDim.x - 1) {     // every CTA's share of these rows is in place
+            p.gather_count[idx] = 0;
+            __threadfence();
+            st_release_sys(p.gather_ready + idx, p.gather_epoch);
+          }
+        }
+      }
+    }
   } else {
     // ------------------------------ epilogue warps (both CTAs) ----------------------------------
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
@@ -213,7 +294,8 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm2cta_kernel(const __grid_co
     const uint32_t leader_empty0 = mapa_cluster(smem_u32(&tmem_empty_bar[0]), 0);
     const uint32_t leader_empty1 = mapa_cluster(smem_u32(&tmem_empty_bar[1]), 0);
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tile_iter) {
-      const int mt = t % m_tiles, nt = t / m_tiles;
+      int mt, nt;
+      tile_mn(t, mt, nt);
       const int acc = tile_iter % G2_ACC;
       const uint32_t acc_ph = (tile_iter / G2_ACC) & 1u;
       ok = mbar_wait_bounded_cluster(smem_u32(&tmem_full_bar[acc]), acc_ph, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
@@ -300,10 +382,11 @@ __global__ void __launch_bounds__(G2_THREADS, 1) gemm2cta_kernel(const __grid_co
 }
 
 // ---------------------------------- host side ------------------------------------------------
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool GATHER = false>
 static int g2_launch(const G2Params& p, int tiles, cudaStream_t stream) {
   using Cfg = G2Cfg<BN>;
-  auto kern = gemm2cta_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm2cta_kernel<BN, A_MN, B_MN, GATHER>;
+  constexpr int THREADS = GATHER ? G2_THREADS_GATHER : G2_THREADS;
   static bool attr_set[64] = {};
   static int max_pairs[64] = {};
   int dev = 0;
@@ -315,7 +398,7 @@ static int g2_launch(const G2Params& p, int tiles, cudaStream_t stream) {
     // how many pairs the device can hold at once (a persistent grid larger than that would only queue)
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms - sms % 2);
-    cfg.blockDim = dim3(G2_THREADS);
+    cfg.blockDim = dim3(THREADS);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
@@ -327,8 +410,9 @@ static int g2_launch(const G2Params& p, int tiles, cudaStream_t stream) {
     attr_set[dev] = true;
   }
   int pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
+  if (GATHER) pairs = max_pairs[dev];      // every resident CTA copies a share of the gather, whatever the tile count
   if (pairs < 1) pairs = 1;
-  return launch_kernel_cluster(kern, dim3(2 * pairs), dim3(G2_THREADS), Cfg::kSmemBytes, stream, 2u, p) == cudaSuccess ? 0 : -11;
+  return launch_kernel_cluster(kern, dim3(2 * pairs), dim3(THREADS), Cfg::kSmemBytes, stream, 2u, p) == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace rb
@@ -379,4 +463,51 @@ extern "C" int rb_gemm2_bf16(const void* A, const void* B, void* C, const void* 
   if (!a_mn_major && !b_mn_major) return g2_launch<128, false, false>(p, tiles, stream);
   if (!a_mn_major && b_mn_major) return g2_launch<128, false, true>(p, tiles, stream);
   return g2_launch<128, true, true>(p, tiles, stream);
+}
+
+// The same GEMM carrying the all-gather of a row-sharded matrix (see G2Params). consume != 0: B is ignored and the
+// gathered matrix ([N, K], K-major, N / parts rows per part, which must be a multiple of 256) is the B operand;
+// consume == 0: the launch computes its own product (the MN/MN weight gradient) and only carries the copy.
+// gather_chunks: pieces a part is published in when consumed (1 = whole parts); the flag and counter arrays hold
+// gather_parts * gather_chunks ints.
+extern "C" int rb_gemm2_bf16_gather(const void* A, const void* B, void* C, const void* bias, const void* residual, int M, int N,
+                                    int K, long long lda, long long ldb, long long ldc, long long ldr, int a_mn_major,
+                                    int b_mn_major, int out_f32, const void* const* gather_src, void* gather_dst,
+                                    long long gather_part_bytes, int* gather_count, int* gather_ready, int gather_epoch,
+                                    int gather_parts, int rank, int consume, int gather_chunks, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || N % 8 != 0 || K % 8 != 0) return -1;
+  if (gather_parts < 1 || gather_parts > 8 || rank < 0 || rank >= gather_parts || gather_dst == nullptr || gather_count == nullptr ||
+      gather_ready == nullptr || gather_part_bytes <= 0 || gather_part_bytes % 16 != 0)
+    return -1;
+  if (a_mn_major != b_mn_major) return -12;                 // forward (K/K) and weight gradient (MN/MN) only
+  if (consume && (a_mn_major || N % gather_parts != 0 || (N / gather_parts) % 256 != 0)) return -12;
+  G2Params p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_f32 = out_f32;
+  p.status = status;
+  for (int r = 0; r < gather_parts; ++r) p.gather_src[r] = gather_src[r];
+  p.gather_dst = gather_dst; p.gather_part_bytes = gather_part_bytes;
+  p.gather_count = gather_count; p.gather_ready = gather_ready; p.gather_epoch = gather_epoch;
+  p.gather_parts = gather_parts; p.rank = rank; p.consume = consume ? 1 : 0;
+  p.n_tiles_per_part = consume ? (N / gather_parts) / 256 : 1;
+  // gather_count / gather_ready hold gather_parts * gather_chunks entries (at most 64)
+  if (!consume || gather_chunks < 1) gather_chunks = 1;
+  if (gather_chunks > p.n_tiles_per_part) gather_chunks = p.n_tiles_per_part;
+  while (gather_chunks > 1 && gather_parts * gather_chunks > 64) --gather_chunks;
+  p.gather_chunk_tiles = consume ? (p.n_tiles_per_part + gather_chunks - 1) / gather_chunks : 1;
+  p.gather_chunks = consume ? (p.n_tiles_per_part + p.gather_chunk_tiles - 1) / p.gather_chunk_tiles : 1;
+  p.gather_chunk_bytes = consume ? (long long)p.gather_chunk_tiles * 256 * K * 2 : gather_part_bytes;
+  if (consume && gather_part_bytes != (long long)(N / gather_parts) * K * 2) return -1;
+  if (consume) { B = gather_dst; ldb = K; }
+  int rc = a_mn_major ? tma_map_2d_bf16(&p.a_map, A, K, M, lda, G2_BK) : tma_map_2d_bf16(&p.a_map, A, M, K, lda, G2_BM);
+  if (rc != 0) return -20 + rc;
+  rc = b_mn_major ? tma_map_2d_bf16(&p.b_map, B, K, N, ldb, G2_BK) : tma_map_2d_bf16(&p.b_map, B, N, K, ldb, 128);
+  if (rc != 0) return -30 + rc;
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  if (!a_mn_major) return g2_launch<256, false, false, true>(p, tiles, stream);
+  return g2_launch<256, true, true, true>(p, tiles, stream);
 }

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -27,7 +28,7 @@ def _lib() -> ctypes.CDLL:
     if not getattr(lib, "_rb_typed", False):
         lib.rb_flash_fwd.argtypes = [c_vp] * 9 + [c_int] * 14 + [c_float, c_vp, c_vp]
         lib.rb_flash_fwd.restype = c_int
-        lib.rb_flash_bwd.argtypes = [c_vp] * 12 + [c_int] * 13 + [c_float, c_vp, c_vp]
+        lib.rb_flash_bwd.argtypes = [c_vp] * 13 + [c_int] * 13 + [c_float, c_vp, c_vp]
         lib.rb_flash_bwd.restype = c_int
         lib._rb_typed = True
     return lib
@@ -133,12 +134,32 @@ def flash_attn_varlen_backward(q, k, v, out, dout, lse, cu_q, cu_k, max_seqlen_q
     dv = torch.empty(Tk, Hkv, D, dtype=torch.bfloat16, device=q.device)
     ws = torch.empty(2 * Hq * Tq, dtype=torch.float32, device=q.device)
     B = cu_q.shape[0] - 1
+    part = None
+    if head_split_pays(B, max_seqlen_q, max_seqlen_k, Hq, Hkv):
+        part = torch.empty(2 * (Hq // Hkv) * Tk * Hkv * D, dtype=torch.float32, device=q.device)
     rc = _lib().rb_flash_bwd(ptr(q), ptr(k), ptr(v), ptr(out), ptr(dout), ptr(lse), ptr(dq), ptr(dk), ptr(dv), ptr(cu_q),
-                             ptr(cu_k), ptr(ws), B, Tq, Tk, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
+                             ptr(cu_k), ptr(ws), ptr(part) if part is not None else None, B, Tq, Tk, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
                              max_seqlen_q, max_seqlen_k, int(causal), int(window), scale,
                              ptr(status_tensor(q.device)), stream_handle(q.device))
     check_rc(rc, "rb_flash_bwd")
     return dq, dk, dv
+
+
+_HEAD_SPLIT = os.environ.get("RB_FLASH_BWD_HEAD_SPLIT", "auto")     # auto | 0 | 1
+
+
+def head_split_pays(B: int, max_seqlen_q: int, max_seqlen_k: int, Hq: int, Hkv: int) -> bool:
+    """dK/dV as one CTA per (key tile, QUERY head) + a reduction over each group, instead of one CTA per (key tile,
+    key/value head) looping over its G query heads. It pays only where the coarse grid has fewer CTAs than the GPU has
+    SMs (one long sequence with two kv heads: 64 CTAs). Measured on the Llama-3-8B step (one 4096-token sequence, 8 kv
+    heads: 256 CTAs, the longest 256 iterations against 228 per SM on average) the split changes nothing: 255.2 ms per
+    step with it, 253.5 without; the kernel is bound by its 3.7 us per iteration, not by balance. The split costs
+    2 * G * Tk * Hkv * D floats of workspace and one pass over them."""
+    G = Hq // Hkv
+    if _HEAD_SPLIT in ("0", "1"):
+        return G > 1 and _HEAD_SPLIT == "1"
+    ctas = -(-max_seqlen_k // 128) * Hkv * B
+    return G > 1 and ctas < 148 and (max_seqlen_q // 64) * G >= 64
 
 
 class FlashAttnVarlen(torch.autograd.Function):

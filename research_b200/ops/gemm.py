@@ -113,11 +113,16 @@ def _lib2() -> ctypes.CDLL:
         lib.rb_gemm2_bf16.argtypes = [vp] * 5 + [i, i, i, ll, ll, ll, ll, i, i, i, i, vp, vp]
         lib.rb_gemm2_bf16.restype = i
         lib.rb_gemm2_pairs.restype = i
+        lib.rb_gemm2_bf16_gather.argtypes = ([vp] * 5 + [i, i, i, ll, ll, ll, ll, i, i, i] +
+                                             [ctypes.POINTER(vp), vp, ll, vp, vp, i, i, i, i, i, vp, vp])
+        lib.rb_gemm2_bf16_gather.restype = i
         lib._rb_typed = True
     return lib
 
 
 _GEMM2 = os.environ.get("RB_GEMM2", "1") != "0"
+_GEMM2_GATHER = os.environ.get("RB_GEMM2_GATHER", "1") != "0"     # gather-carrying launches on the two-CTA kernel too
+_GATHER_CHUNKS = int(os.environ.get("RB_GATHER_CHUNKS", "8"))      # pieces a gathered part is published in (tiles start per piece)
 _GEMM2_PAIRS = 74      # CTA pairs resident on a B200 (148 SMs)
 
 
@@ -149,6 +154,23 @@ def gemm2(a: torch.Tensor, b: torch.Tensor, bias=None, residual=None, out=None, 
                                out.stride(0), residual.stride(0) if residual is not None else 0, int(a_mn_major),
                                int(b_mn_major), int(out_f32), bn, status_tensor(a.device).data_ptr(), stream_handle(a.device))
     check_rc(rc, "rb_gemm2_bf16")
+    return out
+
+
+def _gemm2_gather(a, b, bias, residual, out, M, N, K, mn_major: bool, out_f32: bool, gather, consume: bool) -> torch.Tensor:
+    """A gather-carrying launch on the two-CTA kernel (``rb_gemm2_bf16_gather``): forward (K-major operands, the
+    gathered matrix consumed as B) or weight gradient (both MN-major, the gather only carried)."""
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
+    W = gather.world
+    src = (ctypes.c_void_p * 8)(*[gather.peer_ptrs[r] for r in range(W)])
+    rc = _lib2().rb_gemm2_bf16_gather(
+        a.data_ptr(), None if consume else b.data_ptr(), out.data_ptr(), bias.data_ptr() if bias is not None else None,
+        residual.data_ptr() if residual is not None else None, M, N, K, a.stride(0), K if consume else b.stride(0), out.stride(0),
+        residual.stride(0) if residual is not None else 0, int(mn_major), int(mn_major), int(out_f32), src,
+        gather.b.stage.data_ptr(), gather.part_bytes, gather.b.gather_count.data_ptr(), gather.b.gather_ready.data_ptr(),
+        gather.next_epoch(), W, gather.rank, int(consume), _GATHER_CHUNKS, status_tensor(a.device).data_ptr(), stream_handle(a.device))
+    check_rc(rc, "rb_gemm2_bf16_gather")
     return out
 
 
@@ -254,6 +276,11 @@ def gemm(
     if (gather is None and wait_flag is None and not swiglu and norm_eps is None and alpha == 1.0 and beta == 1.0 and bn == 0 and max_ctas == 0 and split_k in (0, 1)
             and not cluster_split and _use_pair_kernel(M, N, K, a_mn_major, b_mn_major)):
         return gemm2(a, b, bias, residual, out, a_mn_major=a_mn_major, b_mn_major=b_mn_major, out_f32=out_f32)
+    if (gather is not None and _GEMM2_GATHER and wait_flag is None and not swiglu and norm_eps is None and alpha == 1.0 and beta == 1.0
+            and bn == 0 and max_ctas == 0 and split_k in (0, 1) and not cluster_split and a_mn_major == b_mn_major
+            and _use_pair_kernel(M, N, K, a_mn_major, b_mn_major)
+            and (b_gather is None or (N % gather.world == 0 and (N // gather.world) % 256 == 0))):
+        return _gemm2_gather(a, b, bias, residual, out, M, N, K, a_mn_major, out_f32, gather, b_gather is not None)
     if out is None:
         out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.float32 if out_f32 else torch.bfloat16, device=a.device)
     assert out.stride(1) == 1

@@ -132,8 +132,8 @@ class FlatBuckets:
             biggest = max(sp.numel for sp in self.specs.values() if sp.sharded)
             self.stage = torch.empty(biggest, dtype=dtype, device=self.params.device)
             if comm.on_gpu:
-                self.gather_count = torch.zeros(8, dtype=torch.int32, device=self.params.device)
-                self.gather_ready = torch.zeros(8, dtype=torch.int32, device=self.params.device)
+                self.gather_count = torch.zeros(64, dtype=torch.int32, device=self.params.device)    # [parts x pieces of a part]
+                self.gather_ready = torch.zeros(64, dtype=torch.int32, device=self.params.device)
 
     # ---------------------------------------------------------------- deferred parameter updates
     def ensure_chunk(self, chunk: int) -> None:

@@ -153,3 +153,34 @@ def test_flash_long_sequences_two_tile_kernel(cuda_device, D, Hq, Hkv, causal, w
     diff = (got.float() - want.float()).abs()
     assert diff.max().item() < 0.02 and diff.mean().item() < 0.001, (diff.max().item(), diff.mean().item())
     assert torch.allclose(lse, lse_ref, atol=2e-3, rtol=1e-4), (lse - lse_ref).abs().max().item()
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 8, 2), (64, 14, 2)])
+def test_flash_backward_head_split(cuda_device, monkeypatch, D, Hq, Hkv):
+    """dK/dV with one CTA per (key tile, query head) and a reduction over each group: same gradients as the
+    per-kv-head form and as the fp32 reference; the automatic rule picks it only where the coarse grid has fewer CTAs than the GPU has SMs."""
+    lens = [700, 129, 1]
+    T = sum(lens)
+    qkv = _rand((T, (Hq + 2 * Hkv) * D), cuda_device, seed=21)
+    q = qkv[:, : Hq * D].view(T, Hq, D)
+    k = qkv[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D :].view(T, Hkv, D)
+    dout = _rand((T, Hq, D), cuda_device, seed=22)
+    cu = _cu(lens, cuda_device)
+    out, lse = flash.flash_attn_varlen(q, k, v, cu, cu, max(lens), causal=True, return_lse=True)
+    monkeypatch.setattr(flash, "_HEAD_SPLIT", "0")
+    base = flash.flash_attn_varlen_backward(q, k, v, out, dout, lse, cu, cu, max(lens), max(lens), True, 0)
+    monkeypatch.setattr(flash, "_HEAD_SPLIT", "1")
+    split = flash.flash_attn_varlen_backward(q, k, v, out, dout, lse, cu, cu, max(lens), max(lens), True, 0)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o_ref, _ = flash.flash_attn_varlen_reference(qf, kf, vf, cu, cu, causal=True)
+    rq, rk, rv = torch.autograd.grad(o_ref, (qf, kf, vf), dout.float())
+    for got, want, what in zip(split, (rq, rk, rv), ("dq", "dk", "dv")):
+        _grad_check(got, want, what + " (head split)")
+    assert torch.equal(split[0], base[0])                       # dQ does not depend on the split
+    for a, b in zip(split[1:], base[1:]):                       # fp32 sums over the group vs one accumulator: same to bf16 rounding
+        assert (a.float() - b.float()).abs().max().item() < 0.02
+    monkeypatch.setattr(flash, "_HEAD_SPLIT", "auto")
+    assert flash.head_split_pays(1, 4096, 4096, 16, 2) and not flash.head_split_pays(1, 4096, 4096, 32, 8)
+    assert not flash.head_split_pays(32, 512, 512, 14, 2) and not flash.head_split_pays(1, 4096, 4096, 8, 8)
+    ops.check_status()
