@@ -54,7 +54,7 @@ struct G2Params {
   int out_f32;
   int* status;
   // Fused all-gather of a row-sharded matrix (GATHER instantiations; same contract as the one-CTA kernel): part r is
-  // gather_part_bytes at gather_src[r] (rank r's shard, peer memory); the two gather warps of every CTA copy an
+  // gather_part_bytes at gather_src[r] (rank r's shard, peer memory); the gather warps of every CTA copy an
   // interleaved share of each part to gather_dst + r * bytes, own part first, and the last CTA to finish a part
   // publishes gather_ready[r] = gather_epoch. With `consume` the gathered matrix is this launch's K-major B operand:
   // tiles visit the parts starting at the local one and their producers wait for the part they read.
@@ -70,7 +70,8 @@ struct G2Params {
   int gather_chunks, gather_chunk_tiles;
   long long gather_chunk_bytes;
 };
-constexpr int G2_THREADS_GATHER = G2_THREADS + 64;
+constexpr int G2_GATHER_WARPS = 4;      // measured with 2: the copy (159 GB/s over NVLink) set the launch's time
+constexpr int G2_THREADS_GATHER = G2_THREADS + 32 * G2_GATHER_WARPS;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -244,7 +245,7 @@ __global__ void __launch_bounds__(GATHER ? G2_THREADS_GATHER : G2_THREADS, 1) ge
     }
   } else if (GATHER && warp >= 2 + G2_EPI_WARPS) {
     // ------------------------------ gather warps (both CTAs) ------------------------------------
-    constexpr int GT = 64;
+    constexpr int GT = 32 * G2_GATHER_WARPS;
     const int gt = (warp - 2 - G2_EPI_WARPS) * 32 + lane;
     const long long stride = (long long)gridDim.x * GT;
     for (int pp = 0; pp < p.gather_parts; ++pp) {

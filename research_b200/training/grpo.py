@@ -42,6 +42,10 @@ class GRPOConfig:
     inference_backend: str = "native"          # "native" (in-process engine); "sglang"/"vllm" use weight_sync engines
     inference_port: int = 30000
     inference_cuda_device_ids: tuple[int, ...] = (0,)
+    # several inference devices disjoint from the trainers': "replicas" = one engine per device on its own prompts;
+    # "tensor" = ONE tensor-parallel engine over all of them (what the reference's external server does with the same
+    # device tuple, rollouts/training/grpo.py:172-199), fed by the kernel weight sync into its sharded layout
+    inference_parallelism: str = "replicas"
     mem_fraction: float = 0.7
     trainer_cuda_device_ids: tuple[int, ...] = (0,)
     lr: float = 1e-6
@@ -271,6 +275,7 @@ async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls
     rank, world = dist.get_rank(), dist.get_world_size()
     T, E = len(trainer_ranks), len(engine_ranks)
     is_trainer = rank in trainer_ranks
+    engine_tp = config.inference_parallelism == "tensor" and E > 1
     ids = tuple(config.trainer_cuda_device_ids) + tuple(config.inference_cuda_device_ids)
     if device is not None:
         dev = torch.device(device)
@@ -307,19 +312,29 @@ async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls
     else:
         buckets = build_buckets(model_cfg, LayoutComm(T, dev), dtype, False, param_comm=shared_params, with_grads=False)
         ei = engine_ranks.index(rank)
+        tp = None
+        if engine_tp:
+            # one engine over all engine ranks: every one of them runs the same schedule on the same prompts with the
+            # same seeds (the fused GEMM + all-reduce launches keep them in step); only the first reports samples
+            from ..parallel.tp import TensorParallel
+
+            tp = TensorParallel(PeerComm(egroup, dev), max_rows=max(config.max_batch_size * 64 + 64, 2048), max_cols=max(model_cfg.hidden_size, 1024))
+            ei, n_engines = 0, 1
+        else:
+            n_engines = E
         ecfg = EngineConfig(cache_type=config.cache_type, max_batch_size=config.max_batch_size,
                             max_model_len=max(config.max_seq_len + config.max_tokens, 64), num_kv_blocks=config.kv_blocks,
-                            seed=config.seed * 1009 + ei, ignore_eos=tokenizer is None)
-        engine = InferenceEngine(ecfg, model_cfg, weights, tokenizer=tokenizer, device=dev)
-        mine = prompts[ei::E]
-        truths = ground_truths[ei::E] if ground_truths else None
+                            seed=config.seed * 1009 + ei, ignore_eos=tokenizer is None, tensor_parallel_size=E if engine_tp else 1)
+        engine = InferenceEngine(ecfg, model_cfg, weights, tokenizer=tokenizer, device=dev, tp=tp)
+        mine = prompts[ei::n_engines]
+        truths = ground_truths[ei::n_engines] if ground_truths else None
         gen_fn = _create_tito_generate_fn(engine, config, tokenizer)
         if environment_cls is not None and not config.use_tito:
             from .agent_integration import make_agent_generate_fn
 
             gen_fn = make_agent_generate_fn(engine, environment_cls, config, tokenizer)
         manager = AsyncRolloutManager(DataBuffer(mine, seed=config.seed, ground_truths=truths),
-                                      RolloutConfig(batch_size=max(config.batch_size // E, 1), n_samples_per_prompt=config.n_samples_per_prompt,
+                                      RolloutConfig(batch_size=max(config.batch_size // n_engines, 1), n_samples_per_prompt=config.n_samples_per_prompt,
                                                     generate_fn=gen_fn, score_fn=score_fn, filter_fn=filter_fn))
     del weights
     dist.barrier()
@@ -334,11 +349,13 @@ async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls
                 batch = await manager.generate_batch()
                 ei = engine_ranks.index(rank)
                 for s in batch.samples:
-                    s.group_index = (s.group_index or 0) * E + ei          # group ids stay distinct across engines
+                    if not engine_tp:
+                        s.group_index = (s.group_index or 0) * E + ei      # group ids stay distinct across engines
                     rollouts_file.write(json.dumps({"step": step, "reward": s.reward, "tokens": len(s.tokens),
                                                     "response_length": s.response_length, "group": s.group_index,
                                                     "weight_version": s.weight_version}) + "\n")
-                    mine_out.append(s.to_dict())
+                    if not engine_tp or ei == 0:                           # the ranks of one engine all hold the same samples
+                        mine_out.append(s.to_dict())
             t_roll = time.perf_counter() - t0
             gathered: list = [None] * world
             dist.all_gather_object(gathered, mine_out)
@@ -373,7 +390,7 @@ async def _grpo_train_disjoint(config, roles, prompts, score_fn, environment_cls
                 if on_gpu:
                     if not is_trainer:
                         src = trainer_ranks[engine_ranks.index(rank) % T]
-                        plan = sync_engine_from_buckets(engine, buckets, plan, src_rank=src)
+                        plan = sync_engine_from_buckets(engine, buckets, plan, src_rank=src)       # each rank pulls its shard of the layout
                         torch.cuda.synchronize(dev)
                 else:
                     flat = buckets.params

@@ -31,6 +31,7 @@ def main() -> None:
     ap.add_argument("--minibatches", type=int, default=8)
     ap.add_argument("--loss", default="grpo_clipped")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--engine-tp", action="store_true", help="with --trainers: the serving ranks form ONE tensor-parallel engine")
     ap.add_argument("--trainers", type=int, default=0,
                     help="several ranks: the first N ranks only train, the others only serve (disjoint device sets); 0 = every rank does both")
     args = ap.parse_args()
@@ -64,7 +65,9 @@ def main() -> None:
         import dataclasses
 
         gcfg = dataclasses.replace(gcfg, trainer_cuda_device_ids=tuple(range(args.trainers)),
-                                   inference_cuda_device_ids=tuple(range(args.trainers, world)))
+                                   inference_cuda_device_ids=tuple(range(args.trainers, world)),
+                                   inference_parallelism="tensor" if args.engine_tp else "replicas",
+                                   max_batch_size=min(256, args.prompts * args.samples) if args.engine_tp else gcfg.max_batch_size)
     hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=args.device)
     steps = hist[1:]                      # the first step pays one-time set-up (graph capture, allocator growth)
     n = len(steps)
@@ -79,7 +82,8 @@ def main() -> None:
     gen_tokens = samples * args.max_tokens
     trained_tokens = samples * (args.prompt_len * 0.75 + args.max_tokens)     # prompts are U[len/2, len]
     row = {"bench": "grpo_step", "model": args.model, "world": world,
-           "placement": f"{args.trainers} trainer + {world - args.trainers} engine ranks" if disjoint else "every rank trains and serves",
+           "placement": (f"{args.trainers} trainer ranks + " + (f"one tensor-parallel engine over {world - args.trainers} ranks" if args.engine_tp
+                                                                 else f"{world - args.trainers} engine ranks")) if disjoint else "every rank trains and serves",
            "samples_per_step": samples,
            "max_tokens": args.max_tokens, "prompt_len": f"U[{args.prompt_len // 2},{args.prompt_len}]", "loss": args.loss,
            "step_s": round(mean("step_s"), 4),

@@ -316,6 +316,35 @@ def case_grpo_disjoint(comm, dev, dt):
         dist.barrier()
 
 
+def case_grpo_disjoint_tp_engine(comm, dev, dt):
+    """Disjoint placement with ONE tensor-parallel engine over the serving ranks (needs at least 3 ranks: the last two
+    serve): both engine ranks generate the same samples in step, one of them reports, the trainers' new parameters
+    reach both engine shards."""
+    import tempfile
+
+    from research_b200.training.grpo import GRPOConfig, grpo_train
+
+    W = comm.world
+    if W < 3:
+        return
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 4096, (int(n),), generator=g).tolist() for n in torch.randint(16, 48, (12,), generator=g)]
+    with tempfile.TemporaryDirectory() as d:
+        os.environ["ROLLOUTS_RUN_NAME"] = "disjoint_tp_run"
+        gcfg = GRPOConfig(model_name="tiny-qwen2", lr=1e-4, batch_size=4, n_samples_per_prompt=4, num_minibatches=2, max_tokens=6,
+                          max_seq_len=96, temperature=1.0, num_steps=2, output_dir=d, checkpoint_every=0, max_batch_size=16,
+                          kv_blocks=128, trainer_cuda_device_ids=tuple(range(W - 2)), inference_cuda_device_ids=(W - 2, W - 1),
+                          inference_parallelism="tensor")
+        hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=dev)
+        # 4 prompt groups x 4 samples from the one engine (not once per engine rank)
+        assert len(hist) == 2 and hist[-1]["weight_version"] == 2.0 and hist[0]["num_samples"] == 16.0, hist[0]
+        t = torch.tensor([hist[-1]["mean_reward"]], dtype=torch.float64, device=dev)
+        ref = t.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(t, ref)
+        dist.barrier()
+
+
 def case_moe_expert_parallel(comm, dev, dt):
     """Each rank routes its own tokens; experts are split over the ranks; dispatch and combine
     travel through peer memory. Checked against the single-process functional MoE."""
@@ -379,7 +408,7 @@ def case_ep_agree(comm, dev, dt):
 
 CASES = {"ep_agree": case_ep_agree, "barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
          "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo,
-         "fsdp_full_shard": case_fsdp_full_shard, "grpo_disjoint": case_grpo_disjoint,
+         "fsdp_full_shard": case_fsdp_full_shard, "grpo_disjoint": case_grpo_disjoint, "grpo_disjoint_tp_engine": case_grpo_disjoint_tp_engine,
          "moe_ep": case_moe_expert_parallel}
 
 
