@@ -1373,7 +1373,10 @@ __global__ void flash_bwd_reduce_kernel(const float* __restrict__ part, int G, l
 template <int D>
 static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, cudaStream_t stream) {
   using Cfg = FlashBwdCfg<D>;
-  static bool attr = false;
+  static bool attr_dev[64] = {};       // the shared-memory opt-in is a per-device function attribute
+  int dev_i = 0;
+  if (cudaGetDevice(&dev_i) != cudaSuccess || dev_i < 0 || dev_i >= 64) return -10;
+  bool& attr = attr_dev[dev_i];
   if (!attr) {
     if (cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemDkdv) !=
         cudaSuccess)
@@ -1396,7 +1399,10 @@ static int launch_flash_bwd(const FlashBwdParams& p, dim3 grid_kv, dim3 grid_q, 
 
 template <int D>
 static int launch_flash_fwd(const FlashFwdParams& p, int max_seqlen_q, int B, cudaStream_t stream) {
-  static bool attr = false;
+  static bool attr_dev[64] = {};       // the shared-memory opt-in is a per-device function attribute
+  int dev_i = 0;
+  if (cudaGetDevice(&dev_i) != cudaSuccess || dev_i < 0 || dev_i >= 64) return -10;
+  bool& attr = attr_dev[dev_i];
   if (!attr) {
     if (cudaFuncSetAttribute(flash_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashCfg<D>::kSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(flash_fwd2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Flash2Cfg<D>::kSmemBytes) != cudaSuccess)

@@ -1173,7 +1173,10 @@ template <int BN, bool A_MN, bool B_MN, bool NORM = false, bool GATHER = false>
 static int launch_cfg(const GemmParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, NORM, GATHER>;
-  static bool attr_set = false;
+  static bool attr_dev[64] = {};       // the shared-memory opt-in is a per-device function attribute
+  int dev_i = 0;
+  if (cudaGetDevice(&dev_i) != cudaSuccess || dev_i < 0 || dev_i >= 64) return -10;
+  bool& attr_set = attr_dev[dev_i];
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
     if (e != cudaSuccess) return -10;
