@@ -1029,21 +1029,27 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
     const int half = (warp - 2) >> 2;              // which 32 of the 64 query columns
     const int tid = threadIdx.x - 64;              // 0..255
     bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
-      const int h = kvh * G + g_base + it / n_qt, qi0 = (i_begin + it % n_qt) * 64;
-      {   // row statistics of the 64 queries: thread t<64 -> lse2, t>=64 -> delta
-        if (tid < 128) {
-          const int idx = tid & 63, which = tid >> 6;
-          const int qi = qi0 + idx;
-          float val = which == 0 ? INFINITY : 0.f;    // lse2 = +inf makes P exactly 0 for rows past the end
-          if (qi < q_len) val = (which == 0 ? p.lse2 : p.delta)[(long long)h * p.Tq + q_begin + qi];
-          stat[it & 1][which][idx] = val;
-        }
-        mbar_arrive(smem_u32(&stat_bar));
-        ok = mbar_wait_backoff(smem_u32(&stat_bar), (uint32_t)(it & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
+    // Row statistics of an iteration's 64 queries (thread t < 64 -> lse2, 64 <= t < 128 -> delta) are fetched one
+    // iteration ahead: the loads are issued at the top of iteration it for it + 1 and land in shared memory at its
+    // end, so their latency and the 256-thread barrier that publishes them are off the critical path.
+    auto load_stat = [&](int it2) -> float {
+      const int h2 = kvh * G + g_base + it2 / n_qt, qi = (i_begin + it2 % n_qt) * 64 + (tid & 63);
+      const int which = tid >> 6;
+      float val = which == 0 ? INFINITY : 0.f;      // lse2 = +inf makes P exactly 0 for rows past the end
+      if (qi < q_len) val = (which == 0 ? p.lse2 : p.delta)[(long long)h2 * p.Tq + q_begin + qi];
+      return val;
+    };
+    if (n_iter > 0) {
+      if (tid < 128) stat[0][tid >> 6][tid & 63] = load_stat(0);
+      mbar_arrive(smem_u32(&stat_bar));
+      ok = mbar_wait_backoff(smem_u32(&stat_bar), 0u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int qi0 = (i_begin + it % n_qt) * 64;
+      const bool have_next = it + 1 < n_iter;
+      float stat_next = 0.f;
+      if (have_next && tid < 128) stat_next = load_stat(it + 1);
       ok = mbar_wait_backoff(smem_u32(&st_full[it & 1]), (it >> 1) & 1u, abortp, p.status, ST_TIMEOUT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -1079,6 +1085,13 @@ __global__ void __launch_bounds__(FA_BWD_THREADS, 1) flash_bwd_dkdv_kernel(const
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&pds_full[it & 1]));
+      if (have_next) {
+        // every thread has read stat[(it + 1) & 1] for the last time in iteration it - 1, before that iteration's barrier
+        if (tid < 128) stat[(it + 1) & 1][tid >> 6][tid & 63] = stat_next;
+        mbar_arrive(smem_u32(&stat_bar));
+        ok = mbar_wait_backoff(smem_u32(&stat_bar), (uint32_t)((it + 1) & 1), abortp, p.status, ST_TIMEOUT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
     }
     if (ok && n_iter > 0) {
       ok = mbar_wait_backoff(smem_u32(&acc_done), 0, abortp, p.status, ST_TIMEOUT_TMEM_FULL);

@@ -492,3 +492,18 @@ def test_wait_budget_is_a_launch_setting(cuda_device):
     assert lib.rb_comm_get_wait_budget_ns() == 5_000_000
     lib.rb_comm_set_wait_budget_ns(0)
     assert lib.rb_comm_get_wait_budget_ns() == default
+
+
+def test_gemm_waits_for_a_flag_inside_the_launch(cuda_device):
+    """``wait_flag``: the tile producers compare a device flag with a device value before their first load (the
+    tensor-parallel all-reduce uses it to wait for the peers' acknowledgements). Satisfied flag: normal result, on the
+    plain and on the cluster split-K path."""
+    g = torch.Generator().manual_seed(5)
+    flag = torch.tensor([3, 3], dtype=torch.int32, device=cuda_device)      # [0] flag, [1] value it must reach
+    for M, N, K in ((64, 1024, 4096), (256, 512, 256)):
+        a = torch.randn(M, K, generator=g).bfloat16().to(cuda_device)
+        w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(cuda_device)
+        out = ops.gemm(a, w, wait_flag=(flag.data_ptr(), flag.data_ptr() + 4))
+        want = a.float() @ w.float().t()
+        assert (out.float() - want).abs().max().item() < 0.02 * K ** 0.5
+    ops.check_status()
