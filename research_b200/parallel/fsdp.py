@@ -46,6 +46,7 @@ class ParamSpec:
     chunk: int
     p_offset: int = 0  # element offset inside this rank's parameter storage
     sharded: bool = False   # the parameter storage holds rows [rank * rows / world, (rank + 1) * rows / world) only
+    owned: bool = False     # the parameter exists on this rank only (an expert of its expert-parallel share)
 
 
 class FlatBuckets:
@@ -55,11 +56,16 @@ class FlatBuckets:
     training): the parameter storage of a rank then holds its row slab only, the gradient bucket still holds the
     full matrix (backward writes all of it, the reduce-scatter keeps this rank's slab). A chunk holds either sharded
     or unsharded parameters, never both; sharded chunks reduce and update slab by slab and push nothing to the
-    peers, whose GEMM launches fetch the slabs when they need the matrix (``ShardedWeight``)."""
+    peers, whose GEMM launches fetch the slabs when they need the matrix (``ShardedWeight``).
+
+    ``owned_rule(name) -> bool`` marks parameters that exist on this rank ONLY (expert-parallel training: every rank
+    lists its own experts, so the names differ between the ranks while the layout is the same). Their chunks are
+    neither reduced over the ranks nor gathered: the owner computes the whole gradient (every token routed to the
+    expert reaches it), keeps the whole optimizer state and updates in place."""
 
     def __init__(self, comm: PeerComm, named_shapes: list[tuple[str, tuple[int, ...]]], chunk_of=None,
                  dtype: torch.dtype = torch.bfloat16, shard_rule=None, param_comm: PeerComm | None = None,
-                 with_grads: bool = True):
+                 with_grads: bool = True, owned_rule=None):
         """``param_comm``: allocate the parameter storage in the symmetric memory of ANOTHER (larger) group, so that
         ranks outside ``comm`` (inference engines on their own GPUs) can read it over NVLink; the members of ``comm``
         must be that group's first ranks, in order. ``with_grads=False``: a layout-only instance on such an outside
@@ -71,8 +77,9 @@ class FlatBuckets:
         self.chunks: list[tuple[int, int]] = []  # (offset, length) per chunk in the gradient bucket, length % align == 0
         self.p_chunks: list[tuple[int, int]] = []  # the same chunks in this rank's parameter storage
         self.chunk_sharded: list[bool] = []
+        self.chunk_owned: list[bool] = []
         off = p_off = 0
-        cur_chunk, chunk_start, p_chunk_start, cur_sharded = None, 0, 0, False
+        cur_chunk, chunk_start, p_chunk_start, cur_sharded, cur_owned = None, 0, 0, False, False
 
         def close_chunk():
             nonlocal off, p_off
@@ -82,6 +89,7 @@ class FlatBuckets:
                 p_off = p_chunk_start + (off - chunk_start)      # same layout as the gradient chunk
             self.p_chunks.append((p_chunk_start, p_off - p_chunk_start))
             self.chunk_sharded.append(cur_sharded)
+            self.chunk_owned.append(cur_owned)
 
         for name, shape in named_shapes:
             c = chunk_of(name) if chunk_of else 0
@@ -89,17 +97,20 @@ class FlatBuckets:
             for s in shape:
                 n *= s
             sharded = bool(shard_rule(name, tuple(shape))) if (shard_rule is not None and W > 1) else False
+            owned = bool(owned_rule(name)) if (owned_rule is not None and W > 1) else False
+            assert not (sharded and owned), f"{name}: a parameter is either row-sharded or owned by one rank"
             if sharded:
                 assert len(shape) == 2 and shape[0] % W == 0 and (n // W) % 8 == 0, f"{name} {shape} cannot be row-sharded over {W}"
             if cur_chunk is None:
-                cur_chunk, cur_sharded = c, sharded
+                cur_chunk, cur_sharded, cur_owned = c, sharded, owned
             if c != cur_chunk:
                 close_chunk()
-                chunk_start, p_chunk_start, cur_chunk, cur_sharded = off, p_off, c, sharded
+                chunk_start, p_chunk_start, cur_chunk, cur_sharded, cur_owned = off, p_off, c, sharded, owned
             assert sharded == cur_sharded, f"chunk {c} mixes sharded and unsharded parameters ({name})"
+            assert owned == cur_owned, f"chunk {c} mixes replicated parameters and parameters owned by one rank ({name})"
             n_pad = -(-n // 8) * 8  # keep every parameter 16-byte aligned for TMA
             self.specs[name] = ParamSpec(name, tuple(shape), off, n, len(self.chunks),
-                                         p_off if sharded else p_chunk_start + (off - chunk_start), sharded)
+                                         p_off if sharded else p_chunk_start + (off - chunk_start), sharded, owned)
             off += n_pad
             if sharded:
                 p_off += n // W
@@ -107,6 +118,7 @@ class FlatBuckets:
         self.numel = off
         self.p_numel = p_off
         self.any_sharded = any(self.chunk_sharded)
+        self.any_owned = any(self.chunk_owned)
         self.dtype = dtype
         self.params_buf = (param_comm or comm).alloc((self.p_numel,), dtype, zero=True)
         self.params = self.params_buf.local
@@ -285,7 +297,7 @@ class ShardedAdamW:
         even slice of an unsharded chunk, or everything it stores of a sharded one (its row slabs)."""
         b = self.b
         p_off, p_len = b.p_chunks[chunk]
-        if b.chunk_sharded[chunk]:
+        if b.chunk_sharded[chunk] or b.chunk_owned[chunk]:
             return p_off, p_len
         n = p_len // self.comm.world
         return p_off + self.comm.rank * n, n
@@ -310,11 +322,14 @@ class ShardedAdamW:
         b.zero_unwritten(chunk)
         self._passes[chunk] = self._passes.get(chunk, 0) + 1
         sharded = b.chunk_sharded[chunk]
+        owned = b.chunk_owned[chunk]
         if not self.on_gpu:
             g = b.grads[off:off + length].float()
-            if comm.world > 1:
+            if comm.world > 1 and not owned:
                 dist.all_reduce(g, group=comm.group)
-            if sharded:
+            if owned:
+                mine = g * scale         # the owner holds the whole gradient already: only the 1 / world of the mean is left
+            elif sharded:
                 mine = torch.cat([g[o - off:o - off + m] for o, m, _ in b.segments(chunk)]) * scale
             else:
                 mine = g[comm.rank * n:(comm.rank + 1) * n] * scale
@@ -331,6 +346,16 @@ class ShardedAdamW:
             # nothing to reduce: only this chunk's share of the gradient norm (the scale rides in the clip coefficient)
             rc = _lib().rb_rs_reduce_ex(ptrs, None, 0, 0, 0, 1, n, 1.0, None, 0, self.partial.data_ptr(), st, 0,
                                         stream_handle(dev))
+            check_rc(rc, "rb_rs_reduce_ex")
+            self._reduced.add(chunk)
+            return
+        if owned:
+            # nothing to fetch from the peers: cast, scale and the chunk's share of the gradient norm, all local
+            from .symm import ptr_array
+
+            rc = _lib().rb_rs_reduce_ex(ptr_array([b.grads.data_ptr() + off * 2]), None, 0, 0, 0, 1, length, scale,
+                                        self.red[chunk].data_ptr(), int(accumulate), self.partial.data_ptr(), st,
+                                        self.overlap_grid if overlapped else 0, stream_handle(dev))
             check_rc(rc, "rb_rs_reduce_ex")
             self._reduced.add(chunk)
             return
@@ -388,8 +413,8 @@ class ShardedAdamW:
                 p.mul_(1 - self.lr * self.weight_decay)
                 p.addcdiv_(self.exp_avg[c] / bc1, (self.exp_avg_sq[c] / bc2).sqrt() + self.eps, value=-self.lr)
                 off, length = b.p_chunks[c]
-                if b.chunk_sharded[c]:
-                    b.params[off:off + length].copy_(p.to(b.dtype))        # this rank's slabs; nothing is pushed
+                if b.chunk_sharded[c] or b.chunk_owned[c]:
+                    b.params[off:off + length].copy_(p.to(b.dtype))        # this rank's slabs / own experts; nothing is pushed
                 elif comm.world > 1:
                     parts = [torch.empty_like(p) for _ in range(comm.world)]
                     dist.all_gather(parts, p, group=comm.group)
@@ -446,7 +471,7 @@ class ShardedAdamW:
         b, comm = self.b, self.comm
         dev = b.params.device
         p_off, p_len = b.p_chunks[c]
-        if b.chunk_sharded[c]:
+        if b.chunk_sharded[c] or b.chunk_owned[c]:
             # the rank owns everything it stores of this chunk: update in place, nothing is pushed (the peers'
             # GEMM launches fetch the slabs when they need the matrix)
             from .symm import ptr_array

@@ -29,6 +29,10 @@ class FSDPConfig:
     cpu_offload: bool = False
     gradient_checkpointing: bool = False
     clip_grad: float | None = 1.0
+    # Mixture-of-experts models: rank r keeps experts [r E / W, (r + 1) E / W) of every layer (parameters, gradients and
+    # optimizer state exist once in the job); tokens travel to their experts' owners and back inside every MoE layer.
+    # Everything that is not an expert stays data-parallel as above. The reference has no expert-parallel training.
+    expert_parallel: bool = False
 
     def __post_init__(self) -> None:
         assert not self.cpu_offload, "cpu_offload is not supported: 180 GB of HBM per GPU holds the state"
@@ -48,6 +52,7 @@ class FSDPTrainingBackend(NativeTrainingBackend):
         assert group is None or comm.group is group or comm.world == dist.get_world_size(group)
         kw.setdefault("activation_checkpointing", cfg.gradient_checkpointing)
         kw.setdefault("shard_params", cfg.sharding_strategy == "full_shard")
+        kw.setdefault("expert_parallel", cfg.expert_parallel)
         super().__init__(model_config, weights, comm=comm, device=device, **kw)
         self.fsdp_config = cfg
 

@@ -74,14 +74,38 @@ def _shardable(name: str, shape: tuple, world: int) -> bool:
 _VECTOR_CHUNK = 9_000     # sharded mode: the layers' vectors (norm weights, biases) live in one chunk of their own
 
 
+_EXPERT_CHUNK = 20_000    # expert-parallel training: a layer's own experts live in chunk _EXPERT_CHUNK + layer
+
+
 def build_buckets(model_config: ModelConfig, comm, dtype: torch.dtype, shard_params: bool = False, param_comm=None,
-                  with_grads: bool = True) -> FlatBuckets:
+                  with_grads: bool = True, expert_parallel: bool = False) -> FlatBuckets:
     """The flat parameter / gradient layout of a model for ``comm.world`` training ranks. A rank outside the training
     group (an inference engine on its own GPU) builds the SAME layout with a stand-in ``comm`` of the trainers' size and
     ``with_grads=False``: it then knows where every parameter lies in the trainers' storage (``param_comm``: the
     symmetric memory both sides share)."""
     all_shapes = param_shapes(model_config)
     chunk_of, rule = _chunk_of, None
+    owned_rule, ep = None, None
+    if expert_parallel and comm.world > 1 and model_config.is_moe:
+        # Expert-parallel training: rank r keeps experts [r * E / W, (r + 1) * E / W) of every layer and nobody else
+        # does: their parameters, gradients and optimizer state exist once in the job. Everything else is laid out as
+        # before. Every rank lists the same NUMBER of experts, so offsets agree between the ranks although names differ.
+        W, E = comm.world, model_config.num_experts
+        assert E % W == 0, f"{E} experts do not split over {W} ranks"
+        EL = E // W
+        lo = comm.rank * EL
+
+        def owned_rule(name):
+            return _EXPERT.match(name) is not None
+
+        all_shapes = {n: s for n, s in all_shapes.items()
+                      if (m := _EXPERT.match(n)) is None or lo <= int(m.group(2)) < lo + EL}
+        base_chunk_of = chunk_of
+
+        def chunk_of(name, base=base_chunk_of):
+            return _EXPERT_CHUNK + int(name.split(".")[2]) if _EXPERT.match(name) else base(name)
+
+        ep = (comm.rank, W, EL)
     if shard_params and comm.world > 1:
         W = comm.world
 
@@ -92,7 +116,10 @@ def build_buckets(model_config: ModelConfig, comm, dtype: torch.dtype, shard_par
             return _chunk_of(name) if (not name.startswith("model.layers.") or rule(name, tuple(all_shapes[name]))) else _VECTOR_CHUNK
 
     shapes = sorted(all_shapes.items(), key=lambda kv: _order_key(kv[0], chunk_of))
-    return FlatBuckets(comm, shapes, chunk_of, dtype=dtype, shard_rule=rule, param_comm=param_comm, with_grads=with_grads)
+    fb = FlatBuckets(comm, shapes, chunk_of, dtype=dtype, shard_rule=rule, param_comm=param_comm, with_grads=with_grads,
+                     owned_rule=owned_rule)
+    fb.expert_parallel = ep          # (rank, ranks, experts per rank) or None
+    return fb
 
 
 class NativeTrainingBackend:
@@ -103,7 +130,7 @@ class NativeTrainingBackend:
                  trainer_config: TrainerConfig | None = None, lr_schedule: Callable[[int], float] | None = None,
                  checkpoint_dir: str | Path | None = None, activation_checkpointing: bool = False,
                  need_entropy: bool | None = None, seed: int = 0, overlap_comm: bool = True, shard_params: bool = False,
-                 param_comm: PeerComm | None = None):
+                 param_comm: PeerComm | None = None, expert_parallel: bool = False):
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda" if torch.cuda.is_available() else "cpu")
         self.comm = comm if comm is not None else LocalComm(self.device)
@@ -113,7 +140,9 @@ class NativeTrainingBackend:
         on_gpu = self.device.type == "cuda"
         dtype = torch.bfloat16 if on_gpu else torch.float32
         self.shard_params = bool(shard_params) and self.world > 1
-        self.buckets = build_buckets(model_config, self.comm, dtype, self.shard_params, param_comm)
+        self.expert_parallel = bool(expert_parallel) and self.world > 1 and model_config.is_moe
+        assert not (self.expert_parallel and self.shard_params), "expert-parallel training keeps the other parameters replicated"
+        self.buckets = build_buckets(model_config, self.comm, dtype, self.shard_params, param_comm, expert_parallel=self.expert_parallel)
         if weights is None and on_gpu:
             # random init written straight into the bucket (an 8B model never exists twice in memory)
             # whole tensors: the same seed on every rank gives every rank the same values; row slabs: seeded per rank
@@ -126,7 +155,7 @@ class NativeTrainingBackend:
                 elif n.endswith(".bias"):
                     v.zero_()
                 else:
-                    v.normal_(0.0, model_config.init_std, generator=g_slab if sp.sharded else g)
+                    v.normal_(0.0, model_config.init_std, generator=g_slab if (sp.sharded or sp.owned) else g)
         else:
             if weights is None:
                 from ...models.weights import init_random_weights
@@ -159,7 +188,11 @@ class NativeTrainingBackend:
             self.optimizer.update_stream = self._side
             ids = {n: sp.chunk for n, sp in self.buckets.specs.items()}
             first = [ids[n] for n in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight") if n in ids]
-            rest = [c for c in range(len(self.buckets.chunks)) if c not in first]
+            def first_use(c):      # the layer whose forward needs chunk c first (a layer's own experts: that layer)
+                layers = [int(sp.name.split(".")[2]) for sp in self.buckets._chunk_specs[c] if sp.name.startswith("model.layers.")]
+                return min(layers) if layers else (-1 if any(sp.name.startswith("model.embed") for sp in self.buckets._chunk_specs[c]) else 1 << 30)
+
+            rest = sorted((c for c in range(len(self.buckets.chunks)) if c not in first), key=first_use)
             self.optimizer.update_order = list(dict.fromkeys(first)) + rest
         self.model = NativeCausalLM(model_config, self.buckets, self.device, activation_checkpointing)
         self.loss_name = loss_fn if isinstance(loss_fn, str) else getattr(loss_fn, "__name__", "custom")
@@ -289,6 +322,8 @@ class NativeTrainingBackend:
             raise
 
     def get_weights(self) -> TrainFuture[dict[str, Any]]:
+        if self.expert_parallel:      # the whole model, the other ranks' experts included
+            return ImmediateTrainFuture({n: v.detach().clone() for n, v in self.model.state_dict().items()}, "get_weights")
         return ImmediateTrainFuture({n: self.buckets.full_param(n).detach().clone() for n in self.buckets.specs},
                                     "get_weights")
 
@@ -311,7 +346,9 @@ class NativeTrainingBackend:
     def save_checkpoint_to_path(self, path: Path | str, step: int | None = None, metrics: dict | None = None) -> Path:
         path = Path(path)
         path.mkdir(parents=True, exist_ok=True)
-        if self.buckets.any_sharded and self.device.type != "cuda":
+        if self.expert_parallel:
+            gathered = {n: v.detach().cpu() for n, v in self.model.state_dict().items()}           # every rank's experts
+        elif self.buckets.any_sharded and self.device.type != "cuda":
             gathered = {n: self.buckets.full_param(n).detach().cpu() for n in self.buckets.specs}   # a collective on CPU groups
         else:
             gathered = None

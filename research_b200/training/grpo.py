@@ -46,6 +46,10 @@ class GRPOConfig:
     # "tensor" = ONE tensor-parallel engine over all of them (what the reference's external server does with the same
     # device tuple, rollouts/training/grpo.py:172-199), fed by the kernel weight sync into its sharded layout
     inference_parallelism: str = "replicas"
+    # mixture-of-experts models on several ranks: the experts are split over the ranks for BOTH the update (every rank
+    # keeps parameters, gradients and optimizer state of its own experts only) and the rollouts (data-parallel engines in
+    # lock step, tokens dispatched to the experts' owners); the kernel weight sync then only moves a rank's own experts
+    expert_parallel: bool = False
     mem_fraction: float = 0.7
     trainer_cuda_device_ids: tuple[int, ...] = (0,)
     lr: float = 1e-6
@@ -160,11 +164,21 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
     tcfg = TrainerConfig(num_minibatches=config.num_minibatches, max_grad_norm=config.max_grad_norm)
     kw = dict(device=dev, loss_fn=config.loss, lr=config.lr, weight_decay=config.weight_decay, trainer_config=tcfg,
               checkpoint_dir=out_dir / "checkpoints")
+    ep_mode = bool(config.expert_parallel) and distributed and model_cfg.is_moe
+    if ep_mode:
+        from .backends.fsdp import FSDPConfig
+
+        kw["config"] = FSDPConfig(expert_parallel=True)
     backend = FSDPTrainingBackend(model_cfg, weights, **kw) if distributed else PyTorchTrainingBackend(model_cfg, weights, **kw)
     ecfg = EngineConfig(cache_type=config.cache_type, max_batch_size=config.max_batch_size,
                         max_model_len=max(config.max_seq_len + config.max_tokens, 64), num_kv_blocks=config.kv_blocks,
                         seed=config.seed * 1009 + rank, ignore_eos=tokenizer is None)
-    engine = InferenceEngine(ecfg, model_cfg, backend.model.state_dict(), tokenizer=tokenizer, device=dev)
+    ep = None
+    if ep_mode:
+        from ..parallel.ep import ExpertParallel
+
+        ep = ExpertParallel(backend.comm)
+    engine = InferenceEngine(ecfg, model_cfg, backend.model.state_dict(), tokenizer=tokenizer, device=dev, ep=ep)
     del weights
 
     my_prompts = prompts[rank::world] if distributed else prompts

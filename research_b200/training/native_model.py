@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import math
 import os
+import re
 
 import torch
 import torch.nn.functional as F
@@ -172,6 +173,28 @@ class _SwiGLU(torch.autograd.Function):
         return ops.swiglu_backward(gu, dy.contiguous())   # (the kernel indexes dy densely)
 
 
+class _AllToAllRows(torch.autograd.Function):
+    """Rows ``[sum(send), d]`` ordered by destination rank -> rows ``[sum(recv), d]`` ordered by source rank; the
+    gradient takes the way back."""
+
+    @staticmethod
+    def forward(ctx, x, send, recv, group):
+        import torch.distributed as dist
+
+        ctx.send, ctx.recv, ctx.group = send, recv, group
+        out = torch.empty(sum(recv), x.shape[1], dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=recv, input_split_sizes=send, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+
+        out = torch.empty(sum(ctx.send), g.shape[1], dtype=g.dtype, device=g.device)
+        dist.all_to_all_single(out, g.contiguous(), output_split_sizes=ctx.send, input_split_sizes=ctx.recv, group=ctx.group)
+        return out, None, None, None
+
+
 class _Embedding(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ids, table, gtable, sink):
@@ -241,6 +264,7 @@ class NativeCausalLM:
         self._params: dict[str, torch.Tensor] = {}
         self._stacked: dict[str, tuple] = {}
         self._experts: dict[str, tuple | None] = {}
+        self.ep = getattr(buckets, "expert_parallel", None)      # (rank, ranks, experts per rank) in expert-parallel training
         self._sharded: dict[str, object] = {}
         self._cu_cache: dict[tuple[int, int], torch.Tensor] = {}
         self.trace: dict | None = None
@@ -296,11 +320,32 @@ class NativeCausalLM:
         return self._stacked[key]
 
     def state_dict(self) -> dict[str, torch.Tensor]:
-        return {n: self.b.full_param(n) for n in self.b.specs}
+        """Every parameter by name. Expert-parallel training: the other ranks' experts are fetched too (a collective on
+        CPU groups: every rank must call it; peer reads on the GPU), so the result is the whole model on every rank."""
+        sd = {n: self.b.full_param(n) for n in self.b.specs}
+        if self.ep is not None:
+            if not self.on_gpu:
+                sd.update({n: v.detach().to(self.b.dtype) for n, v in self._gather_remote_experts().items()})
+            else:
+                rank, W, _ = self.ep
+                b = self.b
+                b.finish_pending()
+                for c, owned in enumerate(b.chunk_owned):
+                    if not owned:
+                        continue
+                    for q in range(W):
+                        if q == rank:
+                            continue
+                        peer = b.params_buf.peer_tensor(q)
+                        for sp in b._chunk_specs[c]:
+                            sd[self._expert_name_on(sp.name, q)] = peer[sp.p_offset:sp.p_offset + sp.numel].view(sp.shape).clone()
+        return sd
 
     # ---------------------------------------------------------------- CPU / oracle path
     def _logprobs_cpu(self, input_ids, targets, need_entropy):
         leaves = {n: self.b.full_param(n).detach().float().requires_grad_(True) for n in self.b.specs}
+        if self.ep is not None:
+            leaves.update(self._gather_remote_experts())
         logits = causal_lm_forward(input_ids.long(), leaves, self.cfg).float()
         lp_all = F.log_softmax(logits, -1)
         safe = targets.long().clamp(min=0)
@@ -310,11 +355,58 @@ class NativeCausalLM:
         self._leaves = leaves
         return lp, ent
 
+    # Expert-parallel training without a GPU: the oracle needs every expert, so the owners' expert storage is gathered
+    # for the forward pass and every rank's gradient of an expert travels back to its owner afterwards. The layout of
+    # an expert chunk is the same on every rank (rank q's experts are this rank's shifted by (q - rank) * EL).
+    def _expert_name_on(self, name: str, q: int) -> str:
+        rank, _, EL = self.ep
+        head, e, tail = re.match(r"(.*\.experts\.)(\d+)(\..*)$", name).groups()
+        return f"{head}{int(e) + (q - rank) * EL}{tail}"
+
+    def _gather_remote_experts(self) -> dict[str, torch.Tensor]:
+        import torch.distributed as dist
+
+        rank, W, _ = self.ep
+        b, out = self.b, {}
+        for c, owned in enumerate(b.chunk_owned):
+            if not owned:
+                continue
+            p_off, p_len = b.p_chunks[c]
+            parts = [torch.empty(p_len, dtype=b.dtype) for _ in range(W)]
+            dist.all_gather(parts, b.params[p_off:p_off + p_len].contiguous(), group=b.comm.group)
+            for q in range(W):
+                if q == rank:
+                    continue
+                for sp in b._chunk_specs[c]:
+                    rel = sp.p_offset - p_off
+                    out[self._expert_name_on(sp.name, q)] = parts[q][rel:rel + sp.numel].view(sp.shape).float().requires_grad_(True)
+        return out
+
     def collect_cpu_grads(self) -> None:
-        """Move autograd ``.grad`` of the CPU leaves into the flat gradient bucket."""
-        for n, leaf in getattr(self, "_leaves", {}).items():
-            if leaf.grad is not None:
+        """Move autograd ``.grad`` of the CPU leaves into the flat gradient bucket (expert-parallel: an expert's
+        gradients of every rank are summed on its owner)."""
+        leaves = getattr(self, "_leaves", {})
+        for n, leaf in leaves.items():
+            if leaf.grad is not None and n in self.b.specs and not self.b.specs[n].owned:
                 self.b.grad_view(n).add_(leaf.grad.to(self.b.grads.dtype))
+        if self.ep is not None and leaves:
+            import torch.distributed as dist
+
+            rank, W, _ = self.ep
+            b = self.b
+            for c, owned in enumerate(b.chunk_owned):
+                if not owned:
+                    continue
+                off, length = b.chunks[c]
+                buf = torch.zeros(W, length, dtype=torch.float32)
+                for q in range(W):
+                    for sp in b._chunk_specs[c]:
+                        leaf = leaves.get(self._expert_name_on(sp.name, q))
+                        if leaf is not None and leaf.grad is not None:
+                            rel = sp.offset - off
+                            buf[q, rel:rel + sp.numel] = leaf.grad.reshape(-1)
+                dist.all_reduce(buf, group=b.comm.group)
+                b.grads[off:off + length].add_(buf[rank].to(b.grads.dtype))
         self._leaves = {}
 
     # ---------------------------------------------------------------- kernel path
@@ -412,7 +504,10 @@ class NativeCausalLM:
             if cfg.norm_topk_prob:
                 wt = wt / wt.sum(-1, keepdim=True)
         experts = self.stacked_experts(m)
-        if experts is not None:
+        if self.ep is not None:
+            assert experts is not None, "expert-parallel training needs the grouped expert kernels (<= 256 experts per rank, d % 64 == 0)"
+            out = self._moe_ep(h, idx, wt.float(), experts)
+        elif experts is not None:
             from ..ops.moe_train import GroupedExperts, GroupedPlan
 
             wgu, ggu, wd, gd = experts
@@ -425,6 +520,42 @@ class NativeCausalLM:
             gu = torch.cat([lin(h, p + "gate_proj.weight"), lin(h, p + "up_proj.weight")], dim=-1)
             out = out + lin(_SwiGLU.apply(gu), p + "down_proj.weight")
         return out
+
+    def _moe_ep(self, h, idx, wt, experts):
+        """Routed experts with the experts split over the ranks: every (token, slot) row travels to the owner of its
+        expert, the owner runs its experts as grouped GEMMs over everything it received, the results travel back and
+        are combined with the routing weights here. Backward takes the same two trips in reverse (the autograd
+        functions below), so an expert's weight gradient is complete on its owner and nowhere else. The trips are
+        `all_to_all_single` calls of the process group; one host read per layer fetches the split sizes."""
+        import torch.distributed as dist
+
+        from ..ops.moe_train import GroupedExperts, GroupedPlan
+
+        rank, W, EL = self.ep
+        group = self.b.comm.group
+        wgu, ggu, wd, gd = experts
+        T, k = idx.shape
+        d = h.shape[1]
+        flat = idx.reshape(-1)
+        order = flat.argsort(stable=True)                                    # rows by expert, hence by owner
+        counts = torch.bincount(flat, minlength=W * EL).view(W, EL)         # [owner, local expert] rows I send
+        recv_counts = torch.empty_like(counts)                               # [source, local expert] rows I get
+        dist.all_to_all_single(recv_counts, counts, group=group)
+        sizes = torch.stack([counts.sum(1), recv_counts.sum(1)]).tolist()   # the one host read
+        send, recv = [int(x) for x in sizes[0]], [int(x) for x in sizes[1]]
+        xs = h.index_select(0, order // k)                                   # [T k, d] in travel order
+        xr = _AllToAllRows.apply(xs, send, recv, group)                      # [rows received, d], by source then local expert
+        R = xr.shape[0]
+        if R > 0:
+            eid = torch.arange(EL, device=h.device).repeat(W).repeat_interleave(recv_counts.reshape(-1), output_size=R)
+            plan = GroupedPlan(eid.to(torch.int32).view(R, 1).contiguous(), EL, d, self.cfg.moe_intermediate_size)
+            ones = torch.ones(R, 1, dtype=torch.float32, device=h.device)
+            yr = GroupedExperts.apply(xr.contiguous(), ones, wgu, ggu, wd, gd, plan, self.b)
+        else:
+            yr = xr                                                           # nothing arrived: this rank's experts idle this pass
+        yb = _AllToAllRows.apply(yr, recv, send, group)                      # back home, still in travel order
+        w_rows = wt.reshape(-1).index_select(0, order).to(h.dtype)
+        return torch.zeros_like(h).index_add(0, order // k, yb * w_rows[:, None])
 
     def _moe_loop(self, h, m: str, lin, idx, wt):
         """Per-expert loop (one host sync for the counts): layers whose experts do not lie back to back in the bucket,
@@ -455,14 +586,15 @@ class NativeCausalLM:
         None."""
         cfg = self.cfg
         E = cfg.num_experts
-        first = f"{m}experts.0.gate_proj.weight"
+        first = f"{m}experts.{0 if self.ep is None else self.ep[0] * self.ep[2]}.gate_proj.weight"
         if self.b._pending and first in self.b.specs:
             self.b.ensure_chunk(self.b.specs[first].chunk)
         if m not in self._experts:
             self._experts[m] = None
             if os.environ.get("RB_MOE_GROUPED", "1") != "0" and E <= 256 and cfg.hidden_size % 64 == 0 and cfg.moe_intermediate_size % 32 == 0:
-                wgu, ggu = self.stacked(tuple(f"{m}experts.{e}.{p}.weight" for e in range(E) for p in ("gate_proj", "up_proj")))
-                wd, gd = self.stacked(tuple(f"{m}experts.{e}.down_proj.weight" for e in range(E)))
+                mine = range(E) if self.ep is None else range(self.ep[0] * self.ep[2], (self.ep[0] + 1) * self.ep[2])
+                wgu, ggu = self.stacked(tuple(f"{m}experts.{e}.{p}.weight" for e in mine for p in ("gate_proj", "up_proj")))
+                wd, gd = self.stacked(tuple(f"{m}experts.{e}.down_proj.weight" for e in mine))
                 if wgu is not None and wd is not None:
                     self._experts[m] = (wgu, ggu, wd, gd)
         return self._experts[m]
@@ -490,6 +622,10 @@ class NativeCausalLM:
 
         for i in range(cfg.num_layers):
             watch(x, self.b.specs[f"model.layers.{i}.self_attn.o_proj.weight"].chunk)
+            if self.ep is not None:      # the layer's own experts are a chunk of their own
+                own = self.b.specs.get(f"model.layers.{i}.mlp.experts.{self.ep[0] * self.ep[2]}.gate_proj.weight")
+                if own is not None:
+                    watch(x, own.chunk)
             if self.ckpt:
                 x = torch.utils.checkpoint.checkpoint(self._layer, x, i, positions, B, Tn, use_reentrant=False)
             else:

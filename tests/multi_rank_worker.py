@@ -287,6 +287,84 @@ def case_fsdp_full_shard(comm, dev, dt):
         close(pb[n], pa[n], tol, tol, f"full_shard vs replicated {n}")
 
 
+def case_ep_training(comm, dev, dt):
+    """Expert-parallel training against data-parallel training with replicated experts: same data, same steps, same
+    losses and weights afterwards; every rank keeps only its own experts (parameters, gradients, optimizer state)."""
+    from research_b200.models import get_preset, init_random_weights
+    from research_b200.training.backends import FSDPTrainingBackend
+    from research_b200.training.backends.fsdp import FSDPConfig
+
+    W = comm.world
+    E = 4 * W
+    cfg = get_preset("tiny-moe", num_layers=2, num_experts=E, num_experts_per_tok=2, init_std=0.05)
+    w = init_random_weights(cfg, seed=5)
+    g = torch.Generator().manual_seed(2)
+    T = 128 if dev.type == "cuda" else 24
+    all_ids = torch.randint(0, cfg.vocab_size, (2 * W, T), generator=g)
+    mine = all_ids[comm.rank * 2:(comm.rank + 1) * 2]
+    results = {}
+    for ep in (False, True):
+        be = FSDPTrainingBackend(cfg, w, device=dev, loss_fn="ce", lr=2e-3, comm=comm, config=FSDPConfig(expert_parallel=ep))
+        assert be.buckets.any_owned == ep
+        if ep:
+            mine_e = sorted({int(n.split(".experts.")[1].split(".")[0]) for n in be.buckets.specs if ".experts." in n})
+            assert mine_e == list(range(comm.rank * 4, comm.rank * 4 + 4)), mine_e
+            assert be.buckets.numel < results[False][2]
+        losses = []
+        for _ in range(3):
+            losses.append(be.forward_backward({"input_ids": mine, "labels": mine}).wait()["loss"])
+            be.optim_step().wait()
+        sd = be.get_weights().wait()
+        assert len(sd) == len(w), (len(sd), len(w))
+        if ep:      # a checkpoint holds the whole model (every rank's experts) and loads back into the expert-parallel layout
+            import tempfile
+
+            from research_b200.models.weights import load_safetensors_dir
+
+            with tempfile.TemporaryDirectory() as d:
+                path = [d]
+                dist.broadcast_object_list(path, src=0)
+                be.save_checkpoint_to_path(path[0], 3)
+                if comm.rank == 0:
+                    saved, _ = load_safetensors_dir(path[0])
+                    assert {n for n in w if ".experts." in n} <= set(saved), "a checkpoint must hold every rank's experts"
+                    close(saved[f"model.layers.1.mlp.experts.{E - 1}.down_proj.weight"], sd[f"model.layers.1.mlp.experts.{E - 1}.down_proj.weight"],
+                          1e-6, 0, "checkpointed expert of the last rank")
+                be.load_checkpoint(path[0])
+                comm.barrier_host()
+        results[ep] = (losses, {n: sd[n].float().cpu() for n in
+                                (f"model.layers.1.mlp.experts.{E - 1}.down_proj.weight", "model.layers.1.mlp.experts.0.gate_proj.weight",
+                                 f"model.layers.0.mlp.experts.{W * 4 // 2}.up_proj.weight", "model.layers.1.mlp.gate.weight",
+                                 "model.layers.0.self_attn.q_proj.weight", "model.embed_tokens.weight")}, be.buckets.numel)
+        comm.barrier_host()
+    (la, pa, _), (lb, pb, _) = results[False], results[True]
+    tol = 2e-2 if dev.type == "cuda" else 2e-4
+    for x, y in zip(la, lb):
+        assert abs(x - y) < tol * max(1.0, abs(x)), (la, lb)
+    assert lb[-1] < lb[0], lb
+    for n in pa:
+        close(pb[n], pa[n], 2e-2 if dev.type == "cuda" else 2e-4, 1e-3, f"expert parallel vs replicated experts: {n}")
+
+
+def case_grpo_expert_parallel(comm, dev, dt):
+    """The whole GRPO loop on a mixture-of-experts model with the experts split over the ranks for rollouts (lock-step
+    engines) AND for the update; the weight sync moves each rank's own experts into its engine."""
+    import tempfile
+
+    from research_b200.training.grpo import GRPOConfig, grpo_train
+
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 4096, (int(n),), generator=g).tolist() for n in torch.randint(16, 40, (16,), generator=g)]
+    with tempfile.TemporaryDirectory() as d:
+        os.environ["ROLLOUTS_RUN_NAME"] = "ep_run"
+        gcfg = GRPOConfig(model_name="tiny-moe", lr=1e-4, batch_size=2 * comm.world, n_samples_per_prompt=4, num_minibatches=2, max_tokens=6,
+                          max_seq_len=96, temperature=1.0, num_steps=2, output_dir=d, checkpoint_every=0, max_batch_size=16,
+                          kv_blocks=128, expert_parallel=True)
+        hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=dev)
+        assert len(hist) == 2 and hist[-1]["weight_version"] == 2.0, hist[-1]
+        dist.barrier()
+
+
 def case_grpo_disjoint(comm, dev, dt):
     """Trainers and engine on different ranks: the last rank only serves, the others only train; samples travel to the
     trainers, the new parameters travel back into the engine's packed layout."""
@@ -408,7 +486,7 @@ def case_ep_agree(comm, dev, dt):
 
 CASES = {"ep_agree": case_ep_agree, "barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
          "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo,
-         "fsdp_full_shard": case_fsdp_full_shard, "grpo_disjoint": case_grpo_disjoint, "grpo_disjoint_tp_engine": case_grpo_disjoint_tp_engine,
+         "fsdp_full_shard": case_fsdp_full_shard, "ep_training": case_ep_training, "grpo_expert_parallel": case_grpo_expert_parallel, "grpo_disjoint": case_grpo_disjoint, "grpo_disjoint_tp_engine": case_grpo_disjoint_tp_engine,
          "moe_ep": case_moe_expert_parallel}
 
 
