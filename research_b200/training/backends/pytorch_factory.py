@@ -30,11 +30,17 @@ def parse_dtype(name: str | torch.dtype) -> torch.dtype:
     return table[key]
 
 
-def load_model_weights(model_name: str, seed: int = 0) -> tuple[dict[str, torch.Tensor], ModelConfig]:
-    """A checkpoint directory (HF safetensors) or the name of a built-in preset (random init)."""
+def load_model_weights(model_name: str, seed: int = 0, device=None) -> tuple[dict[str, torch.Tensor], ModelConfig]:
+    """A checkpoint directory (HF safetensors) or the name of a built-in preset (random init). Presets above 12 B
+    parameters come back as a lazy mapping that builds one tensor at a time (on ``device`` when given), so that no
+    process ever holds a second full copy of such a model."""
     if Path(model_name).is_dir():
         return load_safetensors_dir(model_name)
     cfg = get_preset(model_name)
+    if cfg.num_params() > 12e9:
+        from ...models.weights import LazyRandomWeights
+
+        return LazyRandomWeights(cfg, seed=seed, device=device or "cpu"), cfg
     return init_random_weights(cfg, seed=seed), cfg
 
 

@@ -160,7 +160,7 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
         config.save(out_dir / "config.json")
     logger = metrics_logger or (JSONLLogger(out_dir) if rank == 0 else None)
 
-    weights, model_cfg = load_model_weights(config.checkpoint_path or config.model_name, config.seed)
+    weights, model_cfg = load_model_weights(config.checkpoint_path or config.model_name, config.seed, device=dev)
     tcfg = TrainerConfig(num_minibatches=config.num_minibatches, max_grad_norm=config.max_grad_norm)
     kw = dict(device=dev, loss_fn=config.loss, lr=config.lr, weight_decay=config.weight_decay, trainer_config=tcfg,
               checkpoint_dir=out_dir / "checkpoints")
@@ -178,7 +178,13 @@ async def _grpo_train_async(config, prompts, score_fn, environment_cls, metrics_
         from ..parallel.ep import ExpertParallel
 
         ep = ExpertParallel(backend.comm)
-    engine = InferenceEngine(ecfg, model_cfg, backend.model.state_dict(), tokenizer=tokenizer, device=dev, ep=ep)
+    if ep_mode and dev.type == "cuda":
+        from .native_model import LazyStateDict
+
+        engine_weights = LazyStateDict(backend.model)      # the engine copies its own experts only, tensor by tensor
+    else:
+        engine_weights = backend.model.state_dict()
+    engine = InferenceEngine(ecfg, model_cfg, engine_weights, tokenizer=tokenizer, device=dev, ep=ep)
     del weights
 
     my_prompts = prompts[rank::world] if distributed else prompts

@@ -24,6 +24,7 @@ from __future__ import annotations
 import math
 import os
 import re
+from collections.abc import Mapping
 
 import torch
 import torch.nn.functional as F
@@ -171,6 +172,36 @@ class _SwiGLU(torch.autograd.Function):
     def backward(ctx, dy):
         (gu,) = ctx.saved_tensors
         return ops.swiglu_backward(gu, dy.contiguous())   # (the kernel indexes dy densely)
+
+
+class LazyStateDict(Mapping):
+    """The model's parameters by name, resolved when asked for: a view of this rank's storage, a gathered row-sharded
+    matrix, or (expert-parallel training on GPUs) a view of the owner's storage in peer memory. An engine that loads
+    from it copies tensor by tensor, so no second copy of the model exists at any time."""
+
+    def __init__(self, model: "NativeCausalLM"):
+        from ..models.weights import param_shapes
+
+        self.model = model
+        self.names = list(param_shapes(model.cfg))
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        m, b = self.model, self.model.b
+        if name in b.specs:
+            return b.full_param(name)
+        assert m.ep is not None and m.on_gpu, f"{name} is not stored on this rank"
+        rank, _, EL = m.ep
+        head, e, tail = re.match(r"(.*\.experts\.)(\d+)(\..*)$", name).groups()
+        q = int(e) // EL
+        sp = b.specs[f"{head}{int(e) - q * EL + rank * EL}{tail}"]       # my expert at the same place of the layout
+        b.finish_pending()
+        return b.params_buf.peer_tensor(q)[sp.p_offset:sp.p_offset + sp.numel].view(sp.shape)
+
+    def __iter__(self):
+        return iter(self.names)
+
+    def __len__(self) -> int:
+        return len(self.names)
 
 
 class _AllToAllRows(torch.autograd.Function):

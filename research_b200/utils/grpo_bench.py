@@ -31,6 +31,7 @@ def main() -> None:
     ap.add_argument("--minibatches", type=int, default=8)
     ap.add_argument("--loss", default="grpo_clipped")
     ap.add_argument("--device", default=None)
+    ap.add_argument("--expert-parallel", action="store_true", help="MoE models on several ranks: experts split over the ranks for rollouts and update")
     ap.add_argument("--engine-tp", action="store_true", help="with --trainers: the serving ranks form ONE tensor-parallel engine")
     ap.add_argument("--trainers", type=int, default=0,
                     help="several ranks: the first N ranks only train, the others only serve (disjoint device sets); 0 = every rank does both")
@@ -60,6 +61,10 @@ def main() -> None:
                       num_minibatches=args.minibatches, max_tokens=args.max_tokens, max_seq_len=args.prompt_len + args.max_tokens,
                       temperature=1.0, num_steps=args.steps + 1, output_dir=out, checkpoint_every=0, loss=args.loss,
                       max_batch_size=min(256, args.prompts * args.samples // max(world - args.trainers, 1)))
+    if args.expert_parallel:
+        import dataclasses
+
+        gcfg = dataclasses.replace(gcfg, expert_parallel=True)
     disjoint = world > 1 and 0 < args.trainers < world
     if disjoint:
         import dataclasses
@@ -83,7 +88,7 @@ def main() -> None:
     trained_tokens = samples * (args.prompt_len * 0.75 + args.max_tokens)     # prompts are U[len/2, len]
     row = {"bench": "grpo_step", "model": args.model, "world": world,
            "placement": (f"{args.trainers} trainer ranks + " + (f"one tensor-parallel engine over {world - args.trainers} ranks" if args.engine_tp
-                                                                 else f"{world - args.trainers} engine ranks")) if disjoint else "every rank trains and serves",
+                                                                 else f"{world - args.trainers} engine ranks")) if disjoint else ("every rank trains and serves" + (", experts split over the ranks" if args.expert_parallel else "")),
            "samples_per_step": samples,
            "max_tokens": args.max_tokens, "prompt_len": f"U[{args.prompt_len // 2},{args.prompt_len}]", "loss": args.loss,
            "step_s": round(mean("step_s"), 4),

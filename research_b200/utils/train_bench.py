@@ -47,6 +47,8 @@ def main() -> None:
     ap.add_argument("--kernel-table", default="", help="write a table of device time per kernel (one extra step under the "
                                                        "PyTorch profiler, after the timed steps) to this file")
     ap.add_argument("--peak-tflops", type=float, default=1426.3, help="sustained cuBLAS bf16 TFLOP/s per GPU for the MFU line")
+    ap.add_argument("--expert-parallel", action="store_true", help="several ranks, MoE models: every rank keeps (and updates) its own "
+                                                                   "experts only; tokens travel to the experts' owners and back")
     ap.add_argument("--layers", type=int, default=0, help="keep only the first N layers of the preset (a model that does not "
                                                           "fit otherwise; the output says so)")
     args = ap.parse_args()
@@ -67,7 +69,13 @@ def main() -> None:
     cfg = get_preset(args.model, num_layers=args.layers) if args.layers else get_preset(args.model)
     kw = dict(loss_fn=args.loss, lr=1e-5, trainer_config=TrainerConfig(micro_batch_size=args.micro_batch), activation_checkpointing=not args.no_checkpointing,
               need_entropy=False)
-    backend = FSDPTrainingBackend(cfg, None, **kw) if world > 1 else NativeTrainingBackend(cfg, None, device=dev, **kw)
+    if world > 1:
+        from ..training.backends.fsdp import FSDPConfig
+
+        backend = FSDPTrainingBackend(cfg, None, config=FSDPConfig(expert_parallel=args.expert_parallel,
+                                                                   gradient_checkpointing=not args.no_checkpointing), **kw)
+    else:
+        backend = NativeTrainingBackend(cfg, None, device=dev, **kw)
     g = torch.Generator().manual_seed(1234 + local)
 
     def batch():
@@ -102,7 +110,8 @@ def main() -> None:
                           "batch_per_gpu": args.batch, "ms_per_step": round(ms.item(), 2), "value": round(tok_s, 1),
                           "mfu_of_sustained_cublas": round(mfu, 3), "loss": round(float(m.get("loss", 0.0)), 4),
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1),
-                          "activation_checkpointing": not args.no_checkpointing, "dtype": "bf16", "data": "synthetic"}))
+                          "activation_checkpointing": not args.no_checkpointing, "expert_parallel": bool(args.expert_parallel and world > 1),
+                          "dtype": "bf16", "data": "synthetic"}))
     if args.kernel_table and local == 0:
         from torch.profiler import ProfilerActivity, profile
 
