@@ -79,7 +79,7 @@ class InferenceEngine:
         self.max_tokens_per_batch = config.max_tokens_per_batch or min(config.max_batch_size * 512, 16384)
         on_gpu = self.device.type == "cuda"
         dtype = torch.bfloat16 if on_gpu else torch.float32
-        num_blocks = config.num_kv_blocks or self._size_kv_cache(model_config, tp)
+        num_blocks = config.num_kv_blocks or self._size_kv_cache(model_config, tp, ep)
         self.runner = ModelRunner(
             model_config, weights, device=self.device, num_kv_blocks=num_blocks, max_batch=config.max_batch_size,
             max_model_len=config.max_model_len, max_prefill_tokens=self.max_tokens_per_batch + 2 * BLOCK,
@@ -110,14 +110,18 @@ class InferenceEngine:
         self.last_step_rows = (0, 0)
 
     # ---------------------------------------------------------------- sizing
-    def _size_kv_cache(self, cfg: ModelConfig, tp) -> int:
+    def _size_kv_cache(self, cfg: ModelConfig, tp, ep=None) -> int:
         tp_size = tp.world if tp is not None else 1
         per_block = cfg.num_layers * 2 * (cfg.num_kv_heads // tp_size) * BLOCK * cfg.head_dim * 2
         want_tokens = self.config.max_batch_size * self.config.max_model_len
         want = -(-want_tokens // BLOCK)
         if self.device.type == "cuda":
             free, _total = torch.cuda.mem_get_info(self.device)
-            weights_bytes = cfg.num_params() * 2 // tp_size
+            params = cfg.num_params()
+            if ep is not None and ep.world > 1 and cfg.is_moe:     # an expert-parallel engine holds its own share of the experts only
+                experts = (cfg.num_layers - cfg.first_k_dense_replace) * cfg.num_experts * 3 * cfg.hidden_size * cfg.moe_intermediate_size
+                params -= experts - experts // ep.world
+            weights_bytes = params * 2 // tp_size
             budget = int(free * self.config.gpu_memory_utilization) - weights_bytes - (4 << 30)
             cap = max(budget // per_block, 64)
             return int(max(64, min(want, cap, (48 << 30) // per_block)))

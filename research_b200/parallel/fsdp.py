@@ -272,7 +272,10 @@ class ShardedAdamW:
             self.master.append(buckets.params[off:off + n].float().clone())
             self.exp_avg.append(torch.zeros(n, dtype=torch.float32, device=dev))
             self.exp_avg_sq.append(torch.zeros(n, dtype=torch.float32, device=dev))
-            self.red.append(None if self.direct_grads else torch.zeros(n, dtype=torch.float32, device=dev))
+            # owned chunks on a GPU keep no fp32 copy of their gradients either: nothing is summed over ranks, AdamW reads
+            # the bf16 bucket and the 1 / world of the mean rides in its coefficient (4 bytes per expert parameter saved)
+            direct = self.direct_grads or (self.on_gpu and buckets.chunk_owned[c])
+            self.red.append(None if direct else torch.zeros(n, dtype=torch.float32, device=dev))
         self.zero_grads_after_step = True
         self.overlap_grid = 0          # CTAs of a reduce launch that shares the GPU with backward (0 = full grid)
         # With a stream here, AdamW and the parameter all-gather of a step run on it chunk by chunk, in the order the
@@ -284,6 +287,7 @@ class ShardedAdamW:
             self.n_partial = _lib().rb_rs_num_partials()
             self.partial = torch.zeros(self.n_partial, dtype=torch.float32, device=dev)
             self.coef = torch.ones(1, dtype=torch.float32, device=dev)
+            self.coef_owned = torch.ones(1, dtype=torch.float32, device=dev)     # coef / world, for chunks this rank owns
             self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
             self.grad_slots = [self.comm.new_slot() for _ in buckets.chunks]    # one ready flag row per chunk
             self.param_slots = [self.comm.new_slot() for _ in buckets.chunks]
@@ -319,10 +323,12 @@ class ShardedAdamW:
         off, length = b.chunks[chunk]
         n = length // comm.world
         scale = grad_scale / comm.world
-        b.zero_unwritten(chunk)
-        self._passes[chunk] = self._passes.get(chunk, 0) + 1
         sharded = b.chunk_sharded[chunk]
         owned = b.chunk_owned[chunk]
+        if owned and self.on_gpu and overlapped:
+            return      # nothing to fetch or copy for an owned chunk: its one pass (the norm) runs in step(), over the final sums
+        b.zero_unwritten(chunk)
+        self._passes[chunk] = self._passes.get(chunk, 0) + 1
         if not self.on_gpu:
             g = b.grads[off:off + length].float()
             if comm.world > 1 and not owned:
@@ -353,9 +359,8 @@ class ShardedAdamW:
             # nothing to fetch from the peers: cast, scale and the chunk's share of the gradient norm, all local
             from .symm import ptr_array
 
-            rc = _lib().rb_rs_reduce_ex(ptr_array([b.grads.data_ptr() + off * 2]), None, 0, 0, 0, 1, length, scale,
-                                        self.red[chunk].data_ptr(), int(accumulate), self.partial.data_ptr(), st,
-                                        self.overlap_grid if overlapped else 0, stream_handle(dev))
+            rc = _lib().rb_rs_reduce_ex(ptr_array([b.grads.data_ptr() + off * 2]), None, 0, 0, 0, 1, length, 1.0 / comm.world,
+                                        None, 0, self.partial.data_ptr(), st, 0, stream_handle(dev))
             check_rc(rc, "rb_rs_reduce_ex")
             self._reduced.add(chunk)
             return
@@ -432,12 +437,19 @@ class ShardedAdamW:
             # several reduce passes were summed into the fp32 slices: the partial sums of squares of the kernels
             # cover intermediate values, so take the norm from the slices themselves (rare path, plain tensor ops)
             self.partial.zero_()
-            self.partial[0] = torch.stack([(r * r).sum() for r in self.red]).sum()
+            terms = [(r * r).sum() for r in self.red if r is not None]
+            for c, owned in enumerate(b.chunk_owned):
+                if owned:
+                    off, length = b.chunks[c]
+                    terms.append((b.grads[off:off + length].float() / comm.world).pow(2).sum())
+            self.partial[0] = torch.stack(terms).sum()
         ep = comm.next_epoch(self.norm_slot)
         rc = _lib().rb_clip_coef_ex(self.partial.data_ptr(), self.n_partial, comm.norm_slots.ptrs(), comm.flags.ptrs(),
                                     self.norm_slot, ep, comm.rank, comm.world, float(self.max_grad_norm), float(grad_scale),
                                     self.coef.data_ptr(), self.norm.data_ptr(), st, stream_handle(dev))
         check_rc(rc, "rb_clip_coef_ex")
+        if b.any_owned:
+            torch.div(self.coef, float(comm.world), out=self.coef_owned)
         deferred = self.update_stream is not None
         order = self.update_order if self.update_order is not None else list(range(len(b.chunks)))
         # the clip kernel has consumed the partial sums: clear them on THIS stream, before anything of the next step
@@ -476,10 +488,14 @@ class ShardedAdamW:
             # GEMM launches fetch the slabs when they need the matrix)
             from .symm import ptr_array
 
+            if b.chunk_owned[c]:      # the bf16 gradient bucket itself, scaled by coef / world inside the kernel
+                grad_ptr, is_bf16, coef = b.grads.data_ptr() + b.chunks[c][0] * 2, 1, self.coef_owned
+            else:
+                grad_ptr, is_bf16, coef = self.red[c].data_ptr(), 0, self.coef
             rc = _lib().rb_adamw_allgather_ex(
                 self.master[c].data_ptr(), self.exp_avg[c].data_ptr(), self.exp_avg_sq[c].data_ptr(),
-                self.red[c].data_ptr(), 0, ptr_array([b.params.data_ptr() + p_off * 2]), 0, 1, p_len, self.lr, b1, b2,
-                self.eps, self.weight_decay, self.step_count, self.coef.data_ptr(), stream_handle(dev))
+                grad_ptr, is_bf16, ptr_array([b.params.data_ptr() + p_off * 2]), 0, 1, p_len, self.lr, b1, b2,
+                self.eps, self.weight_decay, self.step_count, coef.data_ptr(), stream_handle(dev))
             check_rc(rc, "rb_adamw_allgather_ex")
             return
         off = b.chunks[c][0]
