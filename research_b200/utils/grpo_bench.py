@@ -76,7 +76,7 @@ def main() -> None:
     hist = grpo_train(gcfg, prompts, lambda s: float(sum(s.tokens[-s.response_length:]) % 2), device=args.device)
     steps = hist[1:]                      # the first step pays one-time set-up (graph capture, allocator growth)
     n = len(steps)
-    phase = {k: sum(h.get(k, 0.0) for h in steps) / n for k in ("step_s", "rollout_s", "train_s", "sync_s", "num_samples")}
+    phase = {k: sum(h.get(k, 0.0) for h in steps) / n for k in ("step_s", "rollout_s", "train_s", "sync_s", "num_samples", "sync_dev_ms")}
     if disjoint:
         # every rank reports its own phases (an engine does not train, a trainer does not generate): the slowest rank counts
         t = torch.tensor([phase[k] for k in sorted(phase)], dtype=torch.float64, device="cuda" if torch.cuda.is_available() else "cpu")
@@ -93,6 +93,7 @@ def main() -> None:
            "max_tokens": args.max_tokens, "prompt_len": f"U[{args.prompt_len // 2},{args.prompt_len}]", "loss": args.loss,
            "step_s": round(mean("step_s"), 4),
            "rollout_s": round(mean("rollout_s"), 4), "train_s": round(mean("train_s"), 4), "sync_s": round(mean("sync_s"), 5),
+           "sync_device_ms": round(mean("sync_dev_ms"), 3),     # same-GPU placement: the copy kernel's device time (sync_s is its launch)
            "rollout_tokens_per_s": round(gen_tokens / max(mean("rollout_s"), 1e-9), 1),
            "train_tokens_per_s": round(trained_tokens / max(mean("train_s"), 1e-9), 1),
            "samples_per_s": round(samples / max(mean("step_s"), 1e-9), 2),
