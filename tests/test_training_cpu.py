@@ -421,3 +421,25 @@ def test_grouped_experts_layout_and_reference():
     got = grouped_experts_reference(h, idx, wt, wgu, wd)
     want = moe_mlp(h[None], w, m, cfg)[0]
     assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+
+
+def test_lazy_weights_and_lazy_state_dict():
+    """Presets above 12 B parameters come back as a lazy mapping (one tensor at a time); a model's lazy state dict
+    resolves names against its buckets when asked."""
+    from research_b200.models.weights import LazyRandomWeights, param_shapes
+    from research_b200.training.backends import load_model_weights
+    from research_b200.training.backends.native import NativeTrainingBackend
+    from research_b200.training.native_model import LazyStateDict
+
+    w, cfg = load_model_weights("qwen3-30b-a3b")
+    assert isinstance(w, LazyRandomWeights) and len(w) == len(param_shapes(cfg))
+    t = w["model.layers.3.mlp.experts.17.down_proj.weight"]
+    assert t.shape == (cfg.hidden_size, cfg.moe_intermediate_size) and torch.equal(t, w["model.layers.3.mlp.experts.17.down_proj.weight"])
+    small, _ = load_model_weights("tiny-moe")
+    assert isinstance(small, dict)
+    tiny = get_preset("tiny-moe", num_layers=2)
+    be = NativeTrainingBackend(tiny, init_random_weights(tiny, seed=0), device="cpu", loss_fn="ce")
+    lazy = LazyStateDict(be.model)
+    assert set(lazy) == set(param_shapes(tiny)) and len(lazy) == len(param_shapes(tiny))
+    n = "model.layers.1.mlp.experts.3.up_proj.weight"
+    assert torch.equal(lazy[n], be.buckets.full_param(n))
