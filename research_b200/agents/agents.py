@@ -140,7 +140,8 @@ async def run_agent(state: AgentState, run_config: RunConfig | None = None) -> l
     run_config = run_config or RunConfig()
     if run_config.session_store is not None and state.session_id is None:
         sid = await run_config.session_store.create(state.actor.endpoint.to_dict(),
-                                                    await state.environment.serialize() if state.environment else None)
+                                                    await state.environment.serialize() if state.environment else None,
+                                                    tags=dict(run_config.session_tags) if run_config.session_tags else None)
         state = replace(state, session_id=sid)
         for m in state.actor.trajectory.messages:
             await run_config.session_store.append_message(sid, m)

@@ -367,6 +367,7 @@ class Endpoint:
     model: str = ""
     api_base: str = ""
     api_key: str = ""
+    oauth_token: str = ""                       # a subscription log-in's access token; sent as a bearer token instead of the key
     max_tokens: int = 1024
     temperature: float = 1.0
     top_p: float | None = None
@@ -377,7 +378,7 @@ class Endpoint:
     engine: Any = None                          # in-process InferenceEngine for provider == "native"
 
     def to_dict(self) -> dict[str, Any]:
-        d = {f.name: getattr(self, f.name) for f in fields(self) if f.name not in ("engine", "api_key")}
+        d = {f.name: getattr(self, f.name) for f in fields(self) if f.name not in ("engine", "api_key", "oauth_token")}
         return d
 
 
@@ -414,6 +415,7 @@ class RunConfig:
     api_limiter: Any = None
     tool_limiter: Any = None
     session_store: Any = None
+    session_tags: dict[str, Any] | None = None      # stored with a session this run creates (e.g. its fingerprint)
     cancel_event: Any = None
     show_progress: bool = False
 

@@ -23,6 +23,7 @@ from typing import Any, Callable, Iterable, Iterator
 
 from .agents import run_agent
 from .dtypes import Actor, AgentState, EvalConfig, Message, Score, Trajectory
+from .fingerprint import fingerprint_eval, warn_if_changed
 from .providers.base import NonRetryableError, ProviderError
 
 
@@ -240,6 +241,15 @@ async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfi
                       {"status": status, "provider": provider, "turns_used": 0, "total_tokens": 0})
 
 
+def _fingerprint(config: EvalConfig, dataset_path: str) -> dict[str, Any] | None:
+    """The run's fingerprint for the report (never a reason to fail a run: a dirty tree is recorded, and a scoring lambda,
+    whose name identifies nothing, leaves the report without one)."""
+    try:
+        return fingerprint_eval(config, dataset_path=dataset_path or None, allow_dirty=True)
+    except ValueError:
+        return None
+
+
 async def evaluate(dataset: Iterable[dict[str, Any]], config: EvalConfig, *, resume: bool = False,
                    on_sample_done: Callable[[EvalSample, int, int], None] | None = None, dataset_path: str = "") -> EvalReport:
     """Evaluate every row (``config.max_samples`` first rows) with at most ``config.max_concurrent`` agents in flight.
@@ -251,8 +261,16 @@ async def evaluate(dataset: Iterable[dict[str, Any]], config: EvalConfig, *, res
         rows = rows[:config.max_samples]
     ids = [str(r.get("id", i)) for i, r in enumerate(rows)]
     have: dict[str, EvalSample] = {}
+    fp = _fingerprint(config, dataset_path)
     if resume and config.output_dir:
-        have = {s.sample_id: s for s in load_saved_samples(Path(config.output_dir) / config.eval_name) if s.status != "provider_error"}
+        run_dir = Path(config.output_dir) / config.eval_name
+        have = {s.sample_id: s for s in load_saved_samples(run_dir) if s.status != "provider_error"}
+        if fp is not None and (run_dir / "report.json").is_file():
+            try:
+                saved = json.loads((run_dir / "report.json").read_text()).get("config", {}).get("fingerprint")
+            except (OSError, ValueError):
+                saved = None
+            warn_if_changed(saved, fp, context=f"the saved run {run_dir}")
     sem = asyncio.Semaphore(config.max_concurrent)
     done = 0
 
@@ -271,7 +289,7 @@ async def evaluate(dataset: Iterable[dict[str, Any]], config: EvalConfig, *, res
     samples = list(await asyncio.gather(*[one(sid, r) for sid, r in zip(ids, rows)]))
     report = EvalReport(config.eval_name, samples, compute_summary_metrics(samples),
                         {"endpoint": config.endpoint.to_dict(), "max_turns": config.max_turns, "max_concurrent": config.max_concurrent,
-                         "n_retries": config.n_retries, "resumed_samples": len(have)}, dataset_path=dataset_path)
+                         "n_retries": config.n_retries, "resumed_samples": len(have), "fingerprint": fp}, dataset_path=dataset_path)
     if config.output_dir:
         report.save(config.output_dir)
     return report

@@ -346,13 +346,17 @@ async def rollout_anthropic(actor: Actor, run_config: RunConfig) -> Actor:
     extra = dict(ep.extra_params)
     if extra.pop("prompt_caching", True):      # a cache break point at the end of the conversation so far (at most four per request)
         msgs = add_cache_control_to_last_content(msgs)
+    headers = {"anthropic-version": "2023-06-01", **extra.pop("request_headers", {})}
     payload: dict[str, Any] = {"model": ep.model, "max_tokens": ep.max_tokens, "messages": msgs, "stream": True,
                                "temperature": ep.temperature, **extra}
     if system:
         payload["system"] = system
     if actor.tools:
         payload["tools"] = [tool_to_anthropic(t) for t in actor.tools]
-    headers = {"x-api-key": ep.api_key, "anthropic-version": "2023-06-01"}
+    if ep.oauth_token:
+        headers["Authorization"] = f"Bearer {ep.oauth_token}"
+    else:
+        headers["x-api-key"] = ep.api_key
     base = ep.api_base.rstrip("/") or "https://api.anthropic.com"
     events = _stream_post(f"{base}/v1/messages", payload, headers, ep.timeout, "anthropic")
     return _append(actor, await aggregate_anthropic_stream(events, ep.model, run_config.on_chunk))

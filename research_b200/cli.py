@@ -25,6 +25,18 @@ def _store(args):
     return FileSessionStore(args.store or os.path.join(os.path.expanduser("~"), ".research_b200", "sessions"))
 
 
+def _run_coro(coro):
+    """Run a coroutine to completion from synchronous code, also when the caller is itself inside a running loop."""
+    try:
+        asyncio.get_running_loop()
+    except RuntimeError:
+        return asyncio.run(coro)
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(1) as pool:
+        return pool.submit(asyncio.run, coro).result()
+
+
 def _endpoint(args):
     from .agents.dtypes import Endpoint
 
@@ -37,9 +49,19 @@ def _endpoint(args):
             provider, model = parse_model_string(model)
         except NonRetryableError:
             pass          # an organisation prefix of a model name (meta-llama/...), not a provider
+    oauth_token, extra = "", {}
+    if getattr(args, "oauth", ""):          # a stored subscription log-in takes the place of the API key
+        from .agents.oauth import OAuthApp, OAuthClient
+
+        client = OAuthClient(OAuthApp.load(args.oauth))
+        oauth_token = _run_coro(client.get_valid_access_token()) or ""
+        if not oauth_token:
+            raise SystemExit(f"not logged in to {args.oauth!r} (or the log-in was revoked): run `research_b200 auth login {args.oauth}`")
+        if client.app.request_headers:
+            extra["request_headers"] = dict(client.app.request_headers)
     return Endpoint(provider=provider, model=model, api_base=args.api_base or "",
-                    api_key=os.environ.get(args.api_key_env or "", "") if args.api_key_env else "",
-                    max_tokens=args.max_tokens, temperature=args.temperature)
+                    api_key=os.environ.get(args.api_key_env or "", "") if args.api_key_env and not oauth_token else "",
+                    oauth_token=oauth_token, max_tokens=args.max_tokens, temperature=args.temperature, extra_params=extra)
 
 
 def _add_endpoint_args(p: argparse.ArgumentParser) -> None:
@@ -47,6 +69,7 @@ def _add_endpoint_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--model", default="")
     p.add_argument("--api-base", default="")
     p.add_argument("--api-key-env", default="", help="name of the environment variable that holds the API key")
+    p.add_argument("--oauth", default="", help="name of a configured OAuth application whose stored log-in replaces the API key")
     p.add_argument("--max-tokens", type=int, default=1024)
     p.add_argument("--temperature", type=float, default=1.0)
 
@@ -157,9 +180,16 @@ async def _chat(args) -> int:
         env = preset.environment(args.cwd)
         if hasattr(env, "on_session_start"):
             await env.on_session_start(f"cli-{os.getpid()}")
+    tags = None
+    if store is not None and session_id is None:
+        from .agents.fingerprint import fingerprint_session
+
+        tools = [t.function.name for t in env.get_tools()] if env is not None and hasattr(env, "get_tools") else []
+        tags = {"fingerprint": fingerprint_session(f"{ep.provider}/{ep.model}", preset.name, tools, system_prompt, cwd=args.cwd),
+                "preset": preset.name}
     runner = InteractiveRunner(ep, frontend, environment=env, system_prompt=system_prompt, session_store=store,
                                session_id=session_id, max_turns=preset.max_turns, initial_prompt=args.prompt,
-                               single_turn=args.prompt is not None, trajectory=trajectory)
+                               single_turn=args.prompt is not None, trajectory=trajectory, session_tags=tags)
     state = await runner.run()
     if state.session_id and not args.quiet:
         print(f"session: {state.session_id}", file=sys.stderr)
@@ -176,6 +206,34 @@ def parse_model_string(model: str) -> tuple[str, str]:
 
 def cmd_chat(args) -> int:
     return asyncio.run(_chat(args))
+
+
+def cmd_auth(args) -> int:
+    """``auth login|logout|status NAME``: the subscription log-in of one configured OAuth application."""
+    from .agents.oauth import OAuthApp, OAuthClient, OAuthError, auth_report, login
+
+    try:
+        client = OAuthClient(OAuthApp.load(args.name))
+    except OAuthError as e:
+        print(e, file=sys.stderr)
+        return 2
+    if args.action == "login":
+        async def ask(prompt: str) -> str:
+            return await asyncio.to_thread(input, prompt)
+
+        try:
+            asyncio.run(login(client, ask))
+        except OAuthError as e:
+            print(f"log-in failed: {e}", file=sys.stderr)
+            return 1
+        return 0
+    if args.action == "logout":
+        client.logout()
+        print(f"logged out of {args.name}")
+        return 0
+    using, lines = auth_report(args.provider or args.name, args.api_key_env, client)
+    print("\n".join(lines))
+    return 0 if using != "none" else 1
 
 
 async def _sessions(args) -> int:
@@ -305,6 +363,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("-q", "--quiet", action="store_true", help="only the model's text")
     p.add_argument("--list-presets", action="store_true")
     p.set_defaults(fn=cmd_chat)
+    p = sub.add_parser("auth", help="subscription log-in (OAuth) for a hosted provider")
+    p.add_argument("action", choices=["login", "logout", "status"]); p.add_argument("name", help="configured OAuth application")
+    p.add_argument("--provider", default=""); p.add_argument("--api-key-env", default="")
+    p.set_defaults(fn=cmd_auth)
     p = sub.add_parser("sessions")
     p.add_argument("action", choices=["list", "show", "export", "slice", "import", "doctor", "handoff"]); p.add_argument("id", nargs="?")
     p.add_argument("--fix", action="store_true", help="doctor: write a child session without duplicate / orphaned tool results")

@@ -352,8 +352,10 @@ class InteractiveRunner:
 
     def __init__(self, endpoint: Endpoint, frontend: Frontend, environment: Any = None, system_prompt: str | None = None,
                  session_store: Any = None, session_id: str | None = None, max_turns: int = 20,
-                 initial_prompt: str | None = None, single_turn: bool = False, trajectory: Trajectory | None = None):
+                 initial_prompt: str | None = None, single_turn: bool = False, trajectory: Trajectory | None = None,
+                 session_tags: dict[str, Any] | None = None):
         self.endpoint, self.frontend, self.environment = endpoint, frontend, environment
+        self.session_tags = session_tags
         self.system_prompt = system_prompt
         self.store, self.session_id = session_store, session_id
         self.max_turns, self.initial_prompt, self.single_turn = max_turns, initial_prompt, single_turn
@@ -432,7 +434,8 @@ class InteractiveRunner:
         async def on_input(prompt: str) -> str:
             return await fe.get_input(prompt)
 
-        return RunConfig(on_chunk=on_chunk, confirm_tool=confirm, on_input=on_input, session_store=self.store)
+        return RunConfig(on_chunk=on_chunk, confirm_tool=confirm, on_input=on_input, session_store=self.store,
+                         session_tags=self.session_tags)
 
     def _publish_status(self) -> None:
         u = self.state.usage

@@ -68,3 +68,27 @@ def setup_logging(level: str | None = None, log_file: str | Path | None = None, 
         for h in handlers:
             root.addHandler(h)
     return root
+
+
+# chatty libraries that say nothing useful below WARNING during an agent run
+QUIET_LOGGERS = ("httpx", "httpcore", "httpcore.http11", "httpcore.http2", "openai", "anthropic", "paramiko", "paramiko.transport",
+                 "urllib3", "asyncio")
+
+
+def init_run_logging(experiment_name: str, results_base_dir: str | Path = "results", log_level: str = "INFO",
+                     logger_levels: dict[str, str] | None = None, now: float | None = None) -> Path:
+    """A results folder ``<base>/<experiment>_<UTC timestamp>/`` with the run's JSONL log (``error_log.jsonl``) in it,
+    console logging set up, and HTTP / SSH client libraries held at WARNING unless ``logger_levels`` says otherwise
+    (rollouts/logging_utils.py:13-80). Returns the folder: a run writes its other outputs there."""
+    stamp = time.strftime("%Y%m%d-%H%M%S", time.gmtime(now if now is not None else time.time()))
+    result_dir = Path(results_base_dir) / f"{experiment_name}_{stamp}"
+    result_dir.mkdir(parents=True, exist_ok=True)
+    setup_logging(level=log_level, log_file=result_dir / "error_log.jsonl")
+    for name, lvl in {**{n: "WARNING" for n in QUIET_LOGGERS}, **(logger_levels or {})}.items():
+        logging.getLogger(name).setLevel(lvl.upper())
+    logging.getLogger(__name__).info("results directory: %s", result_dir)
+    return result_dir
+
+
+def get_logger(name: str) -> logging.Logger:
+    return logging.getLogger(name)
