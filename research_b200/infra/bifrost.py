@@ -51,6 +51,13 @@ class RemoteError(RuntimeError):
     pass
 
 
+def local_changes(repo: str | Path) -> list[str]:
+    """Paths of ``repo`` that a push would leave behind: modified, staged or untracked (and not ignored) files
+    (bifrost/bifrost/git_sync.py:49-108)."""
+    r = subprocess.run(["git", "-C", str(repo), "status", "--porcelain"], capture_output=True, text=True)
+    return [line[3:] for line in r.stdout.splitlines() if line.strip()] if r.returncode == 0 else []
+
+
 class RemoteClient:
     """``connection``: ``user@host[:port]`` or ``"local"`` (commands run through ``sh -c`` on this machine)."""
 
@@ -76,10 +83,15 @@ class RemoteClient:
         return code, out, err
 
     # ------------------------------------------------------------------ code push
-    def push(self, repo: str | Path, dest: str, ref: str = "HEAD", bootstrap: str | list[str] | None = None) -> str:
+    def push(self, repo: str | Path, dest: str, ref: str = "HEAD", bootstrap: str | list[str] | None = None,
+             warn: Callable[[str], None] | None = None) -> str:
         """Ship ``ref`` of a local git repository to ``dest`` on the target; returns the commit id deployed.
         ``bootstrap``: command(s) run in ``dest`` afterwards (environment set-up, builds); a failure raises."""
         repo = Path(repo)
+        self.not_shipped = local_changes(repo)       # a push ships commits: what is only in the working tree stays behind
+        if self.not_shipped and warn is not None:
+            warn(f"{len(self.not_shipped)} uncommitted or untracked path(s) are NOT part of this push: " +
+                 ", ".join(self.not_shipped[:8]) + (" ..." if len(self.not_shipped) > 8 else ""))
         commit = subprocess.run(["git", "-C", str(repo), "rev-parse", ref], capture_output=True, text=True, check=True).stdout.strip()
         bundle = subprocess.run(["git", "-C", str(repo), "bundle", "create", "-", ref], capture_output=True, check=True).stdout
         q = shlex.quote(dest)
@@ -193,6 +205,36 @@ class RemoteClient:
                 target.write_bytes(tf.extractfile(m).read())
                 n += 1
         return n
+
+    # ------------------------------------------------------------------ single files on the target
+    @staticmethod
+    def _q(path: str) -> str:
+        return path if path.startswith("~") else shlex.quote(path)      # a quoted ~ would not expand
+
+    def ensure_dir(self, path: str) -> None:
+        self.exec(f"mkdir -p {self._q(path)}", check=True)
+
+    def path_exists(self, path: str) -> bool:
+        return self.exec(f"[ -e {self._q(path)} ]")[0] == 0
+
+    def write_file(self, path: str, content: str | bytes, mode: int | None = None) -> None:
+        """Write ``content`` to ``path`` on the target without any shell quoting of the content (it travels on standard
+        input) and atomically: a reader sees the old file or the new one, never a partial write
+        (bifrost/bifrost/remote_fs.py:22)."""
+        q, data = self._q(path), content.encode() if isinstance(content, str) else content
+        chmod = f"chmod {mode:o} {q}.incoming && " if mode is not None else ""
+        self.exec(f"mkdir -p $(dirname {q}) && cat > {q}.incoming && {chmod}mv -f {q}.incoming {q}", check=True, data=data)
+
+    def read_file(self, path: str) -> str:
+        code, out, err = self.exec(f"cat {self._q(path)}")
+        if code != 0:
+            raise FileNotFoundError(f"{path} on {self.connection}: {err.strip()[:200]}")
+        return out
+
+    def remove_file(self, path: str) -> bool:
+        """Remove one file (never a directory, never a pattern); True if it existed."""
+        q = self._q(path)
+        return self.exec(f"[ -f {q} ] && rm -f -- {q}")[0] == 0
 
     # ------------------------------------------------------------------ servers
     def serve(self, spec: ProcessSpec, port: int, health_path: str = "/health", timeout: float = 600.0, poll: float = 1.0) -> "ServerInfo":

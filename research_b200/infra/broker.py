@@ -123,6 +123,44 @@ class StaticProvider:
         return self._busy.pop(instance_id, None) is not None
 
 
+@dataclass
+class ProvisionAttempt:
+    offer_id: str
+    gpu_type: str
+    provider: str
+    price_per_hour: float
+    error: str | None = None                 # None: this attempt produced ``instance``
+    error_category: str | None = None        # credentials | unavailable | network | unknown
+    instance: GPUInstance | None = None
+
+
+@dataclass
+class ProvisionResult:
+    success: bool
+    instance: GPUInstance | None = None
+    attempts: list[ProvisionAttempt] = field(default_factory=list)
+    error_summary: str | None = None
+    no_offers_found: bool = False
+    all_unavailable: bool = False
+    credential_error: bool = False
+    network_error: bool = False
+
+
+def categorize_error(e: BaseException) -> str:
+    """HTTP status where the error carries one (401/403 credentials; 404/409/410/422/429/503 capacity), else the
+    exception type and a few words providers use for "none left"."""
+    status = getattr(e, "status", None)
+    text = str(e).lower()
+    if status in (401, 403) or "unauthorized" in text or "invalid api key" in text or "forbidden" in text:
+        return "credentials"
+    if isinstance(e, (TimeoutError, ConnectionError)) or "timed out" in text or "connection" in text or "unreachable" in text:
+        return "network"
+    if status in (404, 409, 410, 422, 429, 503) or any(w in text for w in ("capacity", "unavailable", "no longer available", "already in use",
+                                                                            "sold out", "not enough", "out of stock")):
+        return "unavailable"
+    return "unknown"
+
+
 class GPUClient:
     def __init__(self, providers: list[Provider]):
         self.providers = {p.name: p for p in providers}
@@ -145,6 +183,50 @@ class GPUClient:
             except Exception as e:  # noqa: BLE001 - try the next offer
                 errors.append(f"{o.provider}/{o.offer_id}: {e}")
         raise RuntimeError("no offer could be provisioned" + (": " + "; ".join(errors) if errors else " (nothing matched)"))
+
+    def provision(self, where: Condition | None = None, max_attempts: int = 3, **kw: Any) -> "ProvisionResult":
+        """``create`` with a record of what was tried (broker/broker/api.py:255-527): up to ``max_attempts`` offers,
+        cheapest first, each failure sorted into a category so that a caller can tell "change the query" (nothing
+        matched), "try another GPU type" (every offer was out of capacity), "fix the API key" and "try again later"
+        apart without parsing messages."""
+        offers = self.search(where)
+        if not offers:
+            return ProvisionResult(False, error_summary="no offer matches the query", no_offers_found=True)
+        attempts: list[ProvisionAttempt] = []
+        for o in offers[:max_attempts]:
+            try:
+                inst = self.providers[o.provider].create(o, **kw)
+            except Exception as e:  # noqa: BLE001 - recorded, next offer
+                attempts.append(ProvisionAttempt(o.offer_id, o.gpu_type, o.provider, o.price_per_hour, str(e)[:300], categorize_error(e)))
+                continue
+            if inst is None:
+                attempts.append(ProvisionAttempt(o.offer_id, o.gpu_type, o.provider, o.price_per_hour, "the provider returned no instance", "unavailable"))
+                continue
+            self.instances[inst.instance_id] = inst
+            attempts.append(ProvisionAttempt(o.offer_id, o.gpu_type, o.provider, o.price_per_hour, instance=inst))
+            return ProvisionResult(True, inst, attempts)
+        cats = [a.error_category for a in attempts]
+        parts = [f"all {len(attempts)} offers tried were out of capacity" if all(c == "unavailable" for c in cats)
+                 else f"failed after {len(attempts)} offer(s)"]
+        parts += [f"{cats.count(c)} {c} error(s)" for c in ("credentials", "network") if c in cats]
+        return ProvisionResult(False, None, attempts, "; ".join(parts), all_unavailable=all(c == "unavailable" for c in cats),
+                               credential_error="credentials" in cats, network_error="network" in cats)
+
+    def list_instances(self, refresh: bool = True) -> list[GPUInstance]:
+        """Instances this client created, their state re-read from the provider where it offers ``refresh``."""
+        out = []
+        for iid, inst in list(self.instances.items()):
+            fn = getattr(self.providers.get(inst.provider), "refresh", None) if refresh else None
+            if fn is not None:
+                try:
+                    inst = self.instances[iid] = fn(iid)
+                except Exception:  # noqa: BLE001 - keep the last known state
+                    pass
+            out.append(inst)
+        return out
+
+    def get_instance(self, instance_id: str, refresh: bool = True) -> GPUInstance | None:
+        return next((i for i in self.list_instances(refresh) if i.instance_id == instance_id), None)
 
     def terminate(self, instance_id: str) -> bool:
         inst = self.instances.pop(instance_id, None)

@@ -46,6 +46,9 @@ _PY_FROM = re.compile(r"^\s*from\s+(\.*)([\w.]*)\s+import\s+", re.M)
 _PY_IMPORT = re.compile(r"^\s*import\s+([\w.]+)", re.M)
 _JS_IMPORT = re.compile(r"""(?:import\s[^'"]*?from\s*|import\s*|require\()\s*['"](\.{1,2}/[^'"]+)['"]""")
 _LUA_REQUIRE = re.compile(r"""require\s*\(?\s*['"]([\w./]+)['"]""")
+_C_INCLUDE = re.compile(r'^\s*#\s*include\s*"([^"]+)"', re.M)
+# a file named on a comment line of its own, "#[./rel/path]" ("//[...]", "--[...]"): context the imports do not reach
+_MARKER = re.compile(r"^\s*(?:#|//|--)\[(\.{1,2}/[^\]]+)\]\s*$", re.M)
 
 
 def imported_files(path: Path, root: Path) -> list[Path]:
@@ -74,6 +77,15 @@ def imported_files(path: Path, root: Path) -> list[Path]:
     elif path.suffix == ".lua":
         for mod in _LUA_REQUIRE.findall(text):
             add(root.joinpath(*mod.replace("/", ".").split(".")))
+    elif path.suffix in (".c", ".h", ".cpp", ".hpp", ".cc", ".cu", ".cuh"):
+        for inc in _C_INCLUDE.findall(text):
+            for base in (path.parent, root):
+                if (base / inc).is_file():
+                    add(base / inc)
+                    break
+    for rel in _MARKER.findall(text):
+        if (path.parent / rel).is_file():
+            add(path.parent / rel)
     return out
 
 
@@ -172,8 +184,52 @@ FILES:
 {files}"""
 
 
+COMPACTION_THRESHOLD_TOKENS = 32_000
+
+COMPACT_PROMPT = """You are preparing context for a refactoring. Below are the TASK and the FILES gathered for it. Name the files
+that are NOT needed to carry out the task, one per line, as <omit file="path"/>. Omit nothing you are unsure about; answer
+with no <omit> line if everything is needed.
+
+TASK:
+{task}
+
+FILES:
+{files}"""
+
+
+def estimate_tokens(text: str) -> int:
+    return len(text) // 4
+
+
+def _render(ctx: dict[str, str]) -> str:
+    return "\n".join(f'<file path="{p}">\n{c}</file>' for p, c in ctx.items())
+
+
+async def compact_context(ctx: dict[str, str], task: str, complete: Callable[[str], Awaitable[str]], keep: set[str] = frozenset(),
+                          threshold_tokens: int = COMPACTION_THRESHOLD_TOKENS) -> dict[str, str]:
+    """When the gathered files exceed ``threshold_tokens``, ask the model which of them the task does not need and
+    drop those (never a file in ``keep``, never a path that was not offered)."""
+    if estimate_tokens(_render(ctx)) <= threshold_tokens:
+        return ctx
+    reply = await complete(COMPACT_PROMPT.format(task=task, files=_render(ctx)))
+    omit = set(re.findall(r'<omit file="([^"]+)"\s*/>', reply)) & set(ctx) - set(keep)
+    return {p: c for p, c in ctx.items() if p not in omit}
+
+
+def save_run_log(log_dir: Path, entry: str, task: str, prompt: str, reply: str, applied: list[str], now: float | None = None) -> Path:
+    """One text file per run (prompt, reply, what was applied) under ``log_dir``, named by time and entry file."""
+    import time
+
+    log_dir.mkdir(parents=True, exist_ok=True)
+    stamp = time.strftime("%Y%m%d-%H%M%S", time.localtime(now if now is not None else time.time()))
+    f = log_dir / f"{stamp}_{Path(entry).stem}.log"
+    f.write_text(f"# task\n{task}\n\n# prompt\n{prompt}\n\n# reply\n{reply}\n\n# applied\n" + "\n".join(applied) + "\n")
+    return f
+
+
 async def refactor(entry: str | Path, complete: Callable[[str], Awaitable[str]], root: str | Path | None = None,
-                   dry_run: bool = False) -> list[str]:
+                   dry_run: bool = False, compaction_threshold_tokens: int = COMPACTION_THRESHOLD_TOKENS,
+                   log_dir: str | Path | None = None) -> list[str]:
     """Run the whole loop for ``entry``: task from its trailing comments, context from its imports, ``complete(prompt)``
     (any async text-in / text-out model call) for the edits, then apply. The task comment is removed from ``entry``
     before the model sees it; the edits apply to that cleaned text."""
@@ -185,9 +241,13 @@ async def refactor(entry: str | Path, complete: Callable[[str], Awaitable[str]],
     ctx = collect_context(entry, root_p)
     rel = str(entry.relative_to(root_p))
     ctx[rel] = code
-    files = "\n".join(f'<file path="{p}">\n{c}</file>' for p, c in ctx.items())
-    reply = await complete(PROMPT.format(task=task, files=files))
+    ctx = await compact_context(ctx, task, complete, keep={rel}, threshold_tokens=compaction_threshold_tokens)
+    prompt = PROMPT.format(task=task, files=_render(ctx))
+    reply = await complete(prompt)
     edits = parse_edits(reply)
     if not edits:
         raise ValueError("the model returned no edit blocks")
-    return apply_edits(edits, root_p, dry_run, initial={entry: code})
+    applied = apply_edits(edits, root_p, dry_run, initial={entry: code})
+    if log_dir is not None:
+        save_run_log(Path(log_dir), rel, task, prompt, reply, applied)
+    return applied

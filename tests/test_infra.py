@@ -40,6 +40,25 @@ def test_remote_client_local_jobs_and_push(tmp_path):
     c.push(repo, str(tmp_path / "deploy"), ref="main")
     c.push(repo, str(tmp_path / "deploy"), ref="main", bootstrap=["cp f.txt copy.txt", "echo built > stamp"])
     assert (tmp_path / "deploy" / "copy.txt").read_text() == "v2" and (tmp_path / "deploy" / "stamp").exists()
+    # what is only in the working tree is named, not shipped
+    (repo / "f.txt").write_text("v3")
+    (repo / "new.txt").write_text("x")
+    said = []
+    c.push(repo, str(tmp_path / "deploy"), ref="main", warn=said.append)
+    assert sorted(c.not_shipped) == ["f.txt", "new.txt"] and "NOT part of this push" in said[0]
+    assert (tmp_path / "deploy" / "f.txt").read_text() == "v2" and not (tmp_path / "deploy" / "new.txt").exists()
+    # single files on the target: content with quotes and newlines, file mode, atomic replace, removal of files only
+    target = str(tmp_path / "fs" / "deep" / "note.txt")
+    c.write_file(target, "it's \"quoted\"\n$HOME stays literal\n", mode=0o600)
+    assert c.read_file(target) == "it's \"quoted\"\n$HOME stays literal\n" and c.path_exists(target)
+    assert oct((tmp_path / "fs" / "deep" / "note.txt").stat().st_mode & 0o777) == "0o600"
+    c.write_file(target, b"\x00\x01second")
+    assert (tmp_path / "fs" / "deep" / "note.txt").read_bytes() == b"\x00\x01second" and not c.path_exists(target + ".incoming")
+    c.ensure_dir(str(tmp_path / "fs" / "made"))
+    assert not c.remove_file(str(tmp_path / "fs" / "made")) and (tmp_path / "fs" / "made").is_dir()
+    assert c.remove_file(target) and not c.remove_file(target) and not c.path_exists(target)
+    with pytest.raises(FileNotFoundError):
+        c.read_file(target)
     with pytest.raises(RemoteError):
         c.push(repo, str(tmp_path / "deploy"), ref="main", bootstrap="exit 9")
     assert (tmp_path / "deploy" / "f.txt").read_text() == "v2"
@@ -301,3 +320,36 @@ def test_infra_cli_gpus_remote_and_code(tmp_path):
     lines.clear()
     main(["code", "index", "--root", str(proj)], lines.append)
     assert main(["code", "search", "later", "--root", str(proj)], lines.append) == 0
+
+
+def test_provision_records_attempts_and_sorts_failures():
+    from research_b200.infra.broker import ProvisionResult, categorize_error
+    from research_b200.infra.broker_providers import ProviderError
+
+    class Flaky(StaticProvider):
+        def __init__(self, name, offers, failures):
+            super().__init__(name, offers, {})
+            self.failures = dict(failures)
+
+        def create(self, offer, **kw):
+            f = self.failures.get(offer.offer_id)
+            if isinstance(f, BaseException):
+                raise f
+            if f == "none":
+                return None
+            return super().create(offer, **kw)
+
+    offers = [GPUOffer("lab", f"m{i}", "B200", 8, 180, float(i)) for i in range(1, 5)]
+    gc = GPUClient([Flaky("lab", offers, {"m1": ProviderError("lab", 503, "no capacity"), "m2": "none"})])
+    r = gc.provision(q.gpu_type == "B200")
+    assert r.success and r.instance.offer.offer_id == "m3" and [a.error_category for a in r.attempts] == ["unavailable", "unavailable", None]
+    assert gc.get_instance(r.instance.instance_id, refresh=False) is r.instance and gc.list_instances() == [r.instance]
+    assert gc.provision(q.gpu_type == "H100").no_offers_found
+    gc = GPUClient([Flaky("lab", offers, {"m1": ProviderError("lab", 401, "invalid api key"), "m2": TimeoutError("timed out"), "m3": "none"})])
+    r = gc.provision(max_attempts=3)
+    assert isinstance(r, ProvisionResult) and not r.success and r.credential_error and r.network_error and not r.all_unavailable
+    assert "1 credentials error(s)" in r.error_summary and len(r.attempts) == 3
+    gc = GPUClient([Flaky("lab", offers, {f"m{i}": RuntimeError("sold out") for i in range(1, 5)})])
+    r = gc.provision(max_attempts=2)
+    assert r.all_unavailable and "out of capacity" in r.error_summary and len(r.attempts) == 2
+    assert categorize_error(ValueError("weird")) == "unknown"

@@ -106,3 +106,36 @@ def test_task_extraction_context_and_edits(tmp_path):
     with pytest.raises(ValueError):
         apply_edits(parse_edits('<patch file="main.py"><search>absent</search><replace>y</replace></patch>'), tmp_path)
     assert main.read_text() == "from pkg.helpers import helper\n\nprint(helper(2))\n"      # failed edits wrote nothing
+
+
+def test_context_from_includes_and_markers_compaction_and_run_log(tmp_path):
+    from research_b200.infra.refactor_task import collect_context, compact_context, refactor
+
+    (tmp_path / "inc").mkdir()
+    (tmp_path / "inc" / "tile.h").write_text('#include "util.h"\nint tile();\n')
+    (tmp_path / "inc" / "util.h").write_text("int util();\n")
+    (tmp_path / "notes.txt").write_text("layout notes " * 20)
+    (tmp_path / "big.py").write_text("X = 1\n" + "# filler\n" * 400 + "Y = 2\n")
+    kern = tmp_path / "kern.cu"
+    kern.write_text('#include <cuda.h>\n#include "inc/tile.h"\n//[./notes.txt]\n//[./absent.txt]\nint main() { return tile(); }\n')
+    assert set(collect_context(kern, tmp_path)) == {"kern.cu", "inc/tile.h", "inc/util.h", "notes.txt"}
+
+    main = tmp_path / "main.py"
+    main.write_text("import big\n#[./notes.txt]\nprint(big.X)\n\n# rename X to WIDTH\n")
+    prompts = []
+
+    async def complete(prompt):
+        prompts.append(prompt)
+        if "NOT needed" in prompt:
+            return '<omit file="notes.txt"/>\n<omit file="main.py"/>\n<omit file="never/offered.py"/>'
+        return '<patch file="main.py"><search>big.X</search><replace>big.WIDTH</replace></patch>'
+
+    # under the threshold nothing is asked; above it the model's omissions apply, except to the entry file
+    ctx = collect_context(main, tmp_path)
+    assert asyncio.run(compact_context(ctx, "t", complete, threshold_tokens=10**6)) is ctx and not prompts
+    log = asyncio.run(refactor(main, complete, root=tmp_path, compaction_threshold_tokens=200, log_dir=tmp_path / "logs"))
+    assert log == ["patch main.py"] and len(prompts) == 2 and "notes.txt" in prompts[0]
+    assert '<file path="notes.txt">' not in prompts[1] and '<file path="main.py">' in prompts[1] and '<file path="big.py">' in prompts[1]
+    assert "big.WIDTH" in main.read_text()
+    saved = list((tmp_path / "logs").iterdir())
+    assert len(saved) == 1 and saved[0].name.endswith("_main.log") and "# applied\npatch main.py" in saved[0].read_text()
