@@ -100,7 +100,8 @@ async def process_pending_tools(state: AgentState, run_config: RunConfig) -> Age
         content = result.content if not result.is_error else f"Error: {result.error or result.content}"
         traj = traj.append(Message("tool", content, tool_call_id=call.id, name=call.name))
         if run_config.on_chunk is not None:
-            await run_config.on_chunk(ToolResultReceived(tool_call_id=call.id, content=content, is_error=result.is_error))
+            await run_config.on_chunk(ToolResultReceived(tool_call_id=call.id, content=content, is_error=result.is_error,
+                                                         details=dict(result.metadata)))
         if run_config.session_store is not None and state.session_id:
             await run_config.session_store.append_message(state.session_id, traj.messages[-1])
         if result.stop_reason is not None:
@@ -127,6 +128,19 @@ async def run_agent_step(state: AgentState, run_config: RunConfig) -> AgentState
         await run_config.session_store.append_message(state.session_id, last)
     usage = state.usage + actor.trajectory.completions[-1].usage if actor.trajectory.completions else state.usage
     state = replace(state, actor=actor, turn_idx=state.turn_idx + 1, usage=usage)
+    hook = getattr(state.environment, "on_assistant_message", None)
+    if hook is not None:
+        # an environment that reads the reply itself (code blocks or answers written as text, by models without tool
+        # calling) may append messages, change its own state, or set a stop reason; messages it adds are stored too
+        before = len(state.actor.trajectory.messages)
+        state = await hook(last, state)
+        if run_config.session_store is not None and state.session_id:
+            for m in state.actor.trajectory.messages[before:]:
+                await run_config.session_store.append_message(state.session_id, m)
+        if state.stop is not None:
+            return state
+        if len(state.actor.trajectory.messages) > before and not last.get_tool_calls():
+            return state                      # the environment answered: next turn, not "no tool calls"
     calls = tuple(last.get_tool_calls())
     if calls:
         state = replace(state, pending_tool_calls=calls, next_tool_idx=0)

@@ -57,6 +57,7 @@ class ToolResultReceived(StreamEvent):
     tool_call_id: str = ""
     content: str = ""
     is_error: bool = False
+    details: dict[str, Any] = field(default_factory=dict)       # the tool's own extras (an edit's diff, ...) for display
     type: str = "tool_result"
 
 

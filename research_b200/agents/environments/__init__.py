@@ -3,8 +3,9 @@ from .chess_puzzle import Board, ChessPuzzleEnvironment
 from .coding import LocalFilesystemEnvironment, MessageParsingREPLEnvironment, REPLEnvironment
 from .git_worktree import GitWorktreeEnvironment
 from .interactive import AskUserQuestionEnvironment, BrowsingEnvironment, ScreenSpotEnvironment
+from .rlm import MessageParsingRLMEnvironment, RLMEnvironment
 
 __all__ = ["BasicEnvironment", "BinarySearchEnvironment", "CalculatorEnvironment", "ComposedEnvironment", "safe_eval",
            "LocalFilesystemEnvironment", "MessageParsingREPLEnvironment", "REPLEnvironment", "Board",
            "ChessPuzzleEnvironment", "GitWorktreeEnvironment", "AskUserQuestionEnvironment", "BrowsingEnvironment",
-           "ScreenSpotEnvironment"]
+           "ScreenSpotEnvironment", "RLMEnvironment", "MessageParsingRLMEnvironment"]

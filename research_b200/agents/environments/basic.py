@@ -168,6 +168,16 @@ class ComposedEnvironment:
                 return e
         return None
 
+    def get_tool_formatter(self, tool_name: str):
+        get = getattr(self._owner(tool_name), "get_tool_formatter", None)
+        return get(tool_name) if get is not None else None
+
+    def get_status_info(self) -> dict[str, str] | None:
+        info: dict[str, str] = {}
+        for e in self.envs:
+            info.update((getattr(e, "get_status_info", None) or (lambda: None))() or {})
+        return info or None
+
     async def exec_tool(self, tool_call: ToolCall, state: AgentState, run_config: RunConfig) -> ToolResult:
         e = self._owner(tool_call.name)
         if e is None:

@@ -1,7 +1,9 @@
 """File-system and REPL environments (rollouts/environments/coding.py:425, repl.py:308-896).
 
-``LocalFilesystemEnvironment`` exposes read / write / edit / list / bash inside a sandbox root
-(paths that escape the root are refused; bash asks for confirmation). ``REPLEnvironment`` keeps a
+``LocalFilesystemEnvironment`` exposes read (offset / limit, long files and lines cut with a note on how to go on) /
+write / edit (exact single match, answers with a diff) / list / glob / grep / bash (own process group, per-call
+timeout) / web_fetch inside a sandbox root (paths that escape the root are refused; bash asks for confirmation); the
+tool set is a preset or a list, and ``format_tool`` renders a call and its result for the front ends. ``REPLEnvironment`` keeps a
 Python namespace across calls and captures stdout; ``MessageParsingREPLEnvironment`` also runs
 ```python fenced blocks found in the assistant's text.
 """
@@ -24,73 +26,245 @@ def _tool(name, desc, props, required=()):
     return Tool(ToolFunction(name, desc, ToolFunctionParameter(props, tuple(required))))
 
 
+MAX_READ_LINES = 2000
+MAX_LINE_CHARS = 2000
+MAX_BASH_CHARS = 30_000
+TOOL_PRESETS = {"full": ("read", "write", "edit", "list", "glob", "grep", "bash", "web_fetch"),
+                "readonly": ("read", "list", "glob", "grep"),
+                "no-write": ("read", "list", "glob", "grep", "bash", "web_fetch")}
+
+
+def unified_diff(old: str, new: str, path: str = "", context: int = 3) -> str:
+    import difflib
+
+    return "".join(difflib.unified_diff(old.splitlines(keepends=True), new.splitlines(keepends=True), f"a/{path}", f"b/{path}", n=context))
+
+
+def _first_lines(text: str, n: int) -> str:
+    lines = text.splitlines()
+    return "\n".join(lines[:n]) + (f"\n... ({len(lines) - n} more lines)" if len(lines) > n else "")
+
+
+def format_tool(name: str, args: dict[str, Any], result: ToolResult | None = None, expanded: bool = False) -> str:
+    """One tool call as a front end shows it: a header line that reads like the action (``$ ls``, ``read a.py:10-60``,
+    ``edit a.py``) and, once there is a result, a body cut to a few lines unless ``expanded`` (the diff for an edit, the
+    command's output for bash, the line count for a read)."""
+    n = 10**6 if expanded else 12
+    if name == "bash":
+        head = f"$ {args.get('command', '')}"
+    elif name == "read":
+        rng = f":{args['offset']}" + (f"-{args['offset'] + args['limit'] - 1}" if args.get("limit") else "") if args.get("offset") else ""
+        head = f"read {args.get('path', '')}{rng}"
+    elif name in ("write", "edit", "list", "glob", "grep", "web_fetch"):
+        what = args.get("path") or args.get("pattern") or args.get("url") or ""
+        head = f"{name} {what}" + (f" ({len(str(args.get('content', '')).splitlines())} lines)" if name == "write" else "")
+    else:
+        head = f"{name}({', '.join(f'{k}={v!r}' for k, v in args.items())})"
+    if result is None:
+        return head
+    if result.is_error:
+        return f"{head}\n  error: {_first_lines(result.error or result.content, n)}"
+    if name == "read" and not expanded:
+        return f"{head}\n  {len(result.content.splitlines())} lines"
+    body = result.metadata.get("diff") if name == "edit" and result.metadata.get("diff") else result.content
+    return f"{head}\n" + "\n".join("  " + ln for ln in _first_lines(body, n).splitlines())
+
+
 @dataclass
 class LocalFilesystemEnvironment:
+    """``tools``: a preset (``full`` / ``readonly`` / ``no-write``) or a list of tool names. ``sandbox``: refuse paths
+    outside ``root`` (on by default; off gives the agent the user's whole file system, ``~`` included)."""
+
     root: str = "."
     allow_bash: bool = True
-    bash_timeout: float = 30.0
+    bash_timeout: float = 120.0
+    tools: str | list[str] | tuple[str, ...] = "full"
+    sandbox: bool = True
+    fetcher: Any = None                 # async url -> (status, content_type, body); default: urllib
+
+    def __post_init__(self) -> None:
+        if isinstance(self.tools, str):
+            if self.tools not in TOOL_PRESETS:
+                raise ValueError(f"unknown tool preset {self.tools!r}; available: {sorted(TOOL_PRESETS)}")
+            names = TOOL_PRESETS[self.tools]
+        else:
+            unknown = set(self.tools) - set(TOOL_PRESETS["full"])
+            if unknown:
+                raise ValueError(f"unknown tools {sorted(unknown)}; available: {list(TOOL_PRESETS['full'])}")
+            names = tuple(self.tools)
+        self._names = tuple(n for n in names if self.allow_bash or n != "bash")
+
+    def get_name(self) -> str:
+        return "coding"
+
+    def get_status_info(self) -> dict[str, str] | None:
+        cwd, home = str(Path(self.root).resolve()), str(Path.home())
+        return {"cwd": "~" + cwd[len(home):] if cwd == home or cwd.startswith(home + "/") else cwd}
+
+    def get_tool_formatter(self, tool_name: str):
+        return format_tool if tool_name in TOOL_PRESETS["full"] else None
 
     def _resolve(self, rel: str) -> Path:
         root = Path(self.root).resolve()
-        p = (root / rel).resolve()
-        if root != p and root not in p.parents:
+        p = Path(rel).expanduser()
+        p = (p if p.is_absolute() else root / p).resolve()
+        if self.sandbox and root != p and root not in p.parents:
             raise PermissionError(f"path {rel!r} escapes the sandbox root")
         return p
 
     def get_tools(self) -> list[Tool]:
-        s = {"type": "string"}
-        tools = [_tool("read", "Read a text file", {"path": s}, ["path"]),
-                 _tool("write", "Create or overwrite a file", {"path": s, "content": s}, ["path", "content"]),
-                 _tool("edit", "Replace one exact occurrence of old with new", {"path": s, "old": s, "new": s}, ["path", "old", "new"]),
-                 _tool("list", "List a directory", {"path": s})]
-        if self.allow_bash:
-            tools.append(_tool("bash", "Run a shell command in the sandbox root", {"command": s}, ["command"]))
-        return tools
+        s, i = {"type": "string"}, {"type": "integer"}
+        every = {
+            "read": _tool("read", f"Read a text file (first {MAX_READ_LINES} lines; offset / limit, 1-based, for the rest)",
+                          {"path": s, "offset": i, "limit": i}, ["path"]),
+            "write": _tool("write", "Create a file or replace its whole content (parent folders are created)", {"path": s, "content": s}, ["path", "content"]),
+            "edit": _tool("edit", "Replace one exact occurrence of old with new (the text must match exactly, whitespace included)",
+                          {"path": s, "old": s, "new": s}, ["path", "old", "new"]),
+            "list": _tool("list", "List a directory", {"path": s}),
+            "glob": _tool("glob", "Files matching a pattern such as **/*.py, newest first", {"pattern": s, "path": s}, ["pattern"]),
+            "grep": _tool("grep", "Lines matching a regular expression, as path:line:text", {"pattern": s, "path": s, "glob": s, "max_results": i}, ["pattern"]),
+            "bash": _tool("bash", "Run a shell command in the working directory", {"command": s, "timeout": {"type": "number"}}, ["command"]),
+            "web_fetch": _tool("web_fetch", "Fetch an http(s) URL and return its text", {"url": s}, ["url"]),
+        }
+        return [every[n] for n in self._names]
+
+    # ---- tools
+    def _read(self, a: dict[str, Any]) -> str:
+        p = self._resolve(a["path"])
+        if not p.exists():
+            raise FileNotFoundError(f"file not found: {a['path']}")
+        if not p.is_file():
+            raise IsADirectoryError(f"not a file: {a['path']}")
+        try:
+            lines = p.read_text(encoding="utf-8").split("\n")
+        except UnicodeDecodeError:
+            raise ValueError(f"cannot read binary file: {a['path']}") from None
+        start = max(int(a.get("offset") or 1) - 1, 0)
+        if start >= len(lines) and lines != [""]:
+            raise ValueError(f"offset {a.get('offset')} is beyond the end of the file ({len(lines)} lines)")
+        end = min(start + int(a.get("limit") or MAX_READ_LINES), len(lines))
+        cut = any(len(ln) > MAX_LINE_CHARS for ln in lines[start:end])
+        text = "\n".join(ln[:MAX_LINE_CHARS] for ln in lines[start:end])
+        notes = ([f"some lines were cut to {MAX_LINE_CHARS} characters"] if cut else []) + \
+                ([f"{len(lines) - end} more lines not shown: continue with offset={end + 1}"] if end < len(lines) else [])
+        return text + (f"\n\n... ({'; '.join(notes)})" if notes else "")
+
+    def _edit(self, cid: str, a: dict[str, Any]) -> ToolResult:
+        p = self._resolve(a["path"])
+        old, new = a.get("old", a.get("old_text")), a.get("new", a.get("new_text"))
+        if old is None or new is None:
+            raise KeyError("old / new")
+        text = p.read_text()
+        n = text.count(old)
+        if n != 1:
+            hint = " (check whitespace and line endings; read the file again)" if n == 0 else " (add surrounding lines to make it unique)"
+            return ToolResult(cid, is_error=True, error=f"expected exactly one occurrence of the old text, found {n}{hint}")
+        if old == new:
+            return ToolResult(cid, is_error=True, error="old and new are identical: nothing to change")
+        after = text.replace(old, new, 1)
+        p.write_text(after)
+        return ToolResult(cid, content=f"edited {a['path']}", metadata={"diff": unified_diff(text, after, a["path"])})
+
+    def _glob(self, a: dict[str, Any]) -> str:
+        base = self._resolve(a.get("path", "."))
+        hits = sorted((p for p in base.glob(a["pattern"]) if p.is_file() and ".git" not in p.parts), key=lambda p: p.stat().st_mtime, reverse=True)
+        root = Path(self.root).resolve()
+        shown = [str(p.relative_to(root)) if root in p.parents else str(p) for p in hits[:200]]
+        return "\n".join(shown) + (f"\n... ({len(hits) - 200} more)" if len(hits) > 200 else "") or "(no files match)"
+
+    def _grep(self, a: dict[str, Any]) -> str:
+        rx = re.compile(a["pattern"])
+        base, limit = self._resolve(a.get("path", ".")), int(a.get("max_results") or 200)
+        files = [base] if base.is_file() else (p for p in sorted(base.rglob(a.get("glob") or "*")) if p.is_file() and ".git" not in p.parts)
+        root, out = Path(self.root).resolve(), []
+        for f in files:
+            try:
+                text = f.read_text(encoding="utf-8")
+            except (UnicodeDecodeError, OSError):
+                continue
+            rel = str(f.relative_to(root)) if root in f.parents else str(f)
+            for no, line in enumerate(text.splitlines(), 1):
+                if rx.search(line):
+                    out.append(f"{rel}:{no}:{line[:300]}")
+                    if len(out) >= limit:
+                        return "\n".join(out) + f"\n... (stopped at {limit} matches)"
+        return "\n".join(out) or "(no matches)"
+
+    async def _bash(self, cid: str, a: dict[str, Any]) -> ToolResult:
+        import os
+        import signal
+
+        limit = float(a.get("timeout") or self.bash_timeout)
+        proc = await asyncio.create_subprocess_shell(a["command"], cwd=str(Path(self.root).resolve()), stdout=asyncio.subprocess.PIPE,
+                                                     stderr=asyncio.subprocess.STDOUT, start_new_session=True)
+        try:
+            out, _ = await asyncio.wait_for(proc.communicate(), limit)
+        except asyncio.TimeoutError:
+            try:
+                os.killpg(proc.pid, signal.SIGKILL)      # the group this call started: the shell and what it spawned
+            except ProcessLookupError:
+                pass
+            await proc.wait()
+            return ToolResult(cid, is_error=True, error=f"command timed out after {limit:g}s")
+        text = out.decode(errors="replace")
+        if len(text) > MAX_BASH_CHARS:
+            text = f"... ({len(text) - MAX_BASH_CHARS} earlier characters cut)\n" + text[-MAX_BASH_CHARS:]
+        if proc.returncode:
+            return ToolResult(cid, content=text, is_error=True, error=f"{text}\n(exit code {proc.returncode})".lstrip())
+        return ToolResult(cid, content=text or "(no output)")
+
+    async def _web_fetch(self, a: dict[str, Any]) -> str:
+        from .interactive import html_to_text, urllib_fetch
+
+        url = str(a["url"])
+        if not url.startswith(("http://", "https://")):
+            raise ValueError("only http(s) URLs can be fetched")
+        status, ctype, body = await (self.fetcher or urllib_fetch)(url)
+        if status != 200:
+            raise OSError(f"HTTP {status} for {url}")
+        text = html_to_text(body) if "html" in ctype.lower() or body.lstrip()[:1] == "<" else body
+        return text[:50_000] + (f"\n... ({len(text) - 50_000} more characters)" if len(text) > 50_000 else "")
 
     async def exec_tool(self, tool_call: ToolCall, state: AgentState, run_config: RunConfig) -> ToolResult:
-        a, cid = tool_call.args, tool_call.id
+        a, cid, name = tool_call.args, tool_call.id, tool_call.name
+        if name not in self._names:
+            return ToolResult(cid, is_error=True, error=f"unknown tool {name!r}" if name not in TOOL_PRESETS["full"] else f"tool {name!r} is not enabled here")
         try:
-            if tool_call.name == "read":
-                return ToolResult(cid, content=self._resolve(a["path"]).read_text())
-            if tool_call.name == "write":
+            if name == "read":
+                return ToolResult(cid, content=self._read(a))
+            if name == "write":
                 p = self._resolve(a["path"])
+                before = p.read_text() if p.is_file() else None
                 p.parent.mkdir(parents=True, exist_ok=True)
                 p.write_text(a["content"])
-                return ToolResult(cid, content=f"wrote {len(a['content'])} characters to {a['path']}")
-            if tool_call.name == "edit":
-                p = self._resolve(a["path"])
-                text = p.read_text()
-                n = text.count(a["old"])
-                if n != 1:
-                    return ToolResult(cid, is_error=True, error=f"expected exactly one occurrence of the old text, found {n}")
-                p.write_text(text.replace(a["old"], a["new"], 1))
-                return ToolResult(cid, content=f"edited {a['path']}")
-            if tool_call.name == "list":
+                return ToolResult(cid, content=f"wrote {len(a['content'])} characters to {a['path']}",
+                                  metadata={"diff": unified_diff(before, a["content"], a["path"])} if before is not None else {"created": True})
+            if name == "edit":
+                return self._edit(cid, a)
+            if name == "list":
                 p = self._resolve(a.get("path", "."))
                 return ToolResult(cid, content="\n".join(sorted(x.name + ("/" if x.is_dir() else "") for x in p.iterdir())))
-            if tool_call.name == "bash" and self.allow_bash:
-                proc = await asyncio.create_subprocess_shell(a["command"], cwd=str(Path(self.root).resolve()),
-                                                             stdout=asyncio.subprocess.PIPE, stderr=asyncio.subprocess.STDOUT)
-                try:
-                    out, _ = await asyncio.wait_for(proc.communicate(), self.bash_timeout)
-                except asyncio.TimeoutError:
-                    proc.kill()  # the child this call started
-                    return ToolResult(cid, is_error=True, error=f"command timed out after {self.bash_timeout}s")
-                text = out.decode(errors="replace")[-20000:]
-                return ToolResult(cid, content=text, is_error=proc.returncode != 0, error=text if proc.returncode else None)
-            return ToolResult(cid, is_error=True, error=f"unknown tool {tool_call.name!r}")
-        except (OSError, KeyError, PermissionError) as e:
+            if name == "glob":
+                return ToolResult(cid, content=self._glob(a))
+            if name == "grep":
+                return ToolResult(cid, content=self._grep(a))
+            if name == "bash":
+                return await self._bash(cid, a)
+            return ToolResult(cid, content=await self._web_fetch(a))
+        except (OSError, KeyError, ValueError, re.error) as e:      # PermissionError, FileNotFoundError are OSErrors
             return ToolResult(cid, is_error=True, error=f"{type(e).__name__}: {e}")
 
     def requires_confirmation(self, tool_call: ToolCall) -> bool:
         return tool_call.name == "bash"
 
     async def serialize(self) -> dict[str, Any]:
-        return {"type": "filesystem", "root": self.root, "allow_bash": self.allow_bash, "bash_timeout": self.bash_timeout}
+        return {"type": "filesystem", "root": self.root, "allow_bash": self.allow_bash, "bash_timeout": self.bash_timeout,
+                "tools": self.tools if isinstance(self.tools, str) else list(self.tools), "sandbox": self.sandbox}
 
     @staticmethod
     async def deserialize(data: dict[str, Any]) -> "LocalFilesystemEnvironment":
-        return LocalFilesystemEnvironment(data.get("root", "."), data.get("allow_bash", True), data.get("bash_timeout", 30.0))
+        return LocalFilesystemEnvironment(data.get("root", "."), data.get("allow_bash", True), data.get("bash_timeout", 120.0),
+                                          data.get("tools", "full"), data.get("sandbox", True))
 
 
 @dataclass

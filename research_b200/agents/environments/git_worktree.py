@@ -31,6 +31,11 @@ class GitWorktreeEnvironment:
     def get_name(self) -> str:
         return "git_worktree"
 
+    def get_tool_formatter(self, tool_name: str):
+        from .coding import TOOL_PRESETS, format_tool
+
+        return format_tool if tool_name in TOOL_PRESETS["full"] else None
+
     def get_status_info(self) -> dict[str, str] | None:
         if not self.worktree_path:
             return None

@@ -3,7 +3,13 @@
 
 from __future__ import annotations
 
-from dataclasses import dataclass
+import importlib
+import importlib.util
+import json
+import re
+import sys
+from dataclasses import asdict, dataclass
+from pathlib import Path
 from typing import Any, Callable
 
 from .environments import (AskUserQuestionEnvironment, BasicEnvironment, BrowsingEnvironment, CalculatorEnvironment,
@@ -38,7 +44,123 @@ PRESETS: dict[str, AgentPreset] = {p.name: p for p in [
 ]}
 
 
+# ------------------------------------------------------------------------------------------- presets as files
+# environment names a preset file (and the command line) may use -> factory(working directory, tool preset)
+ENVIRONMENTS: dict[str, Callable[[str, Any], Any]] = {
+    "none": lambda cwd, tools: BasicEnvironment(),
+    "calculator": lambda cwd, tools: CalculatorEnvironment(),
+    "coding": lambda cwd, tools: LocalFilesystemEnvironment(cwd, tools=tools or "full"),
+    "git": lambda cwd, tools: GitWorktreeEnvironment(cwd),
+    "coding-interactive": lambda cwd, tools: ComposedEnvironment([LocalFilesystemEnvironment(cwd, tools=tools or "full"), AskUserQuestionEnvironment()]),
+    "browsing": lambda cwd, tools: BrowsingEnvironment(),
+    "repl": lambda cwd, tools: REPLEnvironment(),
+    "research": lambda cwd, tools: ComposedEnvironment([BrowsingEnvironment(), REPLEnvironment()]),
+}
+PRESET_DIR = Path(__file__).resolve().parent / "preset_files"
+USER_PRESET_DIR = Path.home() / ".research_b200" / "presets"
+
+
+@dataclass(frozen=True)
+class AgentPresetConfig:
+    """A preset as data (rollouts/agent_presets/base_preset.py:17-82): model, environment name and system prompt, kept in
+    a Python file ``<name>_<id>_<parent id>.py`` that exports ``config``. A variant imports its parent's ``config`` and
+    changes fields with ``dataclasses.replace``, so the file name records the lineage and the file the difference."""
+
+    name: str
+    model: str                              # "provider/model"
+    env: str                                # a key of ENVIRONMENTS
+    system_prompt: str
+    thinking: bool = True
+    temperature: float | None = None
+    working_dir: Path | None = None
+    tools: str | None = None                # tool preset of the coding environment: full | readonly | no-write
+    max_turns: int = 50
+    description: str = ""
+
+    def save(self, path: str | Path) -> None:
+        Path(path).write_text(json.dumps(asdict(self), indent=2, default=str))
+
+    @classmethod
+    def load(cls, path: str | Path) -> "AgentPresetConfig":
+        d = json.loads(Path(path).read_text())
+        if d.get("working_dir") is not None:
+            d["working_dir"] = Path(d["working_dir"])
+        return cls(**d)
+
+    def to_cli_args(self) -> dict[str, Any]:
+        """The fields as the chat command's arguments (unset optional ones left out)."""
+        out: dict[str, Any] = {"model": self.model, "env": self.env, "system_prompt": self.system_prompt, "thinking": self.thinking}
+        for k in ("temperature", "working_dir", "tools"):
+            if getattr(self, k) is not None:
+                out[k] = getattr(self, k)
+        return out
+
+    def to_preset(self) -> AgentPreset:
+        if self.env not in ENVIRONMENTS:
+            raise KeyError(f"preset {self.name!r} names unknown environment {self.env!r}; available: {sorted(ENVIRONMENTS)}")
+        factory, tools, fixed = ENVIRONMENTS[self.env], self.tools, self.working_dir
+        return AgentPreset(self.name, self.description or f"{self.model} in {self.env}", self.system_prompt,
+                           lambda cwd: factory(str(fixed) if fixed is not None else cwd, tools), self.max_turns)
+
+
+def _load_preset_file(path: Path) -> AgentPresetConfig:
+    if path.suffix == ".json":
+        return AgentPresetConfig.load(path)
+    if path.parent.resolve() == PRESET_DIR:      # shipped presets are package modules: relative imports of a parent work
+        module = importlib.import_module(f"{__package__}.preset_files.{path.stem}")
+    else:
+        spec = importlib.util.spec_from_file_location(f"_rb_preset_{path.stem}", path)
+        if spec is None or spec.loader is None:
+            raise ImportError(f"cannot load a preset from {path}")
+        module = importlib.util.module_from_spec(spec)
+        sys.path.insert(0, str(path.parent))      # a variant may import its parent that sits beside it
+        try:
+            spec.loader.exec_module(module)
+        finally:
+            sys.path.remove(str(path.parent))
+    config = getattr(module, "config", None)
+    if not isinstance(config, AgentPresetConfig):
+        raise TypeError(f"{path} must define `config`, an AgentPresetConfig (found {type(config).__name__})")
+    return config
+
+
+_NUMBERED = re.compile(r"^(?P<stem>.+)_(?P<id>\d+)_(?P<parent>\d+)$")
+
+
+def list_presets(preset_dir: str | Path | None = None) -> list[str]:
+    """Names of the preset files (without ``.py``) of ``preset_dir``; by default the shipped ones, then the user's."""
+    dirs = [Path(preset_dir)] if preset_dir is not None else [PRESET_DIR, USER_PRESET_DIR]
+    return [f.stem for d in dirs if d.is_dir() for f in sorted(d.glob("*.py")) if not f.name.startswith("_")]
+
+
+def load_preset(name: str, preset_dir: str | Path | None = None) -> AgentPresetConfig:
+    """By file path (``~/presets/mine.py``, ``.json``), by full file name (``careful_coder_01_01``) or by the name
+    without numbers (``careful_coder``: the highest-numbered file of that stem wins, i.e. the latest variant)."""
+    p = Path(name).expanduser()
+    if p.suffix in (".py", ".json") or "/" in name:
+        if not p.is_file():
+            raise FileNotFoundError(f"preset file not found: {p}")
+        return _load_preset_file(p)
+    dirs = [Path(preset_dir)] if preset_dir is not None else [USER_PRESET_DIR, PRESET_DIR]
+    for d in dirs:
+        if (d / f"{name}.py").is_file():
+            return _load_preset_file(d / f"{name}.py")
+    best: tuple[int, Path] | None = None
+    for d in dirs:
+        for f in (d.glob("*.py") if d.is_dir() else ()):
+            m = _NUMBERED.match(f.stem)
+            if m and m.group("stem") == name and (best is None or int(m.group("id")) > best[0]):
+                best = (int(m.group("id")), f)
+    if best is None:
+        raise KeyError(f"unknown preset {name!r}; built in: {sorted(PRESETS)}; files: {list_presets(preset_dir)}")
+    return _load_preset_file(best[1])
+
+
 def get_preset(name: str) -> AgentPreset:
-    if name not in PRESETS:
-        raise KeyError(f"unknown preset {name!r}; available: {sorted(PRESETS)}")
-    return PRESETS[name]
+    """A built-in preset by name, else a preset file (see ``load_preset``)."""
+    if name in PRESETS:
+        return PRESETS[name]
+    try:
+        return load_preset(name).to_preset()
+    except (KeyError, FileNotFoundError) as e:
+        raise KeyError(f"unknown preset {name!r}; available: {sorted(PRESETS) + list_presets()}") from e

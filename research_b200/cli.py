@@ -151,16 +151,32 @@ def cmd_serve(args) -> int:
 
 async def _chat(args) -> int:
     from .agents.agents import resume_session
-    from .agents.presets import get_preset
+    from .agents.presets import PRESETS, AgentPreset, get_preset, list_presets, load_preset
     from .frontend.terminal import InteractiveRunner, make_frontend
 
     if args.list_presets:
-        from .agents.presets import PRESETS
-
         for p in PRESETS.values():
             print(f"{p.name:<20} {p.description}  (max {p.max_turns} turns)")
+        for name in list_presets():
+            pc = load_preset(name)
+            print(f"{name:<28} {pc.description or pc.env}  [{pc.model}]")
         return 0
-    preset, ep = get_preset(args.preset), _endpoint(args)
+    preset = get_preset(args.preset)
+    if args.preset not in PRESETS:              # a preset file also names its model; --model / --temperature still win
+        pc = load_preset(args.preset)
+        if not args.model:
+            args.model = pc.model
+        if pc.temperature is not None and args.temperature == 1.0:
+            args.temperature = pc.temperature
+        if args.tools:
+            from dataclasses import replace as _replace
+
+            preset = _replace(pc, tools=args.tools).to_preset()
+    elif args.tools and args.preset in ("coding", "coding-interactive"):
+        from .agents.presets import ENVIRONMENTS
+
+        preset = AgentPreset(preset.name, preset.description, preset.system_prompt, lambda cwd: ENVIRONMENTS[args.preset](cwd, args.tools), preset.max_turns)
+    ep = _endpoint(args)
     store = None if args.no_session else _store(args)
     frontend = make_frontend("json" if args.stream_json else ("plain" if args.quiet and args.frontend == "auto" else args.frontend),
                              auto_confirm=args.yes)
@@ -362,6 +378,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--stream-json", action="store_true", help="print every event as one JSON line (for programs)")
     p.add_argument("-q", "--quiet", action="store_true", help="only the model's text")
     p.add_argument("--list-presets", action="store_true")
+    p.add_argument("--tools", default="", choices=["", "full", "readonly", "no-write"], help="tool set of a coding preset")
     p.set_defaults(fn=cmd_chat)
     p = sub.add_parser("auth", help="subscription log-in (OAuth) for a hosted provider")
     p.add_argument("action", choices=["login", "logout", "status"]); p.add_argument("name", help="configured OAuth application")

@@ -60,6 +60,26 @@ class PlainFrontend:
         self.show_thinking, self.auto_confirm = show_thinking, auto_confirm
         self._mid_line = False
         self.status: dict[str, Any] = {}
+        self.environment: Any = None          # set by the runner: its get_tool_formatter(name) renders calls / results
+        self._calls: dict[str, tuple[str, dict[str, Any]]] = {}
+
+    def _formatted(self, event: StreamEvent, expanded: bool = False) -> str | None:
+        """The environment's own rendering of a tool call (``ToolCallEnd``) or of its result (``ToolResultReceived``),
+        None when the environment offers no formatter for that tool."""
+        from ..agents.dtypes import ToolResult
+
+        if isinstance(event, ToolCallEnd):
+            self._calls[event.tool_call_id] = (event.name, event.args)
+            name, args, result = event.name, event.args, None
+        else:
+            if event.tool_call_id not in self._calls:
+                return None
+            name, args = self._calls.pop(event.tool_call_id)
+            result = ToolResult(event.tool_call_id, event.content, event.is_error, event.content if event.is_error else None,
+                                metadata=dict(event.details))
+        get = getattr(self.environment, "get_tool_formatter", None)
+        fmt = get(name) if get is not None else None
+        return fmt(name, args, result, expanded) if fmt is not None else None
 
     def _w(self, s: str) -> None:
         self.out.write(s)
@@ -84,11 +104,13 @@ class PlainFrontend:
                 self._w(event.delta)
         elif isinstance(event, ToolCallEnd):
             self._fresh_line()
-            self._w(f"[tool] {event.name}({json.dumps(event.args, ensure_ascii=False)})\n")
+            text = self._formatted(event)
+            self._w(f"[tool] {text}\n" if text is not None else f"[tool] {event.name}({json.dumps(event.args, ensure_ascii=False)})\n")
         elif isinstance(event, ToolResultReceived):
             self._fresh_line()
             tag = "error" if event.is_error else "result"
-            self._w(f"[{tag}] {_truncate(event.content, 2000)}\n")
+            text = self._formatted(event)
+            self._w(f"[{tag}] {text}\n" if text is not None else f"[{tag}] {_truncate(event.content, 2000)}\n")
         elif isinstance(event, StreamError):
             self._fresh_line()
             self._w(f"[error] {event.error}\n")
@@ -301,6 +323,7 @@ class AnsiFrontend(PlainFrontend):
             self.show_loader(f"{event.name}: receiving arguments")
         elif isinstance(event, ToolCallEnd):
             self._enter("")
+            self._formatted(event)                  # remembers the call for its result
             args = json.dumps(event.args, ensure_ascii=False, indent=2)
             self._w(box(f"tool: {event.name}", truncate_lines(args, 10, self.width - 4), self.width, Theme.TOOL) + "\n")
             self.show_loader(f"running {event.name}")
@@ -308,7 +331,8 @@ class AnsiFrontend(PlainFrontend):
             self._enter("")
             color = Theme.ERROR if event.is_error else Theme.DIM
             title = "error" if event.is_error else "result"
-            self._w(box(title, truncate_lines(event.content, self.max_result_lines, self.width - 4), self.width, color) + "\n")
+            body = self._formatted(event) or event.content
+            self._w(box(title, truncate_lines(body, self.max_result_lines, self.width - 4), self.width, color) + "\n")
         elif isinstance(event, StreamError):
             self._enter("")
             self._w(f"{Theme.ERROR}error: {event.error}{Theme.RESET}\n")
@@ -356,6 +380,8 @@ class InteractiveRunner:
                  session_tags: dict[str, Any] | None = None):
         self.endpoint, self.frontend, self.environment = endpoint, frontend, environment
         self.session_tags = session_tags
+        if hasattr(frontend, "environment"):
+            frontend.environment = environment
         self.system_prompt = system_prompt
         self.store, self.session_id = session_store, session_id
         self.max_turns, self.initial_prompt, self.single_turn = max_turns, initial_prompt, single_turn

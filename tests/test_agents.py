@@ -252,3 +252,159 @@ def test_evaluate_outcomes_resume_and_files(tmp_path):
     assert asyncio.run(simple_evaluate(tmp_path / "d.jsonl", cfg2)).dataset_path.endswith("d.jsonl")
     with pytest.raises(ValueError):
         asyncio.run(simple_evaluate(tmp_path / "d.txt", cfg2))
+
+
+def test_filesystem_environment_tools_presets_and_formatting(tmp_path):
+    """read windows and notes, edit diff, glob / grep, bash timeout and exit codes, web_fetch through an injected fetcher,
+    tool presets, and what the front end prints for a call and its result."""
+    import io
+
+    from research_b200.agents.environments.coding import MAX_READ_LINES, format_tool
+    from research_b200.frontend.terminal import PlainFrontend
+    from research_b200.agents.dtypes import ToolCallEnd, ToolResultReceived
+
+    (tmp_path / "pkg").mkdir()
+    (tmp_path / "pkg" / "big.txt").write_text("\n".join(f"line {i}" for i in range(1, 2501)))
+    (tmp_path / "pkg" / "wide.txt").write_text("x" * 5000 + "\nshort")
+    (tmp_path / "pkg" / "a.py").write_text("import os\n\ndef f():\n    return 1\n")
+    (tmp_path / "pkg" / "bin.dat").write_bytes(b"\xff\xfe\x00\x01")
+
+    async def fetch(url):
+        return (200, "text/html", "<html><script>x()</script><body><h1>Title</h1><p>Body &amp; more</p></body></html>") if "ok" in url else (404, "", "")
+
+    async def go():
+        fs = LocalFilesystemEnvironment(str(tmp_path), bash_timeout=20, fetcher=fetch)
+        st, rc = _state(fs), RunConfig()
+        call = lambda name, **a: fs.exec_tool(ToolCall("c", name, a), st, rc)                                       # noqa: E731
+        r = await call("read", path="pkg/big.txt")
+        assert r.content.startswith("line 1\n") and f"line {MAX_READ_LINES}\n" in r.content and f"offset={MAX_READ_LINES + 1}" in r.content
+        r = await call("read", path="pkg/big.txt", offset=2400, limit=3)
+        assert r.content.startswith("line 2400\nline 2401\nline 2402") and "98 more lines" in r.content
+        assert (await call("read", path="pkg/big.txt", offset=2499, limit=50)).content == "line 2499\nline 2500"
+        assert "beyond the end" in (await call("read", path="pkg/big.txt", offset=9000)).error
+        assert "cut to 2000 characters" in (await call("read", path="pkg/wide.txt")).content
+        assert "binary" in (await call("read", path="pkg/bin.dat")).error and "not found" in (await call("read", path="nope")).error
+        r = await call("edit", path="pkg/a.py", old="return 1", new="return 2")
+        assert "-    return 1" in r.metadata["diff"] and "+    return 2" in r.metadata["diff"]
+        assert "found 0" in (await call("edit", path="pkg/a.py", old="return 1", new="x")).error
+        assert "identical" in (await call("edit", path="pkg/a.py", old_text="import os", new_text="import os")).error
+        assert (await call("write", path="pkg/a.py", content="import sys\n")).metadata["diff"].count("\n-") >= 3
+        assert (await call("write", path="new/b.py", content="def g(): pass\n")).metadata == {"created": True}
+        assert set((await call("glob", pattern="**/*.py")).content.split()) == {"pkg/a.py", "new/b.py"}
+        assert (await call("grep", pattern=r"def \w+", glob="*.py")).content == "new/b.py:1:def g(): pass"
+        assert (await call("grep", pattern="line 24..$", path="pkg/big.txt", max_results=2)).content.endswith("(stopped at 2 matches)")
+        assert "error" in (await call("grep", pattern="(")).error
+        r = await call("bash", command="echo out; echo err >&2; exit 3")
+        assert r.is_error and "out" in r.content and "exit code 3" in r.error
+        r = await call("bash", command="sleep 30", timeout=0.3)
+        assert r.is_error and "timed out after 0.3s" in r.error
+        assert (await call("web_fetch", url="https://ok.example/")).content.split() == ["Title", "Body", "&", "more"]
+        assert "404" in (await call("web_fetch", url="https://gone.example/")).error and "http" in (await call("web_fetch", url="file:///etc/passwd")).error
+        # presets
+        ro = LocalFilesystemEnvironment(str(tmp_path), tools="readonly")
+        assert [t.function.name for t in ro.get_tools()] == ["read", "list", "glob", "grep"]
+        assert "not enabled" in (await ro.exec_tool(ToolCall("c", "write", {"path": "x", "content": ""}), st, rc)).error
+        assert [t.function.name for t in LocalFilesystemEnvironment(str(tmp_path), allow_bash=False, tools=["read", "bash"]).get_tools()] == ["read"]
+        again = await LocalFilesystemEnvironment.deserialize(await ro.serialize())
+        assert again.tools == "readonly" and again.get_status_info()["cwd"].endswith(tmp_path.name)
+        with pytest.raises(ValueError):
+            LocalFilesystemEnvironment(str(tmp_path), tools="everything")
+        # what a front end prints
+        out = io.StringIO()
+        fe = PlainFrontend(out=out)
+        fe.environment = ComposedEnvironment([fs, CalculatorEnvironment()])
+        await fe.handle_event(ToolCallEnd(tool_call_id="e1", name="edit", args={"path": "new/b.py", "old": "pass", "new": "return 1"}))
+        res = await call("edit", path="new/b.py", old="pass", new="return 1")
+        await fe.handle_event(ToolResultReceived(tool_call_id="e1", content=res.content, details=res.metadata))
+        await fe.handle_event(ToolCallEnd(tool_call_id="e2", name="add", args={"value": 2}))
+        await fe.handle_event(ToolResultReceived(tool_call_id="e2", content="2.0"))
+        text = out.getvalue()
+        assert "[tool] edit new/b.py" in text and "+def g(): return 1" in text and '[tool] add({"value": 2})' in text and "[result] 2.0" in text
+
+    asyncio.run(go())
+    assert format_tool("bash", {"command": "ls"}) == "$ ls" and format_tool("read", {"path": "a", "offset": 5, "limit": 10}) == "read a:5-14"
+    from research_b200.agents.dtypes import ToolResult
+
+    long = ToolResult("x", "\n".join(str(i) for i in range(40)))
+    assert "(28 more lines)" in format_tool("bash", {"command": "seq"}, long) and "more lines" not in format_tool("bash", {"command": "seq"}, long, expanded=True)
+    assert format_tool("read", {"path": "a"}, long).endswith("40 lines")
+
+
+def test_rlm_environment_code_calls_models_and_sub_agents():
+    """`context` lives in the namespace; code running in a worker thread calls llm_query / agent, which run on the event
+    loop; a sub-agent works one level deeper on the piece it was given; depth is bounded; state survives serialize()."""
+    from research_b200.agents.environments.rlm import MessageParsingRLMEnvironment, RLMEnvironment, _final_call, run_code
+
+    assert run_code("x = 2\nx * 21", {}) == ("42\n", False) and run_code("1/0", {})[1] and "cut" in run_code("print('a' * 50)", {}, 10)[0]
+    assert _final_call("so FINAL(f(1) + 'x') done") == "f(1) + 'x'" and _final_call('FINAL("quoted")') == "quoted" and _final_call("```repl\nFINAL(1)\n```") is None
+    doc = "\n".join(f"record {i}: value {i * i}" for i in range(200)) + "\nthe secret code is 73519\n"
+
+    async def sub_model(actor, run_config):
+        """Plays both the question-answering sub-model and the sub-agent's policy."""
+        last = actor.trajectory.messages[-1]
+        if actor.tools and last.role == "user":              # a sub-agent's first turn: search its own context
+            return await ScriptedLLM([Message("assistant", "", tool_calls=(ToolCall("s1", "repl", {"code": "import re\nre.findall(r'code is (\\d+)', context)[0]"}),))])(actor, run_config)
+        if actor.tools:                                      # second turn: answer with what the tool printed
+            return await ScriptedLLM([Message("assistant", "", tool_calls=(ToolCall("s2", "final_answer", {"answer": last.text().strip().strip("'")}),))])(actor, run_config)
+        return await ScriptedLLM(["LEN=" + str(len(last.text()))])(actor, run_config)
+
+    register_provider("rlm-sub", sub_model)
+    env = RLMEnvironment(context=doc, sub_endpoint=Endpoint(provider="rlm-sub"), max_depth=2)
+    main = ScriptedLLM([
+        Message("assistant", "", tool_calls=(ToolCall("m1", "repl", {"code": "tail = context[-40:]\nn = llm_query('how long? ' + tail)\nprint(n)"}),)),
+        Message("assistant", "", tool_calls=(ToolCall("m2", "repl", {"code": "found = agent('find the code', context[-100:])\nprint('FOUND', found)"}),)),
+        Message("assistant", "", tool_calls=(ToolCall("m3", "agent", {"task": "find the code"}),)),
+        Message("assistant", "", tool_calls=(ToolCall("m4", "final_answer", {"answer": "73519"}),))])
+    register_provider("mock", main)
+    start = Trajectory((Message("system", env.get_system_prompt()), Message("user", "What is the secret code?")))
+    final = asyncio.run(run_agent(AgentState(Actor(start, Endpoint(provider="mock")), env, max_turns=8)))[-1]
+    tool_msgs = [m.text() for m in final.actor.trajectory.messages if m.role == "tool"]
+    assert final.stop == StopReason.TASK_COMPLETED and final.environment.final_answer == "73519"
+    assert tool_msgs[0].strip() == "LEN=50" and tool_msgs[1].strip() == "FOUND 73519" and tool_msgs[2] == "73519"
+    assert final.environment.namespace["found"] == "73519" and final.environment.sub_calls == 3     # one query, two sub-agents
+    assert "24" in env.get_system_prompt() or str(len(doc)) in env.get_system_prompt().replace(",", "")
+    # depth limit: a sub-agent at the last level is refused
+    deep = RLMEnvironment(context="x", sub_endpoint=Endpoint(provider="rlm-sub"), max_depth=2, depth=1)
+    assert "maximum depth" in asyncio.run(deep._agent("t", None, RunConfig()))
+    assert "no sub_endpoint" in asyncio.run(RLMEnvironment(context="x").exec_tool(ToolCall("q", "llm_query", {"prompt": "p"}), None, RunConfig())).error
+    # text-only models: fenced blocks run, output returns as a user message, FINAL_VAR ends the episode
+    register_provider("mock", ScriptedLLM(["Let me look.\n```repl\nhits = [l for l in context.split('\\n') if 'secret' in l]\nprint(hits[0])\n```",
+                                           "```repl\ncode = hits[0].split()[-1]\n```\nFINAL_VAR(code)"]))
+    mp = MessageParsingRLMEnvironment(context=doc)
+    final = asyncio.run(run_agent(AgentState(Actor(Trajectory((Message("system", mp.get_system_prompt()), Message("user", "code?"))),
+                                                   Endpoint(provider="mock")), mp, max_turns=5)))[-1]
+    msgs = final.actor.trajectory.messages
+    assert final.stop == StopReason.TASK_COMPLETED and final.environment.final_answer == "73519" and final.turn_idx == 2
+    assert msgs[3].role == "user" and "the secret code is 73519" in msgs[3].text() and mp.get_tools() == []
+
+
+def test_preset_files_lineage_lookup_and_environments(tmp_path):
+    from research_b200.agents import presets
+
+    assert set(presets.list_presets(presets.PRESET_DIR)) >= {"careful_coder_01_01", "fast_coder_02_01", "explorer_03_01", "scratchpad_04_04"}
+    root, fast = presets.load_preset("careful_coder_01_01"), presets.load_preset("fast_coder")
+    assert fast.name == "fast_coder" and not fast.thinking and fast.system_prompt.startswith(root.system_prompt) and fast.env == "coding"
+    ex = presets.get_preset("explorer")
+    env = ex.environment(str(tmp_path))
+    assert [t.function.name for t in env.get_tools()] == ["read", "list", "glob", "grep"] and ex.max_turns == 40
+    assert presets.get_preset("coding").name == "coding" and "fast_coder_02_01" in str(pytest.raises(KeyError, presets.get_preset, "nope").value)
+    # a user's folder: the latest variant of a stem wins; a variant imports the parent beside it; JSON round trip
+    (tmp_path / "mine_01_01.py").write_text("from research_b200.agents.presets import AgentPresetConfig\n"
+                                            "config = AgentPresetConfig('mine', 'openai/gpt-4o-mini', 'calculator', 'v1')\n")
+    (tmp_path / "mine_02_01.py").write_text("from dataclasses import replace\nfrom mine_01_01 import config as parent\n"
+                                            "config = replace(parent, system_prompt=parent.system_prompt + ' v2', temperature=0.2)\n")
+    (tmp_path / "broken.py").write_text("config = {'name': 'x'}\n")
+    latest = presets.load_preset("mine", tmp_path)
+    assert latest.system_prompt == "v1 v2" and presets.load_preset("mine_01_01", tmp_path).system_prompt == "v1"
+    assert presets.load_preset(str(tmp_path / "mine_02_01.py")).to_cli_args() == {
+        "model": "openai/gpt-4o-mini", "env": "calculator", "system_prompt": "v1 v2", "thinking": True, "temperature": 0.2}
+    assert type(latest.to_preset().environment(".")).__name__ == "CalculatorEnvironment"
+    with pytest.raises(TypeError):
+        presets.load_preset(str(tmp_path / "broken.py"))
+    with pytest.raises(KeyError):
+        presets.AgentPresetConfig("x", "m", "no-such-env", "p").to_preset()
+    from dataclasses import replace
+
+    replace(latest, working_dir=tmp_path).save(tmp_path / "saved.json")
+    again = presets.load_preset(str(tmp_path / "saved.json"))
+    assert again.working_dir == tmp_path and again.temperature == 0.2
