@@ -408,3 +408,59 @@ def test_preset_files_lineage_lookup_and_environments(tmp_path):
     replace(latest, working_dir=tmp_path).save(tmp_path / "saved.json")
     again = presets.load_preset(str(tmp_path / "saved.json"))
     assert again.working_dir == tmp_path and again.temperature == 0.2
+
+
+def test_tree_search_over_agent_states():
+    """Beam search and UCB search on the number-guessing environment with a policy that samples guesses: values are backed
+    up, the beam keeps the closest states, branches act on their own copies of the environment."""
+    import random
+
+    from research_b200.agents.search import (SearchTree, compose_pruners, make_beam_pruner, make_depth_pruner, make_expand_n_turns,
+                                             make_threshold_pruner, make_ucb_selector, run_tree_search, select_all_frontier, select_one_best,
+                                             select_one_deepest)
+
+    rng = random.Random(0)
+
+    async def policy(actor, run_config):
+        seen = [m.text() for m in actor.trajectory.messages if m.role == "tool"]
+        lo, hi = 0, 100
+        for m, t in zip([m for m in actor.trajectory.messages if m.role == "assistant"], seen):
+            g = m.tool_calls[0].args["number"]
+            lo, hi = (max(lo, g + 1), hi) if "higher" in t.lower() else (lo, min(hi, g - 1)) if "lower" in t.lower() else (g, g)
+        guess = rng.randint(lo, hi)
+        return await ScriptedLLM([Message("assistant", "", tool_calls=(ToolCall(f"g{len(seen)}", "guess", {"number": guess}),))])(actor, run_config)
+
+    register_provider("mock", policy)
+
+    async def value(state):
+        if state.stop == StopReason.TASK_COMPLETED:
+            return 1.0
+        guesses = [m.tool_calls[0].args["number"] for m in state.actor.trajectory.messages if m.role == "assistant" and m.tool_calls]
+        return -abs(guesses[-1] - 37) / 100 if guesses else -1.0
+
+    start = _state(BinarySearchEnvironment(target=37, max_guesses=50), max_turns=50)
+    tree = asyncio.run(run_tree_search(start, RunConfig(), select_all_frontier, make_expand_n_turns(1, branch_factor=3), value,
+                                       compose_pruners(make_beam_pruner(2), make_depth_pruner(12)), max_steps=12))
+    best = tree.best_terminal()
+    assert best is not None and best.value == 1.0 and best.state.stop == StopReason.TASK_COMPLETED
+    path = tree.path_to(best.node_id)
+    assert path[0].node_id == "0" and [n.depth for n in path] == list(range(len(path))) and best.node_id.startswith("0.")
+    assert any(n.pruned for n in tree.nodes.values()) and tree["0"].visits == len(tree.nodes) - 1
+    level1 = [tree[i] for i in tree["0"].children]
+    assert len(level1) == 3 and len({id(n.state.environment) for n in level1}) == 3 and start.environment.guesses == 0
+    # selectors and pruners on a hand-built tree
+    t = SearchTree("root")
+    a, b = t.add_child("0", "a", 0.2), t.add_child("0", "b", 0.8)
+    c = t.add_child(a.node_id, "c", 0.5)
+    t.frontier.remove("0")
+    assert select_one_best(t) == [b.node_id] and select_one_deepest(t) == [c.node_id] and t["0"].mean == pytest.approx(0.5)
+    ucb = make_ucb_selector(c=0.0)
+    assert ucb(t) == [b.node_id]                                        # no exploration: best mean
+    t[b.node_id].visits, t[b.node_id].total = 50, 50 * 0.8
+    assert make_ucb_selector(c=5.0)(t) != [b.node_id]                   # strong exploration: the rarely visited ones
+    make_threshold_pruner(0.4)(t)
+    assert t.frontier == [b.node_id, c.node_id] and t[a.node_id].pruned
+    # MCTS-style: one node per step, expanded nodes stay selectable
+    rng.seed(1)
+    tree = asyncio.run(run_tree_search(start, RunConfig(), make_ucb_selector(1.0), make_expand_n_turns(1, 1, keep_expanded=True), value, max_steps=60))
+    assert tree.best_node().value == 1.0 and len(tree["0"].children) >= 2
