@@ -15,8 +15,8 @@ import uuid
 from dataclasses import replace
 from typing import Any
 
-from .dtypes import (Actor, AgentState, Message, RunConfig, StopReason, StreamDone, ToolCall, ToolResult,
-                     ToolResultReceived, Trajectory)
+from .dtypes import (Actor, AgentState, Message, RunConfig, StopReason, StreamDone, StreamEvent, TextDelta, ThinkingDelta, ToolCall,
+                     ToolCallEnd, ToolConfirmResult, ToolResult, ToolResultReceived, Trajectory)
 
 
 # ------------------------------------------------------------------------------ stop handlers
@@ -42,6 +42,98 @@ def compose_stop_handlers(*handlers):
         return state
 
     return composed
+
+
+def inject_turn_warning(warning_at: int = 2, text: str | None = None):
+    """For ``RunConfig.on_step_start``: when exactly ``warning_at`` turns are left (of ``state.max_turns``), a user message
+    says so, once, so that the model wraps up instead of being cut off (rollouts/agents.py:167-205)."""
+    assert warning_at > 0
+
+    def handler(state: AgentState) -> AgentState:
+        if state.max_turns - state.turn_idx != warning_at or state.max_turns <= warning_at:
+            return state
+        note = Message("user", text or f"You have {warning_at} turn{'s' if warning_at != 1 else ''} left. Finish the task now and give your final answer.")
+        return replace(state, actor=replace(state.actor, trajectory=state.actor.trajectory.append(note)))
+
+    return handler
+
+
+def estimated_tokens(state: AgentState) -> int:
+    """Tokens this episode has used: the providers' own counts when they reported any, else a quarter of the characters
+    in the conversation."""
+    if state.usage.total_tokens:
+        return state.usage.total_tokens
+    return sum(len(m.text()) + sum(len(str(c.args)) for c in m.tool_calls) for m in state.actor.trajectory.messages) // 4
+
+
+def handle_stop_token_budget(max_tokens: int):
+    def handler(state: AgentState) -> AgentState:
+        return replace(state, stop=StopReason.BUDGET_EXCEEDED) if estimated_tokens(state) >= max_tokens else state
+
+    return handler
+
+
+def handle_stop_cost_budget(max_cost_usd: float, cost_fn=None):
+    """Stop once the episode's cost reaches the budget; the default cost is what the providers' usage records add up to."""
+    def handler(state: AgentState) -> AgentState:
+        cost = cost_fn(state) if cost_fn is not None else state.usage.cost.total
+        return replace(state, stop=StopReason.BUDGET_EXCEEDED) if cost >= max_cost_usd else state
+
+    return handler
+
+
+def make_tool_reminder(text: str = "Use the available tools to make progress on the task, or give your final answer.", max_reminders: int = 2):
+    """For ``RunConfig.handle_no_tool``: instead of ending the episode when the model answers without a tool call, remind
+    it, at most ``max_reminders`` times in a row; after that the episode ends as usual."""
+    async def handler(state: AgentState, run_config: RunConfig) -> AgentState:
+        msgs = state.actor.trajectory.messages
+        streak = 0
+        for m in reversed(msgs[:-1]):
+            if m.role == "user" and m.metadata.get("reminder"):
+                streak += 1
+            elif m.role in ("tool",) or (m.role == "user" and not m.metadata.get("reminder")):
+                break
+        if streak >= max_reminders:
+            return replace(state, stop=StopReason.NO_TOOL_CALLS)
+        note = Message("user", text, metadata={"reminder": True})
+        if run_config.session_store is not None and state.session_id:
+            await run_config.session_store.append_message(state.session_id, note)
+        return replace(state, actor=replace(state.actor, trajectory=state.actor.trajectory.append(note)))
+
+    return handler
+
+
+def make_confirm_with_feedback(ask, out=print):
+    """A ``RunConfig.confirm_tool`` for terminals: ``y`` runs the call, ``n`` refuses it and asks why (the reason reaches the
+    model as a user message after the refused result), anything else skips silently. ``ask(prompt) -> str`` may be a plain
+    or an async function."""
+    async def _ask(prompt: str) -> str:
+        r = ask(prompt)
+        return (await r) if asyncio.iscoroutine(r) else r
+
+    async def confirm(call: ToolCall, state: AgentState, run_config: RunConfig) -> ToolConfirmResult:
+        out(f"\nrun {call.name}({call.args})?\n  [y] yes   [n] no, and say why   [s] skip")
+        choice = (await _ask("choice: ")).strip().lower()
+        if choice == "y":
+            return ToolConfirmResult(True)
+        if choice == "n":
+            why = (await _ask("why not / what instead: ")).strip()
+            return ToolConfirmResult(False, ToolResult(call.id, is_error=True, error="rejected by the user"), why or None)
+        return ToolConfirmResult(False, ToolResult(call.id, is_error=True, error="skipped by the user"))
+
+    return confirm
+
+
+async def stdout_handler(event: StreamEvent) -> None:
+    """The plainest ``on_chunk``: text and thinking as they stream, one line per tool call and result."""
+    if isinstance(event, (TextDelta, ThinkingDelta)):
+        print(event.delta, end="", flush=True)
+    elif isinstance(event, ToolCallEnd):
+        print(f"\n[tool] {event.name}({event.args})", flush=True)
+    elif isinstance(event, ToolResultReceived):
+        print(f"[{'error' if event.is_error else 'result'}] {event.content[:500]}", flush=True)
+    elif isinstance(event, StreamDone):
+        print(flush=True)
 
 
 async def handle_no_tool_stop(state: AgentState, run_config: RunConfig) -> AgentState:
@@ -76,13 +168,17 @@ async def process_pending_tools(state: AgentState, run_config: RunConfig) -> Age
         if run_config.cancel_event is not None and run_config.cancel_event.is_set():
             return replace(state, actor=replace(state.actor, trajectory=traj), environment=env, next_tool_idx=i,
                            stop=StopReason.ABORTED)
-        ok = True
+        ok, feedback, refused = True, None, None
         if env is not None and env.requires_confirmation(call) and run_config.confirm_tool is not None:
-            ok = await run_config.confirm_tool(call, state, run_config)
+            answer = await run_config.confirm_tool(call, state, run_config)
+            if isinstance(answer, ToolConfirmResult):
+                ok, refused, feedback = answer.proceed, answer.tool_result, answer.user_message
+            else:
+                ok = bool(answer)
         if env is None:
             result = ToolResult(call.id, is_error=True, error=f"no environment to run tool {call.name!r}")
         elif not ok:
-            result = ToolResult(call.id, is_error=True, error="tool call rejected by the user")
+            result = refused or ToolResult(call.id, is_error=True, error="tool call rejected by the user")
         else:
             try:
                 snapshot = await env.serialize()
@@ -104,6 +200,16 @@ async def process_pending_tools(state: AgentState, run_config: RunConfig) -> Age
                                                          details=dict(result.metadata)))
         if run_config.session_store is not None and state.session_id:
             await run_config.session_store.append_message(state.session_id, traj.messages[-1])
+        if feedback:
+            # the user said why not: every remaining call of this turn gets its (refused) result first, so that the
+            # conversation stays well-formed, then the guidance follows as a user message
+            for rest in state.pending_tool_calls[i + 1:]:
+                traj = traj.append(Message("tool", "Error: not run (the user interrupted this turn)", tool_call_id=rest.id, name=rest.name))
+            traj = traj.append(Message("user", feedback))
+            if run_config.session_store is not None and state.session_id:
+                for m in traj.messages[-(len(state.pending_tool_calls) - i):]:
+                    await run_config.session_store.append_message(state.session_id, m)
+            return replace(state, actor=replace(state.actor, trajectory=traj), environment=env, pending_tool_calls=(), next_tool_idx=0)
         if result.stop_reason is not None:
             return replace(state, actor=replace(state.actor, trajectory=traj), environment=env,
                            pending_tool_calls=(), next_tool_idx=0, stop=result.stop_reason)
@@ -121,6 +227,8 @@ async def run_agent_step(state: AgentState, run_config: RunConfig) -> AgentState
     state = stop_handler(state)
     if state.stop is not None:
         return state
+    if run_config.on_step_start is not None:
+        state = run_config.on_step_start(state)
     tools = tuple(state.environment.get_tools()) if state.environment is not None else ()
     actor = await rollout(replace(state.actor, tools=tools), run_config)
     last = actor.trajectory.messages[-1]

@@ -337,6 +337,7 @@ class StopReason(Enum):
     ERROR = "error"
     LENGTH = "length"
     USER_ABORT = "user_abort"
+    BUDGET_EXCEEDED = "budget_exceeded"
 
 
 @dataclass(frozen=True)
@@ -347,6 +348,15 @@ class ToolResult:
     error: str | None = None
     stop_reason: StopReason | None = None
     metadata: dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class ToolConfirmResult:
+    """What a confirmation callback may return instead of a bare bool: whether to run the call, the result to record when
+    it does not run, and a message from the user that follows the result (guidance on what to do instead)."""
+    proceed: bool
+    tool_result: ToolResult | None = None
+    user_message: str | None = None
 
 
 @runtime_checkable
@@ -407,7 +417,8 @@ class AgentState:
 class RunConfig:
     on_chunk: Callable[[StreamEvent], Awaitable[None]] | None = None
     on_input: Callable[[str], Awaitable[str]] | None = None
-    confirm_tool: Callable[[ToolCall, AgentState, "RunConfig"], Awaitable[bool]] | None = None
+    confirm_tool: Callable[[ToolCall, AgentState, "RunConfig"], Awaitable["bool | ToolConfirmResult"]] | None = None
+    on_step_start: Callable[[AgentState], AgentState] | None = None      # before each model call (e.g. a turns-left warning)
     handle_stop: Callable[[AgentState], AgentState] | None = None
     handle_no_tool: Callable[[AgentState, "RunConfig"], Awaitable[AgentState]] | None = None
     use_tito: bool = False

@@ -79,12 +79,70 @@ class FileSessionStore:
         s.updated_at = time.time()
         self._write_meta(s)
 
-    async def list(self) -> list[AgentSession]:
+    async def list(self, filter_tags: dict[str, Any] | None = None, status: str | None = None, limit: int | None = None) -> list[AgentSession]:
+        """Sessions, oldest first (ids start with their creation time); optionally only those whose tags contain
+        ``filter_tags`` and / or with ``status``; ``limit`` keeps the NEWEST ones. Unreadable folders are skipped."""
         out = []
         for d in sorted(self.root.iterdir()):
-            if (d / "session.json").exists():
-                out.append(self._read_meta(d.name))
-        return out
+            if not (d / "session.json").exists():
+                continue
+            try:
+                s = self._read_meta(d.name)
+            except (ValueError, TypeError, OSError):
+                continue
+            if status is not None and s.status != status:
+                continue
+            if filter_tags and any(s.tags.get(k) != v for k, v in filter_tags.items()):
+                continue
+            out.append(s)
+        return out[-limit:] if limit else out
+
+    async def list_children(self, parent_id: str) -> list[AgentSession]:
+        return [s for s in await self.list() if s.parent_id == parent_id]
+
+    async def lineage(self, session_id: str) -> list[AgentSession]:
+        """The session and its ancestors, root first (follows ``parent_id``; a missing ancestor ends the walk)."""
+        out, seen = [], set()
+        at: str | None = session_id
+        while at and at not in seen and (self._dir(at) / "session.json").exists():
+            seen.add(at)
+            s = self._read_meta(at)
+            out.append(s)
+            at = s.parent_id
+        return out[::-1]
+
+    async def get_latest(self, filter_tags: dict[str, Any] | None = None, status: str | None = None) -> AgentSession | None:
+        """The most recently UPDATED session that matches."""
+        return max(await self.list(filter_tags, status), key=lambda s: s.updated_at, default=None)
+
+    def get_latest_id_sync(self) -> str | None:
+        """For code that is not in an event loop (argument parsing): the id of the most recently updated session."""
+        best, best_t = None, -1.0
+        for d in self.root.iterdir():
+            f = d / "session.json"
+            if f.exists() and f.stat().st_mtime > best_t:
+                best, best_t = d.name, f.stat().st_mtime
+        return best
+
+    def get_config_sync(self, session_id: str) -> dict[str, Any] | None:
+        """Endpoint, environment and tags a session was created with (None if there is no such session)."""
+        try:
+            s = self._read_meta(session_id)
+        except (OSError, ValueError, TypeError):
+            return None
+        return {"endpoint": s.endpoint, "environment": s.environment, "tags": s.tags, "parent_id": s.parent_id}
+
+    async def delete(self, session_id: str) -> bool:
+        """Remove one session's folder (its two files, then the folder). Children keep their ``parent_id``; False if
+        there was no such session."""
+        d = self._dir(session_id)
+        if not (d / "session.json").exists() or d.parent != self.root:
+            return False
+        for f in d.iterdir():
+            if f.is_file():
+                f.unlink()
+        d.rmdir()
+        return True
 
     async def branch(self, session_id: str, at_message: int) -> str:
         """New session that shares the first ``at_message`` messages of ``session_id``."""

@@ -2,6 +2,7 @@
 
 import asyncio
 import json
+from dataclasses import replace
 
 import pytest
 
@@ -464,3 +465,68 @@ def test_tree_search_over_agent_states():
     rng.seed(1)
     tree = asyncio.run(run_tree_search(start, RunConfig(), make_ucb_selector(1.0), make_expand_n_turns(1, 1, keep_expanded=True), value, max_steps=60))
     assert tree.best_node().value == 1.0 and len(tree["0"].children) >= 2
+
+
+def test_step_hooks_budgets_reminders_and_confirmation_feedback(tmp_path):
+    from research_b200.agents.agents import (estimated_tokens, handle_stop_cost_budget, handle_stop_token_budget, inject_turn_warning,
+                                             make_confirm_with_feedback, make_tool_reminder)
+    from research_b200.agents.dtypes import Cost, Usage
+
+    add = lambda i: Message("assistant", "", tool_calls=(ToolCall(f"c{i}", "add", {"value": 1}),))                 # noqa: E731
+    # a warning when two turns are left, exactly once
+    register_provider("mock", ScriptedLLM([add(i) for i in range(6)]))
+    final = asyncio.run(run_agent(_state(CalculatorEnvironment(), max_turns=4), RunConfig(on_step_start=inject_turn_warning(2))))[-1]
+    warns = [i for i, m in enumerate(final.actor.trajectory.messages) if m.role == "user" and "2 turns left" in m.text()]
+    assert final.stop == StopReason.MAX_TURNS and len(warns) == 1 and final.turn_idx == 4
+    # budgets
+    st = _state(CalculatorEnvironment())
+    assert estimated_tokens(st) == sum(len(m.text()) for m in st.actor.trajectory.messages) // 4
+    assert handle_stop_token_budget(10**6)(st).stop is None and handle_stop_token_budget(1)(replace(st, usage=Usage(5, 5))).stop == StopReason.BUDGET_EXCEEDED
+    assert handle_stop_cost_budget(0.5)(replace(st, usage=Usage(cost=Cost(0.3, 0.3)))).stop == StopReason.BUDGET_EXCEEDED
+    assert handle_stop_cost_budget(0.5, lambda s: 0.1)(st).stop is None
+    # reminders: two in a row, then the episode ends
+    register_provider("mock", ScriptedLLM(["thinking...", "still thinking...", "hmm", "never reached"]))
+    final = asyncio.run(run_agent(_state(CalculatorEnvironment(), max_turns=10), RunConfig(handle_no_tool=make_tool_reminder(max_reminders=2))))[-1]
+    assert final.stop == StopReason.NO_TOOL_CALLS and final.turn_idx == 3
+    assert sum(1 for m in final.actor.trajectory.messages if m.metadata.get("reminder")) == 2
+    # refusing a call with a reason: refused result, the turn's other call marked not run, then the reason as a user message
+    fs = LocalFilesystemEnvironment(str(tmp_path))
+    two = Message("assistant", "", tool_calls=(ToolCall("b1", "bash", {"command": "rm -rf build"}), ToolCall("b2", "bash", {"command": "echo hi"})))
+    register_provider("mock", ScriptedLLM([two, "understood"]))
+    answers = iter(["n", "do not delete build, list it first"])
+    said = []
+    rc = RunConfig(confirm_tool=make_confirm_with_feedback(lambda prompt: next(answers), said.append))
+    final = asyncio.run(run_agent(_state(fs, max_turns=5), rc))[-1]
+    roles = [(m.role, m.text()[:40]) for m in final.actor.trajectory.messages[-4:]]
+    assert roles[0] == ("tool", "Error: rejected by the user") and roles[1][1].startswith("Error: not run") and roles[2] == ("user", "do not delete build, list it first")
+    assert roles[3] == ("assistant", "understood") and "rm -rf build" in said[0]
+    answers = iter(["s", "y"])
+    register_provider("mock", ScriptedLLM([two, "done"]))
+    final = asyncio.run(run_agent(_state(fs, max_turns=5), replace(rc, confirm_tool=make_confirm_with_feedback(lambda p: next(answers), said.append))))[-1]
+    tools = [m.text() for m in final.actor.trajectory.messages if m.role == "tool"]
+    assert tools[0] == "Error: skipped by the user" and tools[1].strip() == "hi"
+
+
+def test_session_store_queries_lineage_and_delete(tmp_path):
+    store = FileSessionStore(tmp_path)
+
+    async def go():
+        a = await store.create({"provider": "p", "model": "m"}, tags={"preset": "coding", "run": 1})
+        await store.append_message(a, Message("user", "one"))
+        await store.append_message(a, Message("assistant", "two"))
+        b = await store.branch(a, 1)
+        c = await store.branch(b, 1)
+        d = await store.create({"provider": "p", "model": "m2"}, tags={"preset": "chat"})
+        await store.update(d, status="aborted")
+        assert [s.session_id for s in await store.list_children(a)] == [b] and [s.session_id for s in await store.lineage(c)] == [a, b, c]
+        assert [s.session_id for s in await store.list(filter_tags={"preset": "coding"})] == [a]
+        assert [s.session_id for s in await store.list(status="aborted")] == [d] and len(await store.list(limit=2)) == 2
+        assert (await store.get_latest()).session_id == d and (await store.get_latest(status="active")).session_id == c
+        assert store.get_latest_id_sync() == d and store.get_config_sync(a)["tags"]["run"] == 1 and store.get_config_sync("nope") is None
+        (tmp_path / "junk").mkdir()
+        (tmp_path / "junk" / "session.json").write_text("{not json")
+        assert len(await store.list()) == 4
+        assert await store.delete(b) and not await store.delete(b) and not (tmp_path / b).exists()
+        assert [s.session_id for s in await store.lineage(c)] == [c] and (await store.get(c))[0].parent_id == b
+
+    asyncio.run(go())
