@@ -99,9 +99,83 @@ def build_native_command(config: ServerConfig) -> str:
     return " ".join(parts)
 
 
+SGLANG_VENV = ".venv-sglang"
+
+
+def generate_bootstrap_command(config: ServerConfig, workdir: str = ".") -> str:
+    """What a fresh machine runs once before the launch command (rollouts/deploy.py:124-162). For an external SGLang
+    server: an isolated virtual environment that the launch command then uses (created once, reused afterwards). For the
+    native engine: build the in-tree CUDA extensions of the checkout in ``workdir`` (a no-op when they are current)."""
+    q = shlex.quote(workdir)
+    if config.engine == "sglang":
+        steps = ['export PATH="$HOME/.local/bin:$PATH"',
+                 f'([ -d {SGLANG_VENV} ] && echo "using existing {SGLANG_VENV}") || uv venv {SGLANG_VENV} --python 3.10',
+                 f". {SGLANG_VENV}/bin/activate",
+                 'uv pip install "sglang[all]" --index-strategy unsafe-best-match',
+                 "uv pip show sglang | grep -i '^version' || true"]
+    else:
+        steps = [f"cd {q}", f"{shlex.quote(sys.executable)} -m research_b200.cli build",
+                 f"{shlex.quote(sys.executable)} -c 'import research_b200; print(\"research_b200 importable\")'"]
+    return " && ".join(steps)
+
+
+HttpGet = Callable[[str, dict[str, str]], int]          # url, headers -> HTTP status (raises OSError when unreachable)
+
+
+def _urllib_status(url: str, headers: dict[str, str]) -> int:
+    import urllib.error
+
+    try:
+        with urllib.request.urlopen(urllib.request.Request(url, headers=headers), timeout=10) as r:  # noqa: S310
+            return r.status
+    except urllib.error.HTTPError as e:
+        return e.code
+
+
+def check_model_access(model: str, env: dict[str, str] | None = None, get: HttpGet = _urllib_status) -> tuple[bool, str | None]:
+    """Before a deployment that downloads a gated checkpoint: is ``HF_TOKEN`` set, is ``model`` an ``org/name`` id, and does
+    the hub let this token see it (rollouts/deploy.py:165-233)? A local directory or a built-in preset needs no token. A
+    hub that cannot be reached is a warning, not a refusal: ``(True, "could not verify ...")``."""
+    import os
+
+    if Path(model).exists():
+        return True, None
+    try:
+        from .models.config import get_preset
+
+        get_preset(model)
+        return True, None
+    except (KeyError, AssertionError, ValueError):
+        pass
+    token = (os.environ if env is None else env).get("HF_TOKEN", "")
+    if not token:
+        return False, "HF_TOKEN is not set: export HF_TOKEN=hf_... (needed to download the checkpoint)"
+    if "/" not in model:
+        return False, f"{model!r} is neither a local directory, a built-in preset, nor an 'org/name' model id"
+    try:
+        status = get(f"https://huggingface.co/api/models/{model}", {"Authorization": f"Bearer {token}"})
+    except OSError as e:
+        return True, f"could not verify access to {model}: {e}"
+    if status == 200:
+        return True, None
+    return False, {401: "HF_TOKEN is invalid or expired: create a new one at https://huggingface.co/settings/tokens",
+                   403: f"access to {model} is denied: accept the model's licence on its hub page with this account",
+                   404: f"model not found: {model} (check the name, and that this account may see it)"}.get(
+                       status, f"the hub answered HTTP {status} for {model}")
+
+
+def server_info_to_endpoint(info: ServerInfo, model: str, engine: str = "native", **kw):
+    """The ``Endpoint`` agents use to talk to a launched server (OpenAI-compatible routes under ``/v1``)."""
+    from .agents.dtypes import Endpoint
+
+    return Endpoint(provider="sglang" if engine == "sglang" else "openai", model=model, api_base=info.url, **kw)
+
+
 def build_command(config: ServerConfig) -> str:
     env = f"CUDA_VISIBLE_DEVICES={','.join(map(str, config.gpu_ranks))} "
-    return env + (build_sglang_command(config) if config.engine == "sglang" else build_native_command(config))
+    if config.engine == "sglang":
+        return f"([ -d {SGLANG_VENV} ] && . {SGLANG_VENV}/bin/activate); {env}" + build_sglang_command(config)
+    return env + build_native_command(config)
 
 
 def local_runner(cmd: str) -> tuple[int, str]:
@@ -186,6 +260,9 @@ def deploy_server(config: ServerConfig, wait: bool = True, timeout: float = 600.
         proc = subprocess.Popen(cmd, shell=True, stdout=logf, stderr=subprocess.STDOUT, start_new_session=True)
         pid, alive = proc.pid, (lambda: proc.poll() is None)
     if wait and not wait_until_healthy(config.url, timeout, alive):
-        tail = log_path.read_text()[-2000:] if log_path.exists() else ""
+        if config.ssh_connection:
+            tail = ssh_runner(config.ssh_connection)(f"tail -c 2000 {shlex.quote(str(log_path))}")[1]
+        else:
+            tail = log_path.read_text()[-2000:] if log_path.exists() else ""
         raise RuntimeError(f"server did not become healthy at {config.url}\n--- log tail ---\n{tail}")
     return ServerInfo(config.url, pid, str(log_path), cmd)

@@ -21,7 +21,8 @@ def test_server_commands():
                      attention_backend="triton")
     cmd = build_sglang_command(c)
     assert "--tp 2" in cmd and "--context-length 4096" in cmd and "--enable-radix-cache" in cmd and "--attention-backend triton" in cmd
-    assert build_command(c).startswith("CUDA_VISIBLE_DEVICES=2,3 ")
+    assert "; CUDA_VISIBLE_DEVICES=2,3 python -m sglang.launch_server" in build_command(c)
+    assert build_command(ServerConfig(gpu_ranks=[1])).startswith("CUDA_VISIBLE_DEVICES=1 ")
     n = build_native_command(ServerConfig(model="llama-3-8b", gpu_ranks=[0, 1], tensor_parallel_size=2, port=31000))
     assert "torch.distributed.run" in n and "--nproc-per-node 2" in n and "--master-addr 127.0.0.1" in n and "--tp 2" in n
     assert "research_b200.cli serve" in build_native_command(ServerConfig())
@@ -167,3 +168,35 @@ def test_session_doctor_and_chat_flags(tmp_path, capsys):
     assert len(after) == 1 and after[0].num_messages > first[0].num_messages
     assert cli.main(["chat", "--provider", "cli-mock", "--store", str(tmp_path / "s3"), "-p", "hi", "--no-session"]) == 0
     assert not (tmp_path / "s3").exists() or not list((tmp_path / "s3").iterdir())
+
+
+def test_bootstrap_model_access_and_endpoint(tmp_path):
+    from research_b200.deploy import ServerInfo, check_model_access, generate_bootstrap_command, server_info_to_endpoint
+
+    sg = generate_bootstrap_command(ServerConfig(engine="sglang"))
+    assert "uv venv .venv-sglang" in sg and "sglang[all]" in sg and sg.index("uv venv") < sg.index("uv pip install")
+    native = generate_bootstrap_command(ServerConfig(), workdir="/srv/my checkout")
+    assert native.startswith("cd '/srv/my checkout' && ") and "research_b200.cli build" in native
+    assert ".venv-sglang/bin/activate" in build_command(ServerConfig(engine="sglang")) and ".venv-sglang" not in build_command(ServerConfig())
+    seen = []
+
+    def hub(status):
+        def get(url, headers):
+            seen.append((url, headers))
+            if status is None:
+                raise OSError("no route to host")
+            return status
+        return get
+
+    assert check_model_access(str(tmp_path)) == (True, None) and check_model_access("qwen2.5-0.5b") == (True, None)       # local dir, preset
+    assert "HF_TOKEN is not set" in check_model_access("org/model", env={})[1]
+    assert "neither" in check_model_access("just-a-name", env={"HF_TOKEN": "t"})[1]
+    assert check_model_access("org/model", env={"HF_TOKEN": "tok"}, get=hub(200)) == (True, None)
+    assert seen[0] == ("https://huggingface.co/api/models/org/model", {"Authorization": "Bearer tok"})
+    for status, word in ((401, "invalid or expired"), (403, "licence"), (404, "not found"), (500, "HTTP 500")):
+        ok, why = check_model_access("org/model", env={"HF_TOKEN": "tok"}, get=hub(status))
+        assert not ok and word in why
+    ok, why = check_model_access("org/model", env={"HF_TOKEN": "tok"}, get=hub(None))
+    assert ok and "could not verify" in why
+    ep = server_info_to_endpoint(ServerInfo("http://10.0.0.5:30000", 1, "log", "cmd"), "org/model", engine="sglang", temperature=0.2)
+    assert (ep.provider, ep.api_base, ep.model, ep.temperature) == ("sglang", "http://10.0.0.5:30000", "org/model", 0.2)
