@@ -205,7 +205,7 @@ async def _chat(args) -> int:
                 "preset": preset.name}
     runner = InteractiveRunner(ep, frontend, environment=env, system_prompt=system_prompt, session_store=store,
                                session_id=session_id, max_turns=preset.max_turns, initial_prompt=args.prompt,
-                               single_turn=args.prompt is not None, trajectory=trajectory, session_tags=tags)
+                               single_turn=args.prompt is not None, trajectory=trajectory, session_tags=tags, cwd=args.cwd)
     state = await runner.run()
     if state.session_id and not args.quiet:
         print(f"session: {state.session_id}", file=sys.stderr)

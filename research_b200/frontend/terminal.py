@@ -365,10 +365,13 @@ HELP = """/help               this text
 /clear              start a new conversation (keeps the system prompt)
 /model NAME         switch the model of the endpoint
 /temperature X      sampling temperature
-/thinking on|off    show or hide reasoning text
+/thinking [on|off|N] extended thinking (N = token budget) and whether it is shown
 /status             session, turns, token counts
 /save PATH          write the conversation as JSON lines
-/retry              drop the last assistant turn and ask again"""
+/retry              drop the last assistant turn and ask again
+/slice SPEC         continue on a sliced copy (0:4, summarize:4:20, 20:)
+/env [NAME]         show or switch the environment (the agent's tools)
+/commands           every command, including those from .research_b200/commands/*.md"""
 
 
 class InteractiveRunner:
@@ -377,9 +380,13 @@ class InteractiveRunner:
     def __init__(self, endpoint: Endpoint, frontend: Frontend, environment: Any = None, system_prompt: str | None = None,
                  session_store: Any = None, session_id: str | None = None, max_turns: int = 20,
                  initial_prompt: str | None = None, single_turn: bool = False, trajectory: Trajectory | None = None,
-                 session_tags: dict[str, Any] | None = None):
+                 session_tags: dict[str, Any] | None = None, cwd: str = ".", file_commands: list | None = None):
+        from .slash_commands import load_file_commands
+
         self.endpoint, self.frontend, self.environment = endpoint, frontend, environment
         self.session_tags = session_tags
+        self.cwd = cwd
+        self.file_commands = load_file_commands(cwd) if file_commands is None else file_commands
         if hasattr(frontend, "environment"):
             frontend.environment = environment
         self.system_prompt = system_prompt
@@ -390,7 +397,8 @@ class InteractiveRunner:
         self.turns = 0
         self.commands: dict[str, Callable[[str], Any]] = {
             "help": self._cmd_help, "clear": self._cmd_clear, "model": self._cmd_model, "temperature": self._cmd_temperature,
-            "thinking": self._cmd_thinking, "status": self._cmd_status, "save": self._cmd_save, "retry": self._cmd_retry}
+            "thinking": self._cmd_thinking, "status": self._cmd_status, "save": self._cmd_save, "retry": self._cmd_retry,
+            "slice": self._cmd_slice, "env": self._cmd_env, "commands": self._cmd_commands}
 
     # ---- slash commands: return text to print; "retry" returns a prompt to resend
     def _cmd_help(self, arg: str) -> str:
@@ -418,11 +426,37 @@ class InteractiveRunner:
         self.state = replace(self.state, actor=replace(self.state.actor, endpoint=self.endpoint))
         return f"temperature set to {t}"
 
-    def _cmd_thinking(self, arg: str) -> str:
-        on = arg.strip().lower() in ("on", "1", "true", "yes", "")
-        if hasattr(self.frontend, "show_thinking"):
-            self.frontend.show_thinking = on
-        return f"thinking {'shown' if on else 'hidden'}"
+    def set_endpoint(self, endpoint: Endpoint) -> None:
+        self.endpoint = endpoint
+        self.state = replace(self.state, actor=replace(self.state.actor, endpoint=endpoint))
+
+    def set_environment(self, environment: Any) -> None:
+        self.environment = environment
+        self.state = replace(self.state, environment=environment)
+        if hasattr(self.frontend, "environment"):
+            self.frontend.environment = environment
+
+    def _cmd_thinking(self, arg: str):
+        from .slash_commands import handle_thinking
+
+        return handle_thinking(self, arg)
+
+    def _cmd_slice(self, arg: str):
+        from .slash_commands import handle_slice
+
+        return handle_slice(self, arg)
+
+    def _cmd_env(self, arg: str):
+        from .slash_commands import handle_env
+
+        return handle_env(self, arg)
+
+    def _cmd_commands(self, arg: str) -> str:
+        from .slash_commands import BUILTIN_COMMANDS
+
+        rows = [(f"/{c.name}" + (f" {c.arg_hint}" if c.arg_hint else ""), c.description, c.source) for c in BUILTIN_COMMANDS + self.file_commands]
+        w = max(len(r[0]) for r in rows)
+        return "\n".join(f"{r[0]:<{w}}  {r[1]}" + (f"  {r[2]}" if r[2] != "(builtin)" else "") for r in rows)
 
     def _cmd_status(self, arg: str) -> str:
         u = self.state.usage
@@ -505,8 +539,30 @@ class InteractiveRunner:
                     name, _, arg = text[1:].partition(" ")
                     if name in ("quit", "exit", "q"):
                         break
+                    from .slash_commands import SlashCommandResult, expand_file_command, find_similar_command
+
                     fn = self.commands.get(name)
-                    res = fn(arg.strip()) if fn else f"unknown command /{name} (try /help)"
+                    if fn is None:
+                        expanded = expand_file_command(text, self.file_commands)
+                        if expanded is not None:          # a command from a file is a prompt: it goes to the model
+                            await self._one_exchange(expanded)
+                            if self.single_turn:
+                                break
+                            continue
+                        near = find_similar_command(name, sorted(self.commands) + [c.name for c in self.file_commands])
+                        res = f"unknown command /{name}" + (f" (did you mean /{near}?)" if near else "") + " (try /commands)"
+                    else:
+                        res = fn(arg.strip())
+                        if asyncio.iscoroutine(res):
+                            res = await res
+                    if isinstance(res, SlashCommandResult):
+                        if res.persist and self.store is not None and self.state.session_id:
+                            session, _ = await self.store.get(self.state.session_id)
+                            await self.store.update(self.state.session_id, tags={**session.tags, **res.persist})
+                        if res.expanded_text:
+                            pending = res.expanded_text
+                            continue
+                        res = res.message or ""
                     if isinstance(res, tuple) and res[0] == "retry":
                         pending = res[1]
                     else:

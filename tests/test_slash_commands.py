@@ -1,0 +1,78 @@
+"""Slash commands of the interactive chat: file commands with arguments, thinking budgets, slicing, environment switch."""
+
+import asyncio
+import io
+
+from research_b200.agents.dtypes import Endpoint, Message
+from research_b200.agents.providers import ScriptedLLM, register_provider
+from research_b200.agents.store import FileSessionStore
+from research_b200.frontend import slash_commands as sc
+from research_b200.frontend.terminal import InteractiveRunner, PlainFrontend
+
+
+def test_file_commands_front_matter_arguments_and_precedence(tmp_path):
+    home, proj = tmp_path / "home", tmp_path / "proj"
+    (home / ".research_b200" / "commands" / "git").mkdir(parents=True)
+    (proj / ".research_b200" / "commands").mkdir(parents=True)
+    (home / ".research_b200" / "commands" / "review.md").write_text("---\ndescription: Review a file\nargument-hint: <file> [focus]\n---\nReview $1 with a focus on $2.\nAll: $@\n")
+    (home / ".research_b200" / "commands" / "git" / "pr.md").write_text("# Describe the pull request\nSummarise the diff of $ARGUMENTS.\n")
+    (proj / ".research_b200" / "commands" / "review.md").write_text("Project review of $1 ($3).\n")
+    cmds = sc.load_file_commands(proj, home)
+    by = {c.name: c for c in cmds}
+    assert set(by) == {"review", "git:pr"} and by["review"].source == "(project)" and by["git:pr"].description == "Describe the pull request"
+    user_only = {c.name: c for c in sc.load_file_commands(tmp_path / "elsewhere", home)}
+    assert user_only["review"].arg_hint == "<file> [focus]" and user_only["review"].description == "Review a file"
+    assert sc.expand_file_command('/review "my file.py" errors', list(user_only.values())) == "Review my file.py with a focus on errors.\nAll: my file.py errors"
+    assert sc.expand_file_command("/review a.py", cmds) == "Project review of a.py ()." and sc.expand_file_command("/nope x", cmds) is None
+    assert sc.parse_command_args("""a 'b c' "" d""") == ["a", "b c", "", "d"] and sc.parse_frontmatter("no front matter") == ({}, "no front matter")
+    assert sc.find_similar_command("modle", ["model", "env"]) == "model" and sc.find_similar_command("th", ["thinking"]) == "thinking"
+    assert sc.get_command_arg_hint("slice", sc.BUILTIN_COMMANDS).startswith("[0:5")
+
+
+def test_runner_commands_thinking_slice_env_and_file_prompt(tmp_path):
+    store = FileSessionStore(tmp_path / "sessions")
+    seen = []
+
+    async def model(actor, run_config):
+        seen.append(actor)
+        return await ScriptedLLM([f"reply {len(seen)}"])(actor, run_config)
+
+    register_provider("slash-mock", model)
+    lines = iter(["first question", "second question", "/thinking", "/thinking 8000", "/thinking off", "/thinking 12", "/slice", "/slice 0:1, summarize:1:4",
+                  "/env calculator", "/env", "/env nope", "/modle x", "/explain the scheduler", "/commands", "/quit"])
+    out = io.StringIO()
+
+    class Scripted(PlainFrontend):
+        async def get_input(self, prompt=""):
+            return next(lines)
+
+    fe = Scripted(out=out)
+    cmds = [sc.SlashCommand("explain", "explain something", "<what>", "Explain $@ in two sentences.", "(project)")]
+    runner = InteractiveRunner(Endpoint(provider="slash-mock", model="m"), fe, system_prompt="be brief", session_store=store, cwd=str(tmp_path),
+                               file_commands=cmds)
+    state = asyncio.run(runner.run())
+    text = out.getvalue()
+    assert "thinking: off" in text and "thinking on, budget 8000 tokens" in text and "thinking off" in text and "usage: /thinking" in text
+    assert "5 messages. usage: /slice" in text and "5 -> 2 messages; now in session" in text
+    assert "environment: calculator (tools: add" in text and "unknown environment 'nope'" in text and "did you mean /model?" in text
+    assert "explain something  (project)" in text and "/explain <what> " in text and "/slice [0:5" in text
+    # the file command reached the model as a user message, on the sliced conversation, with the calculator's tools
+    last = seen[-1]
+    assert last.trajectory.messages[-1].text() == "Explain the scheduler in two sentences." and "add" in [t.function.name for t in last.tools]
+    assert [m.role for m in last.trajectory.messages] == ["system", "user", "user"] and "[Summary of messages 1-3]" in last.trajectory.messages[1].text()
+    assert state.actor.trajectory.messages[-1].text() == "reply 3"
+    # the slice made a child session that records its origin; the thinking choice and the environment were stored as tags
+
+    async def check():
+        sessions = await store.list()
+        child = next(s for s in sessions if s.parent_id)
+        assert child.tags["slice"] == "0:1, summarize:1:4" and child.tags["env"] == "calculator" and child.branch_point == 5
+        parent = next(s for s in sessions if s.session_id == child.parent_id)
+        assert parent.tags["thinking"] == "off"
+        assert [m.text() for m in (await store.get(child.session_id))[1]][-2:] == ["Explain the scheduler in two sentences.", "reply 3"]
+
+    asyncio.run(check())
+    ep = runner.endpoint
+    assert "thinking" not in ep.extra_params and ep.reasoning_effort is None
+    sc.handle_thinking(runner, "20000")
+    assert sc.thinking_budget(runner.endpoint) == 20000 and runner.endpoint.reasoning_effort == "high" and runner.endpoint.max_tokens >= 21024
