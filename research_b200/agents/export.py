@@ -86,6 +86,12 @@ def session_to_html(session: AgentSession, messages: list[Message]) -> str:
 async def export_session(store, session_id: str, fmt: str = "md", path: str | None = None) -> str:
     session, messages = await store.get(session_id)
     text = session_to_html(session, messages) if fmt == "html" else session_to_markdown(session, messages)
+    if fmt == "ansi":                          # the Markdown export rendered for a terminal
+        import shutil
+
+        from ..frontend.widgets import render_markdown
+
+        text = "\n".join(render_markdown(text, min(shutil.get_terminal_size((100, 24)).columns, 120)))
     if path:
         with open(path, "w") as f:
             f.write(text)

@@ -389,7 +389,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--fix", action="store_true", help="doctor: write a child session without duplicate / orphaned tool results")
     p.add_argument("--trim", type=int, default=0, help="doctor: write a child session without the last N messages")
     p.add_argument("--goal", default="", help="handoff: what the next session should do")
-    p.add_argument("--spec", default=""); p.add_argument("--format", default="md", choices=["md", "html"])
+    p.add_argument("--spec", default=""); p.add_argument("--format", default="md", choices=["md", "html", "ansi"])
     p.add_argument("--output", default=""); p.add_argument("--store", default=""); p.add_argument("--limit", type=int, default=20)
     p.set_defaults(fn=cmd_sessions)
     p = sub.add_parser("eval")

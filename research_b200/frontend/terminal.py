@@ -243,6 +243,8 @@ class AnsiFrontend(PlainFrontend):
         self.width = width or shutil.get_terminal_size((100, 24)).columns
         self.max_result_lines = max_result_lines
         self._fence = FenceHighlighter()
+        self._editor = None                  # the prompt's line editor, created on first use at a terminal
+        self.completer = None                # set by the runner: slash commands and paths
         self._loader_task: asyncio.Task | None = None
         self._loader_text = ""
         self._mode = ""           # "", "text", "thinking"
@@ -343,8 +345,23 @@ class AnsiFrontend(PlainFrontend):
     async def get_input(self, prompt: str = "") -> str:
         self._enter("")
         self._w(self.status_line() + "\n")
+        if self._is_tty():
+            # a real terminal: the line editor (history, word motions, multi-line, completion) in raw mode
+            from .widgets import LineEditor, read_line_raw
+
+            if self._editor is None:
+                self._editor = LineEditor(completer=self.completer)
+            self._editor.completer = self.completer
+            return await asyncio.to_thread(read_line_raw, self._editor, f"{Theme.USER}{Theme.BOLD}{prompt or '> '}{Theme.RESET}",
+                                           self.inp.fileno(), self._w, self.width)
         self._w(f"{Theme.USER}{Theme.BOLD}{prompt or '> '}{Theme.RESET}")
         return await _readline(self.inp)
+
+    def _is_tty(self) -> bool:
+        try:
+            return bool(self.inp.isatty() and self.out.isatty()) and self.inp.fileno() >= 0
+        except (AttributeError, ValueError, OSError):
+            return False
 
     async def confirm_tool(self, tool_call: ToolCall) -> bool:
         if self.auto_confirm:
@@ -389,6 +406,12 @@ class InteractiveRunner:
         self.file_commands = load_file_commands(cwd) if file_commands is None else file_commands
         if hasattr(frontend, "environment"):
             frontend.environment = environment
+        if hasattr(frontend, "completer"):
+            from .slash_commands import BUILTIN_COMMANDS
+            from .widgets import make_completer
+
+            every = BUILTIN_COMMANDS + self.file_commands
+            frontend.completer = make_completer([c.name for c in every], cwd, {c.name: c.arg_hint for c in every if c.arg_hint})
         self.system_prompt = system_prompt
         self.store, self.session_id = session_store, session_id
         self.max_turns, self.initial_prompt, self.single_turn = max_turns, initial_prompt, single_turn
