@@ -349,12 +349,25 @@ async def rollout_anthropic(actor: Actor, run_config: RunConfig) -> Actor:
     headers = {"anthropic-version": "2023-06-01", **extra.pop("request_headers", {})}
     payload: dict[str, Any] = {"model": ep.model, "max_tokens": ep.max_tokens, "messages": msgs, "stream": True,
                                "temperature": ep.temperature, **extra}
+    if isinstance(payload.get("thinking"), dict) and payload["thinking"].get("type") == "enabled":
+        payload["temperature"] = 1.0           # the API accepts no other temperature together with extended thinking
+        payload["max_tokens"] = max(payload["max_tokens"], int(payload["thinking"].get("budget_tokens", 0)) + 1024)
     if system:
         payload["system"] = system
     if actor.tools:
         payload["tools"] = [tool_to_anthropic(t) for t in actor.tools]
-    if ep.oauth_token:
-        headers["Authorization"] = f"Bearer {ep.oauth_token}"
+    token = ep.oauth_token
+    app_name = extra.pop("oauth_app", None)
+    if app_name:            # a long session outlives an access token: take a fresh one (refreshed when near expiry) per request
+        from ..oauth import OAuthApp, OAuthClient, OAuthError
+
+        try:
+            token = await OAuthClient(OAuthApp.load(app_name)).get_valid_access_token() or token
+        except OAuthError:
+            pass
+        payload.pop("oauth_app", None)
+    if token:
+        headers["Authorization"] = f"Bearer {token}"
     else:
         headers["x-api-key"] = ep.api_key
     base = ep.api_base.rstrip("/") or "https://api.anthropic.com"

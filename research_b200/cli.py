@@ -57,6 +57,7 @@ def _endpoint(args):
         oauth_token = _run_coro(client.get_valid_access_token()) or ""
         if not oauth_token:
             raise SystemExit(f"not logged in to {args.oauth!r} (or the log-in was revoked): run `research_b200 auth login {args.oauth}`")
+        extra["oauth_app"] = args.oauth
         if client.app.request_headers:
             extra["request_headers"] = dict(client.app.request_headers)
     return Endpoint(provider=provider, model=model, api_base=args.api_base or "",

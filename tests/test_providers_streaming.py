@@ -199,3 +199,44 @@ def test_provider_request_hygiene_and_errors():
     with pytest.raises(ProviderError) as ei:
         asyncio.run(always_down())
     assert ei.value.provider == "anthropic" and ei.value.attempts == 2 and isinstance(ei.value.original_error, ConnectionError) and calls["n"] == 2
+
+
+def test_anthropic_request_credentials_thinking_and_headers(tmp_path, monkeypatch):
+    """What leaves for the API: bearer token from a stored log-in (refreshed per request) instead of the key, the
+    application's extra headers, temperature forced to 1 with extended thinking, and no private fields in the payload."""
+    import time
+
+    from research_b200.agents import oauth
+    from research_b200.agents.dtypes import Actor, Endpoint, Message, RunConfig, Trajectory
+    from research_b200.agents.providers import streaming
+
+    sent = {}
+
+    async def fake_post(url, payload, headers, timeout, provider):
+        sent.update(url=url, payload=payload, headers=headers)
+        for ev in ({"type": "message_start", "message": {"id": "m1", "usage": {"input_tokens": 3}}},
+                   {"type": "content_block_start", "index": 0, "content_block": {"type": "text", "text": ""}},
+                   {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": "hi"}},
+                   {"type": "content_block_stop", "index": 0},
+                   {"type": "message_delta", "delta": {"stop_reason": "end_turn"}, "usage": {"output_tokens": 1}}, {"type": "message_stop"}):
+            yield ev
+
+    monkeypatch.setattr(streaming, "_stream_post", fake_post)
+    monkeypatch.setattr(oauth, "DEFAULT_DIR", tmp_path)
+    for k, v in {"AUTHORIZE_URL": "https://a/x", "TOKEN_URL": "https://a/t", "CLIENT_ID": "c", "REDIRECT_URI": "https://a/cb"}.items():
+        monkeypatch.setenv(f"RB_OAUTH_SUB_{k}", v)
+    oauth.TokenStorage(tmp_path / "sub.json").save(oauth.OAuthTokens("fresh-token", "rt", time.time() + 3600))
+    real = oauth.OAuthClient
+    monkeypatch.setattr(oauth, "OAuthClient", lambda app, storage=None, **kw: real(app, storage or oauth.TokenStorage(tmp_path / f"{app.name}.json"), **kw))
+    ep = Endpoint(provider="anthropic", model="claude-x", api_key="sk-key", oauth_token="stale-token", temperature=0.3, max_tokens=2000,
+                  extra_params={"oauth_app": "sub", "request_headers": {"x-app": "1"}, "thinking": {"type": "enabled", "budget_tokens": 4096}})
+    actor = Actor(Trajectory((Message("system", "be brief"), Message("user", "hello"))), ep)
+    out = asyncio.run(streaming.rollout_anthropic(actor, RunConfig()))
+    assert out.trajectory.messages[-1].text() == "hi"
+    h, p = sent["headers"], sent["payload"]
+    assert h["Authorization"] == "Bearer fresh-token" and "x-api-key" not in h and h["x-app"] == "1" and h["anthropic-version"]
+    assert p["temperature"] == 1.0 and p["max_tokens"] == 5120 and p["thinking"]["budget_tokens"] == 4096 and p["system"] == "be brief"
+    assert "oauth_app" not in p and "request_headers" not in p and "prompt_caching" not in p
+    # no log-in: the API key travels in its own header
+    asyncio.run(streaming.rollout_anthropic(Actor(actor.trajectory, Endpoint(provider="anthropic", model="claude-x", api_key="sk-key")), RunConfig()))
+    assert sent["headers"]["x-api-key"] == "sk-key" and "Authorization" not in sent["headers"] and sent["payload"]["temperature"] == 1.0
