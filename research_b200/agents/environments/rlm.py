@@ -16,7 +16,6 @@ is the same for models without tool calling: it runs ```repl fenced blocks found
 from __future__ import annotations
 
 import asyncio
-import contextlib
 import io
 import re
 import traceback
@@ -51,23 +50,33 @@ def _tool(name: str, desc: str, props: dict[str, Any], required: tuple[str, ...]
 
 
 def run_code(code: str, namespace: dict[str, Any], max_chars: int = MAX_OUTPUT_CHARS) -> tuple[str, bool]:
-    """Execute ``code`` in ``namespace`` with stdout captured; the value of a trailing expression is printed as in an
-    interactive session. Returns (output, failed)."""
+    """Execute ``code`` in ``namespace`` with what it prints captured; the value of a trailing expression is printed as in
+    an interactive session. Returns (output, failed).
+
+    Several of these run at once in worker threads (concurrent evaluation samples, sub-agents), so the process-wide
+    ``sys.stdout`` is left alone: the namespace gets its own ``print`` that writes to this call's buffer."""
     import ast
 
     buf, failed = io.StringIO(), False
-    with contextlib.redirect_stdout(buf):
-        try:
-            tree = ast.parse(code, "<repl>", "exec")
-            last = tree.body.pop() if tree.body and isinstance(tree.body[-1], ast.Expr) else None
-            exec(compile(tree, "<repl>", "exec"), namespace)  # noqa: S102 - the purpose of a REPL tool
-            if last is not None:
-                value = eval(compile(ast.Expression(last.value), "<repl>", "eval"), namespace)  # noqa: S307
-                if value is not None:
-                    print(repr(value))
-        except Exception:  # noqa: BLE001 - reported to the model
-            failed = True
-            buf.write(traceback.format_exc(limit=4))
+
+    def _print(*args: Any, **kw: Any) -> None:
+        kw.setdefault("file", buf)
+        print(*args, **kw)
+
+    namespace["print"] = _print
+    try:
+        tree = ast.parse(code, "<repl>", "exec")
+        last = tree.body.pop() if tree.body and isinstance(tree.body[-1], ast.Expr) else None
+        exec(compile(tree, "<repl>", "exec"), namespace)  # noqa: S102 - the purpose of a REPL tool
+        if last is not None:
+            value = eval(compile(ast.Expression(last.value), "<repl>", "eval"), namespace)  # noqa: S307
+            if value is not None:
+                _print(repr(value))
+    except Exception:  # noqa: BLE001 - reported to the model
+        failed = True
+        buf.write(traceback.format_exc(limit=4))
+    finally:
+        namespace.pop("print", None)
     out = buf.getvalue()
     if len(out) > max_chars:
         out = out[:max_chars] + f"\n... ({len(out) - max_chars} more characters cut)"

@@ -172,3 +172,15 @@ def test_browsing_eval_on_the_offline_web():
     assert rep.summary["mean_reward"] == 1.0
     by = {s.sample_id: {m.name: m.value for m in s.score.metrics} for s in rep.samples}
     assert all(1 <= m["pages_read"] <= 3 and m["searches"] == 1 and m["answered"] == 1.0 for m in by.values())
+
+
+def test_intent_gepa_and_rlm_aggregation_examples():
+    from examples.eval.rlm.aggregate_records import make_rows, run as run_aggregate
+    from examples.prompt_optimization.intent_gepa import LABELS, run as run_intent
+
+    best = run_intent(200)
+    assert best.best_score == 1.0 and all(lbl in best.best_candidate["system"] + best.best_candidate["user_template"] for lbl in LABELS)
+    assert "only the label" in (best.best_candidate["system"] + best.best_candidate["user_template"]).lower() and "{input}" in best.best_candidate["user_template"]
+    rep = run_aggregate(make_rows(3, lines=300, seed=1))
+    # every count right, while the prompt the root model saw stayed two orders of magnitude below the input
+    assert rep.summary["mean_correct"] == 1.0 and rep.summary["mean_prompt_chars"] * 10 < rep.summary["mean_context_chars"]
