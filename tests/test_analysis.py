@@ -70,3 +70,57 @@ def test_optimizer_paths():
     assert distance_to_minimum("rosenbrock", rose) < 0.2
     pic = render("rosenbrock", {"adam": rose[::50]}, width=40, height=16)
     assert len(pic.split("\n")) == 16 and "*" in pic and "A" in pic
+
+
+def test_outlier_pipeline_batches_comparison_and_memory_estimate(tmp_path, capsys):
+    from research_b200.analysis import outlier_features as of
+
+    # the two readings of "6 % of the sequence": dim 3 crosses in ONE layer per position, spread over many positions
+    g = torch.Generator().manual_seed(1)
+    layers = [torch.randn(1, 100, 16, generator=g) for _ in range(4)]
+    for li in range(4):
+        layers[li][0, li * 3:(li * 3) + 3, 3] = 8.0                   # 3 positions per layer, 12 distinct positions = 12 %
+    assert of.find_outlier_features(layers, criterion="positions").dims == [3] and of.find_outlier_features(layers, criterion="cells").dims == []
+    rec = of.find_outlier_features(layers, criterion="positions").to_records()[0]
+    assert abs(rec["seq_percentage"] - 0.12) < 1e-6 and abs(rec["cell_percentage"] - 0.03) < 1e-6 and rec["layer_percentage"] == 1.0
+    # text -> windows
+    assert of.chunk_text_by_chars("aaa bbb ccc ddd", 8) == ["aaa bbb", "ccc ddd"] and of.chunk_ids(list(range(10)), 4) == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    assert of.chunk_ids(list(range(10)), 4, stride=2)[-1] == [6, 7, 8, 9] and of.chunk_ids(list(range(10)), 4, drop_last=False)[-1] == [6, 7, 8, 9]
+    from research_b200.utils.char_tokenizer import CharTokenizer
+
+    tok = CharTokenizer()
+    seqs = of.get_token_sequences(["hello world", "second document here"], tok, 3, 8)
+    assert seqs.shape == (3, 8) and tok.eos_token_id in seqs[1].tolist()
+    # a model with a planted outlier dimension: a large embedding column survives the residual stream in every layer
+    cfg = get_preset("tiny-qwen2", num_layers=3)
+    w = init_random_weights(cfg, seed=0)
+    w["model.embed_tokens.weight"][:, 5] = 12.0
+    ids = torch.randint(0, cfg.vocab_size, (4, 16), generator=g)
+    res = of.run_analysis(w, cfg, ids, batch_size=2, model_name="tiny-planted", out_dir=tmp_path / "planted")
+    assert res["num_batches"] == 2 and [o["feature_dim"] for o in res["systematic_outliers"]] == [5] and res["systematic_outliers"][0]["batch_percentage"] == 1.0
+    assert res["layer_max"]["embed"] >= 12.0 and res["perplexity"] > 1.0
+    clean = of.run_analysis(init_random_weights(cfg, seed=0), cfg, ids, 2, "tiny-clean", tmp_path / "clean")
+    assert clean["num_systematic"] == 0
+    agg = of.aggregate_batch_results([{"outliers": [{"feature_dim": 1, "max_magnitude": 7.0, "layer_percentage": 0.5, "seq_percentage": 0.1}], "layer_max": {}, "num_tokens": 10, "perplexity": 4.0},
+                                      {"outliers": [], "layer_max": {}, "num_tokens": 30, "perplexity": 16.0},
+                                      {"outliers": [], "layer_max": {}, "num_tokens": 0, "perplexity": 1.0}])
+    assert agg["num_systematic"] == 0 and agg["candidate_dims"] == 1 and abs(agg["perplexity"] - 16 ** 0.75 * 4 ** 0.25) < 1e-6
+    rows = of.collect_results(tmp_path)
+    assert [r["model"] for r in rows] == ["tiny-planted", "tiny-clean"] or {r["model"] for r in rows} == {"tiny-planted", "tiny-clean"}
+    planted = next(r for r in rows if r["model"] == "tiny-planted")
+    assert planted["num_outliers"] == 1 and planted["mean_layer_pct"] == 100.0
+    assert "tiny-planted" in of.format_table(rows) and of.to_csv(rows).splitlines()[0].startswith("model,num_params,num_outliers")
+    assert "a=tiny" in of.terminal_plot(rows) and of.terminal_plot([]) == "(no results)"
+    # memory: an 8B model in bf16 is ~16 GB of weights; training adds 12 bytes per parameter of optimizer state; sharding divides it
+    big = get_preset("llama-3-8b")
+    inf = of.estimate_vram(big, "bfloat16", batch_size=1, seq_len=4096)
+    assert 15 < inf["weights_gb"] < 17 and abs(inf["kv_cache_gb"] - 2 * 32 * 4096 * 8 * 128 * 2 / 1e9) < 1e-6 and inf["fits"]
+    tr1, tr8 = of.estimate_vram(big, mode="training", seq_len=4096, gpu_gb=80), of.estimate_vram(big, mode="training", seq_len=4096, num_gpus=8, gpu_gb=80)
+    assert of.estimate_vram(big, mode="training", seq_len=4096)["fits"]                      # 180 GB holds an 8B training run on one GPU
+    assert abs(tr1["optimizer_gb"] - 12 * big.num_params() / 1e9) < 1e-6 and not tr1["fits"] and tr8["fits"] and tr1["min_gpus"] >= 2
+    assert abs(tr8["optimizer_gb"] * 8 - tr1["optimizer_gb"]) < 1e-6 and tr8["activations_gb"] == tr1["activations_gb"]
+    assert of.estimate_vram(big, mode="analysis", seq_len=2048)["activations_gb"] > of.estimate_vram(big, seq_len=2048)["activations_gb"]
+    n, how = of.params_from_hf_config(big.to_hf_dict())
+    assert n == big.num_params() and "32 layers" in how and "dense" in how
+    assert of.main(["vram", "--model", "llama-3-8b", "--mode", "training", "--num-gpus", "8"]) == 0 and "optimizer state" in capsys.readouterr().out
+    assert of.main(["compare", str(tmp_path)]) == 0 and "tiny-clean" in capsys.readouterr().out
