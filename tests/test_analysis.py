@@ -124,3 +124,77 @@ def test_outlier_pipeline_batches_comparison_and_memory_estimate(tmp_path, capsy
     assert n == big.num_params() and "32 layers" in how and "dense" in how
     assert of.main(["vram", "--model", "llama-3-8b", "--mode", "training", "--num-gpus", "8"]) == 0 and "optimizer state" in capsys.readouterr().out
     assert of.main(["compare", str(tmp_path)]) == 0 and "tiny-clean" in capsys.readouterr().out
+
+
+def test_cluster_tree_names_annotation_and_stage_similarity(tmp_path):
+    import asyncio
+
+    from research_b200.analysis import corpus_clusters as cc
+
+    assert cc.split_into_sentences("Dr. Smith paid 3.50 dollars. He left! Did she? Yes.") == ["Dr. Smith paid 3.50 dollars.", "He left!", "Did she?", "Yes."]
+    text = "alpha beta gamma delta epsilon zeta eta theta iota kappa lambda mu"
+    fixed = cc.chunk_fixed_chars(text, 24, 0.25)
+    assert all(len(c) <= 24 for c in fixed) and fixed[0].startswith("alpha") and fixed[-1].endswith("mu") and len(fixed) >= 3
+    assert any(a.split()[-1] in b for a, b in zip(fixed, fixed[1:]))                      # neighbours overlap
+    from research_b200.utils.char_tokenizer import CharTokenizer
+
+    toks = cc.chunk("abcdefghij", "fixed_tokens", size=4, overlap_pct=0.5, tokenizer=CharTokenizer())
+    assert toks == ["abcd", "cdef", "efgh", "ghij"] and cc.chunk("p1\n\np2", "paragraph") == ["p1", "p2"]
+    # three well-separated families, one of them with two sub-families
+    g = torch.Generator().manual_seed(0)
+    centres = [torch.eye(12)[0] * 10, torch.eye(12)[1] * 10, torch.eye(12)[2] * 10 + torch.eye(12)[3] * 3, torch.eye(12)[2] * 10 - torch.eye(12)[3] * 3]
+    vectors = torch.cat([c + 0.3 * torch.randn(25, 12, generator=g) for c in centres])
+    texts = [f"{['math', 'cooking', 'law-contracts', 'law-criminal'][i // 25]} text {i}" for i in range(100)]
+    tree = cc.recursive_cluster(vectors, max_depth=2, min_cluster_size=5, seed=0)
+    top = sorted(n.size for n in tree.children)
+    assert len(tree.children) in (3, 4) and sum(top) + len(tree.noise_indices) == 100 and tree.silhouette > 0.5
+    stats = cc.compute_cluster_stats(tree)
+    assert stats["max_depth"] >= 1 and stats["total_clusters"] == len(list(tree.walk())) and stats["clusters_per_depth"][0] == 1
+    m = cc.build_chunk_to_cluster_map(tree)
+    top_of = lambda i: ".".join(m[i].split(".")[:2])                                    # noqa: E731
+    assert len({top_of(i) for i in range(25)} - {"0"}) == 1 and top_of(0) != top_of(30) and all(m[i].startswith(top_of(i)) for i in range(100))
+    again = cc.tree_from_dict(json_round_trip(cc.tree_to_dict(tree)))
+    assert [n.cluster_id for n in again.walk()] == [n.cluster_id for n in tree.walk()] and cc.find_node_by_id(again, "0.1").size == cc.find_node_by_id(tree, "0.1").size
+    # naming: the prompt carries typical members, the parent's name and named siblings; failures leave a node unnamed
+    prompts = []
+
+    async def complete(prompt):
+        prompts.append(prompt)
+        if "cooking" in prompt.split("Excerpts:")[1]:
+            raise RuntimeError("model unavailable")
+        first = prompt.split("1. ")[1].split()[0]
+        return f'Name: "{first} documents."\nextra line'
+
+    n = asyncio.run(cc.name_cluster_tree(tree, vectors, texts, complete, samples_per_cluster=3))
+    names = {c.cluster_id: c.name for c in tree.walk()}
+    assert n == len([v for v in names.values() if v]) and "" in names.values() and any(v == "math documents" for v in names.values())
+    assert any("Sibling groups already named" in p for p in prompts) and any('part of the larger group "' in p for p in prompts)
+    assert "(unnamed)" in cc.format_cluster_tree(tree) and "most typical:" in cc.inspect_cluster(tree, "0.0", vectors, texts) and "no cluster" in cc.inspect_cluster(tree, "9", vectors, texts)
+    # a staged text corpus, stored and loaded, annotates a generation sentence by sentence
+    docs = ["Natalia sold 48 clips in April. She sold half as many in May. How many clips did she sell altogether? " * 2,
+            "The defendant signed the contract. The court found the clause void. Damages were awarded to the buyer. " * 2,
+            "Whisk the eggs with sugar. Fold in the flour gently. Bake for twenty minutes at 180 degrees. " * 2]
+    corpus = cc.ClusteredCorpus.build(docs, stages=["sft", "pretrain", "pretrain"], strategy="sentence", max_depth=1, min_cluster_size=2)
+    for node in corpus.tree.walk():
+        node.name = f"cluster {node.cluster_id}"
+    corpus.save(tmp_path / "corpus")
+    loaded = cc.ClusteredCorpus.load(tmp_path / "corpus")
+    assert loaded.index.chunks == corpus.index.chunks and loaded.metadata[0]["corpus_stage"] == "sft" and loaded.path.endswith("corpus")
+    gen = "She sold half as many in May. The weather on Mars is cold."
+    lps = [("She sold half", -0.1), (" as many in May.", -0.3), (" The weather", -2.0), (" on Mars is cold.", -4.0)]
+    ann = cc.annotate_text(loaded, gen, k=2, prompt="How many clips?", token_logprobs=lps)
+    first, far = [a for a in ann.annotations if a.rank == 1]
+    assert len(ann.annotations) == 4 and first.corpus_stage == "sft" and first.distance < 0.1 < far.distance and first.cluster_name.startswith("cluster 0")
+    assert abs(first.avg_logprob + 0.2) < 1e-9 and abs(far.avg_logprob + 3.0) < 1e-9
+    shown = cc.format_annotations(ann, show_chunks=True)
+    assert "Prompt: How many clips?" in shown and "mean logprob -0.20" in shown and "nearest: She sold half as many in May." in shown
+    assert len(cc.format_annotations_compact(ann).splitlines()) == 2 and cc.AnnotatedOutput.from_dict(json_round_trip(ann.to_dict())).annotations[0] == ann.annotations[0]
+    assert cc.annotate_text(loaded, "  ").annotations == []
+    sim = cc.similarity_by_stage(loaded, ["How many clips did she sell altogether?", "She sold 48 clips."])
+    assert set(sim) == {"pretrain", "sft"} and sim["sft"]["mean"] < sim["pretrain"]["mean"] and sim["sft"]["chunks"] == 6
+
+
+def json_round_trip(obj):
+    import json
+
+    return json.loads(json.dumps(obj))
