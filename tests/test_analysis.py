@@ -198,3 +198,27 @@ def json_round_trip(obj):
     import json
 
     return json.loads(json.dumps(obj))
+
+
+def test_optimizer_comparison_export_and_momentum_rank(tmp_path):
+    import json
+
+    from research_b200.analysis.optimizer_paths import compare, export_viz_data, landscape, momentum_rank_experiment
+
+    res = compare("narrow_valley", steps=400)
+    # plain SGD crawls along the valley floor; momentum and Adam get there
+    assert res["momentum"]["final_distance"] < res["sgd"]["final_distance"] and res["adam"]["final_distance"] < 0.5 and not res["adam"]["diverged"]
+    assert res["momentum"]["steps_to_1pct"] is not None and res["sgd"]["steps_to_1pct"] < 20 and res["sgd"]["final_value"] > 1e6 * res["momentum"]["final_value"]
+    assert compare("quadratic", {"sgd": {"lr": 0.5}}, steps=50)["sgd"]["diverged"]                    # lr above 2 / L = 0.2
+    land = landscape("quadratic", resolution=11)
+    assert len(land["z"]) == 11 and land["z"][5][5] == 0.0 and land["minimum"] == [0.0, 0.0]
+    data = export_viz_data("narrow_valley", {k: res[k] for k in ("sgd", "adam")}, tmp_path / "viz.json", resolution=8)
+    on_disk = json.loads((tmp_path / "viz.json").read_text())
+    assert set(on_disk["trajectories"]) == {"sgd", "adam"} and len(on_disk["trajectories"]["adam"]["points"]) == 401 and len(on_disk["landscape"]["x"]) == 8
+    assert data["trajectories"]["adam"]["values"][-1] < data["trajectories"]["adam"]["values"][0]
+    # a rank-4 problem: the moment matrix of Adam concentrates on four directions while the loss falls
+    r = momentum_rank_experiment(input_dim=24, output_dim=24, true_rank=4, steps=300, lr=0.05, record_every=75)
+    first, last = r["records"][0], r["records"][-1]
+    assert [x["step"] for x in r["records"]] == [1, 75, 150, 225, 300] and last["loss"] < 1e-3 * first["loss"] and r["weight_error"] < 0.01
+    assert first["top_energy"] > 0.99 and first["effective_rank"] < 4.5 and len(first["singular_values"]) == 24
+    assert all(x["top_energy"] > 0.9 for x in r["records"]) and last["effective_rank"] < 2.0      # never far from rank 4, collapsing at the end
