@@ -484,7 +484,99 @@ def case_ep_agree(comm, dev, dt):
         assert ep.agree(r) == (W - 1,)
 
 
-CASES = {"ep_agree": case_ep_agree, "barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
+def case_tp_training(comm, dev, dt):
+    """Tensor-parallel (x data-parallel) training against the single-process functional model: same loss, same full
+    gradient, same weights after two AdamW steps, for a tied and an untied head, with QK-norm, and for the GRPO loss
+    with its entropy term. World 2: tp 2. World 4: tp 2 x dp 2 (each data-parallel half has its own batch)."""
+    from research_b200.models import causal_lm_forward, get_preset, init_random_weights
+    from research_b200.training.backends.tensor_parallel import TensorParallelTrainingBackend, shard_weights, unshard_weights
+    from research_b200.training.backends.torch_func import TorchFuncTrainingBackend
+    from research_b200.training.types import TrainerConfig
+
+    W, r = comm.world, comm.rank
+    tp = 2
+    dp = W // tp
+    tol = dict(atol=2e-5, rtol=2e-4) if dev.type == "cpu" else dict(atol=3e-2, rtol=5e-2)
+    for preset, kw, loss in (("tiny-qwen2", {}, "ce"), ("tiny-llama", {}, "grpo"), ("tiny-qwen3", {}, "ce")):
+        try:
+            cfg = get_preset(preset, num_layers=2, **kw)
+        except (KeyError, AssertionError):
+            continue
+        full = init_random_weights(cfg, seed=3)
+        parts = [shard_weights(full, i, tp) for i in range(tp)]
+        back = unshard_weights(parts)
+        assert all(torch.equal(back[k], full[k]) for k in full) and parts[0]["model.layers.0.self_attn.o_proj.weight"].shape[1] * tp == cfg.num_heads * cfg.head_dim
+        tc = TrainerConfig(max_grad_norm=0.5)
+        be = TensorParallelTrainingBackend(cfg, full, tp_size=tp, device=dev, dtype=dt if dev.type == "cuda" else torch.float32, loss_fn=loss, lr=1e-2, trainer_config=tc)
+        assert (be.tp_rank, be.dp_rank, be.dp_size) == (r % tp, r // tp, dp)
+        ref = TorchFuncTrainingBackend(cfg, full, device="cpu", loss_fn=loss, lr=1e-2, trainer_config=tc)
+
+        def batch_of(group: int, step: int):
+            g = torch.Generator().manual_seed(100 * step + group)
+            ids = torch.randint(0, cfg.vocab_size, (4, 12), generator=g)
+            mask = torch.ones(4, 12)
+            mask[:, :3] = 0
+            b = {"input_ids": ids, "labels": ids.clone(), "loss_mask": mask}
+            if loss == "grpo":
+                b["advantages"] = torch.randn(4, generator=g)
+            return b
+
+        for step in range(2):
+            m = be.forward_backward(batch_of(r // tp, step)).wait()
+            losses = []
+            for grp in range(dp):                       # the oracle sees every data-parallel group's batch
+                losses.append(ref.forward_backward(batch_of(grp, step)).wait()["loss"])
+            assert abs(m["loss"] - losses[r // tp]) < (1e-4 if dev.type == "cpu" else 5e-2), (preset, step, m["loss"], losses)
+            got = be.gathered_grads()
+            for k, g in ref.grads.items():
+                # after a step the two sets of weights differ in single entries (see below), and so do the gradients
+                close(got[k], g / dp, what=f"{preset} step {step} grad {k}", atol=tol["atol"] * (1 if step == 0 else 20), rtol=tol["rtol"] * (1 if step == 0 else 20))
+            n_be = be.optim_step().wait()["grad_norm"]
+            n_ref = ref.optim_step().wait()["grad_norm"]
+            assert abs(n_be - n_ref) <= 1e-3 * max(n_ref, 1.0) + (0 if dev.type == "cpu" else 0.05), (preset, n_be, n_ref)
+            w = be.get_weights().wait()
+            for k, v in ref.params.items():
+                # Adam divides by the root of the second moment: where a gradient is almost zero, rounding differences of
+                # 1e-9 move single entries by a visible fraction of the learning rate (1e-2), so: very few outliers, tiny mean error
+                err = (w[k].float().cpu() - v.float().cpu()).abs()
+                off = (err > (0.05 if dev.type == "cpu" else 0.5) * 1e-2).float().mean()
+                assert off < 1e-3 and err.mean() < (1e-4 if dev.type == "cpu" else 2e-3), f"{preset} step {step} weight {k}: {off:.2%} off, mean {err.mean():.3g}"
+        # ranks of one tensor-parallel group must be fed the same tokens
+        if dev.type == "cpu":
+            bad = batch_of(r // tp, 7)
+            bad["input_ids"] = bad["input_ids"] + (r % tp)
+            try:
+                be.forward_backward(bad)
+                raise SystemExit("different batches inside a tensor-parallel group went unnoticed")
+            except AssertionError as e:
+                assert "different batches" in str(e)
+    # checkpoint: the full model once, optimizer shards per tensor-parallel rank; a fresh backend resumes from it
+    import tempfile
+
+    box = [tempfile.mkdtemp() if r == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    cfg = get_preset("tiny-qwen2", num_layers=1)
+    full = init_random_weights(cfg, seed=5)
+    a = TensorParallelTrainingBackend(cfg, full, tp_size=tp, device=dev, checkpoint_dir=box[0], lr=1e-2)
+    ids = torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(r // tp))
+    a.forward_backward({"input_ids": ids, "labels": ids})
+    a.optim_step()
+    path = a.save_checkpoint()
+    b = TensorParallelTrainingBackend(cfg, init_random_weights(cfg, seed=6), tp_size=tp, device=dev, checkpoint_dir=box[0], lr=1e-2)
+    b.load_checkpoint(path)
+    assert b.current_step == 1 and all(torch.equal(b.master[k], a.master[k]) for k in a.master) and b.opt_state.step == 1
+    from research_b200.models.weights import load_safetensors_dir
+
+    saved, saved_cfg = load_safetensors_dir(path / "hf")
+    wa = a.get_weights().wait()
+    assert saved_cfg.hidden_size == cfg.hidden_size and all(torch.allclose(saved[k].float(), wa[k].float().cpu()) for k in wa)
+    for be2 in (a, b):
+        be2.forward_backward({"input_ids": ids, "labels": ids})
+        be2.optim_step()
+    assert all(torch.equal(b.master[k], a.master[k]) for k in a.master)
+
+
+CASES = {"tp_training": case_tp_training, "ep_agree": case_ep_agree, "barrier": case_barrier, "tp_gemms": case_tp_gemms, "sharded_adamw": case_sharded_adamw,
          "weight_sync_tp_engine": case_weight_sync_and_tp_engine, "fsdp_backend_grpo": case_fsdp_backend_and_grpo,
          "fsdp_full_shard": case_fsdp_full_shard, "ep_training": case_ep_training, "grpo_expert_parallel": case_grpo_expert_parallel, "grpo_disjoint": case_grpo_disjoint, "grpo_disjoint_tp_engine": case_grpo_disjoint_tp_engine,
          "moe_ep": case_moe_expert_parallel}

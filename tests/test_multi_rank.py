@@ -38,14 +38,14 @@ def _run(device: str, nproc: int, cases: str, timeout: int = 600) -> str:
     return proc.stdout
 
 
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms,ep_agree", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "ep_training", "grpo_expert_parallel", "grpo_disjoint", "moe_ep"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms,ep_agree", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "ep_training", "grpo_expert_parallel", "grpo_disjoint", "moe_ep", "tp_training"])
 def test_gloo_two_ranks(cases):
     out = _run("cpu", 2, cases)
     for c in cases.split(","):
         assert f"CASE_OK {c}" in out
 
 
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "fsdp_full_shard", "ep_training", "grpo_disjoint", "grpo_disjoint_tp_engine", "moe_ep"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms", "sharded_adamw", "fsdp_full_shard", "ep_training", "grpo_disjoint", "grpo_disjoint_tp_engine", "moe_ep", "tp_training"])
 def test_gloo_four_ranks(cases):
     """The host-side logic (slab rotation, shard ranges, count matrices, dispatch offsets) at world size 4."""
     out = _run("cpu", 4, cases)

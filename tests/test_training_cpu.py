@@ -443,3 +443,35 @@ def test_lazy_weights_and_lazy_state_dict():
     assert set(lazy) == set(param_shapes(tiny)) and len(lazy) == len(param_shapes(tiny))
     n = "model.layers.1.mlp.experts.3.up_proj.weight"
     assert torch.equal(lazy[n], be.buckets.full_param(n))
+
+
+def test_vocab_parallel_logprob_matches_log_softmax_and_tp_backend_runs_alone():
+    """The split log-softmax on one shard (no group) is the ordinary one, values and gradients, entropy included; the
+    tensor-parallel backend with a single rank is an ordinary trainer."""
+    from research_b200.training.backends.tensor_parallel import TensorParallelTrainingBackend, split_dim, vocab_parallel_logprob
+
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(3, 5, 17, generator=g, requires_grad=True)
+    targets = torch.randint(0, 17, (3, 5), generator=g)
+    targets[0, 0] = -1
+    lp, ent = vocab_parallel_logprob(logits, targets, 0, None, True)
+    w_lp, w_ent = torch.randn(3, 5, generator=g), torch.randn(3, 5, generator=g)
+    ((lp * w_lp).sum() + (ent * w_ent).sum()).backward()
+    ref = logits.detach().clone().requires_grad_(True)
+    lsm = torch.log_softmax(ref, -1)
+    r_lp = torch.where(targets >= 0, lsm.gather(-1, targets.clamp(min=0)[..., None])[..., 0], torch.zeros(3, 5))
+    r_ent = -(lsm.exp() * lsm).sum(-1)
+    ((r_lp * w_lp).sum() + (r_ent * w_ent).sum()).backward()
+    assert torch.allclose(lp, r_lp, atol=1e-6) and torch.allclose(ent, r_ent, atol=1e-5) and torch.allclose(logits.grad, ref.grad, atol=1e-5)
+    assert lp[0, 0] == 0 and split_dim("model.layers.3.mlp.down_proj.weight") == 1 and split_dim("model.norm.weight") is None
+    cfg = get_preset("tiny-qwen2", num_layers=1)
+    be = TensorParallelTrainingBackend(cfg, init_random_weights(cfg, seed=0), lr=1e-2)
+    ids = torch.randint(0, cfg.vocab_size, (2, 10), generator=g)
+    first = be.forward_backward({"input_ids": ids, "labels": ids}).wait()["loss"]
+    be.optim_step()
+    for _ in range(5):
+        be.forward_backward({"input_ids": ids, "labels": ids})
+        be.optim_step()
+    assert be.forward_backward({"input_ids": ids, "labels": ids}).wait()["loss"] < first and be.tp_size == 1 and be.current_step == 6
+    with pytest.raises(AssertionError, match="expert parallelism"):
+        TensorParallelTrainingBackend(get_preset("tiny-moe"))
