@@ -10,6 +10,7 @@ read back by later, unrelated connections. The transport is a callable ``run(arg
 
 from __future__ import annotations
 
+import re
 import shlex
 import subprocess
 import time
@@ -51,6 +52,62 @@ class RemoteError(RuntimeError):
     pass
 
 
+# ------------------------------------------------------------------------------------------- validation of what reaches a shell
+_ENV_NAME = re.compile(r"^[A-Za-z_][A-Za-z0-9_]*$")
+_JOB_NAME = re.compile(r"^[A-Za-z0-9][A-Za-z0-9._-]{0,63}$")
+
+
+def validate_job_name(name: str) -> str:
+    """Job names become directory names on the target: letters, digits, ``. _ -``, at most 64 characters, no leading dot or dash."""
+    if not _JOB_NAME.match(name or "") or ".." in name:
+        raise ValueError(f"invalid job name {name!r}: use letters, digits, '.', '_' or '-' (1-64 characters, starting with a letter or digit)")
+    return name
+
+
+def generate_job_name(prefix: str = "job") -> str:
+    import secrets
+
+    return validate_job_name(f"{prefix}-{time.strftime('%Y%m%d-%H%M%S')}-{secrets.token_hex(3)}")
+
+
+def validate_env(env: dict[str, str]) -> dict[str, str]:
+    for k, v in env.items():
+        if not _ENV_NAME.match(k):
+            raise ValueError(f"invalid environment variable name {k!r}")
+        if not isinstance(v, str) or "\x00" in v:
+            raise ValueError(f"environment variable {k} must be a string without NUL bytes")
+    return env
+
+
+def validate_working_directory(path: str) -> str:
+    if not path or "\x00" in path or "\n" in path or ".." in Path(path).parts:
+        raise ValueError(f"invalid working directory {path!r}: no empty path, no '..' component, no control characters")
+    return path
+
+
+def make_env_payload(env: dict[str, str]) -> bytes:
+    """``NAME='value'`` lines for the loader of ``wrap_with_env_loader``; values are shell-quoted, names validated."""
+    validate_env(env)
+    return ("".join(f"{k}={shlex.quote(v)}\n" for k, v in env.items())).encode()
+
+
+def wrap_with_env_loader(command: str) -> str:
+    """``command`` preceded by a loader that reads exported variables from standard input: secrets travel on the
+    connection's stdin, not in the command line, so they show up neither in ``ps`` on the target nor in shell history or
+    logs of commands (bifrost/bifrost/deploy.py:71-89)."""
+    return f"set -a; . /dev/stdin; set +a; sh -c {shlex.quote(command)}"
+
+
+def detect_bootstrap(files: Callable[[str], bool], extra: str | None = None, frozen: bool = False) -> str:
+    """The dependency-installation command a checkout needs, from the files it has (``files(name) -> exists``):
+    ``uv.lock`` / ``pyproject.toml`` -> ``uv sync``, ``requirements.txt`` -> ``pip install -r``, none -> ``""``."""
+    uv = "pip install uv && uv sync" + (" --frozen" if frozen else "") + (f" --extra {shlex.quote(extra)}" if extra else "")
+    for name, cmd in (("uv.lock", uv), ("pyproject.toml", uv), ("requirements.txt", "pip install -r requirements.txt")):
+        if files(name):
+            return cmd
+    return ""
+
+
 def local_changes(repo: str | Path) -> list[str]:
     """Paths of ``repo`` that a push would leave behind: modified, staged or untracked (and not ignored) files
     (bifrost/bifrost/git_sync.py:49-108)."""
@@ -82,6 +139,15 @@ class RemoteClient:
             raise RemoteError(f"{command!r} exited {code}: {err.strip()[:500]}")
         return code, out, err
 
+    def exec_with_env(self, command: str, env: dict[str, str], cwd: str | None = None, check: bool = False) -> tuple[int, str, str]:
+        """Run ``command`` with ``env`` exported, the variables sent on standard input (see ``wrap_with_env_loader``)."""
+        cd = f"cd {shlex.quote(validate_working_directory(cwd))} && " if cwd else ""
+        return self.exec(wrap_with_env_loader(cd + command), check=check, data=make_env_payload(env))
+
+    def detect_bootstrap(self, dest: str, extra: str | None = None, frozen: bool = False) -> str:
+        q = self._q(dest)
+        return detect_bootstrap(lambda name: self.exec(f"[ -f {q}/{name} ]")[0] == 0, extra, frozen)
+
     # ------------------------------------------------------------------ code push
     def push(self, repo: str | Path, dest: str, ref: str = "HEAD", bootstrap: str | list[str] | None = None,
              warn: Callable[[str], None] | None = None) -> str:
@@ -98,15 +164,36 @@ class RemoteClient:
         script = (f"set -e; mkdir -p {q}; cat > {q}/.incoming.bundle; cd {q}; [ -d .git ] || git init -q; "
                   f"git fetch -q .incoming.bundle {shlex.quote(ref)}; git checkout -q -f {commit}; rm -f .incoming.bundle")
         self.exec(script, check=True, data=bundle)
+        if bootstrap == "auto":
+            bootstrap = self.detect_bootstrap(dest) or None
         for cmd in ([bootstrap] if isinstance(bootstrap, str) else list(bootstrap or [])):
             self.exec(f"cd {q} && {cmd}", check=True)
         return commit
+
+    def push_worktree(self, repo: str | Path, base: str, job: str, ref: str = "HEAD") -> str:
+        """One checkout per job: the repository is pushed to ``<base>/repo`` once (updated on later pushes) and ``ref`` is
+        checked out into ``<base>/jobs/<job>`` as a git worktree, so that concurrent jobs on one machine never share a
+        working tree and an old job's code stays as it ran (bifrost/bifrost/deploy.py:289-440). Returns the worktree path."""
+        validate_job_name(job)
+        main = f"{base.rstrip('/')}/repo"
+        commit = self.push(repo, main, ref)
+        tree = f"{base.rstrip('/')}/jobs/{job}"
+        self.exec(f"mkdir -p {self._q(base.rstrip('/') + '/jobs')} && cd {self._q(main)} && git worktree add -f --detach {self._q(tree)} {commit}", check=True)
+        return tree
+
+    def remove_worktree(self, base: str, job: str) -> bool:
+        validate_job_name(job)
+        main, tree = f"{base.rstrip('/')}/repo", f"{base.rstrip('/')}/jobs/{job}"
+        return self.exec(f"cd {self._q(main)} && git worktree remove --force {self._q(tree)}")[0] == 0
+
 
     # ------------------------------------------------------------------ detached jobs
     def _jd(self, name: str) -> str:
         return f"{self.job_dir}/{name}"
 
     def start_job(self, spec: ProcessSpec) -> JobInfo:
+        validate_job_name(spec.name)
+        validate_env(spec.env)
         d = self._jd(spec.name)
         inner = f"( {spec.shell_line()} ); echo $? > {d}/exit_code"      # subshell: an `exit` in the command must not skip the record
         script = f"mkdir -p {d} && rm -f {d}/exit_code && (nohup sh -c {shlex.quote(inner)} > {d}/log 2>&1 & echo $! > {d}/pid) && cat {d}/pid"

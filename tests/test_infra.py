@@ -353,3 +353,47 @@ def test_provision_records_attempts_and_sorts_failures():
     r = gc.provision(max_attempts=2)
     assert r.all_unavailable and "out of capacity" in r.error_summary and len(r.attempts) == 2
     assert categorize_error(ValueError("weird")) == "unknown"
+
+
+def test_env_injection_bootstrap_detection_worktrees_and_validation(tmp_path):
+    from research_b200.infra import bifrost as bf
+
+    c = RemoteClient("local", job_dir=str(tmp_path / "jobs"))
+    seen = []
+    spy = RemoteClient("local", transport=lambda argv, data=None: (seen.append((argv, data)), bf.subprocess_transport(argv, data))[1])
+    code, out, _ = spy.exec_with_env('echo "$API_KEY|$TRICKY"; cd sub 2>/dev/null; pwd', {"API_KEY": "sk-secret", "TRICKY": "a'b \"c\" $HOME"}, cwd=str(tmp_path))
+    assert code == 0 and out.splitlines()[0] == "sk-secret|a'b \"c\" $HOME" and out.splitlines()[1] == str(tmp_path)
+    argv, data = seen[0]
+    assert "sk-secret" not in " ".join(argv) and b"API_KEY=sk-secret" in data                      # the secret is on stdin only
+    with pytest.raises(ValueError):
+        bf.make_env_payload({"BAD NAME": "x"})
+    with pytest.raises(ValueError):
+        c.start_job(ProcessSpec("true", name="../escape"))
+    with pytest.raises(ValueError):
+        c.start_job(ProcessSpec("true", name="ok", env={"1X": "y"}))
+    assert bf.validate_job_name(bf.generate_job_name("eval")).startswith("eval-") and bf.validate_working_directory("/srv/run") == "/srv/run"
+    for bad in ("", "a/../b", "x\ny"):
+        with pytest.raises(ValueError):
+            bf.validate_working_directory(bad)
+    # dependency bootstrap from the files of a checkout
+    have = {"requirements.txt"}
+    assert bf.detect_bootstrap(have.__contains__) == "pip install -r requirements.txt"
+    have.add("pyproject.toml")
+    assert bf.detect_bootstrap(have.__contains__, extra="dev", frozen=True) == "pip install uv && uv sync --frozen --extra dev"
+    assert bf.detect_bootstrap(set().__contains__) == ""
+    # one worktree per job from one pushed repository
+    repo = tmp_path / "repo"
+    repo.mkdir()
+    git = lambda *a: subprocess.run(["git", "-c", "user.name=t", "-c", "user.email=t@t", "-C", str(repo), *a], check=True, capture_output=True)  # noqa: E731
+    git("init", "-q", "-b", "main")
+    (repo / "f.txt").write_text("v1")
+    (repo / "requirements.txt").write_text("")
+    git("add", "-A"); git("commit", "-qm", "one")
+    base = str(tmp_path / "remote")
+    t1 = c.push_worktree(repo, base, "job-a", ref="main")
+    (repo / "f.txt").write_text("v2")
+    git("commit", "-qam", "two")
+    t2 = c.push_worktree(repo, base, "job-b", ref="main")
+    assert (tmp_path / "remote" / "jobs" / "job-a" / "f.txt").read_text() == "v1" and (tmp_path / "remote" / "jobs" / "job-b" / "f.txt").read_text() == "v2"
+    assert t1.endswith("jobs/job-a") and t2.endswith("jobs/job-b") and c.detect_bootstrap(t2) == "pip install -r requirements.txt"
+    assert c.remove_worktree(base, "job-a") and not (tmp_path / "remote" / "jobs" / "job-a").exists() and (tmp_path / "remote" / "jobs" / "job-b").exists()
