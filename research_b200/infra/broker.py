@@ -162,9 +162,53 @@ def categorize_error(e: BaseException) -> str:
 
 
 class GPUClient:
-    def __init__(self, providers: list[Provider]):
+    """``registry``: a JSON file that remembers the instances this client created across processes (what a command line
+    needs for ``list`` / ``ssh`` / ``cleanup`` after the ``create`` call has exited). Without it, instances live in memory."""
+
+    def __init__(self, providers: list[Provider], registry: str | None = None):
         self.providers = {p.name: p for p in providers}
         self.instances: dict[str, GPUInstance] = {}
+        self.created_at: dict[str, float] = {}
+        self.registry = registry
+        self._load_registry()
+
+    def _load_registry(self) -> None:
+        import json
+        from pathlib import Path
+
+        if not self.registry or not Path(self.registry).is_file():
+            return
+        try:
+            rows = json.loads(Path(self.registry).read_text())
+        except ValueError:
+            return
+        for r in rows:
+            offer = GPUOffer(**r["offer"])
+            self.instances[r["instance_id"]] = GPUInstance(r["provider"], r["instance_id"], offer, r.get("status", "unknown"), r.get("ssh_connection"))
+            self.created_at[r["instance_id"]] = r.get("created_at", 0.0)
+
+    def _save_registry(self) -> None:
+        import json
+        import os
+        from dataclasses import asdict
+        from pathlib import Path
+
+        if not self.registry:
+            return
+        p = Path(self.registry)
+        p.parent.mkdir(parents=True, exist_ok=True)
+        rows = [{"provider": i.provider, "instance_id": i.instance_id, "offer": asdict(i.offer), "status": i.status, "ssh_connection": i.ssh_connection,
+                 "created_at": self.created_at.get(i.instance_id, 0.0)} for i in self.instances.values()]
+        tmp = p.with_suffix(".tmp")
+        tmp.write_text(json.dumps(rows, indent=1))
+        os.replace(tmp, p)
+
+    def _remember(self, inst: GPUInstance) -> None:
+        import time
+
+        self.instances[inst.instance_id] = inst
+        self.created_at.setdefault(inst.instance_id, time.time())
+        self._save_registry()
 
     def search(self, where: Condition | None = None, sort_by: str = "price_per_hour", reverse: bool = False) -> list[GPUOffer]:
         offers = [o for p in self.providers.values() for o in p.search()]
@@ -178,7 +222,7 @@ class GPUClient:
         for o in self.search(where):
             try:
                 inst = self.providers[o.provider].create(o, **kw)
-                self.instances[inst.instance_id] = inst
+                self._remember(inst)
                 return inst
             except Exception as e:  # noqa: BLE001 - try the next offer
                 errors.append(f"{o.provider}/{o.offer_id}: {e}")
@@ -202,7 +246,7 @@ class GPUClient:
             if inst is None:
                 attempts.append(ProvisionAttempt(o.offer_id, o.gpu_type, o.provider, o.price_per_hour, "the provider returned no instance", "unavailable"))
                 continue
-            self.instances[inst.instance_id] = inst
+            self._remember(inst)
             attempts.append(ProvisionAttempt(o.offer_id, o.gpu_type, o.provider, o.price_per_hour, instance=inst))
             return ProvisionResult(True, inst, attempts)
         cats = [a.error_category for a in attempts]
@@ -220,6 +264,7 @@ class GPUClient:
             if fn is not None:
                 try:
                     inst = self.instances[iid] = fn(iid)
+                    self._save_registry()
                 except Exception:  # noqa: BLE001 - keep the last known state
                     pass
             out.append(inst)
@@ -230,7 +275,23 @@ class GPUClient:
 
     def terminate(self, instance_id: str) -> bool:
         inst = self.instances.pop(instance_id, None)
-        return bool(inst) and self.providers[inst.provider].terminate(instance_id)
+        self.created_at.pop(instance_id, None)
+        self._save_registry()
+        return bool(inst) and inst.provider in self.providers and self.providers[inst.provider].terminate(instance_id)
+
+    def older_than(self, hours: float, now: float | None = None) -> list[GPUInstance]:
+        """Instances this client created more than ``hours`` ago (candidates for ``cleanup``: a forgotten instance bills by the hour)."""
+        import time
+
+        now = time.time() if now is None else now
+        return [i for iid, i in self.instances.items() if now - self.created_at.get(iid, now) >= hours * 3600.0]
+
+    def running_cost(self, now: float | None = None) -> float:
+        """What the tracked instances have cost so far at their offers' hourly prices."""
+        import time
+
+        now = time.time() if now is None else now
+        return sum(i.offer.price_per_hour * max(now - self.created_at.get(iid, now), 0.0) / 3600.0 for iid, i in self.instances.items())
 
     def terminate_all(self) -> int:
         return sum(self.terminate(i) for i in list(self.instances))

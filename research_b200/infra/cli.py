@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import re
 import sys
 from dataclasses import asdict
@@ -71,7 +72,31 @@ def _gpu_client(a) -> GPUClient:
     provs = providers_from_env()
     if not provs:
         raise SystemExit("no provider API key in the environment (LAMBDA_API_KEY, RUNPOD_API_KEY, VAST_API_KEY, PRIME_API_KEY)")
-    return GPUClient(provs)
+    return GPUClient(provs, registry=os.path.join(os.path.expanduser("~"), ".research_b200", "instances.json"))
+
+
+def ssh_command(connection: str, key: str | None = None) -> str:
+    host, _, port = connection.partition(":")
+    return " ".join(["ssh"] + (["-p", port] if port else []) + (["-i", key] if key else []) + [host])
+
+
+GPU_QUERY = "nvidia-smi --query-gpu=index,name,memory.used,memory.total,utilization.gpu --format=csv,noheader,nounits"
+
+
+def instance_info(inst, key: str | None = None, transport=None) -> dict:
+    """What is on the machine behind an instance: its GPUs with memory in use and utilisation, free disk, uptime."""
+    from .bifrost import RemoteClient, subprocess_transport
+
+    c = RemoteClient(inst.ssh_connection, key=key, transport=transport or subprocess_transport)
+    code, out, err = c.exec(GPU_QUERY)
+    gpus = []
+    for line in out.splitlines() if code == 0 else []:
+        f = [x.strip() for x in line.split(",")]
+        if len(f) == 5 and f[0].isdigit():
+            gpus.append({"index": int(f[0]), "name": f[1], "memory_used_mib": int(f[2]), "memory_total_mib": int(f[3]), "utilization_pct": int(f[4])})
+    disk = c.exec("df -h / | tail -1")[1].split()
+    return {"instance_id": inst.instance_id, "ssh": inst.ssh_connection, "gpus": gpus, "gpu_error": err.strip()[:200] if code else "",
+            "disk_free": disk[3] if len(disk) > 3 else "?", "uptime": c.exec("uptime -p")[1].strip()}
 
 
 def cmd_gpus(a, out: Callable[[str], None]) -> int:
@@ -88,7 +113,45 @@ def cmd_gpus(a, out: Callable[[str], None]) -> int:
         out(json.dumps({"provider": inst.provider, "id": inst.instance_id, "status": inst.status, "ssh": inst.ssh_connection,
                         "offer": asdict(inst.offer)}))
         return 0
-    ok = gc.providers[a.provider].terminate(a.id)
+    if a.action == "list":
+        rows = gc.list_instances(refresh=not a.no_refresh)
+        if a.json:
+            out(json.dumps([{"provider": i.provider, "id": i.instance_id, "status": i.status, "ssh": i.ssh_connection, "gpu": i.offer.gpu_type,
+                             "count": i.offer.gpu_count, "price_per_hour": i.offer.price_per_hour} for i in rows]))
+        else:
+            out("\n".join(f"{i.provider}:{i.instance_id}  {i.status:<10} {i.offer.gpu_count}x{i.offer.gpu_type}  ${i.offer.price_per_hour:.2f}/h  {i.ssh_connection or '-'}"
+                          for i in rows) or "no instances")
+            if rows:
+                out(f"cost so far: ${gc.running_cost():.2f}")
+        return 0
+    if a.action in ("status", "ssh", "info"):
+        inst = gc.get_instance(a.id, refresh=a.action == "status")
+        if inst is None:
+            out(f"no tracked instance {a.id}")
+            return 1
+        if a.action == "status":
+            out(f"{inst.provider}:{inst.instance_id}: {inst.status}" + (f" ({inst.ssh_connection})" if inst.ssh_connection else ""))
+        elif not inst.ssh_connection:
+            out(f"{inst.instance_id} has no ssh address yet (status {inst.status})")
+            return 1
+        elif a.action == "ssh":
+            out(ssh_command(inst.ssh_connection, a.key))
+        else:
+            out(json.dumps(instance_info(inst, a.key, getattr(a, "_transport", None)), indent=1))
+        return 0
+    if a.action == "cleanup":
+        old = gc.older_than(a.older_than)
+        if not old:
+            out("nothing to clean up")
+            return 0
+        for i in old:
+            out(f"{'terminating' if a.yes else 'would terminate'} {i.provider}:{i.instance_id} ({i.offer.gpu_count}x{i.offer.gpu_type}, ${i.offer.price_per_hour:.2f}/h)")
+            if a.yes:
+                gc.terminate(i.instance_id)
+        if not a.yes:
+            out("run again with --yes to terminate them")
+        return 0
+    ok = gc.terminate(a.id) if a.id in gc.instances else gc.providers[a.provider].terminate(a.id)
     out(f"terminated {a.provider}:{a.id}" if ok else f"{a.provider}:{a.id} was not running")
     return 0 if ok else 1
 
@@ -169,6 +232,10 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--json", action="store_true")
     p = g.add_parser("create"); p.add_argument("--where", default=""); p.add_argument("--provider", default="")
     p = g.add_parser("terminate"); p.add_argument("--provider", required=True); p.add_argument("--id", required=True)
+    p = g.add_parser("list"); p.add_argument("--json", action="store_true"); p.add_argument("--no-refresh", action="store_true")
+    for name in ("status", "ssh", "info"):
+        p = g.add_parser(name); p.add_argument("--id", required=True); p.add_argument("--key", default=None)
+    p = g.add_parser("cleanup"); p.add_argument("--older-than", type=float, default=0.0, metavar="HOURS"); p.add_argument("--yes", action="store_true")
 
     r = top.add_parser("remote").add_subparsers(dest="action", required=True)
     for name in ("exec", "push", "run", "status", "logs", "stop"):

@@ -397,3 +397,37 @@ def test_env_injection_bootstrap_detection_worktrees_and_validation(tmp_path):
     assert (tmp_path / "remote" / "jobs" / "job-a" / "f.txt").read_text() == "v1" and (tmp_path / "remote" / "jobs" / "job-b" / "f.txt").read_text() == "v2"
     assert t1.endswith("jobs/job-a") and t2.endswith("jobs/job-b") and c.detect_bootstrap(t2) == "pip install -r requirements.txt"
     assert c.remove_worktree(base, "job-a") and not (tmp_path / "remote" / "jobs" / "job-a").exists() and (tmp_path / "remote" / "jobs" / "job-b").exists()
+
+
+def test_instance_registry_and_gpus_commands(tmp_path):
+    import json
+
+    from research_b200.infra.cli import instance_info, main, ssh_command
+
+    offers = [GPUOffer("lab", "m1", "B200", 8, 180, 30.0), GPUOffer("lab", "m2", "B200", 1, 180, 4.0)]
+    provider = StaticProvider("lab", offers, {"m1": "root@m1:2222", "m2": "root@m2"})
+    reg = str(tmp_path / "instances.json")
+    gc = GPUClient([provider], registry=reg)
+    inst = gc.create(q.gpu_count >= 8)
+    # another process (a later command) sees the instance through the registry file
+    later = GPUClient([provider], registry=reg)
+    assert list(later.instances) == [inst.instance_id] and later.instances[inst.instance_id].offer.gpu_type == "B200"
+    later.created_at[inst.instance_id] -= 3 * 3600
+    assert [i.instance_id for i in later.older_than(2)] == [inst.instance_id] and later.older_than(5) == [] and abs(later.running_cost() - 90.0) < 0.1
+    lines = []
+    assert main(["gpus", "list", "--no-refresh"], lines.append, later) == 0 and "8xB200" in lines[0] and "root@m1:2222" in lines[0] and lines[1].startswith("cost so far: $90")
+    assert main(["gpus", "ssh", "--id", inst.instance_id, "--key", "/k"], lines.append, later) == 0 and lines[-1] == "ssh -p 2222 -i /k root@m1"
+    assert main(["gpus", "status", "--id", inst.instance_id], lines.append, later) == 0 and "running" in lines[-1]
+    assert main(["gpus", "status", "--id", "ghost"], lines.append, later) == 1 and ssh_command("u@h") == "ssh u@h"
+
+    def fake(argv, data=None):
+        cmd = argv[-1]
+        if "nvidia-smi" in cmd:
+            return 0, "0, NVIDIA B200, 1024, 183359, 17\n1, NVIDIA B200, 0, 183359, 0\n", ""
+        return (0, "/dev/root 2.0T 500G 1.5T 25% /\n", "") if cmd.startswith("df") else (0, "up 3 hours\n", "")
+
+    info = instance_info(later.instances[inst.instance_id], transport=fake)
+    assert [g["memory_used_mib"] for g in info["gpus"]] == [1024, 0] and info["disk_free"] == "1.5T" and info["uptime"] == "up 3 hours"
+    assert main(["gpus", "cleanup", "--older-than", "2"], lines.append, later) == 0 and lines[-1].startswith("run again with --yes") and later.instances
+    assert main(["gpus", "cleanup", "--older-than", "2", "--yes"], lines.append, later) == 0 and not later.instances and len(provider.search()) == 2
+    assert json.loads((tmp_path / "instances.json").read_text()) == [] and main(["gpus", "list"], lines.append, later) == 0 and lines[-1] == "no instances"
