@@ -54,14 +54,14 @@ def test_gloo_four_ranks(cases):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("cases", ["barrier,tp_gemms,ep_agree", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "ep_training", "grpo_expert_parallel", "grpo_disjoint", "grpo_disjoint_tp_engine", "moe_ep"])
+@pytest.mark.parametrize("cases", ["barrier,tp_gemms,ep_agree", "sharded_adamw", "weight_sync_tp_engine", "fsdp_backend_grpo", "fsdp_full_shard", "ep_training", "grpo_expert_parallel", "grpo_disjoint", "grpo_disjoint_tp_engine", "moe_ep", "tp_training"])
 def test_gpu_ranks(cases):
     import torch
 
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    out = _run("cuda", 2 if n < 4 else 4 if cases != "weight_sync_tp_engine" else 2, cases)
+    out = _run("cuda", 2 if n < 4 or cases in ("weight_sync_tp_engine", "tp_training") else 4, cases)
     for c in cases.split(","):
         assert f"CASE_OK {c}" in out
 
