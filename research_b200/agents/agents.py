@@ -15,8 +15,8 @@ import uuid
 from dataclasses import replace
 from typing import Any
 
-from .dtypes import (Actor, AgentState, Message, RunConfig, StopReason, StreamDone, StreamEvent, TextDelta, ThinkingDelta, ToolCall,
-                     ToolCallEnd, ToolConfirmResult, ToolResult, ToolResultReceived, Trajectory)
+from .dtypes import (Actor, AgentState, LLMCallStart, Message, RunConfig, StopReason, StreamDone, StreamEvent, TextDelta, ThinkingDelta, ToolCall,
+                     ToolCallEnd, ToolConfirmResult, ToolExecutionStart, ToolResult, ToolResultReceived, Trajectory)
 
 
 # ------------------------------------------------------------------------------ stop handlers
@@ -181,6 +181,8 @@ async def process_pending_tools(state: AgentState, run_config: RunConfig) -> Age
             result = refused or ToolResult(call.id, is_error=True, error="tool call rejected by the user")
         else:
             try:
+                if run_config.on_chunk is not None:
+                    await run_config.on_chunk(ToolExecutionStart(tool_call_id=call.id, tool_name=call.name))
                 snapshot = await env.serialize()
                 work_env = await type(env).deserialize(snapshot)
                 if run_config.tool_limiter is not None:
@@ -230,6 +232,8 @@ async def run_agent_step(state: AgentState, run_config: RunConfig) -> AgentState
     if run_config.on_step_start is not None:
         state = run_config.on_step_start(state)
     tools = tuple(state.environment.get_tools()) if state.environment is not None else ()
+    if run_config.on_chunk is not None:
+        await run_config.on_chunk(LLMCallStart())
     actor = await rollout(replace(state.actor, tools=tools), run_config)
     last = actor.trajectory.messages[-1]
     if run_config.session_store is not None and state.session_id:

@@ -18,11 +18,122 @@ from pathlib import Path
 from typing import Any, Awaitable, Callable, Protocol, runtime_checkable
 
 
+def parse_streaming_json(partial: str) -> dict[str, Any]:
+    """Best-effort reading of a JSON object that is still being streamed (tool-call arguments arrive in pieces): what is
+    complete so far, with open strings, arrays and objects closed. ``'{"a": 1, "b":'`` -> ``{"a": 1}``;
+    ``'{"path": "src/ma'`` -> ``{"path": "src/ma"}``; anything that is not (yet) an object -> ``{}``."""
+    import json
+
+    s = partial.strip()
+    if not s.startswith("{"):
+        return {}
+    try:
+        v = json.loads(s)
+        return v if isinstance(v, dict) else {}
+    except ValueError:
+        pass
+    closer = {"{": "}", "[": "]"}
+    stack: list[str] = []
+    cuts: list[tuple[int, tuple[str, ...]]] = []         # places where cutting leaves only complete members
+    in_str = esc = False
+    for i, ch in enumerate(s):
+        if in_str:
+            if esc:
+                esc = False
+            elif ch == "\\":
+                esc = True
+            elif ch == '"':
+                in_str = False
+            continue
+        if ch == '"':
+            in_str = True
+        elif ch in "{[":
+            stack.append(ch)
+            cuts.append((i + 1, tuple(stack)))
+        elif ch in "}]" and stack:
+            stack.pop()
+            cuts.append((i + 1, tuple(stack)))
+        elif ch == ",":
+            cuts.append((i, tuple(stack)))
+    tail = s[:-1] if esc else s                                  # a dangling backslash cannot be closed
+    attempts = [(tail + ('"' if in_str else ""), tuple(stack))] + [(s[:pos], st) for pos, st in reversed(cuts[-12:])]
+    for text, st in attempts:
+        try:
+            v = json.loads(text + "".join(closer[c] for c in reversed(st)))
+            return v if isinstance(v, dict) else {}
+        except ValueError:
+            continue
+    return {}
+
+
 # ------------------------------------------------------------------------------ streaming events
 @dataclass(frozen=True)
 class StreamEvent:
     type: str = "event"
     timestamp: float = field(default_factory=time.time)
+
+
+@dataclass(frozen=True)
+class LLMCallStart(StreamEvent):
+    """A request is about to be sent (front ends start their spinner here, before the first byte comes back)."""
+    type: str = "llm_call_start"
+
+
+@dataclass(frozen=True)
+class StreamStart(StreamEvent):
+    type: str = "start"
+
+
+@dataclass(frozen=True)
+class TextStart(StreamEvent):
+    content_index: int = 0
+    type: str = "text_start"
+
+
+@dataclass(frozen=True)
+class TextEnd(StreamEvent):
+    content_index: int = 0
+    content: str = ""                    # the block's complete text
+    type: str = "text_end"
+
+
+@dataclass(frozen=True)
+class ThinkingStart(StreamEvent):
+    content_index: int = 0
+    type: str = "thinking_start"
+
+
+@dataclass(frozen=True)
+class ThinkingEnd(StreamEvent):
+    content_index: int = 0
+    content: str = ""
+    type: str = "thinking_end"
+
+
+@dataclass(frozen=True)
+class ToolCallDelta(StreamEvent):
+    """A piece of a tool call's arguments; ``partial_args`` is what ``parse_streaming_json`` makes of everything so far."""
+    tool_call_id: str = ""
+    delta: str = ""
+    partial_args: dict[str, Any] = field(default_factory=dict)
+    type: str = "toolcall_delta"
+
+
+@dataclass(frozen=True)
+class ToolCallError(StreamEvent):
+    """The model's arguments for a tool call were not valid JSON."""
+    tool_call_id: str = ""
+    tool_name: str = ""
+    error: str = ""
+    raw_arguments: str = ""
+    type: str = "toolcall_error"
+
+
+@dataclass(frozen=True)
+class ToolExecutionStart(StreamEvent):
+    tool_call_id: str = ""
+    tool_name: str = ""
+    type: str = "tool_execution_start"
 
 
 @dataclass(frozen=True)
@@ -327,6 +438,21 @@ class Tool:
         return {"type": "function", "function": {"name": self.function.name, "description": self.function.description,
                                                  "parameters": {"type": p.type, "properties": p.properties,
                                                                 "required": list(p.required)}}}
+
+
+class SessionStatus(Enum):
+    PENDING = "pending"
+    COMPLETED = "completed"
+    TRUNCATED = "truncated"
+    ABORTED = "aborted"
+
+
+@dataclass(frozen=True)
+class TokenInfo:
+    """One candidate of a prompt-logprob entry as inference servers report it (``{token id: {logprob, rank, decoded_token}}``)."""
+    logprob: float
+    rank: int
+    decoded_token: str
 
 
 class StopReason(Enum):

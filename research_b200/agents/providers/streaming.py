@@ -16,8 +16,9 @@ import uuid
 from dataclasses import replace
 from typing import Any, AsyncIterator, Awaitable, Callable
 
-from ..dtypes import (Actor, ChatCompletion, Choice, ImageContent, Message, RunConfig, StreamEvent, TextContent, TextDelta,
-                      ThinkingContent, ThinkingDelta, Tool, ToolCall, ToolCallContent, ToolCallEnd, ToolCallStart, Usage)
+from ..dtypes import (Actor, ChatCompletion, Choice, ImageContent, Message, RunConfig, StreamEvent, StreamStart, TextContent, TextDelta,
+                      TextEnd, TextStart, ThinkingContent, ThinkingDelta, ThinkingEnd, ThinkingStart, Tool, ToolCall, ToolCallContent,
+                      ToolCallDelta, ToolCallEnd, ToolCallError, ToolCallStart, Usage, parse_streaming_json)
 from .base import NonRetryableError, classify_http_status
 from .models import estimate_cost
 
@@ -35,6 +36,16 @@ def _loads(s: str) -> dict[str, Any]:
         return v if isinstance(v, dict) else {"value": v}
     except json.JSONDecodeError:
         return {"_raw": s}
+
+
+async def _tool_call_done(on_chunk: OnChunk, call_id: str, name: str, raw: str) -> dict[str, Any]:
+    """Parse a finished call's arguments; arguments that are not JSON are reported (``ToolCallError``) and still handed
+    on as ``{"_raw": text}``, so that the environment can answer the model with what was wrong."""
+    args = _loads(raw)
+    if "_raw" in args and len(args) == 1:
+        await _emit(on_chunk, ToolCallError(tool_call_id=call_id, tool_name=name, error="the arguments are not valid JSON", raw_arguments=raw))
+    await _emit(on_chunk, ToolCallEnd(tool_call_id=call_id, name=name, args=args))
+    return args
 
 
 def _finish(model: str, blocks: list[Any], stop: str, usage: Usage, cid: str | None = None) -> ChatCompletion:
@@ -114,12 +125,17 @@ async def aggregate_anthropic_stream(events: AsyncIterator[dict[str, Any]], mode
             u = msg.get("usage", {})
             usage = Usage(u.get("input_tokens", 0), u.get("output_tokens", 0), 0, u.get("cache_read_input_tokens", 0),
                           u.get("cache_creation_input_tokens", 0))
+            await _emit(on_chunk, StreamStart())
         elif t == "content_block_start":
             cb = ev.get("content_block", {})
             blocks[ev["index"]] = {"type": cb.get("type"), "text": cb.get("text", ""), "thinking": cb.get("thinking", ""),
                                    "signature": None, "id": cb.get("id"), "name": cb.get("name"), "json": ""}
             if cb.get("type") == "tool_use":
                 await _emit(on_chunk, ToolCallStart(tool_call_id=cb.get("id", ""), name=cb.get("name", "")))
+            elif cb.get("type") == "text":
+                await _emit(on_chunk, TextStart(content_index=ev["index"]))
+            elif cb.get("type") == "thinking":
+                await _emit(on_chunk, ThinkingStart(content_index=ev["index"]))
         elif t == "content_block_delta":
             b, d = blocks.setdefault(ev["index"], {"type": "text", "text": "", "thinking": "", "json": "", "signature": None}), ev.get("delta", {})
             if d.get("type") == "text_delta":
@@ -132,10 +148,15 @@ async def aggregate_anthropic_stream(events: AsyncIterator[dict[str, Any]], mode
                 b["signature"] = (b["signature"] or "") + d.get("signature", "")
             elif d.get("type") == "input_json_delta":
                 b["json"] += d.get("partial_json", "")
+                await _emit(on_chunk, ToolCallDelta(tool_call_id=b.get("id") or "", delta=d.get("partial_json", ""), partial_args=parse_streaming_json(b["json"])))
         elif t == "content_block_stop":
             b = blocks.get(ev["index"], {})
             if b.get("type") == "tool_use":
-                await _emit(on_chunk, ToolCallEnd(tool_call_id=b["id"], name=b["name"], args=_loads(b["json"])))
+                await _tool_call_done(on_chunk, b["id"], b["name"], b["json"])
+            elif b.get("type") == "text":
+                await _emit(on_chunk, TextEnd(content_index=ev["index"], content=b["text"]))
+            elif b.get("type") == "thinking":
+                await _emit(on_chunk, ThinkingEnd(content_index=ev["index"], content=b["thinking"]))
         elif t == "message_delta":
             stop = {"end_turn": "stop", "tool_use": "tool_calls", "max_tokens": "length"}.get(ev.get("delta", {}).get("stop_reason"), stop)
             if "usage" in ev:
@@ -158,7 +179,11 @@ async def aggregate_anthropic_stream(events: AsyncIterator[dict[str, Any]], mode
 # ------------------------------------------------------------------------------------------ OpenAI chat
 async def aggregate_openai_stream(events: AsyncIterator[dict[str, Any]], model: str, on_chunk: OnChunk = None) -> ChatCompletion:
     text, reasoning, calls, stop, usage, cid = "", "", {}, "stop", Usage(), None
+    started = False
     async for ev in events:
+        if not started:
+            started = True
+            await _emit(on_chunk, StreamStart())
         cid = cid or ev.get("id")
         if ev.get("usage"):
             u = ev["usage"]
@@ -167,13 +192,19 @@ async def aggregate_openai_stream(events: AsyncIterator[dict[str, Any]], model: 
                           (u.get("prompt_tokens_details") or {}).get("cached_tokens", 0))
         for ch in ev.get("choices", []):
             d = ch.get("delta", {})
-            if d.get("content"):
-                text += d["content"]
-                await _emit(on_chunk, TextDelta(delta=d["content"]))
             r = d.get("reasoning_content") or d.get("reasoning")
             if r:
+                if not reasoning:
+                    await _emit(on_chunk, ThinkingStart(content_index=0))
                 reasoning += r
                 await _emit(on_chunk, ThinkingDelta(delta=r))
+            if d.get("content"):
+                if not text:
+                    if reasoning:                       # the answer begins: the reasoning block is complete
+                        await _emit(on_chunk, ThinkingEnd(content_index=0, content=reasoning))
+                    await _emit(on_chunk, TextStart(content_index=1 if reasoning else 0))
+                text += d["content"]
+                await _emit(on_chunk, TextDelta(delta=d["content"]))
             for tc in d.get("tool_calls") or []:
                 slot = calls.setdefault(tc.get("index", 0), {"id": "", "name": "", "json": ""})
                 fn = tc.get("function", {})
@@ -182,18 +213,23 @@ async def aggregate_openai_stream(events: AsyncIterator[dict[str, Any]], model: 
                 if fn.get("name"):
                     slot["name"] = fn["name"]
                     await _emit(on_chunk, ToolCallStart(tool_call_id=slot["id"], name=slot["name"]))
-                slot["json"] += fn.get("arguments") or ""
+                if fn.get("arguments"):
+                    slot["json"] += fn["arguments"]
+                    await _emit(on_chunk, ToolCallDelta(tool_call_id=slot["id"], delta=fn["arguments"], partial_args=parse_streaming_json(slot["json"])))
             if ch.get("finish_reason"):
                 stop = ch["finish_reason"]
     blocks: list[Any] = []
     if reasoning:
         blocks.append(ThinkingContent(reasoning))
+        if not text:
+            await _emit(on_chunk, ThinkingEnd(content_index=0, content=reasoning))
     if text or not calls:
         blocks.append(TextContent(text))
+    if text:
+        await _emit(on_chunk, TextEnd(content_index=1 if reasoning else 0, content=text))
     for i in sorted(calls):
         c = calls[i]
-        args = _loads(c["json"])
-        await _emit(on_chunk, ToolCallEnd(tool_call_id=c["id"], name=c["name"], args=args))
+        args = await _tool_call_done(on_chunk, c["id"], c["name"], c["json"])
         blocks.append(ToolCallContent(c["id"] or f"call_{uuid.uuid4().hex[:8]}", c["name"], args))
     return _finish(model, blocks, stop, usage, cid)
 
@@ -221,24 +257,35 @@ async def aggregate_openai_responses_stream(events: AsyncIterator[dict[str, Any]
         t = ev.get("type", "")
         if t == "response.created":
             cid = ev.get("response", {}).get("id")
+            await _emit(on_chunk, StreamStart())
         elif t == "response.output_text.delta":
+            if not text:
+                await _emit(on_chunk, TextStart(content_index=1 if reasoning else 0))
             text += ev.get("delta", "")
             await _emit(on_chunk, TextDelta(delta=ev.get("delta", "")))
+        elif t == "response.output_text.done":
+            await _emit(on_chunk, TextEnd(content_index=1 if reasoning else 0, content=ev.get("text", text)))
         elif t in ("response.reasoning_summary_text.delta", "response.reasoning_text.delta"):
+            if not reasoning:
+                await _emit(on_chunk, ThinkingStart(content_index=0))
             reasoning += ev.get("delta", "")
             await _emit(on_chunk, ThinkingDelta(delta=ev.get("delta", "")))
+        elif t in ("response.reasoning_summary_text.done", "response.reasoning_text.done"):
+            await _emit(on_chunk, ThinkingEnd(content_index=0, content=ev.get("text", reasoning)))
         elif t == "response.output_item.added" and ev.get("item", {}).get("type") == "function_call":
             it = ev["item"]
             calls[it.get("id") or it.get("call_id")] = {"id": it.get("call_id") or it.get("id"), "name": it.get("name", ""), "json": it.get("arguments", "")}
             await _emit(on_chunk, ToolCallStart(tool_call_id=it.get("call_id", ""), name=it.get("name", "")))
         elif t == "response.function_call_arguments.delta":
             if ev.get("item_id") in calls:
-                calls[ev["item_id"]]["json"] += ev.get("delta", "")
+                slot = calls[ev["item_id"]]
+                slot["json"] += ev.get("delta", "")
+                await _emit(on_chunk, ToolCallDelta(tool_call_id=slot["id"] or "", delta=ev.get("delta", ""), partial_args=parse_streaming_json(slot["json"])))
         elif t == "response.output_item.done" and ev.get("item", {}).get("type") == "function_call":
             it = ev["item"]
             slot = calls.setdefault(it.get("id") or it.get("call_id"), {"id": it.get("call_id"), "name": it.get("name", ""), "json": ""})
             slot["json"] = it.get("arguments") or slot["json"]
-            await _emit(on_chunk, ToolCallEnd(tool_call_id=slot["id"], name=slot["name"], args=_loads(slot["json"])))
+            await _tool_call_done(on_chunk, slot["id"], slot["name"], slot["json"])
         elif t in ("response.completed", "response.incomplete"):
             r = ev.get("response", {})
             u = r.get("usage") or {}
@@ -286,13 +333,23 @@ def messages_to_google(messages: tuple[Message, ...]) -> tuple[str, list[dict[st
 
 async def aggregate_google_stream(events: AsyncIterator[dict[str, Any]], model: str, on_chunk: OnChunk = None) -> ChatCompletion:
     text, thinking, calls, usage, stop = "", "", [], Usage(), "stop"
+    started = False
     async for ev in events:
+        if not started:
+            started = True
+            await _emit(on_chunk, StreamStart())
         for cand in ev.get("candidates", []):
             for part in (cand.get("content") or {}).get("parts", []):
                 if "text" in part and part.get("thought"):
+                    if not thinking:
+                        await _emit(on_chunk, ThinkingStart(content_index=0))
                     thinking += part["text"]
                     await _emit(on_chunk, ThinkingDelta(delta=part["text"]))
                 elif "text" in part:
+                    if not text:
+                        if thinking:
+                            await _emit(on_chunk, ThinkingEnd(content_index=0, content=thinking))
+                        await _emit(on_chunk, TextStart(content_index=1 if thinking else 0))
                     text += part["text"]
                     await _emit(on_chunk, TextDelta(delta=part["text"]))
                 elif "functionCall" in part:
@@ -311,8 +368,12 @@ async def aggregate_google_stream(events: AsyncIterator[dict[str, Any]], model: 
     blocks: list[Any] = []
     if thinking:
         blocks.append(ThinkingContent(thinking))
+        if not text:
+            await _emit(on_chunk, ThinkingEnd(content_index=0, content=thinking))
     if text or not calls:
         blocks.append(TextContent(text))
+    if text:
+        await _emit(on_chunk, TextEnd(content_index=1 if thinking else 0, content=text))
     blocks += calls
     if calls:
         stop = "tool_calls"

@@ -27,9 +27,9 @@ from dataclasses import asdict, replace
 from typing import Any, Callable, Protocol, TextIO, runtime_checkable
 
 from ..agents.agents import run_agent
-from ..agents.dtypes import (Actor, AgentState, Endpoint, Message, RunConfig, StopReason, StreamDone, StreamError,
-                             StreamEvent, TextDelta, ThinkingDelta, ToolCall, ToolCallEnd, ToolCallStart,
-                             ToolResultReceived, Trajectory)
+from ..agents.dtypes import (Actor, AgentState, Endpoint, LLMCallStart, Message, RunConfig, StopReason, StreamDone, StreamError,
+                             StreamEvent, TextDelta, ThinkingDelta, ToolCall, ToolCallDelta, ToolCallEnd, ToolCallError, ToolCallStart,
+                             ToolExecutionStart, ToolResultReceived, Trajectory)
 
 
 @runtime_checkable
@@ -243,6 +243,7 @@ class AnsiFrontend(PlainFrontend):
         self.width = width or shutil.get_terminal_size((100, 24)).columns
         self.max_result_lines = max_result_lines
         self._fence = FenceHighlighter()
+        self._tool_names: dict[str, str] = {}
         self._editor = None                  # the prompt's line editor, created on first use at a terminal
         self.completer = None                # set by the runner: slash commands and paths
         self._loader_task: asyncio.Task | None = None
@@ -320,9 +321,23 @@ class AnsiFrontend(PlainFrontend):
             if self.show_thinking:
                 self._enter("thinking")
                 self._w(event.delta)
+        elif isinstance(event, LLMCallStart):
+            if self._mode == "":
+                self.show_loader("waiting for the model")
         elif isinstance(event, ToolCallStart):
             self._enter("")
+            self._tool_names[event.tool_call_id] = event.name
             self.show_loader(f"{event.name}: receiving arguments")
+        elif isinstance(event, ToolCallDelta):
+            if event.partial_args:                  # the arguments as far as they have arrived, in the loader line
+                name = self._tool_names.get(event.tool_call_id, "tool")
+                shown = ", ".join(f"{k}={str(v)[:40]!r}" for k, v in list(event.partial_args.items())[:3])
+                self._loader_text = f"{name}({shown[:self.width - len(name) - 12]}…"
+        elif isinstance(event, ToolCallError):
+            self._enter("")
+            self._w(f"{Theme.ERROR}{event.tool_name}: {event.error}{Theme.RESET}\n")
+        elif isinstance(event, ToolExecutionStart):
+            self.show_loader(f"running {event.tool_name}")
         elif isinstance(event, ToolCallEnd):
             self._enter("")
             self._formatted(event)                  # remembers the call for its result

@@ -530,3 +530,15 @@ def test_session_store_queries_lineage_and_delete(tmp_path):
         assert [s.session_id for s in await store.lineage(c)] == [c] and (await store.get(c))[0].parent_id == b
 
     asyncio.run(go())
+
+
+def test_agent_loop_announces_model_calls_and_tool_execution():
+    events = []
+
+    async def on_chunk(ev):
+        events.append(ev.type)
+
+    register_provider("mock", ScriptedLLM([Message("assistant", "", tool_calls=(ToolCall("c1", "add", {"value": 2}),)), "done"]))
+    asyncio.run(run_agent(_state(CalculatorEnvironment(), max_turns=3), RunConfig(on_chunk=on_chunk)))
+    kept = [e for e in events if e in ("llm_call_start", "tool_execution_start", "tool_result", "done")]
+    assert kept == ["llm_call_start", "tool_execution_start", "tool_result", "llm_call_start", "done"]

@@ -44,10 +44,12 @@ def test_anthropic_stream():
         {"type": "message_delta", "delta": {"stop_reason": "tool_use"}, "usage": {"output_tokens": 30}},
         {"type": "message_stop"},
     ]
-    seen = []
+    seen, partial = [], []
 
     async def on_chunk(ev):
         seen.append(ev.type)
+        if ev.type == "toolcall_delta":
+            partial.append(ev.partial_args)
 
     comp = _run(aggregate_anthropic_stream(_aiter(events), "claude-x", on_chunk))
     msg = comp.choices[0].message
@@ -55,7 +57,9 @@ def test_anthropic_stream():
     assert msg.text() == "Let me compute." and msg.get_tool_calls() == [ToolCall("tu_1", "calc", {"expr": "1+1"})]
     assert isinstance(msg.content[0], ThinkingContent) and msg.content[0].signature == "sig"
     assert comp.usage.input_tokens == 12 and comp.usage.output_tokens == 30 and comp.usage.cache_read_tokens == 4
-    assert seen == ["thinking_delta", "text_delta", "text_delta", "tool_call_start", "tool_call_end"]
+    assert seen == ["start", "thinking_start", "thinking_delta", "thinking_end", "text_start", "text_delta", "text_delta", "text_end",
+                    "tool_call_start", "toolcall_delta", "toolcall_delta", "tool_call_end"]
+    assert partial == [{"expr": "1"}, {"expr": "1+1"}]                   # arguments readable while they stream
 
 
 def test_openai_chat_stream():
@@ -240,3 +244,34 @@ def test_anthropic_request_credentials_thinking_and_headers(tmp_path, monkeypatc
     # no log-in: the API key travels in its own header
     asyncio.run(streaming.rollout_anthropic(Actor(actor.trajectory, Endpoint(provider="anthropic", model="claude-x", api_key="sk-key")), RunConfig()))
     assert sent["headers"]["x-api-key"] == "sk-key" and "Authorization" not in sent["headers"] and sent["payload"]["temperature"] == 1.0
+
+
+def test_fine_grained_events_partial_arguments_and_bad_json():
+    from research_b200.agents.dtypes import parse_streaming_json
+    from research_b200.agents.providers.streaming import aggregate_openai_stream
+
+    for text, want in [('{"foo": "bar"', {"foo": "bar"}), ('{"foo": "bar", "baz":', {"foo": "bar"}), ('{"nested": {"a": 1', {"nested": {"a": 1}}),
+                       ('{"arr": [1, 2', {"arr": [1, 2]}), ("", {}), ("{", {}), ('{"path": "src/ma', {"path": "src/ma"}), ('{"a": 1, "b', {"a": 1}),
+                       ('{"a": tru', {}), ('{"a": "x\\', {"a": "x"}), ("[1,2", {}), ('{"a": "say \\"hi\\", ok", "b": 2', {"a": 'say "hi", ok', "b": 2}),
+                       ('{"a": {"b": [1, {"c": 2}], "d": "e"}, "f', {"a": {"b": [1, {"c": 2}], "d": "e"}})]:
+        assert parse_streaming_json(text) == want, text
+    chunks = [{"id": "c1", "choices": [{"delta": {"reasoning_content": "think"}}]},
+              {"choices": [{"delta": {"content": "Answer"}}]},
+              {"choices": [{"delta": {"tool_calls": [{"index": 0, "id": "t1", "function": {"name": "read", "arguments": '{"path": "a'}}]}}]},
+              {"choices": [{"delta": {"tool_calls": [{"index": 0, "function": {"arguments": '.py"}'}}]}}]},
+              {"choices": [{"delta": {"tool_calls": [{"index": 1, "id": "t2", "function": {"name": "bash", "arguments": "{not json"}}]}, "finish_reason": "tool_calls"}]}]
+    seen = []
+
+    async def on_chunk(ev):
+        seen.append(ev)
+
+    comp = _run(aggregate_openai_stream(_aiter(chunks), "m", on_chunk))
+    kinds = [e.type for e in seen]
+    assert kinds == ["start", "thinking_start", "thinking_delta", "thinking_end", "text_start", "text_delta", "tool_call_start", "toolcall_delta",
+                     "toolcall_delta", "tool_call_start", "toolcall_delta", "text_end", "tool_call_end", "toolcall_error", "tool_call_end"]
+    deltas = [e for e in seen if e.type == "toolcall_delta"]
+    assert deltas[0].partial_args == {"path": "a"} and deltas[1].partial_args == {"path": "a.py"} and deltas[2].partial_args == {}
+    err = next(e for e in seen if e.type == "toolcall_error")
+    assert err.tool_name == "bash" and err.raw_arguments == "{not json" and next(e for e in seen if e.type == "text_end").content == "Answer"
+    calls = comp.choices[0].message.get_tool_calls()
+    assert calls[0].args == {"path": "a.py"} and calls[1].args == {"_raw": "{not json"}
