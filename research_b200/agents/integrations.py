@@ -172,3 +172,107 @@ async def evaluate_env(env: Any, endpoint: Any, limit: int | None = None, max_tu
     if output_dir:
         report.save(output_dir)
     return report
+
+
+class StatefulToolEnvironment:
+    """A verifiers-style *stateful tool* environment (``oai_tools`` + ``env_response(messages, state)``, e.g. a kernel
+    bench that compiles and times what the model wrote) as an agent environment (dev/integration-evaluation/configs/
+    prime_backend_bench.py:140-400): its tools are advertised as they are; a tool call is replayed to the wrapped
+    environment as an assistant message with that call and the first ``tool`` message it answers with is the result; an
+    assistant message WITHOUT tool calls is also shown to it (environments that parse code from text answer with user
+    messages, which are appended). What the wrapped code prints goes to ``logger`` instead of the terminal."""
+
+    def __init__(self, env: Any, state: dict[str, Any] | None = None, messages: list[dict[str, Any]] | None = None, logger: Any = None):
+        import logging
+
+        self.env, self.state, self.messages = env, dict(state or {}), list(messages or [])
+        self.logger = logger or logging.getLogger(f"{__name__}.{type(env).__name__}")
+
+    def get_name(self) -> str:
+        return type(self.env).__name__
+
+    def get_tools(self):
+        from .dtypes import Tool, ToolFunction, ToolFunctionParameter
+
+        out = []
+        for t in getattr(self.env, "oai_tools", None) or []:
+            if t.get("type") != "function":
+                continue
+            f = t["function"]
+            params = f.get("parameters") or {}
+            out.append(Tool(ToolFunction(f["name"], f.get("description", ""), ToolFunctionParameter(params.get("properties", {}), tuple(params.get("required", []))))))
+        return out
+
+    def requires_confirmation(self, tool_call) -> bool:
+        return False
+
+    async def _respond(self):
+        from ..utils.print_capture import intercept_prints
+
+        with intercept_prints(self.logger):
+            new_messages, new_state = await _maybe_await(self.env.env_response(list(self.messages), self.state))
+        if isinstance(new_state, dict):
+            self.state = new_state
+        new_messages = list(new_messages)
+        # either the whole conversation comes back (longer than what was sent) or only the reply
+        fresh = new_messages[len(self.messages):] if len(new_messages) > len(self.messages) and new_messages[:len(self.messages)] == self.messages else new_messages
+        self.messages += fresh
+        return fresh
+
+    async def exec_tool(self, tool_call, state: AgentState, run_config: RunConfig):
+        import json
+
+        from .dtypes import ToolResult
+
+        self.messages.append({"role": "assistant", "content": None, "tool_calls": [
+            {"id": tool_call.id, "type": "function", "function": {"name": tool_call.name, "arguments": json.dumps(tool_call.args)}}]})
+        try:
+            fresh = await self._respond()
+        except Exception as e:  # noqa: BLE001 - the environment's failure is the tool's answer
+            return ToolResult(tool_call.id, is_error=True, error=f"{type(e).__name__}: {e}")
+        reply = next((m for m in fresh if m.get("role") == "tool"), None)
+        if reply is None:
+            return ToolResult(tool_call.id, is_error=True, error="the environment gave no tool response")
+        done = bool(await _maybe_await(self.env.is_completed(self.messages, self.state))) if hasattr(self.env, "is_completed") else False
+        return ToolResult(tool_call.id, content=str(reply.get("content", "")), stop_reason=StopReason.TASK_COMPLETED if done else None,
+                          metadata={"env_state_keys": sorted(self.state)})
+
+    async def on_assistant_message(self, message: Message, state: AgentState) -> AgentState:
+        if message.get_tool_calls():
+            return state                                        # exec_tool will show the call to the environment
+        self.messages.append({"role": "assistant", "content": message.text()})
+        fresh = await self._respond()
+        if hasattr(self.env, "is_completed") and await _maybe_await(self.env.is_completed(self.messages, self.state)):
+            return replace(state, environment=self, stop=StopReason.TASK_COMPLETED)
+        replies = [Message(m.get("role", "user"), m.get("content", "")) for m in fresh if m.get("role") in ("user", "system")]
+        traj = state.actor.trajectory.append(*replies) if replies else state.actor.trajectory
+        return replace(state, actor=replace(state.actor, trajectory=traj), environment=self)
+
+    async def serialize(self) -> dict[str, Any]:
+        """The live wrapped environment cannot be stored: within a process it is found again through a token; a stored
+        session keeps the conversation it had with it (for inspection, not for resumption)."""
+        token = f"env-{id(self.env):x}"
+        _LIVE_ENVS[token] = (self.env, self.logger)
+        plain = {k: v for k, v in self.state.items() if isinstance(v, (int, float, str, bool, list, dict, type(None)))}
+        return {"type": "stateful_tool", "token": token, "messages": self.messages, "state": plain, "_state_ref": _keep(self.state)}
+
+    @staticmethod
+    async def deserialize(data: dict[str, Any]) -> "StatefulToolEnvironment":
+        env, logger = _LIVE_ENVS.get(data.get("token", ""), (None, None))
+        if env is None:
+            raise RuntimeError("the wrapped environment of this session is gone (it lives only inside the process that created it)")
+        return StatefulToolEnvironment(env, _STATES.get(data.get("_state_ref", ""), data.get("state", {})), data.get("messages", []), logger)
+
+
+_LIVE_ENVS: dict[str, tuple[Any, Any]] = {}
+_STATES: dict[str, dict[str, Any]] = {}
+
+
+def _keep(state: dict[str, Any]) -> str:
+    """Environment state may hold objects (compiled kernels, result records) that JSON cannot carry: the full dict is kept
+    in the process and referred to by a key."""
+    key = f"state-{id(state):x}-{len(_STATES)}"
+    _STATES[key] = dict(state)
+    while len(_STATES) > 256:
+        _STATES.pop(next(iter(_STATES)))
+    return key

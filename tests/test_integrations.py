@@ -164,3 +164,55 @@ def test_rate_limit_stress_run():
     auth = asyncio.run(stress(bad_key, requests=4, sleep=no_sleep))
     assert auth.failed == 4 and auth.non_retryable == 4 and auth.retries == 0
     assert main(["--requests", "20", "--concurrency", "4", "--quota", "100", "--latency", "0"]) == 0
+
+
+def test_stateful_tool_environment_adapter(caplog):
+    """A kernel-bench-like environment: one tool that 'tests' submitted code, state that keeps the best result as an
+    object, prints that must end up in the log, completion once a submission passes; and the text-only path."""
+    import asyncio
+    import logging
+
+    from research_b200.agents.agents import run_agent
+    from research_b200.agents.dtypes import Actor, AgentState, Endpoint, Message, RunConfig, StopReason, ToolCall, Trajectory
+    from research_b200.agents.integrations import StatefulToolEnvironment
+    from research_b200.agents.providers import ScriptedLLM, register_provider
+
+    class Result:                                          # not JSON-serialisable on purpose
+        def __init__(self, ok):
+            self.ok = ok
+
+    class KernelBench:
+        oai_tools = [{"type": "function", "function": {"name": "run_code", "description": "compile and test a kernel",
+                                                         "parameters": {"type": "object", "properties": {"code": {"type": "string"}}, "required": ["code"]}}}]
+
+        async def env_response(self, messages, state):
+            last = messages[-1]
+            state = dict(state)
+            if last.get("tool_calls"):
+                import json
+
+                code = json.loads(last["tool_calls"][0]["function"]["arguments"])["code"]
+                ok = "return a + b" in code
+                print(f"testing submission {len(state.get('results', [])) + 1}: {'pass' if ok else 'fail'}")
+                state["results"] = state.get("results", []) + [Result(ok)]
+                return messages + [{"role": "tool", "tool_call_id": last["tool_calls"][0]["id"], "content": "all tests pass" if ok else "wrong output for test 0"}], state
+            return [{"role": "user", "content": "Please submit code with the run_code tool."}], state
+
+        def is_completed(self, messages, state):
+            return any(r.ok for r in state.get("results", []))
+
+    env = StatefulToolEnvironment(KernelBench(), {"task": "add"})
+    assert [t.function.name for t in env.get_tools()] == ["run_code"] and env.get_tools()[0].function.parameters.required == ("code",)
+    register_provider("mock", ScriptedLLM(["I think the kernel should add the inputs.",
+                                           Message("assistant", "", tool_calls=(ToolCall("k1", "run_code", {"code": "return a - b"}),)),
+                                           Message("assistant", "", tool_calls=(ToolCall("k2", "run_code", {"code": "return a + b"}),))]))
+    with caplog.at_level(logging.INFO):
+        start = AgentState(Actor(Trajectory((Message("user", "write an add kernel"),)), Endpoint(provider="mock")), env, max_turns=6)
+        final = asyncio.run(run_agent(start, RunConfig()))[-1]
+    msgs = final.actor.trajectory.messages
+    assert final.stop == StopReason.TASK_COMPLETED and final.turn_idx == 3
+    assert [m.role for m in msgs] == ["user", "assistant", "user", "assistant", "tool", "assistant", "tool"]
+    assert "run_code tool" in msgs[2].text() and "wrong output" in msgs[4].text() and msgs[6].text() == "all tests pass"
+    kept = final.environment.state["results"]
+    assert [r.ok for r in kept] == [False, True] and isinstance(kept[0], Result)             # objects in the state survive the per-call copies
+    assert "testing submission 1: fail" in caplog.text and "testing submission 2: pass" in caplog.text
