@@ -178,3 +178,32 @@ def test_kernel_harness_checks_times_and_round_trips(tmp_path):
     assert not ok and "non-finite" in rep
     assert kh.main(["--tier", "smoke", "--backends", "reference", "--device", "cpu"]) == 0
     assert kh.main(["--list"]) == 0
+
+
+def test_ncu_long_format_summary_bottlenecks_and_comparison(tmp_path, capsys):
+    from research_b200.utils import ncu_report as nr
+
+    hdr = '"ID","Process ID","Process Name","Host Name","Kernel Name","Context","Stream","Block Size","Grid Size","Device","CC","Section Name","Metric Name","Metric Unit","Metric Value"'
+
+    def rows(i, name, grid, dur_us, sm, dram):
+        base = f'"{i}","1","python","box","{name}","1","7","(256, 1, 1)","{grid}","0","10.0","Sec",'
+        return [base + f'"gpu__time_duration.sum","us","{dur_us}"', base + f'"{nr.SM_PCT}","%","{sm}"', base + f'"{nr.DRAM_PCT}","%","{dram}"']
+
+    a = tmp_path / "a.csv"
+    a.write_text("\n".join([hdr] + rows(0, "gemm_kernel", "(148, 1, 1)", "1,200.5", 82, 35) + rows(1, "tiny_norm", "(8, 1, 1)", 45, 6, 3) +
+                           rows(2, "gemm_kernel", "(148, 1, 1)", 1100, 80, 33) + rows(3, "copy_kernel", "(592, 1, 1)", 300, 12, 88) + rows(4, "blip", "(1, 1, 1)", 2, 1, 1)) + "\n")
+    launches = nr.load_launches(str(a))
+    assert len(launches) == 5 and launches[0][nr.DURATION] == 1200.5e3 and launches[0]["grid"] == "(148, 1, 1)"
+    summary = nr.summarize_kernels(launches)
+    assert [s["kernel"] for s in summary][:2] == ["gemm_kernel", "copy_kernel"] and summary[0]["launches"] == 2 and abs(summary[0]["sm_pct"] - 81) < 1e-9
+    assert abs(sum(s["pct_total_time"] for s in summary) - 100) < 1e-6
+    slow = nr.find_bottlenecks(launches)
+    assert [b["kernel"] for b in slow] == ["tiny_norm"] and slow[0]["kind"].startswith("neither")        # copy is DRAM-bound, blip too short
+    b = tmp_path / "b.csv"
+    b.write_text("\n".join([hdr] + rows(0, "fused_kernel", "(148, 1, 1)", 1300, 85, 40)) + "\n")
+    c = nr.compare_backends(launches, nr.load_launches(str(b)))
+    assert abs(c["speedup"] - (1200.5 + 45 + 1100 + 300 + 2) / 1300) < 1e-9 and c["other"]["launches"] == 1
+    assert nr.main([str(a), str(b)]) == 0 and "speed-up 2.04x" in capsys.readouterr().out
+    assert nr.main([str(a)]) == 0
+    out = capsys.readouterr().out
+    assert "gemm_kernel" in out and "neither the SMs nor DRAM" in out and "tiny_norm" in out
