@@ -209,6 +209,36 @@ def benchmark(fn: Callable[[], Any], device: str = "cpu", warmup: int = 3, iters
 
 # -------------------------------------------------------------------------------------------------- results
 
+def profile_kernel(fn: Callable[[], Any], device: str = "cpu", warmup: int = 2, iters: int = 5, row_limit: int = 12, trace_path: str | Path | None = None) -> str:
+    """A ``torch.profiler`` table of what one backend call launches (operators on CPU, kernels with their device time on a
+    GPU), optionally with a Chrome trace written to ``trace_path`` (dev/kernels-gpumode/kernel_utils/utils.py:282-352)."""
+    from torch.profiler import ProfilerActivity, profile
+
+    for _ in range(warmup):
+        fn()
+    acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if device.startswith("cuda") else [])
+    with profile(activities=acts) as prof:
+        for _ in range(iters):
+            fn()
+        if device.startswith("cuda"):
+            torch.cuda.synchronize()
+    if trace_path is not None:
+        prof.export_chrome_trace(str(trace_path))
+    key = "cuda_time_total" if device.startswith("cuda") else "cpu_time_total"
+    return prof.key_averages().table(sort_by=key, row_limit=row_limit)
+
+
+def ncu_command(script_argv: Sequence[str], kernel_regex: str, out: str = "prof", launches: int = 3, skip: int = 0, full: bool = True,
+                sections: Sequence[str] = ("SpeedOfLight", "MemoryWorkloadAnalysis")) -> list[str]:
+    """The Nsight Compute command line for one kernel of a harness run (it is returned, not executed: profiling runs
+    where the GPU is). Clocks are left alone, the capture is bounded to ``launches`` launches of the kernels that match."""
+    cmd = ["ncu", "--clock-control", "none", "-k", f"regex:{kernel_regex}", "-c", str(launches)]
+    if skip:
+        cmd += ["-s", str(skip)]
+    cmd += ["--set", "full"] if full else [x for s in sections for x in ("--section", s)]
+    return cmd + ["-o", out, *script_argv]
+
+
 @dataclass
 class CorrectnessResult:
     case: str

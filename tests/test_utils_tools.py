@@ -207,3 +207,18 @@ def test_ncu_long_format_summary_bottlenecks_and_comparison(tmp_path, capsys):
     assert nr.main([str(a)]) == 0
     out = capsys.readouterr().out
     assert "gemm_kernel" in out and "neither the SMs nor DRAM" in out and "tiny_norm" in out
+
+
+def test_harness_profile_table_and_ncu_command(tmp_path):
+    import torch
+
+    from research_b200.utils.kernel_harness import ncu_command, profile_kernel
+
+    a = torch.randn(64, 64)
+    table = profile_kernel(lambda: (a @ a).relu_(), iters=3, trace_path=tmp_path / "trace.json")
+    assert "aten::mm" in table or "aten::matmul" in table
+    assert (tmp_path / "trace.json").stat().st_size > 100
+    cmd = ncu_command(["python", "-m", "research_b200.utils.kernel_harness", "--tier", "smoke"], "gemv", launches=2, skip=4)
+    assert cmd[:3] == ["ncu", "--clock-control", "none"] and cmd[cmd.index("-c") + 1] == "2" and cmd[cmd.index("-s") + 1] == "4" and "--set" in cmd
+    light = ncu_command(["python", "x.py"], "k", full=False)
+    assert light.count("--section") == 2 and "--set" not in light and light[-2:] == ["python", "x.py"]
