@@ -80,6 +80,45 @@ def rotary_tables(cfg: SpeedrunConfig, device=None) -> tuple[torch.Tensor, torch
     return ang.cos().to(device), ang.sin().to(device)
 
 
+class Yarn:
+    """Rotary frequencies that follow the attention window as it grows during training (dev/speedrun/single-file.py:818-849).
+    When the long window goes from ``old`` to ``new`` blocks, frequencies that complete many rotations inside the old
+    window keep their value (they encode local order) and slow ones are stretched by ``old / new`` so that the positions
+    of the new, longer window fall into the range of angles the model already knows; in between, a linear blend by the
+    number of rotations (``alpha`` .. ``beta``). The softmax scale grows with the logarithm of the window ratio."""
+
+    def __init__(self, cfg: SpeedrunConfig, attn_scale: float = 0.1):
+        self.cfg = cfg
+        q = cfg.head_dim // 4
+        freq = (1.0 / cfg.rope_base) ** torch.linspace(0, 1, q)
+        self.angular_freq = torch.cat([freq, torch.zeros(cfg.head_dim // 2 - q)])
+        self.attn_scale = attn_scale
+        self.window = None                     # the long window (in blocks) the frequencies are currently set for
+
+    def apply(self, old_window: int, new_window: int, alpha: float = 1.0, beta: float = 32.0) -> None:
+        assert old_window > 0 and new_window > 0
+        rotations = self.cfg.block_size * old_window * self.angular_freq / (2 * math.pi)
+        scaling = old_window / new_window
+        blend = torch.clamp((rotations - alpha) / (beta - alpha), 0, 1)
+        self.angular_freq = self.angular_freq * (scaling + blend * (1 - scaling))
+        self.attn_scale *= 0.2 * math.log(new_window / old_window) + 1
+        self.window = new_window
+
+    def follow(self, ws_long: int) -> bool:
+        """Call with the long window of every step: rescales when it has changed. True if it did."""
+        if self.window is None:
+            self.window = ws_long
+            return False
+        if ws_long == self.window:
+            return False
+        self.apply(self.window, ws_long)
+        return True
+
+    def tables(self, device=None) -> tuple[torch.Tensor, torch.Tensor]:
+        ang = torch.arange(self.cfg.max_seq_len, dtype=torch.float32)[:, None] * self.angular_freq[None]
+        return ang.cos().to(device), ang.sin().to(device)
+
+
 def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """``x [T, H, D]``; pairs are (i, i + D/2)."""
     c, s = cos[: x.shape[0], None, :], sin[: x.shape[0], None, :]
@@ -110,7 +149,7 @@ def _attend(q, k, v, cu_seqlens, window: int, scale: float, use_flash: bool) -> 
 
 
 def forward(w: dict[str, torch.Tensor], tokens: torch.Tensor, cfg: SpeedrunConfig, cu_seqlens: torch.Tensor | None = None,
-            ws_short: int = 3, ws_long: int = 7, attn_scale: float = 0.1, use_flash: bool = False) -> torch.Tensor:
+            ws_short: int = 3, ws_long: int = 7, attn_scale: float = 0.1, use_flash: bool = False, yarn: "Yarn | None" = None) -> torch.Tensor:
     """``tokens [T]`` (documents packed back to back, boundaries in ``cu_seqlens``) -> logits ``[T, vocab]`` in (0, 30).
     ``ws_short`` / ``ws_long`` are window lengths in blocks of ``cfg.block_size`` tokens."""
     T, L, H, D, d = tokens.shape[0], cfg.num_layers, cfg.num_heads, cfg.head_dim, cfg.dim
@@ -122,7 +161,9 @@ def forward(w: dict[str, torch.Tensor], tokens: torch.Tensor, cfg: SpeedrunConfi
     smear_lambda, backout_lambda = sc[-2], sc[-1]
     ve = [F.embedding(tokens, w[f"value_embed.{i}"]) for i in range(3)]
     ve = [None, ve[1], ve[2]] + [None] * (L - 6) + [ve[0], ve[1], ve[2]]          # . 1 2 ... 0 1 2
-    cos, sin = rotary_tables(cfg, dev)
+    cos, sin = rotary_tables(cfg, dev) if yarn is None else yarn.tables(dev)
+    if yarn is not None:
+        attn_scale = yarn.attn_scale
 
     x = F.embedding(tokens, w["embed"])
     smear = smear_lambda * torch.sigmoid(x[1:, : cfg.gate_dims] @ w["smear_gate"].T)

@@ -66,6 +66,7 @@ def train(cfg: M.SpeedrunConfig, batches: Iterator[tuple[torch.Tensor, torch.Ten
     dev = torch.device(device)
     w = {k: v.to(dev).requires_grad_(True) for k, v in M.init_weights(cfg, seed=seed).items()}
     adam, muon = make_optimizers(w, h)
+    yarn = M.Yarn(cfg, h.attn_scale)
     losses: list[float] = []
     for step in range(h.num_iterations):
         try:
@@ -73,8 +74,9 @@ def train(cfg: M.SpeedrunConfig, batches: Iterator[tuple[torch.Tensor, torch.Ten
         except StopIteration:
             break
         ws_short, ws_long = get_windows(step, h)
+        yarn.follow(ws_long)                          # the rotary frequencies and the softmax scale follow the growing window
         loss = M.loss(w, inputs.to(dev).long(), targets.to(dev).long(), cfg, cu_seqlens=cu.to(dev), ws_short=ws_short, ws_long=ws_long,
-                      attn_scale=h.attn_scale, use_flash=use_flash)
+                      use_flash=use_flash, yarn=yarn)
         loss.backward()
         mult = get_lr(step, h)
         for opt in (adam, muon):

@@ -95,3 +95,27 @@ def test_speedrun_training_driver_learns_a_repeating_stream(tmp_path):
     cfg = SpeedrunConfig(vocab_size=32, num_heads=2, head_dim=16, max_seq_len=64, block_size=8)
     _, losses = train(cfg, packed_batches([tmp_path / "s.bin"], 64, 16, BOS, loop=True), h)
     assert len(losses) == 40 and losses[0] > 3.0 and losses[-1] < 0.6 * losses[0], (losses[0], losses[-1])
+
+
+def test_yarn_follows_the_window():
+    import math
+
+    from research_b200.models.speedrun import SpeedrunConfig, Yarn, rotary_tables
+
+    cfg = SpeedrunConfig(num_layers=4, num_heads=2, head_dim=16, max_seq_len=256, block_size=16, vocab_size=64)
+    y = Yarn(cfg)
+    cos0, sin0 = y.tables()
+    ref_cos, ref_sin = rotary_tables(cfg)
+    assert torch.allclose(cos0, ref_cos) and torch.allclose(sin0, ref_sin)              # before any growth: the plain tables
+    assert not y.follow(3) and not y.follow(3) and y.attn_scale == 0.1
+    before = y.angular_freq.clone()
+    assert y.follow(6) and y.window == 6
+    rot = cfg.block_size * 3 * before / (2 * math.pi)
+    # the fastest frequency (7.6 rotations inside the old window) moves a little, slow ones are halved, zeros stay zero
+    ratio = y.angular_freq[:4] / before[:4]
+    assert rot[0] > 1 and 0.5 < float(ratio[0]) < 1.0 and torch.allclose(ratio[rot[:4] <= 1], torch.tensor(0.5)) and torch.equal(y.angular_freq[4:], torch.zeros(4))
+    assert abs(y.attn_scale - 0.1 * (0.2 * math.log(2) + 1)) < 1e-12
+    many = Yarn(SpeedrunConfig(num_layers=4, num_heads=2, head_dim=16, max_seq_len=256, block_size=128, vocab_size=64))
+    f0 = many.angular_freq.clone()
+    many.apply(8, 16)
+    assert float(many.angular_freq[0] / f0[0]) == 1.0                                      # >= 32 rotations: left alone
