@@ -654,15 +654,15 @@ def read_line_raw(editor: LineEditor, prompt: str = "> ", fd_in: int = 0, write:
             if "\x1b[200~" in pending and "\x1b[201~" not in pending:
                 continue                                             # wait for the end of a paste before interpreting it
             for key in parse_keys(pending):
-                verdict = editor.feed(key)
-                if verdict == "submit":
+                outcome = editor.feed(key)
+                if outcome == "submit":
                     editor.candidates = []
                     draw()
                     write("\r\n" * (drawn_rows - cursor_row))
                     return editor.accept()
-                if verdict == "eof":
+                if outcome == "eof":
                     raise EOFError
-                if verdict == "cancel":
+                if outcome == "cancel":
                     raise KeyboardInterrupt
             pending = ""
             draw()
