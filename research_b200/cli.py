@@ -370,7 +370,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--preset", default="chat"); p.add_argument("--cwd", default="."); p.add_argument("--store", default="")
     p.add_argument("--session", default="", help="resume this session"); p.add_argument("-p", "--prompt", default=None)
     p.add_argument("-y", "--yes", action="store_true", help="run tools without asking")
-    p.add_argument("--frontend", default="auto", choices=["auto", "plain", "json", "ansi"], help="terminal front end")
+    p.add_argument("--frontend", default="auto", choices=["auto", "plain", "json", "headless", "ansi"], help="terminal front end (headless: whole turns as JSON lines, both ways)")
     p.add_argument("-c", "--continue", dest="continue_session", action="store_true", help="resume the most recent session")
     p.add_argument("--no-session", action="store_true", help="do not store this conversation")
     p.add_argument("--system-prompt", default="", help="text, or a file holding it, that replaces the preset's system prompt")

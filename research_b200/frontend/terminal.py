@@ -419,6 +419,7 @@ class InteractiveRunner:
         self.session_tags = session_tags
         self.cwd = cwd
         self.file_commands = load_file_commands(cwd) if file_commands is None else file_commands
+        self.current_exchange: "asyncio.Future | None" = None
         if hasattr(frontend, "environment"):
             frontend.environment = environment
         if hasattr(frontend, "completer"):
@@ -535,6 +536,27 @@ class InteractiveRunner:
         return RunConfig(on_chunk=on_chunk, confirm_tool=confirm, on_input=on_input, session_store=self.store,
                          session_tags=self.session_tags)
 
+    @staticmethod
+    def _interrupt_with_sigint(task: "asyncio.Future") -> Callable[[], None]:
+        """While ``task`` runs, SIGINT cancels it instead of raising KeyboardInterrupt in the event loop. Returns the function
+        that puts the previous behaviour back. Where signal handlers cannot be installed (not the main thread, not Unix)
+        nothing changes."""
+        import signal
+
+        loop = asyncio.get_running_loop()
+        try:
+            loop.add_signal_handler(signal.SIGINT, task.cancel)
+        except (NotImplementedError, RuntimeError, ValueError):
+            return lambda: None
+
+        def restore() -> None:
+            try:
+                loop.remove_signal_handler(signal.SIGINT)
+            except (NotImplementedError, RuntimeError, ValueError):
+                pass
+
+        return restore
+
     def _publish_status(self) -> None:
         u = self.state.usage
         self.frontend.set_status(model=self.endpoint.model or self.endpoint.provider, turn=self.turns, input_tokens=u.input_tokens,
@@ -547,13 +569,25 @@ class InteractiveRunner:
         if self.store is not None and self.state.session_id:
             await self.store.append_message(self.state.session_id, traj.messages[-1])
         self.frontend.show_loader("thinking")
+        # the exchange runs as a task of its own so that ctrl-c (SIGINT) ends THIS exchange and the chat goes on: the
+        # conversation continues from the user's message, whatever the interrupted turn had produced is dropped
+        task = asyncio.ensure_future(run_agent(self.state, self._run_config()))
+        self.current_exchange = task
+        restore = self._interrupt_with_sigint(task)
         try:
-            states = await run_agent(self.state, self._run_config())
+            states = await task
             self.state = states[-1]
+        except asyncio.CancelledError:
+            if not task.cancelled():
+                raise                                # the runner itself is being cancelled
+            await self.frontend.handle_event(StreamError(error="interrupted"))
+            self.state = replace(self.state, stop=StopReason.ABORTED, pending_tool_calls=())
         except Exception as e:  # noqa: BLE001 - a provider failure ends the exchange, not the chat
             await self.frontend.handle_event(StreamError(error=f"{type(e).__name__}: {e}"))
             self.state = replace(self.state, stop=StopReason.ERROR)
         finally:
+            restore()
+            self.current_exchange = None
             self.frontend.hide_loader()
         self.turns += 1
         self._publish_status()
@@ -615,8 +649,103 @@ class InteractiveRunner:
         return self.state
 
 
+class HeadlessJsonFrontend(PlainFrontend):
+    """Turn-level NDJSON in both directions, for scripts and external user interfaces (rollouts/frontends/headless_json.py:42-413).
+    Unlike ``JsonFrontend`` (every stream event as it happens) this one speaks in whole turns::
+
+        -> {"type": "system", "subtype": "init", "session_id": "...", "tools": [...], "environment": "coding"}
+        <- {"type": "user", "text": "fix the failing test"}                 (or a bare line of text; "/quit" ends)
+        -> {"type": "assistant", "message": {"content": [{"type": "text", ...}, {"type": "tool_use", ...}]}}
+        -> {"type": "user", "message": {"content": [{"type": "tool_result", "tool_use_id": ..., "content": ..., "is_error": false}]}}
+        -> {"type": "input_request"}                                         (the agent waits for the next line)
+        -> {"type": "result", "subtype": "success", "num_turns": 2, "duration_ms": 1234, ...status}
+
+    Slash commands typed as user text are answered by the runner and appear as ``assistant`` text like any other output."""
+
+    def __init__(self, out: TextIO | None = None, inp: TextIO | None = None, include_thinking: bool = False, auto_confirm: bool = True, **_):
+        super().__init__(out, inp, include_thinking, auto_confirm)
+        self.include_thinking = include_thinking
+        self._text: list[str] = []
+        self._thinking: list[str] = []
+        self._calls: list[dict[str, Any]] = []
+        self.num_turns = 0
+        self._t0 = time.time()
+
+    def _emit(self, obj: dict[str, Any]) -> None:
+        self.out.write(json.dumps(obj, ensure_ascii=False, default=str) + "\n")
+        self.out.flush()
+
+    def _flush_turn(self) -> None:
+        content: list[dict[str, Any]] = []
+        thinking = "".join(self._thinking).strip()
+        if thinking and self.include_thinking:
+            content.append({"type": "thinking", "thinking": thinking})
+        text = "".join(self._text).strip()
+        if text:
+            content.append({"type": "text", "text": text})
+        content += self._calls
+        if content:
+            self._emit({"type": "assistant", "message": {"content": content}})
+            self.num_turns += 1
+        self._text, self._thinking, self._calls = [], [], []
+
+    async def start(self) -> None:
+        env = self.environment
+        tools = [t.function.name for t in env.get_tools()] if env is not None and hasattr(env, "get_tools") else []
+        name = env.get_name() if env is not None and hasattr(env, "get_name") else ("none" if env is None else type(env).__name__)
+        self._t0 = time.time()
+        self._emit({"type": "system", "subtype": "init", "session_id": self.status.get("session_id") or "", "tools": tools, "environment": name})
+
+    async def stop(self) -> None:
+        self._flush_turn()
+        self._emit({"type": "result", "subtype": "success", "num_turns": self.num_turns, "duration_ms": int((time.time() - self._t0) * 1000),
+                    **{k: v for k, v in self.status.items()}})
+
+    async def handle_event(self, event: StreamEvent) -> None:
+        if isinstance(event, TextDelta):
+            self._text.append(event.delta)
+        elif isinstance(event, ThinkingDelta):
+            self._thinking.append(event.delta)
+        elif isinstance(event, ToolCallEnd):
+            self._calls.append({"type": "tool_use", "id": event.tool_call_id, "name": event.name, "input": dict(event.args)})
+        elif isinstance(event, ToolResultReceived):
+            self._flush_turn()
+            self._emit({"type": "user", "message": {"content": [{"type": "tool_result", "tool_use_id": event.tool_call_id, "content": event.content,
+                                                                "is_error": event.is_error}]}})
+        elif isinstance(event, StreamDone):
+            self._flush_turn()
+        elif isinstance(event, StreamError):
+            self._flush_turn()
+            self._emit({"type": "error", "error": str(event.error)})
+
+    async def get_input(self, prompt: str = "") -> str:
+        self._flush_turn()
+        self._emit({"type": "input_request"})
+        line = await _readline(self.inp)
+        try:
+            obj = json.loads(line)
+            if isinstance(obj, dict):
+                return str(obj.get("text", obj.get("content", "")))
+        except ValueError:
+            pass
+        return line
+
+    async def confirm_tool(self, tool_call: ToolCall) -> bool:
+        if self.auto_confirm:
+            return True
+        self._flush_turn()
+        self._emit({"type": "confirm_request", "tool": tool_call.name, "input": tool_call.args, "id": tool_call.id})
+        answer = (await _readline(self.inp)).strip()
+        try:
+            obj = json.loads(answer)
+            return bool(obj.get("allow", obj.get("ok", False))) if isinstance(obj, dict) else bool(obj)
+        except ValueError:
+            return answer.lower() in ("y", "yes", "true")
+
+
 def make_frontend(kind: str, **kw: Any) -> Frontend:
-    """``plain`` | ``json`` | ``ansi`` (``auto`` = ansi on a terminal, plain otherwise)."""
+    """``plain`` | ``json`` (every event) | ``headless`` (whole turns, two-way) | ``ansi`` (``auto`` = ansi on a terminal, plain otherwise)."""
     if kind == "auto":
         kind = "ansi" if sys.stdout.isatty() else "plain"
-    return {"plain": PlainFrontend, "none": PlainFrontend, "json": JsonFrontend, "ansi": AnsiFrontend, "tui": AnsiFrontend}[kind](**kw)
+    return {"plain": PlainFrontend, "none": PlainFrontend, "json": JsonFrontend, "headless": HeadlessJsonFrontend, "ansi": AnsiFrontend,
+            "tui": AnsiFrontend}[kind](**kw)

@@ -80,3 +80,50 @@ def test_json_frontend_protocol():
     kinds = [e["type"] for e in events]
     assert kinds[0] == "start" and kinds[-1] == "stop" and "input_request" in kinds and "text_delta" in kinds and "done" in kinds
     assert next(e for e in events if e["type"] == "text_delta")["delta"] == "hello there"
+
+
+def test_headless_json_turns_and_interrupted_exchange(tmp_path):
+    """Whole turns as JSON lines in both directions; an interrupted exchange ends with an error event and the chat goes on."""
+    import asyncio
+    import io
+    import json
+
+    from research_b200.agents.dtypes import Endpoint, Message, ToolCall
+    from research_b200.agents.environments import CalculatorEnvironment
+    from research_b200.agents.providers import ScriptedLLM, register_provider
+    from research_b200.frontend.terminal import HeadlessJsonFrontend, InteractiveRunner, make_frontend
+
+    holder = {}
+
+    async def model(actor, run_config):
+        last = actor.trajectory.messages[-1]
+        if last.role == "user" and "slow" in last.text():
+            asyncio.get_running_loop().call_later(0.05, lambda: holder["runner"].current_exchange.cancel())   # what SIGINT does
+            await asyncio.sleep(30)
+        if last.role == "user" and "add" in last.text():
+            return await ScriptedLLM([Message("assistant", "Adding.", tool_calls=(ToolCall("t1", "add", {"value": 5}),))])(actor, run_config)
+        return await ScriptedLLM(["The result is 5." if last.role == "tool" else "hello"])(actor, run_config)
+
+    register_provider("headless-mock", model)
+    inp = io.StringIO('{"type": "user", "text": "add five"}\nplease be slow\n{"type": "user", "text": "/status"}\n{"type": "user", "text": "hi again"}\n/quit\n')
+    out = io.StringIO()
+    fe = make_frontend("headless", out=out, inp=inp)
+    assert isinstance(fe, HeadlessJsonFrontend)
+    runner = InteractiveRunner(Endpoint(provider="headless-mock", model="m"), fe, environment=CalculatorEnvironment(), cwd=str(tmp_path), file_commands=[])
+    holder["runner"] = runner
+    final = asyncio.run(asyncio.wait_for(runner.run(), 20))
+    events = [json.loads(line) for line in out.getvalue().splitlines()]
+    kinds = [e["type"] for e in events]
+    assert events[0] == {"type": "system", "subtype": "init", "session_id": "", "tools": [t.function.name for t in CalculatorEnvironment().get_tools()], "environment": "CalculatorEnvironment"} \
+        or events[0]["subtype"] == "init" and "add" in events[0]["tools"]
+    first = events[kinds.index("assistant")]
+    assert first["message"]["content"] == [{"type": "text", "text": "Adding."}, {"type": "tool_use", "id": "t1", "name": "add", "input": {"value": 5}}]
+    result = events[kinds.index("user")]["message"]["content"][0]
+    assert result["type"] == "tool_result" and result["tool_use_id"] == "t1" and not result["is_error"] and "5" in result["content"]
+    assert {"type": "error", "error": "interrupted"} in events
+    texts = [c["text"] for e in events if e["type"] == "assistant" for c in e["message"]["content"] if c["type"] == "text"]
+    assert texts[1] == "The result is 5." and any(t.startswith("session") for t in texts) and texts[-1] == "hello"
+    assert kinds.count("input_request") == 5 and events[-1]["type"] == "result" and events[-1]["num_turns"] >= 4
+    # the interrupted turn left no trace in the conversation except the user's message
+    roles = [m.role for m in final.actor.trajectory.messages]
+    assert roles == ["user", "assistant", "tool", "assistant", "user", "user", "assistant"] and final.actor.trajectory.messages[-1].text() == "hello"
