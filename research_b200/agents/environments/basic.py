@@ -168,6 +168,37 @@ class ComposedEnvironment:
                 return e
         return None
 
+    def get_name(self) -> str:
+        return "+".join((getattr(e, "get_name", None) or (lambda e=e: type(e).__name__.replace("Environment", "").lower()))() for e in self.envs)
+
+    def get_system_prompt(self) -> str | None:
+        """What the parts say about themselves, in order (parts that say nothing are skipped)."""
+        parts = [p for p in ((getattr(e, "get_system_prompt", None) or (lambda: None))() for e in self.envs) if p]
+        return "\n\n".join(parts) or None
+
+    async def on_session_start(self, session_id: str) -> None:
+        for e in self.envs:
+            hook = getattr(e, "on_session_start", None)
+            if hook is not None:
+                await hook(session_id)
+
+    async def on_assistant_message(self, message, state: AgentState) -> AgentState:
+        """Every part that reads assistant messages gets its turn, in order; a part sees (and must return) the COMPOSED
+        environment in ``state.environment``. A stop reason set by one part ends the chain."""
+        for i, e in enumerate(self.envs):
+            hook = getattr(e, "on_assistant_message", None)
+            if hook is None:
+                continue
+            from dataclasses import replace as _replace
+
+            out = await hook(message, _replace(state, environment=e))
+            if out.environment is not None and out.environment is not e:
+                self.envs[i] = out.environment               # a part may hand back a new copy of itself
+            state = _replace(out, environment=self)
+            if state.stop is not None:
+                break
+        return state
+
     def get_tool_formatter(self, tool_name: str):
         get = getattr(self._owner(tool_name), "get_tool_formatter", None)
         return get(tool_name) if get is not None else None
@@ -201,3 +232,11 @@ class ComposedEnvironment:
             mod, cls = item["cls"].split(":")
             envs.append(await getattr(importlib.import_module(mod), cls).deserialize(item["state"]))
         return ComposedEnvironment(envs)
+
+
+def compose(*environments: Any) -> ComposedEnvironment:
+    """``compose(a, b, c)``: one environment with the tools of all; nested compositions are flattened."""
+    flat: list[Any] = []
+    for e in environments:
+        flat += e.envs if isinstance(e, ComposedEnvironment) else [e]
+    return ComposedEnvironment(flat)

@@ -542,3 +542,19 @@ def test_agent_loop_announces_model_calls_and_tool_execution():
     asyncio.run(run_agent(_state(CalculatorEnvironment(), max_turns=3), RunConfig(on_chunk=on_chunk)))
     kept = [e for e in events if e in ("llm_call_start", "tool_execution_start", "tool_result", "done")]
     assert kept == ["llm_call_start", "tool_execution_start", "tool_result", "llm_call_start", "done"]
+
+
+def test_composed_environment_forwards_hooks_and_prompts():
+    from research_b200.agents.environments import compose
+    from research_b200.agents.environments.rlm import MessageParsingRLMEnvironment
+
+    rlm = MessageParsingRLMEnvironment(context="alpha\nbeta\ngamma")
+    env = compose(compose(CalculatorEnvironment(), BinarySearchEnvironment(target=3)), rlm)
+    assert len(env.envs) == 3 and env.get_name() == "calculator+binarysearch+repl" and "variable `context`" in env.get_system_prompt()
+    register_provider("mock", ScriptedLLM(["```repl\nn = len(context.split('\\n'))\nprint(n)\n```",
+                                           Message("assistant", "", tool_calls=(ToolCall("a1", "add", {"value": 3}),)), "FINAL_VAR(n)"]))
+    final = asyncio.run(run_agent(_state(env, max_turns=6)))[-1]
+    msgs = final.actor.trajectory.messages
+    assert final.stop == StopReason.TASK_COMPLETED and isinstance(final.environment, ComposedEnvironment)
+    assert final.environment.envs[2].final_answer == "3" and final.environment.envs[0].value == 3.0
+    assert any(m.role == "user" and "Output of block 1" in m.text() for m in msgs) and any(m.role == "tool" for m in msgs)
