@@ -184,6 +184,16 @@ async def _chat(args) -> int:
     system_prompt = preset.system_prompt
     if args.system_prompt:
         system_prompt = Path(args.system_prompt).read_text() if os.path.isfile(args.system_prompt) else args.system_prompt
+    elif args.full_prompt:
+        # assembled for this run: the preset's prompt, what the environment says about itself, the tools it really offers
+        # and the rules that follow from them, where the program's own documentation is, project context files, time, cwd
+        from .agents.prompt import build_system_prompt
+
+        probe = preset.environment(args.cwd)
+        tools = probe.get_tools() if probe is not None and hasattr(probe, "get_tools") else []
+        own = probe.get_system_prompt() if hasattr(probe, "get_system_prompt") else None
+        name = probe.get_name() if hasattr(probe, "get_name") else preset.name
+        system_prompt = build_system_prompt(name, tools, Path(args.cwd).resolve(), base_prompt=preset.system_prompt, env_system_prompt=own)
     context = [c for c in (args.context or [])] + [f"# {f}\n{Path(f).read_text()}" for f in (args.context_file or [])]
     if context:
         system_prompt = system_prompt + "\n\n" + "\n\n".join(context)
@@ -374,6 +384,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("-c", "--continue", dest="continue_session", action="store_true", help="resume the most recent session")
     p.add_argument("--no-session", action="store_true", help="do not store this conversation")
     p.add_argument("--system-prompt", default="", help="text, or a file holding it, that replaces the preset's system prompt")
+    p.add_argument("--full-prompt", action="store_true", help="assemble the system prompt from the preset, the environment's tools, project context files, time and cwd")
     p.add_argument("--context", action="append", help="extra text appended to the system prompt (repeatable)")
     p.add_argument("--context-file", action="append", help="file whose content is appended to the system prompt (repeatable)")
     p.add_argument("--stream-json", action="store_true", help="print every event as one JSON line (for programs)")

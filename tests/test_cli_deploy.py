@@ -200,3 +200,20 @@ def test_bootstrap_model_access_and_endpoint(tmp_path):
     assert ok and "could not verify" in why
     ep = server_info_to_endpoint(ServerInfo("http://10.0.0.5:30000", 1, "log", "cmd"), "org/model", engine="sglang", temperature=0.2)
     assert (ep.provider, ep.api_base, ep.model, ep.temperature) == ("sglang", "http://10.0.0.5:30000", "org/model", 0.2)
+
+
+def test_chat_full_prompt_names_the_tools_and_project_context(tmp_path, capsys):
+    from research_b200.agents.providers import register_provider
+
+    seen = {}
+
+    async def model(actor, run_config):
+        seen["system"] = actor.trajectory.messages[0].text()
+        return await ScriptedLLM(["ok"])(actor, run_config)
+
+    register_provider("prompt-mock", model)
+    (tmp_path / "AGENTS.md").write_text("always run the linter")
+    assert cli.main(["chat", "--provider", "prompt-mock", "--model", "scripted", "--preset", "explorer", "--cwd", str(tmp_path), "--no-session", "--full-prompt", "-q", "-p", "hi"]) == 0
+    s = seen["system"]
+    assert s.startswith("You are a careful software engineer") and "- grep: search file contents" in s and "READ-ONLY mode" in s
+    assert "always run the linter" in s and str(tmp_path) in s and "Working as an explorer" in s
