@@ -106,7 +106,58 @@ class _HTTPEngine:
     launch_cmd: list[str] | None = None
     log_path: str | None = None
     name: str = "http"
+    mem_fraction: float = 0.7
+    extra_args: tuple[str, ...] = ()
+    forward_log: bool = True              # a daemon thread copies the server's log lines to the Python logger
     _proc: subprocess.Popen | None = field(default=None, init=False)
+    _tail: Any = field(default=None, init=False)
+    _tail_stop: Any = field(default=None, init=False)
+
+    def default_launch_cmd(self) -> list[str] | None:
+        """The server's own command line when none was given (subclasses know theirs)."""
+        return None
+
+    def _start_log_tail(self) -> None:
+        """Follow ``log_path`` from where it is now and hand every new line to ``logging`` under ``<name>:<port>``, so that
+        the server's start-up and error messages appear in the run's own log (rollouts/training/weight_sync.py:523-553)."""
+        import logging
+        import threading
+
+        if not (self.forward_log and self.log_path):
+            return
+        log = logging.getLogger(f"{__name__}.{self.name}:{self.port}")
+        stop = self._tail_stop = threading.Event()
+        path = self.log_path
+
+        def follow() -> None:
+            try:
+                with open(path, "r", errors="replace") as f:
+                    f.seek(0, 2)
+                    pending = ""
+                    while not stop.is_set():
+                        chunk = f.read()
+                        if not chunk:
+                            stop.wait(0.2)
+                            continue
+                        pending += chunk
+                        *lines, pending = pending.split("\n")
+                        for line in lines:
+                            if line.strip():
+                                log.info(line.rstrip())
+            except OSError:
+                return
+
+        self._tail = threading.Thread(target=follow, daemon=True, name=f"{self.name}-log-tail")
+        self._tail.start()
+
+    def log_tail(self, n: int = 30) -> str:
+        if not self.log_path:
+            return ""
+        try:
+            with open(self.log_path, "r", errors="replace") as f:
+                return "".join(f.readlines()[-n:])
+        except OSError:
+            return ""
 
     @property
     def base_url(self) -> str:
@@ -114,13 +165,17 @@ class _HTTPEngine:
 
     async def launch(self) -> None:
         """Start ``launch_cmd`` as a child process (its own process group); no GPU processes are touched."""
-        if self.launch_cmd is None:
+        cmd = self.launch_cmd or self.default_launch_cmd()
+        if cmd is None:
             return
         import os
 
         env = dict(os.environ, CUDA_VISIBLE_DEVICES=",".join(map(str, self.cuda_device_ids)))
+        if self.log_path:
+            os.makedirs(os.path.dirname(os.path.abspath(self.log_path)), exist_ok=True)
         log = open(self.log_path, "ab") if self.log_path else subprocess.DEVNULL
-        self._proc = subprocess.Popen(self.launch_cmd, env=env, stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
+        self._start_log_tail()
+        self._proc = subprocess.Popen(cmd, env=env, stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
 
     async def wait_until_ready(self, timeout: float = 120.0) -> None:
         import httpx
@@ -128,7 +183,7 @@ class _HTTPEngine:
         t0 = time.time()
         while time.time() - t0 < timeout:
             if self._proc is not None and self._proc.poll() is not None:
-                raise RuntimeError(f"{self.name} server exited with code {self._proc.returncode} during start-up")
+                raise RuntimeError(f"{self.name} server exited with code {self._proc.returncode} during start-up\n--- log tail ---\n{self.log_tail()}")
             try:
                 async with httpx.AsyncClient(timeout=2.0) as c:
                     if (await c.get(f"{self.base_url}/health")).status_code == 200:
@@ -136,9 +191,11 @@ class _HTTPEngine:
             except Exception:
                 pass
             await asyncio.sleep(1.0)
-        raise TimeoutError(f"{self.name} server not ready after {timeout}s")
+        raise TimeoutError(f"{self.name} server not ready after {timeout}s\n--- log tail ---\n{self.log_tail()}")
 
     async def shutdown(self) -> None:
+        if self._tail_stop is not None:
+            self._tail_stop.set()
         if self._proc is not None and self._proc.poll() is None:
             self._proc.terminate()  # exactly the child we started
             try:
@@ -151,6 +208,15 @@ class _HTTPEngine:
 class SGLangEngine(_HTTPEngine):
     name: str = "sglang"
 
+    def default_launch_cmd(self) -> list[str]:
+        import sys
+
+        cmd = [sys.executable, "-m", "sglang.launch_server", "--model-path", self.model_name, "--host", self.host, "--port", str(self.port),
+               "--mem-fraction-static", str(self.mem_fraction), "--trust-remote-code"]
+        if len(self.cuda_device_ids) > 1:
+            cmd += ["--tp", str(len(self.cuda_device_ids))]
+        return cmd + list(self.extra_args)
+
     async def update_weights_from_checkpoint(self, checkpoint_path: str) -> dict:
         return await update_sglang_weights_from_disk(self.base_url, checkpoint_path)
 
@@ -158,6 +224,15 @@ class SGLangEngine(_HTTPEngine):
 @dataclass
 class VLLMEngine(_HTTPEngine):
     name: str = "vllm"
+
+    def default_launch_cmd(self) -> list[str]:
+        import sys
+
+        cmd = [sys.executable, "-m", "vllm.entrypoints.openai.api_server", "--model", self.model_name, "--host", self.host, "--port", str(self.port),
+               "--gpu-memory-utilization", str(self.mem_fraction), "--trust-remote-code"]
+        if len(self.cuda_device_ids) > 1:
+            cmd += ["--tensor-parallel-size", str(len(self.cuda_device_ids))]
+        return cmd + list(self.extra_args)
 
     async def update_weights_from_checkpoint(self, checkpoint_path: str) -> dict:
         return await update_vllm_weights_from_disk(self.base_url, checkpoint_path)

@@ -180,3 +180,54 @@ def test_generation_comparison_helpers():
     assert not check_logprobs_close(bare, alt, ref.logprobs).ok
     assert topn_at(fwd, [1, 2, 3], 4)[0][0] == ref.output_ids[0]
     assert check_outputs_equal([ref, ref], [ref, GenerationOutput(ref.input_ids, alt, ref.logprobs)]) == [True, False]
+
+
+def test_http_engine_lifecycle_logs_health_and_crash(tmp_path, caplog):
+    """An external inference server as a child process: default command lines, its log lines forwarded to the Python logger,
+    readiness by health poll, a start-up crash reported with the tail of its log, shutdown of exactly that child."""
+    import asyncio
+    import logging
+    import socket
+    import sys
+    import time
+
+    from research_b200.training.weight_sync import SGLangEngine, VLLMEngine
+
+    sg = SGLangEngine("org/model", port=31001, cuda_device_ids=(2, 3), mem_fraction=0.8, extra_args=("--attention-backend", "triton"))
+    cmd = sg.default_launch_cmd()
+    assert cmd[1:3] == ["-m", "sglang.launch_server"] and cmd[cmd.index("--tp") + 1] == "2" and cmd[-2:] == ["--attention-backend", "triton"]
+    assert "--tensor-parallel-size" not in VLLMEngine("m").default_launch_cmd() and "vllm.entrypoints.openai.api_server" in VLLMEngine("m").default_launch_cmd()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    server = ("import http.server, sys\nprint('loading weights', flush=True)\n"
+              "class H(http.server.BaseHTTPRequestHandler):\n"
+              "    def do_GET(self):\n        self.send_response(200 if self.path == '/health' else 404); self.end_headers()\n"
+              "    def log_message(self, *a): pass\n"
+              f"print('server ready', flush=True)\nhttp.server.HTTPServer(('127.0.0.1', {port}), H).serve_forever()\n")
+    eng = SGLangEngine("m", port=port, launch_cmd=[sys.executable, "-u", "-c", server], log_path=str(tmp_path / "logs" / "server.log"))
+
+    async def go():
+        await eng.launch()
+        await eng.wait_until_ready(timeout=30)
+        pid = eng._proc.pid
+        await asyncio.sleep(0.5)
+        await eng.shutdown()
+        return pid
+
+    with caplog.at_level(logging.INFO):
+        pid = asyncio.run(go())
+    assert eng._proc.poll() is not None and pid > 0 and "server ready" in eng.log_tail()
+    deadline = time.time() + 5
+    while "server ready" not in caplog.text and time.time() < deadline:
+        time.sleep(0.1)
+    assert "loading weights" in caplog.text and f"sglang:{port}" in caplog.text                # the child's lines reached the logger
+    bad = VLLMEngine("m", port=port, launch_cmd=[sys.executable, "-c", "print('CUDA out of memory'); raise SystemExit(3)"], log_path=str(tmp_path / "bad.log"))
+
+    async def crash():
+        await bad.launch()
+        await bad.wait_until_ready(timeout=20)
+
+    with pytest.raises(RuntimeError, match="exited with code 3") as e:
+        asyncio.run(crash())
+    assert "CUDA out of memory" in str(e.value)
