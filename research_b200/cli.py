@@ -214,9 +214,23 @@ async def _chat(args) -> int:
         tools = [t.function.name for t in env.get_tools()] if env is not None and hasattr(env, "get_tools") else []
         tags = {"fingerprint": fingerprint_session(f"{ep.provider}/{ep.model}", preset.name, tools, system_prompt, cwd=args.cwd),
                 "preset": preset.name}
+    if args.debug:
+        import logging
+
+        logging.basicConfig(level=logging.DEBUG, stream=sys.stderr, format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    if args.theme != "dark":
+        from .frontend.terminal import apply_theme
+
+        apply_theme(args.theme)
     runner = InteractiveRunner(ep, frontend, environment=env, system_prompt=system_prompt, session_store=store,
                                session_id=session_id, max_turns=preset.max_turns, initial_prompt=args.prompt,
                                single_turn=args.prompt is not None, trajectory=trajectory, session_tags=tags, cwd=args.cwd)
+    if args.thinking:
+        from .frontend.slash_commands import handle_thinking
+
+        note = handle_thinking(runner, args.thinking).message or ""
+        if note.startswith("usage"):
+            raise SystemExit(f"--thinking {args.thinking}: {note}")
     state = await runner.run()
     if state.session_id and not args.quiet:
         print(f"session: {state.session_id}", file=sys.stderr)
@@ -391,6 +405,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("-q", "--quiet", action="store_true", help="only the model's text")
     p.add_argument("--list-presets", action="store_true")
     p.add_argument("--tools", default="", choices=["", "full", "readonly", "no-write"], help="tool set of a coding preset")
+    p.add_argument("--thinking", default="", metavar="on|off|TOKENS", help="extended thinking of the model (a token budget)")
+    p.add_argument("--theme", default="dark", choices=["dark", "light", "none"], help="colours of the ANSI front end (none: no colour codes)")
+    p.add_argument("--debug", action="store_true", help="log at DEBUG level to stderr")
     p.set_defaults(fn=cmd_chat)
     p = sub.add_parser("auth", help="subscription log-in (OAuth) for a hosted provider")
     p.add_argument("action", choices=["login", "logout", "status"]); p.add_argument("name", help="configured OAuth application")

@@ -181,6 +181,22 @@ class Theme:
     CLEAR_LINE, HIDE_CURSOR, SHOW_CURSOR = "\r\x1b[2K", "\x1b[?25l", "\x1b[?25h"
 
 
+_THEMES = {
+    "dark": dict(USER="\x1b[36m", ASSISTANT="\x1b[0m", TOOL="\x1b[33m", ERROR="\x1b[31m", CODE="\x1b[32m", STATUS="\x1b[7m", DIM="\x1b[2m"),
+    # on a light background dim yellow and green wash out: darker blue / magenta, and no dimming of secondary text
+    "light": dict(USER="\x1b[34m", ASSISTANT="\x1b[0m", TOOL="\x1b[35m", ERROR="\x1b[31m", CODE="\x1b[34m", STATUS="\x1b[7m", DIM="\x1b[90m"),
+    "none": dict(USER="", ASSISTANT="", TOOL="", ERROR="", CODE="", STATUS="", DIM="", RESET="", BOLD="", ITALIC=""),
+}
+
+
+def apply_theme(name: str) -> None:
+    """Switch the colours of the ANSI front end (``dark`` | ``light`` | ``none``). Cursor and line control stay as they are."""
+    if name not in _THEMES:
+        raise ValueError(f"unknown theme {name!r}: {sorted(_THEMES)}")
+    for k, v in {"RESET": "\x1b[0m", "BOLD": "\x1b[1m", "ITALIC": "\x1b[3m", **_THEMES[name]}.items():
+        setattr(Theme, k, v)
+
+
 def _truncate(text: str, limit: int) -> str:
     return text if len(text) <= limit else text[:limit] + f"... (+{len(text) - limit} chars)"
 

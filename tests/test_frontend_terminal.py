@@ -1,4 +1,5 @@
 """Terminal front ends and the interactive chat loop, driven by scripted input and a scripted model."""
+import pytest
 
 import asyncio
 import io
@@ -127,3 +128,34 @@ def test_headless_json_turns_and_interrupted_exchange(tmp_path):
     # the interrupted turn left no trace in the conversation except the user's message
     roles = [m.role for m in final.actor.trajectory.messages]
     assert roles == ["user", "assistant", "tool", "assistant", "user", "user", "assistant"] and final.actor.trajectory.messages[-1].text() == "hello"
+
+
+def test_themes_and_thinking_flag(tmp_path):
+    import io
+
+    from research_b200 import cli
+    from research_b200.agents.providers import ScriptedLLM, register_provider
+    from research_b200.frontend import terminal
+
+    try:
+        terminal.apply_theme("none")
+        assert terminal.Theme.USER == "" and terminal.Theme.RESET == "" and terminal.box("t", ["x"], 20, terminal.Theme.TOOL).count("\x1b") == 0
+        terminal.apply_theme("light")
+        assert terminal.Theme.TOOL == "\x1b[35m" and terminal.Theme.RESET == "\x1b[0m"
+        with pytest.raises(ValueError):
+            terminal.apply_theme("neon")
+    finally:
+        terminal.apply_theme("dark")
+    assert terminal.Theme.TOOL == "\x1b[33m"
+    seen = {}
+
+    async def model(actor, run_config):
+        seen["extra"] = dict(actor.endpoint.extra_params)
+        seen["max_tokens"] = actor.endpoint.max_tokens
+        return await ScriptedLLM(["ok"])(actor, run_config)
+
+    register_provider("think-mock", model)
+    assert cli.main(["chat", "--provider", "think-mock", "--model", "m", "--no-session", "-q", "-p", "hi", "--thinking", "4096", "--cwd", str(tmp_path)]) == 0
+    assert seen["extra"]["thinking"] == {"type": "enabled", "budget_tokens": 4096} and seen["max_tokens"] >= 5120
+    with pytest.raises(SystemExit, match="usage"):
+        cli.main(["chat", "--provider", "think-mock", "--model", "m", "--no-session", "-q", "-p", "hi", "--thinking", "maybe"])
