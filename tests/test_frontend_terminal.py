@@ -1,9 +1,10 @@
 """Terminal front ends and the interactive chat loop, driven by scripted input and a scripted model."""
-import pytest
 
 import asyncio
 import io
 import json
+
+import pytest
 
 from research_b200.agents.dtypes import (Endpoint, StreamDone, TextDelta, ThinkingDelta, ToolCallEnd, ToolResultReceived)
 from research_b200.agents.environments import CalculatorEnvironment
