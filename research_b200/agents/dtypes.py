@@ -596,6 +596,8 @@ class EvalConfig:
     output_dir: str | None = None
     eval_name: str = "eval"
     run_config: RunConfig = field(default_factory=RunConfig)
+    sample_timeout_s: float | None = None        # a sample that runs longer is recorded as failed ("timeout") and the run goes on
+    show_progress: bool = False                  # one overall bar plus a line per sample in flight, on stderr
 
 
 @dataclass

@@ -195,7 +195,25 @@ def compute_summary_metrics(samples: list[EvalSample]) -> dict[str, Any]:
     return out
 
 
-async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfig) -> EvalSample:
+class _SampleTimeout(Exception):
+    pass
+
+
+def _progress_status(event: Any) -> str | None:
+    """What a sample is doing right now, from a stream event (shown beside its line of the progress display)."""
+    t = getattr(event, "type", "")
+    if t == "llm_call_start":
+        return "waiting for the model"
+    if t in ("text_delta", "thinking_delta"):
+        return "streaming"
+    if t == "tool_execution_start":
+        return f"running {getattr(event, 'tool_name', 'tool')}"
+    if t == "tool_result":
+        return "tool done"
+    return None
+
+
+async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfig, run_config: Any = None) -> EvalSample:
     """One agent run + scoring. Transient provider errors are retried with the configured delays; what is left after
     the last attempt is a ``provider_error`` sample. Any other exception makes a ``failed`` sample at once."""
     t0 = time.time()
@@ -211,7 +229,13 @@ async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfi
             if asyncio.iscoroutine(env):
                 env = await env
             state = AgentState(Actor(Trajectory(tuple(msgs)), config.endpoint), env, max_turns=config.max_turns)
-            states = await run_agent(state, config.run_config)
+            run = run_agent(state, run_config or config.run_config)
+            try:
+                states = await (asyncio.wait_for(run, config.sample_timeout_s) if config.sample_timeout_s else run)
+            except asyncio.TimeoutError:
+                if config.sample_timeout_s:          # the sample's own limit, not a provider's: no retry
+                    raise _SampleTimeout(f"no result after {config.sample_timeout_s:g} s") from None
+                raise
             final = states[-1]
             score = config.score_fn(final.actor.trajectory, row)
             if asyncio.iscoroutine(score):
@@ -227,6 +251,9 @@ async def evaluate_sample(row: dict[str, Any], sample_id: str, config: EvalConfi
                               time.time() - t0, meta)
         except NonRetryableError as e:
             last_err = f"{type(e).__name__}: {e}"
+            break
+        except _SampleTimeout as e:
+            last_err, status = f"timeout: {e}", "failed"
             break
         except (ProviderError, asyncio.TimeoutError, ConnectionError) as e:
             last_err = f"{type(e).__name__}: {e}"
@@ -273,6 +300,30 @@ async def evaluate(dataset: Iterable[dict[str, Any]], config: EvalConfig, *, res
             warn_if_changed(saved, fp, context=f"the saved run {run_dir}")
     sem = asyncio.Semaphore(config.max_concurrent)
     done = 0
+    finished: dict[str, EvalSample] = {}
+    progress = None
+    if config.show_progress:
+        from .progress import MultiProgress
+
+        progress = MultiProgress()
+        progress.add_task(config.eval_name, total=len(rows))
+
+    def sample_run_config(sid: str):
+        """The run's ``RunConfig`` with the sample's status line fed from its stream events (the caller's own ``on_chunk`` still runs)."""
+        if progress is None:
+            return None
+        from dataclasses import replace as _replace
+
+        inner = config.run_config.on_chunk
+
+        async def on_chunk(ev: Any) -> None:
+            status = _progress_status(ev)
+            if status and sid in progress.tasks:
+                progress.update(sid, advance=0, message=status)
+            if inner is not None:
+                await inner(ev)
+
+        return _replace(config.run_config, on_chunk=on_chunk)
 
     async def one(sid: str, row: dict[str, Any]) -> EvalSample:
         nonlocal done
@@ -280,19 +331,44 @@ async def evaluate(dataset: Iterable[dict[str, Any]], config: EvalConfig, *, res
             s = have[sid]
         else:
             async with sem:
-                s = await evaluate_sample(row, sid, config)
+                if progress is not None:
+                    progress.add_task(sid)
+                s = await evaluate_sample(row, sid, config, sample_run_config(sid))
+                if progress is not None:
+                    progress.finish(sid, "done" if s.status == "success" else "failed", s.error or f"reward {s.score.reward:.3g}")
+                    progress.tasks.pop(sid, None)               # finished samples leave the display; the overall bar counts them
+        finished[sid] = s
         done += 1
+        if progress is not None:
+            progress.update(config.eval_name, message=f"mean reward {sum(x.score.reward for x in finished.values()) / len(finished):.3f}")
         if on_sample_done is not None:
             on_sample_done(s, done, len(rows))
         return s
 
-    samples = list(await asyncio.gather(*[one(sid, r) for sid, r in zip(ids, rows)]))
-    report = EvalReport(config.eval_name, samples, compute_summary_metrics(samples),
-                        {"endpoint": config.endpoint.to_dict(), "max_turns": config.max_turns, "max_concurrent": config.max_concurrent,
-                         "n_retries": config.n_retries, "resumed_samples": len(have), "fingerprint": fp}, dataset_path=dataset_path)
-    if config.output_dir:
-        report.save(config.output_dir)
-    return report
+    def report_of(samples: list[EvalSample], interrupted: bool) -> EvalReport:
+        cfg = {"endpoint": config.endpoint.to_dict(), "max_turns": config.max_turns, "max_concurrent": config.max_concurrent,
+               "n_retries": config.n_retries, "resumed_samples": len(have), "fingerprint": fp}
+        if interrupted:
+            cfg.update(interrupted=True, planned_samples=len(rows))
+        r = EvalReport(config.eval_name, samples, compute_summary_metrics(samples) if samples else {}, cfg, dataset_path=dataset_path)
+        if config.output_dir:
+            r.save(config.output_dir)
+        return r
+
+    tasks = [asyncio.ensure_future(one(sid, r)) for sid, r in zip(ids, rows)]
+    try:
+        samples = list(await asyncio.gather(*tasks))
+    except (asyncio.CancelledError, KeyboardInterrupt):
+        # interrupted: stop what is in flight, keep what finished (``resume=True`` picks the run up from there)
+        for t in tasks:
+            t.cancel()
+        await asyncio.gather(*tasks, return_exceptions=True)
+        report_of([finished[sid] for sid in ids if sid in finished], interrupted=True)
+        raise
+    finally:
+        if progress is not None:
+            progress.__exit__(None, None, None)
+    return report_of(samples, interrupted=False)
 
 
 def load_jsonl(path: str | Path) -> Iterator[dict[str, Any]]:

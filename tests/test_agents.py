@@ -558,3 +558,42 @@ def test_composed_environment_forwards_hooks_and_prompts():
     assert final.stop == StopReason.TASK_COMPLETED and isinstance(final.environment, ComposedEnvironment)
     assert final.environment.envs[2].final_answer == "3" and final.environment.envs[0].value == 3.0
     assert any(m.role == "user" and "Output of block 1" in m.text() for m in msgs) and any(m.role == "tool" for m in msgs)
+
+
+def test_evaluate_sample_timeout_progress_and_partial_report_on_interrupt(tmp_path, capsys):
+    from research_b200.agents.evaluation import EvalReport, evaluate
+
+    async def model(actor, run_config):
+        text = actor.trajectory.messages[-1].text()
+        if "stuck" in text:
+            await asyncio.sleep(30)
+        if "slow" in text:
+            await asyncio.sleep(0.6)
+        return await ScriptedLLM(["4"])(actor, run_config)
+
+    register_provider("mock", model)
+    score = lambda traj, row: float(traj.messages[-1].text() == "4")                                  # noqa: E731
+    rows = [{"id": "a", "prompt": "2+2"}, {"id": "b", "prompt": "stuck forever"}, {"id": "c", "prompt": "2+2 again"}]
+    cfg = EvalConfig(endpoint=Endpoint(provider="mock"), score_fn=score, max_turns=1, n_retries=2, retry_delays=(0.01,), sample_timeout_s=0.3,
+                     show_progress=True, output_dir=str(tmp_path), eval_name="t", max_concurrent=3)
+    t0 = asyncio.run(evaluate(rows, cfg))
+    by = {s.sample_id: s for s in t0.samples}
+    assert by["b"].status == "failed" and by["b"].error.startswith("timeout") and by["b"].attempts == 1 and by["a"].score.reward == 1.0
+    err = capsys.readouterr().err
+    assert "3/3" in err and "mean reward" in err
+    # an interrupt saves what had finished; resuming completes the rest
+    rows2 = [{"id": "x", "prompt": "2+2"}, {"id": "y", "prompt": "slow one"}, {"id": "z", "prompt": "slow two"}]
+    cfg2 = EvalConfig(endpoint=Endpoint(provider="mock"), score_fn=score, max_turns=1, n_retries=0, output_dir=str(tmp_path), eval_name="cut", max_concurrent=3)
+
+    async def interrupted():
+        task = asyncio.ensure_future(evaluate(rows2, cfg2))
+        await asyncio.sleep(0.25)
+        task.cancel()
+        with pytest.raises(asyncio.CancelledError):
+            await task
+
+    asyncio.run(interrupted())
+    part = EvalReport.load(tmp_path / "cut")
+    assert [s.sample_id for s in part.samples] == ["x"] and part.config["interrupted"] and part.config["planned_samples"] == 3
+    full = asyncio.run(evaluate(rows2, cfg2, resume=True))
+    assert len(full.samples) == 3 and full.config["resumed_samples"] == 1 and "interrupted" not in full.config and full.summary["mean_reward"] == 1.0
