@@ -35,7 +35,7 @@ def schedule(waiting: list[Sequence], running: list[Sequence], num_free_blocks: 
         n = len(seq.token_ids)
         if tokens + n > config.max_tokens_per_batch:
             break
-        need = -(-n // config.block_size)
+        need = config.blocks_for(n)
         if need > blocks:
             break
         prefill.append(seq.seq_id)
@@ -49,7 +49,7 @@ def can_schedule_any(waiting: list[Sequence], running: list[Sequence], num_free_
         return True
     if not waiting:
         return False
-    return -(-len(waiting[0].token_ids) // config.block_size) <= num_free_blocks
+    return config.blocks_for(len(waiting[0].token_ids)) <= num_free_blocks
 
 
 def schedule_native(waiting: list[Sequence], running: list[Sequence], num_free_blocks: int, config: SchedulerConfig) -> SchedulerOutput:
