@@ -103,9 +103,45 @@ class AgentPresetConfig:
                            lambda cwd: factory(str(fixed) if fixed is not None else cwd, tools), self.max_turns)
 
 
+USER_PRESET_YAML = Path.home() / ".research_b200" / "presets.yaml"
+
+
+def load_yaml_presets(path: str | Path) -> dict[str, AgentPresetConfig]:
+    """Presets written as YAML: either one preset (``model: ... env: ... system_prompt: ...``) or several under their names
+    (``fast-coder: {model: ..., env: ..., system_prompt: ...}``). Unknown keys are an error (a typo must not be ignored)."""
+    import yaml
+
+    p = Path(path)
+    data = yaml.safe_load(p.read_text()) or {}
+    if not isinstance(data, dict):
+        raise TypeError(f"{p} must hold a mapping")
+    allowed = set(AgentPresetConfig.__dataclass_fields__)
+    single = "model" in data and "env" in data
+    out = {}
+    for name, body in ({data.get("name", p.stem): data} if single else data).items():
+        if not isinstance(body, dict):
+            raise TypeError(f"{p}: preset {name!r} must be a mapping")
+        unknown = set(body) - allowed
+        if unknown:
+            raise KeyError(f"{p}: preset {name!r} has unknown field(s) {sorted(unknown)}; allowed: {sorted(allowed)}")
+        fields_ = {"name": name, **body}
+        if fields_.get("working_dir") is not None:
+            fields_["working_dir"] = Path(fields_["working_dir"]).expanduser()
+        missing = [k for k in ("model", "env", "system_prompt") if k not in fields_]
+        if missing:
+            raise KeyError(f"{p}: preset {name!r} lacks {missing}")
+        out[name] = AgentPresetConfig(**fields_)
+    return out
+
+
 def _load_preset_file(path: Path) -> AgentPresetConfig:
     if path.suffix == ".json":
         return AgentPresetConfig.load(path)
+    if path.suffix in (".yaml", ".yml"):
+        found = load_yaml_presets(path)
+        if len(found) != 1:
+            raise KeyError(f"{path} defines {len(found)} presets ({sorted(found)}): name one of them instead of the file")
+        return next(iter(found.values()))
     if path.parent.resolve() == PRESET_DIR:      # shipped presets are package modules: relative imports of a parent work
         module = importlib.import_module(f"{__package__}.preset_files.{path.stem}")
     else:
@@ -137,11 +173,16 @@ def load_preset(name: str, preset_dir: str | Path | None = None) -> AgentPresetC
     """By file path (``~/presets/mine.py``, ``.json``), by full file name (``careful_coder_01_01``) or by the name
     without numbers (``careful_coder``: the highest-numbered file of that stem wins, i.e. the latest variant)."""
     p = Path(name).expanduser()
-    if p.suffix in (".py", ".json") or "/" in name:
+    if p.suffix in (".py", ".json", ".yaml", ".yml") or "/" in name:
         if not p.is_file():
             raise FileNotFoundError(f"preset file not found: {p}")
         return _load_preset_file(p)
     dirs = [Path(preset_dir)] if preset_dir is not None else [USER_PRESET_DIR, PRESET_DIR]
+    for y in ([d / "presets.yaml" for d in dirs] if preset_dir is not None else [USER_PRESET_YAML]):
+        if y.is_file():
+            found = load_yaml_presets(y)
+            if name in found:
+                return found[name]
     for d in dirs:
         if (d / f"{name}.py").is_file():
             return _load_preset_file(d / f"{name}.py")

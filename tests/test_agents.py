@@ -597,3 +597,25 @@ def test_evaluate_sample_timeout_progress_and_partial_report_on_interrupt(tmp_pa
     assert [s.sample_id for s in part.samples] == ["x"] and part.config["interrupted"] and part.config["planned_samples"] == 3
     full = asyncio.run(evaluate(rows2, cfg2, resume=True))
     assert len(full.samples) == 3 and full.config["resumed_samples"] == 1 and "interrupted" not in full.config and full.summary["mean_reward"] == 1.0
+
+
+def test_yaml_presets(tmp_path):
+    from research_b200.agents import presets
+
+    (tmp_path / "presets.yaml").write_text("fast-coder:\n  model: anthropic/claude-haiku-4-5\n  env: coding\n  tools: readonly\n  system_prompt: |\n    Be quick.\n    Be right.\n"
+                                           "careful-coder:\n  model: openai/gpt-5.1\n  env: calculator\n  system_prompt: slow\n  temperature: 0.1\n")
+    both = presets.load_yaml_presets(tmp_path / "presets.yaml")
+    assert set(both) == {"fast-coder", "careful-coder"} and both["fast-coder"].system_prompt == "Be quick.\nBe right.\n" and both["careful-coder"].temperature == 0.1
+    fast = presets.load_preset("fast-coder", tmp_path)
+    assert fast.tools == "readonly" and [t.function.name for t in fast.to_preset().environment(str(tmp_path)).get_tools()] == ["read", "list", "glob", "grep"]
+    (tmp_path / "one.yml").write_text("model: m/x\nenv: none\nsystem_prompt: hi\nworking_dir: ~/proj\n")
+    one = presets.load_preset(str(tmp_path / "one.yml"))
+    assert one.name == "one" and one.working_dir == (presets.Path.home() / "proj")
+    with pytest.raises(KeyError, match="defines 2 presets"):
+        presets.load_preset(str(tmp_path / "presets.yaml"))
+    (tmp_path / "typo.yaml").write_text("model: m/x\nenv: none\nsystem_prompt: hi\ntemprature: 0.3\n")
+    with pytest.raises(KeyError, match="temprature"):
+        presets.load_preset(str(tmp_path / "typo.yaml"))
+    (tmp_path / "short.yaml").write_text("p:\n  model: m/x\n  env: none\n")
+    with pytest.raises(KeyError, match="system_prompt"):
+        presets.load_yaml_presets(tmp_path / "short.yaml")
