@@ -166,7 +166,14 @@ _NUMBERED = re.compile(r"^(?P<stem>.+)_(?P<id>\d+)_(?P<parent>\d+)$")
 def list_presets(preset_dir: str | Path | None = None) -> list[str]:
     """Names of the preset files (without ``.py``) of ``preset_dir``; by default the shipped ones, then the user's."""
     dirs = [Path(preset_dir)] if preset_dir is not None else [PRESET_DIR, USER_PRESET_DIR]
-    return [f.stem for d in dirs if d.is_dir() for f in sorted(d.glob("*.py")) if not f.name.startswith("_")]
+    names = [f.stem for d in dirs if d.is_dir() for f in sorted(d.glob("*.py")) if not f.name.startswith("_")]
+    for y in ([d / "presets.yaml" for d in dirs] if preset_dir is not None else [USER_PRESET_YAML]):
+        if y.is_file():
+            try:
+                names += sorted(load_yaml_presets(y))
+            except (KeyError, TypeError, ValueError):
+                pass                                   # a broken file is reported when a preset of it is asked for
+    return names
 
 
 def load_preset(name: str, preset_dir: str | Path | None = None) -> AgentPresetConfig:

@@ -606,6 +606,7 @@ def test_yaml_presets(tmp_path):
                                            "careful-coder:\n  model: openai/gpt-5.1\n  env: calculator\n  system_prompt: slow\n  temperature: 0.1\n")
     both = presets.load_yaml_presets(tmp_path / "presets.yaml")
     assert set(both) == {"fast-coder", "careful-coder"} and both["fast-coder"].system_prompt == "Be quick.\nBe right.\n" and both["careful-coder"].temperature == 0.1
+    assert presets.list_presets(tmp_path) == ["careful-coder", "fast-coder"]
     fast = presets.load_preset("fast-coder", tmp_path)
     assert fast.tools == "readonly" and [t.function.name for t in fast.to_preset().environment(str(tmp_path)).get_tools()] == ["read", "list", "glob", "grep"]
     (tmp_path / "one.yml").write_text("model: m/x\nenv: none\nsystem_prompt: hi\nworking_dir: ~/proj\n")
