@@ -620,3 +620,88 @@ def test_yaml_presets(tmp_path):
     (tmp_path / "short.yaml").write_text("p:\n  model: m/x\n  env: none\n")
     with pytest.raises(KeyError, match="system_prompt"):
         presets.load_yaml_presets(tmp_path / "short.yaml")
+
+
+def test_abort_between_tools_keeps_the_queue_and_cancellation_marks_the_session(tmp_path):
+    """A cancel request during a turn with several tool calls stops before the next call and leaves the remaining calls
+    queued; the state can be run again to finish them. Cancelling the task itself records the session as aborted."""
+    import threading
+
+    cancel = threading.Event()
+    store = FileSessionStore(tmp_path)
+
+    class Slow(CalculatorEnvironment):
+        async def exec_tool(self, tool_call, state, run_config):
+            out = await super().exec_tool(tool_call, state, run_config)
+            cancel.set()                                  # the user asks to stop while the first tool runs
+            return out
+
+        @staticmethod
+        async def deserialize(data):
+            e = Slow()
+            e.value = data.get("value", 0.0)
+            return e
+
+    three = Message("assistant", "", tool_calls=(ToolCall("c1", "add", {"value": 1}), ToolCall("c2", "add", {"value": 2}), ToolCall("c3", "add", {"value": 3})))
+    register_provider("mock", ScriptedLLM([three, "done"]))
+    states = asyncio.run(run_agent(_state(Slow(), max_turns=4), RunConfig(cancel_event=cancel, session_store=store)))
+    st = states[-1]
+    assert st.stop == StopReason.ABORTED and st.next_tool_idx == 1 and [c.id for c in st.pending_tool_calls] == ["c1", "c2", "c3"]
+    assert [m.tool_call_id for m in st.actor.trajectory.messages if m.role == "tool"] == ["c1"] and st.environment.value == 1.0
+    session, stored = asyncio.run(store.get(st.session_id))
+    assert session.status == "aborted" and [m.role for m in stored] == ["user", "assistant", "tool"]
+    # carry on from exactly there: the two remaining calls run, then the model finishes
+    cancel.clear()
+    again = asyncio.run(run_agent(replace(st, stop=None, environment=CalculatorEnvironment(value=st.environment.value)), RunConfig(session_store=store)))[-1]
+    assert again.stop == StopReason.NO_TOOL_CALLS and again.environment.value == 6.0
+    assert [m.tool_call_id for m in again.actor.trajectory.messages if m.role == "tool"] == ["c1", "c2", "c3"]
+    # a resumed session (fresh process) finds the unanswered calls from the stored messages alone
+    sid = asyncio.run(store.create({"provider": "mock"}, {"value": 1.0}))
+    for m in stored:
+        asyncio.run(store.append_message(sid, m))
+    resumed = asyncio.run(resume_session(sid, store, Endpoint(provider="mock"), CalculatorEnvironment))
+    assert [c.id for c in resumed.pending_tool_calls] == ["c2", "c3"]
+
+    async def hang(actor, run_config):
+        await asyncio.sleep(30)
+
+    register_provider("mock", hang)
+
+    async def cancelled():
+        task = asyncio.ensure_future(run_agent(_state(CalculatorEnvironment()), RunConfig(session_store=store)))
+        await asyncio.sleep(0.1)
+        task.cancel()
+        with pytest.raises(asyncio.CancelledError):
+            await task
+
+    asyncio.run(cancelled())
+    # three sessions by now: the first one went on to finish, the copy made for resuming was never run, the cancelled one
+    assert sorted(s.status for s in asyncio.run(store.list())) == ["aborted", "active", "no_tool_calls"]
+
+
+def test_conversation_moves_between_providers():
+    """A conversation produced through one provider (thinking blocks with signatures, tool calls with that provider's ids, one
+    call left unanswered by an interruption) is made acceptable to the others and converts to their wire formats."""
+    from research_b200.agents.dtypes import TextContent, ThinkingContent, ToolCallContent
+    from research_b200.agents.providers import messages_to_anthropic, messages_to_openai
+    from research_b200.agents.transform_messages import transform_messages
+
+    convo = [Message("system", "be brief"), Message("user", "what is in a.py and b.py?"),
+             Message("assistant", [ThinkingContent("I should read both", "sig-abc"), TextContent("Reading."),
+                                   ToolCallContent("toolu_01", "read", {"path": "a.py"}), ToolCallContent("toolu_02", "read", {"path": "b.py"})]),
+             Message("tool", "print('a')", tool_call_id="toolu_01", name="read")]            # toolu_02 never got its result
+    same = transform_messages(convo, source=("anthropic", "claude-x"), target=("anthropic", "claude-x"))
+    assert isinstance(same[2].content[0], ThinkingContent) and same[2].content[0].signature == "sig-abc" and len(same) == 5
+    moved = transform_messages(convo, source=("anthropic", "claude-x"), target=("openai", "gpt-y"))
+    assert not any(isinstance(b, ThinkingContent) for b in moved[2].content) and [m.role for m in moved] == ["system", "user", "assistant", "tool", "tool"]
+    assert moved[4].tool_call_id == "toolu_02" and "interrupted" in moved[4].text()
+    oai = messages_to_openai(Actor(Trajectory(tuple(moved)), Endpoint(provider="openai")))
+    calls = oai[2]["tool_calls"]
+    assert [c["id"] for c in calls] == ["toolu_01", "toolu_02"] and json.loads(calls[0]["function"]["arguments"]) == {"path": "a.py"}
+    assert [m["role"] for m in oai] == ["system", "user", "assistant", "tool", "tool"] and oai[3]["tool_call_id"] == "toolu_01"
+    # and back: an OpenAI-made conversation (reasoning text without a signature) goes to Anthropic with the reasoning inlined
+    from_oai = [Message("user", "2+2?"), Message("assistant", [ThinkingContent("simple sum"), TextContent("4")]), Message("user", "and 3+3?")]
+    to_claude = transform_messages(from_oai, source=("openai", "gpt-y"), target=("anthropic", "claude-x"), inline_thinking="<thinking>{thinking}</thinking>")
+    system, msgs = messages_to_anthropic(tuple(to_claude))
+    flat = json.dumps(msgs)
+    assert system == "" and "<thinking>simple sum</thinking>" in flat and '"type": "thinking"' not in flat and [m["role"] for m in msgs] == ["user", "assistant", "user"]
