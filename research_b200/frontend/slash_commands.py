@@ -45,6 +45,8 @@ BUILTIN_COMMANDS = [SlashCommand("help", "what can be typed here"), SlashCommand
                     SlashCommand("save", "write the conversation to a JSONL file", "<file>"), SlashCommand("retry", "resend the last user message"),
                     SlashCommand("slice", "continue on a sliced copy of the conversation", "[0:5, summarize:5:20, 20:]"),
                     SlashCommand("env", "show or switch the environment", "[name]"), SlashCommand("commands", "list all commands"),
+                    SlashCommand("session", "list recent sessions, or continue in another one", "[id]"),
+                    SlashCommand("branch", "fork the conversation here (or after N messages) into a new session", "[n]"),
                     SlashCommand("quit", "leave")]
 
 
@@ -219,3 +221,54 @@ async def handle_env(runner: Any, arg: str) -> SlashCommandResult:
     runner.set_environment(env)
     return SlashCommandResult(message=f"environment: {name} (tools: {', '.join(t.function.name for t in env.get_tools()) or 'none'})",
                               persist={"env": name})
+
+
+async def handle_session(runner: Any, arg: str) -> SlashCommandResult:
+    """No argument: the ten most recent sessions. An id (a unique prefix is enough): continue in that session, with its
+    messages, its endpoint settings where they were stored, and its environment restored from what the session recorded."""
+    from ..agents.agents import resume_session
+    from ..agents.doctor import format_time_ago
+    from ..agents.dtypes import Endpoint
+
+    if runner.store is None:
+        return SlashCommandResult(message="this chat stores no sessions (--no-session)")
+    sessions = sorted(await runner.store.list(), key=lambda s: s.updated_at, reverse=True)
+    arg = arg.strip()
+    if not arg:
+        rows = [f"{'*' if s.session_id == runner.state.session_id else ' '} {s.session_id}  {s.num_messages:>3} msgs  {format_time_ago(s.updated_at):>9}  "
+                f"{s.endpoint.get('model', '?')}" for s in sessions[:10]]
+        return SlashCommandResult(message="\n".join(rows) or "no sessions yet")
+    hits = [s for s in sessions if s.session_id.startswith(arg)]
+    if len(hits) != 1:
+        return SlashCommandResult(message=f"{len(hits)} sessions match {arg!r}" + (": " + ", ".join(s.session_id for s in hits[:5]) if hits else ""))
+    target = hits[0]
+    stored = {k: v for k, v in target.endpoint.items() if k in Endpoint.__dataclass_fields__ and k not in ("api_key", "oauth_token", "engine")}
+    endpoint = replace(runner.endpoint, **stored) if stored.get("provider") == runner.endpoint.provider else runner.endpoint
+    env_cls = type(runner.environment) if runner.environment is not None else None
+    try:
+        state = await resume_session(target.session_id, runner.store, endpoint, env_cls if target.environment is not None else None, runner.max_turns)
+    except Exception as e:  # noqa: BLE001 - a session written by another environment type, a damaged file ...
+        return SlashCommandResult(message=f"cannot continue {target.session_id}: {type(e).__name__}: {e}")
+    runner.set_endpoint(endpoint)
+    if state.environment is not None:
+        runner.set_environment(state.environment)
+    runner.state = replace(state, environment=runner.environment, stop=None)
+    return SlashCommandResult(message=f"now in session {target.session_id} ({len(state.actor.trajectory.messages)} messages, model {endpoint.model or endpoint.provider})")
+
+
+async def handle_branch(runner: Any, arg: str) -> SlashCommandResult:
+    if runner.store is None or not runner.state.session_id:
+        return SlashCommandResult(message="nothing stored to branch from yet")
+    msgs = runner.state.actor.trajectory.messages
+    try:
+        n = int(arg) if arg.strip() else len(msgs)
+    except ValueError:
+        return SlashCommandResult(message="usage: /branch [number of messages to keep]")
+    if not 0 < n <= len(msgs):
+        return SlashCommandResult(message=f"keep between 1 and {len(msgs)} messages")
+    from ..agents.dtypes import Actor, Trajectory
+
+    parent = runner.state.session_id
+    sid = await runner.store.branch(parent, n)
+    runner.state = replace(runner.state, actor=Actor(Trajectory(tuple(msgs[:n])), runner.endpoint), session_id=sid, stop=None, pending_tool_calls=())
+    return SlashCommandResult(message=f"branched after message {n}: now in session {sid} (parent {parent})")

@@ -419,6 +419,8 @@ HELP = """/help               this text
 /retry              drop the last assistant turn and ask again
 /slice SPEC         continue on a sliced copy (0:4, summarize:4:20, 20:)
 /env [NAME]         show or switch the environment (the agent's tools)
+/session [ID]       recent sessions, or continue in another one
+/branch [N]         fork the conversation (after N messages) into a new session
 /commands           every command, including those from .research_b200/commands/*.md"""
 
 
@@ -453,7 +455,8 @@ class InteractiveRunner:
         self.commands: dict[str, Callable[[str], Any]] = {
             "help": self._cmd_help, "clear": self._cmd_clear, "model": self._cmd_model, "temperature": self._cmd_temperature,
             "thinking": self._cmd_thinking, "status": self._cmd_status, "save": self._cmd_save, "retry": self._cmd_retry,
-            "slice": self._cmd_slice, "env": self._cmd_env, "commands": self._cmd_commands}
+            "slice": self._cmd_slice, "env": self._cmd_env, "commands": self._cmd_commands, "session": self._cmd_session,
+            "branch": self._cmd_branch}
 
     # ---- slash commands: return text to print; "retry" returns a prompt to resend
     def _cmd_help(self, arg: str) -> str:
@@ -505,6 +508,16 @@ class InteractiveRunner:
         from .slash_commands import handle_env
 
         return handle_env(self, arg)
+
+    def _cmd_session(self, arg: str):
+        from .slash_commands import handle_session
+
+        return handle_session(self, arg)
+
+    def _cmd_branch(self, arg: str):
+        from .slash_commands import handle_branch
+
+        return handle_branch(self, arg)
 
     def _cmd_commands(self, arg: str) -> str:
         from .slash_commands import BUILTIN_COMMANDS

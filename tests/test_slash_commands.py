@@ -76,3 +76,48 @@ def test_runner_commands_thinking_slice_env_and_file_prompt(tmp_path):
     assert "thinking" not in ep.extra_params and ep.reasoning_effort is None
     sc.handle_thinking(runner, "20000")
     assert sc.thinking_budget(runner.endpoint) == 20000 and runner.endpoint.reasoning_effort == "high" and runner.endpoint.max_tokens >= 21024
+
+
+def test_session_switch_and_branch(tmp_path):
+    store = FileSessionStore(tmp_path / "sessions")
+
+    async def seed():
+        sid = await store.create({"provider": "slash-mock", "model": "older-model", "temperature": 0.3})
+        for m in (Message("user", "earlier question"), Message("assistant", "earlier answer")):
+            await store.append_message(sid, m)
+        return sid
+
+    old = asyncio.run(seed())
+    seen = []
+
+    async def model(actor, run_config):
+        seen.append(actor)
+        return await ScriptedLLM([f"reply {len(seen)}"])(actor, run_config)
+
+    register_provider("slash-mock", model)
+    lines = iter(["hello", "/session", f"/session {old[:8]}", f"/session {old}", "and now?", "/branch 2", "different follow-up", "/session nope", "/quit"])
+    out = io.StringIO()
+
+    class Scripted(PlainFrontend):
+        async def get_input(self, prompt=""):
+            return next(lines)
+
+    runner = InteractiveRunner(Endpoint(provider="slash-mock", model="m"), Scripted(out=out), session_store=store, cwd=str(tmp_path), file_commands=[])
+    asyncio.run(runner.run())
+    text = out.getvalue()
+    assert f"now in session {old} (2 messages, model older-model)" in text and "0 sessions match 'nope'" in text and old in text.split("now in session")[0]
+    assert f"2 sessions match '{old[:8]}'" in text                     # a prefix that two sessions share switches nothing
+    # after the switch the model saw the old conversation with the stored model and temperature
+    after_switch = seen[1]
+    assert [m.text() for m in after_switch.trajectory.messages] == ["earlier question", "earlier answer", "and now?"]
+    assert after_switch.endpoint.model == "older-model" and after_switch.endpoint.temperature == 0.3
+    # the branch kept two messages, continued in a child session, and left the old session as it was
+    assert [m.text() for m in seen[2].trajectory.messages] == ["earlier question", "earlier answer", "different follow-up"]
+
+    async def check():
+        sessions = {s.session_id: s for s in await store.list()}
+        child = next(s for s in sessions.values() if s.parent_id == old)
+        assert child.branch_point == 2 and [m.text() for m in (await store.get(child.session_id))[1]][-2:] == ["different follow-up", "reply 3"]
+        assert [m.text() for m in (await store.get(old))[1]] == ["earlier question", "earlier answer", "and now?", "reply 2"]
+
+    asyncio.run(check())
