@@ -55,7 +55,25 @@ ENVIRONMENTS: dict[str, Callable[[str, Any], Any]] = {
     "browsing": lambda cwd, tools: BrowsingEnvironment(),
     "repl": lambda cwd, tools: REPLEnvironment(),
     "research": lambda cwd, tools: ComposedEnvironment([BrowsingEnvironment(), REPLEnvironment()]),
+    "ask_user": lambda cwd, tools: AskUserQuestionEnvironment(),
 }
+
+
+def environment_from_spec(spec: str, cwd: str = ".", tools: Any = None) -> Any:
+    """``coding`` or ``coding+ask_user+browsing``: one environment, or the composition of several (``+`` as on the command
+    line of the reference: rollouts/toolslash_spec.md). Unknown names are an error that lists the known ones."""
+    from .environments import compose
+
+    names = [n.strip() for n in spec.split("+") if n.strip()]
+    if not names:
+        raise KeyError("empty environment spec")
+    unknown = [n for n in names if n not in ENVIRONMENTS]
+    if unknown:
+        raise KeyError(f"unknown environment(s) {unknown}; available: {sorted(ENVIRONMENTS)}")
+    if len(set(names)) != len(names):
+        raise KeyError(f"an environment appears twice in {spec!r}")
+    built = [ENVIRONMENTS[n](cwd, tools) for n in names]
+    return built[0] if len(built) == 1 else compose(*built)
 PRESET_DIR = Path(__file__).resolve().parent / "preset_files"
 USER_PRESET_DIR = Path.home() / ".research_b200" / "presets"
 

@@ -177,6 +177,13 @@ async def _chat(args) -> int:
         from .agents.presets import ENVIRONMENTS
 
         preset = AgentPreset(preset.name, preset.description, preset.system_prompt, lambda cwd: ENVIRONMENTS[args.preset](cwd, args.tools), preset.max_turns)
+    if args.env:
+        # --env coding+ask_user: the preset's prompt and turn budget, with these environments instead of the preset's own
+        from .agents.presets import environment_from_spec
+
+        environment_from_spec(args.env, args.cwd, args.tools or None)          # fail now on a bad spec
+        preset = AgentPreset(preset.name, preset.description, preset.system_prompt, lambda cwd: environment_from_spec(args.env, cwd, args.tools or None),
+                             max(preset.max_turns, 30))
     ep = _endpoint(args)
     store = None if args.no_session else _store(args)
     frontend = make_frontend("json" if args.stream_json else ("plain" if args.quiet and args.frontend == "auto" else args.frontend),
@@ -405,6 +412,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("-q", "--quiet", action="store_true", help="only the model's text")
     p.add_argument("--list-presets", action="store_true")
     p.add_argument("--tools", default="", choices=["", "full", "readonly", "no-write"], help="tool set of a coding preset")
+    p.add_argument("--env", default="", metavar="A+B", help="environment(s) to use instead of the preset's, combined with + (coding+ask_user)")
     p.add_argument("--thinking", default="", metavar="on|off|TOKENS", help="extended thinking of the model (a token budget)")
     p.add_argument("--theme", default="dark", choices=["dark", "light", "none"], help="colours of the ANSI front end (none: no colour codes)")
     p.add_argument("--debug", action="store_true", help="log at DEBUG level to stderr")

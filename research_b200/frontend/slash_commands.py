@@ -200,27 +200,44 @@ def current_env_name(env: Any) -> str:
 
 
 async def handle_env(runner: Any, arg: str) -> SlashCommandResult:
-    from ..agents.presets import ENVIRONMENTS
+    """``/env``: what is active. ``/env list``: what exists. ``/env coding+ask_user [tool preset]``: switch, in a child session
+    that branches from here (the parent keeps the conversation as it was under the old tools)."""
+    from ..agents.presets import ENVIRONMENTS, environment_from_spec
 
     arg = arg.strip()
+    current = getattr(runner, "env_spec", None) or current_env_name(runner.environment)
     if not arg:
         tools = [t.function.name for t in runner.environment.get_tools()] if runner.environment is not None else []
-        return SlashCommandResult(message=f"environment: {current_env_name(runner.environment)} (tools: {', '.join(tools) or 'none'}); "
+        return SlashCommandResult(message=f"environment: {current} (tools: {', '.join(tools) or 'none'}); "
                                           f"available: {', '.join(sorted(ENVIRONMENTS))}")
-    name, _, tools = arg.partition(" ")
-    if name not in ENVIRONMENTS:
-        near = find_similar_command(name, sorted(ENVIRONMENTS))
-        return SlashCommandResult(message=f"unknown environment {name!r}" + (f" (did you mean {near}?)" if near else "") +
-                                          f"; available: {', '.join(sorted(ENVIRONMENTS))}")
+    if arg == "list":
+        return SlashCommandResult(message="available environments (combine with +):\n" + "\n".join(f"  {n}" for n in sorted(ENVIRONMENTS)))
+    spec, _, tools = arg.partition(" ")
+    if spec == current and not tools.strip():
+        return SlashCommandResult(message=f"already using env: {spec}")
     try:
-        env = ENVIRONMENTS[name](runner.cwd, tools.strip() or None)
+        env = environment_from_spec(spec, runner.cwd, tools.strip() or None)
+    except KeyError as e:
+        first = spec.split("+")[0]
+        near = find_similar_command(first, sorted(ENVIRONMENTS)) if first not in ENVIRONMENTS else None
+        return SlashCommandResult(message=str(e).strip("'\"") + (f" (did you mean {near}?)" if near else ""))
     except ValueError as e:
         return SlashCommandResult(message=str(e))
     if hasattr(env, "on_session_start"):
         await env.on_session_start(runner.state.session_id or "chat")
     runner.set_environment(env)
-    return SlashCommandResult(message=f"environment: {name} (tools: {', '.join(t.function.name for t in env.get_tools()) or 'none'})",
-                              persist={"env": name})
+    runner.env_spec = spec
+    note = ""
+    if runner.store is not None and runner.state.session_id:
+        msgs = runner.state.actor.trajectory.messages
+        child = await runner.store.create(runner.endpoint.to_dict(), await env.serialize(), parent_id=runner.state.session_id, branch_point=len(msgs),
+                                          tags={**(runner.session_tags or {}), "env": spec})
+        for m in msgs:
+            await runner.store.append_message(child, m)
+        runner.state = replace(runner.state, session_id=child)
+        note = f"; now in session {child}"
+    return SlashCommandResult(message=f"environment: {spec} (tools: {', '.join(t.function.name for t in env.get_tools()) or 'none'}){note}",
+                              persist={"env": spec})
 
 
 async def handle_session(runner: Any, arg: str) -> SlashCommandResult:

@@ -3,6 +3,8 @@
 import asyncio
 import io
 
+import pytest
+
 from research_b200.agents.dtypes import Endpoint, Message
 from research_b200.agents.providers import ScriptedLLM, register_provider
 from research_b200.agents.store import FileSessionStore
@@ -54,7 +56,7 @@ def test_runner_commands_thinking_slice_env_and_file_prompt(tmp_path):
     text = out.getvalue()
     assert "thinking: off" in text and "thinking on, budget 8000 tokens" in text and "thinking off" in text and "usage: /thinking" in text
     assert "5 messages. usage: /slice" in text and "5 -> 2 messages; now in session" in text
-    assert "environment: calculator (tools: add" in text and "unknown environment 'nope'" in text and "did you mean /model?" in text
+    assert "environment: calculator (tools: add" in text and "unknown environment(s) ['nope']" in text and "did you mean /model?" in text
     assert "explain something  (project)" in text and "/explain <what> " in text and "/slice [0:5" in text
     # the file command reached the model as a user message, on the sliced conversation, with the calculator's tools
     last = seen[-1]
@@ -64,12 +66,14 @@ def test_runner_commands_thinking_slice_env_and_file_prompt(tmp_path):
     # the slice made a child session that records its origin; the thinking choice and the environment were stored as tags
 
     async def check():
-        sessions = await store.list()
-        child = next(s for s in sessions if s.parent_id)
-        assert child.tags["slice"] == "0:1, summarize:1:4" and child.tags["env"] == "calculator" and child.branch_point == 5
-        parent = next(s for s in sessions if s.session_id == child.parent_id)
-        assert parent.tags["thinking"] == "off"
-        assert [m.text() for m in (await store.get(child.session_id))[1]][-2:] == ["Explain the scheduler in two sentences.", "reply 3"]
+        sessions = {s.session_id: s for s in await store.list()}
+        sliced = next(s for s in sessions.values() if "slice" in s.tags and "env" not in s.tags)
+        assert sliced.tags["slice"] == "0:1, summarize:1:4" and sliced.branch_point == 5 and sessions[sliced.parent_id].tags["thinking"] == "off"
+        # switching the environment branched once more: the child carries the new tools, its parent stays as it was
+        swapped = next(s for s in sessions.values() if s.parent_id == sliced.session_id)
+        assert swapped.tags["env"] == "calculator" and swapped.environment is not None and swapped.branch_point == 2
+        assert [m.text() for m in (await store.get(swapped.session_id))[1]][-2:] == ["Explain the scheduler in two sentences.", "reply 3"]
+        assert len((await store.get(sliced.session_id))[1]) == 2
 
     asyncio.run(check())
     ep = runner.endpoint
@@ -121,3 +125,27 @@ def test_session_switch_and_branch(tmp_path):
         assert [m.text() for m in (await store.get(old))[1]] == ["earlier question", "earlier answer", "and now?", "reply 2"]
 
     asyncio.run(check())
+
+
+def test_environment_specs_compose_and_cli_env_flag(tmp_path):
+    from research_b200 import cli
+    from research_b200.agents.presets import environment_from_spec
+
+    env = environment_from_spec("coding+ask_user+calculator", str(tmp_path), "readonly")
+    names = [t.function.name for t in env.get_tools()]
+    assert names[:4] == ["read", "list", "glob", "grep"] and "ask_user_question" in names and "add" in names and env.get_name() == "coding+ask_user+calculator"
+    assert type(environment_from_spec("calculator")).__name__ == "CalculatorEnvironment"
+    for bad in ("coding+nope", "", "coding+coding"):
+        with pytest.raises(KeyError):
+            environment_from_spec(bad, str(tmp_path))
+    seen = {}
+
+    async def model(actor, run_config):
+        seen["tools"] = [t.function.name for t in actor.tools]
+        return await ScriptedLLM(["ok"])(actor, run_config)
+
+    register_provider("env-mock", model)
+    assert cli.main(["chat", "--provider", "env-mock", "--model", "m", "--env", "calculator+ask_user", "--no-session", "-q", "-p", "hi", "--cwd", str(tmp_path)]) == 0
+    assert "add" in seen["tools"] and "ask_user_question" in seen["tools"]
+    with pytest.raises(KeyError):
+        cli.main(["chat", "--provider", "env-mock", "--model", "m", "--env", "calculator+typo", "--no-session", "-q", "-p", "hi"])
