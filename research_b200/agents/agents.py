@@ -15,7 +15,7 @@ import uuid
 from dataclasses import replace
 from typing import Any
 
-from .dtypes import (Actor, AgentState, LLMCallStart, Message, RunConfig, StopReason, StreamDone, StreamEvent, TextDelta, ThinkingDelta, ToolCall,
+from .dtypes import (Actor, AgentState, ImageContent, LLMCallStart, Message, TextContent, RunConfig, StopReason, StreamDone, StreamEvent, TextDelta, ThinkingDelta, ToolCall,
                      ToolCallEnd, ToolConfirmResult, ToolExecutionStart, ToolResult, ToolResultReceived, Trajectory)
 
 
@@ -196,10 +196,16 @@ async def process_pending_tools(state: AgentState, run_config: RunConfig) -> Age
             except Exception as e:  # noqa: BLE001 - tool failures are fed back to the model
                 result = ToolResult(call.id, is_error=True, error=f"{type(e).__name__}: {e}")
         content = result.content if not result.is_error else f"Error: {result.error or result.content}"
-        traj = traj.append(Message("tool", content, tool_call_id=call.id, name=call.name))
+        image = result.metadata.get("image") if not result.is_error else None
+        if isinstance(image, dict) and image.get("data"):
+            # a tool that returns a picture (a screenshot, an image file that was read): text and image blocks together
+            body: Any = [TextContent(content), ImageContent(image["data"], image.get("mime_type", "image/png"))]
+        else:
+            body = content
+        traj = traj.append(Message("tool", body, tool_call_id=call.id, name=call.name))
         if run_config.on_chunk is not None:
             await run_config.on_chunk(ToolResultReceived(tool_call_id=call.id, content=content, is_error=result.is_error,
-                                                         details=dict(result.metadata)))
+                                                         details={k: v for k, v in result.metadata.items() if k != "image"}))
         if run_config.session_store is not None and state.session_id:
             await run_config.session_store.append_message(state.session_id, traj.messages[-1])
         if feedback:

@@ -15,7 +15,7 @@ import contextlib
 import io
 import re
 import traceback
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from pathlib import Path
 from typing import Any
 
@@ -26,6 +26,8 @@ def _tool(name, desc, props, required=()):
     return Tool(ToolFunction(name, desc, ToolFunctionParameter(props, tuple(required))))
 
 
+IMAGE_TYPES = {".png": "image/png", ".jpg": "image/jpeg", ".jpeg": "image/jpeg", ".gif": "image/gif", ".webp": "image/webp"}
+MAX_IMAGE_BYTES = 5 << 20
 MAX_READ_LINES = 2000
 MAX_LINE_CHARS = 2000
 MAX_BASH_CHARS = 30_000
@@ -41,7 +43,7 @@ def unified_diff(old: str, new: str, path: str = "", context: int = 3) -> str:
 
 
 def _first_lines(text: str, n: int) -> str:
-    lines = text.splitlines()
+    lines = text.expandtabs(4).splitlines()               # tabs would break the alignment of boxes and diffs
     return "\n".join(lines[:n]) + (f"\n... ({len(lines) - n} more lines)" if len(lines) > n else "")
 
 
@@ -129,12 +131,21 @@ class LocalFilesystemEnvironment:
         return [every[n] for n in self._names]
 
     # ---- tools
-    def _read(self, a: dict[str, Any]) -> str:
+    def _read(self, a: dict[str, Any]) -> "str | ToolResult":
         p = self._resolve(a["path"])
         if not p.exists():
             raise FileNotFoundError(f"file not found: {a['path']}")
         if not p.is_file():
             raise IsADirectoryError(f"not a file: {a['path']}")
+        if p.suffix.lower() in IMAGE_TYPES:
+            # an image is handed to the model as an image block (the agent loop attaches it to the tool message)
+            import base64
+
+            size = p.stat().st_size
+            if size > MAX_IMAGE_BYTES:
+                raise ValueError(f"image too large to attach: {size} bytes (limit {MAX_IMAGE_BYTES})")
+            return ToolResult("", content=f"[image {a['path']}, {size} bytes]",
+                              metadata={"image": {"data": base64.b64encode(p.read_bytes()).decode(), "mime_type": IMAGE_TYPES[p.suffix.lower()]}})
         try:
             lines = p.read_text(encoding="utf-8").split("\n")
         except UnicodeDecodeError:
@@ -231,7 +242,8 @@ class LocalFilesystemEnvironment:
             return ToolResult(cid, is_error=True, error=f"unknown tool {name!r}" if name not in TOOL_PRESETS["full"] else f"tool {name!r} is not enabled here")
         try:
             if name == "read":
-                return ToolResult(cid, content=self._read(a))
+                got = self._read(a)
+                return replace(got, tool_call_id=cid) if isinstance(got, ToolResult) else ToolResult(cid, content=got)
             if name == "write":
                 p = self._resolve(a["path"])
                 before = p.read_text() if p.is_file() else None

@@ -10,7 +10,7 @@ import uuid
 from dataclasses import replace
 from typing import Any
 
-from ..dtypes import (Actor, ChatCompletion, Choice, Cost, Message, RunConfig, TextDelta, ToolCall, ToolCallEnd, ToolCallStart,
+from ..dtypes import (Actor, ChatCompletion, Choice, Cost, ImageContent, Message, RunConfig, TextDelta, ToolCall, ToolCallEnd, ToolCallStart,
                       Usage)
 from .base import (NonRetryableError, async_retry, classify_http_status, classify_server_error, explain_server_error,
                    prepare_messages_for_llm, sanitize_request_for_logging)
@@ -26,8 +26,16 @@ def messages_to_openai(actor: Actor) -> list[dict[str, Any]]:
         if m.role == "assistant" and calls:
             d["tool_calls"] = [{"id": c.id, "type": "function", "function": {"name": c.name, "arguments": json.dumps(c.args)}}
                                for c in calls]
+        images = [b for b in m.content if isinstance(b, ImageContent)] if isinstance(m.content, list) else []
+        image_parts = [{"type": "image_url", "image_url": {"url": f"data:{b.mime_type};base64,{b.data}"}} for b in images]
         if m.role == "tool":
             d["tool_call_id"] = m.tool_call_id
+            out.append(d)
+            if image_parts:                                  # tool messages carry text only: the picture follows as a user message
+                out.append({"role": "user", "content": [{"type": "text", "text": f"(image returned by {m.name or 'the tool'})"}] + image_parts})
+            continue
+        if image_parts and m.role == "user":
+            d["content"] = ([{"type": "text", "text": m.text()}] if m.text() else []) + image_parts
         out.append(d)
     return out
 

@@ -84,7 +84,12 @@ def messages_to_anthropic(messages: tuple[Message, ...]) -> tuple[str, list[dict
         if m.role == "system":
             continue
         if m.role == "tool":
-            role, blocks = "user", [{"type": "tool_result", "tool_use_id": m.tool_call_id, "content": m.text()}]
+            images = [b for b in m.content if isinstance(b, ImageContent)] if isinstance(m.content, list) else []
+            body: Any = m.text()
+            if images:                                       # a tool that returned a picture: text and image blocks in the result
+                body = ([{"type": "text", "text": m.text()}] if m.text() else []) + [
+                    {"type": "image", "source": {"type": "base64", "media_type": b.mime_type, "data": b.data}} for b in images]
+            role, blocks = "user", [{"type": "tool_result", "tool_use_id": m.tool_call_id, "content": body}]
         else:
             role, blocks = m.role, []
             if isinstance(m.content, list):

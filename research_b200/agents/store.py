@@ -79,6 +79,26 @@ class FileSessionStore:
         s.updated_at = time.time()
         self._write_meta(s)
 
+    def record_config_change(self, session_id: str, what: str, before: Any, after: Any) -> None:
+        """A change of model, sampling settings or environment in the middle of a conversation, kept beside the messages
+        with the index of the message it took effect after, so that a replay knows which configuration produced which
+        turn. The session's own record is brought up to date as well (a resumed session continues with the new one)."""
+        s = self._read_meta(session_id)
+        with open(self._dir(session_id) / "config_changes.jsonl", "a") as f:
+            f.write(json.dumps({"at_message": s.num_messages, "time": time.time(), "what": what, "before": before, "after": after}) + "\n")
+        if what == "endpoint" and isinstance(after, dict):
+            s.endpoint = after
+        elif what == "environment" and isinstance(after, dict):
+            s.environment = after
+        s.updated_at = time.time()
+        self._write_meta(s)
+
+    def config_changes(self, session_id: str) -> list[dict[str, Any]]:
+        path = self._dir(session_id) / "config_changes.jsonl"
+        if not path.exists():
+            return []
+        return [json.loads(line) for line in path.read_text().splitlines() if line.strip()]
+
     async def list(self, filter_tags: dict[str, Any] | None = None, status: str | None = None, limit: int | None = None) -> list[AgentSession]:
         """Sessions, oldest first (ids start with their creation time); optionally only those whose tags contain
         ``filter_tags`` and / or with ``status``; ``limit`` keeps the NEWEST ones. Unreadable folders are skipped."""

@@ -210,6 +210,20 @@ def truncate_lines(text: str, max_lines: int, width: int) -> list[str]:
     return shown
 
 
+def colour_diff_line(line: str) -> str:
+    """One line of a unified diff (possibly indented by a formatter): additions green, removals red, hunk headers dim."""
+    s = line.lstrip()
+    if s.startswith(("+++", "---")):
+        return f"{Theme.DIM}{line}{Theme.RESET}"
+    if s.startswith("+"):
+        return f"{Theme.CODE}{line}{Theme.RESET}"
+    if s.startswith("-"):
+        return f"{Theme.ERROR}{line}{Theme.RESET}"
+    if s.startswith("@@"):
+        return f"{Theme.DIM}{line}{Theme.RESET}"
+    return line
+
+
 def box(title: str, body_lines: list[str], width: int, color: str = "") -> str:
     """A one-line-border box around ``body_lines``; ``width`` is the total width in columns."""
     inner = max(width - 4, 8)
@@ -365,7 +379,11 @@ class AnsiFrontend(PlainFrontend):
             color = Theme.ERROR if event.is_error else Theme.DIM
             title = "error" if event.is_error else "result"
             body = self._formatted(event) or event.content
-            self._w(box(title, truncate_lines(body, self.max_result_lines, self.width - 4), self.width, color) + "\n")
+            lines = truncate_lines(body, self.max_result_lines, self.width - 4)
+            if event.details.get("diff") and not event.is_error:
+                self._w("\n".join(colour_diff_line(ln) for ln in lines) + "\n")      # a diff reads better unboxed: removed red, added green
+            else:
+                self._w(box(title, lines, self.width, color) + "\n")
         elif isinstance(event, StreamError):
             self._enter("")
             self._w(f"{Theme.ERROR}error: {event.error}{Theme.RESET}\n")
@@ -471,8 +489,7 @@ class InteractiveRunner:
     def _cmd_model(self, arg: str) -> str:
         if not arg:
             return f"model: {self.endpoint.model}"
-        self.endpoint = replace(self.endpoint, model=arg)
-        self.state = replace(self.state, actor=replace(self.state.actor, endpoint=self.endpoint))
+        self.set_endpoint(replace(self.endpoint, model=arg))
         return f"model set to {arg}"
 
     def _cmd_temperature(self, arg: str) -> str:
@@ -480,15 +497,24 @@ class InteractiveRunner:
             t = float(arg)
         except ValueError:
             return "usage: /temperature 0.7"
-        self.endpoint = replace(self.endpoint, temperature=t)
-        self.state = replace(self.state, actor=replace(self.state.actor, endpoint=self.endpoint))
+        self.set_endpoint(replace(self.endpoint, temperature=t))
         return f"temperature set to {t}"
 
+    def _log_config_change(self, what: str, before: Any, after: Any) -> None:
+        # every exchange is its own agent run with a fixed endpoint and environment; a change between two runs is
+        # recorded in the session so that the conversation can be replayed with the configuration each turn had
+        record = getattr(self.store, "record_config_change", None)
+        if record is not None and self.state.session_id and before != after:
+            record(self.state.session_id, what, before, after)
+
     def set_endpoint(self, endpoint: Endpoint) -> None:
+        self._log_config_change("endpoint", self.endpoint.to_dict(), endpoint.to_dict())
         self.endpoint = endpoint
         self.state = replace(self.state, actor=replace(self.state.actor, endpoint=endpoint))
 
     def set_environment(self, environment: Any) -> None:
+        name = lambda e: {"name": e.get_name() if hasattr(e, "get_name") else type(e).__name__} if e is not None else None  # noqa: E731
+        self._log_config_change("environment", name(self.environment), name(environment))
         self.environment = environment
         self.state = replace(self.state, environment=environment)
         if hasattr(self.frontend, "environment"):

@@ -336,3 +336,51 @@ def test_auth_report_and_endpoint_credentials(tmp_path, monkeypatch):
     assert ep.oauth_token == "at-live" and ep.api_key == "" and "oauth_token" not in ep.to_dict()
     with pytest.raises(oauth.OAuthError, match="not configured"):
         oauth.OAuthApp.load("other", tmp_path / "home", env={})
+
+
+def test_read_of_an_image_reaches_the_model_as_an_image_block(tmp_path):
+    """An image file read by the coding environment becomes text + image content of the tool message, and both wire
+    formats carry it: inside the tool result for Anthropic, as a following user message for chat completions."""
+    import asyncio
+    import base64
+
+    from research_b200.agents.agents import process_pending_tools
+    from research_b200.agents.dtypes import Actor, AgentState, Endpoint, ImageContent, Message, RunConfig, ToolCall, Trajectory
+    from research_b200.agents.environments.coding import LocalFilesystemEnvironment
+    from research_b200.agents.providers.chat import messages_to_openai
+    from research_b200.agents.providers.streaming import messages_to_anthropic
+
+    png = b"\x89PNG\r\n\x1a\n" + b"\0" * 32
+    (tmp_path / "shot.png").write_bytes(png)
+    env = LocalFilesystemEnvironment(tmp_path)
+    call = ToolCall("c1", "read", {"path": "shot.png"})
+    actor = Actor(Trajectory((Message("user", "look"), Message("assistant", "", tool_calls=(call,)))), Endpoint("mock", "m"))
+    state = AgentState(actor, env, pending_tool_calls=(call,))
+    events = []
+
+    async def on_chunk(e):
+        events.append(e)
+
+    new = asyncio.run(process_pending_tools(state, RunConfig(on_chunk=on_chunk)))
+    tool_msg = new.actor.trajectory.messages[-1]
+    assert tool_msg.role == "tool" and isinstance(tool_msg.content, list)
+    image = [b for b in tool_msg.content if isinstance(b, ImageContent)][0]
+    assert base64.b64decode(image.data) == png and image.mime_type == "image/png"
+    assert "shot.png" in tool_msg.text()
+    assert all("image" not in getattr(e, "details", {}) for e in events)         # the event stream does not carry the bytes
+
+    _, wire = messages_to_anthropic(new.actor.trajectory.messages)
+    result_block = wire[-1]["content"][0]
+    assert result_block["type"] == "tool_result" and result_block["content"][-1]["type"] == "image"
+    chat = messages_to_openai(new.actor)
+    assert chat[-2]["role"] == "tool" and chat[-1]["role"] == "user"
+    assert chat[-1]["content"][-1]["image_url"]["url"].startswith("data:image/png;base64,")
+
+
+def test_diff_lines_are_coloured_and_tabs_expanded():
+    from research_b200.agents.environments.coding import _first_lines
+    from research_b200.frontend.terminal import Theme, colour_diff_line
+
+    assert colour_diff_line("+new").startswith(Theme.CODE) and colour_diff_line("  -old").startswith(Theme.ERROR)
+    assert colour_diff_line(" same") == " same" and colour_diff_line("@@ -1 +1 @@").startswith(Theme.DIM)
+    assert "\t" not in _first_lines("a\tb\n\tc", 5)

@@ -160,3 +160,28 @@ def test_themes_and_thinking_flag(tmp_path):
     assert seen["extra"]["thinking"] == {"type": "enabled", "budget_tokens": 4096} and seen["max_tokens"] >= 5120
     with pytest.raises(SystemExit, match="usage"):
         cli.main(["chat", "--provider", "think-mock", "--model", "m", "--no-session", "-q", "-p", "hi", "--thinking", "maybe"])
+
+
+def test_model_and_temperature_changes_are_recorded_in_the_session(tmp_path):
+    """A configuration change between two exchanges lands in the session's change log with the message index it took
+    effect at, and a later resume sees the new endpoint."""
+    import asyncio
+    import io
+
+    from research_b200.agents.dtypes import Endpoint, Message
+    from research_b200.agents.store import FileSessionStore
+    from research_b200.frontend.terminal import InteractiveRunner, PlainFrontend
+
+    store = FileSessionStore(tmp_path)
+    ep = Endpoint("mock", "m1")
+    sid = asyncio.run(store.create(ep.to_dict()))
+    asyncio.run(store.append_message(sid, Message("user", "hi")))
+    agent = InteractiveRunner(ep, PlainFrontend(out=io.StringIO()), session_store=store, session_id=sid)
+    assert "m2" in agent._cmd_model("m2")
+    agent._cmd_temperature("0.3")
+    agent._cmd_temperature("0.3")                               # no change: not recorded twice
+    changes = store.config_changes(sid)
+    assert [c["what"] for c in changes] == ["endpoint", "endpoint"]
+    assert changes[0]["at_message"] == 1 and changes[0]["before"]["model"] == "m1" and changes[0]["after"]["model"] == "m2"
+    session, _ = asyncio.run(store.get(sid))
+    assert session.endpoint["model"] == "m2" and session.endpoint["temperature"] == 0.3
