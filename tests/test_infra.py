@@ -431,3 +431,96 @@ def test_instance_registry_and_gpus_commands(tmp_path):
     assert main(["gpus", "cleanup", "--older-than", "2"], lines.append, later) == 0 and lines[-1].startswith("run again with --yes") and later.instances
     assert main(["gpus", "cleanup", "--older-than", "2", "--yes"], lines.append, later) == 0 and not later.instances and len(provider.search()) == 2
     assert json.loads((tmp_path / "instances.json").read_text()) == [] and main(["gpus", "list"], lines.append, later) == 0 and lines[-1] == "no instances"
+
+
+def _tiny_repo(path):
+    import subprocess
+
+    path.mkdir()
+    (path / "work.sh").write_text("mkdir -p out && echo result-$TAG > out/result.txt && touch .done\n")
+    (path / "fail.sh").write_text("echo broken >&2; touch .failed; sleep 30\n")
+    for argv in (["init", "-q"], ["add", "-A"], ["-c", "user.email=a@b", "-c", "user.name=t", "commit", "-q", "-m", "one"]):
+        subprocess.run(["git", "-C", str(path), *argv], check=True)
+    return path
+
+
+def test_deploy_experiment_runs_pushes_waits_and_brings_results_back(tmp_path):
+    """The whole deployment against this machine as the target: the commit is shipped, the run starts detached with its
+    environment, the marker file ends the wait, results come back; a run that writes its failure marker is reported as
+    failed at the wait stage with its log, while it is still running."""
+    from research_b200.infra.experiment_deploy import DeployJob, deploy_experiment
+
+    repo = _tiny_repo(tmp_path / "repo")
+    said = []
+    job = DeployJob("demo", "sh work.sh", repo=str(repo), dest=str(tmp_path / "remote"), env={"TAG": "seven"}, bootstrap=None,
+                    results=("out", "missing.txt"), local_results=str(tmp_path / "got"), success_marker=".done", poll_s=0.05, timeout_s=20)
+    out = deploy_experiment(job, ssh="local", log=said.append)
+    assert out.ok and out.stage == "done" and out.commit and out.fetched == {"out": 1}
+    assert (tmp_path / "got" / "demo" / "out" / "result.txt").read_text().strip() == "result-seven"
+    assert any("no missing.txt" in line for line in said)
+
+    bad = DeployJob("bad", "sh fail.sh", repo=str(repo), dest=str(tmp_path / "remote2"), bootstrap=None, local_results=str(tmp_path / "got"),
+                    success_marker=".done", failure_marker=".failed", poll_s=0.05, timeout_s=20)
+    out = deploy_experiment(bad, ssh="local", log=said.append)
+    assert not out.ok and out.stage == "sync" or out.stage == "wait"
+    assert ".failed" in out.error and "broken" in out.log_tail
+    assert (tmp_path / "got" / "bad" / "run.log.tail").exists()
+
+
+def test_deploy_experiment_rents_and_returns_the_machine(tmp_path):
+    """With a broker instead of an ssh target the instance is created from the job's query and terminated afterwards,
+    also when the run fails; ``keep_running`` leaves it."""
+    from dataclasses import replace
+
+    from research_b200.infra.bifrost import GPUQuery
+    from research_b200.infra.broker import GPUClient, GPUOffer, StaticProvider
+    from research_b200.infra.experiment_deploy import DeployJob, deploy_experiment
+
+    repo = _tiny_repo(tmp_path / "repo")
+    offer = GPUOffer("static", "o1", "B200", 1, 180, 3.0)
+    provider = StaticProvider("static", [offer], connections={"o1": "local"})
+    client = GPUClient([provider])
+    job = DeployJob("rent", "sh work.sh", repo=str(repo), dest=str(tmp_path / "r"), bootstrap=None, gpu=GPUQuery("B200", min_vram_gb=100),
+                    success_marker=".done", poll_s=0.05, local_results=str(tmp_path / "got"))
+    out = deploy_experiment(job, gpu_client=client, log=lambda m: None)
+    assert out.ok and out.instance_id and out.terminated and not client.instances
+    out = deploy_experiment(replace(job, name="exit1", command="exit 3", success_marker=None), gpu_client=client, log=lambda m: None)
+    assert not out.ok and out.exit_code == 3 and out.terminated
+    out = deploy_experiment(replace(job, name="keep", keep_running=True), gpu_client=client, log=lambda m: None)
+    assert out.ok and not out.terminated and len(client.instances) == 1
+    nothing = deploy_experiment(replace(job, gpu=GPUQuery("H100")), gpu_client=client, log=lambda m: None)
+    assert not nothing.ok and nothing.stage == "provision"
+
+
+def test_sweep_launches_one_process_per_config_and_reports_status(tmp_path):
+    import time
+
+    from research_b200.infra.experiment_deploy import discover_configs, display_name, format_status, launch_sweep, load_job, main, sweep_status
+
+    repo = _tiny_repo(tmp_path / "repo")
+    cfgs = tmp_path / "configs"
+    cfgs.mkdir()
+    for stem, cmd in (("01_small_model", "sh work.sh"), ("02_big_model", "exit 2"), ("_shared", "")):
+        (cfgs / f"{stem}.py").write_text(
+            "from research_b200.infra.experiment_deploy import DeployJob\n"
+            f"job = DeployJob({stem!r}, {cmd!r}, repo={str(repo)!r}, dest={str(tmp_path / ('remote_' + stem))!r}, bootstrap=None,\n"
+            f"                results=('out',), local_results={str(tmp_path / 'got')!r}, poll_s=0.05)\n")
+    found = discover_configs(cfgs)
+    assert [p.stem for p in found] == ["01_small_model", "02_big_model"] and display_name(found[0]) == "small-model"
+    assert [p.stem for p in discover_configs(cfgs, only=["02"])] == ["02_big_model"]
+    assert load_job(found[0]).command == "sh work.sh"
+    assert main(["sweep", str(cfgs), "--dry-run", "--log-dir", str(tmp_path / "logs")]) == 0 and not (tmp_path / "logs").exists()
+
+    record = launch_sweep(found, tmp_path / "logs", extra_args=["--ssh", "local"], stagger_s=0.0)
+    assert len(record["runs"]) == 2 and all("pid" in r for r in record["runs"])
+    deadline = time.time() + 120
+    while time.time() < deadline:
+        rows = sweep_status(tmp_path / "logs")
+        if all(r["state"] != "running" for r in rows):
+            break
+        time.sleep(0.3)
+    states = {r["name"]: r["state"] for r in rows}
+    assert states == {"small-model": "ok", "big-model": "failed"}, rows
+    text = format_status(rows)
+    assert "1 ok" in text and "1 failed" in text and "exited with code 2" in text
+    assert (tmp_path / "got" / "01_small_model" / "out" / "result.txt").exists()
