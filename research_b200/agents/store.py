@@ -164,13 +164,63 @@ class FileSessionStore:
         d.rmdir()
         return True
 
-    async def branch(self, session_id: str, at_message: int) -> str:
-        """New session that shares the first ``at_message`` messages of ``session_id``."""
+    async def branch(self, session_id: str, at_message: int, reason: str | None = None) -> str:
+        """New session that shares the first ``at_message`` messages of ``session_id``; ``reason`` (why the conversation
+        forked: an edit, a configuration change, an exploration) is kept in the child's tags."""
         parent, msgs = await self.get(session_id)
-        sid = await self.create(parent.endpoint, parent.environment, parent_id=session_id, branch_point=at_message)
+        tags = {"branch_reason": reason} if reason else None
+        sid = await self.create(parent.endpoint, parent.environment, parent_id=session_id, branch_point=at_message, tags=tags)
         for m in msgs[:at_message]:
             await self.append_message(sid, m)
         return sid
+
+    async def branch_with_edit(self, session_id: str, index: int, new_content: str) -> str:
+        """Child session in which message ``index`` says ``new_content`` instead and nothing follows it yet: the
+        conversation is replayed from there. The parent keeps the original wording and everything after it."""
+        _, msgs = await self.get(session_id)
+        if not 0 <= index < len(msgs):
+            raise IndexError(f"session {session_id} has {len(msgs)} messages, no message {index}")
+        if msgs[index].role not in ("user", "system"):
+            raise ValueError(f"message {index} is a {msgs[index].role} message; only user and system messages can be reworded")
+        sid = await self.branch(session_id, index, reason="message_edit")
+        await self.append_message(sid, Message(msgs[index].role, new_content))
+        return sid
+
+    async def root_of(self, session_id: str) -> str:
+        return (await self.lineage(session_id))[0].session_id
+
+    async def tree(self, root_id: str) -> dict[str, Any]:
+        """``{"session": AgentSession, "children": [subtrees]}`` under ``root_id``, children oldest first."""
+        by_parent: dict[str, list[AgentSession]] = {}
+        for s in await self.list():
+            if s.parent_id:
+                by_parent.setdefault(s.parent_id, []).append(s)
+
+        def build(s: AgentSession, seen: frozenset[str]) -> dict[str, Any]:
+            kids = sorted(by_parent.get(s.session_id, []), key=lambda c: c.created_at)
+            return {"session": s, "children": [build(c, seen | {c.session_id}) for c in kids if c.session_id not in seen]}
+
+        return build(self._read_meta(root_id), frozenset({root_id}))
+
+
+def format_session_tree(tree: dict[str, Any], current: str | None = None) -> str:
+    """The tree as indented lines: id, where it left its parent and why, size, model; ``current`` is marked with ``*``."""
+    lines: list[str] = []
+
+    def walk(node: dict[str, Any], prefix: str, last: bool, top: bool) -> None:
+        s = node["session"]
+        fork = ""
+        if s.parent_id is not None:
+            fork = f" @{s.branch_point}" + (f" ({s.tags['branch_reason']})" if s.tags.get("branch_reason") else "")
+        mark = " *" if s.session_id == current else ""
+        lines.append(f"{prefix}{'' if top else ('`-- ' if last else '|-- ')}{s.session_id}{fork}  {s.num_messages} msgs  "
+                     f"{s.endpoint.get('model', '?')}  {s.status}{mark}")
+        kids = node["children"]
+        for i, k in enumerate(kids):
+            walk(k, prefix + ("" if top else ("    " if last else "|   ")), i == len(kids) - 1, False)
+
+    walk(tree, "", True, True)
+    return "\n".join(lines)
 
 
 def log_crash(root: str | Path, error: BaseException, context: dict[str, Any] | None = None) -> Path:

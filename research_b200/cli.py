@@ -296,6 +296,14 @@ async def _sessions(args) -> int:
         for s in sorted(await store.list(), key=lambda s: s.updated_at, reverse=True)[: args.limit]:
             print(f"{s.session_id}  {s.status:<10} {s.num_messages:>4} msgs  {format_time_ago(s.updated_at):>9}  "
                   f"{s.endpoint.get('provider', '?')}/{s.endpoint.get('model', '?')}")
+    elif args.action == "tree":
+        from .agents.store import format_session_tree
+
+        sid = args.id or await _latest(store)
+        if not sid:
+            print("no session found", file=sys.stderr)
+            return 1
+        print(format_session_tree(await store.tree(await store.root_of(sid)), current=sid))
     elif args.action in ("show", "export"):
         text = await export_session(store, args.id, args.format, args.output)
         if not args.output:
@@ -422,7 +430,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--provider", default=""); p.add_argument("--api-key-env", default="")
     p.set_defaults(fn=cmd_auth)
     p = sub.add_parser("sessions")
-    p.add_argument("action", choices=["list", "show", "export", "slice", "import", "doctor", "handoff"]); p.add_argument("id", nargs="?")
+    p.add_argument("action", choices=["list", "show", "export", "slice", "import", "doctor", "handoff", "tree"]); p.add_argument("id", nargs="?")
     p.add_argument("--fix", action="store_true", help="doctor: write a child session without duplicate / orphaned tool results")
     p.add_argument("--trim", type=int, default=0, help="doctor: write a child session without the last N messages")
     p.add_argument("--goal", default="", help="handoff: what the next session should do")

@@ -47,6 +47,8 @@ BUILTIN_COMMANDS = [SlashCommand("help", "what can be typed here"), SlashCommand
                     SlashCommand("env", "show or switch the environment", "[name]"), SlashCommand("commands", "list all commands"),
                     SlashCommand("session", "list recent sessions, or continue in another one", "[id]"),
                     SlashCommand("branch", "fork the conversation here (or after N messages) into a new session", "[n]"),
+                    SlashCommand("edit", "reword a user message (default: the last one) and continue from there in a new session", "[n] <new text>"),
+                    SlashCommand("tree", "the tree of sessions this conversation belongs to"),
                     SlashCommand("quit", "leave")]
 
 
@@ -289,3 +291,39 @@ async def handle_branch(runner: Any, arg: str) -> SlashCommandResult:
     sid = await runner.store.branch(parent, n)
     runner.state = replace(runner.state, actor=Actor(Trajectory(tuple(msgs[:n])), runner.endpoint), session_id=sid, stop=None, pending_tool_calls=())
     return SlashCommandResult(message=f"branched after message {n}: now in session {sid} (parent {parent})")
+
+
+async def handle_edit(runner: Any, arg: str) -> SlashCommandResult:
+    """``/edit new text`` rewords the last user message, ``/edit 3 new text`` message 3: the conversation forks into a
+    child session that ends just before that message, and the new wording is sent."""
+    msgs = runner.state.actor.trajectory.messages
+    head, _, rest = arg.strip().partition(" ")
+    if head.isdigit() and rest.strip():
+        index, text = int(head), rest.strip()
+    else:
+        index, text = next((i for i in range(len(msgs) - 1, -1, -1) if msgs[i].role == "user"), -1), arg.strip()
+    if not text:
+        return SlashCommandResult(message="usage: /edit [message number] <new text>")
+    if not 0 <= index < len(msgs) or msgs[index].role != "user":
+        users = [i for i, m in enumerate(msgs) if m.role == "user"]
+        return SlashCommandResult(message=f"message {index} is not a user message (user messages: {users})" if users else "no user message to edit yet")
+    from ..agents.dtypes import Actor, Trajectory
+
+    note = f"reworded message {index}"
+    sid = runner.state.session_id
+    if runner.store is not None and sid:
+        parent = sid
+        sid = await runner.store.branch(parent, index, reason="message_edit")      # the runner appends the new wording itself
+        note += f": now in session {sid} (parent {parent})"
+    runner.state = replace(runner.state, actor=Actor(Trajectory(tuple(msgs[:index])), runner.endpoint), session_id=sid, stop=None,
+                           pending_tool_calls=())
+    return SlashCommandResult(message=note, expanded_text=text)
+
+
+async def handle_tree(runner: Any, arg: str) -> SlashCommandResult:
+    if runner.store is None or not runner.state.session_id:
+        return SlashCommandResult(message="this conversation is not stored")
+    from ..agents.store import format_session_tree
+
+    root = await runner.store.root_of(runner.state.session_id)
+    return SlashCommandResult(message=format_session_tree(await runner.store.tree(root), current=runner.state.session_id))

@@ -439,6 +439,8 @@ HELP = """/help               this text
 /env [NAME]         show or switch the environment (the agent's tools)
 /session [ID]       recent sessions, or continue in another one
 /branch [N]         fork the conversation (after N messages) into a new session
+/edit [N] TEXT      reword a user message (default: the last) and continue from there in a new session
+/tree               the tree of sessions this conversation belongs to
 /commands           every command, including those from .research_b200/commands/*.md"""
 
 
@@ -474,7 +476,7 @@ class InteractiveRunner:
             "help": self._cmd_help, "clear": self._cmd_clear, "model": self._cmd_model, "temperature": self._cmd_temperature,
             "thinking": self._cmd_thinking, "status": self._cmd_status, "save": self._cmd_save, "retry": self._cmd_retry,
             "slice": self._cmd_slice, "env": self._cmd_env, "commands": self._cmd_commands, "session": self._cmd_session,
-            "branch": self._cmd_branch}
+            "branch": self._cmd_branch, "edit": self._cmd_edit, "tree": self._cmd_tree}
 
     # ---- slash commands: return text to print; "retry" returns a prompt to resend
     def _cmd_help(self, arg: str) -> str:
@@ -544,6 +546,16 @@ class InteractiveRunner:
         from .slash_commands import handle_branch
 
         return handle_branch(self, arg)
+
+    def _cmd_edit(self, arg: str):
+        from .slash_commands import handle_edit
+
+        return handle_edit(self, arg)
+
+    def _cmd_tree(self, arg: str):
+        from .slash_commands import handle_tree
+
+        return handle_tree(self, arg)
 
     def _cmd_commands(self, arg: str) -> str:
         from .slash_commands import BUILTIN_COMMANDS
@@ -687,6 +699,9 @@ class InteractiveRunner:
                             session, _ = await self.store.get(self.state.session_id)
                             await self.store.update(self.state.session_id, tags={**session.tags, **res.persist})
                         if res.expanded_text:
+                            if res.message:
+                                await fe.handle_event(TextDelta(delta=res.message + "\n"))
+                                await fe.handle_event(StreamDone())
                             pending = res.expanded_text
                             continue
                         res = res.message or ""

@@ -149,3 +149,71 @@ def test_environment_specs_compose_and_cli_env_flag(tmp_path):
     assert "add" in seen["tools"] and "ask_user_question" in seen["tools"]
     with pytest.raises(KeyError):
         cli.main(["chat", "--provider", "env-mock", "--model", "m", "--env", "calculator+typo", "--no-session", "-q", "-p", "hi"])
+
+
+def test_edit_branches_before_the_message_and_tree_shows_the_family(tmp_path):
+    """`/edit` forks the stored conversation just before the reworded message and hands the new wording back to be sent;
+    the store can also write the reworded message itself; `/tree` draws parent and children with fork points."""
+    import asyncio
+    import io
+
+    from research_b200.agents.dtypes import Endpoint, Message
+    from research_b200.agents.store import FileSessionStore, format_session_tree
+    from research_b200.frontend.slash_commands import handle_edit, handle_tree
+    from research_b200.frontend.terminal import InteractiveRunner, PlainFrontend
+
+    async def go():
+        store = FileSessionStore(tmp_path)
+        ep = Endpoint("mock", "m")
+        root = await store.create(ep.to_dict())
+        history = [Message("user", "first question"), Message("assistant", "first answer"), Message("user", "secnod question"),
+                   Message("assistant", "second answer")]
+        for m in history:
+            await store.append_message(root, m)
+        from research_b200.agents.dtypes import Trajectory
+
+        runner = InteractiveRunner(ep, PlainFrontend(out=io.StringIO()), session_store=store, session_id=root, trajectory=Trajectory(tuple(history)))
+        res = await handle_edit(runner, "second question")
+        assert res.expanded_text == "second question" and "reworded message 2" in res.message
+        child = runner.state.session_id
+        assert child != root and [m.text() for m in runner.state.actor.trajectory.messages] == ["first question", "first answer"]
+        session, msgs = await store.get(child)
+        assert session.parent_id == root and session.branch_point == 2 and session.tags["branch_reason"] == "message_edit" and len(msgs) == 2
+
+        assert "not a user message" in (await handle_edit(runner, "1 nope")).message
+        assert "usage" in (await handle_edit(runner, "")).message
+
+        other = await store.branch_with_edit(root, 0, "a different first question")
+        _, msgs = await store.get(other)
+        assert [m.text() for m in msgs] == ["a different first question"]
+        import pytest
+
+        with pytest.raises(ValueError):
+            await store.branch_with_edit(root, 1, "cannot reword the model")
+        grandchild = await store.branch(child, 1, reason="exploration")
+
+        assert await store.root_of(grandchild) == root
+        tree = await store.tree(root)
+        assert {c["session"].session_id for c in tree["children"]} == {child, other}
+        text = format_session_tree(tree, current=child)
+        lines = text.splitlines()
+        assert lines[0].startswith(root) and any(child in ln and "@2 (message_edit)" in ln and ln.rstrip().endswith("*") for ln in lines)
+        assert any(grandchild in ln and "(exploration)" in ln and ln.startswith(("|   ", "    ")) for ln in lines)
+        assert (await handle_tree(runner, "")).message == text
+    asyncio.run(go())
+
+
+def test_sessions_tree_command(tmp_path, capsys):
+    import asyncio
+
+    from research_b200.agents.dtypes import Endpoint, Message
+    from research_b200.agents.store import FileSessionStore
+    from research_b200.cli import main
+
+    store = FileSessionStore(tmp_path)
+    root = asyncio.run(store.create(Endpoint("mock", "m").to_dict()))
+    asyncio.run(store.append_message(root, Message("user", "q")))
+    kid = asyncio.run(store.branch(root, 1))
+    assert main(["sessions", "tree", kid, "--store", str(tmp_path)]) == 0
+    out = capsys.readouterr().out
+    assert out.splitlines()[0].startswith(root) and f"`-- {kid} @1" in out and out.rstrip().endswith("*")
