@@ -28,6 +28,25 @@ def _tool(name, desc, props, required=()):
 
 IMAGE_TYPES = {".png": "image/png", ".jpg": "image/jpeg", ".jpeg": "image/jpeg", ".gif": "image/gif", ".webp": "image/webp"}
 MAX_IMAGE_BYTES = 5 << 20
+
+
+def sniff_image(path: Path) -> str | None:
+    """The image type by the file's first bytes (a wrongly named file is still recognised; a text file called .png is
+    not taken for a picture); None for anything else."""
+    try:
+        with open(path, "rb") as f:
+            head = f.read(16)
+    except OSError:
+        return None
+    if head.startswith(b"\x89PNG\r\n\x1a\n"):
+        return "image/png"
+    if head.startswith(b"\xff\xd8\xff"):
+        return "image/jpeg"
+    if head.startswith((b"GIF87a", b"GIF89a")):
+        return "image/gif"
+    if head[:4] == b"RIFF" and head[8:12] == b"WEBP":
+        return "image/webp"
+    return None
 MAX_READ_LINES = 2000
 MAX_LINE_CHARS = 2000
 MAX_BASH_CHARS = 30_000
@@ -137,7 +156,8 @@ class LocalFilesystemEnvironment:
             raise FileNotFoundError(f"file not found: {a['path']}")
         if not p.is_file():
             raise IsADirectoryError(f"not a file: {a['path']}")
-        if p.suffix.lower() in IMAGE_TYPES:
+        mime = sniff_image(p)
+        if mime is not None:
             # an image is handed to the model as an image block (the agent loop attaches it to the tool message)
             import base64
 
@@ -145,7 +165,7 @@ class LocalFilesystemEnvironment:
             if size > MAX_IMAGE_BYTES:
                 raise ValueError(f"image too large to attach: {size} bytes (limit {MAX_IMAGE_BYTES})")
             return ToolResult("", content=f"[image {a['path']}, {size} bytes]",
-                              metadata={"image": {"data": base64.b64encode(p.read_bytes()).decode(), "mime_type": IMAGE_TYPES[p.suffix.lower()]}})
+                              metadata={"image": {"data": base64.b64encode(p.read_bytes()).decode(), "mime_type": mime}})
         try:
             lines = p.read_text(encoding="utf-8").split("\n")
         except UnicodeDecodeError:

@@ -429,6 +429,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("action", choices=["login", "logout", "status"]); p.add_argument("name", help="configured OAuth application")
     p.add_argument("--provider", default=""); p.add_argument("--api-key-env", default="")
     p.set_defaults(fn=cmd_auth)
+    p = sub.add_parser("track", help="terminal charts of the runs a utils.tracker.Tracker wrote")
+    p.add_argument("rest", nargs=argparse.REMAINDER)
+    p.set_defaults(fn=lambda a: __import__("research_b200.utils.tracker", fromlist=["main"]).main(a.rest))
     p = sub.add_parser("sessions")
     p.add_argument("action", choices=["list", "show", "export", "slice", "import", "doctor", "handoff", "tree"]); p.add_argument("id", nargs="?")
     p.add_argument("--fix", action="store_true", help="doctor: write a child session without duplicate / orphaned tool results")

@@ -222,3 +222,85 @@ def test_harness_profile_table_and_ncu_command(tmp_path):
     assert cmd[:3] == ["ncu", "--clock-control", "none"] and cmd[cmd.index("-c") + 1] == "2" and cmd[cmd.index("-s") + 1] == "4" and "--set" in cmd
     light = ncu_command(["python", "x.py"], "k", full=False)
     assert light.count("--section") == 2 and "--set" not in light and light[-2:] == ["python", "x.py"]
+
+
+def test_tracker_writes_runs_and_the_viewer_draws_them(tmp_path):
+    """Two runs logged through the Tracker: file layout, auto-incremented steps, non-JSON values coerced, meta closed by
+    finish / by an exception; the viewer lists both, tabulates latest values and draws braille charts on a shared scale."""
+    import io
+    import json
+
+    import pytest
+    import torch
+
+    from research_b200.utils.tracker import Tracker, braille_chart, list_runs, load_run, main, render, watch
+
+    t = [1000.0]
+    clock = lambda: t[0]                                                        # noqa: E731
+    a = Tracker("baseline", config={"lr": 0.1}, dir=tmp_path, run_id="run-a", clock=clock)
+    for i in range(50):
+        t[0] += 1
+        assert a.log({"loss": 3.0 * 0.95**i, "acc": torch.tensor(i / 50), "note": object()}) == i
+    assert a.log({"loss": 0.2}, step=100) == 100
+    a.log_system({"gpu_util": 0.9})
+    a.finish()
+    t[0] += 10
+    with pytest.raises(RuntimeError):
+        with Tracker("variant", config={"lr": 0.3}, dir=tmp_path, run_id="run-b", clock=clock) as b:
+            for i in range(20):
+                b.log({"loss": 3.0 * 0.8**i})
+            raise RuntimeError("boom")
+    live = Tracker("live", dir=tmp_path, run_id="run-c", clock=clock)
+    live.log({"loss": 1.0})
+
+    meta = json.loads((tmp_path / "run-a" / "meta.json").read_text())
+    assert meta["name"] == "baseline" and meta["finished_at"] == t[0] - 10 and meta["status"] == "finished"
+    assert json.loads((tmp_path / "run-b" / "meta.json").read_text())["status"] == "failed"
+    first = json.loads((tmp_path / "run-a" / "metrics.jsonl").read_text().splitlines()[0])
+    assert first["_step"] == 0 and first["acc"] == 0.0 and isinstance(first["note"], str)
+    assert json.loads((tmp_path / "run-a" / "system.jsonl").read_text())["gpu_util"] == 0.9
+
+    runs = list_runs(tmp_path)
+    assert [r.run_id for r in runs] == ["run-a", "run-b", "run-c"]
+    run = load_run(tmp_path / "run-a")
+    xs, ys = run.series("loss")
+    assert xs[-1] == 100 and ys[-1] == 0.2 and run.metrics() == ["loss", "acc"] and run.latest("nothing") is None
+    assert list_runs(tmp_path / "run-a")[0].run_id == "run-a"
+
+    chart = braille_chart([run.series("loss"), runs[1].series("loss")], width=40, height=6)
+    assert len(chart) == 8 and chart[0].lstrip().startswith("3") and all(len(row.split("|", 1)[1]) == 40 for row in chart[:6])
+    dots = "".join(chart[:6])
+    assert sum(0x2800 < ord(c) <= 0x28FF for c in dots) >= 40                   # a connected line, not scattered points
+    first_row, last_row = chart[0].split("|", 1)[1], chart[5].split("|", 1)[1]
+    assert first_row.strip() and first_row.index(first_row.strip()[0]) < 3      # the decaying loss starts top left ...
+    assert last_row.rstrip() and len(last_row.rstrip()) > 30                    # ... and ends bottom right
+    assert braille_chart([([], [])]) == ["(no data)"] and len(braille_chart([([0, 1], [2.0, 2.0])], 10, 3)) == 5
+
+    text = render(tmp_path, width=40, height=6)
+    assert "run-a" in text and "run-b" in text and "* run-c" in text and "latest:" in text and "\nloss\n" in text and "\nacc\n" in text
+    row = next(ln for ln in text.splitlines() if ln.strip().startswith("loss") and "[" not in ln and "|" not in ln)
+    assert "0.2" in row and "-" not in row.split()[1:]
+    assert "no run has it" in render(tmp_path, metrics=["ghost"]) and "run-b" not in render(tmp_path, run_filter="baseline")
+    assert render(tmp_path / "empty") .startswith("no runs")
+
+    out = io.StringIO()
+    watch(tmp_path, out=out, iterations=2, sleep=lambda s: live.log({"loss": 0.5}), width=30, height=4)
+    assert out.getvalue().count("runs:") == 2                                   # redrawn because a file grew
+    out = io.StringIO()
+    live.finish()
+    watch(tmp_path, out=out, iterations=3, sleep=lambda s: None, width=30, height=4)
+    assert out.getvalue().count("runs:") == 1                                   # nothing changed: drawn once
+    assert main([str(tmp_path), "--metric", "loss", "--no-colour"]) == 0
+
+
+def test_tracker_is_a_metrics_sink_and_has_a_command(tmp_path, capsys):
+    from research_b200.cli import main
+    from research_b200.training.metrics import MetricsLogger
+    from research_b200.utils.tracker import Tracker
+
+    t = Tracker("x", dir=tmp_path, run_id="run-x")
+    assert isinstance(t, MetricsLogger)
+    t.log({"loss": 1.5}, 7)
+    t.finish()
+    assert main(["track", str(tmp_path), "--no-colour"]) == 0
+    assert "run-x" in capsys.readouterr().out
