@@ -49,23 +49,37 @@ def _tool(name: str, desc: str, props: dict[str, Any], required: tuple[str, ...]
     return Tool(ToolFunction(name, desc, ToolFunctionParameter(props, required)))
 
 
-def run_code(code: str, namespace: dict[str, Any], max_chars: int = MAX_OUTPUT_CHARS) -> tuple[str, bool]:
+def run_code(code: str, namespace: dict[str, Any], max_chars: int = MAX_OUTPUT_CHARS, timeout_s: float | None = None) -> tuple[str, bool]:
     """Execute ``code`` in ``namespace`` with what it prints captured; the value of a trailing expression is printed as in
     an interactive session. Returns (output, failed).
 
     Several of these run at once in worker threads (concurrent evaluation samples, sub-agents), so the process-wide
-    ``sys.stdout`` is left alone: the namespace gets its own ``print`` that writes to this call's buffer."""
+    ``sys.stdout`` is left alone: the namespace gets its own ``print`` that writes to this call's buffer.
+
+    ``timeout_s`` bounds the run with a per-thread trace function that raises once the time is up (signals only reach
+    the main thread, and this runs in workers). It ends Python-level loops; a single blocking call into C is not cut."""
     import ast
+    import sys
+    import time
 
     buf, failed = io.StringIO(), False
+    deadline = time.monotonic() + timeout_s if timeout_s else None
+
+    def _watch(frame, event, arg):
+        if time.monotonic() > deadline:
+            raise TimeoutError(f"the code ran longer than {timeout_s:g} s and was stopped")
+        return _watch
 
     def _print(*args: Any, **kw: Any) -> None:
         kw.setdefault("file", buf)
         print(*args, **kw)
 
     namespace["print"] = _print
+    old_trace = sys.gettrace()
     try:
         tree = ast.parse(code, "<repl>", "exec")
+        if deadline is not None:
+            sys.settrace(_watch)
         last = tree.body.pop() if tree.body and isinstance(tree.body[-1], ast.Expr) else None
         exec(compile(tree, "<repl>", "exec"), namespace)  # noqa: S102 - the purpose of a REPL tool
         if last is not None:
@@ -76,6 +90,8 @@ def run_code(code: str, namespace: dict[str, Any], max_chars: int = MAX_OUTPUT_C
         failed = True
         buf.write(traceback.format_exc(limit=4))
     finally:
+        if deadline is not None:
+            sys.settrace(old_trace)
         namespace.pop("print", None)
     out = buf.getvalue()
     if len(out) > max_chars:
@@ -93,12 +109,18 @@ class RLMEnvironment:
     namespace: dict[str, Any] = field(default_factory=dict)
     final_answer: str | None = None
     sub_calls: int = 0                          # llm_query + agent calls made so far (a cost signal for evaluations)
+    repl_timeout_s: float | None = 120.0        # one repl call may run this long (sub-model calls inside it count)
+    exec_count: int = 0
+    last_exec_s: float = 0.0
 
     def get_name(self) -> str:
         return "repl"
 
     def get_status_info(self) -> dict[str, str] | None:
-        return {"context": f"{len(self.context):,} chars", "depth": f"{self.depth}/{self.max_depth}"}
+        info = {"context": f"{len(self.context):,} chars", "depth": f"{self.depth}/{self.max_depth}"}
+        if self.exec_count:
+            info["repl"] = f"{self.exec_count} runs, last {self.last_exec_s:.2f}s"
+        return info
 
     def get_system_prompt(self) -> str:
         return SYSTEM_PROMPT.format(n_chars=f"{len(self.context):,}", max_out=f"{MAX_OUTPUT_CHARS:,}")
@@ -159,8 +181,15 @@ class RLMEnvironment:
         self.namespace["agent"] = lambda task, context=None: from_thread(self._agent, str(task), context)
 
     async def run_repl(self, code: str, run_config: RunConfig) -> tuple[str, bool]:
+        import time
+
         self._bind(run_config)
-        return await asyncio.to_thread(run_code, code, self.namespace)
+        t0 = time.monotonic()
+        try:
+            return await asyncio.to_thread(run_code, code, self.namespace, MAX_OUTPUT_CHARS, self.repl_timeout_s)
+        finally:
+            self.exec_count += 1
+            self.last_exec_s = time.monotonic() - t0
 
     # ---- tools
     async def exec_tool(self, tool_call: ToolCall, state: AgentState, run_config: RunConfig) -> ToolResult:
@@ -199,7 +228,8 @@ class RLMEnvironment:
             _LIVE_ENDPOINTS[token] = self.sub_endpoint
             ep = {**self.sub_endpoint.to_dict(), "_token": token}
         return {"type": "rlm", "context": self.context, "namespace": keep, "final_answer": self.final_answer, "depth": self.depth,
-                "max_depth": self.max_depth, "max_agent_turns": self.max_agent_turns, "sub_calls": self.sub_calls, "sub_endpoint": ep}
+                "max_depth": self.max_depth, "max_agent_turns": self.max_agent_turns, "sub_calls": self.sub_calls, "sub_endpoint": ep,
+                "repl_timeout_s": self.repl_timeout_s, "exec_count": self.exec_count, "last_exec_s": self.last_exec_s}
 
     @classmethod
     async def deserialize(cls, data: dict[str, Any]) -> "RLMEnvironment":
@@ -209,7 +239,8 @@ class RLMEnvironment:
             ep = _LIVE_ENDPOINTS.get(d.pop("_token", "")) or Endpoint(**{k: v for k, v in d.items() if k in Endpoint.__dataclass_fields__})
         return cls(context=data.get("context", ""), sub_endpoint=ep, max_depth=data.get("max_depth", 3), max_agent_turns=data.get("max_agent_turns", 15),
                    depth=data.get("depth", 0), namespace=dict(data.get("namespace", {})), final_answer=data.get("final_answer"),
-                   sub_calls=data.get("sub_calls", 0))
+                   sub_calls=data.get("sub_calls", 0), repl_timeout_s=data.get("repl_timeout_s", 120.0), exec_count=data.get("exec_count", 0),
+                   last_exec_s=data.get("last_exec_s", 0.0))
 
 
 _BLOCK = re.compile(r"```(?:repl|python|py)\n(.*?)```", re.DOTALL)

@@ -705,3 +705,36 @@ def test_conversation_moves_between_providers():
     system, msgs = messages_to_anthropic(tuple(to_claude))
     flat = json.dumps(msgs)
     assert system == "" and "<thinking>simple sum</thinking>" in flat and '"type": "thinking"' not in flat and [m["role"] for m in msgs] == ["user", "assistant", "user"]
+
+
+def test_repl_time_limit_stops_loops_in_worker_threads():
+    """A loop that would not end is stopped by the per-thread time limit (the REPL runs in worker threads, where signals
+    do not arrive), the namespace keeps what ran before, and the environment counts and times its runs."""
+    import asyncio
+    import threading
+
+    from research_b200.agents.dtypes import RunConfig
+    from research_b200.agents.environments.rlm import RLMEnvironment, run_code
+
+    ns: dict = {}
+    got = {}
+    t = threading.Thread(target=lambda: got.update(r=run_code("n = 0\nwhile True:\n    n += 1", ns, timeout_s=0.2)))
+    t.start()
+    t.join(20)
+    assert not t.is_alive()
+    out, failed = got["r"]
+    assert failed and "TimeoutError" in out and "0.2 s" in out and ns["n"] > 0
+    assert run_code("sum(range(10))", ns, timeout_s=5.0) == ("45\n", False)
+    assert threading.current_thread() is threading.main_thread() and __import__("sys").gettrace() is None
+
+    env = RLMEnvironment(context="abc", repl_timeout_s=0.2)
+
+    async def go():
+        out, failed = await env.run_repl("while True:\n    pass", RunConfig())
+        assert failed and "TimeoutError" in out
+        out, failed = await env.run_repl("len(context)", RunConfig())
+        assert (out, failed) == ("3\n", False)
+        again = await RLMEnvironment.deserialize(await env.serialize())
+        assert again.exec_count == 2 and again.repl_timeout_s == 0.2
+    asyncio.run(go())
+    assert "2 runs" in env.get_status_info()["repl"]
