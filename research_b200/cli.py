@@ -205,8 +205,23 @@ async def _chat(args) -> int:
     if context:
         system_prompt = system_prompt + "\n\n" + "\n\n".join(context)
     trajectory = session_id = None
+    if args.prompt == "-":                                   # the question comes on standard input: echo ... | chat -p -
+        args.prompt = sys.stdin.read().strip()
+        if not args.prompt:
+            print("nothing on standard input", file=sys.stderr)
+            return 2
     if getattr(args, "continue_session", False) and not args.session and store is not None:
         args.session = await _latest(store) or ""
+    if getattr(args, "branch", None) is not None:
+        if not args.session or store is None:
+            print("--branch needs a stored session (--session ID or --continue)", file=sys.stderr)
+            return 2
+        _, stored = await store.get(args.session)
+        if not 0 < args.branch <= len(stored):
+            print(f"--branch: keep between 1 and {len(stored)} messages", file=sys.stderr)
+            return 2
+        args.session = await store.branch(args.session, args.branch, reason="command_line")
+        print(f"branched into session {args.session}", file=sys.stderr)
     if args.session and store is not None:
         state = await resume_session(args.session, store, ep, type(preset.environment(args.cwd)), preset.max_turns)
         env, trajectory, session_id = state.environment, state.actor.trajectory, state.session_id
@@ -412,6 +427,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--frontend", default="auto", choices=["auto", "plain", "json", "headless", "ansi"], help="terminal front end (headless: whole turns as JSON lines, both ways)")
     p.add_argument("-c", "--continue", dest="continue_session", action="store_true", help="resume the most recent session")
     p.add_argument("--no-session", action="store_true", help="do not store this conversation")
+    p.add_argument("--branch", type=int, default=None, metavar="N", help="with --session / --continue: fork after the first N messages and continue in the fork")
     p.add_argument("--system-prompt", default="", help="text, or a file holding it, that replaces the preset's system prompt")
     p.add_argument("--full-prompt", action="store_true", help="assemble the system prompt from the preset, the environment's tools, project context files, time and cwd")
     p.add_argument("--context", action="append", help="extra text appended to the system prompt (repeatable)")

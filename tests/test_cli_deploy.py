@@ -169,6 +169,25 @@ def test_session_doctor_and_chat_flags(tmp_path, capsys):
     assert cli.main(["chat", "--provider", "cli-mock", "--store", str(tmp_path / "s3"), "-p", "hi", "--no-session"]) == 0
     assert not (tmp_path / "s3").exists() or not list((tmp_path / "s3").iterdir())
 
+    # the question on standard input, and a fork of the stored conversation from the command line
+    import io
+    import sys
+
+    monkey_stdin, sys.stdin = sys.stdin, io.StringIO("piped question\n")
+    try:
+        assert cli.main(["chat", "--provider", "cli-mock", "--store", store2, "-p", "-", "--continue", "--branch", "2"]) == 0
+        sys.stdin = io.StringIO("")
+        assert cli.main(["chat", "--provider", "cli-mock", "--store", store2, "-p", "-", "--no-session"]) == 2
+    finally:
+        sys.stdin = monkey_stdin
+    sessions = asyncio.run(FileSessionStore(store2).list())
+    assert len(sessions) == 2
+    fork = next(x for x in sessions if x.parent_id)
+    assert fork.branch_point == 2 and fork.tags.get("branch_reason") == "command_line"
+    _, fork_msgs = asyncio.run(FileSessionStore(store2).get(fork.session_id))
+    assert any(m.role == "user" and m.text() == "piped question" for m in fork_msgs)
+    assert cli.main(["chat", "--provider", "cli-mock", "--store", store2, "-p", "x", "--continue", "--branch", "99"]) == 2
+
 
 def test_bootstrap_model_access_and_endpoint(tmp_path):
     from research_b200.deploy import ServerInfo, check_model_access, generate_bootstrap_command, server_info_to_endpoint
